@@ -1,0 +1,241 @@
+"""Each CUDA kernel against the plain PyTorch FP32 restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+from uniserve_v1_b200.ops import functional as F
+from uniserve_v1_b200.ops import native as N
+from uniserve_v1_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+def rnd(*shape, scale=1.0, dtype=BF, seed=None):
+    g = torch.Generator(device=DEV)
+    g.manual_seed(seed if seed is not None else (hash(shape) & 0xFFFF))
+    return (torch.randn(*shape, generator=g, device=DEV) * scale).to(dtype)
+
+
+def close(a, b, atol, rtol):
+    torch.testing.assert_close(a.float(), b.float(), atol=atol, rtol=rtol)
+
+
+def teardown_function(_):
+    torch.cuda.synchronize()
+    N.raise_on_device_error()
+
+
+@pytest.mark.parametrize("T,H", [(1, 256), (64, 2048), (7, 5376)])
+def test_rmsnorm(T, H):
+    x, w = rnd(T, H), rnd(H)
+    close(F.rmsnorm(x, w, 1e-6), R.rmsnorm(x, w, 1e-6), 2e-2, 2e-2)
+
+
+def test_add_rmsnorm():
+    x, w = rnd(33, 2048), rnd(2048)
+    y0, r0 = F.add_rmsnorm(x, None, w, 1e-6)
+    ye, re_ = R.add_rmsnorm(x, None, w, 1e-6)
+    close(y0, ye, 2e-2, 2e-2)
+    close(r0, re_, 1e-6, 1e-6)
+    x2 = rnd(33, 2048, seed=5)
+    y1, r1 = F.add_rmsnorm(x2, r0, w, 1e-6)
+    ye1, re1 = R.add_rmsnorm(x2, re_, w, 1e-6)
+    close(y1, ye1, 2e-2, 2e-2)
+    close(r1, re1, 1e-5, 1e-5)
+
+
+def test_modulated_rmsnorm_and_gated_residual():
+    T, H = 50, 512
+    x, u = rnd(T, H), rnd(T, H, seed=2)
+    table = rnd(9 * 6, H, dtype=torch.float32, seed=3) * 0.1
+    idx = torch.randint(0, 9, (T,), device=DEV, dtype=torch.int32)
+    close(F.modulated_rmsnorm(x, None, table, idx, 6, 0, 1, 1e-6),
+          R.modulated_rmsnorm(x, None, table, idx, 6, 0, 1, 1e-6), 2e-2, 2e-2)
+    h = x.clone()
+    F.gated_residual_(h, u, table, idx, 6, 2)
+    close(h, R.gated_residual(x, u, table, idx, 6, 2), 2e-2, 2e-2)
+
+
+def test_layer_norm():
+    x, w, b = rnd(19, 1152), rnd(1152), rnd(1152, seed=4)
+    close(F.layer_norm(x, w, b, 1e-5), R.layer_norm(x, w, b, 1e-5), 3e-2, 2e-2)
+
+
+@pytest.mark.parametrize("rows,M,K", [(1, 128, 64), (16, 256, 128), (5, 384, 2048), (64, 5120, 2048),
+                                       (200, 256, 512), (300, 1024, 768), (64, 1000, 264)])
+def test_linear_bf16(rows, M, K):
+    x, w = rnd(rows, K), rnd(M, K, scale=0.05)
+    y = F.linear(x, w)
+    ref = R.linear(x, w)
+    close(y, ref, 2e-2 * math.sqrt(K / 64), 2e-2)
+
+
+def test_linear_fp32_out_bias():
+    x, w, b = rnd(40, 512), rnd(300, 512, scale=0.05), rnd(300, dtype=torch.float32)
+    y = F.linear(x, w, bias=b, out_dtype=torch.float32)
+    ref = (x.float() @ w.float().t()) + b
+    close(y, ref, 5e-3, 5e-3)
+
+
+@pytest.mark.parametrize("rows", [3, 64, 150])
+def test_linear_gated(rows):
+    x, w = rnd(rows, 1024), rnd(2 * 384, 1024, scale=0.05)
+    close(F.linear_gated(x, w), R.linear_gated(x, w), 3e-2, 3e-2)
+    close(F.linear_gated(x, w, stepwise=True), R.linear_gated(x, w, stepwise=True), 3e-2, 3e-2)
+
+
+def test_qk_norm_rope_kv():
+    T, Hq, Hkv, D, page = 37, 8, 2, 128, 16
+    qkv = rnd(T, (Hq + 2 * Hkv) * D)
+    qw, kw = rnd(D), rnd(D, seed=9)
+    pos = torch.randint(0, 5000, (T,), device=DEV, dtype=torch.int32)
+    inv = R.rope_inv_freq(D, 1e6, DEV)
+    slots = torch.randperm(8 * page, device=DEV)[:T].to(torch.int32)
+    slots[3] = -1
+    kc = torch.zeros(8, page, Hkv, D, dtype=BF, device=DEV)
+    vc = torch.zeros_like(kc)
+    ref = qkv.clone().cpu()
+    kc_r, vc_r = kc.clone().cpu(), vc.clone().cpu()
+    F.qk_norm_rope_kv_(ref, qw.cpu(), kw.cpu(), pos.cpu(), inv.cpu(), slots.cpu(), kc_r, vc_r,
+                       Hq, Hkv, D)
+    F.qk_norm_rope_kv_(qkv, qw, kw, pos, inv, slots, kc, vc, Hq, Hkv, D)
+    close(qkv.cpu(), ref, 3e-2, 3e-2)
+    close(kc.cpu(), kc_r, 3e-2, 3e-2)
+    close(vc.cpu(), vc_r, 0, 0)
+
+
+def test_qk_norm_rope3():
+    T, H, D, Fq = 45, 4, 128, 16
+    q, k = rnd(T, H * D), rnd(T, H * D, seed=3)
+    qw, kw = rnd(D), rnd(D, seed=8)
+    coords = torch.rand(3, T, device=DEV) * 40
+    inv = R.rope_inv_freq(2 * Fq, 10000.0, DEV)
+    qr, kr = R.qk_norm_rope3(q.view(T, H, D), k.view(T, H, D), qw, kw, coords, inv, Fq, 1e-6)
+    F.qk_norm_rope3_(q, k, qw, kw, coords, inv, H, H, D, Fq)
+    close(q.view(T, H, D), qr, 3e-2, 3e-2)
+    close(k.view(T, H, D), kr, 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,splits", [(32, 4, 128, 1), (32, 4, 128, 4), (4, 2, 64, 2),
+                                              (16, 1, 128, 3)])
+def test_paged_decode_attention(Hq, Hkv, D, splits):
+    B, page, pages = 5, 16, 200
+    lens = torch.tensor([1, 17, 300, 64, 511], dtype=torch.int32, device=DEV)
+    q = rnd(B, Hq, D)
+    kc, vc = rnd(pages, page, Hkv, D, seed=1), rnd(pages, page, Hkv, D, seed=2)
+    pt = torch.randperm(pages - 1, device=DEV)[:B * 32].view(B, 32).to(torch.int32) + 1
+    out = F.paged_decode_attention(q, kc, vc, pt, lens, 1 / math.sqrt(D), splits=splits)
+    ref = R.paged_decode_attention(q, kc, vc, pt, lens, 1 / math.sqrt(D))
+    close(out, ref, 2e-2, 2e-2)
+
+
+def test_topk_softmax():
+    T, E, k = 70, 128, 8
+    logits = rnd(T, E, dtype=torch.float32)
+    ids, w = F.topk_softmax(logits, k, True)
+    ids_r, w_r = R.topk_softmax(logits, k, True)
+    assert torch.equal(ids.cpu(), ids_r.cpu())
+    close(w, w_r, 1e-5, 1e-4)
+    live = torch.tensor([10], dtype=torch.int32, device=DEV)
+    ids2, w2 = F.topk_softmax(logits, k, True, live=live)
+    assert (ids2[10:] == -1).all() and (w2[10:] == 0).all()
+    assert torch.equal(ids2[:10].cpu(), ids_r[:10].cpu())
+
+
+@pytest.mark.parametrize("T,E,k,H,I", [(64, 128, 8, 2048, 768), (5, 8, 2, 256, 128),
+                                        (300, 16, 4, 512, 256)])
+def test_moe_experts(T, E, k, H, I):
+    x = rnd(T, H)
+    w13, w2 = rnd(E, 2 * I, H, scale=0.03), rnd(E, H, I, scale=0.03, seed=4)
+    logits = rnd(T, E, dtype=torch.float32, seed=6)
+    ids, w = F.topk_softmax(logits, k, True)
+    out = F.moe_experts(x, ids, w, w13, w2)
+    ref = R.moe_experts(x, ids, w, w13, w2)
+    close(out, ref, 3e-2, 3e-2)
+    # expert-parallel window: only experts [E/2, E) are local
+    out2 = F.moe_experts(x, ids, w, w13[E // 2:].contiguous(), w2[E // 2:].contiguous(),
+                         e_lo=E // 2)
+    ref2 = R.moe_experts(x, ids, w, w13[E // 2:], w2[E // 2:], e_lo=E // 2)
+    close(out2, ref2, 3e-2, 3e-2)
+
+
+def test_argmax_and_logprob_stats():
+    logits = rnd(9, 151936, dtype=torch.float32)
+    am = F.argmax(logits)
+    assert torch.equal(am.cpu(), R.argmax(logits).cpu())
+    lse, lp, rank = F.logprob_stats(logits, am)
+    lse_r, lp_r, rank_r = R.logprob_stats(logits, am)
+    close(lse, lse_r, 1e-3, 1e-4)
+    close(lp, lp_r, 1e-3, 1e-4)
+    assert torch.equal(rank.cpu(), rank_r.cpu())
+
+
+def test_sample_from_logits_matches_reference_rule():
+    B, V = 12, 4096
+    logits = rnd(B, V, dtype=torch.float32, scale=3.0)
+    top_k = torch.tensor([0, 1, 20, 50, 0, 0, 20, 5, 0, 100, 3, 0], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([1, 1, 1, .9, .5, .95, .95, 1, .1, .8, 1, 1], dtype=torch.float32, device=DEV)
+    min_p = torch.tensor([0, 0, 0, 0, 0, 0, .05, 0, 0, 0, 0, .2], dtype=torch.float32, device=DEV)
+    seeds = torch.arange(B, dtype=torch.int64, device=DEV) + 1234
+    pos = torch.arange(B, dtype=torch.int64, device=DEV) * 7 + 3
+    out = F.sample_from_logits(logits, top_k, top_p, min_p, seeds, pos)
+    ref = R.sample_from_logits(logits.cpu(), top_k.cpu(), top_p.cpu(), min_p.cpu(), seeds.cpu(),
+                               pos.cpu())
+    assert torch.equal(out.cpu(), ref), (out.cpu(), ref)
+    # same (seed, position, distribution) -> same token, whatever the batch
+    out1 = F.sample_from_logits(logits[5:6].contiguous(), top_k[5:6], top_p[5:6], min_p[5:6],
+                                seeds[5:6], pos[5:6])
+    assert int(out1[0]) == int(out[5])
+
+
+def test_sampler_distribution():
+    V, n = 64, 4000
+    base = rnd(1, V, dtype=torch.float32, scale=1.5)
+    logits = base.expand(n, V).contiguous()
+    seeds = torch.full((n,), 77, dtype=torch.int64, device=DEV)
+    pos = torch.arange(n, dtype=torch.int64, device=DEV)
+    out = F.sample_from_logits(logits, None, None, None, seeds, pos)
+    freq = torch.bincount(out.long(), minlength=V).float() / n
+    p = base[0].softmax(-1)
+    assert (freq - p).abs().max() < 0.03
+
+
+def test_logits_shape():
+    B, V = 4, 1000
+    logits = rnd(B, V, dtype=torch.float32)
+    counts = torch.randint(0, 3, (B, V), device=DEV).to(torch.int16)
+    pm = (torch.rand(B, V, device=DEV) < 0.1).to(torch.uint8)
+    ban = (torch.rand(B, V, device=DEV) < 0.05).to(torch.uint8)
+    rep = torch.tensor([1.0, 1.3, 1.1, 1.0], device=DEV)
+    fr = torch.tensor([0.0, 0.5, 0.0, 0.2], device=DEV)
+    pr = torch.tensor([0.3, 0.0, 0.0, 0.2], device=DEV)
+    temp = torch.tensor([1.0, 0.7, 0.0, 2.0], device=DEV)
+    bo = torch.tensor([0, 2, 2, 3, 3], dtype=torch.int32, device=DEV)
+    bi = torch.tensor([5, 9, 700], dtype=torch.int32, device=DEV)
+    bv = torch.tensor([2.0, -1.0, 5.0], device=DEV)
+    ref = R.logits_shape(logits, ban, [[(5, 2.0), (9, -1.0)], [], [(700, 5.0)], []], counts, pm,
+                         rep, fr, pr, temp)
+    out = F.logits_shape_(logits.clone(), ban, (bo, bi, bv), counts, pm, rep, fr, pr, temp)
+    close(out, ref, 1e-5, 1e-5)
+
+
+def test_embedding_gather_advance():
+    table = rnd(1000, 256)
+    ids = torch.randint(0, 1000, (33,), device=DEV, dtype=torch.int32)
+    close(F.embedding(ids, table), table[ids.long()], 0, 0)
+    out = F.embedding(ids, table[100:600].contiguous(), 100, 600)
+    ok = (ids >= 100) & (ids < 600)
+    close(out[ok], table[ids[ok].long()], 0, 0)
+    assert (out[~ok] == 0).all()
+    idx = torch.tensor([3, -1, 7], dtype=torch.int32, device=DEV)
+    g = F.gather_rows(table, idx)
+    close(g[0], table[3], 0, 0)
+    assert (g[1] == 0).all()
+
+
+def test_bounded_wait_reports_timeout_status():
+    """The status word starts clean and a read clears it."""
+    assert N.read_status() == 0

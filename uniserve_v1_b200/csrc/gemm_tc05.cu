@@ -1,0 +1,319 @@
+// Weight-stationary tcgen05 GEMM family:  out[row, m] = sum_k X[row, k] * W[g, m, k].
+//
+// The weight matrix is the A operand (128 output features per CTA sit in the
+// 128 TMEM lanes) and the activation rows are the B operand, so the UMMA N
+// extent is the number of rows in the tile: 16 for a decode step, up to 256
+// for prefill or the video transformer.  One kernel therefore serves skinny
+// memory-bound shapes and large compute-bound ones, dense or grouped (one
+// group per expert, tiles listed by the MoE sort).
+//
+// Warp roles: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2-5 = epilogue (one TMEM lane quarter each).
+//
+// Epilogues: plain store (bf16 or fp32, optional bias / per-row scale / output
+// row map) and the dual-accumulator gated activation out = first * act(second)
+// used by the experts' FC1 (first = up rows, second = gate rows of the stacked
+// weight) and the video transformer's value-first SwiGLU.
+#include "include/us_common.cuh"
+#include "include/us_tc05.cuh"
+#include "include/us_tmap.h"
+
+namespace {
+
+struct GemmArgs {
+  int M;            // output features per group
+  int K;
+  int rows;         // activation rows (dense)
+  int dual_offset;  // row offset of the second weight tile (dual epilogue)
+  int stages;
+  int act;          // dual: 0 = silu fused rounding, 1 = silu stepwise rounding, 2 = gelu-tanh
+  int out_dtype;    // 0 = bf16, 1 = fp32
+  int bias_dtype;   // 0 = bf16, 1 = fp32
+  long long ldo;
+  void* out;
+  const void* bias;        // [G, M] or null
+  const float* row_scale;  // [rows] or null
+  const int* out_row_map;  // [rows] destination row, <0 skips; null = identity
+  const int* tile_group;   // grouped: group of each row tile
+  const int* tile_row0;    // grouped: first activation row of each tile
+  const int* tile_rows;    // grouped: valid rows of each tile
+  const int* num_tiles;    // grouped: device word, number of row tiles
+  unsigned int* status;
+};
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;
+constexpr int kATile = kBlockM * kBlockK * 2;  // 16 KiB
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+
+template <int BN>
+constexpr int tmem_cols(bool dual) {
+  int need = dual ? 2 * BN : BN;
+  int c = 32;
+  while (c < need) c <<= 1;
+  return c;
+}
+
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(192)
+gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const GemmArgs args) {
+  constexpr int kBTile = BN * kBlockK * 2;
+  constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
+  constexpr uint32_t kCols = tmem_cols<BN>(DUAL);
+  constexpr uint32_t kIdesc = tc::make_idesc(kBlockM, BN, tc::kFmtBF16, tc::kFmtBF16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tile = blockIdx.x;
+  const int n_tile = blockIdx.y;
+
+  int group = 0, row0 = n_tile * BN, nrows;
+  if (args.num_tiles != nullptr) {
+    if (n_tile >= *args.num_tiles) return;
+    group = args.tile_group[n_tile];
+    row0 = args.tile_row0[n_tile];
+    nrows = args.tile_rows[n_tile];
+  } else {
+    nrows = min(BN, args.rows - row0);
+  }
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stages = args.stages;
+  uint64_t* full_bar = (uint64_t*)(smem + (size_t)stages * kStageBytes);
+  uint64_t* empty_bar = full_bar + stages;
+  uint64_t* acc_bar = empty_bar + stages;
+  uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      tc::mbar_init(&full_bar[s], 1);
+      tc::mbar_init(&empty_bar[s], 1);
+    }
+    tc::mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, kCols);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_k = (args.K + kBlockK - 1) / kBlockK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tc::tma_prefetch_desc(&tmA);
+      tc::tma_prefetch_desc(&tmB);
+      for (int kb = 0; kb < num_k; ++kb) {
+        const int s = kb % stages;
+        const uint32_t ph = (uint32_t)(kb / stages) & 1u;
+        if (!tc::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
+          us_dev_fail(args.status, US_DEV_TIMEOUT_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        uint8_t* st = smem + (size_t)s * kStageBytes;
+        tc::mbar_expect_tx(&full_bar[s], kStageBytes);
+        tc::tma_load_3d(st, &tmA, &full_bar[s], kb * kBlockK, m_tile * kBlockM, group);
+        if (DUAL)
+          tc::tma_load_3d(st + kATile, &tmA, &full_bar[s], kb * kBlockK,
+                          args.dual_offset + m_tile * kBlockM, group);
+        tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmB, &full_bar[s], kb * kBlockK, row0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < num_k; ++kb) {
+        const int s = kb % stages;
+        const uint32_t ph = (uint32_t)(kb / stages) & 1u;
+        if (!tc::mbar_wait(&full_bar[s], ph, abort_flag)) {
+          us_dev_fail(args.status, US_DEV_TIMEOUT_FULL);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc::tc_fence_after_sync();
+        const uint32_t a_addr = tc::smem_u32(smem + (size_t)s * kStageBytes);
+        const uint32_t b_addr = a_addr + kATile * (DUAL ? 2 : 1);
+        const uint64_t adesc = tc::smem_desc_kmajor_sw128(a_addr);
+        const uint64_t bdesc = tc::smem_desc_kmajor_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < kBlockK / 16; ++k) {
+          const uint32_t acc = (kb | k) != 0;
+          // 16 bf16 along K = 32 bytes = 2 descriptor address units
+          tc::umma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+          if (DUAL) {
+            const uint64_t a2desc = tc::smem_desc_kmajor_sw128(a_addr + kATile);
+            tc::umma_f16(tmem_base + BN, a2desc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+          }
+        }
+        tc::umma_commit(&empty_bar[s]);
+      }
+      if (ok) tc::umma_commit(acc_bar);
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int m = m_tile * kBlockM + q * 32 + lane;
+    const bool m_ok = m < args.M;
+    if (tc::mbar_wait(acc_bar, 0, abort_flag)) {
+      tc::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+      float bias = 0.f;
+      if (args.bias != nullptr && m_ok) {
+        const size_t bi = (size_t)group * args.M + m;
+        bias = args.bias_dtype == 0 ? us::bf2f(((const __nv_bfloat16*)args.bias)[bi])
+                                    : ((const float*)args.bias)[bi];
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        if (c >= nrows) break;  // warp-uniform
+        uint32_t v[16], g[16];
+        tc::tmem_ld16(taddr + c, v);
+        if (DUAL) tc::tmem_ld16(taddr + BN + c, g);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int r = c + j;
+          if (r < nrows && m_ok) {
+            float val = __uint_as_float(v[j]);
+            if (DUAL) {
+              const float gate = __uint_as_float(g[j]);
+              if (args.act == 0) {
+                val = val * silu_f(gate);
+              } else if (args.act == 1) {
+                const float sg = us::bf2f(us::f2bf(silu_f(us::bf2f(us::f2bf(gate)))));
+                val = us::bf2f(us::f2bf(val)) * sg;
+              } else {
+                val = val * gelu_tanh_f(gate);
+              }
+            }
+            val += bias;
+            int orow = row0 + r;
+            if (args.row_scale != nullptr) val *= args.row_scale[orow];
+            if (args.out_row_map != nullptr) orow = args.out_row_map[orow];
+            if (orow >= 0) {
+              const size_t o = (size_t)orow * args.ldo + m;
+              if (args.out_dtype == 0)
+                ((__nv_bfloat16*)args.out)[o] = us::f2bf(val);
+              else
+                ((float*)args.out)[o] = val;
+            }
+          }
+        }
+      }
+    } else {
+      us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
+    }
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::tmem_dealloc(tmem_base, kCols);
+  }
+}
+
+template <int BN, bool DUAL>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs a, int m_tiles, int n_tiles,
+           cudaStream_t stream) {
+  constexpr int kBTile = BN * kBlockK * 2;
+  constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
+  const int num_k = (a.K + kBlockK - 1) / kBlockK;
+  // Small row tiles are memory-bound: keep two CTAs per SM resident.
+  const int budget = (BN <= 64 && !DUAL) ? 100 * 1024 : (BN <= 32 ? 104 * 1024 : 200 * 1024);
+  int stages = budget / kStageBytes;
+  if (stages > 8) stages = 8;
+  if (stages > num_k) stages = num_k;
+  if (stages < 1) stages = 1;
+  a.stages = stages;
+  const size_t smem = (size_t)stages * kStageBytes + (2 * stages + 1) * 8 + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    US_CUDA_CHECK(cudaFuncSetAttribute(gemm_wx_kernel<BN, DUAL>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured = true;
+  }
+  dim3 grid(m_tiles, n_tiles);
+  gemm_wx_kernel<BN, DUAL><<<grid, 192, smem, stream>>>(tmA, tmB, a);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}
+
+}  // namespace
+
+// W: [G, w_rows, K] bf16 (ld = ldw elements between rows, groups contiguous),
+// X: [x_rows, K] bf16 with ldx.  Dense when num_tiles == nullptr (then
+// n_tiles = ceil(rows / block_n)); grouped otherwise with `max_tiles` CTAs
+// along the row-tile axis.
+US_API int us_gemm_wx(const void* W, const void* X, void* out, int G, int w_rows, int M, int K,
+                      int x_rows, long long ldw, long long ldx, long long ldo, int dual,
+                      int dual_offset, int act, int out_dtype, const void* bias, int bias_dtype,
+                      const float* row_scale, const int* out_row_map, const int* tile_group,
+                      const int* tile_row0, const int* tile_rows, const int* num_tiles,
+                      int max_tiles, int block_n, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  US_REQUIRE(W && X && out && G >= 1 && M >= 1 && K >= 8 && (K % 8) == 0);
+  US_REQUIRE((ldw % 8) == 0 && (ldx % 8) == 0);
+  US_REQUIRE(((uintptr_t)W % 16) == 0 && ((uintptr_t)X % 16) == 0);
+  US_REQUIRE(x_rows >= 1);
+  if (num_tiles) US_REQUIRE(tile_group && tile_row0 && tile_rows && max_tiles >= 1);
+
+  CUtensorMap tmA, tmB;
+  int rc = us_tmap_3d(&tmA, W, US_TMAP_BF16, (uint64_t)G, (uint64_t)w_rows, (uint64_t)K,
+                      (uint64_t)ldw, (uint64_t)w_rows * (uint64_t)ldw, kBlockM, kBlockK,
+                      US_SWZ_128);
+  if (rc) return rc;
+  rc = us_tmap_2d(&tmB, X, US_TMAP_BF16, (uint64_t)x_rows, (uint64_t)K, (uint64_t)ldx,
+                  (uint32_t)block_n, kBlockK, US_SWZ_128);
+  if (rc) return rc;
+
+  GemmArgs a;
+  a.M = M;
+  a.K = K;
+  a.rows = x_rows;
+  a.dual_offset = dual_offset;
+  a.stages = 0;
+  a.act = act;
+  a.out_dtype = out_dtype;
+  a.bias_dtype = bias_dtype;
+  a.ldo = ldo;
+  a.out = out;
+  a.bias = bias;
+  a.row_scale = row_scale;
+  a.out_row_map = out_row_map;
+  a.tile_group = tile_group;
+  a.tile_row0 = tile_row0;
+  a.tile_rows = tile_rows;
+  a.num_tiles = num_tiles;
+  a.status = us_status_ptr();
+
+  const int m_tiles = (M + kBlockM - 1) / kBlockM;
+  const int n_tiles = num_tiles ? max_tiles : (x_rows + block_n - 1) / block_n;
+  US_REQUIRE(n_tiles <= 65535);
+
+#define US_GEMM_CASE(BN)                                                              \
+  case BN:                                                                            \
+    return dual ? launch<BN, true>(tmA, tmB, a, m_tiles, n_tiles, stream)             \
+                : launch<BN, false>(tmA, tmB, a, m_tiles, n_tiles, stream);
+  switch (block_n) {
+    US_GEMM_CASE(16)
+    US_GEMM_CASE(32)
+    US_GEMM_CASE(64)
+    US_GEMM_CASE(128)
+    US_GEMM_CASE(256)
+    default:
+      return US_ERR_ARG;
+  }
+#undef US_GEMM_CASE
+}

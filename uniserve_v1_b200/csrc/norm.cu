@@ -1,0 +1,238 @@
+// Normalisation and residual kernels (bandwidth-bound, one CTA per row, 16-byte
+// accesses).  Reductions run in FP32 and every output is rounded once.
+//
+//   rmsnorm            y = x * rsqrt(mean(x^2) + eps) * w
+//   add_rmsnorm        r += x (FP32 residual stream);  y = rmsnorm(r) * w
+//   modulated_rmsnorm  y = rmsnorm(x) [* w] * (1 + scale[idx]) + shift[idx]   (AdaLN)
+//   gated_residual     h = h + gate[idx] * u
+//   layer_norm         y = (x - mean) * rsqrt(var + eps) * w + b
+//
+// Reference behaviour: crates/ops/kernels/{rms_norm,add_rms_norm,modulated_rms_norm,
+// gated_residual,layer_norm}/triton (reference project paths).
+#include "include/us_common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+               __nv_bfloat16* __restrict__ y, int H, long long ldx, long long ldy, float eps) {
+  __shared__ float scratch[33];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * ldx;
+  __nv_bfloat16* yr = y + row * ldy;
+  const int nvec = H >> 3;
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    us::Pack16 p;
+    p.u = *reinterpret_cast<const uint4*>(xr + v * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float f = us::bf2f(p.b[i]);
+      ss += f * f;
+    }
+  }
+  ss = us::block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    us::Pack16 p, q, o;
+    p.u = *reinterpret_cast<const uint4*>(xr + v * 8);
+    q.u = *reinterpret_cast<const uint4*>(w + v * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.b[i] = us::f2bf(us::bf2f(p.b[i]) * inv * us::bf2f(q.b[i]));
+    *reinterpret_cast<uint4*>(yr + v * 8) = o.u;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ residual,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int H,
+                   float eps, int first) {
+  __shared__ float scratch[33];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * H;
+  float* rr = residual + row * H;
+  __nv_bfloat16* yr = y + row * H;
+  const int nvec = H >> 3;
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    us::Pack16 p;
+    p.u = *reinterpret_cast<const uint4*>(xr + v * 8);
+    float4 r0, r1;
+    if (first) {
+      r0 = make_float4(0.f, 0.f, 0.f, 0.f);
+      r1 = r0;
+    } else {
+      r0 = *reinterpret_cast<const float4*>(rr + v * 8);
+      r1 = *reinterpret_cast<const float4*>(rr + v * 8 + 4);
+    }
+    r0.x += us::bf2f(p.b[0]); r0.y += us::bf2f(p.b[1]);
+    r0.z += us::bf2f(p.b[2]); r0.w += us::bf2f(p.b[3]);
+    r1.x += us::bf2f(p.b[4]); r1.y += us::bf2f(p.b[5]);
+    r1.z += us::bf2f(p.b[6]); r1.w += us::bf2f(p.b[7]);
+    *reinterpret_cast<float4*>(rr + v * 8) = r0;
+    *reinterpret_cast<float4*>(rr + v * 8 + 4) = r1;
+    ss += r0.x * r0.x + r0.y * r0.y + r0.z * r0.z + r0.w * r0.w;
+    ss += r1.x * r1.x + r1.y * r1.y + r1.z * r1.z + r1.w * r1.w;
+  }
+  ss = us::block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    // Each thread re-reads the residual values it wrote itself.
+    const float4 r0 = *reinterpret_cast<const float4*>(rr + v * 8);
+    const float4 r1 = *reinterpret_cast<const float4*>(rr + v * 8 + 4);
+    us::Pack16 q, o;
+    q.u = *reinterpret_cast<const uint4*>(w + v * 8);
+    o.b[0] = us::f2bf(r0.x * inv * us::bf2f(q.b[0]));
+    o.b[1] = us::f2bf(r0.y * inv * us::bf2f(q.b[1]));
+    o.b[2] = us::f2bf(r0.z * inv * us::bf2f(q.b[2]));
+    o.b[3] = us::f2bf(r0.w * inv * us::bf2f(q.b[3]));
+    o.b[4] = us::f2bf(r1.x * inv * us::bf2f(q.b[4]));
+    o.b[5] = us::f2bf(r1.y * inv * us::bf2f(q.b[5]));
+    o.b[6] = us::f2bf(r1.z * inv * us::bf2f(q.b[6]));
+    o.b[7] = us::f2bf(r1.w * inv * us::bf2f(q.b[7]));
+    *reinterpret_cast<uint4*>(yr + v * 8) = o.u;
+  }
+}
+
+// table: [table_rows, H] FP32 vectors; shift row = idx[row] * stride + shift_slot, etc.
+__global__ void __launch_bounds__(kThreads)
+modulated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                         const float* __restrict__ table, const int* __restrict__ idx,
+                         int vectors_per_row, int shift_slot, int scale_slot,
+                         __nv_bfloat16* __restrict__ y, int H, float eps) {
+  __shared__ float scratch[33];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * H;
+  __nv_bfloat16* yr = y + row * H;
+  const long long trow = (long long)idx[row] * vectors_per_row;
+  const float* shift = table + (trow + shift_slot) * H;
+  const float* scale = table + (trow + scale_slot) * H;
+  const int nvec = H >> 3;
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    us::Pack16 p;
+    p.u = *reinterpret_cast<const uint4*>(xr + v * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float f = us::bf2f(p.b[i]);
+      ss += f * f;
+    }
+  }
+  ss = us::block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    us::Pack16 p, q, o;
+    p.u = *reinterpret_cast<const uint4*>(xr + v * 8);
+    if (w) q.u = *reinterpret_cast<const uint4*>(w + v * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float n = us::bf2f(p.b[i]) * inv;
+      if (w) n *= us::bf2f(q.b[i]);
+      o.b[i] = us::f2bf(n * (1.f + scale[v * 8 + i]) + shift[v * 8 + i]);
+    }
+    *reinterpret_cast<uint4*>(yr + v * 8) = o.u;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+gated_residual_kernel(__nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ u,
+                      const float* __restrict__ table, const int* __restrict__ idx,
+                      int vectors_per_row, int gate_slot, int H) {
+  const long long row = blockIdx.x;
+  __nv_bfloat16* hr = h + row * H;
+  const __nv_bfloat16* ur = u + row * H;
+  const float* gate = table + ((long long)idx[row] * vectors_per_row + gate_slot) * H;
+  const int nvec = H >> 3;
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    us::Pack16 p, q, o;
+    p.u = *reinterpret_cast<const uint4*>(hr + v * 8);
+    q.u = *reinterpret_cast<const uint4*>(ur + v * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      o.b[i] = us::f2bf(us::bf2f(p.b[i]) + gate[v * 8 + i] * us::bf2f(q.b[i]));
+    *reinterpret_cast<uint4*>(hr + v * 8) = o.u;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+layer_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                  const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, int H,
+                  float eps) {
+  __shared__ float scratch[33];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * H;
+  __nv_bfloat16* yr = y + row * H;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < H; i += kThreads) s += us::bf2f(xr[i]);
+  const float mean = us::block_sum(s, scratch) / (float)H;
+  float vs = 0.f;
+  for (int i = threadIdx.x; i < H; i += kThreads) {
+    const float d = us::bf2f(xr[i]) - mean;
+    vs += d * d;
+  }
+  const float inv = rsqrtf(us::block_sum(vs, scratch) / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += kThreads) {
+    float n = (us::bf2f(xr[i]) - mean) * inv;
+    if (w) n *= us::bf2f(w[i]);
+    if (b) n += us::bf2f(b[i]);
+    yr[i] = us::f2bf(n);
+  }
+}
+
+}  // namespace
+
+US_API int us_rmsnorm(const void* x, const void* w, void* y, int T, int H, long long ldx,
+                      long long ldy, float eps, void* stream) {
+  US_REQUIRE(x && w && y && T >= 0 && H > 0 && (H % 8) == 0 && (ldx % 8) == 0 && (ldy % 8) == 0);
+  if (T == 0) return US_OK;
+  rmsnorm_kernel<<<T, kThreads, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}
+
+US_API int us_add_rmsnorm(const void* x, void* residual, const void* w, void* y, int T, int H,
+                          float eps, int first, void* stream) {
+  US_REQUIRE(x && residual && w && y && T >= 0 && H > 0 && (H % 8) == 0);
+  if (T == 0) return US_OK;
+  add_rmsnorm_kernel<<<T, kThreads, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (float*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps,
+      first);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}
+
+US_API int us_modulated_rmsnorm(const void* x, const void* w, const float* table, const int* idx,
+                                int vectors_per_row, int shift_slot, int scale_slot, void* y, int T,
+                                int H, float eps, void* stream) {
+  US_REQUIRE(x && table && idx && y && T >= 0 && H > 0 && (H % 8) == 0);
+  if (T == 0) return US_OK;
+  modulated_rmsnorm_kernel<<<T, kThreads, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, table, idx, vectors_per_row, shift_slot,
+      scale_slot, (__nv_bfloat16*)y, H, eps);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}
+
+US_API int us_gated_residual(void* h, const void* u, const float* table, const int* idx,
+                             int vectors_per_row, int gate_slot, int T, int H, void* stream) {
+  US_REQUIRE(h && u && table && idx && T >= 0 && H > 0 && (H % 8) == 0);
+  if (T == 0) return US_OK;
+  gated_residual_kernel<<<T, kThreads, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)h, (const __nv_bfloat16*)u, table, idx, vectors_per_row, gate_slot, H);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}
+
+US_API int us_layer_norm(const void* x, const void* w, const void* b, void* y, int T, int H,
+                         float eps, void* stream) {
+  US_REQUIRE(x && y && T >= 0 && H > 0);
+  if (T == 0) return US_OK;
+  layer_norm_kernel<<<T, kThreads, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y,
+      H, eps);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}

@@ -1,0 +1,208 @@
+// Per-head q/k RMSNorm fused with the rotary embedding and the paged KV write.
+//
+// One warp owns one (token, head) row of the fused QKV projection output.  The
+// row is normalised in FP32, rotated in FP32 and rounded once; K and V rows are
+// also scattered into the paged cache at `slot_mapping[token]` (slot =
+// page * page_size + offset, a negative slot writes nothing).
+//
+// Text models: one position per token, NeoX (half-split) or interleaved pairing
+// over the first `rot` channels.  Video transformer: three coordinates per row
+// (time, height, width), `freqs_per_axis` frequencies each, rotating
+// 2 * 3 * freqs_per_axis channels of every head.
+//
+// Reference behaviour: crates/ops/kernels/qk_norm_rope/triton, crates/ops/src/rope.rs,
+// crates/ops/src/kv.rs (reference project paths).
+#include "include/us_common.cuh"
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kMaxD = 256;
+
+struct RopeArgs {
+  __nv_bfloat16* qkv;      // [T, (Hq + 2 Hkv) * D], rotated in place
+  const __nv_bfloat16* qw; // [D] or null
+  const __nv_bfloat16* kw; // [D] or null
+  const int* positions;    // [T]
+  const float* inv_freq;   // [rot / 2]
+  const int* slots;        // [T] or null
+  __nv_bfloat16* kcache;   // [slots_total, Hkv, D] or null
+  __nv_bfloat16* vcache;
+  int T, Hq, Hkv, D, rot, interleaved;
+  float eps;
+};
+
+__global__ void __launch_bounds__(kWarps * 32) qk_norm_rope_kv_kernel(const RopeArgs a) {
+  __shared__ float rows[kWarps][kMaxD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = a.Hq + 2 * a.Hkv;
+  const long long unit = (long long)blockIdx.x * kWarps + warp;
+  if (unit >= (long long)a.T * heads) return;
+  const int t = (int)(unit / heads), h = (int)(unit % heads);
+  __nv_bfloat16* row = a.qkv + ((long long)t * heads + h) * a.D;
+  float* buf = rows[warp];
+  const int D = a.D;
+
+  const bool is_q = h < a.Hq;
+  const bool is_k = !is_q && h < a.Hq + a.Hkv;
+  const int slot = a.slots ? a.slots[t] : -1;
+
+  if (!is_q && !is_k) {  // V head: copy into the cache
+    if (a.vcache && slot >= 0) {
+      __nv_bfloat16* dst = a.vcache + ((long long)slot * a.Hkv + (h - a.Hq - a.Hkv)) * D;
+      for (int i = lane; i < D; i += 32) dst[i] = row[i];
+    }
+    return;
+  }
+
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    const float f = us::bf2f(row[i]);
+    buf[i] = f;
+    ss += f * f;
+  }
+  const __nv_bfloat16* w = is_q ? a.qw : a.kw;
+  if (w) {
+    ss = us::warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + a.eps);
+    __syncwarp();
+    for (int i = lane; i < D; i += 32) buf[i] = buf[i] * inv * us::bf2f(w[i]);
+  }
+  __syncwarp();
+
+  const float pos = (float)a.positions[t];
+  const int half = a.rot >> 1;
+  __nv_bfloat16* kdst = nullptr;
+  if (is_k && a.kcache && slot >= 0)
+    kdst = a.kcache + ((long long)slot * a.Hkv + (h - a.Hq)) * D;
+
+  for (int i = lane; i < D; i += 32) {
+    float out;
+    if (i < a.rot) {
+      int pair, fidx;
+      float sign;
+      if (a.interleaved) {
+        fidx = i >> 1;
+        pair = i ^ 1;
+        sign = (i & 1) ? 1.f : -1.f;
+      } else {
+        fidx = i < half ? i : i - half;
+        pair = i < half ? i + half : i - half;
+        sign = i < half ? -1.f : 1.f;
+      }
+      float sn, cs;
+      sincosf(pos * a.inv_freq[fidx], &sn, &cs);
+      out = buf[i] * cs + sign * buf[pair] * sn;
+    } else {
+      out = buf[i];
+    }
+    const __nv_bfloat16 o = us::f2bf(out);
+    row[i] = o;
+    if (kdst) kdst[i] = o;
+  }
+}
+
+struct Rope3Args {
+  __nv_bfloat16* q;        // [T, Hq * D] rows with leading dimension ldq
+  __nv_bfloat16* k;        // [T, Hk * D] rows with leading dimension ldk
+  const __nv_bfloat16* qw; // [D] or null
+  const __nv_bfloat16* kw;
+  const float* coords;     // [3, T] (time, height, width)
+  const float* inv_freq;   // [freqs_per_axis]
+  int T, Hq, Hk, D, freqs_per_axis;
+  long long ldq, ldk;
+  float eps;
+};
+
+// Channel layout of the rotated part: axis a in {0,1,2} owns channels
+// [a * 2F, (a + 1) * 2F) as F half-split pairs (i, i + F).
+__global__ void __launch_bounds__(kWarps * 32) qk_norm_rope3_kernel(const Rope3Args a) {
+  __shared__ float rows[kWarps][kMaxD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = a.Hq + a.Hk;
+  const long long unit = (long long)blockIdx.x * kWarps + warp;
+  if (unit >= (long long)a.T * heads) return;
+  const int t = (int)(unit / heads), h = (int)(unit % heads);
+  const bool is_q = h < a.Hq;
+  __nv_bfloat16* row = is_q ? a.q + (long long)t * a.ldq + (long long)h * a.D
+                            : a.k + (long long)t * a.ldk + (long long)(h - a.Hq) * a.D;
+  float* buf = rows[warp];
+  const int D = a.D;
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    const float f = us::bf2f(row[i]);
+    buf[i] = f;
+    ss += f * f;
+  }
+  const __nv_bfloat16* w = is_q ? a.qw : a.kw;
+  if (w) {
+    ss = us::warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + a.eps);
+    __syncwarp();
+    for (int i = lane; i < D; i += 32) buf[i] = buf[i] * inv * us::bf2f(w[i]);
+  }
+  __syncwarp();
+  const int F = a.freqs_per_axis;
+  const int rot = 6 * F;
+  for (int i = lane; i < D; i += 32) {
+    float out = buf[i];
+    if (i < rot) {
+      const int axis = i / (2 * F);
+      const int j = i - axis * 2 * F;
+      const int fidx = j < F ? j : j - F;
+      const int pair = j < F ? i + F : i - F;
+      const float sign = j < F ? -1.f : 1.f;
+      float sn, cs;
+      sincosf(a.coords[(long long)axis * a.T + t] * a.inv_freq[fidx], &sn, &cs);
+      out = buf[i] * cs + sign * buf[pair] * sn;
+    }
+    row[i] = us::f2bf(out);
+  }
+}
+
+}  // namespace
+
+US_API int us_qk_norm_rope_kv(void* qkv, const void* qw, const void* kw, const int* positions,
+                              const float* inv_freq, const int* slots, void* kcache, void* vcache,
+                              int T, int Hq, int Hkv, int D, int rot, int interleaved, float eps,
+                              void* stream) {
+  US_REQUIRE(qkv && positions && inv_freq && T >= 0 && D > 0 && D <= kMaxD && rot <= D &&
+             (rot % 2) == 0);
+  if (T == 0) return US_OK;
+  RopeArgs a;
+  a.qkv = (__nv_bfloat16*)qkv;
+  a.qw = (const __nv_bfloat16*)qw;
+  a.kw = (const __nv_bfloat16*)kw;
+  a.positions = positions;
+  a.inv_freq = inv_freq;
+  a.slots = slots;
+  a.kcache = (__nv_bfloat16*)kcache;
+  a.vcache = (__nv_bfloat16*)vcache;
+  a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.rot = rot; a.interleaved = interleaved;
+  a.eps = eps;
+  const long long units = (long long)T * (Hq + 2 * Hkv);
+  const int blocks = (int)((units + kWarps - 1) / kWarps);
+  qk_norm_rope_kv_kernel<<<blocks, kWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}
+
+US_API int us_qk_norm_rope3(void* q, void* k, const void* qw, const void* kw, const float* coords,
+                            const float* inv_freq, int T, int Hq, int Hk, int D,
+                            int freqs_per_axis, long long ldq, long long ldk, float eps,
+                            void* stream) {
+  US_REQUIRE(q && k && coords && inv_freq && T >= 0 && D > 0 && D <= kMaxD &&
+             6 * freqs_per_axis <= D);
+  if (T == 0) return US_OK;
+  Rope3Args a;
+  a.q = (__nv_bfloat16*)q; a.k = (__nv_bfloat16*)k;
+  a.qw = (const __nv_bfloat16*)qw; a.kw = (const __nv_bfloat16*)kw;
+  a.coords = coords; a.inv_freq = inv_freq;
+  a.T = T; a.Hq = Hq; a.Hk = Hk; a.D = D; a.freqs_per_axis = freqs_per_axis;
+  a.ldq = ldq; a.ldk = ldk; a.eps = eps;
+  const long long units = (long long)T * (Hq + Hk);
+  const int blocks = (int)((units + kWarps - 1) / kWarps);
+  qk_norm_rope3_kernel<<<blocks, kWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}

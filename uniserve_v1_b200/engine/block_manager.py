@@ -1,0 +1,123 @@
+"""Python face of the native paged-KV block manager (``csrc/host/block_manager.cpp``).
+
+Page 0 is the padding sentinel.  Full pages are committed under chained SHA-256
+content keys so later requests with the same prefix (and the same isolation
+salt) reuse them; the last prompt token is always recomputed
+(crates/storage/src/key.rs:1-30, reference project path).
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+from typing import Optional, Sequence
+
+import numpy as np
+
+from ..ops import native as N
+
+_bound = False
+
+
+def _lib():
+    global _bound
+    lib = N.host()
+    if not _bound:
+        vp, i32p, u64p = ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_uint64)
+        lib.us_bm_create.restype = vp
+        lib.us_bm_create.argtypes = [ctypes.c_int, ctypes.c_int]
+        lib.us_bm_destroy.argtypes = [vp]
+        lib.us_bm_num_free.argtypes = [vp]
+        lib.us_bm_num_cached.argtypes = [vp]
+        lib.us_bm_alloc.argtypes = [vp, ctypes.c_int, vp]
+        lib.us_bm_release.argtypes = [vp, vp, ctypes.c_int]
+        lib.us_bm_hash_chain.argtypes = [vp, vp, ctypes.c_int, ctypes.c_int, vp]
+        lib.us_bm_match_prefix.argtypes = [vp, vp, ctypes.c_int, vp]
+        lib.us_bm_commit.argtypes = [vp, ctypes.c_int, ctypes.c_uint64, ctypes.c_uint64]
+        lib.us_bm_stats.argtypes = [vp, vp, vp, vp]
+        lib.us_bm_refcount.argtypes = [vp, ctypes.c_int]
+        lib.us_bm_flush.argtypes = [vp]
+        _bound = True
+    return lib
+
+
+class BlockManager:
+    def __init__(self, num_pages: int, page_size: int = 16, weights_identity: str = "",
+                 enable_prefix_cache: bool = True):
+        self.lib = _lib()
+        self.num_pages = num_pages
+        self.page_size = page_size
+        self.enable_prefix_cache = enable_prefix_cache
+        self.identity = weights_identity
+        self.h = self.lib.us_bm_create(num_pages, page_size)
+        if not self.h:
+            raise ValueError("block manager needs at least 2 pages")
+
+    def __del__(self):
+        try:
+            if getattr(self, "h", None):
+                self.lib.us_bm_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ verbs --
+    @property
+    def num_free(self) -> int:
+        return self.lib.us_bm_num_free(self.h)
+
+    @property
+    def num_cached(self) -> int:
+        return self.lib.us_bm_num_cached(self.h)
+
+    def can_allocate(self, n: int) -> bool:
+        return n <= self.num_free
+
+    def allocate(self, n: int) -> Optional[list]:
+        if n == 0:
+            return []
+        out = np.empty(n, dtype=np.int32)
+        rc = self.lib.us_bm_alloc(self.h, n, out.ctypes.data)
+        return None if rc != 0 else out.tolist()
+
+    def release(self, pages: Sequence[int]) -> None:
+        if not pages:
+            return
+        arr = np.asarray(pages, dtype=np.int32)
+        self.lib.us_bm_release(self.h, arr.ctypes.data, len(arr))
+
+    def page_keys(self, token_ids: Sequence[int], salt: Optional[str] = None) -> np.ndarray:
+        """Chained keys of every full page of ``token_ids``: uint64 [n_full, 2]."""
+        seed = hashlib.sha256((self.identity + "\0" + (salt or "")).encode()).digest()
+        toks = np.asarray(token_ids, dtype=np.int32)
+        n_full = len(toks) // self.page_size
+        keys = np.zeros((max(n_full, 1), 2), dtype=np.uint64)
+        seed_buf = (ctypes.c_uint8 * 32).from_buffer_copy(seed)
+        self.lib.us_bm_hash_chain(ctypes.addressof(seed_buf), toks.ctypes.data, len(toks),
+                                  self.page_size, keys.ctypes.data)
+        return keys[:n_full]
+
+    def match_prefix(self, keys: np.ndarray) -> list:
+        """Pins and returns the pages of the longest cached leading run."""
+        if not self.enable_prefix_cache or len(keys) == 0:
+            return []
+        keys = np.ascontiguousarray(keys, dtype=np.uint64)
+        out = np.empty(len(keys), dtype=np.int32)
+        m = self.lib.us_bm_match_prefix(self.h, keys.ctypes.data, len(keys), out.ctypes.data)
+        return out[:m].tolist()
+
+    def commit(self, page: int, key) -> int:
+        if not self.enable_prefix_cache:
+            return page
+        return self.lib.us_bm_commit(self.h, int(page), int(key[0]), int(key[1]))
+
+    def refcount(self, page: int) -> int:
+        return self.lib.us_bm_refcount(self.h, page)
+
+    def flush(self) -> int:
+        return self.lib.us_bm_flush(self.h)
+
+    def stats(self) -> dict:
+        a, b, c = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+        self.lib.us_bm_stats(self.h, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
+        return {"hits": a.value, "lookups": b.value, "evictions": c.value,
+                "free": self.num_free, "cached": self.num_cached, "pages": self.num_pages}

@@ -1,0 +1,152 @@
+"""The token engine: scheduler + block manager + runner behind one object.
+
+``LLMEngine.generate`` is the public batch API (what ``bench.py`` times end to
+end); the HTTP layer drives ``add_request`` / ``step`` from its engine loop.
+One engine drives the GPU(s) of one replica; with a tensor/expert group every
+rank runs the same engine in lock step (rank 0's schedule is the schedule:
+all ranks see the same requests in the same order, so their schedulers agree).
+
+Reference behaviour: crates/engine/src/scheduler/mod.rs:796-1065 (run/step),
+crates/engine/src/worker.rs:1587 (worker loop), docs/architecture.md:128
+(two-turn steps) — reference project paths.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from typing import Optional
+
+import torch
+
+from ..models.qwen3_moe import Qwen3MoeModel
+from .block_manager import BlockManager
+from .runner import CausalLmRunner
+from .scheduler import Policy, Scheduler, SchedulerConfig
+from .types import ErrorClass, FinishReason, Request, SamplingParams, StepOutput
+
+
+class Watchdog:
+    """Reports a job in flight longer than ``timeout`` seconds
+    (crates/engine/src/worker/watchdog.rs:1-17, reference path).  Host-side only:
+    device waits are bounded inside the kernels and surface as a status word."""
+
+    def __init__(self, timeout: float = 150.0):
+        self.timeout = timeout
+        self.started: Optional[float] = None
+        self.what = ""
+
+    def begin(self, what: str) -> None:
+        self.started, self.what = time.monotonic(), what
+
+    def end(self) -> None:
+        self.started = None
+
+    def overdue(self) -> Optional[str]:
+        if self.started is not None and time.monotonic() - self.started > self.timeout:
+            return f"{self.what} in flight for more than {self.timeout:.0f}s"
+        return None
+
+
+class LLMEngine:
+    def __init__(self, model: Qwen3MoeModel, num_pages: Optional[int] = None, page_size: int = 16,
+                 max_num_seqs: int = 128, max_model_len: int = 4096,
+                 max_num_batched_tokens: int = 8192, mem_fraction_static: float = 0.9,
+                 enable_prefix_cache: bool = True, use_graphs: bool = True,
+                 policy: Optional[Policy] = None, weights_identity: str = "random-init",
+                 watchdog_timeout: float = 150.0):
+        self.model = model
+        self.device = model.device
+        max_model_len = min(max_model_len, model.cfg.max_position_embeddings)
+        if num_pages is None:
+            num_pages = self._divide_memory(mem_fraction_static, page_size, max_num_seqs,
+                                            max_model_len)
+        self.blocks = BlockManager(num_pages, page_size, weights_identity, enable_prefix_cache)
+        self.config = SchedulerConfig(max_num_seqs=max_num_seqs,
+                                      max_num_batched_tokens=max_num_batched_tokens,
+                                      chunked_prefill_size=max_num_batched_tokens,
+                                      max_model_len=max_model_len, page_size=page_size,
+                                      eos_token_id=model.cfg.eos_token_id)
+        self.scheduler = Scheduler(self.blocks, self.config, policy)
+        self.runner = CausalLmRunner(model, num_pages, page_size, max_num_seqs, max_model_len,
+                                     use_graphs)
+        self.runner.eos_token_id = model.cfg.eos_token_id
+        self.watchdog = Watchdog(watchdog_timeout)
+        self._ids = itertools.count()
+        self.failed: Optional[str] = None
+
+    def _divide_memory(self, fraction, page_size, max_num_seqs, max_model_len) -> int:
+        """Quota division: what is left of ``fraction`` of the device after the
+        weights goes to KV pages (crates/engine/src/memory/division.rs, reference)."""
+        per_page = self.model.kv_bytes_per_page(page_size)
+        want = max_num_seqs * ((max_model_len + page_size - 1) // page_size) + 1
+        if self.device.type != "cuda":
+            return min(want, 4096)
+        free, total = torch.cuda.mem_get_info(self.device)
+        used_by_us = total - free
+        budget = int(total * fraction) - used_by_us - (2 << 30)   # graphs + workspaces
+        pages = max(64, budget // per_page)
+        return int(min(pages, want))
+
+    # -------------------------------------------------------------- requests --
+    def add_request(self, prompt_ids, params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, priority: int = 0,
+                    cache_salt: Optional[str] = None, output_ids: Optional[list] = None) -> str:
+        if self.failed:
+            raise RuntimeError(f"engine stopped: {self.failed}")
+        rid = request_id or f"req-{next(self._ids)}"
+        V = self.model.cfg.vocab_size
+        if any((t < 0 or t >= V) for t in prompt_ids):
+            raise ValueError("input_error: token id outside the vocabulary")
+        req = Request(rid, list(prompt_ids), params or SamplingParams(), priority=priority,
+                      cache_salt=cache_salt)
+        if output_ids:                     # a migrated request resumes with its tokens
+            req.output_ids = list(output_ids)
+        self.scheduler.add_request(req)
+        return rid
+
+    def abort(self, request_id: str) -> bool:
+        return self.scheduler.abort(request_id) is not None
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ step --
+    def step(self) -> list:
+        batch = self.scheduler.schedule()
+        if batch is None:
+            return []
+        self.watchdog.begin(f"{batch.kind} step {batch.step_id}")
+        try:
+            sampled, lps = self.runner.execute(batch)
+        except Exception as e:     # fatal_worker_failure: stop the engine, fail every request
+            self.failed = f"{ErrorClass.FATAL_WORKER_FAILURE.value}: {e}"
+            raise
+        finally:
+            self.watchdog.end()
+        errors = {}
+        V = self.model.cfg.vocab_size
+        for rid, tok in sampled.items():
+            if tok < 0 or tok >= V:
+                errors[rid] = f"{ErrorClass.NUMERICAL_FAULT.value}: sampled token {tok}"
+        return self.scheduler.update(batch, sampled, lps, errors)
+
+    # -------------------------------------------------------------- generate --
+    def generate(self, prompts: list, params=None, on_output=None) -> list:
+        """Runs the prompts to completion; returns the output token lists in
+        prompt order.  ``params`` is one SamplingParams or a list."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while self.scheduler.has_work():
+            outs = self.step()
+            if on_output:
+                for o in outs:
+                    on_output(o)
+        return [self.scheduler.requests[i].output_ids for i in ids]
+
+    def stats(self) -> dict:
+        s = dict(self.scheduler.stats)
+        s.update({"kv": self.blocks.stats(), "running": len(self.scheduler.running),
+                  "waiting": len(self.scheduler.waiting), "h2d_bytes": self.runner.h2d_bytes,
+                  "d2h_bytes": self.runner.d2h_bytes})
+        return s

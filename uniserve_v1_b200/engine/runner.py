@@ -1,0 +1,418 @@
+"""Causal-LM runner: turns a scheduled batch into device work and reads results back.
+
+Decode runs from CUDA graphs, one per (bucket size, sampling variant), captured
+largest bucket first into one shared memory pool; a batch runs in the smallest
+bucket that holds it.  Everything a graph needs from the host travels as one
+pinned input block copied with a single H2D copy into fixed device addresses;
+nothing is called back from a stream.  The graph also advances the device-side
+step state (next input token, position, length, cache slot), so several steps can
+be replayed back to back without the host.
+
+Reference behaviour: crates/engine/src/runner/causal_lm.rs:2643 (start),
+runner/graphs/mod.rs:957-1011 (prepare_inputs / replay), runner/buckets.rs:9-15
+(smallest bucket), docs/architecture.md:141 (inputs travel as one copy) — reference
+project paths.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..models.qwen3_moe import AttnMeta, Qwen3MoeModel
+from ..ops import functional as F
+from ..ops import native as N
+from .scheduler import Batch
+from .types import SamplingParams
+
+DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+class InputBlock:
+    """Named views over one pinned host buffer and its fixed device twin."""
+
+    def __init__(self, fields: list, device):
+        self.device = torch.device(device)
+        off = 0
+        self.layout = {}
+        for name, dtype, shape in fields:
+            n = 1
+            for s in shape:
+                n *= s
+            nbytes = n * torch.empty(0, dtype=dtype).element_size()
+            off = (off + 15) & ~15
+            self.layout[name] = (off, nbytes, dtype, shape)
+            off += nbytes
+        self.nbytes = (off + 15) & ~15
+        pin = self.device.type == "cuda"
+        self.host = torch.zeros(self.nbytes, dtype=torch.uint8, pin_memory=pin)
+        self.dev = torch.zeros(self.nbytes, dtype=torch.uint8, device=self.device)
+        self.h = {k: self.host[o:o + nb].view(dt).view(shape)
+                  for k, (o, nb, dt, shape) in self.layout.items()}
+        self.d = {k: self.dev[o:o + nb].view(dt).view(shape)
+                  for k, (o, nb, dt, shape) in self.layout.items()}
+
+    def upload(self) -> int:
+        self.dev.copy_(self.host, non_blocking=True)
+        return self.nbytes
+
+
+@dataclass
+class DecodeGraph:
+    graph: object
+    variant: str
+    bucket: int
+    logits: Optional[torch.Tensor]
+    sampled: torch.Tensor
+
+
+class CausalLmRunner:
+    def __init__(self, model: Qwen3MoeModel, num_pages: int, page_size: int = 16,
+                 max_num_seqs: int = 128, max_model_len: int = 4096, use_graphs: bool = True,
+                 history_steps: int = 64):
+        self.model = model
+        self.device = model.device
+        self.page_size = page_size
+        self.num_pages = num_pages
+        self.max_num_seqs = max_num_seqs
+        self.max_model_len = max_model_len
+        self.max_pages = (max_model_len + page_size - 1) // page_size
+        self.kv_caches = model.new_kv_caches(num_pages, page_size)
+        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self.buckets = [b for b in DECODE_BUCKETS if b < max_num_seqs] + [max_num_seqs]
+        self.history_steps = history_steps
+        self._blocks: dict = {}
+        self._graphs: dict = {}
+        self._pool = None
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self._readback = None
+        if self.device.type == "cuda":
+            N.kernels().us_status_ptr()       # allocate the status word before any capture
+
+    # ---------------------------------------------------------------- blocks --
+    def _decode_block(self, B: int) -> InputBlock:
+        blk = self._blocks.get(B)
+        if blk is None:
+            i32, f32, i64 = torch.int32, torch.float32, torch.int64
+            blk = InputBlock([
+                ("input_ids", i32, (B,)), ("positions", i32, (B,)), ("slots", i32, (B,)),
+                ("seq_lens", i32, (B,)), ("live", i32, (1,)), ("step", i32, (1,)),
+                ("page_table", i32, (B, self.max_pages)),
+                ("temperature", f32, (B,)), ("top_p", f32, (B,)), ("min_p", f32, (B,)),
+                ("top_k", i32, (B,)), ("seeds", i64, (B,)), ("sample_pos", i64, (B,)),
+            ], self.device)
+            blk.history = torch.full((self.history_steps, B), -1, dtype=torch.int32,
+                                     device=self.device)
+            self._blocks[B] = blk
+        return blk
+
+    def bucket_for(self, n: int) -> int:
+        for b in self.buckets:
+            if n <= b:
+                return b
+        raise ValueError(f"no decode bucket holds {n} rows (largest {self.buckets[-1]})")
+
+    # ----------------------------------------------------------- decode body --
+    def _decode_body(self, blk: InputBlock, B: int, variant: str):
+        """The one forward function: eager, rehearsal and capture all run this."""
+        d = blk.d
+        max_len = self.max_model_len
+        splits = F.decode_splits(B, self.model.Hkv, max_len) if self.device.type == "cuda" else 1
+        meta = AttnMeta(kind="decode", slots=d["slots"], page_table=d["page_table"],
+                        seq_lens=d["seq_lens"], splits=splits)
+        hidden = self.model.forward(d["input_ids"], d["positions"], meta, self.kv_caches)
+        logits = self.model.logits(hidden)
+        if variant == "greedy":
+            sampled = F.argmax(logits)
+        elif variant == "sampled":
+            if logits.is_cuda:
+                F.logits_shape_(logits, temp=d["temperature"])
+            else:
+                logits = F.R.logits_shape(logits, temp=d["temperature"])
+            sampled = F.sample_from_logits(logits, d["top_k"], d["top_p"], d["min_p"], d["seeds"],
+                                           d["sample_pos"])
+        else:                       # "logits": shaping and the draw happen outside
+            return logits, None
+        if sampled.device != self.device:
+            sampled = sampled.to(self.device)
+        # Device-side advance so the next step can run without the host.
+        F.decode_advance_(sampled, d["input_ids"], d["positions"], d["seq_lens"], d["slots"],
+                          d["page_table"], self.page_size, live=d["live"], history=blk.history,
+                          step=d["step"])
+        d["sample_pos"].add_(1)
+        return logits, sampled
+
+    def _graph(self, B: int, variant: str) -> Optional[DecodeGraph]:
+        if not self.use_graphs:
+            return None
+        key = (B, variant)
+        g = self._graphs.get(key)
+        if g is not None:
+            return g
+        blk = self._decode_block(B)
+        # Rehearse on a side stream (loads modules, sizes workspaces), then capture.
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        saved = blk.dev.clone()
+        # Inert inputs: no row is live, no cache slot is written.
+        blk.dev.zero_()
+        blk.d["slots"].fill_(-1)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(s):
+            self._decode_body(blk, B, variant)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        blk.dev.copy_(saved)
+        graph = torch.cuda.CUDAGraph()
+        if self._pool is None:
+            self._pool = torch.cuda.graph_pool_handle()
+        with torch.cuda.graph(graph, pool=self._pool):
+            logits, sampled = self._decode_body(blk, B, variant)
+        blk.dev.copy_(saved)
+        torch.cuda.synchronize()
+        N.raise_on_device_error()
+        g = DecodeGraph(graph, variant, B, logits, sampled)
+        self._graphs[key] = g
+        return g
+
+    def warm_up(self, variants=("greedy",), buckets=None) -> None:
+        """Captures largest first so smaller graphs reuse the big ones' memory."""
+        for B in sorted(buckets or self.buckets, reverse=True):
+            for v in variants:
+                self._graph(B, v)
+
+    # ---------------------------------------------------------------- decode --
+    def _fill_decode(self, blk: InputBlock, rows: list, B: int) -> None:
+        h = blk.h
+        n = len(rows)
+        ps = self.page_size
+        h["live"][0] = n
+        h["step"][0] = 0
+        for i, req in enumerate(rows):
+            pos = req.num_tokens - 1
+            h["input_ids"][i] = req.all_ids[-1]
+            h["positions"][i] = pos
+            h["seq_lens"][i] = pos + 1
+            h["slots"][i] = req.pages[pos // ps] * ps + pos % ps
+            npg = len(req.pages)
+            h["page_table"][i, :npg] = torch.tensor(req.pages, dtype=torch.int32)
+            p: SamplingParams = req.params
+            h["temperature"][i] = 1.0 if p.greedy else p.temperature
+            h["top_k"][i] = 1 if p.greedy else (p.top_k if p.top_k > 0 else 0)
+            h["top_p"][i] = p.top_p
+            h["min_p"][i] = p.min_p
+            h["seeds"][i] = req.seed - (1 << 64) if req.seed >= (1 << 63) else req.seed
+            h["sample_pos"][i] = req.num_tokens
+        if n < B:
+            h["input_ids"][n:] = 0
+            h["positions"][n:] = 0
+            h["seq_lens"][n:] = 0
+            h["slots"][n:] = -1
+            h["temperature"][n:] = 1.0
+            h["top_k"][n:] = 1
+            h["top_p"][n:] = 1.0
+            h["min_p"][n:] = 0.0
+
+    @staticmethod
+    def variant_for(rows: list) -> str:
+        if any(r.params.needs_shaping or r.params.logprobs for r in rows):
+            return "logits"
+        return "greedy" if all(r.params.greedy for r in rows) else "sampled"
+
+    def decode(self, rows: list, steps: int = 1):
+        """Runs ``steps`` decode steps for ``rows`` (requests); returns
+        (tokens [steps, n] on the host, logprob info or None)."""
+        n = len(rows)
+        B = self.bucket_for(n)
+        blk = self._decode_block(B)
+        variant = self.variant_for(rows)
+        assert steps == 1 or variant != "logits"
+        assert steps <= self.history_steps
+        self._fill_decode(blk, rows, B)
+        g = self._graph(B, variant)
+        self.h2d_bytes += blk.upload()
+        logits = sampled = None
+        for _ in range(steps):
+            if g is not None:
+                g.graph.replay()
+                logits, sampled = g.logits, g.sampled
+            else:
+                logits, sampled = self._decode_body(blk, B, variant)
+        info = None
+        if variant == "logits":
+            sampled, info = self._shape_and_sample(logits[:n], rows)
+            out = sampled.view(1, n)
+        elif self.device.type == "cuda":
+            out = self._to_host(blk.history[:steps, :n])
+        else:
+            out = blk.history[:steps, :n].clone()
+        return out, info
+
+    def _to_host(self, t: torch.Tensor) -> torch.Tensor:
+        host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+        host.copy_(t, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += host.numel() * host.element_size()
+        return host
+
+    # ------------------------------------------------ shaping outside graphs --
+    def _shape_and_sample(self, logits: torch.Tensor, rows: list):
+        """Rows with penalties, bias, bans or logprobs: vLLM order on the device,
+        then the same draw kernel.  Logprobs are taken on the raw distribution."""
+        dev = logits.device
+        n, V = logits.shape
+        raw = logits
+        shaped = logits.clone()
+        need_counts = any(r.params.repetition_penalty != 1.0 or r.params.frequency_penalty != 0.0
+                          or r.params.presence_penalty != 0.0 for r in rows)
+        ban = torch.zeros(n, V, dtype=torch.uint8)
+        any_ban = False
+        counts = torch.zeros(n, V, dtype=torch.int16) if need_counts else None
+        pmask = torch.zeros(n, V, dtype=torch.uint8) if need_counts else None
+        bo, bi, bv = [0], [], []
+        eos = getattr(self, "eos_token_id", None)
+        for i, r in enumerate(rows):
+            p = r.params
+            if p.allowed_token_ids:
+                ban[i] = 1
+                ban[i, torch.tensor(p.allowed_token_ids)] = 0
+                any_ban = True
+            for w in (p.bad_words_ids or []):
+                if len(w) == 1:
+                    ban[i, w[0]] = 1
+                    any_ban = True
+                elif len(w) > 1 and r.all_ids[-(len(w) - 1):] == list(w[:-1]):
+                    ban[i, w[-1]] = 1
+                    any_ban = True
+            if len(r.output_ids) < p.min_tokens:
+                for t in ([eos] if eos is not None else []) + list(p.stop_token_ids):
+                    ban[i, t] = 1
+                    any_ban = True
+            for tok, val in (p.logit_bias or {}).items():
+                bi.append(int(tok))
+                bv.append(float(val))
+            bo.append(len(bi))
+            if need_counts:
+                if r.output_ids:
+                    counts[i] = torch.bincount(torch.tensor(r.output_ids), minlength=V)[:V].to(torch.int16)
+                pmask[i, torch.tensor(r.prompt_ids)] = 1
+        f32 = lambda xs: torch.tensor(xs, dtype=torch.float32, device=dev)
+        temp = f32([1.0 if r.params.greedy else r.params.temperature for r in rows])
+        kw = dict(ban_mask=ban.to(dev) if any_ban else None,
+                  out_counts=counts.to(dev) if need_counts else None,
+                  prompt_mask=pmask.to(dev) if need_counts else None,
+                  rep=f32([r.params.repetition_penalty for r in rows]) if need_counts else None,
+                  freq=f32([r.params.frequency_penalty for r in rows]) if need_counts else None,
+                  pres=f32([r.params.presence_penalty for r in rows]) if need_counts else None,
+                  temp=temp)
+        if dev.type == "cuda":
+            csr = None
+            if bi:
+                csr = (torch.tensor(bo, dtype=torch.int32, device=dev),
+                       torch.tensor(bi, dtype=torch.int32, device=dev), f32(bv))
+            F.logits_shape_(shaped, bias_csr=csr, **kw)
+        else:
+            bias = [[(bi[j], bv[j]) for j in range(bo[i], bo[i + 1])] for i in range(n)] if bi else None
+            shaped = F.R.logits_shape(shaped, bias=bias, **kw)
+        top_k = torch.tensor([1 if r.params.greedy else max(r.params.top_k, 0) for r in rows],
+                             dtype=torch.int32, device=dev)
+        top_p = f32([r.params.top_p for r in rows])
+        min_p = f32([r.params.min_p for r in rows])
+        seeds = torch.tensor([r.seed - (1 << 64) if r.seed >= (1 << 63) else r.seed for r in rows],
+                             dtype=torch.int64, device=dev)
+        pos = torch.tensor([r.num_tokens for r in rows], dtype=torch.int64, device=dev)
+        sampled = F.sample_from_logits(shaped, top_k, top_p, min_p, seeds, pos)
+        sampled = sampled.to(dev)
+        info = None
+        if any(r.params.logprobs for r in rows):
+            lse, lp, rank = F.logprob_stats(raw, sampled)
+            kmax = max([r.params.top_logprobs for r in rows] + [0])
+            top = None
+            if kmax > 0:
+                tv, ti = torch.topk(raw.float(), kmax, dim=-1)
+                top = ((tv - lse[:, None]).cpu(), ti.cpu())
+            lp_c, rank_c = lp.cpu(), rank.cpu()
+            info = {}
+            for i, r in enumerate(rows):
+                if not r.params.logprobs:
+                    continue
+                tops = []
+                if top is not None:
+                    k = r.params.top_logprobs
+                    tops = [(int(top[1][i, j]), float(top[0][i, j])) for j in range(k)]
+                info[r.request_id] = (float(lp_c[i]), int(rank_c[i]), tops)
+        host = sampled.cpu()
+        if dev.type == "cuda":
+            self.d2h_bytes += host.numel() * 4
+        return host, info
+
+    # --------------------------------------------------------------- prefill --
+    def prefill(self, chunks: list):
+        """Eager varlen prefill of the scheduled chunks; returns (tokens for the
+        chunks that sample, in chunk order, on the host; logprob info)."""
+        dev = self.device
+        ps = self.page_size
+        ids, pos, slots, cu_q, cu_k, ctx, last_rows, sample_rows = [], [], [], [0], [0], [], [], []
+        max_q = max_k = 0
+        for c in chunks:
+            req = c.request
+            toks = req.all_ids[c.start:c.start + c.length]
+            ids.extend(toks)
+            pos.extend(range(c.start, c.start + c.length))
+            for p_ in range(c.start, c.start + c.length):
+                slots.append(req.pages[p_ // ps] * ps + p_ % ps)
+            cu_q.append(cu_q[-1] + c.length)
+            cu_k.append(cu_k[-1] + c.start + c.length)
+            ctx.append(c.start)
+            max_q = max(max_q, c.length)
+            max_k = max(max_k, c.start + c.length)
+            if c.sample:
+                last_rows.append(cu_q[-1] - 1)
+                sample_rows.append(req)
+        T = len(ids)
+        i32 = torch.int32
+        packed = torch.tensor(ids + pos + slots + cu_q + cu_k, dtype=i32,
+                              pin_memory=dev.type == "cuda")
+        d = packed.to(dev, non_blocking=True)
+        self.h2d_bytes += packed.numel() * 4
+        nq = len(cu_q)
+        page_table = None
+        if any(c > 0 for c in ctx):
+            page_table = torch.zeros(len(chunks), self.max_pages, dtype=i32)
+            for i, c in enumerate(chunks):
+                page_table[i, :len(c.request.pages)] = torch.tensor(c.request.pages, dtype=i32)
+            page_table = page_table.to(dev)
+        meta = AttnMeta(kind="prefill", slots=d[2 * T:3 * T], cu_q=d[3 * T:3 * T + nq],
+                        cu_k=d[3 * T + nq:3 * T + 2 * nq], max_q=max_q, max_k=max_k,
+                        context_lens=ctx, page_table=page_table)
+        hidden = self.model.forward(d[:T], d[T:2 * T], meta, self.kv_caches)
+        if not sample_rows:
+            return None, None, []
+        rows_idx = torch.tensor(last_rows, dtype=i32, device=dev)
+        last = F.gather_rows(hidden, rows_idx)
+        logits = self.model.logits(last)
+        if self.variant_for(sample_rows) == "greedy":
+            toks = F.argmax(logits)
+            host = self._to_host(toks) if dev.type == "cuda" else toks
+            return host, None, sample_rows
+        host, info = self._shape_and_sample(logits, sample_rows)
+        return host, info, sample_rows
+
+    # ---------------------------------------------------------------- execute --
+    def execute(self, batch: Batch):
+        """Returns (sampled {request_id: token}, logprobs {request_id: info})."""
+        sampled, lps = {}, {}
+        if batch.kind == "decode":
+            rows = [c.request for c in batch.chunks]
+            toks, info = self.decode(rows, 1)
+            for i, r in enumerate(rows):
+                sampled[r.request_id] = int(toks[0, i])
+            lps = info or {}
+        else:
+            toks, info, rows = self.prefill(batch.chunks)
+            for i, r in enumerate(rows):
+                sampled[r.request_id] = int(toks[i])
+            lps = info or {}
+        return sampled, lps

@@ -1,0 +1,355 @@
+"""Qwen3 / Qwen3-MoE decoder (vLLM residual form) over the fused operators.
+
+Layer (reference: crates/models/src/qwen3/decoder.rs:1-24, :242-361, reference
+project path)::
+
+    x, residual = add_rmsnorm(hidden, residual)           # FP32 residual stream
+    mixed       = attention(x)                            # QKV GEMM -> q/k norm + rope + kv write
+                                                          #  -> paged / varlen attention -> o_proj
+    x, residual = add_rmsnorm(mixed, residual)
+    hidden      = experts(x)  |  mlp(x)                   # router -> top-k -> grouped FC1/FC2
+
+Weights are fused at load time: ``qkv`` stacks q, k, v rows; ``w13`` stacks each
+expert's up rows *before* its gate rows ([E, 2I, H]); ``w2`` is [E, H, I].
+
+Parallel layouts (crates/nn/src/modules/linear.rs:27-41, moe.rs:50-55, reference
+paths): attention heads and the dense MLP are split column/row-wise over the
+tensor group; with ``expert_parallel`` every rank of the group holds E/P whole
+experts, runs all rows, foreign routes contribute zero and the group all-reduce
+sums the partial outputs.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from ..ops import functional as F
+from ..ops import reference as R
+from ..parallel.context import ParallelContext
+
+
+@dataclass
+class Qwen3MoeConfig:
+    vocab_size: int = 151936
+    hidden_size: int = 2048
+    num_hidden_layers: int = 48
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 4
+    head_dim: int = 128
+    rope_theta: float = 1e6
+    rms_norm_eps: float = 1e-6
+    num_experts: int = 128
+    num_experts_per_tok: int = 8
+    moe_intermediate_size: int = 768
+    intermediate_size: int = 6144          # dense MLP layers (mlp_only_layers)
+    norm_topk_prob: bool = True
+    mlp_only_layers: tuple = ()
+    decoder_sparse_step: int = 1
+    tie_word_embeddings: bool = False
+    max_position_embeddings: int = 40960
+    sliding_window: int = 0
+    eos_token_id: int = 151645
+    architectures: tuple = ("Qwen3MoeForCausalLM",)
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "Qwen3MoeConfig":
+        keys = {f for f in cls.__dataclass_fields__}
+        kw = {k: v for k, v in d.items() if k in keys}
+        if "head_dim" not in kw:
+            kw["head_dim"] = d["hidden_size"] // d["num_attention_heads"]
+        for k in ("mlp_only_layers", "architectures"):
+            if k in kw and kw[k] is not None:
+                kw[k] = tuple(kw[k])
+        if kw.get("sliding_window") is None:
+            kw["sliding_window"] = 0
+        if isinstance(kw.get("eos_token_id"), list):
+            kw["eos_token_id"] = kw["eos_token_id"][0]
+        if "num_experts" not in d:          # dense Qwen3
+            kw["num_experts"] = 0
+        return cls(**kw)
+
+    def is_moe_layer(self, i: int) -> bool:
+        return (self.num_experts > 0 and i not in self.mlp_only_layers
+                and (i + 1) % self.decoder_sparse_step == 0)
+
+    # Named shapes -----------------------------------------------------------
+    @classmethod
+    def tiny(cls) -> "Qwen3MoeConfig":
+        """2 layers, hidden 256, 4 q / 2 kv heads x 64, 8 experts top-2, inter 128, vocab 1024."""
+        return cls(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                   num_key_value_heads=2, head_dim=64, num_experts=8, num_experts_per_tok=2,
+                   moe_intermediate_size=128, intermediate_size=512, eos_token_id=1023,
+                   max_position_embeddings=4096)
+
+    @classmethod
+    def qwen3_30b_a3b(cls) -> "Qwen3MoeConfig":
+        return cls()
+
+    @classmethod
+    def qwen3_235b_a22b(cls) -> "Qwen3MoeConfig":
+        return cls(hidden_size=4096, num_hidden_layers=94, num_attention_heads=64,
+                   num_key_value_heads=4, head_dim=128, num_experts=128, num_experts_per_tok=8,
+                   moe_intermediate_size=1536, intermediate_size=12288)
+
+
+@dataclass
+class LayerWeights:
+    input_norm: torch.Tensor
+    post_norm: torch.Tensor
+    qkv: torch.Tensor            # [(Hq_l + 2 Hkv_l) * D, H]
+    q_norm: Optional[torch.Tensor]
+    k_norm: Optional[torch.Tensor]
+    o_proj: torch.Tensor         # [H, Hq_l * D]
+    router: Optional[torch.Tensor] = None   # [E, H]
+    w13: Optional[torch.Tensor] = None      # [E_l, 2I, H] (or [1, 2I_l, H] dense MLP)
+    w2: Optional[torch.Tensor] = None       # [E_l, H, I]
+    dense: bool = False
+
+
+@dataclass
+class AttnMeta:
+    """What attention needs besides q/k/v.  ``decode``: one row per sequence."""
+    kind: str                                   # "decode" | "prefill"
+    slots: torch.Tensor                         # [T] int32 cache slot per row, -1 skips
+    page_table: Optional[torch.Tensor] = None   # [B, max_pages] int32
+    seq_lens: Optional[torch.Tensor] = None     # [B] int32 keys to attend (incl. this step)
+    splits: int = 1
+    scratch: Optional[torch.Tensor] = None
+    cu_q: Optional[torch.Tensor] = None         # [n+1] int32
+    cu_k: Optional[torch.Tensor] = None
+    max_q: int = 0
+    max_k: int = 0
+    context_lens: Optional[list] = None         # per sequence keys already in the cache
+    logits_rows: Optional[torch.Tensor] = None  # rows whose logits are needed (int32)
+
+
+class Qwen3MoeModel:
+    def __init__(self, cfg: Qwen3MoeConfig, device="cpu", dtype=torch.bfloat16,
+                 ctx: Optional[ParallelContext] = None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.ctx = ctx or ParallelContext.single()
+        tp = self.ctx.tp_size
+        self.Hq = cfg.num_attention_heads // tp
+        assert cfg.num_attention_heads % tp == 0
+        # KV heads are replicated when the tensor group is wider than their count.
+        self.Hkv = max(1, cfg.num_key_value_heads // tp)
+        self.kv_rep = max(1, tp // cfg.num_key_value_heads)
+        self.D = cfg.head_dim
+        self.E_local = cfg.num_experts // self.ctx.ep_size if cfg.num_experts else 0
+        self.e_lo = self.E_local * self.ctx.ep_rank
+        self.inv_freq = R.rope_inv_freq(self.D, cfg.rope_theta, self.device)
+        self.scale = 1.0 / math.sqrt(self.D)
+        self.layers: list[LayerWeights] = []
+        self.embed: Optional[torch.Tensor] = None
+        self.final_norm: Optional[torch.Tensor] = None
+        self.lm_head: Optional[torch.Tensor] = None
+        self.vocab_lo = 0
+        self.vocab_hi = cfg.vocab_size
+        self._moe_ws: dict = {}
+
+    # ------------------------------------------------------------- weights --
+    def init_random(self, seed: int = 0, std: float = 0.02) -> "Qwen3MoeModel":
+        """Random N(0, std) weights of the architecture, generated per tensor on
+        the target device.  Every rank draws the full tensor from the same
+        generator state and keeps its shard, so a sharded model equals the
+        unsharded one."""
+        cfg, dev, dt = self.cfg, self.device, self.dtype
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)
+        tp, tr = self.ctx.tp_size, self.ctx.tp_rank
+
+        def rnd(*shape):
+            return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * std).to(dt)
+
+        def ones(n):
+            return torch.ones(n, device=dev, dtype=dt)
+
+        H, D = cfg.hidden_size, self.D
+        self.embed = rnd(cfg.vocab_size, H)
+        for i in range(cfg.num_hidden_layers):
+            q = rnd(cfg.num_attention_heads * D, H)
+            k = rnd(cfg.num_key_value_heads * D, H)
+            v = rnd(cfg.num_key_value_heads * D, H)
+            o = rnd(H, cfg.num_attention_heads * D)
+            lw = LayerWeights(input_norm=ones(H), post_norm=ones(H),
+                              qkv=self._shard_qkv(q, k, v), q_norm=ones(D), k_norm=ones(D),
+                              o_proj=o[:, tr * self.Hq * D:(tr + 1) * self.Hq * D].contiguous())
+            if cfg.is_moe_layer(i):
+                lw.router = rnd(cfg.num_experts, H)
+                I = cfg.moe_intermediate_size
+                w13 = torch.empty(self.E_local, 2 * I, H, device=dev, dtype=dt)
+                w2 = torch.empty(self.E_local, H, I, device=dev, dtype=dt)
+                for e in range(cfg.num_experts):
+                    gate, up, down = rnd(I, H), rnd(I, H), rnd(H, I)
+                    if self.e_lo <= e < self.e_lo + self.E_local:
+                        w13[e - self.e_lo, :I] = up
+                        w13[e - self.e_lo, I:] = gate
+                        w2[e - self.e_lo] = down
+                lw.w13, lw.w2 = w13, w2
+            else:
+                I = cfg.intermediate_size
+                gate, up, down = rnd(I, H), rnd(I, H), rnd(H, I)
+                Il = I // tp
+                sl = slice(tr * Il, (tr + 1) * Il)
+                lw.w13 = torch.cat([up[sl], gate[sl]], 0).unsqueeze(0).contiguous()
+                lw.w2 = down[:, sl].contiguous().unsqueeze(0)
+                lw.dense = True
+            self.layers.append(lw)
+        self.final_norm = ones(H)
+        self.lm_head = self.embed if cfg.tie_word_embeddings else rnd(cfg.vocab_size, H)
+        self._shard_vocab()
+        return self
+
+    def _shard_qkv(self, q, k, v):
+        tr, D = self.ctx.tp_rank, self.D
+        qs = q[tr * self.Hq * D:(tr + 1) * self.Hq * D]
+        kv_idx = tr // self.kv_rep if self.kv_rep > 1 else tr
+        ks = k[kv_idx * self.Hkv * D:(kv_idx + 1) * self.Hkv * D]
+        vs = v[kv_idx * self.Hkv * D:(kv_idx + 1) * self.Hkv * D]
+        return torch.cat([qs, ks, vs], 0).contiguous()
+
+    def _shard_vocab(self):
+        """LM head rows are split over the tensor group (all-gather of logits)."""
+        tp, tr = self.ctx.tp_size, self.ctx.tp_rank
+        if tp == 1:
+            return
+        V = self.cfg.vocab_size
+        per = (V + tp - 1) // tp
+        self.vocab_lo, self.vocab_hi = tr * per, min(V, (tr + 1) * per)
+        head = self.lm_head[self.vocab_lo:self.vocab_hi]
+        if head.shape[0] < per:      # pad so every rank gathers equal blocks
+            pad = torch.zeros(per - head.shape[0], head.shape[1], dtype=head.dtype,
+                              device=head.device)
+            head = torch.cat([head, pad], 0)
+        self.lm_head = head.contiguous()
+
+    def load_state(self, loader) -> "Qwen3MoeModel":
+        """Loads Hugging Face tensor names through ``loader.get(name)``."""
+        cfg, dev, dt, D = self.cfg, self.device, self.dtype, self.D
+        tp, tr = self.ctx.tp_size, self.ctx.tp_rank
+
+        def get(name):
+            return loader.get(name).to(device=dev, dtype=dt)
+
+        self.embed = get("model.embed_tokens.weight")
+        for i in range(cfg.num_hidden_layers):
+            p = f"model.layers.{i}."
+            q, k, v = (get(p + f"self_attn.{n}_proj.weight") for n in "qkv")
+            o = get(p + "self_attn.o_proj.weight")
+            lw = LayerWeights(
+                input_norm=get(p + "input_layernorm.weight"),
+                post_norm=get(p + "post_attention_layernorm.weight"),
+                qkv=self._shard_qkv(q, k, v),
+                q_norm=get(p + "self_attn.q_norm.weight") if loader.has(p + "self_attn.q_norm.weight") else None,
+                k_norm=get(p + "self_attn.k_norm.weight") if loader.has(p + "self_attn.k_norm.weight") else None,
+                o_proj=o[:, tr * self.Hq * D:(tr + 1) * self.Hq * D].contiguous())
+            if cfg.is_moe_layer(i):
+                lw.router = get(p + "mlp.gate.weight")
+                I = cfg.moe_intermediate_size
+                w13 = torch.empty(self.E_local, 2 * I, cfg.hidden_size, device=dev, dtype=dt)
+                w2 = torch.empty(self.E_local, cfg.hidden_size, I, device=dev, dtype=dt)
+                for e in range(self.e_lo, self.e_lo + self.E_local):
+                    pe = p + f"mlp.experts.{e}."
+                    w13[e - self.e_lo, :I] = get(pe + "up_proj.weight")
+                    w13[e - self.e_lo, I:] = get(pe + "gate_proj.weight")
+                    w2[e - self.e_lo] = get(pe + "down_proj.weight")
+                lw.w13, lw.w2 = w13, w2
+            else:
+                gate, up, down = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
+                Il = gate.shape[0] // tp
+                sl = slice(tr * Il, (tr + 1) * Il)
+                lw.w13 = torch.cat([up[sl], gate[sl]], 0).unsqueeze(0).contiguous()
+                lw.w2 = down[:, sl].contiguous().unsqueeze(0)
+                lw.dense = True
+            self.layers.append(lw)
+        self.final_norm = get("model.norm.weight")
+        self.lm_head = (self.embed if cfg.tie_word_embeddings or not loader.has("lm_head.weight")
+                        else get("lm_head.weight"))
+        self._shard_vocab()
+        return self
+
+    # -------------------------------------------------------------- forward --
+    def _attention(self, lw: LayerWeights, x, positions, meta: AttnMeta, kcache, vcache):
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        T = x.shape[0]
+        qkv = F.linear(x, lw.qkv)
+        F.qk_norm_rope_kv_(qkv, lw.q_norm, lw.k_norm, positions, self.inv_freq, meta.slots,
+                           kcache, vcache, Hq, Hkv, D, eps=self.cfg.rms_norm_eps)
+        if meta.kind == "decode":
+            q = qkv[:, :Hq * D] if qkv.is_cuda else qkv[:, :Hq * D].reshape(T, Hq, D)
+            att = F.paged_decode_attention(q, kcache, vcache, meta.page_table, meta.seq_lens,
+                                           self.scale, meta.splits, self.cfg.sliding_window,
+                                           scratch=meta.scratch, Hq=Hq, D=D)
+        else:
+            from ..ops.attention import prefill_attention
+            att = prefill_attention(qkv, Hq, Hkv, D, meta, kcache, vcache, self.scale)
+        out = F.linear(att.reshape(T, Hq * D), lw.o_proj)
+        return self.ctx.all_reduce_tp(out)
+
+    def _mlp(self, lw: LayerWeights, x):
+        cfg = self.cfg
+        T = x.shape[0]
+        if lw.dense:
+            h = F.linear_gated(x, lw.w13[0])
+            return self.ctx.all_reduce_tp(F.linear(h, lw.w2[0]))
+        logits = F.linear(x, lw.router, out_dtype=torch.float32)
+        ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
+        ws = None
+        if x.is_cuda:
+            key = (T, x.device)
+            ws = self._moe_ws.get(key)
+            if ws is None:
+                ws = F.MoeWorkspace.create(T, cfg.num_experts_per_tok, self.E_local,
+                                           cfg.hidden_size, cfg.moe_intermediate_size, x.device)
+                self._moe_ws[key] = ws
+        out = F.moe_experts(x, ids, weights, lw.w13, lw.w2, e_lo=self.e_lo, ws=ws)
+        if self.ctx.ep_size > 1:
+            out = self.ctx.all_reduce_tp(out)
+        return out
+
+    def forward(self, input_ids, positions, meta: AttnMeta, kv_caches) -> torch.Tensor:
+        """Returns the final-normed hidden rows [T, H] (bf16).
+        ``kv_caches[layer] = (k, v)`` each [pages, page_size, Hkv_local, D]."""
+        hidden = F.embedding(input_ids, self.embed)
+        residual = None
+        for i, lw in enumerate(self.layers):
+            x, residual = F.add_rmsnorm(hidden, residual, lw.input_norm, self.cfg.rms_norm_eps)
+            kc, vc = kv_caches[i]
+            mixed = self._attention(lw, x, positions, meta, kc, vc)
+            x, residual = F.add_rmsnorm(mixed, residual, lw.post_norm, self.cfg.rms_norm_eps)
+            hidden = self._mlp(lw, x)
+        x, _ = F.add_rmsnorm(hidden, residual, self.final_norm, self.cfg.rms_norm_eps)
+        return x
+
+    def logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
+        """FP32 logits [rows, vocab]; vocab-sharded heads are all-gathered and un-padded."""
+        lg = F.linear(hidden_rows, self.lm_head, out_dtype=torch.float32)
+        if self.ctx.tp_size > 1:
+            lg = self.ctx.all_gather_tp_cols(lg)[:, :self.cfg.vocab_size]
+        return lg
+
+    # ------------------------------------------------------------- caches --
+    def new_kv_caches(self, num_pages: int, page_size: int = 16):
+        shape = (num_pages, page_size, self.Hkv, self.D)
+        return [(torch.zeros(shape, dtype=self.dtype, device=self.device),
+                 torch.zeros(shape, dtype=self.dtype, device=self.device))
+                for _ in range(self.cfg.num_hidden_layers)]
+
+    def kv_bytes_per_page(self, page_size: int = 16) -> int:
+        return 2 * page_size * self.Hkv * self.D * 2 * self.cfg.num_hidden_layers
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() + self.final_norm.numel()
+        if self.lm_head is not self.embed:
+            n += self.lm_head.numel()
+        for lw in self.layers:
+            for t in (lw.input_norm, lw.post_norm, lw.qkv, lw.q_norm, lw.k_norm, lw.o_proj,
+                      lw.router, lw.w13, lw.w2):
+                if t is not None:
+                    n += t.numel()
+        return n * 2

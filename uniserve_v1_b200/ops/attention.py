@@ -1,0 +1,59 @@
+"""Prefill / dense attention entry points over the varlen flash kernel.
+
+``prefill_attention`` serves the token path: rows of the fused QKV projection
+(already normalised and rotated, K/V already written to the paged cache) attend
+causally to their sequence.  A sequence with keys already in the cache (chunked
+prefill, prefix-cache hit) reads those pages back into a contiguous buffer in
+front of the new keys.
+
+``dense_attention`` serves the video transformer: bidirectional varlen attention
+with separate query and key offset tables (queries = every row, keys = used rows;
+reference: crates/models/src/minimax_h3/transformer.py:247-256 equivalent
+behaviour, reference project path).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import native as N
+from . import reference as R
+
+BF16 = torch.bfloat16
+
+
+def have_flash() -> bool:
+    try:
+        return hasattr(N.kernels(), "us_flash_attn_varlen")
+    except N.NativeMissing:
+        return False
+
+
+def varlen_attention(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, out=None):
+    """q [Tq, Hq, D], k/v [Tk, Hkv, D] (row-strided views allowed, last dim and
+    head dim contiguous); cu_* int32 [n+1].  Returns [Tq, Hq, D] bf16."""
+    if not q.is_cuda:
+        return R.varlen_attention(q, k, v, cu_q, cu_k, scale, causal)
+    from .flash import flash_attn_varlen
+    return flash_attn_varlen(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, out=out)
+
+
+def prefill_attention(qkv, Hq, Hkv, D, meta, kcache, vcache, scale):
+    T = qkv.shape[0]
+    v3 = qkv.view(T, Hq + 2 * Hkv, D)
+    q, k, v = v3[:, :Hq], v3[:, Hq:Hq + Hkv], v3[:, Hq + Hkv:]
+    ctx_lens = meta.context_lens
+    if ctx_lens is not None and any(c > 0 for c in ctx_lens):
+        # Keys already cached sit in front of this call's keys of each sequence.
+        page = kcache.shape[1]
+        ks, vs = [], []
+        cu_q = meta.cu_q.tolist()
+        for i, c in enumerate(ctx_lens):
+            if c > 0:
+                npg = (c + page - 1) // page
+                idx = meta.page_table[i, :npg].long()
+                ks.append(kcache[idx].reshape(-1, Hkv, D)[:c])
+                vs.append(vcache[idx].reshape(-1, Hkv, D)[:c])
+            ks.append(k[cu_q[i]:cu_q[i + 1]])
+            vs.append(v[cu_q[i]:cu_q[i + 1]])
+        k, v = torch.cat(ks, 0), torch.cat(vs, 0)
+    return varlen_attention(q, k, v, meta.cu_q, meta.cu_k, meta.max_q, meta.max_k, scale, True)

@@ -1,0 +1,33 @@
+"""Varlen flash attention (tcgen05) binding."""
+from __future__ import annotations
+
+import torch
+
+from . import native as N
+from . import reference as R
+
+BF16 = torch.bfloat16
+
+N.register_signatures({
+    "us_flash_attn_varlen": (N.I, [N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.I, N.I,
+                                   N.I, N.L, N.L, N.L, N.L, N.F, N.I, N.P]),
+})
+
+
+def flash_attn_varlen(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, out=None):
+    """q [Tq, Hq, D], k/v [Tk, Hkv, D] bf16 with contiguous (head, dim) and any
+    row stride; cu_q/cu_k int32 [n+1] on the device.  Returns [Tq, Hq, D]."""
+    lib = N.kernels()
+    if not hasattr(lib, "us_flash_attn_varlen"):
+        return R.varlen_attention(q, k, v, cu_q, cu_k, scale, causal)
+    Tq, Hq, D = q.shape
+    Tk, Hkv, _ = k.shape
+    assert q.dtype == BF16 and q.stride(2) == 1 and q.stride(1) == D
+    assert k.stride(2) == 1 and k.stride(1) == D and v.stride(2) == 1 and v.stride(1) == D
+    if out is None:
+        out = torch.empty(Tq, Hq, D, dtype=BF16, device=q.device)
+    n = cu_q.numel() - 1
+    N.call("us_flash_attn_varlen", N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(cu_q),
+           N.ptr(cu_k), n, Tq, Tk, Hq, Hkv, D, max_q, q.stride(0), k.stride(0), v.stride(0),
+           out.stride(0), scale, int(causal), N.stream())
+    return out
