@@ -1,0 +1,267 @@
+#!/usr/bin/env python
+"""Headline benchmark: Qwen3-MoE output tokens/s on the Qwen3-30B-A3B shape.
+
+Workload (the reference's chat-serving configuration): 64 concurrent requests,
+1024 uniform-random prompt ids each, bf16 random-init weights, paged KV with
+16-token pages, greedy decode from CUDA graphs.  A *step* is one decode step of
+the engine over all concurrent requests (64 output tokens); the prompts are
+prefilled before the timed region, so the context grows from 1024 during it.
+``value`` = concurrent_requests * K / device time of K steps (CUDA events on the
+launching stream, max over ranks).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+N > 1 is launched under ``torch.distributed.run`` (one rank per GPU): the
+tensor group spans all ranks, attention heads are split over it and every rank
+holds 128/N whole experts (the total work is fixed, so scaling is "strong").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+BASELINE_TOK_S = 64 / 20.5e-3   # reference: 64 concurrent, 20.5 ms/step on 1xGB200 (docs/configuration.md:468)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def reference_arm(args) -> int:
+    """The reference is a Rust workspace: the offline pip install of its tree
+    yields only package metadata (no `uniserve` executable: it needs cargo /
+    rustc 1.96 and setuptools-rust, absent from this image), and serving also
+    needs Hugging Face checkpoints, FFmpeg 8.1 and NCCL >= 2.30.4."""
+    ref = Path(__file__).resolve().parent / "baseline" / "_ref"
+    exe = list(ref.glob("bin/uniserve")) if ref.exists() else []
+    why = ("reference is a Rust serving binary; offline pip install of /root/reference produced "
+           "metadata only (no cargo/rustc, no setuptools-rust), so no `uniserve` executable, "
+           "checkpoints, FFmpeg 8.1 or NCCL>=2.30.4 exist to run it")
+    if exe:
+        why = "reference executable present but cannot serve without checkpoints and its Build Server toolchain"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--concurrency", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--model", default="qwen3-30b-a3b", choices=["qwen3-30b-a3b", "tiny"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="profiling only: cut the layer count (the printed line is then marked "
+                         "profile_only and is not a benchmark value)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.ops import native
+    from uniserve_v1_b200.parallel.context import ParallelContext
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    ctx = ParallelContext.single()
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        ctx = ParallelContext.from_world(tensor=world, expert_over_tensor=True)
+        from uniserve_v1_b200.parallel.symm import attach_fused
+        attach_fused(ctx, dev)
+
+    cfg = Qwen3MoeConfig.qwen3_30b_a3b() if args.model == "qwen3-30b-a3b" else Qwen3MoeConfig(
+        vocab_size=2048, hidden_size=512, num_hidden_layers=2, num_attention_heads=8,
+        num_key_value_heads=2, head_dim=128, num_experts=16, num_experts_per_tok=4,
+        moe_intermediate_size=256, eos_token_id=2047, max_position_embeddings=8192)
+    if args.layers:
+        cfg.num_hidden_layers = args.layers
+    K, W, C = args.steps, args.warmup, args.concurrency
+    total_steps = 2 * (K + W) + 8
+    max_len = args.prompt_len + total_steps + 16
+
+    t0 = time.time()
+    model = Qwen3MoeModel(cfg, dev, torch.bfloat16, ctx).init_random(seed=0)
+    eng = LLMEngine(model, max_num_seqs=C, max_model_len=max_len,
+                    max_num_batched_tokens=8192, enable_prefix_cache=False)
+    g = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist()
+               for _ in range(C)]
+    sp = SamplingParams(temperature=0.0, max_tokens=total_steps + 4, ignore_eos=True)
+    for p in prompts:
+        eng.add_request(p, sp)
+    # Prefill every prompt (outside the timed region); ends with all rows decoding.
+    while eng.scheduler.waiting or any(not r.output_ids for r in eng.scheduler.running):
+        eng.step()
+    torch.cuda.synchronize()
+    setup_s = time.time() - t0
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- end to end through the public API: every step copies its input block
+    # from pinned host memory and reads the sampled tokens back. ----
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(W):
+            eng.step()
+        h0, d0 = eng.runner.h2d_bytes, eng.runner.d2h_bytes
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(K):
+            eng.step()
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        e2e = {"value": C * K / (ms / 1e3), "unit": "output tokens/s",
+               "ms_per_step": ms / K,
+               "h2d_bytes_per_step": (eng.runner.h2d_bytes - h0) // K,
+               "d2h_bytes_per_step": (eng.runner.d2h_bytes - d0) // K}
+
+    # ---- device-timed decode steps: graph replays back to back, the device
+    # advances its own step state; weights (57 GB) exceed L2, no flush needed. ----
+    rows = list(eng.scheduler.running)
+    for r in rows:
+        need = eng.scheduler._pages_needed(r, r.num_tokens + K + W + 2)
+        r.pages.extend(eng.blocks.allocate(need))
+    runner = eng.runner
+    B = runner.bucket_for(len(rows))
+    blk = runner._decode_block(B)
+    runner._fill_decode(blk, rows, B)
+    graph = runner._graph(B, "greedy")
+    blk.upload()
+    for _ in range(W):
+        graph.graph.replay()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = native.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(K):
+        graph.graph.replay()
+        native.launch_count += graph.launches
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    native.raise_on_device_error()
+    launches = native.launch_count - launches0
+    value = C * K / (ms / 1e3)
+    if rank == 0:
+        line = {
+            "metric": "Qwen3-MoE output tokens/s", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+            "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": value / BASELINE_TOK_S, "dtype": "bf16",
+            "data": "synthetic (uniform-random prompt ids, random-init N(0,0.02) weights)",
+            "config": {"model": "Qwen3-30B-A3B-shaped" if args.model != "tiny" else "tiny",
+                       "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
+                       "experts": cfg.num_experts, "top_k": cfg.num_experts_per_tok,
+                       "global_batch": C, "seq_len": args.prompt_len,
+                       "context_during_timing": [rows[0].num_tokens, rows[0].num_tokens + K + W],
+                       "page_size": 16, "step": "one decode step of all concurrent requests",
+                       "parallelism": "tp1" if world == 1 else f"tp{world}-attention+ep{world}",
+                       "l2": "inputs larger than L2 (weights read per step >> 126 MB)",
+                       "baseline": "64 concurrent, 20.5 ms/step on 1xGB200 (reference docs)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "launches_per_step": graph.launches, "setup_s": round(setup_s, 1),
+        }
+        if args.layers:
+            line["profile_only"] = True
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -231,6 +231,22 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
+extern "C" int us_merge_decode_splits(const float* part_o, const float* part_lse, void* out,
+                                      long long ldo, int B, int Hq, int D, int splits,
+                                      void* stream) {
+  dim3 g2(B, Hq);
+  if (D == 128)
+    merge_splits_kernel<128><<<g2, 128, 0, (cudaStream_t)stream>>>(
+        part_o, part_lse, (__nv_bfloat16*)out, ldo, Hq, splits);
+  else if (D == 64)
+    merge_splits_kernel<64><<<g2, 64, 0, (cudaStream_t)stream>>>(
+        part_o, part_lse, (__nv_bfloat16*)out, ldo, Hq, splits);
+  else
+    return US_ERR_UNSUPPORTED;
+  US_LAUNCH_CHECK();
+  return US_OK;
+}
+
 // Bytes of scratch the split path needs: partial outputs then log-sum-exps.
 US_API long long us_paged_decode_scratch_bytes(int B, int Hq, int D, int splits) {
   return (long long)B * Hq * splits * (D + 1) * (long long)sizeof(float);

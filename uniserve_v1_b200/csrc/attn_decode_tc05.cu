@@ -1,0 +1,422 @@
+// Paged-KV decode attention on tcgen05 with the keys on the MMA M axis.
+//
+// A decode step has one query token per sequence, so a conventional attention
+// tile (queries on M) would be almost empty.  Here a tile is 128 keys:
+//
+//   S^T[key, head] = K_tile[128 keys x 128 d] . Q^T          (M=128, N=16, K=128)
+//   O^T[d,   head] = V_tile^T[128 d x 128 keys] . P[key, head] (M=128, N=16, K=128)
+//
+// K pages are TMA-loaded as the K-major A operand; the same V pages serve as an
+// MN-major A operand (d contiguous), so neither is transposed.  The G query
+// heads that share a kv head are the N columns (zero padded to 16).  Thread t
+// of the four softmax warps owns TMEM lane t: key t of the tile when it reads
+// S^T, channel d = t when it reads O^T; the running output lives in 16
+// registers per thread and is rescaled there, tensor memory holds only the
+// current tile's products.
+//
+// Grid = (sequence, kv head, split); with more than one split the CTAs write
+// normalised partial outputs and log-sum-exps and the merge kernel of
+// attn_decode.cu combines them.
+//
+// Roles: warps 0-3 softmax / output, warp 4 TMA producer, warp 5 TMEM owner +
+// MMA issuer.  Every wait is bounded.
+#include "include/us_common.cuh"
+#include "include/us_tc05.cuh"
+#include "include/us_tmap.h"
+
+namespace {
+
+constexpr int kD = 128;
+constexpr int kTileKeys = 128;
+constexpr int kNPad = 16;                    // padded head count (UMMA N)
+constexpr int kHalfBytes = kTileKeys * 128;  // one 64-column half of a K or V tile
+constexpr int kTileBytes = 2 * kHalfBytes;   // 32 KiB
+constexpr int kSmallHalf = kNPad * 128;      // one half of the Q or P operand (2 KiB)
+
+struct DecTcArgs {
+  const __nv_bfloat16* q;
+  const int* page_table;
+  const int* seq_lens;
+  __nv_bfloat16* out;
+  float* part_o;
+  float* part_lse;
+  long long ldq, ldo;
+  int B, Hq, Hkv, max_pages, page_size, splits, window;
+  float scale_log2;
+  unsigned int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int G>
+__global__ void __launch_bounds__(192)
+paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const DecTcArgs a) {
+  const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+
+  const int seq_len = a.seq_lens[b];
+  int begin_all = 0;
+  if (a.window > 0 && seq_len > a.window) begin_all = seq_len - a.window;
+  begin_all &= ~(a.page_size - 1);  // tiles start on a page; the head is masked
+  const int first_key = (a.window > 0 && seq_len > a.window) ? seq_len - a.window : 0;
+  const int span = seq_len - begin_all;
+  const int tiles_all = (span + kTileKeys - 1) / kTileKeys;
+  const int tiles_per = (tiles_all + a.splits - 1) / a.splits;
+  const int k_begin = begin_all + split * tiles_per * kTileKeys;
+  const int k_end = min(seq_len, k_begin + tiles_per * kTileKeys);
+  const int ntiles = k_end > k_begin ? (k_end - k_begin + kTileKeys - 1) / kTileKeys : 0;
+
+  if (ntiles == 0) {  // nothing to attend in this split (uniform for the CTA)
+    if (tid < kD) {
+      for (int g = 0; g < G; ++g) {
+        const int h = hk * G + g;
+        if (a.splits == 1) {
+          a.out[(long long)b * a.ldo + (long long)h * kD + tid] = us::f2bf(0.f);
+        } else {
+          const long long base = ((long long)b * a.Hq + h) * a.splits + split;
+          a.part_o[base * kD + tid] = 0.f;
+          if (tid == 0) a.part_lse[base] = -INFINITY;
+        }
+      }
+    }
+    return;
+  }
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + kTileBytes;
+  uint8_t* sQ = smem + 2 * kTileBytes;
+  uint8_t* sP = sQ + 2 * kSmallHalf;
+  float* red = (float*)(sP + 2 * kSmallHalf);       // [2][4 warps][16] reduction scratch
+  uint64_t* bars = (uint64_t*)(red + 2 * 4 * kNPad);
+  uint64_t* k_full = bars + 0;
+  uint64_t* k_empty = bars + 1;
+  uint64_t* v_full = bars + 2;
+  uint64_t* v_empty = bars + 3;
+  uint64_t* s_full = bars + 4;
+  uint64_t* p_full = bars + 5;
+  uint64_t* o_full = bars + 6;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 7);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  if (tid == 0) {
+    tc::mbar_init(k_full, 1);
+    tc::mbar_init(k_empty, 1);
+    tc::mbar_init(v_full, 1);
+    tc::mbar_init(v_empty, 1);
+    tc::mbar_init(s_full, 1);
+    tc::mbar_init(p_full, 128);
+    tc::mbar_init(o_full, 1);
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 5) {
+    tc::tmem_alloc(tmem_slot, 32);
+    tc::tmem_relinquish();
+  }
+  // Q operand: rows = heads (zero padded to 16), K-major, 128-byte swizzle.
+  if (tid < 128) {
+    for (int c = tid; c < kNPad * 16; c += 128) {
+      const int g = c >> 4, ch = c & 15;  // 16-byte chunk ch of head row g
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (g < G)
+        v = *reinterpret_cast<const uint4*>(a.q + (long long)b * a.ldq +
+                                            (long long)(hk * G + g) * kD + ch * 8);
+      const int half = ch >> 3;
+      *reinterpret_cast<uint4*>(sQ + half * kSmallHalf + tc::sw128_offset(g, ch & 7)) = v;
+    }
+    // Rows of P that no head owns stay zero.
+    for (int c = tid; c < 2 * kSmallHalf / 16; c += 128)
+      reinterpret_cast<uint4*>(sP)[c] = make_uint4(0, 0, 0, 0);
+    tc::fence_async_smem();
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;
+  const uint32_t tmem_O = tmem_base + kNPad;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      tc::tma_prefetch_desc(&tmK);
+      tc::tma_prefetch_desc(&tmV);
+      const int* pt = a.page_table + (long long)b * a.max_pages;
+      const int pages_per_tile = kTileKeys / a.page_size;
+      const int seq_pages = (seq_len + a.page_size - 1) / a.page_size;
+      for (int t = 0; t < ntiles; ++t) {
+        const uint32_t ph = (uint32_t)t & 1u;
+        const int page0 = (k_begin + t * kTileKeys) / a.page_size;
+        if (!tc::mbar_wait(k_empty, ph ^ 1u, abort_flag)) {
+          us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc::mbar_expect_tx(k_full, kTileBytes);
+        for (int i = 0; i < pages_per_tile; ++i) {
+          const int pi = page0 + i;
+          const int page = (pi < seq_pages && pi < a.max_pages) ? pt[pi] : 0;
+          const int row = page * a.page_size;
+          uint8_t* dst = sK + i * a.page_size * 128;
+          tc::tma_load_2d(dst, &tmK, k_full, hk * kD, row);
+          tc::tma_load_2d(dst + kHalfBytes, &tmK, k_full, hk * kD + 64, row);
+        }
+        if (!tc::mbar_wait(v_empty, ph ^ 1u, abort_flag)) {
+          us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc::mbar_expect_tx(v_full, kTileBytes);
+        for (int i = 0; i < pages_per_tile; ++i) {
+          const int pi = page0 + i;
+          const int page = (pi < seq_pages && pi < a.max_pages) ? pt[pi] : 0;
+          const int row = page * a.page_size;
+          uint8_t* dst = sV + i * a.page_size * 128;
+          tc::tma_load_2d(dst, &tmV, v_full, hk * kD, row);
+          tc::tma_load_2d(dst + kHalfBytes, &tmV, v_full, hk * kD + 64, row);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t kIdescQK = tc::make_idesc(128, kNPad, tc::kFmtBF16, tc::kFmtBF16, 0, 0);
+      constexpr uint32_t kIdescPV = tc::make_idesc(128, kNPad, tc::kFmtBF16, tc::kFmtBF16, 1, 0);
+      const uint32_t k_addr = tc::smem_u32(sK), v_addr = tc::smem_u32(sV);
+      const uint32_t q_addr = tc::smem_u32(sQ), p_addr = tc::smem_u32(sP);
+      auto issue_qk = [&]() {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t half = kk >> 2, sub = kk & 3;
+          const uint64_t ad = tc::smem_desc_kmajor_sw128(k_addr + half * kHalfBytes) + 2 * sub;
+          const uint64_t bd = tc::smem_desc_kmajor_sw128(q_addr + half * kSmallHalf) + 2 * sub;
+          tc::umma_f16(tmem_S, ad, bd, kIdescQK, kk != 0);
+        }
+      };
+      bool ok = tc::mbar_wait(k_full, 0, abort_flag);
+      if (ok) {
+        tc::tc_fence_after_sync();
+        issue_qk();
+        tc::umma_commit(s_full);
+        tc::umma_commit(k_empty);
+      }
+      for (int t = 0; ok && t < ntiles; ++t) {
+        const uint32_t ph = (uint32_t)t & 1u;
+        // P(t) ready: S(t) has been consumed and O(t-1) has been read.
+        if (!tc::mbar_wait(p_full, ph, abort_flag)) { ok = false; break; }
+        if (t + 1 < ntiles) {
+          if (!tc::mbar_wait(k_full, ph ^ 1u, abort_flag)) { ok = false; break; }
+          tc::tc_fence_after_sync();
+          issue_qk();
+          tc::umma_commit(s_full);
+          tc::umma_commit(k_empty);
+        }
+        if (!tc::mbar_wait(v_full, ph, abort_flag)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // A = V^T: d on M (two 64-wide chunks, 16 KiB apart), 16 keys = two
+          // groups of eight rows (1 KiB apart) per instruction.
+          const uint64_t ad =
+              tc::smem_desc_mnmajor_sw128(v_addr + kk * 2048, kHalfBytes, 1024);
+          const uint32_t half = kk >> 2, sub = kk & 3;
+          const uint64_t bd = tc::smem_desc_kmajor_sw128(p_addr + half * kSmallHalf) + 2 * sub;
+          tc::umma_f16(tmem_O, ad, bd, kIdescPV, kk != 0);
+        }
+        tc::umma_commit(o_full);
+        tc::umma_commit(v_empty);
+      }
+      if (!ok) {
+        us_dev_fail(a.status, US_DEV_TIMEOUT_FULL);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ---- softmax / output threads: TMEM lane = tid ----
+    const uint32_t lane_addr = ((uint32_t)(warp * 32) << 16);
+    float m_run[G], l_part[G], o_acc[G], alpha_prev[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      m_run[g] = -INFINITY;
+      l_part[g] = 0.f;
+      o_acc[g] = 0.f;
+      alpha_prev[g] = 0.f;
+    }
+    bool ok = true;
+    for (int t = 0; t < ntiles; ++t) {
+      const uint32_t ph = (uint32_t)t & 1u;
+      if (!tc::mbar_wait(s_full, ph)) { ok = false; break; }
+      tc::tc_fence_after_sync();
+      uint32_t sr[16];
+      tc::tmem_ld16(tmem_S + lane_addr, sr);
+      tc::tmem_ld_wait();
+      const int key = k_begin + t * kTileKeys + tid;
+      const bool valid = key < k_end && key >= first_key;
+      float s[G];
+      float* rbuf = red + (t & 1) * 4 * kNPad;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        s[g] = valid ? __uint_as_float(sr[g]) * a.scale_log2 : -INFINITY;
+        const float wm = us::warp_max(s[g]);
+        if (lane == 0) rbuf[warp * kNPad + g] = wm;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      float alpha[G], p[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float tm = fmaxf(fmaxf(rbuf[g], rbuf[kNPad + g]),
+                               fmaxf(rbuf[2 * kNPad + g], rbuf[3 * kNPad + g]));
+        const float m_new = fmaxf(m_run[g], tm);
+        alpha[g] = (m_run[g] == -INFINITY) ? 0.f : ex2(m_run[g] - m_new);
+        p[g] = valid ? ex2(s[g] - m_new) : 0.f;
+        l_part[g] = l_part[g] * alpha[g] + p[g];
+        m_run[g] = m_new;
+      }
+      if (t > 0) {
+        // O(t-1) is complete: fold it in (it was produced under the previous
+        // maximum, so the previous tile's factor applies to the running sum).
+        if (!tc::mbar_wait(o_full, ph ^ 1u)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+        uint32_t orr[16];
+        tc::tmem_ld16(tmem_O + lane_addr, orr);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+          o_acc[g] = o_acc[g] * alpha_prev[g] + __uint_as_float(orr[g]);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) alpha_prev[g] = alpha[g];
+      // P^T -> smem as the K-major B operand: row = head, column = key of the tile.
+      {
+        const int half = tid >> 6, col = tid & 63;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          uint8_t* dst = sP + half * kSmallHalf + tc::sw128_offset(g, col >> 3) + (col & 7) * 2;
+          *reinterpret_cast<__nv_bfloat16*>(dst) = us::f2bf(p[g]);
+        }
+      }
+      tc::fence_async_smem();
+      tc::tc_fence_before_sync();
+      tc::mbar_arrive(p_full);
+    }
+    if (ok) {
+      const uint32_t ph = (uint32_t)(ntiles - 1) & 1u;
+      if (tc::mbar_wait(o_full, ph)) {
+        tc::tc_fence_after_sync();
+        uint32_t orr[16];
+        tc::tmem_ld16(tmem_O + lane_addr, orr);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+          o_acc[g] = o_acc[g] * alpha_prev[g] + __uint_as_float(orr[g]);
+        // Row sums: every thread holds the share of its keys.
+        float* rbuf = red;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float ws = us::warp_sum(l_part[g]);
+          if (lane == 0) rbuf[warp * kNPad + g] = ws;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float l = rbuf[g] + rbuf[kNPad + g] + rbuf[2 * kNPad + g] + rbuf[3 * kNPad + g];
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          const int h = hk * G + g;
+          if (a.splits == 1) {
+            a.out[(long long)b * a.ldo + (long long)h * kD + tid] = us::f2bf(o_acc[g] * inv);
+          } else {
+            const long long base = ((long long)b * a.Hq + h) * a.splits + split;
+            a.part_o[base * kD + tid] = o_acc[g] * inv;
+            // m_run is in the log2 domain; the merge kernel works in natural logs.
+            if (tid == 0)
+              a.part_lse[base] = l > 0.f ? (m_run[g] + log2f(l)) * 0.6931471805599453f : -INFINITY;
+          }
+        }
+      } else {
+        ok = false;
+      }
+    }
+    if (!ok) us_dev_fail(a.status, US_DEV_TIMEOUT_ACC);
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tc::tmem_dealloc(tmem_base, 32);
+  }
+}
+
+template <int G>
+int launch_tc(const CUtensorMap& tmK, const CUtensorMap& tmV, const DecTcArgs& a,
+              cudaStream_t stream) {
+  const size_t smem = 2 * kTileBytes + 4 * kSmallHalf + 2 * 4 * kNPad * 4 + 8 * 8 + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    US_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tc_kernel<G>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid(a.B, a.Hkv, a.splits);
+  paged_decode_tc_kernel<G><<<grid, 192, smem, stream>>>(tmK, tmV, a);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}
+
+}  // namespace
+
+extern "C" int us_merge_decode_splits(const float* part_o, const float* part_lse, void* out,
+                                      long long ldo, int B, int Hq, int D, int splits,
+                                      void* stream);
+
+// Same contract as us_paged_decode_attention (head_dim 128, page_size dividing 128).
+US_API int us_paged_decode_attention_tc(const void* q, const void* kcache, const void* vcache,
+                                        const int* page_table, const int* seq_lens, void* out,
+                                        void* scratch, int B, int Hq, int Hkv, int D,
+                                        int num_pages, int max_pages, int page_size, int splits,
+                                        int window, float scale, long long ldq, long long ldo,
+                                        void* stream_) {
+  US_REQUIRE(q && kcache && vcache && page_table && seq_lens && out);
+  US_REQUIRE(D == kD && Hkv >= 1 && Hq % Hkv == 0 && Hq / Hkv <= kNPad && splits >= 1);
+  US_REQUIRE(page_size >= 8 && page_size <= 128 && (kTileKeys % page_size) == 0);
+  US_REQUIRE(splits == 1 || scratch != nullptr);
+  US_REQUIRE((ldq % 8) == 0 && ((uintptr_t)q % 16) == 0);
+  if (B == 0) return US_OK;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  CUtensorMap tmK, tmV;
+  const uint64_t rows = (uint64_t)num_pages * page_size, cols = (uint64_t)Hkv * D;
+  int rc = us_tmap_2d(&tmK, kcache, US_TMAP_BF16, rows, cols, cols, page_size, 64, US_SWZ_128);
+  if (rc) return rc;
+  rc = us_tmap_2d(&tmV, vcache, US_TMAP_BF16, rows, cols, cols, page_size, 64, US_SWZ_128);
+  if (rc) return rc;
+  DecTcArgs a;
+  a.q = (const __nv_bfloat16*)q;
+  a.page_table = page_table;
+  a.seq_lens = seq_lens;
+  a.out = (__nv_bfloat16*)out;
+  a.part_o = (float*)scratch;
+  a.part_lse = scratch ? (float*)scratch + (long long)B * Hq * splits * D : nullptr;
+  a.ldq = ldq; a.ldo = ldo;
+  a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.max_pages = max_pages; a.page_size = page_size;
+  a.splits = splits; a.window = window;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = us_status_ptr();
+  const int G = Hq / Hkv;
+  switch (G) {
+    case 1: rc = launch_tc<1>(tmK, tmV, a, stream); break;
+    case 2: rc = launch_tc<2>(tmK, tmV, a, stream); break;
+    case 4: rc = launch_tc<4>(tmK, tmV, a, stream); break;
+    case 8: rc = launch_tc<8>(tmK, tmV, a, stream); break;
+    case 16: rc = launch_tc<16>(tmK, tmV, a, stream); break;
+    default: return US_ERR_UNSUPPORTED;
+  }
+  if (rc) return rc;
+  if (splits > 1)
+    return us_merge_decode_splits(a.part_o, a.part_lse, out, ldo, B, Hq, D, splits, stream_);
+  return US_OK;
+}

@@ -39,6 +39,10 @@ struct GemmArgs {
   const int* tile_rows;    // grouped: valid rows of each tile
   const int* num_tiles;    // grouped: device word, number of row tiles
   unsigned int* status;
+  // split-K (dense, single accumulator): the `splits` CTAs along z form one
+  // thread-block cluster; CTA z owns k-blocks [z * kb_per_split, ...).
+  int splits;
+  int kb_per_split;
 };
 
 constexpr int kBlockM = 128;
@@ -58,6 +62,47 @@ constexpr int tmem_cols(bool dual) {
   while (c < need) c <<= 1;
   return c;
 }
+
+// Per-thread epilogue of one output feature `m`: activation, bias, row scale,
+// row map, rounding.
+template <bool DUAL>
+struct Epilogue {
+  const GemmArgs& a;
+  const int m, row0;
+  const bool m_ok;
+  float bias;
+  __device__ __forceinline__ Epilogue(const GemmArgs& args, int group, int m_, int row0_)
+      : a(args), m(m_), row0(row0_), m_ok(m_ < args.M), bias(0.f) {
+    if (a.bias != nullptr && m_ok) {
+      const size_t bi = (size_t)group * a.M + m;
+      bias = a.bias_dtype == 0 ? us::bf2f(((const __nv_bfloat16*)a.bias)[bi])
+                               : ((const float*)a.bias)[bi];
+    }
+  }
+  __device__ __forceinline__ void store(int r, float val, float gate) const {
+    if (!m_ok) return;
+    if (DUAL) {
+      if (a.act == 0) {
+        val = val * silu_f(gate);
+      } else if (a.act == 1) {
+        const float sg = us::bf2f(us::f2bf(silu_f(us::bf2f(us::f2bf(gate)))));
+        val = us::bf2f(us::f2bf(val)) * sg;
+      } else {
+        val = val * gelu_tanh_f(gate);
+      }
+    }
+    val += bias;
+    int orow = row0 + r;
+    if (a.row_scale != nullptr) val *= a.row_scale[orow];
+    if (a.out_row_map != nullptr) orow = a.out_row_map[orow];
+    if (orow < 0) return;
+    const size_t o = (size_t)orow * a.ldo + m;
+    if (a.out_dtype == 0)
+      ((__nv_bfloat16*)a.out)[o] = us::f2bf(val);
+    else
+      ((float*)a.out)[o] = val;
+  }
+};
 
 template <int BN, bool DUAL>
 __global__ void __launch_bounds__(192)
@@ -108,7 +153,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const int num_k = (args.K + kBlockK - 1) / kBlockK;
+  const int num_k_total = (args.K + kBlockK - 1) / kBlockK;
+  const int kb0 = blockIdx.z * args.kb_per_split;
+  const int num_k = min(num_k_total - kb0, args.kb_per_split);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -124,11 +171,12 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         uint8_t* st = smem + (size_t)s * kStageBytes;
         tc::mbar_expect_tx(&full_bar[s], kStageBytes);
-        tc::tma_load_3d(st, &tmA, &full_bar[s], kb * kBlockK, m_tile * kBlockM, group);
+        const int kx = (kb0 + kb) * kBlockK;
+        tc::tma_load_3d(st, &tmA, &full_bar[s], kx, m_tile * kBlockM, group);
         if (DUAL)
-          tc::tma_load_3d(st + kATile, &tmA, &full_bar[s], kb * kBlockK,
+          tc::tma_load_3d(st + kATile, &tmA, &full_bar[s], kx,
                           args.dual_offset + m_tile * kBlockM, group);
-        tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmB, &full_bar[s], kb * kBlockK, row0);
+        tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmB, &full_bar[s], kx, row0);
       }
     }
   } else if (warp == 1) {
@@ -164,57 +212,62 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const int m = m_tile * kBlockM + q * 32 + lane;
-    const bool m_ok = m < args.M;
+    const int ml = q * 32 + lane;
     if (tc::mbar_wait(acc_bar, 0, abort_flag)) {
       tc::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-      float bias = 0.f;
-      if (args.bias != nullptr && m_ok) {
-        const size_t bi = (size_t)group * args.M + m;
-        bias = args.bias_dtype == 0 ? us::bf2f(((const __nv_bfloat16*)args.bias)[bi])
-                                    : ((const float*)args.bias)[bi];
-      }
+      if (!DUAL && args.splits > 1) {
+        // Split-K: park the FP32 partial tile [row][feature] in this CTA's shared
+        // memory (the pipeline stages are idle now); the cluster reduces it below.
+        float* part = reinterpret_cast<float*>(smem);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        if (c >= nrows) break;  // warp-uniform
-        uint32_t v[16], g[16];
-        tc::tmem_ld16(taddr + c, v);
-        if (DUAL) tc::tmem_ld16(taddr + BN + c, g);
-        tc::tmem_ld_wait();
+        for (int c = 0; c < BN; c += 16) {
+          if (c >= nrows) break;
+          uint32_t v[16];
+          tc::tmem_ld16(taddr + c, v);
+          tc::tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int r = c + j;
-          if (r < nrows && m_ok) {
-            float val = __uint_as_float(v[j]);
-            if (DUAL) {
-              const float gate = __uint_as_float(g[j]);
-              if (args.act == 0) {
-                val = val * silu_f(gate);
-              } else if (args.act == 1) {
-                const float sg = us::bf2f(us::f2bf(silu_f(us::bf2f(us::f2bf(gate)))));
-                val = us::bf2f(us::f2bf(val)) * sg;
-              } else {
-                val = val * gelu_tanh_f(gate);
-              }
-            }
-            val += bias;
-            int orow = row0 + r;
-            if (args.row_scale != nullptr) val *= args.row_scale[orow];
-            if (args.out_row_map != nullptr) orow = args.out_row_map[orow];
-            if (orow >= 0) {
-              const size_t o = (size_t)orow * args.ldo + m;
-              if (args.out_dtype == 0)
-                ((__nv_bfloat16*)args.out)[o] = us::f2bf(val);
-              else
-                ((float*)args.out)[o] = val;
-            }
-          }
+          for (int j = 0; j < 16; ++j) part[(c + j) * kBlockM + ml] = __uint_as_float(v[j]);
+        }
+      } else {
+        Epilogue<DUAL> epi(args, group, m_tile * kBlockM + ml, row0);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if (c >= nrows) break;  // warp-uniform
+          uint32_t v[16], g[16];
+          tc::tmem_ld16(taddr + c, v);
+          if (DUAL) tc::tmem_ld16(taddr + BN + c, g);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c + j < nrows)
+              epi.store(c + j, __uint_as_float(v[j]), DUAL ? __uint_as_float(g[j]) : 0.f);
         }
       }
     } else {
       us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
     }
+  }
+  if (!DUAL && args.splits > 1) {
+    // The `splits` CTAs of a tile form one cluster along z.  After the first
+    // cluster barrier every partial is visible through distributed shared
+    // memory; CTA r sums rows r, r + splits, ... over the CTAs in rank order (a
+    // fixed order, so the result does not depend on timing) and stores them.
+    tc::cluster_sync();
+    if (warp >= 2 && !*abort_flag) {
+      const int q = warp & 3;
+      const int ml = q * 32 + lane;
+      const uint32_t my_rank = tc::cluster_ctarank();
+      Epilogue<false> epi(args, group, m_tile * kBlockM + ml, row0);
+      const uint32_t local = tc::smem_u32(smem) + (uint32_t)ml * 4u;
+      for (int r = (int)my_rank; r < nrows; r += args.splits) {
+        float acc = 0.f;
+        for (int sp = 0; sp < args.splits; ++sp)
+          acc += tc::ld_dsmem_f32(tc::map_to_cta(local + (uint32_t)r * kBlockM * 4u, sp));
+        epi.store(r, acc, 0.f);
+      }
+    }
+    tc::cluster_sync();  // peers may still be reading this CTA's partial
   }
   tc::tc_fence_before_sync();
   __syncthreads();
@@ -230,11 +283,24 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs a, int m_til
   constexpr int kBTile = BN * kBlockK * 2;
   constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
   const int num_k = (a.K + kBlockK - 1) / kBlockK;
+  // Split K over a cluster when a dense launch would leave most SMs idle
+  // (skinny weights): up to 8 CTAs per tile, at least two k-blocks each.
+  int splits = 1;
+  const int tiles = m_tiles * n_tiles;
+  if (!DUAL && BN <= 64 && a.num_tiles == nullptr && tiles < 96 && num_k >= 4) {
+    splits = (200 + tiles - 1) / tiles;
+    if (splits > num_k / 2) splits = num_k / 2;
+    if (splits > 8) splits = 8;
+  }
+  int kb_per = (num_k + splits - 1) / splits;
+  splits = (num_k + kb_per - 1) / kb_per;
+  a.splits = splits;
+  a.kb_per_split = kb_per;
   // Small row tiles are memory-bound: keep two CTAs per SM resident.
   const int budget = (BN <= 64 && !DUAL) ? 100 * 1024 : (BN <= 32 ? 104 * 1024 : 200 * 1024);
   int stages = budget / kStageBytes;
   if (stages > 8) stages = 8;
-  if (stages > num_k) stages = num_k;
+  if (stages > kb_per) stages = kb_per;
   if (stages < 1) stages = 1;
   a.stages = stages;
   const size_t smem = (size_t)stages * kStageBytes + (2 * stages + 1) * 8 + 16 + 1024;
@@ -244,9 +310,22 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs a, int m_til
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     configured = true;
   }
-  dim3 grid(m_tiles, n_tiles);
-  gemm_wx_kernel<BN, DUAL><<<grid, 192, smem, stream>>>(tmA, tmB, a);
-  US_LAUNCH_CHECK();
+  // The split-K partial tile (BN x 128 fp32, BN <= 64) reuses the stage memory:
+  // at least two stages of >= 18 KiB each are always there for it.
+  const size_t smem_needed = smem;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(m_tiles, n_tiles, splits);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem_needed;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  US_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_wx_kernel<BN, DUAL>, tmA, tmB, a));
   return US_OK;
 }
 
@@ -297,6 +376,8 @@ US_API int us_gemm_wx(const void* W, const void* X, void* out, int G, int w_rows
   a.tile_rows = tile_rows;
   a.num_tiles = num_tiles;
   a.status = us_status_ptr();
+  a.splits = 1;
+  a.kb_per_split = 0;
 
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
   const int n_tiles = num_tiles ? max_tiles : (x_rows + block_n - 1) / block_n;

@@ -45,12 +45,14 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
                                       int* __restrict__ slots, const int* __restrict__ page_table,
                                       int max_pages, int page_size, int B,
                                       const int* __restrict__ live, int* __restrict__ history,
-                                      int history_stride, const int* __restrict__ step) {
+                                      int history_stride, int history_rows,
+                                      const int* __restrict__ step) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   const bool on = !live || b < *live;
   const int tok = sampled[b];
-  if (history && step) history[(long long)(*step) * history_stride + b] = on ? tok : -1;
+  if (history && step && *step >= 0 && *step < history_rows)
+    history[(long long)(*step) * history_stride + b] = on ? tok : -1;
   if (!on) {
     slots[b] = -1;
     return;
@@ -104,15 +106,15 @@ US_API int us_gather_rows(const void* src, const int* idx, int M, int H, long lo
 
 US_API int us_decode_advance(const int* sampled, int* input_ids, int* positions, int* seq_lens,
                              int* slots, const int* page_table, int max_pages, int page_size,
-                             int B, const int* live, int* history, int history_stride, int* step,
-                             void* stream_) {
+                             int B, const int* live, int* history, int history_stride,
+                             int history_rows, int* step, void* stream_) {
   US_REQUIRE(sampled && input_ids && positions && seq_lens && slots && page_table && B >= 0);
   if (B == 0) return US_OK;
   cudaStream_t stream = (cudaStream_t)stream_;
   decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(sampled, input_ids, positions,
                                                              seq_lens, slots, page_table, max_pages,
                                                              page_size, B, live, history,
-                                                             history_stride, step);
+                                                             history_stride, history_rows, step);
   US_LAUNCH_CHECK();
   if (step) {
     bump_kernel<<<1, 1, 0, stream>>>(step);

@@ -130,6 +130,36 @@ class LLMEngine:
                 errors[rid] = f"{ErrorClass.NUMERICAL_FAULT.value}: sampled token {tok}"
         return self.scheduler.update(batch, sampled, lps, errors)
 
+    def decode_burst(self, steps: int) -> list:
+        """Multi-step decode: when every running request is decoding, ensures
+        pages for ``steps`` more tokens, replays the decode graph ``steps`` times
+        with the device advancing its own step state, then applies the tokens.
+        Requests that stop inside the burst drop their surplus tokens."""
+        sch = self.scheduler
+        rows = [r for r in sch.running if r.output_ids and r.num_computed == r.num_tokens - 1]
+        if not rows or len(rows) != len(sch.running) or sch.waiting:
+            return self.step()
+        steps = min(steps, self.runner.history_steps,
+                    min(self.config.max_model_len - r.num_tokens for r in rows))
+        if steps <= 1 or self.runner.variant_for(rows) == "logits":
+            return self.step()
+        for r in rows:
+            pages = self.blocks.allocate(sch._pages_needed(r, r.num_tokens + steps))
+            if pages is None:
+                return self.step()
+            r.pages.extend(pages)
+        toks, _ = self.runner.decode(rows, steps)
+        outs = []
+        from .scheduler import Batch, Chunk
+        for s_ in range(steps):
+            live = [(i, r) for i, r in enumerate(rows) if not r.finished]
+            if not live:
+                break
+            batch = Batch("decode", [Chunk(r, r.num_tokens - 1, 1, True) for _, r in live])
+            sch.stats["decode_tokens"] += len(live)
+            outs.extend(sch.update(batch, {r.request_id: int(toks[s_, i]) for i, r in live}))
+        return outs
+
     # -------------------------------------------------------------- generate --
     def generate(self, prompts: list, params=None, on_output=None) -> list:
         """Runs the prompts to completion; returns the output token lists in

@@ -65,6 +65,7 @@ class DecodeGraph:
     bucket: int
     logits: Optional[torch.Tensor]
     sampled: torch.Tensor
+    launches: int = 0
 
 
 class CausalLmRunner:
@@ -168,12 +169,14 @@ class CausalLmRunner:
         graph = torch.cuda.CUDAGraph()
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
+        before = N.launch_count
         with torch.cuda.graph(graph, pool=self._pool):
             logits, sampled = self._decode_body(blk, B, variant)
+        launches = N.launch_count - before
         blk.dev.copy_(saved)
         torch.cuda.synchronize()
         N.raise_on_device_error()
-        g = DecodeGraph(graph, variant, B, logits, sampled)
+        g = DecodeGraph(graph, variant, B, logits, sampled, launches)
         self._graphs[key] = g
         return g
 
@@ -237,6 +240,7 @@ class CausalLmRunner:
         for _ in range(steps):
             if g is not None:
                 g.graph.replay()
+                N.launch_count += g.launches
                 logits, sampled = g.logits, g.sampled
             else:
                 logits, sampled = self._decode_body(blk, B, variant)

@@ -130,6 +130,10 @@ def qk_norm_rope3_(q, k, qw, kw, coords, inv_freq, Hq, Hk, D, freqs_per_axis, ep
 
 
 # -------------------------------------------------------------- attention --
+import os as _os
+DECODE_SIMT = _os.environ.get("US_DECODE_SIMT", "0") == "1"   # A/B switch: CUDA-core kernel
+
+
 def decode_splits(B: int, Hkv: int, max_len: int, sm_count: int = 148) -> int:
     """Number of KV splits so the grid fills the GPU about twice over."""
     ctas = max(1, B * Hkv)
@@ -157,6 +161,13 @@ def paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, split
     if splits > 1 and scratch is None:
         nbytes = N.kernels().us_paged_decode_scratch_bytes(B, Hq, D, splits)
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    if D == 128 and 128 % page_size == 0 and Hq // Hkv <= 16 and not DECODE_SIMT:
+        # keys-on-M tcgen05 kernel
+        N.call("us_paged_decode_attention_tc", N.ptr(q), N.ptr(kcache), N.ptr(vcache),
+               N.ptr(page_table), N.ptr(seq_lens), N.ptr(out), N.ptr(scratch), B, Hq, Hkv, D,
+               pages, page_table.shape[1], page_size, splits, window, scale, ldq, ldo,
+               N.stream(), launches=2 if splits > 1 else 1)
+        return out
     N.call("us_paged_decode_attention", N.ptr(q), N.ptr(kcache), N.ptr(vcache),
            N.ptr(page_table), N.ptr(seq_lens), N.ptr(out), N.ptr(scratch), B, Hq, Hkv, D,
            page_table.shape[1], page_size, splits, window, scale, ldq, ldo, N.stream(),
@@ -389,7 +400,7 @@ def decode_advance_(sampled, input_ids, positions, seq_lens, slots, page_table, 
         pg = page_table[torch.arange(n), pos // page_size]
         slots[:n] = pg * page_size + (pos % page_size).to(slots.dtype)
         slots[n:] = -1
-        if history is not None and step is not None:
+        if history is not None and step is not None and int(step) < history.shape[0]:
             history[int(step)] = -1
             history[int(step), :n] = sampled[:n]
             step += 1
@@ -397,4 +408,5 @@ def decode_advance_(sampled, input_ids, positions, seq_lens, slots, page_table, 
     N.call("us_decode_advance", N.ptr(sampled), N.ptr(input_ids), N.ptr(positions),
            N.ptr(seq_lens), N.ptr(slots), N.ptr(page_table), page_table.shape[1], page_size, B,
            N.ptr(live), N.ptr(history), history.shape[1] if history is not None else 0,
+           history.shape[0] if history is not None else 0,
            N.ptr(step), N.stream(), launches=2 if step is not None else 1)

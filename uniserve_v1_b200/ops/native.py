@@ -47,6 +47,7 @@ _SIGNATURES = {
     "us_qk_norm_rope3": (I, [P, P, P, P, P, P, I, I, I, I, I, L, L, F, P]),
     "us_paged_decode_scratch_bytes": (L, [I, I, I, I]),
     "us_paged_decode_attention": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, L, L, P]),
+    "us_paged_decode_attention_tc": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, L, L, P]),
     "us_topk_softmax": (I, [P, P, P, I, I, I, I, P, P, P, P]),
     "us_moe_sort": (I, [P, I, I, I, I, I, P, P, P, P, P, P, P, P]),
     "us_moe_gather": (I, [P, P, P, I, I, I, P, P]),
@@ -57,7 +58,7 @@ _SIGNATURES = {
     "us_logprob_stats": (I, [P, I, I, L, P, P, P, P, P]),
     "us_embedding": (I, [P, P, I, I, I, I, P, P]),
     "us_gather_rows": (I, [P, P, I, I, L, P, P]),
-    "us_decode_advance": (I, [P, P, P, P, P, P, I, I, I, P, P, I, P, P]),
+    "us_decode_advance": (I, [P, P, P, P, P, P, I, I, I, P, P, I, I, P, P]),
     "us_cast": (I, [P, P, L, I, P]),
 }
 
