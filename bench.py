@@ -134,6 +134,16 @@ def main() -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    t_start = time.time()
+
+    def mark(what: str) -> None:
+        """Progress trace (one file per rank) when BENCH_TRACE names a directory."""
+        d = os.environ.get("BENCH_TRACE")
+        if d:
+            with open(os.path.join(d, f"bench_rank{rank}.log"), "a") as f:
+                f.write(f"{time.time() - t_start:8.2f}s {what}\n")
+
+    mark("start")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     ctx = ParallelContext.single()
@@ -141,8 +151,11 @@ def main() -> int:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
         ctx = ParallelContext.from_world(tensor=world, expert_over_tensor=True)
-        from uniserve_v1_b200.parallel.symm import attach_fused
-        attach_fused(ctx, dev)
+        mark("groups ready")
+        if os.environ.get("US_NO_FUSED", "0") != "1":
+            from uniserve_v1_b200.parallel.symm import attach_fused
+            attach_fused(ctx, dev, hidden=2048 if args.model != "tiny" else 512)
+        mark("heap attached")
 
     cfg = Qwen3MoeConfig.qwen3_30b_a3b() if args.model == "qwen3-30b-a3b" else Qwen3MoeConfig(
         vocab_size=2048, hidden_size=512, num_hidden_layers=2, num_attention_heads=8,
@@ -169,6 +182,7 @@ def main() -> int:
         eng.step()
     torch.cuda.synchronize()
     setup_s = time.time() - t0
+    mark("prefill done")
 
     def barrier():
         if world > 1:
@@ -181,6 +195,7 @@ def main() -> int:
     if not args.no_e2e:
         for _ in range(W):
             eng.step()
+            mark("e2e warm-up step")
         h0, d0 = eng.runner.h2d_bytes, eng.runner.d2h_bytes
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -199,6 +214,7 @@ def main() -> int:
                "h2d_bytes_per_step": (eng.runner.h2d_bytes - h0) // K,
                "d2h_bytes_per_step": (eng.runner.d2h_bytes - d0) // K}
 
+    mark("e2e done")
     # ---- device-timed decode steps: graph replays back to back, the device
     # advances its own step state; weights (57 GB) exceed L2, no flush needed. ----
     rows = list(eng.scheduler.running)
@@ -213,11 +229,11 @@ def main() -> int:
     blk.upload()
     for _ in range(W):
         graph.graph.replay()
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    barrier()
     launches0 = native.launch_count
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
@@ -227,6 +243,7 @@ def main() -> int:
     ev1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
+    mark("timed region done")
     ms = ev0.elapsed_time(ev1)
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -257,9 +274,16 @@ def main() -> int:
         if args.layers:
             line["profile_only"] = True
         print(json.dumps(line))
+    mark("line printed")
     if world > 1:
+        # Graphs that captured collectives must go before their communicator.
+        eng.runner.release_graphs()
+        del graph
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        mark("exit")
+        os._exit(0)     # skip communicator teardown: nothing is left to save
     return 0
 
 

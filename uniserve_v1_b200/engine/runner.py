@@ -52,6 +52,7 @@ class InputBlock:
                   for k, (o, nb, dt, shape) in self.layout.items()}
         self.d = {k: self.dev[o:o + nb].view(dt).view(shape)
                   for k, (o, nb, dt, shape) in self.layout.items()}
+        self.hn = {k: v.numpy() for k, v in self.h.items()}
 
     def upload(self) -> int:
         self.dev.copy_(self.host, non_blocking=True)
@@ -106,6 +107,8 @@ class CausalLmRunner:
             ], self.device)
             blk.history = torch.full((self.history_steps, B), -1, dtype=torch.int32,
                                      device=self.device)
+            blk.readback = torch.empty((self.history_steps, B), dtype=torch.int32,
+                                       pin_memory=self.device.type == "cuda")
             self._blocks[B] = blk
         return blk
 
@@ -188,26 +191,42 @@ class CausalLmRunner:
 
     # ---------------------------------------------------------------- decode --
     def _fill_decode(self, blk: InputBlock, rows: list, B: int) -> None:
-        h = blk.h
+        """Column assembly of a decode batch into the pinned input block (numpy
+        views over the pinned memory; one pass over the rows)."""
+        h = blk.hn
         n = len(rows)
         ps = self.page_size
         h["live"][0] = n
         h["step"][0] = 0
+        ids, pos, slots, temp, top_k, top_p, min_p, seeds = [], [], [], [], [], [], [], []
+        pt = h["page_table"]
         for i, req in enumerate(rows):
-            pos = req.num_tokens - 1
-            h["input_ids"][i] = req.all_ids[-1]
-            h["positions"][i] = pos
-            h["seq_lens"][i] = pos + 1
-            h["slots"][i] = req.pages[pos // ps] * ps + pos % ps
-            npg = len(req.pages)
-            h["page_table"][i, :npg] = torch.tensor(req.pages, dtype=torch.int32)
+            p_ = req.num_tokens - 1
+            ids.append(req.output_ids[-1] if req.output_ids else req.prompt_ids[-1])
+            pos.append(p_)
+            pages = req.pages
+            slots.append(pages[p_ // ps] * ps + p_ % ps)
+            pt[i, :len(pages)] = pages
             p: SamplingParams = req.params
-            h["temperature"][i] = 1.0 if p.greedy else p.temperature
-            h["top_k"][i] = 1 if p.greedy else (p.top_k if p.top_k > 0 else 0)
-            h["top_p"][i] = p.top_p
-            h["min_p"][i] = p.min_p
-            h["seeds"][i] = req.seed - (1 << 64) if req.seed >= (1 << 63) else req.seed
-            h["sample_pos"][i] = req.num_tokens
+            greedy = p.greedy
+            temp.append(1.0 if greedy else p.temperature)
+            top_k.append(1 if greedy else (p.top_k if p.top_k > 0 else 0))
+            top_p.append(p.top_p)
+            min_p.append(p.min_p)
+            sd = req.seed
+            seeds.append(sd - (1 << 64) if sd >= (1 << 63) else sd)
+        h["input_ids"][:n] = ids
+        h["positions"][:n] = pos
+        h["seq_lens"][:n] = pos
+        h["seq_lens"][:n] += 1
+        h["slots"][:n] = slots
+        h["temperature"][:n] = temp
+        h["top_k"][:n] = top_k
+        h["top_p"][:n] = top_p
+        h["min_p"][:n] = min_p
+        h["seeds"][:n] = seeds
+        h["sample_pos"][:n] = pos
+        h["sample_pos"][:n] += 1
         if n < B:
             h["input_ids"][n:] = 0
             h["positions"][n:] = 0
@@ -217,6 +236,12 @@ class CausalLmRunner:
             h["top_k"][n:] = 1
             h["top_p"][n:] = 1.0
             h["min_p"][n:] = 0.0
+
+    def release_graphs(self) -> None:
+        """Drops every captured graph (do this before tearing down a process
+        group whose collectives the graphs captured)."""
+        self._graphs.clear()
+        self._pool = None
 
     @staticmethod
     def variant_for(rows: list) -> str:
@@ -249,7 +274,12 @@ class CausalLmRunner:
             sampled, info = self._shape_and_sample(logits[:n], rows)
             out = sampled.view(1, n)
         elif self.device.type == "cuda":
-            out = self._to_host(blk.history[:steps, :n])
+            # one D2H copy of the step results into a fixed pinned buffer
+            host = blk.readback[:steps]
+            host.copy_(blk.history[:steps], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            self.d2h_bytes += steps * n * 4
+            out = host[:, :n]
         else:
             out = blk.history[:steps, :n].clone()
         return out, info

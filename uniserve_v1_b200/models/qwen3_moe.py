@@ -274,7 +274,30 @@ class Qwen3MoeModel:
         return self
 
     # -------------------------------------------------------------- forward --
-    def _attention(self, lw: LayerWeights, x, positions, meta: AttnMeta, kcache, vcache):
+    def _fused(self, T: int, on_cuda: bool):
+        """The peer-memory path serves small row counts (decode); larger batches
+        take the library collective."""
+        fc = self.ctx.fused
+        if fc is not None and on_cuda and self.ctx.tp_size > 1 and \
+                fc.fits(T, self.cfg.hidden_size):
+            return fc
+        return None
+
+    def _partial_out(self, fc, T: int):
+        """(site, buffer) for a row-parallel output whose sum is still pending."""
+        if fc is None:
+            return None, None
+        site = fc.next_site()
+        return site, fc.site_tensor(site, T, self.cfg.hidden_size)
+
+    def _reduce_norm(self, fc, h, site, residual, w):
+        """residual += sum over ranks of h;  returns (rmsnorm(residual) * w, residual).
+        With a pending site the sum, the residual add and the norm are one kernel."""
+        if site is None:
+            return F.add_rmsnorm(h, residual, w, self.cfg.rms_norm_eps)
+        return fc.allreduce_add_rmsnorm(site, h.shape[0], residual, w, self.cfg.rms_norm_eps)
+
+    def _attention(self, fc, lw: LayerWeights, x, positions, meta: AttnMeta, kcache, vcache):
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         T = x.shape[0]
         qkv = F.linear(x, lw.qkv)
@@ -288,15 +311,22 @@ class Qwen3MoeModel:
         else:
             from ..ops.attention import prefill_attention
             att = prefill_attention(qkv, Hq, Hkv, D, meta, kcache, vcache, self.scale)
-        out = F.linear(att.reshape(T, Hq * D), lw.o_proj)
-        return self.ctx.all_reduce_tp(out)
+        site, buf = self._partial_out(fc, T)
+        out = F.linear(att.reshape(T, Hq * D), lw.o_proj, out=buf)
+        if site is None:
+            out = self.ctx.all_reduce_tp(out)
+        return out, site
 
-    def _mlp(self, lw: LayerWeights, x):
+    def _mlp(self, fc, lw: LayerWeights, x):
         cfg = self.cfg
         T = x.shape[0]
         if lw.dense:
             h = F.linear_gated(x, lw.w13[0])
-            return self.ctx.all_reduce_tp(F.linear(h, lw.w2[0]))
+            site, buf = self._partial_out(fc, T)
+            out = F.linear(h, lw.w2[0], out=buf)
+            if site is None:
+                out = self.ctx.all_reduce_tp(out)
+            return out, site
         logits = F.linear(x, lw.router, out_dtype=torch.float32)
         ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
         ws = None
@@ -307,23 +337,28 @@ class Qwen3MoeModel:
                 ws = F.MoeWorkspace.create(T, cfg.num_experts_per_tok, self.E_local,
                                            cfg.hidden_size, cfg.moe_intermediate_size, x.device)
                 self._moe_ws[key] = ws
-        out = F.moe_experts(x, ids, weights, lw.w13, lw.w2, e_lo=self.e_lo, ws=ws)
-        if self.ctx.ep_size > 1:
+        reduce = self.ctx.ep_size > 1
+        site, buf = self._partial_out(fc if reduce else None, T)
+        out = F.moe_experts(x, ids, weights, lw.w13, lw.w2, e_lo=self.e_lo, ws=ws, out=buf)
+        if reduce and site is None:
             out = self.ctx.all_reduce_tp(out)
-        return out
+        return out, site
 
     def forward(self, input_ids, positions, meta: AttnMeta, kv_caches) -> torch.Tensor:
         """Returns the final-normed hidden rows [T, H] (bf16).
         ``kv_caches[layer] = (k, v)`` each [pages, page_size, Hkv_local, D]."""
         hidden = F.embedding(input_ids, self.embed)
-        residual = None
+        fc = self._fused(hidden.shape[0], hidden.is_cuda)
+        if fc is not None:
+            fc.begin_forward()
+        residual, site = None, None
         for i, lw in enumerate(self.layers):
-            x, residual = F.add_rmsnorm(hidden, residual, lw.input_norm, self.cfg.rms_norm_eps)
+            x, residual = self._reduce_norm(fc, hidden, site, residual, lw.input_norm)
             kc, vc = kv_caches[i]
-            mixed = self._attention(lw, x, positions, meta, kc, vc)
-            x, residual = F.add_rmsnorm(mixed, residual, lw.post_norm, self.cfg.rms_norm_eps)
-            hidden = self._mlp(lw, x)
-        x, _ = F.add_rmsnorm(hidden, residual, self.final_norm, self.cfg.rms_norm_eps)
+            mixed, site = self._attention(fc, lw, x, positions, meta, kc, vc)
+            x, residual = self._reduce_norm(fc, mixed, site, residual, lw.post_norm)
+            hidden, site = self._mlp(fc, lw, x)
+        x, _ = self._reduce_norm(fc, hidden, site, residual, self.final_norm)
         return x
 
     def logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
