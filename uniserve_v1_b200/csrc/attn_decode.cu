@@ -13,7 +13,10 @@
 //
 // Reference behaviour: crates/ops/src/attention/mod.rs:7-15 and
 // crates/ops/kernels/paged_attention (reference project paths).
+#include <stdio.h>
+
 #include "include/us_common.cuh"
+#include "include/us_noalloc.h"
 
 namespace {
 
@@ -281,4 +284,49 @@ US_API int us_paged_decode_attention(const void* q, const void* kcache, const vo
   US_DEC(64, 1) US_DEC(64, 2) US_DEC(64, 4) US_DEC(64, 8)
 #undef US_DEC
   return US_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant (see include/us_noalloc.h).  The partial outputs and
+// log-sum-exps of the split path live in this array, which is part of the
+// library image on every device that loads it.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[US_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kNoallocMaxDevices = 64;
+void* g_noalloc_ptr[kNoallocMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" void us_set_last_error_text(const char* text);
+
+US_API int us_paged_decode_attention_noalloc(const void* q, const void* kcache,
+                                             const void* vcache, const int* page_table,
+                                             const int* seq_lens, void* out, int B, int Hq,
+                                             int Hkv, int D, int max_pages, int page_size,
+                                             int splits, int window, float scale, long long ldq,
+                                             long long ldo, void* stream_) {
+  US_REQUIRE(B >= 0 && Hq >= 1 && D >= 1 && splits >= 1);
+  const long long need = splits > 1 ? us_paged_decode_scratch_bytes(B, Hq, D, splits) : 0;
+  if (need > (long long)US_NOALLOC_SCRATCH_BYTES) {
+    char msg[256];
+    snprintf(msg, sizeof(msg),
+             "us_paged_decode_attention_noalloc: B*Hq*splits*(D+1)*4 = %lld bytes exceeds the "
+             "built-in scratch of %u bytes; lower `splits` or the batch",
+             need, (unsigned)US_NOALLOC_SCRATCH_BYTES);
+    us_set_last_error_text(msg);
+    return US_ERR_LIMIT;
+  }
+  // In host code the array's name is only a stand-in; the kernel needs the
+  // address the array has on the current device.  Looked up once per device.
+  int dev = 0;
+  US_CUDA_CHECK(cudaGetDevice(&dev));
+  US_REQUIRE(dev >= 0 && dev < kNoallocMaxDevices);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    US_CUDA_CHECK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    g_noalloc_ptr[dev] = p;
+  }
+  return us_paged_decode_attention(q, kcache, vcache, page_table, seq_lens, out,
+                                   splits > 1 ? g_noalloc_ptr[dev] : nullptr, B, Hq, Hkv, D,
+                                   max_pages, page_size, splits, window, scale, ldq, ldo, stream_);
 }

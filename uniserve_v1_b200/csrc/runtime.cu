@@ -44,6 +44,10 @@ extern "C" void us_set_last_cuda_error(int code, const char* file, int line) {
     snprintf(g_err_text, sizeof(g_err_text), "%s:%d: argument check failed", file, line);
 }
 
+extern "C" void us_set_last_error_text(const char* text) {
+  snprintf(g_err_text, sizeof(g_err_text), "%s", text);
+}
+
 US_API const char* us_last_error() { return g_err_text; }
 
 // Device pointer of the status word of the current device (allocated on first
