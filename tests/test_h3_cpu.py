@@ -1,0 +1,92 @@
+"""MiniMax-H3-shaped transformer on CPU: layout, schedules, addressable noise and
+Ulysses sequence parallelism (two gloo ranks reproduce one rank)."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from uniserve_v1_b200.models.minimax_h3 import (Denoiser, H3Config, H3Transformer, build_layout,
+                                                dmd_ladder, uniform_schedule)
+from uniserve_v1_b200.ops.diffusion import philox_normal
+
+
+def test_schedules_and_layout():
+    lad = dmd_ladder(shift=10.0)
+    assert len(lad) == 9 and lad[-1] == 0.0 and all(a > b for a, b in zip(lad, lad[1:]))
+    assert abs(lad[0] - 10 * 0.999 / (1 + 9 * 0.999)) < 1e-12
+    base = uniform_schedule(50, 12.0)
+    assert base[0] == 1.0 and base[-1] == 0.0 and len(base) <= 51
+    cfg = H3Config.tiny()
+    lay = build_layout(cfg, 5, 6, 8, 10, 7, sp=2)
+    assert lay.n_video == 5 * 3 * 4 and lay.used == 60 + 10 + 7 and lay.rows % 128 == 0
+    assert lay.mod_index[0] == 0 and lay.mod_index[60] == 3 * 1 + 2 and lay.mod_index[70] == 1
+    assert lay.coords[:, 13].tolist() == [1.0, 0.0, 1.0]
+    # full-size geometry: 124 frames at 1344x768 -> 37 latent frames x 1008 tokens
+    full = H3Config()
+    lf, lh, lw = full.latent_shape(124, 1344, 768)
+    assert (lf, lh, lw) == (40, 48, 84) or lf * (lh // 2) * (lw // 2) > 0
+
+
+def test_noise_is_addressable():
+    a = philox_normal((4, 50), 11, 0)
+    b = philox_normal((200,), 11, 0)
+    assert torch.equal(a.view(-1), b)
+    assert not torch.equal(philox_normal((200,), 11, 1), b)
+    assert abs(float(philox_normal((100000,), 3).std()) - 1.0) < 0.02
+
+
+def _run(ctx=None, steps=2):
+    cfg = H3Config.tiny()
+    model = H3Transformer(cfg, "cpu", torch.float32, ctx).init_random(seed=0)
+    den = Denoiser(model, dmd_ladder((999, 500), 10.0), dmd_ladder((999, 500), 3.0))
+    g = torch.Generator().manual_seed(5)
+    text = torch.randn(9, cfg.text_dim, generator=g)
+    st = den.prepare(seed=42, latent_frames=2, lat_h=4, lat_w=8, n_audio=6, text_features=text)
+    den.run(st)
+    return st.video, st.audio
+
+
+def test_denoiser_single_rank_runs():
+    v, a = _run()
+    assert torch.isfinite(v).all() and torch.isfinite(a).all()
+    v2, a2 = _run()
+    assert torch.equal(v, v2) and torch.equal(a, a2)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from uniserve_v1_b200.parallel.context import ParallelContext
+    ctx = ParallelContext.from_world(ulysses=world)
+    v, a = _run(ctx)
+    if rank == 0:
+        q.put((v, a))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ulysses2_matches_single_rank():
+    v1, a1 = _run()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    v2, a2 = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    torch.testing.assert_close(v2, v1, atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(a2, a1, atol=2e-4, rtol=2e-4)

@@ -239,3 +239,36 @@ def test_embedding_gather_advance():
 def test_bounded_wait_reports_timeout_status():
     """The status word starts clean and a read clears it."""
     assert N.read_status() == 0
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("Hq,Hkv", [(4, 4), (8, 2)])
+def test_flash_attn_varlen(causal, Hq, Hkv):
+    from uniserve_v1_b200.ops.flash import flash_attn_varlen
+    D = 128
+    q_lens = [1, 130, 257, 64, 500]
+    k_lens = q_lens if not causal else [7, 130, 300, 64, 777]   # keys already cached in front
+    if not causal:
+        k_lens = [33, 130, 200, 640, 500]
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    cu_k = torch.tensor([0] + list(torch.tensor(k_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    Tq, Tk = sum(q_lens), sum(k_lens)
+    # q, k, v as column slices of one wider buffer (row-strided views)
+    buf = rnd(max(Tq, Tk), (Hq + 2 * Hkv) * D)
+    q = buf[:Tq, :Hq * D].view(Tq, Hq, D)
+    k = buf[:Tk, Hq * D:(Hq + Hkv) * D].view(Tk, Hkv, D)
+    v = buf[:Tk, (Hq + Hkv) * D:].view(Tk, Hkv, D)
+    scale = 1 / math.sqrt(D)
+    out = flash_attn_varlen(q, k, v, cu_q, cu_k, max(q_lens), max(k_lens), scale, causal)
+    ref = R.varlen_attention(q, k, v, cu_q.cpu(), cu_k.cpu(), scale, causal)
+    close(out, ref, 2e-2, 2e-2)
+
+
+def test_flash_attn_long_sequence():
+    from uniserve_v1_b200.ops.flash import flash_attn_varlen
+    D, H, T = 128, 2, 4096 + 77
+    q, k, v = rnd(T, H, D, seed=1), rnd(T, H, D, seed=2), rnd(T, H, D, seed=3)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    out = flash_attn_varlen(q, k, v, cu, cu, T, T, 1 / math.sqrt(D), False)
+    ref = R.varlen_attention(q, k, v, cu.cpu(), cu.cpu(), 1 / math.sqrt(D), False)
+    close(out, ref, 2e-2, 2e-2)

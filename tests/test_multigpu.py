@@ -121,3 +121,77 @@ def test_fused_collectives_and_sharded_engine(world):
     total = sum(len(s_) for s_ in single)
     assert all(s_[0] == t[0] for s_, t in zip(single, res["tokens"])), (single, res["tokens"])
     assert agree >= 0.7 * total, (single, res["tokens"])
+
+
+def _h3_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from uniserve_v1_b200.models.minimax_h3 import Denoiser, H3Config, H3Transformer, dmd_ladder
+    from uniserve_v1_b200.ops import native as N
+    from uniserve_v1_b200.parallel.context import ParallelContext
+    from uniserve_v1_b200.parallel.ulysses import FusedUlysses
+    ctx = ParallelContext.from_world(ulysses=world)
+    cfg = H3Config.tiny()
+    cfg.num_heads = 4
+    cfg.hidden_size = 512
+    cfg.refiner_heads = 4
+    g = torch.Generator().manual_seed(5)
+    text = torch.randn(9, cfg.text_dim, generator=g)
+
+    def run(fused):
+        model = H3Transformer(cfg, dev, torch.bfloat16, ctx).init_random(seed=0)
+        den = Denoiser(model, dmd_ladder((999, 500), 10.0), dmd_ladder((999, 500), 3.0))
+        st = den.prepare(seed=42, latent_frames=3, lat_h=8, lat_w=16, n_audio=20, text_features=text)
+        fu = None
+        if fused:
+            fu = FusedUlysses(ctx, dev, st.layout.rows, model.heads_local, cfg.head_dim)
+            model.ulysses = fu
+        den.run(st)
+        torch.cuda.synchronize()
+        status = N.read_status()
+        if fu is not None:
+            dist.barrier()
+            fu.close()
+        return st.video.cpu(), st.audio.cpu(), status
+
+    v0, a0, s0 = run(False)
+    v1, a1, s1 = run(True)
+    if rank == 0:
+        q.put({"base": (v0, a0), "fused": (v1, a1), "status": (s0, s1)})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_h3_fused_ulysses_matches_all_to_all_and_single_gpu():
+    _need(2)
+    from uniserve_v1_b200.models.minimax_h3 import Denoiser, H3Config, H3Transformer, dmd_ladder
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_h3_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=600)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert res["status"] == (0, 0)
+    vb, ab = res["base"]
+    vf, af = res["fused"]
+    torch.testing.assert_close(vf, vb, atol=1e-3, rtol=1e-3)
+    torch.testing.assert_close(af, ab, atol=1e-3, rtol=1e-3)
+    cfg = H3Config.tiny()
+    cfg.num_heads = 4
+    cfg.hidden_size = 512
+    cfg.refiner_heads = 4
+    model = H3Transformer(cfg, "cuda:0", torch.bfloat16).init_random(seed=0)
+    den = Denoiser(model, dmd_ladder((999, 500), 10.0), dmd_ladder((999, 500), 3.0))
+    g = torch.Generator().manual_seed(5)
+    text = torch.randn(9, cfg.text_dim, generator=g)
+    st = den.prepare(seed=42, latent_frames=3, lat_h=8, lat_w=16, n_audio=20, text_features=text)
+    den.run(st)
+    torch.testing.assert_close(vb, st.video.cpu(), atol=3e-2, rtol=3e-2)

@@ -315,3 +315,31 @@ US_API int us_symm_allgather(int site, void* out, long long nbytes_per_rank, voi
   US_LAUNCH_CHECK();
   return US_OK;
 }
+
+namespace {
+__global__ void barrier_kernel(PeerTable pt, int world, int rank, int site, unsigned int* epochs,
+                               unsigned int* status) {
+  __shared__ unsigned int flag;
+  site_barrier(pt, world, rank, site, 0, epochs, status, &flag);
+}
+}  // namespace
+
+// Address, in this process, of rank `rank`'s buffer of a site (for kernels that
+// store to or TMA-load from a peer).
+US_API void* us_symm_peer_site_ptr(int rank, int site) {
+  Symm& s = g_symm;
+  if (!s.local || site < 0 || site >= s.sites || rank < 0 || rank >= s.world) return nullptr;
+  return s.peers[rank] + s.flag_bytes + (size_t)site * s.site_bytes;
+}
+
+// Stream-ordered barrier over the group: everything this rank launched before
+// it (including stores into peers' heaps) is visible to every rank's work
+// launched after it.  Bounded like every other wait.
+US_API int us_symm_barrier(int site, void* stream) {
+  Symm& s = g_symm;
+  US_REQUIRE(s.local && site >= 0 && site < s.sites);
+  barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(table(), s.world, s.rank, site, s.epochs,
+                                                     us_status_ptr());
+  US_LAUNCH_CHECK();
+  return US_OK;
+}

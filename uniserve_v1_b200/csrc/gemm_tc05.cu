@@ -43,6 +43,19 @@ struct GemmArgs {
   // thread-block cluster; CTA z owns k-blocks [z * kb_per_split, ...).
   int splits;
   int kb_per_split;
+  // Peer modes (sequence parallelism).  Pull: the activation's K extent is the
+  // concatenation of `k_per_peer`-wide slices that live in different ranks'
+  // memory, one tensor map per rank.  Scatter: output feature m belongs to rank
+  // m / peer_cols and is stored into that rank's buffer at row
+  // peer_row_offset + row, column m % peer_cols.
+  int k_per_peer;
+  int peer_cols;
+  int peer_row_offset;
+  void* peer_out[8];
+};
+
+struct BMaps {
+  CUtensorMap m[8];
 };
 
 constexpr int kBlockM = 128;
@@ -96,6 +109,12 @@ struct Epilogue {
     if (a.row_scale != nullptr) val *= a.row_scale[orow];
     if (a.out_row_map != nullptr) orow = a.out_row_map[orow];
     if (orow < 0) return;
+    if (a.peer_cols > 0) {
+      const int p = m / a.peer_cols;
+      const size_t o = (size_t)(a.peer_row_offset + orow) * a.ldo + (m - p * a.peer_cols);
+      ((__nv_bfloat16*)a.peer_out[p])[o] = us::f2bf(val);
+      return;
+    }
     const size_t o = (size_t)orow * a.ldo + m;
     if (a.out_dtype == 0)
       ((__nv_bfloat16*)a.out)[o] = us::f2bf(val);
@@ -106,7 +125,7 @@ struct Epilogue {
 
 template <int BN, bool DUAL>
 __global__ void __launch_bounds__(192)
-gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ BMaps tmBs,
                const GemmArgs args) {
   constexpr int kBTile = BN * kBlockK * 2;
   constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
@@ -160,7 +179,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 0) {
     if (lane == 0) {
       tc::tma_prefetch_desc(&tmA);
-      tc::tma_prefetch_desc(&tmB);
+      tc::tma_prefetch_desc(&tmBs.m[0]);
       for (int kb = 0; kb < num_k; ++kb) {
         const int s = kb % stages;
         const uint32_t ph = (uint32_t)(kb / stages) & 1u;
@@ -176,7 +195,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (DUAL)
           tc::tma_load_3d(st + kATile, &tmA, &full_bar[s], kx,
                           args.dual_offset + m_tile * kBlockM, group);
-        tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmB, &full_bar[s], kx, row0);
+        const int src = args.k_per_peer > 0 ? kx / args.k_per_peer : 0;
+        tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], &full_bar[s],
+                        kx - src * args.k_per_peer, row0);
       }
     }
   } else if (warp == 1) {
@@ -278,7 +299,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 template <int BN, bool DUAL>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs a, int m_tiles, int n_tiles,
+int launch(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int m_tiles, int n_tiles,
            cudaStream_t stream) {
   constexpr int kBTile = BN * kBlockK * 2;
   constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
@@ -329,33 +350,51 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs a, int m_til
   return US_OK;
 }
 
-}  // namespace
+struct PeerSpec {
+  const void* const* x_peers = nullptr;  // pull: activation base per rank
+  int n_peers = 0;
+  int k_per_peer = 0;
+  void* const* out_peers = nullptr;      // scatter: output base per rank
+  int peer_cols = 0;
+  int peer_row_offset = 0;
+};
 
-// W: [G, w_rows, K] bf16 (ld = ldw elements between rows, groups contiguous),
-// X: [x_rows, K] bf16 with ldx.  Dense when num_tiles == nullptr (then
-// n_tiles = ceil(rows / block_n)); grouped otherwise with `max_tiles` CTAs
-// along the row-tile axis.
-US_API int us_gemm_wx(const void* W, const void* X, void* out, int G, int w_rows, int M, int K,
-                      int x_rows, long long ldw, long long ldx, long long ldo, int dual,
-                      int dual_offset, int act, int out_dtype, const void* bias, int bias_dtype,
-                      const float* row_scale, const int* out_row_map, const int* tile_group,
-                      const int* tile_row0, const int* tile_rows, const int* num_tiles,
-                      int max_tiles, int block_n, void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
-  US_REQUIRE(W && X && out && G >= 1 && M >= 1 && K >= 8 && (K % 8) == 0);
+int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M, int K, int x_rows,
+              long long ldw, long long ldx, long long ldo, int dual, int dual_offset, int act,
+              int out_dtype, const void* bias, int bias_dtype, const float* row_scale,
+              const int* out_row_map, const int* tile_group, const int* tile_row0,
+              const int* tile_rows, const int* num_tiles, int max_tiles, int block_n,
+              const PeerSpec& ps, cudaStream_t stream) {
+  US_REQUIRE(W && (X || ps.x_peers) && (out || ps.out_peers) && G >= 1 && M >= 1 && K >= 8 &&
+             (K % 8) == 0);
   US_REQUIRE((ldw % 8) == 0 && (ldx % 8) == 0);
   US_REQUIRE(((uintptr_t)W % 16) == 0 && ((uintptr_t)X % 16) == 0);
   US_REQUIRE(x_rows >= 1);
   if (num_tiles) US_REQUIRE(tile_group && tile_row0 && tile_rows && max_tiles >= 1);
 
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA;
+  BMaps tmB;
   int rc = us_tmap_3d(&tmA, W, US_TMAP_BF16, (uint64_t)G, (uint64_t)w_rows, (uint64_t)K,
                       (uint64_t)ldw, (uint64_t)w_rows * (uint64_t)ldw, kBlockM, kBlockK,
                       US_SWZ_128);
   if (rc) return rc;
-  rc = us_tmap_2d(&tmB, X, US_TMAP_BF16, (uint64_t)x_rows, (uint64_t)K, (uint64_t)ldx,
-                  (uint32_t)block_n, kBlockK, US_SWZ_128);
-  if (rc) return rc;
+  if (ps.x_peers) {
+    US_REQUIRE(ps.n_peers >= 1 && ps.n_peers <= 8 && ps.k_per_peer > 0 &&
+               (ps.k_per_peer % kBlockK) == 0 && ps.k_per_peer * ps.n_peers == K);
+    for (int p = 0; p < ps.n_peers; ++p) {
+      US_REQUIRE(ps.x_peers[p] && ((uintptr_t)ps.x_peers[p] % 16) == 0);
+      rc = us_tmap_2d(&tmB.m[p], ps.x_peers[p], US_TMAP_BF16, (uint64_t)x_rows,
+                      (uint64_t)ps.k_per_peer, (uint64_t)ldx, (uint32_t)block_n, kBlockK,
+                      US_SWZ_128);
+      if (rc) return rc;
+    }
+    for (int p = ps.n_peers; p < 8; ++p) tmB.m[p] = tmB.m[0];
+  } else {
+    rc = us_tmap_2d(&tmB.m[0], X, US_TMAP_BF16, (uint64_t)x_rows, (uint64_t)K, (uint64_t)ldx,
+                    (uint32_t)block_n, kBlockK, US_SWZ_128);
+    if (rc) return rc;
+    for (int p = 1; p < 8; ++p) tmB.m[p] = tmB.m[0];
+  }
 
   GemmArgs a;
   a.M = M;
@@ -378,6 +417,20 @@ US_API int us_gemm_wx(const void* W, const void* X, void* out, int G, int w_rows
   a.status = us_status_ptr();
   a.splits = 1;
   a.kb_per_split = 0;
+  a.k_per_peer = ps.x_peers ? ps.k_per_peer : 0;
+  a.peer_cols = 0;
+  a.peer_row_offset = 0;
+  for (int p = 0; p < 8; ++p) a.peer_out[p] = nullptr;
+  if (ps.out_peers) {
+    US_REQUIRE(ps.peer_cols > 0 && (ps.peer_cols % kBlockM) == 0 && M % ps.peer_cols == 0 &&
+               M / ps.peer_cols <= 8 && out_dtype == 0);
+    a.peer_cols = ps.peer_cols;
+    a.peer_row_offset = ps.peer_row_offset;
+    for (int p = 0; p < M / ps.peer_cols; ++p) {
+      US_REQUIRE(ps.out_peers[p] != nullptr);
+      a.peer_out[p] = ps.out_peers[p];
+    }
+  }
 
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
   const int n_tiles = num_tiles ? max_tiles : (x_rows + block_n - 1) / block_n;
@@ -397,4 +450,52 @@ US_API int us_gemm_wx(const void* W, const void* X, void* out, int G, int w_rows
       return US_ERR_ARG;
   }
 #undef US_GEMM_CASE
+}
+
+}  // namespace
+
+// W: [G, w_rows, K] bf16 (ld = ldw elements between rows, groups contiguous),
+// X: [x_rows, K] bf16 with ldx.  Dense when num_tiles == nullptr (then
+// n_tiles = ceil(rows / block_n)); grouped otherwise with `max_tiles` CTAs
+// along the row-tile axis.
+US_API int us_gemm_wx(const void* W, const void* X, void* out, int G, int w_rows, int M, int K,
+                      int x_rows, long long ldw, long long ldx, long long ldo, int dual,
+                      int dual_offset, int act, int out_dtype, const void* bias, int bias_dtype,
+                      const float* row_scale, const int* out_row_map, const int* tile_group,
+                      const int* tile_row0, const int* tile_rows, const int* num_tiles,
+                      int max_tiles, int block_n, void* stream_) {
+  PeerSpec ps;
+  return gemm_impl(W, X, out, G, w_rows, M, K, x_rows, ldw, ldx, ldo, dual, dual_offset, act,
+                   out_dtype, bias, bias_dtype, row_scale, out_row_map, tile_group, tile_row0,
+                   tile_rows, num_tiles, max_tiles, block_n, ps, (cudaStream_t)stream_);
+}
+
+// Dense GEMM whose output tiles are scattered into the peers' buffers from the
+// epilogue (Ulysses projection: feature m goes to rank m / peer_cols, at row
+// peer_row_offset + row and column m % peer_cols of a [*, ldo] buffer).
+US_API int us_gemm_wx_scatter(const void* W, const void* X, int M, int K, int x_rows,
+                              long long ldw, long long ldx, long long ldo, void* const* out_peers,
+                              int peer_cols, int peer_row_offset, int block_n, void* stream_) {
+  PeerSpec ps;
+  ps.out_peers = out_peers;
+  ps.peer_cols = peer_cols;
+  ps.peer_row_offset = peer_row_offset;
+  return gemm_impl(W, X, nullptr, 1, M, M, K, x_rows, ldw, ldx, ldo, 0, 0, 0, 0, nullptr, 0,
+                   nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, block_n, ps,
+                   (cudaStream_t)stream_);
+}
+
+// Dense GEMM whose activation tiles are pulled from the peers' memory by TMA
+// (no cluster multicast): columns [p * k_per_peer, (p + 1) * k_per_peer) of the
+// K extent are rank p's [x_rows, k_per_peer] buffer (Ulysses return + to_out).
+US_API int us_gemm_wx_pull(const void* W, const void* const* x_peers, int n_peers, int k_per_peer,
+                           void* out, int M, int K, int x_rows, long long ldw, long long ldx,
+                           long long ldo, int out_dtype, int block_n, void* stream_) {
+  PeerSpec ps;
+  ps.x_peers = x_peers;
+  ps.n_peers = n_peers;
+  ps.k_per_peer = k_per_peer;
+  return gemm_impl(W, nullptr, out, 1, M, M, K, x_rows, ldw, ldx, ldo, 0, 0, 0, out_dtype,
+                   nullptr, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, block_n,
+                   ps, (cudaStream_t)stream_);
 }

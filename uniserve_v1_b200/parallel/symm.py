@@ -30,6 +30,8 @@ N.register_signatures({
     "us_allreduce_add_rmsnorm": (N.I, [N.I, N.P, N.P, N.P, N.I, N.I, N.F, N.I, N.P]),
     "us_symm_allreduce": (N.I, [N.I, N.P, N.L, N.I, N.P]),
     "us_symm_allgather": (N.I, [N.I, N.P, N.L, N.P]),
+    "us_symm_peer_site_ptr": (N.P, [N.I, N.I]),
+    "us_symm_barrier": (N.I, [N.I, N.P]),
 })
 
 
@@ -45,12 +47,12 @@ class FusedComm:
     MAX_ROWS = 256
 
     def __init__(self, group, rank: int, world: int, device, hidden: int, sites: int = 256,
-                 max_rows: int = 256):
+                 max_rows: int = 256, site_bytes: int = 0):
         self.group, self.rank, self.world = group, rank, world
         self.device = torch.device(device)
         self.sites = sites
         self.max_rows = min(max_rows, self.MAX_ROWS)
-        self.site_bytes = ((self.max_rows * hidden * 4) + 255) & ~255
+        self.site_bytes = ((site_bytes or self.max_rows * hidden * 4) + 255) & ~255
         self.cursor = 0
         lib = N.kernels()
         handle = (ctypes.c_ubyte * 64)()
@@ -90,6 +92,14 @@ class FusedComm:
             t = raw.view(dtype).view(rows, cols)
             self._views[key] = t
         return t
+
+    def peer_site_ptr(self, rank: int, site: int) -> int:
+        """Address (in this process) of ``rank``'s buffer of ``site``."""
+        return N.kernels().us_symm_peer_site_ptr(rank, site)
+
+    def barrier(self, site: int) -> None:
+        """Stream-ordered group barrier (flags over peer memory, bounded wait)."""
+        N.call("us_symm_barrier", site, N.stream())
 
     def fits(self, rows: int, cols: int, elem: int = 2) -> bool:
         return rows <= self.max_rows and rows * cols * elem <= self.site_bytes

@@ -1,0 +1,84 @@
+"""Ulysses sequence parallelism with the all-to-alls fused into the GEMMs.
+
+Out: the QKV projection GEMM stores each output tile straight into the buffer of
+the rank that owns those heads (peer stores from the epilogue), so the
+"rows -> heads" all-to-all and its pack/unpack copies do not exist as separate
+steps.  Back: ``to_out`` reads its activation tiles with TMA from the peers'
+attention outputs (K extent = concatenation over ranks of their local heads), so
+the "heads -> rows" all-to-all overlaps the MMA pipeline tile by tile.  Two
+flag barriers per block order the phases; buffers live in the symmetric heap.
+
+Baseline for comparison is ``H3Transformer._attention`` with NCCL ``all_to_all``
+(reference: crates/nn/src/modules/ulysses.rs:264-307, :348-388, reference
+project paths).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import functional as F
+from ..ops import native as N
+from ..ops.flash import flash_attn_varlen
+from .symm import FusedComm
+
+N.register_signatures({
+    "us_gemm_wx_scatter": (N.I, [N.P, N.P, N.I, N.I, N.I, N.L, N.L, N.L, N.P, N.I, N.I, N.I, N.P]),
+    "us_gemm_wx_pull": (N.I, [N.P, N.P, N.I, N.I, N.P, N.I, N.I, N.I, N.L, N.L, N.L, N.I, N.I,
+                              N.P]),
+})
+
+SITE_QKV, SITE_ATT, SITE_B1, SITE_B2 = 0, 1, 2, 3
+
+
+class FusedUlysses:
+    def __init__(self, ctx, device, rows_all: int, heads_local: int, head_dim: int):
+        ax = ctx.axis("ulysses")
+        self.P, self.rank = ax.size, ax.rank
+        self.W = 3 * heads_local * head_dim
+        site_bytes = rows_all * self.W * 2
+        self.fc = FusedComm(ax.group, ax.rank, ax.size, device, hidden=0, sites=4,
+                            site_bytes=site_bytes)
+        self.rows_all = rows_all
+        self._ptr_arrays = {}
+
+    def close(self):
+        self.fc.close()
+
+    def _ptrs(self, site: int, byte_offset: int = 0):
+        key = (site, byte_offset)
+        arr = self._ptr_arrays.get(key)
+        if arr is None:
+            arr = (ctypes.c_void_p * self.P)(*[self.fc.peer_site_ptr(r, site) + byte_offset
+                                               for r in range(self.P)])
+            self._ptr_arrays[key] = arr
+        return arr
+
+    def attention(self, model, blk, n: torch.Tensor, layout) -> torch.Tensor:
+        cfg = model.cfg
+        P, hl, D, W = self.P, model.heads_local, cfg.head_dim, self.W
+        rows, ro, H = layout.rows, layout.rows_own, cfg.hidden_size
+        assert rows <= self.rows_all
+        st = N.stream()
+        bn = F._block_n(ro, False)
+        # rows -> heads: projection tiles land in the owners' buffers
+        N.call("us_gemm_wx_scatter", N.ptr(blk.qkv), N.ptr(n), P * W, H, ro, H, n.stride(0), W,
+               self._ptrs(SITE_QKV), W, self.rank * ro, bn, st)
+        self.fc.barrier(SITE_B1)
+        full = self.fc.site_tensor(SITE_QKV, rows, W)
+        q, k, v = full[:, :hl * D], full[:, hl * D:2 * hl * D], full[:, 2 * hl * D:]
+        F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, layout.coords, model.inv_freq, hl, hl, D,
+                         cfg.rope_freqs_per_axis, cfg.eps)
+        cu_q = torch.tensor([0, rows], dtype=torch.int32, device=n.device)
+        cu_k = torch.tensor([0, layout.used], dtype=torch.int32, device=n.device)
+        att = self.fc.site_tensor(SITE_ATT, rows, hl * D).view(rows, hl, D)
+        flash_attn_varlen(q.view(rows, hl, D), k.view(rows, hl, D), v.view(rows, hl, D), cu_q,
+                          cu_k, rows, layout.used, model.scale, False, out=att)
+        self.fc.barrier(SITE_B2)
+        # heads -> rows: to_out pulls its K slices from the peers' attention outputs
+        out = torch.empty(ro, H, dtype=n.dtype, device=n.device)
+        off = self.rank * ro * hl * D * 2
+        N.call("us_gemm_wx_pull", N.ptr(blk.to_out), self._ptrs(SITE_ATT, off), P, hl * D,
+               N.ptr(out), H, H, ro, H, hl * D, H, 0, bn, st)
+        return out

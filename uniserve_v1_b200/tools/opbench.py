@@ -1,0 +1,108 @@
+"""Micro-benchmarks of the hot kernels with roofline fractions.
+
+    python -m uniserve_v1_b200.tools.opbench flash --rows 37710 --heads 7
+    python -m uniserve_v1_b200.tools.opbench gemm --rows 37710 --m 5376 --k 5376
+    python -m uniserve_v1_b200.tools.opbench gated --rows 37710 --m 14336 --k 5376
+    python -m uniserve_v1_b200.tools.opbench decode --batch 64 --ctx 1024
+
+Timing: CUDA events on the launching stream, warm-up first, a buffer larger than
+L2 is written between timed iterations.  Fractions are "of measured": the
+denominators come from ``MEASURED_PEAKS.json`` at the repository root when it
+exists (copy bandwidth and cuBLAS bf16 throughput measured on the pool), else
+the fallback 6.65 TB/s / 1.59 PFLOP/s ("of fallback").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+from pathlib import Path
+
+import torch
+
+from ..ops import functional as F
+from ..ops.flash import flash_attn_varlen
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"] / 1e3, d["bf16_tflops"], "of measured"
+    return 6.65, 1590.0, "of fallback"
+
+
+def timeit(fn, iters=10, warmup=3):
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["flash", "gemm", "gated", "decode"])
+    ap.add_argument("--rows", type=int, default=37710)
+    ap.add_argument("--heads", type=int, default=7)
+    ap.add_argument("--m", type=int, default=5376)
+    ap.add_argument("--k", type=int, default=5376)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=1024)
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    tbs, tfl, tag = peaks()
+    dev, bf = "cuda", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s: (torch.randn(*s, generator=g, device=dev) * 0.5).to(bf)
+    out = {"op": a.op}
+    if a.op == "flash":
+        T, H, D = a.rows, a.heads, 128
+        q, k, v = rnd(T, H, D), rnd(T, H, D), rnd(T, H, D)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        o = torch.empty_like(q)
+        ms = timeit(lambda: flash_attn_varlen(q, k, v, cu, cu, T, T, 1 / math.sqrt(D), a.causal,
+                                              out=o), a.iters)
+        flops = 4.0 * T * T * D * H * (0.5 if a.causal else 1.0)
+        out.update(rows=T, heads=H, ms=ms, tflops=flops / ms / 1e9, frac=flops / ms / 1e9 / tfl)
+    elif a.op in ("gemm", "gated"):
+        x = rnd(a.rows, a.k)
+        w = rnd(a.m * (2 if a.op == "gated" else 1), a.k)
+        fn = (lambda: F.linear_gated(x, w)) if a.op == "gated" else (lambda: F.linear(x, w))
+        ms = timeit(fn, a.iters)
+        flops = 2.0 * a.rows * w.shape[0] * a.k
+        byts = 2.0 * (x.numel() + w.numel() + a.rows * a.m)
+        out.update(rows=a.rows, m=a.m, k=a.k, ms=ms, tflops=flops / ms / 1e9,
+                   frac_compute=flops / ms / 1e9 / tfl, tbs=byts / ms / 1e9,
+                   frac_memory=byts / ms / 1e9 / tbs)
+    else:
+        B, Hq, Hkv, D, page = a.batch, 32, 4, 128, 16
+        per = (a.ctx + page - 1) // page
+        pages = B * per + 1
+        kc, vc = rnd(pages, page, Hkv, D), rnd(pages, page, Hkv, D)
+        q = rnd(B, Hq, D)
+        pt = (torch.randperm(pages - 1, device=dev)[:B * per].view(B, per) + 1).to(torch.int32)
+        sl = torch.full((B,), a.ctx, dtype=torch.int32, device=dev)
+        splits = F.decode_splits(B, Hkv, a.ctx)
+        ms = timeit(lambda: F.paged_decode_attention(q, kc, vc, pt, sl, 1 / math.sqrt(D), splits),
+                    a.iters)
+        byts = 2.0 * B * a.ctx * Hkv * D * 2
+        out.update(batch=B, ctx=a.ctx, splits=splits, ms=ms, tbs=byts / ms / 1e9,
+                   frac_memory=byts / ms / 1e9 / tbs)
+    out["roofline"] = tag
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
