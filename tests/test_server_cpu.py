@@ -1,0 +1,151 @@
+"""HTTP API on CPU with the tiny model: chat (stream / non-stream), validation,
+auth, admin policy, metrics query, and the video routes end to end (MP4 out)."""
+import json
+
+import pytest
+import torch
+from fastapi.testclient import TestClient
+
+from uniserve_v1_b200.config.policy import Package
+from uniserve_v1_b200.engine.engine import LLMEngine
+from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+from uniserve_v1_b200.server.app import create_app
+from uniserve_v1_b200.server.tokenizer import ByteTokenizer
+
+
+@pytest.fixture(scope="module")
+def chat_client():
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    eng = LLMEngine(model, num_pages=256, max_num_seqs=8, max_model_len=512, use_graphs=False)
+    pkg = Package.parse('model = "random:tiny"\nserved_model_name = "tiny"\n')
+    app = create_app(package=pkg, engine=eng, tokenizer=ByteTokenizer(1024, 1023),
+                     served_model_name="tiny")
+    with TestClient(app) as c:
+        yield c
+
+
+def test_basics_and_404(chat_client):
+    assert chat_client.get("/health").json()["status"] == "ok"
+    assert chat_client.get("/v1/models").json()["data"][0]["id"] == "tiny"
+    r = chat_client.get("/nope")
+    assert r.status_code == 404 and r.json() == {"detail": "Not Found"}
+    assert chat_client.get("/v1/capabilities").status_code == 404      # text deployment
+
+
+def test_chat_non_stream_and_determinism(chat_client):
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hello"}],
+            "max_tokens": 8, "temperature": 0, "ignore_eos": True, "logprobs": True, "top_logprobs": 2}
+    a = chat_client.post("/v1/chat/completions", json=body).json()
+    b = chat_client.post("/v1/chat/completions", json=body).json()
+    assert a["choices"][0]["message"] == b["choices"][0]["message"]
+    assert a["usage"]["completion_tokens"] == 8 and a["choices"][0]["finish_reason"] == "length"
+    assert len(a["choices"][0]["logprobs"]["content"]) == 8
+    assert len(a["choices"][0]["logprobs"]["content"][0]["top_logprobs"]) == 2
+    # second run reuses the cached prompt pages
+    assert b["usage"]["prompt_tokens_details"]["cached_tokens"] > 0
+    body["seed"], body["temperature"], body["top_p"] = 7, 0.9, 0.9
+    c = chat_client.post("/v1/chat/completions", json=body).json()
+    d = chat_client.post("/v1/chat/completions", json=body).json()
+    assert c["choices"][0]["message"] == d["choices"][0]["message"]
+
+
+def test_chat_stream(chat_client):
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 5,
+            "temperature": 0, "stream": True, "ignore_eos": True,
+            "stream_options": {"include_usage": True}}
+    with chat_client.stream("POST", "/v1/chat/completions", json=body) as r:
+        lines = [l for l in r.iter_lines() if l.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]"
+    chunks = [json.loads(l[6:]) for l in lines[:-1]]
+    assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    assert chunks[-1]["usage"]["completion_tokens"] == 5
+    assert any(c["choices"] and c["choices"][0]["finish_reason"] == "length" for c in chunks)
+
+
+def test_chat_validation(chat_client):
+    r = chat_client.post("/v1/chat/completions", json={"model": "tiny", "messages": [], "x": 1})
+    assert r.status_code == 400
+    r = chat_client.post("/v1/chat/completions",
+                         json={"model": "tiny", "messages": [{"role": "user", "content": "a"}],
+                               "unknown_field": 1})
+    assert r.status_code == 400 and "unknown_field" in r.json()["error"]["message"]
+    r = chat_client.post("/v1/chat/completions",
+                         json={"model": "other", "messages": [{"role": "user", "content": "a"}]})
+    assert r.status_code == 404 and r.json()["error"]["code"] == "model_not_found"
+
+
+def test_admin_policy_and_query(chat_client):
+    assert chat_client.get("/admin/policy").json()["config"]["served_model_name"] == "tiny"
+    r = chat_client.put("/admin/policy", content='model = "random:tiny"\nserved_model_name = "tiny"\n'
+                                                 '[kv_cache_config]\nprefix_caching = false\n')
+    assert r.status_code == 200 and r.json()["effect"] == "step"
+    r = chat_client.put("/admin/policy", content='model = "random:tiny"\ntensor_parallel_size = 2\n')
+    assert r.status_code == 409
+    r = chat_client.put("/admin/policy", content='modle = "x"\n')
+    assert r.status_code == 400
+    q = chat_client.get("/admin/query", params={"q": "select kind, count(*) from events group by kind"})
+    assert q.status_code == 200 and any(row[0] == "request" for row in q.json()["rows"])
+    assert "uniserve_requests_total" in chat_client.get("/metrics").text
+    assert chat_client.get("/admin/query", params={"q": "drop table events"}).status_code == 400
+
+
+def test_api_key():
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    eng = LLMEngine(model, num_pages=64, max_num_seqs=2, max_model_len=128, use_graphs=False)
+    pkg = Package.parse('model = "random:tiny"\n[server_config]\napi_key = "sekret"\n')
+    app = create_app(package=pkg, engine=eng, tokenizer=ByteTokenizer(1024, 1023),
+                     served_model_name="tiny")
+    with TestClient(app) as c:
+        assert c.get("/health").status_code == 200
+        assert c.get("/v1/models").status_code == 401
+        assert c.get("/v1/models", headers={"Authorization": "Bearer sekret"}).status_code == 200
+
+
+def test_video_routes_produce_mp4():
+    import cv2
+    from uniserve_v1_b200.models.h3_vae import (AudioVaeConfig, AudioVaeDecoder, VideoVaeConfig,
+                                                VideoVaeDecoder)
+    from uniserve_v1_b200.models.minimax_h3 import H3Config, H3Transformer
+    from uniserve_v1_b200.server.video_service import VideoService
+    cfg = H3Config.tiny()
+    cfg.vae_spatial = 64          # keep the CPU test small: 256x256 -> 4x4 latent
+    tr = H3Transformer(cfg, "cpu", torch.float32).init_random(0)
+    vc = VideoVaeConfig.tiny()
+    vc.latent_channels, vc.spatial = cfg.latent_channels, 64
+    vv = VideoVaeDecoder(vc, "cpu", torch.float32).init_random(1)
+    av = AudioVaeDecoder(AudioVaeConfig(latent_channels=cfg.audio_channels, decoder_dim=128,
+                                        rates=(5, 5, 2, 2, 2, 2, 2), kernels=(9, 9, 4, 4, 4, 4, 4),
+                                        res_kernels=(3,), res_dilations=(1,)), "cpu").init_random(2)
+    svc = VideoService(tr, vv, av, sizes=["256x256"], max_seconds=5)
+    pkg = Package.parse('model = "random:h3:tiny"\nserved_model_name = "FastH3"\n')
+    app = create_app(package=pkg, video_service=svc, served_model_name="FastH3")
+    with TestClient(app) as c:
+        caps = c.get("/v1/capabilities").json()
+        assert caps["frame_rule"] == "17n + 5" and caps["sizes"] == ["256x256"]
+        bad = c.post("/v1/videos/sync", json={"model": "FastH3", "prompt": "x", "seconds": 2})
+        assert bad.status_code == 400 and bad.json()["error"]["param"] == "seconds"
+        bad = c.post("/v1/videos/sync", json={"model": "FastH3", "prompt": "x", "guidance_scale": 2})
+        assert bad.status_code == 400
+        r = c.post("/v1/videos/sync", json={"model": "FastH3", "prompt": "a stream in a forest",
+                                            "size": "256x256", "seconds": 4, "seed": 1000})
+        assert r.status_code == 200, r.text
+        assert r.headers["x-video-size"] == "256x256" and r.headers["x-video-num-frames"] == "107"
+        assert r.headers["x-video-fps"] == "24" and r.content[4:8] == b"ftyp"
+        open("/tmp/_us_test.mp4", "wb").write(r.content)
+        cap = cv2.VideoCapture("/tmp/_us_test.mp4")
+        assert cap.isOpened() and int(cap.get(cv2.CAP_PROP_FRAME_COUNT)) == 107
+        ok, frame = cap.read()
+        assert ok and frame.shape == (256, 256, 3)
+        job = c.post("/v1/videos", json={"model": "FastH3", "prompt": "x", "num_frames": 107,
+                                         "size": "256x256", "seed": 5}).json()
+        assert job["status"] in ("queued", "in_progress", "completed") and job["num_frames"] == 107
+        import time
+        for _ in range(600):
+            st = c.get(f"/v1/videos/{job['id']}").json()
+            if st["status"] in ("completed", "failed"):
+                break
+            time.sleep(0.1)
+        assert st["status"] == "completed", st
+        assert c.get(f"/v1/videos/{job['id']}/content").content[4:8] == b"ftyp"
+        assert c.delete(f"/v1/videos/{job['id']}").json()["deleted"] is True
+        assert c.get(f"/v1/videos/{job['id']}").status_code == 404

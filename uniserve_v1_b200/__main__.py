@@ -1,0 +1,113 @@
+"""Command line: ``python -m uniserve_v1_b200 serve PACKAGE [--ready-fd N] [--log-level L]``.
+
+Like the reference's ``uniserve serve PACKAGE`` the command takes no deployment
+option: everything is the package's ``config.toml`` (src/cli.rs:59-90, reference
+project path).  ``build`` compiles the native libraries, ``layout`` prints the
+resolved device layout of a package.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import logging
+import os
+import sys
+
+
+def serve(args) -> int:
+    import torch
+    import uvicorn
+
+    from .checkpoint.safetensors_io import CheckpointLoader, resolve_family, resolve_hub
+    from .config.policy import Package
+    from .server.app import create_app
+
+    pkg = Package.load(args.package)
+    logging.basicConfig(level=getattr(logging, (args.log_level or pkg.logging_config.level).upper()))
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    dtype = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}[pkg.dtype]
+    if device == "cpu":
+        dtype = torch.float32
+    directory = pkg.model_dir or None
+    if directory is None and pkg.model and not pkg.model.startswith("random:"):
+        directory = str(resolve_hub(pkg.model))
+    family = "qwen3_moe"
+    if directory:
+        family = resolve_family(directory)
+    elif pkg.model and "h3" in pkg.model.lower():
+        family = "minimax_h3"
+    name = pkg.served_model_name or (pkg.model or "model").split("/")[-1]
+    if family == "minimax_h3":
+        from .models.h3_vae import AudioVaeConfig, AudioVaeDecoder, VideoVaeConfig, VideoVaeDecoder
+        from .models.minimax_h3 import H3Config, H3Transformer
+        from .server.video_service import VideoService
+        tiny = pkg.model and pkg.model.endswith(":tiny")
+        cfg = H3Config.tiny() if tiny else H3Config()
+        tr = H3Transformer(cfg, device, dtype).init_random(0)
+        vv = VideoVaeDecoder(VideoVaeConfig.tiny() if tiny else VideoVaeConfig(), device, dtype).init_random(1)
+        if tiny:
+            vv.cfg.latent_channels = cfg.latent_channels
+            vv = VideoVaeDecoder(vv.cfg, device, dtype).init_random(1)
+        av = AudioVaeDecoder(AudioVaeConfig.tiny() if tiny else AudioVaeConfig(), device).init_random(2)
+        app = create_app(package=pkg, served_model_name=name,
+                         video_service=VideoService(tr, vv, av, max_seconds=15))
+    else:
+        from .engine.engine import LLMEngine
+        from .models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+        from .server.tokenizer import load_tokenizer
+        if directory:
+            ld = CheckpointLoader(directory)
+            cfg = Qwen3MoeConfig.from_hf(ld.config)
+            model = Qwen3MoeModel(cfg, device, dtype).load_state(ld)
+        else:
+            cfg = Qwen3MoeConfig.tiny() if (pkg.model or "").endswith(":tiny") \
+                else Qwen3MoeConfig.qwen3_30b_a3b()
+            model = Qwen3MoeModel(cfg, device, dtype).init_random(0)
+
+        def make_engine():
+            return LLMEngine(model, page_size=min(pkg.kv_cache_config.block_size, 16)
+                             if device == "cuda" else pkg.kv_cache_config.block_size,
+                             max_num_seqs=min(pkg.max_running_requests, pkg.scheduler_config.max_batch),
+                             max_model_len=pkg.max_model_len or min(cfg.max_position_embeddings, 8192),
+                             max_num_batched_tokens=pkg.max_num_batched_tokens,
+                             mem_fraction_static=pkg.mem_fraction_static,
+                             enable_prefix_cache=pkg.kv_cache_config.prefix_caching,
+                             watchdog_timeout=float(pkg.profiling_config.watchdog_timeout))
+
+        tok = load_tokenizer(directory, cfg.vocab_size, cfg.eos_token_id)
+        app = create_app(package=pkg, engine=make_engine(), tokenizer=tok, served_model_name=name,
+                         engine_factory=make_engine)
+    if args.ready_fd is not None:
+        os.write(args.ready_fd, json.dumps({"state": "listening", "host": pkg.admin_config.host,
+                                            "port": pkg.admin_config.port}).encode() + b"\n")
+    uvicorn.run(app, host=pkg.admin_config.host, port=pkg.admin_config.port or 8000,
+                uds=pkg.admin_config.uds, log_level=(args.log_level_http or "warning"))
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="uniserve_v1_b200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    s = sub.add_parser("serve", help="serve a policy package")
+    s.add_argument("package")
+    s.add_argument("--ready-fd", type=int, default=None)
+    s.add_argument("--log-level", default=None)
+    s.add_argument("--log-level-http", default=None)
+    b = sub.add_parser("build", help="compile the native libraries for sm_100a")
+    b.add_argument("--force", action="store_true")
+    l = sub.add_parser("layout", help="print the resolved device layout of a package")
+    l.add_argument("package")
+    a = ap.parse_args(argv)
+    if a.cmd == "serve":
+        return serve(a)
+    if a.cmd == "build":
+        from . import build
+        print(build.build(force=a.force)["kernels"])
+        return 0
+    from .config.policy import Package
+    print(json.dumps(Package.load(a.package).layout(), indent=1))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -81,10 +81,17 @@ class H3Config:
                    audio_channels=8, time_embed_dim=128, sinusoid_dim=64)
 
     def latent_shape(self, frames: int, width: int, height: int):
-        """Latent grid of a clip: frames follow the 17n+5 rule (5 latent frames per 17)."""
-        lf = ((frames + self.vae_temporal_frames - 1) // self.vae_temporal_frames) * \
-            self.vae_latent_frames
+        """Latent grid of a clip.  Frame counts follow the rule 17n + 5; each clip
+        of 17 frames gives 5 latent frames and the 5-frame tail 2 more
+        (124 frames -> 37 latent frames; 1344x768 -> 84x48 latent, 1008 tokens each)."""
+        n = max(0, (frames - 5)) // self.vae_temporal_frames
+        lf = self.vae_latent_frames * n + 2
         return lf, height // self.vae_spatial, width // self.vae_spatial
+
+    def audio_rows(self, frames: int) -> int:
+        """Audio latent rows of a clip: 40 latents per second, two channels."""
+        import math
+        return 2 * int(math.ceil(frames / self.fps * self.audio_latents_per_second))
 
 
 # ------------------------------------------------------------------ schedules --

@@ -1,0 +1,171 @@
+"""The engine loop of a serving process and the request-side adapter around it.
+
+One thread owns the engine (one issuer per device); HTTP handlers hand it
+requests through a queue and receive step outputs on per-request asyncio queues.
+A finished, failed or aborted request always ends its stream.  Requests are kept
+as migratable facts (prompt, generated tokens, seed) so a restarted engine can
+resume them (crates/daemon/src/migration.rs:12-25, leader.rs:1559, engine/hold.rs,
+reference project paths).
+"""
+from __future__ import annotations
+
+import asyncio
+import queue
+import threading
+import time
+import uuid
+from typing import Optional
+
+from ..engine.types import FinishReason, SamplingParams, StepOutput
+
+
+class Overloaded(RuntimeError):
+    pass
+
+
+class EngineService:
+    def __init__(self, engine, observation=None, max_queued: Optional[int] = None,
+                 max_migrations: int = 3, engine_factory=None):
+        self.engine = engine
+        self.obs = observation
+        self.max_queued = max_queued
+        self.max_migrations = max_migrations
+        self.engine_factory = engine_factory      # rebuilds the engine after a fatal failure
+        self.inbox: queue.Queue = queue.Queue()
+        self.streams: dict = {}                   # request_id -> (loop, asyncio.Queue)
+        self.meta: dict = {}
+        self.lock = threading.Lock()
+        self.wake = threading.Event()
+        self.stopping = False
+        self.paused = False
+        self.thread = threading.Thread(target=self._run, name="engine-loop", daemon=True)
+        self.started = False
+        self.last_snapshot = 0.0
+        self.steps = 0
+
+    def start(self):
+        if not self.started:
+            self.started = True
+            self.thread.start()
+
+    def stop(self, timeout: float = 30.0):
+        self.stopping = True
+        self.wake.set()
+        if self.started:
+            self.thread.join(timeout)
+
+    # ------------------------------------------------------------ submission --
+    def submit(self, prompt_ids, params: SamplingParams, request_id: Optional[str] = None,
+               priority: int = 0, cache_salt: Optional[str] = None):
+        """Returns (request_id, asyncio.Queue of StepOutput); call from an event loop."""
+        if self.max_queued is not None and self.inbox.qsize() + len(self.streams) >= self.max_queued:
+            raise Overloaded("too many queued requests")
+        rid = request_id or "chatcmpl-" + uuid.uuid4().hex
+        loop = asyncio.get_running_loop()
+        q: asyncio.Queue = asyncio.Queue()
+        with self.lock:
+            self.streams[rid] = (loop, q)
+            self.meta[rid] = {"arrival": time.monotonic(), "first": None, "tokens": 0,
+                              "prompt": list(prompt_ids), "params": params, "outputs": [],
+                              "migrations": 0, "priority": priority, "salt": cache_salt}
+        self.inbox.put(("add", rid, list(prompt_ids), params, priority, cache_salt, None))
+        self.wake.set()
+        return rid, q
+
+    def abort(self, request_id: str):
+        self.inbox.put(("abort", request_id))
+        self.wake.set()
+
+    # ------------------------------------------------------------------ loop --
+    def _deliver(self, out: StepOutput):
+        with self.lock:
+            ent = self.streams.get(out.request_id)
+            meta = self.meta.get(out.request_id)
+        if meta is not None and out.new_token_ids:
+            now = time.monotonic()
+            if meta["first"] is None:
+                meta["first"] = now
+                if self.obs:
+                    self.obs.observe("uniserve_ttft_seconds", now - meta["arrival"])
+            meta["tokens"] += len(out.new_token_ids)
+            meta["outputs"].extend(out.new_token_ids)
+        if ent is not None:
+            loop, q = ent
+            loop.call_soon_threadsafe(q.put_nowait, out)
+        if out.finished:
+            with self.lock:
+                self.streams.pop(out.request_id, None)
+                meta = self.meta.pop(out.request_id, None)
+            if self.obs and meta:
+                dur = time.monotonic() - meta["arrival"]
+                outcome = out.finish_reason.value if out.finish_reason else "unknown"
+                self.obs.inc("uniserve_requests_total", {"outcome": outcome})
+                if meta["tokens"] > 1 and meta["first"]:
+                    self.obs.observe("uniserve_tpot_seconds",
+                                     (time.monotonic() - meta["first"]) / (meta["tokens"] - 1))
+                self.obs.event("request", out.request_id, outcome=outcome, seconds=dur,
+                               output_tokens=meta["tokens"], prompt_tokens=len(meta["prompt"]),
+                               cached_tokens=out.num_cached_tokens)
+
+    def _recover(self, error: Exception):
+        """Fatal worker failure: rebuild the engine and resubmit every live request
+        with the tokens it already generated (bounded by ``max_migrations``)."""
+        if self.engine_factory is None:
+            with self.lock:
+                live = list(self.streams.keys())
+            for rid in live:
+                self._deliver(StepOutput(rid, [], True, FinishReason.ERROR, error=str(error)))
+            return
+        self.engine = self.engine_factory()
+        with self.lock:
+            live = list(self.meta.items())
+        for rid, m in live:
+            m["migrations"] += 1
+            if m["migrations"] > self.max_migrations:
+                self._deliver(StepOutput(rid, [], True, FinishReason.ERROR,
+                                         error=f"migrated more than {self.max_migrations} times"))
+                continue
+            self.inbox.put(("add", rid, m["prompt"], m["params"], m["priority"], m["salt"],
+                            list(m["outputs"])))
+        if self.obs:
+            self.obs.inc("uniserve_engine_restarts_total")
+
+    def _run(self):
+        while not self.stopping:
+            try:
+                while True:
+                    msg = self.inbox.get_nowait()
+                    if msg[0] == "add":
+                        _, rid, ids, params, prio, salt, outputs = msg
+                        try:
+                            self.engine.add_request(ids, params, request_id=rid, priority=prio,
+                                                    cache_salt=salt, output_ids=outputs)
+                        except Exception as e:      # input_error rejects the request
+                            self._deliver(StepOutput(rid, [], True, FinishReason.ERROR, error=str(e)))
+                    elif msg[0] == "abort":
+                        if self.engine.abort(msg[1]):
+                            self._deliver(StepOutput(msg[1], [], True, FinishReason.ABORT))
+            except queue.Empty:
+                pass
+            if self.paused or not self.engine.has_work():
+                self.wake.wait(0.05)
+                self.wake.clear()
+                continue
+            try:
+                outs = self.engine.step()
+            except Exception as e:
+                self._recover(e)
+                continue
+            self.steps += 1
+            for o in outs:
+                self._deliver(o)
+            now = time.monotonic()
+            if self.obs and now - self.last_snapshot > 1.0:
+                self.last_snapshot = now
+                st = self.engine.stats()
+                self.obs.set("uniserve_kv_cache_used_pages", st["kv"]["pages"] - st["kv"]["free"],
+                             {"tier": "device"})
+                self.obs.set("uniserve_running_requests", st["running"])
+                self.obs.set("uniserve_waiting_requests", st["waiting"])
+                self.obs.set("uniserve_preemptions_total", st["preemptions"])
+                self.obs.snapshot()

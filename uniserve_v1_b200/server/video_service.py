@@ -1,0 +1,223 @@
+"""Video generation service: the request state machine and the job store.
+
+Phases of a request (crates/engine/src/scheduler/video.rs:1-33, :86-116, reference
+project path): ``TextEncode`` -> ``LatentPrepare`` -> ``Denoise`` x steps ->
+``VideoDecode`` || ``AudioDecode`` -> ``VideoEncode``, ``AudioEncode`` -> ``Mux``.
+A trajectory is resumable at step boundaries: the job keeps (seed, step, latents),
+and because the noise is addressable a restarted job redraws identical latents.
+Jobs are kept for an hour, within one GiB of results (oldest evicted first).
+"""
+from __future__ import annotations
+
+import asyncio
+import hashlib
+import threading
+import time
+import uuid
+from collections import OrderedDict
+from typing import Optional
+
+import torch
+
+from ..models.h3_vae import AudioVaeDecoder, VideoVaeDecoder
+from ..models.minimax_h3 import Denoiser, H3Transformer
+from ..ops import media as M
+
+
+class TextEncoder:
+    """Prompt -> text features [n, text_dim].  The served family conditions on a
+    Qwen3-VL encoder (50 of 64 layers); without its checkpoint the stand-in here
+    embeds the prompt's bytes deterministically (hash-seeded normal rows), which
+    keeps prompt capacity, caching by key and every downstream shape real."""
+
+    def __init__(self, text_dim: int, max_tokens: int = 512):
+        self.text_dim, self.max_tokens = text_dim, max_tokens
+        self.cache: OrderedDict = OrderedDict()
+
+    def key(self, prompt: str) -> str:
+        return hashlib.sha256(prompt.encode()).hexdigest()
+
+    def encode(self, prompt: str, device) -> torch.Tensor:
+        k = self.key(prompt)
+        if k in self.cache:
+            self.cache.move_to_end(k)
+            return self.cache[k].to(device)
+        toks = list(prompt.encode())[:self.max_tokens] or [0]
+        rows = []
+        for i, t in enumerate(toks):
+            g = torch.Generator().manual_seed((t << 20) ^ i)
+            rows.append(torch.randn(self.text_dim, generator=g))
+        feats = torch.stack(rows, 0)
+        self.cache[k] = feats
+        while len(self.cache) > 64:
+            self.cache.popitem(last=False)
+        return feats.to(device)
+
+
+class VideoJob:
+    def __init__(self, prompt: str, plan):
+        self.id = "video_" + uuid.uuid4().hex[:24]
+        self.prompt, self.plan = prompt, plan
+        self.state = "queued"
+        self.phase = "Queued"
+        self.progress = 0.0
+        self.created = int(time.time())
+        self.completed_at: Optional[int] = None
+        self.error: Optional[str] = None
+        self.content: Optional[bytes] = None
+        self.step = 0
+        self.cancelled = False
+        self._done = threading.Event()
+        self._waiters: list = []
+
+    def record(self) -> dict:
+        p = self.plan
+        return {"id": self.id, "object": "video", "status": self.state, "phase": self.phase,
+                "progress": round(self.progress, 3), "created_at": self.created,
+                "completed_at": self.completed_at, "size": f"{p.width}x{p.height}",
+                "num_frames": p.num_frames, "fps": p.fps, "seconds": f"{p.seconds:.3f}",
+                "seed": p.seed, "task": p.task, "error": self.error,
+                "bytes": len(self.content) if self.content else None}
+
+    async def wait(self):
+        loop = asyncio.get_running_loop()
+        await loop.run_in_executor(None, self._done.wait)
+
+    def finish(self, state: str, error: Optional[str] = None):
+        self.state, self.error = state, error
+        self.completed_at = int(time.time())
+        self._done.set()
+
+
+class VideoService:
+    def __init__(self, transformer: H3Transformer, video_vae: VideoVaeDecoder,
+                 audio_vae: AudioVaeDecoder, sizes=None, max_seconds: int = 15,
+                 retention_s: float = 3600.0, store_bytes: int = 1 << 30, observation=None):
+        from .video_rules import SIZES
+        self.model = transformer
+        self.denoiser = Denoiser(transformer)
+        self.steps = self.denoiser.steps
+        self.video_vae, self.audio_vae = video_vae, audio_vae
+        self.text = TextEncoder(transformer.cfg.text_dim)
+        self.sizes = sizes or SIZES
+        self.max_seconds = max_seconds
+        self.retention_s, self.store_bytes = retention_s, store_bytes
+        self.obs = observation
+        self._jobs: OrderedDict = OrderedDict()
+        self._queue: list = []
+        self._cv = threading.Condition()
+        self._stop = False
+        self._thread = threading.Thread(target=self._run, name="video-loop", daemon=True)
+        self._started = False
+
+    def start(self):
+        if not self._started:
+            self._started = True
+            self._thread.start()
+
+    def stop(self):
+        with self._cv:
+            self._stop = True
+            self._cv.notify_all()
+
+    # ------------------------------------------------------------------- jobs --
+    def submit(self, prompt: str, plan) -> VideoJob:
+        job = VideoJob(prompt, plan)
+        with self._cv:
+            self._jobs[job.id] = job
+            self._queue.append(job)
+            self._cv.notify_all()
+        self.start()
+        return job
+
+    def get(self, job_id: str) -> Optional[VideoJob]:
+        self._evict()
+        return self._jobs.get(job_id)
+
+    def jobs(self) -> list:
+        self._evict()
+        return list(self._jobs.values())
+
+    def delete(self, job_id: str) -> bool:
+        with self._cv:
+            job = self._jobs.pop(job_id, None)
+            if job is None:
+                return False
+            job.cancelled = True
+            if job in self._queue:
+                self._queue.remove(job)
+                job.finish("failed", "cancelled")
+        return True
+
+    def _evict(self):
+        now = time.time()
+        with self._cv:
+            for jid, j in list(self._jobs.items()):
+                if j.completed_at and now - j.completed_at > self.retention_s:
+                    del self._jobs[jid]
+            total = sum(len(j.content or b"") for j in self._jobs.values())
+            for jid, j in list(self._jobs.items()):
+                if total <= self.store_bytes:
+                    break
+                if j.content:
+                    total -= len(j.content)
+                    del self._jobs[jid]
+
+    # ---------------------------------------------------------------- pipeline --
+    def generate(self, job: VideoJob) -> bytes:
+        cfg, p, dev = self.model.cfg, job.plan, self.model.device
+        job.phase = "TextEncode"
+        feats = self.text.encode(job.prompt, dev)
+        job.phase = "LatentPrepare"
+        lf, lh, lw = cfg.latent_shape(p.num_frames, p.width, p.height)
+        n_audio_rows = cfg.audio_rows(p.num_frames)
+        st = self.denoiser.prepare(p.seed, lf, lh, lw, n_audio_rows, feats)
+        job.phase = "Denoise"
+        while st.step < self.denoiser.steps:
+            if job.cancelled:
+                raise RuntimeError("cancelled")
+            self.denoiser.step(st)
+            job.step = st.step
+            job.progress = 0.8 * st.step / self.denoiser.steps
+        job.phase = "VideoDecode"
+        units = self.video_vae.decode(st.video)
+        frames = torch.cat([f for _, f in units], 0)[:p.num_frames]
+        if frames.shape[-2:] != (p.height, p.width):
+            frames = torch.nn.functional.interpolate(frames, size=(p.height, p.width),
+                                                     mode="bilinear", align_corners=False)
+        job.progress = 0.9
+        job.phase = "AudioDecode"
+        # audio rows are [time x 2 channels, latent_channels]: split channels into the batch
+        a = st.audio.view(-1, 2, cfg.audio_channels).permute(1, 2, 0).contiguous()
+        wav = self.audio_vae.decode(a)
+        want = int(round(p.num_frames / p.fps * self.audio_vae.cfg.sample_rate))
+        wav = wav[:, :want] if wav.shape[1] >= want else torch.nn.functional.pad(
+            wav, (0, want - wav.shape[1]))
+        job.phase = "VideoEncode"
+        y, u, v = M.rgb_to_yuv420(frames)
+        job.phase = "AudioEncode"
+        pcm = M.pcm_interleave(wav)
+        job.phase = "Mux"
+        return M.write_mp4(y, u, v, p.fps, pcm, self.audio_vae.cfg.sample_rate)
+
+    def _run(self):
+        while True:
+            with self._cv:
+                while not self._queue and not self._stop:
+                    self._cv.wait(0.5)
+                if self._stop:
+                    return
+                job = self._queue.pop(0)
+            job.state = "in_progress"
+            t0 = time.monotonic()
+            try:
+                job.content = self.generate(job)
+                job.progress = 1.0
+                job.finish("completed")
+                if self.obs:
+                    self.obs.observe("uniserve_video_seconds", time.monotonic() - t0)
+                    self.obs.inc("uniserve_requests_total", {"outcome": "completed"})
+            except Exception as e:
+                job.finish("failed", str(e))
+                if self.obs:
+                    self.obs.inc("uniserve_requests_total", {"outcome": "failed"})
