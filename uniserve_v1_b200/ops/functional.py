@@ -189,8 +189,16 @@ def linear(x, w, bias=None, out_dtype=None, out=None, block_n=None):
     out_dtype = out_dtype or x.dtype
     if not _cuda(x):
         return R.linear(x, w, bias, out_dtype)
-    assert x.dtype == BF16 and w.dtype == BF16 and x.stride(-1) == 1 and w.is_contiguous()
+    assert x.dtype == BF16 and w.dtype == BF16
     x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    if not w.is_contiguous():
+        w = w.contiguous()
+    if x2.shape[1] % 8:                       # TMA rows are 16-byte multiples: pad K with zeros
+        padk = 8 - x2.shape[1] % 8
+        x2 = torch.nn.functional.pad(x2, (0, padk))
+        w = torch.nn.functional.pad(w, (0, padk))
     rows, K = x2.shape
     M = w.shape[0]
     if out is None:

@@ -58,12 +58,13 @@ class FusedComm:
         handle = (ctypes.c_ubyte * 64)()
         N.check(lib.us_symm_create(world, rank, sites, self.site_bytes, handle), "us_symm_create")
         mine = bytes(handle)
-        gathered = [None] * world
-        dist.all_gather_object(gathered, mine, group=group)
-        blob = b"".join(gathered)
-        buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
-        N.check(lib.us_symm_attach(buf), "us_symm_attach")
-        dist.barrier(group=group)
+        if world > 1:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, mine, group=group)
+            blob = b"".join(gathered)
+            buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
+            N.check(lib.us_symm_attach(buf), "us_symm_attach")
+            dist.barrier(group=group)
         self._views = {}
 
     def close(self):

@@ -52,7 +52,12 @@ def timeit(fn, iters=10, warmup=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["flash", "gemm", "gated", "decode"])
+    ap.add_argument("op", choices=["flash", "gemm", "gated", "decode", "moe", "fused-norm",
+                                   "ulysses"])
+    ap.add_argument("--experts", type=int, default=128)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--hidden", type=int, default=2048)
+    ap.add_argument("--inter", type=int, default=768)
     ap.add_argument("--rows", type=int, default=37710)
     ap.add_argument("--heads", type=int, default=7)
     ap.add_argument("--m", type=int, default=5376)
@@ -86,6 +91,61 @@ def main():
         out.update(rows=a.rows, m=a.m, k=a.k, ms=ms, tflops=flops / ms / 1e9,
                    frac_compute=flops / ms / 1e9 / tfl, tbs=byts / ms / 1e9,
                    frac_memory=byts / ms / 1e9 / tbs)
+    elif a.op == "moe":
+        # one MoE layer of a decode step: route, sort, gather, grouped FC1 + FC2, un-permute
+        T, E, k, H, I = a.batch, a.experts, a.topk, a.hidden, a.inter
+        x = rnd(T, H)
+        w13, w2 = rnd(E, 2 * I, H), rnd(E, H, I)
+        logits = torch.randn(T, E, generator=g, device=dev)
+        ids, wts = F.topk_softmax(logits, k, True)
+        ws = F.MoeWorkspace.create(T, k, E, H, I, dev)
+        ms = timeit(lambda: F.moe_experts(x, ids, wts, w13, w2, ws=ws), a.iters)
+        active = int(torch.unique(ids).numel())
+        byts = active * (w13[0].numel() + w2[0].numel()) * 2.0
+        out.update(tokens=T, experts=E, active_experts=active, ms=ms, tbs=byts / ms / 1e9,
+                   frac_memory=byts / ms / 1e9 / tbs)
+    elif a.op == "fused-norm":
+        # all-reduce + residual + RMSNorm over the peer heap; one rank (its own peer) so a
+        # profiler can attach; the 2/8-rank numbers come from bench.py
+        from ..parallel.symm import FusedComm
+        T, H = a.batch, a.hidden
+        fc = FusedComm(None, 0, 1, dev, H, sites=4)
+        w = torch.ones(H, dtype=bf, device=dev)
+        fc.site_tensor(0, T, H).copy_(rnd(T, H))
+        res = torch.zeros(T, H, dtype=torch.float32, device=dev)
+
+        def run():
+            N_.call("us_allreduce_add_rmsnorm", 0, N_.ptr(res), N_.ptr(w), N_.ptr(y), T, H, 1e-6, 0,
+                    N_.stream())
+        from ..ops import native as N_
+        y = torch.empty(T, H, dtype=bf, device=dev)
+        ms = timeit(run, a.iters)
+        out.update(rows=T, hidden=H, ms=ms)
+    elif a.op == "ulysses":
+        # the two fused GEMMs of the Ulysses block with this rank as its own peer:
+        # QKV projection scattering from the epilogue, to_out pulling its K slices by TMA
+        import ctypes
+        from ..ops import native as N_
+        from ..parallel import ulysses as U
+        from ..parallel.symm import FusedComm
+        rows, H, hl, D = a.rows, a.m, a.heads, 128
+        W = 3 * hl * D
+        fc = FusedComm(None, 0, 1, dev, 0, sites=4, site_bytes=rows * max(W, H) * 2)
+        x = rnd(rows, H)
+        wqkv, wout = rnd(W, H), rnd(H, hl * D)
+        ptr_q = (ctypes.c_void_p * 1)(fc.peer_site_ptr(0, 0))
+        ptr_a = (ctypes.c_void_p * 1)(fc.peer_site_ptr(0, 1))
+        fc.site_tensor(1, rows, hl * D).copy_(rnd(rows, hl * D))
+        o = torch.empty(rows, H, dtype=bf, device=dev)
+        bn = F._block_n(rows, False)
+        ms1 = timeit(lambda: N_.call("us_gemm_wx_scatter", N_.ptr(wqkv), N_.ptr(x), W, H, rows, H,
+                                     H, W, ptr_q, W, 0, bn, N_.stream()), a.iters)
+        ms2 = timeit(lambda: N_.call("us_gemm_wx_pull", N_.ptr(wout), ptr_a, 1, hl * D, N_.ptr(o),
+                                     H, hl * D, rows, hl * D, hl * D, H, 0, bn, N_.stream()),
+                     a.iters)
+        out.update(rows=rows, hidden=H, heads_local=hl, scatter_ms=ms1,
+                   scatter_tflops=2.0 * rows * W * H / ms1 / 1e9, pull_ms=ms2,
+                   pull_tflops=2.0 * rows * H * hl * D / ms2 / 1e9)
     else:
         B, Hq, Hkv, D, page = a.batch, 32, 4, 128, 16
         per = (a.ctx + page - 1) // page
