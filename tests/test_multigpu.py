@@ -195,3 +195,70 @@ def test_h3_fused_ulysses_matches_all_to_all_and_single_gpu():
     st = den.prepare(seed=42, latent_frames=3, lat_h=8, lat_w=16, n_audio=20, text_features=text)
     den.run(st)
     torch.testing.assert_close(vb, st.video.cpu(), atol=3e-2, rtol=3e-2)
+
+
+def _ep_worker(rank, world, port, q, afd):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from uniserve_v1_b200.ops import functional as F
+    from uniserve_v1_b200.ops import native as N
+    from uniserve_v1_b200.ops import reference as R
+    from uniserve_v1_b200.parallel.expert_exchange import ExpertExchange
+    T, k, H, E, I = 24, 4, 512, 16, 256
+    src = (0,) if afd else (0, 1)
+    exp = (1,) if afd else (0, 1)
+    ex = ExpertExchange(dist.group.WORLD, rank, world, dev, T, k, H, E, I, src, exp)
+    g = torch.Generator(device="cpu").manual_seed(7)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.03).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.03).to(torch.bfloat16)
+    norm_w = torch.ones(H, dtype=torch.bfloat16, device=dev)
+    ok = True
+    for it in range(3):                                    # epochs advance across layers
+        gt = torch.Generator(device="cpu").manual_seed(100 * it + rank)
+        x = (torch.randn(T, H, generator=gt) * 0.5).to(torch.bfloat16).to(dev)
+        logits = torch.randn(T, E, generator=gt).to(dev)
+        residual = torch.randn(T, H, generator=gt).to(dev)
+        live = torch.tensor([T - 3], dtype=torch.int32, device=dev)
+        if ex.is_source:
+            ids, wts = F.topk_softmax(logits, k, True, live=live)
+            ex.dispatch(x, ids, wts, live)
+        if ex.is_expert:
+            lo = ex.e_lo
+            ex.experts(w13[lo:lo + ex.experts_per_rank].to(dev).contiguous(),
+                       w2[lo:lo + ex.experts_per_rank].to(dev).contiguous())
+        if ex.is_source:
+            res2 = residual.clone()
+            y, res2 = ex.combine_add_rmsnorm(ids, live, res2, norm_w, 1e-6)
+            torch.cuda.synchronize()
+            moe = R.moe_experts(x.cpu(), ids.cpu(), wts.cpu(), w13, w2).float()
+            ref_res = residual.cpu() + moe
+            ref_y = ref_res * torch.rsqrt(ref_res.pow(2).mean(-1, keepdim=True) + 1e-6)
+            ok &= bool(torch.allclose(res2.cpu(), ref_res, atol=3e-2, rtol=3e-2))
+            ok &= bool(torch.allclose(y.float().cpu(), ref_y, atol=5e-2, rtol=5e-2))
+    torch.cuda.synchronize()
+    q.put((rank, ok, N.read_status()))
+    dist.barrier()
+    ex.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("afd", [False, True])
+def test_expert_exchange_dispatch_combine(afd):
+    """EP (every rank is source and expert) and AFD (rank 0 attention, rank 1 experts)."""
+    _need(2)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ep_worker, args=(r, 2, port, q, afd)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=600) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, ok, status in res:
+        assert ok and status == 0, res

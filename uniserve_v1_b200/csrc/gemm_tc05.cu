@@ -52,6 +52,13 @@ struct GemmArgs {
   int peer_cols;
   int peer_row_offset;
   void* peer_out[8];
+  // Route push (expert-parallel combine): permuted row r carries route
+  // i = route_map[r] = (source rank * route_per + token * top_k + slot); the epilogue
+  // multiplies by the gate weight route_w[i] and stores the row into the source
+  // rank's combine buffer at row i % route_per.
+  const int* route_map;
+  const float* route_w;
+  int route_per;
 };
 
 struct BMaps {
@@ -106,6 +113,13 @@ struct Epilogue {
     }
     val += bias;
     int orow = row0 + r;
+    if (a.route_map != nullptr) {
+      const int i = a.route_map[orow];
+      const int src = i / a.route_per;
+      const int dst = i - src * a.route_per;
+      ((__nv_bfloat16*)a.peer_out[src])[(size_t)dst * a.ldo + m] = us::f2bf(val * a.route_w[i]);
+      return;
+    }
     if (a.row_scale != nullptr) val *= a.row_scale[orow];
     if (a.out_row_map != nullptr) orow = a.out_row_map[orow];
     if (orow < 0) return;
@@ -357,6 +371,10 @@ struct PeerSpec {
   void* const* out_peers = nullptr;      // scatter: output base per rank
   int peer_cols = 0;
   int peer_row_offset = 0;
+  const int* route_map = nullptr;        // route push: see GemmArgs
+  const float* route_w = nullptr;
+  int route_per = 0;
+  int n_out_peers = 0;
 };
 
 int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M, int K, int x_rows,
@@ -421,7 +439,20 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
   a.peer_cols = 0;
   a.peer_row_offset = 0;
   for (int p = 0; p < 8; ++p) a.peer_out[p] = nullptr;
-  if (ps.out_peers) {
+  a.route_map = nullptr;
+  a.route_w = nullptr;
+  a.route_per = 0;
+  if (ps.route_map) {
+    US_REQUIRE(ps.out_peers && ps.route_w && ps.route_per > 0 && ps.n_out_peers >= 1 &&
+               ps.n_out_peers <= 8 && out_dtype == 0);
+    a.route_map = ps.route_map;
+    a.route_w = ps.route_w;
+    a.route_per = ps.route_per;
+    for (int p = 0; p < ps.n_out_peers; ++p) {
+      US_REQUIRE(ps.out_peers[p] != nullptr);
+      a.peer_out[p] = ps.out_peers[p];
+    }
+  } else if (ps.out_peers) {
     US_REQUIRE(ps.peer_cols > 0 && (ps.peer_cols % kBlockM) == 0 && M % ps.peer_cols == 0 &&
                M / ps.peer_cols <= 8 && out_dtype == 0);
     a.peer_cols = ps.peer_cols;
@@ -498,4 +529,24 @@ US_API int us_gemm_wx_pull(const void* W, const void* const* x_peers, int n_peer
   return gemm_impl(W, nullptr, out, 1, M, M, K, x_rows, ldw, ldx, ldo, 0, 0, 0, out_dtype,
                    nullptr, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, block_n,
                    ps, (cudaStream_t)stream_);
+}
+
+// Grouped FC2 of an expert-parallel layer: the epilogue applies the gate weight and
+// stores every output row into the combine buffer of the rank that owns the token
+// (see GemmArgs::route_map).  `recv_peers[p]` is rank p's combine buffer [*, ldo].
+US_API int us_gemm_wx_route_push(const void* W, const void* X, int G, int M, int K, int x_rows,
+                                 long long ldw, long long ldx, long long ldo,
+                                 void* const* recv_peers, int n_peers, const int* route_map,
+                                 const float* route_w, int route_per, const int* tile_group,
+                                 const int* tile_row0, const int* tile_rows, const int* num_tiles,
+                                 int max_tiles, int block_n, void* stream_) {
+  PeerSpec ps;
+  ps.out_peers = recv_peers;
+  ps.n_out_peers = n_peers;
+  ps.route_map = route_map;
+  ps.route_w = route_w;
+  ps.route_per = route_per;
+  return gemm_impl(W, X, nullptr, G, M, M, K, x_rows, ldw, ldx, ldo, 0, 0, 0, 0, nullptr, 0,
+                   nullptr, nullptr, tile_group, tile_row0, tile_rows, num_tiles, max_tiles,
+                   block_n, ps, (cudaStream_t)stream_);
 }

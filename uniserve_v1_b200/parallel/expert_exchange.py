@@ -1,0 +1,128 @@
+"""Expert-parallel token exchange (dispatch / combine) over peer memory.
+
+Data-parallel attention + expert parallelism: every rank keeps its own tokens,
+experts are whole on one rank.  Per MoE layer the source side routes and pushes
+token rows into the expert ranks' windows (``route_dispatch``), the expert side
+sorts what arrived and runs the grouped FC1 / FC2 where FC2's epilogue applies
+the gate weight and stores each row into the token owner's combine buffer, and
+the owner's next norm sums the k rows (``combine_add_rmsnorm``).  With disjoint
+``source_ranks`` / ``expert_ranks`` the same exchange is the attention-FFN
+disaggregated layout.  Steps are lock-step: every rank takes part in every layer
+of every step (idle ranks join with zero live tokens).
+
+Reference behaviour: docs/expert_parallelism.md:5-31, :58-85;
+crates/engine/src/runner/causal_lm/experts.rs:377-460 (reference project paths).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as F
+from ..ops import native as N
+
+N.register_signatures({
+    "us_ep_create": (N.I, [N.I, N.I, N.I, N.I, N.I, N.P]),
+    "us_ep_attach": (N.I, [N.P]),
+    "us_ep_destroy": (N.I, []),
+    "us_ep_window": (N.P, [N.I]),
+    "us_ep_peer_recv": (N.P, [N.I]),
+    "us_ep_route_dispatch": (N.I, [N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.P]),
+    "us_ep_wait": (N.I, [N.I, N.I, N.I, N.P]),
+    "us_ep_signal_combined": (N.I, [N.I, N.I, N.P]),
+    "us_ep_combine_add_rmsnorm": (N.I, [N.P, N.P, N.P, N.P, N.P, N.I, N.F, N.I, N.I, N.P]),
+    "us_gemm_wx_route_push": (N.I, [N.P, N.P, N.I, N.I, N.I, N.I, N.L, N.L, N.L, N.P, N.I, N.P,
+                                    N.P, N.I, N.P, N.P, N.P, N.P, N.I, N.I, N.P]),
+})
+
+
+class _DevBuf:
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1",
+                                         "data": (ptr, False), "version": 2}
+
+
+class ExpertExchange:
+    def __init__(self, group, rank: int, world: int, device, t_max: int, top_k: int, hidden: int,
+                 num_experts: int, inter: int, source_ranks=None, expert_ranks=None):
+        self.group, self.rank, self.world = group, rank, world
+        self.device = torch.device(device)
+        self.T, self.k, self.H, self.E, self.I = t_max, top_k, hidden, num_experts, inter
+        self.source_ranks = tuple(source_ranks if source_ranks is not None else range(world))
+        self.expert_ranks = tuple(expert_ranks if expert_ranks is not None else range(world))
+        # both role sets are contiguous rank ranges
+        assert list(self.source_ranks) == list(range(self.source_ranks[0], self.source_ranks[-1] + 1))
+        assert list(self.expert_ranks) == list(range(self.expert_ranks[0], self.expert_ranks[-1] + 1))
+        self.is_source = rank in self.source_ranks
+        self.is_expert = rank in self.expert_ranks
+        self.experts_per_rank = num_experts // len(self.expert_ranks)
+        assert self.experts_per_rank * len(self.expert_ranks) == num_experts
+        self.e_lo = (rank - self.expert_ranks[0]) * self.experts_per_rank if self.is_expert else 0
+        lib = N.kernels()
+        handle = (ctypes.c_ubyte * 64)()
+        N.check(lib.us_ep_create(world, rank, t_max, top_k, hidden, handle), "us_ep_create")
+        if world > 1:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, bytes(handle), group=group)
+            blob = b"".join(gathered)
+            buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
+            N.check(lib.us_ep_attach(buf), "us_ep_attach")
+            dist.barrier(group=group)
+        R = world * t_max * top_k
+
+        def view(which, nbytes, dtype, shape):
+            raw = torch.as_tensor(_DevBuf(lib.us_ep_window(which), nbytes), device=self.device)
+            return raw.view(dtype).view(*shape)
+
+        self.win_x = view(0, world * t_max * hidden * 2, torch.bfloat16, (world * t_max, hidden))
+        self.win_ids = view(1, R * 4, torch.int32, (world * t_max, top_k))
+        self.win_w = view(2, R * 4, torch.float32, (R,))
+        self.recv_ptrs = (ctypes.c_void_p * world)(*[lib.us_ep_peer_recv(r) for r in range(world)])
+        self.ws = None
+        if self.is_expert:
+            self.ws = F.MoeWorkspace.create(world * t_max, top_k, self.experts_per_rank, hidden,
+                                            inter, self.device)
+
+    def close(self):
+        N.kernels().us_ep_destroy()
+
+    # ------------------------------------------------------------- source side --
+    def dispatch(self, x, ids, weights, live=None) -> None:
+        """Pushes the rows of this rank's tokens to the ranks that own their experts."""
+        T = x.shape[0]
+        N.call("us_ep_route_dispatch", N.ptr(x), N.ptr(ids), N.ptr(weights), N.ptr(live), T,
+               self.experts_per_rank, self.expert_ranks[0], N.stream())
+
+    def combine_add_rmsnorm(self, ids, live, residual, w, eps: float):
+        T = ids.shape[0]
+        y = torch.empty(T, self.H, dtype=torch.bfloat16, device=self.device)
+        N.call("us_ep_combine_add_rmsnorm", N.ptr(ids), N.ptr(live), N.ptr(residual), N.ptr(w),
+               N.ptr(y), T, eps, self.expert_ranks[0], self.expert_ranks[-1] + 1, N.stream())
+        return y, residual
+
+    # ------------------------------------------------------------- expert side --
+    def experts(self, w13, w2, act: str = "silu") -> None:
+        """Waits for every source's rows, runs the local experts over what arrived and
+        pushes the weighted outputs to the token owners."""
+        ws, st = self.ws, N.stream()
+        E, I2, H = w13.shape
+        I_ = I2 // 2
+        R = self.world * self.T * self.k
+        N.call("us_ep_wait", 0, self.source_ranks[0], self.source_ranks[-1] + 1, st)
+        N.call("us_moe_sort", N.ptr(self.win_ids), R, self.e_lo, E, ws.block_n, ws.max_tiles,
+               N.ptr(ws.sorted_route), N.ptr(ws.perm_of_route), N.ptr(ws.expert_offsets),
+               N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
+               N.ptr(ws.num_tiles), st)
+        total = ws.expert_offsets[E:]
+        N.call("us_moe_gather", N.ptr(self.win_x), N.ptr(ws.sorted_route), N.ptr(total), R, self.k,
+               H, N.ptr(ws.xp), st)
+        N.call("us_gemm_wx", N.ptr(w13), N.ptr(ws.xp), N.ptr(ws.h), E, I2, I_, H, R, H, H, I_, 1,
+               I_, F._ACT[act], 0, None, 0, None, None, N.ptr(ws.tile_group), N.ptr(ws.tile_row0),
+               N.ptr(ws.tile_rows), N.ptr(ws.num_tiles), ws.max_tiles, ws.block_n, st)
+        N.call("us_gemm_wx_route_push", N.ptr(w2), N.ptr(ws.h), E, H, I_, R, I_, I_, H,
+               self.recv_ptrs, self.world, N.ptr(ws.sorted_route), N.ptr(self.win_w),
+               self.T * self.k, N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
+               N.ptr(ws.num_tiles), ws.max_tiles, ws.block_n, st)
+        N.call("us_ep_signal_combined", self.source_ranks[0], self.source_ranks[-1] + 1, st)
