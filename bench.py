@@ -111,9 +111,17 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--concurrency", type=int, default=64)
-    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--concurrency", type=int, default=0,
+                    help="concurrent requests (default 64; per rank in the dp-ep layout; "
+                         "128 in total in the afd layout)")
+    ap.add_argument("--prompt-len", type=int, default=0)
     ap.add_argument("--model", default="qwen3-30b-a3b", choices=["qwen3-30b-a3b", "tiny"])
+    ap.add_argument("--layout", default="tp-ep", choices=["tp-ep", "dp-ep", "afd"],
+                    help="tp-ep: attention heads split over all ranks, whole experts per rank, "
+                         "all-reduce fused into the norms (strong scaling, the default); "
+                         "dp-ep: data-parallel attention + expert-parallel dispatch/combine "
+                         "(weak scaling: `concurrency` requests per rank); "
+                         "afd: attention on the first half of the ranks, experts on the second")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0,
                     help="profiling only: cut the layer count (the printed line is then marked "
@@ -144,35 +152,83 @@ def main() -> int:
                 f.write(f"{time.time() - t_start:8.2f}s {what}\n")
 
     mark("start")
+    layout = args.layout if world > 1 else "tp-ep"
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    ctx = ParallelContext.single()
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-        ctx = ParallelContext.from_world(tensor=world, expert_over_tensor=True)
-        mark("groups ready")
-        if os.environ.get("US_NO_FUSED", "0") != "1":
-            from uniserve_v1_b200.parallel.symm import attach_fused
-            attach_fused(ctx, dev, hidden=2048 if args.model != "tiny" else 512)
-        mark("heap attached")
-
     cfg = Qwen3MoeConfig.qwen3_30b_a3b() if args.model == "qwen3-30b-a3b" else Qwen3MoeConfig(
         vocab_size=2048, hidden_size=512, num_hidden_layers=2, num_attention_heads=8,
         num_key_value_heads=2, head_dim=128, num_experts=16, num_experts_per_tok=4,
         moe_intermediate_size=256, eos_token_id=2047, max_position_embeddings=8192)
     if args.layers:
         cfg.num_hidden_layers = args.layers
-    K, W, C = args.steps, args.warmup, args.concurrency
+    ctx = ParallelContext.single()
+    sync_group, n_attn, is_attention = None, world, True
+    exchange, control, announcer = None, None, None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        sync_group = dist.group.WORLD
+        if layout == "tp-ep":
+            ctx = ParallelContext.from_world(tensor=world, expert_over_tensor=True)
+            mark("groups ready")
+            if os.environ.get("US_NO_FUSED", "0") != "1":
+                from uniserve_v1_b200.parallel.symm import attach_fused
+                attach_fused(ctx, dev, hidden=cfg.hidden_size)
+        else:
+            from uniserve_v1_b200.parallel.expert_exchange import ExpertExchange
+            ctx = ParallelContext.from_world(tensor=1)
+            if layout == "afd":
+                assert world % 2 == 0, "the afd layout splits the ranks in two halves"
+                n_attn = world // 2
+                ctx.source_ranks = tuple(range(n_attn))
+                ctx.expert_ranks = tuple(range(n_attn, world))
+                is_attention = rank < n_attn
+                attn_group = dist.new_group(list(range(n_attn)))
+                control = dist.new_group([0] + list(range(n_attn, world)), backend="gloo")
+                sync_group = attn_group
+            else:
+                ctx.source_ranks = ctx.expert_ranks = tuple(range(world))
+            exchange = ExpertExchange(dist.group.WORLD, rank, world, dev, 8192,
+                                      cfg.num_experts_per_tok, cfg.hidden_size, cfg.num_experts,
+                                      cfg.moe_intermediate_size, ctx.source_ranks,
+                                      ctx.expert_ranks)
+        mark("heap attached")
+
+    if args.concurrency:
+        C = args.concurrency
+    else:
+        C = 128 // n_attn if layout == "afd" else 64       # requests on this rank
+    if layout == "afd" and args.concurrency:
+        C = args.concurrency // n_attn
+    prompt_len = args.prompt_len or (512 if layout == "afd" else 1024)
+    K, W = args.steps, args.warmup
     total_steps = 2 * (K + W) + 8
-    max_len = args.prompt_len + total_steps + 16
+    max_len = prompt_len + total_steps + 16
 
     t0 = time.time()
     model = Qwen3MoeModel(cfg, dev, torch.bfloat16, ctx).init_random(seed=0)
+    model.exchange = exchange
+    mark("weights ready")
+
+    if not is_attention:
+        # Expert rank of the disaggregated layout: join every announced forward.
+        from uniserve_v1_b200.parallel.join import ExpertJoinLoop
+        joins = ExpertJoinLoop(model, control, 0).run()
+        torch.cuda.synchronize()
+        native.raise_on_device_error()
+        mark(f"joined {joins} forwards")
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
+
     eng = LLMEngine(model, max_num_seqs=C, max_model_len=max_len,
                     max_num_batched_tokens=8192, enable_prefix_cache=False)
-    g = torch.Generator().manual_seed(1234)
-    prompts = [torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist()
+    if layout == "afd":
+        from uniserve_v1_b200.parallel.join import StepAnnouncer
+        announcer = StepAnnouncer(control, 0, rank == 0)
+        eng.runner.announce = announcer
+    g = torch.Generator().manual_seed(1234 + (rank if layout != "tp-ep" else 0))
+    prompts = [torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist()
                for _ in range(C)]
     sp = SamplingParams(temperature=0.0, max_tokens=total_steps + 4, ignore_eos=True)
     for p in prompts:
@@ -186,8 +242,15 @@ def main() -> int:
 
     def barrier():
         if world > 1:
-            dist.barrier()
+            dist.barrier(group=sync_group)
         torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=sync_group)
+            return float(t.item())
+        return ms
 
     # ---- end to end through the public API: every step copies its input block
     # from pinned host memory and reads the sampled tokens back. ----
@@ -195,7 +258,7 @@ def main() -> int:
     if not args.no_e2e:
         for _ in range(W):
             eng.step()
-            mark("e2e warm-up step")
+        mark("e2e warm-up done")
         h0, d0 = eng.runner.h2d_bytes, eng.runner.d2h_bytes
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -204,17 +267,14 @@ def main() -> int:
             eng.step()
         ev1.record()
         barrier()
-        ms = ev0.elapsed_time(ev1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        e2e = {"value": C * K / (ms / 1e3), "unit": "output tokens/s",
+        ms = max_over_ranks(ev0.elapsed_time(ev1))
+        total_c = C * (n_attn if layout != "tp-ep" else 1)
+        e2e = {"value": total_c * K / (ms / 1e3), "unit": "output tokens/s",
                "ms_per_step": ms / K,
                "h2d_bytes_per_step": (eng.runner.h2d_bytes - h0) // K,
                "d2h_bytes_per_step": (eng.runner.d2h_bytes - d0) // K}
-
     mark("e2e done")
+
     # ---- device-timed decode steps: graph replays back to back, the device
     # advances its own step state; weights (57 GB) exceed L2, no flush needed. ----
     rows = list(eng.scheduler.running)
@@ -227,6 +287,7 @@ def main() -> int:
     runner._fill_decode(blk, rows, B)
     graph = runner._graph(B, "greedy")
     blk.upload()
+    runner.announce("replay", B, W)
     for _ in range(W):
         graph.graph.replay()
     sampler = ClockSampler(local)
@@ -236,6 +297,7 @@ def main() -> int:
     barrier()
     launches0 = native.launch_count
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    runner.announce("replay", B, K)
     ev0.record()
     for _ in range(K):
         graph.graph.replay()
@@ -244,28 +306,28 @@ def main() -> int:
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     mark("timed region done")
-    ms = ev0.elapsed_time(ev1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = max_over_ranks(ev0.elapsed_time(ev1))
     native.raise_on_device_error()
     launches = native.launch_count - launches0
-    value = C * K / (ms / 1e3)
+    total_c = C * (n_attn if layout != "tp-ep" else 1)
+    value = total_c * K / (ms / 1e3)
     if rank == 0:
+        par = {"tp-ep": "tp1" if world == 1 else f"tp{world}-attention+ep{world}",
+               "dp-ep": f"dp{world}-attention+ep{world} (dispatch/combine over peer memory)",
+               "afd": f"afd: attention dp{n_attn} + experts ep{world - n_attn}"}[layout]
         line = {
             "metric": "Qwen3-MoE output tokens/s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
-            "higher_is_better": True, "scaling": "strong",
+            "higher_is_better": True, "scaling": "weak" if layout == "dp-ep" else "strong",
             "vs_baseline": value / BASELINE_TOK_S, "dtype": "bf16",
             "data": "synthetic (uniform-random prompt ids, random-init N(0,0.02) weights)",
             "config": {"model": "Qwen3-30B-A3B-shaped" if args.model != "tiny" else "tiny",
                        "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
                        "experts": cfg.num_experts, "top_k": cfg.num_experts_per_tok,
-                       "global_batch": C, "seq_len": args.prompt_len,
+                       "global_batch": total_c, "seq_len": prompt_len,
                        "context_during_timing": [rows[0].num_tokens, rows[0].num_tokens + K + W],
                        "page_size": 16, "step": "one decode step of all concurrent requests",
-                       "parallelism": "tp1" if world == 1 else f"tp{world}-attention+ep{world}",
+                       "parallelism": par, "layout": layout,
                        "l2": "inputs larger than L2 (weights read per step >> 126 MB)",
                        "baseline": "64 concurrent, 20.5 ms/step on 1xGB200 (reference docs)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
@@ -277,6 +339,8 @@ def main() -> int:
     mark("line printed")
     if world > 1:
         # Graphs that captured collectives must go before their communicator.
+        if announcer is not None:
+            announcer.stop()
         eng.runner.release_graphs()
         del graph
         torch.cuda.synchronize()

@@ -229,7 +229,7 @@ def _ep_worker(rank, world, port, q, afd):
         if ex.is_expert:
             lo = ex.e_lo
             ex.experts(w13[lo:lo + ex.experts_per_rank].to(dev).contiguous(),
-                       w2[lo:lo + ex.experts_per_rank].to(dev).contiguous())
+                       w2[lo:lo + ex.experts_per_rank].to(dev).contiguous(), T)
         if ex.is_source:
             res2 = residual.clone()
             y, res2 = ex.combine_add_rmsnorm(ids, live, res2, norm_w, 1e-6)

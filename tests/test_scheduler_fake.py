@@ -1,0 +1,143 @@
+"""The real scheduler and block manager against a deterministic fake executor:
+chunked prefill, prefix reuse, recompute preemption, limits, priorities, aborts,
+failure classes and migration through the engine service."""
+import asyncio
+import random
+
+import pytest
+
+from uniserve_v1_b200.engine.scheduler import Policy
+from uniserve_v1_b200.engine.types import FinishReason, SamplingParams
+from uniserve_v1_b200.testing.fakes import FakeEngine, expected_output
+
+
+def _prompts(n, lo=3, hi=70, seed=0):
+    rng = random.Random(seed)
+    return [[rng.randrange(1000) for _ in range(rng.randrange(lo, hi))] for _ in range(n)]
+
+
+def test_outputs_are_exact_under_chunking_and_batching():
+    eng = FakeEngine(num_pages=256, max_num_seqs=4, max_num_batched_tokens=24)
+    prompts = _prompts(9)
+    ids = [eng.add_request(p, SamplingParams(max_tokens=11)) for p in prompts]
+    eng.run()
+    for rid, p in zip(ids, prompts):
+        r = eng.scheduler.requests[rid]
+        assert r.output_ids == expected_output(p, 11) and r.finish_reason == FinishReason.LENGTH
+    kinds = [k for k, _ in eng.runner.calls]
+    assert "prefill" in kinds and "decode" in kinds
+    # no chunk exceeds the token budget and at most 31 prompts share a prefill call
+    for kind, chunks in eng.runner.calls:
+        if kind == "prefill":
+            assert sum(c[2] for c in chunks) <= 24 and len(chunks) <= 31
+    assert eng.blocks.num_free + eng.blocks.num_cached >= 0 and not eng.scheduler.running
+
+
+def test_preemption_by_recompute_keeps_tokens_exact():
+    # 12 pages of 16 tokens cannot hold 4 long requests at once
+    eng = FakeEngine(num_pages=13, max_num_seqs=4, max_num_batched_tokens=64,
+                     enable_prefix_cache=False)
+    prompts = _prompts(4, 30, 40, seed=1)
+    ids = [eng.add_request(p, SamplingParams(max_tokens=40)) for p in prompts]
+    eng.run()
+    assert eng.scheduler.stats["preemptions"] > 0
+    for rid, p in zip(ids, prompts):
+        assert eng.scheduler.requests[rid].output_ids == expected_output(p, 40)
+    assert eng.blocks.num_free == 12
+
+
+def test_prefix_cache_reuse_and_salt_isolation():
+    eng = FakeEngine(num_pages=64, max_num_seqs=2)
+    base = list(range(100, 150))
+    a = eng.add_request(base + [1, 2], SamplingParams(max_tokens=3))
+    eng.run()
+    b = eng.add_request(base + [7, 8, 9], SamplingParams(max_tokens=3))
+    eng.run()
+    rb = eng.scheduler.requests[b]
+    assert rb.num_cached == 48 and rb.output_ids == expected_output(base + [7, 8, 9], 3)
+    c = eng.add_request(base + [7, 8, 9], SamplingParams(max_tokens=3), cache_salt="tenant-b")
+    eng.run()
+    assert eng.scheduler.requests[c].num_cached == 0
+    assert eng.scheduler.requests[a].output_ids == expected_output(base + [1, 2], 3)
+
+
+def test_stop_conditions_and_limits():
+    eng = FakeEngine(num_pages=64, max_model_len=40)
+    p = _prompts(1, 10, 11)[0]
+    full = expected_output(p, 30)
+    stop_tok = full[4]
+    r1 = eng.add_request(p, SamplingParams(max_tokens=30, stop_token_ids=(stop_tok,)))
+    r2 = eng.add_request(p, SamplingParams(max_tokens=30, stop_token_ids=(stop_tok,), min_tokens=8))
+    r3 = eng.add_request(p, SamplingParams(max_tokens=100))
+    eng.run()
+    q = eng.scheduler.requests
+    first = full.index(stop_tok)
+    assert q[r1].output_ids == full[:first + 1] and q[r1].finish_reason == FinishReason.STOP
+    assert len(q[r2].output_ids) >= 8
+    assert q[r3].num_tokens == 40 and q[r3].finish_reason == FinishReason.LENGTH
+    with pytest.raises(ValueError):
+        eng.add_request(list(range(40)), SamplingParams())
+    with pytest.raises(ValueError):
+        eng.add_request([], SamplingParams())
+
+
+def test_priority_and_abort():
+    class Prio(Policy):
+        pass
+    eng = FakeEngine(num_pages=64, max_num_seqs=1, policy=Prio())
+    lo = eng.add_request([1, 2, 3], SamplingParams(max_tokens=4), priority=0)
+    hi = eng.add_request([4, 5, 6], SamplingParams(max_tokens=4), priority=5)
+    gone = eng.add_request([7, 8, 9], SamplingParams(max_tokens=4), priority=9)
+    assert eng.abort(gone) and not eng.abort(gone)
+    order = []
+    for o in eng.run():
+        if o.finished:
+            order.append(o.request_id)
+    assert order == [hi, lo]
+    assert eng.scheduler.requests[gone].finish_reason == FinishReason.ABORT
+
+
+def test_numerical_fault_fails_only_its_row():
+    eng = FakeEngine(num_pages=64, nan_on={"bad"})
+    eng.add_request([1, 2, 3], SamplingParams(max_tokens=5), request_id="bad")
+    ok = eng.add_request([4, 5, 6], SamplingParams(max_tokens=5))
+    eng.run()
+    q = eng.scheduler.requests
+    assert q["bad"].finish_reason == FinishReason.ERROR and "numerical_fault" in q["bad"].error
+    assert q[ok].output_ids == expected_output([4, 5, 6], 5)
+
+
+def test_engine_service_migrates_requests_after_worker_failure():
+    """A fatal worker failure stops the engine; the service rebuilds it and every
+    live request continues from its delivered tokens (bounded by max_migrations)."""
+    from uniserve_v1_b200.server.engine_service import EngineService
+    made = []
+
+    def factory():
+        e = FakeEngine(num_pages=64, max_num_seqs=4)
+        made.append(e)
+        return e
+
+    first = FakeEngine(num_pages=64, max_num_seqs=4, fail_on={4})
+    svc = EngineService(first, None, None, max_migrations=3, engine_factory=factory)
+
+    async def go():
+        svc.start()
+        prompts = _prompts(3, 5, 20, seed=3)
+        qs = [svc.submit(p, SamplingParams(max_tokens=9)) for p in prompts]
+        outs = []
+        for (rid, q), p in zip(qs, prompts):
+            toks = []
+            while True:
+                o = await asyncio.wait_for(q.get(), 20)
+                toks += o.new_token_ids
+                if o.finished:
+                    assert o.finish_reason == FinishReason.LENGTH, o
+                    break
+            outs.append((toks, expected_output(p, 9)))
+        svc.stop()
+        return outs
+
+    for got, want in asyncio.run(go()):
+        assert got == want
+    assert len(made) == 1

@@ -3,6 +3,10 @@
 // Layout: every rank owns T local tokens per step (data-parallel attention) and
 // E / P whole experts.  Per MoE layer:
 //
+// The windows are laid out with the step's row count T as the per-source stride
+// (every rank runs the same T in a step), so a decode step of 64 rows sorts
+// P x 64 x k routes, not the prefill capacity.
+//
 //   source rank   route_dispatch   one CTA per token: stores the token's row once into
 //                                  the window of every rank that owns one of its top-k
 //                                  experts, and its ids / gate weights into every rank's
@@ -273,7 +277,7 @@ US_API int us_ep_route_dispatch(const void* x, const int* ids, const float* weig
   Ep& e = g_ep;
   US_REQUIRE(e.local && x && ids && weights && T >= 1 && T <= e.T && experts_per_rank >= 1);
   route_dispatch_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(
-      table(), e.world, e.rank, (const __nv_bfloat16*)x, ids, weights, live, e.T, e.k, e.H,
+      table(), e.world, e.rank, (const __nv_bfloat16*)x, ids, weights, live, T, e.k, e.H,
       experts_per_rank, first_expert_rank, e.off_x, e.off_ids, e.off_w, e.off_flags, e.state);
   US_LAUNCH_CHECK();
   return US_OK;

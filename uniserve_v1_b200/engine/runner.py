@@ -90,6 +90,9 @@ class CausalLmRunner:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._readback = None
+        # Called before every forward with (kind, rows, count): the disaggregated layout
+        # hooks its step announcer in here so expert ranks can join (parallel/join.py).
+        self.announce = lambda kind, rows, count=1: None
         if self.device.type == "cuda":
             N.kernels().us_status_ptr()       # allocate the status word before any capture
 
@@ -125,7 +128,7 @@ class CausalLmRunner:
         max_len = self.max_model_len
         splits = F.decode_splits(B, self.model.Hkv, max_len) if self.device.type == "cuda" else 1
         meta = AttnMeta(kind="decode", slots=d["slots"], page_table=d["page_table"],
-                        seq_lens=d["seq_lens"], splits=splits)
+                        seq_lens=d["seq_lens"], splits=splits, live=d["live"])
         hidden = self.model.forward(d["input_ids"], d["positions"], meta, self.kv_caches)
         logits = self.model.logits(hidden)
         if variant == "greedy":
@@ -164,6 +167,7 @@ class CausalLmRunner:
         blk.dev.zero_()
         blk.d["slots"].fill_(-1)
         torch.cuda.synchronize()
+        self.announce("eager", B)
         with torch.cuda.stream(s):
             self._decode_body(blk, B, variant)
         torch.cuda.current_stream().wait_stream(s)
@@ -173,6 +177,7 @@ class CausalLmRunner:
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
         before = N.launch_count
+        self.announce("capture", B)
         with torch.cuda.graph(graph, pool=self._pool):
             logits, sampled = self._decode_body(blk, B, variant)
         launches = N.launch_count - before
@@ -262,6 +267,7 @@ class CausalLmRunner:
         g = self._graph(B, variant)
         self.h2d_bytes += blk.upload()
         logits = sampled = None
+        self.announce("replay" if g is not None else "eager", B, steps)
         for _ in range(steps):
             if g is not None:
                 g.graph.replay()
@@ -421,6 +427,7 @@ class CausalLmRunner:
         meta = AttnMeta(kind="prefill", slots=d[2 * T:3 * T], cu_q=d[3 * T:3 * T + nq],
                         cu_k=d[3 * T + nq:3 * T + 2 * nq], max_q=max_q, max_k=max_k,
                         context_lens=ctx, page_table=page_table)
+        self.announce("eager", T)
         hidden = self.model.forward(d[:T], d[T:2 * T], meta, self.kv_caches)
         if not sample_rows:
             return None, None, []

@@ -124,6 +124,7 @@ class AttnMeta:
     max_k: int = 0
     context_lens: Optional[list] = None         # per sequence keys already in the cache
     logits_rows: Optional[torch.Tensor] = None  # rows whose logits are needed (int32)
+    live: Optional[torch.Tensor] = None         # device word: rows that are real (padding after)
 
 
 class Qwen3MoeModel:
@@ -142,6 +143,18 @@ class Qwen3MoeModel:
         self.D = cfg.head_dim
         self.E_local = cfg.num_experts // self.ctx.ep_size if cfg.num_experts else 0
         self.e_lo = self.E_local * self.ctx.ep_rank
+        # Exchange layout (data-parallel attention + expert parallelism, or attention-FFN
+        # disaggregation): experts live whole on the expert ranks, attention is not split.
+        self.expert_ranks = getattr(self.ctx, "expert_ranks", None)
+        self.source_ranks = getattr(self.ctx, "source_ranks", None)
+        self.exchange = None
+        if self.expert_ranks is not None:
+            r = self.ctx.world_rank
+            n = len(self.expert_ranks)
+            self.E_local = cfg.num_experts // n if r in self.expert_ranks else 0
+            self.e_lo = (r - self.expert_ranks[0]) * (cfg.num_experts // n) \
+                if r in self.expert_ranks else 0
+        self.is_source = self.source_ranks is None or self.ctx.world_rank in self.source_ranks
         self.inv_freq = R.rope_inv_freq(self.D, cfg.rope_theta, self.device)
         self.scale = 1.0 / math.sqrt(self.D)
         self.layers: list[LayerWeights] = []
@@ -295,6 +308,9 @@ class Qwen3MoeModel:
         With a pending site the sum, the residual add and the norm are one kernel."""
         if site is None:
             return F.add_rmsnorm(h, residual, w, self.cfg.rms_norm_eps)
+        if isinstance(site, tuple):         # pending expert-parallel combine
+            return self.exchange.combine_add_rmsnorm(site[1], getattr(self, "_live", None),
+                                                     residual, w, self.cfg.rms_norm_eps)
         return fc.allreduce_add_rmsnorm(site, h.shape[0], residual, w, self.cfg.rms_norm_eps)
 
     def _attention(self, fc, lw: LayerWeights, x, positions, meta: AttnMeta, kcache, vcache):
@@ -328,6 +344,14 @@ class Qwen3MoeModel:
                 out = self.ctx.all_reduce_tp(out)
             return out, site
         logits = F.linear(x, lw.router, out_dtype=torch.float32)
+        if self.exchange is not None and x.is_cuda:
+            live = getattr(self, "_live", None)
+            ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob,
+                                          live=live)
+            self.exchange.dispatch(x, ids, weights, live)
+            if self.exchange.is_expert:
+                self.exchange.experts(lw.w13, lw.w2, T)
+            return x, ("ep", ids)
         ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
         ws = None
         if x.is_cuda:
@@ -347,6 +371,7 @@ class Qwen3MoeModel:
     def forward(self, input_ids, positions, meta: AttnMeta, kv_caches) -> torch.Tensor:
         """Returns the final-normed hidden rows [T, H] (bf16).
         ``kv_caches[layer] = (k, v)`` each [pages, page_size, Hkv_local, D]."""
+        self._live = meta.live
         hidden = F.embedding(input_ids, self.embed)
         fc = self._fused(hidden.shape[0], hidden.is_cuda)
         if fc is not None:
@@ -360,6 +385,13 @@ class Qwen3MoeModel:
             hidden, site = self._mlp(fc, lw, x)
         x, _ = self._reduce_norm(fc, hidden, site, residual, self.final_norm)
         return x
+
+    def forward_experts_only(self, t_step: int) -> None:
+        """An expert rank of the disaggregated layout: every forward is the join - per
+        layer it waits for the attention ranks' rows, runs its experts and pushes back."""
+        for lw in self.layers:
+            if not lw.dense:
+                self.exchange.experts(lw.w13, lw.w2, t_step)
 
     def logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
         """FP32 logits [rows, vocab]; vocab-sharded heads are all-gathered and un-padded."""

@@ -80,10 +80,17 @@ class ExpertExchange:
         self.win_ids = view(1, R * 4, torch.int32, (world * t_max, top_k))
         self.win_w = view(2, R * 4, torch.float32, (R,))
         self.recv_ptrs = (ctypes.c_void_p * world)(*[lib.us_ep_peer_recv(r) for r in range(world)])
-        self.ws = None
-        if self.is_expert:
-            self.ws = F.MoeWorkspace.create(world * t_max, top_k, self.experts_per_rank, hidden,
-                                            inter, self.device)
+        self._ws = {}
+
+    def workspace(self, t_step: int):
+        """Sort / GEMM workspace for a step of ``t_step`` rows per source (the window
+        stride of that step; the same on every rank, which run in lock step)."""
+        ws = self._ws.get(t_step)
+        if ws is None:
+            ws = F.MoeWorkspace.create(self.world * t_step, self.k, self.experts_per_rank, self.H,
+                                       self.I, self.device)
+            self._ws[t_step] = ws
+        return ws
 
     def close(self):
         N.kernels().us_ep_destroy()
@@ -92,6 +99,7 @@ class ExpertExchange:
     def dispatch(self, x, ids, weights, live=None) -> None:
         """Pushes the rows of this rank's tokens to the ranks that own their experts."""
         T = x.shape[0]
+        assert T <= self.T, f"step of {T} rows exceeds the exchange capacity {self.T}"
         N.call("us_ep_route_dispatch", N.ptr(x), N.ptr(ids), N.ptr(weights), N.ptr(live), T,
                self.experts_per_rank, self.expert_ranks[0], N.stream())
 
@@ -103,13 +111,14 @@ class ExpertExchange:
         return y, residual
 
     # ------------------------------------------------------------- expert side --
-    def experts(self, w13, w2, act: str = "silu") -> None:
+    def experts(self, w13, w2, t_step: int, act: str = "silu") -> None:
         """Waits for every source's rows, runs the local experts over what arrived and
-        pushes the weighted outputs to the token owners."""
-        ws, st = self.ws, N.stream()
+        pushes the weighted outputs to the token owners.  ``t_step`` is the row count
+        per source of this step (the windows are laid out with that stride)."""
+        ws, st = self.workspace(t_step), N.stream()
         E, I2, H = w13.shape
         I_ = I2 // 2
-        R = self.world * self.T * self.k
+        R = self.world * t_step * self.k
         N.call("us_ep_wait", 0, self.source_ranks[0], self.source_ranks[-1] + 1, st)
         N.call("us_moe_sort", N.ptr(self.win_ids), R, self.e_lo, E, ws.block_n, ws.max_tiles,
                N.ptr(ws.sorted_route), N.ptr(ws.perm_of_route), N.ptr(ws.expert_offsets),
@@ -123,6 +132,6 @@ class ExpertExchange:
                N.ptr(ws.tile_rows), N.ptr(ws.num_tiles), ws.max_tiles, ws.block_n, st)
         N.call("us_gemm_wx_route_push", N.ptr(w2), N.ptr(ws.h), E, H, I_, R, I_, I_, H,
                self.recv_ptrs, self.world, N.ptr(ws.sorted_route), N.ptr(self.win_w),
-               self.T * self.k, N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
+               t_step * self.k, N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
                N.ptr(ws.num_tiles), ws.max_tiles, ws.block_n, st)
         N.call("us_ep_signal_combined", self.source_ranks[0], self.source_ranks[-1] + 1, st)
