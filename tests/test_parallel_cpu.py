@@ -1,5 +1,5 @@
 """Tensor- and expert-parallel sharding on CPU ranks (gloo): a model split over
-two ranks must reproduce the unsharded model."""
+two or four ranks (four: KV heads replicated twice) must reproduce the unsharded model."""
 import os
 import socket
 
@@ -40,7 +40,8 @@ def _worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-def test_tp2_ep2_matches_single_rank():
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_ep_matches_single_rank(world):
     from uniserve_v1_b200.engine.engine import LLMEngine
     from uniserve_v1_b200.engine.types import SamplingParams
     from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
@@ -53,7 +54,7 @@ def test_tp2_ep2_matches_single_rank():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     out = q.get(timeout=240)

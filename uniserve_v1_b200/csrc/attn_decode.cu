@@ -51,6 +51,7 @@ __device__ __forceinline__ void cp_async_wait() {
 
 template <int D, int G>
 __global__ void __launch_bounds__(kThreads) paged_decode_kernel(const DecodeArgs a) {
+  US_PDL_PROLOGUE();
   constexpr int kPad = 8;                      // bf16 elements of row padding for K
   constexpr int kPairs = D / 2;                // bf16x2 columns of V
   constexpr int kGroups = kThreads / kPairs;   // head groups in the PV phase
@@ -203,6 +204,7 @@ __global__ void __launch_bounds__(D) merge_splits_kernel(const float* __restrict
                                                          const float* __restrict__ part_lse,
                                                          __nv_bfloat16* __restrict__ out,
                                                          long long ldo, int Hq, int splits) {
+  US_PDL_PROLOGUE();
   const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const long long base = ((long long)b * Hq + h) * splits;
   float m = -INFINITY;
@@ -221,11 +223,11 @@ __global__ void __launch_bounds__(D) merge_splits_kernel(const float* __restrict
 template <int D, int G>
 int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
   dim3 grid(a.B, a.Hkv, a.splits);
-  paged_decode_kernel<D, G><<<grid, kThreads, 0, stream>>>(a);
+  us::launch_pdl(paged_decode_kernel<D, G>, dim3(grid), dim3(kThreads), 0, stream, a);
   US_LAUNCH_CHECK();
   if (a.splits > 1) {
     dim3 g2(a.B, a.Hq);
-    merge_splits_kernel<D><<<g2, D, 0, stream>>>(a.part_o, a.part_lse, a.out, a.ldo, a.Hq,
+    us::launch_pdl(merge_splits_kernel<D>, dim3(g2), dim3(D), 0, stream, a.part_o, a.part_lse, a.out, a.ldo, a.Hq,
                                                  a.splits);
     US_LAUNCH_CHECK();
   }
@@ -239,11 +241,9 @@ extern "C" int us_merge_decode_splits(const float* part_o, const float* part_lse
                                       void* stream) {
   dim3 g2(B, Hq);
   if (D == 128)
-    merge_splits_kernel<128><<<g2, 128, 0, (cudaStream_t)stream>>>(
-        part_o, part_lse, (__nv_bfloat16*)out, ldo, Hq, splits);
+    us::launch_pdl(merge_splits_kernel<128>, dim3(g2), dim3(128), 0, (cudaStream_t)stream, part_o, part_lse, (__nv_bfloat16*)out, ldo, Hq, splits);
   else if (D == 64)
-    merge_splits_kernel<64><<<g2, 64, 0, (cudaStream_t)stream>>>(
-        part_o, part_lse, (__nv_bfloat16*)out, ldo, Hq, splits);
+    us::launch_pdl(merge_splits_kernel<64>, dim3(g2), dim3(64), 0, (cudaStream_t)stream, part_o, part_lse, (__nv_bfloat16*)out, ldo, Hq, splits);
   else
     return US_ERR_UNSUPPORTED;
   US_LAUNCH_CHECK();

@@ -56,6 +56,7 @@ template <int G>
 __global__ void __launch_bounds__(192)
 paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const DecTcArgs a) {
+  US_PDL_PROLOGUE();
   const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
@@ -363,7 +364,7 @@ int launch_tc(const CUtensorMap& tmK, const CUtensorMap& tmV, const DecTcArgs& a
     configured = true;
   }
   dim3 grid(a.B, a.Hkv, a.splits);
-  paged_decode_tc_kernel<G><<<grid, 192, smem, stream>>>(tmK, tmV, a);
+  us::launch_pdl(paged_decode_tc_kernel<G>, dim3(grid), dim3(192), smem, stream, tmK, tmV, a);
   US_LAUNCH_CHECK();
   return US_OK;
 }

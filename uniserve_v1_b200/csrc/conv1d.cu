@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(256)
 conv1d_kernel(const float* __restrict__ x, const float* __restrict__ w,
               const float* __restrict__ bias, float* __restrict__ out, int Cin, int Cout, int Lin,
               int Lout, int K, int stride, int pad, int dil) {
+  US_PDL_PROLOGUE();
   extern __shared__ float sm[];
   const int span = (kT - 1) * stride + (K - 1) * dil + 1;
   float* xs = sm;                       // [kCi][span]
@@ -79,6 +80,7 @@ __global__ void __launch_bounds__(256)
 conv_transpose1d_kernel(const float* __restrict__ x, const float* __restrict__ w,
                         const float* __restrict__ bias, float* __restrict__ out, int Cin, int Cout,
                         int Lin, int Lout, int K, int stride, int pad) {
+  US_PDL_PROLOGUE();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int co = blockIdx.y, b = blockIdx.z;
   if (t >= Lout) return;
@@ -102,6 +104,7 @@ __global__ void __launch_bounds__(256)
 snake_kernel(const float* __restrict__ x, const float* __restrict__ log_alpha,
              const float* __restrict__ log_beta, float* __restrict__ out, int C, long long L,
              long long total) {
+  US_PDL_PROLOGUE();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const int c = (int)((i / L) % C);
@@ -115,6 +118,7 @@ __global__ void __launch_bounds__(256)
 activation1d_kernel(const float* __restrict__ x, const float* __restrict__ taps,
                     const float* __restrict__ log_alpha, const float* __restrict__ log_beta,
                     float* __restrict__ out, int C, int L, int ntaps) {
+  US_PDL_PROLOGUE();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int c = blockIdx.y % C;
   const size_t row = (size_t)blockIdx.y * L;
@@ -153,7 +157,7 @@ US_API int us_conv1d(const float* x, const float* w, const float* bias, float* o
     US_CUDA_CHECK(cudaFuncSetAttribute(conv1d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem));
   dim3 grid((Lout + kT - 1) / kT, (Cout + kCo - 1) / kCo, B);
-  conv1d_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(x, w, bias, out, Cin, Cout, Lin, Lout,
+  us::launch_pdl(conv1d_kernel, dim3(grid), dim3(256), smem, (cudaStream_t)stream, x, w, bias, out, Cin, Cout, Lin, Lout,
                                                            K, stride, pad, dil);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -166,7 +170,7 @@ US_API int us_conv_transpose1d(const float* x, const float* w, const float* bias
   const int Lout = (Lin - 1) * stride - 2 * pad + K;
   US_REQUIRE(Lout >= 1 && Cout <= 65535);
   dim3 grid((Lout + 255) / 256, Cout, B);
-  conv_transpose1d_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, w, bias, out, Cin, Cout, Lin,
+  us::launch_pdl(conv_transpose1d_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, x, w, bias, out, Cin, Cout, Lin,
                                                                   Lout, K, stride, pad);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -178,7 +182,7 @@ US_API int us_snake(const float* x, const float* log_alpha, const float* log_bet
   const long long total = (long long)B * C * L;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  snake_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(x, log_alpha, log_beta, out, C, L,
+  us::launch_pdl(snake_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, x, log_alpha, log_beta, out, C, L,
                                                               total);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -190,7 +194,7 @@ US_API int us_activation1d(const float* x, const float* taps, const float* log_a
   US_REQUIRE(x && taps && log_alpha && log_beta && out && ntaps >= 2 && (ntaps % 2) == 0);
   US_REQUIRE((long long)B * C <= 65535);
   dim3 grid((L + 255) / 256, B * C);
-  activation1d_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, taps, log_alpha, log_beta, out, C,
+  us::launch_pdl(activation1d_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, x, taps, log_alpha, log_beta, out, C,
                                                               L, ntaps);
   US_LAUNCH_CHECK();
   return US_OK;

@@ -19,6 +19,7 @@ namespace {
 __global__ void __launch_bounds__(256)
 philox_normal_kernel(float* __restrict__ out, long long n, unsigned long long seed,
                      unsigned int stream_id, float scale) {
+  US_PDL_PROLOGUE();
   // One counter yields two normals: element pair p covers indices 2p, 2p + 1.
   const long long pairs = (n + 1) / 2;
   for (long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x; p < pairs;
@@ -32,6 +33,7 @@ philox_normal_kernel(float* __restrict__ out, long long n, unsigned long long se
 
 __global__ void __launch_bounds__(256)
 scaled_add_kernel(float* __restrict__ x, const float* __restrict__ v, float s, long long n) {
+  US_PDL_PROLOGUE();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x)
     x[i] += v[i] * s;
@@ -41,6 +43,7 @@ scaled_add_kernel(float* __restrict__ x, const float* __restrict__ v, float s, l
 __global__ void __launch_bounds__(256)
 patchify_kernel(const float* __restrict__ latent, float* __restrict__ rows, int C, int Fr, int H,
                 int W) {
+  US_PDL_PROLOGUE();
   const int Hp = H / 2, Wp = W / 2;
   const long long total = (long long)Fr * Hp * Wp * C * 4;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -58,6 +61,7 @@ patchify_kernel(const float* __restrict__ latent, float* __restrict__ rows, int 
 __global__ void __launch_bounds__(256)
 unpatchify_kernel(const float* __restrict__ rows, float* __restrict__ latent, int C, int Fr,
                   int H, int W) {
+  US_PDL_PROLOGUE();
   const int Hp = H / 2, Wp = W / 2;
   const long long total = (long long)Fr * Hp * Wp * C * 4;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -75,6 +79,7 @@ unpatchify_kernel(const float* __restrict__ rows, float* __restrict__ latent, in
 __global__ void __launch_bounds__(256)
 value_first_swiglu_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                           long long rows, int I) {
+  US_PDL_PROLOGUE();
   const long long total = rows * I;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -98,7 +103,7 @@ US_API int us_philox_normal(float* out, long long n, unsigned long long seed,
                             unsigned int stream_id, float scale, void* stream) {
   US_REQUIRE(out && n >= 0);
   if (n == 0) return US_OK;
-  philox_normal_kernel<<<blocks_for((n + 1) / 2), 256, 0, (cudaStream_t)stream>>>(out, n, seed,
+  us::launch_pdl(philox_normal_kernel, dim3(blocks_for((n + 1) / 2)), dim3(256), 0, (cudaStream_t)stream, out, n, seed,
                                                                                  stream_id, scale);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -107,7 +112,7 @@ US_API int us_philox_normal(float* out, long long n, unsigned long long seed,
 US_API int us_scaled_add(float* x, const float* v, float s, long long n, void* stream) {
   US_REQUIRE(x && v && n >= 0);
   if (n == 0) return US_OK;
-  scaled_add_kernel<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(x, v, s, n);
+  us::launch_pdl(scaled_add_kernel, dim3(blocks_for(n)), dim3(256), 0, (cudaStream_t)stream, x, v, s, n);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -118,10 +123,9 @@ US_API int us_patchify(const float* latent, float* rows, int C, int Fr, int H, i
              (W % 2) == 0);
   const long long total = (long long)Fr * (H / 2) * (W / 2) * C * 4;
   if (inverse)
-    unpatchify_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(
-        rows, const_cast<float*>(latent), C, Fr, H, W);
+    us::launch_pdl(unpatchify_kernel, dim3(blocks_for(total)), dim3(256), 0, (cudaStream_t)stream, rows, const_cast<float*>(latent), C, Fr, H, W);
   else
-    patchify_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(latent, rows, C, Fr, H,
+    us::launch_pdl(patchify_kernel, dim3(blocks_for(total)), dim3(256), 0, (cudaStream_t)stream, latent, rows, C, Fr, H,
                                                                          W);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -130,8 +134,7 @@ US_API int us_patchify(const float* latent, float* rows, int C, int Fr, int H, i
 US_API int us_value_first_swiglu(const void* x, void* y, long long rows, int I, void* stream) {
   US_REQUIRE(x && y && rows >= 0 && I >= 1);
   if (rows == 0) return US_OK;
-  value_first_swiglu_kernel<<<blocks_for(rows * I), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, I);
+  us::launch_pdl(value_first_swiglu_kernel, dim3(blocks_for(rows * I)), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, I);
   US_LAUNCH_CHECK();
   return US_OK;
 }

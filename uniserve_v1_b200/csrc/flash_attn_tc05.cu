@@ -51,6 +51,7 @@ __device__ __forceinline__ float ex2f(float x) {
 __global__ void __launch_bounds__(192, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashArgs a) {
+  US_PDL_PROLOGUE();
   const int q_tile = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int q_start = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_start;
@@ -367,7 +368,7 @@ US_API int us_flash_attn_varlen(const void* q, const void* k, const void* v, voi
     configured = true;
   }
   dim3 grid((max_q + kBM - 1) / kBM, Hq, n_seqs);
-  flash_fwd_kernel<<<grid, 192, smem, stream>>>(tmQ, tmK, tmV, a);
+  us::launch_pdl(flash_fwd_kernel, dim3(grid), dim3(192), smem, stream, tmQ, tmK, tmV, a);
   US_LAUNCH_CHECK();
   return US_OK;
 }

@@ -66,6 +66,7 @@ route_dispatch_kernel(peer::Table pt, int world, int rank, const __nv_bfloat16* 
                       const int* __restrict__ live, int T, int k, int H, int experts_per_rank,
                       int first_expert_rank, size_t off_x, size_t off_ids, size_t off_w,
                       size_t off_flags, unsigned int* state) {
+  US_PDL_PROLOGUE();
   const int t = blockIdx.x;
   const bool on = !live || t < *live;
   __shared__ unsigned int targets;
@@ -110,6 +111,7 @@ route_dispatch_kernel(peer::Table pt, int world, int rank, const __nv_bfloat16* 
 // Waits until every rank in [lo, hi) has raised flag row `which` to the next epoch.
 __global__ void ep_wait_kernel(peer::Table pt, int rank, int lo, int hi, int which,
                                size_t off_flags, unsigned int* state, unsigned int* status) {
+  US_PDL_PROLOGUE();
   __shared__ unsigned int ep;
   if (threadIdx.x == 0) ep = ++state[3 + which];
   __syncthreads();
@@ -122,6 +124,7 @@ __global__ void ep_wait_kernel(peer::Table pt, int rank, int lo, int hi, int whi
 // Raises this rank's flag of row `which` at the ranks in [lo, hi).
 __global__ void ep_signal_kernel(peer::Table pt, int rank, int lo, int hi, int which,
                                  size_t off_flags, unsigned int* state) {
+  US_PDL_PROLOGUE();
   __shared__ unsigned int ep;
   if (threadIdx.x == 0) ep = ++state[which];
   __syncthreads();
@@ -140,6 +143,7 @@ combine_add_rmsnorm_kernel(peer::Table pt, int rank, int lo, int hi, size_t off_
                            const int* __restrict__ live, float* __restrict__ residual,
                            const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                            int k, int H, float eps, unsigned int* state, unsigned int* status) {
+  US_PDL_PROLOGUE();
   __shared__ float scratch[33];
   __shared__ unsigned int ep;
   const int t = blockIdx.x;
@@ -276,8 +280,7 @@ US_API int us_ep_route_dispatch(const void* x, const int* ids, const float* weig
                                 int first_expert_rank, void* stream) {
   Ep& e = g_ep;
   US_REQUIRE(e.local && x && ids && weights && T >= 1 && T <= e.T && experts_per_rank >= 1);
-  route_dispatch_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(
-      table(), e.world, e.rank, (const __nv_bfloat16*)x, ids, weights, live, T, e.k, e.H,
+  us::launch_pdl(route_dispatch_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, table(), e.world, e.rank, (const __nv_bfloat16*)x, ids, weights, live, T, e.k, e.H,
       experts_per_rank, first_expert_rank, e.off_x, e.off_ids, e.off_w, e.off_flags, e.state);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -287,7 +290,7 @@ US_API int us_ep_route_dispatch(const void* x, const int* ids, const float* weig
 US_API int us_ep_wait(int which, int lo, int hi, void* stream) {
   Ep& e = g_ep;
   US_REQUIRE(e.local && (which == 0 || which == 1) && lo >= 0 && hi <= e.world && lo < hi);
-  ep_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(table(), e.rank, lo, hi, which, e.off_flags,
+  us::launch_pdl(ep_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, table(), e.rank, lo, hi, which, e.off_flags,
                                                      e.state, us_status_ptr());
   US_LAUNCH_CHECK();
   return US_OK;
@@ -297,7 +300,7 @@ US_API int us_ep_wait(int which, int lo, int hi, void* stream) {
 US_API int us_ep_signal_combined(int lo, int hi, void* stream) {
   Ep& e = g_ep;
   US_REQUIRE(e.local && lo >= 0 && hi <= e.world && lo < hi);
-  ep_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(table(), e.rank, lo, hi, 1, e.off_flags,
+  us::launch_pdl(ep_signal_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, table(), e.rank, lo, hi, 1, e.off_flags,
                                                        e.state);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -308,8 +311,7 @@ US_API int us_ep_combine_add_rmsnorm(const int* ids, const int* live, void* resi
                                      int expert_hi, void* stream) {
   Ep& e = g_ep;
   US_REQUIRE(e.local && ids && residual && w && y && T >= 1 && T <= e.T);
-  combine_add_rmsnorm_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(
-      table(), e.rank, expert_lo, expert_hi, e.off_recv, e.off_flags, ids, live, (float*)residual,
+  us::launch_pdl(combine_add_rmsnorm_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, table(), e.rank, expert_lo, expert_hi, e.off_recv, e.off_flags, ids, live, (float*)residual,
       (const __nv_bfloat16*)w, (__nv_bfloat16*)y, e.k, e.H, eps, e.state, us_status_ptr());
   US_LAUNCH_CHECK();
   return US_OK;

@@ -105,6 +105,7 @@ allreduce_add_rmsnorm_kernel(PeerTable pt, int world, int rank, int site, size_t
                              unsigned int* epochs, float* __restrict__ residual,
                              const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                              int H, float eps, int first, unsigned int* status) {
+  US_PDL_PROLOGUE();
   __shared__ float scratch[33];
   __shared__ unsigned int flag;
   const int row = blockIdx.x;
@@ -159,6 +160,7 @@ __global__ void __launch_bounds__(256)
 allreduce_kernel(PeerTable pt, int world, int rank, int site, size_t data_off,
                  unsigned int* epochs, void* __restrict__ out, long long units16, int is_f32,
                  unsigned int* status) {
+  US_PDL_PROLOGUE();
   __shared__ unsigned int flag;
   site_barrier(pt, world, rank, site, blockIdx.x, epochs, status, &flag);
   const long long per = (units16 + gridDim.x - 1) / gridDim.x;
@@ -195,6 +197,7 @@ __global__ void __launch_bounds__(256)
 allgather_kernel(PeerTable pt, int world, int rank, int site, size_t data_off,
                  unsigned int* epochs, void* __restrict__ out, long long units16,
                  unsigned int* status) {
+  US_PDL_PROLOGUE();
   __shared__ unsigned int flag;
   site_barrier(pt, world, rank, site, blockIdx.x, epochs, status, &flag);
   const long long per = (units16 + gridDim.x - 1) / gridDim.x;
@@ -278,8 +281,7 @@ US_API int us_allreduce_add_rmsnorm(int site, void* residual, const void* w, voi
   Symm& s = g_symm;
   US_REQUIRE(s.local && site >= 0 && site < s.sites && T >= 1 && T <= kMaxCtas && (H % 8) == 0);
   US_REQUIRE((size_t)T * H * 2 <= s.site_bytes && residual && w && y);
-  allreduce_add_rmsnorm_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(
-      table(), s.world, s.rank, site, s.flag_bytes + (size_t)site * s.site_bytes, s.epochs,
+  us::launch_pdl(allreduce_add_rmsnorm_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, table(), s.world, s.rank, site, s.flag_bytes + (size_t)site * s.site_bytes, s.epochs,
       (float*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps, first,
       us_status_ptr());
   US_LAUNCH_CHECK();
@@ -294,8 +296,7 @@ US_API int us_symm_allreduce(int site, void* out, long long nbytes, int is_f32, 
   int ctas = (int)((units + 1023) / 1024);
   if (ctas > kMaxCtas) ctas = kMaxCtas;
   if (ctas < 1) ctas = 1;
-  allreduce_kernel<<<ctas, 256, 0, (cudaStream_t)stream>>>(
-      table(), s.world, s.rank, site, s.flag_bytes + (size_t)site * s.site_bytes, s.epochs, out,
+  us::launch_pdl(allreduce_kernel, dim3(ctas), dim3(256), 0, (cudaStream_t)stream, table(), s.world, s.rank, site, s.flag_bytes + (size_t)site * s.site_bytes, s.epochs, out,
       units, is_f32, us_status_ptr());
   US_LAUNCH_CHECK();
   return US_OK;
@@ -309,8 +310,7 @@ US_API int us_symm_allgather(int site, void* out, long long nbytes_per_rank, voi
   int ctas = (int)((units + 1023) / 1024);
   if (ctas > kMaxCtas) ctas = kMaxCtas;
   if (ctas < 1) ctas = 1;
-  allgather_kernel<<<ctas, 256, 0, (cudaStream_t)stream>>>(
-      table(), s.world, s.rank, site, s.flag_bytes + (size_t)site * s.site_bytes, s.epochs, out,
+  us::launch_pdl(allgather_kernel, dim3(ctas), dim3(256), 0, (cudaStream_t)stream, table(), s.world, s.rank, site, s.flag_bytes + (size_t)site * s.site_bytes, s.epochs, out,
       units, us_status_ptr());
   US_LAUNCH_CHECK();
   return US_OK;
@@ -319,6 +319,7 @@ US_API int us_symm_allgather(int site, void* out, long long nbytes_per_rank, voi
 namespace {
 __global__ void barrier_kernel(PeerTable pt, int world, int rank, int site, unsigned int* epochs,
                                unsigned int* status) {
+  US_PDL_PROLOGUE();
   __shared__ unsigned int flag;
   site_barrier(pt, world, rank, site, 0, epochs, status, &flag);
 }
@@ -338,7 +339,7 @@ US_API void* us_symm_peer_site_ptr(int rank, int site) {
 US_API int us_symm_barrier(int site, void* stream) {
   Symm& s = g_symm;
   US_REQUIRE(s.local && site >= 0 && site < s.sites);
-  barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(table(), s.world, s.rank, site, s.epochs,
+  us::launch_pdl(barrier_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, table(), s.world, s.rank, site, s.epochs,
                                                      us_status_ptr());
   US_LAUNCH_CHECK();
   return US_OK;

@@ -141,6 +141,7 @@ template <int BN, bool DUAL>
 __global__ void __launch_bounds__(192)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ BMaps tmBs,
                const GemmArgs args) {
+  US_PDL_PROLOGUE();
   constexpr int kBTile = BN * kBlockK * 2;
   constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
   constexpr uint32_t kCols = tmem_cols<BN>(DUAL);
@@ -353,13 +354,15 @@ int launch(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int m_tiles, in
   cfg.blockDim = dim3(192);
   cfg.dynamicSmemBytes = smem_needed;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = us::pdl_enabled() ? 1 : 0;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   US_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_wx_kernel<BN, DUAL>, tmA, tmB, a));
   return US_OK;
 }

@@ -5,6 +5,7 @@
 // here depends on PyTorch, so a translation unit compiles in seconds.
 #pragma once
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -61,7 +62,42 @@ __device__ __forceinline__ void us_dev_fail(unsigned int* status, unsigned int c
   if (status) atomicCAS(status, 0u, code);
 }
 
+// Programmatic dependent launch: every kernel lets its dependents be launched as soon
+// as it starts (their launch latency and prologue then overlap this kernel) and
+// waits, as its first action, until the kernels it depends on have completed and
+// their writes are visible.  Semantics are those of ordinary stream order.
+#define US_PDL_PROLOGUE()                                           \
+  do {                                                              \
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); \
+    asm volatile("griddepcontrol.wait;" ::: "memory");              \
+  } while (0)
+
 namespace us {
+
+// US_NO_PDL=1 launches every kernel with plain stream serialisation (A/B switch).
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("US_NO_PDL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 template <typename T> struct Vec8;  // 8 x 16-bit values moved as one 16-byte access
 

@@ -26,6 +26,7 @@ __device__ __forceinline__ unsigned char to_u8(float v) {
 __global__ void __launch_bounds__(128)
 rgb_to_yuv420_kernel(const float* __restrict__ rgb, unsigned char* __restrict__ y,
                      unsigned char* __restrict__ u, unsigned char* __restrict__ v, int H, int W) {
+  US_PDL_PROLOGUE();
   const int qx = blockIdx.x * blockDim.x + threadIdx.x, qy = blockIdx.y, f = blockIdx.z;
   if (qx >= W / 2) return;
   const size_t plane = (size_t)H * W;
@@ -52,6 +53,7 @@ rgb_to_yuv420_kernel(const float* __restrict__ rgb, unsigned char* __restrict__ 
 __global__ void __launch_bounds__(256)
 rgb_bytes_kernel(const float* __restrict__ rgb, unsigned char* __restrict__ out, int H, int W,
                  long long total) {
+  US_PDL_PROLOGUE();
   const size_t plane = (size_t)H * W;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -65,6 +67,7 @@ rgb_bytes_kernel(const float* __restrict__ rgb, unsigned char* __restrict__ out,
 __global__ void __launch_bounds__(256)
 pcm_interleave_kernel(const float* __restrict__ x, short* __restrict__ out, int channels,
                       long long samples) {
+  US_PDL_PROLOGUE();
   const long long total = samples * channels;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -89,6 +92,7 @@ __global__ void __launch_bounds__(256)
 tile_stitch_kernel(const float* __restrict__ tile, float* __restrict__ canvas,
                    float* __restrict__ weight, int FC, int H, int W, int th, int tw, int y0,
                    int x0, int overlap, int first_plane) {
+  US_PDL_PROLOGUE();
   const long long total = (long long)FC * th * tw;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -107,6 +111,7 @@ tile_stitch_kernel(const float* __restrict__ tile, float* __restrict__ canvas,
 __global__ void __launch_bounds__(256)
 tile_normalise_kernel(float* __restrict__ canvas, const float* __restrict__ weight, int FC,
                       long long plane) {
+  US_PDL_PROLOGUE();
   const long long total = (long long)FC * plane;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -119,6 +124,7 @@ tile_normalise_kernel(float* __restrict__ canvas, const float* __restrict__ weig
 __global__ void __launch_bounds__(256)
 cross_fade_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
                   int n, long long inner) {
+  US_PDL_PROLOGUE();
   const long long total = (long long)n * inner;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -131,6 +137,7 @@ cross_fade_kernel(const float* __restrict__ a, const float* __restrict__ b, floa
 __global__ void __launch_bounds__(256)
 frame_moments_kernel(const float* __restrict__ x, float* __restrict__ mean,
                      float* __restrict__ rstd, long long per_group, float eps) {
+  US_PDL_PROLOGUE();
   __shared__ float scratch[33];
   const float* p = x + (size_t)blockIdx.x * per_group;
   float s = 0.f;
@@ -154,6 +161,7 @@ frame_norm_pad_kernel(const float* __restrict__ x, const float* __restrict__ mea
                       const float* __restrict__ rstd, const float* __restrict__ gamma,
                       const float* __restrict__ beta, float* __restrict__ out, int C, int H, int W,
                       int groups, int pad, long long total) {
+  US_PDL_PROLOGUE();
   const int Ho = H + 2 * pad, Wo = W + 2 * pad;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -184,8 +192,7 @@ US_API int us_rgb_to_yuv420(const float* rgb, void* y, void* u, void* v, int F, 
                             void* stream) {
   US_REQUIRE(rgb && y && u && v && F >= 1 && H >= 2 && W >= 2 && (H % 2) == 0 && (W % 2) == 0);
   dim3 grid((W / 2 + 127) / 128, H / 2, F);
-  rgb_to_yuv420_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(
-      rgb, (unsigned char*)y, (unsigned char*)u, (unsigned char*)v, H, W);
+  us::launch_pdl(rgb_to_yuv420_kernel, dim3(grid), dim3(128), 0, (cudaStream_t)stream, rgb, (unsigned char*)y, (unsigned char*)u, (unsigned char*)v, H, W);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -193,7 +200,7 @@ US_API int us_rgb_to_yuv420(const float* rgb, void* y, void* u, void* v, int F, 
 US_API int us_rgb_bytes(const float* rgb, void* out, int F, int H, int W, void* stream) {
   US_REQUIRE(rgb && out && F >= 1 && H >= 1 && W >= 1);
   const long long total = (long long)F * H * W * 3;
-  rgb_bytes_kernel<<<grid_for(total), 256, 0, (cudaStream_t)stream>>>(rgb, (unsigned char*)out, H,
+  us::launch_pdl(rgb_bytes_kernel, dim3(grid_for(total)), dim3(256), 0, (cudaStream_t)stream, rgb, (unsigned char*)out, H,
                                                                       W, total);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -203,8 +210,7 @@ US_API int us_pcm_interleave(const float* x, void* out, int channels, long long 
                              void* stream) {
   US_REQUIRE(x && out && channels >= 1 && samples >= 0);
   if (samples == 0) return US_OK;
-  pcm_interleave_kernel<<<grid_for(samples * channels), 256, 0, (cudaStream_t)stream>>>(
-      x, (short*)out, channels, samples);
+  us::launch_pdl(pcm_interleave_kernel, dim3(grid_for(samples * channels)), dim3(256), 0, (cudaStream_t)stream, x, (short*)out, channels, samples);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -213,8 +219,7 @@ US_API int us_tile_stitch(const float* tile, float* canvas, float* weight, int F
                           int th, int tw, int y0, int x0, int overlap, void* stream) {
   US_REQUIRE(tile && canvas && weight && FC >= 1 && th >= 1 && tw >= 1 && overlap >= 0);
   const long long total = (long long)FC * th * tw;
-  tile_stitch_kernel<<<grid_for(total), 256, 0, (cudaStream_t)stream>>>(
-      tile, canvas, weight, FC, H, W, th, tw, y0, x0, overlap, 1);
+  us::launch_pdl(tile_stitch_kernel, dim3(grid_for(total)), dim3(256), 0, (cudaStream_t)stream, tile, canvas, weight, FC, H, W, th, tw, y0, x0, overlap, 1);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -223,7 +228,7 @@ US_API int us_tile_normalise(float* canvas, const float* weight, int FC, int H, 
                              void* stream) {
   US_REQUIRE(canvas && weight && FC >= 1);
   const long long plane = (long long)H * W;
-  tile_normalise_kernel<<<grid_for(plane * FC), 256, 0, (cudaStream_t)stream>>>(canvas, weight, FC,
+  us::launch_pdl(tile_normalise_kernel, dim3(grid_for(plane * FC)), dim3(256), 0, (cudaStream_t)stream, canvas, weight, FC,
                                                                                plane);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -232,7 +237,7 @@ US_API int us_tile_normalise(float* canvas, const float* weight, int FC, int H, 
 US_API int us_cross_fade(const float* a, const float* b, float* out, int n, long long inner,
                          void* stream) {
   US_REQUIRE(a && b && out && n >= 1 && inner >= 1);
-  cross_fade_kernel<<<grid_for((long long)n * inner), 256, 0, (cudaStream_t)stream>>>(a, b, out, n,
+  us::launch_pdl(cross_fade_kernel, dim3(grid_for((long long)n * inner)), dim3(256), 0, (cudaStream_t)stream, a, b, out, n,
                                                                                       inner);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -241,7 +246,7 @@ US_API int us_cross_fade(const float* a, const float* b, float* out, int n, long
 US_API int us_frame_moments(const float* x, float* mean, float* rstd, int frames_x_groups,
                             long long per_group, float eps, void* stream) {
   US_REQUIRE(x && mean && rstd && frames_x_groups >= 1 && per_group >= 1);
-  frame_moments_kernel<<<frames_x_groups, 256, 0, (cudaStream_t)stream>>>(x, mean, rstd, per_group,
+  us::launch_pdl(frame_moments_kernel, dim3(frames_x_groups), dim3(256), 0, (cudaStream_t)stream, x, mean, rstd, per_group,
                                                                           eps);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -252,8 +257,7 @@ US_API int us_frame_norm_pad(const float* x, const float* mean, const float* rst
                              int H, int W, int groups, int pad, void* stream) {
   US_REQUIRE(x && mean && rstd && gamma && beta && out && C % groups == 0 && pad >= 0);
   const long long total = (long long)F * C * (H + 2 * pad) * (W + 2 * pad);
-  frame_norm_pad_kernel<<<grid_for(total), 256, 0, (cudaStream_t)stream>>>(
-      x, mean, rstd, gamma, beta, out, C, H, W, groups, pad, total);
+  us::launch_pdl(frame_norm_pad_kernel, dim3(grid_for(total)), dim3(256), 0, (cudaStream_t)stream, x, mean, rstd, gamma, beta, out, C, H, W, groups, pad, total);
   US_LAUNCH_CHECK();
   return US_OK;
 }

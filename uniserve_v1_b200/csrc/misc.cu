@@ -11,6 +11,7 @@ namespace {
 __global__ void __launch_bounds__(256)
 embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, int H,
                  int vocab_lo, int vocab_hi, __nv_bfloat16* __restrict__ out) {
+  US_PDL_PROLOGUE();
   const int t = blockIdx.x;
   const int id = ids[t];
   uint4* dst = reinterpret_cast<uint4*>(out + (long long)t * H);
@@ -25,6 +26,7 @@ embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ 
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ idx, int H,
                    long long lds, __nv_bfloat16* __restrict__ dst) {
+  US_PDL_PROLOGUE();
   const int r = blockIdx.x;
   const int s = idx[r];
   uint4* d = reinterpret_cast<uint4*>(dst + (long long)r * H);
@@ -47,6 +49,7 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
                                       const int* __restrict__ live, int* __restrict__ history,
                                       int history_stride, int history_rows,
                                       const int* __restrict__ step) {
+  US_PDL_PROLOGUE();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   const bool on = !live || b < *live;
@@ -67,16 +70,19 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
                  : -1;
 }
 
-__global__ void bump_kernel(int* p) { *p += 1; }
+__global__ void bump_kernel(int* p) {
+  US_PDL_PROLOGUE(); *p += 1; }
 
 __global__ void __launch_bounds__(256)
 cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  US_PDL_PROLOGUE();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x)
     dst[i] = us::f2bf(src[i]);
 }
 __global__ void __launch_bounds__(256)
 cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, long long n) {
+  US_PDL_PROLOGUE();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x)
     dst[i] = us::bf2f(src[i]);
@@ -88,7 +94,7 @@ US_API int us_embedding(const int* ids, const void* table, int T, int H, int voc
                         int vocab_hi, void* out, void* stream) {
   US_REQUIRE(ids && table && out && T >= 0 && (H % 8) == 0);
   if (T == 0) return US_OK;
-  embedding_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(ids, (const __nv_bfloat16*)table, H,
+  us::launch_pdl(embedding_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, ids, (const __nv_bfloat16*)table, H,
                                                         vocab_lo, vocab_hi, (__nv_bfloat16*)out);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -98,7 +104,7 @@ US_API int us_gather_rows(const void* src, const int* idx, int M, int H, long lo
                           void* stream) {
   US_REQUIRE(src && idx && dst && M >= 0 && (H % 8) == 0 && (lds % 8) == 0);
   if (M == 0) return US_OK;
-  gather_rows_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src, idx, H, lds,
+  us::launch_pdl(gather_rows_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)src, idx, H, lds,
                                                           (__nv_bfloat16*)dst);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -111,13 +117,13 @@ US_API int us_decode_advance(const int* sampled, int* input_ids, int* positions,
   US_REQUIRE(sampled && input_ids && positions && seq_lens && slots && page_table && B >= 0);
   if (B == 0) return US_OK;
   cudaStream_t stream = (cudaStream_t)stream_;
-  decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(sampled, input_ids, positions,
+  us::launch_pdl(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, sampled, input_ids, positions,
                                                              seq_lens, slots, page_table, max_pages,
                                                              page_size, B, live, history,
                                                              history_stride, history_rows, step);
   US_LAUNCH_CHECK();
   if (step) {
-    bump_kernel<<<1, 1, 0, stream>>>(step);
+    us::launch_pdl(bump_kernel, dim3(1), dim3(1), 0, stream, step);
     US_LAUNCH_CHECK();
   }
   return US_OK;
@@ -129,10 +135,10 @@ US_API int us_cast(const void* src, void* dst, long long n, int to_bf16, void* s
   const int blocks = (int)((n + 256 * 8 - 1) / (256 * 8) < 65535 ? (n + 256 * 8 - 1) / (256 * 8)
                                                                   : 65535);
   if (to_bf16)
-    cast_f32_bf16_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)src,
+    us::launch_pdl(cast_f32_bf16_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (const float*)src,
                                                                    (__nv_bfloat16*)dst, n);
   else
-    cast_bf16_f32_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src,
+    us::launch_pdl(cast_bf16_f32_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)src,
                                                                    (float*)dst, n);
   US_LAUNCH_CHECK();
   return US_OK;

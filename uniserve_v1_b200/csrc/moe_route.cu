@@ -29,6 +29,7 @@ topk_softmax_kernel(const float* __restrict__ logits, int* __restrict__ ids,
                     float* __restrict__ weights, int T, int E, int top_k, int renorm,
                     const int* __restrict__ live, const int* __restrict__ expert_map,
                     int* __restrict__ load) {
+  US_PDL_PROLOGUE();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp;
   if (t >= T) return;
@@ -107,6 +108,7 @@ moe_sort_kernel(const int* __restrict__ ids, int R, int e_lo, int E, int block_n
                 int* __restrict__ expert_offsets, int* __restrict__ tile_group,
                 int* __restrict__ tile_row0, int* __restrict__ tile_rows,
                 int* __restrict__ num_tiles, unsigned int* status) {
+  US_PDL_PROLOGUE();
   __shared__ int cnt[kMaxExperts];
   __shared__ int off[kMaxExperts + 1];
   __shared__ int toff[kMaxExperts + 1];
@@ -192,6 +194,7 @@ __global__ void __launch_bounds__(256)
 moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_route,
                   const int* __restrict__ total, int top_k, int H,
                   __nv_bfloat16* __restrict__ xp) {
+  US_PDL_PROLOGUE();
   const int p = blockIdx.x;
   if (p >= *total) return;
   const int t = sorted_route[p] / top_k;
@@ -204,6 +207,7 @@ __global__ void __launch_bounds__(256)
 moe_unpermute_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ perm_of_route,
                      const float* __restrict__ weights, int top_k, int H,
                      __nv_bfloat16* __restrict__ out) {
+  US_PDL_PROLOGUE();
   const int t = blockIdx.x;
   for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -236,7 +240,7 @@ US_API int us_topk_softmax(const float* logits, int* ids, float* weights, int T,
   const int per = (E + 31) / 32;
 #define US_TOPK(P)                                                                          \
   if (per <= P) {                                                                           \
-    topk_softmax_kernel<P><<<blocks, 128, 0, stream>>>(logits, ids, weights, T, E, top_k,   \
+    us::launch_pdl(topk_softmax_kernel<P>, dim3(blocks), dim3(128), 0, stream, logits, ids, weights, T, E, top_k,   \
                                                        renorm, live, expert_map, load);     \
     US_LAUNCH_CHECK();                                                                      \
     return US_OK;                                                                           \
@@ -252,8 +256,7 @@ US_API int us_moe_sort(const int* ids, int R, int e_lo, int E, int block_n, int 
   US_REQUIRE(ids && R >= 0 && E >= 1 && E <= kMaxExperts && block_n >= 1 && max_tiles >= 1);
   US_REQUIRE(sorted_route && perm_of_route && expert_offsets && tile_group && tile_row0 &&
              tile_rows && num_tiles);
-  moe_sort_kernel<<<1, 1024, 0, (cudaStream_t)stream_>>>(
-      ids, R, e_lo, E, block_n, max_tiles, sorted_route, perm_of_route, expert_offsets, tile_group,
+  us::launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream_, ids, R, e_lo, E, block_n, max_tiles, sorted_route, perm_of_route, expert_offsets, tile_group,
       tile_row0, tile_rows, num_tiles, us_status_ptr());
   US_LAUNCH_CHECK();
   return US_OK;
@@ -263,8 +266,7 @@ US_API int us_moe_gather(const void* x, const int* sorted_route, const int* tota
                          int top_k, int H, void* xp, void* stream_) {
   US_REQUIRE(x && sorted_route && total && xp && R >= 0 && (H % 8) == 0 && top_k >= 1);
   if (R == 0) return US_OK;
-  moe_gather_kernel<<<R, 256, 0, (cudaStream_t)stream_>>>(
-      (const __nv_bfloat16*)x, sorted_route, total, top_k, H, (__nv_bfloat16*)xp);
+  us::launch_pdl(moe_gather_kernel, dim3(R), dim3(256), 0, (cudaStream_t)stream_, (const __nv_bfloat16*)x, sorted_route, total, top_k, H, (__nv_bfloat16*)xp);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -273,8 +275,7 @@ US_API int us_moe_unpermute(const void* y, const int* perm_of_route, const float
                             int top_k, int H, void* out, void* stream_) {
   US_REQUIRE(y && perm_of_route && weights && out && T >= 0 && (H % 8) == 0);
   if (T == 0) return US_OK;
-  moe_unpermute_kernel<<<T, 256, 0, (cudaStream_t)stream_>>>(
-      (const __nv_bfloat16*)y, perm_of_route, weights, top_k, H, (__nv_bfloat16*)out);
+  us::launch_pdl(moe_unpermute_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream_, (const __nv_bfloat16*)y, perm_of_route, weights, top_k, H, (__nv_bfloat16*)out);
   US_LAUNCH_CHECK();
   return US_OK;
 }

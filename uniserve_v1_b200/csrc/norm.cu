@@ -18,6 +18,7 @@ constexpr int kThreads = 256;
 __global__ void __launch_bounds__(kThreads)
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                __nv_bfloat16* __restrict__ y, int H, long long ldx, long long ldy, float eps) {
+  US_PDL_PROLOGUE();
   __shared__ float scratch[33];
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * ldx;
@@ -49,6 +50,7 @@ __global__ void __launch_bounds__(kThreads)
 add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ residual,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int H,
                    float eps, int first) {
+  US_PDL_PROLOGUE();
   __shared__ float scratch[33];
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * H;
@@ -102,6 +104,7 @@ modulated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
                          const float* __restrict__ table, const int* __restrict__ idx,
                          int vectors_per_row, int shift_slot, int scale_slot,
                          __nv_bfloat16* __restrict__ y, int H, float eps) {
+  US_PDL_PROLOGUE();
   __shared__ float scratch[33];
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * H;
@@ -140,6 +143,7 @@ __global__ void __launch_bounds__(kThreads)
 gated_residual_kernel(__nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ u,
                       const float* __restrict__ table, const int* __restrict__ idx,
                       int vectors_per_row, int gate_slot, int H) {
+  US_PDL_PROLOGUE();
   const long long row = blockIdx.x;
   __nv_bfloat16* hr = h + row * H;
   const __nv_bfloat16* ur = u + row * H;
@@ -160,6 +164,7 @@ __global__ void __launch_bounds__(kThreads)
 layer_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                   const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, int H,
                   float eps) {
+  US_PDL_PROLOGUE();
   __shared__ float scratch[33];
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * H;
@@ -187,8 +192,7 @@ US_API int us_rmsnorm(const void* x, const void* w, void* y, int T, int H, long 
                       long long ldy, float eps, void* stream) {
   US_REQUIRE(x && w && y && T >= 0 && H > 0 && (H % 8) == 0 && (ldx % 8) == 0 && (ldy % 8) == 0);
   if (T == 0) return US_OK;
-  rmsnorm_kernel<<<T, kThreads, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
+  us::launch_pdl(rmsnorm_kernel, dim3(T), dim3(kThreads), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -197,8 +201,7 @@ US_API int us_add_rmsnorm(const void* x, void* residual, const void* w, void* y,
                           float eps, int first, void* stream) {
   US_REQUIRE(x && residual && w && y && T >= 0 && H > 0 && (H % 8) == 0);
   if (T == 0) return US_OK;
-  add_rmsnorm_kernel<<<T, kThreads, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (float*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps,
+  us::launch_pdl(add_rmsnorm_kernel, dim3(T), dim3(kThreads), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, (float*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps,
       first);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -209,8 +212,7 @@ US_API int us_modulated_rmsnorm(const void* x, const void* w, const float* table
                                 int H, float eps, void* stream) {
   US_REQUIRE(x && table && idx && y && T >= 0 && H > 0 && (H % 8) == 0);
   if (T == 0) return US_OK;
-  modulated_rmsnorm_kernel<<<T, kThreads, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, table, idx, vectors_per_row, shift_slot,
+  us::launch_pdl(modulated_rmsnorm_kernel, dim3(T), dim3(kThreads), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, table, idx, vectors_per_row, shift_slot,
       scale_slot, (__nv_bfloat16*)y, H, eps);
   US_LAUNCH_CHECK();
   return US_OK;
@@ -220,8 +222,7 @@ US_API int us_gated_residual(void* h, const void* u, const float* table, const i
                              int vectors_per_row, int gate_slot, int T, int H, void* stream) {
   US_REQUIRE(h && u && table && idx && T >= 0 && H > 0 && (H % 8) == 0);
   if (T == 0) return US_OK;
-  gated_residual_kernel<<<T, kThreads, 0, (cudaStream_t)stream>>>(
-      (__nv_bfloat16*)h, (const __nv_bfloat16*)u, table, idx, vectors_per_row, gate_slot, H);
+  us::launch_pdl(gated_residual_kernel, dim3(T), dim3(kThreads), 0, (cudaStream_t)stream, (__nv_bfloat16*)h, (const __nv_bfloat16*)u, table, idx, vectors_per_row, gate_slot, H);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -230,8 +231,7 @@ US_API int us_layer_norm(const void* x, const void* w, const void* b, void* y, i
                          float eps, void* stream) {
   US_REQUIRE(x && y && T >= 0 && H > 0);
   if (T == 0) return US_OK;
-  layer_norm_kernel<<<T, kThreads, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y,
+  us::launch_pdl(layer_norm_kernel, dim3(T), dim3(kThreads), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y,
       H, eps);
   US_LAUNCH_CHECK();
   return US_OK;

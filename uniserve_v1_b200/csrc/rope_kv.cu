@@ -33,6 +33,7 @@ struct RopeArgs {
 };
 
 __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope_kv_kernel(const RopeArgs a) {
+  US_PDL_PROLOGUE();
   __shared__ float rows[kWarps][kMaxD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = a.Hq + 2 * a.Hkv;
@@ -117,6 +118,7 @@ struct Rope3Args {
 // Channel layout of the rotated part: axis a in {0,1,2} owns channels
 // [a * 2F, (a + 1) * 2F) as F half-split pairs (i, i + F).
 __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope3_kernel(const Rope3Args a) {
+  US_PDL_PROLOGUE();
   __shared__ float rows[kWarps][kMaxD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = a.Hq + a.Hk;
@@ -182,7 +184,7 @@ US_API int us_qk_norm_rope_kv(void* qkv, const void* qw, const void* kw, const i
   a.eps = eps;
   const long long units = (long long)T * (Hq + 2 * Hkv);
   const int blocks = (int)((units + kWarps - 1) / kWarps);
-  qk_norm_rope_kv_kernel<<<blocks, kWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  us::launch_pdl(qk_norm_rope_kv_kernel, dim3(blocks), dim3(kWarps * 32), 0, (cudaStream_t)stream, a);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -202,7 +204,7 @@ US_API int us_qk_norm_rope3(void* q, void* k, const void* qw, const void* kw, co
   a.ldq = ldq; a.ldk = ldk; a.eps = eps;
   const long long units = (long long)T * (Hq + Hk);
   const int blocks = (int)((units + kWarps - 1) / kWarps);
-  qk_norm_rope3_kernel<<<blocks, kWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  us::launch_pdl(qk_norm_rope3_kernel, dim3(blocks), dim3(kWarps * 32), 0, (cudaStream_t)stream, a);
   US_LAUNCH_CHECK();
   return US_OK;
 }

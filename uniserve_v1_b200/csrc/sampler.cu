@@ -33,6 +33,7 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 
 __global__ void __launch_bounds__(kThreads)
 argmax_kernel(const float* __restrict__ logits, int V, long long ld, int* __restrict__ out) {
+  US_PDL_PROLOGUE();
   __shared__ float sv[32];
   __shared__ int si[32];
   const float* row = logits + (long long)blockIdx.x * ld;
@@ -85,6 +86,7 @@ logits_shape_kernel(float* __restrict__ logits, int V, long long ld,
                     const unsigned char* __restrict__ prompt_mask, // [B, V] or null
                     const float* __restrict__ rep, const float* __restrict__ freq,
                     const float* __restrict__ pres, const float* __restrict__ temp) {
+  US_PDL_PROLOGUE();
   const int b = blockIdx.y;
   float* row = logits + (long long)b * ld;
   const float r = rep ? rep[b] : 1.f;
@@ -111,6 +113,7 @@ __global__ void logits_bias_kernel(float* __restrict__ logits, long long ld,
                                    const int* __restrict__ bias_offsets,
                                    const int* __restrict__ bias_ids,
                                    const float* __restrict__ bias_vals, int V) {
+  US_PDL_PROLOGUE();
   const int b = blockIdx.x;
   for (int j = bias_offsets[b] + threadIdx.x; j < bias_offsets[b + 1]; j += blockDim.x) {
     const int id = bias_ids[j];
@@ -198,6 +201,7 @@ __device__ uint32_t radix_select_mass(const float* row, int V, float mx,
 }
 
 __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleArgs a) {
+  US_PDL_PROLOGUE();
   __shared__ float fscratch[33];
   __shared__ unsigned int hist32[256];
   __shared__ unsigned long long hist64[256];
@@ -301,6 +305,7 @@ __global__ void __launch_bounds__(kThreads)
 logprob_stats_kernel(const float* __restrict__ logits, long long ld, int V,
                      const int* __restrict__ chosen, float* __restrict__ lse_out,
                      float* __restrict__ logprob_out, int* __restrict__ rank_out) {
+  US_PDL_PROLOGUE();
   __shared__ float fscratch[33];
   const int b = blockIdx.x;
   const float* row = logits + (long long)b * ld;
@@ -331,7 +336,7 @@ logprob_stats_kernel(const float* __restrict__ logits, long long ld, int V,
 US_API int us_argmax(const float* logits, int B, int V, long long ld, int* out, void* stream) {
   US_REQUIRE(logits && out && B >= 0 && V >= 1);
   if (B == 0) return US_OK;
-  argmax_kernel<<<B, kThreads, 0, (cudaStream_t)stream>>>(logits, V, ld, out);
+  us::launch_pdl(argmax_kernel, dim3(B), dim3(kThreads), 0, (cudaStream_t)stream, logits, V, ld, out);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -348,11 +353,11 @@ US_API int us_logits_shape(float* logits, int B, int V, long long ld,
   if (bias_offsets) {
     // Bias comes after bans and before penalties; bans stay -inf under an add,
     // so applying the sparse bias first keeps the documented order.
-    logits_bias_kernel<<<B, 128, 0, stream>>>(logits, ld, bias_offsets, bias_ids, bias_vals, V);
+    us::launch_pdl(logits_bias_kernel, dim3(B), dim3(128), 0, stream, logits, ld, bias_offsets, bias_ids, bias_vals, V);
     US_LAUNCH_CHECK();
   }
   dim3 grid((V + 256 * 8 - 1) / (256 * 8), B);
-  logits_shape_kernel<<<grid, 256, 0, stream>>>(logits, V, ld, ban_mask, bias_offsets, bias_ids,
+  us::launch_pdl(logits_shape_kernel, dim3(grid), dim3(256), 0, stream, logits, V, ld, ban_mask, bias_offsets, bias_ids,
                                                 bias_vals, out_counts, prompt_mask, rep, freq,
                                                 pres, temp);
   US_LAUNCH_CHECK();
@@ -368,7 +373,7 @@ US_API int us_sample_from_logits(const float* logits, int B, int V, long long ld
   SampleArgs a;
   a.logits = logits; a.ld = ld; a.V = V; a.top_k = top_k; a.top_p = top_p; a.min_p = min_p;
   a.seeds = seeds; a.positions = positions; a.out = out;
-  sample_kernel<<<B, kThreads, 0, (cudaStream_t)stream>>>(a);
+  us::launch_pdl(sample_kernel, dim3(B), dim3(kThreads), 0, (cudaStream_t)stream, a);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -377,7 +382,7 @@ US_API int us_logprob_stats(const float* logits, int B, int V, long long ld, con
                             float* lse, float* logprob, int* rank, void* stream) {
   US_REQUIRE(logits && B >= 0 && V >= 1);
   if (B == 0) return US_OK;
-  logprob_stats_kernel<<<B, kThreads, 0, (cudaStream_t)stream>>>(logits, ld, V, chosen, lse,
+  us::launch_pdl(logprob_stats_kernel, dim3(B), dim3(kThreads), 0, (cudaStream_t)stream, logits, ld, V, chosen, lse,
                                                                  logprob, rank);
   US_LAUNCH_CHECK();
   return US_OK;
