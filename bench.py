@@ -105,8 +105,165 @@ def reference_arm(args) -> int:
     return 0
 
 
+BASELINE_CLIP_S = 8.194         # reference: FastH3 8-step, Ulysses8, bf16, 5 s clip on 8xH200 (docs/minimax_h3/evaluation.md:169)
+
+
+def fasth3_main(args) -> int:
+    """FastH3 8-step clip latency.  A *step* is one denoising step (one transformer
+    evaluation over the packed rows of the clip on every rank of the Ulysses
+    group, the velocity all-gather and the Euler update); ``value`` is the
+    device time of the 8 steps of one clip.  ``e2e`` is one whole request through
+    ``VideoService.generate``: prompt features copied from pinned host memory,
+    latent preparation, 8 steps, video and audio VAE decode (temporal units dealt
+    over the ranks), colour conversion, read-back of the planes and MP4 mux."""
+    import torch
+    import torch.distributed as dist
+    from uniserve_v1_b200.models.h3_vae import (AudioVaeConfig, AudioVaeDecoder, VideoVaeConfig,
+                                                VideoVaeDecoder)
+    from uniserve_v1_b200.models.minimax_h3 import Denoiser, H3Config, H3Transformer
+    from uniserve_v1_b200.ops import native
+    from uniserve_v1_b200.parallel.context import ParallelContext
+    from uniserve_v1_b200.server.video_rules import VideoPlan
+    from uniserve_v1_b200.server.video_service import VideoJob, VideoService
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    tiny = args.model == "tiny"
+    cfg = H3Config.tiny() if tiny else H3Config()
+    if tiny:
+        cfg.num_heads = 8
+        cfg.hidden_size = 1024
+    if args.layers:
+        cfg.num_layers = args.layers
+    frames = args.frames or (22 if tiny else 124)
+    width, height = (256, 256) if tiny else (1344, 768)
+    n_text = args.prompt_len or (64 if tiny else 1000)
+    ctx = ParallelContext.single()
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        ctx = ParallelContext.from_world(ulysses=world)
+    t0 = time.time()
+    model = H3Transformer(cfg, dev, torch.bfloat16, ctx).init_random(seed=0)
+    vcfg = VideoVaeConfig.tiny() if tiny else VideoVaeConfig()
+    if tiny:
+        vcfg.latent_channels, vcfg.spatial = cfg.latent_channels, cfg.vae_spatial
+    acfg = AudioVaeConfig.tiny() if tiny else AudioVaeConfig()
+    if tiny:
+        acfg.latent_channels = cfg.audio_channels
+    video_vae = VideoVaeDecoder(vcfg, dev).init_random(seed=1)
+    audio_vae = AudioVaeDecoder(acfg, dev).init_random(seed=2)
+    svc = VideoService(model, video_vae, audio_vae)
+    svc.text.max_tokens = n_text
+    den = svc.denoiser
+    lf, lh, lw = cfg.latent_shape(frames, width, height)
+    n_audio = cfg.audio_rows(frames)
+    g = torch.Generator().manual_seed(7)
+    feats = torch.randn(n_text, cfg.text_dim, generator=g).pin_memory().to(dev)
+    st = den.prepare(1000, lf, lh, lw, n_audio, feats)
+    fused = world > 1 and os.environ.get("US_NO_FUSED", "0") != "1"
+    if fused:
+        from uniserve_v1_b200.parallel.ulysses import FusedUlysses
+        model.ulysses = FusedUlysses(ctx, dev, st.layout.rows, model.heads_local, cfg.head_dim)
+    torch.cuda.synchronize()
+    setup_s = time.time() - t0
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    K, W = args.steps, args.warmup
+    nsteps = den.steps
+    for i in range(W):
+        st.step = i % nsteps
+        den.step(st)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    launches0 = native.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(K):
+        st.step = i % nsteps
+        den.step(st)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = max_over_ranks(ev0.elapsed_time(ev1))
+    native.raise_on_device_error()
+    launches = native.launch_count - launches0
+    value = ms / K * nsteps / 1e3
+
+    e2e = None
+    if not args.no_e2e:
+        plan = VideoPlan("t2va", width, height, frames, 24, 1000, nsteps)
+        prompt = "".join(chr(97 + (i * 7) % 26) for i in range(n_text))
+        job = VideoJob(prompt, plan)
+        h0, d0 = svc.h2d_bytes, svc.d2h_bytes
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_host = time.time()
+        ev0.record()
+        mp4 = svc.generate(job)
+        ev1.record()
+        barrier()
+        e2e_ms = max_over_ranks(ev0.elapsed_time(ev1))
+        e2e = {"value": e2e_ms / 1e3, "unit": "s", "host_wall_s": round(time.time() - t_host, 3),
+               "h2d_bytes_per_step": svc.h2d_bytes - h0, "d2h_bytes_per_step": svc.d2h_bytes - d0,
+               "mp4_bytes": len(mp4),
+               "includes": "prompt features H2D from pinned memory, latent prepare, 8 steps, "
+                           "video+audio VAE decode, colour conversion, plane read-back, MP4 mux"}
+    if rank == 0:
+        line = {
+            "metric": "FastH3 8-step clip latency", "value": value, "unit": "s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+            "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": value / BASELINE_CLIP_S, "dtype": "bf16",
+            "data": "synthetic (Philox N(0,1) latents, N(0,1) text features, random-init N(0,0.02) weights)",
+            "config": {"model": "MiniMax-H3/FastH3-shaped DiT" if not tiny else "tiny",
+                       "layers": cfg.num_layers, "hidden": cfg.hidden_size,
+                       "heads": cfg.num_heads, "ffn": cfg.ffn_size, "frames": frames,
+                       "size": f"{width}x{height}", "latent": [lf, lh, lw],
+                       "rows": st.layout.rows, "rows_used": st.layout.used,
+                       "global_batch": 1, "seq_len": st.layout.used, "text_tokens": n_text,
+                       "step": "one denoising step of the clip",
+                       "parallelism": "single GPU" if world == 1 else
+                       f"ulysses{world} ({'all-to-all fused into the projection GEMMs' if fused else 'NCCL all_to_all'})",
+                       "l2": "inputs larger than L2 (weights read per step >> 126 MB)",
+                       "baseline": "8.194 s on 8xH200 (reference docs, whole request)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "launches_per_step": launches // max(K, 1), "setup_s": round(setup_s, 1),
+        }
+        if args.layers:
+            line["profile_only"] = True
+        print(json.dumps(line))
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="qwen3-moe", choices=["qwen3-moe", "fasth3"],
+                    help="qwen3-moe: decode tokens/s (the default); fasth3: 8-step clip latency "
+                         "of the video transformer under Ulysses sequence parallelism")
+    ap.add_argument("--frames", type=int, default=0, help="fasth3: frame count (rule 17n + 5)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
@@ -130,6 +287,10 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
+    if args.workload == "fasth3":
+        if "--steps" not in sys.argv:
+            args.steps = 8
+        return fasth3_main(args)
 
     import torch
     import torch.distributed as dist

@@ -181,3 +181,18 @@ def test_safetensors_roundtrip_and_model_load(tmp_path):
     assert torch.equal(loaded.layers[1].w13, ref.layers[1].w13)
     assert torch.equal(loaded.layers[0].qkv, ref.layers[0].qkv)
     assert parse_model_id("Qwen/Qwen3-30B-A3B@abc/sub/dir") == ("Qwen/Qwen3-30B-A3B", "abc", "sub/dir")
+
+
+def test_fp8_block_weight_roundtrip_and_cpu_linear():
+    import torch
+    from uniserve_v1_b200.ops import fp8 as Q
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(2, 256, 384, generator=g) * 0.1
+    q, s = Q.quantize_weight_block128(w)
+    assert q.dtype == torch.uint8 and s.shape == (2, 2, 3)
+    back = Q.dequantize_weight_block128(q, s)
+    assert (back - w).abs().max() <= 0.07 * w.abs().max()
+    x = torch.randn(5, 384, generator=g).to(torch.bfloat16)
+    y = Q.linear_fp8_block(x, q[0], s[0])
+    ref = x.float() @ w[0].t()
+    assert ((y.float() - ref).norm() / ref.norm()) < 0.08

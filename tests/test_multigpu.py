@@ -262,3 +262,81 @@ def test_expert_exchange_dispatch_combine(afd):
         assert p.exitcode == 0
     for rank, ok, status in res:
         assert ok and status == 0, res
+
+
+def _tp_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from uniserve_v1_b200.ops import native as N
+    from uniserve_v1_b200.parallel import tp_fused as TP
+    rows, H, I, eps = 384, 512, 1024, 1e-6
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(rows, H, generator=g)
+    w13 = torch.randn(2 * I, H, generator=g) * 0.05
+    w2 = torch.randn(H, I, generator=g) * 0.05
+    nw = 1.0 + 0.1 * torch.randn(H, generator=g)
+    bf = lambda t: t.to(dev).to(torch.bfloat16)
+    tp = TP.FusedTP(dist.group.WORLD, rank, world, dev, rows, H)
+    ro, Il = rows // world, I // world
+    lo = rank * ro
+    # own rows: residual x, normalised rows into the heap
+    res = x[lo:lo + ro].to(dev).clone()
+    xn = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * nw
+    tp.norm_rows(TP.SITE_NORM_A).copy_(bf(xn[lo:lo + ro]))
+    # weight shards: value rows then gate rows of this rank's slice of I
+    w13_l = bf(torch.cat([w13[rank * Il:(rank + 1) * Il], w13[I + rank * Il:I + (rank + 1) * Il]]))
+    w2_l = bf(w2[:, rank * Il:(rank + 1) * Il]).contiguous()
+    outs = []
+    for it in range(2):     # twice: the barriers' epochs advance
+        r = res.clone()
+        y = tp.mlp(r, TP.SITE_NORM_A, w13_l, w2_l, bf(nw), TP.SITE_NORM_B, eps)
+        torch.cuda.synchronize()
+        outs.append((r.cpu(), y.float().cpu()))
+    status = N.read_status()
+    gathered = [None] * world
+    dist.all_gather_object(gathered, outs[-1])
+    same = torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    if rank == 0:
+        q.put({"status": status, "parts": gathered, "same": same})
+    dist.barrier()
+    tp.close()
+    dist.destroy_process_group()
+
+
+def test_tp_gather_gemm_and_reduce_scatter_gemm_match_reference():
+    """Column-parallel GEMM reading the peers' rows + row-parallel GEMM pushing
+    partial rows to their owners + slot reduction fused with residual/RMSNorm,
+    against the unsharded FP32 computation."""
+    _need(2)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=600)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert res["status"] == (0, 0)
+    assert res["same"]
+    rows, H, I, eps = 384, 512, 1024, 1e-6
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(rows, H, generator=g)
+    w13 = torch.randn(2 * I, H, generator=g) * 0.05
+    w2 = torch.randn(H, I, generator=g) * 0.05
+    nw = 1.0 + 0.1 * torch.randn(H, generator=g)
+    r16 = lambda t: t.to(torch.bfloat16).float()
+    xn = r16(x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * nw)
+    up, gate = xn @ r16(w13[:I]).t(), xn @ r16(w13[I:]).t()
+    hid = r16(up * torch.nn.functional.silu(gate))
+    want_res = x + hid @ r16(w2).t()
+    want_y = want_res / torch.sqrt((want_res * want_res).mean(-1, keepdim=True) + eps) * r16(nw)
+    got_res = torch.cat([p[0] for p in res["parts"]], 0)
+    got_y = torch.cat([p[1] for p in res["parts"]], 0)
+    torch.testing.assert_close(got_res, want_res, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(got_y, want_y, atol=3e-2, rtol=3e-2)

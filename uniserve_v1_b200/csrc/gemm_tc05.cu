@@ -17,125 +17,9 @@
 #include "include/us_common.cuh"
 #include "include/us_tc05.cuh"
 #include "include/us_tmap.h"
+#include "include/us_gemm_args.cuh"
 
 namespace {
-
-struct GemmArgs {
-  int M;            // output features per group
-  int K;
-  int rows;         // activation rows (dense)
-  int dual_offset;  // row offset of the second weight tile (dual epilogue)
-  int stages;
-  int act;          // dual: 0 = silu fused rounding, 1 = silu stepwise rounding, 2 = gelu-tanh
-  int out_dtype;    // 0 = bf16, 1 = fp32
-  int bias_dtype;   // 0 = bf16, 1 = fp32
-  long long ldo;
-  void* out;
-  const void* bias;        // [G, M] or null
-  const float* row_scale;  // [rows] or null
-  const int* out_row_map;  // [rows] destination row, <0 skips; null = identity
-  const int* tile_group;   // grouped: group of each row tile
-  const int* tile_row0;    // grouped: first activation row of each tile
-  const int* tile_rows;    // grouped: valid rows of each tile
-  const int* num_tiles;    // grouped: device word, number of row tiles
-  unsigned int* status;
-  // split-K (dense, single accumulator): the `splits` CTAs along z form one
-  // thread-block cluster; CTA z owns k-blocks [z * kb_per_split, ...).
-  int splits;
-  int kb_per_split;
-  // Peer modes (sequence parallelism).  Pull: the activation's K extent is the
-  // concatenation of `k_per_peer`-wide slices that live in different ranks'
-  // memory, one tensor map per rank.  Scatter: output feature m belongs to rank
-  // m / peer_cols and is stored into that rank's buffer at row
-  // peer_row_offset + row, column m % peer_cols.
-  int k_per_peer;
-  int peer_cols;
-  int peer_row_offset;
-  void* peer_out[8];
-  // Route push (expert-parallel combine): permuted row r carries route
-  // i = route_map[r] = (source rank * route_per + token * top_k + slot); the epilogue
-  // multiplies by the gate weight route_w[i] and stores the row into the source
-  // rank's combine buffer at row i % route_per.
-  const int* route_map;
-  const float* route_w;
-  int route_per;
-};
-
-struct BMaps {
-  CUtensorMap m[8];
-};
-
-constexpr int kBlockM = 128;
-constexpr int kBlockK = 64;
-constexpr int kATile = kBlockM * kBlockK * 2;  // 16 KiB
-
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
-__device__ __forceinline__ float gelu_tanh_f(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
-}
-
-template <int BN>
-constexpr int tmem_cols(bool dual) {
-  int need = dual ? 2 * BN : BN;
-  int c = 32;
-  while (c < need) c <<= 1;
-  return c;
-}
-
-// Per-thread epilogue of one output feature `m`: activation, bias, row scale,
-// row map, rounding.
-template <bool DUAL>
-struct Epilogue {
-  const GemmArgs& a;
-  const int m, row0;
-  const bool m_ok;
-  float bias;
-  __device__ __forceinline__ Epilogue(const GemmArgs& args, int group, int m_, int row0_)
-      : a(args), m(m_), row0(row0_), m_ok(m_ < args.M), bias(0.f) {
-    if (a.bias != nullptr && m_ok) {
-      const size_t bi = (size_t)group * a.M + m;
-      bias = a.bias_dtype == 0 ? us::bf2f(((const __nv_bfloat16*)a.bias)[bi])
-                               : ((const float*)a.bias)[bi];
-    }
-  }
-  __device__ __forceinline__ void store(int r, float val, float gate) const {
-    if (!m_ok) return;
-    if (DUAL) {
-      if (a.act == 0) {
-        val = val * silu_f(gate);
-      } else if (a.act == 1) {
-        const float sg = us::bf2f(us::f2bf(silu_f(us::bf2f(us::f2bf(gate)))));
-        val = us::bf2f(us::f2bf(val)) * sg;
-      } else {
-        val = val * gelu_tanh_f(gate);
-      }
-    }
-    val += bias;
-    int orow = row0 + r;
-    if (a.route_map != nullptr) {
-      const int i = a.route_map[orow];
-      const int src = i / a.route_per;
-      const int dst = i - src * a.route_per;
-      ((__nv_bfloat16*)a.peer_out[src])[(size_t)dst * a.ldo + m] = us::f2bf(val * a.route_w[i]);
-      return;
-    }
-    if (a.row_scale != nullptr) val *= a.row_scale[orow];
-    if (a.out_row_map != nullptr) orow = a.out_row_map[orow];
-    if (orow < 0) return;
-    if (a.peer_cols > 0) {
-      const int p = m / a.peer_cols;
-      const size_t o = (size_t)(a.peer_row_offset + orow) * a.ldo + (m - p * a.peer_cols);
-      ((__nv_bfloat16*)a.peer_out[p])[o] = us::f2bf(val);
-      return;
-    }
-    const size_t o = (size_t)orow * a.ldo + m;
-    if (a.out_dtype == 0)
-      ((__nv_bfloat16*)a.out)[o] = us::f2bf(val);
-    else
-      ((float*)a.out)[o] = val;
-  }
-};
 
 template <int BN, bool DUAL>
 __global__ void __launch_bounds__(192)
@@ -210,9 +94,15 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (DUAL)
           tc::tma_load_3d(st + kATile, &tmA, &full_bar[s], kx,
                           args.dual_offset + m_tile * kBlockM, group);
-        const int src = args.k_per_peer > 0 ? kx / args.k_per_peer : 0;
-        tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], &full_bar[s],
-                        kx - src * args.k_per_peer, row0);
+        if (args.rows_per_peer > 0) {
+          const int src = row0 / args.rows_per_peer;
+          tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], &full_bar[s], kx,
+                          row0 - src * args.rows_per_peer);
+        } else {
+          const int src = args.k_per_peer > 0 ? kx / args.k_per_peer : 0;
+          tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], &full_bar[s],
+                          kx - src * args.k_per_peer, row0);
+        }
       }
     }
   } else if (warp == 1) {
@@ -378,6 +268,9 @@ struct PeerSpec {
   const float* route_w = nullptr;
   int route_per = 0;
   int n_out_peers = 0;
+  int rows_per_peer = 0;                 // gather: rows of the activation per rank
+  int peer_rows = 0;                     // reduce-scatter: rows owned per rank
+  int peer_slot = 0;
 };
 
 int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M, int K, int x_rows,
@@ -399,7 +292,17 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
                       (uint64_t)ldw, (uint64_t)w_rows * (uint64_t)ldw, kBlockM, kBlockK,
                       US_SWZ_128);
   if (rc) return rc;
-  if (ps.x_peers) {
+  if (ps.x_peers && ps.rows_per_peer > 0) {
+    US_REQUIRE(ps.n_peers >= 1 && ps.n_peers <= 8 && (ps.rows_per_peer % block_n) == 0 &&
+               ps.rows_per_peer * ps.n_peers >= x_rows && num_tiles == nullptr);
+    for (int p = 0; p < ps.n_peers; ++p) {
+      US_REQUIRE(ps.x_peers[p] && ((uintptr_t)ps.x_peers[p] % 16) == 0);
+      rc = us_tmap_2d(&tmB.m[p], ps.x_peers[p], US_TMAP_BF16, (uint64_t)ps.rows_per_peer,
+                      (uint64_t)K, (uint64_t)ldx, (uint32_t)block_n, kBlockK, US_SWZ_128);
+      if (rc) return rc;
+    }
+    for (int p = ps.n_peers; p < 8; ++p) tmB.m[p] = tmB.m[0];
+  } else if (ps.x_peers) {
     US_REQUIRE(ps.n_peers >= 1 && ps.n_peers <= 8 && ps.k_per_peer > 0 &&
                (ps.k_per_peer % kBlockK) == 0 && ps.k_per_peer * ps.n_peers == K);
     for (int p = 0; p < ps.n_peers; ++p) {
@@ -438,7 +341,10 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
   a.status = us_status_ptr();
   a.splits = 1;
   a.kb_per_split = 0;
-  a.k_per_peer = ps.x_peers ? ps.k_per_peer : 0;
+  a.k_per_peer = (ps.x_peers && ps.rows_per_peer == 0) ? ps.k_per_peer : 0;
+  a.rows_per_peer = ps.x_peers ? ps.rows_per_peer : 0;
+  a.peer_rows = 0;
+  a.peer_slot = 0;
   a.peer_cols = 0;
   a.peer_row_offset = 0;
   for (int p = 0; p < 8; ++p) a.peer_out[p] = nullptr;
@@ -451,6 +357,16 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
     a.route_map = ps.route_map;
     a.route_w = ps.route_w;
     a.route_per = ps.route_per;
+    for (int p = 0; p < ps.n_out_peers; ++p) {
+      US_REQUIRE(ps.out_peers[p] != nullptr);
+      a.peer_out[p] = ps.out_peers[p];
+    }
+  } else if (ps.out_peers && ps.peer_rows > 0) {
+    US_REQUIRE(ps.n_out_peers >= 1 && ps.n_out_peers <= 8 && ps.peer_slot >= 0 &&
+               ps.peer_slot < ps.n_out_peers && ps.peer_rows * ps.n_out_peers >= x_rows &&
+               num_tiles == nullptr);
+    a.peer_rows = ps.peer_rows;
+    a.peer_slot = ps.peer_slot;
     for (int p = 0; p < ps.n_out_peers; ++p) {
       US_REQUIRE(ps.out_peers[p] != nullptr);
       a.peer_out[p] = ps.out_peers[p];
@@ -552,4 +468,40 @@ US_API int us_gemm_wx_route_push(const void* W, const void* X, int G, int M, int
   return gemm_impl(W, X, nullptr, G, M, M, K, x_rows, ldw, ldx, ldo, 0, 0, 0, 0, nullptr, 0,
                    nullptr, nullptr, tile_group, tile_row0, tile_rows, num_tiles, max_tiles,
                    block_n, ps, (cudaStream_t)stream_);
+}
+
+// Column-parallel linear with the all-gather fused into its operand loads: the
+// activation's rows [p * rows_per_peer, ...) are read by TMA (no cluster multicast)
+// from rank p's [rows_per_peer, K] buffer; W is this rank's [w_rows, K] weight shard.
+// `dual` selects the gated form (value rows [0, M), gate rows [dual_offset, dual_offset + M)).
+US_API int us_gemm_wx_gather(const void* W, const void* const* x_peers, int n_peers,
+                             int rows_per_peer, void* out, int w_rows, int M, int K, int x_rows,
+                             long long ldw, long long ldx, long long ldo, int dual,
+                             int dual_offset, int act, int out_dtype, int block_n,
+                             void* stream_) {
+  PeerSpec ps;
+  ps.x_peers = x_peers;
+  ps.n_peers = n_peers;
+  ps.rows_per_peer = rows_per_peer;
+  return gemm_impl(W, nullptr, out, 1, w_rows, M, K, x_rows, ldw, ldx, ldo, dual, dual_offset,
+                   act, out_dtype, nullptr, 0, nullptr, nullptr, nullptr, nullptr, nullptr,
+                   nullptr, 0, block_n, ps, (cudaStream_t)stream_);
+}
+
+// Row-parallel linear with the reduce-scatter fused into its epilogue: row r of
+// this rank's partial product is stored into slot `slot` of the buffer of the
+// rank that owns the row (`out_peers[r / peer_rows]`, laid out
+// [n_peers, peer_rows, ldo], bf16 or fp32 by out_dtype).
+US_API int us_gemm_wx_reduce_scatter(const void* W, const void* X, int M, int K, int x_rows,
+                                     long long ldw, long long ldx, long long ldo,
+                                     void* const* out_peers, int n_peers, int peer_rows, int slot,
+                                     int out_dtype, int block_n, void* stream_) {
+  PeerSpec ps;
+  ps.out_peers = out_peers;
+  ps.n_out_peers = n_peers;
+  ps.peer_rows = peer_rows;
+  ps.peer_slot = slot;
+  return gemm_impl(W, X, nullptr, 1, M, M, K, x_rows, ldw, ldx, ldo, 0, 0, 0, out_dtype, nullptr,
+                   0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, block_n, ps,
+                   (cudaStream_t)stream_);
 }

@@ -186,6 +186,58 @@ layer_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   }
 }
 
+// Second half of a fused reduce-scatter: `slots` holds one partial product per
+// rank for this rank's own rows ([n_slots, T, H] bf16).  r += sum of the slots
+// (FP32, fixed order), y = rmsnorm(r) * w, both for the own rows only; the
+// normalised rows are then read by the peers' gather GEMMs.
+__global__ void __launch_bounds__(kThreads)
+reduce_slots_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots,
+                                float* __restrict__ residual, const __nv_bfloat16* __restrict__ w,
+                                __nv_bfloat16* __restrict__ y, int T, int H, long long ldy,
+                                float eps, int first) {
+  US_PDL_PROLOGUE();
+  __shared__ float scratch[33];
+  const long long row = blockIdx.x;
+  float* rr = residual + row * H;
+  __nv_bfloat16* yr = y + row * ldy;
+  const int nvec = H >> 3;
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    float acc[8];
+    if (first) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    } else {
+      const float4 r0 = *reinterpret_cast<const float4*>(rr + v * 8);
+      const float4 r1 = *reinterpret_cast<const float4*>(rr + v * 8 + 4);
+      acc[0] = r0.x; acc[1] = r0.y; acc[2] = r0.z; acc[3] = r0.w;
+      acc[4] = r1.x; acc[5] = r1.y; acc[6] = r1.z; acc[7] = r1.w;
+    }
+    for (int s = 0; s < n_slots; ++s) {
+      us::Pack16 p;
+      p.u = *reinterpret_cast<const uint4*>(slots + ((long long)s * T + row) * H + v * 8);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += us::bf2f(p.b[i]);
+    }
+    *reinterpret_cast<float4*>(rr + v * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(rr + v * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += acc[i] * acc[i];
+  }
+  ss = us::block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    const float4 r0 = *reinterpret_cast<const float4*>(rr + v * 8);
+    const float4 r1 = *reinterpret_cast<const float4*>(rr + v * 8 + 4);
+    const float r[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    us::Pack16 q, o;
+    q.u = *reinterpret_cast<const uint4*>(w + v * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.b[i] = us::f2bf(r[i] * inv * us::bf2f(q.b[i]));
+    *reinterpret_cast<uint4*>(yr + v * 8) = o.u;
+  }
+}
+
 }  // namespace
 
 US_API int us_rmsnorm(const void* x, const void* w, void* y, int T, int H, long long ldx,
@@ -233,6 +285,19 @@ US_API int us_layer_norm(const void* x, const void* w, const void* b, void* y, i
   if (T == 0) return US_OK;
   us::launch_pdl(layer_norm_kernel, dim3(T), dim3(kThreads), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b, (__nv_bfloat16*)y,
       H, eps);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}
+
+US_API int us_reduce_slots_add_rmsnorm(const void* slots, int n_slots, void* residual,
+                                       const void* w, void* y, int T, int H, long long ldy,
+                                       float eps, int first, void* stream) {
+  US_REQUIRE(slots && residual && w && y && n_slots >= 1 && T >= 0 && H > 0 && (H % 8) == 0 &&
+             (ldy % 8) == 0);
+  if (T == 0) return US_OK;
+  us::launch_pdl(reduce_slots_add_rmsnorm_kernel, dim3(T), dim3(kThreads), 0,
+                 (cudaStream_t)stream, (const __nv_bfloat16*)slots, n_slots, (float*)residual,
+                 (const __nv_bfloat16*)w, (__nv_bfloat16*)y, T, H, ldy, eps, first);
   US_LAUNCH_CHECK();
   return US_OK;
 }

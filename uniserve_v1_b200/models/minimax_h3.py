@@ -144,6 +144,16 @@ class H3Layout:
     def interval(self, rank: int):
         return rank * self.rows_own, (rank + 1) * self.rows_own
 
+    def cu(self, device):
+        """Cumulative lengths of the one packed sequence: (queries = all rows,
+        keys = the rows in use); built once per layout."""
+        c = getattr(self, "_cu", None)
+        if c is None or c[0].device != torch.device(device):
+            c = (torch.tensor([0, self.rows], dtype=torch.int32, device=device),
+                 torch.tensor([0, self.used], dtype=torch.int32, device=device))
+            self._cu = c
+        return c
+
 
 def build_layout(cfg: H3Config, latent_frames: int, lat_h: int, lat_w: int, n_audio: int,
                  n_text: int, sp: int = 1, n_cond: int = 0, device="cpu") -> H3Layout:
@@ -342,8 +352,7 @@ class H3Transformer:
         q, k, v = full[:, :hl * D], full[:, hl * D:2 * hl * D], full[:, 2 * hl * D:]
         F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, layout.coords, self.inv_freq, hl, hl, D,
                          cfg.rope_freqs_per_axis, cfg.eps)
-        cu_q = torch.tensor([0, rows], dtype=torch.int32, device=n.device)
-        cu_k = torch.tensor([0, layout.used], dtype=torch.int32, device=n.device)
+        cu_q, cu_k = layout.cu(n.device)
         att = self._dense_attention(q.view(rows, hl, D), k.view(rows, hl, D), v.view(rows, hl, D),
                                     cu_q, cu_k, rows, layout.used).reshape(rows, hl * D)
         if P > 1:

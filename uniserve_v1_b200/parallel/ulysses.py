@@ -70,8 +70,7 @@ class FusedUlysses:
         q, k, v = full[:, :hl * D], full[:, hl * D:2 * hl * D], full[:, 2 * hl * D:]
         F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, layout.coords, model.inv_freq, hl, hl, D,
                          cfg.rope_freqs_per_axis, cfg.eps)
-        cu_q = torch.tensor([0, rows], dtype=torch.int32, device=n.device)
-        cu_k = torch.tensor([0, layout.used], dtype=torch.int32, device=n.device)
+        cu_q, cu_k = layout.cu(n.device)
         att = self.fc.site_tensor(SITE_ATT, rows, hl * D).view(rows, hl, D)
         flash_attn_varlen(q.view(rows, hl, D), k.view(rows, hl, D), v.view(rows, hl, D), cu_q,
                           cu_k, rows, layout.used, model.scale, False, out=att)

@@ -95,6 +95,12 @@ class VideoService:
                  retention_s: float = 3600.0, store_bytes: int = 1 << 30, observation=None):
         from .video_rules import SIZES
         self.model = transformer
+        # Ranks of the sequence group also share the decode work: temporal units
+        # are dealt round-robin and the encoded planes gathered on every rank
+        # (crates/engine/src/runner/decoder.rs:57-70, reference project path).
+        ax = transformer.ctx.axis("ulysses")
+        self.world, self.rank, self.group = ax.size, ax.rank, ax.group
+        self.h2d_bytes = self.d2h_bytes = 0
         self.denoiser = Denoiser(transformer)
         self.steps = self.denoiser.steps
         self.video_vae, self.audio_vae = video_vae, audio_vae
@@ -167,7 +173,10 @@ class VideoService:
     def generate(self, job: VideoJob) -> bytes:
         cfg, p, dev = self.model.cfg, job.plan, self.model.device
         job.phase = "TextEncode"
-        feats = self.text.encode(job.prompt, dev)
+        feats = self.text.encode(job.prompt, "cpu")
+        if dev.type == "cuda":
+            feats = feats.pin_memory().to(dev, non_blocking=True)
+            self.h2d_bytes += feats.numel() * feats.element_size()
         job.phase = "LatentPrepare"
         lf, lh, lw = cfg.latent_shape(p.num_frames, p.width, p.height)
         n_audio_rows = cfg.audio_rows(p.num_frames)
@@ -180,11 +189,15 @@ class VideoService:
             job.step = st.step
             job.progress = 0.8 * st.step / self.denoiser.steps
         job.phase = "VideoDecode"
-        units = self.video_vae.decode(st.video)
-        frames = torch.cat([f for _, f in units], 0)[:p.num_frames]
-        if frames.shape[-2:] != (p.height, p.width):
-            frames = torch.nn.functional.interpolate(frames, size=(p.height, p.width),
-                                                     mode="bilinear", align_corners=False)
+        units = self.video_vae.decode(st.video, self.rank, self.world)
+        planes = []
+        for _, f in units:
+            if f.shape[-2:] != (p.height, p.width):
+                f = torch.nn.functional.interpolate(f, size=(p.height, p.width),
+                                                    mode="bilinear", align_corners=False)
+            y, u, v = M.rgb_to_yuv420(f)
+            planes.append(torch.cat([y.flatten(1), u.flatten(1), v.flatten(1)], 1))
+        packed = self._collect_units(planes, lf, p)
         job.progress = 0.9
         job.phase = "AudioDecode"
         # audio rows are [time x 2 channels, latent_channels]: split channels into the batch
@@ -194,11 +207,53 @@ class VideoService:
         wav = wav[:, :want] if wav.shape[1] >= want else torch.nn.functional.pad(
             wav, (0, want - wav.shape[1]))
         job.phase = "VideoEncode"
-        y, u, v = M.rgb_to_yuv420(frames)
+        if self.rank != 0:
+            return b""
+        hw = p.height * p.width
+        host = packed.cpu()
+        self.d2h_bytes += host.numel()
+        y = host[:, :hw].view(-1, p.height, p.width)
+        u = host[:, hw:hw + hw // 4].view(-1, p.height // 2, p.width // 2)
+        v = host[:, hw + hw // 4:].view(-1, p.height // 2, p.width // 2)
         job.phase = "AudioEncode"
         pcm = M.pcm_interleave(wav)
+        self.d2h_bytes += pcm.numel() * pcm.element_size()
         job.phase = "Mux"
         return M.write_mp4(y, u, v, p.fps, pcm, self.audio_vae.cfg.sample_rate)
+
+    def _collect_units(self, planes: list, latent_frames: int, p) -> torch.Tensor:
+        """Packed 4:2:0 planes of every frame in order, [frames, 1.5 * H * W] uint8.
+        Under a sequence group each rank encoded its own temporal units; the
+        blocks are all-gathered (padded to the largest share) and put in order."""
+        width = p.height * p.width * 3 // 2
+        dev = self.model.device
+        own = torch.cat(planes, 0) if planes else torch.empty(0, width, dtype=torch.uint8,
+                                                                device=dev)
+        if self.world == 1:
+            return own[:p.num_frames]
+        import torch.distributed as dist
+        unit = 5
+        n_units = (latent_frames + unit - 1) // unit
+        T = self.video_vae.cfg.temporal
+
+        def frames_of(k):   # frames unit k produces
+            f = min(unit, latent_frames - k * unit)
+            return 1 + T * (f - 1)
+        share = [sum(frames_of(k) for k in range(r, n_units, self.world))
+                 for r in range(self.world)]
+        cap = max(share)
+        buf = torch.zeros(cap, width, dtype=torch.uint8, device=dev)
+        buf[:own.shape[0]] = own
+        allb = torch.empty(self.world * cap, width, dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(allb, buf, group=self.group)
+        allb = allb.view(self.world, cap, width)
+        cursor = [0] * self.world
+        out = []
+        for k in range(n_units):
+            r, n = k % self.world, frames_of(k)
+            out.append(allb[r, cursor[r]:cursor[r] + n])
+            cursor[r] += n
+        return torch.cat(out, 0)[:p.num_frames]
 
     def _run(self):
         while True:

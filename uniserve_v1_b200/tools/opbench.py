@@ -53,7 +53,7 @@ def timeit(fn, iters=10, warmup=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["flash", "gemm", "gated", "decode", "moe", "fused-norm",
-                                   "ulysses"])
+                                   "ulysses", "tp", "moe-fp8", "gemm-fp8"])
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=2048)
@@ -104,6 +104,37 @@ def main():
         byts = active * (w13[0].numel() + w2[0].numel()) * 2.0
         out.update(tokens=T, experts=E, active_experts=active, ms=ms, tbs=byts / ms / 1e9,
                    frac_memory=byts / ms / 1e9 / tbs)
+    elif a.op == "moe-fp8":
+        # the same layer with block-scaled FP8 expert weights (quantise rows, grouped FC1,
+        # quantise, grouped FC2)
+        from ..ops import fp8 as Q
+        T, E, k, H, I = a.batch, a.experts, a.topk, a.hidden, a.inter
+        x = rnd(T, H)
+        ex = Q.Fp8Experts.from_bf16(rnd(E, 2 * I, H), rnd(E, H, I))
+        logits = torch.randn(T, E, generator=g, device=dev)
+        ids, wts = F.topk_softmax(logits, k, True)
+        ws = F.MoeWorkspace.create(T, k, E, H, I, dev)
+        if ws.block_n > 64:
+            ws = F.MoeWorkspace.create(T, k, E, H, I, dev, block_n=64)
+        ms = timeit(lambda: Q.moe_experts_fp8(x, ids, wts, ex, ws=ws), a.iters)
+        active = int(torch.unique(ids).numel())
+        byts = active * (ex.w13[0].numel() + ex.w2[0].numel()) * 1.0
+        flops = 2.0 * T * k * 3 * I * H
+        out.update(tokens=T, experts=E, active_experts=active, block_n=ws.block_n, ms=ms,
+                   tbs=byts / ms / 1e9, frac_memory=byts / ms / 1e9 / tbs,
+                   tflops=flops / ms / 1e9)
+    elif a.op == "gemm-fp8":
+        from ..ops import fp8 as Q
+        x, w = rnd(a.rows, a.k), rnd(a.m, a.k)
+        wq, wsc = Q.quantize_weight_block128(w)
+        xq, xs = Q.quantize_rows_block128(x)
+        ms = timeit(lambda: Q.linear_fp8_block(None, wq, wsc, xq=xq, x_scale=xs), a.iters)
+        msq = timeit(lambda: Q.quantize_rows_block128(x, None, xq, xs), a.iters)
+        flops = 2.0 * a.rows * a.m * a.k
+        byts = 1.0 * (x.numel() + w.numel()) + 2.0 * a.rows * a.m
+        out.update(rows=a.rows, m=a.m, k=a.k, ms=ms, tflops=flops / ms / 1e9,
+                   tbs=byts / ms / 1e9, frac_memory=byts / ms / 1e9 / tbs, quantize_ms=msq,
+                   quantize_tbs=3.0 * x.numel() / msq / 1e9)
     elif a.op == "fused-norm":
         # all-reduce + residual + RMSNorm over the peer heap; one rank (its own peer) so a
         # profiler can attach; the 2/8-rank numbers come from bench.py
@@ -146,6 +177,24 @@ def main():
         out.update(rows=rows, hidden=H, heads_local=hl, scatter_ms=ms1,
                    scatter_tflops=2.0 * rows * W * H / ms1 / 1e9, pull_ms=ms2,
                    pull_tflops=2.0 * rows * H * hl * D / ms2 / 1e9)
+    elif a.op == "tp":
+        # the fused tensor-parallel MLP with this rank as its own (only) peer: gated
+        # up-projection gathering its rows by TMA from the heap, down-projection
+        # storing its partial rows into the owner's slot, slot sum + residual + norm
+        from ..parallel import tp_fused as TP
+        rows, H, I = a.rows, a.m, a.inter
+        tp = TP.FusedTP(None, 0, 1, dev, rows, H)
+        tp.norm_rows(TP.SITE_NORM_A).copy_(rnd(rows, H))
+        w13, w2, nw = rnd(2 * I, H), rnd(H, I), rnd(H)
+        res = torch.zeros(rows, H, dtype=torch.float32, device=dev)
+        hid = tp.gather_linear(w13, TP.SITE_NORM_A, gated=True)
+        ms1 = timeit(lambda: tp.gather_linear(w13, TP.SITE_NORM_A, gated=True), a.iters)
+        ms2 = timeit(lambda: tp.reduce_scatter_linear(w2, hid), a.iters)
+        ms3 = timeit(lambda: tp.reduce_add_rmsnorm(res, nw, TP.SITE_NORM_B, 1e-6), a.iters)
+        out.update(rows=rows, hidden=H, inter_local=I, gather_gated_ms=ms1,
+                   gather_gated_tflops=4.0 * rows * I * H / ms1 / 1e9, reduce_scatter_ms=ms2,
+                   reduce_scatter_tflops=2.0 * rows * I * H / ms2 / 1e9, reduce_norm_ms=ms3,
+                   reduce_norm_tbs=rows * H * (2 + 4 + 4 + 2) / ms3 / 1e9)
     else:
         B, Hq, Hkv, D, page = a.batch, 32, 4, 128, 16
         per = (a.ctx + page - 1) // page
