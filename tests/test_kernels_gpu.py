@@ -272,3 +272,21 @@ def test_flash_attn_long_sequence():
     out = flash_attn_varlen(q, k, v, cu, cu, T, T, 1 / math.sqrt(D), False)
     ref = R.varlen_attention(q, k, v, cu.cpu(), cu.cpu(), 1 / math.sqrt(D), False)
     close(out, ref, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("single", [True, False])
+@pytest.mark.parametrize("causal", [False, True])
+def test_flash_attn_both_kernels(single, causal, monkeypatch):
+    """The single-tile kernel and the two-tile ping-pong kernel on the same input:
+    causal self-attention (the first tile of a pair walks fewer key blocks than
+    the second) and a ragged tail (the second tile of the last pair is partial)."""
+    import uniserve_v1_b200.ops.flash as FL
+    monkeypatch.setattr(FL, "_SINGLE_TILE_ONLY", single)
+    D, H = 128, 3
+    lens = [1000, 129, 384]
+    T = sum(lens)
+    q, k, v = rnd(T, H, D, seed=11), rnd(T, H, D, seed=12), rnd(T, H, D, seed=13)
+    cu = torch.tensor([0, 1000, 1129, 1513], dtype=torch.int32, device=DEV)
+    out = FL.flash_attn_varlen(q, k, v, cu, cu, max(lens), max(lens), 1 / math.sqrt(D), causal)
+    ref = R.varlen_attention(q, k, v, cu.cpu(), cu.cpu(), 1 / math.sqrt(D), causal)
+    close(out, ref, 2e-2, 2e-2)

@@ -203,6 +203,203 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
+// Persistent form for dense problems of more than one wave: one CTA per SM
+// walks the output tiles (weight tile fastest, so CTAs running together share an
+// activation tile in L2); two TMEM accumulators let the epilogue of tile i run
+// under the multiplications of tile i + 1, and the TMA ring never drains
+// between tiles.
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(192)
+gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
+                       const __grid_constant__ BMaps tmBs, const GemmArgs args) {
+  US_PDL_PROLOGUE();
+  constexpr int kBTile = BN * kBlockK * 2;
+  constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
+  constexpr uint32_t kAccCols = DUAL ? 2 * BN : BN;
+  constexpr uint32_t kCols = tmem_cols<2 * BN>(DUAL);
+  static_assert(kCols <= 512, "two accumulators must fit tensor memory");
+  constexpr uint32_t kIdesc = tc::make_idesc(kBlockM, BN, tc::kFmtBF16, tc::kFmtBF16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (args.M + kBlockM - 1) / kBlockM;
+  const int n_tiles = (args.rows + BN - 1) / BN;
+  const int total = m_tiles * n_tiles;
+  const int num_k = (args.K + kBlockK - 1) / kBlockK;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stages = args.stages;
+  uint64_t* full_bar = (uint64_t*)(smem + (size_t)stages * kStageBytes);
+  uint64_t* empty_bar = full_bar + stages;
+  uint64_t* acc_full = empty_bar + stages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      tc::mbar_init(&full_bar[s], 1);
+      tc::mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&acc_full[b], 1);
+      tc::mbar_init(&acc_empty[b], 128);
+    }
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, kCols);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tc::tma_prefetch_desc(&tmA);
+      tc::tma_prefetch_desc(&tmBs.m[0]);
+      uint32_t kbg = 0;   // k-blocks issued so far, over all tiles
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total; t += gridDim.x) {
+        const int m_tile = t % m_tiles, row0 = (t / m_tiles) * BN;
+        for (int kb = 0; kb < num_k; ++kb, ++kbg) {
+          const int s = kbg % stages;
+          const uint32_t ph = (kbg / stages) & 1u;
+          if (!tc::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
+            us_dev_fail(args.status, US_DEV_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + (size_t)s * kStageBytes;
+          tc::mbar_expect_tx(&full_bar[s], kStageBytes);
+          const int kx = kb * kBlockK;
+          tc::tma_load_3d(st, &tmA, &full_bar[s], kx, m_tile * kBlockM, 0);
+          if (DUAL)
+            tc::tma_load_3d(st + kATile, &tmA, &full_bar[s], kx,
+                            args.dual_offset + m_tile * kBlockM, 0);
+          if (args.rows_per_peer > 0) {
+            const int src = row0 / args.rows_per_peer;
+            tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], &full_bar[s], kx,
+                            row0 - src * args.rows_per_peer);
+          } else {
+            const int src = args.k_per_peer > 0 ? kx / args.k_per_peer : 0;
+            tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], &full_bar[s],
+                            kx - src * args.k_per_peer, row0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t kbg = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = blockIdx.x; ok && t < total; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        if (!tc::mbar_wait(&acc_empty[buf], ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag)) {
+          us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
+          *abort_flag = 1;
+          break;
+        }
+        tc::tc_fence_after_sync();
+        const uint32_t d = tmem_base + (uint32_t)buf * kAccCols;
+        for (int kb = 0; kb < num_k; ++kb, ++kbg) {
+          const int s = kbg % stages;
+          const uint32_t ph = (kbg / stages) & 1u;
+          if (!tc::mbar_wait(&full_bar[s], ph, abort_flag)) {
+            us_dev_fail(args.status, US_DEV_TIMEOUT_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc::tc_fence_after_sync();
+          const uint32_t a_addr = tc::smem_u32(smem + (size_t)s * kStageBytes);
+          const uint32_t b_addr = a_addr + kATile * (DUAL ? 2 : 1);
+          const uint64_t adesc = tc::smem_desc_kmajor_sw128(a_addr);
+          const uint64_t bdesc = tc::smem_desc_kmajor_sw128(b_addr);
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            const uint32_t acc = (kb | k) != 0;
+            tc::umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            if (DUAL) {
+              const uint64_t a2desc = tc::smem_desc_kmajor_sw128(a_addr + kATile);
+              tc::umma_f16(d + BN, a2desc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            }
+          }
+          tc::umma_commit(&empty_bar[s]);
+        }
+        if (ok) tc::umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int ml = q * 32 + lane;
+    int it = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const int m_tile = t % m_tiles, row0 = (t / m_tiles) * BN;
+      const int nrows = min(BN, args.rows - row0);
+      if (!tc::mbar_wait(&acc_full[buf], (uint32_t)(it >> 1) & 1u, abort_flag)) {
+        us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
+        break;
+      }
+      tc::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t)buf * kAccCols + ((uint32_t)(q * 32) << 16);
+      Epilogue<DUAL> epi(args, 0, m_tile * kBlockM + ml, row0);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        if (c >= nrows) break;  // warp-uniform
+        uint32_t v[16], g[16];
+        tc::tmem_ld16(taddr + c, v);
+        if (DUAL) tc::tmem_ld16(taddr + BN + c, g);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (c + j < nrows)
+            epi.store(c + j, __uint_as_float(v[j]), DUAL ? __uint_as_float(g[j]) : 0.f);
+      }
+      tc::tc_fence_before_sync();
+      tc::mbar_arrive(&acc_empty[buf]);
+    }
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::tmem_dealloc(tmem_base, kCols);
+  }
+}
+
+template <int BN, bool DUAL>
+int launch_persist(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int tiles,
+                   cudaStream_t stream) {
+  constexpr int kBTile = BN * kBlockK * 2;
+  constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
+  int stages = (200 * 1024) / kStageBytes;
+  if (stages > 8) stages = 8;
+  a.stages = stages;
+  a.splits = 1;
+  const size_t smem = (size_t)stages * kStageBytes + (2 * stages + 4) * 8 + 16 + 1024;
+  static bool configured = false;
+  static int sms = 0;
+  if (!configured) {
+    US_CUDA_CHECK(cudaFuncSetAttribute(gemm_wx_persist_kernel<BN, DUAL>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    int dev = 0;
+    US_CUDA_CHECK(cudaGetDevice(&dev));
+    US_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    configured = true;
+  }
+  const int grid = tiles < sms ? tiles : sms;
+  US_CUDA_CHECK(us::launch_pdl(gemm_wx_persist_kernel<BN, DUAL>, dim3(grid), dim3(192), smem,
+                               stream, tmA, tmB, a));
+  return US_OK;
+}
+
 template <int BN, bool DUAL>
 int launch(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int m_tiles, int n_tiles,
            cudaStream_t stream) {
@@ -364,7 +561,7 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
   } else if (ps.out_peers && ps.peer_rows > 0) {
     US_REQUIRE(ps.n_out_peers >= 1 && ps.n_out_peers <= 8 && ps.peer_slot >= 0 &&
                ps.peer_slot < ps.n_out_peers && ps.peer_rows * ps.n_out_peers >= x_rows &&
-               num_tiles == nullptr);
+               (ps.peer_rows % block_n) == 0 && num_tiles == nullptr);
     a.peer_rows = ps.peer_rows;
     a.peer_slot = ps.peer_slot;
     for (int p = 0; p < ps.n_out_peers; ++p) {
@@ -386,6 +583,19 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
   const int n_tiles = num_tiles ? max_tiles : (x_rows + block_n - 1) / block_n;
   US_REQUIRE(n_tiles <= 65535);
 
+  // Dense problems of more than one wave run the persistent kernel (two
+  // accumulators in tensor memory: row tiles up to 256, gated up to 128).
+  static const bool no_persist = [] {
+    const char* e = getenv("US_NO_PERSIST");
+    return e && e[0] == '1';
+  }();
+  if (!no_persist && num_tiles == nullptr && G == 1 && m_tiles * n_tiles > 148 &&
+      (dual ? block_n == 128 : (block_n == 128 || block_n == 256))) {
+    const int tiles = m_tiles * n_tiles;
+    if (dual) return launch_persist<128, true>(tmA, tmB, a, tiles, stream);
+    if (block_n == 128) return launch_persist<128, false>(tmA, tmB, a, tiles, stream);
+    return launch_persist<256, false>(tmA, tmB, a, tiles, stream);
+  }
 #define US_GEMM_CASE(BN)                                                              \
   case BN:                                                                            \
     return dual ? launch<BN, true>(tmA, tmB, a, m_tiles, n_tiles, stream)             \

@@ -79,19 +79,39 @@ constexpr int tmem_cols(bool dual) {
 }
 
 // Per-thread epilogue of one output feature `m`: activation, bias, row scale,
-// row map, rounding.
+// row map, rounding.  The destination of row 0 of the tile is resolved once
+// (which buffer, which rank); rows then advance by a fixed stride unless a row
+// map or a route map redirects them one by one.
 template <bool DUAL>
 struct Epilogue {
   const GemmArgs& a;
   const int m, row0;
   const bool m_ok;
   float bias;
+  char* base;          // element (row0, m) of the destination; null = per-row lookup
+  long long row_bytes;
   __device__ __forceinline__ Epilogue(const GemmArgs& args, int group, int m_, int row0_)
-      : a(args), m(m_), row0(row0_), m_ok(m_ < args.M), bias(0.f) {
-    if (a.bias != nullptr && m_ok) {
+      : a(args), m(m_), row0(row0_), m_ok(m_ < args.M), bias(0.f), base(nullptr), row_bytes(0) {
+    if (!m_ok) return;
+    if (a.bias != nullptr) {
       const size_t bi = (size_t)group * a.M + m;
       bias = a.bias_dtype == 0 ? us::bf2f(((const __nv_bfloat16*)a.bias)[bi])
                                : ((const float*)a.bias)[bi];
+    }
+    const int esz = a.out_dtype == 0 ? 2 : 4;
+    row_bytes = a.ldo * esz;
+    if (a.route_map != nullptr || a.out_row_map != nullptr) return;
+    if (a.peer_rows > 0) {   // a tile lies inside one owner's interval
+      const int p = row0 / a.peer_rows;
+      base = (char*)a.peer_out[p] +
+             (((size_t)a.peer_slot * a.peer_rows + (size_t)(row0 - p * a.peer_rows)) * a.ldo + m) *
+                 esz;
+    } else if (a.peer_cols > 0) {
+      const int p = m / a.peer_cols;
+      base = (char*)a.peer_out[p] +
+             ((size_t)(a.peer_row_offset + row0) * a.ldo + (m - p * a.peer_cols)) * esz;
+    } else {
+      base = (char*)a.out + ((size_t)row0 * a.ldo + m) * esz;
     }
   }
   __device__ __forceinline__ void store(int r, float val, float gate) const {
@@ -116,24 +136,16 @@ struct Epilogue {
       return;
     }
     if (a.row_scale != nullptr) val *= a.row_scale[orow];
-    if (a.out_row_map != nullptr) orow = a.out_row_map[orow];
-    if (orow < 0) return;
-    if (a.peer_rows > 0) {
-      const int p = orow / a.peer_rows;
-      const size_t o =
-          ((size_t)a.peer_slot * a.peer_rows + (size_t)(orow - p * a.peer_rows)) * a.ldo + m;
+    if (base != nullptr) {
+      char* dst = base + (long long)r * row_bytes;
       if (a.out_dtype == 0)
-        ((__nv_bfloat16*)a.peer_out[p])[o] = us::f2bf(val);
+        *(__nv_bfloat16*)dst = us::f2bf(val);
       else
-        ((float*)a.peer_out[p])[o] = val;
+        *(float*)dst = val;
       return;
     }
-    if (a.peer_cols > 0) {
-      const int p = m / a.peer_cols;
-      const size_t o = (size_t)(a.peer_row_offset + orow) * a.ldo + (m - p * a.peer_cols);
-      ((__nv_bfloat16*)a.peer_out[p])[o] = us::f2bf(val);
-      return;
-    }
+    orow = a.out_row_map[orow];
+    if (orow < 0) return;
     const size_t o = (size_t)orow * a.ldo + m;
     if (a.out_dtype == 0)
       ((__nv_bfloat16*)a.out)[o] = us::f2bf(val);

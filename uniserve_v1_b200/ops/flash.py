@@ -8,10 +8,15 @@ from . import reference as R
 
 BF16 = torch.bfloat16
 
-N.register_signatures({
-    "us_flash_attn_varlen": (N.I, [N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.I, N.I,
-                                   N.I, N.L, N.L, N.L, N.L, N.F, N.I, N.P]),
-})
+import os
+
+_SIG = (N.I, [N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.L, N.L, N.L, N.L,
+              N.F, N.I, N.P])
+N.register_signatures({"us_flash_attn_varlen": _SIG, "us_flash_attn_varlen2": _SIG})
+
+# Two kernels share one contract: the two-tile ping-pong kernel (default when a
+# sequence has more than one 128-row query tile) and the single-tile kernel.
+_SINGLE_TILE_ONLY = os.environ.get("US_FLASH_V1", "0") == "1"
 
 
 def flash_attn_varlen(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, out=None):
@@ -27,7 +32,9 @@ def flash_attn_varlen(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, out=None
     if out is None:
         out = torch.empty(Tq, Hq, D, dtype=BF16, device=q.device)
     n = cu_q.numel() - 1
-    N.call("us_flash_attn_varlen", N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(cu_q),
+    name = "us_flash_attn_varlen" if (_SINGLE_TILE_ONLY or max_q <= 128) else \
+        "us_flash_attn_varlen2"
+    N.call(name, N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(cu_q),
            N.ptr(cu_k), n, Tq, Tk, Hq, Hkv, D, max_q, q.stride(0), k.stride(0), v.stride(0),
            out.stride(0), scale, int(causal), N.stream())
     return out
