@@ -90,3 +90,18 @@ def test_ulysses2_matches_single_rank():
         assert p.exitcode == 0
     torch.testing.assert_close(v2, v1, atol=2e-4, rtol=2e-4)
     torch.testing.assert_close(a2, a1, atol=2e-4, rtol=2e-4)
+
+
+def test_attention_width_differs_from_stream_width():
+    """The served shape has 56 x 128 = 7168 attention channels on a 5376-wide stream."""
+    cfg = H3Config.tiny()
+    cfg.num_heads = 3                      # 384 attention channels, hidden 256
+    model = H3Transformer(cfg, "cpu", torch.float32).init_random(seed=0)
+    assert model.blocks[0].qkv.shape == (3 * 384, 256)
+    assert model.blocks[0].to_out.shape == (256, 384)
+    den = Denoiser(model, dmd_ladder((999, 500), 10.0), dmd_ladder((999, 500), 3.0))
+    g = torch.Generator().manual_seed(5)
+    text = torch.randn(9, cfg.text_dim, generator=g)
+    st = den.prepare(seed=1, latent_frames=2, lat_h=4, lat_w=4, n_audio=6, text_features=text)
+    den.run(st)
+    assert torch.isfinite(st.video).all() and torch.isfinite(st.audio).all()

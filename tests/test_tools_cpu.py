@@ -1,0 +1,76 @@
+"""The evaluation tool against a live server on CPU (tiny model), and its checks."""
+import asyncio
+import socket
+import threading
+import time
+
+import pytest
+import torch
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.fixture(scope="module")
+def live_server():
+    import uvicorn
+    from uniserve_v1_b200.config.policy import Package
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.server.app import create_app
+    from uniserve_v1_b200.server.tokenizer import ByteTokenizer
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    eng = LLMEngine(model, num_pages=512, max_num_seqs=8, max_model_len=512, use_graphs=False)
+    pkg = Package.parse('model = "random:tiny"\nserved_model_name = "tiny"\n')
+    app = create_app(package=pkg, engine=eng, tokenizer=ByteTokenizer(1024, 1023),
+                     served_model_name="tiny")
+    port = _free_port()
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    for _ in range(200):
+        if server.started:
+            break
+        time.sleep(0.05)
+    assert server.started
+    yield f"http://127.0.0.1:{port}"
+    server.should_exit = True
+    th.join(timeout=10)
+
+
+def test_eval_run_and_checks(live_server):
+    from uniserve_v1_b200.tools import eval as E
+    b = asyncio.run(E.run_load(live_server, concurrency=4, requests=8, prompt_tokens=12,
+                               max_tokens=6, model="tiny"))
+    s = b["summary"]
+    assert s["succeeded"] == 8 and s["failed"] == 0 and s["output_tokens"] == 48
+    assert s["ttft_s"]["p50"] is not None and s["tpot_s"]["p50"] is not None
+    assert all(r["finish_reason"] == "length" for r in b["records"])
+    assert E.check_stop(b) == [] and E.check_faults(b) == []
+    assert E.compare_bundles(b, b) == []
+    slow = {"summary": dict(s, output_tokens_per_s=s["output_tokens_per_s"] * 0.5), "records": []}
+    assert any("tokens/s" in f for f in E.compare_bundles(b, slow))
+    # non-streaming path
+    b2 = asyncio.run(E.run_load(live_server, 2, 2, 8, 4, stream=False, model="tiny"))
+    assert b2["summary"]["succeeded"] == 2
+
+
+def test_eval_check_rules():
+    from uniserve_v1_b200.tools import eval as E
+    rec = dict(index=0, ok=True, status=200, error=None, latency_s=1.0, ttft_s=0.1,
+               output_tokens=5, prompt_tokens=3, cached_tokens=0, finish_reason="length",
+               text="abc END", chunks=5, stop=["END"], max_tokens=8)
+    fails = E.check_stop({"records": [rec]})
+    assert len(fails) == 2          # stop string present; 'length' short of the budget
+    hung = dict(rec, ok=False, status=0, error=None, finish_reason=None)
+    assert E.check_faults({"records": [hung]})
+    failed = dict(rec, ok=False, status=503, error="engine failed")
+    assert E.check_faults({"records": [failed]}) == []
+    acc = E.compare_accuracy(1248, 1233, 1319)
+    assert acc["pass"] and abs(acc["reference"] - 0.946171) < 1e-6
+    assert not E.compare_accuracy(1248, 1100, 1319)["pass"]

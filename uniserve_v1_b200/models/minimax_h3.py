@@ -191,7 +191,7 @@ class H3Block:
     qkv: torch.Tensor        # [3 * hidden, hidden], rows grouped by destination rank
     q_norm: torch.Tensor
     k_norm: torch.Tensor
-    to_out: torch.Tensor     # [hidden, hidden]
+    to_out: torch.Tensor     # [hidden, heads * head_dim]
     ff1: torch.Tensor        # [2 * ffn, hidden] value rows, then gate rows
     ff2: torch.Tensor        # [hidden, ffn]
 
@@ -242,8 +242,9 @@ class H3Transformer:
                                              rnd(2 * Fn, H), rnd(H, Fn)))
         self.refiner_norm = ones(H)
         for _ in range(cfg.num_layers):
-            q, k, v = rnd(H, H), rnd(H, H), rnd(H, H)
-            self.blocks.append(H3Block(self._group_qkv(q, k, v), ones(D), ones(D), rnd(H, H),
+            inner = cfg.num_heads * D     # 56 x 128 = 7168 on a 5376-wide stream
+            q, k, v = rnd(inner, H), rnd(inner, H), rnd(inner, H)
+            self.blocks.append(H3Block(self._group_qkv(q, k, v), ones(D), ones(D), rnd(H, inner),
                                        rnd(2 * Fn, H), rnd(H, Fn)))
         self.proj_out = rnd(cfg.patch_width, H, dtype=torch.float32)
         self.audio_proj_out = rnd(cfg.audio_channels, H, dtype=torch.float32)

@@ -1,0 +1,292 @@
+"""Measures a serving system through its public HTTP interface.
+
+    python -m uniserve_v1_b200.tools.eval run --url http://127.0.0.1:8000 --concurrency 64 \
+        --requests 256 --prompt-tokens 128 --max-tokens 256 --out bundle.json
+    python -m uniserve_v1_b200.tools.eval compare reference.json candidate.json
+    python -m uniserve_v1_b200.tools.eval check-stop bundle.json
+    python -m uniserve_v1_b200.tools.eval check-faults bundle.json
+
+``run`` drives ``POST /v1/chat/completions`` with a closed loop of ``concurrency``
+clients (streaming, so the first-token time is observed), validates every
+response and writes a *bundle*: one record per request plus a summary (output
+tokens/s, request latency, time to first token and time per output token at
+p50/p95/p99).  ``compare`` holds a candidate bundle to a reference bundle with a
+relative tolerance, or two GSM8K-style accuracy counts to the two-sided 95 %
+interval of a difference of proportions.  ``check-stop`` verifies stop handling
+(no stop string in any text, finish reasons agree with the budget) and
+``check-faults`` that every request of a fault-injection run ended in a clean
+terminal state.  Exit status 2 marks a failed validation.
+
+Reference: tools/eval/src/main.rs:1-7, tools/eval/src/check.rs (reference project paths).
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import math
+import random
+import statistics
+import sys
+import time
+from dataclasses import asdict, dataclass, field
+from typing import Optional
+
+
+@dataclass
+class Record:
+    index: int
+    ok: bool = False
+    status: int = 0
+    error: Optional[str] = None
+    latency_s: float = 0.0
+    ttft_s: Optional[float] = None
+    output_tokens: int = 0
+    prompt_tokens: int = 0
+    cached_tokens: int = 0
+    finish_reason: Optional[str] = None
+    text: str = ""
+    chunks: int = 0
+    stop: list = field(default_factory=list)
+    max_tokens: int = 0
+
+
+def percentile(xs, p):
+    if not xs:
+        return None
+    xs = sorted(xs)
+    k = (len(xs) - 1) * p
+    lo, hi = math.floor(k), math.ceil(k)
+    return xs[lo] + (xs[hi] - xs[lo]) * (k - lo)
+
+
+def synth_prompt(rng: random.Random, tokens: int) -> str:
+    """About ``tokens`` tokens of pronounceable filler (one short word per token)."""
+    syll = ["ka", "mi", "to", "ra", "ne", "so", "lu", "vi", "pe", "da", "go", "he"]
+    return " ".join(rng.choice(syll) + rng.choice(syll) for _ in range(max(1, tokens)))
+
+
+async def one_request(session, url, headers, body, rec: Record, timeout_s: float):
+    import aiohttp
+    t0 = time.perf_counter()
+    try:
+        async with session.post(url + "/v1/chat/completions", json=body, headers=headers,
+                                timeout=aiohttp.ClientTimeout(total=timeout_s)) as resp:
+            rec.status = resp.status
+            if resp.status != 200:
+                rec.error = (await resp.text())[:500]
+                return
+            if body.get("stream"):
+                async for raw in resp.content:
+                    line = raw.decode().strip()
+                    if not line.startswith("data:"):
+                        continue
+                    data = line[5:].strip()
+                    if data == "[DONE]":
+                        break
+                    ev = json.loads(data)
+                    if "error" in ev:
+                        rec.error = json.dumps(ev["error"])[:500]
+                        return
+                    for ch in ev.get("choices", []):
+                        delta = ch.get("delta", {})
+                        piece = (delta.get("content") or "") + (delta.get("reasoning") or "")
+                        if piece or delta.get("tool_calls"):
+                            if rec.ttft_s is None:
+                                rec.ttft_s = time.perf_counter() - t0
+                            rec.text += piece
+                            rec.chunks += 1
+                        if ch.get("finish_reason"):
+                            rec.finish_reason = ch["finish_reason"]
+                    if ev.get("usage"):
+                        u = ev["usage"]
+                        rec.output_tokens = u.get("completion_tokens", 0)
+                        rec.prompt_tokens = u.get("prompt_tokens", 0)
+                        rec.cached_tokens = (u.get("prompt_tokens_details") or {}).get(
+                            "cached_tokens", 0)
+            else:
+                ev = await resp.json()
+                ch = ev["choices"][0]
+                rec.text = ch["message"].get("content") or ""
+                rec.finish_reason = ch.get("finish_reason")
+                u = ev.get("usage", {})
+                rec.output_tokens = u.get("completion_tokens", 0)
+                rec.prompt_tokens = u.get("prompt_tokens", 0)
+            rec.ok = rec.finish_reason is not None
+    except Exception as e:     # noqa: BLE001 - a load generator records every failure
+        rec.error = f"{type(e).__name__}: {e}"
+    finally:
+        rec.latency_s = time.perf_counter() - t0
+
+
+async def run_load(url: str, concurrency: int, requests: int, prompt_tokens: int, max_tokens: int,
+                   stream: bool = True, api_key: Optional[str] = None, model: str = "default",
+                   seed: int = 0, stop: Optional[list] = None, temperature: float = 0.0,
+                   timeout_s: float = 600.0, ignore_eos: bool = True) -> dict:
+    import aiohttp
+    rng = random.Random(seed)
+    headers = {"Authorization": f"Bearer {api_key}"} if api_key else {}
+    records = [Record(i, stop=stop or [], max_tokens=max_tokens) for i in range(requests)]
+    queue: asyncio.Queue = asyncio.Queue()
+    for r in records:
+        queue.put_nowait(r)
+    t0 = time.perf_counter()
+
+    async def client(session):
+        while True:
+            try:
+                rec = queue.get_nowait()
+            except asyncio.QueueEmpty:
+                return
+            body = {"model": model, "max_tokens": max_tokens, "temperature": temperature,
+                    "stream": stream, "seed": seed + rec.index, "ignore_eos": ignore_eos,
+                    "messages": [{"role": "user", "content": synth_prompt(rng, prompt_tokens)}]}
+            if stream:
+                body["stream_options"] = {"include_usage": True}
+            if stop:
+                body["stop"] = stop
+            await one_request(session, url, headers, body, rec, timeout_s)
+
+    conn = aiohttp.TCPConnector(limit=0)
+    async with aiohttp.ClientSession(connector=conn) as session:
+        await asyncio.gather(*[client(session) for _ in range(concurrency)])
+    wall = time.perf_counter() - t0
+    return bundle_of(records, wall, dict(url=url, concurrency=concurrency, requests=requests,
+                                         prompt_tokens=prompt_tokens, max_tokens=max_tokens,
+                                         stream=stream, seed=seed))
+
+
+def bundle_of(records, wall_s: float, point: dict) -> dict:
+    good = [r for r in records if r.ok]
+    lat = [r.latency_s for r in good]
+    ttft = [r.ttft_s for r in good if r.ttft_s is not None]
+    tpot = [(r.latency_s - r.ttft_s) / max(1, r.output_tokens - 1) for r in good
+            if r.ttft_s is not None and r.output_tokens > 1]
+    out_tokens = sum(r.output_tokens for r in good)
+    pct = lambda xs: {"p50": percentile(xs, .5), "p95": percentile(xs, .95),
+                      "p99": percentile(xs, .99),
+                      "mean": statistics.fmean(xs) if xs else None}
+    return {"point": point, "wall_s": wall_s,
+            "summary": {"requests": len(records), "succeeded": len(good),
+                        "failed": len(records) - len(good), "output_tokens": out_tokens,
+                        "output_tokens_per_s": out_tokens / wall_s if wall_s > 0 else 0.0,
+                        "requests_per_s": len(good) / wall_s if wall_s > 0 else 0.0,
+                        "latency_s": pct(lat), "ttft_s": pct(ttft), "tpot_s": pct(tpot)},
+            "records": [asdict(r) for r in records]}
+
+
+# ------------------------------------------------------------------ checks ----
+def compare_bundles(ref: dict, cand: dict, tolerance: float = 0.05) -> list:
+    """Regressions of the candidate against the reference (empty = pass)."""
+    fails = []
+    rs, cs = ref["summary"], cand["summary"]
+    if cs["failed"] > rs["failed"]:
+        fails.append(f"failed requests {cs['failed']} > {rs['failed']}")
+    if cs["output_tokens_per_s"] < rs["output_tokens_per_s"] * (1 - tolerance):
+        fails.append(f"output tokens/s {cs['output_tokens_per_s']:.1f} < "
+                     f"{rs['output_tokens_per_s']:.1f} - {tolerance:.0%}")
+    for key in ("latency_s", "ttft_s", "tpot_s"):
+        a, b = rs[key]["p50"], cs[key]["p50"]
+        if a is not None and b is not None and b > a * (1 + tolerance):
+            fails.append(f"{key} p50 {b:.4f} > {a:.4f} + {tolerance:.0%}")
+    return fails
+
+
+def compare_accuracy(ref_correct: int, cand_correct: int, n: int) -> dict:
+    """Two-sided 95 % interval of the difference of two proportions over the same
+    ``n`` problems; the candidate passes when the interval contains zero or lies above it."""
+    p1, p2 = ref_correct / n, cand_correct / n
+    se = math.sqrt(p1 * (1 - p1) / n + p2 * (1 - p2) / n)
+    lo, hi = (p2 - p1) - 1.96 * se, (p2 - p1) + 1.96 * se
+    return {"reference": p1, "candidate": p2, "difference": p2 - p1, "interval": [lo, hi],
+            "pass": hi >= 0.0}
+
+
+def check_stop(bundle: dict) -> list:
+    fails = []
+    for r in bundle["records"]:
+        if not r["ok"]:
+            continue
+        for s in r.get("stop") or []:
+            if s and s in r["text"]:
+                fails.append(f"request {r['index']}: stop string {s!r} in the text")
+        if r["finish_reason"] == "length" and r["max_tokens"] and \
+                r["output_tokens"] != r["max_tokens"]:
+            fails.append(f"request {r['index']}: finish 'length' at {r['output_tokens']} of "
+                         f"{r['max_tokens']} tokens")
+        if r["finish_reason"] == "stop" and r["max_tokens"] and \
+                r["output_tokens"] > r["max_tokens"]:
+            fails.append(f"request {r['index']}: {r['output_tokens']} tokens exceed the budget")
+    return fails
+
+
+def check_faults(bundle: dict) -> list:
+    """Every request of a fault-injection run reached a terminal state: a finish
+    reason, or an HTTP / stream error that names the failure; none hung."""
+    fails = []
+    for r in bundle["records"]:
+        if r["ok"]:
+            continue
+        if not r["error"] and r["status"] in (0, 200):
+            fails.append(f"request {r['index']}: neither finished nor failed")
+        if r["error"] and "TimeoutError" in r["error"]:
+            fails.append(f"request {r['index']}: timed out ({r['latency_s']:.1f} s)")
+    return fails
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="uniserve-eval", description=__doc__.split("\n")[0])
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    r = sub.add_parser("run")
+    r.add_argument("--url", required=True)
+    r.add_argument("--concurrency", type=int, default=8)
+    r.add_argument("--requests", type=int, default=32)
+    r.add_argument("--prompt-tokens", type=int, default=128)
+    r.add_argument("--max-tokens", type=int, default=128)
+    r.add_argument("--no-stream", action="store_true")
+    r.add_argument("--api-key")
+    r.add_argument("--model", default="default")
+    r.add_argument("--seed", type=int, default=0)
+    r.add_argument("--stop", action="append")
+    r.add_argument("--temperature", type=float, default=0.0)
+    r.add_argument("--out")
+    c = sub.add_parser("compare")
+    c.add_argument("reference")
+    c.add_argument("candidate")
+    c.add_argument("--tolerance", type=float, default=0.05)
+    a = sub.add_parser("compare-accuracy")
+    a.add_argument("reference_correct", type=int)
+    a.add_argument("candidate_correct", type=int)
+    a.add_argument("n", type=int)
+    for name in ("check-stop", "check-faults"):
+        s = sub.add_parser(name)
+        s.add_argument("bundle")
+    args = ap.parse_args(argv)
+    if args.cmd == "run":
+        b = asyncio.run(run_load(args.url, args.concurrency, args.requests, args.prompt_tokens,
+                                 args.max_tokens, not args.no_stream, args.api_key, args.model,
+                                 args.seed, args.stop, args.temperature))
+        if args.out:
+            with open(args.out, "w") as f:
+                json.dump(b, f)
+        print(json.dumps(b["summary"], indent=1))
+        return 0 if b["summary"]["failed"] == 0 else 2
+    if args.cmd == "compare":
+        fails = compare_bundles(json.load(open(args.reference)), json.load(open(args.candidate)),
+                                args.tolerance)
+    elif args.cmd == "compare-accuracy":
+        res = compare_accuracy(args.reference_correct, args.candidate_correct, args.n)
+        print(json.dumps(res))
+        return 0 if res["pass"] else 2
+    elif args.cmd == "check-stop":
+        fails = check_stop(json.load(open(args.bundle)))
+    else:
+        fails = check_faults(json.load(open(args.bundle)))
+    for f in fails:
+        print("FAIL:", f)
+    print("pass" if not fails else f"{len(fails)} failure(s)")
+    return 0 if not fails else 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())
