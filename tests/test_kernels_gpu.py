@@ -290,3 +290,17 @@ def test_flash_attn_both_kernels(single, causal, monkeypatch):
     out = FL.flash_attn_varlen(q, k, v, cu, cu, max(lens), max(lens), 1 / math.sqrt(D), causal)
     ref = R.varlen_attention(q, k, v, cu.cpu(), cu.cpu(), 1 / math.sqrt(D), causal)
     close(out, ref, 2e-2, 2e-2)
+
+
+def test_fence_probes_stamp_the_stream_in_order():
+    from uniserve_v1_b200.engine.profiling import ProbeRing
+    ring = ProbeRing(16, DEV)
+    x = rnd(4096, 4096)
+    ring.mark("work.begin", 7)
+    y = F.linear(x, x)
+    ring.mark("work.end", 7)
+    rows = ring.collect()
+    assert [r[0] for r in rows] == ["work.begin", "work.end"]
+    assert rows[1][1] > rows[0][1] > 0 and rows[0][3] == 7
+    assert (rows[1][1] - rows[0][1]) < 1e9          # a sub-second GEMM
+    assert ring.collect() == [] and y.shape == (4096, 4096)

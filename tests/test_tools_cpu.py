@@ -74,3 +74,33 @@ def test_eval_check_rules():
     acc = E.compare_accuracy(1248, 1233, 1319)
     assert acc["pass"] and abs(acc["reference"] - 0.946171) < 1e-6
     assert not E.compare_accuracy(1248, 1100, 1319)["pass"]
+
+
+def test_profile_session_and_trace(tmp_path):
+    """Probes and spans of engine steps land in a session file; the profile tool
+    pairs the probes into device ranges and writes a trace."""
+    import json
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.profiling import StepProfiler
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.tools import profile as P
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    eng = LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128, use_graphs=False)
+    eng.profiler = StepProfiler("cpu")
+    path = str(tmp_path / "rank0.sqlite")
+    eng.profiler.open(path, {"model": "tiny"})
+    eng.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    steps = eng.profiler.steps
+    eng.profiler.close()
+    assert steps >= 4 and eng.profiler.counters()["device_seconds"] > 0
+    s = P.load(path)
+    assert len(s["spans"]) == steps and len(s["probes"]) == 2 * steps
+    assert s["meta"]["model"] == "tiny"
+    ranges = P.device_ranges(s["probes"])
+    assert len(ranges) == steps and all(r[4] >= r[3] for r in ranges)
+    out = tmp_path / "trace.json"
+    assert P.main(["trace", path, "-o", str(out)]) == 0
+    tr = json.loads(out.read_text())
+    assert len(tr["traceEvents"]) == 2 * steps
+    assert {e["tid"] for e in tr["traceEvents"]} >= {"device"}

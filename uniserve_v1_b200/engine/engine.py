@@ -73,6 +73,7 @@ class LLMEngine:
         self.watchdog = Watchdog(watchdog_timeout)
         self._ids = itertools.count()
         self.failed: Optional[str] = None
+        self.profiler = None      # engine.profiling.StepProfiler when profiling is on
 
     def _divide_memory(self, fraction, page_size, max_num_seqs, max_model_len) -> int:
         """Quota division: what is left of ``fraction`` of the device after the
@@ -117,7 +118,11 @@ class LLMEngine:
             return []
         self.watchdog.begin(f"{batch.kind} step {batch.step_id}")
         try:
-            sampled, lps = self.runner.execute(batch)
+            if self.profiler is not None:
+                with self.profiler.step(batch.kind, batch.step_id):
+                    sampled, lps = self.runner.execute(batch)
+            else:
+                sampled, lps = self.runner.execute(batch)
         except Exception as e:     # fatal_worker_failure: stop the engine, fail every request
             self.failed = f"{ErrorClass.FATAL_WORKER_FAILURE.value}: {e}"
             raise

@@ -15,7 +15,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import c_char_p, c_float, c_int, c_longlong, c_void_p, c_size_t, POINTER
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_ulonglong, c_void_p, c_size_t, POINTER
 from pathlib import Path
 
 import torch
