@@ -105,3 +105,36 @@ def test_attention_width_differs_from_stream_width():
     st = den.prepare(seed=1, latent_frames=2, lat_h=4, lat_w=4, n_audio=6, text_features=text)
     den.run(st)
     assert torch.isfinite(st.video).all() and torch.isfinite(st.audio).all()
+
+
+def test_sparse_attention_student_reduces_to_dense_when_every_tile_is_kept():
+    """With every video tile kept and a zero compression gate the sparse layer is the
+    dense layer (same weights, 128-row layout unit)."""
+    def run(sparsity):
+        cfg = H3Config.tiny()
+        cfg.vsa_sparsity = sparsity
+        model = H3Transformer(cfg, "cpu", torch.float32).init_random(seed=0)
+        return cfg, model
+    cfg_s, sparse = run(1e-9)
+    cfg_d, dense = run(0.0)
+    D, hl = cfg_s.head_dim, sparse.heads_local
+    for bs, bd in zip(sparse.blocks, dense.blocks):
+        w = bs.qkv.view(4, hl * D, -1)
+        w[3].zero_()                                   # gate projection off
+        bd.qkv = w[:3].reshape(3 * hl * D, -1).clone()
+        bd.to_out, bd.ff1, bd.ff2 = bs.to_out, bs.ff1, bs.ff2
+    dense.proj_in, dense.audio_proj_in = sparse.proj_in, sparse.audio_proj_in
+    dense.context_embedder, dense.refiner = sparse.context_embedder, sparse.refiner
+    dense.proj_out, dense.audio_proj_out = sparse.proj_out, sparse.audio_proj_out
+    dense.time_w1, dense.time_w2 = sparse.time_w1, sparse.time_w2
+    outs = []
+    for m in (sparse, dense):
+        den = Denoiser(m, dmd_ladder((999, 500), 10.0), dmd_ladder((999, 500), 3.0))
+        g = torch.Generator().manual_seed(5)
+        text = torch.randn(9, m.cfg.text_dim, generator=g)
+        st = den.prepare(seed=1, latent_frames=4, lat_h=16, lat_w=16, n_audio=6,
+                         text_features=text)
+        den.run(st)
+        outs.append(st.video)
+    assert st.layout.tile_sizes is None and outs[0].shape == outs[1].shape
+    torch.testing.assert_close(outs[0], outs[1], atol=2e-2, rtol=2e-2)

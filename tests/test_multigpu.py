@@ -137,7 +137,7 @@ def _h3_worker(rank, world, port, q):
     ctx = ParallelContext.from_world(ulysses=world)
     cfg = H3Config.tiny()
     cfg.num_heads = 4
-    cfg.hidden_size = 512
+    cfg.hidden_size = 256      # attention width 4 x 128 = 512 differs from the stream width
     cfg.refiner_heads = 4
     g = torch.Generator().manual_seed(5)
     text = torch.randn(9, cfg.text_dim, generator=g)
@@ -186,7 +186,7 @@ def test_h3_fused_ulysses_matches_all_to_all_and_single_gpu():
     torch.testing.assert_close(af, ab, atol=1e-3, rtol=1e-3)
     cfg = H3Config.tiny()
     cfg.num_heads = 4
-    cfg.hidden_size = 512
+    cfg.hidden_size = 256      # attention width 4 x 128 = 512 differs from the stream width
     cfg.refiner_heads = 4
     model = H3Transformer(cfg, "cuda:0", torch.bfloat16).init_random(seed=0)
     den = Denoiser(model, dmd_ladder((999, 500), 10.0), dmd_ladder((999, 500), 3.0))

@@ -40,6 +40,14 @@ struct FlashArgs {
   int Hq, Hkv, causal;
   float scale_log2;
   unsigned int* status;
+  // Block-sparse form (one sequence of whole 128-row tiles): query tile t of head h
+  // reads key blocks indices[(h * q_tiles + t) * sel + 0 .. counts[h * q_tiles + t]);
+  // rows of key block b at or past valid[b] are not visible.
+  const int* indices;
+  const int* counts;
+  const int* valid;
+  int sel, q_tiles;
+  float* lse;   // [heads, rows] natural-log normaliser, or null
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -48,6 +56,7 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+template <bool SPARSE>
 __global__ void __launch_bounds__(192, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashArgs a) {
@@ -62,13 +71,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int shift = kv_len - q_len;  // causal: key <= query + shift
   int k_limit = kv_len;
   if (a.causal) k_limit = min(kv_len, q0 + kBM + shift);
-  const int nblocks = k_limit > 0 ? (k_limit + kBN - 1) / kBN : 0;
+  int nblocks = k_limit > 0 ? (k_limit + kBN - 1) / kBN : 0;
+  const int* my_blocks = nullptr;
+  if (SPARSE) {
+    nblocks = min(a.counts[h * a.q_tiles + q_tile], a.sel);
+    my_blocks = a.indices + ((long long)h * a.q_tiles + q_tile) * a.sel;
+  }
 
   if (nblocks == 0) {  // no visible key: zeros
     if (tid < kBM && q0 + tid < q_len) {
       uint4* dst = reinterpret_cast<uint4*>(a.out + (long long)(q_start + q0 + tid) * a.ldo +
                                             (long long)h * kD);
       for (int i = 0; i < kD / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+      if (SPARSE && a.lse) a.lse[(long long)h * q_len + q0 + tid] = -INFINITY;
     }
     return;
   }
@@ -128,7 +143,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; j < nblocks; ++j) {
         const int st = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        const int row = k_start + j * kBN;
+        const int row = k_start + (SPARSE ? my_blocks[j] : j) * kBN;
         if (!tc::mbar_wait(&k_empty[st], ph ^ 1u, abort_flag)) {
           us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
           *abort_flag = 1;
@@ -222,6 +237,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // keys of this block this row may see: [0, lim)
       int lim = kv_len - kbase;
       if (a.causal) lim = min(lim, q_idx + shift - kbase + 1);
+      if (SPARSE) lim = a.valid[my_blocks[j]];
       const bool need_mask = lim < kBN;   // per-thread; the loads below stay uniform
       float mx = -INFINITY;
 #pragma unroll 1
@@ -297,6 +313,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc::tc_fence_after_sync();
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
       const bool row_ok = q_idx < q_len;
+      if (SPARSE && a.lse && row_ok)
+        a.lse[(long long)h * q_len + q_idx] =
+            l_sum > 0.f ? (m_used + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
       __nv_bfloat16* orow = a.out + (long long)(q_start + q_idx) * a.ldo + (long long)h * kD;
 #pragma unroll 1
       for (int c = 0; c < kD; c += 32) {
@@ -327,19 +346,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 }  // namespace
 
-// q [Tq, Hq*128] (row stride ldq), k/v [Tk, Hkv*128] (row strides ldk/ldv), out
-// [Tq, Hq*128] (row stride ldo), all bf16; cu_q/cu_k int32 [n_seqs + 1] on the device.
-US_API int us_flash_attn_varlen(const void* q, const void* k, const void* v, void* out,
-                                const int* cu_q, const int* cu_k, int n_seqs, int Tq, int Tk,
-                                int Hq, int Hkv, int D, int max_q, long long ldq, long long ldk,
-                                long long ldv, long long ldo, float scale, int causal,
-                                void* stream_) {
+namespace {
+
+int flash_impl(const void* q, const void* k, const void* v, void* out, const int* cu_q,
+               const int* cu_k, int n_seqs, int Tq, int Tk, int Hq, int Hkv, int D, int max_q,
+               long long ldq, long long ldk, long long ldv, long long ldo, float scale, int causal,
+               const int* indices, const int* counts, const int* valid, int sel, float* lse,
+               cudaStream_t stream) {
   US_REQUIRE(q && k && v && out && cu_q && cu_k && n_seqs >= 1 && Tq >= 1 && Tk >= 1);
   US_REQUIRE(D == kD && Hkv >= 1 && Hq % Hkv == 0 && max_q >= 1);
   US_REQUIRE((ldq % 8) == 0 && (ldk % 8) == 0 && (ldv % 8) == 0 && (ldo % 8) == 0);
   US_REQUIRE(((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0 && ((uintptr_t)v % 16) == 0 &&
              ((uintptr_t)out % 16) == 0);
-  cudaStream_t stream = (cudaStream_t)stream_;
   CUtensorMap tmQ, tmK, tmV;
   int rc = us_tmap_2d(&tmQ, q, US_TMAP_BF16, (uint64_t)Tq, (uint64_t)Hq * D, (uint64_t)ldq, kBM,
                       64, US_SWZ_128);
@@ -360,15 +378,57 @@ US_API int us_flash_attn_varlen(const void* q, const void* k, const void* v, voi
   a.causal = causal;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = us_status_ptr();
+  a.indices = indices;
+  a.counts = counts;
+  a.valid = valid;
+  a.sel = sel;
+  a.q_tiles = (max_q + kBM - 1) / kBM;
+  a.lse = lse;
   const size_t smem = 6 * (size_t)kTile + 16 * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
-    US_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel,
+    US_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel<false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    US_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel<true>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
   dim3 grid((max_q + kBM - 1) / kBM, Hq, n_seqs);
-  us::launch_pdl(flash_fwd_kernel, dim3(grid), dim3(192), smem, stream, tmQ, tmK, tmV, a);
-  US_LAUNCH_CHECK();
+  if (indices)
+    US_CUDA_CHECK(us::launch_pdl(flash_fwd_kernel<true>, grid, dim3(192), smem, stream, tmQ, tmK,
+                                 tmV, a));
+  else
+    US_CUDA_CHECK(us::launch_pdl(flash_fwd_kernel<false>, grid, dim3(192), smem, stream, tmQ, tmK,
+                                 tmV, a));
   return US_OK;
+}
+
+}  // namespace
+
+// q [Tq, Hq*128] (row stride ldq), k/v [Tk, Hkv*128] (row strides ldk/ldv), out
+// [Tq, Hq*128] (row stride ldo), all bf16; cu_q/cu_k int32 [n_seqs + 1] on the device.
+US_API int us_flash_attn_varlen(const void* q, const void* k, const void* v, void* out,
+                                const int* cu_q, const int* cu_k, int n_seqs, int Tq, int Tk,
+                                int Hq, int Hkv, int D, int max_q, long long ldq, long long ldk,
+                                long long ldv, long long ldo, float scale, int causal,
+                                void* stream_) {
+  return flash_impl(q, k, v, out, cu_q, cu_k, n_seqs, Tq, Tk, Hq, Hkv, D, max_q, ldq, ldk, ldv,
+                    ldo, scale, causal, nullptr, nullptr, nullptr, 0, nullptr,
+                    (cudaStream_t)stream_);
+}
+
+// Block-sparse attention over selected 128-row key blocks (video sparse attention):
+// q [Tq, H*128] and k/v [Tk, H*128] in whole 128-row tiles (one sequence; `cu`
+// is the int32 pair [0, Tq] / [0, Tk] on the device), indices [H, Tq/128, sel] global
+// key-block ids, counts [H, Tq/128], valid [Tk/128] visible rows per key block,
+// lse [H, Tq] FP32 (natural log) or null.  A query tile that selects no block writes
+// zeros and an lse of -inf.
+US_API int us_sparse_attn_block128(const void* q, const void* k, const void* v, void* out,
+                                   const int* cu_q, const int* cu_k, int Tq, int Tk, int H,
+                                   long long ldq, long long ldk, long long ldv, long long ldo,
+                                   float scale, const int* indices, const int* counts,
+                                   const int* valid, int sel, float* lse, void* stream_) {
+  US_REQUIRE(indices && counts && valid && sel >= 1 && (Tq % kBM) == 0 && (Tk % kBN) == 0);
+  return flash_impl(q, k, v, out, cu_q, cu_k, 1, Tq, Tk, H, H, kD, Tq, ldq, ldk, ldv, ldo, scale,
+                    0, indices, counts, valid, sel, lse, (cudaStream_t)stream_);
 }

@@ -69,6 +69,9 @@ class H3Config:
     fps: int = 24
     cond_level_visual: float = 0.999
     cond_level_audio: float = 1.0
+    # Video sparse attention (sparse students): fraction of the video key tiles a query
+    # tile does NOT read; 0 = dense attention.  Tiles are 128 rows.
+    vsa_sparsity: float = 0.0
 
     @property
     def patch_width(self) -> int:
@@ -136,6 +139,9 @@ class H3Layout:
     coords: torch.Tensor      # [3, rows] fp32
     mod_index: torch.Tensor   # [rows] int32 = 3 * group + tag
     sp: int = 1
+    tile_sizes: Optional[torch.Tensor] = None      # VSA: valid rows of each 128-row tile
+    tile_segments: Optional[torch.Tensor] = None   # VSA: 0 = video tile, -1 = read by every query
+    tile_keep: Optional[torch.Tensor] = None       # VSA: tiles kept per segment
 
     @property
     def rows_own(self) -> int:
@@ -160,7 +166,8 @@ def build_layout(cfg: H3Config, latent_frames: int, lat_h: int, lat_w: int, n_au
     hp, wp = lat_h // 2, lat_w // 2
     n_video = latent_frames * hp * wp
     used = n_video + n_audio + n_text + n_cond
-    unit = 64 * sp
+    vsa = cfg.vsa_sparsity > 0
+    unit = (128 if vsa else 64) * sp
     rows = (used + unit - 1) // unit * unit
     coords = torch.zeros(3, rows, dtype=torch.float32)
     f = torch.arange(latent_frames, dtype=torch.float32)
@@ -181,8 +188,19 @@ def build_layout(cfg: H3Config, latent_frames: int, lat_h: int, lat_w: int, n_au
     tags[c0:c0 + n_cond] = TAG_VIDEO
     groups[c0:c0 + n_cond] = GROUP_VCOND
     mod = 3 * groups + tags
-    return H3Layout(n_video, n_audio, n_text, n_cond, rows, used, (latent_frames, lat_h, lat_w),
-                    coords.to(device), mod.to(device), sp)
+    lay = H3Layout(n_video, n_audio, n_text, n_cond, rows, used, (latent_frames, lat_h, lat_w),
+                   coords.to(device), mod.to(device), sp)
+    if vsa:
+        tiles = rows // 128
+        t0 = torch.arange(tiles, dtype=torch.int32) * 128
+        sizes = (used - t0).clamp(0, 128).to(torch.int32)
+        seg = torch.where(t0 + 128 <= n_video, 0, -1).to(torch.int32)
+        n_vid_tiles = int((seg == 0).sum())
+        keep = torch.zeros(tiles, dtype=torch.int32)
+        keep[0] = max(1, math.ceil((1.0 - cfg.vsa_sparsity) * n_vid_tiles))
+        lay.tile_sizes, lay.tile_segments, lay.tile_keep = (sizes.to(device), seg.to(device),
+                                                            keep.to(device))
+    return lay
 
 
 # -------------------------------------------------------------------- weights --
@@ -194,6 +212,8 @@ class H3Block:
     to_out: torch.Tensor     # [hidden, heads * head_dim]
     ff1: torch.Tensor        # [2 * ffn, hidden] value rows, then gate rows
     ff2: torch.Tensor        # [hidden, ffn]
+    # With sparse attention ``qkv`` carries a fourth projection per rank
+    # (to_gate_compress): rows [q | k | v | gate] per destination rank.
 
 
 @dataclass
@@ -244,7 +264,9 @@ class H3Transformer:
         for _ in range(cfg.num_layers):
             inner = cfg.num_heads * D     # 56 x 128 = 7168 on a 5376-wide stream
             q, k, v = rnd(inner, H), rnd(inner, H), rnd(inner, H)
-            self.blocks.append(H3Block(self._group_qkv(q, k, v), ones(D), ones(D), rnd(H, inner),
+            gate = rnd(inner, H) if cfg.vsa_sparsity > 0 else None
+            self.blocks.append(H3Block(self._group_qkv(q, k, v, gate), ones(D), ones(D),
+                                       rnd(H, inner),
                                        rnd(2 * Fn, H), rnd(H, Fn)))
         self.proj_out = rnd(cfg.patch_width, H, dtype=torch.float32)
         self.audio_proj_out = rnd(cfg.audio_channels, H, dtype=torch.float32)
@@ -254,14 +276,14 @@ class H3Transformer:
         self._adaln_seed = seed + 1
         return self
 
-    def _group_qkv(self, q, k, v):
-        """Row order [rank 0: q heads, k heads, v heads | rank 1: ... ] so the
-        projection output is already blocked by destination rank."""
+    def _group_qkv(self, q, k, v, gate=None):
+        """Row order [rank 0: q heads, k heads, v heads (, gate heads) | rank 1: ... ] so
+        the projection output is already blocked by destination rank."""
         P, hl, D = self.sp, self.heads_local, self.cfg.head_dim
         parts = []
         for p in range(P):
             sl = slice(p * hl * D, (p + 1) * hl * D)
-            parts += [q[sl], k[sl], v[sl]]
+            parts += [q[sl], k[sl], v[sl]] + ([gate[sl]] if gate is not None else [])
         return torch.cat(parts, 0).contiguous()
 
     def build_level_tables(self, video_sigmas, audio_sigmas) -> None:
@@ -339,8 +361,9 @@ class H3Transformer:
     def _attention(self, blk: H3Block, n: torch.Tensor, layout: H3Layout) -> torch.Tensor:
         cfg = self.cfg
         hl, D, P = self.heads_local, cfg.head_dim, self.sp
-        W = 3 * hl * D
-        if P > 1 and self.ulysses is not None and n.is_cuda:
+        vsa = cfg.vsa_sparsity > 0
+        W = (4 if vsa else 3) * hl * D
+        if P > 1 and self.ulysses is not None and n.is_cuda and not vsa:
             return self.ulysses.attention(self, blk, n, layout)
         qkv = F.linear(n, blk.qkv)                               # [rows_own, P * W]
         if P > 1:
@@ -353,9 +376,18 @@ class H3Transformer:
         q, k, v = full[:, :hl * D], full[:, hl * D:2 * hl * D], full[:, 2 * hl * D:]
         F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, layout.coords, self.inv_freq, hl, hl, D,
                          cfg.rope_freqs_per_axis, cfg.eps)
-        cu_q, cu_k = layout.cu(n.device)
-        att = self._dense_attention(q.view(rows, hl, D), k.view(rows, hl, D), v.view(rows, hl, D),
-                                    cu_q, cu_k, rows, layout.used).reshape(rows, hl * D)
+        if vsa:
+            from ..ops import vsa as V
+            v3 = full[:, 2 * hl * D:3 * hl * D].view(rows, hl, D)
+            g3 = full[:, 3 * hl * D:].view(rows, hl, D)
+            att = V.vsa_attention(q.view(rows, hl, D), k.view(rows, hl, D), v3, g3,
+                                  layout.tile_sizes, layout.tile_segments, layout.tile_keep,
+                                  self.scale).reshape(rows, hl * D)
+        else:
+            cu_q, cu_k = layout.cu(n.device)
+            att = self._dense_attention(q.view(rows, hl, D), k.view(rows, hl, D),
+                                        v.view(rows, hl, D), cu_q, cu_k, rows,
+                                        layout.used).reshape(rows, hl * D)
         if P > 1:
             ro = rows // P
             back = self.ctx.all_to_all(att.view(P, ro, hl * D), "ulysses")   # [P(heads), ro, hl*D]

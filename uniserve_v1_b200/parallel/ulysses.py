@@ -79,5 +79,5 @@ class FusedUlysses:
         out = torch.empty(ro, H, dtype=n.dtype, device=n.device)
         off = self.rank * ro * hl * D * 2
         N.call("us_gemm_wx_pull", N.ptr(blk.to_out), self._ptrs(SITE_ATT, off), P, hl * D,
-               N.ptr(out), H, H, ro, H, hl * D, H, 0, bn, st)
+               N.ptr(out), H, P * hl * D, ro, blk.to_out.stride(0), hl * D, H, 0, bn, st)
         return out
