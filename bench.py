@@ -207,11 +207,28 @@ def fasth3_main(args) -> int:
     launches = native.launch_count - launches0
     value = ms / K * nsteps / 1e3
 
+    phase_ms = None
+    if os.environ.get("BENCH_PROBES", "0") == "1":
+        # one more step with fence probes around every phase of every block (diagnostic:
+        # outside the timed region; the probes are tiny launches of their own)
+        from uniserve_v1_b200.engine.profiling import ProbeRing
+        from uniserve_v1_b200.tools.profile import device_ranges
+        model.probe = ProbeRing(8192, dev)
+        st.step = 0
+        den.step(st)
+        rows = model.probe.collect()
+        model.probe = None
+        agg = {}
+        for _, base, _, t0, t1, _ in device_ranges([(0,) + r for r in rows]):
+            agg[base] = agg.get(base, 0.0) + (t1 - t0) / 1e6
+        phase_ms = {k: round(v, 3) for k, v in sorted(agg.items())}
+
     e2e = None
     if not args.no_e2e:
         plan = VideoPlan("t2va", width, height, frames, 24, 1000, nsteps)
         prompt = "".join(chr(97 + (i * 7) % 26) for i in range(n_text))
         job = VideoJob(prompt, plan)
+        svc.time_phases = os.environ.get("BENCH_PHASES", "0") == "1"
         h0, d0 = svc.h2d_bytes, svc.d2h_bytes
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -224,6 +241,7 @@ def fasth3_main(args) -> int:
         e2e = {"value": e2e_ms / 1e3, "unit": "s", "host_wall_s": round(time.time() - t_host, 3),
                "h2d_bytes_per_step": svc.h2d_bytes - h0, "d2h_bytes_per_step": svc.d2h_bytes - d0,
                "mp4_bytes": len(mp4),
+               "phases_s": {k: round(v, 3) for k, v in job.timings.items()} or None,
                "includes": "prompt features H2D from pinned memory, latent prepare, 8 steps, "
                            "video+audio VAE decode, colour conversion, plane read-back, MP4 mux"}
     if rank == 0:
@@ -247,6 +265,8 @@ def fasth3_main(args) -> int:
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "launches_per_step": launches // max(K, 1), "setup_s": round(setup_s, 1),
         }
+        if phase_ms:
+            line["phase_ms_of_one_step"] = phase_ms
         if args.layers:
             line["profile_only"] = True
         print(json.dumps(line))
@@ -272,7 +292,11 @@ def main() -> int:
                     help="concurrent requests (default 64; per rank in the dp-ep layout; "
                          "128 in total in the afd layout)")
     ap.add_argument("--prompt-len", type=int, default=0)
-    ap.add_argument("--model", default="qwen3-30b-a3b", choices=["qwen3-30b-a3b", "tiny"])
+    ap.add_argument("--model", default="qwen3-30b-a3b",
+                    choices=["qwen3-30b-a3b", "qwen3-235b-a22b", "tiny"])
+    ap.add_argument("--expert-quant", default=None, choices=["fp8_block"],
+                    help="block-scaled FP8 expert weights (128 x 128 blocks); the value is then "
+                         "reported with dtype fp8 experts + bf16 attention")
     ap.add_argument("--layout", default="tp-ep", choices=["tp-ep", "dp-ep", "afd"],
                     help="tp-ep: attention heads split over all ranks, whole experts per rank, "
                          "all-reduce fused into the norms (strong scaling, the default); "
@@ -316,7 +340,8 @@ def main() -> int:
     layout = args.layout if world > 1 else "tp-ep"
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    cfg = Qwen3MoeConfig.qwen3_30b_a3b() if args.model == "qwen3-30b-a3b" else Qwen3MoeConfig(
+    cfg = Qwen3MoeConfig.qwen3_30b_a3b() if args.model == "qwen3-30b-a3b" else \
+        Qwen3MoeConfig.qwen3_235b_a22b() if args.model == "qwen3-235b-a22b" else Qwen3MoeConfig(
         vocab_size=2048, hidden_size=512, num_hidden_layers=2, num_attention_heads=8,
         num_key_value_heads=2, head_dim=128, num_experts=16, num_experts_per_tok=4,
         moe_intermediate_size=256, eos_token_id=2047, max_position_embeddings=8192)
@@ -367,7 +392,8 @@ def main() -> int:
     max_len = prompt_len + total_steps + 16
 
     t0 = time.time()
-    model = Qwen3MoeModel(cfg, dev, torch.bfloat16, ctx).init_random(seed=0)
+    model = Qwen3MoeModel(cfg, dev, torch.bfloat16, ctx,
+                          expert_quant=args.expert_quant).init_random(seed=0)
     model.exchange = exchange
     mark("weights ready")
 
@@ -480,9 +506,11 @@ def main() -> int:
             "metric": "Qwen3-MoE output tokens/s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
             "higher_is_better": True, "scaling": "weak" if layout == "dp-ep" else "strong",
-            "vs_baseline": value / BASELINE_TOK_S, "dtype": "bf16",
+            "vs_baseline": value / BASELINE_TOK_S if args.model == "qwen3-30b-a3b" else None,
+            "dtype": "bf16" if not args.expert_quant else "fp8 (e4m3, 128x128 blocks) experts + bf16 attention",
             "data": "synthetic (uniform-random prompt ids, random-init N(0,0.02) weights)",
-            "config": {"model": "Qwen3-30B-A3B-shaped" if args.model != "tiny" else "tiny",
+            "config": {"model": {"qwen3-30b-a3b": "Qwen3-30B-A3B-shaped",
+                                 "qwen3-235b-a22b": "Qwen3-235B-A22B-shaped"}.get(args.model, "tiny"),
                        "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
                        "experts": cfg.num_experts, "top_k": cfg.num_experts_per_tok,
                        "global_batch": total_c, "seq_len": prompt_len,

@@ -86,3 +86,35 @@ def test_multi_step_decode_matches_single_steps():
     toks, _ = eng.runner.decode(reqs, steps=8)
     for i, r in enumerate(reqs):
         assert r.output_ids + toks[:, i].tolist() == ref[i]
+
+
+def test_fp8_block_experts_stay_close_to_bf16_and_run_under_graphs():
+    """Block-scaled FP8 expert weights: prefill logits near the bf16 model's, and the
+    decode graphs replay what eager computes."""
+    torch.manual_seed(0)
+    bf = Qwen3MoeModel(_cfg(), "cuda", torch.bfloat16).init_random(seed=0)
+    q8 = Qwen3MoeModel(_cfg(), "cuda", torch.bfloat16, expert_quant="fp8_block").init_random(seed=0)
+    assert q8.layers[0].fp8 is not None and q8.layers[0].w13 is None
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, 2048, (48,), generator=g)
+    outs = []
+    for model in (bf, q8):
+        caches = model.new_kv_caches(16, 16)
+        ids = prompt.to("cuda", torch.int32)
+        pos = torch.arange(48, device="cuda", dtype=torch.int32)
+        slots = torch.arange(16, 16 + 48, device="cuda", dtype=torch.int32)
+        cu = torch.tensor([0, 48], device="cuda", dtype=torch.int32)
+        meta = AttnMeta("prefill", slots, cu_q=cu, cu_k=cu, max_q=48, max_k=48, context_lens=[0])
+        outs.append(model.logits(model.forward(ids, pos, meta, caches)).float().cpu())
+    torch.cuda.synchronize()
+    N.raise_on_device_error()
+    err = (outs[0] - outs[1]).abs().max().item()
+    scale = outs[0].abs().max().item()
+    assert err < 0.15 * scale + 0.05, (err, scale)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    prompts = [prompt.tolist()[:20], prompt.tolist()[5:40]]
+    eager = LLMEngine(q8, num_pages=64, max_num_seqs=4, max_model_len=128,
+                      use_graphs=False).generate(prompts, sp)
+    graphs = LLMEngine(q8, num_pages=64, max_num_seqs=4, max_model_len=128,
+                       use_graphs=True).generate(prompts, sp)
+    assert eager == graphs

@@ -75,6 +75,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t* tempty_bar = tfull_bar + 2;       // [2]
   uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* epi_fail = tmem_slot + 2;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -86,6 +87,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA,
       tc::mbar_init(&tempty_bar[b], 128);
     }
     *abort_flag = 0;
+    *epi_fail = 0;
     tc::mbar_fence_init();
   }
   if (warp == 1) {
@@ -202,11 +204,24 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA,
       tc::tc_fence_before_sync();
       tc::mbar_arrive(&tempty_bar[buf]);
     }
-    if (ok) {
-      Epilogue<DUAL> epi(args, group, m_tile * kBlockM + ml, row0);
+    if (!ok) *epi_fail = 1;
+    // All 128 epilogue threads meet here: the decision is uniform, and every
+    // multiplication has completed, so the pipeline stages can stage the stores.
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (*epi_fail == 0) {
+      Epilogue<DUAL> epi(args, group, m_tile * kBlockM, ml, row0);
 #pragma unroll
-      for (int c = 0; c < BN; ++c)
-        if (c < nrows) epi.store(c, acc[c], DUAL ? acc2[DUAL ? c : 0] : 0.f);
+      for (int c = 0; c < BN; c += 16) {
+        if (c < nrows) {  // uniform over the CTA
+          uint32_t v[16], g[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            v[j] = __float_as_uint(acc[c + j]);
+            g[j] = DUAL ? __float_as_uint(acc2[DUAL ? c + j : 0]) : 0u;
+          }
+          epi.store_chunk16(c, c >> 4, v, g, nrows, smem);
+        }
+      }
     }
   }
   tc::tc_fence_before_sync();
@@ -317,17 +332,24 @@ absmax_kernel(const __nv_bfloat16* __restrict__ x, long long n, float* __restric
 
 }  // namespace
 
-// Wq: [G, w_rows, K] e4m3 bytes (ldw bytes between rows), w_scale [G, w_rows / 128, K / 128];
-// Xq: [x_rows, K] e4m3 with ldx, x_scale [K / 128, xs_ld] (transposed).  Remaining
-// arguments as us_gemm_wx (bf16 or fp32 output, dense when num_tiles is null).
-US_API int us_gemm_fp8_block(const void* Wq, const float* w_scale, const void* Xq,
-                             const float* x_scale, long long xs_ld, void* out, int G, int w_rows,
-                             int M, int K, int x_rows, long long ldw, long long ldx, long long ldo,
-                             int dual, int dual_offset, int act, int out_dtype,
-                             const float* row_scale, const int* out_row_map, const int* tile_group,
-                             const int* tile_row0, const int* tile_rows, const int* num_tiles,
-                             int max_tiles, int block_n, void* stream_) {
-  US_REQUIRE(Wq && w_scale && Xq && x_scale && out && G >= 1 && M >= 1 && K >= 128 &&
+namespace {
+
+struct RouteSpec {
+  void* const* recv_peers = nullptr;
+  int n_peers = 0;
+  const int* route_map = nullptr;
+  const float* route_w = nullptr;
+  int route_per = 0;
+};
+
+int fp8_impl(const void* Wq, const float* w_scale, const void* Xq, const float* x_scale,
+             long long xs_ld, void* out, int G, int w_rows, int M, int K, int x_rows,
+             long long ldw, long long ldx, long long ldo, int dual, int dual_offset, int act,
+             int out_dtype, const float* row_scale, const int* out_row_map, const int* tile_group,
+             const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles,
+             int block_n, const RouteSpec& rs, void* stream_) {
+  US_REQUIRE(Wq && w_scale && Xq && x_scale && (out || rs.route_map) && G >= 1 && M >= 1 &&
+             K >= 128 &&
              (K % 128) == 0 && (w_rows % 128) == 0);
   US_REQUIRE((ldw % 16) == 0 && (ldx % 16) == 0 && ((uintptr_t)Wq % 16) == 0 &&
              ((uintptr_t)Xq % 16) == 0 );
@@ -357,6 +379,24 @@ US_API int us_gemm_fp8_block(const void* Wq, const float* w_scale, const void* X
   a.peer_cols = 0; a.peer_row_offset = 0; a.rows_per_peer = 0; a.peer_rows = 0; a.peer_slot = 0;
   for (int p = 0; p < 8; ++p) a.peer_out[p] = nullptr;
   a.route_map = nullptr; a.route_w = nullptr; a.route_per = 0;
+  a.vec_store = 0;
+  if (rs.route_map) {
+    US_REQUIRE(rs.recv_peers && rs.route_w && rs.route_per > 0 && rs.n_peers >= 1 &&
+               rs.n_peers <= 8 && out_dtype == 0 && !dual);
+    a.route_map = rs.route_map;
+    a.route_w = rs.route_w;
+    a.route_per = rs.route_per;
+    for (int p = 0; p < rs.n_peers; ++p) {
+      US_REQUIRE(rs.recv_peers[p] != nullptr);
+      a.peer_out[p] = rs.recv_peers[p];
+    }
+  }
+  {
+    const long long esz = out_dtype == 0 ? 2 : 4;
+    bool okv = ((ldo * esz) % 16) == 0 && ((uintptr_t)out % 16) == 0;
+    for (int p = 0; p < 8; ++p) okv = okv && ((uintptr_t)a.peer_out[p] % 16) == 0;
+    a.vec_store = okv ? 1 : 0;
+  }
   fa.w_scale = w_scale;
   fa.x_scale = x_scale;
   fa.xs_ld = xs_ld;
@@ -377,6 +417,46 @@ US_API int us_gemm_fp8_block(const void* Wq, const float* w_scale, const void* X
       return US_ERR_ARG;
   }
 #undef US_FP8_CASE
+}
+
+}  // namespace
+
+// Wq: [G, w_rows, K] e4m3 bytes (ldw bytes between rows), w_scale [G, w_rows / 128, K / 128];
+// Xq: [x_rows, K] e4m3 with ldx, x_scale [K / 128, xs_ld] (transposed).  Remaining
+// arguments as us_gemm_wx (bf16 or fp32 output, dense when num_tiles is null).
+US_API int us_gemm_fp8_block(const void* Wq, const float* w_scale, const void* Xq,
+                             const float* x_scale, long long xs_ld, void* out, int G, int w_rows,
+                             int M, int K, int x_rows, long long ldw, long long ldx, long long ldo,
+                             int dual, int dual_offset, int act, int out_dtype,
+                             const float* row_scale, const int* out_row_map, const int* tile_group,
+                             const int* tile_row0, const int* tile_rows, const int* num_tiles,
+                             int max_tiles, int block_n, void* stream_) {
+  RouteSpec rs;
+  return fp8_impl(Wq, w_scale, Xq, x_scale, xs_ld, out, G, w_rows, M, K, x_rows, ldw, ldx, ldo,
+                  dual, dual_offset, act, out_dtype, row_scale, out_row_map, tile_group, tile_row0,
+                  tile_rows, num_tiles, max_tiles, block_n, rs, stream_);
+}
+
+// Grouped FC2 of an expert-parallel layer with block-scaled FP8 weights: the epilogue
+// applies the gate weight and stores every output row into the combine buffer of the
+// rank that owns the token (same routing arguments as us_gemm_wx_route_push).
+US_API int us_gemm_fp8_block_route_push(const void* Wq, const float* w_scale, const void* Xq,
+                                        const float* x_scale, long long xs_ld, int G, int M, int K,
+                                        int x_rows, long long ldw, long long ldx, long long ldo,
+                                        void* const* recv_peers, int n_peers, const int* route_map,
+                                        const float* route_w, int route_per, const int* tile_group,
+                                        const int* tile_row0, const int* tile_rows,
+                                        const int* num_tiles, int max_tiles, int block_n,
+                                        void* stream_) {
+  RouteSpec rs;
+  rs.recv_peers = recv_peers;
+  rs.n_peers = n_peers;
+  rs.route_map = route_map;
+  rs.route_w = route_w;
+  rs.route_per = route_per;
+  return fp8_impl(Wq, w_scale, Xq, x_scale, xs_ld, nullptr, G, M, M, K, x_rows, ldw, ldx, ldo, 0,
+                  0, 0, 0, nullptr, nullptr, tile_group, tile_row0, tile_rows, num_tiles,
+                  max_tiles, block_n, rs, stream_);
 }
 
 // x [rows, K] bf16 -> q [rows, K] e4m3 + scales [K / 128, xs_ld].  `live_rows`

@@ -53,6 +53,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* acc_bar = empty_bar + stages;
   uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* epi_fail = tmem_slot + 2;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -61,6 +62,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     tc::mbar_init(acc_bar, 1);
     *abort_flag = 0;
+    *epi_fail = 0;
     tc::mbar_fence_init();
   }
   if (warp == 1) {
@@ -139,7 +141,14 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int ml = q * 32 + lane;
-    if (tc::mbar_wait(acc_bar, 0, abort_flag)) {
+    if (!tc::mbar_wait(acc_bar, 0, abort_flag)) {
+      us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
+      *epi_fail = 1;
+    }
+    // All 128 epilogue threads meet here, so the decision below is uniform and the
+    // staged stores' barriers cannot be left waiting.
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (*epi_fail == 0) {
       tc::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
       if (!DUAL && args.splits > 1) {
@@ -156,22 +165,19 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < 16; ++j) part[(c + j) * kBlockM + ml] = __uint_as_float(v[j]);
         }
       } else {
-        Epilogue<DUAL> epi(args, group, m_tile * kBlockM + ml, row0);
+        // The pipeline stages are idle: their first 16 KiB stage the stores.
+        Epilogue<DUAL> epi(args, group, m_tile * kBlockM, ml, row0);
+        int chunk = 0;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
-          if (c >= nrows) break;  // warp-uniform
+        for (int c = 0; c < BN; c += 16, ++chunk) {
+          if (c >= nrows) break;  // uniform over the CTA
           uint32_t v[16], g[16];
           tc::tmem_ld16(taddr + c, v);
           if (DUAL) tc::tmem_ld16(taddr + BN + c, g);
           tc::tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c + j < nrows)
-              epi.store(c + j, __uint_as_float(v[j]), DUAL ? __uint_as_float(g[j]) : 0.f);
+          epi.store_chunk16(c, chunk, v, g, nrows, smem);
         }
       }
-    } else {
-      us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
     }
   }
   if (!DUAL && args.splits > 1) {
@@ -184,7 +190,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int q = warp & 3;
       const int ml = q * 32 + lane;
       const uint32_t my_rank = tc::cluster_ctarank();
-      Epilogue<false> epi(args, group, m_tile * kBlockM + ml, row0);
+      Epilogue<false> epi(args, group, m_tile * kBlockM, ml, row0);
       const uint32_t local = tc::smem_u32(smem) + (uint32_t)ml * 4u;
       for (int r = (int)my_rank; r < nrows; r += args.splits) {
         float acc = 0.f;
@@ -235,6 +241,8 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t* acc_empty = acc_full + 2;        // [2]
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* epi_fail = tmem_slot + 2;
+  uint8_t* epi_stage = smem + (size_t)stages * kStageBytes + 1024;   // after the barrier words
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -246,6 +254,7 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
       tc::mbar_init(&acc_empty[b], 128);
     }
     *abort_flag = 0;
+    *epi_fail = 0;
     tc::mbar_fence_init();
   }
   if (warp == 1) {
@@ -345,23 +354,25 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
       const int nrows = min(BN, args.rows - row0);
       if (!tc::mbar_wait(&acc_full[buf], (uint32_t)(it >> 1) & 1u, abort_flag)) {
         us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
-        break;
+        *epi_fail = 1;
       }
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // uniform decision, see above
+      if (*epi_fail != 0) break;
       tc::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)buf * kAccCols + ((uint32_t)(q * 32) << 16);
-      Epilogue<DUAL> epi(args, 0, m_tile * kBlockM + ml, row0);
+      Epilogue<DUAL> epi(args, 0, m_tile * kBlockM, ml, row0);
+      int chunk = 0;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        if (c >= nrows) break;  // warp-uniform
+      for (int c = 0; c < BN; c += 16, ++chunk) {
+        if (c >= nrows) break;  // uniform over the CTA
         uint32_t v[16], g[16];
         tc::tmem_ld16(taddr + c, v);
         if (DUAL) tc::tmem_ld16(taddr + BN + c, g);
         tc::tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (c + j < nrows)
-            epi.store(c + j, __uint_as_float(v[j]), DUAL ? __uint_as_float(g[j]) : 0.f);
+        epi.store_chunk16(c, chunk, v, g, nrows, epi_stage);
       }
+      // the staging halves are reused by the next tile: every read must be done
+      asm volatile("bar.sync 1, 128;" ::: "memory");
       tc::tc_fence_before_sync();
       tc::mbar_arrive(&acc_empty[buf]);
     }
@@ -379,11 +390,11 @@ int launch_persist(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int til
                    cudaStream_t stream) {
   constexpr int kBTile = BN * kBlockK * 2;
   constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
-  int stages = (200 * 1024) / kStageBytes;
+  int stages = (192 * 1024) / kStageBytes;
   if (stages > 8) stages = 8;
   a.stages = stages;
   a.splits = 1;
-  const size_t smem = (size_t)stages * kStageBytes + (2 * stages + 4) * 8 + 16 + 1024;
+  const size_t smem = (size_t)stages * kStageBytes + 1024 + kEpiStageBytes + 1024;
   static bool configured = false;
   static int sms = 0;
   if (!configured) {
@@ -579,6 +590,12 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
     }
   }
 
+  {
+    const long long esz = out_dtype == 0 ? 2 : 4;
+    bool ok = ((ldo * esz) % 16) == 0 && ((uintptr_t)out % 16) == 0;
+    for (int p = 0; p < 8; ++p) ok = ok && ((uintptr_t)a.peer_out[p] % 16) == 0;
+    a.vec_store = ok ? 1 : 0;
+  }
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
   const int n_tiles = num_tiles ? max_tiles : (x_rows + block_n - 1) / block_n;
   US_REQUIRE(n_tiles <= 65535);

@@ -47,6 +47,9 @@ struct GemmArgs {
   int rows_per_peer;
   int peer_rows;
   int peer_slot;
+  // 1 when every destination row starts on a 16-byte boundary (base pointers and
+  // row pitch): the epilogue then stores 16-byte pieces through a staging tile.
+  int vec_store;
   // Route push (expert-parallel combine): permuted row r carries route
   // i = route_map[r] = (source rank * route_per + token * top_k + slot); the epilogue
   // multiplies by the gate weight route_w[i] and stores the row into the source
@@ -78,44 +81,48 @@ constexpr int tmem_cols(bool dual) {
   return c;
 }
 
-// Per-thread epilogue of one output feature `m`: activation, bias, row scale,
-// row map, rounding.  The destination of row 0 of the tile is resolved once
-// (which buffer, which rank); rows then advance by a fixed stride unless a row
-// map or a route map redirects them one by one.
+constexpr int kEpiStageBytes = 16 * 1024;   // two staging tiles of 16 rows x 128 features x 4 B
+
+// Epilogue of one 128-feature tile, run by the four epilogue warps (thread `ml`
+// owns feature m0 + ml, i.e. TMEM lane ml).  Values get their activation, bias and
+// scales in registers; stores go through a shared staging tile, 16 rows at a time,
+// so that every row leaves as contiguous 16-byte pieces (256 B per row for bf16)
+// whatever the destination: the plain output, a row-mapped output, a peer's buffer
+// (scatter by feature, reduce-scatter by row) or the token owner's combine buffer.
 template <bool DUAL>
 struct Epilogue {
   const GemmArgs& a;
-  const int m, row0;
+  const int m0, ml, m, row0;
   const bool m_ok;
   float bias;
-  char* base;          // element (row0, m) of the destination; null = per-row lookup
+  char* tile_base;     // element (row0, m0) of the destination; null = per-row lookup
   long long row_bytes;
-  __device__ __forceinline__ Epilogue(const GemmArgs& args, int group, int m_, int row0_)
-      : a(args), m(m_), row0(row0_), m_ok(m_ < args.M), bias(0.f), base(nullptr), row_bytes(0) {
-    if (!m_ok) return;
-    if (a.bias != nullptr) {
+  int esz;
+  __device__ __forceinline__ Epilogue(const GemmArgs& args, int group, int m0_, int ml_, int row0_)
+      : a(args), m0(m0_), ml(ml_), m(m0_ + ml_), row0(row0_), m_ok(m0_ + ml_ < args.M), bias(0.f),
+        tile_base(nullptr), row_bytes(0), esz(args.out_dtype == 0 ? 2 : 4) {
+    if (a.bias != nullptr && m_ok) {
       const size_t bi = (size_t)group * a.M + m;
       bias = a.bias_dtype == 0 ? us::bf2f(((const __nv_bfloat16*)a.bias)[bi])
                                : ((const float*)a.bias)[bi];
     }
-    const int esz = a.out_dtype == 0 ? 2 : 4;
     row_bytes = a.ldo * esz;
     if (a.route_map != nullptr || a.out_row_map != nullptr) return;
     if (a.peer_rows > 0) {   // a tile lies inside one owner's interval
       const int p = row0 / a.peer_rows;
-      base = (char*)a.peer_out[p] +
-             (((size_t)a.peer_slot * a.peer_rows + (size_t)(row0 - p * a.peer_rows)) * a.ldo + m) *
-                 esz;
+      tile_base = (char*)a.peer_out[p] +
+                  (((size_t)a.peer_slot * a.peer_rows + (size_t)(row0 - p * a.peer_rows)) * a.ldo +
+                   m0) * esz;
     } else if (a.peer_cols > 0) {
-      const int p = m / a.peer_cols;
-      base = (char*)a.peer_out[p] +
-             ((size_t)(a.peer_row_offset + row0) * a.ldo + (m - p * a.peer_cols)) * esz;
+      const int p = m0 / a.peer_cols;
+      tile_base = (char*)a.peer_out[p] +
+                  ((size_t)(a.peer_row_offset + row0) * a.ldo + (m0 - p * a.peer_cols)) * esz;
     } else {
-      base = (char*)a.out + ((size_t)row0 * a.ldo + m) * esz;
+      tile_base = (char*)a.out + ((size_t)row0 * a.ldo + m0) * esz;
     }
   }
-  __device__ __forceinline__ void store(int r, float val, float gate) const {
-    if (!m_ok) return;
+  // Value of tile row r for this thread's feature (everything but the store).
+  __device__ __forceinline__ float value(int r, float val, float gate) const {
     if (DUAL) {
       if (a.act == 0) {
         val = val * silu_f(gate);
@@ -127,30 +134,81 @@ struct Epilogue {
       }
     }
     val += bias;
-    int orow = row0 + r;
+    if (a.route_map != nullptr) return val * a.route_w[a.route_map[row0 + r]];
+    if (a.row_scale != nullptr) val *= a.row_scale[row0 + r];
+    return val;
+  }
+  // Destination of tile row r, feature m0 (null = the row is dropped).
+  __device__ __forceinline__ char* row_ptr(int r) const {
+    if (tile_base != nullptr) return tile_base + (long long)r * row_bytes;
     if (a.route_map != nullptr) {
-      const int i = a.route_map[orow];
+      const int i = a.route_map[row0 + r];
       const int src = i / a.route_per;
       const int dst = i - src * a.route_per;
-      ((__nv_bfloat16*)a.peer_out[src])[(size_t)dst * a.ldo + m] = us::f2bf(val * a.route_w[i]);
-      return;
+      return (char*)a.peer_out[src] + ((size_t)dst * a.ldo + m0) * 2;
     }
-    if (a.row_scale != nullptr) val *= a.row_scale[orow];
-    if (base != nullptr) {
-      char* dst = base + (long long)r * row_bytes;
-      if (a.out_dtype == 0)
-        *(__nv_bfloat16*)dst = us::f2bf(val);
-      else
-        *(float*)dst = val;
-      return;
-    }
-    orow = a.out_row_map[orow];
-    if (orow < 0) return;
-    const size_t o = (size_t)orow * a.ldo + m;
+    const int orow = a.out_row_map[row0 + r];
+    if (orow < 0) return nullptr;
+    return (char*)a.out + ((size_t)orow * a.ldo + m0) * esz;
+  }
+  // Scalar store of one element (split-K reduction, unaligned destinations).
+  __device__ __forceinline__ void store(int r, float val, float gate) const {
+    if (!m_ok) return;
+    char* dst = row_ptr(r);
+    if (dst == nullptr) return;
+    const float x = value(r, val, gate);
     if (a.out_dtype == 0)
-      ((__nv_bfloat16*)a.out)[o] = us::f2bf(val);
+      ((__nv_bfloat16*)dst)[ml] = us::f2bf(x);
     else
-      ((float*)a.out)[o] = val;
+      ((float*)dst)[ml] = x;
+  }
+  // Rows [c, c + 16) of the tile, called by all 128 epilogue threads together.
+  // `stage` is kEpiStageBytes of shared memory; chunks alternate its halves, so
+  // one named barrier per chunk orders writers and readers.
+  __device__ __forceinline__ void store_chunk16(int c, int chunk, const uint32_t (&v)[16],
+                                                const uint32_t (&g)[16], int nrows,
+                                                uint8_t* stage) const {
+    if (!a.vec_store) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (c + j < nrows) store(c + j, __uint_as_float(v[j]), DUAL ? __uint_as_float(g[j]) : 0.f);
+      return;
+    }
+    uint8_t* buf = stage + (chunk & 1) * (kEpiStageBytes / 2);
+    const int pitch = 128 * esz;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float x = (c + j < nrows)
+                          ? value(c + j, __uint_as_float(v[j]), DUAL ? __uint_as_float(g[j]) : 0.f)
+                          : 0.f;
+      if (esz == 2)
+        *reinterpret_cast<__nv_bfloat16*>(buf + j * pitch + ml * 2) = us::f2bf(x);
+      else
+        *reinterpret_cast<float*>(buf + j * pitch + ml * 4) = x;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const int per_row = pitch / 16;                 // 16-byte pieces per row: 16 or 32
+    const int feats = 16 / esz;                     // features per piece: 8 or 4
+    for (int id = ml; id < 16 * per_row; id += 128) {
+      const int r = id / per_row, seg = id - r * per_row;
+      if (c + r >= nrows) continue;
+      char* dst = row_ptr(c + r);
+      if (dst == nullptr) continue;
+      const int f0 = m0 + seg * feats;
+      if (f0 + feats <= a.M) {
+        *reinterpret_cast<uint4*>(dst + seg * 16) =
+            *reinterpret_cast<const uint4*>(buf + r * pitch + seg * 16);
+      } else {
+        for (int f = 0; f0 + f < a.M && f < feats; ++f) {
+          if (esz == 2)
+            ((__nv_bfloat16*)dst)[seg * feats + f] =
+                *reinterpret_cast<const __nv_bfloat16*>(buf + r * pitch + (seg * feats + f) * 2);
+          else
+            ((float*)dst)[seg * feats + f] =
+                *reinterpret_cast<const float*>(buf + r * pitch + (seg * feats + f) * 4);
+        }
+      }
+    }
   }
 };
 

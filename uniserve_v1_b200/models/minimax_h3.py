@@ -242,6 +242,7 @@ class H3Transformer:
         self.tables: list = []        # per level: [layers] of [12 * 6, hidden] fp32
         self.tables_out: list = []    # per level: [12 * 2, hidden] fp32
         self.ulysses = None           # parallel.ulysses.FusedUlysses when a peer heap is attached
+        self.probe = None             # engine.profiling.ProbeRing: per-phase fence probes
 
     # --------------------------------------------------------------- weights --
     def init_random(self, seed: int = 0, std: float = 0.02) -> "H3Transformer":
@@ -358,6 +359,22 @@ class H3Transformer:
         return x[lo:hi].to(self.dtype).contiguous()
 
     # ----------------------------------------------------------------- forward --
+    def _range(self, name: str, tag: int = 0):
+        """Fence-probe range around a phase of a block (no-op without a probe ring)."""
+        import contextlib
+        if self.probe is None:
+            return contextlib.nullcontext()
+        probe = self.probe
+
+        @contextlib.contextmanager
+        def rng():
+            probe.mark(name + ".begin", tag)
+            try:
+                yield
+            finally:
+                probe.mark(name + ".end", tag)
+        return rng()
+
     def _attention(self, blk: H3Block, n: torch.Tensor, layout: H3Layout) -> torch.Tensor:
         cfg = self.cfg
         hl, D, P = self.heads_local, cfg.head_dim, self.sp
@@ -403,12 +420,21 @@ class H3Transformer:
         idx = layout.mod_index[lo:hi].contiguous()
         for b, blk in enumerate(self.blocks):
             table = self.tables[level][b]
-            n = F.modulated_rmsnorm(h, None, table, idx, 6, SLOT_SHIFT_A, SLOT_SCALE_A, cfg.eps)
-            u = self._attention(blk, n, layout)
-            F.gated_residual_(h, u, table, idx, 6, SLOT_GATE_A)
-            n2 = F.modulated_rmsnorm(h, None, table, idx, 6, SLOT_SHIFT_M, SLOT_SCALE_M, cfg.eps)
-            ff = F.linear(F.linear_gated(n2, blk.ff1, stepwise=True), blk.ff2)
-            F.gated_residual_(h, ff, table, idx, 6, SLOT_GATE_M)
+            with self._range("norm_a", b):
+                n = F.modulated_rmsnorm(h, None, table, idx, 6, SLOT_SHIFT_A, SLOT_SCALE_A,
+                                        cfg.eps)
+            with self._range("attention", b):
+                u = self._attention(blk, n, layout)
+            with self._range("gate_norm_m", b):
+                F.gated_residual_(h, u, table, idx, 6, SLOT_GATE_A)
+                n2 = F.modulated_rmsnorm(h, None, table, idx, 6, SLOT_SHIFT_M, SLOT_SCALE_M,
+                                         cfg.eps)
+            with self._range("ff1", b):
+                hid = F.linear_gated(n2, blk.ff1, stepwise=True)
+            with self._range("ff2", b):
+                ff = F.linear(hid, blk.ff2)
+            with self._range("gate_m", b):
+                F.gated_residual_(h, ff, table, idx, 6, SLOT_GATE_M)
         out = F.modulated_rmsnorm(h, None, self.tables_out[level], idx, 2, 0, 1, cfg.eps).float()
         v_lo, v_hi = max(lo, 0), min(hi, layout.n_video)
         a_lo, a_hi = max(lo, layout.n_video), min(hi, layout.n_video + layout.n_audio)

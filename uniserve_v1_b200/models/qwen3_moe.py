@@ -106,6 +106,7 @@ class LayerWeights:
     router: Optional[torch.Tensor] = None   # [E, H]
     w13: Optional[torch.Tensor] = None      # [E_l, 2I, H] (or [1, 2I_l, H] dense MLP)
     w2: Optional[torch.Tensor] = None       # [E_l, H, I]
+    fp8: Optional[object] = None            # ops.fp8.Fp8Experts replacing w13 / w2
     dense: bool = False
 
 
@@ -129,10 +130,12 @@ class AttnMeta:
 
 class Qwen3MoeModel:
     def __init__(self, cfg: Qwen3MoeConfig, device="cpu", dtype=torch.bfloat16,
-                 ctx: Optional[ParallelContext] = None):
+                 ctx: Optional[ParallelContext] = None, expert_quant: Optional[str] = None):
         self.cfg = cfg
         self.device = torch.device(device)
         self.dtype = dtype
+        assert expert_quant in (None, "fp8_block")
+        self.expert_quant = expert_quant
         self.ctx = ctx or ParallelContext.single()
         tp = self.ctx.tp_size
         self.Hq = cfg.num_attention_heads // tp
@@ -204,6 +207,7 @@ class Qwen3MoeModel:
                         w13[e - self.e_lo, I:] = gate
                         w2[e - self.e_lo] = down
                 lw.w13, lw.w2 = w13, w2
+                self._quantize_experts(lw)
             else:
                 I = cfg.intermediate_size
                 gate, up, down = rnd(I, H), rnd(I, H), rnd(H, I)
@@ -272,6 +276,7 @@ class Qwen3MoeModel:
                     w13[e - self.e_lo, I:] = get(pe + "gate_proj.weight")
                     w2[e - self.e_lo] = get(pe + "down_proj.weight")
                 lw.w13, lw.w2 = w13, w2
+                self._quantize_experts(lw)
             else:
                 gate, up, down = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
                 Il = gate.shape[0] // tp
@@ -333,6 +338,15 @@ class Qwen3MoeModel:
             out = self.ctx.all_reduce_tp(out)
         return out, site
 
+    def _quantize_experts(self, lw: LayerWeights) -> None:
+        """``expert_quant == "fp8_block"``: the stacked expert weights are replaced by
+        E4M3 bytes with one FP32 scale per 128 x 128 block."""
+        if self.expert_quant != "fp8_block" or lw.w13 is None or lw.w13.shape[0] == 0:
+            return
+        from ..ops.fp8 import Fp8Experts
+        lw.fp8 = Fp8Experts.from_bf16(lw.w13, lw.w2)
+        lw.w13 = lw.w2 = None
+
     def _mlp(self, fc, lw: LayerWeights, x):
         cfg = self.cfg
         T = x.shape[0]
@@ -350,7 +364,10 @@ class Qwen3MoeModel:
                                           live=live)
             self.exchange.dispatch(x, ids, weights, live)
             if self.exchange.is_expert:
-                self.exchange.experts(lw.w13, lw.w2, T)
+                if lw.fp8 is not None:
+                    self.exchange.experts_fp8(lw.fp8, T)
+                else:
+                    self.exchange.experts(lw.w13, lw.w2, T)
             return x, ("ep", ids)
         ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
         ws = None
@@ -363,7 +380,15 @@ class Qwen3MoeModel:
                 self._moe_ws[key] = ws
         reduce = self.ctx.ep_size > 1
         site, buf = self._partial_out(fc if reduce else None, T)
-        out = F.moe_experts(x, ids, weights, lw.w13, lw.w2, e_lo=self.e_lo, ws=ws, out=buf)
+        if lw.fp8 is not None:
+            from ..ops.fp8 import moe_experts_fp8
+            if ws is not None and ws.block_n > 64:
+                ws = self._moe_ws[key] = F.MoeWorkspace.create(
+                    T, cfg.num_experts_per_tok, self.E_local, cfg.hidden_size,
+                    cfg.moe_intermediate_size, x.device, block_n=64)
+            out = moe_experts_fp8(x, ids, weights, lw.fp8, e_lo=self.e_lo, ws=ws, out=buf)
+        else:
+            out = F.moe_experts(x, ids, weights, lw.w13, lw.w2, e_lo=self.e_lo, ws=ws, out=buf)
         if reduce and site is None:
             out = self.ctx.all_reduce_tp(out)
         return out, site
@@ -390,7 +415,11 @@ class Qwen3MoeModel:
         """An expert rank of the disaggregated layout: every forward is the join - per
         layer it waits for the attention ranks' rows, runs its experts and pushes back."""
         for lw in self.layers:
-            if not lw.dense:
+            if lw.dense:
+                continue
+            if lw.fp8 is not None:
+                self.exchange.experts_fp8(lw.fp8, t_step)
+            else:
                 self.exchange.experts(lw.w13, lw.w2, t_step)
 
     def logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:

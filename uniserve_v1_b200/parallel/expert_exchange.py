@@ -33,6 +33,9 @@ N.register_signatures({
     "us_ep_wait": (N.I, [N.I, N.I, N.I, N.P]),
     "us_ep_signal_combined": (N.I, [N.I, N.I, N.P]),
     "us_ep_combine_add_rmsnorm": (N.I, [N.P, N.P, N.P, N.P, N.P, N.I, N.F, N.I, N.I, N.P]),
+    "us_gemm_fp8_block_route_push": (N.I, [N.P, N.P, N.P, N.P, N.L, N.I, N.I, N.I, N.I, N.L, N.L,
+                                           N.L, N.P, N.I, N.P, N.P, N.I, N.P, N.P, N.P, N.P, N.I,
+                                           N.I, N.P]),
     "us_gemm_wx_route_push": (N.I, [N.P, N.P, N.I, N.I, N.I, N.I, N.L, N.L, N.L, N.P, N.I, N.P,
                                     N.P, N.I, N.P, N.P, N.P, N.P, N.I, N.I, N.P]),
 })
@@ -134,4 +137,44 @@ class ExpertExchange:
                self.recv_ptrs, self.world, N.ptr(ws.sorted_route), N.ptr(self.win_w),
                t_step * self.k, N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
                N.ptr(ws.num_tiles), ws.max_tiles, ws.block_n, st)
+        N.call("us_ep_signal_combined", self.source_ranks[0], self.source_ranks[-1] + 1, st)
+
+    def experts_fp8(self, ex, t_step: int, act: str = "silu") -> None:
+        """``experts`` with block-scaled FP8 weights (``ops.fp8.Fp8Experts``): the rows
+        that arrived are quantised per row and 128-wide K block before each grouped
+        GEMM; FC2's epilogue pushes the weighted rows to the token owners."""
+        from ..ops import fp8 as Q
+        ws, st = self.workspace(t_step), N.stream()
+        if ws.block_n > 64:
+            ws = self._ws[t_step] = F.MoeWorkspace.create(
+                self.world * t_step, self.k, self.experts_per_rank, self.H, self.I, self.device,
+                block_n=64)
+        E, I2, H = ex.w13.shape
+        I_ = I2 // 2
+        R = self.world * t_step * self.k
+        q8 = getattr(ws, "_fp8", None)
+        if q8 is None:
+            z = lambda r, c: torch.zeros(r + Q.PAD_ROWS, c, dtype=torch.uint8,
+                                         device=self.device)[:r]
+            o = lambda kb, r: torch.ones(kb, r + Q.PAD_ROWS, dtype=torch.float32,
+                                         device=self.device)
+            q8 = ws._fp8 = dict(xq=z(R, H), xs=o(H // 128, R), hq=z(R, I_), hs=o(I_ // 128, R))
+        N.call("us_ep_wait", 0, self.source_ranks[0], self.source_ranks[-1] + 1, st)
+        N.call("us_moe_sort", N.ptr(self.win_ids), R, self.e_lo, E, ws.block_n, ws.max_tiles,
+               N.ptr(ws.sorted_route), N.ptr(ws.perm_of_route), N.ptr(ws.expert_offsets),
+               N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
+               N.ptr(ws.num_tiles), st)
+        total = ws.expert_offsets[E:]
+        N.call("us_moe_gather", N.ptr(self.win_x), N.ptr(ws.sorted_route), N.ptr(total), R, self.k,
+               H, N.ptr(ws.xp), st)
+        Q.quantize_rows_block128(ws.xp, total, q8["xq"], q8["xs"])
+        tiles = (N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
+                 N.ptr(ws.num_tiles), ws.max_tiles, ws.block_n)
+        N.call("us_gemm_fp8_block", N.ptr(ex.w13), N.ptr(ex.w13_scale), N.ptr(q8["xq"]),
+               N.ptr(q8["xs"]), q8["xs"].stride(0), N.ptr(ws.h), E, I2, I_, H, R, H, H, I_, 1, I_,
+               F._ACT[act], 0, None, None, *tiles, st)
+        Q.quantize_rows_block128(ws.h, total, q8["hq"], q8["hs"])
+        N.call("us_gemm_fp8_block_route_push", N.ptr(ex.w2), N.ptr(ex.w2_scale), N.ptr(q8["hq"]),
+               N.ptr(q8["hs"]), q8["hs"].stride(0), E, H, I_, R, I_, I_, H, self.recv_ptrs,
+               self.world, N.ptr(ws.sorted_route), N.ptr(self.win_w), t_step * self.k, *tiles, st)
         N.call("us_ep_signal_combined", self.source_ranks[0], self.source_ranks[-1] + 1, st)

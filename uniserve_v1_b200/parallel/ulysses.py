@@ -63,21 +63,27 @@ class FusedUlysses:
         st = N.stream()
         bn = F._block_n(ro, False)
         # rows -> heads: projection tiles land in the owners' buffers
-        N.call("us_gemm_wx_scatter", N.ptr(blk.qkv), N.ptr(n), P * W, H, ro, H, n.stride(0), W,
-               self._ptrs(SITE_QKV), W, self.rank * ro, bn, st)
-        self.fc.barrier(SITE_B1)
+        with model._range("qkv_scatter"):
+            N.call("us_gemm_wx_scatter", N.ptr(blk.qkv), N.ptr(n), P * W, H, ro, H, n.stride(0),
+                   W, self._ptrs(SITE_QKV), W, self.rank * ro, bn, st)
+        with model._range("barrier_1"):
+            self.fc.barrier(SITE_B1)
         full = self.fc.site_tensor(SITE_QKV, rows, W)
         q, k, v = full[:, :hl * D], full[:, hl * D:2 * hl * D], full[:, 2 * hl * D:]
-        F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, layout.coords, model.inv_freq, hl, hl, D,
-                         cfg.rope_freqs_per_axis, cfg.eps)
+        with model._range("rope"):
+            F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, layout.coords, model.inv_freq, hl, hl,
+                             D, cfg.rope_freqs_per_axis, cfg.eps)
         cu_q, cu_k = layout.cu(n.device)
         att = self.fc.site_tensor(SITE_ATT, rows, hl * D).view(rows, hl, D)
-        flash_attn_varlen(q.view(rows, hl, D), k.view(rows, hl, D), v.view(rows, hl, D), cu_q,
-                          cu_k, rows, layout.used, model.scale, False, out=att)
-        self.fc.barrier(SITE_B2)
+        with model._range("flash"):
+            flash_attn_varlen(q.view(rows, hl, D), k.view(rows, hl, D), v.view(rows, hl, D), cu_q,
+                              cu_k, rows, layout.used, model.scale, False, out=att)
+        with model._range("barrier_2"):
+            self.fc.barrier(SITE_B2)
         # heads -> rows: to_out pulls its K slices from the peers' attention outputs
         out = torch.empty(ro, H, dtype=n.dtype, device=n.device)
         off = self.rank * ro * hl * D * 2
-        N.call("us_gemm_wx_pull", N.ptr(blk.to_out), self._ptrs(SITE_ATT, off), P, hl * D,
-               N.ptr(out), H, P * hl * D, ro, blk.to_out.stride(0), hl * D, H, 0, bn, st)
+        with model._range("out_pull"):
+            N.call("us_gemm_wx_pull", N.ptr(blk.to_out), self._ptrs(SITE_ATT, off), P, hl * D,
+                   N.ptr(out), H, P * hl * D, ro, blk.to_out.stride(0), hl * D, H, 0, bn, st)
         return out

@@ -60,6 +60,7 @@ class VideoJob:
         self.prompt, self.plan = prompt, plan
         self.state = "queued"
         self.phase = "Queued"
+        self.timings: dict = {}
         self.progress = 0.0
         self.created = int(time.time())
         self.completed_at: Optional[int] = None
@@ -101,6 +102,7 @@ class VideoService:
         ax = transformer.ctx.axis("ulysses")
         self.world, self.rank, self.group = ax.size, ax.rank, ax.group
         self.h2d_bytes = self.d2h_bytes = 0
+        self.time_phases = False
         self.denoiser = Denoiser(transformer)
         self.steps = self.denoiser.steps
         self.video_vae, self.audio_vae = video_vae, audio_vae
@@ -170,25 +172,38 @@ class VideoService:
                     del self._jobs[jid]
 
     # ---------------------------------------------------------------- pipeline --
+    def _enter(self, job: VideoJob, phase: str) -> None:
+        """Phase transition; with ``time_phases`` the device is drained first and the
+        wall time of the phase that ends is kept in ``job.timings``."""
+        if self.time_phases:
+            if self.model.device.type == "cuda":
+                torch.cuda.synchronize(self.model.device)
+            now = time.perf_counter()
+            prev = getattr(job, "_phase_t0", None)
+            if prev is not None:
+                job.timings[job.phase] = job.timings.get(job.phase, 0.0) + now - prev
+            job._phase_t0 = now
+        job.phase = phase
+
     def generate(self, job: VideoJob) -> bytes:
         cfg, p, dev = self.model.cfg, job.plan, self.model.device
-        job.phase = "TextEncode"
+        self._enter(job, "TextEncode")
         feats = self.text.encode(job.prompt, "cpu")
         if dev.type == "cuda":
             feats = feats.pin_memory().to(dev, non_blocking=True)
             self.h2d_bytes += feats.numel() * feats.element_size()
-        job.phase = "LatentPrepare"
+        self._enter(job, "LatentPrepare")
         lf, lh, lw = cfg.latent_shape(p.num_frames, p.width, p.height)
         n_audio_rows = cfg.audio_rows(p.num_frames)
         st = self.denoiser.prepare(p.seed, lf, lh, lw, n_audio_rows, feats)
-        job.phase = "Denoise"
+        self._enter(job, "Denoise")
         while st.step < self.denoiser.steps:
             if job.cancelled:
                 raise RuntimeError("cancelled")
             self.denoiser.step(st)
             job.step = st.step
             job.progress = 0.8 * st.step / self.denoiser.steps
-        job.phase = "VideoDecode"
+        self._enter(job, "VideoDecode")
         units = self.video_vae.decode(st.video, self.rank, self.world)
         planes = []
         for _, f in units:
@@ -199,14 +214,14 @@ class VideoService:
             planes.append(torch.cat([y.flatten(1), u.flatten(1), v.flatten(1)], 1))
         packed = self._collect_units(planes, lf, p)
         job.progress = 0.9
-        job.phase = "AudioDecode"
+        self._enter(job, "AudioDecode")
         # audio rows are [time x 2 channels, latent_channels]: split channels into the batch
         a = st.audio.view(-1, 2, cfg.audio_channels).permute(1, 2, 0).contiguous()
         wav = self.audio_vae.decode(a)
         want = int(round(p.num_frames / p.fps * self.audio_vae.cfg.sample_rate))
         wav = wav[:, :want] if wav.shape[1] >= want else torch.nn.functional.pad(
             wav, (0, want - wav.shape[1]))
-        job.phase = "VideoEncode"
+        self._enter(job, "VideoEncode")
         if self.rank != 0:
             return b""
         hw = p.height * p.width
@@ -215,11 +230,13 @@ class VideoService:
         y = host[:, :hw].view(-1, p.height, p.width)
         u = host[:, hw:hw + hw // 4].view(-1, p.height // 2, p.width // 2)
         v = host[:, hw + hw // 4:].view(-1, p.height // 2, p.width // 2)
-        job.phase = "AudioEncode"
+        self._enter(job, "AudioEncode")
         pcm = M.pcm_interleave(wav)
         self.d2h_bytes += pcm.numel() * pcm.element_size()
-        job.phase = "Mux"
-        return M.write_mp4(y, u, v, p.fps, pcm, self.audio_vae.cfg.sample_rate)
+        self._enter(job, "Mux")
+        mp4 = M.write_mp4(y, u, v, p.fps, pcm, self.audio_vae.cfg.sample_rate)
+        self._enter(job, "Done")
+        return mp4
 
     def _collect_units(self, planes: list, latent_frames: int, p) -> torch.Tensor:
         """Packed 4:2:0 planes of every frame in order, [frames, 1.5 * H * W] uint8.
