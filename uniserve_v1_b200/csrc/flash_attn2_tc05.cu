@@ -252,19 +252,32 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       int lim = kv_len - kbase;   // keys of this block this row may see: [0, lim)
       if (a.causal) lim = min(lim, q_idx + shift - kbase + 1);
       const bool need_mask = lim < kBN;
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kBN; c += 32) {
-        uint32_t v[32];
-        tc::tmem_ld32(s_tmem + c, v);
-        tc::tmem_ld_wait();
+      // The whole row of S goes to registers in one round trip; four independent
+      // chains keep the maximum and the sum from serialising on instruction latency.
+      uint32_t v0[32], v1[32], v2[32], v3[32];
+      tc::tmem_ld32(s_tmem, v0);
+      tc::tmem_ld32(s_tmem + 32, v1);
+      tc::tmem_ld32(s_tmem + 64, v2);
+      tc::tmem_ld32(s_tmem + 96, v3);
+      tc::tmem_ld_wait();
+      if (need_mask) {   // last key block of the sequence or the causal diagonal
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float xv = __uint_as_float(v[i]);
-          if (need_mask && c + i >= lim) xv = -INFINITY;
-          mx = fmaxf(mx, xv);
+          if (i >= lim) v0[i] = 0xff800000u;
+          if (32 + i >= lim) v1[i] = 0xff800000u;
+          if (64 + i >= lim) v2[i] = 0xff800000u;
+          if (96 + i >= lim) v3[i] = 0xff800000u;
         }
       }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        mx0 = fmaxf(mx0, __uint_as_float(v0[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(v1[i]));
+        mx2 = fmaxf(mx2, __uint_as_float(v2[i]));
+        mx3 = fmaxf(mx3, __uint_as_float(v3[i]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = fmaxf(m_used, mx * a.scale_log2);
       const bool grow = m_new - m_used > kRescaleThreshold;
       const bool any_grow =
@@ -289,27 +302,37 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         m_used = m_new;
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-#pragma unroll 1
-      for (int c = 0; c < kBN; c += 32) {
-        uint32_t v[32];
-        tc::tmem_ld32(s_tmem + c, v);
-        tc::tmem_ld_wait();
-        uint32_t packed[16];
+      const float neg_m = -m_eff;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      uint32_t pk0[32], pk1[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2f(__uint_as_float(v[i]) * a.scale_log2 - m_eff);
-          float p1 = ex2f(__uint_as_float(v[i + 1]) * a.scale_log2 - m_eff);
-          if (need_mask) {
-            if (c + i >= lim) p0 = 0.f;
-            if (c + i + 1 >= lim) p1 = 0.f;
-          }
-          l_sum += p0 + p1;
-          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
-        }
-        // P columns [c/2, c/2 + 16) lie below the S columns still to be read.
-        tc::tmem_st16(s_tmem + (c >> 1), packed);
+      for (int i = 0; i < 32; i += 2) {
+        const float a0 = ex2f(fmaf(__uint_as_float(v0[i]), a.scale_log2, neg_m));
+        const float a1 = ex2f(fmaf(__uint_as_float(v0[i + 1]), a.scale_log2, neg_m));
+        const float b0 = ex2f(fmaf(__uint_as_float(v1[i]), a.scale_log2, neg_m));
+        const float b1 = ex2f(fmaf(__uint_as_float(v1[i + 1]), a.scale_log2, neg_m));
+        const float c0 = ex2f(fmaf(__uint_as_float(v2[i]), a.scale_log2, neg_m));
+        const float c1 = ex2f(fmaf(__uint_as_float(v2[i + 1]), a.scale_log2, neg_m));
+        const float d0 = ex2f(fmaf(__uint_as_float(v3[i]), a.scale_log2, neg_m));
+        const float d1 = ex2f(fmaf(__uint_as_float(v3[i + 1]), a.scale_log2, neg_m));
+        l0 += a0 + a1;
+        l1 += b0 + b1;
+        l2 += c0 + c1;
+        l3 += d0 + d1;
+        __nv_bfloat162 t;
+        t = __floats2bfloat162_rn(a0, a1);
+        pk0[i >> 1] = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(b0, b1);
+        pk0[16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(c0, c1);
+        pk1[i >> 1] = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(d0, d1);
+        pk1[16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&t);
       }
+      l_sum += (l0 + l1) + (l2 + l3);
+      // P (64 packed columns) replaces the first half of S, which is in registers now.
+      tc::tmem_st32(s_tmem, pk0);
+      tc::tmem_st32(s_tmem + 32, pk1);
       tc::tmem_st_wait();
       tc::tc_fence_before_sync();
       tc::mbar_arrive(&p_full[x]);

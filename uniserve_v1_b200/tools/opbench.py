@@ -53,7 +53,7 @@ def timeit(fn, iters=10, warmup=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["flash", "gemm", "gated", "decode", "moe", "fused-norm",
-                                   "ulysses", "tp", "moe-fp8", "gemm-fp8"])
+                                   "ulysses", "tp", "moe-fp8", "gemm-fp8", "ep"])
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=2048)
@@ -135,6 +135,29 @@ def main():
         out.update(rows=a.rows, m=a.m, k=a.k, ms=ms, tflops=flops / ms / 1e9,
                    tbs=byts / ms / 1e9, frac_memory=byts / ms / 1e9 / tbs, quantize_ms=msq,
                    quantize_tbs=3.0 * x.numel() / msq / 1e9)
+    elif a.op == "ep":
+        # one expert-parallel MoE layer with this rank as the only member of both role
+        # sets: route + dispatch (peer stores), sort + gather + grouped FC1, FC2 whose
+        # epilogue pushes gate-weighted rows to the token owner, combine + residual + norm
+        from ..parallel.expert_exchange import ExpertExchange
+        T, E, k, H, I = a.batch, a.experts, a.topk, a.hidden, a.inter
+        ex = ExpertExchange(None, 0, 1, dev, T, k, H, E, I)
+        x = rnd(T, H)
+        w13, w2, nw = rnd(E, 2 * I, H), rnd(E, H, I), rnd(H)
+        logits = torch.randn(T, E, generator=g, device=dev)
+        ids, wts = F.topk_softmax(logits, k, True)
+        live = torch.full((1,), T, dtype=torch.int32, device=dev)
+        res = torch.zeros(T, H, dtype=torch.float32, device=dev)
+
+        def layer():
+            ex.dispatch(x, ids, wts, live)
+            ex.experts(w13, w2, T)
+            ex.combine_add_rmsnorm(ids, live, res, nw, 1e-6)
+        ms = timeit(layer, a.iters)
+        active = int(torch.unique(ids).numel())
+        byts = active * (w13[0].numel() + w2[0].numel()) * 2.0
+        out.update(tokens=T, experts=E, active_experts=active, ms=ms, tbs=byts / ms / 1e9,
+                   frac_memory=byts / ms / 1e9 / tbs)
     elif a.op == "fused-norm":
         # all-reduce + residual + RMSNorm over the peer heap; one rank (its own peer) so a
         # profiler can attach; the 2/8-rank numbers come from bench.py
