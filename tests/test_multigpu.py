@@ -286,7 +286,7 @@ def _tp_worker(rank, world, port, q):
     # own rows: residual x, normalised rows into the heap
     res = x[lo:lo + ro].to(dev).clone()
     xn = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * nw
-    tp.norm_rows(TP.SITE_NORM_A).copy_(bf(xn[lo:lo + ro]))
+    tp.gathered(TP.SITE_NORM_A).copy_(bf(xn))       # as left by the producers of every rank
     # weight shards: value rows then gate rows of this rank's slice of I
     w13_l = bf(torch.cat([w13[rank * Il:(rank + 1) * Il], w13[I + rank * Il:I + (rank + 1) * Il]]))
     w2_l = bf(w2[:, rank * Il:(rank + 1) * Il]).contiguous()
@@ -295,11 +295,18 @@ def _tp_worker(rank, world, port, q):
         r = res.clone()
         y = tp.mlp(r, TP.SITE_NORM_A, w13_l, w2_l, bf(nw), TP.SITE_NORM_B, eps)
         torch.cuda.synchronize()
-        outs.append((r.cpu(), y.float().cpu()))
+        torch.cuda.synchronize()
+        dist.barrier()                               # the peers' rows have landed too
+        full = tp.gathered(TP.SITE_NORM_B).float().cpu()
+        outs.append((r.cpu(), y.float().cpu(), full))
     status = N.read_status()
     gathered = [None] * world
     dist.all_gather_object(gathered, outs[-1])
     same = torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    # every rank holds all rows: its copy equals the concatenation of the owners' rows
+    own = [None] * world
+    dist.all_gather_object(own, outs[-1][1])
+    same = same and torch.equal(outs[-1][2], torch.cat(own, 0))
     if rank == 0:
         q.put({"status": status, "parts": gathered, "same": same})
     dist.barrier()

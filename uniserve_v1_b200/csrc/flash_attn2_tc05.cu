@@ -45,6 +45,14 @@ struct Flash2Args {
   int Hq, Hkv, causal;
   float scale_log2;
   unsigned int* status;
+  // Sequence-parallel return: output row r (one sequence) belongs to rank
+  // r / peer_rows and is stored into that rank's buffer at row r % peer_rows,
+  // column peer_col0 + head * 128 (row pitch peer_ld elements), so the "heads ->
+  // rows" exchange happens as peer stores from this epilogue.
+  void* peer_out[8];
+  int peer_rows;
+  int peer_col0;
+  long long peer_ld;
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -80,8 +88,14 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int x = tid >> 7;
     const int qi = q0 + tid;
     if (nb_t[x] == 0 && qi < q_len) {
-      uint4* dst = reinterpret_cast<uint4*>(a.out + (long long)(q_start + qi) * a.ldo +
-                                            (long long)h * kD);
+      __nv_bfloat16* zrow = a.out + (long long)(q_start + qi) * a.ldo + (long long)h * kD;
+      if (a.peer_rows > 0) {
+        const int row = q_start + qi;
+        const int p = row / a.peer_rows;
+        zrow = (__nv_bfloat16*)a.peer_out[p] + (long long)(row - p * a.peer_rows) * a.peer_ld +
+               a.peer_col0 + (long long)h * kD;
+      }
+      uint4* dst = reinterpret_cast<uint4*>(zrow);
       for (int i = 0; i < kD / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
     }
   }
@@ -343,6 +357,12 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
         const bool row_ok = q_idx < q_len;
         __nv_bfloat16* orow = a.out + (long long)(q_start + q_idx) * a.ldo + (long long)h * kD;
+        if (a.peer_rows > 0) {
+          const int row = q_start + q_idx;
+          const int p = row / a.peer_rows;
+          orow = (__nv_bfloat16*)a.peer_out[p] + (long long)(row - p * a.peer_rows) * a.peer_ld +
+                 a.peer_col0 + (long long)h * kD;
+        }
 #pragma unroll 1
         for (int c = 0; c < kD; c += 32) {
           uint32_t v[32];
@@ -373,19 +393,19 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
 }  // namespace
 
-// Same contract as us_flash_attn_varlen (q [Tq, Hq*128], k/v [Tk, Hkv*128], out
-// [Tq, Hq*128], bf16, cu_q/cu_k int32 [n_seqs + 1] on the device).
-US_API int us_flash_attn_varlen2(const void* q, const void* k, const void* v, void* out,
-                                 const int* cu_q, const int* cu_k, int n_seqs, int Tq, int Tk,
-                                 int Hq, int Hkv, int D, int max_q, long long ldq, long long ldk,
-                                 long long ldv, long long ldo, float scale, int causal,
-                                 void* stream_) {
-  US_REQUIRE(q && k && v && out && cu_q && cu_k && n_seqs >= 1 && Tq >= 1 && Tk >= 1);
+namespace {
+
+int flash2_impl(const void* q, const void* k, const void* v, void* out, const int* cu_q,
+                const int* cu_k, int n_seqs, int Tq, int Tk, int Hq, int Hkv, int D, int max_q,
+                long long ldq, long long ldk, long long ldv, long long ldo, float scale, int causal,
+                void* const* peer_out, int n_peers, int peer_rows, int peer_col0,
+                long long peer_ld, cudaStream_t stream) {
+  US_REQUIRE(q && k && v && (out || peer_out) && cu_q && cu_k && n_seqs >= 1 && Tq >= 1 &&
+             Tk >= 1);
   US_REQUIRE(D == kD && Hkv >= 1 && Hq % Hkv == 0 && max_q >= 1);
   US_REQUIRE((ldq % 8) == 0 && (ldk % 8) == 0 && (ldv % 8) == 0 && (ldo % 8) == 0);
   US_REQUIRE(((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0 && ((uintptr_t)v % 16) == 0 &&
              ((uintptr_t)out % 16) == 0);
-  cudaStream_t stream = (cudaStream_t)stream_;
   CUtensorMap tmQ, tmK, tmV;
   int rc = us_tmap_2d(&tmQ, q, US_TMAP_BF16, (uint64_t)Tq, (uint64_t)Hq * D, (uint64_t)ldq, kBM,
                       64, US_SWZ_128);
@@ -406,6 +426,21 @@ US_API int us_flash_attn_varlen2(const void* q, const void* k, const void* v, vo
   a.causal = causal;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = us_status_ptr();
+  for (int p = 0; p < 8; ++p) a.peer_out[p] = nullptr;
+  a.peer_rows = 0;
+  a.peer_col0 = 0;
+  a.peer_ld = 0;
+  if (peer_out) {
+    US_REQUIRE(n_seqs == 1 && n_peers >= 1 && n_peers <= 8 && peer_rows >= 1 &&
+               (long long)peer_rows * n_peers >= Tq && (peer_ld % 8) == 0 && (peer_col0 % 8) == 0);
+    for (int p = 0; p < n_peers; ++p) {
+      US_REQUIRE(peer_out[p] && ((uintptr_t)peer_out[p] % 16) == 0);
+      a.peer_out[p] = peer_out[p];
+    }
+    a.peer_rows = peer_rows;
+    a.peer_col0 = peer_col0;
+    a.peer_ld = peer_ld;
+  }
   const size_t smem = 6 * (size_t)kTile + 16 * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -416,4 +451,30 @@ US_API int us_flash_attn_varlen2(const void* q, const void* k, const void* v, vo
   dim3 grid((max_q + 2 * kBM - 1) / (2 * kBM), Hq, n_seqs);
   US_CUDA_CHECK(us::launch_pdl(flash2_fwd_kernel, grid, dim3(320), smem, stream, tmQ, tmK, tmV, a));
   return US_OK;
+}
+
+}  // namespace
+
+// Same contract as us_flash_attn_varlen (q [Tq, Hq*128], k/v [Tk, Hkv*128], out
+// [Tq, Hq*128], bf16, cu_q/cu_k int32 [n_seqs + 1] on the device).
+US_API int us_flash_attn_varlen2(const void* q, const void* k, const void* v, void* out,
+                                 const int* cu_q, const int* cu_k, int n_seqs, int Tq, int Tk,
+                                 int Hq, int Hkv, int D, int max_q, long long ldq, long long ldk,
+                                 long long ldv, long long ldo, float scale, int causal,
+                                 void* stream_) {
+  return flash2_impl(q, k, v, out, cu_q, cu_k, n_seqs, Tq, Tk, Hq, Hkv, D, max_q, ldq, ldk, ldv,
+                     ldo, scale, causal, nullptr, 0, 0, 0, 0, (cudaStream_t)stream_);
+}
+
+// One sequence whose output rows are pushed to the ranks that own them (Ulysses
+// return fused into the attention epilogue): row r goes to peer_out[r / peer_rows] at
+// row r % peer_rows, columns [peer_col0 + h * 128, + 128) of a [peer_rows, peer_ld] buffer.
+US_API int us_flash_attn_push(const void* q, const void* k, const void* v, const int* cu_q,
+                              const int* cu_k, int Tq, int Tk, int Hq, int Hkv, long long ldq,
+                              long long ldk, long long ldv, float scale, void* const* peer_out,
+                              int n_peers, int peer_rows, int peer_col0, long long peer_ld,
+                              void* stream_) {
+  return flash2_impl(q, k, v, nullptr, cu_q, cu_k, 1, Tq, Tk, Hq, Hkv, kD, Tq, ldq, ldk, ldv, 8,
+                     scale, 0, peer_out, n_peers, peer_rows, peer_col0, peer_ld,
+                     (cudaStream_t)stream_);
 }

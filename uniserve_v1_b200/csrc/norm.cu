@@ -186,20 +186,26 @@ layer_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   }
 }
 
-// Second half of a fused reduce-scatter: `slots` holds one partial product per
-// rank for this rank's own rows ([n_slots, T, H] bf16).  r += sum of the slots
-// (FP32, fixed order), y = rmsnorm(r) * w, both for the own rows only; the
-// normalised rows are then read by the peers' gather GEMMs.
+// Second half of a fused reduce-scatter and first half of the all-gather that
+// follows: `slots` holds one partial product per rank for this rank's own rows
+// ([n_slots, T, H] bf16).  r += sum of the slots (FP32, fixed order), y = rmsnorm(r) * w
+// for the own rows, and y is stored into every rank's copy of the gathered activations
+// (y_peers[p] + row * ldy): the all-gather rides on this kernel's stores, each row
+// crosses NVLink once per peer, and the next GEMM reads local memory only.
+struct PeerRows {
+  __nv_bfloat16* y[8];
+  int n;
+};
+
 __global__ void __launch_bounds__(kThreads)
 reduce_slots_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots,
                                 float* __restrict__ residual, const __nv_bfloat16* __restrict__ w,
-                                __nv_bfloat16* __restrict__ y, int T, int H, long long ldy,
-                                float eps, int first) {
+                                const PeerRows dst, int T, int H, long long ldy, float eps,
+                                int first) {
   US_PDL_PROLOGUE();
   __shared__ float scratch[33];
   const long long row = blockIdx.x;
   float* rr = residual + row * H;
-  __nv_bfloat16* yr = y + row * ldy;
   const int nvec = H >> 3;
   float ss = 0.f;
   for (int v = threadIdx.x; v < nvec; v += kThreads) {
@@ -234,7 +240,8 @@ reduce_slots_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ slots, int n_s
     q.u = *reinterpret_cast<const uint4*>(w + v * 8);
 #pragma unroll
     for (int i = 0; i < 8; ++i) o.b[i] = us::f2bf(r[i] * inv * us::bf2f(q.b[i]));
-    *reinterpret_cast<uint4*>(yr + v * 8) = o.u;
+    for (int p = 0; p < dst.n; ++p)
+      *reinterpret_cast<uint4*>(dst.y[p] + row * ldy + v * 8) = o.u;
   }
 }
 
@@ -289,15 +296,21 @@ US_API int us_layer_norm(const void* x, const void* w, const void* b, void* y, i
   return US_OK;
 }
 
+// y_peers[p]: address of this rank's first row inside rank p's gathered-activation
+// buffer (n_peers entries; a single entry = a plain local output).
 US_API int us_reduce_slots_add_rmsnorm(const void* slots, int n_slots, void* residual,
-                                       const void* w, void* y, int T, int H, long long ldy,
-                                       float eps, int first, void* stream) {
-  US_REQUIRE(slots && residual && w && y && n_slots >= 1 && T >= 0 && H > 0 && (H % 8) == 0 &&
-             (ldy % 8) == 0);
+                                       const void* w, void* const* y_peers, int n_peers, int T,
+                                       int H, long long ldy, float eps, int first, void* stream) {
+  US_REQUIRE(slots && residual && w && y_peers && n_peers >= 1 && n_peers <= 8 && n_slots >= 1 &&
+             T >= 0 && H > 0 && (H % 8) == 0 && (ldy % 8) == 0);
   if (T == 0) return US_OK;
+  PeerRows dst;
+  dst.n = n_peers;
+  for (int p = 0; p < 8; ++p) dst.y[p] = p < n_peers ? (__nv_bfloat16*)y_peers[p] : nullptr;
+  for (int p = 0; p < n_peers; ++p) US_REQUIRE(dst.y[p] && ((uintptr_t)dst.y[p] % 16) == 0);
   us::launch_pdl(reduce_slots_add_rmsnorm_kernel, dim3(T), dim3(kThreads), 0,
                  (cudaStream_t)stream, (const __nv_bfloat16*)slots, n_slots, (float*)residual,
-                 (const __nv_bfloat16*)w, (__nv_bfloat16*)y, T, H, ldy, eps, first);
+                 (const __nv_bfloat16*)w, dst, T, H, ldy, eps, first);
   US_LAUNCH_CHECK();
   return US_OK;
 }

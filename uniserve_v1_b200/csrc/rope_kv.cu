@@ -110,6 +110,7 @@ struct Rope3Args {
   const __nv_bfloat16* kw;
   const float* coords;     // [3, T] (time, height, width)
   const float* inv_freq;   // [freqs_per_axis]
+  const float2* table;     // optional [T, 3 * freqs_per_axis] (cos, sin): replaces sincosf
   int T, Hq, Hk, D, freqs_per_axis;
   long long ldq, ldk;
   float eps;
@@ -155,7 +156,13 @@ __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope3_kernel(const Rope3A
       const int pair = j < F ? i + F : i - F;
       const float sign = j < F ? -1.f : 1.f;
       float sn, cs;
-      sincosf(a.coords[(long long)axis * a.T + t] * a.inv_freq[fidx], &sn, &cs);
+      if (a.table != nullptr) {
+        const float2 e = a.table[(long long)t * 3 * F + axis * F + fidx];
+        cs = e.x;
+        sn = e.y;
+      } else {
+        sincosf(a.coords[(long long)axis * a.T + t] * a.inv_freq[fidx], &sn, &cs);
+      }
       out = buf[i] * cs + sign * buf[pair] * sn;
     }
     row[i] = us::f2bf(out);
@@ -189,17 +196,18 @@ US_API int us_qk_norm_rope_kv(void* qkv, const void* qw, const void* kw, const i
   return US_OK;
 }
 
-US_API int us_qk_norm_rope3(void* q, void* k, const void* qw, const void* kw, const float* coords,
-                            const float* inv_freq, int T, int Hq, int Hk, int D,
-                            int freqs_per_axis, long long ldq, long long ldk, float eps,
-                            void* stream) {
-  US_REQUIRE(q && k && coords && inv_freq && T >= 0 && D > 0 && D <= kMaxD &&
+namespace {
+int rope3_impl(void* q, void* k, const void* qw, const void* kw, const float* coords,
+               const float* inv_freq, const float* table, int T, int Hq, int Hk, int D,
+               int freqs_per_axis, long long ldq, long long ldk, float eps, void* stream) {
+  US_REQUIRE(q && k && (table || (coords && inv_freq)) && T >= 0 && D > 0 && D <= kMaxD &&
              6 * freqs_per_axis <= D);
   if (T == 0) return US_OK;
   Rope3Args a;
   a.q = (__nv_bfloat16*)q; a.k = (__nv_bfloat16*)k;
   a.qw = (const __nv_bfloat16*)qw; a.kw = (const __nv_bfloat16*)kw;
   a.coords = coords; a.inv_freq = inv_freq;
+  a.table = (const float2*)table;
   a.T = T; a.Hq = Hq; a.Hk = Hk; a.D = D; a.freqs_per_axis = freqs_per_axis;
   a.ldq = ldq; a.ldk = ldk; a.eps = eps;
   const long long units = (long long)T * (Hq + Hk);
@@ -207,4 +215,24 @@ US_API int us_qk_norm_rope3(void* q, void* k, const void* qw, const void* kw, co
   us::launch_pdl(qk_norm_rope3_kernel, dim3(blocks), dim3(kWarps * 32), 0, (cudaStream_t)stream, a);
   US_LAUNCH_CHECK();
   return US_OK;
+}
+}  // namespace
+
+US_API int us_qk_norm_rope3(void* q, void* k, const void* qw, const void* kw, const float* coords,
+                            const float* inv_freq, int T, int Hq, int Hk, int D,
+                            int freqs_per_axis, long long ldq, long long ldk, float eps,
+                            void* stream) {
+  return rope3_impl(q, k, qw, kw, coords, inv_freq, nullptr, T, Hq, Hk, D, freqs_per_axis, ldq,
+                    ldk, eps, stream);
+}
+
+// Same with the rotation factors read from a table [T, 3 * freqs_per_axis] of
+// (cos, sin) pairs, built once per request (the coordinates do not change between
+// blocks or steps).
+US_API int us_qk_norm_rope3_table(void* q, void* k, const void* qw, const void* kw,
+                                  const float* table, int T, int Hq, int Hk, int D,
+                                  int freqs_per_axis, long long ldq, long long ldk, float eps,
+                                  void* stream) {
+  return rope3_impl(q, k, qw, kw, nullptr, nullptr, table, T, Hq, Hk, D, freqs_per_axis, ldq, ldk,
+                    eps, stream);
 }

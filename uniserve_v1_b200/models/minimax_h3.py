@@ -150,6 +150,13 @@ class H3Layout:
     def interval(self, rank: int):
         return rank * self.rows_own, (rank + 1) * self.rows_own
 
+    def rope_table(self, inv_freq):
+        """(cos, sin) table of the rows' rotary factors, built once per layout (CUDA only)."""
+        t = getattr(self, "_rope_table", None)
+        if t is None and self.coords.is_cuda:
+            t = self._rope_table = F.rope3_table(self.coords, inv_freq)
+        return t
+
     def cu(self, device):
         """Cumulative lengths of the one packed sequence: (queries = all rows,
         keys = the rows in use); built once per layout."""
@@ -392,7 +399,7 @@ class H3Transformer:
         rows = full.shape[0]
         q, k, v = full[:, :hl * D], full[:, hl * D:2 * hl * D], full[:, 2 * hl * D:]
         F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, layout.coords, self.inv_freq, hl, hl, D,
-                         cfg.rope_freqs_per_axis, cfg.eps)
+                         cfg.rope_freqs_per_axis, cfg.eps, table=layout.rope_table(self.inv_freq))
         if vsa:
             from ..ops import vsa as V
             v3 = full[:, 2 * hl * D:3 * hl * D].view(rows, hl, D)

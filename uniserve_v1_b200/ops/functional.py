@@ -112,7 +112,8 @@ def qk_norm_rope_kv_(qkv, qw, kw, positions, inv_freq, slots, kcache, vcache, Hq
     return qkv
 
 
-def qk_norm_rope3_(q, k, qw, kw, coords, inv_freq, Hq, Hk, D, freqs_per_axis, eps=1e-6):
+def qk_norm_rope3_(q, k, qw, kw, coords, inv_freq, Hq, Hk, D, freqs_per_axis, eps=1e-6,
+                   table=None):
     """Video transformer: per-head RMSNorm + three-axis rotary, in place.
     q [T, Hq*D] and k [T, Hk*D] may be column slices of a wider buffer."""
     T = q.shape[0]
@@ -123,10 +124,21 @@ def qk_norm_rope3_(q, k, qw, kw, coords, inv_freq, Hq, Hk, D, freqs_per_axis, ep
         k.copy_(kk.reshape(T, Hk * D))
         return q, k
     assert q.stride(1) == 1 and k.stride(1) == 1
+    if table is not None:
+        N.call("us_qk_norm_rope3_table", N.ptr(q), N.ptr(k), N.ptr(qw), N.ptr(kw), N.ptr(table),
+               T, Hq, Hk, D, freqs_per_axis, q.stride(0), k.stride(0), eps, N.stream())
+        return q, k
     N.call("us_qk_norm_rope3", N.ptr(q), N.ptr(k), N.ptr(qw), N.ptr(kw), N.ptr(coords),
            N.ptr(inv_freq), T, Hq, Hk, D, freqs_per_axis, q.stride(0), k.stride(0), eps,
            N.stream())
     return q, k
+
+
+def rope3_table(coords, inv_freq):
+    """(cos, sin) of every (row, axis, frequency): [T, 3 * F, 2] FP32, built once per
+    request and read by ``qk_norm_rope3_`` instead of evaluating sincos per head."""
+    ang = coords.t().float()[:, :, None] * inv_freq.float()[None, None, :]      # [T, 3, F]
+    return torch.stack([ang.cos(), ang.sin()], -1).reshape(coords.shape[1], -1, 2).contiguous()
 
 
 # -------------------------------------------------------------- attention --

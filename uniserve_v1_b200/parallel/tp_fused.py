@@ -3,13 +3,17 @@
 The residual stream is kept sequence-parallel: every rank owns ``rows / P`` rows
 of the FP32 residual and of the normalised activations.  Around it
 
-* a **column-parallel** linear (QKV, MLP up/gate) reads the normalised rows of
-  *all* ranks: the all-gather is the GEMM's own operand traffic (TMA loads from the
-  peers' buffers, one tensor map per rank, no cluster multicast);
 * a **row-parallel** linear (attention output, MLP down) produces a partial sum
   of every row: its epilogue stores each tile into the slot of the rank that owns
   the rows (reduce-scatter as peer stores), and the owner sums the ``P`` slots in
-  FP32 inside the residual-add + RMSNorm kernel that follows anyway.
+  FP32 inside the residual-add + RMSNorm kernel that follows anyway;
+* that same kernel stores the normalised rows into *every* rank's copy of the
+  gathered activations (all-gather as peer stores from the producer), so the
+  **column-parallel** linear that follows (QKV, MLP up/gate) is a local GEMM over
+  all rows.  Each row crosses NVLink once per peer.  (A GEMM that instead pulls the
+  peers' rows through its operand loads exists as ``us_gemm_wx_gather``; peer
+  memory is not cached in the local L2, so every weight tile re-fetched its
+  activation tile over NVLink, and the producer-side form replaced it.)
 
 Two flag barriers per linear pair order the phases; buffers live in the
 symmetric heap.  The unfused baseline is an NCCL all-reduce after every
@@ -31,7 +35,8 @@ N.register_signatures({
                                 N.I, N.I, N.I, N.I, N.P]),
     "us_gemm_wx_reduce_scatter": (N.I, [N.P, N.P, N.I, N.I, N.I, N.L, N.L, N.L, N.P, N.I, N.I, N.I,
                                         N.I, N.I, N.P]),
-    "us_reduce_slots_add_rmsnorm": (N.I, [N.P, N.I, N.P, N.P, N.P, N.I, N.I, N.L, N.F, N.I, N.P]),
+    "us_reduce_slots_add_rmsnorm": (N.I, [N.P, N.I, N.P, N.P, N.P, N.I, N.I, N.I, N.L, N.F, N.I,
+                                          N.P]),
 })
 
 SITE_NORM_A, SITE_NORM_B, SITE_SLOTS, SITE_B0, SITE_B1 = 0, 1, 2, 3, 4
@@ -65,21 +70,32 @@ class FusedTP:
             self._ptrs[site] = arr
         return arr
 
-    def norm_rows(self, site: int) -> torch.Tensor:
-        """This rank's normalised rows [rows_own, hidden] inside the heap."""
-        return self.fc.site_tensor(site, self.ro, self.H)
+    def gathered(self, site: int) -> torch.Tensor:
+        """This rank's copy of the gathered normalised rows [rows, hidden] in the heap."""
+        return self.fc.site_tensor(site, self.rows, self.H)
+
+    def own_rows(self, site: int) -> torch.Tensor:
+        return self.gathered(site)[self.rank * self.ro:(self.rank + 1) * self.ro]
+
+    def _own_row_ptrs(self, site: int):
+        """Address of this rank's row interval inside every rank's gathered buffer."""
+        key = ("rows", site)
+        arr = self._ptrs.get(key)
+        if arr is None:
+            off = self.rank * self.ro * self.H * 2
+            arr = (ctypes.c_void_p * self.P)(*[self.fc.peer_site_ptr(r, site) + off
+                                               for r in range(self.P)])
+            self._ptrs[key] = arr
+        return arr
 
     # ------------------------------------------------------------------ GEMMs --
     def gather_linear(self, w: torch.Tensor, site: int, gated: bool = False,
                       act: str = "silu") -> torch.Tensor:
-        """y[rows, M] = concat_p(norm rows of rank p) @ w.T with this rank's weight
-        shard ``w`` [M, hidden] (or [2M, hidden] value-then-gate when ``gated``)."""
-        M = w.shape[0] // 2 if gated else w.shape[0]
-        out = torch.empty(self.rows, M, dtype=torch.bfloat16, device=w.device)
-        N.call("us_gemm_wx_gather", N.ptr(w), self.ptrs(site), self.P, self.ro, N.ptr(out),
-               w.shape[0], M, self.H, self.rows, w.stride(0), self.H, M, 1 if gated else 0,
-               M if gated else 0, F._ACT[act] if gated else 0, 0, self.bn, N.stream())
-        return out
+        """y[rows, M] = (all ranks' normalised rows) @ w.T with this rank's weight shard
+        ``w`` [M, hidden] (or [2M, hidden] value-then-gate when ``gated``); the rows were
+        gathered by their producers, so this is a local GEMM."""
+        x = self.gathered(site)
+        return F.linear_gated(x, w, act=act) if gated else F.linear(x, w)
 
     def reduce_scatter_linear(self, w: torch.Tensor, x: torch.Tensor) -> None:
         """Partial product x @ w.T ([rows, hidden]) pushed row-interval-wise into the
@@ -93,19 +109,20 @@ class FusedTP:
 
     def reduce_add_rmsnorm(self, residual: torch.Tensor, w: torch.Tensor, out_site: int,
                            eps: float, first: bool = False) -> torch.Tensor:
-        """residual(own rows) += sum of the slots; the normalised rows go to ``out_site``."""
-        y = self.norm_rows(out_site)
+        """residual(own rows) += sum of the slots; the normalised rows are stored into
+        every rank's gathered buffer ``out_site``.  Returns this rank's view of its rows."""
         slots = self.fc.site_tensor(SITE_SLOTS, self.P * self.ro, self.H)
         N.call("us_reduce_slots_add_rmsnorm", N.ptr(slots), self.P, N.ptr(residual), N.ptr(w),
-               N.ptr(y), self.ro, self.H, self.H, eps, 1 if first else 0, N.stream())
-        return y
+               self._own_row_ptrs(out_site), self.P, self.ro, self.H, self.H, eps,
+               1 if first else 0, N.stream())
+        return self.own_rows(out_site)
 
     # ----------------------------------------------------------------- blocks --
     def mlp(self, residual: torch.Tensor, in_site: int, w13: torch.Tensor, w2: torch.Tensor,
             next_norm_w: torch.Tensor, out_site: int, eps: float) -> torch.Tensor:
-        """Gated MLP over the normalised rows in ``in_site``; leaves the updated
-        residual (own rows) and the next normalised rows in ``out_site``."""
-        self.fc.barrier(SITE_B0)                      # everyone's rows are in place
+        """Gated MLP over the gathered normalised rows in ``in_site``; leaves the updated
+        residual (own rows) and the next normalised rows, gathered, in ``out_site``."""
+        self.fc.barrier(SITE_B0)                      # everyone's rows have arrived here
         hidden = self.gather_linear(w13, in_site, gated=True)
         self.reduce_scatter_linear(w2, hidden)
         self.fc.barrier(SITE_B1)                      # every partial has landed

@@ -3,10 +3,14 @@
 Out: the QKV projection GEMM stores each output tile straight into the buffer of
 the rank that owns those heads (peer stores from the epilogue), so the
 "rows -> heads" all-to-all and its pack/unpack copies do not exist as separate
-steps.  Back: ``to_out`` reads its activation tiles with TMA from the peers'
-attention outputs (K extent = concatenation over ranks of their local heads), so
-the "heads -> rows" all-to-all overlaps the MMA pipeline tile by tile.  Two
-flag barriers per block order the phases; buffers live in the symmetric heap.
+steps.  Back: the flash-attention epilogue stores every output row into the
+buffer of the rank that owns the row, at the columns of the producing rank's
+heads, so the "heads -> rows" all-to-all rides on the attention kernel and
+``to_out`` is a local GEMM.  (A ``to_out`` that pulls its K slices from the
+peers with TMA exists as ``us_gemm_wx_pull``; peer memory is not cached in the
+local L2, so every weight tile re-fetched its activation tile over NVLink and the
+push form replaced it.)  Two flag barriers per block order the phases; buffers
+live in the symmetric heap.
 
 Baseline for comparison is ``H3Transformer._attention`` with NCCL ``all_to_all``
 (reference: crates/nn/src/modules/ulysses.rs:264-307, :348-388, reference
@@ -25,6 +29,8 @@ from .symm import FusedComm
 
 N.register_signatures({
     "us_gemm_wx_scatter": (N.I, [N.P, N.P, N.I, N.I, N.I, N.L, N.L, N.L, N.P, N.I, N.I, N.I, N.P]),
+    "us_flash_attn_push": (N.I, [N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.L, N.L, N.L, N.F,
+                                 N.P, N.I, N.I, N.I, N.L, N.P]),
     "us_gemm_wx_pull": (N.I, [N.P, N.P, N.I, N.I, N.P, N.I, N.I, N.I, N.L, N.L, N.L, N.I, N.I,
                               N.P]),
 })
@@ -72,18 +78,20 @@ class FusedUlysses:
         q, k, v = full[:, :hl * D], full[:, hl * D:2 * hl * D], full[:, 2 * hl * D:]
         with model._range("rope"):
             F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, layout.coords, model.inv_freq, hl, hl,
-                             D, cfg.rope_freqs_per_axis, cfg.eps)
+                             D, cfg.rope_freqs_per_axis, cfg.eps,
+                             table=layout.rope_table(model.inv_freq))
         cu_q, cu_k = layout.cu(n.device)
-        att = self.fc.site_tensor(SITE_ATT, rows, hl * D).view(rows, hl, D)
+        # heads -> rows: the attention epilogue stores every output row into the buffer of
+        # the rank that owns it (columns of this rank's heads), so each row crosses NVLink
+        # once and to_out reads local memory only
+        inner = P * hl * D
         with model._range("flash"):
-            flash_attn_varlen(q.view(rows, hl, D), k.view(rows, hl, D), v.view(rows, hl, D), cu_q,
-                              cu_k, rows, layout.used, model.scale, False, out=att)
+            N.call("us_flash_attn_push", N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(cu_q), N.ptr(cu_k),
+                   rows, layout.used, hl, hl, full.stride(0), full.stride(0), full.stride(0),
+                   model.scale, self._ptrs(SITE_ATT), P, ro, self.rank * hl * D, inner, st)
         with model._range("barrier_2"):
             self.fc.barrier(SITE_B2)
-        # heads -> rows: to_out pulls its K slices from the peers' attention outputs
-        out = torch.empty(ro, H, dtype=n.dtype, device=n.device)
-        off = self.rank * ro * hl * D * 2
-        with model._range("out_pull"):
-            N.call("us_gemm_wx_pull", N.ptr(blk.to_out), self._ptrs(SITE_ATT, off), P, hl * D,
-                   N.ptr(out), H, P * hl * D, ro, blk.to_out.stride(0), hl * D, H, 0, bn, st)
+        att = self.fc.site_tensor(SITE_ATT, ro, inner)
+        with model._range("to_out"):
+            out = F.linear(att, blk.to_out)
         return out

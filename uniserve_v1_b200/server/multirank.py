@@ -1,0 +1,210 @@
+"""Serving on several ranks: one leader (HTTP + engine), followers in lock step.
+
+Tensor-parallel and sequence-parallel deployments run one process per GPU.  The
+engine's host state (scheduler, block manager, request table) is *replicated*:
+every rank runs the same deterministic engine and applies the same ordered
+stream of commands, so every rank builds the same batches, launches the same
+kernels and draws the same tokens (logits are all-gathered, sampling is
+addressed by (seed, position)).  Only the commands travel: the leader publishes,
+per step, the requests it admitted or aborted since the last step followed by
+``step``; followers block on the control group (gloo, host memory) and apply.
+
+    leader:    eng = ReplicatedEngine(LLMEngine(...), bus)   # same API as LLMEngine
+    follower:  follower_loop(LLMEngine(...), bus)
+
+Video deployments do the same with one command per request (prompt + plan):
+every rank of the sequence group runs ``VideoService.generate``.
+
+``spawn_followers`` starts ranks 1..N-1 of a package's layout as child processes
+of ``serve`` and returns the leader's context; ``torchrun``-style launches work too
+(RANK / WORLD_SIZE / MASTER_* from the environment).
+
+Reference behaviour: crates/engine/src/executor.rs:86-103 (submit / map / stamp over
+worker groups), crates/engine/src/parallel.rs:1-39 (host collectives for agreement);
+reference project paths.
+"""
+from __future__ import annotations
+
+import os
+import pickle
+from dataclasses import asdict, is_dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class CommandBus:
+    """Ordered broadcast of small Python objects from rank 0 over a gloo group."""
+
+    def __init__(self, group=None, rank: Optional[int] = None):
+        self.group = group
+        self.rank = dist.get_rank() if rank is None else rank
+        self.leader = self.rank == 0
+
+    def publish(self, commands: list) -> None:
+        assert self.leader
+        blob = [pickle.dumps(commands)]
+        dist.broadcast_object_list(blob, src=0, group=self.group)
+
+    def receive(self) -> list:
+        assert not self.leader
+        blob = [None]
+        dist.broadcast_object_list(blob, src=0, group=self.group)
+        return pickle.loads(blob[0])
+
+
+def _plain(params):
+    return asdict(params) if is_dataclass(params) else params
+
+
+def apply_commands(engine, commands: list):
+    """Applies one published batch of commands to a local engine.  Returns the
+    outputs of the step it contained (or None) and whether to keep running."""
+    from ..engine.types import SamplingParams
+    outs, alive = None, True
+    for c in commands:
+        op = c[0]
+        if op == "add":
+            _, rid, ids, params, prio, salt, outputs = c
+            sp = SamplingParams(**params) if isinstance(params, dict) else params
+            try:
+                engine.add_request(ids, sp, request_id=rid, priority=prio, cache_salt=salt,
+                                   output_ids=outputs)
+            except ValueError:
+                pass        # the leader rejected it the same way and told its client
+        elif op == "abort":
+            engine.abort(c[1])
+        elif op == "step":
+            outs = engine.step()
+        elif op == "burst":
+            outs = engine.decode_burst(c[1])
+        elif op == "shutdown":
+            alive = False
+    return outs, alive
+
+
+class ReplicatedEngine:
+    """The leader's engine: same calls as ``LLMEngine``; admissions and aborts are
+    queued and published together with the next step so that every rank applies
+    them at the same point of the step sequence."""
+
+    def __init__(self, engine, bus: CommandBus):
+        self.engine, self.bus = engine, bus
+        self.pending: list = []
+
+    def __getattr__(self, name):          # stats, scheduler, failed, profiler, ...
+        return getattr(self.engine, name)
+
+    def add_request(self, prompt_ids, params=None, request_id: Optional[str] = None,
+                    priority: int = 0, cache_salt: Optional[str] = None,
+                    output_ids: Optional[list] = None) -> str:
+        V = self.engine.model.cfg.vocab_size
+        if any((t < 0 or t >= V) for t in prompt_ids):
+            raise ValueError("input_error: token id outside the vocabulary")
+        rid = request_id or f"req-{next(self.engine._ids)}"
+        self.pending.append(("add", rid, list(prompt_ids), _plain(params), priority, cache_salt,
+                             list(output_ids) if output_ids else None))
+        return rid
+
+    def abort(self, request_id: str) -> bool:
+        known = any(c[0] == "add" and c[1] == request_id for c in self.pending) or \
+            self.engine.scheduler.find(request_id) is not None
+        self.pending.append(("abort", request_id))
+        return known
+
+    def has_work(self) -> bool:
+        return bool(self.pending) or self.engine.has_work()
+
+    def _run(self, last) -> list:
+        cmds, self.pending = self.pending + [last], []
+        self.bus.publish(cmds)
+        outs, _ = apply_commands(self.engine, cmds)
+        return outs or []
+
+    def step(self) -> list:
+        return self._run(("step",))
+
+    def decode_burst(self, steps: int) -> list:
+        return self._run(("burst", steps))
+
+    def shutdown(self) -> None:
+        self.bus.publish([("shutdown",)])
+
+
+def follower_loop(engine, bus: CommandBus) -> int:
+    """Applies the leader's commands until it says shutdown; returns the steps run."""
+    steps = 0
+    while True:
+        cmds = bus.receive()
+        _, alive = apply_commands(engine, cmds)
+        steps += sum(1 for c in cmds if c[0] in ("step", "burst"))
+        if not alive:
+            return steps
+
+
+# ------------------------------------------------------------------- video ----
+class ReplicatedVideoService:
+    """Leader side of a sequence-parallel video deployment: every ``generate`` is
+    announced to the followers, which run the same request."""
+
+    def __init__(self, service, bus: CommandBus):
+        self.service, self.bus = service, bus
+        inner = service.generate
+
+        def generate(job):
+            self.bus.publish([("video", job.prompt, asdict(job.plan))])
+            return inner(job)
+        service.generate = generate
+
+    def shutdown(self) -> None:
+        self.bus.publish([("shutdown",)])
+
+
+def video_follower_loop(service, bus: CommandBus) -> int:
+    from .video_rules import VideoPlan
+    from .video_service import VideoJob
+    done = 0
+    while True:
+        for c in bus.receive():
+            if c[0] == "shutdown":
+                return done
+            if c[0] == "video":
+                service.generate(VideoJob(c[1], VideoPlan(**c[2])))
+                done += 1
+
+
+# ------------------------------------------------------------------ launch ----
+def init_rank(backend: Optional[str] = None):
+    """Joins the job described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT and
+    returns (rank, world, device, control group).  The control group is gloo."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    cuda = torch.cuda.is_available()
+    device = torch.device("cuda", local) if cuda else torch.device("cpu")
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if cuda:
+            torch.cuda.set_device(local)
+            dist.init_process_group(backend or "nccl", device_id=device)
+        else:
+            dist.init_process_group(backend or "gloo")
+        control = dist.new_group(list(range(world)), backend="gloo")
+    else:
+        control = None
+    return rank, world, device, control
+
+
+def spawn_followers(world: int, argv: list, port: int) -> list:
+    """Starts ranks 1..world-1 as child processes running ``argv`` (the same serve
+    command) with the rank environment set; the caller becomes rank 0."""
+    import subprocess
+    import sys
+    procs = []
+    base = dict(os.environ, WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    for r in range(1, world):
+        env = dict(base, RANK=str(r), LOCAL_RANK=str(r))
+        procs.append(subprocess.Popen([sys.executable, "-m", "uniserve_v1_b200"] + argv, env=env))
+    os.environ.update(base, RANK="0", LOCAL_RANK="0")
+    return procs

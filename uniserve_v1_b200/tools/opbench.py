@@ -207,7 +207,7 @@ def main():
         from ..parallel import tp_fused as TP
         rows, H, I = a.rows, a.m, a.inter
         tp = TP.FusedTP(None, 0, 1, dev, rows, H)
-        tp.norm_rows(TP.SITE_NORM_A).copy_(rnd(rows, H))
+        tp.gathered(TP.SITE_NORM_A).copy_(rnd(rows, H))
         w13, w2, nw = rnd(2 * I, H), rnd(H, I), rnd(H)
         res = torch.zeros(rows, H, dtype=torch.float32, device=dev)
         hid = tp.gather_linear(w13, TP.SITE_NORM_A, gated=True)
