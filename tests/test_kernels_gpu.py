@@ -114,9 +114,16 @@ def test_qk_norm_rope3():
     coords = torch.rand(3, T, device=DEV) * 40
     inv = R.rope_inv_freq(2 * Fq, 10000.0, DEV)
     qr, kr = R.qk_norm_rope3(q.view(T, H, D), k.view(T, H, D), qw, kw, coords, inv, Fq, 1e-6)
+    q2, k2 = q.clone(), k.clone()
     F.qk_norm_rope3_(q, k, qw, kw, coords, inv, H, H, D, Fq)
     close(q.view(T, H, D), qr, 3e-2, 3e-2)
     close(k.view(T, H, D), kr, 3e-2, 3e-2)
+    # table-driven fast path (row-strided views of a wider buffer, no q/k norm weights too)
+    wide = torch.cat([q2, k2, rnd(T, 64)], 1)
+    qv, kv = wide[:, :H * D], wide[:, H * D:2 * H * D]
+    F.qk_norm_rope3_(qv, kv, qw, kw, coords, inv, H, H, D, Fq, table=F.rope3_table(coords, inv))
+    close(qv.reshape(T, H, D), qr, 3e-2, 3e-2)
+    close(kv.reshape(T, H, D), kr, 3e-2, 3e-2)
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,splits", [(32, 4, 128, 1), (32, 4, 128, 4), (4, 2, 64, 2),

@@ -15,6 +15,8 @@
 
 #include <string>
 #include <vector>
+#include <thread>
+#include <algorithm>
 
 #define US_API extern "C" __attribute__((visibility("default")))
 
@@ -332,8 +334,23 @@ US_API long long us_mp4_write(const char* path, int width, int height, int fps, 
   vt.sps = nal(3, 7, make_sps(width, height));
   vt.pps = nal(3, 8, make_pps());
   const size_t ys = (size_t)width * height, cs = ys / 4;
+  // Pictures are independent (every one is an IDR): build them on several threads,
+  // a window at a time, and write them in order.
+  const int workers = std::max(1, std::min({(int)std::thread::hardware_concurrency(), 16,
+                                            n_frames}));
+  std::vector<std::vector<uint8_t>> window(workers);
   for (int i = 0; i < n_frames; ++i) {
-    std::vector<uint8_t> au = make_idr(y + i * ys, u + i * cs, v + i * cs, width, height, i);
+    if (i % workers == 0) {
+      std::vector<std::thread> pool;
+      const int n = std::min(workers, n_frames - i);
+      for (int t = 0; t < n; ++t)
+        pool.emplace_back([&, t] {
+          const int fi = i + t;
+          window[t] = make_idr(y + fi * ys, u + fi * cs, v + fi * cs, width, height, fi);
+        });
+      for (auto& th : pool) th.join();
+    }
+    const std::vector<uint8_t>& au = window[i % workers];
     const uint32_t len = (uint32_t)au.size();
     const uint8_t l4[4] = {(uint8_t)(len >> 24), (uint8_t)(len >> 16), (uint8_t)(len >> 8),
                            (uint8_t)len};

@@ -169,6 +169,59 @@ __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope3_kernel(const Rope3A
   }
 }
 
+// Fast path of the three-axis rotary for 128-wide heads with 16 frequencies per
+// axis and a (cos, sin) table: one warp per (row, head), every lane owns four
+// adjacent channels (one 8-byte access each way), the rotation partner of a
+// channel lives in lane ^ 4, no shared memory.
+__global__ void __launch_bounds__(256) qk_norm_rope3_fast_kernel(const Rope3Args a) {
+  US_PDL_PROLOGUE();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = a.Hq + a.Hk;
+  const long long unit = (long long)blockIdx.x * 8 + warp;
+  if (unit >= (long long)a.T * heads) return;
+  const int t = (int)(unit / heads), h = (int)(unit % heads);
+  const bool is_q = h < a.Hq;
+  __nv_bfloat16* row = is_q ? a.q + (long long)t * a.ldq + (long long)h * 128
+                            : a.k + (long long)t * a.ldk + (long long)(h - a.Hq) * 128;
+  uint2 raw = *reinterpret_cast<const uint2*>(row + lane * 4);
+  const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  float x[4] = {__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1)};
+  const __nv_bfloat16* w = is_q ? a.qw : a.kw;
+  if (w) {
+    float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    ss = us::warp_sum(ss);
+    const float inv = rsqrtf(ss / 128.f + a.eps);
+    const uint2 wr = *reinterpret_cast<const uint2*>(w + lane * 4);
+    const __nv_bfloat162 w0 = *reinterpret_cast<const __nv_bfloat162*>(&wr.x);
+    const __nv_bfloat162 w1 = *reinterpret_cast<const __nv_bfloat162*>(&wr.y);
+    x[0] *= inv * __low2float(w0);
+    x[1] *= inv * __high2float(w0);
+    x[2] *= inv * __low2float(w1);
+    x[3] *= inv * __high2float(w1);
+  }
+  // channels [32 axis, 32 axis + 32): lanes 8 axis .. 8 axis + 7; first half pairs with +16
+  float y[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) y[e] = __shfl_xor_sync(0xffffffffu, x[e], 4);
+  if (lane < 24) {
+    const int axis = lane >> 3;
+    const float sign = (lane & 4) ? 1.f : -1.f;
+    const float2* tab = a.table + (long long)t * 48 + axis * 16 + (lane & 3) * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 cs = tab[e];
+      x[e] = x[e] * cs.x + sign * y[e] * cs.y;
+    }
+  }
+  __nv_bfloat162 o0 = __floats2bfloat162_rn(x[0], x[1]);
+  __nv_bfloat162 o1 = __floats2bfloat162_rn(x[2], x[3]);
+  uint2 out;
+  out.x = *reinterpret_cast<uint32_t*>(&o0);
+  out.y = *reinterpret_cast<uint32_t*>(&o1);
+  *reinterpret_cast<uint2*>(row + lane * 4) = out;
+}
+
 }  // namespace
 
 US_API int us_qk_norm_rope_kv(void* qkv, const void* qw, const void* kw, const int* positions,
@@ -211,6 +264,13 @@ int rope3_impl(void* q, void* k, const void* qw, const void* kw, const float* co
   a.T = T; a.Hq = Hq; a.Hk = Hk; a.D = D; a.freqs_per_axis = freqs_per_axis;
   a.ldq = ldq; a.ldk = ldk; a.eps = eps;
   const long long units = (long long)T * (Hq + Hk);
+  if (table && D == 128 && freqs_per_axis == 16 && (ldq % 4) == 0 && (ldk % 4) == 0 &&
+      ((uintptr_t)q % 8) == 0 && ((uintptr_t)k % 8) == 0) {
+    us::launch_pdl(qk_norm_rope3_fast_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), 0,
+                   (cudaStream_t)stream, a);
+    US_LAUNCH_CHECK();
+    return US_OK;
+  }
   const int blocks = (int)((units + kWarps - 1) / kWarps);
   us::launch_pdl(qk_norm_rope3_kernel, dim3(blocks), dim3(kWarps * 32), 0, (cudaStream_t)stream, a);
   US_LAUNCH_CHECK();

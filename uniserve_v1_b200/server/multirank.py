@@ -109,7 +109,7 @@ class ReplicatedEngine:
 
     def abort(self, request_id: str) -> bool:
         known = any(c[0] == "add" and c[1] == request_id for c in self.pending) or \
-            self.engine.scheduler.find(request_id) is not None
+            request_id in self.engine.scheduler.requests
         self.pending.append(("abort", request_id))
         return known
 
