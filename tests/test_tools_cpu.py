@@ -104,3 +104,65 @@ def test_profile_session_and_trace(tmp_path):
     tr = json.loads(out.read_text())
     assert len(tr["traceEvents"]) == 2 * steps
     assert {e["tid"] for e in tr["traceEvents"]} >= {"device"}
+
+
+def test_serve_command_runs_a_two_rank_deployment(tmp_path):
+    """`serve` with tensor_parallel_size = 2 starts the second rank itself (gloo ranks on
+    CPU here), and the deployment answers like a single-rank one."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import urllib.request
+    port = _free_port()
+    pkg = tmp_path / "pkg"
+    pkg.mkdir()
+    (pkg / "config.toml").write_text(
+        'model = "random:tiny"\nserved_model_name = "tiny"\ntensor_parallel_size = 2\n'
+        f'[admin_config]\nhost = "127.0.0.1"\nport = {port}\n')
+    env = dict(os.environ, UNISERVE_CPU_RANKS="1")
+    env.pop("RANK", None)
+    proc = subprocess.Popen([sys.executable, "-m", "uniserve_v1_b200", "serve", str(pkg)], env=env,
+                            cwd=os.path.dirname(os.path.dirname(__file__)))
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}],
+            "max_tokens": 8, "temperature": 0, "ignore_eos": True}
+    try:
+        ok = False
+        for _ in range(240):
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1) as r:
+                    ok = r.status == 200
+                    break
+            except Exception:
+                if proc.poll() is not None:
+                    break
+                time.sleep(0.5)
+        assert ok, "server did not come up"
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions",
+                                     data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            two = json.loads(r.read())
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=30)
+        except Exception:
+            proc.kill()
+    # the same request on an in-process single-rank server
+    from fastapi.testclient import TestClient
+    from uniserve_v1_b200.config.policy import Package
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.server.app import create_app
+    from uniserve_v1_b200.server.tokenizer import load_tokenizer
+    cfg = Qwen3MoeConfig.tiny()
+    model = Qwen3MoeModel(cfg, "cpu", torch.float32).init_random(seed=0)
+    eng = LLMEngine(model, num_pages=512, max_num_seqs=8, max_model_len=512, use_graphs=False)
+    app = create_app(package=Package.parse('model = "random:tiny"\nserved_model_name = "tiny"\n'),
+                     engine=eng, tokenizer=load_tokenizer(None, cfg.vocab_size, cfg.eos_token_id),
+                     served_model_name="tiny")
+    with TestClient(app) as c:
+        one = c.post("/v1/chat/completions", json=body).json()
+    assert two["choices"][0]["message"]["content"] == one["choices"][0]["message"]["content"]
+    assert two["usage"]["completion_tokens"] == 8

@@ -24,9 +24,32 @@ def serve(args) -> int:
 
     pkg = Package.load(args.package)
     logging.basicConfig(level=getattr(logging, (args.log_level or pkg.logging_config.level).upper()))
-    device = "cuda" if torch.cuda.is_available() else "cpu"
+    from .parallel.context import ParallelContext
+    from .server import multirank as MR
+
+    # One process per GPU: the serve command starts ranks 1..N-1 of the package's layout
+    # itself (or joins a job started by a launcher that set RANK / WORLD_SIZE).
+    want = MR.package_world(pkg)
+    cpu_ranks = os.environ.get("UNISERVE_CPU_RANKS", "0") == "1"     # gloo ranks, for tests
+    children = []
+    if want > 1 and "RANK" not in os.environ:
+        have = torch.cuda.device_count() if torch.cuda.is_available() else 0
+        if have >= want or cpu_ranks:
+            import socket
+            sock = socket.socket()
+            sock.bind(("127.0.0.1", 0))
+            port = sock.getsockname()[1]
+            sock.close()
+            children = MR.spawn_followers(want, sys.argv[1:], port)
+        else:
+            logging.warning("layout wants %d ranks, %d GPUs present: serving on one rank", want,
+                            have)
+    rank, world, device, control = MR.init_rank()
+    if cpu_ranks:
+        device = torch.device("cpu")
+    bus = MR.CommandBus(control, rank) if world > 1 else None
     dtype = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}[pkg.dtype]
-    if device == "cpu":
+    if device.type == "cpu":
         dtype = torch.float32
     directory = pkg.model_dir or None
     if directory is None and pkg.model and not pkg.model.startswith("random:"):
@@ -37,51 +60,87 @@ def serve(args) -> int:
     elif pkg.model and "h3" in pkg.model.lower():
         family = "minimax_h3"
     name = pkg.served_model_name or (pkg.model or "model").split("/")[-1]
+    shutdown = None
     if family == "minimax_h3":
         from .models.h3_vae import AudioVaeConfig, AudioVaeDecoder, VideoVaeConfig, VideoVaeDecoder
         from .models.minimax_h3 import H3Config, H3Transformer
         from .server.video_service import VideoService
         tiny = pkg.model and pkg.model.endswith(":tiny")
         cfg = H3Config.tiny() if tiny else H3Config()
-        tr = H3Transformer(cfg, device, dtype).init_random(0)
+        ctx = ParallelContext.from_world(ulysses=world) if world > 1 else None
+        tr = H3Transformer(cfg, device, dtype, ctx).init_random(0)
+        if world > 1 and device.type == "cuda":
+            from .parallel.ulysses import FusedUlysses
+            from .server.video_rules import frames_for_seconds
+            lf, lh, lw = cfg.latent_shape(frames_for_seconds(15), 1536, 768)
+            rows_max = (lf * (lh // 2) * (lw // 2) + cfg.audio_rows(frames_for_seconds(15)) +
+                        4096 + 64 * world) // (64 * world) * (64 * world)
+            tr.ulysses = FusedUlysses(ctx, device, rows_max, tr.heads_local, cfg.head_dim)
         vv = VideoVaeDecoder(VideoVaeConfig.tiny() if tiny else VideoVaeConfig(), device, dtype).init_random(1)
         if tiny:
             vv.cfg.latent_channels = cfg.latent_channels
             vv = VideoVaeDecoder(vv.cfg, device, dtype).init_random(1)
         av = AudioVaeDecoder(AudioVaeConfig.tiny() if tiny else AudioVaeConfig(), device).init_random(2)
-        app = create_app(package=pkg, served_model_name=name,
-                         video_service=VideoService(tr, vv, av, max_seconds=15))
+        service = VideoService(tr, vv, av, max_seconds=15)
+        if rank > 0:
+            return 0 if MR.video_follower_loop(service, bus) >= 0 else 1
+        if bus is not None:
+            shutdown = MR.ReplicatedVideoService(service, bus).shutdown
+        app = create_app(package=pkg, served_model_name=name, video_service=service)
     else:
         from .engine.engine import LLMEngine
         from .models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
         from .server.tokenizer import load_tokenizer
+        ctx = ParallelContext.from_world(tensor=world, expert_over_tensor=True) if world > 1 \
+            else None
         if directory:
             ld = CheckpointLoader(directory)
             cfg = Qwen3MoeConfig.from_hf(ld.config)
-            model = Qwen3MoeModel(cfg, device, dtype).load_state(ld)
+            model = Qwen3MoeModel(cfg, device, dtype, ctx).load_state(ld)
         else:
             cfg = Qwen3MoeConfig.tiny() if (pkg.model or "").endswith(":tiny") \
                 else Qwen3MoeConfig.qwen3_30b_a3b()
-            model = Qwen3MoeModel(cfg, device, dtype).init_random(0)
+            model = Qwen3MoeModel(cfg, device, dtype, ctx).init_random(0)
+        if world > 1 and device.type == "cuda":
+            from .parallel.symm import attach_fused
+            attach_fused(ctx, device, hidden=cfg.hidden_size)
 
         def make_engine():
-            return LLMEngine(model, page_size=min(pkg.kv_cache_config.block_size, 16)
-                             if device == "cuda" else pkg.kv_cache_config.block_size,
-                             max_num_seqs=min(pkg.max_running_requests, pkg.scheduler_config.max_batch),
-                             max_model_len=pkg.max_model_len or min(cfg.max_position_embeddings, 8192),
-                             max_num_batched_tokens=pkg.max_num_batched_tokens,
-                             mem_fraction_static=pkg.mem_fraction_static,
-                             enable_prefix_cache=pkg.kv_cache_config.prefix_caching,
-                             watchdog_timeout=float(pkg.profiling_config.watchdog_timeout))
+            eng = LLMEngine(model, page_size=min(pkg.kv_cache_config.block_size, 16)
+                            if device.type == "cuda" else pkg.kv_cache_config.block_size,
+                            max_num_seqs=min(pkg.max_running_requests, pkg.scheduler_config.max_batch),
+                            max_model_len=pkg.max_model_len or min(cfg.max_position_embeddings, 8192),
+                            max_num_batched_tokens=pkg.max_num_batched_tokens,
+                            mem_fraction_static=pkg.mem_fraction_static,
+                            enable_prefix_cache=pkg.kv_cache_config.prefix_caching,
+                            watchdog_timeout=float(pkg.profiling_config.watchdog_timeout),
+                            **({"num_pages": 512, "use_graphs": False} if device.type == "cpu" else {}))
+            return MR.ReplicatedEngine(eng, bus) if bus is not None and rank == 0 else eng
 
+        if rank > 0:
+            MR.follower_loop(make_engine(), bus)
+            return 0
         tok = load_tokenizer(directory, cfg.vocab_size, cfg.eos_token_id)
-        app = create_app(package=pkg, engine=make_engine(), tokenizer=tok, served_model_name=name,
-                         engine_factory=make_engine)
+        engine = make_engine()
+        if bus is not None:
+            shutdown = engine.shutdown
+        # a replicated engine cannot be rebuilt on one rank alone: no in-place restart
+        app = create_app(package=pkg, engine=engine, tokenizer=tok, served_model_name=name,
+                         engine_factory=make_engine if bus is None else None)
     if args.ready_fd is not None:
         os.write(args.ready_fd, json.dumps({"state": "listening", "host": pkg.admin_config.host,
                                             "port": pkg.admin_config.port}).encode() + b"\n")
-    uvicorn.run(app, host=pkg.admin_config.host, port=pkg.admin_config.port or 8000,
-                uds=pkg.admin_config.uds, log_level=(args.log_level_http or "warning"))
+    try:
+        uvicorn.run(app, host=pkg.admin_config.host, port=pkg.admin_config.port or 8000,
+                    uds=pkg.admin_config.uds, log_level=(args.log_level_http or "warning"))
+    finally:
+        if shutdown is not None:
+            shutdown()
+        for c in children:
+            try:
+                c.wait(timeout=30)
+            except Exception:
+                c.terminate()
     return 0
 
 

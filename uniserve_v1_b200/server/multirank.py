@@ -175,6 +175,14 @@ def video_follower_loop(service, bus: CommandBus) -> int:
 
 
 # ------------------------------------------------------------------ launch ----
+def package_world(pkg) -> int:
+    """Ranks of the model (or denoiser) group a package describes: the top-level
+    ``tensor_parallel_size`` or the rank list of its first worker group."""
+    lay = pkg.layout()
+    return max(len(g["ranks"]) for g in lay["groups"]) if lay["groups"] else 1
+
+
+
 def init_rank(backend: Optional[str] = None):
     """Joins the job described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT and
     returns (rank, world, device, control group).  The control group is gloo."""
