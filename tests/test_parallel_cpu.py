@@ -128,3 +128,55 @@ def test_replicated_engine_keeps_ranks_in_lock_step():
     ref = eng.generate(prompts, sp)
     assert outs[1] == ref[1] and outs[2] == ref[2]
     assert len(outs[0]) < 6 and outs[0] == ref[0][:len(outs[0])]      # aborted early
+
+
+def _pp_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.parallel.context import ParallelContext
+    ctx = ParallelContext.from_world(layer=world)
+    cfg = Qwen3MoeConfig.tiny()
+    cfg.num_hidden_layers = 4
+    model = Qwen3MoeModel(cfg, "cpu", torch.float32, ctx).init_random(seed=0)
+    own = [i for i, lw in enumerate(model.layers) if lw is not None]
+    assert own == list(range(rank * 2, rank * 2 + 2))
+    caches = model.new_kv_caches(4, 16)
+    assert all((caches[i][0] is not None) == (i in own) for i in range(4))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (9, 20)]
+    eng = LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128, use_graphs=False)
+    out = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    q.put((rank, out))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_pipeline_stages_match_single_rank():
+    """Two pipeline stages (two layers each, hand-off of block output and residual by
+    point-to-point messages) generate what the unsplit model generates, on both ranks."""
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    cfg = Qwen3MoeConfig.tiny()
+    cfg.num_hidden_layers = 4
+    model = Qwen3MoeModel(cfg, "cpu", torch.float32).init_random(seed=0)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (9, 20)]
+    ref = LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128,
+                    use_graphs=False).generate(
+        prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    outs = dict(q.get(timeout=60) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert outs[0] == ref and outs[1] == ref

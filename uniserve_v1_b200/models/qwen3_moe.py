@@ -161,6 +161,13 @@ class Qwen3MoeModel:
         self.inv_freq = R.rope_inv_freq(self.D, cfg.rope_theta, self.device)
         self.scale = 1.0 / math.sqrt(self.D)
         self.layers: list[LayerWeights] = []
+        # Pipeline stages: contiguous shares of the layers along the "layer" axis; layers
+        # of other stages are kept as None (their KV caches too).
+        ax = self.ctx.axis("layer")
+        self.pp, self.pp_rank, self.pp_axis = ax.size, ax.rank, ax
+        L = cfg.num_hidden_layers
+        per = (L + self.pp - 1) // self.pp
+        self.layer_lo, self.layer_hi = min(L, self.pp_rank * per), min(L, (self.pp_rank + 1) * per)
         self.embed: Optional[torch.Tensor] = None
         self.final_norm: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
@@ -216,7 +223,7 @@ class Qwen3MoeModel:
                 lw.w13 = torch.cat([up[sl], gate[sl]], 0).unsqueeze(0).contiguous()
                 lw.w2 = down[:, sl].contiguous().unsqueeze(0)
                 lw.dense = True
-            self.layers.append(lw)
+            self.layers.append(lw if self.layer_lo <= i < self.layer_hi else None)
         self.final_norm = ones(H)
         self.lm_head = self.embed if cfg.tie_word_embeddings else rnd(cfg.vocab_size, H)
         self._shard_vocab()
@@ -255,6 +262,9 @@ class Qwen3MoeModel:
 
         self.embed = get("model.embed_tokens.weight")
         for i in range(cfg.num_hidden_layers):
+            if not (self.layer_lo <= i < self.layer_hi):     # another pipeline stage's layer
+                self.layers.append(None)
+                continue
             p = f"model.layers.{i}."
             q, k, v = (get(p + f"self_attn.{n}_proj.weight") for n in "qkv")
             o = get(p + "self_attn.o_proj.weight")
@@ -296,7 +306,7 @@ class Qwen3MoeModel:
         """The peer-memory path serves small row counts (decode); larger batches
         take the library collective."""
         fc = self.ctx.fused
-        if fc is not None and on_cuda and self.ctx.tp_size > 1 and \
+        if fc is not None and on_cuda and self.ctx.tp_size > 1 and self.pp == 1 and \
                 fc.fits(T, self.cfg.hidden_size):
             return fc
         return None
@@ -397,25 +407,63 @@ class Qwen3MoeModel:
         """Returns the final-normed hidden rows [T, H] (bf16).
         ``kv_caches[layer] = (k, v)`` each [pages, page_size, Hkv_local, D]."""
         self._live = meta.live
-        hidden = F.embedding(input_ids, self.embed)
-        fc = self._fused(hidden.shape[0], hidden.is_cuda)
+        T = input_ids.shape[0]
+        fc = self._fused(T, input_ids.is_cuda)
         if fc is not None:
             fc.begin_forward()
         residual, site = None, None
-        for i, lw in enumerate(self.layers):
+        if self.pp == 1 or self.pp_rank == 0:
+            hidden = F.embedding(input_ids, self.embed)
+        else:
+            hidden, residual = self._stage_recv(T)
+        for i in range(self.layer_lo, self.layer_hi):
+            lw = self.layers[i]
             x, residual = self._reduce_norm(fc, hidden, site, residual, lw.input_norm)
             kc, vc = kv_caches[i]
             mixed, site = self._attention(fc, lw, x, positions, meta, kc, vc)
             x, residual = self._reduce_norm(fc, mixed, site, residual, lw.post_norm)
             hidden, site = self._mlp(fc, lw, x)
-        x, _ = self._reduce_norm(fc, hidden, site, residual, self.final_norm)
-        return x
+        if self.pp == 1:
+            x, _ = self._reduce_norm(fc, hidden, site, residual, self.final_norm)
+            return x
+        last = self.pp - 1
+        if self.pp_rank != last:
+            assert site is None      # stages reduce with plain collectives (see _fused)
+            self._stage_send(hidden, residual)
+            x = torch.empty(T, self.cfg.hidden_size, dtype=self.dtype, device=self.device)
+        else:
+            x, _ = self._reduce_norm(fc, hidden, site, residual, self.final_norm)
+        # every stage samples the same tokens from the last stage's rows
+        return self.ctx.broadcast(x.contiguous(), last, "layer")
+
+    # ------------------------------------------------------------ pipeline --
+    def _stage_send(self, hidden, residual) -> None:
+        """Hand-off to the next stage: the block output and the FP32 residual stream
+        (point-to-point on the layer axis)."""
+        import torch.distributed as dist
+        nxt = self.pp_axis.ranks[self.pp_rank + 1]
+        ops = [dist.P2POp(dist.isend, hidden.contiguous(), nxt, self.pp_axis.group),
+               dist.P2POp(dist.isend, residual.contiguous(), nxt, self.pp_axis.group)]
+        for r in dist.batch_isend_irecv(ops):
+            r.wait()
+
+    def _stage_recv(self, T: int):
+        import torch.distributed as dist
+        prev = self.pp_axis.ranks[self.pp_rank - 1]
+        H = self.cfg.hidden_size
+        hidden = torch.empty(T, H, dtype=self.dtype, device=self.device)
+        residual = torch.empty(T, H, dtype=torch.float32, device=self.device)
+        ops = [dist.P2POp(dist.irecv, hidden, prev, self.pp_axis.group),
+               dist.P2POp(dist.irecv, residual, prev, self.pp_axis.group)]
+        for r in dist.batch_isend_irecv(ops):
+            r.wait()
+        return hidden, residual
 
     def forward_experts_only(self, t_step: int) -> None:
         """An expert rank of the disaggregated layout: every forward is the join - per
         layer it waits for the attention ranks' rows, runs its experts and pushes back."""
         for lw in self.layers:
-            if lw.dense:
+            if lw is None or lw.dense:
                 continue
             if lw.fp8 is not None:
                 self.exchange.experts_fp8(lw.fp8, t_step)
@@ -434,16 +482,19 @@ class Qwen3MoeModel:
         shape = (num_pages, page_size, self.Hkv, self.D)
         return [(torch.zeros(shape, dtype=self.dtype, device=self.device),
                  torch.zeros(shape, dtype=self.dtype, device=self.device))
-                for _ in range(self.cfg.num_hidden_layers)]
+                if self.layer_lo <= i < self.layer_hi else (None, None)
+                for i in range(self.cfg.num_hidden_layers)]
 
     def kv_bytes_per_page(self, page_size: int = 16) -> int:
-        return 2 * page_size * self.Hkv * self.D * 2 * self.cfg.num_hidden_layers
+        return 2 * page_size * self.Hkv * self.D * 2 * (self.layer_hi - self.layer_lo)
 
     def weight_bytes(self) -> int:
         n = self.embed.numel() + self.final_norm.numel()
         if self.lm_head is not self.embed:
             n += self.lm_head.numel()
         for lw in self.layers:
+            if lw is None:
+                continue
             for t in (lw.input_norm, lw.post_norm, lw.qkv, lw.q_norm, lw.k_norm, lw.o_proj,
                       lw.router, lw.w13, lw.w2):
                 if t is not None:
