@@ -196,3 +196,48 @@ def test_fp8_block_weight_roundtrip_and_cpu_linear():
     y = Q.linear_fp8_block(x, q[0], s[0])
     ref = x.float() @ w[0].t()
     assert ((y.float() - ref).norm() / ref.norm()) < 0.08
+
+
+def test_adapter_fusion(tmp_path):
+    """Low-rank pairs, full-rank deltas, bias deltas and assigned tensors fuse into the
+    checkpoint's values at the loading boundary; untouched tensors read through."""
+    import torch
+    from uniserve_v1_b200.checkpoint.adapter import AdaptedLoader, Adapter
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, save_file
+    g = torch.Generator().manual_seed(0)
+    r = lambda *s: torch.randn(*s, generator=g)
+    base = {"blocks.0.attn.to_q.weight": r(16, 8).to(torch.bfloat16),
+            "blocks.0.attn.to_q.bias": r(16).to(torch.bfloat16),
+            "blocks.0.ff.weight": r(8, 8).to(torch.bfloat16),
+            "norm.weight": r(8).to(torch.bfloat16)}
+    (tmp_path / "ckpt").mkdir()
+    save_file(base, tmp_path / "ckpt" / "model.safetensors")
+    edits = {"blocks.0.attn.to_q.lora_A": r(2, 8), "blocks.0.attn.to_q.lora_B": r(16, 2),
+             "blocks.0.attn.to_q.diff_b": r(16), "blocks.0.ff.diff": r(8, 8),
+             "blocks.0.attn.to_gate_compress.set_weight": r(16, 8).to(torch.bfloat16)}
+    (tmp_path / "ad").mkdir()
+    save_file(edits, tmp_path / "ad" / "adapter_model.safetensors")
+    ad = Adapter(tmp_path / "ad")
+    assert ad.contents() == {"low_rank": 2, "diff": 2, "assign": 1}
+    ld = AdaptedLoader(CheckpointLoader(tmp_path / "ckpt"), ad)
+    w = ld.get("blocks.0.attn.to_q.weight")
+    want = (edits["blocks.0.attn.to_q.lora_B"] @ edits["blocks.0.attn.to_q.lora_A"] +
+            base["blocks.0.attn.to_q.weight"].float()).to(torch.bfloat16)
+    assert w.dtype == torch.bfloat16 and torch.equal(w, want)
+    assert torch.equal(ld.get("blocks.0.attn.to_q.bias"),
+                       (edits["blocks.0.attn.to_q.diff_b"] + base["blocks.0.attn.to_q.bias"].float())
+                       .to(torch.bfloat16))
+    assert torch.equal(ld.get("blocks.0.ff.weight"),
+                       (edits["blocks.0.ff.diff"] + base["blocks.0.ff.weight"].float())
+                       .to(torch.bfloat16))
+    assert torch.equal(ld.get("norm.weight"), base["norm.weight"])
+    assert ld.has("blocks.0.attn.to_gate_compress.weight")
+    assert torch.equal(ld.get("blocks.0.attn.to_gate_compress.weight"),
+                       edits["blocks.0.attn.to_gate_compress.set_weight"])
+    bad = dict(edits)
+    del bad["blocks.0.attn.to_q.lora_B"]
+    (tmp_path / "bad").mkdir()
+    save_file(bad, tmp_path / "bad" / "adapter_model.safetensors")
+    import pytest
+    with pytest.raises(ValueError):
+        Adapter(tmp_path / "bad")
