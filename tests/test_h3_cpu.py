@@ -3,6 +3,7 @@ Ulysses sequence parallelism (two gloo ranks reproduce one rank)."""
 import os
 import socket
 
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -63,12 +64,12 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, axis="ulysses"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from uniserve_v1_b200.parallel.context import ParallelContext
-    ctx = ParallelContext.from_world(ulysses=world)
+    ctx = ParallelContext.from_world(**{axis: world})
     v, a = _run(ctx)
     if rank == 0:
         q.put((v, a))
@@ -76,12 +77,15 @@ def _worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-def test_ulysses2_matches_single_rank():
+@pytest.mark.parametrize("axis", ["ulysses", "gather"])
+def test_sequence_parallel_2_matches_single_rank(axis):
+    """Rows split over two ranks: heads travelling around attention (Ulysses) or K / V
+    rows all-gathered with every head local (gather)."""
     v1, a1 = _run()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, axis)) for r in range(2)]
     for p in procs:
         p.start()
     v2, a2 = q.get(timeout=240)

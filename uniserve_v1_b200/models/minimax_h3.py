@@ -238,10 +238,16 @@ class H3Transformer:
                  ctx: Optional[ParallelContext] = None):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.ctx = ctx or ParallelContext.single()
-        self.sp = self.ctx.axis("ulysses").size
-        self.sp_rank = self.ctx.axis("ulysses").rank
-        assert cfg.num_heads % self.sp == 0, "heads must divide over the Ulysses group"
-        self.heads_local = cfg.num_heads // self.sp
+        # Rows are split along one sequence axis: "ulysses" (heads travel around attention)
+        # or "gather" (queries stay, K and V rows are all-gathered, every head is local).
+        uly, gat = self.ctx.axis("ulysses").size, self.ctx.axis("gather").size
+        assert uly == 1 or gat == 1, "one sequence axis at a time (no hybrid placement)"
+        self.seq_axis = "gather" if gat > 1 else "ulysses"
+        self.sp = self.ctx.axis(self.seq_axis).size
+        self.sp_rank = self.ctx.axis(self.seq_axis).rank
+        self.head_split = uly
+        assert cfg.num_heads % self.head_split == 0, "heads must divide over the Ulysses group"
+        self.heads_local = cfg.num_heads // self.head_split
         self.inv_freq = R.rope_inv_freq(2 * cfg.rope_freqs_per_axis, cfg.rope_theta, self.device)
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         self.blocks: list = []
@@ -287,7 +293,7 @@ class H3Transformer:
     def _group_qkv(self, q, k, v, gate=None):
         """Row order [rank 0: q heads, k heads, v heads (, gate heads) | rank 1: ... ] so
         the projection output is already blocked by destination rank."""
-        P, hl, D = self.sp, self.heads_local, self.cfg.head_dim
+        P, hl, D = self.head_split, self.heads_local, self.cfg.head_dim
         parts = []
         for p in range(P):
             sl = slice(p * hl * D, (p + 1) * hl * D)
@@ -384,6 +390,8 @@ class H3Transformer:
 
     def _attention(self, blk: H3Block, n: torch.Tensor, layout: H3Layout) -> torch.Tensor:
         cfg = self.cfg
+        if self.seq_axis == "gather" and self.sp > 1:
+            return self._attention_gather(blk, n, layout)
         hl, D, P = self.heads_local, cfg.head_dim, self.sp
         vsa = cfg.vsa_sparsity > 0
         W = (4 if vsa else 3) * hl * D
@@ -417,6 +425,28 @@ class H3Transformer:
             back = self.ctx.all_to_all(att.view(P, ro, hl * D), "ulysses")   # [P(heads), ro, hl*D]
             att = back.permute(1, 0, 2).reshape(ro, P * hl * D).contiguous()
         return F.linear(att, blk.to_out)
+
+    def _attention_gather(self, blk: H3Block, n: torch.Tensor, layout: H3Layout) -> torch.Tensor:
+        """All-gather sequence parallelism: this rank's rows are the queries; K and V of
+        every interval are all-gathered along the gather axis; all heads are local
+        (crates/models/src/minimax_h3/transformer.rs:299-314, reference project path)."""
+        cfg = self.cfg
+        H_, D = cfg.num_heads, cfg.head_dim
+        ro = n.shape[0]
+        lo, hi = layout.interval(self.sp_rank)
+        qkv = F.linear(n, blk.qkv)                               # [rows_own, 3 * heads * D]
+        q, k, v = qkv[:, :H_ * D], qkv[:, H_ * D:2 * H_ * D], qkv[:, 2 * H_ * D:]
+        coords = layout.coords[:, lo:hi].contiguous()
+        F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, coords, self.inv_freq, H_, H_, D,
+                         cfg.rope_freqs_per_axis, cfg.eps)
+        k_all = self.ctx.all_gather_rows(k.contiguous(), "gather")
+        v_all = self.ctx.all_gather_rows(v.contiguous(), "gather")
+        dev = n.device
+        cu_q = torch.tensor([0, ro], dtype=torch.int32, device=dev)
+        cu_k = torch.tensor([0, layout.used], dtype=torch.int32, device=dev)
+        att = self._dense_attention(q.reshape(ro, H_, D), k_all.view(-1, H_, D),
+                                    v_all.view(-1, H_, D), cu_q, cu_k, ro, layout.used)
+        return F.linear(att.reshape(ro, H_ * D), blk.to_out)
 
     def forward(self, h: torch.Tensor, layout: H3Layout, level: int):
         """h: own rows [rows_own, hidden] bf16.  Returns FP32 velocity rows of the
@@ -536,7 +566,7 @@ class Denoiser:
         def gather(x, width, total):
             buf = torch.zeros(ro, width, dtype=torch.float32, device=x.device)
             buf[:x.shape[0]] = x
-            allr = m.ctx.all_gather_rows(buf, "ulysses").view(m.sp, ro, width)
+            allr = m.ctx.all_gather_rows(buf, m.seq_axis).view(m.sp, ro, width)
             return allr
 
         gv = gather(vel_v, m.cfg.patch_width, layout.n_video)

@@ -99,7 +99,7 @@ class VideoService:
         # Ranks of the sequence group also share the decode work: temporal units
         # are dealt round-robin and the encoded planes gathered on every rank
         # (crates/engine/src/runner/decoder.rs:57-70, reference project path).
-        ax = transformer.ctx.axis("ulysses")
+        ax = transformer.ctx.axis(getattr(transformer, "seq_axis", "ulysses"))
         self.world, self.rank, self.group = ax.size, ax.rank, ax.group
         self.h2d_bytes = self.d2h_bytes = 0
         self.time_phases = False
