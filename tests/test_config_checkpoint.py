@@ -241,3 +241,25 @@ def test_adapter_fusion(tmp_path):
     import pytest
     with pytest.raises(ValueError):
         Adapter(tmp_path / "bad")
+
+
+def test_reference_deployment_examples_resolve_to_axes():
+    """Every deployment example of the reference tree parses verbatim and resolves to the
+    parallel axes the serve command builds."""
+    import glob
+    import os
+    from uniserve_v1_b200.config.policy import Package
+    from uniserve_v1_b200.server.multirank import package_parallelism
+    root = "/root/reference/configs"
+    if not os.path.isdir(root):
+        import pytest
+        pytest.skip("reference tree not present")
+    seen = {}
+    for f in sorted(glob.glob(root + "/**/config.toml", recursive=True)):
+        seen[f[len(root) + 1:-len("/config.toml")]] = package_parallelism(
+            Package.parse(open(f).read()))
+    assert seen["qwen3_moe/tp4"] == {"world": 4, "axes": {"tensor": 4}}
+    assert seen["minimax_h3/ulysses8"] == {"world": 8, "axes": {"ulysses": 8}}
+    assert seen["minimax_h3/gather8"] == {"world": 8, "axes": {"gather": 8}}
+    assert seen["minimax_h3/fasth3-ulysses4x2"] == {"world": 4, "axes": {"ulysses": 4}}
+    assert len(seen) >= 10

@@ -29,7 +29,8 @@ def serve(args) -> int:
 
     # One process per GPU: the serve command starts ranks 1..N-1 of the package's layout
     # itself (or joins a job started by a launcher that set RANK / WORLD_SIZE).
-    want = MR.package_world(pkg)
+    par = MR.package_parallelism(pkg)
+    want, axes = par["world"], par["axes"]
     cpu_ranks = os.environ.get("UNISERVE_CPU_RANKS", "0") == "1"     # gloo ranks, for tests
     children = []
     if want > 1 and "RANK" not in os.environ:
@@ -67,9 +68,10 @@ def serve(args) -> int:
         from .server.video_service import VideoService
         tiny = pkg.model and pkg.model.endswith(":tiny")
         cfg = H3Config.tiny() if tiny else H3Config()
-        ctx = ParallelContext.from_world(ulysses=world) if world > 1 else None
+        seq = "gather" if "gather" in axes else "ulysses"
+        ctx = ParallelContext.from_world(**{seq: world}) if world > 1 else None
         tr = H3Transformer(cfg, device, dtype, ctx).init_random(0)
-        if world > 1 and device.type == "cuda":
+        if world > 1 and device.type == "cuda" and seq == "ulysses":
             from .parallel.ulysses import FusedUlysses
             from .server.video_rules import frames_for_seconds
             lf, lh, lw = cfg.latent_shape(frames_for_seconds(15), 1536, 768)
@@ -91,8 +93,11 @@ def serve(args) -> int:
         from .engine.engine import LLMEngine
         from .models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
         from .server.tokenizer import load_tokenizer
-        ctx = ParallelContext.from_world(tensor=world, expert_over_tensor=True) if world > 1 \
-            else None
+        ctx = None
+        if world > 1:
+            pp = axes.get("layer", 1) if world % axes.get("layer", 1) == 0 else 1
+            ctx = ParallelContext.from_world(tensor=world // pp, layer=pp,
+                                             expert_over_tensor=world // pp > 1)
         if directory:
             ld = CheckpointLoader(directory)
             cfg = Qwen3MoeConfig.from_hf(ld.config)
@@ -101,7 +106,7 @@ def serve(args) -> int:
             cfg = Qwen3MoeConfig.tiny() if (pkg.model or "").endswith(":tiny") \
                 else Qwen3MoeConfig.qwen3_30b_a3b()
             model = Qwen3MoeModel(cfg, device, dtype, ctx).init_random(0)
-        if world > 1 and device.type == "cuda":
+        if ctx is not None and ctx.tp_size > 1 and device.type == "cuda":
             from .parallel.symm import attach_fused
             attach_fused(ctx, device, hidden=cfg.hidden_size)
 

@@ -175,12 +175,49 @@ def video_follower_loop(service, bus: CommandBus) -> int:
 
 
 # ------------------------------------------------------------------ launch ----
-def package_world(pkg) -> int:
-    """Ranks of the model (or denoiser) group a package describes: the top-level
-    ``tensor_parallel_size`` or the rank list of its first worker group."""
+def package_parallelism(pkg) -> dict:
+    """How the package's model (or denoiser) group is laid out: ``world`` ranks per copy
+    and the axes to build - ``tensor`` / ``layer`` for text models, ``ulysses`` or
+    ``gather`` for the video transformer.  A group with ``copies = N`` describes N
+    replicas of that layout; one replica is served per ``serve`` command."""
     lay = pkg.layout()
-    return max(len(g["ranks"]) for g in lay["groups"]) if lay["groups"] else 1
+    best = {"world": 1, "axes": {}}
+    for g in lay["groups"]:
+        copies = max(1, int(g.get("copies", 1) or 1))
+        ranks = max(1, len(g["ranks"]) // copies)
+        axes = {}
+        blocks = g.get("blocks", {})
+        tr = next((b for b in blocks.values()
+                   if isinstance(b.get("sequence_parallel"), dict) and
+                   b["sequence_parallel"].get("kind") not in (None, "", "none")), None)
+        if tr:
+            sp = tr["sequence_parallel"]
+            if sp.get("kind") == "allgather":
+                axes["gather"] = int(sp.get("allgather_degree") or ranks)
+            elif sp.get("kind") in ("ulysses", "hybrid"):
+                axes["ulysses"] = int(sp.get("ulysses_degree") or ranks)
+        model = blocks.get("model") or blocks.get("causal_lm")
+        if model and not axes:
+            tp = int(model.get("tensor_parallel_size", 1) or 1)
+            pp = int(model.get("pipeline_parallel_size", 1) or 1)
+            if tp > 1:
+                axes["tensor"] = tp
+            if pp > 1:
+                axes["layer"] = pp
+        world = 1
+        for v in axes.values():
+            world *= v
+        if not axes and ranks > 1 and g.get("role") in ("model", None):
+            axes, world = {"tensor": ranks}, ranks
+        seq = "ulysses" in axes or "gather" in axes
+        if world > best["world"] or (seq and not ("ulysses" in best["axes"] or
+                                                  "gather" in best["axes"])):
+            best = {"world": world, "axes": axes}
+    return best
 
+
+def package_world(pkg) -> int:
+    return package_parallelism(pkg)["world"]
 
 
 def init_rank(backend: Optional[str] = None):
