@@ -63,3 +63,35 @@ def test_sampling_is_batch_invariant():
         alone = LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128,
                           use_graphs=False).generate([p], sp)[0]
         assert alone == t
+
+
+def test_host_kv_tier_brings_back_evicted_prefix_pages():
+    """With a device pool too small to retain an old prompt's pages, the host tier keeps
+    them: the prompt's second run is served from host copies (cached tokens reported,
+    same tokens generated) instead of being recomputed."""
+    import torch
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    g = torch.Generator().manual_seed(3)
+    first = torch.randint(0, 1024, (70,), generator=g).tolist()
+    others = [torch.randint(0, 1024, (70,), generator=g).tolist() for _ in range(3)]
+
+    def run(host_pages):
+        eng = LLMEngine(model, num_pages=12, page_size=16, max_num_seqs=2, max_model_len=128,
+                        use_graphs=False, host_kv_pages=host_pages)
+        a = eng.generate([first], sp)[0]
+        for o in others:                       # push the first prompt's pages out of the pool
+            eng.generate([o], sp)
+        rid = eng.add_request(first, sp)
+        req = eng.scheduler.requests[rid]
+        while eng.has_work():
+            eng.step()
+        return a, req.output_ids, req.num_cached, eng.blocks.host_stats()
+    a0, b0, cached0, st0 = run(0)
+    a1, b1, cached1, st1 = run(32)
+    assert a0 == a1 == b0 == b1
+    assert cached0 == 0 and st0["host_slots"] == 0
+    assert cached1 == 64 and st1["host_hits"] >= 4 and st1["host_offloads"] >= 4

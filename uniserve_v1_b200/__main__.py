@@ -118,6 +118,9 @@ def serve(args) -> int:
                             max_num_batched_tokens=pkg.max_num_batched_tokens,
                             mem_fraction_static=pkg.mem_fraction_static,
                             enable_prefix_cache=pkg.kv_cache_config.prefix_caching,
+                            host_kv_ratio=(pkg.kv_cache_config.host_ratio
+                                           if pkg.kv_cache_config.host_tier else 0.0),
+                            host_kv_gib=pkg.kv_cache_config.host_gib,
                             watchdog_timeout=float(pkg.profiling_config.watchdog_timeout),
                             **({"num_pages": 512, "use_graphs": False} if device.type == "cpu" else {}))
             return MR.ReplicatedEngine(eng, bus) if bus is not None and rank == 0 else eng

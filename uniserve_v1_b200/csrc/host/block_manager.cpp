@@ -14,6 +14,7 @@
 #include <stdint.h>
 #include <string.h>
 
+#include <algorithm>
 #include <list>
 #include <mutex>
 #include <unordered_map>
@@ -113,8 +114,42 @@ struct Pool {
   std::vector<std::list<int>::iterator> lru_pos;
   std::vector<uint8_t> in_lru;
   uint64_t hits = 0, lookups = 0, evictions = 0;
+  // Host tier: content-keyed pages that fell out of the device pool keep living in
+  // `host_slots` slots of pinned host memory, LRU-evicted among themselves.  The pool
+  // only decides; the caller copies (device page -> host slot before the device page
+  // is reused, host slot -> device page on a later hit).
+  int host_slots = 0;
+  std::vector<int> host_free;
+  std::unordered_map<Key, int, KeyHash> host_cached;
+  std::vector<Key> host_key;
+  std::list<int> host_lru;
+  std::vector<std::list<int>::iterator> host_pos;
+  std::vector<std::pair<int, int>> offloads;   // (device page, host slot) decided by alloc
+  uint64_t host_hits = 0, host_offloads = 0;
   std::mutex mu;
 };
+
+// Called with the lock held when a keyed device page is about to be reused.
+void offload_page(Pool* p, int page) {
+  if (p->host_slots == 0) return;
+  const Key k = p->key[page];
+  if (p->host_cached.count(k)) return;   // the host already holds this content
+  int slot;
+  if (!p->host_free.empty()) {
+    slot = p->host_free.back();
+    p->host_free.pop_back();
+  } else {
+    slot = p->host_lru.front();
+    p->host_lru.pop_front();
+    p->host_cached.erase(p->host_key[slot]);
+  }
+  p->host_key[slot] = k;
+  p->host_cached[k] = slot;
+  p->host_lru.push_back(slot);
+  p->host_pos[slot] = std::prev(p->host_lru.end());
+  p->offloads.emplace_back(page, slot);
+  p->host_offloads++;
+}
 
 }  // namespace
 
@@ -161,6 +196,7 @@ US_API int us_bm_alloc(void* h, int n, int* out) {
       page = p->lru.front();
       p->lru.pop_front();
       p->in_lru[page] = 0;
+      offload_page(p, page);
       p->cached.erase(p->key[page]);
       p->has_key[page] = 0;
       p->evictions++;
@@ -279,4 +315,57 @@ US_API int us_bm_flush(void* h) {
     ++n;
   }
   return n;
+}
+
+// ---------------------------------------------------------------- host tier --
+US_API int us_bm_enable_host(void* h, int host_slots) {
+  Pool* p = (Pool*)h;
+  std::lock_guard<std::mutex> g(p->mu);
+  if (host_slots < 0 || p->host_slots != 0) return -1;
+  p->host_slots = host_slots;
+  p->host_key.resize(host_slots);
+  p->host_pos.resize(host_slots);
+  for (int i = host_slots - 1; i >= 0; --i) p->host_free.push_back(i);
+  return 0;
+}
+
+// Moves the (device page, host slot) copies decided since the last call into
+// out[2 * i], out[2 * i + 1]; returns how many (at most `cap`; the rest stay queued).
+US_API int us_bm_take_offloads(void* h, int* out, int cap) {
+  Pool* p = (Pool*)h;
+  std::lock_guard<std::mutex> g(p->mu);
+  const int n = (int)std::min((size_t)cap, p->offloads.size());
+  for (int i = 0; i < n; ++i) {
+    out[2 * i] = p->offloads[i].first;
+    out[2 * i + 1] = p->offloads[i].second;
+  }
+  p->offloads.erase(p->offloads.begin(), p->offloads.begin() + n);
+  return n;
+}
+
+// Host slots of the leading run of `keys` that the host tier holds (refreshes their
+// LRU position); returns the length of the run.
+US_API int us_bm_match_host(void* h, const uint64_t* keys, int n, int* out_slots) {
+  Pool* p = (Pool*)h;
+  std::lock_guard<std::mutex> g(p->mu);
+  int m = 0;
+  for (; m < n; ++m) {
+    auto it = p->host_cached.find(Key{keys[2 * m], keys[2 * m + 1]});
+    if (it == p->host_cached.end()) break;
+    const int slot = it->second;
+    p->host_lru.erase(p->host_pos[slot]);
+    p->host_lru.push_back(slot);
+    p->host_pos[slot] = std::prev(p->host_lru.end());
+    out_slots[m] = slot;
+  }
+  p->host_hits += (uint64_t)m;
+  return m;
+}
+
+US_API void us_bm_host_stats(void* h, uint64_t* hits, uint64_t* offloads, int* used) {
+  Pool* p = (Pool*)h;
+  std::lock_guard<std::mutex> g(p->mu);
+  *hits = p->host_hits;
+  *offloads = p->host_offloads;
+  *used = (int)p->host_cached.size();
 }

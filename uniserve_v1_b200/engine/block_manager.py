@@ -36,6 +36,10 @@ def _lib():
         lib.us_bm_stats.argtypes = [vp, vp, vp, vp]
         lib.us_bm_refcount.argtypes = [vp, ctypes.c_int]
         lib.us_bm_flush.argtypes = [vp]
+        lib.us_bm_enable_host.argtypes = [vp, ctypes.c_int]
+        lib.us_bm_take_offloads.argtypes = [vp, vp, ctypes.c_int]
+        lib.us_bm_match_host.argtypes = [vp, vp, ctypes.c_int, vp]
+        lib.us_bm_host_stats.argtypes = [vp, vp, vp, vp]
         _bound = True
     return lib
 
@@ -59,6 +63,60 @@ class BlockManager:
                 self.h = None
         except Exception:
             pass
+
+    # -------------------------------------------------------------- host tier --
+    def enable_host_tier(self, slots: int) -> None:
+        """Pages that fall out of the device pool keep their content key in ``slots``
+        host slots (LRU among themselves).  The manager only decides; the owner of the
+        cache tensors copies: ``take_moves()`` before every step."""
+        if slots > 0 and self.lib.us_bm_enable_host(self.h, int(slots)) == 0:
+            self.host_slots = int(slots)
+            self.fetches: list = []        # (host slot, device page) decided by fetch_prefix
+
+    def take_moves(self):
+        """(offloads [(device page, host slot)], fetches [(host slot, device page)]) decided
+        since the last call.  Offloads must be copied first: a fetched page may be the one
+        an offload just vacated."""
+        if not getattr(self, "host_slots", 0):
+            return [], []
+        out = np.empty(2 * 4096, dtype=np.int32)
+        offloads = []
+        while True:
+            n = self.lib.us_bm_take_offloads(self.h, out.ctypes.data, 4096)
+            offloads += [(int(out[2 * i]), int(out[2 * i + 1])) for i in range(n)]
+            if n < 4096:
+                break
+        fetches, self.fetches = self.fetches, []
+        return offloads, fetches
+
+    def fetch_prefix(self, keys: np.ndarray, start: int, limit: int) -> list:
+        """Continues a device prefix match at page ``start``: keys the host tier holds get
+        a device page each (pinned, committed under their key) and a pending host -> device
+        copy.  Returns the new pages (possibly fewer than the host run when the pool is full)."""
+        if not getattr(self, "host_slots", 0) or start >= limit:
+            return []
+        ks = np.ascontiguousarray(keys[start:limit], dtype=np.uint64)
+        slots = np.empty(len(ks), dtype=np.int32)
+        m = self.lib.us_bm_match_host(self.h, ks.ctypes.data, len(ks), slots.ctypes.data)
+        pages = []
+        for i in range(m):
+            got = self.allocate(1)
+            if got is None:
+                break
+            page = got[0]
+            owner = self.lib.us_bm_commit(self.h, page, int(ks[i][0]), int(ks[i][1]))
+            if owner != page:          # cannot happen after a device miss; keep the books straight
+                self.release([page])
+                break
+            self.fetches.append((int(slots[i]), page))
+            pages.append(page)
+        return pages
+
+    def host_stats(self) -> dict:
+        a, b, c = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_int()
+        self.lib.us_bm_host_stats(self.h, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
+        return {"host_hits": a.value, "host_offloads": b.value, "host_used": c.value,
+                "host_slots": getattr(self, "host_slots", 0)}
 
     # ------------------------------------------------------------------ verbs --
     @property

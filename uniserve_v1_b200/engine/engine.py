@@ -53,7 +53,8 @@ class LLMEngine:
                  max_num_batched_tokens: int = 8192, mem_fraction_static: float = 0.9,
                  enable_prefix_cache: bool = True, use_graphs: bool = True,
                  policy: Optional[Policy] = None, weights_identity: str = "random-init",
-                 watchdog_timeout: float = 150.0):
+                 watchdog_timeout: float = 150.0, host_kv_pages: int = 0,
+                 host_kv_ratio: float = 0.0, host_kv_gib: Optional[float] = None):
         self.model = model
         self.device = model.device
         max_model_len = min(max_model_len, model.cfg.max_position_embeddings)
@@ -70,6 +71,17 @@ class LLMEngine:
         self.runner = CausalLmRunner(model, num_pages, page_size, max_num_seqs, max_model_len,
                                      use_graphs)
         self.runner.eos_token_id = model.cfg.eos_token_id
+        if host_kv_pages == 0 and host_kv_ratio > 0:
+            # sized as a multiple of the device pool, within a host-memory budget
+            budget = (host_kv_gib if host_kv_gib is not None else 16.0) * (1 << 30)
+            per_page = max(1, model.kv_bytes_per_page(page_size))
+            host_kv_pages = int(min(host_kv_ratio * num_pages, budget // per_page))
+        if host_kv_pages > 0 and enable_prefix_cache:
+            # Second KV tier: prefix pages evicted from the device pool move to host memory
+            # and come back on a later hit (offload / prefetch decisions of the arrival
+            # policy, crates/scheduling/policies/arrival/src/arrival.rs:34-46, reference path).
+            self.blocks.enable_host_tier(host_kv_pages)
+            self.runner.enable_host_tier(host_kv_pages)
         self.watchdog = Watchdog(watchdog_timeout)
         self._ids = itertools.count()
         self.failed: Optional[str] = None
@@ -116,6 +128,8 @@ class LLMEngine:
         batch = self.scheduler.schedule()
         if batch is None:
             return []
+        if getattr(self.blocks, "host_slots", 0):
+            self.runner.apply_kv_moves(*self.blocks.take_moves())
         self.watchdog.begin(f"{batch.kind} step {batch.step_id}")
         try:
             if self.profiler is not None:
@@ -153,6 +167,8 @@ class LLMEngine:
             if pages is None:
                 return self.step()
             r.pages.extend(pages)
+        if getattr(self.blocks, "host_slots", 0):
+            self.runner.apply_kv_moves(*self.blocks.take_moves())
         toks, _ = self.runner.decode(rows, steps)
         outs = []
         from .scheduler import Batch, Chunk

@@ -242,6 +242,50 @@ class CausalLmRunner:
             h["top_p"][n:] = 1.0
             h["min_p"][n:] = 0.0
 
+    # ---------------------------------------------------------------- KV tiers --
+    def enable_host_tier(self, slots: int) -> None:
+        """Host-memory copies of evicted prefix pages: one [slots, page, heads, dim] pair per
+        layer this rank owns, pinned on a GPU deployment."""
+        self.host_kv = []
+        for kc, vc in self.kv_caches:
+            if kc is None:
+                self.host_kv.append((None, None))
+                continue
+            shape = (slots,) + tuple(kc.shape[1:])
+            hk = torch.zeros(shape, dtype=kc.dtype)
+            hv = torch.zeros(shape, dtype=vc.dtype)
+            if self.device.type == "cuda":
+                hk, hv = hk.pin_memory(), hv.pin_memory()
+            self.host_kv.append((hk, hv))
+
+    def apply_kv_moves(self, offloads: list, fetches: list) -> None:
+        """Copies decided by the block manager, in order: device pages about to be reused go
+        to their host slots, then host slots come back into freshly pinned device pages.
+        Runs on the compute stream before the step that reuses the pages."""
+        if not offloads and not fetches:
+            return
+        dev = self.device
+        if offloads:
+            pages = torch.tensor([p for p, _ in offloads], dtype=torch.long, device=dev)
+            slots = torch.tensor([s for _, s in offloads], dtype=torch.long)
+            for (kc, vc), (hk, hv) in zip(self.kv_caches, self.host_kv):
+                if kc is None:
+                    continue
+                hk[slots] = kc.index_select(0, pages).to("cpu")
+                hv[slots] = vc.index_select(0, pages).to("cpu")
+            self.d2h_bytes += sum(2 * len(offloads) * kc[0].numel() * kc.element_size()
+                                  for kc, _ in self.kv_caches if kc is not None)
+        if fetches:
+            slots = torch.tensor([s for s, _ in fetches], dtype=torch.long)
+            pages = torch.tensor([p for _, p in fetches], dtype=torch.long, device=dev)
+            for (kc, vc), (hk, hv) in zip(self.kv_caches, self.host_kv):
+                if kc is None:
+                    continue
+                kc.index_copy_(0, pages, hk[slots].to(dev, non_blocking=True))
+                vc.index_copy_(0, pages, hv[slots].to(dev, non_blocking=True))
+            self.h2d_bytes += sum(2 * len(fetches) * kc[0].numel() * kc.element_size()
+                                  for kc, _ in self.kv_caches if kc is not None)
+
     def release_graphs(self) -> None:
         """Drops every captured graph (do this before tearing down a process
         group whose collectives the graphs captured)."""

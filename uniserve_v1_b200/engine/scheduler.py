@@ -140,6 +140,8 @@ class Scheduler:
             # The last token is always computed so its logits exist.
             max_pages = (req.num_tokens - 1) // self.config.page_size
             hit = self.blocks.match_prefix(keys[:max_pages])
+            if hasattr(self.blocks, "fetch_prefix"):     # continue in the host tier
+                hit = list(hit) + self.blocks.fetch_prefix(keys, len(hit), max_pages)
             req.pages = list(hit)
             req.num_computed = len(hit) * self.config.page_size
             req.committed_pages = len(hit)
