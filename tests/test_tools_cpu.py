@@ -166,3 +166,49 @@ def test_serve_command_runs_a_two_rank_deployment(tmp_path):
         one = c.post("/v1/chat/completions", json=body).json()
     assert two["choices"][0]["message"]["content"] == one["choices"][0]["message"]["content"]
     assert two["usage"]["completion_tokens"] == 8
+
+
+def test_replica_router_spreads_and_sticks(live_server):
+    """Two replicas behind the router: requests spread by load, a cache key sticks to one
+    replica, streaming passes through, a dead replica is skipped."""
+    import json
+    import threading as th
+    import urllib.request
+    import uvicorn
+    from uniserve_v1_b200.server.router import create_router_app
+    port = _free_port()
+    dead = f"http://127.0.0.1:{_free_port()}"
+    app = create_router_app([dead, live_server, live_server])
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+    t = th.Thread(target=server.run, daemon=True)
+    t.start()
+    for _ in range(200):
+        if server.started:
+            break
+        time.sleep(0.05)
+    base = f"http://127.0.0.1:{port}"
+    try:
+        def post(body):
+            req = urllib.request.Request(base + "/v1/chat/completions", data=json.dumps(body).encode(),
+                                         headers={"Content-Type": "application/json"})
+            with urllib.request.urlopen(req, timeout=60) as r:
+                return r.read().decode()
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                "temperature": 0, "ignore_eos": True}
+        out = [json.loads(post(body)) for _ in range(3)]
+        assert all(o["usage"]["completion_tokens"] == 4 for o in out)
+        sse = post(dict(body, stream=True))
+        assert sse.strip().endswith("data: [DONE]")
+        for _ in range(3):
+            post(dict(body, prompt_cache_key="tenant-7"))
+        with urllib.request.urlopen(base + "/router/replicas", timeout=10) as r:
+            stats = json.loads(r.read())
+        assert stats[0]["served"] == 0 and not stats[0]["up"]          # the dead one
+        assert stats[1]["served"] + stats[2]["served"] == 7
+        with urllib.request.urlopen(base + "/health", timeout=10) as r:
+            assert json.loads(r.read())["replicas_up"] == 2
+        with urllib.request.urlopen(base + "/v1/models", timeout=10) as r:
+            assert json.loads(r.read())["data"][0]["id"] == "tiny"
+    finally:
+        server.should_exit = True
+        t.join(timeout=10)

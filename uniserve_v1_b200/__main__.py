@@ -164,9 +164,19 @@ def main(argv=None) -> int:
     b.add_argument("--force", action="store_true")
     l = sub.add_parser("layout", help="print the resolved device layout of a package")
     l.add_argument("package")
+    r = sub.add_parser("route", help="one address in front of data-parallel replicas")
+    r.add_argument("--listen", default="127.0.0.1:8000")
+    r.add_argument("--replica", action="append", required=True, help="base URL of a replica")
     a = ap.parse_args(argv)
     if a.cmd == "serve":
         return serve(a)
+    if a.cmd == "route":
+        import uvicorn
+        from .server.router import create_router_app
+        host, _, port = a.listen.rpartition(":")
+        uvicorn.run(create_router_app(a.replica), host=host or "127.0.0.1", port=int(port),
+                    log_level="warning")
+        return 0
     if a.cmd == "build":
         from . import build
         print(build.build(force=a.force)["kernels"])
