@@ -95,3 +95,56 @@ def test_host_kv_tier_brings_back_evicted_prefix_pages():
     assert a0 == a1 == b0 == b1
     assert cached0 == 0 and st0["host_slots"] == 0
     assert cached1 == 64 and st1["host_hits"] >= 4 and st1["host_offloads"] >= 4
+
+
+def test_speculative_steps_reproduce_plain_decoding():
+    """Verification keeps the agreed prefix plus one model token: whatever the drafter
+    proposes, the output equals step-by-step greedy decoding; an oracle drafter advances
+    k + 1 tokens per step, a wrong one still advances one."""
+    import torch
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.speculation import Drafter, NgramDrafter, accept
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    assert accept([5, 6, 7], [5, 6, 9, 1]) == [5, 6, 9]
+    assert accept([], [4]) == [4] and accept([1], [2, 3]) == [2]
+    assert NgramDrafter(n=2, k=3).propose([1, 2, 3, 4, 9, 2, 3]) == [4, 9, 2]
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (11, 30)]
+    mk = lambda: LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128,
+                           use_graphs=False)
+    ref = mk().generate(prompts, sp)
+
+    class Oracle(Drafter):
+        k = 3
+
+        def propose(self, ids):
+            for p, r in zip(prompts, ref):
+                full = p + r
+                if list(ids) == full[:len(ids)]:
+                    return full[len(ids):len(ids) + self.k]
+            return []
+
+    class Wrong(Drafter):
+        k = 3
+
+        def propose(self, ids):
+            return [(ids[-1] + 1) % 1024] * 3
+
+    for drafter, min_rate in ((Oracle(), 0.99), (Wrong(), 0.0), (NgramDrafter(), 0.0)):
+        eng = mk()
+        rids = [eng.add_request(p, sp) for p in prompts]
+        outs = {r: [] for r in rids}
+        steps = 0
+        while eng.has_work():
+            for o in eng.speculative_step(drafter):
+                outs[o.request_id].extend(o.new_token_ids)
+            steps += 1
+        assert [outs[r] for r in rids] == ref
+        st = eng.spec_stats
+        if st["proposed"]:
+            assert st["accepted"] / st["proposed"] >= min_rate
+        if isinstance(drafter, Oracle):
+            assert steps <= 2 + 4 + 1          # prefill steps + ceil(11 / 4) verify steps

@@ -86,6 +86,7 @@ class LLMEngine:
         self._ids = itertools.count()
         self.failed: Optional[str] = None
         self.profiler = None      # engine.profiling.StepProfiler when profiling is on
+        self.spec_stats = {"steps": 0, "proposed": 0, "accepted": 0}
 
     def _divide_memory(self, fraction, page_size, max_num_seqs, max_model_len) -> int:
         """Quota division: what is left of ``fraction`` of the device after the
@@ -179,6 +180,50 @@ class LLMEngine:
             batch = Batch("decode", [Chunk(r, r.num_tokens - 1, 1, True) for _, r in live])
             sch.stats["decode_tokens"] += len(live)
             outs.extend(sch.update(batch, {r.request_id: int(toks[s_, i]) for i, r in live}))
+        return outs
+
+    def speculative_step(self, drafter) -> list:
+        """One step with speculation: when every running request is decoding greedily, each
+        gets up to ``drafter.k`` proposed tokens verified in one call and advances by the
+        agreed prefix plus one token; otherwise an ordinary step runs."""
+        from .scheduler import Batch, Chunk
+        from .speculation import accept
+        sch = self.scheduler
+        rows = [r for r in sch.running if r.output_ids and r.num_computed == r.num_tokens - 1]
+        if not rows or len(rows) != len(sch.running) or sch.waiting or \
+                self.runner.variant_for(rows) != "greedy":
+            return self.step()
+        drafts = []
+        for r in rows:
+            room = min(self.config.max_model_len - r.num_tokens - 1,
+                       r.params.max_tokens - len(r.output_ids) - 1)
+            d = drafter.propose(r.all_ids)[:max(0, min(drafter.k, room))]
+            pages = self.blocks.allocate(sch._pages_needed(r, r.num_tokens + len(d)))
+            if pages is None:
+                d, pages = [], []
+            r.pages.extend(pages)
+            drafts.append(d)
+        if not any(drafts):
+            return self.step()
+        if getattr(self.blocks, "host_slots", 0):
+            self.runner.apply_kv_moves(*self.blocks.take_moves())
+        self.watchdog.begin("verify step")
+        try:
+            targets = self.runner.verify(rows, drafts)
+        finally:
+            self.watchdog.end()
+        outs = []
+        self.spec_stats["steps"] += 1
+        for r, d, t in zip(rows, drafts, targets):
+            emit = accept(d, t)
+            self.spec_stats["proposed"] += len(d)
+            self.spec_stats["accepted"] += len(emit) - 1
+            for tok in emit:
+                if r.finished:
+                    break
+                batch = Batch("decode", [Chunk(r, r.num_tokens - 1, 1, True)])
+                sch.stats["decode_tokens"] += 1
+                outs.extend(sch.update(batch, {r.request_id: tok}))
         return outs
 
     # -------------------------------------------------------------- generate --

@@ -485,6 +485,46 @@ class CausalLmRunner:
         host, info = self._shape_and_sample(logits, sample_rows)
         return host, info, sample_rows
 
+    # ----------------------------------------------------------------- verify --
+    def verify(self, rows: list, drafts: list):
+        """Speculative verification: request ``rows[i]`` runs its last token followed by
+        ``drafts[i]`` (positions num_tokens - 1 ...) in one causal chunk over its cached
+        context; returns the greedy token after every position, one list per request."""
+        dev, ps = self.device, self.page_size
+        ids, pos, slots, cu_q, cu_k, ctx = [], [], [], [0], [0], []
+        max_q = max_k = 0
+        for req, dr in zip(rows, drafts):
+            start = req.num_tokens - 1
+            toks = [req.all_ids[-1]] + [int(t) for t in dr]
+            ids.extend(toks)
+            pos.extend(range(start, start + len(toks)))
+            for p_ in range(start, start + len(toks)):
+                slots.append(req.pages[p_ // ps] * ps + p_ % ps)
+            cu_q.append(cu_q[-1] + len(toks))
+            cu_k.append(cu_k[-1] + start + len(toks))
+            ctx.append(start)
+            max_q = max(max_q, len(toks))
+            max_k = max(max_k, start + len(toks))
+        T = len(ids)
+        i32 = torch.int32
+        packed = torch.tensor(ids + pos + slots + cu_q + cu_k, dtype=i32,
+                              pin_memory=dev.type == "cuda")
+        d = packed.to(dev, non_blocking=True)
+        self.h2d_bytes += packed.numel() * 4
+        nq = len(cu_q)
+        page_table = torch.zeros(len(rows), self.max_pages, dtype=i32)
+        for i, req in enumerate(rows):
+            page_table[i, :len(req.pages)] = torch.tensor(req.pages, dtype=i32)
+        meta = AttnMeta(kind="prefill", slots=d[2 * T:3 * T], cu_q=d[3 * T:3 * T + nq],
+                        cu_k=d[3 * T + nq:3 * T + 2 * nq], max_q=max_q, max_k=max_k,
+                        context_lens=ctx, page_table=page_table.to(dev))
+        self.announce("eager", T)
+        hidden = self.model.forward(d[:T], d[T:2 * T], meta, self.kv_caches)
+        toks = F.argmax(self.model.logits(hidden))
+        host = (self._to_host(toks) if dev.type == "cuda" else toks).tolist()
+        self.d2h_bytes += T * 4
+        return [host[cu_q[i]:cu_q[i + 1]] for i in range(len(rows))]
+
     # ---------------------------------------------------------------- execute --
     def execute(self, batch: Batch):
         """Returns (sampled {request_id: token}, logprobs {request_id: info})."""
