@@ -212,3 +212,15 @@ def test_replica_router_spreads_and_sticks(live_server):
     finally:
         server.should_exit = True
         t.join(timeout=10)
+
+
+def test_admin_client(live_server, capsys):
+    import json
+    from uniserve_v1_b200.__main__ import main
+    assert main(["admin", "--url", live_server, "health"]) == 0
+    assert json.loads(capsys.readouterr().out)["status"] == "ok"
+    assert main(["admin", "--url", live_server, "get-policy"]) == 0
+    assert json.loads(capsys.readouterr().out)["config"]["served_model_name"] == "tiny"
+    assert main(["admin", "--url", live_server, "query", "select count(*) from events"]) == 0
+    assert "rows" in json.loads(capsys.readouterr().out)
+    assert main(["admin", "--url", live_server, "query", "drop table events"]) == 1

@@ -152,6 +152,33 @@ def serve(args) -> int:
     return 0
 
 
+def admin(args) -> int:
+    """Admin client over plain HTTP (crates/manager/src/main.rs:1-25, reference project
+    path): prints the server's JSON answer; exit status 1 on an HTTP error."""
+    import urllib.error
+    import urllib.request
+    head = {"Authorization": f"Bearer {args.api_key}"} if args.api_key else {}
+    if args.verb == "get-policy":
+        req = urllib.request.Request(args.url + "/admin/policy", headers=head)
+    elif args.verb == "health":
+        req = urllib.request.Request(args.url + "/health", headers=head)
+    elif args.verb == "put-policy":
+        body = open(args.arg, "rb").read()
+        req = urllib.request.Request(args.url + "/admin/policy", data=body, method="PUT",
+                                     headers=dict(head, **{"Content-Type": "application/toml"}))
+    else:
+        req = urllib.request.Request(args.url + "/admin/query", data=(args.arg or "").encode(),
+                                     method="POST",
+                                     headers=dict(head, **{"Content-Type": "text/plain"}))
+    try:
+        with urllib.request.urlopen(req, timeout=60) as r:
+            print(r.read().decode())
+        return 0
+    except urllib.error.HTTPError as e:
+        print(e.read().decode(), file=sys.stderr)
+        return 1
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="uniserve_v1_b200")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -164,12 +191,19 @@ def main(argv=None) -> int:
     b.add_argument("--force", action="store_true")
     l = sub.add_parser("layout", help="print the resolved device layout of a package")
     l.add_argument("package")
+    ad = sub.add_parser("admin", help="admin client: policy get / put, SQL query")
+    ad.add_argument("--url", default="http://127.0.0.1:8000")
+    ad.add_argument("--api-key", default=None)
+    ad.add_argument("verb", choices=["get-policy", "put-policy", "query", "health"])
+    ad.add_argument("arg", nargs="?", help="config.toml to put, or the SQL text")
     r = sub.add_parser("route", help="one address in front of data-parallel replicas")
     r.add_argument("--listen", default="127.0.0.1:8000")
     r.add_argument("--replica", action="append", required=True, help="base URL of a replica")
     a = ap.parse_args(argv)
     if a.cmd == "serve":
         return serve(a)
+    if a.cmd == "admin":
+        return admin(a)
     if a.cmd == "route":
         import uvicorn
         from .server.router import create_router_app
