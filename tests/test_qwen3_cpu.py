@@ -148,3 +148,30 @@ def test_speculative_steps_reproduce_plain_decoding():
             assert st["accepted"] / st["proposed"] >= min_rate
         if isinstance(drafter, Oracle):
             assert steps <= 2 + 4 + 1          # prefill steps + ceil(11 / 4) verify steps
+
+
+def test_dense_qwen3_family():
+    """The dense Qwen3 family (no experts): same decoder, gated MLP in every layer; the
+    Hugging Face config of `Qwen3ForCausalLM` maps onto it."""
+    import torch
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.models.reference_cpu import ReferenceQwen3Moe
+    hf = {"architectures": ["Qwen3ForCausalLM"], "vocab_size": 512, "hidden_size": 128,
+          "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2,
+          "head_dim": 32, "intermediate_size": 256, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
+          "max_position_embeddings": 512, "eos_token_id": 511}
+    cfg = Qwen3MoeConfig.from_hf(hf)
+    assert cfg.num_experts == 0 and not cfg.is_moe_layer(0)
+    model = Qwen3MoeModel(cfg, "cpu", torch.float32).init_random(0)
+    assert all(lw.dense for lw in model.layers)
+    prompt = [1, 2, 3, 4, 5]
+    out = LLMEngine(model, num_pages=32, max_num_seqs=2, max_model_len=128,
+                    use_graphs=False).generate(
+        [prompt], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))[0]
+    seq = list(prompt)
+    for t in out:                                  # every token is the oracle's argmax
+        logits, _ = ReferenceQwen3Moe(model).forward(torch.tensor(seq))
+        assert int(logits[-1].argmax()) == t
+        seq.append(t)
