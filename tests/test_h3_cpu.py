@@ -77,10 +77,11 @@ def _worker(rank, world, port, q, axis="ulysses"):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("axis", ["ulysses", "gather"])
+@pytest.mark.parametrize("axis", ["ulysses", "gather", "layer"])
 def test_sequence_parallel_2_matches_single_rank(axis):
     """Rows split over two ranks: heads travelling around attention (Ulysses) or K / V
-    rows all-gathered with every head local (gather)."""
+    rows all-gathered with every head local (gather); or the blocks split over two
+    stages (layer) with the rows handed from stage to stage."""
     v1, a1 = _run()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

@@ -248,6 +248,14 @@ class H3Transformer:
         self.head_split = uly
         assert cfg.num_heads % self.head_split == 0, "heads must divide over the Ulysses group"
         self.heads_local = cfg.num_heads // self.head_split
+        # Layer split: contiguous shares of the blocks along the "layer" axis; a stage
+        # hands its rows to the next by point-to-point messages and the last stage
+        # broadcasts the velocity rows (transformer.rs:934-953, reference project path).
+        lay = self.ctx.axis("layer")
+        self.pp, self.pp_rank, self.pp_axis = lay.size, lay.rank, lay
+        per = (cfg.num_layers + self.pp - 1) // self.pp
+        self.block_lo = min(cfg.num_layers, self.pp_rank * per)
+        self.block_hi = min(cfg.num_layers, (self.pp_rank + 1) * per)
         self.inv_freq = R.rope_inv_freq(2 * cfg.rope_freqs_per_axis, cfg.rope_theta, self.device)
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         self.blocks: list = []
@@ -279,9 +287,10 @@ class H3Transformer:
             inner = cfg.num_heads * D     # 56 x 128 = 7168 on a 5376-wide stream
             q, k, v = rnd(inner, H), rnd(inner, H), rnd(inner, H)
             gate = rnd(inner, H) if cfg.vsa_sparsity > 0 else None
-            self.blocks.append(H3Block(self._group_qkv(q, k, v, gate), ones(D), ones(D),
-                                       rnd(H, inner),
-                                       rnd(2 * Fn, H), rnd(H, Fn)))
+            blk = H3Block(self._group_qkv(q, k, v, gate), ones(D), ones(D), rnd(H, inner),
+                          rnd(2 * Fn, H), rnd(H, Fn))
+            own = self.block_lo <= len(self.blocks) < self.block_hi
+            self.blocks.append(blk if own else None)
         self.proj_out = rnd(cfg.patch_width, H, dtype=torch.float32)
         self.audio_proj_out = rnd(cfg.audio_channels, H, dtype=torch.float32)
         # time embedder + per-block AdaLN projections (FP32); used to build level tables
@@ -455,7 +464,10 @@ class H3Transformer:
         cfg = self.cfg
         lo, hi = layout.interval(self.sp_rank)
         idx = layout.mod_index[lo:hi].contiguous()
-        for b, blk in enumerate(self.blocks):
+        if self.pp > 1 and self.pp_rank > 0:
+            h = self._stage_recv(h)
+        for b in range(self.block_lo, self.block_hi):
+            blk = self.blocks[b]
             table = self.tables[level][b]
             with self._range("norm_a", b):
                 n = F.modulated_rmsnorm(h, None, table, idx, 6, SLOT_SHIFT_A, SLOT_SCALE_A,
@@ -472,12 +484,33 @@ class H3Transformer:
                 ff = F.linear(hid, blk.ff2)
             with self._range("gate_m", b):
                 F.gated_residual_(h, ff, table, idx, 6, SLOT_GATE_M)
-        out = F.modulated_rmsnorm(h, None, self.tables_out[level], idx, 2, 0, 1, cfg.eps).float()
         v_lo, v_hi = max(lo, 0), min(hi, layout.n_video)
         a_lo, a_hi = max(lo, layout.n_video), min(hi, layout.n_video + layout.n_audio)
-        vel_v = out[v_lo - lo:max(v_hi, v_lo) - lo] @ self.proj_out.t()
-        vel_a = out[a_lo - lo:max(a_hi, a_lo) - lo] @ self.audio_proj_out.t()
+        nv, na = max(v_hi, v_lo) - v_lo, max(a_hi, a_lo) - a_lo
+        last = self.pp - 1
+        if self.pp > 1 and self.pp_rank != last:
+            self._stage_send(h)
+            vel_v = torch.empty(nv, cfg.patch_width, dtype=torch.float32, device=h.device)
+            vel_a = torch.empty(na, cfg.audio_channels, dtype=torch.float32, device=h.device)
+        else:
+            out = F.modulated_rmsnorm(h, None, self.tables_out[level], idx, 2, 0, 1,
+                                      cfg.eps).float()
+            vel_v = out[v_lo - lo:v_lo - lo + nv] @ self.proj_out.t()
+            vel_a = out[a_lo - lo:a_lo - lo + na] @ self.audio_proj_out.t()
+        if self.pp > 1:      # every stage advances the same latents
+            vel_v = self.ctx.broadcast(vel_v.contiguous(), last, "layer")
+            vel_a = self.ctx.broadcast(vel_a.contiguous(), last, "layer")
         return vel_v, vel_a
+
+    def _stage_send(self, h: torch.Tensor) -> None:
+        import torch.distributed as dist
+        dist.send(h.contiguous(), self.pp_axis.ranks[self.pp_rank + 1], group=self.pp_axis.group)
+
+    def _stage_recv(self, like: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+        h = torch.empty_like(like)
+        dist.recv(h, self.pp_axis.ranks[self.pp_rank - 1], group=self.pp_axis.group)
+        return h
 
     def clone_to(self, device, dtype) -> "H3Transformer":
         """The same weights on another device / in another dtype (tests compare a
@@ -492,7 +525,8 @@ class H3Transformer:
         o.refiner_norm = mv(self.refiner_norm)
         o.refiner = [RefinerBlock(*[mv(getattr(b, f.name)) for f in dataclasses.fields(b)])
                      for b in self.refiner]
-        o.blocks = [H3Block(*[mv(getattr(b, f.name)) for f in dataclasses.fields(b)])
+        o.blocks = [None if b is None else
+                    H3Block(*[mv(getattr(b, f.name)) for f in dataclasses.fields(b)])
                     for b in self.blocks]
         o._adaln_seed = self._adaln_seed
         o.tables = [[t.to(o.device) for t in lv] for lv in self.tables]
@@ -502,7 +536,8 @@ class H3Transformer:
     def weight_bytes(self) -> int:
         n = 0
         for b in self.blocks:
-            n += b.qkv.numel() + b.to_out.numel() + b.ff1.numel() + b.ff2.numel()
+            if b is not None:
+                n += b.qkv.numel() + b.to_out.numel() + b.ff1.numel() + b.ff2.numel()
         return n * 2
 
 
