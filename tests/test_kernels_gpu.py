@@ -311,3 +311,18 @@ def test_fence_probes_stamp_the_stream_in_order():
     assert rows[1][1] > rows[0][1] > 0 and rows[0][3] == 7
     assert (rows[1][1] - rows[0][1]) < 1e9          # a sub-second GEMM
     assert ring.collect() == [] and y.shape == (4096, 4096)
+
+
+@pytest.mark.parametrize("T,E,k", [(64, 128, 8), (5, 16, 4), (300, 128, 8)])
+def test_route_and_sort_equals_the_two_kernels(T, E, k):
+    H, I = 256, 128
+    logits = rnd(T, E, dtype=torch.float32, seed=21)
+    ids0, w0 = F.topk_softmax(logits, k, True)
+    ws = F.MoeWorkspace.create(T, k, E // 2, H, I, DEV)
+    ids1, w1 = F.route_and_sort(logits, k, True, ws, E // 2, E // 2)
+    assert torch.equal(ids0, ids1) and torch.equal(w0, w1)
+    x = rnd(T, H, seed=22)
+    w13, w2 = rnd(E // 2, 2 * I, H, scale=0.05, seed=23), rnd(E // 2, H, I, scale=0.05, seed=24)
+    a = F.moe_experts(x, ids0, w0, w13, w2, e_lo=E // 2)
+    b = F.moe_experts(x, ids1, w1, w13, w2, e_lo=E // 2, ws=ws, presorted=True)
+    close(a, b, 1e-3, 1e-3)

@@ -239,19 +239,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (a.causal) lim = min(lim, q_idx + shift - kbase + 1);
       if (SPARSE) lim = a.valid[my_blocks[j]];
       const bool need_mask = lim < kBN;   // per-thread; the loads below stay uniform
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kBN; c += 32) {
-        uint32_t v[32];
-        tc::tmem_ld32(s_tmem + c, v);
-        tc::tmem_ld_wait();
+      // The whole row of S goes to registers in one round trip; four independent
+      // chains keep the maximum and the sum from serialising on instruction latency.
+      uint32_t v0[32], v1[32], v2[32], v3[32];
+      tc::tmem_ld32(s_tmem, v0);
+      tc::tmem_ld32(s_tmem + 32, v1);
+      tc::tmem_ld32(s_tmem + 64, v2);
+      tc::tmem_ld32(s_tmem + 96, v3);
+      tc::tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]);
-          if (need_mask && c + i >= lim) x = -INFINITY;
-          mx = fmaxf(mx, x);
+          if (i >= lim) v0[i] = 0xff800000u;
+          if (32 + i >= lim) v1[i] = 0xff800000u;
+          if (64 + i >= lim) v2[i] = 0xff800000u;
+          if (96 + i >= lim) v3[i] = 0xff800000u;
         }
       }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        mx0 = fmaxf(mx0, __uint_as_float(v0[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(v1[i]));
+        mx2 = fmaxf(mx2, __uint_as_float(v2[i]));
+        mx3 = fmaxf(mx3, __uint_as_float(v3[i]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = fmaxf(m_used, mx * a.scale_log2);
       const bool grow = m_new - m_used > kRescaleThreshold;   // -inf start counts as growth
       const bool any_grow = __any_sync(0xffffffffu, grow || (m_used == -INFINITY && m_new > -INFINITY));
@@ -278,21 +291,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_used = m_new;
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-#pragma unroll 1
-      for (int c = 0; c < kBN; c += 32) {
-        uint32_t v[32];
-        tc::tmem_ld32(s_tmem + c, v);
-        tc::tmem_ld_wait();
+      const float neg_m = -m_eff;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      auto exp_chunk = [&](const uint32_t (&v)[32], int c, float& l) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2f(__uint_as_float(v[i]) * a.scale_log2 - m_eff);
-          float p1 = ex2f(__uint_as_float(v[i + 1]) * a.scale_log2 - m_eff);
-          if (need_mask) {
-            if (c + i >= lim) p0 = 0.f;
-            if (c + i + 1 >= lim) p1 = 0.f;
-          }
-          l_sum += p0 + p1;
+          const float p0 = ex2f(fmaf(__uint_as_float(v[i]), a.scale_log2, neg_m));
+          const float p1 = ex2f(fmaf(__uint_as_float(v[i + 1]), a.scale_log2, neg_m));
+          l += p0 + p1;
           __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
           packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
         }
@@ -303,7 +310,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           *reinterpret_cast<uint4*>(prow + tc::sw128_offset(r, chunk0 + q4)) =
               make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2],
                          packed[4 * q4 + 3]);
-      }
+      };
+      exp_chunk(v0, 0, l0);
+      exp_chunk(v1, 32, l1);
+      exp_chunk(v2, 64, l2);
+      exp_chunk(v3, 96, l3);
+      l_sum += (l0 + l1) + (l2 + l3);
       tc::tc_fence_before_sync();
       tc::mbar_arrive(&s_empty[b]);
       tc::fence_async_smem();

@@ -23,16 +23,15 @@ namespace {
 constexpr int kMaxExperts = 1024;
 constexpr int kMaxPerLane = kMaxExperts / 32;
 
+// Softmax, top-k and renormalisation of one token's router logits by one warp.
 template <int PER_LANE>
-__global__ void __launch_bounds__(128)
-topk_softmax_kernel(const float* __restrict__ logits, int* __restrict__ ids,
-                    float* __restrict__ weights, int T, int E, int top_k, int renorm,
-                    const int* __restrict__ live, const int* __restrict__ expert_map,
-                    int* __restrict__ load) {
-  US_PDL_PROLOGUE();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= T) return;
+__device__ __forceinline__ void topk_token(const float* __restrict__ logits,
+                                           int* __restrict__ ids, float* __restrict__ weights,
+                                           int t, int E, int top_k, int renorm,
+                                           const int* __restrict__ live,
+                                           const int* __restrict__ expert_map,
+                                           int* __restrict__ load) {
+  const int lane = threadIdx.x & 31;
   if (live && t >= *live) {
     for (int j = lane; j < top_k; j += 32) {
       ids[(long long)t * top_k + j] = -1;
@@ -101,14 +100,25 @@ topk_softmax_kernel(const float* __restrict__ logits, int* __restrict__ ids,
   }
 }
 
-// One CTA sorts all routes.  Local experts are [e_lo, e_lo + E).
-__global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ ids, int R, int e_lo, int E, int block_n, int max_tiles,
-                int* __restrict__ sorted_route, int* __restrict__ perm_of_route,
-                int* __restrict__ expert_offsets, int* __restrict__ tile_group,
-                int* __restrict__ tile_row0, int* __restrict__ tile_rows,
-                int* __restrict__ num_tiles, unsigned int* status) {
+template <int PER_LANE>
+__global__ void __launch_bounds__(128)
+topk_softmax_kernel(const float* __restrict__ logits, int* __restrict__ ids,
+                    float* __restrict__ weights, int T, int E, int top_k, int renorm,
+                    const int* __restrict__ live, const int* __restrict__ expert_map,
+                    int* __restrict__ load) {
   US_PDL_PROLOGUE();
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  topk_token<PER_LANE>(logits, ids, weights, t, E, top_k, renorm, live, expert_map, load);
+}
+
+// One CTA sorts all routes.  Local experts are [e_lo, e_lo + E).
+__device__ __forceinline__ void
+sort_routes(const int* __restrict__ ids, int R, int e_lo, int E, int block_n, int max_tiles,
+            int* __restrict__ sorted_route, int* __restrict__ perm_of_route,
+            int* __restrict__ expert_offsets, int* __restrict__ tile_group,
+            int* __restrict__ tile_row0, int* __restrict__ tile_rows,
+            int* __restrict__ num_tiles, unsigned int* status) {
   __shared__ int cnt[kMaxExperts];
   __shared__ int off[kMaxExperts + 1];
   __shared__ int toff[kMaxExperts + 1];
@@ -188,6 +198,36 @@ moe_sort_kernel(const int* __restrict__ ids, int R, int e_lo, int E, int block_n
       perm_of_route[i] = -1;
     }
   }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ ids, int R, int e_lo, int E, int block_n, int max_tiles,
+                int* __restrict__ sorted_route, int* __restrict__ perm_of_route,
+                int* __restrict__ expert_offsets, int* __restrict__ tile_group,
+                int* __restrict__ tile_row0, int* __restrict__ tile_rows,
+                int* __restrict__ num_tiles, unsigned int* status) {
+  US_PDL_PROLOGUE();
+  sort_routes(ids, R, e_lo, E, block_n, max_tiles, sorted_route, perm_of_route, expert_offsets,
+              tile_group, tile_row0, tile_rows, num_tiles, status);
+}
+
+// Routing and sorting in one launch (decode-size batches): the CTA's 32 warps take the
+// tokens in turn, then the whole CTA sorts the routes they wrote.
+template <int PER_LANE>
+__global__ void __launch_bounds__(1024)
+route_sort_kernel(const float* __restrict__ logits, int* __restrict__ ids,
+                  float* __restrict__ weights, int T, int E_all, int top_k, int renorm,
+                  const int* __restrict__ live, int e_lo, int E, int block_n, int max_tiles,
+                  int* __restrict__ sorted_route, int* __restrict__ perm_of_route,
+                  int* __restrict__ expert_offsets, int* __restrict__ tile_group,
+                  int* __restrict__ tile_row0, int* __restrict__ tile_rows,
+                  int* __restrict__ num_tiles, unsigned int* status) {
+  US_PDL_PROLOGUE();
+  for (int t = threadIdx.x >> 5; t < T; t += 32)
+    topk_token<PER_LANE>(logits, ids, weights, t, E_all, top_k, renorm, live, nullptr, nullptr);
+  __syncthreads();   // the routes written above are read below by other threads of the CTA
+  sort_routes(ids, T * top_k, e_lo, E, block_n, max_tiles, sorted_route, perm_of_route,
+              expert_offsets, tile_group, tile_row0, tile_rows, num_tiles, status);
 }
 
 __global__ void __launch_bounds__(256)
@@ -278,4 +318,35 @@ US_API int us_moe_unpermute(const void* y, const int* perm_of_route, const float
   us::launch_pdl(moe_unpermute_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream_, (const __nv_bfloat16*)y, perm_of_route, weights, top_k, H, (__nv_bfloat16*)out);
   US_LAUNCH_CHECK();
   return US_OK;
+}
+
+// topk_softmax followed by moe_sort in one launch, for batches of at most 512 tokens.
+US_API int us_route_sort(const float* logits, int* ids, float* weights, int T, int E_all,
+                         int top_k, int renorm, const int* live, int e_lo, int E, int block_n,
+                         int max_tiles, int* sorted_route, int* perm_of_route,
+                         int* expert_offsets, int* tile_group, int* tile_row0, int* tile_rows,
+                         int* num_tiles, void* stream_) {
+  US_REQUIRE(logits && ids && weights && T >= 1 && T <= 512 && E_all >= 1 &&
+             E_all <= kMaxExperts && top_k >= 1 && top_k <= 32 && top_k <= E_all);
+  US_REQUIRE(E >= 1 && E <= kMaxExperts && block_n >= 1 && max_tiles >= 1 && sorted_route &&
+             perm_of_route && expert_offsets && tile_group && tile_row0 && tile_rows && num_tiles);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int per = (E_all + 31) / 32;
+#define US_RS_CASE(P)                                                                          \
+  if (per <= P) {                                                                              \
+    US_CUDA_CHECK(us::launch_pdl(route_sort_kernel<P>, dim3(1), dim3(1024), 0, stream, logits, \
+                                 ids, weights, T, E_all, top_k, renorm, live, e_lo, E, block_n,\
+                                 max_tiles, sorted_route, perm_of_route, expert_offsets,       \
+                                 tile_group, tile_row0, tile_rows, num_tiles,                  \
+                                 us_status_ptr()));                                            \
+    return US_OK;                                                                              \
+  }
+  US_RS_CASE(1)
+  US_RS_CASE(2)
+  US_RS_CASE(4)
+  US_RS_CASE(8)
+  US_RS_CASE(16)
+  US_RS_CASE(32)
+#undef US_RS_CASE
+  return US_ERR_ARG;
 }

@@ -95,6 +95,11 @@ class Qwen3MoeConfig:
                    moe_intermediate_size=1536, intermediate_size=12288)
 
 
+import os as _os
+
+FUSED_ROUTE_SORT = _os.environ.get("US_NO_ROUTE_SORT", "0") != "1"   # A/B switch
+
+
 @dataclass
 class LayerWeights:
     input_norm: torch.Tensor
@@ -379,7 +384,6 @@ class Qwen3MoeModel:
                 else:
                     self.exchange.experts(lw.w13, lw.w2, T)
             return x, ("ep", ids)
-        ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
         ws = None
         if x.is_cuda:
             key = (T, x.device)
@@ -388,6 +392,13 @@ class Qwen3MoeModel:
                 ws = F.MoeWorkspace.create(T, cfg.num_experts_per_tok, self.E_local,
                                            cfg.hidden_size, cfg.moe_intermediate_size, x.device)
                 self._moe_ws[key] = ws
+        # decode-size batches route and sort in one launch
+        presorted = x.is_cuda and T <= 512 and lw.fp8 is None and FUSED_ROUTE_SORT
+        if presorted:
+            ids, weights = F.route_and_sort(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob,
+                                            ws, self.e_lo, self.E_local)
+        else:
+            ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
         reduce = self.ctx.ep_size > 1
         site, buf = self._partial_out(fc if reduce else None, T)
         if lw.fp8 is not None:
@@ -398,7 +409,8 @@ class Qwen3MoeModel:
                     cfg.moe_intermediate_size, x.device, block_n=64)
             out = moe_experts_fp8(x, ids, weights, lw.fp8, e_lo=self.e_lo, ws=ws, out=buf)
         else:
-            out = F.moe_experts(x, ids, weights, lw.w13, lw.w2, e_lo=self.e_lo, ws=ws, out=buf)
+            out = F.moe_experts(x, ids, weights, lw.w13, lw.w2, e_lo=self.e_lo, ws=ws, out=buf,
+                                presorted=presorted)
         if reduce and site is None:
             out = self.ctx.all_reduce_tp(out)
         return out, site

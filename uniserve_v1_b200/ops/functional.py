@@ -299,7 +299,21 @@ class MoeWorkspace:
             block_n=block_n, max_tiles=max_tiles)
 
 
-def moe_experts(x, ids, weights, w13, w2, e_lo=0, act="silu", stepwise=False, ws=None, out=None):
+def route_and_sort(logits, top_k, renorm, ws, e_lo, E_local):
+    """``topk_softmax`` and the route sort of ``moe_experts`` in one launch (at most 512
+    tokens); the workspace is then passed to ``moe_experts(..., presorted=True)``."""
+    T, E_all = logits.shape
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    weights = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    N.call("us_route_sort", N.ptr(logits), N.ptr(ids), N.ptr(weights), T, E_all, top_k,
+           int(renorm), None, e_lo, E_local, ws.block_n, ws.max_tiles, N.ptr(ws.sorted_route),
+           N.ptr(ws.perm_of_route), N.ptr(ws.expert_offsets), N.ptr(ws.tile_group),
+           N.ptr(ws.tile_row0), N.ptr(ws.tile_rows), N.ptr(ws.num_tiles), N.stream())
+    return ids, weights
+
+
+def moe_experts(x, ids, weights, w13, w2, e_lo=0, act="silu", stepwise=False, ws=None, out=None,
+                presorted=False):
     """Routed experts: sort routes by local expert, gather rows, grouped FC1 with
     the gated activation fused, grouped FC2, weighted un-permute (FP32, one
     rounding).  w13 [E,2I,H] (first/up rows, then gate rows), w2 [E,H,I]."""
@@ -313,9 +327,11 @@ def moe_experts(x, ids, weights, w13, w2, e_lo=0, act="silu", stepwise=False, ws
         ws = MoeWorkspace.create(T, top_k, E, H, I_, x.device)
     R_ = T * top_k
     st = N.stream()
-    N.call("us_moe_sort", N.ptr(ids), R_, e_lo, E, ws.block_n, ws.max_tiles,
-           N.ptr(ws.sorted_route), N.ptr(ws.perm_of_route), N.ptr(ws.expert_offsets),
-           N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows), N.ptr(ws.num_tiles), st)
+    if not presorted:
+        N.call("us_moe_sort", N.ptr(ids), R_, e_lo, E, ws.block_n, ws.max_tiles,
+               N.ptr(ws.sorted_route), N.ptr(ws.perm_of_route), N.ptr(ws.expert_offsets),
+               N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
+               N.ptr(ws.num_tiles), st)
     total = ws.expert_offsets[E:]
     N.call("us_moe_gather", N.ptr(x), N.ptr(ws.sorted_route), N.ptr(total), R_, top_k, H,
            N.ptr(ws.xp), st)

@@ -51,6 +51,7 @@ _SIGNATURES = {
     "us_paged_decode_attention_tc": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, L, L, P]),
     "us_topk_softmax": (I, [P, P, P, I, I, I, I, P, P, P, P]),
     "us_moe_sort": (I, [P, I, I, I, I, I, P, P, P, P, P, P, P, P]),
+    "us_route_sort": (I, [P, P, P, I, I, I, I, P, I, I, I, I, P, P, P, P, P, P, P, P]),
     "us_moe_gather": (I, [P, P, P, I, I, I, P, P]),
     "us_moe_unpermute": (I, [P, P, P, I, I, I, P, P]),
     "us_argmax": (I, [P, I, I, L, P, P]),
