@@ -326,3 +326,47 @@ def test_route_and_sort_equals_the_two_kernels(T, E, k):
     a = F.moe_experts(x, ids0, w0, w13, w2, e_lo=E // 2)
     b = F.moe_experts(x, ids1, w1, w13, w2, e_lo=E // 2, ws=ws, presorted=True)
     close(a, b, 1e-3, 1e-3)
+
+
+def _ptr_array(tensors):
+    import ctypes
+    return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def test_gemm_peer_modes_with_local_buffers_as_peers():
+    """The four peer modes of the GEMM (operand tiles pulled from per-rank K slices or
+    per-rank row intervals; output tiles scattered by feature or reduce-scattered by row)
+    with local tensors standing in for the peers' buffers."""
+    from uniserve_v1_b200.parallel import tp_fused, ulysses  # noqa: F401  (register signatures)
+    rows, K, M, P = 320, 512, 384, 2
+    x, w = rnd(rows, K, seed=31), rnd(M, K, scale=0.05, seed=32)
+    ref = x.float() @ w.float().t()
+    st = N.stream()
+    # pull: K is the concatenation of two peers' [rows, K / 2] buffers
+    parts = [x[:, :K // 2].contiguous(), x[:, K // 2:].contiguous()]
+    out = torch.empty(rows, M, dtype=BF, device=DEV)
+    N.call("us_gemm_wx_pull", N.ptr(w), _ptr_array(parts), P, K // 2, N.ptr(out), M, K, rows, K,
+           K // 2, M, 0, 64, st)
+    close(out, ref, 3e-2, 3e-2)
+    # gather: the rows are the concatenation of two peers' [rows / 2, K] buffers
+    halves = [x[:rows // 2].contiguous(), x[rows // 2:].contiguous()]
+    out2 = torch.empty(rows, M, dtype=BF, device=DEV)
+    N.call("us_gemm_wx_gather", N.ptr(w), _ptr_array(halves), P, rows // 2, N.ptr(out2), M, M, K,
+           rows, K, K, M, 0, 0, 0, 0, 32, st)
+    close(out2, ref, 3e-2, 3e-2)
+    # scatter: features [p * M / 2, ...) go to peer p at row offset 16
+    wide = rnd(256, K, scale=0.05, seed=33)            # 2 x 128 features
+    dst = [torch.zeros(rows + 16, 128, dtype=BF, device=DEV) for _ in range(P)]
+    N.call("us_gemm_wx_scatter", N.ptr(wide), N.ptr(x), 256, K, rows, K, K, 128, _ptr_array(dst),
+           128, 16, 64, st)
+    refw = x.float() @ wide.float().t()
+    for p_ in range(P):
+        close(dst[p_][16:], refw[:, p_ * 128:(p_ + 1) * 128], 3e-2, 3e-2)
+        assert float(dst[p_][:16].abs().max()) == 0.0
+    # reduce-scatter: rows [p * rows / 2, ...) go to peer p, slot 1 of 2
+    slots = [torch.zeros(2, rows // 2, M, dtype=BF, device=DEV) for _ in range(P)]
+    N.call("us_gemm_wx_reduce_scatter", N.ptr(w), N.ptr(x), M, K, rows, K, K, M,
+           _ptr_array(slots), P, rows // 2, 1, 0, 32, st)
+    for p_ in range(P):
+        close(slots[p_][1], ref[p_ * (rows // 2):(p_ + 1) * (rows // 2)], 3e-2, 3e-2)
+        assert float(slots[p_][0].abs().max()) == 0.0
