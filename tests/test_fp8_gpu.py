@@ -95,3 +95,21 @@ def test_moe_experts_fp8(T, E, k, H, I):
             h = qd(h[None])[0]
             ref[t] += float(wts[t, j]) * (w2f[e] @ h).to(BF).float()
     torch.testing.assert_close(out.float().cpu(), ref, rtol=4e-2, atol=4e-2)
+
+
+@pytest.mark.parametrize("T,K,M,gated", [(300, 512, 384, False), (1000, 1024, 640, True),
+                                         (64, 256, 128, False)])
+def test_linear_fp8_per_tensor(T, K, M, gated):
+    """Per-tensor weight scale, per-row dynamic activation scale, whole-K accumulation in
+    tensor memory: against the FP32 product of the same quantised operands."""
+    x = rnd(T, K, seed=41)
+    w = rnd(2 * M if gated else M, K, scale=0.05, seed=42)
+    wq, ws = Q.quantize_weight_tensor(w)
+    out = Q.linear_fp8(x, wq, ws, gated=gated)
+    ref = Q.linear_fp8(x.cpu(), wq.cpu(), ws, gated=gated)
+    torch.testing.assert_close(out.float().cpu(), ref.float(), rtol=2e-2, atol=2e-2)
+    yf = x.float().cpu() @ w.float().cpu().t()
+    if gated:
+        yf = yf[:, :M] * torch.nn.functional.silu(yf[:, M:])
+    err = (out.float().cpu() - yf).norm() / yf.norm()
+    assert err < 0.08, err

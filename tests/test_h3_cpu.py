@@ -143,3 +143,19 @@ def test_sparse_attention_student_reduces_to_dense_when_every_tile_is_kept():
         outs.append(st.video)
     assert st.layout.tile_sizes is None and outs[0].shape == outs[1].shape
     torch.testing.assert_close(outs[0], outs[1], atol=2e-2, rtol=2e-2)
+
+
+def test_fp8_feed_forward_stays_close_to_bf16():
+    outs = []
+    for f8 in (False, True):
+        cfg = H3Config.tiny()
+        cfg.mlp_fp8 = f8
+        model = H3Transformer(cfg, "cpu", torch.float32).init_random(seed=0)
+        assert (model.blocks[0].ff1.dtype == torch.uint8) == f8
+        den = Denoiser(model, dmd_ladder((999, 500), 10.0), dmd_ladder((999, 500), 3.0))
+        g = torch.Generator().manual_seed(5)
+        text = torch.randn(9, cfg.text_dim, generator=g)
+        st = den.prepare(seed=1, latent_frames=2, lat_h=4, lat_w=4, n_audio=6, text_features=text)
+        den.run(st)
+        outs.append(st.video)
+    assert float((outs[0] - outs[1]).norm() / outs[0].norm()) < 1e-2

@@ -291,6 +291,37 @@ quantize_rows_block128_kernel(const __nv_bfloat16* __restrict__ x, long long ldx
   if (lane == 0) scales[(long long)kb * xs_ld + row] = scale;
 }
 
+// One CTA per row: amax over the whole row -> scale = amax / 448 (1 for a zero row),
+// q = x / scale; out_scale[row] = scale * weight_scale (what the GEMM epilogue applies).
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q,
+                     long long ldq, float* __restrict__ out_scale, int K, float weight_scale) {
+  US_PDL_PROLOGUE();
+  __shared__ float scratch[33];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * ldx;
+  uint8_t* qr = q + row * ldq;
+  float amax = 0.f;
+  for (int v = threadIdx.x; v < (K >> 3); v += 256) {
+    us::Pack16 p;
+    p.u = *reinterpret_cast<const uint4*>(xr + v * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(us::bf2f(p.b[i])));
+  }
+  amax = us::block_max(amax, scratch);
+  const float scale = amax > 0.f ? amax / 448.f : 1.f;
+  const float inv = 1.f / scale;
+  for (int v = threadIdx.x; v < (K >> 3); v += 256) {
+    us::Pack16 p;
+    p.u = *reinterpret_cast<const uint4*>(xr + v * 8);
+    uint8_t o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = to_e4m3(us::bf2f(p.b[i]) * inv);
+    *reinterpret_cast<uint2*>(qr + v * 8) = *reinterpret_cast<const uint2*>(o);
+  }
+  if (threadIdx.x == 0) out_scale[row] = scale * weight_scale;
+}
+
 // Per-tensor quantisation with a given scale (q = x / scale), or, when
 // `amax_in` is set, with scale = *amax_in / 448 computed on the device.
 __global__ void __launch_bounds__(256)
@@ -380,6 +411,7 @@ int fp8_impl(const void* Wq, const float* w_scale, const void* Xq, const float* 
   for (int p = 0; p < 8; ++p) a.peer_out[p] = nullptr;
   a.route_map = nullptr; a.route_w = nullptr; a.route_per = 0;
   a.vec_store = 0;
+  a.scale_first = 0;
   if (rs.route_map) {
     US_REQUIRE(rs.recv_peers && rs.route_w && rs.route_per > 0 && rs.n_peers >= 1 &&
                rs.n_peers <= 8 && out_dtype == 0 && !dual);
@@ -495,5 +527,19 @@ US_API int us_fp8_quantize_tensor(const void* x, void* q, long long n, float sca
   US_CUDA_CHECK(us::launch_pdl(quantize_tensor_kernel, dim3(blocks), dim3(256), 0, stream,
                                (const __nv_bfloat16*)x, (uint8_t*)q, n, scale,
                                (const float*)amax_scratch, scale_out));
+  return US_OK;
+}
+
+// x [rows, K] bf16 -> q [rows, K] e4m3 with one dynamic scale per row; out_scale[row] =
+// row scale * weight_scale.
+US_API int us_fp8_quantize_rows(const void* x, long long ldx, void* q, long long ldq,
+                                float* out_scale, int rows, int K, float weight_scale,
+                                void* stream) {
+  US_REQUIRE(x && q && out_scale && rows >= 0 && K >= 8 && (K % 8) == 0 && (ldx % 8) == 0 &&
+             (ldq % 8) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)q % 8) == 0);
+  if (rows == 0) return US_OK;
+  US_CUDA_CHECK(us::launch_pdl(quantize_rows_kernel, dim3(rows), dim3(256), 0,
+                               (cudaStream_t)stream, (const __nv_bfloat16*)x, ldx, (uint8_t*)q,
+                               ldq, out_scale, K, weight_scale));
   return US_OK;
 }

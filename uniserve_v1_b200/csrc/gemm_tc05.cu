@@ -14,6 +14,8 @@
 // row map) and the dual-accumulator gated activation out = first * act(second)
 // used by the experts' FC1 (first = up rows, second = gate rows of the stacked
 // weight) and the video transformer's value-first SwiGLU.
+#include <string.h>
+
 #include "include/us_common.cuh"
 #include "include/us_tc05.cuh"
 #include "include/us_tmap.h"
@@ -214,23 +216,27 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // activation tile in L2); two TMEM accumulators let the epilogue of tile i run
 // under the multiplications of tile i + 1, and the TMA ring never drains
 // between tiles.
-template <int BN, bool DUAL>
+template <int BN, bool DUAL, bool FP8>
 __global__ void __launch_bounds__(192)
 gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
                        const __grid_constant__ BMaps tmBs, const GemmArgs args) {
   US_PDL_PROLOGUE();
+  // A k-block is 128 bytes of K either way: 64 bf16 or 128 e4m3 elements, four
+  // tensor-core instructions (K = 16 resp. 32 each).
+  constexpr int kBK = FP8 ? 2 * kBlockK : kBlockK;
   constexpr int kBTile = BN * kBlockK * 2;
   constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
   constexpr uint32_t kAccCols = DUAL ? 2 * BN : BN;
   constexpr uint32_t kCols = tmem_cols<2 * BN>(DUAL);
   static_assert(kCols <= 512, "two accumulators must fit tensor memory");
-  constexpr uint32_t kIdesc = tc::make_idesc(kBlockM, BN, tc::kFmtBF16, tc::kFmtBF16);
+  constexpr uint32_t kIdesc = FP8 ? tc::make_idesc(kBlockM, BN, tc::kFmtE4M3, tc::kFmtE4M3)
+                                  : tc::make_idesc(kBlockM, BN, tc::kFmtBF16, tc::kFmtBF16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (args.M + kBlockM - 1) / kBlockM;
   const int n_tiles = (args.rows + BN - 1) / BN;
   const int total = m_tiles * n_tiles;
-  const int num_k = (args.K + kBlockK - 1) / kBlockK;
+  const int num_k = (args.K + kBK - 1) / kBK;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -285,7 +291,7 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           uint8_t* st = smem + (size_t)s * kStageBytes;
           tc::mbar_expect_tx(&full_bar[s], kStageBytes);
-          const int kx = kb * kBlockK;
+          const int kx = kb * kBK;
           tc::tma_load_3d(st, &tmA, &full_bar[s], kx, m_tile * kBlockM, 0);
           if (DUAL)
             tc::tma_load_3d(st + kATile, &tmA, &full_bar[s], kx,
@@ -333,10 +339,16 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
           for (int k = 0; k < kBlockK / 16; ++k) {
             const uint32_t acc = (kb | k) != 0;
-            tc::umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            if (FP8)
+              tc::umma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            else
+              tc::umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
             if (DUAL) {
               const uint64_t a2desc = tc::smem_desc_kmajor_sw128(a_addr + kATile);
-              tc::umma_f16(d + BN, a2desc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+              if (FP8)
+                tc::umma_f8(d + BN, a2desc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+              else
+                tc::umma_f16(d + BN, a2desc + 2 * k, bdesc + 2 * k, kIdesc, acc);
             }
           }
           tc::umma_commit(&empty_bar[s]);
@@ -385,7 +397,7 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
   }
 }
 
-template <int BN, bool DUAL>
+template <int BN, bool DUAL, bool FP8 = false>
 int launch_persist(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int tiles,
                    cudaStream_t stream) {
   constexpr int kBTile = BN * kBlockK * 2;
@@ -398,7 +410,7 @@ int launch_persist(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int til
   static bool configured = false;
   static int sms = 0;
   if (!configured) {
-    US_CUDA_CHECK(cudaFuncSetAttribute(gemm_wx_persist_kernel<BN, DUAL>,
+    US_CUDA_CHECK(cudaFuncSetAttribute(gemm_wx_persist_kernel<BN, DUAL, FP8>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     int dev = 0;
     US_CUDA_CHECK(cudaGetDevice(&dev));
@@ -406,7 +418,7 @@ int launch_persist(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int til
     configured = true;
   }
   const int grid = tiles < sms ? tiles : sms;
-  US_CUDA_CHECK(us::launch_pdl(gemm_wx_persist_kernel<BN, DUAL>, dim3(grid), dim3(192), smem,
+  US_CUDA_CHECK(us::launch_pdl(gemm_wx_persist_kernel<BN, DUAL, FP8>, dim3(grid), dim3(192), smem,
                                stream, tmA, tmB, a));
   return US_OK;
 }
@@ -559,6 +571,7 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
   a.route_map = nullptr;
   a.route_w = nullptr;
   a.route_per = 0;
+  a.scale_first = 0;
   if (ps.route_map) {
     US_REQUIRE(ps.out_peers && ps.route_w && ps.route_per > 0 && ps.n_out_peers >= 1 &&
                ps.n_out_peers <= 8 && out_dtype == 0);
@@ -731,4 +744,42 @@ US_API int us_gemm_wx_reduce_scatter(const void* W, const void* X, int M, int K,
   return gemm_impl(W, X, nullptr, 1, M, M, K, x_rows, ldw, ldx, ldo, 0, 0, 0, out_dtype, nullptr,
                    0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, block_n, ps,
                    (cudaStream_t)stream_);
+}
+
+// Per-tensor (or per-row) scaled FP8 GEMM: Wq [w_rows, K] and Xq [x_rows, K] are E4M3
+// bytes; the product accumulates over the whole K in tensor memory and the epilogue
+// multiplies row r by row_scale[r] (activation scale x weight scale).  With `dual`
+// the scale is applied to both halves before the gated activation.  Persistent kernel.
+US_API int us_gemm_fp8_rowscale(const void* Wq, const void* Xq, void* out, int w_rows, int M,
+                                int K, int x_rows, long long ldw, long long ldx, long long ldo,
+                                int dual, int dual_offset, int act, int out_dtype,
+                                const float* row_scale, int block_n, void* stream_) {
+  US_REQUIRE(Wq && Xq && out && row_scale && M >= 1 && K >= 128 && (K % 16) == 0 && x_rows >= 1);
+  US_REQUIRE((ldw % 16) == 0 && (ldx % 16) == 0 && ((uintptr_t)Wq % 16) == 0 &&
+             ((uintptr_t)Xq % 16) == 0);
+  US_REQUIRE(dual ? block_n == 128 : (block_n == 128 || block_n == 256));
+  CUtensorMap tmA;
+  BMaps tmB;
+  int rc = us_tmap_3d(&tmA, Wq, US_TMAP_U8, 1, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw,
+                      (uint64_t)w_rows * (uint64_t)ldw, kBlockM, 2 * kBlockK, US_SWZ_128);
+  if (rc) return rc;
+  rc = us_tmap_2d(&tmB.m[0], Xq, US_TMAP_U8, (uint64_t)x_rows, (uint64_t)K, (uint64_t)ldx,
+                  (uint32_t)block_n, 2 * kBlockK, US_SWZ_128);
+  if (rc) return rc;
+  for (int p = 1; p < 8; ++p) tmB.m[p] = tmB.m[0];
+  GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.M = M; a.K = K; a.rows = x_rows; a.dual_offset = dual_offset; a.act = act;
+  a.out_dtype = out_dtype; a.ldo = ldo; a.out = out; a.row_scale = row_scale;
+  a.scale_first = 1;
+  a.status = us_status_ptr(); a.splits = 1;
+  const long long esz = out_dtype == 0 ? 2 : 4;
+  a.vec_store = (((ldo * esz) % 16) == 0 && ((uintptr_t)out % 16) == 0) ? 1 : 0;
+  const int m_tiles = (M + kBlockM - 1) / kBlockM;
+  const int n_tiles = (x_rows + block_n - 1) / block_n;
+  const int tiles = m_tiles * n_tiles;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (dual) return launch_persist<128, true, true>(tmA, tmB, a, tiles, stream);
+  if (block_n == 128) return launch_persist<128, false, true>(tmA, tmB, a, tiles, stream);
+  return launch_persist<256, false, true>(tmA, tmB, a, tiles, stream);
 }

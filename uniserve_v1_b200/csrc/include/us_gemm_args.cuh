@@ -50,6 +50,9 @@ struct GemmArgs {
   // 1 when every destination row starts on a 16-byte boundary (base pointers and
   // row pitch): the epilogue then stores 16-byte pieces through a staging tile.
   int vec_store;
+  // 1: the row scale multiplies both accumulators before the gated activation
+  // (scaled low-precision operands); 0: it multiplies the finished value.
+  int scale_first;
   // Route push (expert-parallel combine): permuted row r carries route
   // i = route_map[r] = (source rank * route_per + token * top_k + slot); the epilogue
   // multiplies by the gate weight route_w[i] and stores the row into the source
@@ -123,6 +126,11 @@ struct Epilogue {
   }
   // Value of tile row r for this thread's feature (everything but the store).
   __device__ __forceinline__ float value(int r, float val, float gate) const {
+    if (a.scale_first && a.row_scale != nullptr) {
+      const float sc = a.row_scale[row0 + r];
+      val *= sc;
+      gate *= sc;
+    }
     if (DUAL) {
       if (a.act == 0) {
         val = val * silu_f(gate);
@@ -135,7 +143,7 @@ struct Epilogue {
     }
     val += bias;
     if (a.route_map != nullptr) return val * a.route_w[a.route_map[row0 + r]];
-    if (a.row_scale != nullptr) val *= a.row_scale[row0 + r];
+    if (a.row_scale != nullptr && !a.scale_first) val *= a.row_scale[row0 + r];
     return val;
   }
   // Destination of tile row r, feature m0 (null = the row is dropped).

@@ -72,6 +72,9 @@ class H3Config:
     # Video sparse attention (sparse students): fraction of the video key tiles a query
     # tile does NOT read; 0 = dense attention.  Tiles are 128 rows.
     vsa_sparsity: float = 0.0
+    # Feed-forward projections in FP8 (E4M3): per-tensor weight scale, per-row dynamic
+    # activation scale (the reference's "FP8 MLPs" deployment); attention stays bf16.
+    mlp_fp8: bool = False
 
     @property
     def patch_width(self) -> int:
@@ -221,6 +224,8 @@ class H3Block:
     ff2: torch.Tensor        # [hidden, ffn]
     # With sparse attention ``qkv`` carries a fourth projection per rank
     # (to_gate_compress): rows [q | k | v | gate] per destination rank.
+    ff1_scale: Optional[float] = None   # set: ff1 / ff2 hold E4M3 bytes with these scales
+    ff2_scale: Optional[float] = None
 
 
 @dataclass
@@ -290,6 +295,10 @@ class H3Transformer:
             blk = H3Block(self._group_qkv(q, k, v, gate), ones(D), ones(D), rnd(H, inner),
                           rnd(2 * Fn, H), rnd(H, Fn))
             own = self.block_lo <= len(self.blocks) < self.block_hi
+            if own and cfg.mlp_fp8:
+                from ..ops.fp8 import quantize_weight_tensor
+                blk.ff1, blk.ff1_scale = quantize_weight_tensor(blk.ff1)
+                blk.ff2, blk.ff2_scale = quantize_weight_tensor(blk.ff2)
             self.blocks.append(blk if own else None)
         self.proj_out = rnd(cfg.patch_width, H, dtype=torch.float32)
         self.audio_proj_out = rnd(cfg.audio_channels, H, dtype=torch.float32)
@@ -478,10 +487,17 @@ class H3Transformer:
                 F.gated_residual_(h, u, table, idx, 6, SLOT_GATE_A)
                 n2 = F.modulated_rmsnorm(h, None, table, idx, 6, SLOT_SHIFT_M, SLOT_SCALE_M,
                                          cfg.eps)
-            with self._range("ff1", b):
-                hid = F.linear_gated(n2, blk.ff1, stepwise=True)
-            with self._range("ff2", b):
-                ff = F.linear(hid, blk.ff2)
+            if blk.ff1_scale is not None:
+                from ..ops.fp8 import linear_fp8
+                with self._range("ff1", b):
+                    hid = linear_fp8(n2, blk.ff1, blk.ff1_scale, gated=True, stepwise=True)
+                with self._range("ff2", b):
+                    ff = linear_fp8(hid, blk.ff2, blk.ff2_scale)
+            else:
+                with self._range("ff1", b):
+                    hid = F.linear_gated(n2, blk.ff1, stepwise=True)
+                with self._range("ff2", b):
+                    ff = F.linear(hid, blk.ff2)
             with self._range("gate_m", b):
                 F.gated_residual_(h, ff, table, idx, 6, SLOT_GATE_M)
         v_lo, v_hi = max(lo, 0), min(hi, layout.n_video)

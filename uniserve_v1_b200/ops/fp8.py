@@ -197,3 +197,62 @@ def moe_experts_fp8(x, ids, weights, ex: Fp8Experts, e_lo=0, act="silu", ws=None
     N.call("us_moe_unpermute", N.ptr(ws.y), N.ptr(ws.perm_of_route), N.ptr(weights), T, top_k, H,
            N.ptr(out), st)
     return out
+
+
+# ------------------------------------------------- per-tensor weights, per-row rows ----
+N.register_signatures({
+    "us_gemm_fp8_rowscale": (N.I, [N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.L, N.L, N.L, N.I, N.I, N.I,
+                                   N.I, N.P, N.I, N.P]),
+    "us_fp8_quantize_rows": (N.I, [N.P, N.L, N.P, N.L, N.P, N.I, N.I, N.F, N.P]),
+})
+
+
+def quantize_weight_tensor(w: torch.Tensor):
+    """One scale for the whole tensor (the ModelOpt / dynamic per-tensor form):
+    returns (e4m3 bytes like w, scale as a Python float)."""
+    amax = float(w.float().abs().max())
+    scale = amax / E4M3_MAX if amax > 0 else 1.0
+    q = (w.float() * (1.0 / scale)).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
+    return q, scale
+
+
+def quantize_rows(x: torch.Tensor, weight_scale: float = 1.0):
+    """x [T, K] bf16 -> (q [T, K] uint8 e4m3, out_scale [T] = row scale * weight_scale)."""
+    T, K = x.shape
+    if not _cuda(x):
+        amax = x.float().abs().amax(-1)
+        s = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
+        q = (x.float() * (1.0 / s)[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+        return q, s * weight_scale
+    assert x.dtype == BF16 and x.stride(1) == 1
+    q = torch.empty(T, K, dtype=torch.uint8, device=x.device)
+    s = torch.empty(T, dtype=torch.float32, device=x.device)
+    N.call("us_fp8_quantize_rows", N.ptr(x), x.stride(0), N.ptr(q), K, N.ptr(s), T, K,
+           float(weight_scale), N.stream())
+    return q, s
+
+
+def linear_fp8(x, wq, w_scale: float, gated=False, act="silu", stepwise=False, out_dtype=None):
+    """y = x @ (wq * w_scale).T with per-tensor FP8 weights and per-row dynamic FP8
+    activations, FP32 accumulation over the whole K, scales applied in the epilogue
+    (before the gated activation).  ``wq`` [M (x 2 when gated), K] uint8."""
+    xq, xs = quantize_rows(x, w_scale)
+    rows_w, K = wq.shape
+    M = rows_w // 2 if gated else rows_w
+    T = x.shape[0]
+    odt = out_dtype or BF16
+    if not _cuda(x):
+        y = (xq.view(torch.float8_e4m3fn).float() @ wq.view(torch.float8_e4m3fn).float().t()) * \
+            xs[:, None]
+        if gated:
+            g = y[:, M:]
+            a = torch.nn.functional.silu(g) if act == "silu" else \
+                torch.nn.functional.gelu(g, approximate="tanh")
+            y = y[:, :M] * a
+        return y.to(odt)
+    out = torch.empty(T, M, dtype=odt, device=x.device)
+    code = _ACT["silu_stepwise" if (act == "silu" and stepwise) else act] if gated else 0
+    N.call("us_gemm_fp8_rowscale", N.ptr(wq), N.ptr(xq), N.ptr(out), rows_w, M, K, T, wq.stride(0),
+           K, M, 1 if gated else 0, M if gated else 0, code, 0 if odt == BF16 else 1, N.ptr(xs),
+           128 if gated else 256, N.stream())
+    return out
