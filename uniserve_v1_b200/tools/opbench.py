@@ -53,7 +53,7 @@ def timeit(fn, iters=10, warmup=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["flash", "gemm", "gated", "decode", "moe", "fused-norm",
-                                   "ulysses", "tp", "moe-fp8", "gemm-fp8", "ep"])
+                                   "ulysses", "tp", "moe-fp8", "gemm-fp8", "gemm-fp8t", "ep"])
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=2048)
@@ -158,6 +158,22 @@ def main():
         byts = active * (w13[0].numel() + w2[0].numel()) * 2.0
         out.update(tokens=T, experts=E, active_experts=active, ms=ms, tbs=byts / ms / 1e9,
                    frac_memory=byts / ms / 1e9 / tbs)
+    elif a.op == "gemm-fp8t":
+        # per-tensor weights, per-row activations, whole-K accumulation (persistent kernel);
+        # the reference quotes 1525 TFLOPS for 32768 x 28672 x 5376 with pre-encoded operands
+        from ..ops import fp8 as Q
+        from ..ops import native as N_
+        x, w = rnd(a.rows, a.k), rnd(a.m, a.k)
+        wq, wsc = Q.quantize_weight_tensor(w)
+        xq, xs = Q.quantize_rows(x, wsc)
+        o = torch.empty(a.rows, a.m, dtype=bf, device=dev)
+        run = lambda: N_.call("us_gemm_fp8_rowscale", N_.ptr(wq), N_.ptr(xq), N_.ptr(o), a.m, a.m,
+                              a.k, a.rows, a.k, a.k, a.m, 0, 0, 0, 0, N_.ptr(xs), 256, N_.stream())
+        ms = timeit(run, a.iters)
+        msq = timeit(lambda: Q.quantize_rows(x, wsc), a.iters)
+        flops = 2.0 * a.rows * a.m * a.k
+        out.update(rows=a.rows, m=a.m, k=a.k, ms=ms, tflops=flops / ms / 1e9, quantize_ms=msq,
+                   with_quantize_tflops=flops / (ms + msq) / 1e9)
     elif a.op == "fused-norm":
         # all-reduce + residual + RMSNorm over the peer heap; one rank (its own peer) so a
         # profiler can attach; the 2/8-rank numbers come from bench.py
