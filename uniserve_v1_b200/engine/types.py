@@ -68,7 +68,7 @@ class ErrorClass(enum.Enum):
     FATAL_WORKER_FAILURE = "fatal_worker_failure"
 
 
-@dataclass
+@dataclass(eq=False)      # requests are compared and hashed by identity
 class Request:
     request_id: str
     prompt_ids: list
