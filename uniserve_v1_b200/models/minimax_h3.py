@@ -534,7 +534,12 @@ class H3Transformer:
         import copy
         import dataclasses
         o = H3Transformer(self.cfg, device, dtype, self.ctx)
-        mv = lambda t, keep=False: t.to(device=o.device, dtype=t.dtype if keep else dtype)
+        def mv(t, keep=False):
+            if not isinstance(t, torch.Tensor):
+                return t                                    # scales, absent tensors
+            if t.dtype == torch.uint8:
+                keep = True                                 # quantised bytes stay bytes
+            return t.to(device=o.device, dtype=t.dtype if keep else dtype)
         for name in ("proj_in", "audio_proj_in", "proj_out", "audio_proj_out", "time_w1", "time_w2"):
             setattr(o, name, mv(getattr(self, name), True))
         o.context_embedder = mv(self.context_embedder)
