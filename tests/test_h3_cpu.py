@@ -159,3 +159,75 @@ def test_fp8_feed_forward_stays_close_to_bf16():
         den.run(st)
         outs.append(st.video)
     assert float((outs[0] - outs[1]).norm() / outs[0].norm()) < 1e-2
+
+
+def _video_rank(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world))
+    from uniserve_v1_b200.models.h3_vae import (AudioVaeConfig, AudioVaeDecoder, VideoVaeConfig,
+                                                VideoVaeDecoder)
+    from uniserve_v1_b200.parallel.context import ParallelContext
+    from uniserve_v1_b200.server import multirank as MR
+    from uniserve_v1_b200.server.video_rules import VideoPlan
+    from uniserve_v1_b200.server.video_service import VideoJob, VideoService
+    r, w, dev, control = MR.init_rank()
+    ctx = ParallelContext.from_world(ulysses=world) if world > 1 else None
+    svc = _tiny_service(ctx)
+    if world == 1:
+        q.put(svc.generate(VideoJob("a stream in a forest", _plan())))
+        return
+    bus = MR.CommandBus(control, r)
+    if r > 0:
+        done = MR.video_follower_loop(svc, bus)
+        q.put(("follower", done))
+        return
+    rep = MR.ReplicatedVideoService(svc, bus)
+    mp4 = svc.generate(VideoJob("a stream in a forest", _plan()))
+    rep.shutdown()
+    q.put(("leader", mp4))
+
+
+def _plan():
+    from uniserve_v1_b200.server.video_rules import VideoPlan
+    return VideoPlan("t2va", 256, 256, 39, 24, 1000, 8)
+
+
+def _tiny_service(ctx):
+    from uniserve_v1_b200.models.h3_vae import (AudioVaeConfig, AudioVaeDecoder, VideoVaeConfig,
+                                                VideoVaeDecoder)
+    from uniserve_v1_b200.server.video_service import VideoService
+    cfg = H3Config.tiny()
+    cfg.vae_spatial = 64
+    tr = H3Transformer(cfg, "cpu", torch.float32, ctx).init_random(0)
+    vc = VideoVaeConfig.tiny()
+    vc.latent_channels, vc.spatial = cfg.latent_channels, 64
+    vv = VideoVaeDecoder(vc, "cpu", torch.float32).init_random(1)
+    av = AudioVaeDecoder(AudioVaeConfig(latent_channels=cfg.audio_channels, decoder_dim=128,
+                                        rates=(5, 5, 2, 2, 2, 2, 2), kernels=(9, 9, 4, 4, 4, 4, 4),
+                                        res_kernels=(3,), res_dilations=(1,)), "cpu").init_random(2)
+    return VideoService(tr, vv, av, sizes=["256x256"], max_seconds=5)
+
+
+def test_two_rank_video_request_equals_single_rank():
+    """A video request served by a leader and a follower (sequence-parallel transformer,
+    temporal units of the VAE dealt over the ranks, planes gathered on the leader) yields
+    the MP4 a single rank yields."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_video_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=180) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got["follower"] == 1
+    one = _tiny_service(None).generate(
+        __import__("uniserve_v1_b200.server.video_service", fromlist=["VideoJob"]).VideoJob(
+            "a stream in a forest", _plan()))
+    two = got["leader"]
+    assert two[4:8] == b"ftyp" and len(two) == len(one)
+    a = torch.frombuffer(bytearray(one), dtype=torch.uint8).float()
+    b = torch.frombuffer(bytearray(two), dtype=torch.uint8).float()
+    assert (a - b).abs().mean() < 0.5      # same pictures up to reduction-order noise
