@@ -141,3 +141,63 @@ def test_engine_service_migrates_requests_after_worker_failure():
     for got, want in asyncio.run(go()):
         assert got == want
     assert len(made) == 1
+
+
+def test_random_workloads_keep_the_books_straight():
+    """Property test over random arrival / abort / step interleavings on a small KV pool
+    (forcing chunked prefill, prefix reuse and preemption by recompute): every finished
+    request carries exactly the tokens a fresh run of its prompt yields, nothing is lost or
+    duplicated, and every page returns to the pool."""
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+    from uniserve_v1_b200.engine.types import FinishReason, SamplingParams
+    from uniserve_v1_b200.testing.fakes import FakeEngine, expected_output
+
+    events = st.lists(st.one_of(
+        st.tuples(st.just("add"), st.integers(1, 90), st.integers(1, 12), st.integers(0, 5)),
+        st.tuples(st.just("abort"), st.integers(0, 30)),
+        st.tuples(st.just("step"), st.integers(1, 4))), min_size=5, max_size=60)
+
+    @settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(events, st.integers(0, 3))
+    def run(evs, shared_prefix):
+        eng = FakeEngine(num_pages=24, page_size=8, max_num_seqs=4, max_model_len=128,
+                         max_num_batched_tokens=32)
+        total_pages = eng.blocks.num_free
+        prompts, outs, finished, aborted = {}, {}, {}, set()
+        k = 0
+
+        def drain(out_list):
+            for o in out_list:
+                outs.setdefault(o.request_id, []).extend(o.new_token_ids)
+                if o.finished:
+                    finished[o.request_id] = o.finish_reason
+        for ev in evs:
+            if ev[0] == "add":
+                _, plen, max_tok, seed = ev
+                base = [7, 7, 7, 7, 7, 7, 7, 7, 9, 9, 9, 9, 9, 9, 9, 9] * shared_prefix
+                prompt = (base + [(seed * 31 + j * 17) % 1000 for j in range(plen)])[:100]
+                rid = eng.add_request(prompt, SamplingParams(temperature=0.0, max_tokens=max_tok,
+                                                             ignore_eos=True))
+                prompts[rid] = (prompt, max_tok)
+                k += 1
+            elif ev[0] == "abort":
+                rid = f"r{ev[1]}"
+                if rid in prompts and rid not in finished and eng.abort(rid):
+                    aborted.add(rid)
+            else:
+                for _ in range(ev[1]):
+                    drain(eng.step())
+        drain(eng.run())
+        assert not eng.has_work()
+        for rid, (prompt, max_tok) in prompts.items():
+            want = expected_output(prompt, max_tok)
+            got = outs.get(rid, [])
+            if rid in aborted:
+                assert got == want[:len(got)]
+            else:
+                assert got == want, (rid, got, want)
+                assert finished[rid] == FinishReason.LENGTH
+        eng.blocks.flush()
+        assert eng.blocks.num_free == total_pages
+    run()
