@@ -118,3 +118,28 @@ def test_fp8_block_experts_stay_close_to_bf16_and_run_under_graphs():
     graphs = LLMEngine(q8, num_pages=64, max_num_seqs=4, max_model_len=128,
                        use_graphs=True).generate(prompts, sp)
     assert eager == graphs
+
+
+def test_host_kv_tier_on_gpu_restores_evicted_prefix():
+    model = Qwen3MoeModel(_cfg(), "cuda", torch.bfloat16).init_random(seed=0)
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    g = torch.Generator().manual_seed(3)
+    first = torch.randint(0, 2048, (70,), generator=g).tolist()
+    others = [torch.randint(0, 2048, (70,), generator=g).tolist() for _ in range(3)]
+
+    def run(host_pages):
+        eng = LLMEngine(model, num_pages=12, page_size=16, max_num_seqs=2, max_model_len=128,
+                        use_graphs=False, host_kv_pages=host_pages)
+        a = eng.generate([first], sp)[0]
+        for o in others:
+            eng.generate([o], sp)
+        rid = eng.add_request(first, sp)
+        req = eng.scheduler.requests[rid]
+        while eng.has_work():
+            eng.step()
+        return a, req.output_ids, req.num_cached
+    a0, b0, c0 = run(0)
+    a1, b1, c1 = run(32)
+    torch.cuda.synchronize()
+    N.raise_on_device_error()
+    assert a0 == a1 == b0 == b1 and c0 == 0 and c1 == 64
