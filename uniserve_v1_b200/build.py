@@ -94,18 +94,22 @@ def build(force: bool = False, verbose: bool = False) -> dict:
     out = {}
     kern = LIB / "libus_kernels.so"
     if cu_res and (force or not kern.exists() or any(c for _, c, _ in cu_res)):
-        cmd = [nvcc, "-shared", "-o", str(kern), *[str(o) for o, _, _ in cu_res],
+        tmp = kern.with_suffix(".so.tmp")       # linked aside, then moved into place at once
+        cmd = [nvcc, "-shared", "-o", str(tmp), *[str(o) for o, _, _ in cu_res],
                "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed: {proc.stdout}{proc.stderr}")
+        os.replace(tmp, kern)
     out["kernels"] = kern
     host = LIB / "libus_host.so"
     if cpp_res and (force or not host.exists() or any(c for _, c, _ in cpp_res)):
-        cmd = ["g++", "-shared", "-o", str(host), *[str(o) for o, _, _ in cpp_res], "-pthread"]
+        tmp = host.with_suffix(".so.tmp")
+        cmd = ["g++", "-shared", "-o", str(tmp), *[str(o) for o, _, _ in cpp_res], "-pthread"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed: {proc.stdout}{proc.stderr}")
+        os.replace(tmp, host)
     out["host"] = host
     out["logs"] = logs
     return out

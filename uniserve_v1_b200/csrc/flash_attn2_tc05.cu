@@ -61,6 +61,33 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+// Packed FP32 pairs (two lanes per instruction) and the three-input maximum: the
+// softmax warpgroups are bound by instruction issue, not by the special-function unit.
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long r, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
+                                                   unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __global__ void __launch_bounds__(320, 1)
 flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const Flash2Args a) {
@@ -285,11 +312,11 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        mx0 = fmaxf(mx0, __uint_as_float(v0[i]));
-        mx1 = fmaxf(mx1, __uint_as_float(v1[i]));
-        mx2 = fmaxf(mx2, __uint_as_float(v2[i]));
-        mx3 = fmaxf(mx3, __uint_as_float(v3[i]));
+      for (int i = 0; i < 32; i += 2) {
+        mx0 = max3(mx0, __uint_as_float(v0[i]), __uint_as_float(v0[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(v1[i]), __uint_as_float(v1[i + 1]));
+        mx2 = max3(mx2, __uint_as_float(v2[i]), __uint_as_float(v2[i + 1]));
+        mx3 = max3(mx3, __uint_as_float(v3[i]), __uint_as_float(v3[i + 1]));
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = fmaxf(m_used, mx * a.scale_log2);
@@ -317,33 +344,30 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float neg_m = -m_eff;
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      const unsigned long long sc2 = pack2(a.scale_log2, a.scale_log2);
+      const unsigned long long nm2 = pack2(neg_m, neg_m);
+      unsigned long long l0 = pack2(0.f, 0.f), l1 = l0, l2 = l0, l3 = l0;
       uint32_t pk0[32], pk1[32];
+      auto exp_pair = [&](uint32_t x0, uint32_t x1, unsigned long long& l) -> uint32_t {
+        float t0, t1;
+        unpack2(fma2(pack2(__uint_as_float(x0), __uint_as_float(x1)), sc2, nm2), t0, t1);
+        const float p0 = ex2f(t0), p1 = ex2f(t1);
+        l = add2(l, pack2(p0, p1));
+        __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
+        return *reinterpret_cast<uint32_t*>(&t);
+      };
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
-        const float a0 = ex2f(fmaf(__uint_as_float(v0[i]), a.scale_log2, neg_m));
-        const float a1 = ex2f(fmaf(__uint_as_float(v0[i + 1]), a.scale_log2, neg_m));
-        const float b0 = ex2f(fmaf(__uint_as_float(v1[i]), a.scale_log2, neg_m));
-        const float b1 = ex2f(fmaf(__uint_as_float(v1[i + 1]), a.scale_log2, neg_m));
-        const float c0 = ex2f(fmaf(__uint_as_float(v2[i]), a.scale_log2, neg_m));
-        const float c1 = ex2f(fmaf(__uint_as_float(v2[i + 1]), a.scale_log2, neg_m));
-        const float d0 = ex2f(fmaf(__uint_as_float(v3[i]), a.scale_log2, neg_m));
-        const float d1 = ex2f(fmaf(__uint_as_float(v3[i + 1]), a.scale_log2, neg_m));
-        l0 += a0 + a1;
-        l1 += b0 + b1;
-        l2 += c0 + c1;
-        l3 += d0 + d1;
-        __nv_bfloat162 t;
-        t = __floats2bfloat162_rn(a0, a1);
-        pk0[i >> 1] = *reinterpret_cast<uint32_t*>(&t);
-        t = __floats2bfloat162_rn(b0, b1);
-        pk0[16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&t);
-        t = __floats2bfloat162_rn(c0, c1);
-        pk1[i >> 1] = *reinterpret_cast<uint32_t*>(&t);
-        t = __floats2bfloat162_rn(d0, d1);
-        pk1[16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&t);
+        pk0[i >> 1] = exp_pair(v0[i], v0[i + 1], l0);
+        pk0[16 + (i >> 1)] = exp_pair(v1[i], v1[i + 1], l1);
+        pk1[i >> 1] = exp_pair(v2[i], v2[i + 1], l2);
+        pk1[16 + (i >> 1)] = exp_pair(v3[i], v3[i + 1], l3);
       }
-      l_sum += (l0 + l1) + (l2 + l3);
+      {
+        float s0, s1;
+        unpack2(add2(add2(l0, l1), add2(l2, l3)), s0, s1);
+        l_sum += s0 + s1;
+      }
       // P (64 packed columns) replaces the first half of S, which is in registers now.
       tc::tmem_st32(s_tmem, pk0);
       tc::tmem_st32(s_tmem + 32, pk1);

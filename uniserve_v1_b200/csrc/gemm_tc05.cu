@@ -443,7 +443,12 @@ int launch(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int m_tiles, in
   a.splits = splits;
   a.kb_per_split = kb_per;
   // Small row tiles are memory-bound: keep two CTAs per SM resident.
-  const int budget = (BN <= 64 && !DUAL) ? 100 * 1024 : (BN <= 32 ? 104 * 1024 : 200 * 1024);
+  // US_GEMM_SMALL_KB overrides the budget of small single-accumulator tiles (tuning aid).
+  static const int small_kb = [] {
+    const char* e = getenv("US_GEMM_SMALL_KB");
+    return e ? atoi(e) : 100;
+  }();
+  const int budget = (BN <= 64 && !DUAL) ? small_kb * 1024 : (BN <= 32 ? 104 * 1024 : 200 * 1024);
   int stages = budget / kStageBytes;
   if (stages > 8) stages = 8;
   if (stages > kb_per) stages = kb_per;
