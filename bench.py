@@ -95,7 +95,7 @@ def reference_arm(args) -> int:
     needs Hugging Face checkpoints, FFmpeg 8.1 and NCCL >= 2.30.4."""
     ref = Path(__file__).resolve().parent / "baseline" / "_ref"
     exe = list(ref.glob("bin/uniserve")) if ref.exists() else []
-    why = ("reference is a Rust serving binary; offline pip install of /root/reference produced "
+    why = ("reference is a Rust serving binary; offline pip install of the reference tree produced "
            "metadata only (no cargo/rustc, no setuptools-rust), so no `uniserve` executable, "
            "checkpoints, FFmpeg 8.1 or NCCL>=2.30.4 exist to run it")
     if exe:

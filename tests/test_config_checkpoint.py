@@ -250,7 +250,9 @@ def test_reference_deployment_examples_resolve_to_axes():
     import os
     from uniserve_v1_b200.config.policy import Package
     from uniserve_v1_b200.server.multirank import package_parallelism
-    root = "/root/reference/configs"
+    from pathlib import Path
+    root = os.environ.get("UNISERVE_REFERENCE_CONFIGS",
+                          str(Path(__file__).resolve().parents[2] / "reference" / "configs"))
     if not os.path.isdir(root):
         import pytest
         pytest.skip("reference tree not present")
