@@ -1,0 +1,68 @@
+"""Golden parity with Hugging Face transformers: a tiny Qwen3-MoE (and dense Qwen3)
+checkpoint written by transformers is loaded through the safetensors reader and must
+reproduce transformers' own logits and greedy continuation on CPU."""
+import json
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+
+def _save(model, cfg, path):
+    from uniserve_v1_b200.checkpoint.safetensors_io import save_file
+    path.mkdir(parents=True, exist_ok=True)
+    state = {k: v.detach().clone().contiguous() for k, v in model.state_dict().items()}
+    save_file(state, path / "model.safetensors")
+    d = cfg.to_dict()
+    d["architectures"] = [type(model).__name__]
+    (path / "config.json").write_text(json.dumps(d))
+
+
+def _compare(path, hf, prompt):
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, resolve_family
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.models.reference_cpu import ReferenceQwen3Moe
+    assert resolve_family(path) == "qwen3_moe"
+    ld = CheckpointLoader(path)
+    cfg = Qwen3MoeConfig.from_hf(ld.config)
+    model = Qwen3MoeModel(cfg, "cpu", torch.float32).load_state(ld)
+    ids = torch.tensor([prompt])
+    with torch.no_grad():
+        want = hf(ids).logits[0]
+        gen = hf.generate(ids, max_new_tokens=6, do_sample=False)[0, len(prompt):].tolist()
+    got, _ = ReferenceQwen3Moe(model).forward(torch.tensor(prompt))
+    torch.testing.assert_close(got, want, atol=2e-4, rtol=2e-4)
+    out = LLMEngine(model, num_pages=32, max_num_seqs=2, max_model_len=128,
+                    use_graphs=False).generate(
+        [prompt], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))[0]
+    assert out == gen
+
+
+def test_qwen3_moe_matches_transformers(tmp_path):
+    from transformers import Qwen3MoeConfig as HfCfg, Qwen3MoeForCausalLM
+    torch.manual_seed(0)
+    cfg = HfCfg(vocab_size=512, hidden_size=128, intermediate_size=256, moe_intermediate_size=64,
+                num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                num_experts=8, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1,
+                mlp_only_layers=[], max_position_embeddings=256, rope_theta=1e6,
+                rms_norm_eps=1e-6, tie_word_embeddings=False, eos_token_id=511, pad_token_id=0,
+                torch_dtype="float32", attention_dropout=0.0, router_aux_loss_coef=0.0)
+    hf = Qwen3MoeForCausalLM(cfg).eval()
+    _save(hf, cfg, tmp_path / "moe")
+    _compare(tmp_path / "moe", hf, [3, 17, 250, 4, 99, 100, 7, 7, 12])
+
+
+def test_qwen3_dense_matches_transformers(tmp_path):
+    from transformers import Qwen3Config as HfCfg, Qwen3ForCausalLM
+    torch.manual_seed(1)
+    cfg = HfCfg(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                max_position_embeddings=256, rope_theta=1e6, rms_norm_eps=1e-6,
+                tie_word_embeddings=True, eos_token_id=511, pad_token_id=0, torch_dtype="float32",
+                attention_dropout=0.0)
+    hf = Qwen3ForCausalLM(cfg).eval()
+    _save(hf, cfg, tmp_path / "dense")
+    _compare(tmp_path / "dense", hf, [5, 9, 2, 44, 300, 12])

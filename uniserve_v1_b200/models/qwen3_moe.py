@@ -57,6 +57,12 @@ class Qwen3MoeConfig:
     @classmethod
     def from_hf(cls, d: dict) -> "Qwen3MoeConfig":
         keys = {f for f in cls.__dataclass_fields__}
+        d = dict(d)
+        # newer transformers write `num_local_experts` and nest the rotary base
+        if "num_experts" not in d and d.get("num_local_experts"):
+            d["num_experts"] = d["num_local_experts"]
+        if "rope_theta" not in d and isinstance(d.get("rope_parameters"), dict):
+            d["rope_theta"] = d["rope_parameters"].get("rope_theta", 10000.0)
         kw = {k: v for k, v in d.items() if k in keys}
         if "head_dim" not in kw:
             kw["head_dim"] = d["hidden_size"] // d["num_attention_heads"]
@@ -287,11 +293,18 @@ class Qwen3MoeModel:
                 I = cfg.moe_intermediate_size
                 w13 = torch.empty(self.E_local, 2 * I, cfg.hidden_size, device=dev, dtype=dt)
                 w2 = torch.empty(self.E_local, cfg.hidden_size, I, device=dev, dtype=dt)
-                for e in range(self.e_lo, self.e_lo + self.E_local):
-                    pe = p + f"mlp.experts.{e}."
-                    w13[e - self.e_lo, :I] = get(pe + "up_proj.weight")
-                    w13[e - self.e_lo, I:] = get(pe + "gate_proj.weight")
-                    w2[e - self.e_lo] = get(pe + "down_proj.weight")
+                if loader.has(p + "mlp.experts.gate_up_proj"):
+                    # stacked form: [E, 2I, H] gate rows then up rows; [E, H, I]
+                    gu = get(p + "mlp.experts.gate_up_proj")[self.e_lo:self.e_lo + self.E_local]
+                    w13[:, :I] = gu[:, I:]
+                    w13[:, I:] = gu[:, :I]
+                    w2.copy_(get(p + "mlp.experts.down_proj")[self.e_lo:self.e_lo + self.E_local])
+                else:
+                    for e in range(self.e_lo, self.e_lo + self.E_local):
+                        pe = p + f"mlp.experts.{e}."
+                        w13[e - self.e_lo, :I] = get(pe + "up_proj.weight")
+                        w13[e - self.e_lo, I:] = get(pe + "gate_proj.weight")
+                        w2[e - self.e_lo] = get(pe + "down_proj.weight")
                 lw.w13, lw.w2 = w13, w2
                 self._quantize_experts(lw)
             else:
