@@ -370,3 +370,20 @@ def test_gemm_peer_modes_with_local_buffers_as_peers():
     for p_ in range(P):
         close(slots[p_][1], ref[p_ * (rows // 2):(p_ + 1) * (rows // 2)], 3e-2, 3e-2)
         assert float(slots[p_][0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_flash_attn_head_dim_64(causal):
+    """64-wide heads on the two-tile kernel (row-strided q / k / v views, GQA 2:1)."""
+    from uniserve_v1_b200.ops.flash import flash_attn_varlen
+    D, Hq, Hkv = 64, 4, 2
+    lens = [300, 70, 513]
+    T = sum(lens)
+    buf = rnd(T, (Hq + 2 * Hkv) * D, seed=51)
+    q = buf[:, :Hq * D].view(T, Hq, D)
+    k = buf[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    v = buf[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    cu = torch.tensor([0, 300, 370, 883], dtype=torch.int32, device=DEV)
+    out = flash_attn_varlen(q, k, v, cu, cu, max(lens), max(lens), 1 / math.sqrt(D), causal)
+    ref = R.varlen_attention(q, k, v, cu.cpu(), cu.cpu(), 1 / math.sqrt(D), causal)
+    close(out, ref, 2e-2, 2e-2)

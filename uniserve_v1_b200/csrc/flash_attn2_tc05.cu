@@ -1,4 +1,4 @@
-// Varlen flash attention forward, two query tiles per CTA (head_dim 128, bf16, GQA).
+// Varlen flash attention forward, two query tiles per CTA (head_dim 128 or 64, bf16, GQA).
 //
 // One CTA owns 256 query rows of one (sequence, head) as two 128-row tiles A
 // and B and walks the keys in blocks of 128.  The tensor pipe alternates between
@@ -30,11 +30,10 @@
 
 namespace {
 
-constexpr int kD = 128;
+constexpr int kDMax = 128;  // head widths served: 128 and 64 (template parameter kD)
 constexpr int kBM = 128;   // query rows per tile (two tiles per CTA)
 constexpr int kBN = 128;   // keys per block
 constexpr int kHalf = 128 * 128;         // bytes of one 64-column half tile (128 rows x 128 B)
-constexpr int kTile = 2 * kHalf;         // 32 KiB
 constexpr float kRescaleThreshold = 8.f; // log2 units
 
 struct Flash2Args {
@@ -88,10 +87,13 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+template <int kD>
 __global__ void __launch_bounds__(320, 1)
 flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const Flash2Args a) {
   US_PDL_PROLOGUE();
+  constexpr int kHalves = kD / 64;          // 64-column (128-byte) slabs per tile
+  constexpr int kTile = kHalves * kHalf;    // 32 KiB (head 128) or 16 KiB (head 64)
   const int q_pair = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int q_start = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_start;
@@ -177,8 +179,9 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
       for (int x = 0; x < 2; ++x) {
         const int row = q_start + q0 + x * kBM;   // rows past the tensor read as zeros
-        tc::tma_load_2d(sQ + x * kTile, &tmQ, q_full, h * kD, row);
-        tc::tma_load_2d(sQ + x * kTile + kHalf, &tmQ, q_full, h * kD + 64, row);
+#pragma unroll
+        for (int hf = 0; hf < kHalves; ++hf)
+          tc::tma_load_2d(sQ + x * kTile + hf * kHalf, &tmQ, q_full, h * kD + 64 * hf, row);
       }
       for (int j = 0; j < nb; ++j) {
         const int st = j & 1;
@@ -190,16 +193,18 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           break;
         }
         tc::mbar_expect_tx(&k_full[st], kTile);
-        tc::tma_load_2d(sK + st * kTile, &tmK, &k_full[st], hk * kD, row);
-        tc::tma_load_2d(sK + st * kTile + kHalf, &tmK, &k_full[st], hk * kD + 64, row);
+#pragma unroll
+        for (int hf = 0; hf < kHalves; ++hf)
+          tc::tma_load_2d(sK + st * kTile + hf * kHalf, &tmK, &k_full[st], hk * kD + 64 * hf, row);
         if (!tc::mbar_wait(&v_empty[st], ph ^ 1u, abort_flag)) {
           us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
           *abort_flag = 1;
           break;
         }
         tc::mbar_expect_tx(&v_full[st], kTile);
-        tc::tma_load_2d(sV + st * kTile, &tmV, &v_full[st], hk * kD, row);
-        tc::tma_load_2d(sV + st * kTile + kHalf, &tmV, &v_full[st], hk * kD + 64, row);
+#pragma unroll
+        for (int hf = 0; hf < kHalves; ++hf)
+          tc::tma_load_2d(sV + st * kTile + hf * kHalf, &tmV, &v_full[st], hk * kD + 64 * hf, row);
       }
     }
   } else if (warp == 9) {
@@ -211,7 +216,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint32_t k_addr = tc::smem_u32(sK + (j & 1) * kTile);
         const uint32_t s_tmem = tmem_base + (uint32_t)x * kBN;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < kD / 16; ++kk) {
           const uint32_t half = kk >> 2, sub = kk & 3;
           const uint64_t ad = tc::smem_desc_kmajor_sw128(q_addr + half * kHalf) + 2 * sub;
           const uint64_t bd = tc::smem_desc_kmajor_sw128(k_addr + half * kHalf) + 2 * sub;
@@ -426,7 +431,7 @@ int flash2_impl(const void* q, const void* k, const void* v, void* out, const in
                 long long peer_ld, cudaStream_t stream) {
   US_REQUIRE(q && k && v && (out || peer_out) && cu_q && cu_k && n_seqs >= 1 && Tq >= 1 &&
              Tk >= 1);
-  US_REQUIRE(D == kD && Hkv >= 1 && Hq % Hkv == 0 && max_q >= 1);
+  US_REQUIRE((D == 128 || D == 64) && Hkv >= 1 && Hq % Hkv == 0 && max_q >= 1);
   US_REQUIRE((ldq % 8) == 0 && (ldk % 8) == 0 && (ldv % 8) == 0 && (ldo % 8) == 0);
   US_REQUIRE(((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0 && ((uintptr_t)v % 16) == 0 &&
              ((uintptr_t)out % 16) == 0);
@@ -465,15 +470,24 @@ int flash2_impl(const void* q, const void* k, const void* v, void* out, const in
     a.peer_col0 = peer_col0;
     a.peer_ld = peer_ld;
   }
-  const size_t smem = 6 * (size_t)kTile + 16 * 8 + 16 + 1024;
+  const size_t smem = 6 * (size_t)(D / 64) * kHalf + 16 * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
-    US_CUDA_CHECK(cudaFuncSetAttribute(flash2_fwd_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    US_CUDA_CHECK(cudaFuncSetAttribute(flash2_fwd_kernel<128>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(12 * (size_t)kHalf + 16 * 8 + 16 + 1024)));
+    US_CUDA_CHECK(cudaFuncSetAttribute(flash2_fwd_kernel<64>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(6 * (size_t)kHalf + 16 * 8 + 16 + 1024)));
     configured = true;
   }
   dim3 grid((max_q + 2 * kBM - 1) / (2 * kBM), Hq, n_seqs);
-  US_CUDA_CHECK(us::launch_pdl(flash2_fwd_kernel, grid, dim3(320), smem, stream, tmQ, tmK, tmV, a));
+  if (D == 128)
+    US_CUDA_CHECK(us::launch_pdl(flash2_fwd_kernel<128>, grid, dim3(320), smem, stream, tmQ, tmK,
+                                 tmV, a));
+  else
+    US_CUDA_CHECK(us::launch_pdl(flash2_fwd_kernel<64>, grid, dim3(320), smem, stream, tmQ, tmK,
+                                 tmV, a));
   return US_OK;
 }
 
@@ -498,7 +512,7 @@ US_API int us_flash_attn_push(const void* q, const void* k, const void* v, const
                               long long ldk, long long ldv, float scale, void* const* peer_out,
                               int n_peers, int peer_rows, int peer_col0, long long peer_ld,
                               void* stream_) {
-  return flash2_impl(q, k, v, nullptr, cu_q, cu_k, 1, Tq, Tk, Hq, Hkv, kD, Tq, ldq, ldk, ldv, 8,
+  return flash2_impl(q, k, v, nullptr, cu_q, cu_k, 1, Tq, Tk, Hq, Hkv, kDMax, Tq, ldq, ldk, ldv, 8,
                      scale, 0, peer_out, n_peers, peer_rows, peer_col0, peer_ld,
                      (cudaStream_t)stream_);
 }

@@ -79,13 +79,13 @@ class VideoVaeDecoder:
         return self
 
     def _attention(self, q, k, v, n):
-        """64-wide heads on the 128-wide tensor-core kernel: zero-pad the head dim
-        (same scores, the padded value columns are dropped)."""
+        """Dense bidirectional attention over the unit's tokens; 64- and 128-wide heads run
+        the tensor-core flash kernel directly."""
         c = self.cfg
         D = c.head_dim
         cu = torch.tensor([0, n], dtype=torch.int32, device=q.device)
         scale = 1.0 / math.sqrt(D)
-        if q.is_cuda and D < 128:
+        if q.is_cuda and D not in (64, 128):
             pad = lambda t: torch.nn.functional.pad(t, (0, 128 - D))
             o = varlen_attention(pad(q), pad(k), pad(v), cu, cu, n, n, scale, False)
             return o[..., :D]

@@ -32,7 +32,10 @@ def flash_attn_varlen(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, out=None
     if out is None:
         out = torch.empty(Tq, Hq, D, dtype=BF16, device=q.device)
     n = cu_q.numel() - 1
-    name = "us_flash_attn_varlen" if (_SINGLE_TILE_ONLY or max_q <= 128) else \
+    if D not in (64, 128):
+        return R.varlen_attention(q, k, v, cu_q.cpu(), cu_k.cpu(), scale, causal).to(q.dtype)
+    # head 64 is served by the two-tile kernel only
+    name = "us_flash_attn_varlen" if (D == 128 and (_SINGLE_TILE_ONLY or max_q <= 128)) else \
         "us_flash_attn_varlen2"
     N.call(name, N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(cu_q),
            N.ptr(cu_k), n, Tq, Tk, Hq, Hkv, D, max_q, q.stride(0), k.stride(0), v.stride(0),
