@@ -276,13 +276,12 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
     if (lane == 0) {
       tc::tma_prefetch_desc(&tmA);
       tc::tma_prefetch_desc(&tmBs.m[0]);
-      uint32_t kbg = 0;   // k-blocks issued so far, over all tiles
+      int s = 0;          // stage and phase of the ring, carried over all tiles
+      uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total; t += gridDim.x) {
         const int m_tile = t % m_tiles, row0 = (t / m_tiles) * BN;
-        for (int kb = 0; kb < num_k; ++kb, ++kbg) {
-          const int s = kbg % stages;
-          const uint32_t ph = (kbg / stages) & 1u;
+        for (int kb = 0; kb < num_k; ++kb) {
           if (!tc::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
             us_dev_fail(args.status, US_DEV_TIMEOUT_EMPTY);
             *abort_flag = 1;
@@ -305,14 +304,24 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
             tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], &full_bar[s],
                             kx - src * args.k_per_peer, row0);
           }
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1u;
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      uint32_t kbg = 0;
-      bool ok = true;
+      // This one thread feeds the tensor core; everything it executes per k-block is
+      // latency in series with the multiplications, so the loop carries its ring
+      // position instead of dividing, builds descriptors by addition, and probes the
+      // next stage's barrier while the current stage's instructions are in flight.
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true, ready = false;
       int it = 0;
+      const uint64_t desc0 = tc::smem_desc_kmajor_sw128(tc::smem_u32(smem));
       for (int t = blockIdx.x; ok && t < total; t += gridDim.x, ++it) {
         const int buf = it & 1;
         if (!tc::mbar_wait(&acc_empty[buf], ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag)) {
@@ -322,20 +331,23 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         tc::tc_fence_after_sync();
         const uint32_t d = tmem_base + (uint32_t)buf * kAccCols;
-        for (int kb = 0; kb < num_k; ++kb, ++kbg) {
-          const int s = kbg % stages;
-          const uint32_t ph = (kbg / stages) & 1u;
-          if (!tc::mbar_wait(&full_bar[s], ph, abort_flag)) {
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!ready && !tc::mbar_wait(&full_bar[s], ph, abort_flag)) {
             us_dev_fail(args.status, US_DEV_TIMEOUT_FULL);
             *abort_flag = 1;
             ok = false;
             break;
           }
           tc::tc_fence_after_sync();
-          const uint32_t a_addr = tc::smem_u32(smem + (size_t)s * kStageBytes);
-          const uint32_t b_addr = a_addr + kATile * (DUAL ? 2 : 1);
-          const uint64_t adesc = tc::smem_desc_kmajor_sw128(a_addr);
-          const uint64_t bdesc = tc::smem_desc_kmajor_sw128(b_addr);
+          const uint64_t adesc = desc0 + (uint64_t)((uint32_t)s * (uint32_t)(kStageBytes >> 4));
+          const uint64_t bdesc = adesc + (uint64_t)((kATile * (DUAL ? 2 : 1)) >> 4);
+          int sn = s + 1;
+          uint32_t phn = ph;
+          if (sn == stages) {
+            sn = 0;
+            phn ^= 1u;
+          }
+          ready = tc::mbar_test_wait(&full_bar[sn], phn);
 #pragma unroll
           for (int k = 0; k < kBlockK / 16; ++k) {
             const uint32_t acc = (kb | k) != 0;
@@ -344,7 +356,7 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
             else
               tc::umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
             if (DUAL) {
-              const uint64_t a2desc = tc::smem_desc_kmajor_sw128(a_addr + kATile);
+              const uint64_t a2desc = adesc + (uint64_t)(kATile >> 4);
               if (FP8)
                 tc::umma_f8(d + BN, a2desc + 2 * k, bdesc + 2 * k, kIdesc, acc);
               else
@@ -352,6 +364,8 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
             }
           }
           tc::umma_commit(&empty_bar[s]);
+          s = sn;
+          ph = phn;
         }
         if (ok) tc::umma_commit(&acc_full[buf]);
       }
@@ -395,6 +409,297 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
     __syncwarp();
     tc::tmem_dealloc(tmem_base, kCols);
   }
+}
+
+// CTA-pair form of the persistent kernel: the two CTAs of a cluster own one
+// 256 x BN output tile and multiply it with cta_group::2 instructions, so every
+// SM fetches its own 128 weight rows and only half of the activation rows from
+// shared memory per instruction (the single-CTA form is bound by that operand
+// fetch, not by the multipliers).  Each CTA loads its operands with its own TMA
+// ring; the odd CTA forwards its "stage filled" events to the even CTA, whose
+// MMA thread issues for both and releases the stages and accumulators of both
+// through commits addressed to either CTA's barriers.
+template <int BN, bool DUAL, bool FP8>
+__global__ void __launch_bounds__(192)
+gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                    const __grid_constant__ BMaps tmBs, const GemmArgs args) {
+  US_PDL_PROLOGUE();
+  constexpr int kBK = FP8 ? 2 * kBlockK : kBlockK;
+  constexpr int kATiles = kATile * (DUAL ? 2 : 1);
+  constexpr int kBHalf = (BN / 2) * kBlockK * 2;
+  constexpr int kStageBytes = kATiles + kBHalf;
+  constexpr uint32_t kAccCols = DUAL ? 2 * BN : BN;
+  constexpr uint32_t kCols = tmem_cols<2 * BN>(DUAL);
+  static_assert(kCols <= 512, "two accumulators must fit tensor memory");
+  constexpr uint32_t kIdesc =
+      FP8 ? tc::make_idesc(2 * kBlockM, BN, tc::kFmtE4M3, tc::kFmtE4M3)
+          : tc::make_idesc(2 * kBlockM, BN, tc::kFmtBF16, tc::kFmtBF16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = tc::cluster_ctarank();          // 0 issues the multiplications
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int m_tiles = (args.M + kBlockM - 1) / kBlockM;
+  const int m_pairs = (m_tiles + 1) / 2;
+  const int n_tiles = (args.rows + BN - 1) / BN;
+  const int total = m_pairs * n_tiles;
+  const int num_k = (args.K + kBK - 1) / kBK;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stages = args.stages;
+  uint64_t* full_bar = (uint64_t*)(smem + (size_t)stages * kStageBytes);
+  uint64_t* empty_bar = full_bar + stages;
+  uint64_t* peer_full = empty_bar + stages;  // even CTA: the odd CTA's stage is filled
+  uint64_t* acc_full = peer_full + stages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2], used in the even CTA only
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* epi_fail = tmem_slot + 2;
+  uint8_t* epi_stage = smem + (size_t)stages * kStageBytes + 1024;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      tc::mbar_init(&full_bar[s], 1);
+      tc::mbar_init(&empty_bar[s], 1);
+      tc::mbar_init(&peer_full[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&acc_full[b], 1);
+      tc::mbar_init(&acc_empty[b], 256);     // the epilogue threads of both CTAs
+    }
+    *abort_flag = 0;
+    *epi_fail = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, kCols);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before_sync();
+  tc::cluster_sync();     // both CTAs' barriers exist before anything arrives remotely
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  // The pair instruction addresses both CTAs' tensor memory with one address:
+  // both must have received the same columns (all 512 of an otherwise empty SM).
+  const bool tmem_ok = (tmem_base & 0xffffu) == 0;
+  if (!tmem_ok && threadIdx.x == 0) us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
+
+  if (!tmem_ok) {
+    // nothing is issued; the peer's waits run out and report
+  } else if (warp == 0) {
+    if (lane == 0) {
+      tc::tma_prefetch_desc(&tmA);
+      tc::tma_prefetch_desc(&tmBs.m[0]);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = pair; ok && t < total; t += pairs) {
+        const int m_tile = 2 * (t % m_pairs) + (int)rank;
+        const int row0 = (t / m_pairs) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!tc::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
+            us_dev_fail(args.status, US_DEV_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + (size_t)s * kStageBytes;
+          tc::mbar_expect_tx(&full_bar[s], kStageBytes);
+          const int kx = kb * kBK;
+          // a weight tile past the last one reads as zeros
+          tc::tma_load_3d(st, &tmA, &full_bar[s], kx, m_tile * kBlockM, 0);
+          if (DUAL)
+            tc::tma_load_3d(st + kATile, &tmA, &full_bar[s], kx,
+                            args.dual_offset + m_tile * kBlockM, 0);
+          const int src = args.k_per_peer > 0 ? kx / args.k_per_peer : 0;
+          tc::tma_load_2d(st + kATiles, &tmBs.m[src], &full_bar[s], kx - src * args.k_per_peer,
+                          row0);
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 1) {
+      // forward "stage filled" to the issuing CTA
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      const uint32_t peer0 = tc::map_to_cta(tc::smem_u32(&peer_full[0]), 0);
+      for (int t = pair; ok && t < total; t += pairs) {
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!tc::mbar_wait(&full_bar[s], ph, abort_flag)) {
+            us_dev_fail(args.status, US_DEV_TIMEOUT_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc::mbar_arrive_cluster(peer0 + 8u * (uint32_t)s);
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    } else if (lane == 0) {
+      // One thread feeds both tensor cores: its loop is latency in series with the
+      // multiplications, so it carries the ring position, adds descriptors, and
+      // probes the next stage's barriers while the current instructions issue.
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true, ready = false;
+      int it = 0;
+      const uint64_t desc0 = tc::smem_desc_kmajor_sw128(tc::smem_u32(smem));
+      const uint32_t empty0 = tc::smem_u32(&empty_bar[0]);
+      const uint32_t empty0_peer = tc::map_to_cta(empty0, 1);
+      for (int t = pair; ok && t < total; t += pairs, ++it) {
+        const int buf = it & 1;
+        if (!tc::mbar_wait_cluster(&acc_empty[buf], ((uint32_t)(it >> 1) & 1u) ^ 1u,
+                                   abort_flag)) {
+          us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
+          *abort_flag = 1;
+          break;
+        }
+        tc::tc_fence_after_sync();
+        const uint32_t d = tmem_base + (uint32_t)buf * kAccCols;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!ready && (!tc::mbar_wait(&full_bar[s], ph, abort_flag) ||
+                         !tc::mbar_wait_cluster(&peer_full[s], ph, abort_flag))) {
+            us_dev_fail(args.status, US_DEV_TIMEOUT_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc::tc_fence_after_sync();
+          const uint64_t adesc = desc0 + (uint64_t)((uint32_t)s * (uint32_t)(kStageBytes >> 4));
+          const uint64_t bdesc = adesc + (uint64_t)(kATiles >> 4);
+          int sn = s + 1;
+          uint32_t phn = ph;
+          if (sn == stages) {
+            sn = 0;
+            phn ^= 1u;
+          }
+          ready = tc::mbar_test_wait(&full_bar[sn], phn) &&
+                  tc::mbar_test_wait(&peer_full[sn], phn);
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            const uint32_t acc = (kb | k) != 0;
+            if (FP8)
+              tc::umma_f8_pair(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            else
+              tc::umma_f16_pair(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            if (DUAL) {
+              const uint64_t a2desc = adesc + (uint64_t)(kATile >> 4);
+              if (FP8)
+                tc::umma_f8_pair(d + BN, a2desc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+              else
+                tc::umma_f16_pair(d + BN, a2desc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            }
+          }
+          tc::umma_commit_pair(empty0 + 8u * (uint32_t)s);
+          tc::umma_commit_pair(empty0_peer + 8u * (uint32_t)s);
+          s = sn;
+          ph = phn;
+        }
+        if (ok) {
+          const uint32_t f = tc::smem_u32(&acc_full[buf]);
+          tc::umma_commit_pair(f);
+          tc::umma_commit_pair(tc::map_to_cta(f, 1));
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int ml = q * 32 + lane;
+    int it = 0;
+    for (int t = pair; t < total; t += pairs, ++it) {
+      const int buf = it & 1;
+      const int m_tile = 2 * (t % m_pairs) + (int)rank, row0 = (t / m_pairs) * BN;
+      const int nrows = m_tile < m_tiles ? min(BN, args.rows - row0) : 0;
+      if (!tc::mbar_wait(&acc_full[buf], (uint32_t)(it >> 1) & 1u, abort_flag)) {
+        us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
+        *epi_fail = 1;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // uniform decision over the 128 threads
+      if (*epi_fail != 0) break;
+      tc::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t)buf * kAccCols + ((uint32_t)(q * 32) << 16);
+      Epilogue<DUAL> epi(args, 0, m_tile * kBlockM, ml, row0);
+      int chunk = 0;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16, ++chunk) {
+        if (c >= nrows) break;  // uniform over the CTA
+        uint32_t v[16], g[16];
+        tc::tmem_ld16(taddr + c, v);
+        if (DUAL) tc::tmem_ld16(taddr + BN + c, g);
+        tc::tmem_ld_wait();
+        epi.store_chunk16(c, chunk, v, g, nrows, epi_stage);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      tc::tc_fence_before_sync();
+      if (rank == 0)
+        tc::mbar_arrive(&acc_empty[buf]);
+      else
+        tc::mbar_arrive_cluster(tc::map_to_cta(tc::smem_u32(&acc_empty[buf]), 0));
+    }
+  }
+  tc::tc_fence_before_sync();
+  tc::cluster_sync();     // no CTA leaves while the other may still signal it
+  if (warp == 1) {
+    __syncwarp();
+    tc::tmem_dealloc(tmem_base, kCols);
+  }
+}
+
+template <int BN, bool DUAL, bool FP8 = false>
+int launch_pair(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int pair_tiles,
+                cudaStream_t stream) {
+  constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + (BN / 2) * kBlockK * 2;
+  int stages = (192 * 1024) / kStageBytes;
+  if (stages > 8) stages = 8;
+  a.stages = stages;
+  a.splits = 1;
+  const size_t smem = (size_t)stages * kStageBytes + 1024 + kEpiStageBytes + 1024;
+  static bool configured = false;
+  static int sms = 0;
+  if (!configured) {
+    US_CUDA_CHECK(cudaFuncSetAttribute(gemm_wx_pair_kernel<BN, DUAL, FP8>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    int dev = 0;
+    US_CUDA_CHECK(cudaGetDevice(&dev));
+    US_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sms & ~1);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  // Tiles are dealt to the pairs round-robin, so every pair must be resident at
+  // once: not every SM need have a partner free for a cluster of two.
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    US_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_wx_pair_kernel<BN, DUAL, FP8>, &cfg));
+    max_pairs = n < 1 ? 1 : n;
+  }
+  const int pairs = pair_tiles < max_pairs ? pair_tiles : max_pairs;
+  cfg.gridDim = dim3(2 * pairs);
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = us::pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  US_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_wx_pair_kernel<BN, DUAL, FP8>, tmA, tmB, a));
+  return US_OK;
 }
 
 template <int BN, bool DUAL, bool FP8 = false>
@@ -484,6 +789,14 @@ int launch(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int m_tiles, in
   return US_OK;
 }
 
+static bool pair_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("US_GEMM_PAIR");
+    return e != nullptr && e[0] == '1';
+  }();
+  return on;
+}
+
 struct PeerSpec {
   const void* const* x_peers = nullptr;  // pull: activation base per rank
   int n_peers = 0;
@@ -513,6 +826,14 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
   US_REQUIRE(x_rows >= 1);
   if (num_tiles) US_REQUIRE(tile_group && tile_row0 && tile_rows && max_tiles >= 1);
 
+  // Dense problems of more than one wave run on CTA pairs (US_GEMM_PAIR=0: single CTAs).
+  const bool pair = pair_enabled() && num_tiles == nullptr && G == 1 &&
+                    !(ps.x_peers && ps.rows_per_peer > 0) &&
+                    (dual ? block_n == 128 : block_n == 256) &&
+                    (long long)((M + kBlockM - 1) / kBlockM) * ((x_rows + block_n - 1) / block_n) >
+                        148;
+  const uint32_t box_n = (uint32_t)(pair ? block_n / 2 : block_n);
+
   CUtensorMap tmA;
   BMaps tmB;
   int rc = us_tmap_3d(&tmA, W, US_TMAP_BF16, (uint64_t)G, (uint64_t)w_rows, (uint64_t)K,
@@ -535,14 +856,13 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
     for (int p = 0; p < ps.n_peers; ++p) {
       US_REQUIRE(ps.x_peers[p] && ((uintptr_t)ps.x_peers[p] % 16) == 0);
       rc = us_tmap_2d(&tmB.m[p], ps.x_peers[p], US_TMAP_BF16, (uint64_t)x_rows,
-                      (uint64_t)ps.k_per_peer, (uint64_t)ldx, (uint32_t)block_n, kBlockK,
-                      US_SWZ_128);
+                      (uint64_t)ps.k_per_peer, (uint64_t)ldx, box_n, kBlockK, US_SWZ_128);
       if (rc) return rc;
     }
     for (int p = ps.n_peers; p < 8; ++p) tmB.m[p] = tmB.m[0];
   } else {
     rc = us_tmap_2d(&tmB.m[0], X, US_TMAP_BF16, (uint64_t)x_rows, (uint64_t)K, (uint64_t)ldx,
-                    (uint32_t)block_n, kBlockK, US_SWZ_128);
+                    box_n, kBlockK, US_SWZ_128);
     if (rc) return rc;
     for (int p = 1; p < 8; ++p) tmB.m[p] = tmB.m[0];
   }
@@ -626,6 +946,11 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
     const char* e = getenv("US_NO_PERSIST");
     return e && e[0] == '1';
   }();
+  if (pair) {
+    const int pair_tiles = ((m_tiles + 1) / 2) * n_tiles;
+    if (dual) return launch_pair<128, true>(tmA, tmB, a, pair_tiles, stream);
+    return launch_pair<256, false>(tmA, tmB, a, pair_tiles, stream);
+  }
   if (!no_persist && num_tiles == nullptr && G == 1 && m_tiles * n_tiles > 148 &&
       (dual ? block_n == 128 : (block_n == 128 || block_n == 256))) {
     const int tiles = m_tiles * n_tiles;
@@ -770,8 +1095,12 @@ US_API int us_gemm_fp8_rowscale(const void* Wq, const void* Xq, void* out, int w
   int rc = us_tmap_3d(&tmA, Wq, US_TMAP_U8, 1, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw,
                       (uint64_t)w_rows * (uint64_t)ldw, kBlockM, 2 * kBlockK, US_SWZ_128);
   if (rc) return rc;
+  const int m_tiles = (M + kBlockM - 1) / kBlockM;
+  const int n_tiles = (x_rows + block_n - 1) / block_n;
+  const int tiles = m_tiles * n_tiles;
+  const bool pair = pair_enabled() && tiles > 148 && (dual ? block_n == 128 : block_n == 256);
   rc = us_tmap_2d(&tmB.m[0], Xq, US_TMAP_U8, (uint64_t)x_rows, (uint64_t)K, (uint64_t)ldx,
-                  (uint32_t)block_n, 2 * kBlockK, US_SWZ_128);
+                  (uint32_t)(pair ? block_n / 2 : block_n), 2 * kBlockK, US_SWZ_128);
   if (rc) return rc;
   for (int p = 1; p < 8; ++p) tmB.m[p] = tmB.m[0];
   GemmArgs a;
@@ -782,10 +1111,12 @@ US_API int us_gemm_fp8_rowscale(const void* Wq, const void* Xq, void* out, int w
   a.status = us_status_ptr(); a.splits = 1;
   const long long esz = out_dtype == 0 ? 2 : 4;
   a.vec_store = (((ldo * esz) % 16) == 0 && ((uintptr_t)out % 16) == 0) ? 1 : 0;
-  const int m_tiles = (M + kBlockM - 1) / kBlockM;
-  const int n_tiles = (x_rows + block_n - 1) / block_n;
-  const int tiles = m_tiles * n_tiles;
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (pair) {
+    const int pair_tiles = ((m_tiles + 1) / 2) * n_tiles;
+    if (dual) return launch_pair<128, true, true>(tmA, tmB, a, pair_tiles, stream);
+    return launch_pair<256, false, true>(tmA, tmB, a, pair_tiles, stream);
+  }
   if (dual) return launch_persist<128, true, true>(tmA, tmB, a, tiles, stream);
   if (block_n == 128) return launch_persist<128, false, true>(tmA, tmB, a, tiles, stream);
   return launch_persist<256, false, true>(tmA, tmB, a, tiles, stream);
