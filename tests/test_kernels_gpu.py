@@ -73,6 +73,22 @@ def test_linear_bf16(rows, M, K):
     close(y, ref, 2e-2 * math.sqrt(K / 64), 2e-2)
 
 
+@pytest.mark.parametrize("rows,M,K", [(2600, 2176, 512), (4100, 1280, 192), (2304, 2048, 1024)])
+def test_linear_many_tiles(rows, M, K):
+    """More than one wave of tiles: the persistent kernels (CTA pairs by default; an odd
+    number of 128-feature tiles leaves one CTA of the last pair without a tile)."""
+    x, w = rnd(rows, K), rnd(M, K, scale=0.05)
+    close(F.linear(x, w), R.linear(x, w), 2e-2 * math.sqrt(K / 64), 2e-2)
+    b = rnd(M, dtype=torch.float32, seed=3)
+    y = F.linear(x, w, bias=b, out_dtype=torch.float32)
+    close(y, x.float() @ w.float().t() + b, 1e-2 * math.sqrt(K / 64), 5e-3)
+
+
+def test_linear_gated_many_tiles():
+    x, w = rnd(2700, 512), rnd(2 * 1152, 512, scale=0.05)
+    close(F.linear_gated(x, w), R.linear_gated(x, w), 3e-2, 3e-2)
+
+
 def test_linear_fp32_out_bias():
     x, w, b = rnd(40, 512), rnd(300, 512, scale=0.05), rnd(300, dtype=torch.float32)
     y = F.linear(x, w, bias=b, out_dtype=torch.float32)

@@ -411,6 +411,8 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
   }
 }
 
+constexpr int kPairChunks = 2;   // k-blocks per stage of the CTA-pair kernel
+
 // CTA-pair form of the persistent kernel: the two CTAs of a cluster own one
 // 256 x BN output tile and multiply it with cta_group::2 instructions, so every
 // SM fetches its own 128 weight rows and only half of the activation rows from
@@ -418,7 +420,10 @@ gemm_wx_persist_kernel(const __grid_constant__ CUtensorMap tmA,
 // fetch, not by the multipliers).  Each CTA loads its operands with its own TMA
 // ring; the odd CTA forwards its "stage filled" events to the even CTA, whose
 // MMA thread issues for both and releases the stages and accumulators of both
-// through commits addressed to either CTA's barriers.
+// through commits addressed to either CTA's barriers.  A stage holds kPairChunks
+// k-blocks, fetched by one TMA instruction per operand through tensor maps that
+// view K as [K / chunk, chunk]: the feed of the single-CTA form measured a fixed
+// cost per TMA instruction, not per byte.
 template <int BN, bool DUAL, bool FP8>
 __global__ void __launch_bounds__(192)
 gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -427,7 +432,8 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   constexpr int kBK = FP8 ? 2 * kBlockK : kBlockK;
   constexpr int kATiles = kATile * (DUAL ? 2 : 1);
   constexpr int kBHalf = (BN / 2) * kBlockK * 2;
-  constexpr int kStageBytes = kATiles + kBHalf;
+  constexpr int kKC = kPairChunks;
+  constexpr int kStageBytes = kKC * (kATiles + kBHalf);
   constexpr uint32_t kAccCols = DUAL ? 2 * BN : BN;
   constexpr uint32_t kCols = tmem_cols<2 * BN>(DUAL);
   static_assert(kCols <= 512, "two accumulators must fit tensor memory");
@@ -442,7 +448,7 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   const int m_pairs = (m_tiles + 1) / 2;
   const int n_tiles = (args.rows + BN - 1) / BN;
   const int total = m_pairs * n_tiles;
-  const int num_k = (args.K + kBK - 1) / kBK;
+  const int num_k = (args.K + kKC * kBK - 1) / (kKC * kBK);   // stages of K
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -505,15 +511,12 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           uint8_t* st = smem + (size_t)s * kStageBytes;
           tc::mbar_expect_tx(&full_bar[s], kStageBytes);
-          const int kx = kb * kBK;
-          // a weight tile past the last one reads as zeros
-          tc::tma_load_3d(st, &tmA, &full_bar[s], kx, m_tile * kBlockM, 0);
+          // weight rows past the last tile and chunks past K read as zeros
+          tc::tma_load_3d(st, &tmA, &full_bar[s], 0, m_tile * kBlockM, kb * kKC);
           if (DUAL)
-            tc::tma_load_3d(st + kATile, &tmA, &full_bar[s], kx,
-                            args.dual_offset + m_tile * kBlockM, 0);
-          const int src = args.k_per_peer > 0 ? kx / args.k_per_peer : 0;
-          tc::tma_load_2d(st + kATiles, &tmBs.m[src], &full_bar[s], kx - src * args.k_per_peer,
-                          row0);
+            tc::tma_load_3d(st + kKC * kATile, &tmA, &full_bar[s], 0,
+                            args.dual_offset + m_tile * kBlockM, kb * kKC);
+          tc::tma_load_3d(st + kKC * kATiles, &tmBs.m[0], &full_bar[s], 0, row0, kb * kKC);
           if (++s == stages) {
             s = 0;
             ph ^= 1u;
@@ -574,7 +577,7 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           tc::tc_fence_after_sync();
           const uint64_t adesc = desc0 + (uint64_t)((uint32_t)s * (uint32_t)(kStageBytes >> 4));
-          const uint64_t bdesc = adesc + (uint64_t)(kATiles >> 4);
+          const uint64_t bdesc = adesc + (uint64_t)((kKC * kATiles) >> 4);
           int sn = s + 1;
           uint32_t phn = ph;
           if (sn == stages) {
@@ -584,18 +587,23 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           ready = tc::mbar_test_wait(&full_bar[sn], phn) &&
                   tc::mbar_test_wait(&peer_full[sn], phn);
 #pragma unroll
-          for (int k = 0; k < kBlockK / 16; ++k) {
-            const uint32_t acc = (kb | k) != 0;
-            if (FP8)
-              tc::umma_f8_pair(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
-            else
-              tc::umma_f16_pair(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
-            if (DUAL) {
-              const uint64_t a2desc = adesc + (uint64_t)(kATile >> 4);
-              if (FP8)
-                tc::umma_f8_pair(d + BN, a2desc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+          for (int c = 0; c < kKC; ++c) {
+            const uint64_t ad = adesc + (uint64_t)((c * kATile) >> 4);
+            const uint64_t bd = bdesc + (uint64_t)((c * kBHalf) >> 4);
+#pragma unroll
+            for (int k = 0; k < kBlockK / 16; ++k) {
+              const uint32_t acc = (kb | c | k) != 0;
+                if (FP8)
+                tc::umma_f8_pair(d, ad + 2 * k, bd + 2 * k, kIdesc, acc);
               else
-                tc::umma_f16_pair(d + BN, a2desc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+                tc::umma_f16_pair(d, ad + 2 * k, bd + 2 * k, kIdesc, acc);
+              if (DUAL) {
+                const uint64_t a2d = ad + (uint64_t)((kKC * kATile) >> 4);
+                if (FP8)
+                  tc::umma_f8_pair(d + BN, a2d + 2 * k, bd + 2 * k, kIdesc, acc);
+                else
+                  tc::umma_f16_pair(d + BN, a2d + 2 * k, bd + 2 * k, kIdesc, acc);
+              }
             }
           }
           tc::umma_commit_pair(empty0 + 8u * (uint32_t)s);
@@ -656,7 +664,7 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
 template <int BN, bool DUAL, bool FP8 = false>
 int launch_pair(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int pair_tiles,
                 cudaStream_t stream) {
-  constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + (BN / 2) * kBlockK * 2;
+  constexpr int kStageBytes = kPairChunks * (kATile * (DUAL ? 2 : 1) + (BN / 2) * kBlockK * 2);
   int stages = (192 * 1024) / kStageBytes;
   if (stages > 8) stages = 8;
   a.stages = stages;
@@ -789,10 +797,22 @@ int launch(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int m_tiles, in
   return US_OK;
 }
 
+// Operand view of the CTA-pair kernel: [rows, K] row-major seen as
+// (chunk, rows, K / chunk) with chunk = 128 bytes of K, box (chunk, box_rows, kPairChunks).
+static int pair_tmap(CUtensorMap* out, const void* base, int dtype, int rows, int K, long long ld,
+                     uint32_t box_rows) {
+  const uint64_t eb = dtype == US_TMAP_U8 ? 1 : 2;
+  const uint64_t chunk = 128 / eb;
+  uint64_t dims[3] = {chunk, (uint64_t)rows, (uint64_t)K / chunk};
+  uint64_t strides[2] = {(uint64_t)ld * eb, 128};
+  uint32_t box[3] = {(uint32_t)chunk, box_rows, (uint32_t)kPairChunks};
+  return us_tmap_encode(out, base, dtype, 3, dims, strides, box, US_SWZ_128);
+}
+
 static bool pair_enabled() {
   static const bool on = [] {
     const char* e = getenv("US_GEMM_PAIR");
-    return e != nullptr && e[0] == '1';
+    return !(e != nullptr && e[0] == '0');
   }();
   return on;
 }
@@ -827,8 +847,8 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
   if (num_tiles) US_REQUIRE(tile_group && tile_row0 && tile_rows && max_tiles >= 1);
 
   // Dense problems of more than one wave run on CTA pairs (US_GEMM_PAIR=0: single CTAs).
-  const bool pair = pair_enabled() && num_tiles == nullptr && G == 1 &&
-                    !(ps.x_peers && ps.rows_per_peer > 0) &&
+  const bool pair = pair_enabled() && num_tiles == nullptr && G == 1 && !ps.x_peers &&
+                    (K % kBlockK) == 0 &&
                     (dual ? block_n == 128 : block_n == 256) &&
                     (long long)((M + kBlockM - 1) / kBlockM) * ((x_rows + block_n - 1) / block_n) >
                         148;
@@ -836,11 +856,22 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
 
   CUtensorMap tmA;
   BMaps tmB;
-  int rc = us_tmap_3d(&tmA, W, US_TMAP_BF16, (uint64_t)G, (uint64_t)w_rows, (uint64_t)K,
-                      (uint64_t)ldw, (uint64_t)w_rows * (uint64_t)ldw, kBlockM, kBlockK,
-                      US_SWZ_128);
-  if (rc) return rc;
-  if (ps.x_peers && ps.rows_per_peer > 0) {
+  int rc;
+  if (pair) {
+    rc = pair_tmap(&tmA, W, US_TMAP_BF16, w_rows, K, ldw, kBlockM);
+    if (rc) return rc;
+    rc = pair_tmap(&tmB.m[0], X, US_TMAP_BF16, x_rows, K, ldx, box_n);
+    if (rc) return rc;
+    for (int p = 1; p < 8; ++p) tmB.m[p] = tmB.m[0];
+  } else {
+    rc = us_tmap_3d(&tmA, W, US_TMAP_BF16, (uint64_t)G, (uint64_t)w_rows, (uint64_t)K,
+                    (uint64_t)ldw, (uint64_t)w_rows * (uint64_t)ldw, kBlockM, kBlockK,
+                    US_SWZ_128);
+    if (rc) return rc;
+  }
+  if (pair) {
+    // maps built above
+  } else if (ps.x_peers && ps.rows_per_peer > 0) {
     US_REQUIRE(ps.n_peers >= 1 && ps.n_peers <= 8 && (ps.rows_per_peer % block_n) == 0 &&
                ps.rows_per_peer * ps.n_peers >= x_rows && num_tiles == nullptr);
     for (int p = 0; p < ps.n_peers; ++p) {
@@ -1092,15 +1123,23 @@ US_API int us_gemm_fp8_rowscale(const void* Wq, const void* Xq, void* out, int w
   US_REQUIRE(dual ? block_n == 128 : (block_n == 128 || block_n == 256));
   CUtensorMap tmA;
   BMaps tmB;
-  int rc = us_tmap_3d(&tmA, Wq, US_TMAP_U8, 1, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw,
-                      (uint64_t)w_rows * (uint64_t)ldw, kBlockM, 2 * kBlockK, US_SWZ_128);
-  if (rc) return rc;
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
   const int n_tiles = (x_rows + block_n - 1) / block_n;
   const int tiles = m_tiles * n_tiles;
-  const bool pair = pair_enabled() && tiles > 148 && (dual ? block_n == 128 : block_n == 256);
-  rc = us_tmap_2d(&tmB.m[0], Xq, US_TMAP_U8, (uint64_t)x_rows, (uint64_t)K, (uint64_t)ldx,
-                  (uint32_t)(pair ? block_n / 2 : block_n), 2 * kBlockK, US_SWZ_128);
+  const bool pair = pair_enabled() && tiles > 148 && (K % 128) == 0 &&
+                    (dual ? block_n == 128 : block_n == 256);
+  int rc;
+  if (pair) {
+    rc = pair_tmap(&tmA, Wq, US_TMAP_U8, w_rows, K, ldw, kBlockM);
+    if (rc) return rc;
+    rc = pair_tmap(&tmB.m[0], Xq, US_TMAP_U8, x_rows, K, ldx, (uint32_t)block_n / 2);
+  } else {
+    rc = us_tmap_3d(&tmA, Wq, US_TMAP_U8, 1, (uint64_t)w_rows, (uint64_t)K, (uint64_t)ldw,
+                    (uint64_t)w_rows * (uint64_t)ldw, kBlockM, 2 * kBlockK, US_SWZ_128);
+    if (rc) return rc;
+    rc = us_tmap_2d(&tmB.m[0], Xq, US_TMAP_U8, (uint64_t)x_rows, (uint64_t)K, (uint64_t)ldx,
+                    (uint32_t)block_n, 2 * kBlockK, US_SWZ_128);
+  }
   if (rc) return rc;
   for (int p = 1; p < 8; ++p) tmB.m[p] = tmB.m[0];
   GemmArgs a;

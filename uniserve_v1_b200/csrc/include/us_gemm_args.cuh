@@ -2,6 +2,7 @@
 // kernels (bf16 and block-scaled fp8).
 #pragma once
 #include "us_common.cuh"
+#include "us_tc05.cuh"
 #include "us_tmap.h"
 
 namespace {
@@ -94,47 +95,65 @@ constexpr int kEpiStageBytes = 16 * 1024;   // two staging tiles of 16 rows x 12
 // (scatter by feature, reduce-scatter by row) or the token owner's combine buffer.
 template <bool DUAL>
 struct Epilogue {
-  const GemmArgs& a;
+  // Everything the per-element code needs is copied out of the argument block
+  // once: the block lives in parameter memory, and reading it per element (after
+  // every barrier the compiler must re-read it) cost several dependent loads and
+  // branches per value - 3,300 clocks per 16-row chunk, more than the mainloop.
   const int m0, ml, m, row0;
   const bool m_ok;
   float bias;
   char* tile_base;     // element (row0, m0) of the destination; null = per-row lookup
   long long row_bytes;
   int esz;
+  int M, act, route_per, vec_store;
+  long long ldo;
+  const float* scale_rows;   // row_scale + row0, or null
+  bool scale_first;
+  const int* route_rows;     // route_map + row0, or null
+  const float* route_w;
+  const int* out_rows;       // out_row_map + row0, or null
+  char* out;
+  const GemmArgs& a;         // rare paths only (the peer table of the route push)
   __device__ __forceinline__ Epilogue(const GemmArgs& args, int group, int m0_, int ml_, int row0_)
-      : a(args), m0(m0_), ml(ml_), m(m0_ + ml_), row0(row0_), m_ok(m0_ + ml_ < args.M), bias(0.f),
-        tile_base(nullptr), row_bytes(0), esz(args.out_dtype == 0 ? 2 : 4) {
-    if (a.bias != nullptr && m_ok) {
-      const size_t bi = (size_t)group * a.M + m;
-      bias = a.bias_dtype == 0 ? us::bf2f(((const __nv_bfloat16*)a.bias)[bi])
-                               : ((const float*)a.bias)[bi];
+      : m0(m0_), ml(ml_), m(m0_ + ml_), row0(row0_), m_ok(m0_ + ml_ < args.M), bias(0.f),
+        tile_base(nullptr), row_bytes(0), esz(args.out_dtype == 0 ? 2 : 4), M(args.M),
+        act(args.act), route_per(args.route_per), vec_store(args.vec_store), ldo(args.ldo),
+        scale_rows(args.row_scale ? args.row_scale + row0_ : nullptr),
+        scale_first(args.scale_first != 0),
+        route_rows(args.route_map ? args.route_map + row0_ : nullptr), route_w(args.route_w),
+        out_rows(args.out_row_map ? args.out_row_map + row0_ : nullptr), out((char*)args.out),
+        a(args) {
+    if (args.bias != nullptr && m_ok) {
+      const size_t bi = (size_t)group * args.M + m;
+      bias = args.bias_dtype == 0 ? us::bf2f(((const __nv_bfloat16*)args.bias)[bi])
+                                  : ((const float*)args.bias)[bi];
     }
-    row_bytes = a.ldo * esz;
-    if (a.route_map != nullptr || a.out_row_map != nullptr) return;
-    if (a.peer_rows > 0) {   // a tile lies inside one owner's interval
-      const int p = row0 / a.peer_rows;
-      tile_base = (char*)a.peer_out[p] +
-                  (((size_t)a.peer_slot * a.peer_rows + (size_t)(row0 - p * a.peer_rows)) * a.ldo +
-                   m0) * esz;
-    } else if (a.peer_cols > 0) {
-      const int p = m0 / a.peer_cols;
-      tile_base = (char*)a.peer_out[p] +
-                  ((size_t)(a.peer_row_offset + row0) * a.ldo + (m0 - p * a.peer_cols)) * esz;
+    row_bytes = ldo * esz;
+    if (route_rows != nullptr || out_rows != nullptr) return;
+    if (args.peer_rows > 0) {   // a tile lies inside one owner's interval
+      const int p = row0 / args.peer_rows;
+      tile_base = (char*)args.peer_out[p] +
+                  (((size_t)args.peer_slot * args.peer_rows +
+                    (size_t)(row0 - p * args.peer_rows)) * ldo + m0) * esz;
+    } else if (args.peer_cols > 0) {
+      const int p = m0 / args.peer_cols;
+      tile_base = (char*)args.peer_out[p] +
+                  ((size_t)(args.peer_row_offset + row0) * ldo + (m0 - p * args.peer_cols)) * esz;
     } else {
-      tile_base = (char*)a.out + ((size_t)row0 * a.ldo + m0) * esz;
+      tile_base = out + ((size_t)row0 * ldo + m0) * esz;
     }
   }
   // Value of tile row r for this thread's feature (everything but the store).
   __device__ __forceinline__ float value(int r, float val, float gate) const {
-    if (a.scale_first && a.row_scale != nullptr) {
-      const float sc = a.row_scale[row0 + r];
+    if (scale_first && scale_rows != nullptr) {
+      const float sc = scale_rows[r];
       val *= sc;
       gate *= sc;
     }
     if (DUAL) {
-      if (a.act == 0) {
+      if (act == 0) {
         val = val * silu_f(gate);
-      } else if (a.act == 1) {
+      } else if (act == 1) {
         const float sg = us::bf2f(us::f2bf(silu_f(us::bf2f(us::f2bf(gate)))));
         val = us::bf2f(us::f2bf(val)) * sg;
       } else {
@@ -142,22 +161,22 @@ struct Epilogue {
       }
     }
     val += bias;
-    if (a.route_map != nullptr) return val * a.route_w[a.route_map[row0 + r]];
-    if (a.row_scale != nullptr && !a.scale_first) val *= a.row_scale[row0 + r];
+    if (route_rows != nullptr) return val * route_w[route_rows[r]];
+    if (scale_rows != nullptr && !scale_first) val *= scale_rows[r];
     return val;
   }
   // Destination of tile row r, feature m0 (null = the row is dropped).
   __device__ __forceinline__ char* row_ptr(int r) const {
     if (tile_base != nullptr) return tile_base + (long long)r * row_bytes;
-    if (a.route_map != nullptr) {
-      const int i = a.route_map[row0 + r];
-      const int src = i / a.route_per;
-      const int dst = i - src * a.route_per;
-      return (char*)a.peer_out[src] + ((size_t)dst * a.ldo + m0) * 2;
+    if (route_rows != nullptr) {
+      const int i = route_rows[r];
+      const int src = i / route_per;
+      const int dst = i - src * route_per;
+      return (char*)a.peer_out[src] + ((size_t)dst * ldo + m0) * 2;
     }
-    const int orow = a.out_row_map[row0 + r];
+    const int orow = out_rows[r];
     if (orow < 0) return nullptr;
-    return (char*)a.out + ((size_t)orow * a.ldo + m0) * esz;
+    return out + ((size_t)orow * ldo + m0) * esz;
   }
   // Scalar store of one element (split-K reduction, unaligned destinations).
   __device__ __forceinline__ void store(int r, float val, float gate) const {
@@ -165,7 +184,7 @@ struct Epilogue {
     char* dst = row_ptr(r);
     if (dst == nullptr) return;
     const float x = value(r, val, gate);
-    if (a.out_dtype == 0)
+    if (esz == 2)
       ((__nv_bfloat16*)dst)[ml] = us::f2bf(x);
     else
       ((float*)dst)[ml] = x;
@@ -176,44 +195,65 @@ struct Epilogue {
   __device__ __forceinline__ void store_chunk16(int c, int chunk, const uint32_t (&v)[16],
                                                 const uint32_t (&g)[16], int nrows,
                                                 uint8_t* stage) const {
-    if (!a.vec_store) {
+    if (!vec_store) {
 #pragma unroll
       for (int j = 0; j < 16; ++j)
         if (c + j < nrows) store(c + j, __uint_as_float(v[j]), DUAL ? __uint_as_float(g[j]) : 0.f);
       return;
     }
-    uint8_t* buf = stage + (chunk & 1) * (kEpiStageBytes / 2);
-    const int pitch = 128 * esz;
+    const uint32_t buf = tc::smem_u32(stage) + (uint32_t)(chunk & 1) * (kEpiStageBytes / 2);
+    // fast path: nothing per row but the gated activation and the bias
+    const bool plain = scale_rows == nullptr && route_rows == nullptr;
+    if (esz == 2) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float x = (c + j < nrows)
-                          ? value(c + j, __uint_as_float(v[j]), DUAL ? __uint_as_float(g[j]) : 0.f)
-                          : 0.f;
-      if (esz == 2)
-        *reinterpret_cast<__nv_bfloat16*>(buf + j * pitch + ml * 2) = us::f2bf(x);
-      else
-        *reinterpret_cast<float*>(buf + j * pitch + ml * 4) = x;
+      for (int j = 0; j < 16; ++j) {
+        float x = 0.f;
+        if (c + j < nrows) {
+          if (plain && !DUAL)
+            x = __uint_as_float(v[j]) + bias;
+          else
+            x = value(c + j, __uint_as_float(v[j]), DUAL ? __uint_as_float(g[j]) : 0.f);
+        }
+        const unsigned short h = __bfloat16_as_ushort(us::f2bf(x));
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(buf + (uint32_t)(j * 256 + ml * 2)), "h"(h)
+                     : "memory");
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float x = 0.f;
+        if (c + j < nrows)
+          x = value(c + j, __uint_as_float(v[j]), DUAL ? __uint_as_float(g[j]) : 0.f);
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(buf + (uint32_t)(j * 512 + ml * 4)), "f"(x)
+                     : "memory");
+      }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    const int per_row = pitch / 16;                 // 16-byte pieces per row: 16 or 32
-    const int feats = 16 / esz;                     // features per piece: 8 or 4
-    for (int id = ml; id < 16 * per_row; id += 128) {
-      const int r = id / per_row, seg = id - r * per_row;
+    // 16-byte pieces: 16 per row (bf16, 8 features each) or 32 per row (fp32, 4 each)
+    const int shift = esz == 2 ? 4 : 5;
+    const int feats = esz == 2 ? 8 : 4;
+    const int pieces = 16 << shift;
+    for (int id = ml; id < pieces; id += 128) {
+      const int r = id >> shift, seg = id & ((1 << shift) - 1);
       if (c + r >= nrows) continue;
       char* dst = row_ptr(c + r);
       if (dst == nullptr) continue;
       const int f0 = m0 + seg * feats;
-      if (f0 + feats <= a.M) {
-        *reinterpret_cast<uint4*>(dst + seg * 16) =
-            *reinterpret_cast<const uint4*>(buf + r * pitch + seg * 16);
+      uint4 piece;
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(piece.x), "=r"(piece.y), "=r"(piece.z), "=r"(piece.w)
+                   : "r"(buf + (uint32_t)(id * 16))
+                   : "memory");
+      if (f0 + feats <= M) {
+        *reinterpret_cast<uint4*>(dst + seg * 16) = piece;
       } else {
-        for (int f = 0; f0 + f < a.M && f < feats; ++f) {
+        const uint32_t w[4] = {piece.x, piece.y, piece.z, piece.w};
+        for (int f = 0; f0 + f < M && f < feats; ++f) {
           if (esz == 2)
-            ((__nv_bfloat16*)dst)[seg * feats + f] =
-                *reinterpret_cast<const __nv_bfloat16*>(buf + r * pitch + (seg * feats + f) * 2);
+            ((unsigned short*)dst)[seg * feats + f] =
+                (unsigned short)(w[f >> 1] >> ((f & 1) * 16));
           else
-            ((float*)dst)[seg * feats + f] =
-                *reinterpret_cast<const float*>(buf + r * pitch + (seg * feats + f) * 4);
+            ((uint32_t*)dst)[seg * feats + f] = w[f];
         }
       }
     }
