@@ -424,7 +424,14 @@ constexpr int kPairChunks = 2;   // k-blocks per stage of the CTA-pair kernel
 // k-blocks, fetched by one TMA instruction per operand through tensor maps that
 // view K as [K / chunk, chunk]: the feed of the single-CTA form measured a fixed
 // cost per TMA instruction, not per byte.
-template <int BN, bool DUAL, bool FP8>
+//
+// SWAP (gated linears): the operands change roles.  The activation rows are the
+// 256-row side (128 per CTA); the other side is 128 value rows of the weight in
+// the even CTA and the matching 128 gate rows in the odd CTA, so one N = 256
+// instruction produces both halves and a thread (= activation row) finds value j
+// in column j and its gate in column 128 + j of its own lane.  The caller passes
+// the activation's map as tmA and the weight's as tmBs.m[0].
+template <int BN, bool DUAL, bool FP8, bool SWAP>
 __global__ void __launch_bounds__(192)
 gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ BMaps tmBs, const GemmArgs args) {
@@ -444,9 +451,11 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = tc::cluster_ctarank();          // 0 issues the multiplications
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
-  const int m_tiles = (args.M + kBlockM - 1) / kBlockM;
+  static_assert(!SWAP || (BN == 256 && !DUAL), "the swapped form is one 256-column accumulator");
+  // m: tiles of the 256-row (A) side, n: tiles of the other side
+  const int m_tiles = SWAP ? (args.rows + kBlockM - 1) / kBlockM : (args.M + kBlockM - 1) / kBlockM;
   const int m_pairs = (m_tiles + 1) / 2;
-  const int n_tiles = (args.rows + BN - 1) / BN;
+  const int n_tiles = SWAP ? args.M / kBlockM : (args.rows + BN - 1) / BN;
   const int total = m_pairs * n_tiles;
   const int num_k = (args.K + kKC * kBK - 1) / (kKC * kBK);   // stages of K
 
@@ -500,8 +509,11 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t ph = 0;
       bool ok = true;
       for (int t = pair; ok && t < total; t += pairs) {
-        const int m_tile = 2 * (t % m_pairs) + (int)rank;
-        const int row0 = (t / m_pairs) * BN + (int)rank * (BN / 2);
+        // plain: the weight tile runs fastest; swapped: the feature tile does (CTAs
+        // running together share the activation rows either way)
+        const int m_tile = 2 * (SWAP ? t / n_tiles : t % m_pairs) + (int)rank;
+        const int row0 = SWAP ? (t % n_tiles) * kBlockM + (rank ? args.dual_offset : 0)
+                              : (t / m_pairs) * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < num_k; ++kb) {
           if (!tc::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
             us_dev_fail(args.status, US_DEV_TIMEOUT_EMPTY);
@@ -624,8 +636,9 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     int it = 0;
     for (int t = pair; t < total; t += pairs, ++it) {
       const int buf = it & 1;
-      const int m_tile = 2 * (t % m_pairs) + (int)rank, row0 = (t / m_pairs) * BN;
-      const int nrows = m_tile < m_tiles ? min(BN, args.rows - row0) : 0;
+      const int m_tile = 2 * (SWAP ? t / n_tiles : t % m_pairs) + (int)rank;
+      const int row0 = SWAP ? 0 : (t / m_pairs) * BN;
+      const int nrows = SWAP ? 0 : (m_tile < m_tiles ? min(BN, args.rows - row0) : 0);
       if (!tc::mbar_wait(&acc_full[buf], (uint32_t)(it >> 1) & 1u, abort_flag)) {
         us_dev_fail(args.status, US_DEV_TIMEOUT_ACC);
         *epi_fail = 1;
@@ -634,18 +647,65 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       if (*epi_fail != 0) break;
       tc::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)buf * kAccCols + ((uint32_t)(q * 32) << 16);
-      Epilogue<DUAL> epi(args, 0, m_tile * kBlockM, ml, row0);
-      int chunk = 0;
+      if (SWAP) {
+        // this thread's activation row; features f0 .. f0 + 127 leave as 32-byte pieces
+        const int xrow = m_tile * kBlockM + ml;
+        const bool row_ok = xrow < args.rows;
+        const int f0 = (t % n_tiles) * kBlockM;
+        const int act = args.act;
+        const float sc = (args.row_scale != nullptr && row_ok) ? args.row_scale[xrow] : 1.f;
+        __nv_bfloat16* dst = (__nv_bfloat16*)args.out + (size_t)(row_ok ? xrow : 0) * args.ldo + f0;
+        const bool vec = args.vec_store != 0;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16, ++chunk) {
-        if (c >= nrows) break;  // uniform over the CTA
-        uint32_t v[16], g[16];
-        tc::tmem_ld16(taddr + c, v);
-        if (DUAL) tc::tmem_ld16(taddr + BN + c, g);
-        tc::tmem_ld_wait();
-        epi.store_chunk16(c, chunk, v, g, nrows, epi_stage);
+        for (int c = 0; c < kBlockM; c += 16) {
+          uint32_t v[16], g[16];
+          tc::tmem_ld16(taddr + c, v);
+          tc::tmem_ld16(taddr + kBlockM + c, g);
+          tc::tmem_ld_wait();
+          uint32_t o[8];
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            float r2[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              float val = __uint_as_float(v[j + h]) * sc, gate = __uint_as_float(g[j + h]) * sc;
+              if (act == 0) {
+                val = val * silu_f(gate);
+              } else if (act == 1) {
+                const float sg = us::bf2f(us::f2bf(silu_f(us::bf2f(us::f2bf(gate)))));
+                val = us::bf2f(us::f2bf(val)) * sg;
+              } else {
+                val = val * gelu_tanh_f(gate);
+              }
+              r2[h] = val;
+            }
+            o[j >> 1] = (uint32_t)__bfloat16_as_ushort(us::f2bf(r2[0])) |
+                        ((uint32_t)__bfloat16_as_ushort(us::f2bf(r2[1])) << 16);
+          }
+          if (row_ok) {
+            if (vec) {
+              *reinterpret_cast<uint4*>(dst + c) = make_uint4(o[0], o[1], o[2], o[3]);
+              *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) reinterpret_cast<uint32_t*>(dst + c)[j] = o[j];
+            }
+          }
+        }
+      } else {
+        Epilogue<DUAL> epi(args, 0, m_tile * kBlockM, ml, row0);
+        int chunk = 0;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16, ++chunk) {
+          if (c >= nrows) break;  // uniform over the CTA
+          uint32_t v[16], g[16];
+          tc::tmem_ld16(taddr + c, v);
+          if (DUAL) tc::tmem_ld16(taddr + BN + c, g);
+          tc::tmem_ld_wait();
+          epi.store_chunk16(c, chunk, v, g, nrows, epi_stage);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
       tc::tc_fence_before_sync();
       if (rank == 0)
         tc::mbar_arrive(&acc_empty[buf]);
@@ -661,7 +721,7 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   }
 }
 
-template <int BN, bool DUAL, bool FP8 = false>
+template <int BN, bool DUAL, bool FP8 = false, bool SWAP = false>
 int launch_pair(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int pair_tiles,
                 cudaStream_t stream) {
   constexpr int kStageBytes = kPairChunks * (kATile * (DUAL ? 2 : 1) + (BN / 2) * kBlockK * 2);
@@ -673,7 +733,7 @@ int launch_pair(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int pair_t
   static bool configured = false;
   static int sms = 0;
   if (!configured) {
-    US_CUDA_CHECK(cudaFuncSetAttribute(gemm_wx_pair_kernel<BN, DUAL, FP8>,
+    US_CUDA_CHECK(cudaFuncSetAttribute(gemm_wx_pair_kernel<BN, DUAL, FP8, SWAP>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     int dev = 0;
     US_CUDA_CHECK(cudaGetDevice(&dev));
@@ -697,7 +757,7 @@ int launch_pair(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int pair_t
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    US_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_wx_pair_kernel<BN, DUAL, FP8>, &cfg));
+    US_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_wx_pair_kernel<BN, DUAL, FP8, SWAP>, &cfg));
     max_pairs = n < 1 ? 1 : n;
   }
   const int pairs = pair_tiles < max_pairs ? pair_tiles : max_pairs;
@@ -706,7 +766,7 @@ int launch_pair(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int pair_t
   attr[1].val.programmaticStreamSerializationAllowed = us::pdl_enabled() ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  US_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_wx_pair_kernel<BN, DUAL, FP8>, tmA, tmB, a));
+  US_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_wx_pair_kernel<BN, DUAL, FP8, SWAP>, tmA, tmB, a));
   return US_OK;
 }
 
@@ -853,11 +913,21 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
                     (long long)((M + kBlockM - 1) / kBlockM) * ((x_rows + block_n - 1) / block_n) >
                         148;
   const uint32_t box_n = (uint32_t)(pair ? block_n / 2 : block_n);
+  // gated: operands swapped, value and gate rows side by side in one accumulator
+  const bool swap = pair && dual && (M % kBlockM) == 0 && out_dtype == 0 && bias == nullptr &&
+                    row_scale == nullptr && out_row_map == nullptr && ps.out_peers == nullptr &&
+                    out != nullptr;
 
   CUtensorMap tmA;
   BMaps tmB;
   int rc;
-  if (pair) {
+  if (swap) {
+    rc = pair_tmap(&tmA, X, US_TMAP_BF16, x_rows, K, ldx, kBlockM);
+    if (rc) return rc;
+    rc = pair_tmap(&tmB.m[0], W, US_TMAP_BF16, w_rows, K, ldw, kBlockM);
+    if (rc) return rc;
+    for (int p = 1; p < 8; ++p) tmB.m[p] = tmB.m[0];
+  } else if (pair) {
     rc = pair_tmap(&tmA, W, US_TMAP_BF16, w_rows, K, ldw, kBlockM);
     if (rc) return rc;
     rc = pair_tmap(&tmB.m[0], X, US_TMAP_BF16, x_rows, K, ldx, box_n);
@@ -977,6 +1047,11 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
     const char* e = getenv("US_NO_PERSIST");
     return e && e[0] == '1';
   }();
+  if (swap) {
+    const int x_tiles = (x_rows + kBlockM - 1) / kBlockM;
+    return launch_pair<256, false, false, true>(tmA, tmB, a, ((x_tiles + 1) / 2) * (M / kBlockM),
+                                                stream);
+  }
   if (pair) {
     const int pair_tiles = ((m_tiles + 1) / 2) * n_tiles;
     if (dual) return launch_pair<128, true>(tmA, tmB, a, pair_tiles, stream);
@@ -1129,7 +1204,12 @@ US_API int us_gemm_fp8_rowscale(const void* Wq, const void* Xq, void* out, int w
   const bool pair = pair_enabled() && tiles > 148 && (K % 128) == 0 &&
                     (dual ? block_n == 128 : block_n == 256);
   int rc;
-  if (pair) {
+  const bool swap = pair && dual && (M % kBlockM) == 0 && out_dtype == 0;
+  if (swap) {
+    rc = pair_tmap(&tmA, Xq, US_TMAP_U8, x_rows, K, ldx, kBlockM);
+    if (rc) return rc;
+    rc = pair_tmap(&tmB.m[0], Wq, US_TMAP_U8, w_rows, K, ldw, kBlockM);
+  } else if (pair) {
     rc = pair_tmap(&tmA, Wq, US_TMAP_U8, w_rows, K, ldw, kBlockM);
     if (rc) return rc;
     rc = pair_tmap(&tmB.m[0], Xq, US_TMAP_U8, x_rows, K, ldx, (uint32_t)block_n / 2);
@@ -1151,6 +1231,11 @@ US_API int us_gemm_fp8_rowscale(const void* Wq, const void* Xq, void* out, int w
   const long long esz = out_dtype == 0 ? 2 : 4;
   a.vec_store = (((ldo * esz) % 16) == 0 && ((uintptr_t)out % 16) == 0) ? 1 : 0;
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (swap) {
+    const int x_tiles = (x_rows + kBlockM - 1) / kBlockM;
+    return launch_pair<256, false, true, true>(tmA, tmB, a, ((x_tiles + 1) / 2) * (M / kBlockM),
+                                               stream);
+  }
   if (pair) {
     const int pair_tiles = ((m_tiles + 1) / 2) * n_tiles;
     if (dual) return launch_pair<128, true, true>(tmA, tmB, a, pair_tiles, stream);
