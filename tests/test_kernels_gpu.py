@@ -388,6 +388,33 @@ def test_gemm_peer_modes_with_local_buffers_as_peers():
         assert float(slots[p_][0].abs().max()) == 0.0
 
 
+def test_gemm_output_modes_many_tiles():
+    """Scatter by feature block, reduce-scatter by row interval and the row-mapped output on
+    problems of more than one wave of tiles (the CTA-pair kernel, one activation row per
+    epilogue thread), local tensors standing in for the peers' buffers."""
+    from uniserve_v1_b200.parallel import tp_fused, ulysses  # noqa: F401  (register signatures)
+    rows, K, P = 2500, 256, 2
+    x = rnd(rows, K, seed=41)
+    st = N.stream()
+    wide = rnd(2048, K, scale=0.05, seed=42)           # 2 x 1024 features
+    dst = [torch.zeros(rows + 8, 1024, dtype=BF, device=DEV) for _ in range(P)]
+    N.call("us_gemm_wx_scatter", N.ptr(wide), N.ptr(x), 2048, K, rows, K, K, 1024, _ptr_array(dst),
+           1024, 8, 256, st)
+    refw = x.float() @ wide.float().t()
+    for p_ in range(P):
+        close(dst[p_][8:], refw[:, p_ * 1024:(p_ + 1) * 1024], 3e-2, 3e-2)
+        assert float(dst[p_][:8].abs().max()) == 0.0
+    rows2, M = 2560, 2048
+    x2, w = rnd(rows2, K, seed=43), rnd(M, K, scale=0.05, seed=44)
+    ref = x2.float() @ w.float().t()
+    slots = [torch.zeros(2, rows2 // 2, M, dtype=BF, device=DEV) for _ in range(P)]
+    N.call("us_gemm_wx_reduce_scatter", N.ptr(w), N.ptr(x2), M, K, rows2, K, K, M,
+           _ptr_array(slots), P, rows2 // 2, 1, 0, 256, st)
+    for p_ in range(P):
+        close(slots[p_][1], ref[p_ * (rows2 // 2):(p_ + 1) * (rows2 // 2)], 3e-2, 3e-2)
+        assert float(slots[p_][0].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("causal", [False, True])
 def test_flash_attn_head_dim_64(causal):
     """64-wide heads on the two-tile kernel (row-strided q / k / v views, GQA 2:1)."""

@@ -425,13 +425,17 @@ constexpr int kPairChunks = 2;   // k-blocks per stage of the CTA-pair kernel
 // view K as [K / chunk, chunk]: the feed of the single-CTA form measured a fixed
 // cost per TMA instruction, not per byte.
 //
-// SWAP (gated linears): the operands change roles.  The activation rows are the
-// 256-row side (128 per CTA); the other side is 128 value rows of the weight in
+// SWAP: the operands change roles.  The activation rows are the 256-row side (128
+// per CTA) and every epilogue thread owns one activation row, whose features it
+// stores from registers as 32-byte pieces - no staging tile, and every destination
+// (plain, row-mapped, a peer's buffer by feature block or by row interval, the
+// token owner's combine buffer) is one pointer per thread.  SWAP = 2 (dense): the
+// other side is 256 weight rows, 128 per CTA.  SWAP = 1 (gated): 128 value rows in
 // the even CTA and the matching 128 gate rows in the odd CTA, so one N = 256
-// instruction produces both halves and a thread (= activation row) finds value j
-// in column j and its gate in column 128 + j of its own lane.  The caller passes
-// the activation's map as tmA and the weight's as tmBs.m[0].
-template <int BN, bool DUAL, bool FP8, bool SWAP>
+// instruction produces both halves and a thread finds value j in column j and its
+// gate in column 128 + j of its own lane.  The caller passes the activation's map
+// as tmA and the weight's as tmBs.m[0].
+template <int BN, bool DUAL, bool FP8, int SWAP>
 __global__ void __launch_bounds__(192)
 gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ BMaps tmBs, const GemmArgs args) {
@@ -455,7 +459,8 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   // m: tiles of the 256-row (A) side, n: tiles of the other side
   const int m_tiles = SWAP ? (args.rows + kBlockM - 1) / kBlockM : (args.M + kBlockM - 1) / kBlockM;
   const int m_pairs = (m_tiles + 1) / 2;
-  const int n_tiles = SWAP ? args.M / kBlockM : (args.rows + BN - 1) / BN;
+  constexpr int kFeat = SWAP == 2 ? 2 * kBlockM : kBlockM;   // features per swapped tile
+  const int n_tiles = SWAP ? (args.M + kFeat - 1) / kFeat : (args.rows + BN - 1) / BN;
   const int total = m_pairs * n_tiles;
   const int num_k = (args.K + kKC * kBK - 1) / (kKC * kBK);   // stages of K
 
@@ -512,8 +517,9 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         // plain: the weight tile runs fastest; swapped: the feature tile does (CTAs
         // running together share the activation rows either way)
         const int m_tile = 2 * (SWAP ? t / n_tiles : t % m_pairs) + (int)rank;
-        const int row0 = SWAP ? (t % n_tiles) * kBlockM + (rank ? args.dual_offset : 0)
-                              : (t / m_pairs) * BN + (int)rank * (BN / 2);
+        const int row0 = SWAP == 1   ? (t % n_tiles) * kBlockM + (rank ? args.dual_offset : 0)
+                         : SWAP == 2 ? (t % n_tiles) * kFeat + (int)rank * kBlockM
+                                     : (t / m_pairs) * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < num_k; ++kb) {
           if (!tc::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
             us_dev_fail(args.status, US_DEV_TIMEOUT_EMPTY);
@@ -648,27 +654,52 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       tc::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)buf * kAccCols + ((uint32_t)(q * 32) << 16);
       if (SWAP) {
-        // this thread's activation row; features f0 .. f0 + 127 leave as 32-byte pieces
+        // this thread's activation row; its features leave as 32-byte pieces
         const int xrow = m_tile * kBlockM + ml;
-        const bool row_ok = xrow < args.rows;
-        const int f0 = (t % n_tiles) * kBlockM;
+        const int f0 = (t % n_tiles) * kFeat;
         const int act = args.act;
-        const float sc = (args.row_scale != nullptr && row_ok) ? args.row_scale[xrow] : 1.f;
-        __nv_bfloat16* dst = (__nv_bfloat16*)args.out + (size_t)(row_ok ? xrow : 0) * args.ldo + f0;
+        const int esz = args.out_dtype == 0 ? 2 : 4;
+        const int M = args.M;
         const bool vec = args.vec_store != 0;
+        const float* bias_f = args.bias_dtype == 0 ? nullptr : (const float*)args.bias;
+        const __nv_bfloat16* bias_h = args.bias_dtype == 0 ? (const __nv_bfloat16*)args.bias : nullptr;
+        const int peer_cols = args.peer_cols;
+        float pre = 1.f, post = 1.f;          // scale before the activation / of the result
+        char* dst = nullptr;                  // element (xrow, feature 0); null: row dropped
+        if (xrow < args.rows) {
+          if (args.row_scale != nullptr) (args.scale_first ? pre : post) = args.row_scale[xrow];
+          if (args.route_map != nullptr) {
+            const int i = args.route_map[xrow];
+            const int src = i / args.route_per;
+            post *= args.route_w[i];
+            dst = (char*)args.peer_out[src] + (size_t)(i - src * args.route_per) * args.ldo * 2;
+          } else if (args.out_row_map != nullptr) {
+            const int orow = args.out_row_map[xrow];
+            if (orow >= 0) dst = (char*)args.out + (size_t)orow * args.ldo * esz;
+          } else if (args.peer_rows > 0) {
+            const int p = xrow / args.peer_rows;
+            dst = (char*)args.peer_out[p] +
+                  ((size_t)args.peer_slot * args.peer_rows + (size_t)(xrow - p * args.peer_rows)) *
+                      args.ldo * esz;
+          } else if (peer_cols > 0) {
+            dst = (char*)(size_t)1;           // resolved per feature block below
+          } else {
+            dst = (char*)args.out + (size_t)xrow * args.ldo * esz;
+          }
+        }
 #pragma unroll 1
-        for (int c = 0; c < kBlockM; c += 16) {
+        for (int c = 0; c < kFeat; c += 16) {
+          if (f0 + c >= M) break;             // uniform: features past the last one
           uint32_t v[16], g[16];
           tc::tmem_ld16(taddr + c, v);
-          tc::tmem_ld16(taddr + kBlockM + c, g);
+          if (SWAP == 1) tc::tmem_ld16(taddr + kBlockM + c, g);
           tc::tmem_ld_wait();
-          uint32_t o[8];
+          float x[16];
 #pragma unroll
-          for (int j = 0; j < 16; j += 2) {
-            float r2[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              float val = __uint_as_float(v[j + h]) * sc, gate = __uint_as_float(g[j + h]) * sc;
+          for (int j = 0; j < 16; ++j) {
+            float val = __uint_as_float(v[j]) * pre;
+            if (SWAP == 1) {
+              const float gate = __uint_as_float(g[j]) * pre;
               if (act == 0) {
                 val = val * silu_f(gate);
               } else if (act == 1) {
@@ -677,18 +708,48 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
               } else {
                 val = val * gelu_tanh_f(gate);
               }
-              r2[h] = val;
             }
-            o[j >> 1] = (uint32_t)__bfloat16_as_ushort(us::f2bf(r2[0])) |
-                        ((uint32_t)__bfloat16_as_ushort(us::f2bf(r2[1])) << 16);
+            x[j] = val;
           }
-          if (row_ok) {
-            if (vec) {
-              *reinterpret_cast<uint4*>(dst + c) = make_uint4(o[0], o[1], o[2], o[3]);
-              *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+          if (bias_f != nullptr || bias_h != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (f0 + c + j < M)
+                x[j] += bias_f ? bias_f[f0 + c + j] : us::bf2f(bias_h[f0 + c + j]);
+          }
+          if (dst == nullptr) continue;
+          char* d = dst + (size_t)(f0 + c) * esz;
+          if (peer_cols > 0) {
+            const int p = (f0 + c) / peer_cols;
+            d = (char*)args.peer_out[p] +
+                ((size_t)(args.peer_row_offset + xrow) * args.ldo + (f0 + c - p * peer_cols)) * esz;
+          }
+          const bool whole = vec && f0 + c + 16 <= M;
+          if (esz == 2) {
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              o[j] = (uint32_t)__bfloat16_as_ushort(us::f2bf(x[2 * j] * post)) |
+                     ((uint32_t)__bfloat16_as_ushort(us::f2bf(x[2 * j + 1] * post)) << 16);
+            if (whole) {
+              *reinterpret_cast<uint4*>(d) = make_uint4(o[0], o[1], o[2], o[3]);
+              *reinterpret_cast<uint4*>(d + 16) = make_uint4(o[4], o[5], o[6], o[7]);
             } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) reinterpret_cast<uint32_t*>(dst + c)[j] = o[j];
+              for (int j = 0; j < 16; ++j)
+                if (f0 + c + j < M)
+                  ((unsigned short*)d)[j] = (unsigned short)(o[j >> 1] >> ((j & 1) * 16));
+            }
+          } else {
+            if (whole) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4)
+                *reinterpret_cast<float4*>(d + j * 4) =
+                    make_float4(x[j] * post, x[j + 1] * post, x[j + 2] * post, x[j + 3] * post);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (f0 + c + j < M) ((float*)d)[j] = x[j] * post;
             }
           }
         }
@@ -721,7 +782,7 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   }
 }
 
-template <int BN, bool DUAL, bool FP8 = false, bool SWAP = false>
+template <int BN, bool DUAL, bool FP8 = false, int SWAP = 0>
 int launch_pair(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int pair_tiles,
                 cudaStream_t stream) {
   constexpr int kStageBytes = kPairChunks * (kATile * (DUAL ? 2 : 1) + (BN / 2) * kBlockK * 2);
@@ -869,13 +930,16 @@ static int pair_tmap(CUtensorMap* out, const void* base, int dtype, int rows, in
   return us_tmap_encode(out, base, dtype, 3, dims, strides, box, US_SWZ_128);
 }
 
-static bool pair_enabled() {
-  static const bool on = [] {
+// US_GEMM_PAIR: 0 = single-CTA persistent kernel, 2 = CTA pairs with the weight on the
+// 256-row side (staged epilogue), default 1 = CTA pairs with the operands swapped.
+static int pair_mode() {
+  static const int mode = [] {
     const char* e = getenv("US_GEMM_PAIR");
-    return !(e != nullptr && e[0] == '0');
+    return (e != nullptr && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
   }();
-  return on;
+  return mode;
 }
+static bool pair_enabled() { return pair_mode() != 0; }
 
 struct PeerSpec {
   const void* const* x_peers = nullptr;  // pull: activation base per rank
@@ -913,10 +977,8 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
                     (long long)((M + kBlockM - 1) / kBlockM) * ((x_rows + block_n - 1) / block_n) >
                         148;
   const uint32_t box_n = (uint32_t)(pair ? block_n / 2 : block_n);
-  // gated: operands swapped, value and gate rows side by side in one accumulator
-  const bool swap = pair && dual && (M % kBlockM) == 0 && out_dtype == 0 && bias == nullptr &&
-                    row_scale == nullptr && out_row_map == nullptr && ps.out_peers == nullptr &&
-                    out != nullptr;
+  // operands swapped: one activation row per epilogue thread
+  const bool swap = pair && pair_mode() == 1;
 
   CUtensorMap tmA;
   BMaps tmB;
@@ -1048,9 +1110,10 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
     return e && e[0] == '1';
   }();
   if (swap) {
-    const int x_tiles = (x_rows + kBlockM - 1) / kBlockM;
-    return launch_pair<256, false, false, true>(tmA, tmB, a, ((x_tiles + 1) / 2) * (M / kBlockM),
-                                                stream);
+    const int x_pairs = ((x_rows + kBlockM - 1) / kBlockM + 1) / 2;
+    if (dual)
+      return launch_pair<256, false, false, 1>(tmA, tmB, a, x_pairs * ((M + 127) / 128), stream);
+    return launch_pair<256, false, false, 2>(tmA, tmB, a, x_pairs * ((M + 255) / 256), stream);
   }
   if (pair) {
     const int pair_tiles = ((m_tiles + 1) / 2) * n_tiles;
@@ -1204,7 +1267,7 @@ US_API int us_gemm_fp8_rowscale(const void* Wq, const void* Xq, void* out, int w
   const bool pair = pair_enabled() && tiles > 148 && (K % 128) == 0 &&
                     (dual ? block_n == 128 : block_n == 256);
   int rc;
-  const bool swap = pair && dual && (M % kBlockM) == 0 && out_dtype == 0;
+  const bool swap = pair && pair_mode() == 1;
   if (swap) {
     rc = pair_tmap(&tmA, Xq, US_TMAP_U8, x_rows, K, ldx, kBlockM);
     if (rc) return rc;
@@ -1232,9 +1295,10 @@ US_API int us_gemm_fp8_rowscale(const void* Wq, const void* Xq, void* out, int w
   a.vec_store = (((ldo * esz) % 16) == 0 && ((uintptr_t)out % 16) == 0) ? 1 : 0;
   cudaStream_t stream = (cudaStream_t)stream_;
   if (swap) {
-    const int x_tiles = (x_rows + kBlockM - 1) / kBlockM;
-    return launch_pair<256, false, true, true>(tmA, tmB, a, ((x_tiles + 1) / 2) * (M / kBlockM),
-                                               stream);
+    const int x_pairs = ((x_rows + kBlockM - 1) / kBlockM + 1) / 2;
+    if (dual)
+      return launch_pair<256, false, true, 1>(tmA, tmB, a, x_pairs * ((M + 127) / 128), stream);
+    return launch_pair<256, false, true, 2>(tmA, tmB, a, x_pairs * ((M + 255) / 256), stream);
   }
   if (pair) {
     const int pair_tiles = ((m_tiles + 1) / 2) * n_tiles;
