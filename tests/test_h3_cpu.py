@@ -69,7 +69,10 @@ def _worker(rank, world, port, q, axis="ulysses"):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from uniserve_v1_b200.parallel.context import ParallelContext
-    ctx = ParallelContext.from_world(**{axis: world})
+    if axis == "hybrid":
+        ctx = ParallelContext.from_world(ulysses=2, gather=world // 2)
+    else:
+        ctx = ParallelContext.from_world(**{axis: world})
     v, a = _run(ctx)
     if rank == 0:
         q.put((v, a))
@@ -90,6 +93,24 @@ def test_sequence_parallel_2_matches_single_rank(axis):
     for p in procs:
         p.start()
     v2, a2 = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    torch.testing.assert_close(v2, v1, atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(a2, a1, atol=2e-4, rtol=2e-4)
+
+
+def test_hybrid_sequence_placement_4_matches_single_rank():
+    """Two gather places of two Ulysses members each: a place's rows meet on both members
+    for half of the heads, keys and values of that half are gathered across the places."""
+    v1, a1 = _run()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 4, port, q, "hybrid")) for r in range(4)]
+    for p in procs:
+        p.start()
+    v2, a2 = q.get(timeout=300)
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0

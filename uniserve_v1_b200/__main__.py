@@ -68,8 +68,12 @@ def serve(args) -> int:
         from .server.video_service import VideoService
         tiny = pkg.model and pkg.model.endswith(":tiny")
         cfg = H3Config.tiny() if tiny else H3Config()
-        seq = "gather" if "gather" in axes else "ulysses"
-        ctx = ParallelContext.from_world(**{seq: world}) if world > 1 else None
+        hybrid = axes.get("gather", 1) > 1 and axes.get("ulysses", 1) > 1
+        seq = "sequence" if hybrid else ("gather" if "gather" in axes else "ulysses")
+        if hybrid:
+            ctx = ParallelContext.from_world(ulysses=axes["ulysses"], gather=axes["gather"])
+        else:
+            ctx = ParallelContext.from_world(**{seq: world}) if world > 1 else None
         tr = H3Transformer(cfg, device, dtype, ctx).init_random(0)
         if world > 1 and device.type == "cuda" and seq == "ulysses":
             from .parallel.ulysses import FusedUlysses

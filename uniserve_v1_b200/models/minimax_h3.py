@@ -243,14 +243,22 @@ class H3Transformer:
                  ctx: Optional[ParallelContext] = None):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.ctx = ctx or ParallelContext.single()
-        # Rows are split along one sequence axis: "ulysses" (heads travel around attention)
-        # or "gather" (queries stay, K and V rows are all-gathered, every head is local).
+        # Rows are split over the sequence ranks: "ulysses" (heads travel around attention),
+        # "gather" (queries stay, K and V rows are all-gathered, every head is local) or
+        # both ("sequence": Ulysses inside each gather place - the place's rows meet on
+        # every member for its share of the heads, and K / V of that share are gathered
+        # across the places; family.rs:607-690, reference project path).
         uly, gat = self.ctx.axis("ulysses").size, self.ctx.axis("gather").size
-        assert uly == 1 or gat == 1, "one sequence axis at a time (no hybrid placement)"
-        self.seq_axis = "gather" if gat > 1 else "ulysses"
-        self.sp = self.ctx.axis(self.seq_axis).size
-        self.sp_rank = self.ctx.axis(self.seq_axis).rank
+        self.seq_axis = "sequence" if (uly > 1 and gat > 1) else ("gather" if gat > 1
+                                                                   else "ulysses")
+        if self.seq_axis == "sequence":
+            self.sp = uly * gat
+            self.sp_rank = self.ctx.axis("gather").rank * uly + self.ctx.axis("ulysses").rank
+        else:
+            self.sp = self.ctx.axis(self.seq_axis).size
+            self.sp_rank = self.ctx.axis(self.seq_axis).rank
         self.head_split = uly
+        self.gather_places = gat
         assert cfg.num_heads % self.head_split == 0, "heads must divide over the Ulysses group"
         self.heads_local = cfg.num_heads // self.head_split
         # Layer split: contiguous shares of the blocks along the "layer" axis; a stage
@@ -410,10 +418,16 @@ class H3Transformer:
         cfg = self.cfg
         if self.seq_axis == "gather" and self.sp > 1:
             return self._attention_gather(blk, n, layout)
-        hl, D, P = self.heads_local, cfg.head_dim, self.sp
+        hl, D, P = self.heads_local, cfg.head_dim, self.head_split
+        hybrid = self.seq_axis == "sequence"
         vsa = cfg.vsa_sparsity > 0
+        assert not (hybrid and vsa), "block-sparse attention runs on one sequence axis"
+        if hybrid:
+            P_, ro_ = P, n.shape[0]
+            coords = layout.coords[:, self.ctx.axis("gather").rank * P_ * ro_:
+                                   (self.ctx.axis("gather").rank + 1) * P_ * ro_].contiguous()
         W = (4 if vsa else 3) * hl * D
-        if P > 1 and self.ulysses is not None and n.is_cuda and not vsa:
+        if P > 1 and self.ulysses is not None and n.is_cuda and not vsa and not hybrid:
             return self.ulysses.attention(self, blk, n, layout)
         qkv = F.linear(n, blk.qkv)                               # [rows_own, P * W]
         if P > 1:
@@ -424,9 +438,26 @@ class H3Transformer:
             full = qkv
         rows = full.shape[0]
         q, k, v = full[:, :hl * D], full[:, hl * D:2 * hl * D], full[:, 2 * hl * D:]
-        F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, layout.coords, self.inv_freq, hl, hl, D,
-                         cfg.rope_freqs_per_axis, cfg.eps, table=layout.rope_table(self.inv_freq))
-        if vsa:
+        if hybrid:
+            # rows of this gather place, this member's heads; keys and values of the
+            # other places arrive by all-gather over the gather axis
+            F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, coords, self.inv_freq, hl, hl, D,
+                             cfg.rope_freqs_per_axis, cfg.eps)
+            k_all = self.ctx.all_gather_rows(k.contiguous(), "gather")
+            v_all = self.ctx.all_gather_rows(v.contiguous(), "gather")
+            dev = n.device
+            cu_q = torch.tensor([0, rows], dtype=torch.int32, device=dev)
+            cu_k = torch.tensor([0, layout.used], dtype=torch.int32, device=dev)
+            att = self._dense_attention(q.reshape(rows, hl, D), k_all.view(-1, hl, D),
+                                        v_all.view(-1, hl, D), cu_q, cu_k, rows,
+                                        layout.used).reshape(rows, hl * D)
+        else:
+            F.qk_norm_rope3_(q, k, blk.q_norm, blk.k_norm, layout.coords, self.inv_freq, hl, hl,
+                             D, cfg.rope_freqs_per_axis, cfg.eps,
+                             table=layout.rope_table(self.inv_freq))
+        if hybrid:
+            pass
+        elif vsa:
             from ..ops import vsa as V
             v3 = full[:, 2 * hl * D:3 * hl * D].view(rows, hl, D)
             g3 = full[:, 3 * hl * D:].view(rows, hl, D)
@@ -622,7 +653,11 @@ class Denoiser:
         def gather(x, width, total):
             buf = torch.zeros(ro, width, dtype=torch.float32, device=x.device)
             buf[:x.shape[0]] = x
-            allr = m.ctx.all_gather_rows(buf, m.seq_axis).view(m.sp, ro, width)
+            if m.seq_axis == "sequence":
+                allr = m.ctx.all_gather_rows(m.ctx.all_gather_rows(buf, "ulysses"), "gather")
+            else:
+                allr = m.ctx.all_gather_rows(buf, m.seq_axis)
+            allr = allr.view(m.sp, ro, width)
             return allr
 
         gv = gather(vel_v, m.cfg.patch_width, layout.n_video)

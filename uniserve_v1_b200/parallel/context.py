@@ -99,6 +99,20 @@ class ParallelContext:
                 if rank in members:
                     mine = Axis(g, members.index(rank), n, members)
             ctx.axes[name] = mine
+        # "sequence": every rank that holds a row interval of the same clip, ordered
+        # by interval (gather place major, Ulysses member minor).
+        if ulysses > 1 and gather > 1:
+            su, sg = strides["ulysses"], strides["gather"]
+            bases = sorted({r - ((r // su) % ulysses) * su - ((r // sg) % gather) * sg
+                            for r in range(world)})
+            for base in bases:
+                members = tuple(base + iu * su + ig * sg
+                                for ig in range(gather) for iu in range(ulysses))
+                g = dist.new_group(list(members))
+                if rank in members:
+                    ctx.axes["sequence"] = Axis(g, members.index(rank), len(members), members)
+        else:
+            ctx.axes["sequence"] = ctx.axes["gather"] if gather > 1 else ctx.axes["ulysses"]
         if expert_over_tensor:
             ctx.axes["expert"] = ctx.axes["tensor"]
             ctx.expert_parallel = True

@@ -194,7 +194,11 @@ def package_parallelism(pkg) -> dict:
             sp = tr["sequence_parallel"]
             if sp.get("kind") == "allgather":
                 axes["gather"] = int(sp.get("allgather_degree") or ranks)
-            elif sp.get("kind") in ("ulysses", "hybrid"):
+            elif sp.get("kind") == "hybrid":
+                axes["ulysses"] = int(sp.get("ulysses_degree") or 2)
+                axes["gather"] = int(sp.get("allgather_degree") or
+                                     max(1, ranks // axes["ulysses"]))
+            elif sp.get("kind") == "ulysses":
                 axes["ulysses"] = int(sp.get("ulysses_degree") or ranks)
         model = blocks.get("model") or blocks.get("causal_lm")
         if model and not axes:
