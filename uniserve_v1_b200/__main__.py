@@ -103,7 +103,8 @@ def serve(args) -> int:
             ctx = ParallelContext.from_world(tensor=world // pp, layer=pp,
                                              expert_over_tensor=world // pp > 1)
         if directory:
-            ld = CheckpointLoader(directory)
+            from .checkpoint.quantized import open_checkpoint
+            ld = open_checkpoint(directory, dtype)       # NVFP4 / FP8 exports expand on read
             cfg = Qwen3MoeConfig.from_hf(ld.config)
             model = Qwen3MoeModel(cfg, device, dtype, ctx).load_state(ld)
         else:

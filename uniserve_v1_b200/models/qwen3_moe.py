@@ -265,6 +265,38 @@ class Qwen3MoeModel:
             head = torch.cat([head, pad], 0)
         self.lm_head = head.contiguous()
 
+    def export_state(self) -> dict:
+        """Hugging Face tensor names -> tensors of an unsharded model (the inverse of
+        ``load_state``; per-expert names)."""
+        cfg, D = self.cfg, self.D
+        assert self.ctx.tp_size == 1 and self.layer_lo == 0 and self.layer_hi == cfg.num_hidden_layers
+        Hq, Hkv, I = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.moe_intermediate_size
+        out = {"model.embed_tokens.weight": self.embed, "model.norm.weight": self.final_norm,
+               "lm_head.weight": self.lm_head}
+        for i, lw in enumerate(self.layers):
+            p = f"model.layers.{i}."
+            out[p + "input_layernorm.weight"] = lw.input_norm
+            out[p + "post_attention_layernorm.weight"] = lw.post_norm
+            out[p + "self_attn.q_proj.weight"] = lw.qkv[:Hq * D]
+            out[p + "self_attn.k_proj.weight"] = lw.qkv[Hq * D:(Hq + Hkv) * D]
+            out[p + "self_attn.v_proj.weight"] = lw.qkv[(Hq + Hkv) * D:]
+            out[p + "self_attn.o_proj.weight"] = lw.o_proj
+            if lw.q_norm is not None:
+                out[p + "self_attn.q_norm.weight"] = lw.q_norm
+                out[p + "self_attn.k_norm.weight"] = lw.k_norm
+            if cfg.is_moe_layer(i):
+                out[p + "mlp.gate.weight"] = lw.router
+                for e in range(cfg.num_experts):
+                    out[p + f"mlp.experts.{e}.up_proj.weight"] = lw.w13[e, :I]
+                    out[p + f"mlp.experts.{e}.gate_proj.weight"] = lw.w13[e, I:]
+                    out[p + f"mlp.experts.{e}.down_proj.weight"] = lw.w2[e]
+            else:
+                J = lw.w13.shape[-2] // 2
+                out[p + "mlp.up_proj.weight"] = lw.w13[..., :J, :].reshape(J, -1)
+                out[p + "mlp.gate_proj.weight"] = lw.w13[..., J:, :].reshape(J, -1)
+                out[p + "mlp.down_proj.weight"] = lw.w2.reshape(lw.w2.shape[-2], lw.w2.shape[-1])
+        return {k: v.detach().contiguous() for k, v in out.items()}
+
     def load_state(self, loader) -> "Qwen3MoeModel":
         """Loads Hugging Face tensor names through ``loader.get(name)``."""
         cfg, dev, dt, D = self.cfg, self.device, self.dtype, self.D
