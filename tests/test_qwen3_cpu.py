@@ -150,6 +150,48 @@ def test_speculative_steps_reproduce_plain_decoding():
             assert steps <= 2 + 4 + 1          # prefill steps + ceil(11 / 4) verify steps
 
 
+def test_mtp_drafter_keeps_outputs_and_round_trips_its_weights():
+    """A multi-token-prediction head drafts from the target's hidden states: whatever it
+    proposes the output stays the target's greedy decoding; its weights load back from
+    their checkpoint names."""
+    import torch
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.models.qwen3_mtp import MtpDrafter, MtpHead
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    head = MtpHead(model).init_random(seed=7)
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (9, 21)]
+    mk = lambda: LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128,
+                           use_graphs=False)
+    ref = mk().generate(prompts, sp)
+    eng, drafter = mk(), MtpDrafter(head, k=2)
+    rids = [eng.add_request(p, sp) for p in prompts]
+    outs = {r: [] for r in rids}
+    while eng.has_work():
+        for o in eng.speculative_step(drafter):
+            outs[o.request_id].extend(o.new_token_ids)
+    assert [outs[r] for r in rids] == ref
+    assert eng.spec_stats["proposed"] >= 2 * 4          # it did draft, two tokens at a time
+    # the stream holds verified positions only, and finished requests are forgotten
+    drafter.forget(set())
+    assert drafter.state == {}
+
+    class Dict:
+        def __init__(self, d): self.d = d
+        def get(self, n): return self.d[n]
+        def has(self, n): return n in self.d
+    state = head.export_state()
+    assert "mtp.fc.weight" in state and "mtp.layers.0.mlp.experts.3.gate_proj.weight" in state
+    again = MtpHead(model).load_state(Dict(state))
+    h = torch.randn(model.cfg.hidden_size, generator=g)
+    a = head.step(h, 5, 12, [None, None])
+    b = again.step(h, 5, 12, [None, None])
+    torch.testing.assert_close(a[1], b[1], rtol=0, atol=0)
+
+
 def test_dense_qwen3_family():
     """The dense Qwen3 family (no experts): same decoder, gated MLP in every layer; the
     Hugging Face config of `Qwen3ForCausalLM` maps onto it."""

@@ -194,28 +194,41 @@ class LLMEngine:
                 self.runner.variant_for(rows) != "greedy":
             return self.step()
         drafts = []
+        stateful = getattr(drafter, "needs_hidden", False)
+        if stateful:
+            drafter.forget({r.request_id for r in rows})
         for r in rows:
             room = min(self.config.max_model_len - r.num_tokens - 1,
                        r.params.max_tokens - len(r.output_ids) - 1)
-            d = drafter.propose(r.all_ids)[:max(0, min(drafter.k, room))]
+            d = drafter.propose_for(r) if stateful else drafter.propose(r.all_ids)
+            d = d[:max(0, min(drafter.k, room))]
             pages = self.blocks.allocate(sch._pages_needed(r, r.num_tokens + len(d)))
             if pages is None:
                 d, pages = [], []
             r.pages.extend(pages)
             drafts.append(d)
-        if not any(drafts):
+        # a drafter that feeds on the target's hidden states gets its first ones from a
+        # verification of the last token alone
+        if not any(drafts) and not (stateful and
+                                    any(not drafter.ready(r.request_id) for r in rows)):
             return self.step()
         if getattr(self.blocks, "host_slots", 0):
             self.runner.apply_kv_moves(*self.blocks.take_moves())
         self.watchdog.begin("verify step")
         try:
-            targets = self.runner.verify(rows, drafts)
+            if stateful:
+                targets, hiddens = self.runner.verify(rows, drafts, want_hidden=True)
+            else:
+                targets, hiddens = self.runner.verify(rows, drafts), None
         finally:
             self.watchdog.end()
         outs = []
         self.spec_stats["steps"] += 1
         for r, d, t in zip(rows, drafts, targets):
             emit = accept(d, t)
+            if stateful:
+                i = rows.index(r)
+                drafter.observe(r.request_id, r.num_tokens - 1, hiddens[i][:len(emit)], emit)
             self.spec_stats["proposed"] += len(d)
             self.spec_stats["accepted"] += len(emit) - 1
             for tok in emit:

@@ -486,10 +486,12 @@ class CausalLmRunner:
         return host, info, sample_rows
 
     # ----------------------------------------------------------------- verify --
-    def verify(self, rows: list, drafts: list):
+    def verify(self, rows: list, drafts: list, want_hidden: bool = False):
         """Speculative verification: request ``rows[i]`` runs its last token followed by
         ``drafts[i]`` (positions num_tokens - 1 ...) in one causal chunk over its cached
-        context; returns the greedy token after every position, one list per request."""
+        context; returns the greedy token after every position, one list per request (and
+        with ``want_hidden`` the hidden rows of those positions, for drafters that feed on
+        the target's state)."""
         dev, ps = self.device, self.page_size
         ids, pos, slots, cu_q, cu_k, ctx = [], [], [], [0], [0], []
         max_q = max_k = 0
@@ -523,7 +525,10 @@ class CausalLmRunner:
         toks = F.argmax(self.model.logits(hidden))
         host = (self._to_host(toks) if dev.type == "cuda" else toks).tolist()
         self.d2h_bytes += T * 4
-        return [host[cu_q[i]:cu_q[i + 1]] for i in range(len(rows))]
+        out = [host[cu_q[i]:cu_q[i + 1]] for i in range(len(rows))]
+        if want_hidden:       # the target's states of the verified positions, per request
+            return out, [hidden[cu_q[i]:cu_q[i + 1]] for i in range(len(rows))]
+        return out
 
     # ---------------------------------------------------------------- execute --
     def execute(self, batch: Batch):

@@ -9,9 +9,10 @@ row counts), as in the reference; rejected positions leave stale KV entries
 behind ``num_computed`` that the next call overwrites.
 
 ``NgramDrafter`` needs no extra weights: it continues the most recent earlier
-occurrence of the context's last ``n`` tokens (prompt-lookup drafting).  A
-trained multi-token-prediction head would plug in through the same ``propose``
-call; its module is not part of this package.
+occurrence of the context's last ``n`` tokens (prompt-lookup drafting).  The
+multi-token-prediction head (``models/qwen3_mtp.py``) is a drafter with state
+(``needs_hidden``): the engine calls ``propose_for(request)`` and hands it the target's
+hidden states of the verified positions through ``observe``.
 
 Reference behaviour: docs/configuration.md:418-431,
 crates/engine/src/runner/causal_lm/speculation.rs (reference project paths).
