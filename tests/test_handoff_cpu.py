@@ -1,0 +1,72 @@
+"""Prefill / decode disaggregation on CPU engines: a request that moves after its first
+token produces what one engine produces."""
+import torch
+
+from uniserve_v1_b200.engine.engine import LLMEngine
+from uniserve_v1_b200.engine.handoff import (Handoff, PrefillDecodePair, export_request,
+                                             import_request, reshard_heads)
+from uniserve_v1_b200.engine.types import SamplingParams
+from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+
+
+def _engines(n):
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    mk = lambda: LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=160,
+                           use_graphs=False)
+    return [mk() for _ in range(n)]
+
+
+def test_prefill_decode_pair_matches_one_engine():
+    single, pre, dec = _engines(3)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (7, 33, 16)]
+    params = [SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True),
+              SamplingParams(temperature=0.8, top_p=0.9, seed=11, max_tokens=12, ignore_eos=True),
+              SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)]
+    ref = single.generate(prompts, params)
+    for through_bytes in (False, True):
+        pre, dec = _engines(2)
+        pair = PrefillDecodePair(pre, dec, through_bytes=through_bytes)
+        rids = [pair.add_request(p, sp, request_id=f"req-{i + 1}")
+                for i, (p, sp) in enumerate(zip(prompts, params))]
+        outs = {r: [] for r in rids}
+        while pair.has_work():
+            for o in pair.step():
+                outs[o.request_id].extend(o.new_token_ids)
+        assert [outs[r] for r in rids] == ref
+        assert pair.moved == 2 and pair.moved_bytes > 0     # the one-token request ends in place
+        assert pre.blocks.num_free == dec.blocks.num_free == _engines(1)[0].blocks.num_free
+        assert not pre.scheduler.running and not dec.scheduler.running   # nothing leaks
+        assert dec.scheduler.stats["prefill_tokens"] <= 2   # the decode side computed no prompt
+
+
+def test_handoff_frames_and_head_ranges():
+    pre, dec = _engines(2)
+    rid = pre.add_request(list(range(5, 45)), SamplingParams(temperature=0.0, max_tokens=4,
+                                                            ignore_eos=True))
+    while not pre.scheduler.requests[rid].output_ids:
+        pre.step()
+    h = export_request(pre, rid, release=False)
+    assert h.num_computed == 40 and h.kv[0][0].shape[:2] == (3, 16)
+    back = Handoff.from_bytes(h.to_bytes())
+    assert back.prompt_ids == h.prompt_ids and torch.equal(back.kv[1][1], h.kv[1][1])
+    # two exporting ranks with one head each feed an importer that owns both
+    k = h.kv[0][0]
+    whole = reshard_heads([(1, k[:, :, 1:2]), (0, k[:, :, 0:1])], 0, 2)
+    assert torch.equal(whole, k)
+    assert torch.equal(reshard_heads([(0, k)], 1, 1), k[:, :, 1:2])
+    halves = []
+    for lo in (0, 1):
+        part = Handoff(**{**h.__dict__, "head_lo": lo,
+                          "kv": [(a[:, :, lo:lo + 1], b[:, :, lo:lo + 1]) for a, b in h.kv]})
+        halves.append(part)
+    import_request(dec, halves)
+    out = []
+    while dec.has_work():
+        for o in dec.step():
+            out.extend(o.new_token_ids)
+    ref = []
+    while pre.has_work():
+        for o in pre.step():
+            ref.extend(o.new_token_ids)
+    assert out == ref and len(out) == 3
