@@ -66,3 +66,49 @@ def test_qwen3_dense_matches_transformers(tmp_path):
     hf = Qwen3ForCausalLM(cfg).eval()
     _save(hf, cfg, tmp_path / "dense")
     _compare(tmp_path / "dense", hf, [5, 9, 2, 44, 300, 12])
+
+
+def test_qwen3_5_moe_hybrid_decoder_matches_transformers(tmp_path):
+    """Gated-delta-net layers, gated attention with partial rotary embedding, experts plus
+    a gated shared expert: logits of a tiny random `Qwen3_5MoeForCausalLM` checkpoint, for the
+    whole prompt at once and for the same prompt run in chunks and then token by token."""
+    import json
+    import pytest
+    import torch
+    tr = pytest.importorskip("transformers")
+    from transformers.models.qwen3_5_moe.configuration_qwen3_5_moe import Qwen3_5MoeTextConfig
+    from transformers.models.qwen3_5_moe.modeling_qwen3_5_moe import Qwen3_5MoeForCausalLM
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, save_file
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35Config, Qwen35MoeModel
+    hf_cfg = Qwen3_5MoeTextConfig(
+        vocab_size=300, hidden_size=64, num_hidden_layers=4, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=32, linear_num_key_heads=2, linear_num_value_heads=4,
+        linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4,
+        num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
+        shared_expert_intermediate_size=48, max_position_embeddings=256,
+        layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"])
+    torch.manual_seed(0)
+    hf = Qwen3_5MoeForCausalLM(hf_cfg).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():                   # norms and gates away from their init
+            if p.dim() == 1 or "experts" in n:
+                p.copy_(torch.randn_like(p) * 0.3)
+    state = {k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()}
+    save_file(state, tmp_path / "model.safetensors")
+    (tmp_path / "config.json").write_text(json.dumps(hf_cfg.to_dict()))
+    ld = CheckpointLoader(tmp_path)
+    cfg = Qwen35Config.from_hf(ld.config)
+    assert cfg.layer_types[3] == "full_attention" and cfg.partial_rotary_factor == 0.25
+    model = Qwen35MoeModel(cfg, "cpu", torch.float32).load_state(ld)
+    ids = torch.randint(0, 300, (19,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids[None]).logits[0]
+    got = model.forward(ids, model.new_state())
+    torch.testing.assert_close(got, want, atol=2e-4, rtol=2e-3)
+    st = model.new_state()
+    parts = [model.forward(ids[:7], st, 0), model.forward(ids[7:15], st, 7)]
+    parts += [model.forward(ids[i:i + 1], st, i) for i in range(15, 19)]
+    torch.testing.assert_close(torch.cat(parts), want, atol=2e-4, rtol=2e-3)
+    with torch.no_grad():
+        ref_gen = hf.generate(ids[None], max_new_tokens=6, do_sample=False)[0, 19:].tolist()
+    assert model.generate(ids.tolist(), 6, chunk=8)[:len(ref_gen)] == ref_gen

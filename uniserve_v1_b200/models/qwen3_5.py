@@ -1,0 +1,226 @@
+"""Qwen3.5-MoE text decoder: hybrid layers (three gated-delta-net layers for every
+full-attention layer), attention with an output gate and partial rotary embedding,
+experts plus a gated shared expert, zero-centred RMSNorm weights.
+
+The decoder keeps a *dense* per-sequence state - key / value rows for the attention
+layers, (convolution window, delta-rule matrix) for the linear layers - so a prompt
+can be run in chunks and decoding is one more chunk of one token.  Projections, MLPs
+and expert GEMMs go through the package's operators (tensor-core kernels on a GPU);
+the recurrences and the dense attention are the FP32 formulas of
+``ops/gated_delta.py`` / PyTorch.  Serving this family through the paged engine
+(pages for its attention layers, state slots for its linear layers) is not wired.
+
+Hugging Face names (``Qwen3_5MoeForCausalLM``): ``linear_attn.{in_proj_qkv,in_proj_z,
+in_proj_b,in_proj_a,conv1d,out_proj,norm}``, ``dt_bias``, ``A_log``, ``self_attn.q_proj``
+(queries and gates interleaved per head), ``mlp.experts.gate_up_proj`` (stacked),
+``mlp.shared_expert*``.
+
+Reference behaviour: crates/models/src/qwen3/decoder.rs:82-120,
+crates/nn/src/modules/gated_delta_net.rs, crates/models/src/qwen3/config.rs
+(reference project paths).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from ..ops import functional as F
+from ..ops import gated_delta as GD
+from ..ops import reference as R
+
+
+@dataclass
+class Qwen35Config:
+    vocab_size: int = 248320
+    hidden_size: int = 2048
+    num_hidden_layers: int = 40
+    layer_types: list = field(default_factory=list)
+    num_attention_heads: int = 16
+    num_key_value_heads: int = 2
+    head_dim: int = 256
+    partial_rotary_factor: float = 0.25
+    rope_theta: float = 1e7
+    rms_norm_eps: float = 1e-6
+    linear_num_key_heads: int = 16
+    linear_num_value_heads: int = 32
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_conv_kernel_dim: int = 4
+    num_experts: int = 256
+    num_experts_per_tok: int = 8
+    moe_intermediate_size: int = 512
+    shared_expert_intermediate_size: int = 512
+    eos_token_id: int = 0
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "Qwen35Config":
+        d = d.get("text_config", d)
+        rp = d.get("rope_parameters") or {}
+        keys = {f for f in cls.__dataclass_fields__}
+        kw = {k: v for k, v in d.items() if k in keys and v is not None}
+        kw["rope_theta"] = float(rp.get("rope_theta", d.get("rope_theta", 1e7)))
+        kw["partial_rotary_factor"] = float(rp.get("partial_rotary_factor",
+                                                   d.get("partial_rotary_factor", 0.25)))
+        cfg = cls(**kw)
+        if not cfg.layer_types:
+            every = int(d.get("full_attention_interval", 4))
+            cfg.layer_types = ["full_attention" if (i + 1) % every == 0 else "linear_attention"
+                               for i in range(cfg.num_hidden_layers)]
+        if isinstance(cfg.eos_token_id, (list, tuple)):
+            cfg.eos_token_id = int(cfg.eos_token_id[0])
+        return cfg
+
+
+@dataclass
+class LayerState:
+    k: Optional[torch.Tensor] = None        # attention: [n, Hkv, D]
+    v: Optional[torch.Tensor] = None
+    conv: Optional[torch.Tensor] = None     # linear: [K - 1, conv channels]
+    rule: Optional[torch.Tensor] = None     # linear: [Hv, Dk, Dv] FP32
+
+
+class Qwen35MoeModel:
+    def __init__(self, cfg: Qwen35Config, device="cpu", dtype=torch.bfloat16):
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.rot = int(cfg.head_dim * cfg.partial_rotary_factor)
+        self.inv_freq = R.rope_inv_freq(self.rot, cfg.rope_theta, self.device)
+        self.w: dict = {}
+
+    # ------------------------------------------------------------- weights --
+    def load_state(self, loader) -> "Qwen35MoeModel":
+        cfg = self.cfg
+        names = set(loader.names())
+        prefix = "model.language_model." if any(n.startswith("model.language_model.")
+                                                for n in names) else "model."
+
+        def get(n, dtype=None):
+            return loader.get(n).to(device=self.device, dtype=dtype or self.dtype)
+        w = self.w
+        w["embed"] = get(prefix + "embed_tokens.weight")
+        w["norm"] = get(prefix + "norm.weight", torch.float32) + 1.0
+        w["lm_head"] = get("lm_head.weight") if "lm_head.weight" in names else w["embed"]
+        I = cfg.moe_intermediate_size
+        for i, kind in enumerate(cfg.layer_types):
+            p = f"{prefix}layers.{i}."
+            L = {"kind": kind,
+                 "in_norm": get(p + "input_layernorm.weight", torch.float32) + 1.0,
+                 "post_norm": get(p + "post_attention_layernorm.weight", torch.float32) + 1.0}
+            if kind == "full_attention":
+                a = p + "self_attn."
+                L["q"], L["k"], L["v"], L["o"] = (get(a + f"{n}_proj.weight") for n in "qkvo")
+                L["q_norm"] = get(a + "q_norm.weight", torch.float32) + 1.0
+                L["k_norm"] = get(a + "k_norm.weight", torch.float32) + 1.0
+            else:
+                a = p + "linear_attn."
+                L["qkvz"] = torch.cat([get(a + "in_proj_qkv.weight"), get(a + "in_proj_z.weight"),
+                                       get(a + "in_proj_b.weight"), get(a + "in_proj_a.weight")], 0)
+                L["conv"] = get(a + "conv1d.weight", torch.float32).squeeze(1)     # [C, K]
+                L["dt_bias"] = get(a + "dt_bias", torch.float32)
+                L["A"] = -get(a + "A_log", torch.float32).exp()
+                L["gnorm"] = get(a + "norm.weight")
+                L["out"] = get(a + "out_proj.weight")
+            m = p + "mlp."
+            L["router"] = get(m + "gate.weight")
+            gu = get(m + "experts.gate_up_proj")                 # [E, 2I, H]: gate rows, up rows
+            L["w13"] = torch.cat([gu[:, I:], gu[:, :I]], 1).contiguous()
+            L["w2"] = get(m + "experts.down_proj").contiguous()
+            L["s13"] = torch.cat([get(m + "shared_expert.up_proj.weight"),
+                                  get(m + "shared_expert.gate_proj.weight")], 0)
+            L["s2"] = get(m + "shared_expert.down_proj.weight")
+            L["sgate"] = get(m + "shared_expert_gate.weight")
+            w[i] = L
+        return self
+
+    # ------------------------------------------------------------- forward --
+    def new_state(self) -> list:
+        return [LayerState() for _ in self.cfg.layer_types]
+
+    def _attention(self, L, n, st: LayerState, pos0: int):
+        c, D = self.cfg, self.cfg.head_dim
+        T = n.shape[0]
+        Hq, Hkv = c.num_attention_heads, c.num_key_value_heads
+        qg = F.linear(n, L["q"]).view(T, Hq, 2 * D)
+        q, gate = qg[..., :D], qg[..., D:].reshape(T, Hq * D)
+        k = F.linear(n, L["k"]).view(T, Hkv, D)
+        v = F.linear(n, L["v"]).view(T, Hkv, D)
+        pos = torch.arange(pos0, pos0 + T, device=n.device)
+        q, k = R.qk_norm_rope(q.contiguous(), k, L["q_norm"], L["k_norm"], pos, self.inv_freq,
+                              self.rot, False, c.rms_norm_eps)
+        st.k = k if st.k is None else torch.cat([st.k, k], 0)
+        st.v = v if st.v is None else torch.cat([st.v, v], 0)
+        rep = Hq // Hkv
+        K = st.k.float().repeat_interleave(rep, 1)
+        V = st.v.float().repeat_interleave(rep, 1)
+        s = torch.einsum("thd,nhd->htn", q.float(), K) / math.sqrt(D)
+        n_ctx = K.shape[0]
+        mask = torch.arange(n_ctx, device=n.device)[None, :] > (pos[:, None])
+        s = s.masked_fill(mask[None], float("-inf"))
+        att = torch.einsum("htn,nhd->thd", s.softmax(-1), V).reshape(T, Hq * D)
+        att = (att * torch.sigmoid(gate.float())).to(n.dtype)
+        return F.linear(att, L["o"])
+
+    def _linear_attention(self, L, n, st: LayerState):
+        c = self.cfg
+        T = n.shape[0]
+        Hk, Hv, Dk, Dv = (c.linear_num_key_heads, c.linear_num_value_heads,
+                          c.linear_key_head_dim, c.linear_value_head_dim)
+        kd, vd = Hk * Dk, Hv * Dv
+        proj = F.linear(n, L["qkvz"])
+        mixed, z = proj[:, :2 * kd + vd], proj[:, 2 * kd + vd:2 * kd + 2 * vd]
+        b, a = proj[:, 2 * kd + 2 * vd:2 * kd + 2 * vd + Hv], proj[:, 2 * kd + 2 * vd + Hv:]
+        mixed, st.conv = GD.causal_conv1d(mixed.contiguous(), L["conv"], st.conv)
+        q = mixed[:, :kd].reshape(T, Hk, Dk)
+        k = mixed[:, kd:2 * kd].reshape(T, Hk, Dk)
+        v = mixed[:, 2 * kd:].reshape(T, Hv, Dv)
+        if Hv // Hk > 1:
+            q, k = q.repeat_interleave(Hv // Hk, 1), k.repeat_interleave(Hv // Hk, 1)
+        beta = torch.sigmoid(b.float())
+        g = L["A"] * torch.nn.functional.softplus(a.float() + L["dt_bias"])
+        o, st.rule = GD.gated_delta_rule(q, k, v, g, beta, st.rule)
+        o = GD.rmsnorm_gated(o.to(n.dtype), L["gnorm"], z.reshape(T, Hv, Dv), c.rms_norm_eps)
+        return F.linear(o.reshape(T, vd), L["out"])
+
+    def _mlp(self, L, n):
+        c = self.cfg
+        logits = F.linear(n, L["router"], out_dtype=torch.float32)
+        ids, wts = F.topk_softmax(logits, c.num_experts_per_tok, True)
+        y = F.moe_experts(n, ids, wts, L["w13"], L["w2"])
+        shared = F.linear(F.linear_gated(n, L["s13"]), L["s2"])
+        sg = torch.sigmoid(F.linear(n, L["sgate"], out_dtype=torch.float32))
+        return y + (shared.float() * sg).to(n.dtype)
+
+    def forward(self, ids: torch.Tensor, state: list, pos0: int = 0) -> torch.Tensor:
+        """Runs ``ids`` [T] at positions pos0 .. on top of ``state``; returns FP32 logits
+        [T, vocab]."""
+        c, w = self.cfg, self.w
+        x = w["embed"][ids.to(self.device).long()]
+        for i in range(c.num_hidden_layers):
+            L, st = w[i], state[i]
+            n = R.rmsnorm(x, L["in_norm"], c.rms_norm_eps)
+            mix = self._attention(L, n, st, pos0) if L["kind"] == "full_attention" \
+                else self._linear_attention(L, n, st)
+            x = x + mix
+            n = R.rmsnorm(x, L["post_norm"], c.rms_norm_eps)
+            x = x + self._mlp(L, n)
+        return F.linear(R.rmsnorm(x, w["norm"], c.rms_norm_eps), w["lm_head"],
+                        out_dtype=torch.float32)
+
+    def generate(self, prompt_ids: list, max_tokens: int, chunk: int = 512) -> list:
+        """Greedy decoding with chunked prefill."""
+        state, out, pos = self.new_state(), [], 0
+        ids = torch.tensor(prompt_ids, device=self.device)
+        logits = None
+        for lo in range(0, len(prompt_ids), chunk):
+            logits = self.forward(ids[lo:lo + chunk], state, pos)
+            pos += min(chunk, len(prompt_ids) - lo)
+        for _ in range(max_tokens):
+            tok = int(logits[-1].argmax())
+            out.append(tok)
+            if tok == self.cfg.eos_token_id:
+                break
+            logits = self.forward(torch.tensor([tok], device=self.device), state, pos)
+            pos += 1
+        return out
