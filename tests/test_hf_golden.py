@@ -112,3 +112,48 @@ def test_qwen3_5_moe_hybrid_decoder_matches_transformers(tmp_path):
     with torch.no_grad():
         ref_gen = hf.generate(ids[None], max_new_tokens=6, do_sample=False)[0, 19:].tolist()
     assert model.generate(ids.tolist(), 6, chunk=8)[:len(ref_gen)] == ref_gen
+
+
+def test_qwen3_vl_vision_tower_matches_transformers(tmp_path):
+    """Patch embedding, interpolated position grid, 2-D rotary attention per frame, merger
+    and deep-stack mergers of a tiny random `Qwen3VLVisionModel`, for an image and a
+    two-frame video of different sizes in one call; and the splice into text rows."""
+    import pytest
+    import torch
+    pytest.importorskip("transformers")
+    from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLVisionConfig
+    from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLVisionModel
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, save_file
+    from uniserve_v1_b200.models.qwen3_vl_vision import Qwen3VLVisionTower, VisionConfig, splice
+    hf_cfg = Qwen3VLVisionConfig(depth=3, hidden_size=64, intermediate_size=96, num_heads=2,
+                                 in_channels=3, patch_size=4, temporal_patch_size=2,
+                                 spatial_merge_size=2, out_hidden_size=48,
+                                 num_position_embeddings=36, deepstack_visual_indexes=[0, 2])
+    torch.manual_seed(0)
+    hf = Qwen3VLVisionModel(hf_cfg).float().eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.copy_(torch.randn_like(p) * 0.2 + (1.0 if p.abs().mean() > 0.5 else 0.0))
+    save_file({"model.visual." + k: v.detach().clone().contiguous()
+               for k, v in hf.state_dict().items()}, tmp_path / "model.safetensors")
+    (tmp_path / "config.json").write_text("{}")
+    cfg = VisionConfig.from_hf(hf_cfg.to_dict())
+    tower = Qwen3VLVisionTower(cfg, "cpu", torch.float32).load_state(CheckpointLoader(tmp_path))
+    grids = [(1, 4, 6), (2, 6, 4)]
+    n = sum(t * h * w for t, h, w in grids)
+    pixels = torch.randn(n, 3 * 2 * 4 * 4, generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(pixels, grid_thw=torch.tensor(grids))
+    rows, deep = tower.forward(pixels, grids)
+    torch.testing.assert_close(rows, ref.pooler_output, atol=2e-4, rtol=2e-3)
+    assert len(deep) == 2
+    for a, b in zip(deep, ref.deepstack_features):
+        torch.testing.assert_close(a, b, atol=2e-4, rtol=2e-3)
+    assert rows.shape == (n // 4, 48)
+    ids = torch.tensor([1, 9, 9, 2] + [9] * (n // 4 - 2) + [3])
+    emb = torch.zeros(ids.numel(), 48)
+    out = splice(emb, ids, 9, rows)
+    assert torch.equal(out[1], rows[0]) and torch.equal(out[-2], rows[-1]) and out[0].abs().sum() == 0
+    with pytest.raises(ValueError):
+        splice(emb, ids[:-3], 9, rows)
