@@ -157,3 +157,55 @@ def test_qwen3_vl_vision_tower_matches_transformers(tmp_path):
     assert torch.equal(out[1], rows[0]) and torch.equal(out[-2], rows[-1]) and out[0].abs().sum() == 0
     with pytest.raises(ValueError):
         splice(emb, ids[:-3], 9, rows)
+
+
+def test_dense_state_engine_serves_the_hybrid_decoder(tmp_path):
+    """Continuous batching over per-sequence states: requests that arrive at different
+    steps and read their prompts in chunks produce what each produces alone."""
+    import json
+    import pytest
+    import torch
+    pytest.importorskip("transformers")
+    from transformers.models.qwen3_5_moe.configuration_qwen3_5_moe import Qwen3_5MoeTextConfig
+    from transformers.models.qwen3_5_moe.modeling_qwen3_5_moe import Qwen3_5MoeForCausalLM
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, save_file
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35Config, Qwen35MoeModel
+    hf_cfg = Qwen3_5MoeTextConfig(
+        vocab_size=200, hidden_size=32, num_hidden_layers=2, num_attention_heads=2,
+        num_key_value_heads=1, head_dim=16, linear_num_key_heads=1, linear_num_value_heads=2,
+        linear_key_head_dim=8, linear_value_head_dim=8, num_experts=4, num_experts_per_tok=2,
+        moe_intermediate_size=16, shared_expert_intermediate_size=16, max_position_embeddings=128,
+        layer_types=["linear_attention", "full_attention"], eos_token_id=199)
+    torch.manual_seed(3)
+    hf = Qwen3_5MoeForCausalLM(hf_cfg).float().eval()
+    save_file({k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()},
+              tmp_path / "model.safetensors")
+    (tmp_path / "config.json").write_text(json.dumps(hf_cfg.to_dict()))
+    ld = CheckpointLoader(tmp_path)
+    model = Qwen35MoeModel(Qwen35Config.from_hf(ld.config), "cpu", torch.float32).load_state(ld)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 199, (n,), generator=g).tolist() for n in (5, 23, 11)]
+    params = [SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True),
+              SamplingParams(temperature=0.9, top_p=0.8, seed=7, max_tokens=8, ignore_eos=True),
+              SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)]
+    alone = [DenseStateEngine(model).generate([p], sp)[0] for p, sp in zip(prompts, params)]
+    assert alone[0] == model.generate(prompts[0], 6)
+    eng = DenseStateEngine(model, max_num_seqs=2, prefill_chunk=8)
+    rids = [eng.add_request(prompts[0], params[0])]
+    outs = {rids[0]: []}
+    step = 0
+    while eng.has_work() or step < 3:
+        if step == 1:
+            rids.append(eng.add_request(prompts[1], params[1]))
+            rids.append(eng.add_request(prompts[2], params[2]))    # waits for a free state
+            outs.update({rids[1]: [], rids[2]: []})
+        for o in eng.step():
+            outs[o.request_id].extend(o.new_token_ids)
+        step += 1
+    assert [outs[r] for r in rids] == alone
+    assert eng.stats()["finished"] == 3 and not eng.states
+    rid = eng.add_request(prompts[1], params[1])
+    eng.step()
+    assert eng.abort(rid) and not eng.has_work()

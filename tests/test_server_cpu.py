@@ -149,3 +149,25 @@ def test_video_routes_produce_mp4():
         assert c.get(f"/v1/videos/{job['id']}/content").content[4:8] == b"ftyp"
         assert c.delete(f"/v1/videos/{job['id']}").json()["deleted"] is True
         assert c.get(f"/v1/videos/{job['id']}").status_code == 404
+
+
+def test_chat_on_the_dense_state_engine():
+    """The hybrid (gated delta net) family behind the same chat routes."""
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel
+    model = Qwen35MoeModel(Qwen35MoeModel.tiny_config(), "cpu", torch.float32).init_random(seed=0)
+    eng = DenseStateEngine(model, max_num_seqs=4, max_model_len=256)
+    pkg = Package.parse('model = "random:tiny"\nserved_model_name = "hybrid"\n')
+    app = create_app(package=pkg, engine=eng, tokenizer=ByteTokenizer(1024, 1023),
+                     served_model_name="hybrid")
+    with TestClient(app) as c:
+        body = {"model": "hybrid", "messages": [{"role": "user", "content": "hello"}],
+                "max_tokens": 6, "temperature": 0, "ignore_eos": True}
+        a = c.post("/v1/chat/completions", json=body).json()
+        b = c.post("/v1/chat/completions", json=body).json()
+        assert a["choices"][0]["message"] == b["choices"][0]["message"]
+        assert a["usage"]["completion_tokens"] == 6
+        body.update(stream=True, temperature=0.8, seed=3)
+        with c.stream("POST", "/v1/chat/completions", json=body) as r:
+            lines = [l for l in r.iter_lines() if l.startswith("data: ")]
+        assert lines[-1] == "data: [DONE]" and len(lines) >= 4

@@ -93,6 +93,24 @@ def serve(args) -> int:
         if bus is not None:
             shutdown = MR.ReplicatedVideoService(service, bus).shutdown
         app = create_app(package=pkg, served_model_name=name, video_service=service)
+    elif family == "qwen3_5_moe":
+        # hybrid decoder (gated delta net + gated attention): dense per-sequence state
+        from .checkpoint.quantized import open_checkpoint
+        from .engine.dense_state import DenseStateEngine
+        from .models.qwen3_5 import Qwen35Config, Qwen35MoeModel
+        from .server.tokenizer import load_tokenizer
+        assert world == 1, "the hybrid family is served on one GPU"
+        ld = open_checkpoint(directory, dtype)
+        cfg = Qwen35Config.from_hf(ld.config)
+        model = Qwen35MoeModel(cfg, device, dtype).load_state(ld)
+
+        def make_engine():
+            return DenseStateEngine(model, max_num_seqs=min(pkg.max_running_requests,
+                                                            pkg.scheduler_config.max_batch),
+                                    max_model_len=pkg.max_model_len or 8192)
+        tok = load_tokenizer(directory, cfg.vocab_size, cfg.eos_token_id)
+        app = create_app(package=pkg, engine=make_engine(), tokenizer=tok,
+                         served_model_name=name, engine_factory=make_engine)
     else:
         from .engine.engine import LLMEngine
         from .models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel

@@ -1,0 +1,169 @@
+"""An engine for decoders that keep a dense per-sequence state (the hybrid
+Qwen3.5 family: key / value rows for its attention layers, convolution window and
+delta-rule matrix for its linear layers) instead of KV pages.
+
+Same calls as ``LLMEngine`` - ``add_request`` / ``step`` / ``abort`` / ``has_work`` /
+``stats`` - so the HTTP service, the chat layer and the tools run on it unchanged.
+One step admits waiting requests up to ``max_num_seqs``, runs the next prompt chunk of
+every request still reading its prompt, and one decode position for every other one.
+Sampling follows the request's parameters with draws addressed by (seed, position), so
+a request produces the same tokens whatever else is running.  Sequences are advanced
+one after another (their states are separate tensors); batching the linear layers
+across sequences is left open.
+
+Reference behaviour: crates/engine/src/runner/causal_lm (state slots and
+``state_interval`` checkpoints of recurrent layers) - reference project path.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..ops import functional as F
+from .types import FinishReason, Request, RequestState, SamplingParams, StepOutput
+
+
+@dataclass
+class DenseStateConfig:
+    max_num_seqs: int = 8
+    max_model_len: int = 4096
+    prefill_chunk: int = 512
+
+
+class _NoPages:
+    enable_prefix_cache = False
+
+    def flush(self) -> int:
+        return 0
+
+
+class DenseStateEngine:
+    def __init__(self, model, max_num_seqs: int = 8, max_model_len: int = 4096,
+                 prefill_chunk: int = 512):
+        self.model = model
+        self.config = DenseStateConfig(max_num_seqs, max_model_len, prefill_chunk)
+        self.blocks = _NoPages()
+        self.failed: Optional[str] = None
+        self.waiting: list = []
+        self.running: list = []
+        self.requests: dict = {}
+        self.states: dict = {}
+        self._ids = itertools.count(1)
+        self._stats = {"prefill_tokens": 0, "decode_tokens": 0, "finished": 0, "steps": 0,
+                       "preemptions": 0}
+
+    # ------------------------------------------------------------- requests --
+    def add_request(self, prompt_ids, params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, priority: int = 0,
+                    cache_salt: Optional[str] = None, output_ids: Optional[list] = None) -> str:
+        rid = request_id or f"req-{next(self._ids)}"
+        V = self.model.cfg.vocab_size
+        if not prompt_ids:
+            raise ValueError("empty prompt")
+        if any((t < 0 or t >= V) for t in prompt_ids):
+            raise ValueError("input_error: token id outside the vocabulary")
+        if len(prompt_ids) + 1 > self.config.max_model_len:
+            raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds max_model_len "
+                             f"{self.config.max_model_len}")
+        req = Request(rid, list(prompt_ids), params or SamplingParams(), priority=priority,
+                      cache_salt=cache_salt)
+        if output_ids:                      # a resumed request recomputes its state
+            req.output_ids = list(output_ids)
+        self.requests[rid] = req
+        self.waiting.append(req)
+        return rid
+
+    def abort(self, request_id: str) -> bool:
+        req = self.requests.get(request_id)
+        if req is None or req.finished:
+            return False
+        self._finish(req, FinishReason.ABORT)
+        return True
+
+    def has_work(self) -> bool:
+        return bool(self.waiting) or bool(self.running)
+
+    def _finish(self, req: Request, reason: FinishReason) -> None:
+        req.state, req.finish_reason, req.finish_time = RequestState.FINISHED, reason, \
+            time.monotonic()
+        self.states.pop(req.request_id, None)
+        for q in (self.waiting, self.running):
+            if req in q:
+                q.remove(req)
+        self._stats["finished"] += 1
+
+    # ----------------------------------------------------------------- step --
+    def _sample(self, req: Request, logits_row: torch.Tensor) -> int:
+        p = req.params
+        if p.temperature <= 0.0:
+            return int(logits_row.argmax())
+        dev = logits_row.device
+        logits = (logits_row.float() / p.temperature)[None].contiguous()
+        tok = F.sample_from_logits(
+            logits, torch.tensor([p.top_k if p.top_k and p.top_k > 0 else 0], dtype=torch.int32,
+                                 device=dev),
+            torch.tensor([p.top_p], dtype=torch.float32, device=dev),
+            torch.tensor([getattr(p, "min_p", 0.0) or 0.0], dtype=torch.float32, device=dev),
+            torch.tensor([req.seed & 0x7FFFFFFFFFFFFFFF], dtype=torch.int64, device=dev),
+            torch.tensor([req.num_tokens], dtype=torch.int64, device=dev))
+        return int(tok[0])
+
+    def _stop(self, req: Request, tok: int) -> Optional[FinishReason]:
+        p = req.params
+        if not p.ignore_eos and tok == getattr(self.model.cfg, "eos_token_id", -1):
+            return FinishReason.STOP
+        if tok in (getattr(p, "stop_token_ids", None) or ()):
+            return FinishReason.STOP
+        if len(req.output_ids) >= p.max_tokens or req.num_tokens >= self.config.max_model_len:
+            return FinishReason.LENGTH
+        return None
+
+    def step(self) -> list:
+        while self.waiting and len(self.running) < self.config.max_num_seqs:
+            req = self.waiting.pop(0)
+            req.state = RequestState.RUNNING
+            self.states[req.request_id] = self.model.new_state()
+            self.running.append(req)
+        outs = []
+        self._stats["steps"] += 1
+        dev = self.model.device
+        for req in list(self.running):
+            st = self.states[req.request_id]
+            ids = req.all_ids
+            todo = len(ids) - req.num_computed
+            n = min(todo, self.config.prefill_chunk)
+            chunk = torch.tensor(ids[req.num_computed:req.num_computed + n], device=dev)
+            logits = self.model.forward(chunk, st, req.num_computed)
+            req.num_computed += n
+            self._stats["decode_tokens" if (n == 1 and req.output_ids) else "prefill_tokens"] += n
+            if req.num_computed < len(ids):
+                continue                    # still reading its prompt
+            tok = self._sample(req, logits[-1])
+            if req.first_token_time is None:
+                req.first_token_time = time.monotonic()
+            req.output_ids.append(tok)
+            reason = self._stop(req, tok)
+            if reason is not None:
+                self._finish(req, reason)
+            outs.append(StepOutput(req.request_id, [tok], reason is not None, reason))
+        return outs
+
+    def generate(self, prompts: list, params=None) -> list:
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        rids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while self.has_work():
+            self.step()
+        return [self.requests[r].output_ids for r in rids]
+
+    def stats(self) -> dict:
+        s = dict(self._stats)
+        held = sum(1 for _ in self.states)
+        s.update({"kv": {"pages": self.config.max_num_seqs, "free": self.config.max_num_seqs - held,
+                         "cached": 0, "hits": 0, "lookups": 0, "evictions": 0},
+                  "running": len(self.running), "waiting": len(self.waiting)})
+        return s

@@ -134,6 +134,54 @@ class Qwen35MoeModel:
             w[i] = L
         return self
 
+    def init_random(self, seed: int = 0, std: float = 0.05) -> "Qwen35MoeModel":
+        """Random weights of the configured shapes (tests, ``random:`` deployments)."""
+        c, g = self.cfg, torch.Generator().manual_seed(seed)
+        if not c.layer_types:
+            c.layer_types = ["full_attention" if (i + 1) % 4 == 0 else "linear_attention"
+                             for i in range(c.num_hidden_layers)]
+
+        def rnd(*shape, dtype=None):
+            return (torch.randn(*shape, generator=g) * std).to(device=self.device,
+                                                               dtype=dtype or self.dtype)
+
+        def ones(n):
+            return torch.ones(n, dtype=torch.float32, device=self.device)
+        H, D, I = c.hidden_size, c.head_dim, c.moe_intermediate_size
+        kd = c.linear_num_key_heads * c.linear_key_head_dim
+        vd = c.linear_num_value_heads * c.linear_value_head_dim
+        w = self.w
+        w["embed"], w["norm"], w["lm_head"] = rnd(c.vocab_size, H), ones(H), rnd(c.vocab_size, H)
+        for i, kind in enumerate(c.layer_types):
+            L = {"kind": kind, "in_norm": ones(H), "post_norm": ones(H)}
+            if kind == "full_attention":
+                L["q"] = rnd(c.num_attention_heads * 2 * D, H)
+                L["k"], L["v"] = rnd(c.num_key_value_heads * D, H), rnd(c.num_key_value_heads * D, H)
+                L["o"] = rnd(H, c.num_attention_heads * D)
+                L["q_norm"], L["k_norm"] = ones(D), ones(D)
+            else:
+                L["qkvz"] = rnd(2 * kd + 2 * vd + 2 * c.linear_num_value_heads, H)
+                L["conv"] = rnd(2 * kd + vd, c.linear_conv_kernel_dim, dtype=torch.float32) * 4
+                L["dt_bias"] = ones(c.linear_num_value_heads)
+                L["A"] = -(torch.rand(c.linear_num_value_heads, generator=g) * 4 + 0.5).to(self.device)
+                L["gnorm"] = ones(c.linear_value_head_dim).to(self.dtype)
+                L["out"] = rnd(H, vd)
+            L["router"] = rnd(c.num_experts, H)
+            L["w13"], L["w2"] = rnd(c.num_experts, 2 * I, H), rnd(c.num_experts, H, I)
+            S = c.shared_expert_intermediate_size
+            L["s13"], L["s2"], L["sgate"] = rnd(2 * S, H), rnd(H, S), rnd(1, H)
+            w[i] = L
+        return self
+
+    @classmethod
+    def tiny_config(cls) -> Qwen35Config:
+        return Qwen35Config(vocab_size=1024, hidden_size=64, num_hidden_layers=4,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                            linear_num_key_heads=2, linear_num_value_heads=4,
+                            linear_key_head_dim=16, linear_value_head_dim=16, num_experts=8,
+                            num_experts_per_tok=2, moe_intermediate_size=32,
+                            shared_expert_intermediate_size=32, eos_token_id=1023)
+
     # ------------------------------------------------------------- forward --
     def new_state(self) -> list:
         return [LayerState() for _ in self.cfg.layer_types]
