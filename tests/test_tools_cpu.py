@@ -224,3 +224,15 @@ def test_admin_client(live_server, capsys):
     assert main(["admin", "--url", live_server, "query", "select count(*) from events"]) == 0
     assert "rows" in json.loads(capsys.readouterr().out)
     assert main(["admin", "--url", live_server, "query", "drop table events"]) == 1
+
+
+def test_block_manager_bounded_exhaustive_check_and_mutants():
+    """Every operation sequence up to depth 4 on a 5-page pool keeps the invariants of the
+    native block manager; each deliberately broken variant is flagged."""
+    from uniserve_v1_b200.engine.block_manager import BlockManager
+    from uniserve_v1_b200.tools.verify import explore, mutants
+    mk = lambda cls: (lambda pages: cls(pages, page_size=4))
+    r = explore(mk(BlockManager), pages=5, depth=4, n_keys=2)
+    assert r["violation"] is None and r["sequences"] > 2000
+    for name, cls in mutants(BlockManager):
+        assert explore(mk(cls), pages=5, depth=4, n_keys=2)["violation"], name

@@ -1,0 +1,223 @@
+"""Bounded exhaustive checks of the KV block manager.
+
+Every sequence of operations up to a depth - allocate, release, commit under a content
+key, match a key chain, flush - is run against a fresh native block manager
+(``csrc/host/block_manager.cpp``) next to a small abstract model that only tracks what a
+client can know: which pages it holds how often, and which key it committed on which
+page.  After every operation the invariants are checked:
+
+  holds       refcount(page) equals the client's holds, for every page
+  exclusive   allocate never hands out a page that is held
+  capacity    allocate(n) succeeds exactly when n <= num_free, and num_free equals the
+              pages nobody holds (free or cached-and-evictable)
+  content     match returns a leading run of the chain, each page carrying the key it
+              was committed under, and a chain whose pages were never reused is found
+  pinning     matched pages are held (they cannot be evicted under the reader)
+
+``mutants`` are wrappers that break one behaviour each (a dropped release, a match that
+does not pin, a commit under the wrong key, a stale page kept after reuse); the checker
+has to flag every one of them, which shows the invariants have teeth.
+
+    python -m uniserve_v1_b200.tools.verify --pages 5 --depth 5
+
+Reference behaviour: tools/verification/README.md (enumeration, replay and mutation checks
+of the buffer pool and the KV data plane; the TLA+ models themselves are not restated) -
+reference project path.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from typing import Optional
+
+import numpy as np
+
+
+class Violation(Exception):
+    pass
+
+
+class Client:
+    """What a client of the block manager knows."""
+
+    def __init__(self, bm, pages: int):
+        self.bm, self.pages = bm, pages
+        self.holds: dict = {}          # page -> count
+        self.key_of: dict = {}         # page -> key index (until the page is handed out again)
+
+    # ---- operations (return False when not applicable in this state) ----
+    def alloc(self, n: int) -> bool:
+        free_before = self.bm.num_free
+        got = self.bm.allocate(n)
+        if (got is not None) != (n <= free_before):
+            raise Violation(f"capacity: allocate({n}) with {free_before} free -> {got}")
+        if got is None:
+            return True
+        if len(set(got)) != n or any(p <= 0 or p >= self.pages for p in got):
+            raise Violation(f"exclusive: allocate returned {got}")
+        for p in got:
+            if self.holds.get(p, 0):
+                raise Violation(f"exclusive: page {p} handed out while held")
+            self.holds[p] = 1
+            self.key_of.pop(p, None)               # reused: its old content is gone
+        return True
+
+    def release(self, i: int) -> bool:
+        held = sorted(p for p, c in self.holds.items() if c)
+        if i >= len(held):
+            return False
+        p = held[i]
+        self.bm.release([p])
+        self.holds[p] -= 1
+        return True
+
+    def commit(self, i: int, k: int, keys) -> bool:
+        held = sorted(p for p, c in self.holds.items() if c)
+        if i >= len(held):
+            return False
+        p = held[i]
+        if p in self.key_of or k in self.key_of.values():
+            return False                           # one key per page, one page per key here
+        self.bm.commit(p, keys[k])
+        self.key_of[p] = k
+        return True
+
+    def match(self, n: int, keys) -> bool:
+        chain = np.ascontiguousarray(keys[:n], dtype=np.uint64)
+        got = self.bm.match_prefix(chain)
+        if len(got) > n:
+            raise Violation(f"content: match of {n} keys returned {got}")
+        for j, p in enumerate(got):
+            if self.key_of.get(p) != j:
+                raise Violation(f"content: page {p} returned for key {j}, holds {self.key_of.get(p)}")
+            self.holds[p] = self.holds.get(p, 0) + 1
+        want = 0
+        by_key = {k: p for p, k in self.key_of.items()}
+        while want < n and want in by_key:
+            want += 1
+        if len(got) != want:
+            raise Violation(f"content: chain of {want} cached pages, match found {len(got)}")
+        return True
+
+    def flush(self) -> bool:
+        self.bm.flush()
+        for p in [p for p in self.key_of if not self.holds.get(p, 0)]:
+            del self.key_of[p]
+        return True
+
+    # ---- invariants ----
+    def check(self) -> None:
+        held = 0
+        for p in range(1, self.pages):
+            c = self.holds.get(p, 0)
+            if self.bm.refcount(p) != c:
+                raise Violation(f"holds: page {p} refcount {self.bm.refcount(p)}, client holds {c}")
+            held += 1 if c else 0
+        if self.bm.num_free != self.pages - 1 - held:
+            raise Violation(f"capacity: num_free {self.bm.num_free}, "
+                            f"{self.pages - 1 - held} pages are not held")
+
+
+def operations(n_keys: int) -> list:
+    ops = [("alloc", 1), ("alloc", 2), ("flush",)]
+    ops += [("release", i) for i in range(2)]
+    ops += [("commit", i, k) for i in range(2) for k in range(n_keys)]
+    ops += [("match", n) for n in range(1, n_keys + 1)]
+    return ops
+
+
+def explore(make_bm, pages: int = 5, depth: int = 5, n_keys: int = 2) -> dict:
+    """Runs every operation sequence up to ``depth``; returns counts and the first
+    violation (sequence + message) if any."""
+    ops = operations(n_keys)
+    probe = make_bm(pages)
+    keys = probe.page_keys(list(range(n_keys * probe.page_size)))
+    ran = {"sequences": 0, "operations": 0, "violation": None}
+
+    def run(seq) -> Optional[str]:
+        c = Client(make_bm(pages), pages)
+        try:
+            for op in seq:
+                kind = op[0]
+                ok = c.alloc(op[1]) if kind == "alloc" else \
+                    c.release(op[1]) if kind == "release" else \
+                    c.commit(op[1], op[2], keys) if kind == "commit" else \
+                    c.match(op[1], keys) if kind == "match" else c.flush()
+                if not ok:
+                    return "skip"
+                c.check()
+                ran["operations"] += 1
+        except Violation as v:
+            return str(v)
+        return None
+
+    def dfs(seq):
+        if ran["violation"]:
+            return
+        if seq:
+            r = run(seq)
+            if r == "skip":
+                return
+            ran["sequences"] += 1
+            if r:
+                ran["violation"] = {"sequence": [list(o) for o in seq], "message": r}
+                return
+        if len(seq) < depth:
+            for op in ops:
+                dfs(seq + [op])
+    dfs([])
+    return ran
+
+
+# ------------------------------------------------------------------ mutants --
+def mutants(base):
+    """(name, factory) of block managers with one broken behaviour each."""
+    class DropsRelease(base):
+        def release(self, pages):
+            self._n = getattr(self, "_n", 0) + 1
+            if self._n % 2:
+                super().release(pages)
+
+    class MatchDoesNotPin(base):
+        def match_prefix(self, keys):
+            got = super().match_prefix(keys)
+            if got:
+                super().release(got)
+            return got
+
+    class CommitsWrongKey(base):
+        def commit(self, page, key):
+            return super().commit(page, (int(key[0]) ^ 1, int(key[1])))
+
+    class KeepsStalePage(base):
+        def allocate(self, n):
+            got = super().allocate(n)
+            if got and getattr(self, "_last", None) and n == 1:
+                super().release(got)
+                return [self._last]
+            if got:
+                self._last = got[0]
+            return got
+    return [("drops every second release", DropsRelease), ("match does not pin", MatchDoesNotPin),
+            ("commit under another key", CommitsWrongKey), ("hands out a held page", KeepsStalePage)]
+
+
+def main(argv=None) -> int:
+    from ..engine.block_manager import BlockManager
+    ap = argparse.ArgumentParser(prog="uniserve_v1_b200.tools.verify")
+    ap.add_argument("--pages", type=int, default=5)
+    ap.add_argument("--depth", type=int, default=5)
+    ap.add_argument("--keys", type=int, default=2)
+    a = ap.parse_args(argv)
+    mk = lambda cls: (lambda pages: cls(pages, page_size=4))
+    report = {"native": explore(mk(BlockManager), a.pages, a.depth, a.keys), "mutants": {}}
+    for name, cls in mutants(BlockManager):
+        r = explore(mk(cls), a.pages, min(a.depth, 4), a.keys)
+        report["mutants"][name] = "caught" if r["violation"] else "MISSED"
+    print(json.dumps(report, indent=1))
+    bad = report["native"]["violation"] or "MISSED" in report["mutants"].values()
+    return 1 if bad else 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
