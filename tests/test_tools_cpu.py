@@ -236,3 +236,87 @@ def test_block_manager_bounded_exhaustive_check_and_mutants():
     assert r["violation"] is None and r["sequences"] > 2000
     for name, cls in mutants(BlockManager):
         assert explore(mk(cls), pages=5, depth=4, n_keys=2)["violation"], name
+
+
+def _start_chat_server():
+    import uvicorn
+    from uniserve_v1_b200.config.policy import Package
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.server.app import create_app
+    from uniserve_v1_b200.server.tokenizer import ByteTokenizer
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    eng = LLMEngine(model, num_pages=256, max_num_seqs=8, max_model_len=512, use_graphs=False)
+    pkg = Package.parse('model = "random:tiny"\nserved_model_name = "tiny"\n')
+    app = create_app(package=pkg, engine=eng, tokenizer=ByteTokenizer(1024, 1023),
+                     served_model_name="tiny")
+    port = _free_port()
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    for _ in range(200):
+        if server.started:
+            break
+        time.sleep(0.05)
+    assert server.started
+    return f"http://127.0.0.1:{port}", server, th, eng
+
+
+def test_router_disaggregates_prefill_and_decode(live_server):
+    """A prefill replica and a decode replica behind the router: the answers (plain and
+    streamed, greedy and seeded sampling) are those of one replica; the decode replica
+    computes no prompt; a request that ends at its first token is answered by the prefill
+    replica alone."""
+    import json
+    import urllib.request
+    import uvicorn
+    from uniserve_v1_b200.server.router import create_router_app
+    pre_url, pre_srv, pre_th, pre_eng = _start_chat_server()
+    dec_url, dec_srv, dec_th, dec_eng = _start_chat_server()
+    port = _free_port()
+    app = create_router_app([], prefill_urls=[pre_url], decode_urls=[dec_url])
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+    t = threading.Thread(target=server.run, daemon=True)
+    t.start()
+    for _ in range(200):
+        if server.started:
+            break
+        time.sleep(0.05)
+
+    def post(base, body):
+        req = urllib.request.Request(base + "/v1/chat/completions", data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return r.read().decode()
+
+    def text_of_stream(sse):
+        out = ""
+        for line in sse.splitlines():
+            if line.startswith("data: ") and line != "data: [DONE]":
+                ch = json.loads(line[6:])
+                if ch.get("choices"):
+                    out += ch["choices"][0]["delta"].get("content") or ""
+        return out
+    base = f"http://127.0.0.1:{port}"
+    try:
+        for extra in ({"temperature": 0}, {"temperature": 0.9, "top_p": 0.9, "seed": 5}):
+            body = dict({"model": "tiny", "messages": [{"role": "user", "content": "tell me"}],
+                         "max_tokens": 9, "ignore_eos": True}, **extra)
+            want = json.loads(post(live_server, body))
+            got = json.loads(post(base, body))
+            assert got["choices"][0]["message"] == want["choices"][0]["message"]
+            assert got["usage"]["completion_tokens"] == 9
+            assert text_of_stream(post(base, dict(body, stream=True))) == \
+                (want["choices"][0]["message"]["content"] or "")
+        assert dec_eng.scheduler.stats["prefill_tokens"] <= 8      # one token per imported request
+        assert pre_eng.scheduler.stats["decode_tokens"] == 0 and not pre_eng.scheduler.running
+        one = json.loads(post(base, {"model": "tiny", "max_tokens": 1, "temperature": 0,
+                                     "ignore_eos": True,
+                                     "messages": [{"role": "user", "content": "x"}]}))
+        assert one["usage"]["completion_tokens"] == 1
+        with urllib.request.urlopen(base + "/v1/models", timeout=10) as r:
+            assert json.loads(r.read())["data"][0]["id"] == "tiny"
+    finally:
+        for srv, th_ in ((server, t), (pre_srv, pre_th), (dec_srv, dec_th)):
+            srv.should_exit = True
+            th_.join(timeout=10)

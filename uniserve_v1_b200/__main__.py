@@ -221,7 +221,9 @@ def main(argv=None) -> int:
     ad.add_argument("arg", nargs="?", help="config.toml to put, or the SQL text")
     r = sub.add_parser("route", help="one address in front of data-parallel replicas")
     r.add_argument("--listen", default="127.0.0.1:8000")
-    r.add_argument("--replica", action="append", required=True, help="base URL of a replica")
+    r.add_argument("--replica", action="append", default=[], help="base URL of a mixed replica")
+    r.add_argument("--prefill", action="append", default=[], help="base URL of a prefill replica")
+    r.add_argument("--decode", action="append", default=[], help="base URL of a decode replica")
     a = ap.parse_args(argv)
     if a.cmd == "serve":
         return serve(a)
@@ -231,8 +233,11 @@ def main(argv=None) -> int:
         import uvicorn
         from .server.router import create_router_app
         host, _, port = a.listen.rpartition(":")
-        uvicorn.run(create_router_app(a.replica), host=host or "127.0.0.1", port=int(port),
-                    log_level="warning")
+        if not a.replica and not (a.prefill and a.decode):
+            ap.error("route needs --replica, or --prefill together with --decode")
+        uvicorn.run(create_router_app(a.replica, prefill_urls=a.prefill or None,
+                                      decode_urls=a.decode or None),
+                    host=host or "127.0.0.1", port=int(port), log_level="warning")
         return 0
     if a.cmd == "build":
         from . import build

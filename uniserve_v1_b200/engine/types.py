@@ -128,3 +128,4 @@ class StepOutput:
     logprobs: Optional[list] = None
     num_cached_tokens: int = 0
     error: Optional[str] = None
+    handoff: Optional[bytes] = None      # the request left this engine: its framed state

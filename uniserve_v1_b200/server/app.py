@@ -24,7 +24,7 @@ from fastapi.responses import JSONResponse, PlainTextResponse, Response, Streami
 from pydantic import ValidationError
 
 from ..config.policy import ConfigError, Package, strongest_effect
-from ..engine.types import FinishReason, SamplingParams
+from ..engine.types import FinishReason, SamplingParams, StepOutput
 from .chat import ChatTemplate, ReasoningSplitter, StopStrings, ToolCallParser
 from .engine_service import EngineService, Overloaded
 from .observation import ObservationStore
@@ -316,10 +316,33 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
 
     # ------------------------------------------------------------------- chat --
     if engine is not None:
+        @app.post("/internal/prefill")
+        async def chat_prefill(request: Request):
+            """Prefill role: the chat request runs to its first token; the answer is the
+            request's framed state (``application/octet-stream``) for a decode replica, or
+            the ordinary completion when the first token already ended it."""
+            return await _chat(request, role="prefill")
+
+        @app.post("/internal/decode")
+        async def chat_decode(request: Request):
+            """Decode role: body {"request": <chat request>, "handoff": <base64 state>}."""
+            import base64
+            from ..engine.handoff import Handoff
+            try:
+                body = await request.json()
+                h = Handoff.from_bytes(base64.b64decode(body["handoff"]))
+            except Exception as e:
+                return _err(400, f"hand-off body: {e}")
+            return await _chat(request, body=body["request"], handoff=h)
+
         @app.post("/v1/chat/completions")
         async def chat(request: Request):
+            return await _chat(request)
+
+        async def _chat(request: Request, role: Optional[str] = None, body=None, handoff=None):
             try:
-                req = ChatCompletionRequest.model_validate(await request.json())
+                req = ChatCompletionRequest.model_validate(body if body is not None
+                                                           else await request.json())
             except ValidationError as e:
                 err = e.errors()[0]
                 loc = ".".join(str(x) for x in err["loc"])
@@ -353,13 +376,30 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
                 return _err(400, str(e))
             try:
                 rid, q = s.service.submit(ids, params, "chatcmpl-" + request.state.request_id,
-                                          req.priority or 0, req.cache_salt or req.prompt_cache_key)
+                                          req.priority or 0, req.cache_salt or req.prompt_cache_key,
+                                          lend=role == "prefill", handoff=handoff)
             except Overloaded as e:
                 return _err(503, str(e), "overloaded", headers={"Retry-After": "1"})
             run = ChatRun(s, req, rid, len(ids))
+            if role == "prefill":
+                while True:
+                    out = await q.get()
+                    if out.handoff is not None:
+                        return Response(out.handoff, media_type="application/octet-stream",
+                                        headers={"x-uniserve-request-id": rid})
+                    run.feed(out)
+                    if out.finished:
+                        if out.error:
+                            return _err(500, out.error, "server_error")
+                        return JSONResponse(run.response(), headers={"x-uniserve-finished": "1"})
+            # tokens the lending engine already produced open the answer
+            seeded = list(handoff.output_ids) if handoff is not None else []
+            first = StepOutput(rid, seeded, False) if seeded else None
 
             if not req.stream:
                 try:
+                    if first is not None:
+                        run.feed(first)
                     while True:
                         out = await q.get()
                         run.feed(out)
@@ -376,6 +416,9 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
                 keep = float(s.package.server_config.stream_keep_alive)
                 yield "data: " + json.dumps(run.chunk({"role": "assistant", "content": ""})) + "\n\n"
                 try:
+                    if first is not None:
+                        for d in run.feed(first):
+                            yield "data: " + json.dumps(run.chunk(d)) + "\n\n"
                     while True:
                         try:
                             out = await asyncio.wait_for(q.get(), keep)

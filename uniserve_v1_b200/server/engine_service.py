@@ -56,8 +56,12 @@ class EngineService:
 
     # ------------------------------------------------------------ submission --
     def submit(self, prompt_ids, params: SamplingParams, request_id: Optional[str] = None,
-               priority: int = 0, cache_salt: Optional[str] = None):
-        """Returns (request_id, asyncio.Queue of StepOutput); call from an event loop."""
+               priority: int = 0, cache_salt: Optional[str] = None, lend: bool = False,
+               handoff=None):
+        """Returns (request_id, asyncio.Queue of StepOutput); call from an event loop.
+        ``lend``: the request leaves after its first token - its stream ends with an output
+        that carries the framed state (prefill role).  ``handoff``: continue a request that
+        another engine lent (decode role); ``prompt_ids`` are then only kept for accounting."""
         if self.max_queued is not None and self.inbox.qsize() + len(self.streams) >= self.max_queued:
             raise Overloaded("too many queued requests")
         rid = request_id or "chatcmpl-" + uuid.uuid4().hex
@@ -67,8 +71,14 @@ class EngineService:
             self.streams[rid] = (loop, q)
             self.meta[rid] = {"arrival": time.monotonic(), "first": None, "tokens": 0,
                               "prompt": list(prompt_ids), "params": params, "outputs": [],
-                              "migrations": 0, "priority": priority, "salt": cache_salt}
-        self.inbox.put(("add", rid, list(prompt_ids), params, priority, cache_salt, None))
+                              "migrations": 0, "priority": priority, "salt": cache_salt,
+                              "lend": lend}
+        if handoff is not None:
+            handoff.request_id = rid
+            self.meta[rid]["outputs"] = list(handoff.output_ids)
+            self.inbox.put(("import", rid, handoff))
+        else:
+            self.inbox.put(("add", rid, list(prompt_ids), params, priority, cache_salt, None))
         self.wake.set()
         return rid, q
 
@@ -142,6 +152,13 @@ class EngineService:
                                                     cache_salt=salt, output_ids=outputs)
                         except Exception as e:      # input_error rejects the request
                             self._deliver(StepOutput(rid, [], True, FinishReason.ERROR, error=str(e)))
+                    elif msg[0] == "import":
+                        try:
+                            from ..engine.handoff import import_request
+                            import_request(self.engine, msg[2])
+                        except Exception as e:
+                            self._deliver(StepOutput(msg[1], [], True, FinishReason.ERROR,
+                                                     error=f"hand-off refused: {e}"))
                     elif msg[0] == "abort":
                         if self.engine.abort(msg[1]):
                             self._deliver(StepOutput(msg[1], [], True, FinishReason.ABORT))
@@ -158,6 +175,12 @@ class EngineService:
                 continue
             self.steps += 1
             for o in outs:
+                meta = self.meta.get(o.request_id)
+                if meta and meta.get("lend") and o.new_token_ids and not o.finished:
+                    from ..engine.handoff import export_request
+                    o = StepOutput(o.request_id, o.new_token_ids, True, None,
+                                   num_cached_tokens=o.num_cached_tokens,
+                                   handoff=export_request(self.engine, o.request_id).to_bytes())
                 self._deliver(o)
             now = time.monotonic()
             if self.obs and now - self.last_snapshot > 1.0:

@@ -13,6 +13,11 @@ yet.
     python -m uniserve_v1_b200 route --listen 127.0.0.1:8000 \
         --replica http://127.0.0.1:8001 --replica http://127.0.0.1:8002
 
+Roles (``replicas.<id>.role = prefill | decode | mixed``): with ``--prefill URL`` and
+``--decode URL`` replicas a chat request is computed up to its first token on a prefill
+replica and handed, with the contents of its KV pages, to a decode replica that
+streams the answer (``engine/handoff.py``).
+
 Reference behaviour: docs/configuration.md:298, crates/daemon/src/leader.rs:562 (replica
 configs), :1834 (submit_routed); reference project paths.
 """
@@ -63,11 +68,19 @@ class ReplicaRouter:
                 for r in self.replicas]
 
 
-def create_router_app(urls: list, api_key: Optional[str] = None) -> FastAPI:
+def create_router_app(urls: list, api_key: Optional[str] = None,
+                      prefill_urls: Optional[list] = None,
+                      decode_urls: Optional[list] = None) -> FastAPI:
+    """``urls``: replicas of role ``mixed``.  With ``prefill_urls`` and ``decode_urls`` chat
+    requests are disaggregated: a prefill replica computes the prompt and the first token
+    (``/internal/prefill``), its answer - the request's framed state - goes to a decode
+    replica (``/internal/decode``), whose stream is relayed to the client."""
     import aiohttp
-    router = ReplicaRouter(urls)
+    router = ReplicaRouter(urls or (list(prefill_urls or []) + list(decode_urls or [])))
+    pre = ReplicaRouter(prefill_urls) if prefill_urls else None
+    dec = ReplicaRouter(decode_urls) if decode_urls else None
     app = FastAPI(title="uniserve_v1_b200 replica router")
-    app.state.router = router
+    app.state.router, app.state.prefill, app.state.decode = router, pre, dec
     state = {"session": None}
 
     async def session():
@@ -130,6 +143,50 @@ def create_router_app(urls: list, api_key: Optional[str] = None) -> FastAPI:
                 r.served += 1
             return Response(content=data, status_code=up.status, media_type=ctype, headers=extra)
 
+    async def disaggregated(req: Request):
+        import base64
+        body = await req.body()
+        s = await session()
+        p = pre.pick()
+        p.in_flight += 1
+        try:
+            async with s.post(p.url + "/internal/prefill", data=body, headers=_headers(req)) as up:
+                blob, status = await up.read(), up.status
+                ctype = up.headers.get("content-type", "")
+        except aiohttp.ClientConnectionError:
+            pre.mark_down(p)
+            return JSONResponse({"error": {"message": "no prefill replica is reachable",
+                                           "type": "service_unavailable"}}, status_code=503)
+        finally:
+            p.in_flight -= 1
+            p.served += 1
+        if not ctype.startswith("application/octet-stream"):
+            # an error, or a request that its first token already ended
+            return Response(content=blob, status_code=status, media_type=ctype or "application/json")
+        d = dec.pick()
+        d.in_flight += 1
+        payload = json.dumps({"request": json.loads(body),
+                              "handoff": base64.b64encode(blob).decode()})
+        hdr = dict(_headers(req), **{"content-type": "application/json"})
+        try:
+            up = await s.post(d.url + "/internal/decode", data=payload, headers=hdr)
+        except aiohttp.ClientConnectionError:
+            d.in_flight -= 1
+            dec.mark_down(d)
+            return JSONResponse({"error": {"message": "no decode replica is reachable",
+                                           "type": "service_unavailable"}}, status_code=503)
+        ctype = up.headers.get("content-type", "application/json")
+
+        async def relay():
+            try:
+                async for chunk in up.content.iter_any():
+                    yield chunk
+            finally:
+                up.release()
+                d.in_flight -= 1
+                d.served += 1
+        return StreamingResponse(relay(), status_code=up.status, media_type=ctype)
+
     @app.get("/health")
     async def health():
         s = await session()
@@ -150,6 +207,9 @@ def create_router_app(urls: list, api_key: Optional[str] = None) -> FastAPI:
 
     @app.api_route("/{path:path}", methods=["GET", "POST", "PUT", "DELETE"])
     async def any_route(path: str, req: Request):
+        if pre is not None and dec is not None and req.method == "POST" and \
+                path == "v1/chat/completions":
+            return await disaggregated(req)
         return await forward(req, "/" + path)
 
     return app
