@@ -217,3 +217,32 @@ def test_dense_qwen3_family():
         logits, _ = ReferenceQwen3Moe(model).forward(torch.tensor(seq))
         assert int(logits[-1].argmax()) == t
         seq.append(t)
+
+
+def test_gated_delta_rule_chunked_equals_stepwise():
+    """Chunks of 64 (and a ragged tail), carried state, strong and weak decay."""
+    import torch
+    from uniserve_v1_b200.ops import gated_delta as GD
+    g_ = torch.Generator().manual_seed(0)
+    T, H, Dk, Dv = 150, 3, 16, 24
+    q, k = torch.randn(T, H, Dk, generator=g_), torch.randn(T, H, Dk, generator=g_)
+    v = torch.randn(T, H, Dv, generator=g_)
+    beta = torch.rand(T, H, generator=g_)
+    for scale in (0.01, 2.0):
+        g = -torch.rand(T, H, generator=g_) * scale
+        s0 = torch.randn(H, Dk, Dv, generator=g_) * 0.3
+        o1, s1 = GD.gated_delta_rule_steps(q, k, v, g, beta, s0)
+        o2, s2 = GD.gated_delta_rule_chunked(q, k, v, g, beta, s0, chunk=64)
+        torch.testing.assert_close(o2, o1, atol=2e-4, rtol=2e-4)
+        torch.testing.assert_close(s2, s1, atol=2e-4, rtol=2e-4)
+        # a prompt in two calls equals one call
+        oa, sa = GD.gated_delta_rule(q[:70], k[:70], v[:70], g[:70], beta[:70], s0)
+        ob, sb = GD.gated_delta_rule(q[70:], k[70:], v[70:], g[70:], beta[70:], sa)
+        torch.testing.assert_close(torch.cat([oa, ob]), o1, atol=2e-4, rtol=2e-4)
+    x = torch.randn(20, 6, generator=g_)
+    w = torch.randn(6, 4, generator=g_)
+    y_all, st_all = GD.causal_conv1d(x, w)
+    y_a, st = GD.causal_conv1d(x[:7], w)
+    y_b, st = GD.causal_conv1d(x[7:], w, st)
+    torch.testing.assert_close(torch.cat([y_a, y_b]), y_all)
+    torch.testing.assert_close(st, st_all)
