@@ -201,3 +201,58 @@ def test_random_workloads_keep_the_books_straight():
         eng.blocks.flush()
         assert eng.blocks.num_free == total_pages
     run()
+
+
+def test_scheduling_program_decides_under_a_fuel_budget(tmp_path):
+    """A program from the package orders admissions (shortest prompt first) and keeps state
+    across a restart; a runaway program is cut by its budget and the default order applies."""
+    import torch
+    from uniserve_v1_b200.config.policy import Package
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.program import FuelExhausted, ProgramHost, ProgramPolicy
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    (tmp_path / "programs").mkdir()
+    (tmp_path / "programs" / "sjf.py").write_text(
+        "seen = {'n': 0}\n"
+        "def dispatch(waiting, room):\n"
+        "    seen['n'] += len(waiting)\n"
+        "    return [w['id'] for w in sorted(waiting, key=lambda w: (w['prompt_tokens'], w['arrival']))]\n"
+        "def save_state():\n    return seen\n"
+        "def restore_state(s):\n    seen.update(s)\n")
+    (tmp_path / "programs" / "spin.py").write_text(
+        "def dispatch(waiting, room):\n    while True:\n        pass\n")
+    (tmp_path / "config.toml").write_text(
+        'model = "random:tiny"\n[scheduler_config.policy_budget]\ncall_fuel = 20000\n'
+        '[programs.sjf]\nsource = "programs/sjf.py"\n[programs.spin]\nsource = "programs/spin.py"\n')
+    pkg = Package.load(tmp_path)
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    sp = SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)
+    prompts = {"long": list(range(40)), "short": list(range(5)), "mid": list(range(17))}
+
+    def first_tokens(policy):
+        eng = LLMEngine(model, num_pages=64, max_num_seqs=1, max_model_len=128,
+                        use_graphs=False, policy=policy)
+        for rid, p in prompts.items():
+            eng.add_request(p, sp, request_id=rid)
+        order = []
+        while eng.has_work():
+            for o in eng.step():
+                if o.request_id not in order:
+                    order.append(o.request_id)
+        return order
+    assert first_tokens(None) == ["long", "short", "mid"]                    # arrival order
+    host = ProgramHost.load(pkg, "sjf")
+    pol = ProgramPolicy(host)
+    assert first_tokens(pol) == ["short", "mid", "long"] and pol.faults == 0
+    assert host.fuel_used > 0 and host.call_fuel == 20000
+    again = ProgramHost.load(pkg, "sjf")
+    again.restore_state(host.save_state())
+    assert again.ns["seen"]["n"] == host.ns["seen"]["n"] > 0
+    spin = ProgramPolicy(ProgramHost.load(pkg, "spin"))
+    assert first_tokens(spin) == ["long", "short", "mid"] and spin.faults > 0
+    import pytest
+    with pytest.raises(FuelExhausted):
+        spin.host.call("dispatch", [], {})
+    with pytest.raises(Exception):
+        ProgramHost("import os\n", "escape")                                  # no import machinery

@@ -134,7 +134,12 @@ def serve(args) -> int:
             attach_fused(ctx, device, hidden=cfg.hidden_size)
 
         def make_engine():
-            eng = LLMEngine(model, page_size=min(pkg.kv_cache_config.block_size, 16)
+            policy = None
+            if "scheduling" in pkg.programs:        # the package's own scheduling program
+                from .engine.program import ProgramHost, ProgramPolicy
+                policy = ProgramPolicy(ProgramHost.load(pkg, "scheduling"))
+            eng = LLMEngine(model, policy=policy,
+                            page_size=min(pkg.kv_cache_config.block_size, 16)
                             if device.type == "cuda" else pkg.kv_cache_config.block_size,
                             max_num_seqs=min(pkg.max_running_requests, pkg.scheduler_config.max_batch),
                             max_model_len=pkg.max_model_len or min(cfg.max_position_embeddings, 8192),
