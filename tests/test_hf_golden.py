@@ -209,3 +209,28 @@ def test_dense_state_engine_serves_the_hybrid_decoder(tmp_path):
     rid = eng.add_request(prompts[1], params[1])
     eng.step()
     assert eng.abort(rid) and not eng.has_work()
+
+
+def test_fixture_generator_round_trip(tmp_path):
+    """Fixtures written by the generator are reproduced by the package's own loaders and
+    decoders (paged engine for the Qwen3 families, dense-state engine for the hybrid one)."""
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, resolve_family
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35Config, Qwen35MoeModel
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.testing import model_fixtures as MF
+    assert MF.main([str(tmp_path), "qwen3", "qwen3_5_moe"]) == 0
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    for fam in ("qwen3", "qwen3_5_moe"):
+        ref = json.loads((tmp_path / fam / "reference.json").read_text())
+        ld = CheckpointLoader(tmp_path / fam)
+        if resolve_family(tmp_path / fam) == "qwen3_5_moe":
+            model = Qwen35MoeModel(Qwen35Config.from_hf(ld.config), "cpu", torch.float32).load_state(ld)
+            out = DenseStateEngine(model).generate([ref["prompt"]], sp)[0]
+        else:
+            model = Qwen3MoeModel(Qwen3MoeConfig.from_hf(ld.config), "cpu", torch.float32).load_state(ld)
+            out = LLMEngine(model, num_pages=32, max_num_seqs=2, max_model_len=128,
+                            use_graphs=False).generate([ref["prompt"]], sp)[0]
+        assert out == ref["greedy"], fam
