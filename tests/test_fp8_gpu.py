@@ -98,7 +98,9 @@ def test_moe_experts_fp8(T, E, k, H, I):
 
 
 @pytest.mark.parametrize("T,K,M,gated", [(300, 512, 384, False), (1000, 1024, 640, True),
-                                         (64, 256, 128, False)])
+                                         (64, 256, 128, False),
+                                         # more than one wave of tiles: the CTA-pair kernels
+                                         (2600, 256, 2176, False), (2700, 256, 1152, True)])
 def test_linear_fp8_per_tensor(T, K, M, gated):
     """Per-tensor weight scale, per-row dynamic activation scale, whole-K accumulation in
     tensor memory: against the FP32 product of the same quantised operands."""
