@@ -234,3 +234,37 @@ def test_fixture_generator_round_trip(tmp_path):
             out = LLMEngine(model, num_pages=32, max_num_seqs=2, max_model_len=128,
                             use_graphs=False).generate([ref["prompt"]], sp)[0]
         assert out == ref["greedy"], fam
+
+
+def test_decoder_as_text_encoder_matches_transformers_hidden_states(tmp_path):
+    """The cache-free causal pass returns the residual stream after n blocks
+    (`hidden_states[n]` of transformers); the video service's model-backed text encoder
+    serves and caches those rows."""
+    from transformers import Qwen3Config as HfCfg, Qwen3ForCausalLM
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.server.tokenizer import ByteTokenizer
+    from uniserve_v1_b200.server.video_service import ModelTextEncoder
+    torch.manual_seed(2)
+    cfg = HfCfg(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=3,
+                num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                max_position_embeddings=256, rope_theta=1e6, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, eos_token_id=511, pad_token_id=0)
+    hf = Qwen3ForCausalLM(cfg).float().eval()
+    _save(hf, cfg, tmp_path / "enc")
+    ld = CheckpointLoader(tmp_path / "enc")
+    model = Qwen3MoeModel(Qwen3MoeConfig.from_hf(ld.config), "cpu", torch.float32).load_state(ld)
+    ids = [5, 300, 17, 17, 450, 2, 99]
+    with torch.no_grad():
+        hs = hf(torch.tensor([ids]), output_hidden_states=True).hidden_states
+    for n in (0, 1, 2):
+        torch.testing.assert_close(model.encode(ids, n), hs[n][0], atol=2e-4, rtol=2e-4)
+    # transformers reports the last entry after the final norm
+    from uniserve_v1_b200.ops import reference as R
+    torch.testing.assert_close(R.rmsnorm(model.encode(ids), model.final_norm, 1e-6), hs[3][0],
+                               atol=2e-4, rtol=2e-4)
+    enc = ModelTextEncoder(model, ByteTokenizer(512, 511), num_layers=2)
+    a = enc.encode("a sunset over water", "cpu")
+    assert a.shape == (len(ByteTokenizer(512, 511).encode("a sunset over water")), 64)
+    assert enc.encode("a sunset over water", "cpu") is not None and len(enc.cache) == 1
+    torch.testing.assert_close(a, model.encode(ByteTokenizer(512, 511).encode("a sunset over water"), 2))

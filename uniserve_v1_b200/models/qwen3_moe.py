@@ -495,6 +495,32 @@ class Qwen3MoeModel:
         # every stage samples the same tokens from the last stage's rows
         return self.ctx.broadcast(x.contiguous(), last, "layer")
 
+    def encode(self, input_ids, num_layers: Optional[int] = None) -> torch.Tensor:
+        """Encoder use of the decoder (text conditioning of the video family): one causal
+        pass over ``input_ids`` [T] without a KV cache; returns the residual stream after
+        ``num_layers`` blocks (all of them by default), FP32 [T, hidden] - what
+        ``transformers`` calls ``hidden_states[num_layers]``."""
+        assert self.pp == 1, "the encoder pass runs on one pipeline stage"
+        ids = torch.as_tensor(input_ids, dtype=torch.int32, device=self.device)
+        T = ids.shape[0]
+        L = self.cfg.num_hidden_layers if num_layers is None else int(num_layers)
+        i32 = torch.int32
+        cu = torch.tensor([0, T], dtype=i32, device=self.device)
+        meta = AttnMeta(kind="prefill", slots=torch.full((T,), -1, dtype=i32, device=self.device),
+                        cu_q=cu, cu_k=cu, max_q=T, max_k=T, context_lens=[0])
+        pos = torch.arange(T, dtype=i32, device=self.device)
+        kc = torch.zeros(1, 16, self.Hkv, self.D, dtype=self.dtype, device=self.device)
+        hidden, residual = F.embedding(ids, self.embed), None
+        if L == 0:
+            return hidden.float()
+        for i in range(L):
+            lw = self.layers[i]
+            x, residual = self._reduce_norm(None, hidden, None, residual, lw.input_norm)
+            mixed, _ = self._attention(None, lw, x, pos, meta, kc, kc)
+            x, residual = self._reduce_norm(None, mixed, None, residual, lw.post_norm)
+            hidden, _ = self._mlp(None, lw, x)
+        return residual.float() + hidden.float()
+
     # ------------------------------------------------------------ pipeline --
     def _stage_send(self, hidden, residual) -> None:
         """Hand-off to the next stage: the block output and the FP32 residual stream

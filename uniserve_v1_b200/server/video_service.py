@@ -54,6 +54,28 @@ class TextEncoder:
         return feats.to(device)
 
 
+class ModelTextEncoder(TextEncoder):
+    """Prompt features from a language model used as an encoder: the residual stream of a
+    Qwen3 decoder after ``num_layers`` blocks (the served family reads 50 of 64), one row
+    per prompt token.  Same cache and key as the stand-in."""
+
+    def __init__(self, model, tokenizer, num_layers: Optional[int] = None, max_tokens: int = 512):
+        super().__init__(model.cfg.hidden_size, max_tokens)
+        self.model, self.tokenizer, self.num_layers = model, tokenizer, num_layers
+
+    def encode(self, prompt: str, device) -> torch.Tensor:
+        k = self.key(prompt)
+        if k in self.cache:
+            self.cache.move_to_end(k)
+            return self.cache[k].to(device)
+        ids = self.tokenizer.encode(prompt)[:self.max_tokens] or [0]
+        feats = self.model.encode(ids, self.num_layers).float().cpu()
+        self.cache[k] = feats
+        while len(self.cache) > 64:
+            self.cache.popitem(last=False)
+        return feats.to(device)
+
+
 class VideoJob:
     def __init__(self, prompt: str, plan):
         self.id = "video_" + uuid.uuid4().hex[:24]
