@@ -320,3 +320,33 @@ def test_router_disaggregates_prefill_and_decode(live_server):
         for srv, th_ in ((server, t), (pre_srv, pre_th), (dec_srv, dec_th)):
             srv.should_exit = True
             th_.join(timeout=10)
+
+
+def test_block_manager_replays_a_serving_trace():
+    """The block-manager calls of an engine that serves shared prefixes under page pressure
+    (preemption, eviction) replay on a fresh manager with the same answers and with the
+    invariants intact; a tampered trace is flagged."""
+    from uniserve_v1_b200.engine.block_manager import BlockManager
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.tools.verify import record, replay
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    eng = LLMEngine(model, num_pages=14, page_size=4, max_num_seqs=3, max_model_len=64,
+                    use_graphs=False)
+    trace = record(eng.blocks)
+    shared = list(range(100, 113))
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    for tail in ([1, 2, 3], [4, 5], [6], [7, 8, 9, 10]):
+        eng.add_request(shared + tail, sp)
+    while eng.has_work():
+        eng.step()
+    eng.generate([shared + [11]], sp)                      # finds the committed prefix again
+    kinds = {op[0] for op in trace}
+    assert {"allocate", "release", "commit", "match"} <= kinds and len(trace) > 40
+    assert eng.scheduler.stats["preemptions"] > 0 or eng.blocks.stats()["evictions"] > 0
+    mk = lambda pages: BlockManager(pages, page_size=4)
+    assert replay(trace, mk, 14) == {"calls": len(trace), "violation": None}
+    i = next(i for i, op in enumerate(trace) if op[0] == "release")
+    bad = trace[:i] + [trace[i], trace[i]] + trace[i + 1:]           # a double release
+    assert replay(bad, mk, 14)["violation"]

@@ -14,6 +14,10 @@ page.  After every operation the invariants are checked:
               was committed under, and a chain whose pages were never reused is found
   pinning     matched pages are held (they cannot be evicted under the reader)
 
+``record`` / ``replay`` do the same for real traffic: the calls an engine makes while it
+serves requests (shared prefixes, preemption, eviction) are recorded and run again on a
+fresh manager, which must answer identically and keep the invariants.
+
 ``mutants`` are wrappers that break one behaviour each (a dropped release, a match that
 does not pin, a commit under the wrong key, a stale page kept after reuse); the checker
 has to flag every one of them, which shows the invariants have teeth.
@@ -200,6 +204,84 @@ def mutants(base):
             return got
     return [("drops every second release", DropsRelease), ("match does not pin", MatchDoesNotPin),
             ("commit under another key", CommitsWrongKey), ("hands out a held page", KeepsStalePage)]
+
+
+# ------------------------------------------------------------ trace / replay --
+def record(bm) -> list:
+    """Starts recording every call a client makes on ``bm`` (allocate, release, commit,
+    match_prefix, flush) with its result; returns the list that fills up."""
+    trace: list = []
+
+    def wrap(name, encode):
+        inner = getattr(bm, name)
+
+        def call(*args):
+            out = inner(*args)
+            trace.append(encode(args, out))
+            return out
+        setattr(bm, name, call)
+    wrap("allocate", lambda a, out: ("allocate", int(a[0]), None if out is None else list(out)))
+    wrap("release", lambda a, out: ("release", [int(p) for p in a[0]]))
+    wrap("commit", lambda a, out: ("commit", int(a[0]), (int(a[1][0]), int(a[1][1]))))
+    wrap("match_prefix", lambda a, out: ("match", [(int(k[0]), int(k[1])) for k in a[0]],
+                                         list(out)))
+    wrap("flush", lambda a, out: ("flush",))
+    return trace
+
+
+def replay(trace: list, make_bm, pages: int) -> dict:
+    """Runs a recorded serving trace against a fresh block manager: the calls must give the
+    recorded results again (the manager is deterministic) and the client-side invariants
+    (holds, exclusivity, capacity, content) must hold after every call."""
+    bm = make_bm(pages)
+    holds: dict = {}
+    key_of: dict = {}
+    n = 0
+    try:
+        for op in trace:
+            kind = op[0]
+            if kind == "allocate":
+                free = bm.num_free
+                got = bm.allocate(op[1])
+                if got != op[2]:
+                    raise Violation(f"replay: allocate({op[1]}) gave {got}, recorded {op[2]}")
+                if (got is not None) != (op[1] <= free):
+                    raise Violation(f"capacity: allocate({op[1]}) with {free} free -> {got}")
+                for p in got or []:
+                    if holds.get(p, 0):
+                        raise Violation(f"exclusive: page {p} handed out while held")
+                    holds[p] = 1
+                    key_of.pop(p, None)
+            elif kind == "release":
+                bm.release(op[1])
+                for p in op[1]:
+                    holds[p] = holds.get(p, 0) - 1
+                    if holds[p] < 0:
+                        raise Violation(f"holds: page {p} released more often than held")
+            elif kind == "commit":
+                bm.commit(op[1], op[2])
+                if op[2] not in key_of.values():
+                    key_of[op[1]] = op[2]
+            elif kind == "match":
+                got = bm.match_prefix(np.asarray(op[1], dtype=np.uint64).reshape(-1, 2))
+                if list(got) != op[2]:
+                    raise Violation(f"replay: match gave {list(got)}, recorded {op[2]}")
+                for j, p in enumerate(got):
+                    if key_of.get(p) != op[1][j]:
+                        raise Violation(f"content: page {p} returned for another key")
+                    holds[p] = holds.get(p, 0) + 1
+            else:
+                bm.flush()
+                for p in [p for p in key_of if not holds.get(p, 0)]:
+                    del key_of[p]
+            n += 1
+            for p in range(1, pages):
+                if bm.refcount(p) != holds.get(p, 0):
+                    raise Violation(f"holds: page {p} refcount {bm.refcount(p)}, "
+                                    f"client holds {holds.get(p, 0)} after call {n}")
+    except Violation as v:
+        return {"calls": n, "violation": str(v)}
+    return {"calls": n, "violation": None}
 
 
 def main(argv=None) -> int:
