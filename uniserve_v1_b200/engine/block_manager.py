@@ -154,6 +154,19 @@ class BlockManager:
                                   self.page_size, keys.ctypes.data)
         return keys[:n_full]
 
+    def chain_seed(self, salt: Optional[str] = None) -> bytes:
+        """Root of a request's key chain (weights identity + isolation salt)."""
+        return hashlib.sha256((self.identity + "\0" + (salt or "")).encode()).digest()
+
+    def chain_next(self, state: bytes, page_tokens: Sequence[int]):
+        """One link of the chain in Python: (next state, key of the page) - the same bytes
+        as ``page_keys`` produces, so a request extends its chain by the page it just filled
+        instead of hashing its whole history again."""
+        assert len(page_tokens) == self.page_size
+        state = hashlib.sha256(state + np.asarray(page_tokens, dtype="<i4").tobytes()).digest()
+        k = np.frombuffer(state[:16], dtype="<u8")
+        return state, (int(k[0]), int(k[1]))
+
     def match_prefix(self, keys: np.ndarray) -> list:
         """Pins and returns the pages of the longest cached leading run."""
         if not self.enable_prefix_cache or len(keys) == 0:

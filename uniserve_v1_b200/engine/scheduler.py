@@ -181,7 +181,8 @@ class Scheduler:
         prefilling = [r for r in self.running if r.num_computed < r.num_tokens - 1
                       or (not r.output_ids and r.num_computed < r.num_tokens)]
         order = self.policy.dispatch(list(self.waiting),
-                                     {"free_pages": self.blocks.num_free, "budget": budget})
+                                     {"free_pages": self.blocks.num_free, "budget": budget}) \
+            if self.waiting else []
         for req in prefilling + order:
             if budget <= 0 or len(chunks) >= cfg.max_prefill_seqs:
                 break
@@ -233,19 +234,24 @@ class Scheduler:
             if len(self.running) > 1 and self._preempt_one(protect=self.running[0]):
                 return self.schedule()
             raise RuntimeError("KV pool too small for a single request")
+        preempted = False
         for req in decoding:
-            if req not in self.running:
+            if preempted and req not in self.running:
                 continue          # preempted while making room for an earlier row
             while True:
                 need = self._pages_needed(req, req.num_tokens + cfg.decode_lookahead - 1)
+                if need == 0:
+                    break
                 pages = self.blocks.allocate(need)
                 if pages is not None:
                     req.pages.extend(pages)
                     break
+                preempted = True
                 if not self._preempt_one(protect=req):
                     raise RuntimeError("KV pool too small for a single request")
             rows.append(req)
-        rows = [r for r in rows if r in self.running]
+        if preempted:
+            rows = [r for r in rows if r in self.running]
         chunks = [Chunk(r, r.num_tokens - 1, 1, True) for r in rows]
         self.stats["decode_tokens"] += len(chunks)
         b = Batch("decode", chunks, self.step_id)
@@ -258,7 +264,16 @@ class Scheduler:
         full = req.num_computed // ps
         if full <= req.committed_pages or not self.blocks.enable_prefix_cache:
             return
-        keys = self.blocks.page_keys(req.all_ids[:full * ps], req.cache_salt)
+        # the request's key chain grows by the pages it filled (tokens only append, so the
+        # links computed so far stay valid across preemption and recompute)
+        chain = getattr(req, "_chain", None)
+        if chain is None:
+            chain = req._chain = [self.blocks.chain_seed(req.cache_salt), []]
+        keys = chain[1]
+        while len(keys) < full:
+            i = len(keys)
+            chain[0], k = self.blocks.chain_next(chain[0], req.token_slice(i * ps, (i + 1) * ps))
+            keys.append(k)
         for i in range(req.committed_pages, full):
             self.blocks.commit(req.pages[i], keys[i])
         req.committed_pages = full

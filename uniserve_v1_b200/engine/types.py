@@ -107,6 +107,15 @@ class Request:
     def num_tokens(self) -> int:
         return len(self.prompt_ids) + len(self.output_ids)
 
+    def token_slice(self, lo: int, hi: int) -> list:
+        """Tokens [lo, hi) of prompt + outputs without building the whole list."""
+        n = len(self.prompt_ids)
+        if hi <= n:
+            return self.prompt_ids[lo:hi]
+        if lo >= n:
+            return self.output_ids[lo - n:hi - n]
+        return self.prompt_ids[lo:] + self.output_ids[:hi - n]
+
     @property
     def finished(self) -> bool:
         return self.state == RequestState.FINISHED
