@@ -205,13 +205,24 @@ class CausalLmRunner:
         h["step"][0] = 0
         ids, pos, slots, temp, top_k, top_p, min_p, seeds = [], [], [], [], [], [], [], []
         pt = h["page_table"]
+        # A row of the page table is rewritten only when its request or its page list
+        # changed; a list that grew gets its new tail (page lists only ever append, and a
+        # preempted or imported request owns a new list object).
+        held = blk.__dict__.setdefault("_pt_rows", {})
         for i, req in enumerate(rows):
             p_ = req.num_tokens - 1
             ids.append(req.output_ids[-1] if req.output_ids else req.prompt_ids[-1])
             pos.append(p_)
             pages = req.pages
             slots.append(pages[p_ // ps] * ps + p_ % ps)
-            pt[i, :len(pages)] = pages
+            was = held.get(i)
+            n_p = len(pages)
+            if was is not None and was[0] is pages and was[1] <= n_p:
+                if was[1] < n_p:
+                    pt[i, was[1]:n_p] = pages[was[1]:]
+            else:
+                pt[i, :n_p] = pages
+            held[i] = (pages, n_p)
             p: SamplingParams = req.params
             greedy = p.greedy
             temp.append(1.0 if greedy else p.temperature)
