@@ -171,3 +171,26 @@ def test_chat_on_the_dense_state_engine():
         with c.stream("POST", "/v1/chat/completions", json=body) as r:
             lines = [l for l in r.iter_lines() if l.startswith("data: ")]
         assert lines[-1] == "data: [DONE]" and len(lines) >= 4
+
+
+def test_chat_with_speculative_decoding_gives_the_same_answers():
+    """`speculative_config.num_draft_tokens` turns on prompt-lookup drafting in the engine
+    loop; greedy answers are unchanged and sampled requests fall back to ordinary steps."""
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    answers = []
+    for toml in ('model = "random:tiny"\nserved_model_name = "tiny"\n',
+                 'model = "random:tiny"\nserved_model_name = "tiny"\n'
+                 '[speculative_config]\nnum_draft_tokens = 3\n'):
+        eng = LLMEngine(model, num_pages=256, max_num_seqs=8, max_model_len=512, use_graphs=False)
+        app = create_app(package=Package.parse(toml), engine=eng, tokenizer=ByteTokenizer(1024, 1023),
+                         served_model_name="tiny")
+        with TestClient(app) as c:
+            out = []
+            for extra in ({"temperature": 0}, {"temperature": 0.8, "seed": 3}):
+                body = dict({"model": "tiny", "max_tokens": 24, "ignore_eos": True,
+                             "messages": [{"role": "user", "content": "abcabcabcabc abcabc"}]}, **extra)
+                out.append(c.post("/v1/chat/completions", json=body).json()["choices"][0]["message"])
+            answers.append(out)
+            spec = eng.spec_stats
+    assert answers[0] == answers[1]
+    assert spec["steps"] > 0 and spec["proposed"] > 0

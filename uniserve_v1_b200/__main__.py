@@ -161,8 +161,13 @@ def serve(args) -> int:
         if bus is not None:
             shutdown = engine.shutdown
         # a replicated engine cannot be rebuilt on one rank alone: no in-place restart
+        drafter = None
+        k_draft = int(pkg.speculative_config.num_draft_tokens)
+        if k_draft > 0 and bus is None and directory and ld.has("mtp.fc.weight"):
+            from .models.qwen3_mtp import MtpDrafter, MtpHead     # the checkpoint's own drafter
+            drafter = MtpDrafter(MtpHead(model).load_state(ld), k=k_draft)
         app = create_app(package=pkg, engine=engine, tokenizer=tok, served_model_name=name,
-                         engine_factory=make_engine if bus is None else None)
+                         engine_factory=make_engine if bus is None else None, drafter=drafter)
     if args.ready_fd is not None:
         os.write(args.ready_fd, json.dumps({"state": "listening", "host": pkg.admin_config.host,
                                             "port": pkg.admin_config.port}).encode() + b"\n")

@@ -206,7 +206,7 @@ class AppState:
 
 def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None,
                served_model_name: str = "model", video_service=None, generation_defaults=None,
-               reasoning: bool = True, engine_factory=None) -> FastAPI:
+               reasoning: bool = True, engine_factory=None, drafter=None) -> FastAPI:
     """Builds the application.  ``engine`` (an LLMEngine) registers the chat route;
     ``video_service`` registers the video routes and ``/v1/capabilities``."""
     app = FastAPI(title="uniserve-b200", docs_url=None, redoc_url=None, openapi_url=None)
@@ -225,8 +225,15 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
     s.service = None
     if engine is not None:
         sc = s.package.scheduler_config
+        if drafter is None and s.package.speculative_config.num_draft_tokens > 0 and \
+                hasattr(engine, "speculative_step") and hasattr(engine, "scheduler"):
+            # `speculative_config.num_draft_tokens` without a drafter of the model's own:
+            # prompt-lookup drafting (single-process engines; replicated engines step plainly)
+            from ..engine.speculation import NgramDrafter
+            drafter = NgramDrafter(k=int(s.package.speculative_config.num_draft_tokens))
         s.service = EngineService(engine, s.obs, sc.max_queued_requests,
-                                  s.package.migration_config.max_migrations, engine_factory)
+                                  s.package.migration_config.max_migrations, engine_factory,
+                                  drafter=drafter)
     app.state.s = s
 
     @app.on_event("startup")

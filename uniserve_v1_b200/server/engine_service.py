@@ -25,8 +25,11 @@ class Overloaded(RuntimeError):
 
 class EngineService:
     def __init__(self, engine, observation=None, max_queued: Optional[int] = None,
-                 max_migrations: int = 3, engine_factory=None):
+                 max_migrations: int = 3, engine_factory=None, drafter=None):
         self.engine = engine
+        # speculative decoding: every step goes through the drafter when it applies
+        # (all running requests decoding greedily), an ordinary step otherwise
+        self.drafter = drafter
         self.obs = observation
         self.max_queued = max_queued
         self.max_migrations = max_migrations
@@ -169,7 +172,10 @@ class EngineService:
                 self.wake.clear()
                 continue
             try:
-                outs = self.engine.step()
+                if self.drafter is not None and hasattr(self.engine, "speculative_step"):
+                    outs = self.engine.speculative_step(self.drafter)
+                else:
+                    outs = self.engine.step()
             except Exception as e:
                 self._recover(e)
                 continue
