@@ -194,3 +194,48 @@ def test_chat_with_speculative_decoding_gives_the_same_answers():
             spec = eng.spec_stats
     assert answers[0] == answers[1]
     assert spec["steps"] > 0 and spec["proposed"] > 0
+
+
+def test_video_job_resumes_from_its_last_step_boundary():
+    """A denoising step that fails once: the job continues from the trajectory saved at the
+    previous step boundary and produces the bytes of an undisturbed run."""
+    from uniserve_v1_b200.models.h3_vae import (AudioVaeConfig, AudioVaeDecoder, VideoVaeConfig,
+                                                VideoVaeDecoder)
+    from uniserve_v1_b200.models.minimax_h3 import H3Config, H3Transformer
+    from uniserve_v1_b200.server.video_rules import plan_request
+    from uniserve_v1_b200.server.protocol import VideoGenerationRequest
+    from uniserve_v1_b200.server.video_service import VideoService
+    cfg = H3Config.tiny()
+    cfg.vae_spatial = 64
+    tr = H3Transformer(cfg, "cpu", torch.float32).init_random(0)
+    vc = VideoVaeConfig.tiny()
+    vc.latent_channels, vc.spatial = cfg.latent_channels, 64
+    vv = VideoVaeDecoder(vc, "cpu", torch.float32).init_random(1)
+    av = AudioVaeDecoder(AudioVaeConfig(latent_channels=cfg.audio_channels, decoder_dim=128,
+                                        rates=(5, 5, 2, 2, 2, 2, 2), kernels=(9, 9, 4, 4, 4, 4, 4),
+                                        res_kernels=(3,), res_dilations=(1,)), "cpu").init_random(2)
+
+    def service():
+        return VideoService(tr, vv, av, sizes=["256x256"], max_seconds=5)
+    req = VideoGenerationRequest(model="FastH3", prompt="a stream", size="256x256", seconds=4,
+                                 seed=7)
+    svc = service()
+    plan = plan_request(req, svc.sizes, svc.max_seconds, svc.steps)
+    want = svc.submit("a stream", plan)
+    want._done.wait(300)
+    assert want.state == "completed" and want.resumed_from is None and not svc.latent_pool
+    svc2 = service()
+    inner, calls = svc2.denoiser.step, {"n": 0}
+
+    def flaky(st):
+        calls["n"] += 1
+        if calls["n"] == 3:
+            raise RuntimeError("injected step failure")
+        return inner(st)
+    svc2.denoiser.step = flaky
+    job = svc2.submit("a stream", plan)
+    job._done.wait(300)
+    assert job.state == "completed", job.error
+    assert job.resumes == 1 and job.resumed_from == 2          # two steps were kept
+    assert job.content == want.content
+    assert calls["n"] == svc2.steps + 1 and not svc2.latent_pool

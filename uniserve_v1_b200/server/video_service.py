@@ -89,6 +89,8 @@ class VideoJob:
         self.error: Optional[str] = None
         self.content: Optional[bytes] = None
         self.step = 0
+        self.resumes = 0
+        self.resumed_from: Optional[int] = None
         self.cancelled = False
         self._done = threading.Event()
         self._waiters: list = []
@@ -133,6 +135,13 @@ class VideoService:
         self.max_seconds = max_seconds
         self.retention_s, self.store_bytes = retention_s, store_bytes
         self.obs = observation
+        # Host latent pool: the trajectory of every running job at its last step boundary
+        # (step index + video and audio latents, a few tens of MB), so that a job that
+        # failed or was interrupted continues from there - on this or on another layout,
+        # the latents are whole on every rank (runner/denoiser.rs:62-79, reference path).
+        self.latent_pool: OrderedDict = OrderedDict()
+        self.latent_pool_bytes = 1 << 30
+        self.max_resumes = 2
         self._jobs: OrderedDict = OrderedDict()
         self._queue: list = []
         self._cv = threading.Condition()
@@ -218,6 +227,12 @@ class VideoService:
         lf, lh, lw = cfg.latent_shape(p.num_frames, p.width, p.height)
         n_audio_rows = cfg.audio_rows(p.num_frames)
         st = self.denoiser.prepare(p.seed, lf, lh, lw, n_audio_rows, feats)
+        saved = self.latent_pool.get(job.id)
+        if saved is not None and saved["video"].shape == st.video.shape:
+            st.video.copy_(saved["video"].to(st.video.device))
+            st.audio.copy_(saved["audio"].to(st.audio.device))
+            st.step = saved["step"]
+            job.resumed_from = saved["step"]
         self._enter(job, "Denoise")
         while st.step < self.denoiser.steps:
             if job.cancelled:
@@ -225,6 +240,7 @@ class VideoService:
             self.denoiser.step(st)
             job.step = st.step
             job.progress = 0.8 * st.step / self.denoiser.steps
+            self._save_trajectory(job, st)
         self._enter(job, "VideoDecode")
         units = self.video_vae.decode(st.video, self.rank, self.world)
         planes = []
@@ -294,6 +310,32 @@ class VideoService:
             cursor[r] += n
         return torch.cat(out, 0)[:p.num_frames]
 
+    def _save_trajectory(self, job: VideoJob, st) -> None:
+        if st.step >= self.denoiser.steps:
+            self.latent_pool.pop(job.id, None)          # nothing left to resume
+            return
+        ent = {"step": st.step, "video": st.video.detach().to("cpu", copy=True),
+               "audio": st.audio.detach().to("cpu", copy=True)}
+        self.d2h_bytes += ent["video"].numel() * 4 + ent["audio"].numel() * 4
+        self.latent_pool[job.id] = ent
+        self.latent_pool.move_to_end(job.id)
+        size = lambda e: (e["video"].numel() + e["audio"].numel()) * 4
+        while sum(size(e) for e in self.latent_pool.values()) > self.latent_pool_bytes and \
+                len(self.latent_pool) > 1:
+            self.latent_pool.popitem(last=False)
+
+    def resume(self, job_id: str) -> bool:
+        """Queues a failed job again; it continues from its last saved step boundary."""
+        with self._cv:
+            job = self._jobs.get(job_id)
+            if job is None or job.state != "failed" or job.cancelled:
+                return False
+            job.state, job.error, job.completed_at = "queued", None, None
+            job._done.clear()
+            self._queue.append(job)
+            self._cv.notify_all()
+        return True
+
     def _run(self):
         while True:
             with self._cv:
@@ -312,6 +354,14 @@ class VideoService:
                     self.obs.observe("uniserve_video_seconds", time.monotonic() - t0)
                     self.obs.inc("uniserve_requests_total", {"outcome": "completed"})
             except Exception as e:
+                # a failure inside the trajectory is retried from the last boundary
+                if not job.cancelled and job.id in self.latent_pool and \
+                        job.resumes < self.max_resumes:
+                    job.resumes += 1
+                    with self._cv:
+                        self._queue.insert(0, job)
+                    continue
+                self.latent_pool.pop(job.id, None)
                 job.finish("failed", str(e))
                 if self.obs:
                     self.obs.inc("uniserve_requests_total", {"outcome": "failed"})
