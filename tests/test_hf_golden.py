@@ -268,3 +268,62 @@ def test_decoder_as_text_encoder_matches_transformers_hidden_states(tmp_path):
     assert a.shape == (len(ByteTokenizer(512, 511).encode("a sunset over water")), 64)
     assert enc.encode("a sunset over water", "cpu") is not None and len(enc.cache) == 1
     torch.testing.assert_close(a, model.encode(ByteTokenizer(512, 511).encode("a sunset over water"), 2))
+
+
+def test_qwen3_5_multimodal_prompt_matches_transformers(tmp_path):
+    """Image rows from the vision tower spliced at the placeholder tokens, three-axis
+    interleaved rotary positions, then greedy decoding: a tiny random
+    `Qwen3_5MoeForConditionalGeneration`."""
+    import pytest
+    pytest.importorskip("transformers")
+    from transformers.models.qwen3_5_moe.configuration_qwen3_5_moe import (
+        Qwen3_5MoeConfig, Qwen3_5MoeTextConfig, Qwen3_5MoeVisionConfig)
+    from transformers.models.qwen3_5_moe.modeling_qwen3_5_moe import \
+        Qwen3_5MoeForConditionalGeneration
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, save_file
+    from uniserve_v1_b200.models.qwen3_5 import (Qwen35Config, Qwen35MoeModel, Qwen35Multimodal,
+                                                 mrope_positions)
+    from uniserve_v1_b200.models.qwen3_vl_vision import Qwen3VLVisionTower, VisionConfig
+    tc = Qwen3_5MoeTextConfig(
+        vocab_size=300, hidden_size=64, num_hidden_layers=4, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=32, linear_num_key_heads=2, linear_num_value_heads=4,
+        linear_key_head_dim=16, linear_value_head_dim=16, num_experts=8, num_experts_per_tok=2,
+        moe_intermediate_size=32, shared_expert_intermediate_size=48, max_position_embeddings=256,
+        layer_types=["linear_attention", "full_attention", "linear_attention", "full_attention"],
+        rope_parameters={"rope_type": "default", "rope_theta": 10000.0,
+                         "partial_rotary_factor": 0.25, "mrope_section": [2, 1, 1],
+                         "mrope_interleaved": True})
+    vc = Qwen3_5MoeVisionConfig(depth=2, hidden_size=32, intermediate_size=48, num_heads=2,
+                                patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+                                out_hidden_size=64, num_position_embeddings=16)
+    cfg = Qwen3_5MoeConfig(text_config=tc.to_dict(), vision_config=vc.to_dict(),
+                           image_token_id=290, video_token_id=291, vision_start_token_id=292,
+                           vision_end_token_id=293)
+    torch.manual_seed(0)
+    hf = Qwen3_5MoeForConditionalGeneration(cfg).float().eval()
+    save_file({k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()},
+              tmp_path / "model.safetensors")
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_dict()))
+    ld = CheckpointLoader(tmp_path)
+    tcfg = Qwen35Config.from_hf(ld.config)
+    assert tcfg.mrope_section == (2, 1, 1) and tcfg.image_token_id == 290
+    text = Qwen35MoeModel(tcfg, "cpu", torch.float32).load_state(ld)
+    tower = Qwen3VLVisionTower(VisionConfig.from_hf({**ld.config["vision_config"],
+                                                      "deepstack_visual_indexes": []}),
+                               "cpu", torch.float32).load_state(ld)
+    grid = (1, 4, 6)                                   # 24 patches -> 6 merged rows
+    prompt = [5, 17, 292] + [290] * 6 + [293, 40, 41, 7]
+    pixels = torch.randn(24, 3 * 2 * 4 * 4, generator=torch.Generator().manual_seed(1))
+    types = torch.tensor([[1 if t == 290 else 0 for t in prompt]])
+    pos3, nxt = mrope_positions(prompt, 290, [grid], 2)
+    assert pos3[:, 3].tolist() == [3, 3, 3] and pos3[:, 8].tolist() == [3, 4, 5] and nxt == 10
+    with torch.no_grad():
+        out = hf(input_ids=torch.tensor([prompt]), pixel_values=pixels,
+                 image_grid_thw=torch.tensor([grid]), mm_token_type_ids=types)
+        gen = hf.generate(input_ids=torch.tensor([prompt]), pixel_values=pixels,
+                          image_grid_thw=torch.tensor([grid]), mm_token_type_ids=types,
+                          max_new_tokens=5, do_sample=False)[0, len(prompt):].tolist()
+    mm = Qwen35Multimodal(text, tower)
+    logits, _ = mm.prefill(prompt, pixels, [grid], text.new_state())
+    torch.testing.assert_close(logits, out.logits[0], atol=3e-4, rtol=2e-3)
+    assert mm.generate(prompt, pixels, [grid], 5) == gen

@@ -54,9 +54,13 @@ class Qwen35Config:
     moe_intermediate_size: int = 512
     shared_expert_intermediate_size: int = 512
     eos_token_id: int = 0
+    mrope_section: tuple = (11, 11, 10)     # rotary frequencies owned by (t, h, w), interleaved
+    image_token_id: int = 248056
+    video_token_id: int = 248057
 
     @classmethod
     def from_hf(cls, d: dict) -> "Qwen35Config":
+        outer = d
         d = d.get("text_config", d)
         rp = d.get("rope_parameters") or {}
         keys = {f for f in cls.__dataclass_fields__}
@@ -64,6 +68,10 @@ class Qwen35Config:
         kw["rope_theta"] = float(rp.get("rope_theta", d.get("rope_theta", 1e7)))
         kw["partial_rotary_factor"] = float(rp.get("partial_rotary_factor",
                                                    d.get("partial_rotary_factor", 0.25)))
+        kw["mrope_section"] = tuple(rp.get("mrope_section", (11, 11, 10)))
+        for k in ("image_token_id", "video_token_id"):
+            if outer.get(k) is not None:
+                kw[k] = int(outer[k])
         cfg = cls(**kw)
         if not cfg.layer_types:
             every = int(d.get("full_attention_interval", 4))
@@ -186,7 +194,24 @@ class Qwen35MoeModel:
     def new_state(self) -> list:
         return [LayerState() for _ in self.cfg.layer_types]
 
-    def _attention(self, L, n, st: LayerState, pos0: int):
+    def _norm_mrope(self, x, w, pos3):
+        """Per-head RMSNorm, then rotary embedding whose frequency j turns with the temporal,
+        row or column position according to the interleaved sections (t h w t h w ... t t)."""
+        c = self.cfg
+        xf = x.float()
+        xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + c.rms_norm_eps) * w.float()
+        nf = self.rot // 2
+        axis = torch.zeros(nf, dtype=torch.long, device=x.device)
+        for a, off in ((1, 1), (2, 2)):
+            axis[off:c.mrope_section[a] * 3:3] = a
+        ang = pos3.to(x.device).float()[axis, :].t() * self.inv_freq.float()[None, :]     # [T, nf]
+        cos = torch.cat([ang.cos(), ang.cos()], -1)[:, None, :]
+        sin = torch.cat([ang.sin(), ang.sin()], -1)[:, None, :]
+        rot = xf[..., :self.rot]
+        turned = torch.cat([-rot[..., nf:], rot[..., :nf]], -1)
+        return torch.cat([rot * cos + turned * sin, xf[..., self.rot:]], -1).to(x.dtype)
+
+    def _attention(self, L, n, st: LayerState, pos0: int, pos3=None):
         c, D = self.cfg, self.cfg.head_dim
         T = n.shape[0]
         Hq, Hkv = c.num_attention_heads, c.num_key_value_heads
@@ -195,8 +220,11 @@ class Qwen35MoeModel:
         k = F.linear(n, L["k"]).view(T, Hkv, D)
         v = F.linear(n, L["v"]).view(T, Hkv, D)
         pos = torch.arange(pos0, pos0 + T, device=n.device)
-        q, k = R.qk_norm_rope(q.contiguous(), k, L["q_norm"], L["k_norm"], pos, self.inv_freq,
-                              self.rot, False, c.rms_norm_eps)
+        if pos3 is None:
+            q, k = R.qk_norm_rope(q.contiguous(), k, L["q_norm"], L["k_norm"], pos, self.inv_freq,
+                                  self.rot, False, c.rms_norm_eps)
+        else:
+            q, k = self._norm_mrope(q, L["q_norm"], pos3), self._norm_mrope(k, L["k_norm"], pos3)
         st.k = k if st.k is None else torch.cat([st.k, k], 0)
         st.v = v if st.v is None else torch.cat([st.v, v], 0)
         rep = Hq // Hkv
@@ -204,7 +232,8 @@ class Qwen35MoeModel:
         V = st.v.float().repeat_interleave(rep, 1)
         s = torch.einsum("thd,nhd->htn", q.float(), K) / math.sqrt(D)
         n_ctx = K.shape[0]
-        mask = torch.arange(n_ctx, device=n.device)[None, :] > (pos[:, None])
+        seq = torch.arange(n_ctx - T, n_ctx, device=n.device)         # sequence index of each row
+        mask = torch.arange(n_ctx, device=n.device)[None, :] > (seq[:, None])
         s = s.masked_fill(mask[None], float("-inf"))
         att = torch.einsum("htn,nhd->thd", s.softmax(-1), V).reshape(T, Hq * D)
         att = (att * torch.sigmoid(gate.float())).to(n.dtype)
@@ -240,15 +269,19 @@ class Qwen35MoeModel:
         sg = torch.sigmoid(F.linear(n, L["sgate"], out_dtype=torch.float32))
         return y + (shared.float() * sg).to(n.dtype)
 
-    def forward(self, ids: torch.Tensor, state: list, pos0: int = 0) -> torch.Tensor:
+    def forward(self, ids: torch.Tensor, state: list, pos0: int = 0, embeds=None,
+                positions3=None) -> torch.Tensor:
         """Runs ``ids`` [T] at positions pos0 .. on top of ``state``; returns FP32 logits
-        [T, vocab]."""
+        [T, vocab].  ``embeds`` [T, hidden] replaces the embedding lookup (vision rows spliced
+        in); ``positions3`` [3, T] are the (temporal, row, column) rotary positions of a
+        multimodal prompt (text tokens carry the same value on all three)."""
         c, w = self.cfg, self.w
-        x = w["embed"][ids.to(self.device).long()]
+        x = w["embed"][ids.to(self.device).long()] if embeds is None else \
+            embeds.to(device=self.device, dtype=self.dtype)
         for i in range(c.num_hidden_layers):
             L, st = w[i], state[i]
             n = R.rmsnorm(x, L["in_norm"], c.rms_norm_eps)
-            mix = self._attention(L, n, st, pos0) if L["kind"] == "full_attention" \
+            mix = self._attention(L, n, st, pos0, positions3) if L["kind"] == "full_attention" \
                 else self._linear_attention(L, n, st)
             x = x + mix
             n = R.rmsnorm(x, L["post_norm"], c.rms_norm_eps)
@@ -270,5 +303,67 @@ class Qwen35MoeModel:
             if tok == self.cfg.eos_token_id:
                 break
             logits = self.forward(torch.tensor([tok], device=self.device), state, pos)
+            pos += 1
+        return out
+
+
+def mrope_positions(input_ids, image_token_id: int, grids: list, merge: int, start: int = 0):
+    """Rotary positions of a prompt with images: text tokens advance all three axes together;
+    the merged patches of an image (t, h, w) keep the temporal value of the image's start and
+    count rows / columns from it; the text after an image continues at start + max(h, w) / merge.
+    Returns (positions [3, T], next position)."""
+    ids = input_ids.tolist() if hasattr(input_ids, "tolist") else list(input_ids)
+    cols, cur, i, g = [], start, 0, iter(grids)
+    while i < len(ids):
+        if ids[i] != image_token_id:
+            cols.append(torch.tensor([[cur], [cur], [cur]]))
+            cur += 1
+            i += 1
+            continue
+        t, h, w = next(g)
+        gh, gw = h // merge, w // merge
+        n = t * gh * gw
+        assert all(x == image_token_id for x in ids[i:i + n]), "placeholders do not cover the image"
+        hh = torch.arange(cur, cur + gh).repeat_interleave(gw * t)
+        ww = torch.arange(cur, cur + gw).repeat(gh * t)
+        cols.append(torch.stack([torch.full((n,), cur), hh, ww]))
+        cur += max(h, w) // merge
+        i += n
+    return torch.cat(cols, 1), cur
+
+
+class Qwen35Multimodal:
+    """The hybrid decoder with the vision tower in front: image rows replace the
+    placeholder tokens of the prompt, positions are the three-axis ones, decoding continues
+    on all axes from where the prompt ended (``Qwen3_5MoeForConditionalGeneration``)."""
+
+    def __init__(self, text: Qwen35MoeModel, tower):
+        self.text, self.tower = text, tower
+
+    def prefill(self, prompt_ids: list, pixels, grids: list, state: list):
+        """Returns (logits [T, vocab], next rotary position)."""
+        c = self.text.cfg
+        ids = torch.tensor(prompt_ids, device=self.text.device)
+        emb = self.text.w["embed"][ids.long()]
+        if pixels is not None:
+            from .qwen3_vl_vision import splice
+            rows, _ = self.tower.forward(pixels, grids)
+            emb = splice(emb, ids, c.image_token_id, rows)
+        pos3, nxt = mrope_positions(prompt_ids, c.image_token_id, grids or [],
+                                    self.tower.cfg.spatial_merge_size)
+        return self.text.forward(ids, state, 0, embeds=emb, positions3=pos3), nxt
+
+    def generate(self, prompt_ids: list, pixels, grids: list, max_tokens: int) -> list:
+        state = self.text.new_state()
+        logits, pos = self.prefill(prompt_ids, pixels, grids, state)
+        out = []
+        for _ in range(max_tokens):
+            tok = int(logits[-1].argmax())
+            out.append(tok)
+            if tok == self.text.cfg.eos_token_id:
+                break
+            p3 = torch.full((3, 1), pos)
+            logits = self.text.forward(torch.tensor([tok], device=self.text.device), state, 0,
+                                       positions3=p3)
             pos += 1
         return out
