@@ -327,3 +327,38 @@ def test_qwen3_5_multimodal_prompt_matches_transformers(tmp_path):
     logits, _ = mm.prefill(prompt, pixels, [grid], text.new_state())
     torch.testing.assert_close(logits, out.logits[0], atol=3e-4, rtol=2e-3)
     assert mm.generate(prompt, pixels, [grid], 5) == gen
+
+
+def test_image_preprocessing_matches_the_transformers_processor():
+    """Patch rows and grids of the Qwen-VL image processor for an image that needs no
+    resize (exact) and one that does (same grid, close values: resampling filters differ)."""
+    import io
+    import base64
+    import numpy as np
+    import pytest
+    from PIL import Image
+    from transformers.models.qwen2_vl.image_processing_qwen2_vl import Qwen2VLImageProcessor
+    from uniserve_v1_b200.server import images as IM
+    proc = Qwen2VLImageProcessor(patch_size=16, temporal_patch_size=2, merge_size=2,
+                                 min_pixels=64 * 64, max_pixels=1280 * 28 * 28,
+                                 image_mean=[0.5, 0.5, 0.5], image_std=[0.5, 0.5, 0.5])
+    rng = np.random.RandomState(0)
+    exact = rng.randint(0, 256, (96, 160, 3), dtype=np.uint8)
+    want = proc(images=[Image.fromarray(exact)], return_tensors="pt")
+    rows, grid = IM.preprocess(exact)
+    assert list(grid) == want["image_grid_thw"][0].tolist() == [1, 6, 10]
+    torch.testing.assert_close(rows, want["pixel_values"], atol=1e-6, rtol=0)
+    odd = rng.randint(0, 256, (75, 131, 3), dtype=np.uint8)
+    want = proc(images=[Image.fromarray(odd)], return_tensors="pt")
+    rows, grid = IM.preprocess(odd)
+    assert list(grid) == want["image_grid_thw"][0].tolist()
+    assert float((rows - want["pixel_values"]).abs().mean()) < 0.05
+    buf = io.BytesIO()
+    Image.fromarray(exact).save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    assert np.array_equal(IM.load_image(url), exact)
+    with pytest.raises(ValueError):
+        IM.load_image("https://example.com/cat.png")
+    assert IM.expand_placeholders([1, 9, 2], 9, [(1, 6, 10)], 2) == [1] + [9] * 15 + [2]
+    assert IM.collect([{"role": "user", "content": [{"type": "text", "text": "hi"},
+                                                    {"type": "image_url", "image_url": {"url": url}}]}]) == [url]

@@ -239,3 +239,77 @@ def test_video_job_resumes_from_its_last_step_boundary():
     assert job.resumes == 1 and job.resumed_from == 2          # two steps were kept
     assert job.content == want.content
     assert calls["n"] == svc2.steps + 1 and not svc2.latent_pool
+
+
+def test_chat_with_an_image_on_the_hybrid_family():
+    """An `image_url` part (data URL) is decoded, cut into patch rows, run through the vision
+    tower and spliced into the prompt; the answer is the model's own multimodal decoding.
+    A deployment without a tower refuses images."""
+    import base64
+    import io
+    import numpy as np
+    from PIL import Image
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel, Qwen35Multimodal
+    from uniserve_v1_b200.models.qwen3_vl_vision import Qwen3VLVisionTower, VisionConfig
+    from uniserve_v1_b200.server import images as IM
+    cfg = Qwen35MoeModel.tiny_config()
+    cfg.mrope_section, cfg.image_token_id = (2, 1, 1), 1000
+    model = Qwen35MoeModel(cfg, "cpu", torch.float32).init_random(seed=0)
+    vc = VisionConfig(depth=2, hidden_size=32, intermediate_size=48, num_heads=2, patch_size=16,
+                      temporal_patch_size=2, spatial_merge_size=2, out_hidden_size=64,
+                      num_position_embeddings=16, deepstack_visual_indexes=[])
+    tower = Qwen3VLVisionTower(vc, "cpu", torch.float32)
+    g = torch.Generator().manual_seed(1)
+
+    class Rand:
+        def names(self): return ["patch_embed.proj.weight"]
+        def get(self, n):
+            shapes = {"patch_embed.proj.weight": (32, 3, 2, 16, 16), "patch_embed.proj.bias": (32,),
+                      "pos_embed.weight": (16, 32)}
+            if n in shapes:
+                return torch.randn(*shapes[n], generator=g) * 0.05
+            wide = 32 * 4
+            dims = {"attn.qkv.weight": (96, 32), "attn.qkv.bias": (96,), "attn.proj.weight": (32, 32),
+                    "attn.proj.bias": (32,), "mlp.linear_fc1.weight": (48, 32),
+                    "mlp.linear_fc1.bias": (48,), "mlp.linear_fc2.weight": (32, 48),
+                    "mlp.linear_fc2.bias": (32,), "merger.norm.weight": (32,), "merger.norm.bias": (32,),
+                    "merger.linear_fc1.weight": (wide, wide), "merger.linear_fc1.bias": (wide,),
+                    "merger.linear_fc2.weight": (64, wide), "merger.linear_fc2.bias": (64,)}
+            for k, shp in dims.items():
+                if n.endswith(k):
+                    return torch.randn(*shp, generator=g) * 0.05
+            return torch.ones(32) if n.endswith("weight") else torch.zeros(32)     # block norms
+    tower.load_state(Rand(), prefix="")
+    eng = DenseStateEngine(model, max_num_seqs=4, max_model_len=512, tower=tower)
+    pkg = Package.parse('model = "random:tiny"\nserved_model_name = "hybrid"\n')
+    tok = ByteTokenizer(1024, 1023)
+    app = create_app(package=pkg, engine=eng, tokenizer=tok, served_model_name="hybrid")
+    img = np.random.RandomState(0).randint(0, 256, (64, 96, 3), dtype=np.uint8)
+    buf = io.BytesIO()
+    Image.fromarray(img).save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    body = {"model": "hybrid", "max_tokens": 5, "temperature": 0, "ignore_eos": True,
+            "messages": [{"role": "user", "content": [{"type": "text", "text": "what is this? "},
+                                                      {"type": "image_url", "image_url": {"url": url}}]}]}
+    with TestClient(app) as c:
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200, r.text
+        got = r.json()
+        n_img = (64 // 32) * (96 // 32)
+        assert got["usage"]["completion_tokens"] == 5
+        # the same prompt decoded by the model directly
+        rows, grid = IM.preprocess(img)
+        rid = next(iter(eng.requests))
+        prompt_ids = eng.requests[rid].prompt_ids
+        assert prompt_ids.count(1000) == n_img and got["usage"]["prompt_tokens"] == len(prompt_ids)
+        want = Qwen35Multimodal(model, tower).generate(prompt_ids, rows, [grid], 5)
+        assert eng.requests[rid].output_ids == want
+        bad = dict(body, messages=[{"role": "user", "content": [
+            {"type": "image_url", "image_url": {"url": "https://example.com/x.png"}}]}])
+        assert c.post("/v1/chat/completions", json=bad).status_code == 400
+    plain = create_app(package=pkg, engine=DenseStateEngine(model), tokenizer=tok,
+                       served_model_name="hybrid")
+    with TestClient(plain) as c:
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 400 and "images" in r.json()["error"]["message"]

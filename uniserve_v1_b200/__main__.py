@@ -104,10 +104,16 @@ def serve(args) -> int:
         cfg = Qwen35Config.from_hf(ld.config)
         model = Qwen35MoeModel(cfg, device, dtype).load_state(ld)
 
+        tower = None
+        if any(n.startswith("model.visual.") for n in ld.names()):      # image inputs
+            from .models.qwen3_vl_vision import Qwen3VLVisionTower, VisionConfig
+            tower = Qwen3VLVisionTower(VisionConfig.from_hf(ld.config), device,
+                                       dtype).load_state(ld)
+
         def make_engine():
             return DenseStateEngine(model, max_num_seqs=min(pkg.max_running_requests,
                                                             pkg.scheduler_config.max_batch),
-                                    max_model_len=pkg.max_model_len or 8192)
+                                    max_model_len=pkg.max_model_len or 8192, tower=tower)
         tok = load_tokenizer(directory, cfg.vocab_size, cfg.eos_token_id)
         app = create_app(package=pkg, engine=make_engine(), tokenizer=tok,
                          served_model_name=name, engine_factory=make_engine)

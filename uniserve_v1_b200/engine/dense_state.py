@@ -43,8 +43,13 @@ class _NoPages:
 
 class DenseStateEngine:
     def __init__(self, model, max_num_seqs: int = 8, max_model_len: int = 4096,
-                 prefill_chunk: int = 512):
+                 prefill_chunk: int = 512, tower=None):
         self.model = model
+        # with a vision tower requests may carry images: (patch rows, grids) in ``media``
+        self.mm = None
+        if tower is not None:
+            from ..models.qwen3_5 import Qwen35Multimodal
+            self.mm = Qwen35Multimodal(model, tower)
         self.config = DenseStateConfig(max_num_seqs, max_model_len, prefill_chunk)
         self.blocks = _NoPages()
         self.failed: Optional[str] = None
@@ -59,7 +64,8 @@ class DenseStateEngine:
     # ------------------------------------------------------------- requests --
     def add_request(self, prompt_ids, params: Optional[SamplingParams] = None,
                     request_id: Optional[str] = None, priority: int = 0,
-                    cache_salt: Optional[str] = None, output_ids: Optional[list] = None) -> str:
+                    cache_salt: Optional[str] = None, output_ids: Optional[list] = None,
+                    media=None) -> str:
         rid = request_id or f"req-{next(self._ids)}"
         V = self.model.cfg.vocab_size
         if not prompt_ids:
@@ -73,6 +79,16 @@ class DenseStateEngine:
                       cache_salt=cache_salt)
         if output_ids:                      # a resumed request recomputes its state
             req.output_ids = list(output_ids)
+        if media is not None:
+            if self.mm is None:
+                raise ValueError("input_error: this deployment does not take images")
+            pixels, grids = media
+            m = self.mm.tower.cfg.spatial_merge_size
+            want = sum(t * (h // m) * (w // m) for t, h, w in grids)
+            have = sum(1 for t in prompt_ids if t == self.model.cfg.image_token_id)
+            if want != have or pixels.shape[0] != sum(t * h * w for t, h, w in grids):
+                raise ValueError("input_error: image placeholders do not match the images")
+            req.media = (pixels, [tuple(g) for g in grids])
         self.requests[rid] = req
         self.waiting.append(req)
         return rid
@@ -112,6 +128,30 @@ class DenseStateEngine:
             torch.tensor([req.num_tokens], dtype=torch.int64, device=dev))
         return int(tok[0])
 
+    def _forward_media(self, req: Request, chunk: torch.Tensor, st: list, n: int):
+        """A chunk of a request with images: vision rows stand at the placeholder tokens and
+        positions are the three-axis ones; tokens after the prompt continue on all axes."""
+        from ..models.qwen3_5 import mrope_positions
+        from ..models.qwen3_vl_vision import splice
+        cfg = self.model.cfg
+        if not hasattr(req, "_mm"):
+            pixels, grids = req.media
+            ids = torch.tensor(req.prompt_ids, device=self.model.device)
+            rows, _ = self.mm.tower.forward(pixels, grids)
+            emb = splice(self.model.w["embed"][ids.long()], ids, cfg.image_token_id, rows)
+            pos3, nxt = mrope_positions(req.prompt_ids, cfg.image_token_id, grids,
+                                        self.mm.tower.cfg.spatial_merge_size)
+            req._mm = (emb, pos3, nxt - len(req.prompt_ids))
+        emb, pos3, delta = req._mm
+        lo, hi, P = req.num_computed, req.num_computed + n, len(req.prompt_ids)
+        e = self.model.w["embed"][chunk.long()]
+        p = (torch.arange(lo, hi) + delta)[None].expand(3, -1).clone()
+        if lo < P:
+            k = min(hi, P) - lo
+            e = torch.cat([emb[lo:lo + k], e[k:]], 0)
+            p[:, :k] = pos3[:, lo:lo + k]
+        return self.model.forward(chunk, st, lo, embeds=e, positions3=p)
+
     def _stop(self, req: Request, tok: int) -> Optional[FinishReason]:
         p = req.params
         if not p.ignore_eos and tok == getattr(self.model.cfg, "eos_token_id", -1):
@@ -137,7 +177,10 @@ class DenseStateEngine:
             todo = len(ids) - req.num_computed
             n = min(todo, self.config.prefill_chunk)
             chunk = torch.tensor(ids[req.num_computed:req.num_computed + n], device=dev)
-            logits = self.model.forward(chunk, st, req.num_computed)
+            if getattr(req, "media", None) is not None:
+                logits = self._forward_media(req, chunk, st, n)
+            else:
+                logits = self.model.forward(chunk, st, req.num_computed)
             req.num_computed += n
             self._stats["decode_tokens" if (n == 1 and req.output_ids) else "prefill_tokens"] += n
             if req.num_computed < len(ids):

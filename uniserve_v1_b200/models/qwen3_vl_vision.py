@@ -47,7 +47,9 @@ class VisionConfig:
     @classmethod
     def from_hf(cls, d: dict) -> "VisionConfig":
         d = d.get("vision_config", d)
-        return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+        kw = {k: v for k, v in d.items() if k in cls.__dataclass_fields__ and v is not None}
+        kw.setdefault("deepstack_visual_indexes", [])      # absent: a tower without deep stack
+        return cls(**kw)
 
 
 def _gelu(x, tanh: bool):

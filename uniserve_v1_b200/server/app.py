@@ -371,7 +371,32 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
                 prompt = s.template.render(msgs, tools, True, **(req.chat_template_kwargs or {}))
             except Exception as e:
                 return _err(400, f"chat template: {e}", param="messages")
-            ids = s.tokenizer.encode(prompt)
+            media = None
+            from . import images as IM
+            urls = IM.collect(msgs)
+            if urls:
+                mm = getattr(s.engine, "mm", None)
+                if mm is None:
+                    return _err(400, "this deployment does not take images", param="messages")
+                try:
+                    vc = mm.tower.cfg
+                    pre = [IM.preprocess(IM.load_image(u), vc.patch_size, vc.temporal_patch_size,
+                                         vc.spatial_merge_size) for u in urls]
+                except ValueError as e:
+                    return _err(400, str(e), param="messages")
+                grids = [g for _, g in pre]
+                img_tok = s.engine.model.cfg.image_token_id
+                ids = []
+                pieces = prompt.split("<|image_pad|>")
+                for i, piece in enumerate(pieces):
+                    ids.extend(s.tokenizer.encode(piece))
+                    if i < len(pieces) - 1:
+                        ids.append(img_tok)
+                ids = IM.expand_placeholders(ids, img_tok, grids, vc.spatial_merge_size)
+                import torch as _torch
+                media = (_torch.cat([r for r, _ in pre]), grids)
+            else:
+                ids = s.tokenizer.encode(prompt)
             max_len = s.engine.config.max_model_len
             if len(ids) + 1 > max_len:
                 return _err(400, f"the prompt has {len(ids)} tokens; the context holds {max_len}",
@@ -384,7 +409,7 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
             try:
                 rid, q = s.service.submit(ids, params, "chatcmpl-" + request.state.request_id,
                                           req.priority or 0, req.cache_salt or req.prompt_cache_key,
-                                          lend=role == "prefill", handoff=handoff)
+                                          lend=role == "prefill", handoff=handoff, media=media)
             except Overloaded as e:
                 return _err(503, str(e), "overloaded", headers={"Retry-After": "1"})
             run = ChatRun(s, req, rid, len(ids))

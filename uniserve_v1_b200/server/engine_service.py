@@ -60,7 +60,7 @@ class EngineService:
     # ------------------------------------------------------------ submission --
     def submit(self, prompt_ids, params: SamplingParams, request_id: Optional[str] = None,
                priority: int = 0, cache_salt: Optional[str] = None, lend: bool = False,
-               handoff=None):
+               handoff=None, media=None):
         """Returns (request_id, asyncio.Queue of StepOutput); call from an event loop.
         ``lend``: the request leaves after its first token - its stream ends with an output
         that carries the framed state (prefill role).  ``handoff``: continue a request that
@@ -75,13 +75,14 @@ class EngineService:
             self.meta[rid] = {"arrival": time.monotonic(), "first": None, "tokens": 0,
                               "prompt": list(prompt_ids), "params": params, "outputs": [],
                               "migrations": 0, "priority": priority, "salt": cache_salt,
-                              "lend": lend}
+                              "lend": lend, "media": media}
         if handoff is not None:
             handoff.request_id = rid
             self.meta[rid]["outputs"] = list(handoff.output_ids)
             self.inbox.put(("import", rid, handoff))
         else:
-            self.inbox.put(("add", rid, list(prompt_ids), params, priority, cache_salt, None))
+            self.inbox.put(("add", rid, list(prompt_ids), params, priority, cache_salt, None,
+                            media))
         self.wake.set()
         return rid, q
 
@@ -139,7 +140,7 @@ class EngineService:
                                          error=f"migrated more than {self.max_migrations} times"))
                 continue
             self.inbox.put(("add", rid, m["prompt"], m["params"], m["priority"], m["salt"],
-                            list(m["outputs"])))
+                            list(m["outputs"]), m.get("media")))
         if self.obs:
             self.obs.inc("uniserve_engine_restarts_total")
 
@@ -149,10 +150,11 @@ class EngineService:
                 while True:
                     msg = self.inbox.get_nowait()
                     if msg[0] == "add":
-                        _, rid, ids, params, prio, salt, outputs = msg
+                        _, rid, ids, params, prio, salt, outputs, media = msg
                         try:
+                            extra = {"media": media} if media is not None else {}
                             self.engine.add_request(ids, params, request_id=rid, priority=prio,
-                                                    cache_salt=salt, output_ids=outputs)
+                                                    cache_salt=salt, output_ids=outputs, **extra)
                         except Exception as e:      # input_error rejects the request
                             self._deliver(StepOutput(rid, [], True, FinishReason.ERROR, error=str(e)))
                     elif msg[0] == "import":
