@@ -362,3 +362,62 @@ def test_image_preprocessing_matches_the_transformers_processor():
     assert IM.expand_placeholders([1, 9, 2], 9, [(1, 6, 10)], 2) == [1] + [9] * 15 + [2]
     assert IM.collect([{"role": "user", "content": [{"type": "text", "text": "hi"},
                                                     {"type": "image_url", "image_url": {"url": url}}]}]) == [url]
+
+
+def test_qwen3_vl_with_deepstack_matches_transformers(tmp_path):
+    """Dense Qwen3-VL: three-axis rotary positions over the whole head, vision rows at the
+    placeholders, deep-stack rows added after the first layers; logits and greedy decoding of a
+    tiny random `Qwen3VLForConditionalGeneration`, and the dense-state engine on the same
+    request with its prompt read in chunks."""
+    import pytest
+    pytest.importorskip("transformers")
+    from transformers.models.qwen3_vl.configuration_qwen3_vl import (Qwen3VLConfig,
+                                                                     Qwen3VLTextConfig as HfText,
+                                                                     Qwen3VLVisionConfig)
+    from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLForConditionalGeneration
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, save_file
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35Multimodal
+    from uniserve_v1_b200.models.qwen3_vl import Qwen3VLDenseModel, Qwen3VLTextConfig
+    from uniserve_v1_b200.models.qwen3_vl_vision import Qwen3VLVisionTower, VisionConfig
+    tc = HfText(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=3,
+                num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                max_position_embeddings=256, eos_token_id=299,
+                rope_parameters={"rope_type": "default", "rope_theta": 10000.0,
+                                 "mrope_section": [4, 2, 2], "mrope_interleaved": True})
+    vc = Qwen3VLVisionConfig(depth=3, hidden_size=32, intermediate_size=48, num_heads=2,
+                             patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+                             out_hidden_size=64, num_position_embeddings=16,
+                             deepstack_visual_indexes=[0, 2])
+    cfg = Qwen3VLConfig(text_config=tc.to_dict(), vision_config=vc.to_dict(), image_token_id=290,
+                        video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    torch.manual_seed(0)
+    hf = Qwen3VLForConditionalGeneration(cfg).float().eval()
+    save_file({k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()},
+              tmp_path / "model.safetensors")
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_dict()))
+    ld = CheckpointLoader(tmp_path)
+    tcfg = Qwen3VLTextConfig.from_hf(ld.config)
+    assert tcfg.mrope_section == (4, 2, 2) and tcfg.image_token_id == 290
+    text = Qwen3VLDenseModel(tcfg, "cpu", torch.float32).load_state(ld)
+    tower = Qwen3VLVisionTower(VisionConfig.from_hf(ld.config), "cpu", torch.float32).load_state(ld)
+    grid = (1, 4, 6)
+    prompt = [5, 17, 292] + [290] * 6 + [293, 40, 41, 7]
+    pixels = torch.randn(24, 3 * 2 * 4 * 4, generator=torch.Generator().manual_seed(1))
+    types = torch.tensor([[1 if t == 290 else 0 for t in prompt]])
+    kw = dict(input_ids=torch.tensor([prompt]), pixel_values=pixels,
+              image_grid_thw=torch.tensor([grid]), mm_token_type_ids=types)
+    with torch.no_grad():
+        want = hf(**kw).logits[0]
+        gen = hf.generate(**kw, max_new_tokens=5, do_sample=False)[0, len(prompt):].tolist()
+    mm = Qwen35Multimodal(text, tower)
+    logits, _ = mm.prefill(prompt, pixels, [grid], text.new_state())
+    torch.testing.assert_close(logits, want, atol=3e-4, rtol=2e-3)
+    assert mm.generate(prompt, pixels, [grid], 5) == gen
+    eng = DenseStateEngine(text, prefill_chunk=5, tower=tower)
+    rid = eng.add_request(prompt, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True),
+                          media=(pixels, [grid]))
+    while eng.has_work():
+        eng.step()
+    assert eng.requests[rid].output_ids == gen

@@ -93,16 +93,22 @@ def serve(args) -> int:
         if bus is not None:
             shutdown = MR.ReplicatedVideoService(service, bus).shutdown
         app = create_app(package=pkg, served_model_name=name, video_service=service)
-    elif family == "qwen3_5_moe":
-        # hybrid decoder (gated delta net + gated attention): dense per-sequence state
+    elif family in ("qwen3_5_moe", "qwen3_vl"):
+        # hybrid decoder (gated delta net + gated attention) or the dense Qwen3-VL language
+        # model (three-axis positions, deep-stack inputs): dense per-sequence state
         from .checkpoint.quantized import open_checkpoint
         from .engine.dense_state import DenseStateEngine
-        from .models.qwen3_5 import Qwen35Config, Qwen35MoeModel
         from .server.tokenizer import load_tokenizer
-        assert world == 1, "the hybrid family is served on one GPU"
+        assert world == 1, "this family is served on one GPU"
         ld = open_checkpoint(directory, dtype)
-        cfg = Qwen35Config.from_hf(ld.config)
-        model = Qwen35MoeModel(cfg, device, dtype).load_state(ld)
+        if family == "qwen3_vl":
+            from .models.qwen3_vl import Qwen3VLDenseModel, Qwen3VLTextConfig
+            cfg = Qwen3VLTextConfig.from_hf(ld.config)
+            model = Qwen3VLDenseModel(cfg, device, dtype).load_state(ld)
+        else:
+            from .models.qwen3_5 import Qwen35Config, Qwen35MoeModel
+            cfg = Qwen35Config.from_hf(ld.config)
+            model = Qwen35MoeModel(cfg, device, dtype).load_state(ld)
 
         tower = None
         if any(n.startswith("model.visual.") for n in ld.names()):      # image inputs

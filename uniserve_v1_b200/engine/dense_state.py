@@ -137,12 +137,13 @@ class DenseStateEngine:
         if not hasattr(req, "_mm"):
             pixels, grids = req.media
             ids = torch.tensor(req.prompt_ids, device=self.model.device)
-            rows, _ = self.mm.tower.forward(pixels, grids)
+            rows, deep = self.mm.tower.forward(pixels, grids)
             emb = splice(self.model.w["embed"][ids.long()], ids, cfg.image_token_id, rows)
             pos3, nxt = mrope_positions(req.prompt_ids, cfg.image_token_id, grids,
                                         self.mm.tower.cfg.spatial_merge_size)
-            req._mm = (emb, pos3, nxt - len(req.prompt_ids))
-        emb, pos3, delta = req._mm
+            at = (ids == cfg.image_token_id).nonzero(as_tuple=True)[0]
+            req._mm = (emb, pos3, nxt - len(req.prompt_ids), at, deep)
+        emb, pos3, delta, at, deep = req._mm
         lo, hi, P = req.num_computed, req.num_computed + n, len(req.prompt_ids)
         e = self.model.w["embed"][chunk.long()]
         p = (torch.arange(lo, hi) + delta)[None].expand(3, -1).clone()
@@ -150,7 +151,11 @@ class DenseStateEngine:
             k = min(hi, P) - lo
             e = torch.cat([emb[lo:lo + k], e[k:]], 0)
             p[:, :k] = pos3[:, lo:lo + k]
-        return self.model.forward(chunk, st, lo, embeds=e, positions3=p)
+        ds = None
+        if deep:                                  # deep-stack rows of the image positions in [lo, hi)
+            sel = ((at >= lo) & (at < hi)).nonzero(as_tuple=True)[0]
+            ds = (at[sel] - lo, [d[sel] for d in deep])
+        return self.model.forward(chunk, st, lo, embeds=e, positions3=p, deepstack=ds)
 
     def _stop(self, req: Request, tok: int) -> Optional[FinishReason]:
         p = req.params

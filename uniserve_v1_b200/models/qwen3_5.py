@@ -82,6 +82,24 @@ class Qwen35Config:
         return cfg
 
 
+def norm_mrope(x, w, pos3, inv_freq, rot: int, section, eps: float):
+    """Per-head RMSNorm (weight ``w``), then rotary embedding over the first ``rot`` channels
+    whose frequency j turns with the temporal, row or column position according to the
+    interleaved sections (t h w t h w ... t t).  x [T, H, D], pos3 [3, T]."""
+    xf = x.float()
+    xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    nf = rot // 2
+    axis = torch.zeros(nf, dtype=torch.long, device=x.device)
+    for a, off in ((1, 1), (2, 2)):
+        axis[off:section[a] * 3:3] = a
+    ang = pos3.to(x.device).float()[axis, :].t() * inv_freq.float()[None, :]          # [T, nf]
+    cos = torch.cat([ang.cos(), ang.cos()], -1)[:, None, :]
+    sin = torch.cat([ang.sin(), ang.sin()], -1)[:, None, :]
+    r = xf[..., :rot]
+    turned = torch.cat([-r[..., nf:], r[..., :nf]], -1)
+    return torch.cat([r * cos + turned * sin, xf[..., rot:]], -1).to(x.dtype)
+
+
 @dataclass
 class LayerState:
     k: Optional[torch.Tensor] = None        # attention: [n, Hkv, D]
@@ -195,21 +213,8 @@ class Qwen35MoeModel:
         return [LayerState() for _ in self.cfg.layer_types]
 
     def _norm_mrope(self, x, w, pos3):
-        """Per-head RMSNorm, then rotary embedding whose frequency j turns with the temporal,
-        row or column position according to the interleaved sections (t h w t h w ... t t)."""
-        c = self.cfg
-        xf = x.float()
-        xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + c.rms_norm_eps) * w.float()
-        nf = self.rot // 2
-        axis = torch.zeros(nf, dtype=torch.long, device=x.device)
-        for a, off in ((1, 1), (2, 2)):
-            axis[off:c.mrope_section[a] * 3:3] = a
-        ang = pos3.to(x.device).float()[axis, :].t() * self.inv_freq.float()[None, :]     # [T, nf]
-        cos = torch.cat([ang.cos(), ang.cos()], -1)[:, None, :]
-        sin = torch.cat([ang.sin(), ang.sin()], -1)[:, None, :]
-        rot = xf[..., :self.rot]
-        turned = torch.cat([-rot[..., nf:], rot[..., :nf]], -1)
-        return torch.cat([rot * cos + turned * sin, xf[..., self.rot:]], -1).to(x.dtype)
+        return norm_mrope(x, w, pos3, self.inv_freq, self.rot, self.cfg.mrope_section,
+                          self.cfg.rms_norm_eps)
 
     def _attention(self, L, n, st: LayerState, pos0: int, pos3=None):
         c, D = self.cfg, self.cfg.head_dim
@@ -270,7 +275,7 @@ class Qwen35MoeModel:
         return y + (shared.float() * sg).to(n.dtype)
 
     def forward(self, ids: torch.Tensor, state: list, pos0: int = 0, embeds=None,
-                positions3=None) -> torch.Tensor:
+                positions3=None, deepstack=None) -> torch.Tensor:
         """Runs ``ids`` [T] at positions pos0 .. on top of ``state``; returns FP32 logits
         [T, vocab].  ``embeds`` [T, hidden] replaces the embedding lookup (vision rows spliced
         in); ``positions3`` [3, T] are the (temporal, row, column) rotary positions of a
@@ -345,13 +350,16 @@ class Qwen35Multimodal:
         c = self.text.cfg
         ids = torch.tensor(prompt_ids, device=self.text.device)
         emb = self.text.w["embed"][ids.long()]
+        deep = None
         if pixels is not None:
             from .qwen3_vl_vision import splice
-            rows, _ = self.tower.forward(pixels, grids)
+            rows, deep_rows = self.tower.forward(pixels, grids)
             emb = splice(emb, ids, c.image_token_id, rows)
+            if deep_rows:
+                deep = ((ids == c.image_token_id).nonzero(as_tuple=True)[0], deep_rows)
         pos3, nxt = mrope_positions(prompt_ids, c.image_token_id, grids or [],
                                     self.tower.cfg.spatial_merge_size)
-        return self.text.forward(ids, state, 0, embeds=emb, positions3=pos3), nxt
+        return self.text.forward(ids, state, 0, embeds=emb, positions3=pos3, deepstack=deep), nxt
 
     def generate(self, prompt_ids: list, pixels, grids: list, max_tokens: int) -> list:
         state = self.text.new_state()
