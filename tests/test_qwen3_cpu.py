@@ -246,3 +246,42 @@ def test_gated_delta_rule_chunked_equals_stepwise():
     y_b, st = GD.causal_conv1d(x[7:], w, st)
     torch.testing.assert_close(torch.cat([y_a, y_b]), y_all)
     torch.testing.assert_close(st, st_all)
+
+
+def test_hybrid_decoder_batched_decode_equals_sequential():
+    """Several sequences advancing in one batched step (shared projections and experts,
+    vectorised delta rule and convolution, per-sequence attention) produce the logits of
+    separate calls, and the dense-state engine takes that path."""
+    import torch
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel
+    model = Qwen35MoeModel(Qwen35MoeModel.tiny_config(), "cpu", torch.float32).init_random(seed=0)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1000, (n,), generator=g) for n in (7, 19, 4)]
+    states = [model.new_state() for _ in prompts]
+    for p, st in zip(prompts, states):
+        model.forward(p, st, 0)
+    import copy
+    seq_states = copy.deepcopy(states)
+    toks = torch.tensor([11, 22, 33])
+    pos = torch.tensor([len(p) for p in prompts])
+    got = model.decode_batch(toks, states, pos[None].expand(3, -1))
+    want = torch.cat([model.forward(toks[i:i + 1], seq_states[i], int(pos[i])) for i in range(3)])
+    torch.testing.assert_close(got, want, atol=2e-5, rtol=2e-5)
+    again = model.decode_batch(toks, states, (pos + 1)[None].expand(3, -1))      # states advanced
+    want2 = torch.cat([model.forward(toks[i:i + 1], seq_states[i], int(pos[i]) + 1) for i in range(3)])
+    torch.testing.assert_close(again, want2, atol=2e-5, rtol=2e-5)
+    calls = {"n": 0}
+    inner = model.decode_batch
+
+    def counted(*a):
+        calls["n"] += 1
+        return inner(*a)
+    model.decode_batch = counted
+    eng = DenseStateEngine(model, max_num_seqs=4)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = eng.generate([p.tolist() for p in prompts], sp)
+    model.decode_batch = inner
+    assert calls["n"] >= 4
+    assert outs == [DenseStateEngine(model).generate([p.tolist()], sp)[0] for p in prompts]

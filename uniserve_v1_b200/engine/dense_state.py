@@ -7,9 +7,10 @@ Same calls as ``LLMEngine`` - ``add_request`` / ``step`` / ``abort`` / ``has_wor
 One step admits waiting requests up to ``max_num_seqs``, runs the next prompt chunk of
 every request still reading its prompt, and one decode position for every other one.
 Sampling follows the request's parameters with draws addressed by (seed, position), so
-a request produces the same tokens whatever else is running.  Sequences are advanced
-one after another (their states are separate tensors); batching the linear layers
-across sequences is left open.
+a request produces the same tokens whatever else is running.  Requests that have read
+their prompt advance together when the model offers ``decode_batch`` (projections, experts,
+the delta rule and the convolution run on all rows at once, attention per sequence);
+prompt chunks run one sequence at a time.
 
 Reference behaviour: crates/engine/src/runner/causal_lm (state slots and
 ``state_interval`` checkpoints of recurrent layers) - reference project path.
@@ -176,13 +177,28 @@ class DenseStateEngine:
         outs = []
         self._stats["steps"] += 1
         dev = self.model.device
+        # requests that have read their prompt advance together: one batched decode step
+        batched = {}
+        if hasattr(self.model, "decode_batch"):
+            rows = [r for r in self.running if r.output_ids and
+                    r.num_computed == r.num_tokens - 1]
+            if len(rows) >= 2:
+                toks = torch.tensor([r.output_ids[-1] for r in rows], device=dev)
+                pos = torch.tensor([r.num_computed + (r._mm[2] if hasattr(r, "_mm") else 0)
+                                    for r in rows])
+                logits = self.model.decode_batch(toks, [self.states[r.request_id] for r in rows],
+                                                 pos[None].expand(3, -1))
+                for i, r in enumerate(rows):
+                    batched[r.request_id] = logits[i:i + 1]
         for req in list(self.running):
             st = self.states[req.request_id]
             ids = req.all_ids
             todo = len(ids) - req.num_computed
             n = min(todo, self.config.prefill_chunk)
             chunk = torch.tensor(ids[req.num_computed:req.num_computed + n], device=dev)
-            if getattr(req, "media", None) is not None:
+            if req.request_id in batched:
+                logits = batched[req.request_id]
+            elif getattr(req, "media", None) is not None:
                 logits = self._forward_media(req, chunk, st, n)
             else:
                 logits = self.model.forward(chunk, st, req.num_computed)

@@ -294,6 +294,72 @@ class Qwen35MoeModel:
         return F.linear(R.rmsnorm(x, w["norm"], c.rms_norm_eps), w["lm_head"],
                         out_dtype=torch.float32)
 
+    def decode_batch(self, tokens: torch.Tensor, states: list, pos3: torch.Tensor) -> torch.Tensor:
+        """One decode position of B sequences at once: ``tokens`` [B], ``states`` a list of B
+        per-sequence states, ``pos3`` [3, B] rotary positions.  Projections, MLPs and experts
+        run on all rows together; the delta rule and the convolution advance as one batched
+        step; attention reads each sequence's own keys.  Returns FP32 logits [B, vocab]."""
+        c, w = self.cfg, self.w
+        B = tokens.shape[0]
+        x = w["embed"][tokens.to(self.device).long()]
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        Hk, Hv, Dk, Dv = (c.linear_num_key_heads, c.linear_num_value_heads,
+                          c.linear_key_head_dim, c.linear_value_head_dim)
+        kd, vd = Hk * Dk, Hv * Dv
+        for i in range(c.num_hidden_layers):
+            L = w[i]
+            n = R.rmsnorm(x, L["in_norm"], c.rms_norm_eps)
+            if L["kind"] == "full_attention":
+                qg = F.linear(n, L["q"]).view(B, Hq, 2 * D)
+                q, gate = qg[..., :D], qg[..., D:].reshape(B, Hq * D)
+                k = F.linear(n, L["k"]).view(B, Hkv, D)
+                v = F.linear(n, L["v"]).view(B, Hkv, D)
+                q = self._norm_mrope(q, L["q_norm"], pos3)
+                k = self._norm_mrope(k, L["k_norm"], pos3)
+                att = torch.empty(B, Hq * D, dtype=torch.float32, device=x.device)
+                rep = Hq // Hkv
+                for b in range(B):
+                    st = states[b][i]
+                    st.k = k[b:b + 1] if st.k is None else torch.cat([st.k, k[b:b + 1]], 0)
+                    st.v = v[b:b + 1] if st.v is None else torch.cat([st.v, v[b:b + 1]], 0)
+                    K = st.k.float().repeat_interleave(rep, 1)
+                    V = st.v.float().repeat_interleave(rep, 1)
+                    p = (torch.einsum("hd,nhd->hn", q[b].float(), K) / math.sqrt(D)).softmax(-1)
+                    att[b] = torch.einsum("hn,nhd->hd", p, V).reshape(Hq * D)
+                mix = F.linear((att * torch.sigmoid(gate.float())).to(n.dtype), L["o"])
+            else:
+                proj = F.linear(n, L["qkvz"])
+                mixed, z = proj[:, :2 * kd + vd], proj[:, 2 * kd + vd:2 * kd + 2 * vd]
+                bb, aa = proj[:, 2 * kd + 2 * vd:2 * kd + 2 * vd + Hv], proj[:, 2 * kd + 2 * vd + Hv:]
+                Kc = L["conv"].shape[1]
+                conv = torch.stack([states[b][i].conv if states[b][i].conv is not None else
+                                    torch.zeros(Kc - 1, mixed.shape[1], dtype=mixed.dtype,
+                                                device=mixed.device) for b in range(B)])
+                win = torch.cat([conv, mixed[:, None, :]], 1).float()            # [B, K, C]
+                y = torch.nn.functional.silu((win * L["conv"].float().t()[None]).sum(1)).to(mixed.dtype)
+                q = GD.l2norm(y[:, :kd].reshape(B, Hk, Dk).float()) * (Dk ** -0.5)
+                k = GD.l2norm(y[:, kd:2 * kd].reshape(B, Hk, Dk).float())
+                v = y[:, 2 * kd:].reshape(B, Hv, Dv).float()
+                if Hv // Hk > 1:
+                    q, k = q.repeat_interleave(Hv // Hk, 1), k.repeat_interleave(Hv // Hk, 1)
+                beta = torch.sigmoid(bb.float())
+                g = L["A"] * torch.nn.functional.softplus(aa.float() + L["dt_bias"])
+                S = torch.stack([states[b][i].rule if states[b][i].rule is not None else
+                                 torch.zeros(Hv, Dk, Dv, device=x.device) for b in range(B)])
+                S = S * g.exp()[:, :, None, None]
+                d = (v - torch.einsum("bhkv,bhk->bhv", S, k)) * beta[:, :, None]
+                S = S + k[:, :, :, None] * d[:, :, None, :]
+                o = torch.einsum("bhkv,bhk->bhv", S, q)
+                for b in range(B):
+                    states[b][i].conv = win[b, 1:].to(mixed.dtype)
+                    states[b][i].rule = S[b]
+                o = GD.rmsnorm_gated(o.to(n.dtype), L["gnorm"], z.reshape(B, Hv, Dv), c.rms_norm_eps)
+                mix = F.linear(o.reshape(B, vd), L["out"])
+            x = x + mix
+            x = x + self._mlp(L, R.rmsnorm(x, L["post_norm"], c.rms_norm_eps))
+        return F.linear(R.rmsnorm(x, w["norm"], c.rms_norm_eps), w["lm_head"],
+                        out_dtype=torch.float32)
+
     def generate(self, prompt_ids: list, max_tokens: int, chunk: int = 512) -> list:
         """Greedy decoding with chunked prefill."""
         state, out, pos = self.new_state(), [], 0
