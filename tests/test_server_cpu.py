@@ -313,3 +313,30 @@ def test_chat_with_an_image_on_the_hybrid_family():
     with TestClient(plain) as c:
         r = c.post("/v1/chat/completions", json=body)
         assert r.status_code == 400 and "images" in r.json()["error"]["message"]
+
+
+def test_dense_state_engine_shapes_logits_like_the_paged_engine():
+    """Penalties, bias, bans, minimum length and log-probabilities on the hybrid family go
+    through the same shaping code as on the paged engine."""
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel
+    model = Qwen35MoeModel(Qwen35MoeModel.tiny_config(), "cpu", torch.float32).init_random(seed=0)
+    eng = DenseStateEngine(model, max_num_seqs=4, max_model_len=256)
+    pkg = Package.parse('model = "random:tiny"\nserved_model_name = "hybrid"\n')
+    app = create_app(package=pkg, engine=eng, tokenizer=ByteTokenizer(1024, 1023),
+                     served_model_name="hybrid")
+    with TestClient(app) as c:
+        base = {"model": "hybrid", "messages": [{"role": "user", "content": "hello"}],
+                "max_tokens": 6, "temperature": 0, "ignore_eos": True}
+        plain = c.post("/v1/chat/completions", json=base).json()
+        lp = c.post("/v1/chat/completions", json=dict(base, logprobs=True, top_logprobs=3)).json()
+        assert lp["choices"][0]["message"] == plain["choices"][0]["message"]
+        ent = lp["choices"][0]["logprobs"]["content"]
+        assert len(ent) == 6 and len(ent[0]["top_logprobs"]) == 3 and ent[0]["logprob"] <= 0.0
+        first = eng.requests[next(reversed(eng.requests))].output_ids[0]
+        banned = c.post("/v1/chat/completions", json=dict(base, logit_bias={str(first): -100})).json()
+        rid = next(reversed(eng.requests))
+        assert eng.requests[rid].output_ids[0] != first and banned["usage"]["completion_tokens"] == 6
+        rep = c.post("/v1/chat/completions", json=dict(base, repetition_penalty=1.8,
+                                                       presence_penalty=1.0)).json()
+        assert rep["usage"]["completion_tokens"] == 6

@@ -116,6 +116,19 @@ class DenseStateEngine:
     # ----------------------------------------------------------------- step --
     def _sample(self, req: Request, logits_row: torch.Tensor) -> int:
         p = req.params
+        if p.needs_shaping or p.logprobs:
+            # penalties, bias, bans, minimum length and log-probabilities: the paged
+            # runner's shaping code on this one row (same order, same draw addressing)
+            from .runner import CausalLmRunner as ModelRunner
+
+            class _Row:
+                eos_token_id = getattr(self.model.cfg, "eos_token_id", None)
+                d2h_bytes = 0
+            toks, info = ModelRunner._shape_and_sample(_Row(), logits_row.float()[None].contiguous(),
+                                                       [req])
+            if info and req.request_id in info:
+                req.logprobs.append(info[req.request_id])
+            return int(toks[0])
         if p.temperature <= 0.0:
             return int(logits_row.argmax())
         dev = logits_row.device
@@ -125,7 +138,8 @@ class DenseStateEngine:
                                  device=dev),
             torch.tensor([p.top_p], dtype=torch.float32, device=dev),
             torch.tensor([getattr(p, "min_p", 0.0) or 0.0], dtype=torch.float32, device=dev),
-            torch.tensor([req.seed & 0x7FFFFFFFFFFFFFFF], dtype=torch.int64, device=dev),
+            torch.tensor([req.seed - (1 << 64) if req.seed >= (1 << 63) else req.seed],
+                         dtype=torch.int64, device=dev),
             torch.tensor([req.num_tokens], dtype=torch.int64, device=dev))
         return int(tok[0])
 
@@ -206,6 +220,7 @@ class DenseStateEngine:
             self._stats["decode_tokens" if (n == 1 and req.output_ids) else "prefill_tokens"] += n
             if req.num_computed < len(ids):
                 continue                    # still reading its prompt
+            p_lp = bool(req.params.logprobs)
             tok = self._sample(req, logits[-1])
             if req.first_token_time is None:
                 req.first_token_time = time.monotonic()
@@ -213,7 +228,8 @@ class DenseStateEngine:
             reason = self._stop(req, tok)
             if reason is not None:
                 self._finish(req, reason)
-            outs.append(StepOutput(req.request_id, [tok], reason is not None, reason))
+            outs.append(StepOutput(req.request_id, [tok], reason is not None, reason,
+                                   logprobs=[req.logprobs[-1]] if (p_lp and req.logprobs) else None))
         return outs
 
     def generate(self, prompts: list, params=None) -> list:
