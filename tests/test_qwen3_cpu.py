@@ -175,6 +175,15 @@ def test_mtp_drafter_keeps_outputs_and_round_trips_its_weights():
             outs[o.request_id].extend(o.new_token_ids)
     assert [outs[r] for r in rids] == ref
     assert eng.spec_stats["proposed"] >= 2 * 4          # it did draft, two tokens at a time
+    # the prompt's hidden rows reached the head at prefill: its stream covered the prompt
+    # before the first draft, without a bootstrap verification
+    eng2, d2 = mk(), MtpDrafter(head, k=2)
+    rid = eng2.add_request(prompts[1], sp)
+    eng2.speculative_step(d2)                           # prefill
+    assert d2.state[rid]["kv"][0].shape[0] == len(prompts[1]) - 1 and "pending" in d2.state[rid]
+    eng2.speculative_step(d2)                           # first verification, already with drafts
+    assert eng2.spec_stats["proposed"] == 2
+    assert d2.state[rid]["kv"][0].shape[0] >= len(prompts[1]) + 1
     # the stream holds verified positions only, and finished requests are forgotten
     drafter.forget(set())
     assert drafter.state == {}

@@ -189,14 +189,17 @@ class LLMEngine:
         from .scheduler import Batch, Chunk
         from .speculation import accept
         sch = self.scheduler
+        stateful = getattr(drafter, "needs_hidden", False)
+        if stateful and getattr(self.runner, "hidden_tap", None) is None and hasattr(drafter, "tap"):
+            self.runner.hidden_tap = drafter.tap       # prompt rows reach the drafter at prefill
         rows = [r for r in sch.running if r.output_ids and r.num_computed == r.num_tokens - 1]
         if not rows or len(rows) != len(sch.running) or sch.waiting or \
                 self.runner.variant_for(rows) != "greedy":
             return self.step()
         drafts = []
-        stateful = getattr(drafter, "needs_hidden", False)
         if stateful:
-            drafter.forget({r.request_id for r in rows})
+            drafter.forget({r.request_id for r in self.scheduler.requests.values()
+                            if not r.finished})
         for r in rows:
             room = min(self.config.max_model_len - r.num_tokens - 1,
                        r.params.max_tokens - len(r.output_ids) - 1)

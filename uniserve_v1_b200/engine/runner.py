@@ -484,6 +484,10 @@ class CausalLmRunner:
                         context_lens=ctx, page_table=page_table)
         self.announce("eager", T)
         hidden = self.model.forward(d[:T], d[T:2 * T], meta, self.kv_caches)
+        tap = getattr(self, "hidden_tap", None)
+        if tap is not None:          # a drafter that feeds on the target's states (MTP head)
+            for i, c in enumerate(chunks):
+                tap(c.request, c.start, hidden[cu_q[i]:cu_q[i + 1]])
         if not sample_rows:
             return None, None, []
         rows_idx = torch.tensor(last_rows, dtype=i32, device=dev)

@@ -13,10 +13,10 @@ next hidden state and its own prediction for the next token.
 
 ``MtpDrafter`` plugs into ``LLMEngine.speculative_step``: the verification call hands it
 the target's hidden states of the verified positions (``observe``), from which it
-extends its stream and proposes the next drafts (``propose_for``).  Its key / value
-stream starts where speculation starts for a request (the reference also fills it for
-the prompt during prefill; that only changes the acceptance rate, never the output,
-which is always the target's own greedy choice).
+extends its stream and proposes the next drafts (``propose_for``).  The runner's prefill
+hands it the prompt's hidden rows too (``tap``), so the head's key / value stream covers the
+prompt as the reference's draft KV group does.  Whatever the head proposes, the output is
+the target's own greedy choice.
 
 Checkpoint names (``mtp.`` prefix): ``fc.weight`` [H, 2H], ``pre_fc_norm_embedding.weight``,
 ``pre_fc_norm_hidden.weight``, ``norm.weight``, ``layers.0.*`` as a decoder layer.
@@ -122,23 +122,25 @@ class MtpHead:
         return {k: v.detach().contiguous() for k, v in out.items()}
 
     # ------------------------------------------------------------- forward --
-    def step(self, hidden: torch.Tensor, next_token: int, position: int, kv: list):
-        """One position: ``hidden`` [H] of position p, the token after it, the head's
-        key / value stream ``kv`` = [K [n, Hkv, D], V] (extended in place).  Returns
-        (head output [H], logits [V])."""
+    def rows(self, hidden: torch.Tensor, next_tokens, position: int, kv: list):
+        """T consecutive positions at once: ``hidden`` [T, H] of positions p .. p + T - 1, the
+        token after each, the head's key / value stream ``kv`` = [K [n, Hkv, D], V] (extended in
+        place; attention is causal inside the call and sees the whole earlier stream).
+        Returns (head outputs [T, H], logits [T, V])."""
         c, w, t = self.cfg, self.w, self.t
         eps, D = c.rms_norm_eps, c.head_dim
         Hq, Hkv = c.num_attention_heads, c.num_key_value_heads
-        emb = t.embed[int(next_token)][None]
-        x = torch.cat([R.rmsnorm(emb, w["pre_fc_norm_embedding.weight"], eps),
-                       R.rmsnorm(hidden[None].to(self.dtype), w["pre_fc_norm_hidden.weight"], eps)],
-                      -1)
+        toks = torch.as_tensor(next_tokens, device=self.device).long().reshape(-1)
+        T = toks.shape[0]
+        x = torch.cat([R.rmsnorm(t.embed[toks], w["pre_fc_norm_embedding.weight"], eps),
+                       R.rmsnorm(hidden.reshape(T, -1).to(self.dtype),
+                                 w["pre_fc_norm_hidden.weight"], eps)], -1)
         x = R.linear(x, w["fc.weight"])
         n = R.rmsnorm(x, w["layers.0.input_layernorm.weight"], eps)
-        q = R.linear(n, w["layers.0.self_attn.q_proj.weight"]).view(1, Hq, D)
-        k = R.linear(n, w["layers.0.self_attn.k_proj.weight"]).view(1, Hkv, D)
-        v = R.linear(n, w["layers.0.self_attn.v_proj.weight"]).view(1, Hkv, D)
-        pos = torch.tensor([position], device=self.device)
+        q = R.linear(n, w["layers.0.self_attn.q_proj.weight"]).view(T, Hq, D)
+        k = R.linear(n, w["layers.0.self_attn.k_proj.weight"]).view(T, Hkv, D)
+        v = R.linear(n, w["layers.0.self_attn.v_proj.weight"]).view(T, Hkv, D)
+        pos = torch.arange(position, position + T, device=self.device)
         q, k = R.qk_norm_rope(q, k, w["layers.0.self_attn.q_norm.weight"],
                               w["layers.0.self_attn.k_norm.weight"], pos, t.inv_freq, D, False, eps)
         kv[0] = k if kv[0] is None else torch.cat([kv[0], k], 0)
@@ -146,8 +148,12 @@ class MtpHead:
         rep = Hq // Hkv
         K = kv[0].float().repeat_interleave(rep, 1)                     # [n, Hq, D]
         V = kv[1].float().repeat_interleave(rep, 1)
-        s = torch.einsum("hd,nhd->hn", q[0].float(), K) / math.sqrt(D)
-        att = torch.einsum("hn,nhd->hd", s.softmax(-1), V).reshape(1, Hq * D).to(self.dtype)
+        s = torch.einsum("thd,nhd->htn", q.float(), K) / math.sqrt(D)
+        n_ctx = K.shape[0]
+        seq = torch.arange(n_ctx - T, n_ctx, device=self.device)
+        s = s.masked_fill((torch.arange(n_ctx, device=self.device)[None, :] > seq[:, None])[None],
+                          float("-inf"))
+        att = torch.einsum("htn,nhd->thd", s.softmax(-1), V).reshape(T, Hq * D).to(self.dtype)
         x = x + R.linear(att, w["layers.0.self_attn.o_proj.weight"])
         n = R.rmsnorm(x, w["layers.0.post_attention_layernorm.weight"], eps)
         if c.num_experts:
@@ -160,7 +166,12 @@ class MtpHead:
                          w["layers.0.mlp.down_proj.weight"])
         x = x + y
         out = R.rmsnorm(x, w["norm.weight"], eps)
-        return x[0], R.linear(out, t.lm_head, out_dtype=torch.float32)[0]
+        return x, R.linear(out, t.lm_head, out_dtype=torch.float32)
+
+    def step(self, hidden: torch.Tensor, next_token: int, position: int, kv: list):
+        """One position: (head output [H], logits [V])."""
+        x, logits = self.rows(hidden[None], [int(next_token)], position, kv)
+        return x[0], logits[0]
 
 
 class MtpDrafter(Drafter):
@@ -173,7 +184,7 @@ class MtpDrafter(Drafter):
         self.state: dict = {}           # request id -> {"kv": [K, V], "pos": int, "out", "tok"}
 
     def ready(self, request_id: str) -> bool:
-        return request_id in self.state
+        return "tok" in self.state.get(request_id, {})
 
     def forget(self, keep_ids) -> None:
         for rid in [r for r in self.state if r not in keep_ids]:
@@ -184,16 +195,40 @@ class MtpDrafter(Drafter):
         """``hidden[i]`` is the target's state at position ``first_position + i`` and
         ``next_tokens[i]`` the token that follows it (accepted or the target's own)."""
         st = self.state.setdefault(request_id, {"kv": [None, None]})
-        for i, tok in enumerate(next_tokens):
-            out, logits = self.head.step(hidden[i], tok, first_position + i, st["kv"])
+        if not len(next_tokens):
+            return
+        outs, logits_all = self.head.rows(hidden[:len(next_tokens)], list(next_tokens),
+                                          first_position, st["kv"])
+        out, logits = outs[-1], logits_all[-1]
         if st["kv"][0].shape[0] > self.window:
             st["kv"] = [st["kv"][0][-self.window:], st["kv"][1][-self.window:]]
         st["pos"] = first_position + len(next_tokens) - 1
         st["out"], st["tok"] = out, int(logits.argmax())
 
+    def tap(self, request, start: int, hidden: torch.Tensor) -> None:
+        """Prefill hook of the runner: the target's hidden rows of prompt positions
+        start .. start + T - 1.  Every position whose next token is already known extends the
+        head's stream, so drafting starts with the prompt's context (the last position waits
+        for its sampled token and arrives through ``observe``)."""
+        ids = request.all_ids
+        rid = request.request_id
+        if start == 0:
+            self.state.pop(rid, None)              # a fresh (or recomputed) prompt: new stream
+        n = min(hidden.shape[0], len(ids) - 1 - start)
+        if n > 0:
+            self.observe(rid, start, hidden[:n], ids[start + 1:start + 1 + n])
+        if n < hidden.shape[0]:                    # the last position: its token is being sampled
+            self.state.setdefault(rid, {"kv": [None, None]})["pending"] = \
+                (start + n, hidden[n:n + 1].detach().clone())
+
     def propose_for(self, request) -> list:
         st = self.state.get(request.request_id)
-        if st is None:
+        if st is not None and st.get("pending") is not None:
+            pos, row = st.pop("pending")
+            ids = request.all_ids
+            if pos + 1 < len(ids) and (st["kv"][0] is None or "pos" not in st or st["pos"] == pos - 1):
+                self.observe(request.request_id, pos, row, [ids[pos + 1]])
+        if st is None or "tok" not in st:
             return []
         drafts = [st["tok"]]
         # recurrent drafts run on a copy of the stream: only verified positions stay in it
