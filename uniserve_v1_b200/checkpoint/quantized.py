@@ -75,7 +75,6 @@ class DequantizingLoader:
 def open_checkpoint(directory, dtype=torch.bfloat16):
     """A ``CheckpointLoader`` for ``directory``, wrapped when its config declares a
     quantization (``quantization_config`` or ModelOpt's ``hf_quant_config.json``)."""
-    import json
     from pathlib import Path
 
     from .safetensors_io import CheckpointLoader

@@ -27,7 +27,6 @@ crates/engine/src/runner/causal_lm/speculation.rs (reference project paths).
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 
