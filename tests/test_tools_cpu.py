@@ -350,3 +350,15 @@ def test_block_manager_replays_a_serving_trace():
     i = next(i for i, op in enumerate(trace) if op[0] == "release")
     bad = trace[:i] + [trace[i], trace[i]] + trace[i + 1:]           # a double release
     assert replay(bad, mk, 14)["violation"]
+
+
+def test_site_protocol_interleavings():
+    """The flag / epoch protocol of the fused collectives: no interleaving of 2 or 3 ranks reads a
+    stale or overwritten partial or blocks, as long as another site's barrier lies between two
+    uses of a buffer; a single site is caught."""
+    from uniserve_v1_b200.tools.verify import explore_site_protocol
+    assert explore_site_protocol(2, 2, 3)["violation"] is None
+    assert explore_site_protocol(3, 2, 2)["violation"] is None
+    assert explore_site_protocol(3, 3, 2)["violation"] is None
+    bad = explore_site_protocol(2, 1, 2)["violation"]
+    assert bad and "finds pass" in bad

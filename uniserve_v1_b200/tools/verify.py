@@ -18,6 +18,9 @@ page.  After every operation the invariants are checked:
 serves requests (shared prefixes, preemption, eviction) are recorded and run again on a
 fresh manager, which must answer identically and keep the invariants.
 
+``explore_site_protocol`` walks every interleaving of the flag / epoch protocol of the fused
+collectives for a few ranks, sites and passes (stale or overwritten partials, deadlock).
+
 ``mutants`` are wrappers that break one behaviour each (a dropped release, a match that
 does not pin, a commit under the wrong key, a stale page kept after reuse); the checker
 has to flag every one of them, which shows the invariants have teeth.
@@ -284,6 +287,75 @@ def replay(trace: list, make_bm, pages: int) -> dict:
     return {"calls": n, "violation": None}
 
 
+# ------------------------------------------------------------ site protocol --
+def explore_site_protocol(world: int = 2, sites: int = 2, passes: int = 2) -> dict:
+    """Every interleaving of the fused collectives' flag protocol (``csrc/fused/peer_comm.cu``)
+    for ``world`` ranks that run ``passes`` forward passes over ``sites`` collective sites.
+
+    A rank's program at a site: write its partial into its own buffer of the site; store the
+    site's next epoch into its flag slot on every peer (one store per peer, any order); wait
+    until every peer's slot on this rank shows that epoch; read every peer's buffer.  Kernels
+    of one rank run in stream order, ranks run freely against each other.  Checked: a read
+    always finds the partial of the *same* pass (neither the previous pass's nor one a fast
+    rank already overwrote), and no interleaving blocks for good.  Buffers are reused one
+    pass later without a second barrier, which is safe only because another site's barrier
+    lies in between: with ``sites = 1`` the exploration finds the overwrite."""
+    peers = [[q for q in range(world) if q != r] for r in range(world)]
+    prog = []
+    for r in range(world):
+        ops = []
+        for n in range(passes):
+            for st in range(sites):
+                ops.append(("write", st, n))
+                ops.extend(("announce", st, n, q) for q in peers[r])
+                ops.append(("wait", st, n))
+                ops.extend(("read", st, n, q) for q in peers[r])
+        prog.append(ops)
+    # state: program counters, buffer[r][site] = pass of its content, flag[r][site][from] = epoch
+    start = (tuple([0] * world), tuple(tuple([-1] * sites) for _ in range(world)),
+             tuple(tuple(tuple([0] * world) for _ in range(sites)) for _ in range(world)))
+    seen, frontier, steps = {start}, [start], 0
+    while frontier:
+        nxt = []
+        for pcs, buf, flag in frontier:
+            moved = False
+            for r in range(world):
+                if pcs[r] >= len(prog[r]):
+                    continue
+                op = prog[r][pcs[r]]
+                b2, f2 = buf, flag
+                if op[0] == "write":
+                    row = list(buf[r])
+                    row[op[1]] = op[2]
+                    b2 = buf[:r] + (tuple(row),) + buf[r + 1:]
+                elif op[0] == "announce":
+                    q, st = op[3], op[1]
+                    slots = list(flag[q][st])
+                    slots[r] = op[2] + 1
+                    site_rows = list(flag[q])
+                    site_rows[st] = tuple(slots)
+                    f2 = flag[:q] + (tuple(site_rows),) + flag[q + 1:]
+                elif op[0] == "wait":
+                    if any(flag[r][op[1]][q] < op[2] + 1 for q in peers[r]):
+                        continue                     # blocked
+                else:
+                    got = buf[op[3]][op[1]]
+                    if got != op[2]:
+                        return {"states": len(seen), "violation":
+                                f"rank {r} reads rank {op[3]}'s site {op[1]} in pass {op[2]} "
+                                f"and finds pass {got}"}
+                moved = True
+                steps += 1
+                state = (pcs[:r] + (pcs[r] + 1,) + pcs[r + 1:], b2, f2)
+                if state not in seen:
+                    seen.add(state)
+                    nxt.append(state)
+            if not moved and any(pcs[r] < len(prog[r]) for r in range(world)):
+                return {"states": len(seen), "violation": f"deadlock at {pcs}"}
+        frontier = nxt
+    return {"states": len(seen), "violation": None}
+
+
 def main(argv=None) -> int:
     from ..engine.block_manager import BlockManager
     ap = argparse.ArgumentParser(prog="uniserve_v1_b200.tools.verify")
@@ -297,7 +369,13 @@ def main(argv=None) -> int:
         r = explore(mk(cls), a.pages, min(a.depth, 4), a.keys)
         report["mutants"][name] = "caught" if r["violation"] else "MISSED"
     print(json.dumps(report, indent=1))
-    bad = report["native"]["violation"] or "MISSED" in report["mutants"].values()
+    report["site_protocol"] = {"2 ranks x 2 sites x 3 passes": explore_site_protocol(2, 2, 3),
+                               "3 ranks x 2 sites x 2 passes": explore_site_protocol(3, 2, 2),
+                               "1 site (must fail)": explore_site_protocol(2, 1, 2)}
+    bad = report["native"]["violation"] or "MISSED" in report["mutants"].values() or \
+        report["site_protocol"]["2 ranks x 2 sites x 3 passes"]["violation"] or \
+        report["site_protocol"]["3 ranks x 2 sites x 2 passes"]["violation"] or \
+        not report["site_protocol"]["1 site (must fail)"]["violation"]
     return 1 if bad else 0
 
 
