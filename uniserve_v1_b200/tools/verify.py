@@ -368,7 +368,6 @@ def main(argv=None) -> int:
     for name, cls in mutants(BlockManager):
         r = explore(mk(cls), a.pages, min(a.depth, 4), a.keys)
         report["mutants"][name] = "caught" if r["violation"] else "MISSED"
-    print(json.dumps(report, indent=1))
     report["site_protocol"] = {"2 ranks x 2 sites x 3 passes": explore_site_protocol(2, 2, 3),
                                "3 ranks x 2 sites x 2 passes": explore_site_protocol(3, 2, 2),
                                "1 site (must fail)": explore_site_protocol(2, 1, 2)}
@@ -376,6 +375,7 @@ def main(argv=None) -> int:
         report["site_protocol"]["2 ranks x 2 sites x 3 passes"]["violation"] or \
         report["site_protocol"]["3 ranks x 2 sites x 2 passes"]["violation"] or \
         not report["site_protocol"]["1 site (must fail)"]["violation"]
+    print(json.dumps(report, indent=1))
     return 1 if bad else 0
 
 
