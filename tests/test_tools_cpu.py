@@ -362,3 +362,10 @@ def test_site_protocol_interleavings():
     assert explore_site_protocol(3, 3, 2)["violation"] is None
     bad = explore_site_protocol(2, 1, 2)["violation"]
     assert bad and "finds pass" in bad
+
+
+def test_ulysses_protocol_interleavings():
+    from uniserve_v1_b200.tools.verify import explore_ulysses_protocol
+    assert explore_ulysses_protocol(2, 3)["violation"] is None
+    assert explore_ulysses_protocol(3, 2)["violation"] is None
+    assert explore_ulysses_protocol(2, 2, second_barrier=False)["violation"]

@@ -356,6 +356,87 @@ def explore_site_protocol(world: int = 2, sites: int = 2, passes: int = 2) -> di
     return {"states": len(seen), "violation": None}
 
 
+def explore_programs(programs: list, n_bufs: int, n_bars: int) -> dict:
+    """Generic explorer: ``programs[r]`` is rank r's list of steps, run in order; ranks
+    interleave freely.  Steps: ("store", rank, buf, value) writes slot [buf][me] of ``rank``'s
+    memory; ("announce", rank, bar, epoch) raises flag [bar][me] on ``rank``; ("wait", bar,
+    epoch, peers) blocks until every peer's flag on this rank reached the epoch; ("load", buf,
+    src, value) reads slot [buf][src] of the own memory and expects ``value``."""
+    world = len(programs)
+    zero = tuple(tuple([None] * world) for _ in range(n_bufs))
+    start = (tuple([0] * world), tuple(zero for _ in range(world)),
+             tuple(tuple(tuple([0] * world) for _ in range(n_bars)) for _ in range(world)))
+
+    def put(mem, rank, a, b, val):
+        row = list(mem[rank][a])
+        row[b] = val
+        inner = list(mem[rank])
+        inner[a] = tuple(row)
+        return mem[:rank] + (tuple(inner),) + mem[rank + 1:]
+    seen, frontier = {start}, [start]
+    while frontier:
+        nxt = []
+        for pcs, mem, flag in frontier:
+            moved = False
+            for r in range(world):
+                if pcs[r] >= len(programs[r]):
+                    continue
+                op = programs[r][pcs[r]]
+                m2, f2 = mem, flag
+                if op[0] == "store":
+                    m2 = put(mem, op[1], op[2], r, op[3])
+                elif op[0] == "announce":
+                    f2 = put(flag, op[1], op[2], r, op[3])
+                elif op[0] == "wait":
+                    if any(flag[r][op[1]][q] < op[2] for q in op[3]):
+                        continue
+                else:
+                    got = mem[r][op[1]][op[2]]
+                    if got != op[3]:
+                        return {"states": len(seen), "violation":
+                                f"rank {r} loads buffer {op[1]} slot {op[2]}: expects {op[3]}, finds {got}"}
+                moved = True
+                state = (pcs[:r] + (pcs[r] + 1,) + pcs[r + 1:], m2, f2)
+                if state not in seen:
+                    seen.add(state)
+                    nxt.append(state)
+            if not moved and any(pcs[r] < len(programs[r]) for r in range(world)):
+                return {"states": len(seen), "violation": f"deadlock at {pcs}"}
+        frontier = nxt
+    return {"states": len(seen), "violation": None}
+
+
+def explore_ulysses_protocol(world: int = 2, layers: int = 2, second_barrier: bool = True) -> dict:
+    """The sequence-parallel attention of the video transformer (``parallel/ulysses.py``): per
+    layer every rank stores its share of q / k / v into every peer's QKV buffer (the projection
+    GEMM's epilogue), barrier, reads the whole QKV buffer and pushes its attention output into
+    every peer's output buffer (the flash kernel's epilogue), barrier, reads the output buffer
+    (the local output projection).  Both buffers are reused by the next layer without a third
+    barrier; the exploration shows that the two barriers per layer suffice in every interleaving
+    (a fast rank's next-layer q / k / v cannot land under a slow rank's attention, nor its next
+    output under a slow rank's projection).  Without the second barrier a rank reads the output
+    buffer before its peers pushed into it, which the exploration reports."""
+    QKV, ATT = 0, 1
+    programs = []
+    for r in range(world):
+        peers = [q for q in range(world) if q != r]
+        ops = []
+        for layer in range(layers):
+            for q in range(world):
+                ops.append(("store", q, QKV, layer))
+            ops.extend(("announce", q, 0, layer + 1) for q in peers)
+            ops.append(("wait", 0, layer + 1, peers))
+            ops.extend(("load", QKV, q, layer) for q in range(world))
+            for q in range(world):
+                ops.append(("store", q, ATT, layer))
+            if second_barrier:
+                ops.extend(("announce", q, 1, layer + 1) for q in peers)
+                ops.append(("wait", 1, layer + 1, peers))
+            ops.extend(("load", ATT, q, layer) for q in range(world))
+        programs.append(ops)
+    return explore_programs(programs, 2, 2)
+
+
 def main(argv=None) -> int:
     from ..engine.block_manager import BlockManager
     ap = argparse.ArgumentParser(prog="uniserve_v1_b200.tools.verify")
@@ -371,10 +452,17 @@ def main(argv=None) -> int:
     report["site_protocol"] = {"2 ranks x 2 sites x 3 passes": explore_site_protocol(2, 2, 3),
                                "3 ranks x 2 sites x 2 passes": explore_site_protocol(3, 2, 2),
                                "1 site (must fail)": explore_site_protocol(2, 1, 2)}
+    report["ulysses_protocol"] = {"2 ranks x 3 layers": explore_ulysses_protocol(2, 3),
+                                  "3 ranks x 2 layers": explore_ulysses_protocol(3, 2),
+                                  "one barrier per layer (must fail)":
+                                      explore_ulysses_protocol(2, 2, second_barrier=False)}
     bad = report["native"]["violation"] or "MISSED" in report["mutants"].values() or \
         report["site_protocol"]["2 ranks x 2 sites x 3 passes"]["violation"] or \
         report["site_protocol"]["3 ranks x 2 sites x 2 passes"]["violation"] or \
-        not report["site_protocol"]["1 site (must fail)"]["violation"]
+        not report["site_protocol"]["1 site (must fail)"]["violation"] or \
+        report["ulysses_protocol"]["2 ranks x 3 layers"]["violation"] or \
+        report["ulysses_protocol"]["3 ranks x 2 layers"]["violation"] or \
+        not report["ulysses_protocol"]["one barrier per layer (must fail)"]["violation"]
     print(json.dumps(report, indent=1))
     return 1 if bad else 0
 
