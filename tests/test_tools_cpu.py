@@ -369,3 +369,10 @@ def test_ulysses_protocol_interleavings():
     assert explore_ulysses_protocol(2, 3)["violation"] is None
     assert explore_ulysses_protocol(3, 2)["violation"] is None
     assert explore_ulysses_protocol(2, 2, second_barrier=False)["violation"]
+
+
+def test_tp_protocol_interleavings():
+    from uniserve_v1_b200.tools.verify import explore_tp_protocol
+    assert explore_tp_protocol(2, 4)["violation"] is None
+    assert explore_tp_protocol(3, 2)["violation"] is None
+    assert explore_tp_protocol(2, 3, norm_sites=1)["violation"] is None

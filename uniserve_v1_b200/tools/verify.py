@@ -437,6 +437,34 @@ def explore_ulysses_protocol(world: int = 2, layers: int = 2, second_barrier: bo
     return explore_programs(programs, 2, 2)
 
 
+def explore_tp_protocol(world: int = 2, blocks: int = 3, norm_sites: int = 2) -> dict:
+    """Tensor parallelism with the collectives fused into the GEMMs (``parallel/tp_fused.py``):
+    per MLP block the normalised rows of the previous block sit in every rank's gathered buffer
+    (written by all owners), barrier B0, the column-parallel GEMM reads them and the row-parallel
+    GEMM stores partial sums into the owners' slot buffers, barrier B1, the owner sums its slots
+    and stores the next normalised rows into every rank's gathered buffer of the next block.
+    The slot buffer is reused by every block and the gathered buffers alternate; the exploration
+    passes with two buffers and also with one (``norm_sites = 1``): a peer's B1 arrival already
+    lies after its reads of the gathered rows, so the alternation is a margin, not a need."""
+    SLOTS = norm_sites
+    programs = []
+    for r in range(world):
+        peers = [q for q in range(world) if q != r]
+        ops = [("store", q, 0, -1) for q in range(world)]          # rows of the embedding
+        for b in range(blocks):
+            src, dst = b % norm_sites, (b + 1) % norm_sites
+            ops.extend(("announce", q, 0, b + 1) for q in peers)
+            ops.append(("wait", 0, b + 1, peers))
+            ops.extend(("load", src, q, b - 1) for q in range(world))      # gathered rows
+            ops.extend(("store", q, SLOTS, b) for q in range(world))       # reduce-scatter
+            ops.extend(("announce", q, 1, b + 1) for q in peers)
+            ops.append(("wait", 1, b + 1, peers))
+            ops.extend(("load", SLOTS, q, b) for q in range(world))        # slot sum
+            ops.extend(("store", q, dst, b) for q in range(world))         # all-gather
+        programs.append(ops)
+    return explore_programs(programs, norm_sites + 1, 2)
+
+
 def main(argv=None) -> int:
     from ..engine.block_manager import BlockManager
     ap = argparse.ArgumentParser(prog="uniserve_v1_b200.tools.verify")
@@ -452,6 +480,9 @@ def main(argv=None) -> int:
     report["site_protocol"] = {"2 ranks x 2 sites x 3 passes": explore_site_protocol(2, 2, 3),
                                "3 ranks x 2 sites x 2 passes": explore_site_protocol(3, 2, 2),
                                "1 site (must fail)": explore_site_protocol(2, 1, 2)}
+    report["tp_protocol"] = {"2 ranks x 4 blocks": explore_tp_protocol(2, 4),
+                             "3 ranks x 2 blocks": explore_tp_protocol(3, 2),
+                             "one gathered buffer": explore_tp_protocol(2, 3, 1)}
     report["ulysses_protocol"] = {"2 ranks x 3 layers": explore_ulysses_protocol(2, 3),
                                   "3 ranks x 2 layers": explore_ulysses_protocol(3, 2),
                                   "one barrier per layer (must fail)":
@@ -460,6 +491,9 @@ def main(argv=None) -> int:
         report["site_protocol"]["2 ranks x 2 sites x 3 passes"]["violation"] or \
         report["site_protocol"]["3 ranks x 2 sites x 2 passes"]["violation"] or \
         not report["site_protocol"]["1 site (must fail)"]["violation"] or \
+        report["tp_protocol"]["2 ranks x 4 blocks"]["violation"] or \
+        report["tp_protocol"]["3 ranks x 2 blocks"]["violation"] or \
+        report["tp_protocol"]["one gathered buffer"]["violation"] or \
         report["ulysses_protocol"]["2 ranks x 3 layers"]["violation"] or \
         report["ulysses_protocol"]["3 ranks x 2 layers"]["violation"] or \
         not report["ulysses_protocol"]["one barrier per layer (must fail)"]["violation"]
