@@ -415,7 +415,12 @@ def explore_ulysses_protocol(world: int = 2, layers: int = 2, second_barrier: bo
     barrier; the exploration shows that the two barriers per layer suffice in every interleaving
     (a fast rank's next-layer q / k / v cannot land under a slow rank's attention, nor its next
     output under a slow rank's projection).  Without the second barrier a rank reads the output
-    buffer before its peers pushed into it, which the exploration reports."""
+    buffer before its peers pushed into it, which the exploration reports.
+
+    The expert exchange (``csrc/fused/ep_exchange.cu``) has the same shape with flags in place
+    of barriers: dispatch into every expert rank's window, "dispatched" flags, sort / GEMMs read
+    the window and push into the token owners' combine buffers, "combined" flags, combine reads;
+    its single-buffered windows are covered by the same exploration."""
     QKV, ATT = 0, 1
     programs = []
     for r in range(world):
