@@ -241,18 +241,10 @@ def test_video_job_resumes_from_its_last_step_boundary():
     assert calls["n"] == svc2.steps + 1 and not svc2.latent_pool
 
 
-def test_chat_with_an_image_on_the_hybrid_family():
-    """An `image_url` part (data URL) is decoded, cut into patch rows, run through the vision
-    tower and spliced into the prompt; the answer is the model's own multimodal decoding.
-    A deployment without a tower refuses images."""
-    import base64
-    import io
-    import numpy as np
-    from PIL import Image
+def _hybrid_mm_engine():
     from uniserve_v1_b200.engine.dense_state import DenseStateEngine
-    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel, Qwen35Multimodal
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel
     from uniserve_v1_b200.models.qwen3_vl_vision import Qwen3VLVisionTower, VisionConfig
-    from uniserve_v1_b200.server import images as IM
     cfg = Qwen35MoeModel.tiny_config()
     cfg.mrope_section, cfg.image_token_id = (2, 1, 1), 1000
     model = Qwen35MoeModel(cfg, "cpu", torch.float32).init_random(seed=0)
@@ -281,7 +273,22 @@ def test_chat_with_an_image_on_the_hybrid_family():
                     return torch.randn(*shp, generator=g) * 0.05
             return torch.ones(32) if n.endswith("weight") else torch.zeros(32)     # block norms
     tower.load_state(Rand(), prefix="")
-    eng = DenseStateEngine(model, max_num_seqs=4, max_model_len=512, tower=tower)
+    return DenseStateEngine(model, max_num_seqs=4, max_model_len=512, tower=tower), model, tower
+
+
+def test_chat_with_an_image_on_the_hybrid_family():
+    """An `image_url` part (data URL) is decoded, cut into patch rows, run through the vision
+    tower and spliced into the prompt; the answer is the model's own multimodal decoding.
+    A deployment without a tower refuses images."""
+    import base64
+    import io
+    import numpy as np
+    from PIL import Image
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel, Qwen35Multimodal
+    from uniserve_v1_b200.models.qwen3_vl_vision import Qwen3VLVisionTower, VisionConfig
+    from uniserve_v1_b200.server import images as IM
+    eng, model, tower = _hybrid_mm_engine()
     pkg = Package.parse('model = "random:tiny"\nserved_model_name = "hybrid"\n')
     tok = ByteTokenizer(1024, 1023)
     app = create_app(package=pkg, engine=eng, tokenizer=tok, served_model_name="hybrid")
@@ -340,3 +347,72 @@ def test_dense_state_engine_shapes_logits_like_the_paged_engine():
         rep = c.post("/v1/chat/completions", json=dict(base, repetition_penalty=1.8,
                                                        presence_penalty=1.0)).json()
         assert rep["usage"]["completion_tokens"] == 6
+
+
+def test_video_frames_become_timestamped_images(tmp_path):
+    """A `video_url` part: frames are sampled, cut into temporal patches and enter the prompt as
+    one timestamped placeholder group per patch; the rows equal the image path's rows for the
+    same frame pair."""
+    import cv2
+    import numpy as np
+    from uniserve_v1_b200.server import images as IM
+    from uniserve_v1_b200.server.chat import _flatten_content
+    path = str(tmp_path / "clip.avi")
+    wr = cv2.VideoWriter(path, cv2.VideoWriter_fourcc(*"MJPG"), 8.0, (96, 64))
+    assert wr.isOpened()
+    rng = np.random.RandomState(0)
+    base = rng.randint(0, 256, (64, 96, 3), dtype=np.uint8)
+    for i in range(16):
+        wr.write(np.roll(base, 4 * i, axis=1))
+    wr.release()
+    frames, secs = IM.load_video("file://" + path, fps=2.0)
+    assert frames.shape == (4, 64, 96, 3) and secs == [0.0, 0.5, 1.0, 1.5]
+    rows, grid = IM.preprocess_video(frames)
+    assert grid == (2, 4, 6) and rows.shape == (48, 3 * 2 * 16 * 16)
+    # temporal patch 0 holds frames 0 and 1: channel-major, then the two frames
+    one, g1 = IM.patch_rows(((torch.from_numpy(frames[:2].copy()).permute(0, 3, 1, 2).float() / 255)
+                             - 0.5) / 0.5, 16, 2, 2)
+    assert g1 == (1, 4, 6) and torch.equal(one, rows[:24])
+    assert IM.video_prompt(secs) == ("<0.2 seconds><|vision_start|><|image_pad|><|vision_end|>"
+                                     "<1.2 seconds><|vision_start|><|image_pad|><|vision_end|>")
+    assert _flatten_content([{"type": "text", "text": "see "},
+                             {"type": "video_url", "video_url": {"url": "file://x"}}]) == \
+        "see <|vision_start|><|video_pad|><|vision_end|>"
+    assert IM.collect_media([{"role": "user", "content": [
+        {"type": "video_url", "video_url": {"url": "file://" + path}},
+        {"type": "image_url", "image_url": "data:x"}]}]) == [("video", "file://" + path),
+                                                              ("image", "data:x")]
+
+
+def test_chat_with_a_video_on_the_hybrid_family(tmp_path):
+    """End to end: a `video_url` file is sampled, every temporal patch becomes a timestamped
+    image group of the prompt, and the answer is the model's own decoding of those ids and rows."""
+    import cv2
+    import numpy as np
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35Multimodal
+    from uniserve_v1_b200.server import images as IM
+    path = str(tmp_path / "clip.avi")
+    wr = cv2.VideoWriter(path, cv2.VideoWriter_fourcc(*"MJPG"), 8.0, (96, 64))
+    base = np.random.RandomState(1).randint(0, 256, (64, 96, 3), dtype=np.uint8)
+    for i in range(16):
+        wr.write(np.roll(base, 4 * i, axis=1))
+    wr.release()
+    eng, model, tower = _hybrid_mm_engine()
+    pkg = Package.parse('model = "random:tiny"\nserved_model_name = "hybrid"\n')
+    app = create_app(package=pkg, engine=eng, tokenizer=ByteTokenizer(1024, 1023),
+                     served_model_name="hybrid")
+    body = {"model": "hybrid", "max_tokens": 4, "temperature": 0, "ignore_eos": True,
+            "messages": [{"role": "user", "content": [
+                {"type": "text", "text": "what happens? "},
+                {"type": "video_url", "video_url": {"url": "file://" + path}}]}]}
+    with TestClient(app) as c:
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200, r.text
+        rid = next(iter(eng.requests))
+        req = eng.requests[rid]
+        frames, secs = IM.load_video("file://" + path)
+        rows, (gt, gh, gw) = IM.preprocess_video(frames)
+        assert req.prompt_ids.count(1000) == gt * (gh // 2) * (gw // 2) == 12
+        grids = [(1, gh, gw)] * gt
+        want = Qwen35Multimodal(model, tower).generate(req.prompt_ids, rows, grids, 4)
+        assert req.output_ids == want and r.json()["usage"]["completion_tokens"] == 4

@@ -373,15 +373,27 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
                 return _err(400, f"chat template: {e}", param="messages")
             media = None
             from . import images as IM
-            urls = IM.collect(msgs)
+            urls = IM.collect_media(msgs)
             if urls:
                 mm = getattr(s.engine, "mm", None)
                 if mm is None:
                     return _err(400, "this deployment does not take images", param="messages")
                 try:
                     vc = mm.tower.cfg
-                    pre = [IM.preprocess(IM.load_image(u), vc.patch_size, vc.temporal_patch_size,
-                                         vc.spatial_merge_size) for u in urls]
+                    pre = []
+                    for kind, u in urls:
+                        if kind == "image":
+                            pre.append(IM.preprocess(IM.load_image(u), vc.patch_size,
+                                                     vc.temporal_patch_size, vc.spatial_merge_size))
+                            continue
+                        # a video is a run of timestamped images, one per temporal patch
+                        frames, secs = IM.load_video(u)
+                        rows, (gt, gh, gw) = IM.preprocess_video(
+                            frames, vc.patch_size, vc.temporal_patch_size, vc.spatial_merge_size)
+                        per = gh * gw
+                        pre.extend((rows[i * per:(i + 1) * per], (1, gh, gw)) for i in range(gt))
+                        prompt = prompt.replace("<|vision_start|><|video_pad|><|vision_end|>",
+                                                IM.video_prompt(secs, vc.temporal_patch_size), 1)
                 except ValueError as e:
                     return _err(400, str(e), param="messages")
                 grids = [g for _, g in pre]

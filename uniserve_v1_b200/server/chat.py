@@ -58,6 +58,8 @@ def _flatten_content(content):
             out.append(part.get("text", ""))
         elif t == "image_url":
             out.append("<|vision_start|><|image_pad|><|vision_end|>")
+        elif t == "video_url":
+            out.append("<|vision_start|><|video_pad|><|vision_end|>")
         else:
             raise ValueError(f"unsupported content part type {t!r}")
     return "".join(out)

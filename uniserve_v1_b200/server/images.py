@@ -1,5 +1,5 @@
-"""Image inputs of chat requests: decode, resize, normalise and cut into the patch rows the
-vision tower reads.
+"""Image and video inputs of chat requests: decode, resize, normalise and cut into the patch
+rows the vision tower reads.
 
 ``image_url`` content parts carry ``data:`` URLs (base64) or ``file://`` paths; remote URLs
 are refused (a serving process does not fetch from the network on a client's behalf).
@@ -8,6 +8,8 @@ Preprocessing follows the Qwen-VL image processor: both sides become multiples o
 the same aspect ratio, values are scaled to [0, 1] and normalised with mean = std = 0.5,
 a still image is repeated ``temporal_patch`` times, and patches leave in merge-block order
 as rows of ``C * T * P * P`` values - the layout ``Qwen3VLVisionTower.forward`` expects.
+A video is sampled at a fixed rate; every temporal patch (two frames) becomes one image-like
+group of rows that the prompt introduces with its time ("<1.2 seconds>").
 
 Reference behaviour: crates/processing (image and frame preparation, reference project
 path).
@@ -98,12 +100,86 @@ def expand_placeholders(ids: list, image_token_id: int, grids: list, merge: int)
 
 def collect(messages: list) -> list:
     """The image URLs of a chat request, in prompt order."""
-    urls = []
+    return [u for kind, u in collect_media(messages) if kind == "image"]
+
+
+def collect_media(messages: list) -> list:
+    """(kind, url) of every ``image_url`` / ``video_url`` part, in prompt order."""
+    out = []
     for m in messages:
         c = m.get("content")
         if isinstance(c, list):
             for part in c:
-                if part.get("type") == "image_url":
-                    u = part.get("image_url")
-                    urls.append(u.get("url") if isinstance(u, dict) else u)
-    return urls
+                t = part.get("type")
+                if t in ("image_url", "video_url"):
+                    u = part.get(t)
+                    out.append((t[:5], u.get("url") if isinstance(u, dict) else u))
+    return out
+
+
+def load_video(url: str, fps: float = 2.0, max_frames: int = 64):
+    """Decodes a ``file://`` (or base64 ``data:``) video and samples it at ``fps``: returns
+    (frames uint8 [F, H, W, 3] with F even, seconds of each sampled frame)."""
+    import os
+    import tempfile
+
+    import cv2
+    tmp = None
+    if url.startswith("data:"):
+        head, _, payload = url.partition(",")
+        if not head.endswith(";base64"):
+            raise ValueError("data URLs must be base64-encoded")
+        fd, tmp = tempfile.mkstemp(suffix=".mp4")
+        with os.fdopen(fd, "wb") as f:
+            f.write(base64.b64decode(payload, validate=True))
+        path = tmp
+    elif url.startswith("file://"):
+        path = url[7:]
+    else:
+        raise ValueError("video URLs must be data: or file:// URLs; remote URLs are not fetched")
+    try:
+        cap = cv2.VideoCapture(path)
+        native = cap.get(cv2.CAP_PROP_FPS) or 0.0
+        frames = []
+        while True:
+            ok, f = cap.read()
+            if not ok:
+                break
+            frames.append(cv2.cvtColor(f, cv2.COLOR_BGR2RGB))
+        cap.release()
+    finally:
+        if tmp:
+            os.unlink(tmp)
+    if not frames:
+        raise ValueError("cannot decode the video")
+    native = native if native > 0 else 24.0
+    step = max(1.0, native / fps)
+    idx = [int(round(i * step)) for i in range(int(len(frames) / step) or 1)]
+    idx = [i for i in idx if i < len(frames)][:max_frames]
+    if len(idx) % 2:
+        idx.append(idx[-1])                    # whole temporal patches of two frames
+    return np.stack([frames[i] for i in idx]), [i / native for i in idx]
+
+
+def preprocess_video(frames: np.ndarray, patch: int = 16, temporal_patch: int = 2, merge: int = 2,
+                     min_pixels: int = 64 * 64, max_pixels: int = 256 * 28 * 28):
+    """uint8 [F, H, W, 3] -> (rows float32 [t * h * w, C * T * P * P], grid (t, h, w)); every
+    frame gets the size ``smart_resize`` picks for the first one."""
+    from PIL import Image
+    H, W = frames.shape[1:3]
+    h, w = smart_resize(H, W, patch * merge, min_pixels, max_pixels)
+    out = []
+    for f in frames:
+        if (h, w) != (H, W):
+            f = np.asarray(Image.fromarray(f).resize((w, h), Image.BICUBIC))
+        out.append(torch.from_numpy(f.copy()).permute(2, 0, 1).float() / 255.0)
+    x = (torch.stack(out) - 0.5) / 0.5
+    return patch_rows(x, patch, temporal_patch, merge)
+
+
+def video_prompt(seconds: list, temporal_patch: int = 2) -> str:
+    """The text that stands for a video: one timestamped, delimited placeholder per temporal
+    patch (the language model sees every pair of frames as an image at its time)."""
+    groups = [sum(seconds[i:i + temporal_patch]) / temporal_patch
+              for i in range(0, len(seconds), temporal_patch)]
+    return "".join(f"<{t:.1f} seconds><|vision_start|><|image_pad|><|vision_end|>" for t in groups)
