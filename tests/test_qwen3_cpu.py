@@ -294,3 +294,32 @@ def test_hybrid_decoder_batched_decode_equals_sequential():
     model.decode_batch = inner
     assert calls["n"] >= 4
     assert outs == [DenseStateEngine(model).generate([p.tolist()], sp)[0] for p in prompts]
+
+
+def test_dense_state_engine_reuses_state_snapshots_of_a_shared_prefix():
+    """Recurrent decoders cache whole-state snapshots at interval boundaries of a prompt: a
+    later request with the same prefix (and the same isolation salt) starts from the longest
+    one, reads only the rest, and answers the same."""
+    import torch
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel
+    model = Qwen35MoeModel(Qwen35MoeModel.tiny_config(), "cpu", torch.float32).init_random(seed=0)
+    g = torch.Generator().manual_seed(3)
+    shared = torch.randint(0, 1000, (70,), generator=g).tolist()
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    cold = DenseStateEngine(model, state_cache_entries=0)
+    want_a = cold.generate([shared + [1, 2, 3]], sp)[0]
+    want_b = cold.generate([shared + [9, 8]], sp)[0]
+    assert cold.stats()["cached_tokens"] == 0
+    eng = DenseStateEngine(model, state_interval=16, prefill_chunk=32)
+    assert eng.generate([shared + [1, 2, 3]], sp)[0] == want_a
+    first = eng.stats()["prefill_tokens"]
+    assert eng.generate([shared + [9, 8]], sp)[0] == want_b
+    st = eng.stats()
+    assert st["cached_tokens"] == 64 and st["prefill_tokens"] - first == 72 - 64
+    rid = eng.add_request(shared + [9, 8], sp, cache_salt="tenant-2")       # another tenant
+    while eng.has_work():
+        eng.step()
+    assert eng.requests[rid].num_cached == 0 and eng.requests[rid].output_ids == want_b
+    assert eng.blocks.flush() > 0 and not eng.state_cache

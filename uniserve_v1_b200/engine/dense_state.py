@@ -10,15 +10,19 @@ Sampling follows the request's parameters with draws addressed by (seed, positio
 a request produces the same tokens whatever else is running.  Requests that have read
 their prompt advance together when the model offers ``decode_batch`` (projections, experts,
 the delta rule and the convolution run on all rows at once, attention per sequence);
-prompt chunks run one sequence at a time.
+prompt chunks run one sequence at a time.  Prompts share work through snapshots of the whole
+state at interval boundaries (``state_interval``), the recurrent counterpart of prefix pages.
 
 Reference behaviour: crates/engine/src/runner/causal_lm (state slots and
 ``state_interval`` checkpoints of recurrent layers) - reference project path.
 """
 from __future__ import annotations
 
+import copy
+import hashlib
 import itertools
 import time
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Optional
 
@@ -36,23 +40,46 @@ class DenseStateConfig:
 
 
 class _NoPages:
-    enable_prefix_cache = False
+    """The face of a block manager for the admin routes: the prefix cache here holds state
+    snapshots, not pages."""
+
+    def __init__(self, engine):
+        self._e = engine
+
+    @property
+    def enable_prefix_cache(self) -> bool:
+        return self._e.enable_prefix_cache
+
+    @enable_prefix_cache.setter
+    def enable_prefix_cache(self, on: bool) -> None:
+        self._e.enable_prefix_cache = bool(on)
 
     def flush(self) -> int:
-        return 0
+        n = len(self._e.state_cache)
+        self._e.state_cache.clear()
+        return n
 
 
 class DenseStateEngine:
     def __init__(self, model, max_num_seqs: int = 8, max_model_len: int = 4096,
-                 prefill_chunk: int = 512, tower=None):
+                 prefill_chunk: int = 512, tower=None, state_interval: int = 64,
+                 state_cache_entries: int = 32):
         self.model = model
+        # Prefix cache of recurrent decoders: a snapshot of the whole per-sequence state at
+        # every ``state_interval`` tokens of a prompt, keyed by the chained hash of the tokens
+        # before it (and the isolation salt).  A later request with the same prefix starts from
+        # the longest snapshot instead of reading those tokens again.
+        self.state_interval = max(1, int(state_interval))
+        self.state_cache_entries = int(state_cache_entries)
+        self.state_cache: "OrderedDict[bytes, tuple]" = OrderedDict()
+        self.enable_prefix_cache = state_cache_entries > 0
         # with a vision tower requests may carry images: (patch rows, grids) in ``media``
         self.mm = None
         if tower is not None:
             from ..models.qwen3_5 import Qwen35Multimodal
             self.mm = Qwen35Multimodal(model, tower)
         self.config = DenseStateConfig(max_num_seqs, max_model_len, prefill_chunk)
-        self.blocks = _NoPages()
+        self.blocks = _NoPages(self)
         self.failed: Optional[str] = None
         self.waiting: list = []
         self.running: list = []
@@ -60,7 +87,7 @@ class DenseStateEngine:
         self.states: dict = {}
         self._ids = itertools.count(1)
         self._stats = {"prefill_tokens": 0, "decode_tokens": 0, "finished": 0, "steps": 0,
-                       "preemptions": 0}
+                       "preemptions": 0, "cached_tokens": 0}
 
     # ------------------------------------------------------------- requests --
     def add_request(self, prompt_ids, params: Optional[SamplingParams] = None,
@@ -143,6 +170,45 @@ class DenseStateEngine:
             torch.tensor([req.num_tokens], dtype=torch.int64, device=dev))
         return int(tok[0])
 
+    # ------------------------------------------------------------ prefix states --
+    def _prefix_keys(self, req: Request) -> list:
+        """Chained keys of the prompt at every multiple of the interval (the last token is
+        always read, so its logits exist)."""
+        import numpy as np
+        iv, ids = self.state_interval, req.prompt_ids
+        h = hashlib.sha256(("state\0" + (req.cache_salt or "")).encode()).digest()
+        keys = []
+        for hi in range(iv, len(ids), iv):
+            h = hashlib.sha256(h + np.asarray(ids[hi - iv:hi], dtype="<i4").tobytes()).digest()
+            keys.append((hi, h))
+        return keys
+
+    def _restore_prefix(self, req: Request) -> None:
+        if not self.enable_prefix_cache or getattr(req, "media", None) is not None or \
+                req.output_ids:
+            return
+        req._keys = self._prefix_keys(req)
+        for hi, key in reversed(req._keys):
+            snap = self.state_cache.get(key)
+            if snap is not None:
+                self.state_cache.move_to_end(key)
+                self.states[req.request_id] = copy.deepcopy(snap)
+                req.num_computed = req.num_cached = hi
+                self._stats["cached_tokens"] += hi
+                return
+
+    def _snapshot(self, req: Request) -> None:
+        keys = getattr(req, "_keys", None)
+        if not keys or req.num_computed % self.state_interval or \
+                req.num_computed > len(req.prompt_ids):
+            return
+        key = next((k for hi, k in keys if hi == req.num_computed), None)
+        if key is None or key in self.state_cache:
+            return
+        self.state_cache[key] = copy.deepcopy(self.states[req.request_id])
+        while len(self.state_cache) > self.state_cache_entries:
+            self.state_cache.popitem(last=False)
+
     def _forward_media(self, req: Request, chunk: torch.Tensor, st: list, n: int):
         """A chunk of a request with images: vision rows stand at the placeholder tokens and
         positions are the three-axis ones; tokens after the prompt continue on all axes."""
@@ -187,6 +253,7 @@ class DenseStateEngine:
             req = self.waiting.pop(0)
             req.state = RequestState.RUNNING
             self.states[req.request_id] = self.model.new_state()
+            self._restore_prefix(req)
             self.running.append(req)
         outs = []
         self._stats["steps"] += 1
@@ -209,6 +276,12 @@ class DenseStateEngine:
             ids = req.all_ids
             todo = len(ids) - req.num_computed
             n = min(todo, self.config.prefill_chunk)
+            if n > 1 and getattr(req, "_keys", None):
+                # chunks end on snapshot boundaries while the prompt is being read
+                iv = self.state_interval
+                edge = (req.num_computed // iv + 1) * iv
+                span = max(iv, (self.config.prefill_chunk // iv) * iv)
+                n = min(n, edge - req.num_computed + span - iv)
             chunk = torch.tensor(ids[req.num_computed:req.num_computed + n], device=dev)
             if req.request_id in batched:
                 logits = batched[req.request_id]
@@ -217,6 +290,7 @@ class DenseStateEngine:
             else:
                 logits = self.model.forward(chunk, st, req.num_computed)
             req.num_computed += n
+            self._snapshot(req)
             self._stats["decode_tokens" if (n == 1 and req.output_ids) else "prefill_tokens"] += n
             if req.num_computed < len(ids):
                 continue                    # still reading its prompt
@@ -229,6 +303,7 @@ class DenseStateEngine:
             if reason is not None:
                 self._finish(req, reason)
             outs.append(StepOutput(req.request_id, [tok], reason is not None, reason,
+                                   num_cached_tokens=req.num_cached,
                                    logprobs=[req.logprobs[-1]] if (p_lp and req.logprobs) else None))
         return outs
 
