@@ -421,3 +421,64 @@ def test_qwen3_vl_with_deepstack_matches_transformers(tmp_path):
     while eng.has_work():
         eng.step()
     assert eng.requests[rid].output_ids == gen
+
+
+def test_qwen3_vl_moe_matches_transformers(tmp_path):
+    """The expert variant of Qwen3-VL (stacked expert tensors, routed MLP in every layer) with
+    an image in the prompt."""
+    import pytest
+    pytest.importorskip("transformers")
+    from transformers.models.qwen3_vl_moe.configuration_qwen3_vl_moe import (
+        Qwen3VLMoeConfig, Qwen3VLMoeTextConfig, Qwen3VLMoeVisionConfig)
+    from transformers.models.qwen3_vl_moe.modeling_qwen3_vl_moe import \
+        Qwen3VLMoeForConditionalGeneration
+    from uniserve_v1_b200.checkpoint.safetensors_io import (CheckpointLoader, resolve_family,
+                                                            save_file)
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35Multimodal
+    from uniserve_v1_b200.models.qwen3_vl import Qwen3VLDenseModel, Qwen3VLTextConfig
+    from uniserve_v1_b200.models.qwen3_vl_vision import Qwen3VLVisionTower, VisionConfig
+    tc = Qwen3VLMoeTextConfig(vocab_size=300, hidden_size=64, intermediate_size=96,
+                              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                              head_dim=16, num_experts=4, num_experts_per_tok=2,
+                              moe_intermediate_size=32, max_position_embeddings=256,
+                              eos_token_id=299,
+                              rope_parameters={"rope_type": "default", "rope_theta": 10000.0,
+                                               "mrope_section": [4, 2, 2],
+                                               "mrope_interleaved": True})
+    vc = Qwen3VLMoeVisionConfig(depth=2, hidden_size=32, intermediate_size=48, num_heads=2,
+                                patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+                                out_hidden_size=64, num_position_embeddings=16,
+                                deepstack_visual_indexes=[1])
+    cfg = Qwen3VLMoeConfig(text_config=tc.to_dict(), vision_config=vc.to_dict(),
+                           image_token_id=290, video_token_id=291, vision_start_token_id=292,
+                           vision_end_token_id=293)
+    torch.manual_seed(0)
+    hf = Qwen3VLMoeForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "experts" in n:
+                p.copy_(torch.randn_like(p) * 0.1)
+    save_file({k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()},
+              tmp_path / "model.safetensors")
+    d = cfg.to_dict()
+    d["architectures"] = ["Qwen3VLMoeForConditionalGeneration"]
+    (tmp_path / "config.json").write_text(json.dumps(d))
+    assert resolve_family(tmp_path) == "qwen3_vl"
+    ld = CheckpointLoader(tmp_path)
+    tcfg = Qwen3VLTextConfig.from_hf(ld.config)
+    assert tcfg.num_experts == 4 and tcfg.is_moe_layer(0)
+    text = Qwen3VLDenseModel(tcfg, "cpu", torch.float32).load_state(ld)
+    tower = Qwen3VLVisionTower(VisionConfig.from_hf(ld.config), "cpu", torch.float32).load_state(ld)
+    grid = (1, 4, 4)
+    prompt = [5, 292] + [290] * 4 + [293, 40, 7]
+    pixels = torch.randn(16, 3 * 2 * 4 * 4, generator=torch.Generator().manual_seed(1))
+    types = torch.tensor([[1 if t == 290 else 0 for t in prompt]])
+    kw = dict(input_ids=torch.tensor([prompt]), pixel_values=pixels,
+              image_grid_thw=torch.tensor([grid]), mm_token_type_ids=types)
+    with torch.no_grad():
+        want = hf(**kw).logits[0]
+        gen = hf.generate(**kw, max_new_tokens=4, do_sample=False)[0, len(prompt):].tolist()
+    mm = Qwen35Multimodal(text, tower)
+    logits, _ = mm.prefill(prompt, pixels, [grid], text.new_state())
+    torch.testing.assert_close(logits, want, atol=3e-4, rtol=2e-3)
+    assert mm.generate(prompt, pixels, [grid], 4) == gen

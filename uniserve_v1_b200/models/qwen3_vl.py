@@ -1,5 +1,5 @@
-"""Qwen3-VL language model (dense Qwen3 decoder with three-axis rotary positions and
-deep-stack inputs) on a dense per-sequence state.
+"""Qwen3-VL language model (Qwen3 decoder, dense or with experts, with three-axis rotary
+positions and deep-stack inputs) on a dense per-sequence state.
 
 Differences from the text-only Qwen3 decoder: the rotary embedding covers the whole head
 and its frequencies are shared out between the temporal, row and column position
@@ -9,7 +9,7 @@ layers.  The class has the interface of ``Qwen35MoeModel`` (``new_state`` /
 ``forward(ids, state, pos0, embeds, positions3, deepstack)``), so the dense-state engine
 and ``Qwen35Multimodal`` drive it unchanged.
 
-Hugging Face names (``Qwen3VLForConditionalGeneration``): ``model.language_model.*``,
+Hugging Face names (``Qwen3VLForConditionalGeneration``, ``Qwen3VLMoeForConditionalGeneration``): ``model.language_model.*``,
 ``model.visual.*``, ``lm_head.weight``.
 
 Reference behaviour: crates/models/src/qwen3/vl.rs, crates/models/src/qwen3/positions.rs
@@ -43,6 +43,15 @@ class Qwen3VLTextConfig:
     image_token_id: int = 151655
     video_token_id: int = 151656
     tie_word_embeddings: bool = False
+    num_experts: int = 0                 # > 0: Qwen3-VL-MoE (experts in every sparse layer)
+    num_experts_per_tok: int = 8
+    moe_intermediate_size: int = 768
+    decoder_sparse_step: int = 1
+    mlp_only_layers: tuple = ()
+
+    def is_moe_layer(self, i: int) -> bool:
+        return (self.num_experts > 0 and i not in self.mlp_only_layers
+                and (i + 1) % self.decoder_sparse_step == 0)
 
     @classmethod
     def from_hf(cls, d: dict) -> "Qwen3VLTextConfig":
@@ -52,6 +61,9 @@ class Qwen3VLTextConfig:
         kw["rope_theta"] = float(rp.get("rope_theta", d.get("rope_theta", 5e6)))
         kw["mrope_section"] = tuple(rp.get("mrope_section", (24, 20, 20)))
         kw.setdefault("head_dim", d["hidden_size"] // d["num_attention_heads"])
+        kw["mlp_only_layers"] = tuple(kw.get("mlp_only_layers") or ())
+        if not kw.get("num_experts") and d.get("num_local_experts"):    # newer config key
+            kw["num_experts"] = int(d["num_local_experts"])
         for k in ("image_token_id", "video_token_id", "tie_word_embeddings"):
             if outer.get(k) is not None:
                 kw[k] = outer[k]
@@ -85,10 +97,17 @@ class Qwen3VLDenseModel:
                     "qkv": torch.cat([get(a + f"{n}_proj.weight") for n in "qkv"], 0),
                     "o": get(a + "o_proj.weight"),
                     "q_norm": get(a + "q_norm.weight", torch.float32),
-                    "k_norm": get(a + "k_norm.weight", torch.float32),
-                    "w13": torch.cat([get(p + "mlp.up_proj.weight"),
-                                      get(p + "mlp.gate_proj.weight")], 0),
-                    "w2": get(p + "mlp.down_proj.weight")}
+                    "k_norm": get(a + "k_norm.weight", torch.float32)}
+            if c.is_moe_layer(i):
+                I = c.moe_intermediate_size
+                gu = get(p + "mlp.experts.gate_up_proj")             # [E, 2I, H]: gate, then up
+                w[i]["router"] = get(p + "mlp.gate.weight")
+                w[i]["w13"] = torch.cat([gu[:, I:], gu[:, :I]], 1).contiguous()
+                w[i]["w2"] = get(p + "mlp.experts.down_proj").contiguous()
+            else:
+                w[i]["w13"] = torch.cat([get(p + "mlp.up_proj.weight"),
+                                         get(p + "mlp.gate_proj.weight")], 0)
+                w[i]["w2"] = get(p + "mlp.down_proj.weight")
         return self
 
     def new_state(self) -> list:
@@ -130,7 +149,12 @@ class Qwen3VLDenseModel:
             x = x + self._attention(L, R.rmsnorm(x, L["in_norm"], c.rms_norm_eps), state[i],
                                     positions3)
             n = R.rmsnorm(x, L["post_norm"], c.rms_norm_eps)
-            x = x + F.linear(F.linear_gated(n, L["w13"]), L["w2"])
+            if "router" in L:
+                logits = F.linear(n, L["router"], out_dtype=torch.float32)
+                ids_, wts = F.topk_softmax(logits, c.num_experts_per_tok, True)
+                x = x + F.moe_experts(n, ids_, wts, L["w13"], L["w2"])
+            else:
+                x = x + F.linear(F.linear_gated(n, L["w13"]), L["w2"])
             if deepstack is not None and i < len(deepstack[1]) and deepstack[0].numel():
                 x = x.clone()
                 x[deepstack[0]] += deepstack[1][i].to(x.dtype)
