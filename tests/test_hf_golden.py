@@ -482,3 +482,36 @@ def test_qwen3_vl_moe_matches_transformers(tmp_path):
     logits, _ = mm.prefill(prompt, pixels, [grid], text.new_state())
     torch.testing.assert_close(logits, want, atol=3e-4, rtol=2e-3)
     assert mm.generate(prompt, pixels, [grid], 4) == gen
+
+
+def test_qwen3_5_dense_variant_matches_transformers(tmp_path):
+    """`Qwen3_5ForCausalLM`: the hybrid decoder with one gated MLP per layer instead of experts."""
+    import pytest
+    pytest.importorskip("transformers")
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5TextConfig
+    from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5ForCausalLM
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, save_file
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35Config, Qwen35MoeModel
+    hf_cfg = Qwen3_5TextConfig(
+        vocab_size=200, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=32, linear_num_key_heads=2,
+        linear_num_value_heads=4, linear_key_head_dim=16, linear_value_head_dim=16,
+        max_position_embeddings=128,
+        layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"])
+    torch.manual_seed(4)
+    hf = Qwen3_5ForCausalLM(hf_cfg).float().eval()
+    save_file({k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()},
+              tmp_path / "model.safetensors")
+    (tmp_path / "config.json").write_text(json.dumps(hf_cfg.to_dict()))
+    ld = CheckpointLoader(tmp_path)
+    cfg = Qwen35Config.from_hf(ld.config)
+    assert cfg.num_experts == 0 and cfg.intermediate_size == 96
+    model = Qwen35MoeModel(cfg, "cpu", torch.float32).load_state(ld)
+    ids = torch.randint(0, 200, (23,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids[None]).logits[0]
+        gen = hf.generate(ids[None], max_new_tokens=5, do_sample=False)[0, 23:].tolist()
+    st = model.new_state()
+    got = torch.cat([model.forward(ids[:20], st, 0), model.forward(ids[20:], st, 20)])
+    torch.testing.assert_close(got, want, atol=2e-4, rtol=2e-3)
+    assert model.generate(ids.tolist(), 5)[:len(gen)] == gen

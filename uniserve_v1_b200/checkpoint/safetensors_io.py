@@ -175,7 +175,8 @@ def resolve_hub(spec: str, cache_dir: Optional[str] = None) -> Path:
 FAMILIES = {
     "Qwen3MoeForCausalLM": "qwen3_moe", "Qwen3ForCausalLM": "qwen3_moe",
     "Qwen3_5MoeForConditionalGeneration": "qwen3_5_moe", "Qwen3_5MoeForCausalLM": "qwen3_5_moe",
-    "Qwen3NextForCausalLM": "qwen3_5_moe", "Qwen3VLForConditionalGeneration": "qwen3_vl",
+    "Qwen3NextForCausalLM": "qwen3_5_moe", "Qwen3_5ForCausalLM": "qwen3_5_moe",
+    "Qwen3_5ForConditionalGeneration": "qwen3_5_moe", "Qwen3VLForConditionalGeneration": "qwen3_vl",
     "Qwen3VLMoeForConditionalGeneration": "qwen3_vl",
     "MiniMaxH3Pipeline": "minimax_h3", "FastH3Pipeline": "minimax_h3",
     "MiniMaxH3Transformer3DModel": "minimax_h3",

@@ -53,6 +53,7 @@ class Qwen35Config:
     num_experts_per_tok: int = 8
     moe_intermediate_size: int = 512
     shared_expert_intermediate_size: int = 512
+    intermediate_size: int = 0              # dense variant (num_experts = 0): MLP width
     eos_token_id: int = 0
     mrope_section: tuple = (11, 11, 10)     # rotary frequencies owned by (t, h, w), interleaved
     image_token_id: int = 248056
@@ -69,6 +70,8 @@ class Qwen35Config:
         kw["partial_rotary_factor"] = float(rp.get("partial_rotary_factor",
                                                    d.get("partial_rotary_factor", 0.25)))
         kw["mrope_section"] = tuple(rp.get("mrope_section", (11, 11, 10)))
+        if "num_experts" not in d and "num_local_experts" not in d:
+            kw["num_experts"] = 0            # the dense variant of the family
         for k in ("image_token_id", "video_token_id"):
             if outer.get(k) is not None:
                 kw[k] = int(outer[k])
@@ -149,6 +152,11 @@ class Qwen35MoeModel:
                 L["gnorm"] = get(a + "norm.weight")
                 L["out"] = get(a + "out_proj.weight")
             m = p + "mlp."
+            if not cfg.num_experts:          # dense variant: one gated MLP a layer
+                L["d13"] = torch.cat([get(m + "up_proj.weight"), get(m + "gate_proj.weight")], 0)
+                L["d2"] = get(m + "down_proj.weight")
+                w[i] = L
+                continue
             L["router"] = get(m + "gate.weight")
             gu = get(m + "experts.gate_up_proj")                 # [E, 2I, H]: gate rows, up rows
             L["w13"] = torch.cat([gu[:, I:], gu[:, :I]], 1).contiguous()
@@ -267,6 +275,8 @@ class Qwen35MoeModel:
 
     def _mlp(self, L, n):
         c = self.cfg
+        if "d13" in L:
+            return F.linear(F.linear_gated(n, L["d13"]), L["d2"])
         logits = F.linear(n, L["router"], out_dtype=torch.float32)
         ids, wts = F.topk_softmax(logits, c.num_experts_per_tok, True)
         y = F.moe_experts(n, ids, wts, L["w13"], L["w2"])
