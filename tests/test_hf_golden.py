@@ -515,3 +515,32 @@ def test_qwen3_5_dense_variant_matches_transformers(tmp_path):
     got = torch.cat([model.forward(ids[:20], st, 0), model.forward(ids[20:], st, 20)])
     torch.testing.assert_close(got, want, atol=2e-4, rtol=2e-3)
     assert model.generate(ids.tolist(), 5)[:len(gen)] == gen
+
+
+def test_qwen3_next_packed_projections_match_transformers(tmp_path):
+    """`Qwen3NextForCausalLM` stores the linear layers' projections packed per key head; the
+    loader unpacks them into the hybrid decoder's layout."""
+    import pytest
+    pytest.importorskip("transformers")
+    from transformers.models.qwen3_next.configuration_qwen3_next import Qwen3NextConfig
+    from transformers.models.qwen3_next.modeling_qwen3_next import Qwen3NextForCausalLM
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, save_file
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35Config, Qwen35MoeModel
+    hf_cfg = Qwen3NextConfig(
+        vocab_size=200, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=32, linear_num_key_heads=2,
+        linear_num_value_heads=4, linear_key_head_dim=16, linear_value_head_dim=16,
+        num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
+        shared_expert_intermediate_size=32, max_position_embeddings=128, norm_topk_prob=True,
+        layer_types=["linear_attention", "full_attention"])
+    torch.manual_seed(6)
+    hf = Qwen3NextForCausalLM(hf_cfg).float().eval()
+    save_file({k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()},
+              tmp_path / "model.safetensors")
+    (tmp_path / "config.json").write_text(json.dumps(hf_cfg.to_dict()))
+    ld = CheckpointLoader(tmp_path)
+    model = Qwen35MoeModel(Qwen35Config.from_hf(ld.config), "cpu", torch.float32).load_state(ld)
+    ids = torch.randint(0, 200, (17,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids[None]).logits[0]
+    torch.testing.assert_close(model.forward(ids, model.new_state()), want, atol=2e-4, rtol=2e-3)

@@ -144,8 +144,21 @@ class Qwen35MoeModel:
                 L["k_norm"] = get(a + "k_norm.weight", torch.float32) + 1.0
             else:
                 a = p + "linear_attn."
-                L["qkvz"] = torch.cat([get(a + "in_proj_qkv.weight"), get(a + "in_proj_z.weight"),
-                                       get(a + "in_proj_b.weight"), get(a + "in_proj_a.weight")], 0)
+                if (a + "in_proj_qkvz.weight") in names:
+                    # Qwen3-Next packs the projections per key head: [q k v.. z..] and [b.. a..]
+                    Hk, Dk, Dv = (cfg.linear_num_key_heads, cfg.linear_key_head_dim,
+                                  cfg.linear_value_head_dim)
+                    r = cfg.linear_num_value_heads // Hk
+                    qkvz = get(a + "in_proj_qkvz.weight").view(Hk, 2 * Dk + 2 * r * Dv, -1)
+                    ba = get(a + "in_proj_ba.weight").view(Hk, 2 * r, -1)
+                    parts = [qkvz[:, :Dk], qkvz[:, Dk:2 * Dk], qkvz[:, 2 * Dk:2 * Dk + r * Dv],
+                             qkvz[:, 2 * Dk + r * Dv:], ba[:, :r], ba[:, r:]]
+                    L["qkvz"] = torch.cat([t.reshape(-1, t.shape[-1]) for t in parts], 0).contiguous()
+                else:
+                    L["qkvz"] = torch.cat([get(a + "in_proj_qkv.weight"),
+                                           get(a + "in_proj_z.weight"),
+                                           get(a + "in_proj_b.weight"),
+                                           get(a + "in_proj_a.weight")], 0)
                 L["conv"] = get(a + "conv1d.weight", torch.float32).squeeze(1)     # [C, K]
                 L["dt_bias"] = get(a + "dt_bias", torch.float32)
                 L["A"] = -get(a + "A_log", torch.float32).exp()
