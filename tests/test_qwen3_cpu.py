@@ -323,3 +323,49 @@ def test_dense_state_engine_reuses_state_snapshots_of_a_shared_prefix():
         eng.step()
     assert eng.requests[rid].num_cached == 0 and eng.requests[rid].output_ids == want_b
     assert eng.blocks.flush() > 0 and not eng.state_cache
+
+
+def test_dense_state_engine_speculation_rolls_recurrent_state_back():
+    """Speculative steps on the hybrid decoder: accepted drafts advance several tokens per
+    call, a refused draft restores the snapshot of the recurrent state and replays the accepted
+    part; outputs equal plain decoding whatever the drafter proposes."""
+    import torch
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.engine.speculation import Drafter, NgramDrafter
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel
+    model = Qwen35MoeModel(Qwen35MoeModel.tiny_config(), "cpu", torch.float32).init_random(seed=0)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (12, 25)]
+    sp = SamplingParams(temperature=0.0, max_tokens=11, ignore_eos=True)
+    ref = DenseStateEngine(model).generate(prompts, sp)
+
+    class Oracle(Drafter):
+        k = 3
+
+        def propose(self, ids):
+            for p, r in zip(prompts, ref):
+                full = p + r
+                if list(ids) == full[:len(ids)]:
+                    return full[len(ids):len(ids) + self.k]
+            return []
+
+    class HalfWrong(Oracle):
+        def propose(self, ids):
+            d = super().propose(ids)
+            return d[:1] + [(t + 1) % 1000 for t in d[1:]]
+    for drafter, lo, hi in ((Oracle(), 0.99, 1.0), (HalfWrong(), 0.2, 0.6), (NgramDrafter(), 0.0, 1.0)):
+        eng = DenseStateEngine(model)
+        rids = [eng.add_request(p, sp) for p in prompts]
+        outs = {r: [] for r in rids}
+        steps = 0
+        while eng.has_work():
+            for o in eng.speculative_step(drafter):
+                outs[o.request_id].extend(o.new_token_ids)
+            steps += 1
+        assert [outs[r] for r in rids] == ref
+        st = eng.spec_stats
+        if st["proposed"]:
+            assert lo <= st["accepted"] / st["proposed"] <= hi
+        if isinstance(drafter, Oracle) and not isinstance(drafter, HalfWrong):
+            assert steps <= 1 + 4          # one prompt step, then ceil(10 / 4) + 1 verifications

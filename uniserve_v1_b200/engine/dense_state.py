@@ -88,6 +88,7 @@ class DenseStateEngine:
         self._ids = itertools.count(1)
         self._stats = {"prefill_tokens": 0, "decode_tokens": 0, "finished": 0, "steps": 0,
                        "preemptions": 0, "cached_tokens": 0}
+        self.spec_stats = {"steps": 0, "proposed": 0, "accepted": 0}
 
     # ------------------------------------------------------------- requests --
     def add_request(self, prompt_ids, params: Optional[SamplingParams] = None,
@@ -305,6 +306,51 @@ class DenseStateEngine:
             outs.append(StepOutput(req.request_id, [tok], reason is not None, reason,
                                    num_cached_tokens=req.num_cached,
                                    logprobs=[req.logprobs[-1]] if (p_lp and req.logprobs) else None))
+        return outs
+
+    # ------------------------------------------------------------ speculation --
+    def speculative_step(self, drafter) -> list:
+        """A step with speculation for recurrent decoders: when every running request decodes
+        greedily (no images), each gets the drafter's proposal verified in one call over its
+        last token plus the drafts.  Keys and values of rejected positions could simply be cut,
+        but the recurrent layers cannot step back: the state is snapshotted before the call and,
+        on a rejection, restored and advanced again over the accepted tokens only."""
+        from .speculation import accept
+        rows = [r for r in self.running if r.output_ids and r.num_computed == r.num_tokens - 1]
+        if not rows or len(rows) != len(self.running) or self.waiting or \
+                any(r.params.temperature > 0.0 or r.params.needs_shaping or r.params.logprobs or
+                    getattr(r, "media", None) is not None for r in rows):
+            return self.step()
+        self._stats["steps"] += 1
+        outs, dev = [], self.model.device
+        for req in rows:
+            room = min(self.config.max_model_len - req.num_tokens - 1,
+                       req.params.max_tokens - len(req.output_ids) - 1)
+            d = [int(t) for t in drafter.propose(req.all_ids)][:max(0, min(drafter.k, room))]
+            st = self.states[req.request_id]
+            keep = copy.deepcopy(st) if d else None
+            toks = [req.output_ids[-1]] + d
+            logits = self.model.forward(torch.tensor(toks, device=dev), st, req.num_computed)
+            emit = accept(d, logits.argmax(-1).tolist())
+            self.spec_stats["steps"] += 1
+            self.spec_stats["proposed"] += len(d)
+            self.spec_stats["accepted"] += len(emit) - 1
+            if len(emit) - 1 < len(d):             # a draft was refused: replay the accepted part
+                st = self.states[req.request_id] = keep
+                self.model.forward(torch.tensor(toks[:len(emit)], device=dev), st, req.num_computed)
+            self._stats["decode_tokens"] += len(emit)
+            new = []
+            for tok in emit:
+                req.num_computed += 1
+                req.output_ids.append(tok)
+                new.append(tok)
+                reason = self._stop(req, tok)
+                if reason is not None:
+                    break
+            if reason is not None:
+                self._finish(req, reason)
+            outs.append(StepOutput(req.request_id, new, reason is not None, reason,
+                                   num_cached_tokens=req.num_cached))
         return outs
 
     def generate(self, prompts: list, params=None) -> list:

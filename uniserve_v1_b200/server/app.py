@@ -226,7 +226,8 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
     if engine is not None:
         sc = s.package.scheduler_config
         if drafter is None and s.package.speculative_config.num_draft_tokens > 0 and \
-                hasattr(engine, "speculative_step") and hasattr(engine, "scheduler"):
+                hasattr(engine, "speculative_step") and \
+                (hasattr(engine, "scheduler") or hasattr(engine, "states")):
             # `speculative_config.num_draft_tokens` without a drafter of the model's own:
             # prompt-lookup drafting (single-process engines; replicated engines step plainly)
             from ..engine.speculation import NgramDrafter
