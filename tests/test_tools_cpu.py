@@ -376,3 +376,28 @@ def test_tp_protocol_interleavings():
     assert explore_tp_protocol(2, 4)["violation"] is None
     assert explore_tp_protocol(3, 2)["violation"] is None
     assert explore_tp_protocol(2, 3, norm_sites=1)["violation"] is None
+
+
+def test_eval_check_change_against_control(live_server):
+    """A load during which the policy is changed twice (prefix caching off, then on) loses no
+    request, no token and no admission against its control; tampered bundles are flagged."""
+    import copy
+    from uniserve_v1_b200.tools import eval as E
+    kw = dict(concurrency=3, requests=9, prompt_tokens=10, max_tokens=5, model="tiny", seed=3)
+    control = asyncio.run(E.run_load(live_server, **kw))
+    base = 'model = "random:tiny"\nserved_model_name = "tiny"\n'
+    off = base + "[kv_cache_config]\nprefix_caching = false\n"
+    run = asyncio.run(E.run_load(live_server, changes=[(0.05, off), (0.25, base)], **kw))
+    assert len(run["timeline"]) == 2 and all(e["status"] == 200 for e in run["timeline"])
+    assert E.check_change(run, control) == []
+    lost = copy.deepcopy(run)
+    lost["records"][2]["text"] = lost["records"][2]["text"] + "x"
+    lost["records"][4]["error"] = "ClientPayloadError: closed"
+    lost["timeline"][0]["status"] = 409
+    fails = E.check_change(lost, control)
+    assert len(fails) == 3 and any("text differs" in f for f in fails)
+    late = copy.deepcopy(run)
+    w1 = max(e["done_s"] for e in late["timeline"])
+    r = late["records"][0]
+    r["submit_s"], r["ttft_s"] = late["timeline"][0]["issued_s"] + 0.001, w1 + 30.0
+    assert any("inside the change window" in f for f in E.check_change(late, control))

@@ -4,6 +4,7 @@
         --requests 256 --prompt-tokens 128 --max-tokens 256 --out bundle.json
     python -m uniserve_v1_b200.tools.eval compare reference.json candidate.json
     python -m uniserve_v1_b200.tools.eval check-stop bundle.json
+    python -m uniserve_v1_b200.tools.eval check-change run.json control.json
     python -m uniserve_v1_b200.tools.eval check-faults bundle.json
 
 ``run`` drives ``POST /v1/chat/completions`` with a closed loop of ``concurrency``
@@ -49,6 +50,7 @@ class Record:
     chunks: int = 0
     stop: list = field(default_factory=list)
     max_tokens: int = 0
+    submit_s: float = 0.0          # when the load issued it, from the load's start
 
 
 def percentile(xs, p):
@@ -91,13 +93,18 @@ async def one_request(session, url, headers, body, rec: Record, timeout_s: float
                     for ch in ev.get("choices", []):
                         delta = ch.get("delta", {})
                         piece = (delta.get("content") or "") + (delta.get("reasoning") or "")
-                        if piece or delta.get("tool_calls"):
-                            if rec.ttft_s is None:
+                        # the first chunk after the role announcement carries the first token,
+                        # even when its bytes do not yet form printable text
+                        if piece or delta.get("tool_calls") or "role" not in delta:
+                            if rec.ttft_s is None and not ch.get("finish_reason"):
                                 rec.ttft_s = time.perf_counter() - t0
+                        if piece or delta.get("tool_calls"):
                             rec.text += piece
                             rec.chunks += 1
                         if ch.get("finish_reason"):
                             rec.finish_reason = ch["finish_reason"]
+                            if rec.ttft_s is None:      # no printable piece was ever streamed
+                                rec.ttft_s = time.perf_counter() - t0
                     if ev.get("usage"):
                         u = ev["usage"]
                         rec.output_tokens = u.get("completion_tokens", 0)
@@ -122,11 +129,17 @@ async def one_request(session, url, headers, body, rec: Record, timeout_s: float
 async def run_load(url: str, concurrency: int, requests: int, prompt_tokens: int, max_tokens: int,
                    stream: bool = True, api_key: Optional[str] = None, model: str = "default",
                    seed: int = 0, stop: Optional[list] = None, temperature: float = 0.0,
-                   timeout_s: float = 600.0, ignore_eos: bool = True) -> dict:
+                   timeout_s: float = 600.0, ignore_eos: bool = True,
+                   changes: Optional[list] = None) -> dict:
+    """``changes``: [(seconds from the start, policy text)] - each is PUT to ``/admin/policy``
+    while the load runs; the bundle's ``timeline`` records when each was issued and applied."""
     import aiohttp
-    rng = random.Random(seed)
     headers = {"Authorization": f"Bearer {api_key}"} if api_key else {}
     records = [Record(i, stop=stop or [], max_tokens=max_tokens) for i in range(requests)]
+    # prompts depend on the request's index only, so a run and its control send the same ones
+    prompts = [synth_prompt(random.Random(seed * 1000003 + i), prompt_tokens)
+               for i in range(requests)]
+    timeline: list = []
     queue: asyncio.Queue = asyncio.Queue()
     for r in records:
         queue.put_nowait(r)
@@ -140,20 +153,37 @@ async def run_load(url: str, concurrency: int, requests: int, prompt_tokens: int
                 return
             body = {"model": model, "max_tokens": max_tokens, "temperature": temperature,
                     "stream": stream, "seed": seed + rec.index, "ignore_eos": ignore_eos,
-                    "messages": [{"role": "user", "content": synth_prompt(rng, prompt_tokens)}]}
+                    "messages": [{"role": "user", "content": prompts[rec.index]}]}
             if stream:
                 body["stream_options"] = {"include_usage": True}
             if stop:
                 body["stop"] = stop
+            rec.submit_s = time.perf_counter() - t0
             await one_request(session, url, headers, body, rec, timeout_s)
+
+    async def changer(session):
+        for at, text in sorted(changes or []):
+            await asyncio.sleep(max(0.0, at - (time.perf_counter() - t0)))
+            ev = {"issued_s": time.perf_counter() - t0}
+            try:
+                async with session.put(url + "/admin/policy", data=text, headers=dict(
+                        headers, **{"Content-Type": "application/toml"})) as resp:
+                    ev["status"] = resp.status
+                    ev["answer"] = (await resp.text())[:300]
+            except Exception as e:     # noqa: BLE001
+                ev["status"], ev["answer"] = 0, f"{type(e).__name__}: {e}"
+            ev["done_s"] = time.perf_counter() - t0
+            timeline.append(ev)
 
     conn = aiohttp.TCPConnector(limit=0)
     async with aiohttp.ClientSession(connector=conn) as session:
-        await asyncio.gather(*[client(session) for _ in range(concurrency)])
+        await asyncio.gather(changer(session), *[client(session) for _ in range(concurrency)])
     wall = time.perf_counter() - t0
-    return bundle_of(records, wall, dict(url=url, concurrency=concurrency, requests=requests,
-                                         prompt_tokens=prompt_tokens, max_tokens=max_tokens,
-                                         stream=stream, seed=seed))
+    b = bundle_of(records, wall, dict(url=url, concurrency=concurrency, requests=requests,
+                                      prompt_tokens=prompt_tokens, max_tokens=max_tokens,
+                                      stream=stream, seed=seed))
+    b["timeline"] = timeline
+    return b
 
 
 def bundle_of(records, wall_s: float, point: dict) -> dict:
@@ -220,6 +250,45 @@ def check_stop(bundle: dict) -> list:
     return fails
 
 
+def check_change(run: dict, control: dict) -> list:
+    """A run whose deployment was changed while it served, against its control (the same load
+    without the changes): (1) no failed request - each answered 200 and ended at ``length``
+    with exactly its requested tokens; (2) no closed connection; (3) no token lost or
+    repeated - each text equals the control's text of the same request; (4) new requests
+    were admitted throughout - a request submitted inside the changes' window had its first
+    token by the window's end plus the control's 99th-percentile time to first token; and
+    every change was accepted."""
+    fails = []
+    ctl = {r["index"]: r for r in control["records"]}
+    for ev in run.get("timeline") or []:
+        if ev.get("status") != 200:
+            fails.append(f"change at {ev.get('issued_s', 0):.2f} s answered {ev.get('status')}: "
+                         f"{ev.get('answer')}")
+    win = None
+    if run.get("timeline"):
+        win = (min(e["issued_s"] for e in run["timeline"]),
+               max(e["done_s"] for e in run["timeline"]))
+    p99 = (control["summary"]["ttft_s"] or {}).get("p99") or 0.0
+    for r in run["records"]:
+        i = r["index"]
+        if r["error"]:
+            fails.append(f"request {i}: connection ended: {r['error']}")
+            continue
+        if r["status"] != 200 or r["finish_reason"] != "length" or \
+                (r["max_tokens"] and r["output_tokens"] != r["max_tokens"]):
+            fails.append(f"request {i}: status {r['status']}, finish {r['finish_reason']}, "
+                         f"{r['output_tokens']} of {r['max_tokens']} tokens")
+            continue
+        c = ctl.get(i)
+        if c is not None and c["ok"] and c["text"] != r["text"]:
+            fails.append(f"request {i}: text differs from the control's")
+        if win and win[0] <= r["submit_s"] <= win[1] and r["ttft_s"] is not None and \
+                r["submit_s"] + r["ttft_s"] > win[1] + p99 + 1e-3:
+            fails.append(f"request {i}: submitted at {r['submit_s']:.2f} s inside the change "
+                         f"window, first token only at {r['submit_s'] + r['ttft_s']:.2f} s")
+    return fails
+
+
 def check_faults(bundle: dict) -> list:
     """Every request of a fault-injection run reached a terminal state: a finish
     reason, or an HTTP / stream error that names the failure; none hung."""
@@ -250,6 +319,11 @@ def main(argv=None) -> int:
     r.add_argument("--stop", action="append")
     r.add_argument("--temperature", type=float, default=0.0)
     r.add_argument("--out")
+    r.add_argument("--change", action="append", default=[], metavar="SECONDS:FILE",
+                   help="PUT the policy text of FILE to /admin/policy SECONDS into the load")
+    cc = sub.add_parser("check-change")
+    cc.add_argument("run")
+    cc.add_argument("control")
     c = sub.add_parser("compare")
     c.add_argument("reference")
     c.add_argument("candidate")
@@ -265,7 +339,9 @@ def main(argv=None) -> int:
     if args.cmd == "run":
         b = asyncio.run(run_load(args.url, args.concurrency, args.requests, args.prompt_tokens,
                                  args.max_tokens, not args.no_stream, args.api_key, args.model,
-                                 args.seed, args.stop, args.temperature))
+                                 args.seed, args.stop, args.temperature,
+                                 changes=[(float(c.split(":", 1)[0]), open(c.split(":", 1)[1]).read())
+                                          for c in args.change]))
         if args.out:
             with open(args.out, "w") as f:
                 json.dump(b, f)
@@ -278,6 +354,8 @@ def main(argv=None) -> int:
         res = compare_accuracy(args.reference_correct, args.candidate_correct, args.n)
         print(json.dumps(res))
         return 0 if res["pass"] else 2
+    elif args.cmd == "check-change":
+        fails = check_change(json.load(open(args.run)), json.load(open(args.control)))
     elif args.cmd == "check-stop":
         fails = check_stop(json.load(open(args.bundle)))
     else:
