@@ -256,3 +256,24 @@ def test_scheduling_program_decides_under_a_fuel_budget(tmp_path):
         spin.host.call("dispatch", [], {})
     with pytest.raises(Exception):
         ProgramHost("import os\n", "escape")                                  # no import machinery
+
+
+def test_routing_program_picks_replicas_and_falls_back():
+    from uniserve_v1_b200.engine.program import ProgramHost
+    from uniserve_v1_b200.server.router import ReplicaRouter
+    big_to_last = ProgramHost(
+        "def route(request, replicas):\n"
+        "    if request['bytes'] > 1000:\n"
+        "        return replicas[-1]['index']\n"
+        "    return min(replicas, key=lambda r: r['in_flight'])['index']\n", "routing", 100000)
+    rt = ReplicaRouter(["http://a", "http://b", "http://c"], program=big_to_last)
+    rt.replicas[0].in_flight = 2
+    assert rt.pick(size=5000).url == "http://c" and rt.pick(size=10).url == "http://b"
+    assert rt.pick(size=5000, exclude=[rt.replicas[2]]).url == "http://b"
+    bad = ReplicaRouter(["http://a", "http://b"], program=ProgramHost(
+        "def route(request, replicas):\n    return 7\n", "routing", 100000))
+    bad.replicas[0].in_flight = 1
+    assert bad.pick().url == "http://b" and bad.program_faults == 1
+    spin = ReplicaRouter(["http://a"], program=ProgramHost(
+        "def route(request, replicas):\n    while True:\n        pass\n", "routing", 5000))
+    assert spin.pick().url == "http://a" and spin.program_faults == 1

@@ -246,6 +246,7 @@ def main(argv=None) -> int:
     r.add_argument("--replica", action="append", default=[], help="base URL of a mixed replica")
     r.add_argument("--prefill", action="append", default=[], help="base URL of a prefill replica")
     r.add_argument("--decode", action="append", default=[], help="base URL of a decode replica")
+    r.add_argument("--program", help="routing program: a file that defines route(request, replicas)")
     a = ap.parse_args(argv)
     if a.cmd == "serve":
         return serve(a)
@@ -257,8 +258,12 @@ def main(argv=None) -> int:
         host, _, port = a.listen.rpartition(":")
         if not a.replica and not (a.prefill and a.decode):
             ap.error("route needs --replica, or --prefill together with --decode")
+        program = None
+        if a.program:
+            from .engine.program import ProgramHost
+            program = ProgramHost(open(a.program).read(), "routing", call_fuel=1_000_000)
         uvicorn.run(create_router_app(a.replica, prefill_urls=a.prefill or None,
-                                      decode_urls=a.decode or None),
+                                      decode_urls=a.decode or None, program=program),
                     host=host or "127.0.0.1", port=int(port), log_level="warning")
         return 0
     if a.cmd == "build":

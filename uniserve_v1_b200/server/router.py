@@ -45,16 +45,33 @@ class Replica:
 
 
 class ReplicaRouter:
-    def __init__(self, urls: list, retry_after_s: float = 2.0):
+    def __init__(self, urls: list, retry_after_s: float = 2.0, program=None):
+        """``program``: an ``engine.program.ProgramHost`` whose ``route(request, replicas)``
+        returns the index of the replica to use (facts: the request's body size and cache key;
+        per replica its index, requests in flight, requests served and whether it is up).  A
+        missing, faulting or out-of-range answer falls back to fewest-in-flight."""
         assert urls, "at least one replica"
         self.replicas = [Replica(u) for u in urls]
         self.retry_after_s = retry_after_s
+        self.program = program
+        self.program_faults = 0
 
-    def pick(self, affinity: Optional[str] = None, exclude=()) -> Optional[Replica]:
+    def pick(self, affinity: Optional[str] = None, exclude=(), size: int = 0) -> Optional[Replica]:
         live = [r for r in self.replicas if r.up and r not in exclude] or \
             [r for r in self.replicas if r not in exclude]
         if not live:
             return None
+        if self.program is not None and self.program.has("route"):
+            try:
+                i = self.program.call("route", {"bytes": size, "cache_key": affinity},
+                                      [{"index": self.replicas.index(r), "in_flight": r.in_flight,
+                                        "served": r.served, "up": r.up} for r in live])
+                by_index = {self.replicas.index(r): r for r in live}
+                if isinstance(i, int) and i in by_index:
+                    return by_index[i]
+                self.program_faults += 1
+            except Exception:
+                self.program_faults += 1
         if affinity:
             h = int.from_bytes(hashlib.sha256(affinity.encode()).digest()[:8], "big")
             return live[h % len(live)]
@@ -70,13 +87,14 @@ class ReplicaRouter:
 
 def create_router_app(urls: list, api_key: Optional[str] = None,
                       prefill_urls: Optional[list] = None,
-                      decode_urls: Optional[list] = None) -> FastAPI:
+                      decode_urls: Optional[list] = None, program=None) -> FastAPI:
     """``urls``: replicas of role ``mixed``.  With ``prefill_urls`` and ``decode_urls`` chat
     requests are disaggregated: a prefill replica computes the prompt and the first token
     (``/internal/prefill``), its answer - the request's framed state - goes to a decode
     replica (``/internal/decode``), whose stream is relayed to the client."""
     import aiohttp
-    router = ReplicaRouter(urls or (list(prefill_urls or []) + list(decode_urls or [])))
+    router = ReplicaRouter(urls or (list(prefill_urls or []) + list(decode_urls or [])),
+                           program=program)
     pre = ReplicaRouter(prefill_urls) if prefill_urls else None
     dec = ReplicaRouter(decode_urls) if decode_urls else None
     app = FastAPI(title="uniserve_v1_b200 replica router")
@@ -109,7 +127,7 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
         tried = []
         s = await session()
         while True:
-            r = router.pick(affinity, exclude=tried)
+            r = router.pick(affinity, exclude=tried, size=len(body or b""))
             if r is None:
                 return JSONResponse({"error": {"message": "no replica is reachable",
                                                "type": "service_unavailable"}}, status_code=503)
