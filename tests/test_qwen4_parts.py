@@ -1,0 +1,75 @@
+"""Qwen4-exp building blocks against their own definitions."""
+import torch
+
+from uniserve_v1_b200.models.qwen4_exp import HyperConnection, NgramEmbedding, PleLayer, ngram_ids
+
+
+def test_hyper_connection_reduces_to_a_plain_residual_and_defers_its_combine():
+    g = torch.Generator().manual_seed(0)
+    plain = HyperConnection(hidden=16, streams=1, rank=4)           # all-zero gates
+    S = torch.randn(5, 16, generator=g)
+    _, h, logits = plain.read(S)
+    sn = S * torch.rsqrt(S.pow(2).mean(-1, keepdim=True) + 1e-6)
+    torch.testing.assert_close(h, 0.5 * sn)                          # sigmoid(0) = 1 / 2
+    y = torch.randn(5, 16, generator=g)
+    torch.testing.assert_close(HyperConnection.fold(S, y, logits, 1), S + y)   # gain 2 * 1 / 2
+    hc = HyperConnection(hidden=8, streams=3, rank=4).init_random(1, 0.3)
+    S = torch.randn(6, 24, generator=g)
+    y = torch.randn(6, 8, generator=g)
+    S0, h0, r0 = hc.read(S)
+    nxt = HyperConnection(hidden=8, streams=3, rank=4).init_random(2, 0.3)
+    S1, h1, _ = nxt.read(S0, pending=(y, r0))                        # deferred combine
+    want = S.view(6, 3, 8) + y[:, None, :] * (2 * torch.sigmoid(r0 / 3))[:, :, None]
+    torch.testing.assert_close(S1, want.view(6, 24))
+    torch.testing.assert_close(h1, nxt.read(want.view(6, 24))[1])
+    tail = HyperConnection(hidden=8, streams=3, rank=4, injects=False).init_random(3)
+    assert tail.read(S)[2] is None and tail.down.shape == (4, 24)
+
+
+def test_ngram_ids_match_wrapping_integer_arithmetic():
+    mult = torch.tensor([0x9E3779B97F4A7C15 - (1 << 64), 0x2545F4914F6CDD1D, 0x632BE59BD9B4E019],
+                        dtype=torch.int64)
+    parts = torch.tensor([1009, 2003, 3001, 4001], dtype=torch.int64)
+    offs = torch.tensor([0, 1009, 3012, 6013], dtype=torch.int64)
+    eos = 7
+    toks = torch.tensor([5, 9, 7, 11, 13, 2], dtype=torch.int64)
+    ids = ngram_ids(toks, eos, mult, parts, offs, heads_per_ngram=2)
+    assert ids.shape == (6, 4)
+    M = [(int(m) + (1 << 64)) % (1 << 64) for m in mult]
+
+    def signed(x):
+        x %= 1 << 64
+        return x - (1 << 64) if x >= (1 << 63) else x
+    for t in range(6):
+        prev, stopped = [], False
+        for k in (1, 2):
+            p = int(toks[t - k]) if t - k >= 0 else eos
+            stopped = stopped or p == eos
+            prev.append(eos if stopped else p)
+        mix = (int(toks[t]) * M[0]) % (1 << 64)
+        for k in (1, 2):
+            mix ^= (prev[k - 1] * M[k]) % (1 << 64)
+            for h in range((k - 1) * 2, k * 2):
+                assert int(ids[t, h]) == signed(mix) % int(parts[h]) + int(offs[h]), (t, h)
+    assert bool(((ids >= offs) & (ids < offs + parts)).all())
+    table = (torch.randn(10100, 8, generator=torch.Generator().manual_seed(1)) * 2).to(
+        torch.float8_e4m3fn).view(torch.uint8)
+    emb = NgramEmbedding(table, 0.5, eos, mult, parts, offs, 2)
+    e = emb.forward(toks, torch.float32)
+    assert e.shape == (6, 32)
+    torch.testing.assert_close(e[3, :8], table.view(torch.float8_e4m3fn)[ids[3, 0]].float() * 0.5)
+
+
+def test_ple_layer_is_causal_and_carries_its_convolution_state():
+    g = torch.Generator().manual_seed(2)
+    ple = PleLayer(hidden=8, streams=2, embed=12, kernel=3, dilation=2).init_random(0, 0.3)
+    e, S = torch.randn(9, 12, generator=g), torch.randn(9, 16, generator=g)
+    out, st = ple.forward(e, S)
+    assert out.shape == (9, 16) and st.shape == (4, 16)
+    e2, S2 = e.clone(), S.clone()
+    e2[6:], S2[6:] = 0.0, 1.0                                        # later tokens change
+    torch.testing.assert_close(ple.forward(e2, S2)[0][:6], out[:6])
+    a, sa = ple.forward(e[:4], S[:4])
+    b, sb = ple.forward(e[4:], S[4:], sa)
+    torch.testing.assert_close(torch.cat([a, b]), out)
+    torch.testing.assert_close(sb, st)
