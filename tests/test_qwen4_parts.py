@@ -73,3 +73,61 @@ def test_ple_layer_is_causal_and_carries_its_convolution_state():
     b, sb = ple.forward(e[4:], S[4:], sa)
     torch.testing.assert_close(torch.cat([a, b]), out)
     torch.testing.assert_close(sb, st)
+
+
+def _dense_gated(att, x, mask):
+    """Causal gated attention of the same weights over the tokens ``mask`` [T, T] allows."""
+    from uniserve_v1_b200.models.qwen4_exp import gemma_norm, partial_rope
+    T, H, hd = x.shape[0], att.heads, att.hd
+    pos = torch.arange(T)
+    qg = (x @ att.q_proj.t()).view(T, H, 2, hd)
+    q = partial_rope(gemma_norm(qg[:, :, 0], att.q_norm, att.eps), pos, att.rot, att.theta)
+    k = partial_rope(gemma_norm((x @ att.k_proj.t()).view(T, att.kv, hd), att.k_norm, att.eps),
+                     pos, att.rot, att.theta).repeat_interleave(H // att.kv, 1)
+    v = (x @ att.v_proj.t()).view(T, att.kv, hd).repeat_interleave(H // att.kv, 1)
+    sc = torch.einsum("thd,shd->hts", q, k) * hd ** -0.5
+    sc = sc.masked_fill(~mask[None], float("-inf"))
+    o = torch.einsum("hts,shd->thd", torch.softmax(sc, -1), v) * torch.sigmoid(qg[:, :, 1])
+    return o.reshape(T, H * hd) @ att.o_proj.t()
+
+
+def test_indexed_attention_selects_groups_and_matches_masked_attention():
+    from uniserve_v1_b200.models.qwen4_exp import IndexedAttention
+    g = torch.Generator().manual_seed(3)
+    T = 23
+    x = torch.randn(T, 32, generator=g)
+    kw = dict(hidden=32, heads=4, kv_heads=2, head_dim=16, index_heads=2, index_dim=8, ratio=4,
+              rotary_dim=8)
+    wide = IndexedAttention(budget=24, **kw).init_random(0)          # every group fits
+    out, cache, sel = wide.forward(x)
+    assert sel.shape == (T, 24 + 3) and cache["k"].shape == (T, 2, 16)
+    causal = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    torch.testing.assert_close(out, _dense_gated(wide, x, causal), rtol=1e-4, atol=1e-5)
+    for t in range(T):                                               # what a row names
+        row = sel[t][sel[t] >= 0].tolist()
+        assert sorted(row) == list(range(t + 1))
+        assert row[len(row) - (t + 1) % 4:] == list(range((t + 1) // 4 * 4, t + 1))
+    narrow = IndexedAttention(budget=8, **kw).init_random(0)         # two groups of the visible
+    out2, _, sel2 = narrow.forward(x)
+    mask = torch.zeros(T, T, dtype=torch.bool)
+    for t in range(T):
+        row = sel2[t][sel2[t] >= 0]
+        assert len(set(row.tolist())) == len(row) and int(row.max()) <= t
+        assert len(row) == min((t + 1) // 4, 2) * 4 + (t + 1) % 4
+        mask[t, row] = True
+    torch.testing.assert_close(out2, _dense_gated(narrow, x, mask), rtol=1e-4, atol=1e-5)
+    assert not torch.allclose(out2[12:], out[12:], atol=1e-4)        # the budget binds
+    keys = narrow.index_keys(cache["raw"])                           # rank order by score
+    s = torch.relu(torch.einsum("hd,gd->hg", _q_idx(narrow, x)[T - 1], keys)).sum(0)[:(T) // 4]
+    assert sel2[T - 1, :8:4].tolist() == (s.topk(2).indices * 4).tolist()
+    a, c, sa = narrow.forward(x[:10])                                # a prompt in pieces
+    b, c, sb = narrow.forward(x[10:], c)
+    torch.testing.assert_close(torch.cat([a, b]), out2, rtol=1e-4, atol=1e-5)
+    assert torch.equal(torch.cat([sa, sb]), sel2)
+
+
+def _q_idx(att, x):
+    from uniserve_v1_b200.models.qwen4_exp import gemma_norm, partial_rope
+    iq = (x @ att.index_qk_proj.t()).view(x.shape[0], att.ih + 1, att.idim)
+    return partial_rope(gemma_norm(iq[:, :att.ih], att.q_layernorm, att.eps),
+                        torch.arange(x.shape[0]), att.irot, att.theta)

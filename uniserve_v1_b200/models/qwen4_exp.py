@@ -1,8 +1,8 @@
 """Building blocks of the Qwen4-exp ("Qwen3.8 Flash Next") family: the gated hyper-connection
 around every block, the hashed n-gram embedding and the layer that gates it into the residual
-streams.  The family's decoder (gated delta net or indexed attention, then experts with a gated
-shared expert, each between two hyper-connections) is not assembled here, nor is the indexed
-(sparse-token) attention with its group index.
+streams, and the indexed (sparse-token) attention with its group index.  The family's decoder
+(gated delta net or indexed attention, then experts with a gated shared expert, each between two
+hyper-connections) is not assembled here.
 
 **Hyper-connection.**  The residual is C streams of width H, ``S`` [tokens, C * H]::
 
@@ -161,3 +161,114 @@ class PleLayer:
             conv += self.conv.float()[:, k][None, :] * full[span - back:span - back + T]
         out = gv.view(T, C * H).float() + torch.nn.functional.silu(conv.to(S.dtype).float())
         return out.to(S.dtype), full[-span:].to(S.dtype) if span else state
+
+
+def partial_rope(x: torch.Tensor, pos: torch.Tensor, rotary_dim: int, theta: float) -> torch.Tensor:
+    """Half-rotation rotary embedding over the leading ``rotary_dim`` channels of x [T, n, d]."""
+    half = rotary_dim // 2
+    inv = theta ** (-torch.arange(half, dtype=torch.float32) / half)
+    ang = pos.float()[:, None] * inv[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    xf = x.float()
+    a, b, rest = xf[..., :half], xf[..., half:rotary_dim], xf[..., rotary_dim:]
+    return torch.cat([a * cos - b * sin, b * cos + a * sin, rest], -1).to(x.dtype)
+
+
+class IndexedAttention:
+    """Gated attention over the tokens an indexer selects, one request at a time.
+
+    Tokens form groups of ``ratio``; a complete group has one index key, the normalised and
+    rotated mean of its tokens' raw index keys at the position of its first token.  A row at
+    position t sees the ``(t + 1) // ratio`` complete groups, scores them
+    ``sum_h relu(q_idx[h] . key)``, keeps the tokens of the best ``budget // ratio`` in rank order
+    and then the ``(t + 1) % ratio`` tokens of its own unfinished group: ``budget + ratio - 1``
+    entries, -1 where it has fewer.  Softmax attention runs over those tokens only; the output is
+    ``o_proj(o * sigmoid(gate))`` with the gate taken from the query projection.
+
+    ``cache`` holds the request's rotated keys, values and raw index keys; index keys of complete
+    groups are pooled from the raw ones at every call.  Reference behaviour:
+    crates/models/src/qwen4_exp/attention.rs:1-40, 408-526 (reference project paths).
+    """
+
+    def __init__(self, hidden, heads, kv_heads, head_dim, index_heads, index_dim, ratio, budget,
+                 rotary_dim=None, theta=10000.0, eps=1e-6, dtype=torch.float32):
+        assert budget % ratio == 0 and heads % kv_heads == 0
+        self.hidden, self.heads, self.kv, self.hd = hidden, heads, kv_heads, head_dim
+        self.ih, self.idim, self.ratio, self.budget = index_heads, index_dim, ratio, budget
+        self.rot = rotary_dim or head_dim
+        self.irot = min(self.rot, index_dim)
+        self.theta, self.eps = theta, eps
+        z = lambda *s: torch.zeros(*s, dtype=dtype)
+        self.q_proj = z(heads * 2 * head_dim, hidden)             # per head: query rows, gate rows
+        self.k_proj, self.v_proj = z(kv_heads * head_dim, hidden), z(kv_heads * head_dim, hidden)
+        self.o_proj = z(hidden, heads * head_dim)
+        self.q_norm, self.k_norm = z(head_dim), z(head_dim)
+        self.index_qk_proj = z((index_heads + 1) * index_dim, hidden)
+        self.q_layernorm, self.k_layernorm = z(index_dim), z(index_dim)
+
+    def init_random(self, seed: int = 0, std: float = 0.2) -> "IndexedAttention":
+        g = torch.Generator().manual_seed(seed)
+        for name in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm", "index_qk_proj",
+                     "q_layernorm", "k_layernorm"):
+            t = getattr(self, name)
+            t.copy_((torch.randn(t.shape, generator=g) * std).to(t.dtype))
+        return self
+
+    def index_keys(self, raw: torch.Tensor) -> torch.Tensor:
+        """raw [n, idim] from position 0 -> [n // ratio, idim], one key per complete group."""
+        G = raw.shape[0] // self.ratio
+        pooled = raw[:G * self.ratio].float().view(G, self.ratio, self.idim).mean(1).to(raw.dtype)
+        first = torch.arange(G) * self.ratio
+        return partial_rope(gemma_norm(pooled, self.k_layernorm, self.eps)[:, None, :], first,
+                            self.irot, self.theta)[:, 0]
+
+    def select(self, q_idx: torch.Tensor, keys: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """q_idx [T, ih, idim], keys [G, idim], pos [T] -> selection [T, budget + ratio - 1]."""
+        T, r, top = q_idx.shape[0], self.ratio, self.budget // self.ratio
+        visible, partial = (pos + 1) // r, (pos + 1) % r
+        sel = torch.full((T, self.budget + r - 1), -1, dtype=torch.int64)
+        G = keys.shape[0]
+        if G:
+            s = torch.relu(torch.einsum("thd,gd->thg", q_idx.float(), keys.float())).sum(1)
+            s = s.masked_fill(torch.arange(G)[None, :] >= visible[:, None], float("-inf"))
+            kept = min(top, G)
+            best = s.topk(kept, dim=1).indices                                   # rank order
+            named = torch.arange(kept)[None, :] < visible.clamp_max(kept)[:, None]
+            toks = best[:, :, None] * r + torch.arange(r)[None, None, :]
+            toks = torch.where(named[:, :, None], toks, torch.full_like(toks, -1))
+            sel[:, :kept * r] = toks.reshape(T, kept * r)
+        tail = visible[:, None] * r + torch.arange(r - 1)[None, :]
+        sel[:, self.budget:] = torch.where(torch.arange(r - 1)[None, :] < partial[:, None], tail,
+                                           torch.full_like(tail, -1))
+        return sel
+
+    def forward(self, x: torch.Tensor, cache: Optional[dict] = None):
+        """x [T, hidden], the request's next T tokens -> (output [T, hidden], cache, selection)."""
+        T, H, hd = x.shape[0], self.heads, self.hd
+        cache = cache if cache is not None else {"k": x.new_zeros(0, self.kv, hd),
+                                                 "v": x.new_zeros(0, self.kv, hd),
+                                                 "raw": x.new_zeros(0, self.idim)}
+        pos = cache["k"].shape[0] + torch.arange(T)
+        lin = lambda w: (x.float() @ w.float().t()).to(x.dtype)
+        qg = lin(self.q_proj).view(T, H, 2, hd)
+        q, gate = qg[:, :, 0], qg[:, :, 1]
+        q = partial_rope(gemma_norm(q, self.q_norm, self.eps), pos, self.rot, self.theta)
+        k = partial_rope(gemma_norm(lin(self.k_proj).view(T, self.kv, hd), self.k_norm, self.eps),
+                         pos, self.rot, self.theta)
+        iq = lin(self.index_qk_proj).view(T, self.ih + 1, self.idim)
+        q_idx = partial_rope(gemma_norm(iq[:, :self.ih], self.q_layernorm, self.eps), pos,
+                             self.irot, self.theta)
+        cache = {"k": torch.cat([cache["k"], k]),
+                 "v": torch.cat([cache["v"], lin(self.v_proj).view(T, self.kv, hd)]),
+                 "raw": torch.cat([cache["raw"], iq[:, self.ih]])}
+        sel = self.select(q_idx, self.index_keys(cache["raw"]), pos)
+        valid = sel >= 0
+        at = sel.clamp_min(0)
+        rep = H // self.kv
+        ks = cache["k"][at].repeat_interleave(rep, 2).float()                   # [T, S, H, hd]
+        vs = cache["v"][at].repeat_interleave(rep, 2).float()
+        sc = torch.einsum("thd,tshd->ths", q.float(), ks) * hd ** -0.5
+        sc = sc.masked_fill(~valid[:, None, :], float("-inf"))
+        o = torch.einsum("ths,tshd->thd", torch.softmax(sc, -1), vs).to(x.dtype)
+        o = (o.float() * torch.sigmoid(gate.float())).to(x.dtype).reshape(T, H * hd)
+        return (o.float() @ self.o_proj.float().t()).to(x.dtype), cache, sel
