@@ -131,3 +131,30 @@ def _q_idx(att, x):
     iq = (x @ att.index_qk_proj.t()).view(x.shape[0], att.ih + 1, att.idim)
     return partial_rope(gemma_norm(iq[:, :att.ih], att.q_layernorm, att.eps),
                         torch.arange(x.shape[0]), att.irot, att.theta)
+
+
+def test_qwen4_decoder_runs_a_prompt_in_pieces_and_is_causal():
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel
+    from uniserve_v1_b200.models.qwen4_exp import Qwen4ExpModel
+    mult = torch.tensor([0x9E3779B97F4A7C15 - (1 << 64), 0x2545F4914F6CDD1D], dtype=torch.int64)
+    parts, offs = torch.tensor([211, 307], dtype=torch.int64), torch.tensor([0, 211])
+    table = torch.randn(518, 6, generator=torch.Generator().manual_seed(5)).to(
+        torch.float8_e4m3fn).view(torch.uint8)
+    cfg = Qwen35MoeModel.tiny_config()
+    ngram = NgramEmbedding(table, 0.25, cfg.eos_token_id, mult, parts, offs, 2)
+    model = Qwen4ExpModel(cfg, streams=2, ple_layers=(0, 3), ngram=ngram).init_random(0)
+    assert [("self_attn" in L) for L in model.layers] == [False, False, False, True]
+    ids = torch.randint(0, 1000, (21,), generator=torch.Generator().manual_seed(6))
+    whole = model.forward(ids, model.new_state())
+    assert whole.shape == (21, cfg.vocab_size) and bool(torch.isfinite(whole).all())
+    st = model.new_state()
+    pieces = torch.cat([model.forward(ids[:7], st), model.forward(ids[7:8], st),
+                        model.forward(ids[8:], st)])
+    torch.testing.assert_close(pieces, whole, rtol=2e-3, atol=2e-4)
+    other = ids.clone()
+    other[15:] = 3
+    torch.testing.assert_close(model.forward(other, model.new_state())[:15], whole[:15],
+                               rtol=2e-3, atol=2e-4)
+    out = model.generate(ids.tolist(), 5)
+    assert out == model.generate(ids.tolist(), 5) and len(out) == 5
+    assert out[0] == int(whole[-1].argmax())

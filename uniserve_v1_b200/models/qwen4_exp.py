@@ -1,8 +1,8 @@
 """Building blocks of the Qwen4-exp ("Qwen3.8 Flash Next") family: the gated hyper-connection
 around every block, the hashed n-gram embedding and the layer that gates it into the residual
-streams, and the indexed (sparse-token) attention with its group index.  The family's decoder
-(gated delta net or indexed attention, then experts with a gated shared expert, each between two
-hyper-connections) is not assembled here.
+streams, the indexed (sparse-token) attention with its group index, and the decoder that puts
+them together (``Qwen4ExpModel``: gated delta net or indexed attention, then experts with a gated
+shared expert, each behind a hyper-connection) as FP32 formulas for one request.
 
 **Hyper-connection.**  The residual is C streams of width H, ``S`` [tokens, C * H]::
 
@@ -272,3 +272,92 @@ class IndexedAttention:
         o = torch.einsum("ths,tshd->thd", torch.softmax(sc, -1), vs).to(x.dtype)
         o = (o.float() * torch.sigmoid(gate.float())).to(x.dtype).reshape(T, H * hd)
         return (o.float() @ self.o_proj.float().t()).to(x.dtype), cache, sel
+
+
+class Qwen4ExpModel:
+    """The decoder over hyper-connected streams, one request at a time (FP32 formulas)::
+
+        x = embed(ids);  S = [x | x | ...]  (C copies);  pending = none
+        per layer:  PLE layers first fold ``pending`` and add ple(S, ngram(ids))
+                    S, h, r = attn_hc.read(S, pending);  y = linear_attn(h) or self_attn(h)
+                    S, h, r = mlp_hc.read(S, (y, r));     y = experts(h) + gated shared expert
+                    pending = (y, r)
+        read-out:   S = fold(S, pending);  logits = lm_head(mixer.read(S))      no final norm
+
+    A layer has no norm of its own: each read normalises the streams.  The gated delta network
+    and the experts are the hybrid family's (``Qwen35MoeModel``), built at the same widths; full
+    attention layers become indexed attention.  Reference behaviour:
+    crates/models/src/qwen4_exp/decoder.rs:1-17, crates/models/src/qwen4_exp/causal_lm.rs:1-30
+    (reference project paths).
+    """
+
+    def __init__(self, cfg, streams: int = 2, rank: int = 8, index_heads: int = 2,
+                 index_dim: int = 16, ratio: int = 4, budget: int = 8, ple_layers=(),
+                 ngram: Optional[NgramEmbedding] = None):
+        from .qwen3_5 import Qwen35MoeModel
+        self.cfg, self.C = cfg, streams
+        self.inner = Qwen35MoeModel(cfg, "cpu", torch.float32)
+        self.ngram, self.ple_layers = ngram, tuple(ple_layers)
+        self._hc = lambda injects=True: HyperConnection(cfg.hidden_size, streams, rank,
+                                                        cfg.rms_norm_eps, injects)
+        self._att = lambda: IndexedAttention(
+            cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+            index_heads, index_dim, ratio, budget,
+            rotary_dim=int(cfg.head_dim * cfg.partial_rotary_factor), theta=cfg.rope_theta,
+            eps=cfg.rms_norm_eps)
+        self.layers: list = []
+
+    def init_random(self, seed: int = 0) -> "Qwen4ExpModel":
+        self.inner.init_random(seed)
+        c = self.cfg
+        for i, kind in enumerate(c.layer_types):
+            L = {"attn_hc": self._hc().init_random(seed * 100 + 2 * i, 0.2),
+                 "mlp_hc": self._hc().init_random(seed * 100 + 2 * i + 1, 0.2)}
+            if kind == "full_attention":
+                L["self_attn"] = self._att().init_random(seed * 100 + i)
+            if i in self.ple_layers:
+                dim = self.ngram.table.shape[1] * self.ngram.P.shape[0]
+                L["ple"] = PleLayer(c.hidden_size, self.C, dim, eps=c.rms_norm_eps).init_random(
+                    seed * 100 + i, 0.2)
+            self.layers.append(L)
+        self.mixer = self._hc(False).init_random(seed * 100 + 99, 0.2)
+        return self
+
+    def new_state(self) -> dict:
+        return {"inner": self.inner.new_state(), "attn": {}, "ple": {}, "ids": []}
+
+    def forward(self, ids: torch.Tensor, state: dict) -> torch.Tensor:
+        """The request's next tokens ``ids`` [T] on top of ``state`` -> FP32 logits [T, vocab]."""
+        w, T = self.inner.w, ids.shape[0]
+        x = w["embed"][ids.long()]
+        S = x.repeat(1, self.C)
+        pending = None
+        if self.ngram is not None:
+            seen = len(state["ids"])
+            state["ids"] = state["ids"] + ids.tolist()
+            e = self.ngram.forward(torch.tensor(state["ids"]), torch.float32)[seen:]
+        for i, L in enumerate(self.layers):
+            if "ple" in L:
+                if pending is not None:
+                    S, pending = HyperConnection.fold(S, pending[0], pending[1], self.C), None
+                add, state["ple"][i] = L["ple"].forward(e, S, state["ple"].get(i))
+                S = S + add
+            S, h, r = L["attn_hc"].read(S, pending)
+            if "self_attn" in L:
+                y, state["attn"][i], _ = L["self_attn"].forward(h, state["attn"].get(i))
+            else:
+                y = self.inner._linear_attention(w[i], h, state["inner"][i])
+            S, h, r = L["mlp_hc"].read(S, (y, r))
+            pending = (self.inner._mlp(w[i], h), r)
+        S = HyperConnection.fold(S, pending[0], pending[1], self.C)
+        return self.mixer.read(S)[1].float() @ w["lm_head"].float().t()
+
+    def generate(self, prompt_ids: list, max_tokens: int) -> list:
+        state, out = self.new_state(), []
+        logits = self.forward(torch.tensor(prompt_ids), state)
+        for _ in range(max_tokens):
+            out.append(int(logits[-1].argmax()))
+            if out[-1] == self.cfg.eos_token_id:
+                break
+            logits = self.forward(torch.tensor(out[-1:]), state)
+        return out
