@@ -158,3 +158,33 @@ def test_qwen4_decoder_runs_a_prompt_in_pieces_and_is_causal():
     out = model.generate(ids.tolist(), 5)
     assert out == model.generate(ids.tolist(), 5) and len(out) == 5
     assert out[0] == int(whole[-1].argmax())
+
+
+def test_qwen4_decoder_serves_through_the_dense_state_engine():
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel
+    from uniserve_v1_b200.models.qwen4_exp import Qwen4ExpModel
+    cfg = Qwen35MoeModel.tiny_config()
+    mult = torch.tensor([0x9E3779B97F4A7C15 - (1 << 64), 0x2545F4914F6CDD1D], dtype=torch.int64)
+    table = torch.randn(518, 6, generator=torch.Generator().manual_seed(5)).to(
+        torch.float8_e4m3fn).view(torch.uint8)
+    ngram = NgramEmbedding(table, 0.25, cfg.eos_token_id, mult,
+                           torch.tensor([211, 307]), torch.tensor([0, 211]), 2)
+    model = Qwen4ExpModel(cfg, ple_layers=(1,), ngram=ngram).init_random(1)
+    g = torch.Generator().manual_seed(7)
+    shared = torch.randint(0, 1000, (40,), generator=g).tolist()
+    prompts = [shared + torch.randint(0, 1000, (n,), generator=g).tolist() for n in (5, 11, 3)]
+    want = [model.generate(p, 6) for p in prompts]
+    eng = DenseStateEngine(model, max_num_seqs=2, prefill_chunk=16, state_interval=8)
+    p = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    ids = [eng.add_request(q, p) for q in prompts]
+    got = {i: [] for i in ids}
+    for _ in range(200):
+        for o in eng.step():
+            got[o.request_id] += o.new_token_ids
+        if not eng.running and not eng.waiting:
+            break
+    for i, w in zip(ids, want):
+        assert got[i][:len(w)] == w, (got[i], w)
+    assert eng._stats["cached_tokens"] >= 32                         # the third began from a snapshot

@@ -295,7 +295,7 @@ class Qwen4ExpModel:
                  index_dim: int = 16, ratio: int = 4, budget: int = 8, ple_layers=(),
                  ngram: Optional[NgramEmbedding] = None):
         from .qwen3_5 import Qwen35MoeModel
-        self.cfg, self.C = cfg, streams
+        self.cfg, self.C, self.device = cfg, streams, torch.device("cpu")
         self.inner = Qwen35MoeModel(cfg, "cpu", torch.float32)
         self.ngram, self.ple_layers = ngram, tuple(ple_layers)
         self._hc = lambda injects=True: HyperConnection(cfg.hidden_size, streams, rank,
@@ -326,9 +326,13 @@ class Qwen4ExpModel:
     def new_state(self) -> dict:
         return {"inner": self.inner.new_state(), "attn": {}, "ple": {}, "ids": []}
 
-    def forward(self, ids: torch.Tensor, state: dict) -> torch.Tensor:
-        """The request's next tokens ``ids`` [T] on top of ``state`` -> FP32 logits [T, vocab]."""
+    def forward(self, ids: torch.Tensor, state: dict, pos0: Optional[int] = None) -> torch.Tensor:
+        """The request's next tokens ``ids`` [T] on top of ``state`` -> FP32 logits [T, vocab].
+        Positions follow from the state; ``pos0`` (what the dense-state engine passes) is
+        checked against it where the state counts tokens."""
         w, T = self.inner.w, ids.shape[0]
+        if pos0 is not None and self.ngram is not None and pos0 != len(state["ids"]):
+            raise ValueError(f"state holds {len(state['ids'])} tokens, the step starts at {pos0}")
         x = w["embed"][ids.long()]
         S = x.repeat(1, self.C)
         pending = None
