@@ -188,3 +188,24 @@ def test_qwen4_decoder_serves_through_the_dense_state_engine():
     for i, w in zip(ids, want):
         assert got[i][:len(w)] == w, (got[i], w)
     assert eng._stats["cached_tokens"] >= 32                         # the third began from a snapshot
+
+
+def test_qwen4_decoder_answers_chat_requests():
+    from fastapi.testclient import TestClient
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.models.qwen4_exp import Qwen4ExpModel
+    from uniserve_v1_b200.server.app import create_app
+    from uniserve_v1_b200.config.policy import Package
+    from uniserve_v1_b200.server.tokenizer import ByteTokenizer
+    model = Qwen4ExpModel.tiny()
+    eng = DenseStateEngine(model, max_num_seqs=4, max_model_len=256)
+    pkg = Package.parse('model = "random:qwen4_exp:tiny"\nserved_model_name = "q4"\n')
+    app = create_app(package=pkg, engine=eng, tokenizer=ByteTokenizer(1024, 1023),
+                     served_model_name="q4")
+    with TestClient(app) as c:
+        body = {"model": "q4", "messages": [{"role": "user", "content": "hello"}],
+                "max_tokens": 5, "temperature": 0, "ignore_eos": True}
+        a = c.post("/v1/chat/completions", json=body).json()
+        b = c.post("/v1/chat/completions", json=body).json()
+        assert a["choices"][0]["message"] == b["choices"][0]["message"]
+        assert a["usage"]["completion_tokens"] == 5

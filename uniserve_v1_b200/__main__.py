@@ -60,6 +60,8 @@ def serve(args) -> int:
         family = resolve_family(directory)
     elif pkg.model and "h3" in pkg.model.lower():
         family = "minimax_h3"
+    elif pkg.model and "qwen4_exp" in pkg.model.lower():
+        family = "qwen4_exp"
     name = pkg.served_model_name or (pkg.model or "model").split("/")[-1]
     shutdown = None
     if family == "minimax_h3":
@@ -93,6 +95,22 @@ def serve(args) -> int:
         if bus is not None:
             shutdown = MR.ReplicatedVideoService(service, bus).shutdown
         app = create_app(package=pkg, served_model_name=name, video_service=service)
+    elif family == "qwen4_exp":
+        # the hyper-connected decoder exists as FP32 formulas on the host only: a random model
+        # of every part behind the usual routes
+        from .engine.dense_state import DenseStateEngine
+        from .models.qwen4_exp import Qwen4ExpModel
+        from .server.tokenizer import load_tokenizer
+        assert world == 1, "this family is served on one rank"
+        model = Qwen4ExpModel.tiny()
+
+        def make_engine():
+            return DenseStateEngine(model, max_num_seqs=min(pkg.max_running_requests,
+                                                            pkg.scheduler_config.max_batch),
+                                    max_model_len=pkg.max_model_len or 2048)
+        tok = load_tokenizer(None, model.cfg.vocab_size, model.cfg.eos_token_id)
+        app = create_app(package=pkg, engine=make_engine(), tokenizer=tok,
+                         served_model_name=name, engine_factory=make_engine)
     elif family in ("qwen3_5_moe", "qwen3_vl"):
         # hybrid decoder (gated delta net + gated attention) or the dense Qwen3-VL language
         # model (three-axis positions, deep-stack inputs): dense per-sequence state

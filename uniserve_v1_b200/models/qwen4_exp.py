@@ -307,6 +307,19 @@ class Qwen4ExpModel:
             eps=cfg.rms_norm_eps)
         self.layers: list = []
 
+    @classmethod
+    def tiny(cls, seed: int = 0) -> "Qwen4ExpModel":
+        """A small random model of every part (tests, ``random:qwen4_exp:tiny`` deployments)."""
+        from .qwen3_5 import Qwen35MoeModel
+        cfg = Qwen35MoeModel.tiny_config()
+        g = torch.Generator().manual_seed(seed + 17)
+        table = torch.randn(518, 6, generator=g).to(torch.float8_e4m3fn).view(torch.uint8)
+        mult = torch.tensor([0x9E3779B97F4A7C15 - (1 << 64), 0x2545F4914F6CDD1D],
+                            dtype=torch.int64)
+        ngram = NgramEmbedding(table, 0.25, cfg.eos_token_id, mult, torch.tensor([211, 307]),
+                               torch.tensor([0, 211]), 2)
+        return cls(cfg, ple_layers=(0, 3), ngram=ngram).init_random(seed)
+
     def init_random(self, seed: int = 0) -> "Qwen4ExpModel":
         self.inner.init_random(seed)
         c = self.cfg
