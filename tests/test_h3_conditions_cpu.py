@@ -1,0 +1,122 @@
+"""Keyframe conditions of the video pipeline: the VAE encoder, condition rows in the denoiser,
+first / last frame requests over HTTP."""
+import base64
+import io
+
+import numpy as np
+import pytest
+import torch
+
+from uniserve_v1_b200.models.h3_vae_encoder import (VideoEncoderConfig, VideoVaeEncoder,
+                                                    normalize_pixels)
+
+
+def test_encoder_is_causal_in_time_and_follows_the_frame_rule():
+    cfg = VideoEncoderConfig.tiny(latent_channels=4, spatial=4)
+    assert (cfg.spatial, cfg.temporal) == (4, 4)
+    enc = VideoVaeEncoder(cfg).init_random(0)
+    x = torch.randn(1, 3, 17, 32, 48, generator=torch.Generator().manual_seed(0))
+    m = enc.forward(x)
+    assert m.shape == (1, 8, 5, 8, 12)                       # 17 frames -> 5 latent frames
+    later = x.clone()
+    later[:, :, 9:] = 0.0                                     # frames 9.. change
+    m2 = enc.forward(later)
+    torch.testing.assert_close(m2[:, :, :3], m[:, :, :3])     # latent frame k reads frames <= 4k
+    assert float((m2[:, :, 3:] - m[:, :, 3:]).abs().max()) > 1e-3
+    still = enc.forward(x[:, :, :1])                          # a still is the clip's first frame
+    torch.testing.assert_close(still[:, :, 0], m[:, :, 0])
+    z = enc.encode_condition(x[0, :, :1], seed=3)
+    assert z.shape == (4, 1, 8, 12)
+    torch.testing.assert_close(z, enc.encode_condition(x[0, :, :1], seed=3))
+    assert not torch.equal(z, enc.encode_condition(x[0, :, :1], seed=4))
+    torch.testing.assert_close(z, z.half().float())           # rounded through FP16
+    with pytest.raises(ValueError):
+        enc.encode_condition(x[0, :, :1, :30], seed=3)
+    with pytest.raises(ValueError):
+        VideoVaeEncoder(VideoEncoderConfig(spatial_downsample_factors=(2, 2, 3, 2, 1)))
+    px = normalize_pixels(torch.full((1, 2, 2, 3), 255, dtype=torch.uint8))
+    torch.testing.assert_close(px[:, 0, 0, 0], (1 - torch.tensor([0.485, 0.456, 0.406])) /
+                               torch.tensor([0.229, 0.224, 0.225]))
+
+
+def _tiny_pipeline():
+    from uniserve_v1_b200.models.h3_vae import (AudioVaeConfig, AudioVaeDecoder, VideoVaeConfig,
+                                                VideoVaeDecoder)
+    from uniserve_v1_b200.models.minimax_h3 import H3Config, H3Transformer
+    cfg = H3Config.tiny()
+    cfg.vae_spatial = 64
+    tr = H3Transformer(cfg, "cpu", torch.float32).init_random(0)
+    vc = VideoVaeConfig.tiny()
+    vc.latent_channels, vc.spatial = cfg.latent_channels, 64
+    vv = VideoVaeDecoder(vc, "cpu", torch.float32).init_random(1)
+    av = AudioVaeDecoder(AudioVaeConfig(latent_channels=cfg.audio_channels, decoder_dim=128,
+                                        rates=(5, 5, 2, 2, 2, 2, 2), kernels=(9, 9, 4, 4, 4, 4, 4),
+                                        res_kernels=(3,), res_dilations=(1,)), "cpu").init_random(2)
+    enc = VideoVaeEncoder(VideoEncoderConfig.tiny(cfg.latent_channels, 64)).init_random(3)
+    return cfg, tr, vv, av, enc
+
+
+def test_denoiser_takes_keyframe_rows_at_the_pinned_frames():
+    from uniserve_v1_b200.models.minimax_h3 import GROUP_VCOND, Denoiser
+    cfg, tr, _, _, enc = _tiny_pipeline()
+    den = Denoiser(tr)
+    g = torch.Generator().manual_seed(1)
+    feats = torch.randn(6, cfg.text_dim, generator=g)
+    lf, lh, lw = 3, 4, 4
+    first = enc.encode_condition(torch.randn(3, 1, 256, 256, generator=g), 1)
+    last = enc.encode_condition(torch.randn(3, 1, 256, 256, generator=g), 1)
+    st = den.prepare(5, lf, lh, lw, 8, feats, [(0, first), (-1, last)])
+    lay, per = st.layout, 4
+    assert lay.n_cond == 2 * per and st.cond_rows.shape == (2 * per, cfg.hidden_size)
+    c0 = lay.n_video + lay.n_audio + lay.n_text
+    torch.testing.assert_close(lay.coords[:, c0:c0 + per], lay.coords[:, :per])
+    torch.testing.assert_close(lay.coords[:, c0 + per:c0 + 2 * per],
+                               lay.coords[:, 2 * per:3 * per])
+    assert bool((lay.mod_index[c0:c0 + 2 * per] == 3 * GROUP_VCOND).all())
+    a = den.run(st).video.clone()
+    plain = den.run(den.prepare(5, lf, lh, lw, 8, feats)).video
+    other = den.run(den.prepare(5, lf, lh, lw, 8, feats, [(0, last), (-1, first)])).video
+    again = den.run(den.prepare(5, lf, lh, lw, 8, feats, [(0, first), (-1, last)])).video
+    assert torch.isfinite(a).all() and torch.equal(a, again)
+    assert not torch.allclose(a, plain) and not torch.allclose(a, other)
+    with pytest.raises(ValueError):
+        den.prepare(5, lf, lh, lw, 8, feats, [(0, first[:, :, :2])])
+
+
+def _png(seed: int) -> str:
+    from PIL import Image
+    rgb = np.random.default_rng(seed).integers(0, 255, (90, 120, 3), dtype=np.uint8)
+    buf = io.BytesIO()
+    Image.fromarray(rgb).save(buf, format="PNG")
+    return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+
+def test_first_and_last_frame_requests_over_http():
+    from fastapi.testclient import TestClient
+    from uniserve_v1_b200.config.policy import Package
+    from uniserve_v1_b200.server.app import create_app
+    from uniserve_v1_b200.server.video_service import VideoService
+    cfg, tr, vv, av, enc = _tiny_pipeline()
+    pkg = Package.parse('model = "random:h3:tiny"\nserved_model_name = "FastH3"\n')
+    body = {"model": "FastH3", "prompt": "a kite", "size": "256x256", "seconds": 4, "seed": 9,
+            "input_references": [{"type": "image", "url": _png(0), "frame_index": 0},
+                                 {"type": "image", "url": _png(1), "frame_index": -1}]}
+    bare = VideoService(tr, vv, av, sizes=["256x256"], max_seconds=5)
+    with TestClient(create_app(package=pkg, video_service=bare, served_model_name="FastH3")) as c:
+        assert c.get("/v1/capabilities").json()["tasks"] == ["t2va"]
+        r = c.post("/v1/videos/sync", json=body)
+        assert r.status_code == 400 and r.json()["error"]["param"] == "input_references"
+        plain = c.post("/v1/videos/sync", json={k: v for k, v in body.items()
+                                                if k != "input_references"})
+        assert plain.status_code == 200
+    svc = VideoService(tr, vv, av, sizes=["256x256"], max_seconds=5, video_encoder=enc)
+    with TestClient(create_app(package=pkg, video_service=svc, served_model_name="FastH3")) as c:
+        assert c.get("/v1/capabilities").json()["tasks"] == ["t2va", "fl2va"]
+        r = c.post("/v1/videos/sync", json=body)
+        assert r.status_code == 200, r.text
+        assert r.content[4:8] == b"ftyp" and r.content != plain.content
+        again = c.post("/v1/videos/sync", json=body)
+        assert again.content == r.content
+        body["input_references"][0]["url"] = "data:image/png;base64,AAAA"
+        bad = c.post("/v1/videos/sync", json=body)
+        assert bad.status_code == 400 and bad.json()["error"]["param"] == "input_references"

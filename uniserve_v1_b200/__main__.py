@@ -89,7 +89,12 @@ def serve(args) -> int:
             vv.cfg.latent_channels = cfg.latent_channels
             vv = VideoVaeDecoder(vv.cfg, device, dtype).init_random(1)
         av = AudioVaeDecoder(AudioVaeConfig.tiny() if tiny else AudioVaeConfig(), device).init_random(2)
-        service = VideoService(tr, vv, av, max_seconds=15)
+        # the VAE's causal-convolution encoder turns first / last frame images into condition rows
+        from .models.h3_vae_encoder import VideoEncoderConfig, VideoVaeEncoder
+        ec = VideoEncoderConfig.tiny(cfg.latent_channels, cfg.vae_spatial) if tiny \
+            else VideoEncoderConfig(latent_channels=cfg.latent_channels)
+        service = VideoService(tr, vv, av, max_seconds=15,
+                               video_encoder=VideoVaeEncoder(ec, device).init_random(3))
         if rank > 0:
             return 0 if MR.video_follower_loop(service, bus) >= 0 else 1
         if bus is not None:

@@ -602,6 +602,7 @@ class DenoiseState:
     text_rows: torch.Tensor
     step: int = 0
     seed: int = 0
+    cond_rows: Optional[torch.Tensor] = None    # [n_cond, hidden] FP32, fixed over the steps
 
 
 class Denoiser:
@@ -619,21 +620,39 @@ class Denoiser:
             model.build_level_tables(self.video_sigmas[:-1], self.audio_sigmas[:-1])
 
     def prepare(self, seed: int, latent_frames: int, lat_h: int, lat_w: int, n_audio: int,
-                text_features: torch.Tensor) -> DenoiseState:
-        from ..ops.diffusion import philox_normal
+                text_features: torch.Tensor, conditions=None) -> DenoiseState:
+        """``conditions``: keyframes as (latent frame index, latent [C, 1, lat_h, lat_w]) pairs.
+        Their rows follow the text rows in the visual-condition timestep group, at the rotary
+        coordinates of the frame they pin, and stay as encoded through every step."""
+        from ..ops.diffusion import patchify, philox_normal
         m, cfg = self.model, self.model.cfg
         dev = m.device
+        conditions = list(conditions or [])
+        per = (lat_h // 2) * (lat_w // 2)
         layout = build_layout(cfg, latent_frames, lat_h, lat_w, n_audio, text_features.shape[0],
-                              m.sp, 0, dev)
+                              m.sp, per * len(conditions), dev)
+        cond_rows = None
+        if conditions:
+            c0 = layout.n_video + layout.n_audio + layout.n_text
+            rows = []
+            for k, (frame, latent) in enumerate(conditions):
+                if tuple(latent.shape) != (cfg.latent_channels, 1, lat_h, lat_w):
+                    raise ValueError(f"a keyframe latent is [{cfg.latent_channels}, 1, {lat_h}, "
+                                     f"{lat_w}], got {tuple(latent.shape)}")
+                frame = frame % latent_frames
+                layout.coords[:, c0 + k * per:c0 + (k + 1) * per] = \
+                    layout.coords[:, frame * per:(frame + 1) * per]
+                rows.append(patchify(latent.to(dev).float()) @ m.proj_in.t())
+            cond_rows = torch.cat(rows, 0)
         video = philox_normal((cfg.latent_channels, latent_frames, lat_h, lat_w), seed, 0, 1.0, dev)
         audio = philox_normal((n_audio, cfg.audio_channels), seed, 1, 1.0, dev)
         text_rows = m.refine_text(text_features.to(dev))
-        return DenoiseState(layout, video, audio, text_rows, 0, seed)
+        return DenoiseState(layout, video, audio, text_rows, 0, seed, cond_rows)
 
     def step(self, st: DenoiseState) -> DenoiseState:
         from ..ops.diffusion import scaled_add_, unpatchify
         m, cfg, i = self.model, self.model.cfg, st.step
-        h = m.embed_rows(st.layout, st.video, st.audio, st.text_rows)
+        h = m.embed_rows(st.layout, st.video, st.audio, st.text_rows, st.cond_rows)
         vel_v, vel_a = m.forward(h, st.layout, i)
         if m.sp > 1:
             vel_v, vel_a = self._gather(vel_v, vel_a, st.layout)

@@ -496,6 +496,7 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         @app.get("/v1/capabilities")
         async def caps():
             c = capabilities(video_service.sizes, video_service.max_seconds, video_service.steps)
+            c["tasks"] = list(video_service.tasks)
             c["model"] = s.served
             return c
 
@@ -515,7 +516,7 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
             if req.model != s.served:
                 raise LookupError(req.model)
             return req, plan_request(req, video_service.sizes, video_service.max_seconds,
-                                     video_service.steps)
+                                     video_service.steps, served_tasks=video_service.tasks)
 
         def _video_error(e):
             if isinstance(e, ValidationError):
@@ -538,6 +539,8 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
             job = video_service.submit(req.prompt, plan)
             await job.wait()
             if job.state != "completed":
+                if (job.error or "").startswith("input_error"):     # the request's own media
+                    return _err(400, job.error, param="input_references")
                 return _err(500, job.error or "generation failed", "server_error")
             return Response(job.content, media_type="video/mp4",
                             headers={"x-video-size": f"{plan.width}x{plan.height}",

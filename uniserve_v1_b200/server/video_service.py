@@ -117,9 +117,14 @@ class VideoJob:
 class VideoService:
     def __init__(self, transformer: H3Transformer, video_vae: VideoVaeDecoder,
                  audio_vae: AudioVaeDecoder, sizes=None, max_seconds: int = 15,
-                 retention_s: float = 3600.0, store_bytes: int = 1 << 30, observation=None):
+                 retention_s: float = 3600.0, store_bytes: int = 1 << 30, observation=None,
+                 video_encoder=None):
         from .video_rules import SIZES
         self.model = transformer
+        # keyframe conditions (first / last frame images) are encoded by the VAE's encoder;
+        # a deployment without one serves text-to-video only
+        self.video_encoder = video_encoder
+        self.tasks = ("t2va", "fl2va") if video_encoder is not None else ("t2va",)
         # Ranks of the sequence group also share the decode work: temporal units
         # are dealt round-robin and the encoded planes gathered on every rank
         # (crates/engine/src/runner/decoder.rs:57-70, reference project path).
@@ -216,17 +221,48 @@ class VideoService:
             job._phase_t0 = now
         job.phase = phase
 
+    def _keyframe_latents(self, p, lf: int, lh: int, lw: int) -> list:
+        """The plan's keyframe images as (latent frame, latent) pairs: each image is resized
+        to the clip's raster, normalised and encoded alone (a still is one frame).  Every rank
+        encodes the same pixels under the same seed, so the latents agree without a copy."""
+        if not p.keyframes:
+            return []
+        if p.references:
+            raise ValueError("input_error: reference media (ref2va) are not served here")
+        if self.video_encoder is None:
+            raise ValueError("input_error: this deployment has no condition encoder")
+        from ..models.h3_vae_encoder import normalize_pixels
+        from . import images as IM
+        enc, out = self.video_encoder, []
+        sp = enc.cfg.spatial
+        for frame_index, ref in p.keyframes:
+            url = ref["url"] if isinstance(ref, dict) else ref.url
+            try:
+                rgb = torch.from_numpy(IM.load_image(url).copy()).to(enc.device)
+            except (ValueError, OSError) as e:
+                raise ValueError(f"input_error: input_references: {e}")
+            self.h2d_bytes += rgb.numel()
+            x = rgb.permute(2, 0, 1)[None].float()
+            x = torch.nn.functional.interpolate(x, size=(lh * sp, lw * sp), mode="bilinear",
+                                                align_corners=False, antialias=True)
+            x = x.clamp(0, 255).round().to(torch.uint8)[0].permute(1, 2, 0)[None]
+            z = enc.encode_condition(normalize_pixels(x), seed=p.seed)
+            out.append((0 if frame_index == 0 else lf - 1, z))
+        return out
+
     def generate(self, job: VideoJob) -> bytes:
         cfg, p, dev = self.model.cfg, job.plan, self.model.device
+        lf, lh, lw = cfg.latent_shape(p.num_frames, p.width, p.height)
+        self._enter(job, "MediaRead")
+        conditions = self._keyframe_latents(p, lf, lh, lw)
         self._enter(job, "TextEncode")
         feats = self.text.encode(job.prompt, "cpu")
         if dev.type == "cuda":
             feats = feats.pin_memory().to(dev, non_blocking=True)
             self.h2d_bytes += feats.numel() * feats.element_size()
         self._enter(job, "LatentPrepare")
-        lf, lh, lw = cfg.latent_shape(p.num_frames, p.width, p.height)
         n_audio_rows = cfg.audio_rows(p.num_frames)
-        st = self.denoiser.prepare(p.seed, lf, lh, lw, n_audio_rows, feats)
+        st = self.denoiser.prepare(p.seed, lf, lh, lw, n_audio_rows, feats, conditions)
         saved = self.latent_pool.get(job.id)
         if saved is not None and saved["video"].shape == st.video.shape:
             st.video.copy_(saved["video"].to(st.video.device))
