@@ -81,6 +81,16 @@ def test_denoiser_takes_keyframe_rows_at_the_pinned_frames():
     assert not torch.allclose(a, plain) and not torch.allclose(a, other)
     with pytest.raises(ValueError):
         den.prepare(5, lf, lh, lw, 8, feats, [(0, first[:, :, :2])])
+    # reference images: the clip's spatial grid, one time unit apart, before the clip
+    st = den.prepare(5, lf, lh, lw, 8, feats, [(None, first), (0, last), (None, last)])
+    lay = st.layout
+    c0 = lay.n_video + lay.n_audio + lay.n_text
+    assert lay.coords[0, c0:c0 + per].tolist() == [-2.0] * per
+    assert lay.coords[0, c0 + 2 * per:c0 + 3 * per].tolist() == [-1.0] * per
+    torch.testing.assert_close(lay.coords[1:, c0:c0 + per], lay.coords[1:, :per])
+    torch.testing.assert_close(lay.coords[:, c0 + per:c0 + 2 * per], lay.coords[:, :per])
+    b = den.run(st).video
+    assert torch.isfinite(b).all() and not torch.allclose(b, a)
 
 
 def _png(seed: int) -> str:
@@ -111,12 +121,18 @@ def test_first_and_last_frame_requests_over_http():
         assert plain.status_code == 200
     svc = VideoService(tr, vv, av, sizes=["256x256"], max_seconds=5, video_encoder=enc)
     with TestClient(create_app(package=pkg, video_service=svc, served_model_name="FastH3")) as c:
-        assert c.get("/v1/capabilities").json()["tasks"] == ["t2va", "fl2va"]
+        assert c.get("/v1/capabilities").json()["tasks"] == ["t2va", "fl2va", "ref2va"]
         r = c.post("/v1/videos/sync", json=body)
         assert r.status_code == 200, r.text
         assert r.content[4:8] == b"ftyp" and r.content != plain.content
         again = c.post("/v1/videos/sync", json=body)
         assert again.content == r.content
+        refs = dict(body, input_references=[{"type": "image", "url": _png(2)}])
+        with_ref = c.post("/v1/videos/sync", json=refs)
+        assert with_ref.status_code == 200 and with_ref.content not in (r.content, plain.content)
+        refs["input_references"] = [{"type": "audio", "url": "file:///nowhere.wav"}]
+        no = c.post("/v1/videos/sync", json=refs)
+        assert no.status_code == 400 and "audio" in no.json()["error"]["message"]
         body["input_references"][0]["url"] = "data:image/png;base64,AAAA"
         bad = c.post("/v1/videos/sync", json=body)
         assert bad.status_code == 400 and bad.json()["error"]["param"] == "input_references"

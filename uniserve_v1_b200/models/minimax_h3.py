@@ -621,9 +621,12 @@ class Denoiser:
 
     def prepare(self, seed: int, latent_frames: int, lat_h: int, lat_w: int, n_audio: int,
                 text_features: torch.Tensor, conditions=None) -> DenoiseState:
-        """``conditions``: keyframes as (latent frame index, latent [C, 1, lat_h, lat_w]) pairs.
-        Their rows follow the text rows in the visual-condition timestep group, at the rotary
-        coordinates of the frame they pin, and stay as encoded through every step."""
+        """``conditions``: (latent frame index, latent [C, 1, lat_h, lat_w]) pairs.  A keyframe
+        names the frame it pins (0, or -1 for the last) and sits at that frame's rotary
+        coordinates; a reference image has index ``None`` and sits on the same spatial grid one
+        time unit apart from the others, before the clip (the k-th of n at time k - n).  The rows
+        follow the text rows in the visual-condition timestep group and stay as encoded through
+        every step."""
         from ..ops.diffusion import patchify, philox_normal
         m, cfg = self.model, self.model.cfg
         dev = m.device
@@ -639,9 +642,14 @@ class Denoiser:
                 if tuple(latent.shape) != (cfg.latent_channels, 1, lat_h, lat_w):
                     raise ValueError(f"a keyframe latent is [{cfg.latent_channels}, 1, {lat_h}, "
                                      f"{lat_w}], got {tuple(latent.shape)}")
-                frame = frame % latent_frames
-                layout.coords[:, c0 + k * per:c0 + (k + 1) * per] = \
-                    layout.coords[:, frame * per:(frame + 1) * per]
+                own = layout.coords[:, c0 + k * per:c0 + (k + 1) * per]
+                if frame is None:
+                    refs = [j for j, (f, _) in enumerate(conditions) if f is None]
+                    own.copy_(layout.coords[:, :per])
+                    own[0] = float(refs.index(k) - len(refs))
+                else:
+                    frame = frame % latent_frames
+                    own.copy_(layout.coords[:, frame * per:(frame + 1) * per])
                 rows.append(patchify(latent.to(dev).float()) @ m.proj_in.t())
             cond_rows = torch.cat(rows, 0)
         video = philox_normal((cfg.latent_channels, latent_frames, lat_h, lat_w), seed, 0, 1.0, dev)

@@ -124,7 +124,7 @@ class VideoService:
         # keyframe conditions (first / last frame images) are encoded by the VAE's encoder;
         # a deployment without one serves text-to-video only
         self.video_encoder = video_encoder
-        self.tasks = ("t2va", "fl2va") if video_encoder is not None else ("t2va",)
+        self.tasks = ("t2va", "fl2va", "ref2va") if video_encoder is not None else ("t2va",)
         # Ranks of the sequence group also share the decode work: temporal units
         # are dealt round-robin and the encoded planes gathered on every rank
         # (crates/engine/src/runner/decoder.rs:57-70, reference project path).
@@ -222,20 +222,23 @@ class VideoService:
         job.phase = phase
 
     def _keyframe_latents(self, p, lf: int, lh: int, lw: int) -> list:
-        """The plan's keyframe images as (latent frame, latent) pairs: each image is resized
-        to the clip's raster, normalised and encoded alone (a still is one frame).  Every rank
-        encodes the same pixels under the same seed, so the latents agree without a copy."""
-        if not p.keyframes:
+        """The plan's keyframe and reference images as (latent frame, latent) pairs (frame
+        ``None`` for a reference): each image is resized to the clip's raster, normalised and
+        encoded alone (a still is one frame).  Every rank encodes the same pixels under the
+        same seed, so the latents agree without a copy."""
+        if not p.keyframes and not p.references:
             return []
-        if p.references:
-            raise ValueError("input_error: reference media (ref2va) are not served here")
+        kind = lambda r: r["type"] if isinstance(r, dict) else r.type
+        if any(kind(r) != "image" for r in p.references):
+            raise ValueError("input_error: input_references: reference clips and audio tracks "
+                             "are not served here, reference images are")
         if self.video_encoder is None:
             raise ValueError("input_error: this deployment has no condition encoder")
         from ..models.h3_vae_encoder import normalize_pixels
         from . import images as IM
         enc, out = self.video_encoder, []
         sp = enc.cfg.spatial
-        for frame_index, ref in p.keyframes:
+        for frame_index, ref in list(p.keyframes) + [(None, r) for r in p.references]:
             url = ref["url"] if isinstance(ref, dict) else ref.url
             try:
                 rgb = torch.from_numpy(IM.load_image(url).copy()).to(enc.device)
@@ -247,7 +250,7 @@ class VideoService:
                                                 align_corners=False, antialias=True)
             x = x.clamp(0, 255).round().to(torch.uint8)[0].permute(1, 2, 0)[None]
             z = enc.encode_condition(normalize_pixels(x), seed=p.seed)
-            out.append((0 if frame_index == 0 else lf - 1, z))
+            out.append((None if frame_index is None else 0 if frame_index == 0 else lf - 1, z))
         return out
 
     def generate(self, job: VideoJob) -> bytes:
