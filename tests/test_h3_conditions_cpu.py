@@ -39,6 +39,59 @@ def test_encoder_is_causal_in_time_and_follows_the_frame_rule():
                                torch.tensor([0.229, 0.224, 0.225]))
 
 
+def test_audio_encoder_keeps_channels_apart_and_projects_causally():
+    from uniserve_v1_b200.models.h3_audio_encoder import (AudioEncoderConfig, AudioVaeEncoder,
+                                                          padded_samples)
+    cfg = AudioEncoderConfig.tiny(latent_channels=8)
+    assert cfg.hop == 8 and AudioEncoderConfig().hop == 800           # 40 latent frames / s
+    enc = AudioVaeEncoder(cfg).init_random(0)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 1, cfg.hop * 10, generator=g) * 0.3
+    z = enc.encode(x)
+    assert z.shape == (20, 8) and bool(torch.isfinite(z).all())
+    muted = x.clone()
+    muted[1] = 0.0                                                     # the other channel
+    z2 = enc.encode(muted).view(10, 2, 8)
+    torch.testing.assert_close(z2[:, 0], z.view(10, 2, 8)[:, 0])
+    assert not torch.allclose(z2[:, 1], z.view(10, 2, 8)[:, 1])
+    rows = torch.randn(10, cfg.latent_dim, generator=g)
+    later = rows.clone()
+    later[6:] = 0.0
+    torch.testing.assert_close(enc.project(later)[:6], enc.project(rows)[:6])
+    assert padded_samples(17, 8) == 24 and padded_samples(16, 8) == 16
+    for bad in (x[:1], x[:, :, :-1], x.double()):
+        with pytest.raises(ValueError):
+            enc.encode(bad)
+    with pytest.raises(ValueError):
+        padded_samples(0, 8)
+    with pytest.raises(ValueError):
+        AudioVaeEncoder(AudioEncoderConfig(latent_dim=30, latent_channels=8))
+
+
+def _wav(seed: int, rate: int = 320, seconds: float = 0.5, channels: int = 1) -> str:
+    import wave
+    pcm = (np.random.default_rng(seed).standard_normal((int(rate * seconds), channels)) * 8000
+           ).astype(np.int16)
+    buf = io.BytesIO()
+    with wave.open(buf, "wb") as wv:
+        wv.setnchannels(channels)
+        wv.setsampwidth(2)
+        wv.setframerate(rate)
+        wv.writeframes(pcm.tobytes())
+    return "data:audio/wav;base64," + base64.b64encode(buf.getvalue()).decode()
+
+
+def test_wav_tracks_load_as_the_stereo_pair():
+    from uniserve_v1_b200.models.h3_audio_encoder import load_wav
+    mono = load_wav(_wav(0, 320, 0.5, 1), 320)
+    assert mono.shape == (2, 1, 160) and torch.equal(mono[0], mono[1])
+    stereo = load_wav(_wav(1, 640, 0.5, 2), 320)                       # resampled
+    assert stereo.shape == (2, 1, 160) and not torch.equal(stereo[0], stereo[1])
+    for bad in ("http://x/y.wav", "data:audio/wav;base64,AAAA", "data:audio/wav,xx"):
+        with pytest.raises(ValueError):
+            load_wav(bad, 320)
+
+
 def _tiny_pipeline():
     from uniserve_v1_b200.models.h3_vae import (AudioVaeConfig, AudioVaeDecoder, VideoVaeConfig,
                                                 VideoVaeDecoder)
@@ -91,6 +144,22 @@ def test_denoiser_takes_keyframe_rows_at_the_pinned_frames():
     torch.testing.assert_close(lay.coords[:, c0 + per:c0 + 2 * per], lay.coords[:, :per])
     b = den.run(st).video
     assert torch.isfinite(b).all() and not torch.allclose(b, a)
+    # a reference track: clean audio-condition rows spread over its time unit
+    from uniserve_v1_b200.models.minimax_h3 import GROUP_ACOND, TAG_AUDIO
+    track = torch.randn(6, cfg.audio_channels, generator=g)
+    st = den.prepare(5, lf, lh, lw, 8, feats, [(None, track), (None, first)])
+    lay = st.layout
+    c0 = lay.n_video + lay.n_audio + lay.n_text
+    assert lay.n_cond == 6 + per and st.cond_rows.shape[0] == 6 + per
+    assert bool((lay.mod_index[c0:c0 + 6] == 3 * GROUP_ACOND + TAG_AUDIO).all())
+    assert bool((lay.mod_index[c0 + 6:c0 + 6 + per] == 3 * GROUP_VCOND).all())
+    t = lay.coords[0, c0:c0 + 6]
+    assert float(t[0]) == -2.0 and bool((t[1:] > t[:-1]).all()) and float(t[-1]) < -1.0
+    assert lay.coords[0, c0 + 6:c0 + 6 + per].tolist() == [-1.0] * per
+    c = den.run(st)
+    assert torch.isfinite(c.video).all() and torch.isfinite(c.audio).all()
+    with pytest.raises(ValueError):
+        den.prepare(5, lf, lh, lw, 8, feats, [(0, track)])
 
 
 def _png(seed: int) -> str:
@@ -130,9 +199,17 @@ def test_first_and_last_frame_requests_over_http():
         refs = dict(body, input_references=[{"type": "image", "url": _png(2)}])
         with_ref = c.post("/v1/videos/sync", json=refs)
         assert with_ref.status_code == 200 and with_ref.content not in (r.content, plain.content)
-        refs["input_references"] = [{"type": "audio", "url": "file:///nowhere.wav"}]
+        refs["input_references"] = [{"type": "audio", "url": _wav(3)}]
         no = c.post("/v1/videos/sync", json=refs)
         assert no.status_code == 400 and "audio" in no.json()["error"]["message"]
+        from uniserve_v1_b200.models.h3_audio_encoder import AudioEncoderConfig, AudioVaeEncoder
+        svc.audio_encoder = AudioVaeEncoder(AudioEncoderConfig.tiny(cfg.audio_channels)
+                                            ).init_random(4)
+        track = c.post("/v1/videos/sync", json=refs)
+        assert track.status_code == 200, track.text
+        assert track.content not in (with_ref.content, plain.content)
+        refs["input_references"] = [{"type": "video", "url": "file:///nowhere.mp4"}]
+        assert c.post("/v1/videos/sync", json=refs).status_code == 400
         body["input_references"][0]["url"] = "data:image/png;base64,AAAA"
         bad = c.post("/v1/videos/sync", json=body)
         assert bad.status_code == 400 and bad.json()["error"]["param"] == "input_references"

@@ -93,8 +93,12 @@ def serve(args) -> int:
         from .models.h3_vae_encoder import VideoEncoderConfig, VideoVaeEncoder
         ec = VideoEncoderConfig.tiny(cfg.latent_channels, cfg.vae_spatial) if tiny \
             else VideoEncoderConfig(latent_channels=cfg.latent_channels)
+        from .models.h3_audio_encoder import AudioEncoderConfig, AudioVaeEncoder
+        ac = AudioEncoderConfig.tiny(cfg.audio_channels) if tiny \
+            else AudioEncoderConfig(latent_channels=cfg.audio_channels)
         service = VideoService(tr, vv, av, max_seconds=15,
-                               video_encoder=VideoVaeEncoder(ec, device).init_random(3))
+                               video_encoder=VideoVaeEncoder(ec, device).init_random(3),
+                               audio_encoder=AudioVaeEncoder(ac, device).init_random(4))
         if rank > 0:
             return 0 if MR.video_follower_loop(service, bus) >= 0 else 1
         if bus is not None:

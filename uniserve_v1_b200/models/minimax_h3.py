@@ -624,33 +624,50 @@ class Denoiser:
         """``conditions``: (latent frame index, latent [C, 1, lat_h, lat_w]) pairs.  A keyframe
         names the frame it pins (0, or -1 for the last) and sits at that frame's rotary
         coordinates; a reference image has index ``None`` and sits on the same spatial grid one
-        time unit apart from the others, before the clip (the k-th of n at time k - n).  The rows
-        follow the text rows in the visual-condition timestep group and stay as encoded through
-        every step."""
+        time unit apart from the others, before the clip (the k-th of n at time k - n).  A
+        reference track is (None, latent rows [n, audio channels]): audio rows of the clean
+        audio-condition group spread over its time unit.  The rows follow the text rows, the
+        visual ones in the visual-condition timestep group, and stay as encoded through every
+        step."""
         from ..ops.diffusion import patchify, philox_normal
         m, cfg = self.model, self.model.cfg
         dev = m.device
         conditions = list(conditions or [])
         per = (lat_h // 2) * (lat_w // 2)
+        sizes = [lat.shape[0] if lat.dim() == 2 else per for _, lat in conditions]
         layout = build_layout(cfg, latent_frames, lat_h, lat_w, n_audio, text_features.shape[0],
-                              m.sp, per * len(conditions), dev)
+                              m.sp, sum(sizes), dev)
         cond_rows = None
         if conditions:
-            c0 = layout.n_video + layout.n_audio + layout.n_text
+            refs = [j for j, (f, _) in enumerate(conditions) if f is None]
+            at = layout.n_video + layout.n_audio + layout.n_text
             rows = []
             for k, (frame, latent) in enumerate(conditions):
-                if tuple(latent.shape) != (cfg.latent_channels, 1, lat_h, lat_w):
-                    raise ValueError(f"a keyframe latent is [{cfg.latent_channels}, 1, {lat_h}, "
-                                     f"{lat_w}], got {tuple(latent.shape)}")
-                own = layout.coords[:, c0 + k * per:c0 + (k + 1) * per]
-                if frame is None:
-                    refs = [j for j, (f, _) in enumerate(conditions) if f is None]
-                    own.copy_(layout.coords[:, :per])
-                    own[0] = float(refs.index(k) - len(refs))
+                own = layout.coords[:, at:at + sizes[k]]
+                clock = float(refs.index(k) - len(refs)) if frame is None else None
+                if latent.dim() == 2:
+                    # a reference track: audio rows, clean, along time from its place before
+                    # the clip at the generated audio's rate
+                    if frame is not None or latent.shape[1] != cfg.audio_channels:
+                        raise ValueError(f"a reference track is [rows, {cfg.audio_channels}] "
+                                         "without a frame to pin")
+                    own.zero_()
+                    own[0] = clock + torch.arange(sizes[k], device=dev, dtype=torch.float32) / \
+                        max(sizes[k], 1)
+                    layout.mod_index[at:at + sizes[k]] = 3 * GROUP_ACOND + TAG_AUDIO
+                    rows.append(latent.to(dev).float() @ m.audio_proj_in.t())
                 else:
-                    frame = frame % latent_frames
-                    own.copy_(layout.coords[:, frame * per:(frame + 1) * per])
-                rows.append(patchify(latent.to(dev).float()) @ m.proj_in.t())
+                    if tuple(latent.shape) != (cfg.latent_channels, 1, lat_h, lat_w):
+                        raise ValueError(f"a keyframe latent is [{cfg.latent_channels}, 1, "
+                                         f"{lat_h}, {lat_w}], got {tuple(latent.shape)}")
+                    if frame is None:
+                        own.copy_(layout.coords[:, :per])
+                        own[0] = clock
+                    else:
+                        frame = frame % latent_frames
+                        own.copy_(layout.coords[:, frame * per:(frame + 1) * per])
+                    rows.append(patchify(latent.to(dev).float()) @ m.proj_in.t())
+                at += sizes[k]
             cond_rows = torch.cat(rows, 0)
         video = philox_normal((cfg.latent_channels, latent_frames, lat_h, lat_w), seed, 0, 1.0, dev)
         audio = philox_normal((n_audio, cfg.audio_channels), seed, 1, 1.0, dev)

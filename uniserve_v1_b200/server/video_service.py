@@ -118,12 +118,12 @@ class VideoService:
     def __init__(self, transformer: H3Transformer, video_vae: VideoVaeDecoder,
                  audio_vae: AudioVaeDecoder, sizes=None, max_seconds: int = 15,
                  retention_s: float = 3600.0, store_bytes: int = 1 << 30, observation=None,
-                 video_encoder=None):
+                 video_encoder=None, audio_encoder=None):
         from .video_rules import SIZES
         self.model = transformer
         # keyframe conditions (first / last frame images) are encoded by the VAE's encoder;
         # a deployment without one serves text-to-video only
-        self.video_encoder = video_encoder
+        self.video_encoder, self.audio_encoder = video_encoder, audio_encoder
         self.tasks = ("t2va", "fl2va", "ref2va") if video_encoder is not None else ("t2va",)
         # Ranks of the sequence group also share the decode work: temporal units
         # are dealt round-robin and the encoded planes gathered on every rank
@@ -229,9 +229,13 @@ class VideoService:
         if not p.keyframes and not p.references:
             return []
         kind = lambda r: r["type"] if isinstance(r, dict) else r.type
-        if any(kind(r) != "image" for r in p.references):
-            raise ValueError("input_error: input_references: reference clips and audio tracks "
-                             "are not served here, reference images are")
+        if any(kind(r) == "video" for r in p.references):
+            raise ValueError("input_error: input_references: reference clips are not served "
+                             "here, reference images and audio tracks are")
+        tracks = [r for r in p.references if kind(r) == "audio"]
+        if tracks and self.audio_encoder is None:
+            raise ValueError("input_error: input_references: this deployment has no audio "
+                             "encoder")
         if self.video_encoder is None:
             raise ValueError("input_error: this deployment has no condition encoder")
         from ..models.h3_vae_encoder import normalize_pixels
@@ -240,6 +244,19 @@ class VideoService:
         sp = enc.cfg.spatial
         for frame_index, ref in list(p.keyframes) + [(None, r) for r in p.references]:
             url = ref["url"] if isinstance(ref, dict) else ref.url
+            if frame_index is None and kind(ref) == "audio":
+                from ..models.h3_audio_encoder import load_wav, padded_samples
+                ac = self.audio_encoder.cfg
+                try:
+                    wav = load_wav(url, ac.sample_rate)
+                except (ValueError, OSError) as e:
+                    raise ValueError(f"input_error: input_references: {e}")
+                wav = wav[:, :, :int(self.max_seconds * ac.sample_rate)]
+                wav = torch.nn.functional.pad(wav, (0, padded_samples(wav.shape[2], ac.hop) -
+                                                    wav.shape[2]))
+                self.h2d_bytes += wav.numel() * 4
+                out.append((None, self.audio_encoder.encode(wav.to(self.audio_encoder.device))))
+                continue
             try:
                 rgb = torch.from_numpy(IM.load_image(url).copy()).to(enc.device)
             except (ValueError, OSError) as e:
