@@ -160,6 +160,18 @@ def test_denoiser_takes_keyframe_rows_at_the_pinned_frames():
     assert torch.isfinite(c.video).all() and torch.isfinite(c.audio).all()
     with pytest.raises(ValueError):
         den.prepare(5, lf, lh, lw, 8, feats, [(0, track)])
+    # a reference clip: several latent frames within one time unit
+    clip = torch.cat([first, last, first], 1)
+    st = den.prepare(5, lf, lh, lw, 8, feats, [(None, clip)])
+    lay = st.layout
+    c0 = lay.n_video + lay.n_audio + lay.n_text
+    assert lay.n_cond == 3 * per
+    torch.testing.assert_close(lay.coords[0, c0:c0 + 3 * per],
+                               torch.tensor([-1.0, -2 / 3, -1 / 3]).repeat_interleave(per))
+    torch.testing.assert_close(lay.coords[1:, c0 + per:c0 + 2 * per], lay.coords[1:, :per])
+    assert torch.isfinite(den.run(st).video).all()
+    with pytest.raises(ValueError):
+        den.prepare(5, lf, lh, lw, 8, feats, [(0, clip)])
 
 
 def _png(seed: int) -> str:
@@ -170,7 +182,18 @@ def _png(seed: int) -> str:
     return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
 
 
-def test_first_and_last_frame_requests_over_http():
+def _clip(tmp_path, frames: int) -> str:
+    import cv2
+    path = str(tmp_path / f"clip{frames}.mp4")
+    out = cv2.VideoWriter(path, cv2.VideoWriter_fourcc(*"mp4v"), 24.0, (96, 64))
+    rng = np.random.default_rng(frames)
+    for _ in range(frames):
+        out.write(rng.integers(0, 255, (64, 96, 3), dtype=np.uint8))
+    out.release()
+    return "file://" + path
+
+
+def test_first_and_last_frame_requests_over_http(tmp_path):
     from fastapi.testclient import TestClient
     from uniserve_v1_b200.config.policy import Package
     from uniserve_v1_b200.server.app import create_app
@@ -210,6 +233,13 @@ def test_first_and_last_frame_requests_over_http():
         assert track.content not in (with_ref.content, plain.content)
         refs["input_references"] = [{"type": "video", "url": "file:///nowhere.mp4"}]
         assert c.post("/v1/videos/sync", json=refs).status_code == 400
+        refs["input_references"] = [{"type": "video", "url": _clip(tmp_path, 30)}]
+        clip = c.post("/v1/videos/sync", json=refs)
+        assert clip.status_code == 200, clip.text
+        assert clip.content not in (track.content, with_ref.content, plain.content)
+        refs["input_references"] = [{"type": "video", "url": _clip(tmp_path, 9)}]
+        short = c.post("/v1/videos/sync", json=refs)
+        assert short.status_code == 400 and "17 frames" in short.json()["error"]["message"]
         body["input_references"][0]["url"] = "data:image/png;base64,AAAA"
         bad = c.post("/v1/videos/sync", json=body)
         assert bad.status_code == 400 and bad.json()["error"]["param"] == "input_references"

@@ -624,7 +624,8 @@ class Denoiser:
         """``conditions``: (latent frame index, latent [C, 1, lat_h, lat_w]) pairs.  A keyframe
         names the frame it pins (0, or -1 for the last) and sits at that frame's rotary
         coordinates; a reference image has index ``None`` and sits on the same spatial grid one
-        time unit apart from the others, before the clip (the k-th of n at time k - n).  A
+        time unit apart from the others, before the clip (the k-th of n at time k - n); a
+        reference clip is the same with several latent frames, spread over its unit.  A
         reference track is (None, latent rows [n, audio channels]): audio rows of the clean
         audio-condition group spread over its time unit.  The rows follow the text rows, the
         visual ones in the visual-condition timestep group, and stay as encoded through every
@@ -634,7 +635,8 @@ class Denoiser:
         dev = m.device
         conditions = list(conditions or [])
         per = (lat_h // 2) * (lat_w // 2)
-        sizes = [lat.shape[0] if lat.dim() == 2 else per for _, lat in conditions]
+        sizes = [lat.shape[0] if lat.dim() == 2 else per * (lat.shape[1] if lat.dim() == 4 else 1)
+                 for _, lat in conditions]
         layout = build_layout(cfg, latent_frames, lat_h, lat_w, n_audio, text_features.shape[0],
                               m.sp, sum(sizes), dev)
         cond_rows = None
@@ -657,12 +659,17 @@ class Denoiser:
                     layout.mod_index[at:at + sizes[k]] = 3 * GROUP_ACOND + TAG_AUDIO
                     rows.append(latent.to(dev).float() @ m.audio_proj_in.t())
                 else:
-                    if tuple(latent.shape) != (cfg.latent_channels, 1, lat_h, lat_w):
+                    fr = latent.shape[1] if latent.dim() == 4 else 0
+                    if tuple(latent.shape) != (cfg.latent_channels, fr, lat_h, lat_w) or \
+                            fr < 1 or (frame is not None and fr != 1):
                         raise ValueError(f"a keyframe latent is [{cfg.latent_channels}, 1, "
-                                         f"{lat_h}, {lat_w}], got {tuple(latent.shape)}")
+                                         f"{lat_h}, {lat_w}] (a reference clip has more "
+                                         f"frames), got {tuple(latent.shape)}")
                     if frame is None:
-                        own.copy_(layout.coords[:, :per])
-                        own[0] = clock
+                        # a reference clip's latent frames share its time unit
+                        own.copy_(layout.coords[:, :per].repeat(1, fr))
+                        own[0] = clock + torch.arange(fr, device=dev, dtype=torch.float32
+                                                      ).repeat_interleave(per) / fr
                     else:
                         frame = frame % latent_frames
                         own.copy_(layout.coords[:, frame * per:(frame + 1) * per])

@@ -17,6 +17,7 @@ import uuid
 from collections import OrderedDict
 from typing import Optional
 
+import numpy as np
 import torch
 
 from ..models.h3_vae import AudioVaeDecoder, VideoVaeDecoder
@@ -229,9 +230,6 @@ class VideoService:
         if not p.keyframes and not p.references:
             return []
         kind = lambda r: r["type"] if isinstance(r, dict) else r.type
-        if any(kind(r) == "video" for r in p.references):
-            raise ValueError("input_error: input_references: reference clips are not served "
-                             "here, reference images and audio tracks are")
         tracks = [r for r in p.references if kind(r) == "audio"]
         if tracks and self.audio_encoder is None:
             raise ValueError("input_error: input_references: this deployment has no audio "
@@ -257,16 +255,31 @@ class VideoService:
                 self.h2d_bytes += wav.numel() * 4
                 out.append((None, self.audio_encoder.encode(wav.to(self.audio_encoder.device))))
                 continue
+            clip = frame_index is None and kind(ref) == "video"
             try:
-                rgb = torch.from_numpy(IM.load_image(url).copy()).to(enc.device)
+                if clip:
+                    # frames at the clip's rate, cut to the frame rule (17 n + 5, or one clip
+                    # of 17); the soundtrack of a reference clip is not read
+                    from .video_rules import FPS
+                    frames, _ = IM.load_video(url, fps=float(FPS),
+                                              max_frames=int(self.max_seconds * FPS))
+                    n = (len(frames) - 5) // 17
+                    keep = 17 * n + 5 if n >= 1 else 17 if len(frames) >= 17 else 0
+                    if keep == 0:
+                        raise ValueError("a reference clip has at least 17 frames")
+                    rgb = torch.from_numpy(np.ascontiguousarray(frames[:keep])).to(enc.device)
+                else:
+                    rgb = torch.from_numpy(IM.load_image(url).copy()).to(enc.device)[None]
             except (ValueError, OSError) as e:
                 raise ValueError(f"input_error: input_references: {e}")
             self.h2d_bytes += rgb.numel()
-            x = rgb.permute(2, 0, 1)[None].float()
+            x = rgb.permute(0, 3, 1, 2).float()
             x = torch.nn.functional.interpolate(x, size=(lh * sp, lw * sp), mode="bilinear",
                                                 align_corners=False, antialias=True)
-            x = x.clamp(0, 255).round().to(torch.uint8)[0].permute(1, 2, 0)[None]
-            z = enc.encode_condition(normalize_pixels(x), seed=p.seed)
+            x = normalize_pixels(x.clamp(0, 255).round().to(torch.uint8).permute(0, 2, 3, 1))
+            # every 17-frame clip (and the 5-frame tail) is encoded alone
+            z = torch.cat([enc.encode_condition(x[:, lo:lo + 17], seed=p.seed)
+                           for lo in range(0, x.shape[1], 17)], 1)
             out.append((None if frame_index is None else 0 if frame_index == 0 else lf - 1, z))
         return out
 
