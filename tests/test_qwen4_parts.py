@@ -155,6 +155,16 @@ def test_qwen4_decoder_runs_a_prompt_in_pieces_and_is_causal():
     other[15:] = 3
     torch.testing.assert_close(model.forward(other, model.new_state())[:15], whole[:15],
                                rtol=2e-3, atol=2e-4)
+    tri = torch.tensor([0x9E3779B97F4A7C15 - (1 << 64), 0x2545F4914F6CDD1D, 0x632BE59BD9B4E019],
+                       dtype=torch.int64)                     # 3-grams: the window reaches two back
+    ngram3 = NgramEmbedding(table, 0.25, cfg.eos_token_id, tri, torch.tensor([211, 307]),
+                            torch.tensor([0, 211]), 1)
+    m3 = Qwen4ExpModel(cfg, streams=2, ple_layers=(1,), ngram=ngram3).init_random(2)
+    assert m3.layers[1]["ple"].dil == 3
+    w3, st = m3.forward(ids, m3.new_state()), m3.new_state()
+    p3 = torch.cat([m3.forward(ids[:1], st), m3.forward(ids[1:2], st), m3.forward(ids[2:9], st),
+                    m3.forward(ids[9:], st)])
+    torch.testing.assert_close(p3, w3, rtol=2e-3, atol=2e-4)
     out = model.generate(ids.tolist(), 5)
     assert out == model.generate(ids.tolist(), 5) and len(out) == 5
     assert out[0] == int(whole[-1].argmax())

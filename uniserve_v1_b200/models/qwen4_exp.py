@@ -329,9 +329,17 @@ class Qwen4ExpModel:
             if kind == "full_attention":
                 L["self_attn"] = self._att().init_random(seed * 100 + i)
             if i in self.ple_layers:
-                dim = self.ngram.table.shape[1] * self.ngram.P.shape[0]
-                L["ple"] = PleLayer(c.hidden_size, self.C, dim, eps=c.rms_norm_eps).init_random(
-                    seed * 100 + i, 0.2)
+                # every PLE layer has a table of its own (``ple.ple_embedding``) over the same
+                # hashing constants, and its convolution is dilated by the n-gram length
+                ng = self.ngram
+                g = torch.Generator().manual_seed(seed * 100 + 50 + i)
+                table = torch.randn(ng.table.shape, generator=g).to(torch.float8_e4m3fn).view(
+                    torch.uint8)
+                L["ple_embedding"] = NgramEmbedding(table, ng.scale, ng.eos, ng.m, ng.P, ng.O,
+                                                    ng.hpn)
+                dim = ng.table.shape[1] * ng.P.shape[0]
+                L["ple"] = PleLayer(c.hidden_size, self.C, dim, dilation=int(ng.m.shape[0]),
+                                    eps=c.rms_norm_eps).init_random(seed * 100 + i, 0.2)
             self.layers.append(L)
         self.mixer = self._hc(False).init_random(seed * 100 + 99, 0.2)
         return self
@@ -352,11 +360,15 @@ class Qwen4ExpModel:
         if self.ngram is not None:
             seen = len(state["ids"])
             state["ids"] = state["ids"] + ids.tolist()
-            e = self.ngram.forward(torch.tensor(state["ids"]), torch.float32)[seen:]
+            # an n-gram reaches n - 1 tokens back (further back reads as end of text only when
+            # the request starts there)
+            back = min(seen, int(self.ngram.m.shape[0]) - 1) if seen else 0
+            recent = torch.tensor(state["ids"][seen - back:])
         for i, L in enumerate(self.layers):
             if "ple" in L:
                 if pending is not None:
                     S, pending = HyperConnection.fold(S, pending[0], pending[1], self.C), None
+                e = self._ngram_rows(L["ple_embedding"], recent, back, seen)
                 add, state["ple"][i] = L["ple"].forward(e, S, state["ple"].get(i))
                 S = S + add
             S, h, r = L["attn_hc"].read(S, pending)
@@ -368,6 +380,13 @@ class Qwen4ExpModel:
             pending = (self.inner._mlp(w[i], h), r)
         S = HyperConnection.fold(S, pending[0], pending[1], self.C)
         return self.mixer.read(S)[1].float() @ w["lm_head"].float().t()
+
+    @staticmethod
+    def _ngram_rows(emb: NgramEmbedding, recent: torch.Tensor, back: int, seen: int):
+        """Embedding rows of the new tokens; ``recent`` is the ``back`` tokens before them (the
+        n-gram's reach, or the whole history when it is shorter) and them.  The window's first
+        rows are computed and dropped."""
+        return emb.forward(recent, torch.float32)[back:]
 
     def generate(self, prompt_ids: list, max_tokens: int) -> list:
         state, out = self.new_state(), []
