@@ -219,3 +219,49 @@ def test_qwen4_decoder_answers_chat_requests():
         b = c.post("/v1/chat/completions", json=body).json()
         assert a["choices"][0]["message"] == b["choices"][0]["message"]
         assert a["usage"]["completion_tokens"] == 5
+
+
+def test_qwen4_speculative_steps_replay_every_kind_of_state():
+    """A refused draft restores the delta-rule matrices, the convolution windows of the PLE
+    layers, the attention's keys, values and raw index keys and the token history."""
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.engine.speculation import Drafter
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen4_exp import Qwen4ExpModel
+    model = Qwen4ExpModel.tiny(3)
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (9, 14)]
+    want = [model.generate(p, 9) for p in prompts]
+
+    class Oracle(Drafter):
+        k = 3
+
+        def propose(self, ids):
+            for p, w in zip(prompts, want):
+                if ids[:len(p)] == p:
+                    done = len(ids) - len(p)
+                    return w[done:done + 3]
+            return []
+
+    class HalfRight(Oracle):
+        def propose(self, ids):
+            d = super().propose(ids)
+            return d[:1] + [(t + 1) % 1000 for t in d[1:]]
+
+    sp = SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True)
+    for drafter in (Oracle(), HalfRight()):
+        eng = DenseStateEngine(model, max_num_seqs=4, state_cache_entries=0)
+        ids = [eng.add_request(p, sp) for p in prompts]
+        got = {i: [] for i in ids}
+        for _ in range(100):
+            for o in eng.speculative_step(drafter):
+                got[o.request_id] += o.new_token_ids
+            if not eng.running and not eng.waiting:
+                break
+        assert [got[i] for i in ids] == [w[:9] for w in want]
+        st = eng.spec_stats
+        assert st["proposed"] > 0
+        if isinstance(drafter, HalfRight):
+            assert 0 < st["accepted"] < st["proposed"]
+        else:
+            assert st["accepted"] == st["proposed"]
