@@ -265,3 +265,65 @@ def test_qwen4_speculative_steps_replay_every_kind_of_state():
             assert 0 < st["accepted"] < st["proposed"]
         else:
             assert st["accepted"] == st["proposed"]
+
+
+def test_qwen4_mtp_entries_in_pieces_and_chained_drafts_leave_the_cache_as_it_was():
+    from uniserve_v1_b200.models.qwen4_exp import Qwen4ExpModel, Qwen4Mtp
+    model = Qwen4ExpModel.tiny(1)
+    mtp = Qwen4Mtp(model).init_random(4)
+    ids = torch.randint(0, 1000, (18,), generator=torch.Generator().manual_seed(2))
+    logits, S = model.forward(ids, model.new_state(), return_streams=True)
+    assert S.shape == (18, model.C * model.cfg.hidden_size)
+    nxt = torch.cat([ids[1:], logits[-1].argmax()[None]])            # the token after each position
+    st = mtp.new_state()
+    S1, d = mtp.observe(S, nxt, st)
+    assert d.shape == (18, model.cfg.vocab_size) and bool(torch.isfinite(d).all())
+    st2 = mtp.new_state()
+    a = mtp.observe(S[:7], nxt[:7], st2)
+    b = mtp.observe(S[7:], nxt[7:], st2)
+    torch.testing.assert_close(torch.cat([a[1], b[1]]), d, rtol=2e-3, atol=2e-4)
+    torch.testing.assert_close(torch.cat([a[0], b[0]]), S1, rtol=2e-3, atol=2e-4)
+    other = nxt.clone()
+    other[12:] = 5                                                    # causal in its entries
+    torch.testing.assert_close(mtp.observe(S, other, mtp.new_state())[1][:12], d[:12],
+                               rtol=2e-3, atol=2e-4)
+    before = {n: t.clone() for n, t in st["attn"].items()}
+    drafts = mtp.draft(S1[-1:], d[-1], 3, st)
+    assert len(drafts) == 3 and drafts[0] == int(d[-1].argmax())
+    assert all(torch.equal(st["attn"][n], before[n]) for n in before)
+    assert mtp.draft(S1[-1:], d[-1], 3, st) == drafts
+    # the second draft is the entry chained on the drafter's own streams
+    S2, d2 = mtp.forward(S1[-1:], torch.tensor(drafts[:1]), {"attn": {n: t.clone() for n, t in
+                                                                   before.items()}})
+    assert drafts[1] == int(d2[-1].argmax())
+
+
+def test_qwen4_mtp_drafter_in_the_engine_matches_plain_decoding():
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen4_exp import Qwen4ExpModel, Qwen4Mtp, Qwen4MtpDrafter
+    model = Qwen4ExpModel.tiny(5)
+    g = torch.Generator().manual_seed(13)
+    shared = torch.randint(0, 1000, (24,), generator=g).tolist()
+    prompts = [shared + torch.randint(0, 1000, (n,), generator=g).tolist() for n in (6, 3)]
+    want = [model.generate(p, 8) for p in prompts]
+    drafter = Qwen4MtpDrafter(Qwen4Mtp(model).init_random(6), k=3)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    eng = DenseStateEngine(model, max_num_seqs=1, prefill_chunk=16, state_interval=8)
+    ids = [eng.add_request(p, sp) for p in prompts]     # the second starts from a snapshot
+    got = {i: [] for i in ids}
+    for _ in range(200):
+        for o in eng.speculative_step(drafter):
+            got[o.request_id] += o.new_token_ids
+        if not eng.running and not eng.waiting:
+            break
+    assert [got[i][:len(w)] for i, w in zip(ids, want)] == want
+    assert eng.spec_stats["proposed"] >= 3 * 4 and eng._stats["cached_tokens"] >= 16
+    # the cache the drafter keeps in a request's state holds the committed positions only
+    st = model.new_state()
+    model.forward(torch.tensor(prompts[0]), st)
+    assert st["mtp"]["attn"]["k"].shape[0] == len(prompts[0]) - 1
+    d1 = drafter.propose_from_state(prompts[0] + [7], st)
+    assert len(d1) == 3 and st["mtp"]["attn"]["k"].shape[0] == len(prompts[0]) - 1
+    assert drafter.propose_from_state(prompts[0] + [7], st) == d1
+    model.tap = None

@@ -118,8 +118,13 @@ def serve(args) -> int:
                                                             pkg.scheduler_config.max_batch),
                                     max_model_len=pkg.max_model_len or 2048)
         tok = load_tokenizer(None, model.cfg.vocab_size, model.cfg.eos_token_id)
+        drafter = None
+        if int(pkg.speculative_config.num_draft_tokens) > 0:     # the family's own MTP module
+            from .models.qwen4_exp import Qwen4Mtp, Qwen4MtpDrafter
+            drafter = Qwen4MtpDrafter(Qwen4Mtp(model).init_random(1),
+                                      k=int(pkg.speculative_config.num_draft_tokens))
         app = create_app(package=pkg, engine=make_engine(), tokenizer=tok,
-                         served_model_name=name, engine_factory=make_engine)
+                         served_model_name=name, engine_factory=make_engine, drafter=drafter)
     elif family in ("qwen3_5_moe", "qwen3_vl"):
         # hybrid decoder (gated delta net + gated attention) or the dense Qwen3-VL language
         # model (three-axis positions, deep-stack inputs): dense per-sequence state

@@ -326,8 +326,11 @@ class DenseStateEngine:
         for req in rows:
             room = min(self.config.max_model_len - req.num_tokens - 1,
                        req.params.max_tokens - len(req.output_ids) - 1)
-            d = [int(t) for t in drafter.propose(req.all_ids)][:max(0, min(drafter.k, room))]
             st = self.states[req.request_id]
+            # a drafter that keeps its own cache in the request's state reads it from there
+            d = drafter.propose_from_state(req.all_ids, st) \
+                if hasattr(drafter, "propose_from_state") else drafter.propose(req.all_ids)
+            d = [int(t) for t in d][:max(0, min(drafter.k, room))]
             keep = copy.deepcopy(st) if d else None
             toks = [req.output_ids[-1]] + d
             logits = self.model.forward(torch.tensor(toks, device=dev), st, req.num_computed)

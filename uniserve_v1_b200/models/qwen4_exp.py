@@ -296,6 +296,7 @@ class Qwen4ExpModel:
                  ngram: Optional[NgramEmbedding] = None):
         from .qwen3_5 import Qwen35MoeModel
         self.cfg, self.C, self.device = cfg, streams, torch.device("cpu")
+        self.tap = None          # called with (state, ids, streams) after every forward
         self.inner = Qwen35MoeModel(cfg, "cpu", torch.float32)
         self.ngram, self.ple_layers = ngram, tuple(ple_layers)
         self._hc = lambda injects=True: HyperConnection(cfg.hidden_size, streams, rank,
@@ -347,8 +348,10 @@ class Qwen4ExpModel:
     def new_state(self) -> dict:
         return {"inner": self.inner.new_state(), "attn": {}, "ple": {}, "ids": []}
 
-    def forward(self, ids: torch.Tensor, state: dict, pos0: Optional[int] = None) -> torch.Tensor:
-        """The request's next tokens ``ids`` [T] on top of ``state`` -> FP32 logits [T, vocab].
+    def forward(self, ids: torch.Tensor, state: dict, pos0: Optional[int] = None,
+                return_streams: bool = False):
+        """The request's next tokens ``ids`` [T] on top of ``state`` -> FP32 logits [T, vocab]
+        (with ``return_streams`` also the read-out streams [T, C * H], which the drafter reads).
         Positions follow from the state; ``pos0`` (what the dense-state engine passes) is
         checked against it where the state counts tokens."""
         w, T = self.inner.w, ids.shape[0]
@@ -379,7 +382,10 @@ class Qwen4ExpModel:
             S, h, r = L["mlp_hc"].read(S, (y, r))
             pending = (self.inner._mlp(w[i], h), r)
         S = HyperConnection.fold(S, pending[0], pending[1], self.C)
-        return self.mixer.read(S)[1].float() @ w["lm_head"].float().t()
+        logits = self.mixer.read(S)[1].float() @ w["lm_head"].float().t()
+        if self.tap is not None:
+            self.tap(state, ids, S)
+        return (logits, S) if return_streams else logits
 
     @staticmethod
     def _ngram_rows(emb: NgramEmbedding, recent: torch.Tensor, back: int, seen: int):
@@ -396,4 +402,115 @@ class Qwen4ExpModel:
             if out[-1] == self.cfg.eos_token_id:
                 break
             logits = self.forward(torch.tensor(out[-1:]), state)
+        return out
+
+
+class Qwen4Mtp:
+    """The family's multi-token-prediction module.  An entry at position i reads the model's
+    streams S of position i and the embedding e of the token at i + 1::
+
+        e'   = fc_embedding(gemma(e; pre_fc_norm_embedding))
+        S0_c = fc_hidden(gemma(S; pre_fc_norm_hidden)_c) + e'        one RMS over all C * H values
+        S'   = layer(S0)       indexed attention with a cache of its own, then experts, each
+                               behind a hyper-connection; the last combine folded
+        draft logits = lm_head(mixer.read(S'))                      the model's head
+
+    ``observe`` runs the entries of positions the model has computed (the drafter's cache then
+    holds every committed position); ``draft`` chains further entries on the drafter's own
+    streams and cuts the cache back to the committed length afterwards.  Reference behaviour:
+    crates/models/src/qwen4_exp/mtp.rs:1-43 (reference project path).
+    """
+
+    def __init__(self, model: Qwen4ExpModel):
+        self.model = model
+        c, C = model.cfg, model.C
+        H = c.hidden_size
+        z = lambda *sh: torch.zeros(*sh)
+        self.pre_fc_norm_embedding, self.pre_fc_norm_hidden = z(H), z(C * H)
+        self.fc_embedding, self.fc_hidden = z(H, H), z(H, H)
+        self.attn_hc, self.mlp_hc, self.mixer = model._hc(), model._hc(), model._hc(False)
+        self.self_attn = model._att()
+        self.mlp: dict = {}
+
+    def init_random(self, seed: int = 0, std: float = 0.2) -> "Qwen4Mtp":
+        c, g = self.model.cfg, torch.Generator().manual_seed(seed)
+        rnd = lambda *sh: torch.randn(*sh, generator=g) * std
+        H, I, S, E = c.hidden_size, c.moe_intermediate_size, c.shared_expert_intermediate_size, \
+            c.num_experts
+        self.pre_fc_norm_embedding, self.pre_fc_norm_hidden = rnd(H), rnd(self.model.C * H)
+        self.fc_embedding, self.fc_hidden = rnd(H, H) / H ** 0.5 * 5, rnd(H, H) / H ** 0.5 * 5
+        for j, m in enumerate((self.attn_hc, self.mlp_hc, self.mixer, self.self_attn)):
+            m.init_random(seed * 10 + j, std)
+        self.mlp = {"router": rnd(E, H), "w13": rnd(E, 2 * I, H) * 0.25, "w2": rnd(E, H, I) * 0.25,
+                    "s13": rnd(2 * S, H) * 0.25, "s2": rnd(H, S) * 0.25, "sgate": rnd(1, H)}
+        return self
+
+    def new_state(self) -> dict:
+        return {"attn": None}
+
+    def forward(self, S: torch.Tensor, next_ids: torch.Tensor, state: dict):
+        """S [T, C * H] of positions p .. p + T - 1 with the tokens at p + 1 .. p + T ->
+        (the entries' streams [T, C * H], draft logits [T, vocab] for positions p + 2 ..)."""
+        m, C = self.model, self.model.C
+        T, H = S.shape[0], m.cfg.hidden_size
+        e = gemma_norm(m.inner.w["embed"][next_ids.long()].float(), self.pre_fc_norm_embedding,
+                       m.cfg.rms_norm_eps) @ self.fc_embedding.t()
+        Sn = gemma_norm(S.float(), self.pre_fc_norm_hidden, m.cfg.rms_norm_eps).view(T * C, H)
+        S0 = ((Sn @ self.fc_hidden.t()).view(T, C, H) + e[:, None, :]).reshape(T, C * H)
+        S1, h, r = self.attn_hc.read(S0)
+        y, state["attn"], _ = self.self_attn.forward(h, state["attn"])
+        S1, h, r = self.mlp_hc.read(S1, (y, r))
+        S1 = HyperConnection.fold(S1, m.inner._mlp(self.mlp, h), r, C)
+        return S1, self.mixer.read(S1)[1].float() @ m.inner.w["lm_head"].float().t()
+
+    observe = forward
+
+    def draft(self, S_last: torch.Tensor, logits_last: torch.Tensor, k: int, state: dict) -> list:
+        """After ``observe`` over the committed positions: ``S_last`` [1, C * H] and
+        ``logits_last`` [vocab] are its last entry's.  Returns k draft tokens: the first is the
+        last entry's own prediction, the others come from entries chained on the drafter's
+        streams, whose cache rows are cut away again."""
+        out = [int(logits_last.argmax())]
+        kept = None if state["attn"] is None else {n: t.shape[0] for n, t in state["attn"].items()}
+        S = S_last
+        for _ in range(k - 1):
+            S, logits = self.forward(S, torch.tensor(out[-1:]), state)
+            out.append(int(logits[-1].argmax()))
+        if k > 1:
+            state["attn"] = None if kept is None else \
+                {n: t[:kept[n]] for n, t in state["attn"].items()}
+        return out
+
+
+class Qwen4MtpDrafter:
+    """Drafts with the family's own multi-token-prediction module inside the dense-state
+    engine.  The drafter's cache lives in the request's state (``state["mtp"]``), so the
+    engine's snapshots, prefix restores and replays after a refused draft carry it along.
+    After every forward of the model the entries of the positions whose next token is known
+    are run; the last position waits for its token, which ``propose_from_state`` supplies
+    before it chains the further drafts and cuts the cache back."""
+
+    def __init__(self, mtp: Qwen4Mtp, k: int = 3):
+        self.mtp, self.k = mtp, k
+        mtp.model.tap = self._tap
+
+    def _tap(self, state: dict, ids: torch.Tensor, S: torch.Tensor) -> None:
+        ms = state.setdefault("mtp", {"attn": None, "S": None})
+        rows = S[:-1] if ms["S"] is None else torch.cat([ms["S"], S[:-1]])
+        nxt = ids[1:] if ms["S"] is None else ids
+        if rows.shape[0]:
+            self.mtp.observe(rows, nxt.to(torch.int64), ms)
+        ms["S"] = S[-1:].clone()
+
+    def propose(self, token_ids) -> list:
+        return []                       # without the request's state there is nothing to read
+
+    def propose_from_state(self, token_ids, state: dict) -> list:
+        ms = state.get("mtp")
+        if ms is None or ms["S"] is None:
+            return []
+        kept = None if ms["attn"] is None else {n: t.shape[0] for n, t in ms["attn"].items()}
+        S, logits = self.mtp.forward(ms["S"], torch.tensor(list(token_ids[-1:])), ms)
+        out = self.mtp.draft(S, logits[-1], self.k, ms)
+        ms["attn"] = None if kept is None else {n: t[:kept[n]] for n, t in ms["attn"].items()}
         return out
