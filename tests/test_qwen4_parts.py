@@ -327,3 +327,30 @@ def test_qwen4_mtp_drafter_in_the_engine_matches_plain_decoding():
     assert len(d1) == 3 and st["mtp"]["attn"]["k"].shape[0] == len(prompts[0]) - 1
     assert drafter.propose_from_state(prompts[0] + [7], st) == d1
     model.tap = None
+
+
+def test_qwen4_checkpoint_round_trip(tmp_path):
+    import json
+    from uniserve_v1_b200.checkpoint.safetensors_io import (CheckpointLoader, resolve_family,
+                                                            save_file)
+    from uniserve_v1_b200.models.qwen4_exp import Qwen4ExpModel
+    model = Qwen4ExpModel.tiny(7)
+    tensors = model.export_state()
+    assert "model.language_model.layers.0.attn_hyper_connection.block_inject_weight.weight" in tensors
+    assert "model.language_model.layers.3.self_attn.indexer.index_qk_proj.weight" in tensors
+    assert tensors["model.language_model.layers.0.ple.ple_embedding.ngram_embedding.shard_0.weight"
+                   ].dtype == torch.float8_e4m3fn
+    assert "model.language_model.hyper_connection_mixer.block_inject_weight.weight" not in tensors
+    names = sorted(tensors)
+    save_file({n: tensors[n] for n in names[::2]}, tmp_path / "model-00001-of-00002.safetensors")
+    save_file({n: tensors[n] for n in names[1::2]}, tmp_path / "model-00002-of-00002.safetensors")
+    (tmp_path / "config.json").write_text(json.dumps(model.hf_config()))
+    assert resolve_family(tmp_path) == "qwen4_exp"
+    again = Qwen4ExpModel.from_checkpoint(CheckpointLoader(tmp_path))
+    assert again.C == model.C and again.ple_layers == model.ple_layers
+    assert [("self_attn" in L, "ple" in L) for L in again.layers] == \
+        [("self_attn" in L, "ple" in L) for L in model.layers]
+    ids = torch.randint(0, 1000, (19,), generator=torch.Generator().manual_seed(3))
+    torch.testing.assert_close(again.forward(ids, again.new_state()),
+                               model.forward(ids, model.new_state()), rtol=1e-4, atol=1e-5)
+    assert again.generate(ids.tolist(), 4) == model.generate(ids.tolist(), 4)

@@ -105,21 +105,26 @@ def serve(args) -> int:
             shutdown = MR.ReplicatedVideoService(service, bus).shutdown
         app = create_app(package=pkg, served_model_name=name, video_service=service)
     elif family == "qwen4_exp":
-        # the hyper-connected decoder exists as FP32 formulas on the host only: a random model
-        # of every part behind the usual routes
+        # the hyper-connected decoder exists as FP32 formulas on the host only: a checkpoint's
+        # or a random model of every part behind the usual routes (a checkpoint's ``mtp.*``
+        # tensors are not read: only the random deployment drafts with the MTP module)
         from .engine.dense_state import DenseStateEngine
         from .models.qwen4_exp import Qwen4ExpModel
         from .server.tokenizer import load_tokenizer
         assert world == 1, "this family is served on one rank"
-        model = Qwen4ExpModel.tiny()
+        if directory:
+            from .checkpoint.safetensors_io import CheckpointLoader
+            model = Qwen4ExpModel.from_checkpoint(CheckpointLoader(directory))
+        else:
+            model = Qwen4ExpModel.tiny()
 
         def make_engine():
             return DenseStateEngine(model, max_num_seqs=min(pkg.max_running_requests,
                                                             pkg.scheduler_config.max_batch),
                                     max_model_len=pkg.max_model_len or 2048)
-        tok = load_tokenizer(None, model.cfg.vocab_size, model.cfg.eos_token_id)
+        tok = load_tokenizer(directory, model.cfg.vocab_size, model.cfg.eos_token_id)
         drafter = None
-        if int(pkg.speculative_config.num_draft_tokens) > 0:     # the family's own MTP module
+        if int(pkg.speculative_config.num_draft_tokens) > 0 and not directory:
             from .models.qwen4_exp import Qwen4Mtp, Qwen4MtpDrafter
             drafter = Qwen4MtpDrafter(Qwen4Mtp(model).init_random(1),
                                       k=int(pkg.speculative_config.num_draft_tokens))

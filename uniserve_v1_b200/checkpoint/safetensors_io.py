@@ -178,6 +178,7 @@ FAMILIES = {
     "Qwen3NextForCausalLM": "qwen3_5_moe", "Qwen3_5ForCausalLM": "qwen3_5_moe",
     "Qwen3_5ForConditionalGeneration": "qwen3_5_moe", "Qwen3VLForConditionalGeneration": "qwen3_vl",
     "Qwen3VLMoeForConditionalGeneration": "qwen3_vl",
+    "Qwen4ExpForConditionalGeneration": "qwen4_exp", "Qwen4ExpForCausalLM": "qwen4_exp",
     "MiniMaxH3Pipeline": "minimax_h3", "FastH3Pipeline": "minimax_h3",
     "MiniMaxH3Transformer3DModel": "minimax_h3",
 }

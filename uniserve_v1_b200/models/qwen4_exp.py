@@ -345,6 +345,183 @@ class Qwen4ExpModel:
         self.mixer = self._hc(False).init_random(seed * 100 + 99, 0.2)
         return self
 
+    # ---------------------------------------------------------- checkpoints --
+    _HC = (("hc_norm.weight", "hc_norm"), ("input_mix_weight_up.weight", "up"))
+    _ATT = (("q_proj.weight", "q_proj"), ("k_proj.weight", "k_proj"), ("v_proj.weight", "v_proj"),
+            ("o_proj.weight", "o_proj"), ("q_norm.weight", "q_norm"), ("k_norm.weight", "k_norm"),
+            ("indexer.index_qk_proj.weight", "index_qk_proj"),
+            ("indexer.q_layernorm.weight", "q_layernorm"),
+            ("indexer.k_layernorm.weight", "k_layernorm"))
+    _PLE = (("key_proj.weight", "key_proj"), ("value_proj.weight", "value_proj"))
+
+    def hf_config(self) -> dict:
+        c, ng = self.cfg, self.ngram
+        att = next((L["self_attn"] for L in self.layers if "self_attn" in L), None)
+        text = {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size,
+                "num_hidden_layers": c.num_hidden_layers,
+                "num_attention_heads": c.num_attention_heads,
+                "num_key_value_heads": c.num_key_value_heads, "head_dim": c.head_dim,
+                "rms_norm_eps": c.rms_norm_eps, "eos_token_id": c.eos_token_id,
+                "layer_types": list(c.layer_types), "rope_theta": c.rope_theta,
+                "partial_rotary_factor": c.partial_rotary_factor,
+                "linear_num_key_heads": c.linear_num_key_heads,
+                "linear_num_value_heads": c.linear_num_value_heads,
+                "linear_key_head_dim": c.linear_key_head_dim,
+                "linear_value_head_dim": c.linear_value_head_dim,
+                "linear_conv_kernel_dim": c.linear_conv_kernel_dim,
+                "num_experts": c.num_experts, "num_experts_per_tok": c.num_experts_per_tok,
+                "moe_intermediate_size": c.moe_intermediate_size,
+                "shared_expert_intermediate_size": c.shared_expert_intermediate_size,
+                "hc_count": self.C, "hc_lowrank": self.mixer.rank,
+                "ple_layer_ids": list(self.ple_layers)}
+        if att is not None:
+            text.update(indexer_n_heads=att.ih, indexer_head_dim=att.idim,
+                        indexer_budget=att.budget, indexer_compress_ratio=att.ratio)
+        if ng is not None:
+            text.update(ngram_size=int(ng.m.shape[0]), heads_per_ngram=ng.hpn,
+                        ple_embed_dim=int(ng.table.shape[1] * ng.P.shape[0]),
+                        ple_conv_kernel_size=next(L["ple"].K for L in self.layers if "ple" in L))
+        return {"architectures": ["Qwen4ExpForConditionalGeneration"], "text_config": text}
+
+    def export_state(self) -> dict:
+        """Tensors under the names the family's checkpoints use (the hybrid family's names for
+        the gated delta network and the experts)."""
+        w, out, c = self.inner.w, {}, self.cfg
+        m = "model.language_model."
+        out[m + "embed_tokens.weight"], out["lm_head.weight"] = w["embed"], w["lm_head"]
+
+        def hc(prefix, h):
+            for name, attr in self._HC:
+                out[prefix + name] = getattr(h, attr)
+            out[prefix + "input_mix_weight_down.weight"] = h.down[:h.rank]
+            if h.injects:
+                out[prefix + "block_inject_weight.weight"] = h.down[h.rank:]
+        hc(m + "hyper_connection_mixer.", self.mixer)
+        kd = c.linear_num_key_heads * c.linear_key_head_dim
+        vd = c.linear_num_value_heads * c.linear_value_head_dim
+        I = c.moe_intermediate_size
+        for i, L in enumerate(self.layers):
+            p, W = f"{m}layers.{i}.", w[i]
+            hc(p + "attn_hyper_connection.", L["attn_hc"])
+            hc(p + "mlp_hyper_connection.", L["mlp_hc"])
+            if "self_attn" in L:
+                for name, attr in self._ATT:
+                    out[p + "self_attn." + name] = getattr(L["self_attn"], attr)
+            else:
+                a, q = p + "linear_attn.", W["qkvz"]
+                out[a + "in_proj_qkv.weight"], out[a + "in_proj_z.weight"] = \
+                    q[:2 * kd + vd], q[2 * kd + vd:2 * kd + 2 * vd]
+                Hv = c.linear_num_value_heads
+                out[a + "in_proj_b.weight"] = q[2 * kd + 2 * vd:2 * kd + 2 * vd + Hv]
+                out[a + "in_proj_a.weight"] = q[2 * kd + 2 * vd + Hv:]
+                out[a + "conv1d.weight"] = W["conv"].unsqueeze(1)
+                out[a + "dt_bias"], out[a + "A_log"] = W["dt_bias"], (-W["A"]).log()
+                out[a + "norm.weight"], out[a + "out_proj.weight"] = W["gnorm"], W["out"]
+            x = p + "mlp."
+            out[x + "gate.weight"] = W["router"]
+            out[x + "experts.gate_up_proj"] = torch.cat([W["w13"][:, I:], W["w13"][:, :I]], 1)
+            out[x + "experts.down_proj"] = W["w2"]
+            S = c.shared_expert_intermediate_size
+            out[x + "shared_expert.up_proj.weight"] = W["s13"][:S]
+            out[x + "shared_expert.gate_proj.weight"] = W["s13"][S:]
+            out[x + "shared_expert.down_proj.weight"] = W["s2"]
+            out[x + "shared_expert_gate.weight"] = W["sgate"]
+            if "ple" in L:
+                e, ple, ng = p + "ple.", L["ple"], L["ple_embedding"]
+                for name, attr in self._PLE:
+                    out[e + name] = getattr(ple, attr)
+                for n in ("norm_key", "norm_query", "norm_conv"):
+                    out[e + n + ".weight"] = getattr(ple, n).reshape(-1)
+                out[e + "conv1d.weight"] = ple.conv.unsqueeze(1)
+                t = e + "ple_embedding."
+                out[t + "ngram_embedding.shard_0.weight"] = ng.table.view(torch.float8_e4m3fn)
+                out[t + "ngram_embedding.weight_scale"] = torch.tensor([ng.scale])
+                out[t + "layer_multipliers"], out[t + "ngram_heads_vocab_sizes"] = ng.m, ng.P
+                out[t + "ngram_heads_offsets"] = ng.O
+        return {k: v.contiguous() for k, v in out.items()}
+
+    @classmethod
+    def from_checkpoint(cls, loader) -> "Qwen4ExpModel":
+        """The model a checkpoint directory states (``config.json`` with ``text_config``:
+        ``hc_count``, ``hc_lowrank``, ``indexer_*``, ``ple_layer_ids``, ``ngram_size`` ...)."""
+        from .qwen3_5 import Qwen35Config
+        t = dict(loader.config.get("text_config") or loader.config)
+        cfg = Qwen35Config.from_hf({"text_config": t})
+        f32 = lambda n: loader.get(n).to(torch.float32)
+        m = "model.language_model."
+        self = cls(cfg, streams=int(t["hc_count"]), rank=int(t["hc_lowrank"]),
+                   index_heads=int(t.get("indexer_n_heads", 1)),
+                   index_dim=int(t.get("indexer_head_dim", cfg.head_dim)),
+                   ratio=int(t.get("indexer_compress_ratio", 1)),
+                   budget=int(t.get("indexer_budget", 1)),
+                   ple_layers=tuple(t.get("ple_layer_ids") or ()))
+        self.inner.init_random(0)                       # shapes; every tensor is replaced below
+        w, c = self.inner.w, cfg
+        w["embed"] = f32(m + "embed_tokens.weight")
+        w["lm_head"] = f32("lm_head.weight") if loader.has("lm_head.weight") else w["embed"]
+
+        def hc(prefix, injects=True):
+            h = self._hc(injects)
+            for name, attr in self._HC:
+                setattr(h, attr, f32(prefix + name))
+            parts = [f32(prefix + "input_mix_weight_down.weight")]
+            if injects:
+                parts.append(f32(prefix + "block_inject_weight.weight"))
+            h.down = torch.cat(parts, 0)
+            return h
+        self.mixer = hc(m + "hyper_connection_mixer.", False)
+        I = c.moe_intermediate_size
+        for i, kind in enumerate(c.layer_types):
+            p, W = f"{m}layers.{i}.", w[i]
+            L = {"attn_hc": hc(p + "attn_hyper_connection."),
+                 "mlp_hc": hc(p + "mlp_hyper_connection.")}
+            if kind == "full_attention":
+                L["self_attn"] = self._att()
+                for name, attr in self._ATT:
+                    setattr(L["self_attn"], attr, f32(p + "self_attn." + name))
+            else:
+                a = p + "linear_attn."
+                W["qkvz"] = torch.cat([f32(a + "in_proj_qkv.weight"), f32(a + "in_proj_z.weight"),
+                                       f32(a + "in_proj_b.weight"), f32(a + "in_proj_a.weight")], 0)
+                W["conv"], W["dt_bias"] = f32(a + "conv1d.weight").squeeze(1), f32(a + "dt_bias")
+                W["A"], W["gnorm"] = -f32(a + "A_log").exp(), f32(a + "norm.weight")
+                W["out"] = f32(a + "out_proj.weight")
+            x = p + "mlp."
+            gu = f32(x + "experts.gate_up_proj")
+            W["router"], W["w13"] = f32(x + "gate.weight"), torch.cat([gu[:, I:], gu[:, :I]], 1)
+            W["w2"] = f32(x + "experts.down_proj")
+            W["s13"] = torch.cat([f32(x + "shared_expert.up_proj.weight"),
+                                  f32(x + "shared_expert.gate_proj.weight")], 0)
+            W["s2"], W["sgate"] = f32(x + "shared_expert.down_proj.weight"), \
+                f32(x + "shared_expert_gate.weight")
+            if i in self.ple_layers:
+                e = p + "ple."
+                t_ = e + "ple_embedding."
+                shards = sorted((n for n in loader.names()
+                                 if n.startswith(t_ + "ngram_embedding.shard_")),
+                                key=lambda n: int(n.split("shard_")[1].split(".")[0]))
+                table = torch.cat([loader.get(n).view(torch.uint8) for n in shards], 0) \
+                    if shards else loader.get(t_ + "ngram_embedding.weight").view(torch.uint8)
+                ng = NgramEmbedding(table, float(loader.get(t_ + "ngram_embedding.weight_scale")
+                                                 .float().reshape(-1)[0]),
+                                    c.eos_token_id, loader.get(t_ + "layer_multipliers"),
+                                    loader.get(t_ + "ngram_heads_vocab_sizes"),
+                                    loader.get(t_ + "ngram_heads_offsets"),
+                                    int(t["heads_per_ngram"]))
+                self.ngram = self.ngram or ng
+                conv = f32(e + "conv1d.weight").squeeze(1)
+                ple = PleLayer(c.hidden_size, self.C, int(t["ple_embed_dim"]),
+                               kernel=conv.shape[1], dilation=int(ng.m.shape[0]),
+                               eps=c.rms_norm_eps)
+                for name, attr in self._PLE:
+                    setattr(ple, attr, f32(e + name))
+                for n in ("norm_key", "norm_query", "norm_conv"):
+                    setattr(ple, n, f32(e + n + ".weight").view(self.C, c.hidden_size))
+                ple.conv = conv
+                L["ple"], L["ple_embedding"] = ple, ng
+            self.layers.append(L)
+        return self
+
     def new_state(self) -> dict:
         return {"inner": self.inner.new_state(), "attn": {}, "ple": {}, "ids": []}
 
