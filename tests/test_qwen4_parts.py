@@ -354,3 +354,14 @@ def test_qwen4_checkpoint_round_trip(tmp_path):
     torch.testing.assert_close(again.forward(ids, again.new_state()),
                                model.forward(ids, model.new_state()), rtol=1e-4, atol=1e-5)
     assert again.generate(ids.tolist(), 4) == model.generate(ids.tolist(), 4)
+    # the checkpoint's own drafter
+    from uniserve_v1_b200.models.qwen4_exp import Qwen4Mtp
+    mtp = Qwen4Mtp(model).init_random(8)
+    save_file(mtp.export_state(), tmp_path / "model-mtp.safetensors")
+    ld = CheckpointLoader(tmp_path)
+    assert ld.has("mtp.fc_hidden.weight") and ld.has("mtp.layers.0.self_attn.indexer.index_qk_proj.weight")
+    mtp2 = Qwen4Mtp(again).load_state(ld)
+    _, S = model.forward(ids, model.new_state(), return_streams=True)
+    nxt = torch.roll(ids, -1)
+    torch.testing.assert_close(mtp2.observe(S, nxt, mtp2.new_state())[1],
+                               mtp.observe(S, nxt, mtp.new_state())[1], rtol=1e-4, atol=1e-5)

@@ -106,15 +106,17 @@ def serve(args) -> int:
         app = create_app(package=pkg, served_model_name=name, video_service=service)
     elif family == "qwen4_exp":
         # the hyper-connected decoder exists as FP32 formulas on the host only: a checkpoint's
-        # or a random model of every part behind the usual routes (a checkpoint's ``mtp.*``
-        # tensors are not read: only the random deployment drafts with the MTP module)
+        # or a random model of every part behind the usual routes, drafting with the MTP module
+        # (the checkpoint's ``mtp.*``) when the package asks for draft tokens
         from .engine.dense_state import DenseStateEngine
         from .models.qwen4_exp import Qwen4ExpModel
         from .server.tokenizer import load_tokenizer
         assert world == 1, "this family is served on one rank"
+        ld = None
         if directory:
             from .checkpoint.safetensors_io import CheckpointLoader
-            model = Qwen4ExpModel.from_checkpoint(CheckpointLoader(directory))
+            ld = CheckpointLoader(directory)
+            model = Qwen4ExpModel.from_checkpoint(ld)
         else:
             model = Qwen4ExpModel.tiny()
 
@@ -124,10 +126,12 @@ def serve(args) -> int:
                                     max_model_len=pkg.max_model_len or 2048)
         tok = load_tokenizer(directory, model.cfg.vocab_size, model.cfg.eos_token_id)
         drafter = None
-        if int(pkg.speculative_config.num_draft_tokens) > 0 and not directory:
+        if int(pkg.speculative_config.num_draft_tokens) > 0 and \
+                (ld is None or ld.has("mtp.fc_hidden.weight")):
             from .models.qwen4_exp import Qwen4Mtp, Qwen4MtpDrafter
-            drafter = Qwen4MtpDrafter(Qwen4Mtp(model).init_random(1),
-                                      k=int(pkg.speculative_config.num_draft_tokens))
+            mtp = Qwen4Mtp(model)
+            mtp = mtp.load_state(ld) if ld is not None else mtp.init_random(1)
+            drafter = Qwen4MtpDrafter(mtp, k=int(pkg.speculative_config.num_draft_tokens))
         app = create_app(package=pkg, engine=make_engine(), tokenizer=tok,
                          served_model_name=name, engine_factory=make_engine, drafter=drafter)
     elif family in ("qwen3_5_moe", "qwen3_vl"):

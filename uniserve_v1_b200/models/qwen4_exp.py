@@ -622,6 +622,65 @@ class Qwen4Mtp:
                     "s13": rnd(2 * S, H) * 0.25, "s2": rnd(H, S) * 0.25, "sgate": rnd(1, H)}
         return self
 
+    def _hcs(self):
+        return (("mtp.layers.0.attn_hyper_connection.", "attn_hc"),
+                ("mtp.layers.0.mlp_hyper_connection.", "mlp_hc"),
+                ("mtp.hyper_connection_mixer.", "mixer"))
+
+    def export_state(self) -> dict:
+        """The module's tensors under ``mtp.*`` (one layer; the embedding and the head are the
+        model's)."""
+        c, out = self.model.cfg, {}
+        for n in ("pre_fc_norm_embedding", "pre_fc_norm_hidden", "fc_embedding", "fc_hidden"):
+            out[f"mtp.{n}.weight"] = getattr(self, n)
+        for prefix, attr in self._hcs():
+            h = getattr(self, attr)
+            for name, field in Qwen4ExpModel._HC:
+                out[prefix + name] = getattr(h, field)
+            out[prefix + "input_mix_weight_down.weight"] = h.down[:h.rank]
+            if h.injects:
+                out[prefix + "block_inject_weight.weight"] = h.down[h.rank:]
+        for name, field in Qwen4ExpModel._ATT:
+            out["mtp.layers.0.self_attn." + name] = getattr(self.self_attn, field)
+        x, W, I, S = "mtp.layers.0.mlp.", self.mlp, c.moe_intermediate_size, \
+            c.shared_expert_intermediate_size
+        out[x + "gate.weight"] = W["router"]
+        out[x + "experts.gate_up_proj"] = torch.cat([W["w13"][:, I:], W["w13"][:, :I]], 1)
+        out[x + "experts.down_proj"] = W["w2"]
+        out[x + "shared_expert.up_proj.weight"] = W["s13"][:S]
+        out[x + "shared_expert.gate_proj.weight"] = W["s13"][S:]
+        out[x + "shared_expert.down_proj.weight"] = W["s2"]
+        out[x + "shared_expert_gate.weight"] = W["sgate"]
+        return {k: v.contiguous() for k, v in out.items()}
+
+    def load_state(self, loader) -> "Qwen4Mtp":
+        if loader.has("mtp.layers.1.self_attn.q_proj.weight"):
+            raise ValueError("a multi-token-prediction module of more than one layer is not "
+                             "served: a forward is not told its step")
+        c = self.model.cfg
+        f32 = lambda n: loader.get(n).to(torch.float32)
+        for n in ("pre_fc_norm_embedding", "pre_fc_norm_hidden", "fc_embedding", "fc_hidden"):
+            setattr(self, n, f32(f"mtp.{n}.weight"))
+        for prefix, attr in self._hcs():
+            h = getattr(self, attr)
+            for name, field in Qwen4ExpModel._HC:
+                setattr(h, field, f32(prefix + name))
+            parts = [f32(prefix + "input_mix_weight_down.weight")]
+            if h.injects:
+                parts.append(f32(prefix + "block_inject_weight.weight"))
+            h.down = torch.cat(parts, 0)
+        for name, field in Qwen4ExpModel._ATT:
+            setattr(self.self_attn, field, f32("mtp.layers.0.self_attn." + name))
+        x, I = "mtp.layers.0.mlp.", c.moe_intermediate_size
+        gu = f32(x + "experts.gate_up_proj")
+        self.mlp = {"router": f32(x + "gate.weight"), "w13": torch.cat([gu[:, I:], gu[:, :I]], 1),
+                    "w2": f32(x + "experts.down_proj"),
+                    "s13": torch.cat([f32(x + "shared_expert.up_proj.weight"),
+                                      f32(x + "shared_expert.gate_proj.weight")], 0),
+                    "s2": f32(x + "shared_expert.down_proj.weight"),
+                    "sgate": f32(x + "shared_expert_gate.weight")}
+        return self
+
     def new_state(self) -> dict:
         return {"attn": None}
 
