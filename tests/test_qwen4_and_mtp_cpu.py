@@ -365,3 +365,66 @@ def test_qwen4_checkpoint_round_trip(tmp_path):
     nxt = torch.roll(ids, -1)
     torch.testing.assert_close(mtp2.observe(S, nxt, mtp2.new_state())[1],
                                mtp.observe(S, nxt, mtp.new_state())[1], rtol=1e-4, atol=1e-5)
+
+
+def test_hybrid_family_mtp_drafter_in_the_engine(tmp_path):
+    """The hybrid (gated delta net) family drafts with its own MTP layer: same answers as plain
+    decoding, the module's stream covers exactly the committed positions, batched decode steps
+    keep it in step, and a checkpoint's mtp.* tensors load."""
+    from uniserve_v1_b200.checkpoint.safetensors_io import CheckpointLoader, save_file
+    from uniserve_v1_b200.engine.dense_state import DenseStateEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_5 import HybridMtp, HybridMtpDrafter, Qwen35MoeModel
+    model = Qwen35MoeModel(Qwen35MoeModel.tiny_config(), "cpu", torch.float32).init_random(0)
+    g = torch.Generator().manual_seed(17)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (13, 7)]
+    want = [model.generate(p, 8) for p in prompts]
+    mtp = HybridMtp(model).init_random(3)
+    drafter = HybridMtpDrafter(mtp, k=2)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    eng = DenseStateEngine(model, max_num_seqs=2, state_cache_entries=0)
+    ids = [eng.add_request(p, sp) for p in prompts]
+    got = {i: [] for i in ids}
+    for n in range(200):
+        step = eng.step if n == 2 else (lambda: eng.speculative_step(drafter))   # one batched step
+        for o in step():
+            got[o.request_id] += o.new_token_ids
+        if not eng.running and not eng.waiting:
+            break
+    assert [got[i][:len(w)] for i, w in zip(ids, want)] == want
+    assert eng.spec_stats["proposed"] >= 8
+    st = model.new_state()
+    model.forward(torch.tensor(prompts[0]), st)
+    assert st.mtp["pos"] == len(prompts[0]) - 1 == st.mtp["kv"].k.shape[0]
+    d = drafter.propose_from_state(prompts[0] + [5], st)
+    assert len(d) == 2 and st.mtp["kv"].k.shape[0] == len(prompts[0]) - 1
+    assert drafter.propose_from_state(prompts[0] + [5, 6], st) == []      # the stream is behind
+    import copy
+    assert copy.deepcopy(st).mtp["pos"] == st.mtp["pos"]
+    # mtp.* names of a checkpoint
+    L, I, S = mtp.w["layer"], model.cfg.moe_intermediate_size, model.cfg.shared_expert_intermediate_size
+    t = {"mtp.fc.weight": mtp.w["fc"], "mtp.norm.weight": mtp.w["norm"] - 1,
+         "mtp.pre_fc_norm_embedding.weight": mtp.w["norm_e"] - 1,
+         "mtp.pre_fc_norm_hidden.weight": mtp.w["norm_h"] - 1,
+         "mtp.layers.0.input_layernorm.weight": L["in_norm"] - 1,
+         "mtp.layers.0.post_attention_layernorm.weight": L["post_norm"] - 1,
+         "mtp.layers.0.self_attn.q_norm.weight": L["q_norm"] - 1,
+         "mtp.layers.0.self_attn.k_norm.weight": L["k_norm"] - 1,
+         "mtp.layers.0.mlp.gate.weight": L["router"],
+         "mtp.layers.0.mlp.experts.gate_up_proj": torch.cat([L["w13"][:, I:], L["w13"][:, :I]], 1),
+         "mtp.layers.0.mlp.experts.down_proj": L["w2"],
+         "mtp.layers.0.mlp.shared_expert.up_proj.weight": L["s13"][:S],
+         "mtp.layers.0.mlp.shared_expert.gate_proj.weight": L["s13"][S:],
+         "mtp.layers.0.mlp.shared_expert.down_proj.weight": L["s2"],
+         "mtp.layers.0.mlp.shared_expert_gate.weight": L["sgate"]}
+    for n in "qkvo":
+        t[f"mtp.layers.0.self_attn.{n}_proj.weight"] = L[n]
+    save_file({k: v.contiguous() for k, v in t.items()}, tmp_path / "model.safetensors")
+    (tmp_path / "config.json").write_text("{}")
+    loaded = HybridMtp(model).load_state(CheckpointLoader(tmp_path))
+    h = torch.randn(5, model.cfg.hidden_size, generator=g)
+    from uniserve_v1_b200.models.qwen3_5 import LayerState
+    a = mtp.rows(h, torch.tensor([1, 2, 3, 4, 5]), 0, LayerState())[1]
+    b = loaded.rows(h, torch.tensor([1, 2, 3, 4, 5]), 0, LayerState())[1]
+    torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    model.tap = None

@@ -162,8 +162,13 @@ def serve(args) -> int:
                                                             pkg.scheduler_config.max_batch),
                                     max_model_len=pkg.max_model_len or 8192, tower=tower)
         tok = load_tokenizer(directory, cfg.vocab_size, cfg.eos_token_id)
+        drafter = None
+        k_draft = int(pkg.speculative_config.num_draft_tokens)
+        if k_draft > 0 and family == "qwen3_5_moe" and ld.has("mtp.fc.weight"):
+            from .models.qwen3_5 import HybridMtp, HybridMtpDrafter    # the checkpoint's drafter
+            drafter = HybridMtpDrafter(HybridMtp(model).load_state(ld), k=k_draft)
         app = create_app(package=pkg, engine=make_engine(), tokenizer=tok,
-                         served_model_name=name, engine_factory=make_engine)
+                         served_model_name=name, engine_factory=make_engine, drafter=drafter)
     else:
         from .engine.engine import LLMEngine
         from .models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel

@@ -111,9 +111,16 @@ class LayerState:
     rule: Optional[torch.Tensor] = None     # linear: [Hv, Dk, Dv] FP32
 
 
+class SequenceState(list):
+    """The per-layer states of one sequence; ``mtp`` is where a drafter keeps its own cache, so
+    that copies of the state (snapshots, replays) carry it."""
+    mtp = None
+
+
 class Qwen35MoeModel:
     def __init__(self, cfg: Qwen35Config, device="cpu", dtype=torch.bfloat16):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.tap = None      # called with (state, ids, hidden rows before the final norm, pos0)
         self.rot = int(cfg.head_dim * cfg.partial_rotary_factor)
         self.inv_freq = R.rope_inv_freq(self.rot, cfg.rope_theta, self.device)
         self.w: dict = {}
@@ -231,7 +238,7 @@ class Qwen35MoeModel:
 
     # ------------------------------------------------------------- forward --
     def new_state(self) -> list:
-        return [LayerState() for _ in self.cfg.layer_types]
+        return SequenceState(LayerState() for _ in self.cfg.layer_types)
 
     def _norm_mrope(self, x, w, pos3):
         return norm_mrope(x, w, pos3, self.inv_freq, self.rot, self.cfg.mrope_section,
@@ -314,6 +321,8 @@ class Qwen35MoeModel:
             x = x + mix
             n = R.rmsnorm(x, L["post_norm"], c.rms_norm_eps)
             x = x + self._mlp(L, n)
+        if self.tap is not None:
+            self.tap(state, ids, x, pos0)
         return F.linear(R.rmsnorm(x, w["norm"], c.rms_norm_eps), w["lm_head"],
                         out_dtype=torch.float32)
 
@@ -380,6 +389,9 @@ class Qwen35MoeModel:
                 mix = F.linear(o.reshape(B, vd), L["out"])
             x = x + mix
             x = x + self._mlp(L, R.rmsnorm(x, L["post_norm"], c.rms_norm_eps))
+        if self.tap is not None:
+            for b in range(B):
+                self.tap(states[b], tokens[b:b + 1], x[b:b + 1], int(pos3[0, b]))
         return F.linear(R.rmsnorm(x, w["norm"], c.rms_norm_eps), w["lm_head"],
                         out_dtype=torch.float32)
 
@@ -463,4 +475,120 @@ class Qwen35Multimodal:
             logits = self.text.forward(torch.tensor([tok], device=self.text.device), state, 0,
                                        positions3=p3)
             pos += 1
+        return out
+
+
+class HybridMtp:
+    """Multi-token-prediction module of the hybrid family (``mtp.*``): one gated-attention
+    decoder layer over ``fc([norm_e(embed(t_{p+1})) ; norm_h(h_p)])`` with a key / value stream
+    of its own, the model's embedding and output matrices, and ``mtp.norm`` before the head.
+    Reference behaviour: crates/models/src/qwen3/mtp.rs (reference project path)."""
+
+    def __init__(self, model: Qwen35MoeModel):
+        self.model, self.w = model, {}
+
+    def init_random(self, seed: int = 0, std: float = 0.05) -> "HybridMtp":
+        m, c = self.model, self.model.cfg
+        g = torch.Generator().manual_seed(seed)
+        rnd = lambda *sh: (torch.randn(*sh, generator=g) * std).to(m.device, m.dtype)
+        ones = lambda n: torch.ones(n, dtype=torch.float32, device=m.device)
+        H, D, I, S = c.hidden_size, c.head_dim, c.moe_intermediate_size, \
+            c.shared_expert_intermediate_size
+        L = {"kind": "full_attention", "in_norm": ones(H), "post_norm": ones(H),
+             "q": rnd(c.num_attention_heads * 2 * D, H), "k": rnd(c.num_key_value_heads * D, H),
+             "v": rnd(c.num_key_value_heads * D, H), "o": rnd(H, c.num_attention_heads * D),
+             "q_norm": ones(D), "k_norm": ones(D)}
+        if c.num_experts:
+            L.update(router=rnd(c.num_experts, H), w13=rnd(c.num_experts, 2 * I, H),
+                     w2=rnd(c.num_experts, H, I), s13=rnd(2 * S, H), s2=rnd(H, S),
+                     sgate=rnd(1, H))
+        else:
+            L.update(d13=rnd(2 * c.intermediate_size, H), d2=rnd(H, c.intermediate_size))
+        self.w = {"fc": rnd(H, 2 * H), "norm_e": ones(H), "norm_h": ones(H), "norm": ones(H),
+                  "layer": L}
+        return self
+
+    def load_state(self, loader, prefix: str = "mtp.") -> "HybridMtp":
+        m, c = self.model, self.model.cfg
+        get = lambda n, dt=None: loader.get(prefix + n).to(device=m.device, dtype=dt or m.dtype)
+        gain = lambda n: get(n, torch.float32) + 1.0
+        p, I = "layers.0.", c.moe_intermediate_size
+        L = {"kind": "full_attention", "in_norm": gain(p + "input_layernorm.weight"),
+             "post_norm": gain(p + "post_attention_layernorm.weight"),
+             "q_norm": gain(p + "self_attn.q_norm.weight"),
+             "k_norm": gain(p + "self_attn.k_norm.weight")}
+        for n in "qkvo":
+            L[n] = get(p + f"self_attn.{n}_proj.weight")
+        x = p + "mlp."
+        if c.num_experts:
+            gu = get(x + "experts.gate_up_proj")
+            L.update(router=get(x + "gate.weight"),
+                     w13=torch.cat([gu[:, I:], gu[:, :I]], 1).contiguous(),
+                     w2=get(x + "experts.down_proj").contiguous(),
+                     s13=torch.cat([get(x + "shared_expert.up_proj.weight"),
+                                    get(x + "shared_expert.gate_proj.weight")], 0),
+                     s2=get(x + "shared_expert.down_proj.weight"),
+                     sgate=get(x + "shared_expert_gate.weight"))
+        else:
+            L.update(d13=torch.cat([get(x + "up_proj.weight"), get(x + "gate_proj.weight")], 0),
+                     d2=get(x + "down_proj.weight"))
+        self.w = {"fc": get("fc.weight"), "norm_e": gain("pre_fc_norm_embedding.weight"),
+                  "norm_h": gain("pre_fc_norm_hidden.weight"), "norm": gain("norm.weight"),
+                  "layer": L}
+        return self
+
+    def rows(self, hidden: torch.Tensor, next_ids: torch.Tensor, pos0: int, st: LayerState):
+        """hidden [T, H] of positions pos0 .. with the token after each -> (the layer's output
+        [T, H], logits [T, vocab]); ``st`` is the module's own key / value stream."""
+        m, c, w = self.model, self.model.cfg, self.w
+        e = m.w["embed"][next_ids.to(m.device).long()]
+        x = F.linear(torch.cat([R.rmsnorm(e, w["norm_e"], c.rms_norm_eps),
+                                R.rmsnorm(hidden.to(m.dtype), w["norm_h"], c.rms_norm_eps)], -1),
+                     w["fc"])
+        L = w["layer"]
+        x = x + m._attention(L, R.rmsnorm(x, L["in_norm"], c.rms_norm_eps), st, pos0)
+        x = x + m._mlp(L, R.rmsnorm(x, L["post_norm"], c.rms_norm_eps))
+        return x, F.linear(R.rmsnorm(x, w["norm"], c.rms_norm_eps), m.w["lm_head"],
+                           out_dtype=torch.float32)
+
+
+class HybridMtpDrafter:
+    """Drafts with ``HybridMtp`` inside the dense-state engine.  The module's key / value
+    stream and the hidden row that still waits for its next token live in the sequence's state
+    (``state.mtp``); every forward of the model extends them, ``propose_from_state`` runs the
+    waiting row with the newest token, chains k - 1 further entries on the module's own outputs
+    and cuts the stream back."""
+
+    def __init__(self, mtp: HybridMtp, k: int = 2):
+        self.mtp, self.k = mtp, k
+        mtp.model.tap = self._tap
+
+    def _tap(self, state, ids, hidden, pos0: int) -> None:
+        if not isinstance(state, SequenceState):
+            return
+        ms = state.mtp
+        if ms is None:
+            ms = state.mtp = {"kv": LayerState(), "h": None, "pos": 0}
+        rows = hidden[:-1] if ms["h"] is None else torch.cat([ms["h"], hidden[:-1]])
+        nxt = ids[1:] if ms["h"] is None else ids
+        if rows.shape[0]:
+            self.mtp.rows(rows, nxt, ms["pos"], ms["kv"])
+            ms["pos"] += rows.shape[0]
+        ms["h"] = hidden[-1:].clone()
+
+    def propose(self, token_ids) -> list:
+        return []
+
+    def propose_from_state(self, token_ids, state) -> list:
+        ms = getattr(state, "mtp", None)
+        if ms is None or ms["h"] is None or ms["pos"] != len(token_ids) - 2:
+            return []                    # the stream does not cover the sequence: no drafts
+        kv = ms["kv"]
+        kept = 0 if kv.k is None else kv.k.shape[0]
+        h, tok, out = ms["h"], int(token_ids[-1]), []
+        for j in range(self.k):
+            h, logits = self.mtp.rows(h, torch.tensor([tok]), ms["pos"] + j, kv)
+            tok = int(logits[-1].argmax())
+            out.append(tok)
+        kv.k, kv.v = (None, None) if kept == 0 else (kv.k[:kept], kv.v[:kept])
         return out
