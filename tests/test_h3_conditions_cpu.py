@@ -39,6 +39,32 @@ def test_encoder_is_causal_in_time_and_follows_the_frame_rule():
                                torch.tensor([0.229, 0.224, 0.225]))
 
 
+def test_tiled_encode_cross_fades_the_moments():
+    from uniserve_v1_b200.models.h3_vae_encoder import blend_tiles
+    a, b = torch.full((2, 4, 6), 1.0), torch.full((2, 4, 6), 3.0)
+    out = blend_tiles([(0, 0, a), (0, 4, b)], 4, 10, 2)              # columns 4 and 5 shared
+    assert out.shape == (2, 4, 10)
+    torch.testing.assert_close(out[0, 0], torch.tensor([1, 1, 1, 1, 1 + 2 / 3, 1 + 4 / 3, 3, 3,
+                                                        3, 3.0]))
+    same = blend_tiles([(0, 0, a), (0, 4, a), (2, 0, a[:, :2]), (2, 4, a[:, :2])], 4, 10, 2)
+    torch.testing.assert_close(same, torch.ones(2, 4, 10))             # weights sum to one
+    cfg = VideoEncoderConfig.tiny(latent_channels=4, spatial=4)
+    enc = VideoVaeEncoder(cfg).init_random(0)
+    x = torch.randn(3, 1, 32, 48, generator=torch.Generator().manual_seed(1))
+    whole = enc.moments(x)
+    cfg.tile, cfg.tile_overlap = 64, 8
+    torch.testing.assert_close(enc.moments(x), whole)                  # one tile holds the raster
+    cfg.tile, cfg.tile_overlap = 32, 8
+    tiled = enc.moments(x)
+    assert tiled.shape == whole.shape and bool(torch.isfinite(tiled).all())
+    left = enc._conv("quant_conv", enc.forward(x[None, :, :, :, :32]))[0]
+    torch.testing.assert_close(tiled[..., :6], left[..., :6])          # outside the overlap
+    assert enc.encode_condition(x, 2).shape == (4, 1, 8, 12)
+    cfg.tile_overlap = 6
+    with pytest.raises(ValueError):
+        enc.moments(x)
+
+
 def test_audio_encoder_keeps_channels_apart_and_projects_causally():
     from uniserve_v1_b200.models.h3_audio_encoder import (AudioEncoderConfig, AudioVaeEncoder,
                                                           padded_samples)

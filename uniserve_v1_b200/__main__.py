@@ -92,7 +92,7 @@ def serve(args) -> int:
         # the VAE's causal-convolution encoder turns first / last frame images into condition rows
         from .models.h3_vae_encoder import VideoEncoderConfig, VideoVaeEncoder
         ec = VideoEncoderConfig.tiny(cfg.latent_channels, cfg.vae_spatial) if tiny \
-            else VideoEncoderConfig(latent_channels=cfg.latent_channels)
+            else VideoEncoderConfig(latent_channels=cfg.latent_channels, tile=768, tile_overlap=128)
         from .models.h3_audio_encoder import AudioEncoderConfig, AudioVaeEncoder
         ac = AudioEncoderConfig.tiny(cfg.audio_channels) if tiny \
             else AudioEncoderConfig(latent_channels=cfg.audio_channels)

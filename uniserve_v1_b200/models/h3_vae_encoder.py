@@ -14,8 +14,8 @@ Structure (FP32 throughout; convolutions are library calls, this is not a hot pa
 
 ``encode_condition`` samples the posterior under a seed (the same condition always encodes to
 the same latent): ``mean + exp(0.5 * clamp(logvar, -30, 20)) * noise`` rounded through FP16, then
-``(sample - latents_mean) / latents_std`` per channel.  Whole rasters are encoded at once; the
-reference's overlapping-tile encode with cross-faded moments is not built.
+``(sample - latents_mean) / latents_std`` per channel.  With ``tile`` set, a raster wider than
+the tile is encoded in overlapping tiles whose projected moments cross-fade where they meet.
 
 Reference behaviour: crates/models/src/minimax_h3/video_vae.rs:46-55, 852-886, 1082-1120
 (reference project paths).
@@ -43,6 +43,8 @@ class VideoEncoderConfig:
     norm_eps: float = 1e-6
     latents_mean: tuple = ()
     latents_std: tuple = ()
+    tile: int = 0          # pixels a side of an encode tile (0: whole rasters)
+    tile_overlap: int = 0  # pixels two neighbouring tiles share
 
     @classmethod
     def tiny(cls, latent_channels: int = 4, spatial: int = 4):
@@ -160,6 +162,26 @@ class VideoVaeEncoder:
                                w["encoder.norm_out.bias"], c.norm_eps))
         return self._conv("encoder.conv_out", causal_pad(h))
 
+    def moments(self, pixels: torch.Tensor) -> torch.Tensor:
+        """pixels [3, T, H, W] -> projected moments [2 * C, T', H / s, W / s].  A raster wider
+        than the configured tile is encoded tile by tile (each tile's moments projected by
+        ``quant_conv``) and the tiles cross-fade over their overlap."""
+        c = self.cfg
+        H, W = pixels.shape[2:]
+        one = lambda px: self._conv("quant_conv", self.forward(px[None]))[0]
+        if not c.tile or (H <= c.tile and W <= c.tile):
+            return one(pixels)
+        if c.tile % c.spatial or c.tile_overlap % c.spatial or not 0 <= c.tile_overlap < c.tile:
+            raise ValueError("encode tiles and their overlap are whole latent cells, the overlap "
+                             "smaller than the tile")
+        step, s, tiles = c.tile - c.tile_overlap, c.spatial, []
+        ys = list(range(0, max(H - c.tile_overlap, 1), step))
+        xs = list(range(0, max(W - c.tile_overlap, 1), step))
+        for y0 in ys:
+            for x0 in xs:
+                tiles.append((y0 // s, x0 // s, one(pixels[:, :, y0:y0 + c.tile, x0:x0 + c.tile])))
+        return blend_tiles(tiles, H // s, W // s, c.tile_overlap // s)
+
     def encode_condition(self, pixels: torch.Tensor, seed: int = 0) -> torch.Tensor:
         """pixels [3, T, H, W] normalised by the ImageNet constants (one frame for a still) ->
         the normalised latent [C, ceil(T / temporal), H / s, W / s] in FP32."""
@@ -169,7 +191,7 @@ class VideoVaeEncoder:
             raise ValueError(f"the video encoder reads [{c.in_channels}, frames, height, width]")
         if pixels.shape[2] % c.spatial or pixels.shape[3] % c.spatial:
             raise ValueError(f"a condition's raster is whole {c.spatial}-pixel cells")
-        m = self._conv("quant_conv", self.forward(pixels[None]))[0]
+        m = self.moments(pixels)
         mean, logvar = m[:c.latent_channels], m[c.latent_channels:].clamp(-30.0, 20.0)
         noise = philox_normal(tuple(mean.shape), seed, 7, 1.0, self.device)
         z = (mean + torch.exp(0.5 * logvar) * noise).half().float()
@@ -178,6 +200,31 @@ class VideoVaeEncoder:
             sd = torch.tensor(c.latents_std, device=self.device).view(-1, 1, 1, 1)
             z = (z - mu) / sd
         return z
+
+
+def blend_tiles(tiles: list, height: int, width: int, overlap: int) -> torch.Tensor:
+    """Stitches ``tiles`` = [(row, column, tensor [..., h, w])] into [..., height, width]: where
+    two tiles meet, the earlier fades out and the later fades in linearly over ``overlap`` cells
+    (weights i / (overlap + 1)); a tile's outer edges keep full weight."""
+    first = tiles[0][2]
+    out = torch.zeros(*first.shape[:-2], height, width, dtype=first.dtype, device=first.device)
+    total = torch.zeros(height, width, dtype=first.dtype, device=first.device)
+    for y0, x0, t in tiles:
+        h, w = t.shape[-2:]
+
+        def ramp(n, origin, limit):
+            r = torch.ones(n, dtype=first.dtype, device=first.device)
+            k = min(overlap, n)
+            if k and origin > 0:                      # fades in over what the previous tile covers
+                r[:k] = torch.arange(1, k + 1, device=first.device) / (k + 1)
+            if k and origin + n < limit:              # fades out under the next tile
+                r[n - k:] = torch.minimum(r[n - k:], torch.arange(k, 0, -1, device=first.device)
+                                          / (k + 1))
+            return r
+        wgt = ramp(h, y0, height)[:, None] * ramp(w, x0, width)[None, :]
+        out[..., y0:y0 + h, x0:x0 + w] += t * wgt
+        total[y0:y0 + h, x0:x0 + w] += wgt
+    return out / total.clamp_min(1e-12)
 
 
 def normalize_pixels(rgb_u8: torch.Tensor) -> torch.Tensor:
