@@ -237,6 +237,21 @@ def test_first_and_last_frame_requests_over_http(tmp_path):
         plain = c.post("/v1/videos/sync", json={k: v for k, v in body.items()
                                                 if k != "input_references"})
         assert plain.status_code == 200
+        # multipart: text parts only, one per field
+        form = {"model": "FastH3", "prompt": "a kite", "size": "256x256", "seconds": "4",
+                "seed": "9"}
+        same = c.post("/v1/videos/sync", data=form, files={"x": (None, "")})
+        assert same.status_code == 400                               # a field outside the schema
+        multi = c.post("/v1/videos/sync", files=[(k, (None, v)) for k, v in form.items()])
+        assert multi.status_code == 200 and multi.content == plain.content
+        up = c.post("/v1/videos/sync", data=form,
+                    files={"input_reference": ("image.png", b"\x89PNG", "image/png")})
+        assert up.status_code == 400 and up.json()["error"]["param"] == "input_reference"
+        twice = c.post("/v1/videos/sync", files=[(k, (None, v)) for k, v in form.items()] +
+                       [("seed", (None, "3"))])
+        assert twice.status_code == 400 and twice.json()["error"]["param"] == "seed"
+        assert c.post("/v1/videos/sync", content=b"x", headers={"content-type": "text/plain"}
+                      ).status_code == 415
     svc = VideoService(tr, vv, av, sizes=["256x256"], max_seconds=5, video_encoder=enc)
     with TestClient(create_app(package=pkg, video_service=svc, served_model_name="FastH3")) as c:
         assert c.get("/v1/capabilities").json()["tasks"] == ["t2va", "fl2va", "ref2va"]

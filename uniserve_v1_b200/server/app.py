@@ -34,6 +34,10 @@ from .tokenizer import IncrementalDecoder
 VERSION = "0.1.0"
 
 
+class _UnsupportedMedia(Exception):
+    pass
+
+
 def _err(status: int, message: str, type_="invalid_request_error", code=None, param=None,
          headers=None):
     return JSONResponse(openai_error(message, type_, code, param), status_code=status,
@@ -503,15 +507,27 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         async def _parse_video(request: Request):
             ctype = request.headers.get("content-type", "")
             if ctype.startswith("multipart/form-data"):
+                # every field is a text part of its own name; file parts and repeated fields
+                # are refused (media travel as URLs in ``input_references``)
                 form = await request.form()
                 data = {}
-                for k, v in form.items():
-                    data[k] = json.loads(v) if k in ("input_references", "extra_params") else v
+                for k, v in form.multi_items():
+                    if not isinstance(v, str):
+                        raise VideoRuleError(k, "file parts are not accepted: name media by URL "
+                                                "in input_references")
+                    if k in data:
+                        raise VideoRuleError(k, "the field is repeated")
+                    try:
+                        data[k] = json.loads(v) if k in ("input_references", "extra_params") else v
+                    except ValueError:
+                        raise VideoRuleError(k, "not JSON")
                 for k in ("num_frames", "fps", "seed", "num_inference_steps"):
                     if k in data:
                         data[k] = int(data[k])
-            else:
+            elif ctype.startswith("application/json") or not ctype:
                 data = await request.json()
+            else:
+                raise _UnsupportedMedia(ctype)
             req = VideoGenerationRequest.model_validate(data)
             if req.model != s.served:
                 raise LookupError(req.model)
@@ -519,6 +535,8 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
                                      video_service.steps, served_tasks=video_service.tasks)
 
         def _video_error(e):
+            if isinstance(e, _UnsupportedMedia):
+                return _err(415, "use application/json or multipart/form-data")
             if isinstance(e, ValidationError):
                 err = e.errors()[0]
                 loc = ".".join(str(x) for x in err["loc"])
