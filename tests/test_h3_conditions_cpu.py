@@ -278,6 +278,15 @@ def test_first_and_last_frame_requests_over_http(tmp_path):
         clip = c.post("/v1/videos/sync", json=refs)
         assert clip.status_code == 200, clip.text
         assert clip.content not in (track.content, with_ref.content, plain.content)
+        refs["input_references"] = [{"type": "video", "url": _clip(tmp_path, 30),
+                                     "start_time_seconds": 0.25}]      # 24 frames are left
+        later = c.post("/v1/videos/sync", json=refs)
+        assert later.status_code == 200 and later.content != clip.content
+        refs["input_references"][0]["start_time_seconds"] = 1.0        # 6 frames are left
+        assert c.post("/v1/videos/sync", json=refs).status_code == 400
+        refs["input_references"] = [{"type": "audio", "url": _wav(3), "start_time_seconds": 2.0}]
+        gone = c.post("/v1/videos/sync", json=refs)
+        assert gone.status_code == 400 and "ends before" in gone.json()["error"]["message"]
         refs["input_references"] = [{"type": "video", "url": _clip(tmp_path, 9)}]
         short = c.post("/v1/videos/sync", json=refs)
         assert short.status_code == 400 and "17 frames" in short.json()["error"]["message"]

@@ -242,6 +242,11 @@ class VideoService:
         sp = enc.cfg.spatial
         for frame_index, ref in list(p.keyframes) + [(None, r) for r in p.references]:
             url = ref["url"] if isinstance(ref, dict) else ref.url
+            # a clip or a track is read from ``start_time_seconds`` on
+            start = float((ref.get("start_time_seconds") if isinstance(ref, dict)
+                           else ref.start_time_seconds) or 0.0)
+            if start < 0:
+                raise ValueError("input_error: input_references: start_time_seconds is negative")
             if frame_index is None and kind(ref) == "audio":
                 from ..models.h3_audio_encoder import load_wav, padded_samples
                 ac = self.audio_encoder.cfg
@@ -249,7 +254,11 @@ class VideoService:
                     wav = load_wav(url, ac.sample_rate)
                 except (ValueError, OSError) as e:
                     raise ValueError(f"input_error: input_references: {e}")
-                wav = wav[:, :, :int(self.max_seconds * ac.sample_rate)]
+                wav = wav[:, :, int(start * ac.sample_rate):][:, :, :int(self.max_seconds *
+                                                                         ac.sample_rate)]
+                if wav.shape[2] == 0:
+                    raise ValueError("input_error: input_references: the track ends before "
+                                     "start_time_seconds")
                 wav = torch.nn.functional.pad(wav, (0, padded_samples(wav.shape[2], ac.hop) -
                                                     wav.shape[2]))
                 self.h2d_bytes += wav.numel() * 4
@@ -261,8 +270,10 @@ class VideoService:
                     # frames at the clip's rate, cut to the frame rule (17 n + 5, or one clip
                     # of 17); the soundtrack of a reference clip is not read
                     from .video_rules import FPS
+                    skip = int(round(start * FPS))
                     frames, _ = IM.load_video(url, fps=float(FPS),
-                                              max_frames=int(self.max_seconds * FPS))
+                                              max_frames=skip + int(self.max_seconds * FPS))
+                    frames = frames[skip:]
                     n = (len(frames) - 5) // 17
                     keep = 17 * n + 5 if n >= 1 else 17 if len(frames) >= 17 else 0
                     if keep == 0:
