@@ -38,13 +38,19 @@ def test_noise_is_addressable():
     assert abs(float(philox_normal((100000,), 3).std()) - 1.0) < 0.02
 
 
-def _run(ctx=None, steps=2):
+def _run(ctx=None, steps=2, conditions=False):
     cfg = H3Config.tiny()
     model = H3Transformer(cfg, "cpu", torch.float32, ctx).init_random(seed=0)
     den = Denoiser(model, dmd_ladder((999, 500), 10.0), dmd_ladder((999, 500), 3.0))
     g = torch.Generator().manual_seed(5)
     text = torch.randn(9, cfg.text_dim, generator=g)
-    st = den.prepare(seed=42, latent_frames=2, lat_h=4, lat_w=8, n_audio=6, text_features=text)
+    conds = None
+    if conditions:       # a last-frame keyframe, a reference image and a reference track
+        conds = [(-1, torch.randn(cfg.latent_channels, 1, 4, 8, generator=g) * 30),
+                 (None, torch.randn(cfg.latent_channels, 1, 4, 8, generator=g) * 30),
+                 (None, torch.randn(10, cfg.audio_channels, generator=g) * 30)]
+    st = den.prepare(seed=42, latent_frames=2, lat_h=4, lat_w=8, n_audio=6, text_features=text,
+                     conditions=conds)
     den.run(st)
     return st.video, st.audio
 
@@ -64,7 +70,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, q, axis="ulysses"):
+def _worker(rank, world, port, q, axis="ulysses", conditions=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -73,11 +79,34 @@ def _worker(rank, world, port, q, axis="ulysses"):
         ctx = ParallelContext.from_world(ulysses=2, gather=world // 2)
     else:
         ctx = ParallelContext.from_world(**{axis: world})
-    v, a = _run(ctx)
+    v, a = _run(ctx, conditions=conditions)
     if rank == 0:
         q.put((v, a))
     dist.barrier()
     dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("axis", ["ulysses", "gather"])
+def test_sequence_parallel_2_with_conditions_matches_single_rank(axis):
+    """Condition rows (keyframe, reference image, reference track) follow the text rows; split
+    over two ranks the clip is the one a single rank makes, and not the unconditioned one."""
+    v1, a1 = _run(conditions=True)
+    v0, _ = _run()
+    effect = float((v1 - v0).abs().max())
+    assert effect > 0
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, axis, True)) for r in range(2)]
+    for p in procs:
+        p.start()
+    v2, a2 = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    torch.testing.assert_close(v2, v1, atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(a2, a1, atol=2e-4, rtol=2e-4)
+    assert float((v2 - v1).abs().max()) < 0.1 * effect       # the conditions are what is compared
 
 
 @pytest.mark.parametrize("axis", ["ulysses", "gather", "layer"])
