@@ -81,8 +81,10 @@ def serve(args) -> int:
             from .parallel.ulysses import FusedUlysses
             from .server.video_rules import frames_for_seconds
             lf, lh, lw = cfg.latent_shape(frames_for_seconds(15), 1536, 768)
+            # generated rows of the longest clip, then the prompt and the condition rows (two
+            # keyframes and a dozen reference images at full raster fit; larger sets are refused)
             rows_max = (lf * (lh // 2) * (lw // 2) + cfg.audio_rows(frames_for_seconds(15)) +
-                        4096 + 64 * world) // (64 * world) * (64 * world)
+                        16384 + 64 * world) // (64 * world) * (64 * world)
             tr.ulysses = FusedUlysses(ctx, device, rows_max, tr.heads_local, cfg.head_dim)
         vv = VideoVaeDecoder(VideoVaeConfig.tiny() if tiny else VideoVaeConfig(), device, dtype).init_random(1)
         if tiny:

@@ -25,6 +25,7 @@ reference project paths.
 """
 from __future__ import annotations
 
+import logging
 import os
 import pickle
 from dataclasses import asdict, is_dataclass
@@ -170,7 +171,12 @@ def video_follower_loop(service, bus: CommandBus) -> int:
             if c[0] == "shutdown":
                 return done
             if c[0] == "video":
-                service.generate(VideoJob(c[1], VideoPlan(**c[2])))
+                try:
+                    service.generate(VideoJob(c[1], VideoPlan(**c[2])))
+                except (ValueError, OSError) as e:
+                    # the request's own media or size: every rank refuses it at the same point,
+                    # before any exchange, and the leader answers the client
+                    logging.getLogger(__name__).warning("video request refused: %s", e)
                 done += 1
 
 

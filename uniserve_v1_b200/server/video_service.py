@@ -307,6 +307,10 @@ class VideoService:
         self._enter(job, "LatentPrepare")
         n_audio_rows = cfg.audio_rows(p.num_frames)
         st = self.denoiser.prepare(p.seed, lf, lh, lw, n_audio_rows, feats, conditions)
+        cap = getattr(getattr(self.model, "ulysses", None), "rows_all", None)
+        if cap is not None and st.layout.rows > cap:      # the exchange buffers are sized at start
+            raise ValueError(f"input_error: input_references: {st.layout.rows} rows with the "
+                             f"conditions, the deployment's exchange buffers hold {cap}")
         saved = self.latent_pool.get(job.id)
         if saved is not None and saved["video"].shape == st.video.shape:
             st.video.copy_(saved["video"].to(st.video.device))
