@@ -216,6 +216,8 @@ def _clip(tmp_path, frames: int) -> str:
     for _ in range(frames):
         out.write(rng.integers(0, 255, (64, 96, 3), dtype=np.uint8))
     out.release()
+    from uniserve_v1_b200.server import images as IM
+    IM.set_media_directory(tmp_path)
     return "file://" + path
 
 

@@ -70,3 +70,48 @@ def test_handoff_frames_and_head_ranges():
         for o in pre.step():
             ref.extend(o.new_token_ids)
     assert out == ref and len(out) == 3
+
+
+def test_frame_is_explicit_and_validated():
+    """The framed state is a JSON header plus raw tensor bytes: it round-trips, a pickle
+    stream or a truncated body is refused, and fields that do not fit the importing engine
+    (token outside the vocabulary, wrong page size, too many KV heads, more computed
+    positions than tokens, page tensors of the wrong shape) are refused before any page is
+    written."""
+    import dataclasses
+    import pickle
+    import pytest
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.handoff import (Handoff, HandoffError, export_request,
+                                                  import_request)
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    mk = lambda: LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=256, use_graphs=False)
+    a, b = mk(), mk()
+    rid = a.add_request(list(range(5, 40)), SamplingParams(temperature=0.0, max_tokens=6,
+                                                           ignore_eos=True, logit_bias={7: 1.5},
+                                                           stop_token_ids=(3,)))
+    while not a.scheduler.requests[rid].output_ids:
+        a.step()
+    h = export_request(a, rid)
+    blob = h.to_bytes()
+    assert blob[:4] == b"USHO" and b"torch" not in blob[:200]
+    g = Handoff.from_bytes(blob)
+    assert g.prompt_ids == h.prompt_ids and g.num_computed == h.num_computed
+    assert all(torch.equal(x[0], y[0]) and torch.equal(x[1], y[1]) for x, y in zip(g.kv, h.kv) if x)
+    for bad in (pickle.dumps({"request_id": "x"}), blob[:40], b"USHO\x01" + b"\xff" * 8, b""):
+        with pytest.raises(HandoffError):
+            Handoff.from_bytes(bad)
+    free = b.blocks.num_free
+    for change in ({"prompt_ids": [10 ** 9] + g.prompt_ids[1:]}, {"page_size": g.page_size * 2},
+                   {"heads_total": g.heads_total + 64}, {"num_computed": 10 ** 6},
+                   {"head_lo": g.heads_total}, {"kv": [None] * (len(g.kv) + 1)},
+                   {"kv": [(k[:1], v[:1]) if k is not None else None
+                           for k, v in (p or (None, None) for p in g.kv)]}):
+        with pytest.raises(HandoffError):
+            import_request(b, dataclasses.replace(g, **change))
+    assert b.blocks.num_free == free
+    import_request(b, g)                         # the honest state still imports
+    while b.has_work():
+        b.step()

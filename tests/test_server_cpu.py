@@ -365,6 +365,7 @@ def test_video_frames_become_timestamped_images(tmp_path):
     for i in range(16):
         wr.write(np.roll(base, 4 * i, axis=1))
     wr.release()
+    IM.set_media_directory(tmp_path)
     frames, secs = IM.load_video("file://" + path, fps=2.0)
     assert frames.shape == (4, 64, 96, 3) and secs == [0.0, 0.5, 1.0, 1.5]
     rows, grid = IM.preprocess_video(frames)
@@ -398,14 +399,34 @@ def test_chat_with_a_video_on_the_hybrid_family(tmp_path):
         wr.write(np.roll(base, 4 * i, axis=1))
     wr.release()
     eng, model, tower = _hybrid_mm_engine()
-    pkg = Package.parse('model = "random:tiny"\nserved_model_name = "hybrid"\n')
+    pkg = Package.parse('model = "random:tiny"\nserved_model_name = "hybrid"\n'
+                        f'[media_config]\ndirectory = "{tmp_path}"\n')
     app = create_app(package=pkg, engine=eng, tokenizer=ByteTokenizer(1024, 1023),
                      served_model_name="hybrid")
     body = {"model": "hybrid", "max_tokens": 4, "temperature": 0, "ignore_eos": True,
             "messages": [{"role": "user", "content": [
                 {"type": "text", "text": "what happens? "},
                 {"type": "video_url", "video_url": {"url": "file://" + path}}]}]}
+
+    def with_url(url, kind="video_url"):
+        return dict(body, messages=[{"role": "user", "content": [
+            {"type": "text", "text": "what happens? "}, {"type": kind, kind: {"url": url}}]}])
     with TestClient(app) as c:
+        # file:// is read below the media directory only: no traversal, no symbolic link out
+        # of it, no host part, and a missing file is the request's own error (400, not 500)
+        import os
+        outside = tmp_path.parent / "outside.png"
+        outside.write_bytes(b"secret")
+        os.symlink(outside, tmp_path / "link.png")
+        for url, kind in ((f"file://{tmp_path}/../outside.png", "image_url"),
+                          (f"file://{tmp_path}/link.png", "image_url"),
+                          ("file:///etc/passwd", "image_url"),
+                          (f"file://otherhost{path}", "video_url"),
+                          (f"file://{tmp_path}/missing.avi", "video_url"),
+                          (f"file://{tmp_path}/missing.png", "image_url")):
+            bad = c.post("/v1/chat/completions", json=with_url(url, kind))
+            assert bad.status_code == 400, (url, bad.text)
+            assert bad.json()["error"]["type"] in ("input_error", "invalid_request_error")
         r = c.post("/v1/chat/completions", json=body)
         assert r.status_code == 200, r.text
         rid = next(iter(eng.requests))
@@ -416,3 +437,10 @@ def test_chat_with_a_video_on_the_hybrid_family(tmp_path):
         grids = [(1, gh, gw)] * gt
         want = Qwen35Multimodal(model, tower).generate(req.prompt_ids, rows, grids, 4)
         assert req.output_ids == want and r.json()["usage"]["completion_tokens"] == 4
+    # without a media directory every file:// URL is refused
+    bare = create_app(package=Package.parse('model = "random:tiny"\nserved_model_name = "hybrid"\n'),
+                      engine=_hybrid_mm_engine()[0], tokenizer=ByteTokenizer(1024, 1023),
+                      served_model_name="hybrid")
+    with TestClient(bare) as c:
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 400 and "media_config.directory" in r.text

@@ -238,7 +238,7 @@ def test_block_manager_bounded_exhaustive_check_and_mutants():
         assert explore(mk(cls), pages=5, depth=4, n_keys=2)["violation"], name
 
 
-def _start_chat_server():
+def _start_chat_server(role="mixed", key=None):
     import uvicorn
     from uniserve_v1_b200.config.policy import Package
     from uniserve_v1_b200.engine.engine import LLMEngine
@@ -249,7 +249,7 @@ def _start_chat_server():
     eng = LLMEngine(model, num_pages=256, max_num_seqs=8, max_model_len=512, use_graphs=False)
     pkg = Package.parse('model = "random:tiny"\nserved_model_name = "tiny"\n')
     app = create_app(package=pkg, engine=eng, tokenizer=ByteTokenizer(1024, 1023),
-                     served_model_name="tiny")
+                     served_model_name="tiny", role=role, internal_key=key)
     port = _free_port()
     server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
     th = threading.Thread(target=server.run, daemon=True)
@@ -271,10 +271,11 @@ def test_router_disaggregates_prefill_and_decode(live_server):
     import urllib.request
     import uvicorn
     from uniserve_v1_b200.server.router import create_router_app
-    pre_url, pre_srv, pre_th, pre_eng = _start_chat_server()
-    dec_url, dec_srv, dec_th, dec_eng = _start_chat_server()
+    pre_url, pre_srv, pre_th, pre_eng = _start_chat_server("prefill", "k3y")
+    dec_url, dec_srv, dec_th, dec_eng = _start_chat_server("decode", "k3y")
     port = _free_port()
-    app = create_router_app([], prefill_urls=[pre_url], decode_urls=[dec_url])
+    app = create_router_app([], prefill_urls=[pre_url], decode_urls=[dec_url],
+                            internal_key="k3y")
     server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
     t = threading.Thread(target=server.run, daemon=True)
     t.start()
@@ -316,6 +317,36 @@ def test_router_disaggregates_prefill_and_decode(live_server):
         assert one["usage"]["completion_tokens"] == 1
         with urllib.request.urlopen(base + "/v1/models", timeout=10) as r:
             assert json.loads(r.read())["data"][0]["id"] == "tiny"
+
+        # the internal routes: absent on a mixed replica, closed without the key, and a
+        # pickle stream (what an attacker would send to get code run) is refused as a frame
+        import base64
+        import pickle
+        import urllib.error
+
+        class Boom:
+            def __reduce__(self):
+                return (os.system, ("touch /tmp/us_handoff_pwned",))
+        import os
+        evil = base64.b64encode(pickle.dumps(Boom())).decode()
+        chat = {"model": "tiny", "messages": [{"role": "user", "content": "x"}], "max_tokens": 2}
+
+        def status(url, body, key=None):
+            hdr = {"Content-Type": "application/json"}
+            if key:
+                hdr["x-uniserve-internal-key"] = key
+            rq = urllib.request.Request(url, data=json.dumps(body).encode(), headers=hdr)
+            try:
+                with urllib.request.urlopen(rq, timeout=30) as r:
+                    return r.status, r.read().decode()
+            except urllib.error.HTTPError as e:
+                return e.code, e.read().decode()
+        assert status(live_server + "/internal/decode", {"request": chat, "handoff": evil})[0] == 404
+        assert status(dec_url + "/internal/decode", {"request": chat, "handoff": evil})[0] == 401
+        assert status(pre_url + "/internal/prefill", chat)[0] == 401
+        code, text = status(dec_url + "/internal/decode", {"request": chat, "handoff": evil}, "k3y")
+        assert code == 400 and "hand-off" in text
+        assert not os.path.exists("/tmp/us_handoff_pwned")
     finally:
         for srv, th_ in ((server, t), (pre_srv, pre_th), (dec_srv, dec_th)):
             srv.should_exit = True

@@ -226,8 +226,12 @@ def serve(args) -> int:
         if k_draft > 0 and bus is None and directory and ld.has("mtp.fc.weight"):
             from .models.qwen3_mtp import MtpDrafter, MtpHead     # the checkpoint's own drafter
             drafter = MtpDrafter(MtpHead(model).load_state(ld), k=k_draft)
+        # prefill / decode role of this replica: `--role`, or `replicas.<id>.role` of the
+        # package for `--replica-id`; the internal routes need UNISERVE_INTERNAL_KEY
+        role = args.role or (pkg.replicas[args.replica_id].role if args.replica_id else "mixed")
         app = create_app(package=pkg, engine=engine, tokenizer=tok, served_model_name=name,
-                         engine_factory=make_engine if bus is None else None, drafter=drafter)
+                         engine_factory=make_engine if bus is None else None, drafter=drafter,
+                         role=role, internal_key=os.environ.get("UNISERVE_INTERNAL_KEY"))
     if args.ready_fd is not None:
         os.write(args.ready_fd, json.dumps({"state": "listening", "host": pkg.admin_config.host,
                                             "port": pkg.admin_config.port}).encode() + b"\n")
@@ -280,6 +284,10 @@ def main(argv=None) -> int:
     s.add_argument("--ready-fd", type=int, default=None)
     s.add_argument("--log-level", default=None)
     s.add_argument("--log-level-http", default=None)
+    s.add_argument("--role", choices=["mixed", "prefill", "decode"], default=None,
+                   help="disaggregation role of this replica (default: the package's "
+                        "replicas.<id>.role for --replica-id, else mixed)")
+    s.add_argument("--replica-id", default=None, help="key of this replica in [replicas]")
     b = sub.add_parser("build", help="compile the native libraries for sm_100a")
     b.add_argument("--force", action="store_true")
     l = sub.add_parser("layout", help="print the resolved device layout of a package")
@@ -295,6 +303,8 @@ def main(argv=None) -> int:
     r.add_argument("--prefill", action="append", default=[], help="base URL of a prefill replica")
     r.add_argument("--decode", action="append", default=[], help="base URL of a decode replica")
     r.add_argument("--program", help="routing program: a file that defines route(request, replicas)")
+    r.add_argument("--internal-key", default=os.environ.get("UNISERVE_INTERNAL_KEY"),
+                   help="key presented to prefill / decode replicas on their internal routes")
     a = ap.parse_args(argv)
     if a.cmd == "serve":
         return serve(a)
@@ -311,7 +321,8 @@ def main(argv=None) -> int:
             from .engine.program import ProgramHost
             program = ProgramHost(open(a.program).read(), "routing", call_fuel=1_000_000)
         uvicorn.run(create_router_app(a.replica, prefill_urls=a.prefill or None,
-                                      decode_urls=a.decode or None, program=program),
+                                      decode_urls=a.decode or None, program=program,
+                                      internal_key=a.internal_key),
                     host=host or "127.0.0.1", port=int(port), log_level="warning")
         return 0
     if a.cmd == "build":

@@ -220,6 +220,8 @@ class LoggingConfig:
 class MediaConfig:
     max_request_bytes: ByteSize = opt(ByteSize(256 << 20), "daemon")
     allow_private: bool = opt(False, "daemon", "allow media URLs on private networks")
+    directory: Optional[str] = opt(None, "daemon", "the only directory file:// media are read "
+                                                   "from; unset refuses file:// URLs")
     fetch_timeout: Duration = opt(Duration(30.0), "daemon")
     max_redirects: int = opt(5, "daemon")
     job_retention: Duration = opt(Duration(3600.0), "daemon")

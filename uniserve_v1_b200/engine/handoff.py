@@ -19,13 +19,25 @@ crates/storage/src/runtime.rs:394-402 (reference project paths).
 """
 from __future__ import annotations
 
-import io
+import json
+import struct
 from dataclasses import asdict, dataclass, field, is_dataclass
 from typing import Optional
 
 import torch
 
 from .types import SamplingParams
+
+MAGIC = b"USHO\x01"
+MAX_HEADER = 64 << 20
+MAX_LAYERS = 4096
+_DTYPES = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16,
+           "float8_e4m3fn": torch.float8_e4m3fn, "uint8": torch.uint8}
+_DTYPE_NAMES = {v: k for k, v in _DTYPES.items()}
+
+
+class HandoffError(ValueError):
+    """A framed request state that is malformed or does not fit the importing engine."""
 
 
 @dataclass
@@ -46,15 +58,134 @@ class Handoff:
         return sum(k.numel() * k.element_size() * 2 for k, _ in (p for p in self.kv if p))
 
     def to_bytes(self) -> bytes:
-        buf = io.BytesIO()
+        """Explicit framing, nothing executable: ``MAGIC | u32 header length | JSON header |
+        raw tensor bytes``.  The header carries every scalar field and, per layer, the dtype,
+        shape and byte range of the K and V page tensors."""
+        tensors, blobs, off = [], [], 0
+        for pair in self.kv:
+            if pair is None:
+                tensors.append(None)
+                continue
+            entry = []
+            for t in pair:
+                t = t.detach().cpu().contiguous()
+                raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+                entry.append({"dtype": _DTYPE_NAMES[t.dtype], "shape": list(t.shape),
+                              "offset": off, "nbytes": len(raw)})
+                blobs.append(raw)
+                off += len(raw)
+            tensors.append(entry)
         d = asdict(self)
-        d["kv"] = [None if p is None else (p[0].cpu(), p[1].cpu()) for p in self.kv]
-        torch.save(d, buf)
-        return buf.getvalue()
+        d["kv"] = tensors
+        head = json.dumps(d, separators=(",", ":")).encode()
+        return b"".join([MAGIC, struct.pack("<I", len(head)), head, *blobs])
 
     @classmethod
     def from_bytes(cls, blob: bytes) -> "Handoff":
-        return cls(**torch.load(io.BytesIO(blob), weights_only=False))
+        """Parses the framing of ``to_bytes``; raises ``HandoffError`` on anything else (a
+        pickle stream, a truncated body, ranges outside the body, unknown dtypes)."""
+        blob = bytes(blob)
+        if len(blob) < len(MAGIC) + 4 or blob[:len(MAGIC)] != MAGIC:
+            raise HandoffError("not a hand-off frame")
+        (n,) = struct.unpack_from("<I", blob, len(MAGIC))
+        start = len(MAGIC) + 4
+        if n > MAX_HEADER or start + n > len(blob):
+            raise HandoffError("header length outside the body")
+        try:
+            d = json.loads(blob[start:start + n].decode())
+        except (UnicodeDecodeError, ValueError) as e:
+            raise HandoffError(f"header is not JSON: {e}") from None
+        if not isinstance(d, dict) or set(d) != set(cls.__dataclass_fields__):
+            raise HandoffError("header fields do not match the hand-off record")
+        body = memoryview(blob)[start + n:]
+        kv = []
+        if not isinstance(d["kv"], list) or len(d["kv"]) > MAX_LAYERS:
+            raise HandoffError("kv: not a list of layers")
+        for entry in d["kv"]:
+            if entry is None:
+                kv.append(None)
+                continue
+            if not isinstance(entry, list) or len(entry) != 2:
+                raise HandoffError("kv: a layer holds one K and one V tensor")
+            pair = []
+            for spec in entry:
+                try:
+                    dt = _DTYPES[spec["dtype"]]
+                    shape = [int(x) for x in spec["shape"]]
+                    off, nb = int(spec["offset"]), int(spec["nbytes"])
+                except (KeyError, TypeError, ValueError):
+                    raise HandoffError("kv: malformed tensor record") from None
+                numel = 1
+                for x in shape:
+                    if x < 0:
+                        raise HandoffError("kv: negative extent")
+                    numel *= x
+                if len(shape) != 4 or off < 0 or nb != numel * dt.itemsize or off + nb > len(body):
+                    raise HandoffError("kv: tensor bytes outside the body")
+                t = torch.frombuffer(bytearray(body[off:off + nb]), dtype=dt) if nb else \
+                    torch.empty(0, dtype=dt)
+                pair.append(t.reshape(shape))
+            kv.append(tuple(pair))
+        d["kv"] = kv
+        h = cls(**d)
+        h.check_fields()
+        return h
+
+    def check_fields(self) -> None:
+        """Type and range checks that need no model (``validate_for`` adds the importer's)."""
+        def ints(xs, what):
+            if not isinstance(xs, list) or not all(isinstance(x, int) and not isinstance(x, bool)
+                                                   and x >= 0 for x in xs):
+                raise HandoffError(f"{what}: a list of non-negative token ids")
+        if not isinstance(self.request_id, str) or len(self.request_id) > 256:
+            raise HandoffError("request_id: a short string")
+        ints(self.prompt_ids, "prompt_ids")
+        ints(self.output_ids, "output_ids")
+        if not isinstance(self.params, dict) or \
+                not set(self.params) <= set(SamplingParams.__dataclass_fields__):
+            raise HandoffError("params: unknown sampling field")
+        for name in ("priority", "num_computed", "page_size", "head_lo", "heads_total"):
+            v = getattr(self, name)
+            if not isinstance(v, int) or isinstance(v, bool):
+                raise HandoffError(f"{name}: an integer")
+        if self.cache_salt is not None and not isinstance(self.cache_salt, str):
+            raise HandoffError("cache_salt: a string")
+        if not self.prompt_ids or self.page_size <= 0 or self.num_computed < 0 or \
+                self.num_computed > len(self.prompt_ids) + len(self.output_ids):
+            raise HandoffError("num_computed exceeds the tokens of the request")
+
+    def validate_for(self, engine) -> None:
+        """Checks every field against the importing engine's model and cache before a page
+        is written: vocabulary range, KV-head range, page size, page count and tensor shapes."""
+        self.check_fields()
+        runner, model = engine.runner, engine.model
+        vocab = model.cfg.vocab_size
+        if any(t >= vocab for t in self.prompt_ids) or any(t >= vocab for t in self.output_ids):
+            raise HandoffError("token id outside the vocabulary")
+        if self.page_size != runner.page_size:
+            raise HandoffError(f"page size {self.page_size} differs from the importer's "
+                               f"{runner.page_size}")
+        if self.heads_total != model.cfg.num_key_value_heads:
+            raise HandoffError("heads_total differs from the model's KV heads")
+        max_len = getattr(getattr(engine, "config", None), "max_model_len", None)
+        if max_len is not None and len(self.prompt_ids) + len(self.output_ids) >= max_len:
+            raise HandoffError("the request is longer than the importer's context")
+        if len(self.kv) != len(runner.kv_caches):
+            raise HandoffError("kv: layer count differs from the importer's")
+        n = (self.num_computed + self.page_size - 1) // self.page_size
+        for pair, mine in zip(self.kv, runner.kv_caches):
+            if pair is None:
+                continue
+            if mine is None or mine[0] is None:
+                raise HandoffError("kv: pages for a layer this rank does not hold")
+            for t, m in zip(pair, mine):
+                heads = t.shape[2]
+                if t.shape[0] != n or t.shape[1] != self.page_size or t.shape[3] != m.shape[3] \
+                        or heads < 1 or self.head_lo < 0 \
+                        or self.head_lo + heads > self.heads_total:
+                    raise HandoffError("kv: page tensor shape does not fit the request")
+                if not t.dtype.is_floating_point:
+                    raise HandoffError("kv: pages are floating point")
 
 
 def export_request(engine, request_id: str, release: bool = True) -> Handoff:
@@ -89,6 +220,16 @@ def export_request(engine, request_id: str, release: bool = True) -> Handoff:
     return h
 
 
+def _params_of(d: dict) -> SamplingParams:
+    """Sampling parameters back from their JSON form (token-id keys and tuples restored)."""
+    d = dict(d)
+    if d.get("logit_bias"):
+        d["logit_bias"] = {int(k): float(v) for k, v in d["logit_bias"].items()}
+    if d.get("stop_token_ids") is not None:
+        d["stop_token_ids"] = tuple(int(x) for x in d["stop_token_ids"])
+    return SamplingParams(**d)
+
+
 def reshard_heads(shards: list, want_lo: int, want_n: int) -> torch.Tensor:
     """``shards``: (head_lo, tensor [pages, page, heads, D]) from the exporting ranks;
     returns heads [want_lo, want_lo + want_n) in order."""
@@ -108,7 +249,8 @@ def import_request(engine, handoffs) -> str:
     hs = handoffs if isinstance(handoffs, (list, tuple)) else [handoffs]
     h = hs[0]
     sch, runner, model = engine.scheduler, engine.runner, engine.model
-    assert h.page_size == runner.page_size, "both sides use the same page size"
+    for x in hs:
+        x.validate_for(engine)
     n = (h.num_computed + h.page_size - 1) // h.page_size
     pages = engine.blocks.allocate(n)
     if pages is None:
@@ -122,7 +264,7 @@ def import_request(engine, handoffs) -> str:
             shards = [(x.head_lo, x.kv[layer][which]) for x in hs if x.kv[layer] is not None]
             t = reshard_heads(shards, want_lo, pair[which].shape[2])
             pair[which].index_copy_(0, idx, t.to(device=runner.device, dtype=pair[which].dtype))
-    rid = engine.add_request(h.prompt_ids, SamplingParams(**h.params), request_id=h.request_id,
+    rid = engine.add_request(h.prompt_ids, _params_of(h.params), request_id=h.request_id,
                              priority=h.priority, cache_salt=h.cache_salt,
                              output_ids=h.output_ids)
     req = sch.requests[rid]

@@ -184,8 +184,8 @@ def load_wav(url: str, sample_rate: int) -> torch.Tensor:
             raise ValueError("data URLs must be base64-encoded")
         raw = base64.b64decode(payload, validate=True)
     elif url.startswith("file://"):
-        with open(url[7:], "rb") as f:
-            raw = f.read()
+        from ..server.images import read_file_url      # media-directory rule of the deployment
+        raw = read_file_url(url)
     else:
         raise ValueError("audio URLs must be data: or file:// URLs; remote URLs are not fetched")
     try:

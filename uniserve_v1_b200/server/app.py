@@ -210,12 +210,23 @@ class AppState:
 
 def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None,
                served_model_name: str = "model", video_service=None, generation_defaults=None,
-               reasoning: bool = True, engine_factory=None, drafter=None) -> FastAPI:
+               reasoning: bool = True, engine_factory=None, drafter=None,
+               role: str = "mixed", internal_key: Optional[str] = None) -> FastAPI:
     """Builds the application.  ``engine`` (an LLMEngine) registers the chat route;
-    ``video_service`` registers the video routes and ``/v1/capabilities``."""
+    ``video_service`` registers the video routes and ``/v1/capabilities``.  ``role`` =
+    ``prefill`` / ``decode`` also mounts ``/internal/prefill`` / ``/internal/decode`` for a
+    disaggregating router; those routes require ``internal_key`` (header
+    ``x-uniserve-internal-key``) and exist on no other deployment."""
+    if role not in ("mixed", "prefill", "decode"):
+        raise ConfigError("role", f"unknown role {role!r}")
+    if role != "mixed" and not internal_key:
+        raise ConfigError("role", "a prefill or decode replica needs an internal key "
+                                  "(the router presents it on /internal/*)")
     app = FastAPI(title="uniserve-b200", docs_url=None, redoc_url=None, openapi_url=None)
     s = AppState()
     s.package = package or Package.parse(f'model = "local/{served_model_name}"\n')
+    from . import images as _images
+    _images.set_media_directory(s.package.media_config.directory)
     s.served = s.package.served_model_name or served_model_name
     s.tokenizer = tokenizer
     s.template = ChatTemplate(getattr(tokenizer, "chat_template", None)) if tokenizer else None
@@ -328,24 +339,40 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
 
     # ------------------------------------------------------------------- chat --
     if engine is not None:
-        @app.post("/internal/prefill")
-        async def chat_prefill(request: Request):
-            """Prefill role: the chat request runs to its first token; the answer is the
-            request's framed state (``application/octet-stream``) for a decode replica, or
-            the ordinary completion when the first token already ended it."""
-            return await _chat(request, role="prefill")
+        def _internal_ok(request: Request) -> bool:
+            import hmac
+            got = request.headers.get("x-uniserve-internal-key", "")
+            return hmac.compare_digest(got.encode(), internal_key.encode())
 
-        @app.post("/internal/decode")
-        async def chat_decode(request: Request):
-            """Decode role: body {"request": <chat request>, "handoff": <base64 state>}."""
-            import base64
-            from ..engine.handoff import Handoff
-            try:
-                body = await request.json()
-                h = Handoff.from_bytes(base64.b64decode(body["handoff"]))
-            except Exception as e:
-                return _err(400, f"hand-off body: {e}")
-            return await _chat(request, body=body["request"], handoff=h)
+        if role == "prefill":
+            @app.post("/internal/prefill")
+            async def chat_prefill(request: Request):
+                """Prefill role: the chat request runs to its first token; the answer is the
+                request's framed state (``application/octet-stream``) for a decode replica, or
+                the ordinary completion when the first token already ended it."""
+                if not _internal_ok(request):
+                    return _err(401, "invalid or missing internal key", "authentication_error")
+                return await _chat(request, role="prefill")
+
+        if role == "decode":
+            @app.post("/internal/decode")
+            async def chat_decode(request: Request):
+                """Decode role: body {"request": <chat request>, "handoff": <base64 state>}.
+                The state is the explicit frame of ``Handoff.to_bytes`` (a JSON header and raw
+                tensor bytes); every field is checked against this engine before a page is
+                written."""
+                import base64
+                from ..engine.handoff import Handoff
+                if not _internal_ok(request):
+                    return _err(401, "invalid or missing internal key", "authentication_error")
+                try:
+                    body = await request.json()
+                    h = Handoff.from_bytes(base64.b64decode(body["handoff"], validate=True))
+                    h.validate_for(s.engine)
+                    chat_body = body["request"]
+                except Exception as e:
+                    return _err(400, f"hand-off body: {e}")
+                return await _chat(request, body=chat_body, handoff=h)
 
         @app.post("/v1/chat/completions")
         async def chat(request: Request):
@@ -383,8 +410,9 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
                 mm = getattr(s.engine, "mm", None)
                 if mm is None:
                     return _err(400, "this deployment does not take images", param="messages")
-                try:
-                    vc = mm.tower.cfg
+                vc = mm.tower.cfg
+
+                def decode_media(prompt):
                     pre = []
                     for kind, u in urls:
                         if kind == "image":
@@ -399,8 +427,12 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
                         pre.extend((rows[i * per:(i + 1) * per], (1, gh, gw)) for i in range(gt))
                         prompt = prompt.replace("<|vision_start|><|video_pad|><|vision_end|>",
                                                 IM.video_prompt(secs, vc.temporal_patch_size), 1)
-                except ValueError as e:
-                    return _err(400, str(e), param="messages")
+                    return pre, prompt
+                try:
+                    # file reads and decoding leave the event loop
+                    pre, prompt = await asyncio.to_thread(decode_media, prompt)
+                except (ValueError, OSError) as e:
+                    return _err(400, str(e), type_="input_error", param="messages")
                 grids = [g for _, g in pre]
                 img_tok = s.engine.model.cfg.image_token_id
                 ids = []

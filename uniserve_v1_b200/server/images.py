@@ -3,6 +3,11 @@ rows the vision tower reads.
 
 ``image_url`` content parts carry ``data:`` URLs (base64) or ``file://`` paths; remote URLs
 are refused (a serving process does not fetch from the network on a client's behalf).
+``file://`` is read only below the deployment's media directory
+(``media_config.directory``): the URL names an absolute path without a host part, the
+canonical path (symbolic links resolved) must lie under the canonical directory, and with
+no directory configured every ``file://`` URL is refused (api/input/media.rs of the
+reference project reads local media under the same rule).
 Preprocessing follows the Qwen-VL image processor: both sides become multiples of
 ``patch * merge`` with the pixel count clamped to [min_pixels, max_pixels] at (nearly)
 the same aspect ratio, values are scaled to [0, 1] and normalised with mean = std = 0.5,
@@ -19,9 +24,56 @@ from __future__ import annotations
 import base64
 import io
 import math
+import os
 
 import numpy as np
 import torch
+
+
+_MEDIA_DIRECTORY = None          # canonical path, or None: file:// URLs are refused
+
+
+def set_media_directory(path) -> None:
+    """The one directory ``file://`` media may be read from (None closes ``file://``)."""
+    global _MEDIA_DIRECTORY
+    _MEDIA_DIRECTORY = os.path.realpath(str(path)) if path else None
+
+
+def media_directory():
+    return _MEDIA_DIRECTORY
+
+
+def resolve_file_url(url: str) -> str:
+    """``file:///abs/path`` -> the canonical path, if it lies below the media directory.
+    Raises ValueError otherwise (no directory configured, a host part, a relative path,
+    ``..`` or a symbolic link that leaves the directory)."""
+    from urllib.parse import unquote, urlparse
+    if _MEDIA_DIRECTORY is None:
+        raise ValueError("file:// URLs are not served: the deployment sets no "
+                         "media_config.directory")
+    u = urlparse(url)
+    if u.scheme != "file" or u.netloc not in ("", "localhost") or u.query or u.fragment:
+        raise ValueError("file:// URLs name a local absolute path and nothing else")
+    path = unquote(u.path)
+    if not path.startswith("/") or "\x00" in path:
+        raise ValueError("file:// URLs name an absolute path")
+    real = os.path.realpath(path)
+    if os.path.commonpath([real, _MEDIA_DIRECTORY]) != _MEDIA_DIRECTORY:
+        raise ValueError("the file lies outside the deployment's media directory")
+    return real
+
+
+def read_file_url(url: str, limit: int = 256 << 20) -> bytes:
+    """Bytes of a ``file://`` medium (``resolve_file_url`` rules; I/O errors become
+    ValueError so that a request naming a missing file is an input error)."""
+    real = resolve_file_url(url)
+    try:
+        if os.path.getsize(real) > limit:
+            raise ValueError("the file is larger than the deployment accepts")
+        with open(real, "rb") as f:
+            return f.read()
+    except OSError as e:
+        raise ValueError(f"cannot read the file: {e.strerror or e}")
 
 
 def load_image(url: str) -> np.ndarray:
@@ -33,8 +85,7 @@ def load_image(url: str) -> np.ndarray:
             raise ValueError("data URLs must be base64-encoded")
         raw = base64.b64decode(payload, validate=True)
     elif url.startswith("file://"):
-        with open(url[7:], "rb") as f:
-            raw = f.read()
+        raw = read_file_url(url)
     else:
         raise ValueError("image URLs must be data: or file:// URLs; remote URLs are not fetched")
     try:
@@ -120,7 +171,6 @@ def collect_media(messages: list) -> list:
 def load_video(url: str, fps: float = 2.0, max_frames: int = 64):
     """Decodes a ``file://`` (or base64 ``data:``) video and samples it at ``fps``: returns
     (frames uint8 [F, H, W, 3] with F even, seconds of each sampled frame)."""
-    import os
     import tempfile
 
     import cv2
@@ -134,7 +184,9 @@ def load_video(url: str, fps: float = 2.0, max_frames: int = 64):
             f.write(base64.b64decode(payload, validate=True))
         path = tmp
     elif url.startswith("file://"):
-        path = url[7:]
+        path = resolve_file_url(url)
+        if not os.path.isfile(path):
+            raise ValueError("cannot read the file: no such file")
     else:
         raise ValueError("video URLs must be data: or file:// URLs; remote URLs are not fetched")
     try:

@@ -87,11 +87,13 @@ class ReplicaRouter:
 
 def create_router_app(urls: list, api_key: Optional[str] = None,
                       prefill_urls: Optional[list] = None,
-                      decode_urls: Optional[list] = None, program=None) -> FastAPI:
+                      decode_urls: Optional[list] = None, program=None,
+                      internal_key: Optional[str] = None) -> FastAPI:
     """``urls``: replicas of role ``mixed``.  With ``prefill_urls`` and ``decode_urls`` chat
     requests are disaggregated: a prefill replica computes the prompt and the first token
     (``/internal/prefill``), its answer - the request's framed state - goes to a decode
-    replica (``/internal/decode``), whose stream is relayed to the client."""
+    replica (``/internal/decode``), whose stream is relayed to the client.  ``internal_key``
+    is presented on both internal routes; the replicas refuse them without it."""
     import aiohttp
     router = ReplicaRouter(urls or (list(prefill_urls or []) + list(decode_urls or [])),
                            program=program)
@@ -115,6 +117,9 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
     def _headers(req: Request) -> dict:
         keep = ("authorization", "content-type", "accept")
         return {k: v for k, v in req.headers.items() if k.lower() in keep}
+
+    def _internal(req: Request) -> dict:
+        return dict(_headers(req), **{"x-uniserve-internal-key": internal_key or ""})
 
     async def forward(req: Request, path: str):
         body = await req.body()
@@ -168,7 +173,7 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
         p = pre.pick()
         p.in_flight += 1
         try:
-            async with s.post(p.url + "/internal/prefill", data=body, headers=_headers(req)) as up:
+            async with s.post(p.url + "/internal/prefill", data=body, headers=_internal(req)) as up:
                 blob, status = await up.read(), up.status
                 ctype = up.headers.get("content-type", "")
         except aiohttp.ClientConnectionError:
@@ -185,7 +190,7 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
         d.in_flight += 1
         payload = json.dumps({"request": json.loads(body),
                               "handoff": base64.b64encode(blob).decode()})
-        hdr = dict(_headers(req), **{"content-type": "application/json"})
+        hdr = dict(_internal(req), **{"content-type": "application/json"})
         try:
             up = await s.post(d.url + "/internal/decode", data=payload, headers=hdr)
         except aiohttp.ClientConnectionError:
