@@ -97,6 +97,58 @@ def test_host_kv_tier_brings_back_evicted_prefix_pages():
     assert cached1 == 64 and st1["host_hits"] >= 4 and st1["host_offloads"] >= 4
 
 
+def test_host_slot_with_pending_fetch_is_not_recycled_by_offloads_of_the_same_step():
+    """A tiny host tier: a prefix match hands out host slots, and the device pages it then
+    allocates evict cached pages whose offloads would recycle exactly those slots.  The
+    matched slots stay pinned until the copies are handed over, so after the moves every
+    fetched device page holds the content of its own key; offloads with no unpinned slot
+    are dropped, and no slot appears twice in one offload batch."""
+    import numpy as np
+    from uniserve_v1_b200.engine.block_manager import BlockManager
+    bm = BlockManager(num_pages=5, page_size=4)          # 4 usable device pages
+    bm.enable_host_tier(2)
+    key = lambda i: (1000 + i, 7)
+    device = {}                                          # page -> content tag
+    host = {}                                            # slot -> content tag
+
+    def moves():
+        off, fet = bm.take_moves()
+        assert len({s for _, s in off}) == len(off)
+        for page, slot in off:
+            host[slot] = device[page]
+        for slot, page in fet:
+            device[page] = host[slot]
+
+    # contents 0..3 committed on the device, released (cached, unreferenced)
+    pages = bm.allocate(4)
+    for i, pg in enumerate(pages):
+        device[pg] = i
+        assert bm.commit(pg, key(i)) == pg
+    bm.release(pages)
+    # two fresh pages push contents 0 and 1 to the two host slots
+    a = bm.allocate(2)
+    moves()
+    for pg in a:
+        device[pg] = "x"
+    assert sorted(host.values()) == [0, 1]
+    bm.release(a)                                        # unkeyed: plain free pages
+    keys = np.array([key(0), key(1)], dtype=np.uint64)
+    # take every free page so that the fetch below must evict cached pages 2 and 3,
+    # whose offloads want host slots while both slots have a pending fetch
+    hold = bm.allocate(2)
+    got = bm.fetch_prefix(keys, 0, 2)
+    assert len(got) == 2
+    moves()
+    assert [device[pg] for pg in got] == [0, 1]          # not the evicted pages' content
+    assert bm.host_stats()["host_used"] == 2
+    bm.release(hold + got)
+    # the pins are gone: later evictions use the slots again
+    more = bm.allocate(4)
+    moves()
+    assert sorted(host.values()) == [0, 1]               # contents 0, 1 offloaded again
+    bm.release(more)
+
+
 def test_speculative_steps_reproduce_plain_decoding():
     """Verification keeps the agreed prefix plus one model token: whatever the drafter
     proposes, the output equals step-by-step greedy decoding; an oracle drafter advances

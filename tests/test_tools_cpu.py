@@ -238,6 +238,21 @@ def test_block_manager_bounded_exhaustive_check_and_mutants():
         assert explore(mk(cls), pages=5, depth=4, n_keys=2)["violation"], name
 
 
+def test_host_tier_contents_enumerated_and_unpinned_mutant_caught():
+    """Page contents through the host tier, enumerated: whatever the order of allocations,
+    commits, fetches and steps (also from a state where the host tier is full and every fetch
+    must evict), a fetched page holds what was committed under its key; a manager that does
+    not pin matched host slots is flagged."""
+    from uniserve_v1_b200.engine.block_manager import BlockManager
+    from uniserve_v1_b200.tools.verify import HOST_FULL, explore_host_tier, host_mutant
+    mk = lambda cls: (lambda pages: cls(pages, page_size=4))
+    for slots in (1, 2):
+        r = explore_host_tier(mk(BlockManager), 4, slots, 4, 2)
+        assert r["violation"] is None and r["sequences"] > 1000
+    assert explore_host_tier(mk(BlockManager), 4, 1, 4, 2, HOST_FULL)["violation"] is None
+    assert explore_host_tier(mk(host_mutant(BlockManager)), 4, 1, 3, 2, HOST_FULL)["violation"]
+
+
 def _start_chat_server(role="mixed", key=None):
     import uvicorn
     from uniserve_v1_b200.config.policy import Package

@@ -124,8 +124,11 @@ struct Pool {
   std::vector<Key> host_key;
   std::list<int> host_lru;
   std::vector<std::list<int>::iterator> host_pos;
+  // A slot matched for a fetch is pinned (out of `host_lru`) until its host -> device copy
+  // has been handed to the caller: an offload decided in between must not recycle it.
+  std::vector<int> host_pins;
   std::vector<std::pair<int, int>> offloads;   // (device page, host slot) decided by alloc
-  uint64_t host_hits = 0, host_offloads = 0;
+  uint64_t host_hits = 0, host_offloads = 0, host_dropped = 0;
   std::mutex mu;
 };
 
@@ -138,10 +141,13 @@ void offload_page(Pool* p, int page) {
   if (!p->host_free.empty()) {
     slot = p->host_free.back();
     p->host_free.pop_back();
-  } else {
+  } else if (!p->host_lru.empty()) {
     slot = p->host_lru.front();
     p->host_lru.pop_front();
     p->host_cached.erase(p->host_key[slot]);
+  } else {
+    p->host_dropped++;                   // every slot is pinned by a pending fetch
+    return;
   }
   p->host_key[slot] = k;
   p->host_cached[k] = slot;
@@ -325,6 +331,7 @@ US_API int us_bm_enable_host(void* h, int host_slots) {
   p->host_slots = host_slots;
   p->host_key.resize(host_slots);
   p->host_pos.resize(host_slots);
+  p->host_pins.assign(host_slots, 0);
   for (int i = host_slots - 1; i >= 0; --i) p->host_free.push_back(i);
   return 0;
 }
@@ -343,8 +350,9 @@ US_API int us_bm_take_offloads(void* h, int* out, int cap) {
   return n;
 }
 
-// Host slots of the leading run of `keys` that the host tier holds (refreshes their
-// LRU position); returns the length of the run.
+// Host slots of the leading run of `keys` that the host tier holds; returns the length of
+// the run.  Every returned slot is pinned (taken out of the LRU list, so no offload can
+// recycle it) until `us_bm_unpin_host` gives it back.
 US_API int us_bm_match_host(void* h, const uint64_t* keys, int n, int* out_slots) {
   Pool* p = (Pool*)h;
   std::lock_guard<std::mutex> g(p->mu);
@@ -353,13 +361,26 @@ US_API int us_bm_match_host(void* h, const uint64_t* keys, int n, int* out_slots
     auto it = p->host_cached.find(Key{keys[2 * m], keys[2 * m + 1]});
     if (it == p->host_cached.end()) break;
     const int slot = it->second;
-    p->host_lru.erase(p->host_pos[slot]);
-    p->host_lru.push_back(slot);
-    p->host_pos[slot] = std::prev(p->host_lru.end());
+    if (p->host_pins[slot]++ == 0) p->host_lru.erase(p->host_pos[slot]);
     out_slots[m] = slot;
   }
   p->host_hits += (uint64_t)m;
   return m;
+}
+
+// Ends the pins `us_bm_match_host` took (once the copies are issued, or for slots the
+// caller did not use); an unpinned slot re-enters the LRU list as most recently used.
+US_API void us_bm_unpin_host(void* h, const int* slots, int n) {
+  Pool* p = (Pool*)h;
+  std::lock_guard<std::mutex> g(p->mu);
+  for (int i = 0; i < n; ++i) {
+    const int slot = slots[i];
+    if (slot < 0 || slot >= p->host_slots || p->host_pins[slot] <= 0) continue;
+    if (--p->host_pins[slot] == 0) {
+      p->host_lru.push_back(slot);
+      p->host_pos[slot] = std::prev(p->host_lru.end());
+    }
+  }
 }
 
 US_API void us_bm_host_stats(void* h, uint64_t* hits, uint64_t* offloads, int* used) {

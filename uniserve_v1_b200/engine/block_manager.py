@@ -40,6 +40,7 @@ def _lib():
         lib.us_bm_take_offloads.argtypes = [vp, vp, ctypes.c_int]
         lib.us_bm_match_host.argtypes = [vp, vp, ctypes.c_int, vp]
         lib.us_bm_host_stats.argtypes = [vp, vp, vp, vp]
+        lib.us_bm_unpin_host.argtypes = [vp, vp, ctypes.c_int]
         _bound = True
     return lib
 
@@ -76,18 +77,29 @@ class BlockManager:
     def take_moves(self):
         """(offloads [(device page, host slot)], fetches [(host slot, device page)]) decided
         since the last call.  Offloads must be copied first: a fetched page may be the one
-        an offload just vacated."""
+        an offload just vacated.  A host slot with a pending fetch is pinned from its match
+        until this call, so no offload of the batch names it; a slot recycled twice within
+        the batch keeps its last page only (each slot appears once in the offloads)."""
         if not getattr(self, "host_slots", 0):
             return [], []
         out = np.empty(2 * 4096, dtype=np.int32)
-        offloads = []
+        by_slot = {}
         while True:
             n = self.lib.us_bm_take_offloads(self.h, out.ctypes.data, 4096)
-            offloads += [(int(out[2 * i]), int(out[2 * i + 1])) for i in range(n)]
+            for i in range(n):
+                by_slot.pop(int(out[2 * i + 1]), None)      # keep the order of the last writers
+                by_slot[int(out[2 * i + 1])] = int(out[2 * i])
             if n < 4096:
                 break
+        offloads = [(page, slot) for slot, page in by_slot.items()]
         fetches, self.fetches = self.fetches, []
+        self._unpin([s for s, _ in fetches])
         return offloads, fetches
+
+    def _unpin(self, slots) -> None:
+        if slots:
+            arr = np.asarray(slots, dtype=np.int32)
+            self.lib.us_bm_unpin_host(self.h, arr.ctypes.data, len(arr))
 
     def fetch_prefix(self, keys: np.ndarray, start: int, limit: int) -> list:
         """Continues a device prefix match at page ``start``: keys the host tier holds get
@@ -96,8 +108,7 @@ class BlockManager:
         if not getattr(self, "host_slots", 0) or start >= limit:
             return []
         ks = np.ascontiguousarray(keys[start:limit], dtype=np.uint64)
-        slots = np.empty(len(ks), dtype=np.int32)
-        m = self.lib.us_bm_match_host(self.h, ks.ctypes.data, len(ks), slots.ctypes.data)
+        m, slots = self._match_host(ks)
         pages = []
         for i in range(m):
             got = self.allocate(1)
@@ -110,7 +121,14 @@ class BlockManager:
                 break
             self.fetches.append((int(slots[i]), page))
             pages.append(page)
+        self._unpin([int(x) for x in slots[len(pages):m]])      # matched, not fetched
         return pages
+
+    def _match_host(self, ks: np.ndarray):
+        """(length of the leading run the host tier holds, its slots); the slots are pinned."""
+        slots = np.empty(len(ks), dtype=np.int32)
+        m = self.lib.us_bm_match_host(self.h, ks.ctypes.data, len(ks), slots.ctypes.data)
+        return m, slots
 
     def host_stats(self) -> dict:
         a, b, c = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_int()

@@ -209,6 +209,130 @@ def mutants(base):
             ("commit under another key", CommitsWrongKey), ("hands out a held page", KeepsStalePage)]
 
 
+# ---------------------------------------------------------------- host tier --
+def explore_host_tier(make_bm, pages: int = 4, host_slots: int = 1, depth: int = 5,
+                      n_keys: int = 2, prefix: tuple = ()) -> dict:
+    """Every operation sequence up to ``depth`` on a block manager with a host tier of
+    ``host_slots`` slots, with the page *contents* simulated: an allocated page is written
+    with a fresh tag, a commit records the tag under its key, the copies of ``take_moves``
+    run in its order (offloads, then fetches) once per "step".  ``fetch`` matches the key
+    chain on the device first and continues on the host tier, as the scheduler does.
+    Checked after every step: a page returned for key k holds the tag committed under k
+    (so a host slot with a pending fetch was not recycled by an offload of the same step,
+    including when host_slots <= matched + offloads), and no host slot is written twice in
+    one batch.  ``prefix`` is run before every enumerated sequence (``HOST_FULL`` leaves the
+    first key on the host tier and every device page held, one of them committed under the
+    second key: the state from which two more operations reach the recycled-slot fault).
+    ``host_mutant`` is a manager without the pins; the check has to flag it."""
+    probe = make_bm(pages)
+    keys = probe.page_keys(list(range(n_keys * probe.page_size)))
+    ops = [("alloc", 1), ("alloc", 2), ("step",)] + [("release", i) for i in range(2)] + \
+        [("commit", i, k) for i in range(2) for k in range(n_keys)] + \
+        [("fetch", n) for n in range(1, n_keys + 1)]
+    ran = {"sequences": 0, "violation": None}
+
+    def run(seq):
+        bm = make_bm(pages)
+        bm.enable_host_tier(host_slots)
+        dev, host, tag_of_key, held, key_of, fresh = {}, {}, {}, [], {}, [0]
+        pending = []                    # (page, key index) fetched, checked after the moves
+
+        def step():
+            off, fet = bm.take_moves()
+            if len({s for _, s in off}) != len(off):
+                raise Violation(f"host: a slot written twice in one batch {off}")
+            for page, slot in off:
+                host[slot] = dev.get(page)
+            for slot, page in fet:
+                dev[page] = host.get(slot)
+            for page, k in pending:
+                if dev.get(page) != tag_of_key[k]:
+                    raise Violation(f"host: page {page} fetched for key {k} holds "
+                                    f"{dev.get(page)}, committed {tag_of_key[k]}")
+            pending.clear()
+        try:
+            for op in list(prefix) + list(seq):
+                kind = op[0]
+                if kind == "alloc":
+                    got = bm.allocate(op[1])
+                    if got is None:
+                        continue
+                    step()              # pages about to be overwritten are saved first
+                    for p_ in got:
+                        fresh[0] += 1
+                        dev[p_] = fresh[0]
+                        key_of.pop(p_, None)
+                        held.append(p_)
+                elif kind == "release":
+                    if op[1] >= len(held):
+                        return "skip"
+                    bm.release([held.pop(op[1])])
+                elif kind == "commit":
+                    if op[1] >= len(held) or held[op[1]] in key_of or op[2] in tag_of_key:
+                        return "skip"
+                    if op[2] > 0 and (op[2] - 1) not in tag_of_key:
+                        return "skip"                  # chains are committed in order
+                    page = held[op[1]]
+                    bm.commit(page, keys[op[2]])
+                    key_of[page] = op[2]
+                    tag_of_key[op[2]] = dev[page]
+                elif kind == "fetch":
+                    chain = np.ascontiguousarray(keys[:op[1]], dtype=np.uint64)
+                    got = bm.match_prefix(chain)
+                    pending.extend((p_, j) for j, p_ in enumerate(got))   # its copy may be queued
+                    more = bm.fetch_prefix(chain, len(got), op[1])
+                    pending.extend((p_, len(got) + j) for j, p_ in enumerate(more))
+                    held.extend(list(got) + list(more))
+                    for j, p_ in enumerate(more):
+                        key_of[p_] = len(got) + j
+                else:
+                    step()
+            step()
+        except Violation as v:
+            return str(v)
+        return None
+
+    def dfs(seq):
+        if ran["violation"]:
+            return
+        if seq:
+            r = run(seq)
+            if r == "skip":
+                return
+            ran["sequences"] += 1
+            if r:
+                ran["violation"] = {"sequence": [list(o) for o in seq], "message": r}
+                return
+        if len(seq) < depth:
+            for op in ops:
+                dfs(seq + [op])
+    dfs([])
+    return ran
+
+
+# 4 pages (3 usable), 1 host slot: key 0 committed and pushed to the host, key 1 committed on
+# a held device page, no free page left
+HOST_FULL = (("alloc", 1), ("commit", 0, 0), ("release", 0), ("alloc", 2), ("alloc", 1),
+             ("step",), ("commit", 0, 1))
+
+
+def host_mutant(base):
+    """A block manager whose matched host slots are not pinned (they return to the LRU list
+    at once, so an offload of the same step may recycle them before their fetch)."""
+    class UnpinnedHostSlots(base):
+        def _match_host(self, ks):
+            m, slots = super()._match_host(ks)
+            self._unpin([int(x) for x in slots[:m]])
+            return m, slots
+
+        def _unpin(self, slots):
+            if not getattr(self, "_in_match", False):
+                self._in_match = True
+                super()._unpin(slots)
+                self._in_match = False
+    return UnpinnedHostSlots
+
+
 # ------------------------------------------------------------ trace / replay --
 def record(bm) -> list:
     """Starts recording every call a client makes on ``bm`` (allocate, release, commit,
@@ -482,6 +606,13 @@ def main(argv=None) -> int:
     for name, cls in mutants(BlockManager):
         r = explore(mk(cls), a.pages, min(a.depth, 4), a.keys)
         report["mutants"][name] = "caught" if r["violation"] else "MISSED"
+    report["host_tier"] = {f"{hs} host slot(s)": explore_host_tier(mk(BlockManager), 4, hs,
+                                                                   min(a.depth, 5), a.keys)
+                           for hs in (1, 2)}
+    report["mutants"]["host slots not pinned"] = "caught" if explore_host_tier(
+        mk(host_mutant(BlockManager)), 4, 1, 3, 2, HOST_FULL)["violation"] else "MISSED"
+    report["host_tier"]["1 host slot, from a full tier"] = explore_host_tier(
+        mk(BlockManager), 4, 1, 4, 2, HOST_FULL)
     report["site_protocol"] = {"2 ranks x 2 sites x 3 passes": explore_site_protocol(2, 2, 3),
                                "3 ranks x 2 sites x 2 passes": explore_site_protocol(3, 2, 2),
                                "1 site (must fail)": explore_site_protocol(2, 1, 2)}
@@ -493,6 +624,7 @@ def main(argv=None) -> int:
                                   "one barrier per layer (must fail)":
                                       explore_ulysses_protocol(2, 2, second_barrier=False)}
     bad = report["native"]["violation"] or "MISSED" in report["mutants"].values() or \
+        any(r["violation"] for r in report["host_tier"].values()) or \
         report["site_protocol"]["2 ranks x 2 sites x 3 passes"]["violation"] or \
         report["site_protocol"]["3 ranks x 2 sites x 2 passes"]["violation"] or \
         not report["site_protocol"]["1 site (must fail)"]["violation"] or \
