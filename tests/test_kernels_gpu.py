@@ -259,9 +259,115 @@ def test_embedding_gather_advance():
     assert (g[1] == 0).all()
 
 
-def test_bounded_wait_reports_timeout_status():
-    """The status word starts clean and a read clears it."""
+def test_peer_wait_that_runs_out_sets_the_status_and_later_waits_give_up():
+    """A wait on a peer flag that nothing ever writes: with the budget set to a few
+    milliseconds the kernel returns, the status word reads "peer flag timeout", the next fused
+    launch gives up at once (its wait budget is zero while the word is set), the host check
+    raises, and after the word is cleared and the heap reset a clean launch passes.  The
+    silent peer is a second allocation of this process (a loopback heap of two ranks): no
+    GPU waits for longer than the budget and nothing faults."""
+    import time
+    from uniserve_v1_b200.parallel.symm import FusedComm, set_peer_wait_clocks
     assert N.read_status() == 0
+    T, H = 8, 512
+    w = torch.ones(H, dtype=BF, device=DEV)
+    part = rnd(T, H, seed=90)
+    set_peer_wait_clocks(6_000_000)                    # about 3 ms at 1.9 GHz
+    lone = FusedComm(None, 0, 2, DEV, H, sites=4, loopback=True)
+    try:
+        t0 = time.perf_counter()
+        lone.allreduce_add_rmsnorm(part, None, w, 1e-6)
+        torch.cuda.synchronize()
+        first = time.perf_counter() - t0
+        assert first < 1.0                             # bounded by the budget, not by 1.5 s
+        t0 = time.perf_counter()
+        for _ in range(20):                            # every later wait gives up at once
+            lone.allreduce_add_rmsnorm(part, None, w, 1e-6)
+        lone.barrier(lone.SITE_AUX)
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 0.5
+        with pytest.raises(RuntimeError, match="peer flag"):
+            N.raise_on_device_error()
+        assert N.read_status() == 0                    # the read cleared it
+        # the serving path's form: the word copied behind the results, checked without a
+        # synchronisation of its own, and cleared for whoever runs next
+        from uniserve_v1_b200.engine.runner import DeviceStepError
+        host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        lone.allreduce_add_rmsnorm(part, None, w, 1e-6)
+        N.kernels().us_status_copy_async(N.ptr(host), N.stream())
+        torch.cuda.synchronize()
+        assert int(host[0]) == 0x400
+        with pytest.raises(DeviceStepError):
+            raise DeviceStepError(int(host[0]))
+        N.kernels().us_status_clear_async(N.stream())
+        torch.cuda.synchronize()
+        assert N.read_status() == 0
+    finally:
+        lone.close()
+        set_peer_wait_clocks(0)
+    # a clean launch after the failure: one rank, nothing to wait for
+    solo = FusedComm(None, 0, 1, DEV, H, sites=4)
+    try:
+        y, res = solo.allreduce_add_rmsnorm(part, None, w, 1e-6)
+        ye, re_ = R.add_rmsnorm(part, None, w, 1e-6)
+        torch.cuda.synchronize()
+        close(y, ye, 2e-2, 2e-2)
+        close(res, re_, 1e-6, 1e-6)
+        solo.reset()
+        y2, _ = solo.allreduce_add_rmsnorm(part, None, w, 1e-6)
+        close(y2, ye, 2e-2, 2e-2)
+        lg = rnd(5, 3000, dtype=torch.float32, seed=91)
+        assert torch.equal(solo.argmax(lg, 2900, 0).long(), lg[:, :2900].argmax(-1))
+    finally:
+        solo.close()
+    assert N.read_status() == 0
+
+
+@pytest.mark.parametrize("T,E,k,H", [(64, 128, 8, 2048), (5, 16, 4, 256), (300, 128, 8, 512)])
+def test_route_sort_gather_and_unpermute_norm_equal_the_separate_kernels(T, E, k, H):
+    """One launch for routing + route sort + row gather, and the un-permute folded into the
+    residual add + RMSNorm: same ids, weights, expert outputs and norm as the separate
+    kernels; run twice (the grid-wide counters put themselves back)."""
+    I = 128
+    logits = rnd(T, E, dtype=torch.float32, seed=31)
+    x = rnd(T, H, seed=32)
+    w13, w2 = rnd(E // 2, 2 * I, H, scale=0.05, seed=33), rnd(E // 2, H, I, scale=0.05, seed=34)
+    nw = rnd(H, seed=35)
+    res0 = rnd(T, H, dtype=torch.float32, seed=36)
+    ids0, w0 = F.topk_softmax(logits, k, True)
+    plain = F.moe_experts(x, ids0, w0, w13, w2, e_lo=E // 2)
+    y_ref, r_ref = F.add_rmsnorm(plain, res0.clone(), nw, 1e-6)
+    ws = F.MoeWorkspace.create(T, k, E // 2, H, I, DEV)
+    for _ in range(2):
+        ids1, w1 = F.route_sort_gather(logits, x, k, True, ws, E // 2, E // 2)
+        assert torch.equal(ids0, ids1) and torch.equal(w0, w1)
+        y_perm, perm = F.moe_experts(x, ids1, w1, w13, w2, e_lo=E // 2, ws=ws, pregathered=True,
+                                     defer_unpermute=True)
+        y, r = F.unpermute_add_rmsnorm(y_perm, perm, w1, res0.clone(), nw, 1e-6)
+        close(r, r_ref, 1e-5, 1e-5)
+        close(y, y_ref, 2e-2, 2e-2)
+    assert int(ws.sync.sum()) == 0
+    live = torch.tensor([max(1, T - 3)], dtype=torch.int32, device=DEV)
+    ids2, _ = F.route_sort_gather(logits, x, k, True, ws, E // 2, E // 2, live=live)
+    assert (ids2[int(live):] == -1).all() and torch.equal(ids2[:int(live)], ids0[:int(live)])
+
+
+@pytest.mark.parametrize("Hq,Hkv,splits", [(32, 4, 4), (16, 1, 3), (8, 1, 8)])
+def test_paged_decode_attention_merges_its_splits_in_the_kernel(Hq, Hkv, splits):
+    B, page, pages, D = 5, 16, 200, 128
+    lens = torch.tensor([1, 17, 300, 64, 511], dtype=torch.int32, device=DEV)
+    q = rnd(B, Hq, D)
+    kc, vc = rnd(pages, page, Hkv, D, seed=1), rnd(pages, page, Hkv, D, seed=2)
+    pt = torch.randperm(pages - 1, device=DEV)[:B * 32].view(B, 32).to(torch.int32) + 1
+    scratch, counters = F.decode_scratch(B, Hq, Hkv, D, splits, DEV)
+    ref = R.paged_decode_attention(q, kc, vc, pt, lens, 1 / math.sqrt(D))
+    two = F.paged_decode_attention(q, kc, vc, pt, lens, 1 / math.sqrt(D), splits=splits)
+    for _ in range(3):                                  # the counters return to zero
+        out = F.paged_decode_attention(q, kc, vc, pt, lens, 1 / math.sqrt(D), splits=splits,
+                                       scratch=scratch, counters=counters)
+        close(out, ref, 2e-2, 2e-2)
+        close(out, two, 1e-3, 1e-3)
+    assert int(counters.sum()) == 0
 
 
 @pytest.mark.parametrize("causal", [False, True])

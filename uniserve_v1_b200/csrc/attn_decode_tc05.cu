@@ -15,8 +15,11 @@
 // current tile's products.
 //
 // Grid = (sequence, kv head, split); with more than one split the CTAs write
-// normalised partial outputs and log-sum-exps and the merge kernel of
-// attn_decode.cu combines them.
+// normalised partial outputs and log-sum-exps.  With an arrival counter per
+// (sequence, kv head) the CTA that finishes last merges the splits itself (no
+// second launch); without one the merge kernel of attn_decode.cu combines them.
+// The first tile's K and V loads are issued before the CTA's set-up (query
+// operand, tensor-memory allocation) so that set-up overlaps the first fetch.
 //
 // Roles: warps 0-3 softmax / output, warp 4 TMA producer, warp 5 TMEM owner +
 // MMA issuer.  Every wait is bounded.
@@ -40,6 +43,7 @@ struct DecTcArgs {
   __nv_bfloat16* out;
   float* part_o;
   float* part_lse;
+  int* counters;          // [B * Hkv] zero between launches, or NULL (separate merge kernel)
   long long ldq, ldo;
   int B, Hq, Hkv, max_pages, page_size, splits, window;
   float scale_log2;
@@ -50,6 +54,60 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+
+// Arrival counter of (sequence, kv head): the CTA that adds the last of `splits` arrivals
+// merges the partial outputs of the G heads (threads 0..127 own one channel each) and puts
+// the counter back to zero for the next launch.  Called by every thread of the CTA.
+template <int G>
+__device__ __forceinline__ void merge_if_last(const DecTcArgs& a, int b, int hk) {
+  __shared__ int last_s;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* c = a.counters + (long long)b * a.Hkv + hk;
+    const int old = atomicAdd(c, 1);
+    last_s = old == a.splits - 1;
+    if (last_s) *c = 0;
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  // log-sum-exps of the G heads x splits first (one load per thread), then every channel
+  // thread merges its G heads with independent loads
+  __shared__ float lse_s[kNPad * 32];
+  const int tid = threadIdx.x;
+  const long long base0 = ((long long)b * a.Hq + (long long)hk * G) * a.splits;
+  const int n_lse = G * a.splits;
+  for (int i = tid; i < n_lse && i < kNPad * 32; i += blockDim.x)
+    lse_s[i] = __ldcg(a.part_lse + base0 + i);
+  __syncthreads();
+  if (tid >= kD) return;
+  float m[G], acc[G], den[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    acc[g] = 0.f;
+    den[g] = 0.f;
+    for (int s = 0; s < a.splits; ++s) m[g] = fmaxf(m[g], lse_s[g * a.splits + s]);
+  }
+  for (int s = 0; s < a.splits; ++s) {
+    float v[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) v[g] = __ldcg(a.part_o + (base0 + g * a.splits + s) * kD + tid);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float l = lse_s[g * a.splits + s];
+      const float wgt = (l == -INFINITY) ? 0.f : __expf(l - m[g]);
+      den[g] += wgt;
+      acc[g] += wgt * v[g];
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+    a.out[(long long)b * a.ldo + (long long)(hk * G + g) * kD + tid] =
+        us::f2bf(den[g] > 0.f ? acc[g] / den[g] : 0.f);
 }
 
 template <int G>
@@ -85,6 +143,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
         }
       }
     }
+    if (a.splits > 1 && a.counters) merge_if_last<G>(a, b, hk);
     return;
   }
 
@@ -117,6 +176,31 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
+  __syncthreads();
+  const int* pt_row = a.page_table + (long long)b * a.max_pages;
+  const int pages_per_tile = kTileKeys / a.page_size;
+  const int seq_pages = (seq_len + a.page_size - 1) / a.page_size;
+  // One tile's K (or V) pages into their buffer; `bar` was armed by the caller.
+  auto load_tile = [&](const CUtensorMap* tm, uint8_t* buf, uint64_t* bar, int t) {
+    const int page0 = (k_begin + t * kTileKeys) / a.page_size;
+    for (int i = 0; i < pages_per_tile; ++i) {
+      const int pi = page0 + i;
+      const int page = (pi < seq_pages && pi < a.max_pages) ? pt_row[pi] : 0;
+      const int row = page * a.page_size;
+      uint8_t* dst = buf + i * a.page_size * 128;
+      tc::tma_load_2d(dst, tm, bar, hk * kD, row);
+      tc::tma_load_2d(dst + kHalfBytes, tm, bar, hk * kD + 64, row);
+    }
+  };
+  if (warp == 4 && lane == 0) {
+    // the first tile needs nothing of the set-up below: fetch it now
+    tc::tma_prefetch_desc(&tmK);
+    tc::tma_prefetch_desc(&tmV);
+    tc::mbar_expect_tx(k_full, kTileBytes);
+    load_tile(&tmK, sK, k_full, 0);
+    tc::mbar_expect_tx(v_full, kTileBytes);
+    load_tile(&tmV, sV, v_full, 0);
+  }
   if (warp == 5) {
     tc::tmem_alloc(tmem_slot, 32);
     tc::tmem_relinquish();
@@ -146,42 +230,22 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
 
   if (warp == 4) {
     if (lane == 0) {
-      tc::tma_prefetch_desc(&tmK);
-      tc::tma_prefetch_desc(&tmV);
-      const int* pt = a.page_table + (long long)b * a.max_pages;
-      const int pages_per_tile = kTileKeys / a.page_size;
-      const int seq_pages = (seq_len + a.page_size - 1) / a.page_size;
-      for (int t = 0; t < ntiles; ++t) {
+      for (int t = 1; t < ntiles; ++t) {
         const uint32_t ph = (uint32_t)t & 1u;
-        const int page0 = (k_begin + t * kTileKeys) / a.page_size;
         if (!tc::mbar_wait(k_empty, ph ^ 1u, abort_flag)) {
           us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
           *abort_flag = 1;
           break;
         }
         tc::mbar_expect_tx(k_full, kTileBytes);
-        for (int i = 0; i < pages_per_tile; ++i) {
-          const int pi = page0 + i;
-          const int page = (pi < seq_pages && pi < a.max_pages) ? pt[pi] : 0;
-          const int row = page * a.page_size;
-          uint8_t* dst = sK + i * a.page_size * 128;
-          tc::tma_load_2d(dst, &tmK, k_full, hk * kD, row);
-          tc::tma_load_2d(dst + kHalfBytes, &tmK, k_full, hk * kD + 64, row);
-        }
+        load_tile(&tmK, sK, k_full, t);
         if (!tc::mbar_wait(v_empty, ph ^ 1u, abort_flag)) {
           us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
           *abort_flag = 1;
           break;
         }
         tc::mbar_expect_tx(v_full, kTileBytes);
-        for (int i = 0; i < pages_per_tile; ++i) {
-          const int pi = page0 + i;
-          const int page = (pi < seq_pages && pi < a.max_pages) ? pt[pi] : 0;
-          const int row = page * a.page_size;
-          uint8_t* dst = sV + i * a.page_size * 128;
-          tc::tma_load_2d(dst, &tmV, v_full, hk * kD, row);
-          tc::tma_load_2d(dst + kHalfBytes, &tmV, v_full, hk * kD + 64, row);
-        }
+        load_tile(&tmV, sV, v_full, t);
       }
     }
   } else if (warp == 5) {
@@ -351,6 +415,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
     __syncwarp();
     tc::tmem_dealloc(tmem_base, 32);
   }
+  if (a.splits > 1 && a.counters) merge_if_last<G>(a, b, hk);
 }
 
 template <int G>
@@ -375,13 +440,11 @@ extern "C" int us_merge_decode_splits(const float* part_o, const float* part_lse
                                       long long ldo, int B, int Hq, int D, int splits,
                                       void* stream);
 
-// Same contract as us_paged_decode_attention (head_dim 128, page_size dividing 128).
-US_API int us_paged_decode_attention_tc(const void* q, const void* kcache, const void* vcache,
-                                        const int* page_table, const int* seq_lens, void* out,
-                                        void* scratch, int B, int Hq, int Hkv, int D,
-                                        int num_pages, int max_pages, int page_size, int splits,
-                                        int window, float scale, long long ldq, long long ldo,
-                                        void* stream_) {
+static int decode_tc(const void* q, const void* kcache, const void* vcache,
+                     const int* page_table, const int* seq_lens, void* out, void* scratch,
+                     int* counters, int B, int Hq, int Hkv, int D, int num_pages, int max_pages,
+                     int page_size, int splits, int window, float scale, long long ldq,
+                     long long ldo, void* stream_) {
   US_REQUIRE(q && kcache && vcache && page_table && seq_lens && out);
   US_REQUIRE(D == kD && Hkv >= 1 && Hq % Hkv == 0 && Hq / Hkv <= kNPad && splits >= 1);
   US_REQUIRE(page_size >= 8 && page_size <= 128 && (kTileKeys % page_size) == 0);
@@ -402,6 +465,7 @@ US_API int us_paged_decode_attention_tc(const void* q, const void* kcache, const
   a.out = (__nv_bfloat16*)out;
   a.part_o = (float*)scratch;
   a.part_lse = scratch ? (float*)scratch + (long long)B * Hq * splits * D : nullptr;
+  a.counters = splits > 1 ? counters : nullptr;
   a.ldq = ldq; a.ldo = ldo;
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.max_pages = max_pages; a.page_size = page_size;
   a.splits = splits; a.window = window;
@@ -417,7 +481,34 @@ US_API int us_paged_decode_attention_tc(const void* q, const void* kcache, const
     default: return US_ERR_UNSUPPORTED;
   }
   if (rc) return rc;
-  if (splits > 1)
+  if (splits > 1 && !counters)
     return us_merge_decode_splits(a.part_o, a.part_lse, out, ldo, B, Hq, D, splits, stream_);
   return US_OK;
+}
+
+// Same contract as us_paged_decode_attention (head_dim 128, page_size dividing 128); the
+// splits are merged by a second launch.
+US_API int us_paged_decode_attention_tc(const void* q, const void* kcache, const void* vcache,
+                                        const int* page_table, const int* seq_lens, void* out,
+                                        void* scratch, int B, int Hq, int Hkv, int D,
+                                        int num_pages, int max_pages, int page_size, int splits,
+                                        int window, float scale, long long ldq, long long ldo,
+                                        void* stream_) {
+  return decode_tc(q, kcache, vcache, page_table, seq_lens, out, scratch, nullptr, B, Hq, Hkv, D,
+                   num_pages, max_pages, page_size, splits, window, scale, ldq, ldo, stream_);
+}
+
+// One launch: `counters` [B * Hkv] int32 must be zero before the first call and is left zero
+// by every call (the last CTA of a (sequence, kv head) merges its splits and resets it).
+// Calls that share `scratch` / `counters` must be ordered on the device.
+US_API int us_paged_decode_attention_tc_merged(const void* q, const void* kcache,
+                                               const void* vcache, const int* page_table,
+                                               const int* seq_lens, void* out, void* scratch,
+                                               int* counters, int B, int Hq, int Hkv, int D,
+                                               int num_pages, int max_pages, int page_size,
+                                               int splits, int window, float scale,
+                                               long long ldq, long long ldo, void* stream_) {
+  US_REQUIRE((splits == 1 || counters != nullptr) && splits <= 32);
+  return decode_tc(q, kcache, vcache, page_table, seq_lens, out, scratch, counters, B, Hq, Hkv, D,
+                   num_pages, max_pages, page_size, splits, window, scale, ldq, ldo, stream_);
 }

@@ -27,7 +27,12 @@ template <int BN, bool DUAL>
 __global__ void __launch_bounds__(192)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ BMaps tmBs,
                const GemmArgs args) {
-  US_PDL_PROLOGUE();
+  // Programmatic dependent launch, with the wait moved down: what does not depend on the
+  // kernels before this one - barrier set-up, the tensor-memory allocation and, for a dense
+  // problem, the first stages' WEIGHT tiles (weights are never written by a kernel) - runs
+  // while the previous kernel is still finishing.  Everything that reads activations or the
+  // tile lists comes after griddepcontrol.wait.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int kBTile = BN * kBlockK * 2;
   constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
   constexpr uint32_t kCols = tmem_cols<BN>(DUAL);
@@ -36,16 +41,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tile = blockIdx.x;
   const int n_tile = blockIdx.y;
-
-  int group = 0, row0 = n_tile * BN, nrows;
-  if (args.num_tiles != nullptr) {
-    if (n_tile >= *args.num_tiles) return;
-    group = args.tile_group[n_tile];
-    row0 = args.tile_row0[n_tile];
-    nrows = args.tile_rows[n_tile];
-  } else {
-    nrows = min(BN, args.rows - row0);
-  }
+  const bool grouped = args.num_tiles != nullptr;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -56,7 +52,24 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* epi_fail = tmem_slot + 2;
+  const int num_k_total = (args.K + kBlockK - 1) / kBlockK;
+  const int kb0 = blockIdx.z * args.kb_per_split;
+  const int num_k = min(num_k_total - kb0, args.kb_per_split);
+  // stages whose weight tiles are fetched ahead of the wait (dense problems only)
+  const int early = (grouped || !args.early) ? 0 : min(stages, num_k);
 
+  int group = 0, row0 = n_tile * BN, nrows;
+  if (grouped || !args.early) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (grouped) {
+    // the tile list comes from the kernels before: leave at once when this CTA's tile is
+    // past the list (nothing is allocated yet)
+    if (n_tile >= *args.num_tiles) return;
+    group = args.tile_group[n_tile];
+    row0 = args.tile_row0[n_tile];
+    nrows = args.tile_rows[n_tile];
+  } else {
+    nrows = min(BN, args.rows - row0);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       tc::mbar_init(&full_bar[s], 1);
@@ -66,24 +79,45 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     *abort_flag = 0;
     *epi_fail = 0;
     tc::mbar_fence_init();
+    tc::tma_prefetch_desc(&tmA);
+    tc::tma_prefetch_desc(&tmBs.m[0]);
+    for (int kb = 0; kb < early; ++kb) {
+      uint8_t* st = smem + (size_t)kb * kStageBytes;
+      tc::mbar_expect_tx(&full_bar[kb], kStageBytes);
+      const int kx = (kb0 + kb) * kBlockK;
+      tc::tma_load_3d(st, &tmA, &full_bar[kb], kx, m_tile * kBlockM, 0);
+      if (DUAL)
+        tc::tma_load_3d(st + kATile, &tmA, &full_bar[kb], kx,
+                        args.dual_offset + m_tile * kBlockM, 0);
+    }
   }
   if (warp == 1) {
     tc::tmem_alloc(tmem_slot, kCols);
     tc::tmem_relinquish();
   }
+  if (!grouped && args.early) asm volatile("griddepcontrol.wait;" ::: "memory");
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const int num_k_total = (args.K + kBlockK - 1) / kBlockK;
-  const int kb0 = blockIdx.z * args.kb_per_split;
-  const int num_k = min(num_k_total - kb0, args.kb_per_split);
 
   if (warp == 0) {
     if (lane == 0) {
-      tc::tma_prefetch_desc(&tmA);
-      tc::tma_prefetch_desc(&tmBs.m[0]);
-      for (int kb = 0; kb < num_k; ++kb) {
+      auto load_b = [&](uint8_t* st, uint64_t* bar, int kx) {
+        if (args.rows_per_peer > 0) {
+          const int src = row0 / args.rows_per_peer;
+          tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], bar, kx,
+                          row0 - src * args.rows_per_peer);
+        } else {
+          const int src = args.k_per_peer > 0 ? kx / args.k_per_peer : 0;
+          tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], bar,
+                          kx - src * args.k_per_peer, row0);
+        }
+      };
+      // activation tiles of the stages whose weights are already on their way
+      for (int kb = 0; kb < early; ++kb)
+        load_b(smem + (size_t)kb * kStageBytes, &full_bar[kb], (kb0 + kb) * kBlockK);
+      for (int kb = early; kb < num_k; ++kb) {
         const int s = kb % stages;
         const uint32_t ph = (uint32_t)(kb / stages) & 1u;
         if (!tc::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
@@ -98,15 +132,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (DUAL)
           tc::tma_load_3d(st + kATile, &tmA, &full_bar[s], kx,
                           args.dual_offset + m_tile * kBlockM, group);
-        if (args.rows_per_peer > 0) {
-          const int src = row0 / args.rows_per_peer;
-          tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], &full_bar[s], kx,
-                          row0 - src * args.rows_per_peer);
-        } else {
-          const int src = args.k_per_peer > 0 ? kx / args.k_per_peer : 0;
-          tc::tma_load_2d(st + kATile * (DUAL ? 2 : 1), &tmBs.m[src], &full_bar[s],
-                          kx - src * args.k_per_peer, row0);
-        }
+        load_b(st, &full_bar[s], kx);
       }
     }
   } else if (warp == 1) {
@@ -873,6 +899,9 @@ int launch_persist(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int til
   return US_OK;
 }
 
+// Live CTAs expected of the next grouped launch of this thread (us_gemm_wx_hint); 0 = none.
+thread_local int g_cta_hint = 0;
+
 template <int BN, bool DUAL>
 int launch(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int m_tiles, int n_tiles,
            cudaStream_t stream) {
@@ -900,12 +929,39 @@ int launch(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int m_tiles, in
     const char* e = getenv("US_GEMM_SMALL_KB");
     return e ? atoi(e) : 56;
   }();
-  const int budget = (BN <= 64 && !DUAL) ? small_kb * 1024 : (BN <= 32 ? 104 * 1024 : 200 * 1024);
+  int budget = (BN <= 64 && !DUAL) ? small_kb * 1024 : (BN <= 32 ? 104 * 1024 : 200 * 1024);
+  // A launch that cannot fill the SMs (a rank's share under tensor / expert parallelism)
+  // is bound by the bytes each CTA keeps in flight, not by occupancy: give every CTA the
+  // shared memory the missing neighbours would have used.  Grouped launches list more
+  // tiles than are live (the list is sized for the worst case): the caller's hint, else
+  // half the list, stands for the live count.
+  // Measured on a 64-row decode step: deeper pipelines for the grouped expert GEMMs are
+  // 7 % faster at 16 experts per rank and neutral at 128; deepening the dense skinny
+  // GEMMs too cost 2.7 % on one GPU, so they keep their depth (US_GEMM_DEEP=2 deepens both,
+  // 0 neither).
+  static const int deep_mode = [] {
+    const char* e = getenv("US_GEMM_DEEP");
+    return (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
+  }();
+  const int hint = g_cta_hint;
+  g_cta_hint = 0;
+  if ((deep_mode == 1 && a.num_tiles && hint > 0) || deep_mode == 2) {
+    const int est = hint > 0 ? hint
+                             : (a.num_tiles ? m_tiles * ((n_tiles + 1) / 2) : tiles * splits);
+    const int per_sm = (est + 147) / 148;
+    const int room = per_sm <= 1 ? 200 * 1024 : per_sm == 2 ? 110 * 1024 : per_sm == 3 ? 72 * 1024 : 0;
+    if (room > budget) budget = room;
+  }
   int stages = budget / kStageBytes;
   if (stages > 8) stages = 8;
   if (stages > kb_per) stages = kb_per;
   if (stages < 1) stages = 1;
   a.stages = stages;
+  static const bool early_ok = [] {
+    const char* e = getenv("US_GEMM_EARLY");
+    return !(e && e[0] == '0');
+  }();
+  a.early = early_ok ? 1 : 0;
   const size_t smem = (size_t)stages * kStageBytes + (2 * stages + 1) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -1052,6 +1108,7 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
   a.rows = x_rows;
   a.dual_offset = dual_offset;
   a.stages = 0;
+  a.early = 0;
   a.act = act;
   a.out_dtype = out_dtype;
   a.bias_dtype = bias_dtype;
@@ -1165,6 +1222,14 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
 // X: [x_rows, K] bf16 with ldx.  Dense when num_tiles == nullptr (then
 // n_tiles = ceil(rows / block_n)); grouped otherwise with `max_tiles` CTAs
 // along the row-tile axis.
+// Expected number of live CTAs of this thread's next grouped us_gemm_wx launch (the tile
+// list of a grouped launch is sized for the worst case; the pipeline depth is chosen from
+// how many CTAs will really run).  Consumed by that launch.
+US_API int us_gemm_wx_hint(int live_ctas) {
+  g_cta_hint = live_ctas > 0 ? live_ctas : 0;
+  return US_OK;
+}
+
 US_API int us_gemm_wx(const void* W, const void* X, void* out, int G, int w_rows, int M, int K,
                       int x_rows, long long ldw, long long ldx, long long ldo, int dual,
                       int dual_offset, int act, int out_dtype, const void* bias, int bias_dtype,

@@ -29,6 +29,7 @@ enum UsDevError : unsigned int {
   US_DEV_TIMEOUT_ACC = 0x300,    // epilogue gave up waiting for the accumulator
   US_DEV_TIMEOUT_PEER = 0x400,   // a wait on another GPU's flag ran out
   US_DEV_BOUNDS = 0x500,         // an index fell outside its table
+  US_DEV_TIMEOUT_GRID = 0x600,   // a wait on another CTA of the same grid ran out
 };
 
 #define US_CUDA_CHECK(expr)                                  \

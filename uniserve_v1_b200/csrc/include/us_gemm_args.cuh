@@ -13,6 +13,7 @@ struct GemmArgs {
   int rows;         // activation rows (dense)
   int dual_offset;  // row offset of the second weight tile (dual epilogue)
   int stages;
+  int early;        // dense: weight tiles of the first stages are fetched before the PDL wait
   int act;          // dual: 0 = silu fused rounding, 1 = silu stepwise rounding, 2 = gelu-tanh
   int out_dtype;    // 0 = bf16, 1 = fp32
   int bias_dtype;   // 0 = bf16, 1 = fp32

@@ -1,6 +1,8 @@
 // System-scope flag helpers shared by the kernels that talk to other GPUs.
 // Every wait is bounded: on expiry the caller records US_DEV_TIMEOUT_PEER in the
 // status word and carries on; once the word is set later waits give up at once.
+// The budget of a wait (SM clocks) is the 64-bit word at byte 8 of the status block
+// (us_set_peer_wait_clocks; kWaitClocks when it was never set).
 #pragma once
 #include "us_common.cuh"
 
@@ -39,7 +41,12 @@ __device__ __forceinline__ void st16_sys(void* p, uint4 v) {
 __device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int epoch,
                                           unsigned int* status) {
   const long long t0 = clock64();
-  const long long budget = (status && *(volatile unsigned int*)status) ? 0 : kWaitClocks;
+  long long budget = kWaitClocks;
+  if (status) {
+    const long long set = *reinterpret_cast<volatile long long*>(status + 2);
+    if (set > 0) budget = set;
+    if (*(volatile unsigned int*)status) budget = 0;
+  }
   while ((int)(ld_acquire_sys(flag) - epoch) < 0) {
     if (clock64() - t0 > budget) {
       us_dev_fail(status, US_DEV_TIMEOUT_PEER);

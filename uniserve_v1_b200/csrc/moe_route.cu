@@ -10,6 +10,11 @@
 //                  list of row tiles the grouped GEMM walks.
 //   moe_gather     permuted activation rows  xp[p] = x[route(p) / top_k].
 //   moe_unpermute  out[t] = sum_j w[t, j] * y[perm(t, j)]  in FP32, one rounding.
+//   unpermute_add_rmsnorm   the same sum, added to the FP32 residual stream and
+//                  normalised in the same launch (the next block's input norm).
+//   route_sort_gather   topk_softmax + moe_sort + moe_gather of a decode-size batch in
+//                  one launch: the CTAs route their tokens, the last one to arrive
+//                  sorts, then all of them gather (two bounded grid-wide waits).
 //
 // Reference behaviour: crates/ops/kernels/topk_softmax/nvcc/src/topk_softmax.cu:1-27,
 // crates/nn/src/functional/moe.rs:301-330, crates/ops/kernels/moe_unpermute
@@ -267,6 +272,146 @@ moe_unpermute_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict_
   }
 }
 
+// out[t] = sum of the token's routed rows, then residual += out, y = rmsnorm(residual) * w.
+// One CTA per token; the partial sum is rounded to bf16 once before it joins the FP32
+// residual, as the separate un-permute kernel's output would be.
+constexpr int kNormVec = 4;   // hidden sizes up to 4 x 256 x 8
+__global__ void __launch_bounds__(256)
+unpermute_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y_perm,
+                             const int* __restrict__ perm, const float* __restrict__ weights,
+                             int top_k, float* __restrict__ residual,
+                             const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                             int H, float eps, int first) {
+  US_PDL_PROLOGUE();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const int nvec = H >> 3;
+  float* rr = residual + (size_t)t * H;
+  float ss = 0.f;
+  float4 keep[kNormVec][2];
+#pragma unroll
+  for (int i = 0; i < kNormVec; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v >= nvec) break;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      const int p = perm[(size_t)t * top_k + j];
+      if (p < 0) continue;
+      const float wj = weights[(size_t)t * top_k + j];
+      us::Pack16 q;
+      q.u = *reinterpret_cast<const uint4*>(y_perm + (size_t)p * H + v * 8);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[c] += wj * us::bf2f(q.b[c]);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = us::bf2f(us::f2bf(acc[c]));
+    float4 r0 = make_float4(0.f, 0.f, 0.f, 0.f), r1 = r0;
+    if (!first) {
+      r0 = *reinterpret_cast<const float4*>(rr + v * 8);
+      r1 = *reinterpret_cast<const float4*>(rr + v * 8 + 4);
+    }
+    r0.x += acc[0]; r0.y += acc[1]; r0.z += acc[2]; r0.w += acc[3];
+    r1.x += acc[4]; r1.y += acc[5]; r1.z += acc[6]; r1.w += acc[7];
+    *reinterpret_cast<float4*>(rr + v * 8) = r0;
+    *reinterpret_cast<float4*>(rr + v * 8 + 4) = r1;
+    keep[i][0] = r0;
+    keep[i][1] = r1;
+    ss += r0.x * r0.x + r0.y * r0.y + r0.z * r0.z + r0.w * r0.w;
+    ss += r1.x * r1.x + r1.y * r1.y + r1.z * r1.z + r1.w * r1.w;
+  }
+  ss = us::block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int i = 0; i < kNormVec; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v >= nvec) break;
+    const float4 r0 = keep[i][0], r1 = keep[i][1];
+    us::Pack16 q, o;
+    q.u = *reinterpret_cast<const uint4*>(w + v * 8);
+    o.b[0] = us::f2bf(r0.x * inv * us::bf2f(q.b[0]));
+    o.b[1] = us::f2bf(r0.y * inv * us::bf2f(q.b[1]));
+    o.b[2] = us::f2bf(r0.z * inv * us::bf2f(q.b[2]));
+    o.b[3] = us::f2bf(r0.w * inv * us::bf2f(q.b[3]));
+    o.b[4] = us::f2bf(r1.x * inv * us::bf2f(q.b[4]));
+    o.b[5] = us::f2bf(r1.y * inv * us::bf2f(q.b[5]));
+    o.b[6] = us::f2bf(r1.z * inv * us::bf2f(q.b[6]));
+    o.b[7] = us::f2bf(r1.w * inv * us::bf2f(q.b[7]));
+    *reinterpret_cast<uint4*>(y + (size_t)t * H + v * 8) = o.u;
+  }
+}
+
+// Bounded spin on a device counter that other CTAs of the same grid advance.
+__device__ __forceinline__ bool grid_wait(const unsigned int* ctr, unsigned int want,
+                                          unsigned int* status) {
+  const long long t0 = clock64();
+  while (*(volatile const unsigned int*)ctr < want) {
+    if (clock64() - t0 > 400000000LL) {          // about 0.2 s
+      us_dev_fail(status, US_DEV_TIMEOUT_GRID);
+      return false;
+    }
+  }
+  __threadfence();
+  return true;
+}
+
+// Routing, route sort and row gather of a decode-size batch in one launch.  Every CTA of
+// the grid is resident at once (the host launches at most 128 CTAs of 256 threads).
+// `sync` holds three zero-initialised counters: [0] CTAs that routed their tokens, [1] set
+// by CTA 0 once the sort is written, [2] CTAs that passed the second wait (the last one
+// clears all three for the next launch).
+template <int PER_LANE>
+__global__ void __launch_bounds__(256)
+route_sort_gather_kernel(const float* __restrict__ logits, int* __restrict__ ids,
+                         float* __restrict__ weights, int T, int E_all, int top_k, int renorm,
+                         const int* __restrict__ live, int e_lo, int E, int block_n,
+                         int max_tiles, int* __restrict__ sorted_route,
+                         int* __restrict__ perm_of_route, int* __restrict__ expert_offsets,
+                         int* __restrict__ tile_group, int* __restrict__ tile_row0,
+                         int* __restrict__ tile_rows, int* __restrict__ num_tiles,
+                         const __nv_bfloat16* __restrict__ x, int H,
+                         __nv_bfloat16* __restrict__ xp, unsigned int* sync,
+                         unsigned int* status) {
+  US_PDL_PROLOGUE();
+  const int warps = blockDim.x >> 5;
+  for (int t = blockIdx.x * warps + (threadIdx.x >> 5); t < T; t += gridDim.x * warps)
+    topk_token<PER_LANE>(logits, ids, weights, t, E_all, top_k, renorm, live, nullptr, nullptr);
+  __threadfence();
+  __syncthreads();
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) {
+    atomicAdd(&sync[0], 1u);
+    ok_s = 1;
+  }
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) ok_s = grid_wait(&sync[0], gridDim.x, status) ? 1 : 0;
+    __syncthreads();
+    if (ok_s)
+      sort_routes(ids, T * top_k, e_lo, E, block_n, max_tiles, sorted_route, perm_of_route,
+                  expert_offsets, tile_group, tile_row0, tile_rows, num_tiles, status);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) atomicExch(&sync[1], 1u);
+  } else {
+    if (threadIdx.x == 0) ok_s = grid_wait(&sync[1], 1u, status) ? 1 : 0;
+    __syncthreads();
+  }
+  const int total = ok_s ? *(volatile const int*)(expert_offsets + E) : 0;
+  for (int p = blockIdx.x; p < total; p += gridDim.x) {
+    const int t = sorted_route[p] / top_k;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)t * H);
+    uint4* dst = reinterpret_cast<uint4*>(xp + (long long)p * H);
+    for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x) dst[v] = src[v];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(&sync[2], 1u) == gridDim.x - 1) {
+      sync[0] = 0;
+      sync[1] = 0;
+      sync[2] = 0;
+    }
+  }
+}
+
 }  // namespace
 
 US_API int us_topk_softmax(const float* logits, int* ids, float* weights, int T, int E, int top_k,
@@ -348,5 +493,57 @@ US_API int us_route_sort(const float* logits, int* ids, float* weights, int T, i
   US_RS_CASE(16)
   US_RS_CASE(32)
 #undef US_RS_CASE
+  return US_ERR_ARG;
+}
+
+// out-of-place un-permute fused with the residual add and the RMSNorm that follow it.
+US_API int us_unpermute_add_rmsnorm(const void* y_perm, const int* perm, const float* weights,
+                                    int T, int top_k, int H, void* residual, const void* w,
+                                    void* y, float eps, int first, void* stream_) {
+  US_REQUIRE(y_perm && perm && weights && residual && w && y && T >= 0 && top_k >= 1);
+  US_REQUIRE((H % 8) == 0 && H <= 8 * 256 * kNormVec);
+  if (T == 0) return US_OK;
+  US_CUDA_CHECK(us::launch_pdl(unpermute_add_rmsnorm_kernel, dim3(T), dim3(256), 0,
+                               (cudaStream_t)stream_, (const __nv_bfloat16*)y_perm, perm, weights,
+                               top_k, (float*)residual, (const __nv_bfloat16*)w,
+                               (__nv_bfloat16*)y, H, eps, first));
+  return US_OK;
+}
+
+// topk_softmax + moe_sort + moe_gather in one launch, for batches of at most 512 tokens.
+// `sync`: three zero-initialised uint32 counters owned by the caller's workspace.
+US_API int us_route_sort_gather(const float* logits, int* ids, float* weights, int T, int E_all,
+                                int top_k, int renorm, const int* live, int e_lo, int E,
+                                int block_n, int max_tiles, int* sorted_route,
+                                int* perm_of_route, int* expert_offsets, int* tile_group,
+                                int* tile_row0, int* tile_rows, int* num_tiles, const void* x,
+                                int H, void* xp, void* sync, void* stream_) {
+  US_REQUIRE(logits && ids && weights && T >= 1 && T <= 512 && E_all >= 1 &&
+             E_all <= kMaxExperts && top_k >= 1 && top_k <= 32 && top_k <= E_all);
+  US_REQUIRE(E >= 1 && E <= kMaxExperts && block_n >= 1 && max_tiles >= 1 && sorted_route &&
+             perm_of_route && expert_offsets && tile_group && tile_row0 && tile_rows && num_tiles);
+  US_REQUIRE(x && xp && sync && (H % 8) == 0);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int ctas = (T * top_k + 3) / 4;
+  if (ctas < 8) ctas = 8;
+  if (ctas > 128) ctas = 128;
+  const int per = (E_all + 31) / 32;
+#define US_RSG_CASE(P)                                                                         \
+  if (per <= P) {                                                                              \
+    US_CUDA_CHECK(us::launch_pdl(route_sort_gather_kernel<P>, dim3(ctas), dim3(256), 0, stream,\
+                                 logits, ids, weights, T, E_all, top_k, renorm, live, e_lo, E, \
+                                 block_n, max_tiles, sorted_route, perm_of_route,              \
+                                 expert_offsets, tile_group, tile_row0, tile_rows, num_tiles,  \
+                                 (const __nv_bfloat16*)x, H, (__nv_bfloat16*)xp,               \
+                                 (unsigned int*)sync, us_status_ptr()));                       \
+    return US_OK;                                                                              \
+  }
+  US_RSG_CASE(1)
+  US_RSG_CASE(2)
+  US_RSG_CASE(4)
+  US_RSG_CASE(8)
+  US_RSG_CASE(16)
+  US_RSG_CASE(32)
+#undef US_RSG_CASE
   return US_ERR_ARG;
 }

@@ -65,13 +65,42 @@ extern "C" __attribute__((visibility("default"))) unsigned int* us_status_ptr() 
   return p;
 }
 
-// Reads the status word (synchronises the device) and clears it.
+// Reads the status word (synchronises the device) and clears it.  The block's other words
+// (the peer-wait budget at byte 8) stay.
 US_API int us_status_read(unsigned int* out) {
   unsigned int* p = us_status_ptr();
   US_REQUIRE(p != nullptr && out != nullptr);
   US_CUDA_CHECK(cudaDeviceSynchronize());
   US_CUDA_CHECK(cudaMemcpy(out, p, sizeof(unsigned int), cudaMemcpyDeviceToHost));
-  US_CUDA_CHECK(cudaMemset(p, 0, 64));
+  US_CUDA_CHECK(cudaMemset(p, 0, 8));
+  return US_OK;
+}
+
+// Stream-ordered copy of the status word into (pinned) host memory: the serving loop reads
+// it with the step's tokens, without a synchronisation of its own.
+US_API int us_status_copy_async(unsigned int* host_out, void* stream) {
+  unsigned int* p = us_status_ptr();
+  US_REQUIRE(p != nullptr && host_out != nullptr);
+  US_CUDA_CHECK(cudaMemcpyAsync(host_out, p, sizeof(unsigned int), cudaMemcpyDeviceToHost,
+                                (cudaStream_t)stream));
+  return US_OK;
+}
+
+// Stream-ordered clear of the status word (after a failed step was reported).
+US_API int us_status_clear_async(void* stream) {
+  unsigned int* p = us_status_ptr();
+  US_REQUIRE(p != nullptr);
+  US_CUDA_CHECK(cudaMemsetAsync(p, 0, 8, (cudaStream_t)stream));
+  return US_OK;
+}
+
+// Budget (SM clocks) of every wait on another GPU's flag on the current device; 0 restores
+// the default (about 1.5 s).  Takes effect for kernels launched after the call returns.
+US_API int us_set_peer_wait_clocks(long long clocks) {
+  unsigned int* p = us_status_ptr();
+  US_REQUIRE(p != nullptr && clocks >= 0);
+  US_CUDA_CHECK(cudaDeviceSynchronize());
+  US_CUDA_CHECK(cudaMemcpy(p + 2, &clocks, sizeof(clocks), cudaMemcpyHostToDevice));
   return US_OK;
 }
 

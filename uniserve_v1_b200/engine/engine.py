@@ -85,6 +85,7 @@ class LLMEngine:
         self.watchdog = Watchdog(watchdog_timeout)
         self._ids = itertools.count()
         self.failed: Optional[str] = None
+        self.health = None        # parallel.health.Heartbeat of a multi-rank deployment
         self.profiler = None      # engine.profiling.StepProfiler when profiling is on
         self.spec_stats = {"steps": 0, "proposed": 0, "accepted": 0}
 
@@ -140,6 +141,8 @@ class LLMEngine:
                 sampled, lps = self.runner.execute(batch)
         except Exception as e:     # fatal_worker_failure: stop the engine, fail every request
             self.failed = f"{ErrorClass.FATAL_WORKER_FAILURE.value}: {e}"
+            if self.health is not None:     # the peers learn of it before their next launch
+                self.health.report_failure(self.failed)
             raise
         finally:
             self.watchdog.end()

@@ -27,6 +27,18 @@ from .scheduler import Batch
 from .types import SamplingParams
 
 DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+# US_DECODE_MERGE=1 merges the decode attention's splits inside the attention kernel (the CTA
+# that arrives last); measured 4 us per layer slower than the second launch behind
+# programmatic dependent launch at 64 x 1024 keys, so the second launch is the default.
+DECODE_MERGE_IN_KERNEL = __import__("os").environ.get("US_DECODE_MERGE", "0") == "1"
+
+
+class DeviceStepError(RuntimeError):
+    """The device status word was set during a step (``code``: see ``ops.native.STATUS_NAMES``)."""
+
+    def __init__(self, code: int):
+        self.code = code
+        super().__init__(f"device status {code:#x}: {N.STATUS_NAMES.get(code, 'unknown')}")
 
 
 class InputBlock:
@@ -93,8 +105,12 @@ class CausalLmRunner:
         # Called before every forward with (kind, rows, count): the disaggregated layout
         # hooks its step announcer in here so expert ranks can join (parallel/join.py).
         self.announce = lambda kind, rows, count=1: None
+        self._scratch: dict = {}
+        self._status_host = None
         if self.device.type == "cuda":
             N.kernels().us_status_ptr()       # allocate the status word before any capture
+            from ..parallel import symm as _symm      # registers the status entry points
+            self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
 
     # ---------------------------------------------------------------- blocks --
     def _decode_block(self, B: int) -> InputBlock:
@@ -127,12 +143,19 @@ class CausalLmRunner:
         d = blk.d
         max_len = self.max_model_len
         splits = F.decode_splits(B, self.model.Hkv, max_len) if self.device.type == "cuda" else 1
+        scratch, counters = self._attn_scratch(B, splits)
         meta = AttnMeta(kind="decode", slots=d["slots"], page_table=d["page_table"],
-                        seq_lens=d["seq_lens"], splits=splits, live=d["live"])
+                        seq_lens=d["seq_lens"], splits=splits, live=d["live"], scratch=scratch,
+                        counters=counters)
         hidden = self.model.forward(d["input_ids"], d["positions"], meta, self.kv_caches)
-        logits = self.model.logits(hidden)
+        logits = None
+        if variant == "greedy" and hasattr(self.model, "greedy_tokens"):
+            sampled = self.model.greedy_tokens(hidden)      # sharded heads trade candidates only
+        else:
+            logits = self.model.logits(hidden)
         if variant == "greedy":
-            sampled = F.argmax(logits)
+            if logits is not None:
+                sampled = F.argmax(logits)
         elif variant == "sampled":
             if logits.is_cuda:
                 F.logits_shape_(logits, temp=d["temperature"])
@@ -150,6 +173,35 @@ class CausalLmRunner:
                           step=d["step"])
         d["sample_pos"].add_(1)
         return logits, sampled
+
+    def _attn_scratch(self, B: int, splits: int):
+        """Split-KV partials and arrival counters of the decode attention, one pair per
+        (bucket, splits), shared by every layer (allocated outside any capture)."""
+        m = self.model
+        if self.device.type != "cuda" or splits <= 1 or m.D != 128:
+            return None, None
+        key = (B, splits)
+        got = self._scratch.get(key)
+        if got is None:
+            got = F.decode_scratch(B, m.Hq, m.Hkv, m.D, splits, self.device)
+            if not DECODE_MERGE_IN_KERNEL:
+                got = (got[0], None)
+            self._scratch[key] = got
+        return got
+
+    def check_device_status(self) -> None:
+        """Raises when the status word copied behind the step's results is set: a bounded
+        device wait ran out (a peer more than the budget late, or gone), so the step's
+        tokens are not to be trusted.  The word is cleared so the next engine starts clean."""
+        code = int(self._status_host[0]) if self._status_host is not None else 0
+        if code:
+            self._status_host[0] = 0
+            N.kernels().us_status_clear_async(N.stream())
+            raise DeviceStepError(code)
+
+    def _queue_status_copy(self) -> None:
+        if self._status_host is not None:
+            N.kernels().us_status_copy_async(N.ptr(self._status_host), N.stream())
 
     def _graph(self, B: int, variant: str) -> Optional[DecodeGraph]:
         if not self.use_graphs:
@@ -338,8 +390,10 @@ class CausalLmRunner:
             # one D2H copy of the step results into a fixed pinned buffer
             host = blk.readback[:steps]
             host.copy_(blk.history[:steps], non_blocking=True)
+            self._queue_status_copy()          # read with the tokens, no extra synchronisation
             torch.cuda.current_stream().synchronize()
-            self.d2h_bytes += steps * n * 4
+            self.check_device_status()
+            self.d2h_bytes += steps * n * 4 + 4
             out = host[:, :n]
         else:
             out = blk.history[:steps, :n].clone()
@@ -348,7 +402,9 @@ class CausalLmRunner:
     def _to_host(self, t: torch.Tensor) -> torch.Tensor:
         host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
         host.copy_(t, non_blocking=True)
+        self._queue_status_copy()
         torch.cuda.current_stream().synchronize()
+        self.check_device_status()
         self.d2h_bytes += host.numel() * host.element_size()
         return host
 
@@ -438,9 +494,10 @@ class CausalLmRunner:
                     k = r.params.top_logprobs
                     tops = [(int(top[1][i, j]), float(top[0][i, j])) for j in range(k)]
                 info[r.request_id] = (float(lp_c[i]), int(rank_c[i]), tops)
-        host = sampled.cpu()
         if dev.type == "cuda":
-            self.d2h_bytes += host.numel() * 4
+            host = self._to_host(sampled)
+        else:
+            host = sampled.cpu()
         return host, info
 
     # --------------------------------------------------------------- prefill --

@@ -103,9 +103,16 @@ class Qwen3MoeConfig:
 
 import os as _os
 
-# Routing and route sort in one launch: measured 8 us per layer slower than the two
-# kernels at 64 tokens (one CTA routes every token), so it is opt-in.
+# Routing and route sort in one launch by one CTA: measured 8 us per layer slower than the
+# two kernels at 64 tokens (one CTA routes every token), so it is opt-in.
 FUSED_ROUTE_SORT = _os.environ.get("US_ROUTE_SORT", "0") == "1"
+# Routing, route sort and row gather in one launch over many CTAs (decode-size batches):
+# its two grid-wide waits cost more than the two launches they save behind programmatic
+# dependent launch (measured +5 us per layer at 64 tokens), so it is opt-in (US_ROUTE_FUSED=1).
+# The weighted un-permute is folded into the norm (or the fused all-reduce) that follows the
+# experts; US_UNPERMUTE_FUSED=0 is the A/B switch.
+FUSED_ROUTE_GATHER = _os.environ.get("US_ROUTE_FUSED", "0") == "1"
+FUSED_UNPERMUTE = _os.environ.get("US_UNPERMUTE_FUSED", "1") == "1"
 
 
 @dataclass
@@ -132,6 +139,7 @@ class AttnMeta:
     seq_lens: Optional[torch.Tensor] = None     # [B] int32 keys to attend (incl. this step)
     splits: int = 1
     scratch: Optional[torch.Tensor] = None
+    counters: Optional[torch.Tensor] = None     # arrival counters: splits merged in-kernel
     cu_q: Optional[torch.Tensor] = None         # [n+1] int32
     cu_k: Optional[torch.Tensor] = None
     max_q: int = 0
@@ -363,22 +371,27 @@ class Qwen3MoeModel:
             return fc
         return None
 
-    def _partial_out(self, fc, T: int):
-        """(site, buffer) for a row-parallel output whose sum is still pending."""
-        if fc is None:
-            return None, None
-        site = fc.next_site()
-        return site, fc.site_tensor(site, T, self.cfg.hidden_size)
-
-    def _reduce_norm(self, fc, h, site, residual, w):
+    def _reduce_norm(self, fc, h, pending, residual, w):
         """residual += sum over ranks of h;  returns (rmsnorm(residual) * w, residual).
-        With a pending site the sum, the residual add and the norm are one kernel."""
-        if site is None:
-            return F.add_rmsnorm(h, residual, w, self.cfg.rms_norm_eps)
-        if isinstance(site, tuple):         # pending expert-parallel combine
-            return self.exchange.combine_add_rmsnorm(site[1], getattr(self, "_live", None),
-                                                     residual, w, self.cfg.rms_norm_eps)
-        return fc.allreduce_add_rmsnorm(site, h.shape[0], residual, w, self.cfg.rms_norm_eps)
+        ``pending`` says what is still owed to ``h``: nothing (None), the tensor group's sum
+        ("sum": push-form all-reduce, residual add and norm in one kernel), the expert
+        exchange's combine ("ep"), or the weighted un-permute of the local expert rows
+        ("routed": folded into the norm kernel, or into the fused all-reduce when the
+        experts are spread over the group)."""
+        eps = self.cfg.rms_norm_eps
+        if pending is None:
+            return F.add_rmsnorm(h, residual, w, eps)
+        kind = pending[0]
+        if kind == "ep":            # pending expert-parallel combine
+            return self.exchange.combine_add_rmsnorm(pending[1], getattr(self, "_live", None),
+                                                     residual, w, eps)
+        if kind == "routed":
+            _, y_perm, perm, weights, reduce = pending
+            if reduce:
+                return fc.allreduce_add_rmsnorm(None, residual, w, eps,
+                                                routed=(y_perm, perm, weights))
+            return F.unpermute_add_rmsnorm(y_perm, perm, weights, residual, w, eps)
+        return fc.allreduce_add_rmsnorm(h, residual, w, eps)
 
     def _attention(self, fc, lw: LayerWeights, x, positions, meta: AttnMeta, kcache, vcache):
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
@@ -390,15 +403,15 @@ class Qwen3MoeModel:
             q = qkv[:, :Hq * D] if qkv.is_cuda else qkv[:, :Hq * D].reshape(T, Hq, D)
             att = F.paged_decode_attention(q, kcache, vcache, meta.page_table, meta.seq_lens,
                                            self.scale, meta.splits, self.cfg.sliding_window,
-                                           scratch=meta.scratch, Hq=Hq, D=D)
+                                           scratch=meta.scratch, Hq=Hq, D=D,
+                                           counters=meta.counters)
         else:
             from ..ops.attention import prefill_attention
             att = prefill_attention(qkv, Hq, Hkv, D, meta, kcache, vcache, self.scale)
-        site, buf = self._partial_out(fc, T)
-        out = F.linear(att.reshape(T, Hq * D), lw.o_proj, out=buf)
-        if site is None:
-            out = self.ctx.all_reduce_tp(out)
-        return out, site
+        out = F.linear(att.reshape(T, Hq * D), lw.o_proj)
+        if fc is not None:
+            return out, ("sum",)
+        return self.ctx.all_reduce_tp(out), None
 
     def _quantize_experts(self, lw: LayerWeights) -> None:
         """``expert_quant == "fp8_block"``: the stacked expert weights are replaced by
@@ -409,16 +422,17 @@ class Qwen3MoeModel:
         lw.fp8 = Fp8Experts.from_bf16(lw.w13, lw.w2)
         lw.w13 = lw.w2 = None
 
-    def _mlp(self, fc, lw: LayerWeights, x):
+    def _mlp(self, fc, lw: LayerWeights, x, defer: bool = True):
+        """Returns (hidden, pending); see ``_reduce_norm``.  ``defer=False`` returns finished
+        rows (no pending un-permute) for callers that use them without a norm."""
         cfg = self.cfg
         T = x.shape[0]
         if lw.dense:
             h = F.linear_gated(x, lw.w13[0])
-            site, buf = self._partial_out(fc, T)
-            out = F.linear(h, lw.w2[0], out=buf)
-            if site is None:
-                out = self.ctx.all_reduce_tp(out)
-            return out, site
+            out = F.linear(h, lw.w2[0])
+            if fc is not None:
+                return out, ("sum",)
+            return self.ctx.all_reduce_tp(out), None
         logits = F.linear(x, lw.router, out_dtype=torch.float32)
         if self.exchange is not None and x.is_cuda:
             live = getattr(self, "_live", None)
@@ -437,30 +451,44 @@ class Qwen3MoeModel:
             ws = self._moe_ws.get(key)
             if ws is None:
                 ws = F.MoeWorkspace.create(T, cfg.num_experts_per_tok, self.E_local,
-                                           cfg.hidden_size, cfg.moe_intermediate_size, x.device)
+                                           cfg.hidden_size, cfg.moe_intermediate_size, x.device,
+                                           E_total=cfg.num_experts)
                 self._moe_ws[key] = ws
-        # decode-size batches route and sort in one launch
-        presorted = x.is_cuda and T <= 512 and lw.fp8 is None and FUSED_ROUTE_SORT
-        if presorted:
+        reduce = self.ctx.ep_size > 1
+        small = x.is_cuda and T <= 512 and lw.fp8 is None
+        # decode-size batches: route, sort and gather in one launch; the un-permute rides on
+        # the norm (or the fused all-reduce) that follows
+        fused_route = small and FUSED_ROUTE_GATHER and self.E_local > 0
+        presorted = small and FUSED_ROUTE_SORT and not fused_route
+        if fused_route:
+            ids, weights = F.route_sort_gather(logits, x, cfg.num_experts_per_tok,
+                                               cfg.norm_topk_prob, ws, self.e_lo, self.E_local,
+                                               live=getattr(self, "_live", None))
+        elif presorted:
             ids, weights = F.route_and_sort(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob,
                                             ws, self.e_lo, self.E_local)
         else:
             ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
-        reduce = self.ctx.ep_size > 1
-        site, buf = self._partial_out(fc if reduce else None, T)
         if lw.fp8 is not None:
             from ..ops.fp8 import moe_experts_fp8
             if ws is not None and ws.block_n > 64:
                 ws = self._moe_ws[key] = F.MoeWorkspace.create(
                     T, cfg.num_experts_per_tok, self.E_local, cfg.hidden_size,
                     cfg.moe_intermediate_size, x.device, block_n=64)
-            out = moe_experts_fp8(x, ids, weights, lw.fp8, e_lo=self.e_lo, ws=ws, out=buf)
+            out = moe_experts_fp8(x, ids, weights, lw.fp8, e_lo=self.e_lo, ws=ws)
         else:
-            out = F.moe_experts(x, ids, weights, lw.w13, lw.w2, e_lo=self.e_lo, ws=ws, out=buf,
-                                presorted=presorted)
-        if reduce and site is None:
+            later = defer and small and FUSED_UNPERMUTE and (fc is not None or not reduce)
+            out = F.moe_experts(x, ids, weights, lw.w13, lw.w2, e_lo=self.e_lo, ws=ws,
+                                presorted=presorted, pregathered=fused_route,
+                                defer_unpermute=later)
+            if later:
+                y_perm, perm = out
+                return y_perm, ("routed", y_perm, perm, weights, reduce and fc is not None)
+        if reduce:
+            if fc is not None:
+                return out, ("sum",)
             out = self.ctx.all_reduce_tp(out)
-        return out, site
+        return out, None
 
     def forward(self, input_ids, positions, meta: AttnMeta, kv_caches) -> torch.Tensor:
         """Returns the final-normed hidden rows [T, H] (bf16).
@@ -481,7 +509,7 @@ class Qwen3MoeModel:
             kc, vc = kv_caches[i]
             mixed, site = self._attention(fc, lw, x, positions, meta, kc, vc)
             x, residual = self._reduce_norm(fc, mixed, site, residual, lw.post_norm)
-            hidden, site = self._mlp(fc, lw, x)
+            hidden, site = self._mlp(fc, lw, x, defer=self.pp == 1)
         if self.pp == 1:
             x, _ = self._reduce_norm(fc, hidden, site, residual, self.final_norm)
             return x
@@ -518,7 +546,7 @@ class Qwen3MoeModel:
             x, residual = self._reduce_norm(None, hidden, None, residual, lw.input_norm)
             mixed, _ = self._attention(None, lw, x, pos, meta, kc, kc)
             x, residual = self._reduce_norm(None, mixed, None, residual, lw.post_norm)
-            hidden, _ = self._mlp(None, lw, x)
+            hidden, _ = self._mlp(None, lw, x, defer=False)
         return residual.float() + hidden.float()
 
     # ------------------------------------------------------------ pipeline --
@@ -554,6 +582,18 @@ class Qwen3MoeModel:
                 self.exchange.experts_fp8(lw.fp8, t_step)
             else:
                 self.exchange.experts(lw.w13, lw.w2, t_step)
+
+    def greedy_tokens(self, hidden_rows: torch.Tensor) -> torch.Tensor:
+        """arg-max token of every row, int32 [rows], the same on every rank.  With a
+        vocabulary-sharded head and a peer heap only (value, column) pairs cross NVLink
+        (one kernel: local arg-max, push, pick); the logits are never gathered."""
+        lg = F.linear(hidden_rows, self.lm_head, out_dtype=torch.float32)
+        if self.ctx.tp_size > 1:
+            fc = self.ctx.fused
+            if fc is not None and lg.is_cuda and lg.shape[0] <= fc.max_rows:
+                return fc.argmax(lg, self.vocab_hi - self.vocab_lo, self.vocab_lo)
+            lg = self.ctx.all_gather_tp_cols(lg)[:, :self.cfg.vocab_size]
+        return F.argmax(lg)
 
     def logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
         """FP32 logits [rows, vocab]; vocab-sharded heads are all-gathered and un-padded."""

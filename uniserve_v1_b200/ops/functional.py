@@ -154,10 +154,20 @@ def decode_splits(B: int, Hkv: int, max_len: int, sm_count: int = 148) -> int:
     return int(max(1, min(want, by_len, 32)))
 
 
+def decode_scratch(B: int, Hq: int, Hkv: int, D: int, splits: int, device):
+    """(scratch bytes, arrival counters) for ``paged_decode_attention`` with its splits
+    merged inside the kernel.  The counters start at zero and every call leaves them zero,
+    so one pair serves every layer of a forward pass (calls ordered on the device)."""
+    nbytes = N.kernels().us_paged_decode_scratch_bytes(B, Hq, D, max(1, splits))
+    return (torch.empty(nbytes, dtype=torch.uint8, device=device),
+            torch.zeros(B * Hkv, dtype=torch.int32, device=device))
+
+
 def paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, splits=1, window=0,
-                           out=None, scratch=None, Hq=None, D=None):
+                           out=None, scratch=None, Hq=None, D=None, counters=None):
     """q: [B, Hq, D] (or a [B, >=Hq*D] row-strided view with Hq, D given);
-    caches [pages, page_size, Hkv, D]; returns [B, Hq, D] bf16."""
+    caches [pages, page_size, Hkv, D]; returns [B, Hq, D] bf16.  With ``counters`` (from
+    ``decode_scratch``) the split merge happens inside the attention kernel."""
     if not _cuda(q):
         return R.paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, window)
     if q.dim() == 3:
@@ -175,6 +185,12 @@ def paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, split
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     if D == 128 and 128 % page_size == 0 and Hq // Hkv <= 16 and not DECODE_SIMT:
         # keys-on-M tcgen05 kernel
+        if counters is not None:
+            N.call("us_paged_decode_attention_tc_merged", N.ptr(q), N.ptr(kcache), N.ptr(vcache),
+                   N.ptr(page_table), N.ptr(seq_lens), N.ptr(out), N.ptr(scratch),
+                   N.ptr(counters), B, Hq, Hkv, D, pages, page_table.shape[1], page_size, splits,
+                   window, scale, ldq, ldo, N.stream())
+            return out
         N.call("us_paged_decode_attention_tc", N.ptr(q), N.ptr(kcache), N.ptr(vcache),
                N.ptr(page_table), N.ptr(seq_lens), N.ptr(out), N.ptr(scratch), B, Hq, Hkv, D,
                pages, page_table.shape[1], page_size, splits, window, scale, ldq, ldo,
@@ -279,9 +295,13 @@ class MoeWorkspace:
     y: torch.Tensor       # [R, H]
     block_n: int
     max_tiles: int
+    sync: Optional[torch.Tensor] = None   # grid-wide counters of the fused route kernel
+    live_tiles: int = 0                   # expected number of non-empty row tiles
 
     @staticmethod
-    def create(T, top_k, E_local, H, I, device, block_n=None):
+    def create(T, top_k, E_local, H, I, device, block_n=None, E_total=None):
+        """``E_total``: experts of the whole model when this rank holds only ``E_local`` of
+        them (the routes then spread over all ranks; sizes the expected live tiles)."""
         R_ = T * top_k
         if block_n is None:
             avg = max(1, R_ // max(1, E_local))
@@ -296,7 +316,16 @@ class MoeWorkspace:
             xp=torch.zeros(R_ + 256, H, dtype=BF16, device=device)[:R_],
             h=torch.zeros(R_ + 256, I, dtype=BF16, device=device)[:R_],
             y=torch.empty(R_, H, dtype=BF16, device=device),
-            block_n=block_n, max_tiles=max_tiles)
+            block_n=block_n, max_tiles=max_tiles, sync=torch.zeros(4, **i32),
+            live_tiles=MoeWorkspace._expected_tiles(R_, E_local, E_total or E_local, block_n))
+
+    @staticmethod
+    def _expected_tiles(R_, E_local, E_total, block_n) -> int:
+        if E_local <= 0:
+            return 0
+        per = R_ / max(1, E_total)                        # mean routes per expert
+        hit = E_local * (1.0 - math.exp(-per))            # experts with at least one route
+        return max(1, int(math.ceil(hit + E_local * per / block_n)))
 
 
 def route_and_sort(logits, top_k, renorm, ws, e_lo, E_local):
@@ -312,11 +341,42 @@ def route_and_sort(logits, top_k, renorm, ws, e_lo, E_local):
     return ids, weights
 
 
+def route_sort_gather(logits, x, top_k, renorm, ws, e_lo, E_local, live=None):
+    """``topk_softmax``, the route sort and the row gather of ``moe_experts`` in one launch
+    (at most 512 tokens); pass the workspace on with ``moe_experts(..., pregathered=True)``."""
+    T, E_all = logits.shape
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    weights = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    N.call("us_route_sort_gather", N.ptr(logits), N.ptr(ids), N.ptr(weights), T, E_all, top_k,
+           int(renorm), N.ptr(live), e_lo, E_local, ws.block_n, ws.max_tiles,
+           N.ptr(ws.sorted_route), N.ptr(ws.perm_of_route), N.ptr(ws.expert_offsets),
+           N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows), N.ptr(ws.num_tiles),
+           N.ptr(x), x.shape[1], N.ptr(ws.xp), N.ptr(ws.sync), N.stream())
+    return ids, weights
+
+
+def unpermute_add_rmsnorm(y_perm, perm, weights, residual, w, eps=1e-6):
+    """The weighted un-permute of the expert rows, the residual add and the RMSNorm of the
+    next block in one launch: returns (normed bf16 [T, H], FP32 residual)."""
+    T, top_k = perm.shape
+    H = w.shape[0]
+    first = residual is None
+    if first:
+        residual = torch.empty(T, H, dtype=torch.float32, device=y_perm.device)
+    y = torch.empty(T, H, dtype=BF16, device=y_perm.device)
+    N.call("us_unpermute_add_rmsnorm", N.ptr(y_perm), N.ptr(perm), N.ptr(weights), T, top_k, H,
+           N.ptr(residual), N.ptr(w), N.ptr(y), eps, int(first), N.stream())
+    return y, residual
+
+
 def moe_experts(x, ids, weights, w13, w2, e_lo=0, act="silu", stepwise=False, ws=None, out=None,
-                presorted=False):
+                presorted=False, pregathered=False, defer_unpermute=False):
     """Routed experts: sort routes by local expert, gather rows, grouped FC1 with
     the gated activation fused, grouped FC2, weighted un-permute (FP32, one
-    rounding).  w13 [E,2I,H] (first/up rows, then gate rows), w2 [E,H,I]."""
+    rounding).  w13 [E,2I,H] (first/up rows, then gate rows), w2 [E,H,I].
+    ``pregathered``: ``route_sort_gather`` already filled the workspace.
+    ``defer_unpermute``: returns (expert rows [R, H], perm [T, top_k]) for a consumer that
+    forms the weighted sum itself (``unpermute_add_rmsnorm``, the fused all-reduce)."""
     if not _cuda(x):
         return R.moe_experts(x, ids, weights, w13, w2, e_lo, act, stepwise)
     T, H = x.shape
@@ -327,23 +387,31 @@ def moe_experts(x, ids, weights, w13, w2, e_lo=0, act="silu", stepwise=False, ws
         ws = MoeWorkspace.create(T, top_k, E, H, I_, x.device)
     R_ = T * top_k
     st = N.stream()
-    if not presorted:
+    if not presorted and not pregathered:
         N.call("us_moe_sort", N.ptr(ids), R_, e_lo, E, ws.block_n, ws.max_tiles,
                N.ptr(ws.sorted_route), N.ptr(ws.perm_of_route), N.ptr(ws.expert_offsets),
                N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
                N.ptr(ws.num_tiles), st)
-    total = ws.expert_offsets[E:]
-    N.call("us_moe_gather", N.ptr(x), N.ptr(ws.sorted_route), N.ptr(total), R_, top_k, H,
-           N.ptr(ws.xp), st)
+    if not pregathered:
+        total = ws.expert_offsets[E:]
+        N.call("us_moe_gather", N.ptr(x), N.ptr(ws.sorted_route), N.ptr(total), R_, top_k, H,
+               N.ptr(ws.xp), st)
     code = _ACT["silu_stepwise" if (act == "silu" and stepwise) else act]
     # FC1: [R, H] x [E, 2I, H] -> [R, I] with first * act(gate)
+    live = ws.live_tiles
+    if live:
+        N.kernels().us_gemm_wx_hint(live * ((I_ + 127) // 128))
     N.call("us_gemm_wx", N.ptr(w13), N.ptr(ws.xp), N.ptr(ws.h), E, I2, I_, H, R_, H, H, I_, 1, I_,
            code, 0, None, 0, None, None, N.ptr(ws.tile_group), N.ptr(ws.tile_row0),
            N.ptr(ws.tile_rows), N.ptr(ws.num_tiles), ws.max_tiles, ws.block_n, st)
     # FC2: [R, I] x [E, H, I] -> [R, H]
+    if live:
+        N.kernels().us_gemm_wx_hint(live * ((H + 127) // 128))
     N.call("us_gemm_wx", N.ptr(w2), N.ptr(ws.h), N.ptr(ws.y), E, H, H, I_, R_, I_, I_, H, 0, 0, 0,
            0, None, 0, None, None, N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
            N.ptr(ws.num_tiles), ws.max_tiles, ws.block_n, st)
+    if defer_unpermute:
+        return ws.y, ws.perm_of_route.view(T, top_k)
     if out is None:
         out = torch.empty(T, H, dtype=BF16, device=x.device)
     N.call("us_moe_unpermute", N.ptr(ws.y), N.ptr(ws.perm_of_route), N.ptr(weights), T, top_k, H,

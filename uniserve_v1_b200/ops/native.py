@@ -38,6 +38,7 @@ _SIGNATURES = {
     "us_status_read": (I, [P]),
     "us_device_info": (I, [P, P, P, P]),
     "us_gemm_wx": (I, [P, P, P, I, I, I, I, I, L, L, L, I, I, I, I, P, I, P, P, P, P, P, P, I, I, P]),
+    "us_gemm_wx_hint": (I, [I]),
     "us_rmsnorm": (I, [P, P, P, I, I, L, L, F, P]),
     "us_add_rmsnorm": (I, [P, P, P, P, I, I, F, I, P]),
     "us_modulated_rmsnorm": (I, [P, P, P, P, I, I, I, P, I, I, F, P]),
@@ -49,6 +50,11 @@ _SIGNATURES = {
     "us_paged_decode_scratch_bytes": (L, [I, I, I, I]),
     "us_paged_decode_attention": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, L, L, P]),
     "us_paged_decode_attention_tc": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, L, L, P]),
+    "us_paged_decode_attention_tc_merged": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F,
+                                            L, L, P]),
+    "us_unpermute_add_rmsnorm": (I, [P, P, P, I, I, I, P, P, P, F, I, P]),
+    "us_route_sort_gather": (I, [P, P, P, I, I, I, I, P, I, I, I, I, P, P, P, P, P, P, P, P, I, P,
+                                 P, P]),
     "us_topk_softmax": (I, [P, P, P, I, I, I, I, P, P, P, P]),
     "us_moe_sort": (I, [P, I, I, I, I, I, P, P, P, P, P, P, P, P]),
     "us_route_sort": (I, [P, P, P, I, I, I, I, P, I, I, I, I, P, P, P, P, P, P, P, P]),
@@ -174,6 +180,7 @@ STATUS_NAMES = {
     0x300: "timeout waiting for the accumulator",
     0x400: "timeout waiting for a peer flag",
     0x500: "index outside its table",
+    0x600: "timeout waiting for another CTA of the grid",
 }
 
 

@@ -55,7 +55,7 @@ class FusedTP:
         self.P, self.rank, self.H = world, rank, hidden
         self.rows, self.ro = rows_all, rows_all // world
         self.bn = _row_block(self.ro)
-        self.fc = FusedComm(group, rank, world, device, hidden=0, sites=5,
+        self.fc = FusedComm(group, rank, world, device, hidden=0, sites=7,
                             site_bytes=world * self.ro * hidden * 2)
         self._ptrs = {}
 

@@ -44,7 +44,7 @@ class FusedUlysses:
         self.P, self.rank = ax.size, ax.rank
         self.W = 3 * heads_local * head_dim
         site_bytes = rows_all * self.W * 2
-        self.fc = FusedComm(ax.group, ax.rank, ax.size, device, hidden=0, sites=4,
+        self.fc = FusedComm(ax.group, ax.rank, ax.size, device, hidden=0, sites=6,
                             site_bytes=site_bytes)
         self.rows_all = rows_all
         self._ptr_arrays = {}

@@ -53,7 +53,10 @@ def timeit(fn, iters=10, warmup=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["flash", "gemm", "gated", "decode", "moe", "fused-norm",
-                                   "ulysses", "tp", "moe-fp8", "gemm-fp8", "gemm-fp8t", "ep"])
+                                   "ulysses", "tp", "moe-fp8", "gemm-fp8", "gemm-fp8t", "ep",
+                                   "rank-decode"])
+    ap.add_argument("--tp", type=int, default=8, help="rank-decode: ranks of the emulated layout")
+    ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=2048)
@@ -81,6 +84,62 @@ def main():
                                               out=o), a.iters)
         flops = 4.0 * T * T * D * H * (0.5 if a.causal else 1.0)
         out.update(rows=T, heads=H, ms=ms, tflops=flops / ms / 1e9, frac=flops / ms / 1e9 / tfl)
+    elif a.op == "rank-decode":
+        # One rank's share of a tensor-parallel + whole-experts decode step, alone on one GPU:
+        # the model is built as rank 0 of `--tp` ranks over a detached context whose
+        # collectives are local stand-ins (results are meaningless, kernel shapes are the
+        # rank's), so the per-rank compute floor of the N-GPU step can be timed and profiled
+        # without peers.  --layers cuts the depth; ms_per_layer is what scales.
+        from ..engine.engine import LLMEngine
+        from ..engine.types import SamplingParams
+        from ..models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+        from ..parallel.context import Axis, ParallelContext
+
+        class Detached(ParallelContext):
+            def all_reduce(self, x, axis="tensor"):
+                return x
+
+            def all_gather_tp_cols(self, x):
+                return x.repeat(1, self.tp_size)
+
+        P = a.tp
+        ctx = Detached(world_rank=0, world_size=P)
+        ctx.axes["tensor"] = Axis(None, 0, P, tuple(range(P)))
+        ctx.axes["expert"] = ctx.axes["tensor"]
+        ctx.expert_parallel = True
+        cfg = Qwen3MoeConfig.qwen3_30b_a3b()
+        cfg.num_hidden_layers = a.layers
+        model = Qwen3MoeModel(cfg, dev, bf, ctx).init_random(seed=0)
+        eng = LLMEngine(model, max_num_seqs=a.batch, max_model_len=a.ctx + 64,
+                        enable_prefix_cache=False)
+        gp = torch.Generator().manual_seed(1)
+        sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+        for _ in range(a.batch):
+            eng.add_request(torch.randint(0, cfg.vocab_size, (a.ctx,), generator=gp).tolist(), sp)
+        while eng.scheduler.waiting or any(not r.output_ids for r in eng.scheduler.running):
+            eng.step()
+        rows = list(eng.scheduler.running)
+        for r in rows:
+            r.pages.extend(eng.blocks.allocate(eng.scheduler._pages_needed(r, r.num_tokens + 40)))
+        runner = eng.runner
+        B = runner.bucket_for(len(rows))
+        blk = runner._decode_block(B)
+        runner._fill_decode(blk, rows, B)
+        graph = runner._graph(B, "greedy")
+        blk.upload()
+        for _ in range(3):
+            graph.graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.iters):
+            graph.graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / a.iters
+        out.update(tp=P, layers=a.layers, batch=a.batch, ctx=a.ctx, ms_per_step=ms,
+                   launches=graph.launches, ms_per_layer=ms / a.layers,
+                   note="includes embedding, head and sampling once per step")
     elif a.op in ("gemm", "gated"):
         x = rnd(a.rows, a.k)
         w = rnd(a.m * (2 if a.op == "gated" else 1), a.k)
@@ -177,19 +236,14 @@ def main():
     elif a.op == "fused-norm":
         # all-reduce + residual + RMSNorm over the peer heap; one rank (its own peer) so a
         # profiler can attach; the 2/8-rank numbers come from bench.py
+        from ..ops import native as N_
         from ..parallel.symm import FusedComm
         T, H = a.batch, a.hidden
         fc = FusedComm(None, 0, 1, dev, H, sites=4)
         w = torch.ones(H, dtype=bf, device=dev)
-        fc.site_tensor(0, T, H).copy_(rnd(T, H))
+        part = rnd(T, H)
         res = torch.zeros(T, H, dtype=torch.float32, device=dev)
-
-        def run():
-            N_.call("us_allreduce_add_rmsnorm", 0, N_.ptr(res), N_.ptr(w), N_.ptr(y), T, H, 1e-6, 0,
-                    N_.stream())
-        from ..ops import native as N_
-        y = torch.empty(T, H, dtype=bf, device=dev)
-        ms = timeit(run, a.iters)
+        ms = timeit(lambda: fc.allreduce_add_rmsnorm(part, res, w, 1e-6), a.iters)
         out.update(rows=T, hidden=H, ms=ms)
     elif a.op == "ulysses":
         # the two fused GEMMs of the Ulysses block with this rank as its own peer:
@@ -243,7 +297,9 @@ def main():
         pt = (torch.randperm(pages - 1, device=dev)[:B * per].view(B, per) + 1).to(torch.int32)
         sl = torch.full((B,), a.ctx, dtype=torch.int32, device=dev)
         splits = F.decode_splits(B, Hkv, a.ctx)
-        ms = timeit(lambda: F.paged_decode_attention(q, kc, vc, pt, sl, 1 / math.sqrt(D), splits),
+        scratch, counters = F.decode_scratch(B, Hq, Hkv, D, splits, dev)
+        ms = timeit(lambda: F.paged_decode_attention(q, kc, vc, pt, sl, 1 / math.sqrt(D), splits,
+                                                     scratch=scratch, counters=counters),
                     a.iters)
         byts = 2.0 * B * a.ctx * Hkv * D * 2
         out.update(batch=B, ctx=a.ctx, splits=splits, ms=ms, tbs=byts / ms / 1e9,
