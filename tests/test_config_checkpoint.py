@@ -265,3 +265,21 @@ def test_reference_deployment_examples_resolve_to_axes():
     assert seen["minimax_h3/gather8"] == {"world": 8, "axes": {"gather": 8}}
     assert seen["minimax_h3/fasth3-ulysses4x2"] == {"world": 4, "axes": {"ulysses": 4}}
     assert len(seen) >= 10
+
+
+def test_reference_afd_package_resolves_to_an_expert_union():
+    """The reference's disaggregated deployment (a TP2 attention group and two expert
+    ranks) resolves to a union of two attention members and two experts-only ranks; its
+    tensor-parallel deployment does not."""
+    import os
+    import pytest
+    from uniserve_v1_b200.config.policy import Package
+    from uniserve_v1_b200.server import multirank as MR
+    root = "/root/reference/configs"
+    if not os.path.isdir(root):
+        pytest.skip("reference configs not present")
+    afd = Package.load(os.path.join(root, "afd/qwen3_moe"))
+    assert MR.package_union(afd) == {"sources": 2, "experts": 2, "shared": False}
+    assert MR.package_world(afd) == 4
+    tp4 = Package.load(os.path.join(root, "qwen3_moe/tp4"))
+    assert MR.package_union(tp4) is None and MR.package_world(tp4) == 4

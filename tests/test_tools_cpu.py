@@ -106,9 +106,22 @@ def test_profile_session_and_trace(tmp_path):
     assert {e["tid"] for e in tr["traceEvents"]} >= {"device"}
 
 
-def test_serve_command_runs_a_two_rank_deployment(tmp_path):
-    """`serve` with tensor_parallel_size = 2 starts the second rank itself (gloo ranks on
-    CPU here), and the deployment answers like a single-rank one."""
+_LAYOUTS = {
+    "tp2": "tensor_parallel_size = 2\n",
+    # data-parallel attention + expert parallelism: two members, each with half the experts
+    "dp_ep2": "data_parallel_size = 2\n[moe_config]\nexpert_parallel = true\n",
+    # attention / expert disaggregation: two attention members, one experts-only rank
+    "afd": '[moe_config]\nexpert_parallel = true\n[[worker_groups]]\nid = "attention"\n'
+           'ranks = ["cuda:0-1"]\n[[worker_groups]]\nid = "experts"\nrole = "experts"\n'
+           'ranks = ["cuda:2"]\n',
+}
+
+
+@pytest.mark.parametrize("layout", ["tp2", "dp_ep2", "afd"])
+def test_serve_command_runs_a_two_rank_deployment(tmp_path, layout):
+    """`serve` starts the other ranks of the package's layout itself (gloo ranks on CPU
+    here) - a tensor-parallel pair, an expert union of two members, or two attention members
+    with an experts-only rank - and the deployment answers like a single-rank one."""
     import json
     import os
     import subprocess
@@ -117,9 +130,11 @@ def test_serve_command_runs_a_two_rank_deployment(tmp_path):
     port = _free_port()
     pkg = tmp_path / "pkg"
     pkg.mkdir()
-    (pkg / "config.toml").write_text(
-        'model = "random:tiny"\nserved_model_name = "tiny"\ntensor_parallel_size = 2\n'
-        f'[admin_config]\nhost = "127.0.0.1"\nport = {port}\n')
+    head = 'model = "random:tiny"\nserved_model_name = "tiny"\n'
+    admin = f'[admin_config]\nhost = "127.0.0.1"\nport = {port}\n'
+    body_toml = _LAYOUTS[layout]
+    (pkg / "config.toml").write_text(head + (body_toml + admin if not body_toml.startswith("[")
+                                             else admin + body_toml))
     env = dict(os.environ, UNISERVE_CPU_RANKS="1")
     env.pop("RANK", None)
     proc = subprocess.Popen([sys.executable, "-m", "uniserve_v1_b200", "serve", str(pkg)], env=env,

@@ -31,6 +31,9 @@ def serve(args) -> int:
     # itself (or joins a job started by a launcher that set RANK / WORLD_SIZE).
     par = MR.package_parallelism(pkg)
     want, axes = par["world"], par["axes"]
+    union = MR.package_union(pkg)
+    if union:
+        want, axes = MR.package_world(pkg), {}
     cpu_ranks = os.environ.get("UNISERVE_CPU_RANKS", "0") == "1"     # gloo ranks, for tests
     children = []
     if want > 1 and "RANK" not in os.environ:
@@ -171,6 +174,61 @@ def serve(args) -> int:
             drafter = HybridMtpDrafter(HybridMtp(model).load_state(ld), k=k_draft)
         app = create_app(package=pkg, engine=make_engine(), tokenizer=tok,
                          served_model_name=name, engine_factory=make_engine, drafter=drafter)
+    elif union and world > 1:
+        # expert union: every attention member owns a scheduler and its requests, every MoE
+        # layer is a lock-step exchange, steps are agreed over the control group
+        from .engine.engine import LLMEngine
+        from .engine.union import UnionFront, UnionMember, member_loop
+        from .models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+        from .server.tokenizer import load_tokenizer
+        n_src = union["sources"]
+        sources = tuple(range(n_src))
+        experts = sources if union["shared"] else tuple(range(n_src, world))
+        ctx = ParallelContext(world_rank=rank, world_size=world)
+        ctx.source_ranks, ctx.expert_ranks = sources, experts
+        if directory:
+            from .checkpoint.quantized import open_checkpoint
+            ld = open_checkpoint(directory, dtype)
+            cfg = Qwen3MoeConfig.from_hf(ld.config)
+            model = Qwen3MoeModel(cfg, device, dtype, ctx).load_state(ld)
+        else:
+            cfg = Qwen3MoeConfig.tiny() if (pkg.model or "").endswith(":tiny") \
+                else Qwen3MoeConfig.qwen3_30b_a3b()
+            model = Qwen3MoeModel(cfg, device, dtype, ctx).init_random(0)
+        limit = min(int(pkg.max_num_batched_tokens or 8192), 8192)
+        if device.type == "cuda":
+            import torch.distributed as dist
+            from .parallel.expert_exchange import ExpertExchange
+            model.exchange = ExpertExchange(dist.group.WORLD, rank, world, device, limit,
+                                            cfg.num_experts_per_tok, cfg.hidden_size,
+                                            cfg.num_experts, cfg.moe_intermediate_size,
+                                            sources, experts)
+        else:
+            from .parallel.expert_exchange import HostExpertExchange
+            model.exchange = HostExpertExchange(control, rank, world, limit,
+                                                cfg.num_experts_per_tok, cfg.hidden_size,
+                                                cfg.num_experts, sources, experts)
+        eng = None
+        if rank in sources:
+            eng = LLMEngine(model,
+                            page_size=min(pkg.kv_cache_config.block_size, 16)
+                            if device.type == "cuda" else pkg.kv_cache_config.block_size,
+                            max_num_seqs=min(pkg.max_running_requests, pkg.scheduler_config.max_batch),
+                            max_model_len=pkg.max_model_len or min(cfg.max_position_embeddings, 8192),
+                            max_num_batched_tokens=limit,
+                            mem_fraction_static=pkg.mem_fraction_static,
+                            enable_prefix_cache=pkg.kv_cache_config.prefix_caching,
+                            watchdog_timeout=float(pkg.profiling_config.watchdog_timeout),
+                            **({"num_pages": 512, "use_graphs": False} if device.type == "cpu" else {}))
+        member = UnionMember(control, rank, world, sources, experts, engine=eng, model=model,
+                             capacity_limit=limit)
+        if rank > 0:
+            member_loop(member, 0)
+            return 0
+        tok = load_tokenizer(directory, cfg.vocab_size, cfg.eos_token_id)
+        front = UnionFront(member, 0)
+        shutdown = front.shutdown
+        app = create_app(package=pkg, engine=front, tokenizer=tok, served_model_name=name)
     else:
         from .engine.engine import LLMEngine
         from .models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel

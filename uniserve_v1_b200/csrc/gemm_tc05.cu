@@ -915,7 +915,12 @@ int launch(const CUtensorMap& tmA, const BMaps& tmB, GemmArgs a, int m_tiles, in
   if (!DUAL && BN <= 64 && a.num_tiles == nullptr && tiles < 96 && num_k >= 4) {
     splits = (200 + tiles - 1) / tiles;
     if (splits > num_k / 2) splits = num_k / 2;
-    if (splits > 8) splits = 8;
+    static const int max_splits = [] {
+      const char* e = getenv("US_GEMM_SPLITS");
+      const int v = e ? atoi(e) : 8;
+      return v >= 1 && v <= 8 ? v : 8;
+    }();
+    if (splits > max_splits) splits = max_splits;
   }
   int kb_per = (num_k + splits - 1) / splits;
   splits = (num_k + kb_per - 1) / kb_per;

@@ -130,13 +130,20 @@ class LLMEngine:
         batch = self.scheduler.schedule()
         if batch is None:
             return []
+        return self.run_batch(batch)
+
+    def run_batch(self, batch, capacity: Optional[int] = None) -> list:
+        """Executes a scheduled batch and applies its results.  ``capacity``: the row count
+        the members of an expert union agreed on for this step (``engine/union.py``)."""
         if getattr(self.blocks, "host_slots", 0):
             self.runner.apply_kv_moves(*self.blocks.take_moves())
         self.watchdog.begin(f"{batch.kind} step {batch.step_id}")
         try:
             if self.profiler is not None:
                 with self.profiler.step(batch.kind, batch.step_id):
-                    sampled, lps = self.runner.execute(batch)
+                    sampled, lps = self.runner.execute(batch, capacity)
+            elif capacity is not None:
+                sampled, lps = self.runner.execute(batch, capacity)
             else:
                 sampled, lps = self.runner.execute(batch)
         except Exception as e:     # fatal_worker_failure: stop the engine, fail every request

@@ -361,17 +361,21 @@ class CausalLmRunner:
             return "logits"
         return "greedy" if all(r.params.greedy for r in rows) else "sampled"
 
-    def decode(self, rows: list, steps: int = 1):
+    def decode(self, rows: list, steps: int = 1, capacity: Optional[int] = None):
         """Runs ``steps`` decode steps for ``rows`` (requests); returns
-        (tokens [steps, n] on the host, logprob info or None)."""
+        (tokens [steps, n] on the host, logprob info or None).  ``capacity``: the row count
+        the step was agreed to run at (an expert union steps with one capacity on every
+        member); rows past ``len(rows)`` are padding.  With no rows at all the forward is a
+        *join*: every kernel of the step is issued with zero live rows."""
         n = len(rows)
-        B = self.bucket_for(n)
+        B = capacity if capacity is not None else self.bucket_for(n)
+        assert n <= B
         blk = self._decode_block(B)
-        variant = self.variant_for(rows)
+        variant = self.variant_for(rows) if rows else "greedy"
         assert steps == 1 or variant != "logits"
         assert steps <= self.history_steps
         self._fill_decode(blk, rows, B)
-        g = self._graph(B, variant)
+        g = self._graph(B, variant) if B <= self.buckets[-1] or B in self._graphs else None
         self.h2d_bytes += blk.upload()
         logits = sampled = None
         self.announce("replay" if g is not None else "eager", B, steps)
@@ -501,9 +505,14 @@ class CausalLmRunner:
         return host, info
 
     # --------------------------------------------------------------- prefill --
-    def prefill(self, chunks: list):
+    def join(self, capacity: int) -> None:
+        """An idle member's part of an agreed step: the whole forward with zero live rows."""
+        self.decode([], 1, capacity=capacity)
+
+    def prefill(self, chunks: list, capacity: Optional[int] = None):
         """Eager varlen prefill of the scheduled chunks; returns (tokens for the
-        chunks that sample, in chunk order, on the host; logprob info)."""
+        chunks that sample, in chunk order, on the host; logprob info).  ``capacity`` pads
+        the rows to an agreed count (padding rows write no cache slot and route nowhere)."""
         dev = self.device
         ps = self.page_size
         ids, pos, slots, cu_q, cu_k, ctx, last_rows, sample_rows = [], [], [], [0], [0], [], [], []
@@ -523,6 +532,13 @@ class CausalLmRunner:
             if c.sample:
                 last_rows.append(cu_q[-1] - 1)
                 sample_rows.append(req)
+        T_real = len(ids)
+        live = None
+        if capacity is not None:
+            assert T_real <= capacity, (T_real, capacity)
+            pad = capacity - T_real
+            ids, pos, slots = ids + [0] * pad, pos + [0] * pad, slots + [-1] * pad
+            live = torch.tensor([T_real], dtype=torch.int32, device=dev)
         T = len(ids)
         i32 = torch.int32
         packed = torch.tensor(ids + pos + slots + cu_q + cu_k, dtype=i32,
@@ -538,7 +554,7 @@ class CausalLmRunner:
             page_table = page_table.to(dev)
         meta = AttnMeta(kind="prefill", slots=d[2 * T:3 * T], cu_q=d[3 * T:3 * T + nq],
                         cu_k=d[3 * T + nq:3 * T + 2 * nq], max_q=max_q, max_k=max_k,
-                        context_lens=ctx, page_table=page_table)
+                        context_lens=ctx, page_table=page_table, live=live, rows_real=T_real)
         self.announce("eager", T)
         hidden = self.model.forward(d[:T], d[T:2 * T], meta, self.kv_caches)
         tap = getattr(self, "hidden_tap", None)
@@ -603,17 +619,17 @@ class CausalLmRunner:
         return out
 
     # ---------------------------------------------------------------- execute --
-    def execute(self, batch: Batch):
+    def execute(self, batch: Batch, capacity: Optional[int] = None):
         """Returns (sampled {request_id: token}, logprobs {request_id: info})."""
         sampled, lps = {}, {}
         if batch.kind == "decode":
             rows = [c.request for c in batch.chunks]
-            toks, info = self.decode(rows, 1)
+            toks, info = self.decode(rows, 1, capacity=capacity)
             for i, r in enumerate(rows):
                 sampled[r.request_id] = int(toks[0, i])
             lps = info or {}
         else:
-            toks, info, rows = self.prefill(batch.chunks)
+            toks, info, rows = self.prefill(batch.chunks, capacity=capacity)
             for i, r in enumerate(rows):
                 sampled[r.request_id] = int(toks[i])
             lps = info or {}

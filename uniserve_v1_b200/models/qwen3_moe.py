@@ -147,6 +147,7 @@ class AttnMeta:
     context_lens: Optional[list] = None         # per sequence keys already in the cache
     logits_rows: Optional[torch.Tensor] = None  # rows whose logits are needed (int32)
     live: Optional[torch.Tensor] = None         # device word: rows that are real (padding after)
+    rows_real: Optional[int] = None             # prefill padded to a capacity: rows before the padding
 
 
 class Qwen3MoeModel:
@@ -434,7 +435,7 @@ class Qwen3MoeModel:
                 return out, ("sum",)
             return self.ctx.all_reduce_tp(out), None
         logits = F.linear(x, lw.router, out_dtype=torch.float32)
-        if self.exchange is not None and x.is_cuda:
+        if self.exchange is not None and (x.is_cuda or getattr(self.exchange, "host", False)):
             live = getattr(self, "_live", None)
             ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob,
                                           live=live)

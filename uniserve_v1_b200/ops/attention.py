@@ -39,6 +39,16 @@ def varlen_attention(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, out=None)
 
 def prefill_attention(qkv, Hq, Hkv, D, meta, kcache, vcache, scale):
     T = qkv.shape[0]
+    real = getattr(meta, "rows_real", None)
+    if real is not None and real < T:
+        # rows padded up to an agreed capacity: they attend to nothing and stay zero
+        out = torch.zeros(T, Hq, D, dtype=qkv.dtype, device=qkv.device)
+        if real > 0:
+            import copy
+            m2 = copy.copy(meta)
+            m2.rows_real = None
+            out[:real] = prefill_attention(qkv[:real], Hq, Hkv, D, m2, kcache, vcache, scale)
+        return out
     v3 = qkv.view(T, Hq + 2 * Hkv, D)
     q, k, v = v3[:, :Hq], v3[:, Hq:Hq + Hkv], v3[:, Hq + Hkv:]
     ctx_lens = meta.context_lens

@@ -178,3 +178,82 @@ class ExpertExchange:
                N.ptr(q8["hs"]), q8["hs"].stride(0), E, H, I_, R, I_, I_, H, self.recv_ptrs,
                self.world, N.ptr(ws.sorted_route), N.ptr(self.win_w), t_step * self.k, *tiles, st)
         N.call("us_ep_signal_combined", self.source_ranks[0], self.source_ranks[-1] + 1, st)
+
+
+class HostExpertExchange:
+    """The same exchange for CPU ranks (gloo): the calls and their lock-step contract are
+    those of ``ExpertExchange``; rows travel through host collectives.  It exists for the
+    host-side logic (capacity agreement, idle-rank joins, disjoint attention / expert roles)
+    to be tested without GPUs, and for CPU deployments of the tiny model.
+
+    Per layer every rank takes part in two collectives, in this order: an all-gather of
+    (rows, ids, weights) of ``t_step`` rows per rank, and an all-reduce of the experts'
+    weighted output rows.  A source-only rank joins the first in ``dispatch`` and the second
+    in ``combine_add_rmsnorm``; an expert-only rank does both in ``experts``; a rank with
+    both roles gathers in ``experts`` (after its own ``dispatch`` stashed the rows)."""
+    host = True
+
+    def __init__(self, group, rank: int, world: int, t_max: int, top_k: int, hidden: int,
+                 num_experts: int, source_ranks=None, expert_ranks=None):
+        self.group, self.rank, self.world = group, rank, world
+        self.T, self.k, self.H, self.E = t_max, top_k, hidden, num_experts
+        self.source_ranks = tuple(source_ranks if source_ranks is not None else range(world))
+        self.expert_ranks = tuple(expert_ranks if expert_ranks is not None else range(world))
+        self.is_source = rank in self.source_ranks
+        self.is_expert = rank in self.expert_ranks
+        self.experts_per_rank = num_experts // len(self.expert_ranks)
+        assert self.experts_per_rank * len(self.expert_ranks) == num_experts
+        self.e_lo = (self.expert_ranks.index(rank)) * self.experts_per_rank if self.is_expert else 0
+        self.device = torch.device("cpu")
+        self._mine = None
+        self._partial = None
+        self.layers = 0
+
+    def close(self):
+        pass
+
+    def _gather(self, t_step: int):
+        x, ids, w = self._mine if self._mine is not None else (
+            torch.zeros(t_step, self.H), torch.full((t_step, self.k), -1, dtype=torch.int32),
+            torch.zeros(t_step, self.k))
+        self._mine = None
+        xs = [torch.empty_like(x) for _ in range(self.world)]
+        is_ = [torch.empty_like(ids) for _ in range(self.world)]
+        ws = [torch.empty_like(w) for _ in range(self.world)]
+        dist.all_gather(xs, x.contiguous(), group=self.group)
+        dist.all_gather(is_, ids.contiguous(), group=self.group)
+        dist.all_gather(ws, w.contiguous(), group=self.group)
+        return torch.cat(xs), torch.cat(is_), torch.cat(ws)
+
+    def dispatch(self, x, ids, weights, live=None) -> None:
+        T = x.shape[0]
+        assert T <= self.T, f"step of {T} rows exceeds the exchange capacity {self.T}"
+        ids, weights = ids.clone().to(torch.int32), weights.clone().float()
+        if live is not None:
+            n = int(live)
+            ids[n:] = -1
+            weights[n:] = 0
+        self._mine = (x.float(), ids, weights)
+        self._t = T
+        if not self.is_expert:
+            self._gather(T)             # source-only: joins the gather, keeps nothing
+
+    def experts(self, w13, w2, t_step: int, act: str = "silu") -> None:
+        from ..ops import reference as R
+        x, ids, w = self._gather(t_step)
+        out = R.moe_experts(x, ids, w, w13.float(), w2.float(), e_lo=self.e_lo, act=act).float()
+        self.layers += 1
+        if self.is_source:
+            self._partial = out
+        else:
+            dist.all_reduce(out, group=self.group)      # expert-only: nothing to keep
+
+    def combine_add_rmsnorm(self, ids, live, residual, w, eps: float):
+        from ..ops import reference as R
+        T = ids.shape[0]
+        out = self._partial if self._partial is not None else \
+            torch.zeros(self.world * T, self.H)
+        self._partial = None
+        dist.all_reduce(out, group=self.group)
+        mine = out[self.rank * T:(self.rank + 1) * T]
+        return R.add_rmsnorm(mine.to(w.dtype), residual, w, eps)

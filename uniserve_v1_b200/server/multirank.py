@@ -226,7 +226,38 @@ def package_parallelism(pkg) -> dict:
     return best
 
 
+def package_union(pkg) -> Optional[dict]:
+    """The expert union a package describes, or None.
+
+    * ``moe_config.expert_parallel`` with ``data_parallel_size = N`` and no tensor
+      parallelism: N attention members that each hold 1/N of the experts.
+    * a worker group with ``role = "experts"``: the ranks of the model groups are the
+      attention members, the ranks of the experts groups hold the experts (the
+      disaggregated layout).  Attention members are data parallel: a
+      ``tensor_parallel_size`` inside the attention group of such a layout is served as
+      that many attention members.
+    Returns {"sources": n, "experts": m, "shared": bool} (``shared``: every member has
+    both roles)."""
+    if not pkg.moe_config.expert_parallel:
+        return None
+    lay = pkg.layout()
+    groups = lay["groups"]
+    exp = sum(len(g["ranks"]) for g in groups if g.get("role") == "experts")
+    if exp:
+        src = sum(len(g["ranks"]) for g in groups if g.get("role") != "experts")
+        return {"sources": max(1, src), "experts": exp, "shared": False}
+    dp = int(lay.get("data_parallel_size") or 1)
+    tp = max([int((g.get("blocks", {}).get("model") or {}).get("tensor_parallel_size", 1) or 1)
+              for g in groups] + [int(pkg.top.get("tensor_parallel_size", 1) or 1)])
+    if dp > 1 and tp == 1:
+        return {"sources": dp, "experts": dp, "shared": True}
+    return None
+
+
 def package_world(pkg) -> int:
+    u = package_union(pkg)
+    if u:
+        return u["sources"] + (0 if u["shared"] else u["experts"])
     return package_parallelism(pkg)["world"]
 
 
