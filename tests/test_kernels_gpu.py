@@ -73,6 +73,28 @@ def test_linear_bf16(rows, M, K):
     close(y, ref, 2e-2 * math.sqrt(K / 64), 2e-2)
 
 
+@pytest.mark.parametrize("rows,M,K", [(64, 768, 2048), (64, 2048, 512), (33, 128, 2048),
+                                       (7, 1000, 256), (16, 5120, 4096), (1, 24, 768)])
+def test_linear_decode_kernel(rows, M, K, monkeypatch):
+    """The weight-streaming kernel of decode-size projections (at most 64 rows, K a multiple
+    of 256): bf16 and fp32 outputs, bias, a strided activation view, and the same result as
+    the tcgen05 kernel it stands in for."""
+    monkeypatch.setattr(F, "LINEAR_DECODE_MAX", 1 << 40)
+    x, w = rnd(rows, K), rnd(M, K, scale=0.05)
+    ref = x.float() @ w.float().t()
+    tol = 1e-3 * math.sqrt(K / 64)            # fp32 accumulation of bf16 products
+    y32 = F.linear(x, w, out_dtype=torch.float32)
+    close(y32, ref, tol, 1e-3)
+    close(F.linear(x, w), ref, 2e-2 * math.sqrt(K / 64), 2e-2)
+    b = rnd(M, dtype=torch.float32, seed=3)
+    close(F.linear(x, w, bias=b, out_dtype=torch.float32), ref + b, tol, 1e-3)
+    wide = rnd(rows, K + 64, seed=9)
+    close(F.linear(wide[:, :K], w, out_dtype=torch.float32), wide[:, :K].float() @ w.float().t(),
+          tol, 1e-3)
+    monkeypatch.setattr(F, "LINEAR_DECODE", False)
+    close(F.linear(x, w, out_dtype=torch.float32), y32, tol, 1e-3)
+
+
 @pytest.mark.parametrize("rows,M,K", [(2600, 2176, 512), (4100, 1280, 192), (2304, 2048, 1024)])
 def test_linear_many_tiles(rows, M, K):
     """More than one wave of tiles: the persistent kernels (CTA pairs by default; an odd

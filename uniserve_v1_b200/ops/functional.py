@@ -204,6 +204,12 @@ def paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, split
 
 
 # ------------------------------------------------------------------ GEMMs --
+# US_LINEAR_DECODE=0: projections of at most 64 rows go to the tcgen05 kernel as well
+LINEAR_DECODE = _os.environ.get("US_LINEAR_DECODE", "1") == "1"
+# weights up to this many elements take it (larger ones are bandwidth-bound: tcgen05 + TMA)
+LINEAR_DECODE_MAX = int(_os.environ.get("US_LINEAR_DECODE_MAX", str(4 << 20)))
+
+
 def _block_n(rows: int, dual: bool) -> int:
     for bn in (16, 32, 64, 128):
         if rows <= bn:
@@ -233,6 +239,15 @@ def linear(x, w, bias=None, out_dtype=None, out=None, block_n=None):
         out = torch.empty(rows, M, dtype=out_dtype, device=x.device)
     if rows == 0:
         return out
+    if LINEAR_DECODE and rows <= 64 and K % 256 == 0 and block_n is None and \
+            M * K <= LINEAR_DECODE_MAX and \
+            out.dtype in (BF16, torch.float32) and x2.data_ptr() % 16 == 0 and \
+            w.data_ptr() % 16 == 0 and w.stride(0) % 8 == 0:
+        # decode-size projection: weight-streaming kernel (latency-bound shape)
+        N.call("us_linear_decode", N.ptr(w), N.ptr(x2), N.ptr(out), N.ptr(bias), rows, M, K,
+               w.stride(0), x2.stride(0), out.stride(0), int(out.dtype == torch.float32),
+               0 if (bias is None or bias.dtype == BF16) else 1, N.stream())
+        return out.view(*x.shape[:-1], M)
     bn = block_n or _block_n(rows, False)
     N.call("us_gemm_wx", N.ptr(w), N.ptr(x2), N.ptr(out), 1, M, M, K, rows, w.stride(0),
            x2.stride(0), out.stride(0), 0, 0, 0, 0 if out.dtype == BF16 else 1, N.ptr(bias),

@@ -39,6 +39,7 @@ _SIGNATURES = {
     "us_device_info": (I, [P, P, P, P]),
     "us_gemm_wx": (I, [P, P, P, I, I, I, I, I, L, L, L, I, I, I, I, P, I, P, P, P, P, P, P, I, I, P]),
     "us_gemm_wx_hint": (I, [I]),
+    "us_linear_decode": (I, [P, P, P, P, I, I, I, L, L, L, I, I, P]),
     "us_rmsnorm": (I, [P, P, P, I, I, L, L, F, P]),
     "us_add_rmsnorm": (I, [P, P, P, P, I, I, F, I, P]),
     "us_modulated_rmsnorm": (I, [P, P, P, P, I, I, I, P, I, I, F, P]),
