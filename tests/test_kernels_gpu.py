@@ -558,3 +558,21 @@ def test_flash_attn_head_dim_64(causal):
     out = flash_attn_varlen(q, k, v, cu, cu, max(lens), max(lens), 1 / math.sqrt(D), causal)
     ref = R.varlen_attention(q, k, v, cu.cpu(), cu.cpu(), 1 / math.sqrt(D), causal)
     close(out, ref, 2e-2, 2e-2)
+
+
+def test_flash_attn_head_dim_96():
+    """96-wide heads (the text refiner's) run on the tensor-core kernel, zero-padded to 128
+    channels; a width the kernels do not serve is refused, not computed elsewhere."""
+    from uniserve_v1_b200.ops.flash import flash_attn_varlen
+    D, H = 96, 3
+    lens = [200, 57]
+    T = sum(lens)
+    q, k, v = rnd(T, H, D, seed=61), rnd(T, H, D, seed=62), rnd(T, H, D, seed=63)
+    cu = torch.tensor([0, 200, 257], dtype=torch.int32, device=DEV)
+    out = flash_attn_varlen(q, k, v, cu, cu, max(lens), max(lens), 1 / math.sqrt(D), False)
+    ref = R.varlen_attention(q, k, v, cu.cpu(), cu.cpu(), 1 / math.sqrt(D), False)
+    assert out.shape == (T, H, D)
+    close(out, ref, 2e-2, 2e-2)
+    with pytest.raises(ValueError):
+        flash_attn_varlen(rnd(T, H, 100), rnd(T, H, 100), rnd(T, H, 100), cu, cu, 200, 200, 0.1,
+                          False)

@@ -180,26 +180,42 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
   const int* pt_row = a.page_table + (long long)b * a.max_pages;
   const int pages_per_tile = kTileKeys / a.page_size;
   const int seq_pages = (seq_len + a.page_size - 1) / a.page_size;
-  // One tile's K (or V) pages into their buffer; `bar` was armed by the caller.
-  auto load_tile = [&](const CUtensorMap* tm, uint8_t* buf, uint64_t* bar, int t) {
+  // Page ids of a tile: independent loads issued together (one memory latency per tile, not
+  // one per page), shared by the K and the V fetch.
+  constexpr int kMaxPagesPerTile = kTileKeys / 8;
+  auto load_pages = [&](int t, int (&pg)[kMaxPagesPerTile]) {
     const int page0 = (k_begin + t * kTileKeys) / a.page_size;
-    for (int i = 0; i < pages_per_tile; ++i) {
+#pragma unroll
+    for (int i = 0; i < kMaxPagesPerTile; ++i) {
       const int pi = page0 + i;
-      const int page = (pi < seq_pages && pi < a.max_pages) ? pt_row[pi] : 0;
-      const int row = page * a.page_size;
-      uint8_t* dst = buf + i * a.page_size * 128;
-      tc::tma_load_2d(dst, tm, bar, hk * kD, row);
-      tc::tma_load_2d(dst + kHalfBytes, tm, bar, hk * kD + 64, row);
+      pg[i] = (i < pages_per_tile && pi < seq_pages && pi < a.max_pages) ? __ldg(pt_row + pi) : 0;
     }
   };
+  // One tile's K (or V) pages into their buffer; `bar` was armed by the caller.
+  auto issue_tile = [&](const CUtensorMap* tm, uint8_t* buf, uint64_t* bar,
+                        const int (&pg)[kMaxPagesPerTile]) {
+#pragma unroll
+    for (int i = 0; i < kMaxPagesPerTile; ++i) {
+      if (i < pages_per_tile) {
+        const int row = pg[i] * a.page_size;
+        uint8_t* dst = buf + i * a.page_size * 128;
+        tc::tma_load_2d(dst, tm, bar, hk * kD, row);
+        tc::tma_load_2d(dst + kHalfBytes, tm, bar, hk * kD + 64, row);
+      }
+    }
+  };
+  int pg_next[kMaxPagesPerTile];
   if (warp == 4 && lane == 0) {
     // the first tile needs nothing of the set-up below: fetch it now
     tc::tma_prefetch_desc(&tmK);
     tc::tma_prefetch_desc(&tmV);
+    int pg[kMaxPagesPerTile];
+    load_pages(0, pg);
+    if (ntiles > 1) load_pages(1, pg_next);
     tc::mbar_expect_tx(k_full, kTileBytes);
-    load_tile(&tmK, sK, k_full, 0);
+    issue_tile(&tmK, sK, k_full, pg);
     tc::mbar_expect_tx(v_full, kTileBytes);
-    load_tile(&tmV, sV, v_full, 0);
+    issue_tile(&tmV, sV, v_full, pg);
   }
   if (warp == 5) {
     tc::tmem_alloc(tmem_slot, 32);
@@ -232,20 +248,24 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
     if (lane == 0) {
       for (int t = 1; t < ntiles; ++t) {
         const uint32_t ph = (uint32_t)t & 1u;
+        int pg[kMaxPagesPerTile];
+#pragma unroll
+        for (int i = 0; i < kMaxPagesPerTile; ++i) pg[i] = pg_next[i];
+        if (t + 1 < ntiles) load_pages(t + 1, pg_next);     // in flight during the waits below
         if (!tc::mbar_wait(k_empty, ph ^ 1u, abort_flag)) {
           us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
           *abort_flag = 1;
           break;
         }
         tc::mbar_expect_tx(k_full, kTileBytes);
-        load_tile(&tmK, sK, k_full, t);
+        issue_tile(&tmK, sK, k_full, pg);
         if (!tc::mbar_wait(v_empty, ph ^ 1u, abort_flag)) {
           us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
           *abort_flag = 1;
           break;
         }
         tc::mbar_expect_tx(v_full, kTileBytes);
-        load_tile(&tmV, sV, v_full, t);
+        issue_tile(&tmV, sV, v_full, pg);
       }
     }
   } else if (warp == 5) {

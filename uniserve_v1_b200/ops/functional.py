@@ -147,9 +147,12 @@ DECODE_SIMT = _os.environ.get("US_DECODE_SIMT", "0") == "1"   # A/B switch: CUDA
 
 
 def decode_splits(B: int, Hkv: int, max_len: int, sm_count: int = 148) -> int:
-    """Number of KV splits so the grid fills the GPU about twice over."""
+    """Number of KV splits.  A CTA of the decode kernel has a fixed cost of several
+    microseconds, so splits only pay while (sequence, kv head) pairs alone leave SMs idle:
+    measured at 64 sequences x 1100 keys, 4 kv heads (256 pairs) run fastest unsplit
+    (48 us against 58 us with two splits), 1 kv head (64 pairs) with three to four."""
     ctas = max(1, B * Hkv)
-    want = max(1, (2 * sm_count + ctas - 1) // ctas)
+    want = max(1, 256 // ctas)
     by_len = max(1, max_len // 256)
     return int(max(1, min(want, by_len, 32)))
 

@@ -57,6 +57,9 @@ def main():
                                    "rank-decode"])
     ap.add_argument("--tp", type=int, default=8, help="rank-decode: ranks of the emulated layout")
     ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--splits", type=int, default=0, help="decode: KV splits (0 = heuristic)")
+    ap.add_argument("--kv-heads", type=int, default=4)
+    ap.add_argument("--q-heads", type=int, default=32)
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=2048)
@@ -289,14 +292,14 @@ def main():
                    reduce_scatter_tflops=2.0 * rows * I * H / ms2 / 1e9, reduce_norm_ms=ms3,
                    reduce_norm_tbs=rows * H * (2 + 4 + 4 + 2) / ms3 / 1e9)
     else:
-        B, Hq, Hkv, D, page = a.batch, 32, 4, 128, 16
+        B, Hq, Hkv, D, page = a.batch, a.q_heads, a.kv_heads, 128, 16
         per = (a.ctx + page - 1) // page
         pages = B * per + 1
         kc, vc = rnd(pages, page, Hkv, D), rnd(pages, page, Hkv, D)
         q = rnd(B, Hq, D)
         pt = (torch.randperm(pages - 1, device=dev)[:B * per].view(B, per) + 1).to(torch.int32)
         sl = torch.full((B,), a.ctx, dtype=torch.int32, device=dev)
-        splits = F.decode_splits(B, Hkv, a.ctx)
+        splits = a.splits or F.decode_splits(B, Hkv, a.ctx)
         scratch, counters = F.decode_scratch(B, Hq, Hkv, D, splits, dev)
         ms = timeit(lambda: F.paged_decode_attention(q, kc, vc, pt, sl, 1 / math.sqrt(D), splits,
                                                      scratch=scratch, counters=counters),
