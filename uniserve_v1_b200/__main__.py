@@ -251,7 +251,7 @@ def serve(args) -> int:
             from .parallel.symm import attach_fused
             attach_fused(ctx, device, hidden=cfg.hidden_size)
 
-        def make_engine():
+        def make_engine(pkg=pkg):
             policy = None
             if "scheduling" in pkg.programs:        # the package's own scheduling program
                 from .engine.program import ProgramHost, ProgramPolicy
@@ -289,7 +289,11 @@ def serve(args) -> int:
         role = args.role or (pkg.replicas[args.replica_id].role if args.replica_id else "mixed")
         app = create_app(package=pkg, engine=engine, tokenizer=tok, served_model_name=name,
                          engine_factory=make_engine if bus is None else None, drafter=drafter,
-                         role=role, internal_key=os.environ.get("UNISERVE_INTERNAL_KEY"))
+                         role=role, internal_key=os.environ.get("UNISERVE_INTERNAL_KEY"),
+                         # epoch updates build the target engine (a second scheduler and KV
+                         # cache over the same weights) beside the serving one
+                         engine_builder=make_engine if bus is None else None,
+                         state_dir=getattr(args, "state_dir", None))
     if args.ready_fd is not None:
         os.write(args.ready_fd, json.dumps({"state": "listening", "host": pkg.admin_config.host,
                                             "port": pkg.admin_config.port}).encode() + b"\n")
@@ -342,6 +346,8 @@ def main(argv=None) -> int:
     s.add_argument("--ready-fd", type=int, default=None)
     s.add_argument("--log-level", default=None)
     s.add_argument("--log-level-http", default=None)
+    s.add_argument("--state-dir", default=None,
+                   help="directory where control programs keep their state across restarts")
     s.add_argument("--role", choices=["mixed", "prefill", "decode"], default=None,
                    help="disaggregation role of this replica (default: the package's "
                         "replicas.<id>.role for --replica-id, else mixed)")

@@ -18,6 +18,7 @@ import dataclasses
 import os
 import re
 import shutil
+import json
 import tomllib
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -319,6 +320,42 @@ TOP_LEVEL = {
 _RANK_RE = re.compile(r"^(?:(?P<host>[^/]+)/)?(?P<dev>cuda|cpu):(?P<lo>\d+)(?:-(?P<hi>\d+))?$")
 
 
+def _toml_value(v) -> str:
+    if isinstance(v, bool):
+        return "true" if v else "false"
+    if isinstance(v, (int, float)):
+        return repr(v)
+    if isinstance(v, str):
+        return json.dumps(v)
+    if isinstance(v, (list, tuple)):
+        return "[" + ", ".join(_toml_value(x) for x in v) + "]"
+    if isinstance(v, dict):
+        return "{ " + ", ".join(f"{json.dumps(str(k))} = {_toml_value(x)}" for k, x in v.items()) + " }"
+    raise ConfigError("", f"cannot write {type(v).__name__} as TOML")
+
+
+def dump_toml(data: dict) -> str:
+    """Writes a parsed package back as TOML text (scalars and arrays first, then tables;
+    tables inside arrays as inline tables)."""
+    lines = []
+
+    def emit(table: dict, prefix: str) -> None:
+        subs = []
+        for k, v in table.items():
+            if isinstance(v, dict):
+                subs.append((k, v))
+            else:
+                lines.append(f"{json.dumps(str(k)) if not str(k).replace('_', 'a').replace('-', 'a').isalnum() else k} = {_toml_value(v)}")
+        for k, v in subs:
+            key = k if str(k).replace("_", "a").replace("-", "a").isalnum() else json.dumps(str(k))
+            name = f"{prefix}.{key}" if prefix else key
+            lines.append("")
+            lines.append(f"[{name}]")
+            emit(v, name)
+    emit(data, "")
+    return "\n".join(lines) + "\n"
+
+
 def parse_ranks(items, path: str) -> list:
     """``["cuda:0-3"]`` / ``["rank-1/cuda:0-1"]`` -> expanded Rank list."""
     out = []
@@ -409,6 +446,26 @@ class Package:
         if name in tables:
             return tables[name]
         raise AttributeError(name)
+
+    # ------------------------------------------------------------- changes --
+    def with_options(self, changes: dict) -> "Package":
+        """A new package with ``{option path: value}`` written over this one's
+        (``scheduler_config.chunked_prefill_size``, ``replicas.a.role``, ``kernels.<op>`` ...);
+        the result is parsed and validated like a package read from a file."""
+        import copy
+        data = copy.deepcopy(self.raw)
+        for path, value in changes.items():
+            node = data
+            parts = path.split(".")
+            for part in parts[:-1]:
+                node = node.setdefault(part, {})
+                if not isinstance(node, dict):
+                    raise ConfigError(path, "not a table")
+            if value is None:
+                node.pop(parts[-1], None)
+            else:
+                node[parts[-1]] = value
+        return Package.parse(dump_toml(data), self.source_dir)
 
     # ---------------------------------------------------------------- load --
     @classmethod

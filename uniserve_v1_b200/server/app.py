@@ -211,12 +211,17 @@ class AppState:
 def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None,
                served_model_name: str = "model", video_service=None, generation_defaults=None,
                reasoning: bool = True, engine_factory=None, drafter=None,
-               role: str = "mixed", internal_key: Optional[str] = None) -> FastAPI:
+               role: str = "mixed", internal_key: Optional[str] = None,
+               engine_builder=None, state_dir: Optional[str] = None) -> FastAPI:
     """Builds the application.  ``engine`` (an LLMEngine) registers the chat route;
     ``video_service`` registers the video routes and ``/v1/capabilities``.  ``role`` =
     ``prefill`` / ``decode`` also mounts ``/internal/prefill`` / ``/internal/decode`` for a
     disaggregating router; those routes require ``internal_key`` (header
-    ``x-uniserve-internal-key``) and exist on no other deployment."""
+    ``x-uniserve-internal-key``) and exist on no other deployment.  ``engine_builder(package)``
+    builds an engine for a changed package: with it, a change of effect ``epoch`` /
+    ``generation`` / ``storage`` runs as an epoch update (prepare, switch, trial, commit or
+    roll back; ``server/updates.py``) instead of being refused.  Control programs of the
+    package (``server/control.py``) run once a second beside the server."""
     if role not in ("mixed", "prefill", "decode"):
         raise ConfigError("role", f"unknown role {role!r}")
     if role != "mixed" and not internal_key:
@@ -635,6 +640,60 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         return {"config": s.package.raw, "layout": s.package.layout(),
                 "revision": s.obs.revision}
 
+    def apply_package(new: Package, writer: str = "admin"):
+        """Applies a parsed package: in place for step / order effects, as an epoch update
+        when an engine builder exists, refused otherwise.  Returns (status, body)."""
+        changes = s.package.diff(new)
+        eff = strongest_effect(changes)
+        names = [c[0] for c in changes]
+        if eff not in (None, "step", "order"):
+            upd = getattr(s.service, "update", None) if s.service else None
+            if engine_builder is None or s.service is None or eff == "daemon":
+                return 409, openai_error(
+                    f"the change needs effect `{eff}`, which a running process cannot apply "
+                    f"in place: restart the deployment with the new package", "conflict",
+                    None, changes[0][0] if changes else None)
+            if upd is not None and not upd.done:
+                return 409, openai_error(f"an update is {upd.phase}", "conflict")
+            from .updates import EpochUpdate
+            old = s.package
+            uc = new.update_config
+
+            def on_phase(phase, why):
+                if phase == "switching":
+                    s.package = new
+                    s.served = new.served_model_name or s.served
+                    s.obs.revision += 1
+                elif phase in ("rolled_back", "abandoned"):
+                    s.package = old
+                s.obs.event("update", "", phase=phase, reason=why, writer=writer, changes=names)
+                if phase == "switching":
+                    s.engine = s.service.engine
+            rb = uc.rollback
+            upd = EpochUpdate(lambda: engine_builder(new), trial_s=float(uc.trial),
+                              drain_s=float(uc.drain_s), failure_rate=rb.failure_rate,
+                              step_time_regression=rb.step_time_regression,
+                              throughput_regression=rb.throughput_regression, on_phase=on_phase)
+            s.service.begin_update(upd)
+            return 202, {"applied": names, "effect": eff, "update": upd.phase}
+        s.package = new
+        s.served = new.served_model_name or s.served
+        if s.service:
+            s.service.paused = bool(new.paused)
+            s.service.wake.set()
+            if s.engine is not None and hasattr(s.engine, "blocks"):
+                s.engine.blocks.enable_prefix_cache = bool(new.kv_cache_config.prefix_caching)
+                if any(c[0] == "flush" for c in changes):
+                    s.engine.blocks.flush()
+                cps = new.scheduler_config.chunked_prefill_size
+                if cps and hasattr(s.engine, "config"):
+                    s.engine.config.chunked_prefill_size = int(cps)
+        s.obs.revision += 1
+        s.obs.event("policy", "", changes=names, effect=eff, writer=writer)
+        return 200, {"applied": names, "effect": eff, "revision": s.obs.revision}
+
+    s.apply_package = apply_package
+
     @app.put("/admin/policy")
     async def put_policy(request: Request):
         text = (await request.body()).decode()
@@ -642,24 +701,41 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
             new = Package.parse(text)
         except ConfigError as e:
             return _err(400, str(e), param=e.path)
-        changes = s.package.diff(new)
-        eff = strongest_effect(changes)
-        if eff not in (None, "step", "order"):
-            return _err(409, f"the change needs effect `{eff}`, which a running process cannot apply "
-                             f"in place: restart the deployment with the new package",
-                        "conflict", param=changes[0][0] if changes else None)
-        s.package = new
-        s.served = new.served_model_name or s.served
-        if s.service:
-            s.service.paused = bool(new.paused)
-            s.service.wake.set()
-            if s.engine is not None:
-                s.engine.blocks.enable_prefix_cache = bool(new.kv_cache_config.prefix_caching)
-                if any(c[0] == "flush" for c in changes):
-                    s.engine.blocks.flush()
-        s.obs.revision += 1
-        s.obs.event("policy", "", changes=[c[0] for c in changes], effect=eff)
-        return {"applied": [c[0] for c in changes], "effect": eff, "revision": s.obs.revision}
+        status, body = apply_package(new)
+        return JSONResponse(body, status_code=status)
+
+    @app.get("/admin/update")
+    async def get_update():
+        upd = getattr(s.service, "update", None) if s.service else None
+        if upd is None:
+            return {"phase": None}
+        return {"phase": upd.phase, "reason": upd.reason, "history": upd.history}
+
+    # control programs of the package: read the store, write options through apply_package
+    from .control import ControlLoop
+
+    def _apply_options(changes: dict) -> bool:
+        try:
+            new = s.package.with_options(changes)
+        except ConfigError:
+            return False
+        status, _ = apply_package(new, writer="program")
+        return status in (200, 202)
+    s.control = ControlLoop(lambda: s.package, s.obs, _apply_options, state_dir)
+
+    @app.on_event("startup")
+    async def _start_control():
+        if not s.control.hosts:
+            return
+
+        async def loop():
+            while True:
+                await asyncio.sleep(1.0)
+                try:
+                    await asyncio.to_thread(s.control.tick)
+                except Exception:
+                    pass
+        s.control_task = asyncio.create_task(loop())
 
     @app.api_route("/admin/query", methods=["GET", "POST"])
     async def query(request: Request):

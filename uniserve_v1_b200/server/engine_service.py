@@ -45,6 +45,10 @@ class EngineService:
         self.started = False
         self.last_snapshot = 0.0
         self.steps = 0
+        from .updates import StepClock
+        self.step_clock = StepClock()
+        self.update = None                        # server.updates.EpochUpdate in progress
+        self.draining = None                      # the previous engine while it drains
 
     def start(self):
         if not self.started:
@@ -144,8 +148,52 @@ class EngineService:
         if self.obs:
             self.obs.inc("uniserve_engine_restarts_total")
 
+    # ---------------------------------------------------------------- updates --
+    def begin_update(self, update) -> None:
+        """Starts an epoch update (``server.updates.EpochUpdate``); the loop advances it."""
+        if self.update is not None and not self.update.done:
+            raise RuntimeError("an update is already in progress")
+        self.update = update
+        self.wake.set()
+
+    def migrate_all(self, source, target) -> int:
+        """Every live request of ``source`` continues on ``target`` from its migratable facts
+        (prompt, generated tokens, sampling parameters); returns how many moved."""
+        moved = 0
+        for req in list(source.scheduler.running) + list(source.scheduler.waiting):
+            rid = req.request_id
+            with self.lock:
+                m = self.meta.get(rid)
+            source.abort(rid)
+            if m is None:
+                continue
+            m["migrations"] += 1
+            if m["migrations"] > self.max_migrations:
+                self._deliver(StepOutput(rid, [], True, FinishReason.ERROR,
+                                         error=f"migrated more than {self.max_migrations} times"))
+                continue
+            try:
+                target.add_request(m["prompt"], m["params"], request_id=rid,
+                                   priority=m["priority"], cache_salt=m["salt"],
+                                   output_ids=list(m["outputs"]))
+                moved += 1
+            except Exception as e:
+                self._deliver(StepOutput(rid, [], True, FinishReason.ERROR, error=str(e)))
+        return moved
+
     def _run(self):
         while not self.stopping:
+            if self.update is not None and not self.update.done:
+                try:
+                    self.update.advance(self)
+                except Exception as e:
+                    self.update.phase, self.update.reason = "abandoned", str(e)
+            if self.draining is not None and self.draining.has_work():
+                try:                            # the previous engine steps what it still holds
+                    for o in self.draining.step():
+                        self._deliver(o)
+                except Exception:
+                    self.migrate_all(self.draining, self.engine)
             try:
                 while True:
                     msg = self.inbox.get_nowait()
@@ -165,23 +213,38 @@ class EngineService:
                             self._deliver(StepOutput(msg[1], [], True, FinishReason.ERROR,
                                                      error=f"hand-off refused: {e}"))
                     elif msg[0] == "abort":
-                        if self.engine.abort(msg[1]):
+                        if self.engine.abort(msg[1]) or \
+                                (self.draining is not None and self.draining.abort(msg[1])):
                             self._deliver(StepOutput(msg[1], [], True, FinishReason.ABORT))
             except queue.Empty:
                 pass
             if self.paused or not self.engine.has_work():
-                self.wake.wait(0.05)
-                self.wake.clear()
+                busy = self.draining is not None and self.draining.has_work()
+                if not busy:
+                    self.wake.wait(0.05 if self.update is None or self.update.done else 0.005)
+                    self.wake.clear()
                 continue
+            t_step = time.monotonic()
             try:
                 if self.drafter is not None and hasattr(self.engine, "speculative_step"):
                     outs = self.engine.speculative_step(self.drafter)
                 else:
                     outs = self.engine.step()
             except Exception as e:
+                if self.update is not None and self.update.phase == "trial":
+                    self.update.rollback(self, f"target failed: {e}")     # back to the previous
+                    continue
                 self._recover(e)
                 continue
             self.steps += 1
+            self.step_clock.record(time.monotonic() - t_step,
+                                   sum(len(o.new_token_ids) for o in outs))
+            for o in outs:
+                if o.finished:
+                    if o.finish_reason == FinishReason.ERROR:
+                        self.step_clock.failed += 1
+                    else:
+                        self.step_clock.finished += 1
             for o in outs:
                 meta = self.meta.get(o.request_id)
                 if meta and meta.get("lend") and o.new_token_ids and not o.finished:
