@@ -595,3 +595,126 @@ def test_flash_attn_head_dim_96():
     with pytest.raises(ValueError):
         flash_attn_varlen(rnd(T, H, 100), rnd(T, H, 100), rnd(T, H, 100), cu, cu, 200, 200, 0.1,
                           False)
+
+
+# ------------------------------------------------- recurrent token mixers --
+@pytest.mark.parametrize("dtype", [BF, torch.float32])
+def test_causal_conv1d_packed_batch_and_state(dtype):
+    """Three packed sequences (one shorter than the filter) against the FP32 restatement run
+    per sequence, outputs and carried state, then a second call that continues from the state."""
+    from uniserve_v1_b200.ops import gated_delta as GD
+    C, K = 640, 4
+    lens = [37, 2, 9]
+    w = rnd(C, K, scale=0.5, dtype=dtype)
+    pool = rnd(5, K - 1, C, dtype=dtype, seed=3)
+    slots = torch.tensor([4, 0, 2], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, 37, 39, 48], dtype=torch.int32, device=DEV)
+    wide = rnd(sum(lens), C + 64, dtype=dtype, seed=4)
+    x = wide[:, 32:32 + C]                                   # a strided view, as in the model
+    before = pool.clone()
+    y, _ = GD.causal_conv1d(x, w, pool, cu=cu, slots=slots)
+    # K products in FP32, silu, one store: a rounding bound (terms can cancel: relative to max)
+    tol = Tolerance.dot(K, out=dtype).then(Tolerance(0.0, 2.0 ** -20, True))
+    lo = 0
+    for n, s in zip(lens, slots.tolist()):
+        ref_y, ref_state = GD.causal_conv1d(x[lo:lo + n].cpu().float(), w.cpu().float(),
+                                            before[s].cpu().float())
+        tol.check(y[lo:lo + n], ref_y, "causal_conv1d")
+        Tolerance.exact().check(pool[s], ref_state.to(dtype), "causal_conv1d state")
+        lo += n
+    Tolerance.exact().check(pool[1], before[1], "untouched slot")
+    # the single-sequence form returns a new state and leaves the caller's alone
+    st = before[0].clone()
+    y1, st1 = GD.causal_conv1d(x[:5].contiguous(), w, st)
+    ref_y, ref_state = GD.causal_conv1d(x[:5].cpu().float(), w.cpu().float(), before[0].cpu().float())
+    tol.check(y1, ref_y, "causal_conv1d single")
+    Tolerance.exact().check(st, before[0], "caller's state")
+    Tolerance.exact().check(st1, ref_state.to(dtype), "returned state")
+
+
+@pytest.mark.parametrize("Dk,Dv,Hk,Hv,dtype", [(128, 128, 4, 8, BF), (16, 16, 2, 4, torch.float32),
+                                               (64, 96, 2, 2, BF)])
+def test_gated_delta_rule_kernel(Dk, Dv, Hk, Hv, dtype):
+    """Packed sequences (lengths across the 16-token staging boundary, and a decode-size one)
+    against the step-by-step FP32 recurrence; gates given and gates formed in the kernel."""
+    from uniserve_v1_b200.ops import gated_delta as GD
+    lens = [37, 1, 16]
+    T = sum(lens)
+    q, k, v = rnd(T, Hk, Dk, dtype=dtype, seed=1), rnd(T, Hk, Dk, dtype=dtype, seed=2), \
+        rnd(T, Hv, Dv, dtype=dtype, seed=3)
+    a_raw, b_raw = rnd(T, Hv, dtype=dtype, seed=4), rnd(T, Hv, dtype=dtype, seed=5)
+    A = -(torch.rand(Hv, device=DEV) * 2 + 0.2)
+    dt_bias = torch.rand(Hv, device=DEV)
+    g = A * torch.nn.functional.softplus(a_raw.float() + dt_bias)
+    beta = torch.sigmoid(b_raw.float())
+    pool0 = rnd(4, Hv, Dk, Dv, dtype=torch.float32, scale=0.1, seed=6)
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, 37, 38, 54], dtype=torch.int32, device=DEV)
+    rep = Hv // Hk
+    # per token two Dk-long FP32 dots whose error feeds the next token; fast exp / rsqrt
+    # intrinsics add about 2^-21 per use
+    tol = Tolerance.dot(Dk, out=torch.float32).then(Tolerance(0.0, 2.0 ** -19, True)).scaled(max(lens))
+    for mode in ("given", "raw"):
+        pool = pool0.clone()
+        if mode == "given":
+            out = GD.gated_delta_rule_packed(q, k, v, pool, cu, slots, g=g.contiguous(),
+                                             beta=beta.contiguous())
+        else:
+            out = GD.gated_delta_rule_packed(q, k, v, pool, cu, slots, raw=(a_raw, b_raw, A, dt_bias))
+        lo = 0
+        for n, s in zip(lens, slots.tolist()):
+            sl = slice(lo, lo + n)
+            ref_o, ref_S = GD.gated_delta_rule_steps(
+                q[sl].cpu().repeat_interleave(rep, 1), k[sl].cpu().repeat_interleave(rep, 1),
+                v[sl].cpu(), g[sl].cpu(), beta[sl].cpu(), pool0[s].cpu())
+            tol.check(out[sl], ref_o, f"gated delta rule output ({mode})")
+            tol.check(pool[s], ref_S, f"gated delta rule state ({mode})")
+            lo += n
+        Tolerance.exact().check(pool[1], pool0[1], "untouched slot")
+    # the dispatching entry point (one sequence, expanded heads) takes the kernel on a GPU
+    qe, ke = q[:37].repeat_interleave(rep, 1), k[:37].repeat_interleave(rep, 1)
+    o2, S2 = GD.gated_delta_rule(qe, ke, v[:37], g[:37], beta[:37], pool0[2])
+    ref_o, ref_S = GD.gated_delta_rule_chunked(qe.cpu(), ke.cpu(), v[:37].cpu(), g[:37].cpu(),
+                                               beta[:37].cpu(), pool0[2].cpu())
+    tol.check(o2, ref_o, "gated delta rule vs the chunked form")
+    tol.check(S2, ref_S, "state vs the chunked form")
+
+
+def test_rmsnorm_gated_kernel():
+    from uniserve_v1_b200.ops import gated_delta as GD
+    T, Hv, Dv = 19, 8, 128
+    x = rnd(T, Hv, Dv, dtype=torch.float32, seed=1)
+    w = rnd(Dv, seed=2)
+    wide = rnd(T, Hv * Dv + 32, seed=3)
+    z = wide[:, 16:16 + Hv * Dv].unflatten(1, (Hv, Dv))
+    y = GD.rmsnorm_gated(x, w, z, 1e-6)
+    assert y.dtype == BF
+    ref = GD.rmsnorm_gated(x.cpu().to(BF).float().to(BF), w.cpu(), z.cpu(), 1e-6)
+    # the restatement rounds x to bf16 first; the kernel normalises the FP32 values
+    Tolerance.rounding(Dv, out=BF, inputs=BF).then(BF16_STORE).then(BF16_STORE).check(y, ref, "rmsnorm_gated")
+
+
+def test_hybrid_model_on_the_kernels_matches_restatement():
+    """The Qwen3.5-style hybrid model with its linear-attention layers on the recurrent
+    kernels against the same bf16 model with those layers on the PyTorch restatement: logits
+    of a prompt run in chunks and the recurrent state after it."""
+    from uniserve_v1_b200.models.qwen3_5 import Qwen35MoeModel
+    from uniserve_v1_b200.ops import gated_delta as GD
+    cfg = Qwen35MoeModel.tiny_config()
+    model = Qwen35MoeModel(cfg, DEV, BF).init_random(seed=0)
+    prompt = torch.tensor([(7 * i + 3) % cfg.vocab_size for i in range(45)], device=DEV)
+    runs = {}
+    for use in (True, False):
+        GD.USE_KERNELS = use
+        try:
+            st = model.new_state()
+            runs[use] = ([model.forward(prompt[lo:lo + 20], st, lo) for lo in (0, 20, 40)], st)
+        finally:
+            GD.USE_KERNELS = True
+    for a, b in zip(runs[True][0], runs[False][0]):
+        cos = torch.nn.functional.cosine_similarity(a.float(), b.float(), dim=-1)
+        assert float(cos.min()) > 0.995, f"cosine {float(cos.min()):.4f}"
+    for i, (a, b) in enumerate(zip(runs[True][1], runs[False][1])):
+        if a.rule is not None:
+            rel = (a.rule - b.rule).norm() / b.rule.norm()
+            assert float(rel) < 0.02, f"layer {i}: recurrent state off by {float(rel):.3f}"

@@ -56,6 +56,7 @@ def _worker(rank, world, port, q):
     residual = None
     ref_res = None
     ok = True
+    budget = 1e-4        # FP32 sums in another order; grows by what the routed rounds may add
     for it in range(4):
         fc.begin_forward()
         g = torch.Generator(device=dev).manual_seed(100 * it + rank)
@@ -71,13 +72,19 @@ def _worker(rank, world, port, q):
                                                    routed=(rows, perm, wts))
             pick = rows.float()[perm.clamp_min(0).long()] * (perm >= 0)[..., None] * wts[..., None]
             mine = pick.sum(1).to(torch.bfloat16)
+            # the kernel adds a token's k rows in its own order before it rounds the partial
+            # row to bf16 for the push: one bf16 unit round-off per rank, relative to the
+            # largest partial value
+            top = mine.float().abs().max()
+            dist.all_reduce(top, op=dist.ReduceOp.MAX)
+            budget += world * 2.0 ** -8 * float(top)
         total = mine.float().clone()
         dist.all_reduce(total)          # NCCL reference sum of the bf16 partials in fp32
         ref_res = total if ref_res is None else ref_res + total
         y_ref = (ref_res * torch.rsqrt(ref_res.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float())
         torch.cuda.synchronize()
-        ok &= bool(torch.allclose(residual, ref_res, atol=1e-4, rtol=1e-4))
-        ok &= bool(torch.allclose(y.float(), y_ref, atol=3e-2, rtol=3e-2))
+        ok &= bool(torch.allclose(residual, ref_res, atol=budget, rtol=1e-4))
+        ok &= bool(torch.allclose(y.float(), y_ref, atol=3e-2 + 2 * budget, rtol=3e-2))
     result["fused_norm"] = ok
     # every rank formed the same sum in the same order: bitwise equal results
     mine_sum = residual.double().sum().item()

@@ -23,6 +23,15 @@
 //
 // Roles: warps 0-3 softmax / output, warp 4 TMA producer, warp 5 TMEM owner +
 // MMA issuer.  Every wait is bounded.
+//
+// FP8 pages (template FP8): a page plane holds E4M3 bytes and one FP32 scale per page.  The
+// TMA producer fetches the raw 16 KiB tiles; four more warps (6-9, one key row per thread)
+// expand them to FP16 into the operand buffers in the layout the bf16 fetch would have
+// produced, so the multiplications are the same instructions with FP16 operand formats
+// (Q and P are written as FP16 too).  The page scales never touch the tiles: the key
+// scale multiplies the key's score, the value scale its probability, in the softmax
+// threads.  HBM traffic per key halves; the expansion runs while the next tiles land.
+#include <cuda_fp8.h>
 #include "include/us_common.cuh"
 #include "include/us_tc05.cuh"
 #include "include/us_tmap.h"
@@ -48,7 +57,34 @@ struct DecTcArgs {
   int B, Hq, Hkv, max_pages, page_size, splits, window;
   float scale_log2;
   unsigned int* status;
+  const float* k_scale;   // FP8 pages: one scale per page and plane
+  const float* v_scale;
 };
+
+constexpr int kRawBytes = kTileKeys * 128;   // one E4M3 tile: 128 keys x 128 bytes
+
+// Thread `row` expands its key row of an E4M3 tile (128-byte rows, 128-byte swizzle) into the
+// two 64-column FP16 halves of an operand buffer.
+__device__ __forceinline__ void expand_row(const uint8_t* raw, uint8_t* buf, int row) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint4 in = *reinterpret_cast<const uint4*>(raw + tc::sw128_offset(row, c));
+    const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[j] & 0xffffu), __NV_E4M3);
+      const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[j] >> 16), __NV_E4M3);
+      o[2 * j] = (uint32_t)lo.x | ((uint32_t)lo.y << 16);
+      o[2 * j + 1] = (uint32_t)hi.x | ((uint32_t)hi.y << 16);
+    }
+    uint8_t* half = buf + (c >> 2) * kHalfBytes;
+    *reinterpret_cast<uint4*>(half + tc::sw128_offset(row, (2 * c) & 7)) =
+        make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(half + tc::sw128_offset(row, (2 * c + 1) & 7)) =
+        make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -110,8 +146,8 @@ __device__ __forceinline__ void merge_if_last(const DecTcArgs& a, int b, int hk)
         us::f2bf(den[g] > 0.f ? acc[g] / den[g] : 0.f);
 }
 
-template <int G>
-__global__ void __launch_bounds__(192)
+template <int G, bool FP8>
+__global__ void __launch_bounds__(FP8 ? 320 : 192)
 paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const DecTcArgs a) {
   US_PDL_PROLOGUE();
@@ -151,7 +187,9 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
   uint8_t* sV = smem + kTileBytes;
-  uint8_t* sQ = smem + 2 * kTileBytes;
+  uint8_t* sRawK = smem + 2 * kTileBytes;              // FP8 only
+  uint8_t* sRawV = sRawK + kRawBytes;
+  uint8_t* sQ = smem + 2 * kTileBytes + (FP8 ? 2 * kRawBytes : 0);
   uint8_t* sP = sQ + 2 * kSmallHalf;
   float* red = (float*)(sP + 2 * kSmallHalf);       // [2][4 warps][16] reduction scratch
   uint64_t* bars = (uint64_t*)(red + 2 * 4 * kNPad);
@@ -162,14 +200,22 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
   uint64_t* s_full = bars + 4;
   uint64_t* p_full = bars + 5;
   uint64_t* o_full = bars + 6;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 7);
+  uint64_t* rawk_full = bars + 7;    // FP8: the raw tile has landed / has been expanded
+  uint64_t* rawk_empty = bars + 8;
+  uint64_t* rawv_full = bars + 9;
+  uint64_t* rawv_empty = bars + 10;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 11);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   if (tid == 0) {
-    tc::mbar_init(k_full, 1);
+    tc::mbar_init(k_full, FP8 ? 128 : 1);     // FP8: the expanding threads fill the operand
     tc::mbar_init(k_empty, 1);
-    tc::mbar_init(v_full, 1);
+    tc::mbar_init(v_full, FP8 ? 128 : 1);
     tc::mbar_init(v_empty, 1);
+    tc::mbar_init(rawk_full, 1);
+    tc::mbar_init(rawk_empty, 128);
+    tc::mbar_init(rawv_full, 1);
+    tc::mbar_init(rawv_empty, 128);
     tc::mbar_init(s_full, 1);
     tc::mbar_init(p_full, 128);
     tc::mbar_init(o_full, 1);
@@ -200,7 +246,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
         const int row = pg[i] * a.page_size;
         uint8_t* dst = buf + i * a.page_size * 128;
         tc::tma_load_2d(dst, tm, bar, hk * kD, row);
-        tc::tma_load_2d(dst + kHalfBytes, tm, bar, hk * kD + 64, row);
+        if (!FP8) tc::tma_load_2d(dst + kHalfBytes, tm, bar, hk * kD + 64, row);
       }
     }
   };
@@ -212,10 +258,17 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
     int pg[kMaxPagesPerTile];
     load_pages(0, pg);
     if (ntiles > 1) load_pages(1, pg_next);
-    tc::mbar_expect_tx(k_full, kTileBytes);
-    issue_tile(&tmK, sK, k_full, pg);
-    tc::mbar_expect_tx(v_full, kTileBytes);
-    issue_tile(&tmV, sV, v_full, pg);
+    if (FP8) {
+      tc::mbar_expect_tx(rawk_full, kRawBytes);
+      issue_tile(&tmK, sRawK, rawk_full, pg);
+      tc::mbar_expect_tx(rawv_full, kRawBytes);
+      issue_tile(&tmV, sRawV, rawv_full, pg);
+    } else {
+      tc::mbar_expect_tx(k_full, kTileBytes);
+      issue_tile(&tmK, sK, k_full, pg);
+      tc::mbar_expect_tx(v_full, kTileBytes);
+      issue_tile(&tmV, sV, v_full, pg);
+    }
   }
   if (warp == 5) {
     tc::tmem_alloc(tmem_slot, 32);
@@ -229,6 +282,16 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
       if (g < G)
         v = *reinterpret_cast<const uint4*>(a.q + (long long)b * a.ldq +
                                             (long long)(hk * G + g) * kD + ch * 8);
+      if (FP8) {                              // operands are FP16 in this form
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+          w[j] = (uint32_t)__half_as_ushort(__float2half_rn(lo)) |
+                 ((uint32_t)__half_as_ushort(__float2half_rn(hi)) << 16);
+        }
+        v = make_uint4(w[0], w[1], w[2], w[3]);
+      }
       const int half = ch >> 3;
       *reinterpret_cast<uint4*>(sQ + half * kSmallHalf + tc::sw128_offset(g, ch & 7)) = v;
     }
@@ -252,26 +315,37 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
 #pragma unroll
         for (int i = 0; i < kMaxPagesPerTile; ++i) pg[i] = pg_next[i];
         if (t + 1 < ntiles) load_pages(t + 1, pg_next);     // in flight during the waits below
-        if (!tc::mbar_wait(k_empty, ph ^ 1u, abort_flag)) {
+        if (!tc::mbar_wait(FP8 ? rawk_empty : k_empty, ph ^ 1u, abort_flag)) {
           us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
           *abort_flag = 1;
           break;
         }
-        tc::mbar_expect_tx(k_full, kTileBytes);
-        issue_tile(&tmK, sK, k_full, pg);
-        if (!tc::mbar_wait(v_empty, ph ^ 1u, abort_flag)) {
+        if (FP8) {
+          tc::mbar_expect_tx(rawk_full, kRawBytes);
+          issue_tile(&tmK, sRawK, rawk_full, pg);
+        } else {
+          tc::mbar_expect_tx(k_full, kTileBytes);
+          issue_tile(&tmK, sK, k_full, pg);
+        }
+        if (!tc::mbar_wait(FP8 ? rawv_empty : v_empty, ph ^ 1u, abort_flag)) {
           us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
           *abort_flag = 1;
           break;
         }
-        tc::mbar_expect_tx(v_full, kTileBytes);
-        issue_tile(&tmV, sV, v_full, pg);
+        if (FP8) {
+          tc::mbar_expect_tx(rawv_full, kRawBytes);
+          issue_tile(&tmV, sRawV, rawv_full, pg);
+        } else {
+          tc::mbar_expect_tx(v_full, kTileBytes);
+          issue_tile(&tmV, sV, v_full, pg);
+        }
       }
     }
   } else if (warp == 5) {
     if (lane == 0) {
-      constexpr uint32_t kIdescQK = tc::make_idesc(128, kNPad, tc::kFmtBF16, tc::kFmtBF16, 0, 0);
-      constexpr uint32_t kIdescPV = tc::make_idesc(128, kNPad, tc::kFmtBF16, tc::kFmtBF16, 1, 0);
+      constexpr uint32_t kFmt = FP8 ? tc::kFmtF16 : tc::kFmtBF16;
+      constexpr uint32_t kIdescQK = tc::make_idesc(128, kNPad, kFmt, kFmt, 0, 0);
+      constexpr uint32_t kIdescPV = tc::make_idesc(128, kNPad, kFmt, kFmt, 1, 0);
       const uint32_t k_addr = tc::smem_u32(sK), v_addr = tc::smem_u32(sV);
       const uint32_t q_addr = tc::smem_u32(sQ), p_addr = tc::smem_u32(sP);
       auto issue_qk = [&]() {
@@ -321,6 +395,29 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
         *abort_flag = 1;
       }
     }
+  } else if (FP8 && warp >= 6) {
+    // ---- expanding threads: key row = tid - 192 of every tile ----
+    const int row = tid - 192;
+    bool ok = true;
+    for (int t = 0; ok && t < ntiles; ++t) {
+      const uint32_t ph = (uint32_t)t & 1u;
+      if (!tc::mbar_wait(rawk_full, ph, abort_flag)) { ok = false; break; }
+      if (t > 0 && !tc::mbar_wait(k_empty, ph ^ 1u, abort_flag)) { ok = false; break; }
+      expand_row(sRawK, sK, row);
+      tc::fence_async_smem();
+      tc::mbar_arrive(k_full);
+      tc::mbar_arrive(rawk_empty);
+      if (!tc::mbar_wait(rawv_full, ph, abort_flag)) { ok = false; break; }
+      if (t > 0 && !tc::mbar_wait(v_empty, ph ^ 1u, abort_flag)) { ok = false; break; }
+      expand_row(sRawV, sV, row);
+      tc::fence_async_smem();
+      tc::mbar_arrive(v_full);
+      tc::mbar_arrive(rawv_empty);
+    }
+    if (!ok) {
+      us_dev_fail(a.status, US_DEV_TIMEOUT_FULL);
+      *abort_flag = 1;
+    }
   } else {
     // ---- softmax / output threads: TMEM lane = tid ----
     const uint32_t lane_addr = ((uint32_t)(warp * 32) << 16);
@@ -335,6 +432,16 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
     bool ok = true;
     for (int t = 0; t < ntiles; ++t) {
       const uint32_t ph = (uint32_t)t & 1u;
+      float ksc = 1.f, vsc = 1.f;           // FP8: scales of this thread's key's page
+      if (FP8) {
+        const int key = k_begin + t * kTileKeys + tid;
+        const int pi = key / a.page_size;
+        if (key < k_end && pi < a.max_pages) {
+          const int pg = __ldg(pt_row + pi);
+          ksc = __ldg(a.k_scale + pg);
+          vsc = __ldg(a.v_scale + pg);
+        }
+      }
       if (!tc::mbar_wait(s_full, ph)) { ok = false; break; }
       tc::tc_fence_after_sync();
       uint32_t sr[16];
@@ -346,7 +453,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
       float* rbuf = red + (t & 1) * 4 * kNPad;
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        s[g] = valid ? __uint_as_float(sr[g]) * a.scale_log2 : -INFINITY;
+        s[g] = valid ? __uint_as_float(sr[g]) * (a.scale_log2 * ksc) : -INFINITY;
         const float wm = us::warp_max(s[g]);
         if (lane == 0) rbuf[warp * kNPad + g] = wm;
       }
@@ -382,7 +489,8 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
 #pragma unroll
         for (int g = 0; g < G; ++g) {
           uint8_t* dst = sP + half * kSmallHalf + tc::sw128_offset(g, col >> 3) + (col & 7) * 2;
-          *reinterpret_cast<__nv_bfloat16*>(dst) = us::f2bf(p[g]);
+          if (FP8) *reinterpret_cast<__half*>(dst) = __float2half_rn(p[g] * vsc);
+          else *reinterpret_cast<__nv_bfloat16*>(dst) = us::f2bf(p[g]);
         }
       }
       tc::fence_async_smem();
@@ -438,18 +546,20 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK,
   if (a.splits > 1 && a.counters) merge_if_last<G>(a, b, hk);
 }
 
-template <int G>
+template <int G, bool FP8>
 int launch_tc(const CUtensorMap& tmK, const CUtensorMap& tmV, const DecTcArgs& a,
               cudaStream_t stream) {
-  const size_t smem = 2 * kTileBytes + 4 * kSmallHalf + 2 * 4 * kNPad * 4 + 8 * 8 + 16 + 1024;
+  const size_t smem = 2 * kTileBytes + (FP8 ? 2 * kRawBytes : 0) + 4 * kSmallHalf +
+                      2 * 4 * kNPad * 4 + 12 * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
-    US_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tc_kernel<G>,
+    US_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tc_kernel<G, FP8>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
   dim3 grid(a.B, a.Hkv, a.splits);
-  us::launch_pdl(paged_decode_tc_kernel<G>, dim3(grid), dim3(192), smem, stream, tmK, tmV, a);
+  us::launch_pdl(paged_decode_tc_kernel<G, FP8>, dim3(grid), dim3(FP8 ? 320 : 192), smem, stream,
+                 tmK, tmV, a);
   US_LAUNCH_CHECK();
   return US_OK;
 }
@@ -461,7 +571,7 @@ extern "C" int us_merge_decode_splits(const float* part_o, const float* part_lse
                                       void* stream);
 
 static int decode_tc(const void* q, const void* kcache, const void* vcache,
-                     const int* page_table, const int* seq_lens, void* out, void* scratch,
+                     const float* k_scale, const float* v_scale, const int* page_table, const int* seq_lens, void* out, void* scratch,
                      int* counters, int B, int Hq, int Hkv, int D, int num_pages, int max_pages,
                      int page_size, int splits, int window, float scale, long long ldq,
                      long long ldo, void* stream_) {
@@ -474,9 +584,14 @@ static int decode_tc(const void* q, const void* kcache, const void* vcache,
   cudaStream_t stream = (cudaStream_t)stream_;
   CUtensorMap tmK, tmV;
   const uint64_t rows = (uint64_t)num_pages * page_size, cols = (uint64_t)Hkv * D;
-  int rc = us_tmap_2d(&tmK, kcache, US_TMAP_BF16, rows, cols, cols, page_size, 64, US_SWZ_128);
+  const bool fp8 = k_scale != nullptr;
+  US_REQUIRE(!fp8 || v_scale != nullptr);
+  // bf16 pages are fetched as two 64-column halves per page, E4M3 pages as one 128-byte box
+  int rc = us_tmap_2d(&tmK, kcache, fp8 ? US_TMAP_U8 : US_TMAP_BF16, rows, cols, cols, page_size,
+                      fp8 ? 128 : 64, US_SWZ_128);
   if (rc) return rc;
-  rc = us_tmap_2d(&tmV, vcache, US_TMAP_BF16, rows, cols, cols, page_size, 64, US_SWZ_128);
+  rc = us_tmap_2d(&tmV, vcache, fp8 ? US_TMAP_U8 : US_TMAP_BF16, rows, cols, cols, page_size,
+                  fp8 ? 128 : 64, US_SWZ_128);
   if (rc) return rc;
   DecTcArgs a;
   a.q = (const __nv_bfloat16*)q;
@@ -491,14 +606,27 @@ static int decode_tc(const void* q, const void* kcache, const void* vcache,
   a.splits = splits; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = us_status_ptr();
+  a.k_scale = k_scale;
+  a.v_scale = v_scale;
   const int G = Hq / Hkv;
-  switch (G) {
-    case 1: rc = launch_tc<1>(tmK, tmV, a, stream); break;
-    case 2: rc = launch_tc<2>(tmK, tmV, a, stream); break;
-    case 4: rc = launch_tc<4>(tmK, tmV, a, stream); break;
-    case 8: rc = launch_tc<8>(tmK, tmV, a, stream); break;
-    case 16: rc = launch_tc<16>(tmK, tmV, a, stream); break;
-    default: return US_ERR_UNSUPPORTED;
+  if (fp8) {
+    switch (G) {
+      case 1: rc = launch_tc<1, true>(tmK, tmV, a, stream); break;
+      case 2: rc = launch_tc<2, true>(tmK, tmV, a, stream); break;
+      case 4: rc = launch_tc<4, true>(tmK, tmV, a, stream); break;
+      case 8: rc = launch_tc<8, true>(tmK, tmV, a, stream); break;
+      case 16: rc = launch_tc<16, true>(tmK, tmV, a, stream); break;
+      default: return US_ERR_UNSUPPORTED;
+    }
+  } else {
+    switch (G) {
+      case 1: rc = launch_tc<1, false>(tmK, tmV, a, stream); break;
+      case 2: rc = launch_tc<2, false>(tmK, tmV, a, stream); break;
+      case 4: rc = launch_tc<4, false>(tmK, tmV, a, stream); break;
+      case 8: rc = launch_tc<8, false>(tmK, tmV, a, stream); break;
+      case 16: rc = launch_tc<16, false>(tmK, tmV, a, stream); break;
+      default: return US_ERR_UNSUPPORTED;
+    }
   }
   if (rc) return rc;
   if (splits > 1 && !counters)
@@ -514,8 +642,9 @@ US_API int us_paged_decode_attention_tc(const void* q, const void* kcache, const
                                         int num_pages, int max_pages, int page_size, int splits,
                                         int window, float scale, long long ldq, long long ldo,
                                         void* stream_) {
-  return decode_tc(q, kcache, vcache, page_table, seq_lens, out, scratch, nullptr, B, Hq, Hkv, D,
-                   num_pages, max_pages, page_size, splits, window, scale, ldq, ldo, stream_);
+  return decode_tc(q, kcache, vcache, nullptr, nullptr, page_table, seq_lens, out, scratch, nullptr,
+                   B, Hq, Hkv, D, num_pages, max_pages, page_size, splits, window, scale, ldq, ldo,
+                   stream_);
 }
 
 // One launch: `counters` [B * Hkv] int32 must be zero before the first call and is left zero
@@ -529,6 +658,23 @@ US_API int us_paged_decode_attention_tc_merged(const void* q, const void* kcache
                                                int splits, int window, float scale,
                                                long long ldq, long long ldo, void* stream_) {
   US_REQUIRE((splits == 1 || counters != nullptr) && splits <= 32);
-  return decode_tc(q, kcache, vcache, page_table, seq_lens, out, scratch, counters, B, Hq, Hkv, D,
-                   num_pages, max_pages, page_size, splits, window, scale, ldq, ldo, stream_);
+  return decode_tc(q, kcache, vcache, nullptr, nullptr, page_table, seq_lens, out, scratch,
+                   counters, B, Hq, Hkv, D, num_pages, max_pages, page_size, splits, window, scale,
+                   ldq, ldo, stream_);
+}
+
+// E4M3 pages with one FP32 scale per page and plane (k_scale, v_scale [num_pages]); the
+// other arguments as above.  `counters` may be null (the splits are then merged by a second
+// launch).
+US_API int us_paged_decode_attention_fp8(const void* q, const void* kcache, const void* vcache,
+                                         const float* k_scale, const float* v_scale,
+                                         const int* page_table, const int* seq_lens, void* out,
+                                         void* scratch, int* counters, int B, int Hq, int Hkv,
+                                         int D, int num_pages, int max_pages, int page_size,
+                                         int splits, int window, float scale, long long ldq,
+                                         long long ldo, void* stream_) {
+  US_REQUIRE(k_scale && v_scale && splits <= 32);
+  return decode_tc(q, kcache, vcache, k_scale, v_scale, page_table, seq_lens, out, scratch,
+                   counters, B, Hq, Hkv, D, num_pages, max_pages, page_size, splits, window, scale,
+                   ldq, ldo, stream_);
 }

@@ -475,6 +475,13 @@ __device__ __forceinline__ void swapped_tile(int t, int m_pairs, int n_tiles, in
 // instruction produces both halves and a thread finds value j in column j and its
 // gate in column 128 + j of its own lane.  The caller passes the activation's map
 // as tmA and the weight's as tmBs.m[0].
+// Whether the swapped epilogue's rows go to other GPUs' buffers (env US_GEMM_LINES=0 keeps
+// the per-thread 32-byte pieces for an A/B measurement; the host sets args.remote_lines).
+__device__ __forceinline__ bool remote_lines(const GemmArgs& a) {
+  return a.remote_lines != 0 &&
+         (a.route_map != nullptr || a.peer_rows > 0 || a.peer_cols > 0);
+}
+
 template <int BN, bool DUAL, bool FP8, int SWAP>
 __global__ void __launch_bounds__(192)
 gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -729,6 +736,13 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
             dst = (char*)args.out + (size_t)xrow * args.ldo * esz;
           }
         }
+        // Rows that leave for another GPU go out as whole 128-byte lines: a thread's 32-byte
+        // pieces of 32 different rows would cross NVLink as 32 small packets per store
+        // instruction.  The warp collects 64 features of its 32 rows in its 4 KiB of the
+        // staging area (16-byte chunks XOR-swizzled by row) and writes them back out with
+        // eight lanes per row; the row's destination comes from the lane that owns it.
+        const bool lines = remote_lines(args) && esz == 2 && vec && (M % 64) == 0;
+        uint8_t* wstage = epi_stage + q * 4096;
 #pragma unroll 1
         for (int c = 0; c < kFeat; c += 16) {
           if (f0 + c >= M) break;             // uniform: features past the last one
@@ -758,6 +772,42 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
             for (int j = 0; j < 16; ++j)
               if (f0 + c + j < M)
                 x[j] += bias_f ? bias_f[f0 + c + j] : us::bf2f(bias_h[f0 + c + j]);
+          }
+          if (lines) {
+            const int ch = (c & 63) >> 3;     // first of this piece's two 16-byte chunks
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              o[j] = (uint32_t)__bfloat16_as_ushort(us::f2bf(x[2 * j] * post)) |
+                     ((uint32_t)__bfloat16_as_ushort(us::f2bf(x[2 * j + 1] * post)) << 16);
+            *reinterpret_cast<uint4*>(wstage + lane * 128 + ((ch ^ (lane & 7)) << 4)) =
+                make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(wstage + lane * 128 + (((ch + 1) ^ (lane & 7)) << 4)) =
+                make_uint4(o[4], o[5], o[6], o[7]);
+            if ((c & 63) != 48) continue;
+            // this lane's row, features [f0 + c - 48, f0 + c + 16)
+            const int fb = f0 + c - 48;
+            char* d64 = nullptr;
+            if (dst != nullptr) {
+              d64 = dst + (size_t)fb * 2;
+              if (peer_cols > 0) {
+                const int p = fb / peer_cols;
+                d64 = (char*)args.peer_out[p] +
+                      ((size_t)(args.peer_row_offset + xrow) * args.ldo + (fb - p * peer_cols)) * 2;
+              }
+            }
+            __syncwarp();
+            const unsigned long long mine = (unsigned long long)(uintptr_t)d64;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3), cc = lane & 7;
+              const unsigned long long dp = __shfl_sync(0xffffffffu, mine, r);
+              const uint4 val =
+                  *reinterpret_cast<const uint4*>(wstage + r * 128 + ((cc ^ (r & 7)) << 4));
+              if (dp != 0ull) *reinterpret_cast<uint4*>((char*)(uintptr_t)dp + cc * 16) = val;
+            }
+            __syncwarp();
+            continue;
           }
           if (dst == nullptr) continue;
           char* d = dst + (size_t)(f0 + c) * esz;
@@ -1176,6 +1226,11 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
     bool ok = ((ldo * esz) % 16) == 0 && ((uintptr_t)out % 16) == 0;
     for (int p = 0; p < 8; ++p) ok = ok && ((uintptr_t)a.peer_out[p] % 16) == 0;
     a.vec_store = ok ? 1 : 0;
+    static const int lines = [] {
+      const char* e = getenv("US_GEMM_LINES");
+      return (e && e[0] == '0') ? 0 : 1;
+    }();
+    a.remote_lines = lines;
   }
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
   const int n_tiles = num_tiles ? max_tiles : (x_rows + block_n - 1) / block_n;

@@ -281,6 +281,20 @@ class Qwen35MoeModel:
         proj = F.linear(n, L["qkvz"])
         mixed, z = proj[:, :2 * kd + vd], proj[:, 2 * kd + vd:2 * kd + 2 * vd]
         b, a = proj[:, 2 * kd + 2 * vd:2 * kd + 2 * vd + Hv], proj[:, 2 * kd + 2 * vd + Hv:]
+        if n.is_cuda and GD.USE_KERNELS and Dk in GD._KERNEL_DK:
+            # kernels: the convolution reads the projection in place, the rule reads q / k / v
+            # as views of the convolved rows (a key head serves Hv / Hk value heads) and forms
+            # the gates from the raw projections; the state is updated where it lives
+            mixed, st.conv = GD.causal_conv1d(mixed, L["conv"], st.conv)
+            if st.rule is None:
+                st.rule = torch.zeros(Hv, Dk, Dv, dtype=torch.float32, device=n.device)
+            cu, slots = GD._one_sequence(T, n.device)
+            o = GD.gated_delta_rule_packed(
+                mixed[:, :kd].view(T, Hk, Dk), mixed[:, kd:2 * kd].view(T, Hk, Dk),
+                mixed[:, 2 * kd:].view(T, Hv, Dv), st.rule.unsqueeze(0), cu, slots,
+                raw=(a, b, L["A"].float().contiguous(), L["dt_bias"].float().contiguous()))
+            o = GD.rmsnorm_gated(o, L["gnorm"], z.unflatten(1, (Hv, Dv)), c.rms_norm_eps)
+            return F.linear(o.reshape(T, vd), L["out"])
         mixed, st.conv = GD.causal_conv1d(mixed.contiguous(), L["conv"], st.conv)
         q = mixed[:, :kd].reshape(T, Hk, Dk)
         k = mixed[:, kd:2 * kd].reshape(T, Hk, Dk)
@@ -364,6 +378,26 @@ class Qwen35MoeModel:
                 mixed, z = proj[:, :2 * kd + vd], proj[:, 2 * kd + vd:2 * kd + 2 * vd]
                 bb, aa = proj[:, 2 * kd + 2 * vd:2 * kd + 2 * vd + Hv], proj[:, 2 * kd + 2 * vd + Hv:]
                 Kc = L["conv"].shape[1]
+                if x.is_cuda and GD.USE_KERNELS and Dk in GD._KERNEL_DK:
+                    # one packed launch per operator over the batch; the per-request states
+                    # are slots of a pool that the kernels update in place
+                    pool_c = torch.stack([states[b][i].conv if states[b][i].conv is not None else
+                                          torch.zeros(Kc - 1, mixed.shape[1], dtype=mixed.dtype,
+                                                      device=mixed.device) for b in range(B)])
+                    pool_r = torch.stack([states[b][i].rule if states[b][i].rule is not None else
+                                          torch.zeros(Hv, Dk, Dv, device=x.device) for b in range(B)])
+                    cu = torch.arange(B + 1, dtype=torch.int32, device=x.device)
+                    y, _ = GD.causal_conv1d(mixed, L["conv"], pool_c, cu=cu, slots=cu[:B])
+                    o = GD.gated_delta_rule_packed(
+                        y[:, :kd].view(B, Hk, Dk), y[:, kd:2 * kd].view(B, Hk, Dk),
+                        y[:, 2 * kd:].view(B, Hv, Dv), pool_r, cu, cu[:B],
+                        raw=(aa, bb, L["A"].float().contiguous(), L["dt_bias"].float().contiguous()))
+                    for b in range(B):
+                        states[b][i].conv, states[b][i].rule = pool_c[b], pool_r[b]
+                    o = GD.rmsnorm_gated(o, L["gnorm"], z.unflatten(1, (Hv, Dv)), c.rms_norm_eps)
+                    x = x + F.linear(o.reshape(B, vd), L["out"])
+                    x = x + self._mlp(L, R.rmsnorm(x, L["post_norm"], c.rms_norm_eps))
+                    continue
                 conv = torch.stack([states[b][i].conv if states[b][i].conv is not None else
                                     torch.zeros(Kc - 1, mixed.shape[1], dtype=mixed.dtype,
                                                 device=mixed.device) for b in range(B)])

@@ -40,6 +40,10 @@ _SIGNATURES = {
     "us_gemm_wx": (I, [P, P, P, I, I, I, I, I, L, L, L, I, I, I, I, P, I, P, P, P, P, P, P, I, I, P]),
     "us_gemm_wx_hint": (I, [I]),
     "us_linear_decode": (I, [P, P, P, P, I, I, I, L, L, L, I, I, P]),
+    "us_causal_conv1d": (I, [P, L, P, P, P, L, P, P, I, I, I, I, I, I, P]),
+    "us_gated_delta_rule": (I, [P, P, P, L, L, L, I, I, I, I, P, P, P, P, L, P, P, P, P, P, P,
+                                I, I, I, I, I, F, P]),
+    "us_rmsnorm_gated": (I, [P, P, P, L, I, P, I, I, I, F, I, P]),
     "us_rmsnorm": (I, [P, P, P, I, I, L, L, F, P]),
     "us_add_rmsnorm": (I, [P, P, P, P, I, I, F, I, P]),
     "us_modulated_rmsnorm": (I, [P, P, P, P, I, I, I, P, I, I, F, P]),
