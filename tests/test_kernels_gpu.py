@@ -689,9 +689,9 @@ def test_rmsnorm_gated_kernel():
     z = wide[:, 16:16 + Hv * Dv].unflatten(1, (Hv, Dv))
     y = GD.rmsnorm_gated(x, w, z, 1e-6)
     assert y.dtype == BF
-    ref = GD.rmsnorm_gated(x.cpu().to(BF).float().to(BF), w.cpu(), z.cpu(), 1e-6)
-    # the restatement rounds x to bf16 first; the kernel normalises the FP32 values
-    Tolerance.rounding(Dv, out=BF, inputs=BF).then(BF16_STORE).then(BF16_STORE).check(y, ref, "rmsnorm_gated")
+    ref = GD.rmsnorm_gated(x.cpu().to(BF), w.cpu(), z.cpu(), 1e-6)
+    # both round x to bf16 first, the normalised value and its product with w once each
+    Tolerance.rounding(Dv, out=BF).then(BF16_STORE).then(BF16_STORE).check(y, ref, "rmsnorm_gated")
 
 
 def test_hybrid_model_on_the_kernels_matches_restatement():
@@ -718,3 +718,117 @@ def test_hybrid_model_on_the_kernels_matches_restatement():
         if a.rule is not None:
             rel = (a.rule - b.rule).norm() / b.rule.norm()
             assert float(rel) < 0.02, f"layer {i}: recurrent state off by {float(rel):.3f}"
+
+
+# ----------------------------------------------------------- FP8 KV pages --
+def test_kv_write_scaled_matches_the_page_rule():
+    """The scaled page write against its CPU restatement through a prefill-sized launch (runs
+    of rows per page, a skipped row) and two decode-sized appends, one of which grows a
+    page's scale and re-encodes it."""
+    page, Hkv, D, pages = 16, 4, 128, 12
+    kc = torch.zeros(pages, page, Hkv, D, dtype=torch.uint8, device=DEV)
+    vc = torch.zeros_like(kc)
+    ks = torch.zeros(pages, dtype=torch.float32, device=DEV)
+    vs = torch.zeros_like(ks)
+    ref = [t.cpu().clone() for t in (kc, vc, ks, vs)]
+    # two sequences: pages (3, 7, 1) rows 0..36 and pages (5,) rows 0..8; one skipped row
+    slots = [3 * page + i for i in range(16)] + [7 * page + i for i in range(16)] + \
+        [1 * page + i for i in range(5)] + [-1] + [5 * page + i for i in range(9)]
+    steps = [(slots, 1.0), ([1 * page + 5, 5 * page + 9], 0.3), ([1 * page + 6, 5 * page + 10], 6.0)]
+    for n, (sl, mag) in enumerate(steps):
+        T = len(sl)
+        wide = rnd(T, (8 + 2 * Hkv) * D, scale=mag, seed=10 + n)
+        v3 = wide.view(T, 8 + 2 * Hkv, D)
+        k, v = v3[:, 8:8 + Hkv], v3[:, 8 + Hkv:]                 # views of a fused projection
+        st = torch.tensor(sl, dtype=torch.int32, device=DEV)
+        F.kv_write_scaled(k, v, st, kc, vc, ks, vs)
+        R.kv_write_scaled(ref[0], ref[1], ref[2], ref[3], k.cpu(), v.cpu(), st.cpu())
+        torch.cuda.synchronize()
+        # the scale is one FP32 division of the same maximum on both sides
+        Tolerance(0.0, 2.0 ** -22).check(ks, ref[2], f"key scales, step {n}")
+        Tolerance(0.0, 2.0 ** -22).check(vs, ref[3], f"value scales, step {n}")
+        # bytes: the same rounding of the same quotient up to the last bit of the FP32
+        # reciprocal; compare the decoded values within one E4M3 step (2^-3 relative)
+        tol = Tolerance(float(ref[2].max()) * 2.0 ** -9, 2.0 ** -3)
+        tol.check(R.kv_dequant(kc.cpu(), ks.cpu()), R.kv_dequant(ref[0], ref[2]), f"key pages {n}")
+        tol.check(R.kv_dequant(vc.cpu(), vs.cpu()), R.kv_dequant(ref[1], ref[3]), f"value pages {n}")
+        same = (kc.cpu() == ref[0]).float().mean()
+        assert float(same) > 0.995, f"step {n}: {float(same):.4f} of the key bytes agree"
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,ctx,splits", [(4, 32, 4, 300, 1), (3, 8, 1, 1100, 3),
+                                                 (64, 32, 4, 1040, 1)])
+def test_paged_decode_attention_fp8_pages(B, Hq, Hkv, ctx, splits):
+    """E4M3 pages with per-page scales against the FP32 restatement over the decoded values:
+    what differs is FP16 rounding of Q and P and the accumulation order."""
+    D, page = 128, 16
+    per = (ctx + page - 1) // page
+    pages = B * per + 1
+    g = torch.Generator(device=DEV).manual_seed(5)
+    kc = torch.randint(0, 256, (pages, page, Hkv, D), dtype=torch.uint8, device=DEV, generator=g)
+    vc = torch.randint(0, 256, (pages, page, Hkv, D), dtype=torch.uint8, device=DEV, generator=g)
+    nan = lambda t: (t & 0x7F) == 0x7F                       # the two E4M3 NaN encodings
+    kc[nan(kc)] = 0
+    vc[nan(vc)] = 0
+    ks = (torch.rand(pages, device=DEV, generator=g) * 0.004 + 0.0005)
+    vs = (torch.rand(pages, device=DEV, generator=g) * 0.01 + 0.001)
+    q = rnd(B, Hq, D, seed=6)
+    pt = (torch.randperm(pages - 1, device=DEV, generator=g)[:B * per].view(B, per) + 1).to(torch.int32)
+    sl = torch.tensor([ctx - (7 * b) % 50 for b in range(B)], dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(D)
+    scratch, counters = F.decode_scratch(B, Hq, Hkv, D, splits, DEV)
+    out = F.paged_decode_attention(q, kc, vc, pt, sl, scale, splits, scratch=scratch,
+                                   counters=counters if splits > 1 else None, k_scale=ks, v_scale=vs)
+    ref = R.paged_decode_attention(q.cpu().float(), kc.cpu(), vc.cpu(), pt.cpu(), sl.cpu(), scale, 0,
+                                   ks.cpu(), vs.cpu())
+    # scores: D products with Q rounded to FP16; probabilities rounded to FP16, ctx of them
+    # summed against values that are exact in FP16; one bf16 store
+    f16 = torch.float16
+    smax = float(q.float().abs().max()) * 448.0 * float(ks.max()) * math.sqrt(D) * scale
+    tol = Tolerance.dot(D, out=torch.float32, inputs=f16).scaled(max(1.0, smax)) \
+        .then(Tolerance.dot(ctx, out=BF, inputs=f16)).then(BF16_STORE)
+    tol.check(out, ref, "fp8 paged decode attention")
+
+
+def test_kv_gather_and_cached_context_prefill():
+    """Pages -> packed rows through the page table (bf16 and E4M3 pages), then a chunked
+    prefill through the engine: the second chunk attends to the first through the gather and
+    gives the tokens of an unchunked run."""
+    page, Hkv, D, pages = 16, 2, 128, 20
+    kc, vc = rnd(pages, page, Hkv, D, seed=1), rnd(pages, page, Hkv, D, seed=2)
+    pt = torch.tensor([[3, 9, 4, 0], [7, 1, 0, 0]], dtype=torch.int32, device=DEV)
+    lens = [37, 20]
+    cu = torch.tensor([0, 37, 57], dtype=torch.int32, device=DEV)
+    ko, vo = F.kv_gather(kc, vc, pt, cu, 57)
+    for s, n in enumerate(lens):
+        want = kc[pt[s].long()].reshape(-1, Hkv, D)[:n]
+        Tolerance.exact().check(ko[int(cu[s]):int(cu[s]) + n], want, "gathered keys")
+        want = vc[pt[s].long()].reshape(-1, Hkv, D)[:n]
+        Tolerance.exact().check(vo[int(cu[s]):int(cu[s]) + n], want, "gathered values")
+    k8 = torch.randint(0, 120, (pages, page, Hkv, D), dtype=torch.uint8, device=DEV)
+    sc = torch.rand(pages, device=DEV) * 0.01 + 0.001
+    out_cu = torch.tensor([5, 60], dtype=torch.int32, device=DEV)       # room between sequences
+    buf = (torch.zeros(100, Hkv, D, dtype=BF, device=DEV), torch.zeros(100, Hkv, D, dtype=BF, device=DEV))
+    F.kv_gather(k8, k8, pt, cu, 57, sc, sc, out=buf, out_cu=out_cu)
+    deq = R.kv_dequant(k8.cpu(), sc.cpu())
+    for s, n in enumerate(lens):
+        want = deq[pt[s].cpu().long()].reshape(-1, Hkv, D)[:n]
+        Tolerance(0.0, 2.0 ** -8).check(buf[0][int(out_cu[s]):int(out_cu[s]) + n], want, "fp8 gather")
+    assert float(buf[0][:5].abs().max()) == 0.0
+
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    import dataclasses
+    cfg = dataclasses.replace(Qwen3MoeConfig.tiny(), head_dim=128)     # the FP8 kernel's width
+    prompts = [[(5 * i + j) % cfg.vocab_size for i in range(n)] for j, n in enumerate((150, 33, 70))]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    outs = {}
+    for name, kw in (("whole", {}), ("chunked", {"max_num_batched_tokens": 64}),
+                     ("fp8", {"max_num_batched_tokens": 64, "kv_dtype": "fp8"})):
+        model = Qwen3MoeModel(cfg, DEV, BF).init_random(seed=0)
+        eng = LLMEngine(model, num_pages=128, max_num_seqs=4, max_model_len=256, **kw)
+        outs[name] = eng.generate(prompts, sp)
+    agree = lambda a, b: sum(x == y for p, q_ in zip(a, b) for x, y in zip(p, q_)) / 24.0
+    assert agree(outs["whole"], outs["chunked"]) >= 0.9, outs
+    assert agree(outs["whole"], outs["fp8"]) >= 0.6, outs

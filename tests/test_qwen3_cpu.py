@@ -1,5 +1,6 @@
 """Tiny Qwen3-MoE on CPU: the engine (paged cache, scheduler, fused-op CPU
 formulas) must reproduce an independent FP32 reference decode."""
+import pytest
 import torch
 
 from uniserve_v1_b200.engine.engine import LLMEngine
@@ -421,3 +422,63 @@ def test_dense_state_engine_speculation_rolls_recurrent_state_back():
             assert lo <= st["accepted"] / st["proposed"] <= hi
         if isinstance(drafter, Oracle) and not isinstance(drafter, HalfWrong):
             assert steps <= 1 + 4          # one prompt step, then ceil(10 / 4) + 1 verifications
+
+
+def test_fp8_kv_pages_write_rule_and_engine_tokens():
+    """The scaled page write on the CPU restatement: a page's scale is the largest magnitude
+    it has seen / 448, rows written earlier are re-encoded when it grows, a row at offset 0
+    starts the page afresh; then an engine with E4M3 pages gives (nearly) the tokens of the
+    bf16-page engine and its hand-off carries floating-point pages."""
+    from uniserve_v1_b200.ops import reference as R
+    page, Hkv, D = 4, 2, 8
+    kc = torch.zeros(3, page, Hkv, D, dtype=torch.uint8)
+    vc = torch.zeros_like(kc)
+    ks, vs = torch.zeros(3), torch.zeros(3)
+    g = torch.Generator().manual_seed(0)
+    k1 = torch.randn(2, Hkv, D, generator=g)
+    R.kv_write_scaled(kc, vc, ks, vs, k1, k1 * 2, torch.tensor([4, 5]))          # page 1, rows 0-1
+    assert float(ks[1]) == pytest.approx(float(k1.abs().max()) / 448.0)
+    assert float(vs[1]) == pytest.approx(float(k1.abs().max()) * 2 / 448.0)
+    big = torch.randn(1, Hkv, D, generator=g) * 10
+    R.kv_write_scaled(kc, vc, ks, vs, big, big, torch.tensor([6]))               # grows the scale
+    assert float(ks[1]) == pytest.approx(float(big.abs().max()) / 448.0)
+    back = R.kv_dequant(kc, ks)[1]
+    assert torch.allclose(back[2], big[0], rtol=0.07, atol=float(ks[1]))
+    assert torch.allclose(back[:2], k1, rtol=0.07, atol=float(ks[1]) * 2)        # re-encoded rows
+    small = torch.randn(1, Hkv, D, generator=g) * 0.01
+    R.kv_write_scaled(kc, vc, ks, vs, small, small, torch.tensor([4]))           # offset 0: afresh
+    assert float(ks[1]) == pytest.approx(float(small.abs().max()) / 448.0)
+    assert float(ks[0]) == 0.0 and float(ks[2]) == 0.0
+
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.handoff import export_request, import_request
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    cfg = Qwen3MoeConfig.tiny()
+    prompts = [[(5 * i + j) % cfg.vocab_size for i in range(n)] for j, n in enumerate((21, 9, 40))]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    outs = {}
+    for kv in (None, "fp8"):
+        model = Qwen3MoeModel(cfg, "cpu", torch.float32).init_random(seed=0)
+        eng = LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128, use_graphs=False,
+                        max_num_batched_tokens=16, kv_dtype=kv)            # chunked prefill too
+        outs[kv] = eng.generate(prompts, sp)
+        if kv == "fp8":
+            assert eng.runner.kv_caches[0][0].dtype == torch.uint8
+            rid = eng.add_request(prompts[0], SamplingParams(temperature=0.0, max_tokens=6,
+                                                             ignore_eos=True))
+            while eng.scheduler.requests[rid].num_computed < len(prompts[0]):
+                eng.step()
+            h = export_request(eng, rid)
+            assert h.kv[0][0].dtype == torch.bfloat16
+            model2 = Qwen3MoeModel(cfg, "cpu", torch.float32).init_random(seed=0)
+            eng2 = LLMEngine(model2, num_pages=64, max_num_seqs=4, max_model_len=128,
+                             use_graphs=False, kv_dtype="fp8")
+            import_request(eng2, [h])
+            done = []
+            while eng2.has_work():
+                done += [o for o in eng2.step() if o.finished]
+            assert done and len(eng2.scheduler.requests) >= 0
+    same = sum(a == b for x, y in zip(outs[None], outs["fp8"]) for a, b in zip(x, y))
+    total = sum(len(x) for x in outs[None])
+    assert same >= 0.7 * total, (outs[None], outs["fp8"])

@@ -268,6 +268,7 @@ def serve(args) -> int:
                                            if pkg.kv_cache_config.host_tier else 0.0),
                             host_kv_gib=pkg.kv_cache_config.host_gib,
                             watchdog_timeout=float(pkg.profiling_config.watchdog_timeout),
+                            kv_dtype=pkg.kv_cache_config.dtype,
                             **({"num_pages": 512, "use_graphs": False} if device.type == "cpu" else {}))
             return MR.ReplicatedEngine(eng, bus) if bus is not None and rank == 0 else eng
 

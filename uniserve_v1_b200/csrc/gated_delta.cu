@@ -231,7 +231,8 @@ __global__ void __launch_bounds__(128) gated_delta_rule_kernel(const RuleArgs a)
   }
 }
 
-// One warp per (token, head) row: y = round(round(x * rsqrt(mean x^2 + eps)) * w) * silu(z).
+// One warp per (token, head) row: y = round(round(x * rsqrt(mean x^2 + eps)) * w) * silu(z)
+// (the roundings are those of a bf16 model; an FP32 model rounds nowhere).
 __global__ void __launch_bounds__(256)
 rmsnorm_gated_kernel(const float* __restrict__ x, const void* __restrict__ w,
                      const void* __restrict__ z, long long ldz, int hsz, void* __restrict__ y,
@@ -241,11 +242,15 @@ rmsnorm_gated_kernel(const float* __restrict__ x, const void* __restrict__ w,
   if (r >= rows) return;
   const int t = r / Hv, h = r - t * Hv;
   const float* xr = x + (long long)r * Dv;
+  // a bf16 model rounds the rule's output to bf16 before this norm; the same values here
   float ss = 0.f;
-  for (int d = lane; d < Dv; d += 32) ss += xr[d] * xr[d];
+  for (int d = lane; d < Dv; d += 32) {
+    const float xv = bf16 ? us::bf2f(us::f2bf(xr[d])) : xr[d];
+    ss += xv * xv;
+  }
   const float inv = rsqrtf(us::warp_sum(ss) / (float)Dv + eps);
   for (int d = lane; d < Dv; d += 32) {
-    float v = xr[d] * inv;
+    float v = (bf16 ? us::bf2f(us::f2bf(xr[d])) : xr[d]) * inv;
     float wv = ld_any(w, d, bf16);
     if (bf16) v = us::bf2f(us::f2bf(us::bf2f(us::f2bf(v)) * wv));
     else v = v * wv;

@@ -92,13 +92,15 @@ kv_write_scaled_kernel(const __nv_bfloat16* __restrict__ k_src, const __nv_bfloa
   if (threadIdx.x == 0) *scale = now;
 }
 
-// Packed context rows of a batch: sequence s contributes rows [0, ctx[s]) of its pages to
-// out rows [cu[s], cu[s] + ctx[s]).  grid (row tiles of 8, 2 planes); a warp moves one row.
+// Packed context rows of a batch: sequence s contributes rows [0, cu[s + 1] - cu[s]) of its
+// pages to out rows [out_cu[s], ...) (out_cu = cu unless the caller leaves room behind each
+// sequence's cached rows for its new ones).  grid (row tiles of 8, 2 planes); a warp moves
+// one row.
 __global__ void __launch_bounds__(256)
 kv_gather_kernel(const void* __restrict__ k_cache, const void* __restrict__ v_cache,
                  const float* __restrict__ k_scale, const float* __restrict__ v_scale,
                  const int* __restrict__ page_table, int max_pages, const int* __restrict__ cu,
-                 int B, int page_size, int row_elems, __nv_bfloat16* __restrict__ k_out,
+                 const int* __restrict__ out_cu, int B, int page_size, int row_elems, __nv_bfloat16* __restrict__ k_out,
                  __nv_bfloat16* __restrict__ v_out, long long ldo, int fp8) {
   US_PDL_PROLOGUE();
   const int total = cu[B];
@@ -115,7 +117,7 @@ kv_gather_kernel(const void* __restrict__ k_cache, const void* __restrict__ v_ca
   const int page = page_table[(long long)lo * max_pages + pi];
   const long long src_row = (long long)page * page_size + (pos - pi * page_size);
   const bool plane_v = blockIdx.y == 1;
-  __nv_bfloat16* out = (plane_v ? v_out : k_out) + (long long)r * ldo;
+  __nv_bfloat16* out = (plane_v ? v_out : k_out) + (long long)(out_cu[lo] + pos) * ldo;
   if (fp8) {
     const unsigned char* src = (const unsigned char*)(plane_v ? v_cache : k_cache) + src_row * row_elems;
     const float sc = (plane_v ? v_scale : k_scale)[page];
@@ -157,14 +159,14 @@ US_API int us_kv_write_scaled(const void* k_src, const void* v_src, long long ld
 // scheduler's plan; the device reads the exact layout from `cu`).
 US_API int us_kv_gather(const void* k_cache, const void* v_cache, const float* k_scale,
                         const float* v_scale, const int* page_table, int max_pages, const int* cu,
-                        int B, int total_rows, int page_size, int heads, int head_dim, void* k_out,
+                        const int* out_cu, int B, int total_rows, int page_size, int heads, int head_dim, void* k_out,
                         void* v_out, long long ldo, int fp8, void* stream_) {
   US_REQUIRE(k_cache && v_cache && page_table && cu && k_out && v_out && B >= 1);
   US_REQUIRE(((heads * head_dim) % 8) == 0 && (ldo % 8) == 0 && (!fp8 || (k_scale && v_scale)));
   if (total_rows == 0) return US_OK;
   US_CUDA_CHECK(us::launch_pdl(kv_gather_kernel, dim3((total_rows + 7) / 8, 2), dim3(256), 0,
                                (cudaStream_t)stream_, k_cache, v_cache, k_scale, v_scale, page_table,
-                               max_pages, cu, B, page_size, heads * head_dim,
+                               max_pages, cu, out_cu ? out_cu : cu, B, page_size, heads * head_dim,
                                (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, ldo, fp8));
   return US_OK;
 }

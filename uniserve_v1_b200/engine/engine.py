@@ -54,9 +54,14 @@ class LLMEngine:
                  enable_prefix_cache: bool = True, use_graphs: bool = True,
                  policy: Optional[Policy] = None, weights_identity: str = "random-init",
                  watchdog_timeout: float = 150.0, host_kv_pages: int = 0,
-                 host_kv_ratio: float = 0.0, host_kv_gib: Optional[float] = None):
+                 host_kv_ratio: float = 0.0, host_kv_gib: Optional[float] = None,
+                 kv_dtype: Optional[str] = None):
         self.model = model
         self.device = model.device
+        if kv_dtype in ("fp8", "fp8_e4m3", "e4m3"):
+            model.kv_dtype = "fp8"       # E4M3 pages, one FP32 scale per page and plane
+        elif kv_dtype not in (None, "auto", "bf16", "bfloat16"):
+            raise ValueError(f"kv cache dtype {kv_dtype!r} is not served (bf16 or fp8)")
         max_model_len = min(max_model_len, model.cfg.max_position_embeddings)
         if num_pages is None:
             num_pages = self._divide_memory(mem_fraction_static, page_size, max_num_seqs,

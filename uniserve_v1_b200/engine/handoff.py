@@ -188,6 +188,29 @@ class Handoff:
                     raise HandoffError("kv: pages are floating point")
 
 
+def _export_plane(plane: torch.Tensor, pages: torch.Tensor) -> torch.Tensor:
+    """Pages of a cache plane as floating-point values (E4M3 planes are expanded with their
+    page scales, so a hand-off is independent of either side's cache type)."""
+    sel = plane.index_select(0, pages)
+    scale = getattr(plane, "page_scale", None)
+    if scale is None:
+        return sel.clone()
+    return (sel.view(torch.float8_e4m3fn).float() *
+            scale.index_select(0, pages)[:, None, None, None]).to(torch.bfloat16)
+
+
+def _import_plane(plane: torch.Tensor, idx: torch.Tensor, t: torch.Tensor) -> None:
+    scale = getattr(plane, "page_scale", None)
+    if scale is None:
+        plane.index_copy_(0, idx, t.to(plane.dtype))
+        return
+    f = t.float()
+    s = f.abs().amax(dim=(1, 2, 3)).clamp_min(1e-12) / 448.0
+    q = (f / s[:, None, None, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    plane.index_copy_(0, idx, q.view(torch.uint8))
+    scale.index_copy_(0, idx, s)
+
+
 def export_request(engine, request_id: str, release: bool = True) -> Handoff:
     """Lends ``request_id`` (running, at least its prompt computed).  With ``release``
     the request ends here (its pages go back to the pool, committed prefix pages stay
@@ -204,7 +227,7 @@ def export_request(engine, request_id: str, release: bool = True) -> Handoff:
         if pair is None or pair[0] is None:
             kv.append(None)
         else:
-            kv.append((pair[0].index_select(0, pages).clone(), pair[1].index_select(0, pages).clone()))
+            kv.append((_export_plane(pair[0], pages), _export_plane(pair[1], pages)))
     model = engine.model
     params = req.params
     h = Handoff(request_id=req.request_id, prompt_ids=list(req.prompt_ids),
@@ -263,7 +286,7 @@ def import_request(engine, handoffs) -> str:
         for which in (0, 1):
             shards = [(x.head_lo, x.kv[layer][which]) for x in hs if x.kv[layer] is not None]
             t = reshard_heads(shards, want_lo, pair[which].shape[2])
-            pair[which].index_copy_(0, idx, t.to(device=runner.device, dtype=pair[which].dtype))
+            _import_plane(pair[which], idx, t.to(device=runner.device))
     rid = engine.add_request(h.prompt_ids, _params_of(h.params), request_id=h.request_id,
                              priority=h.priority, cache_salt=h.cache_salt,
                              output_ids=h.output_ids)

@@ -319,6 +319,9 @@ class CausalLmRunner:
             hv = torch.zeros(shape, dtype=vc.dtype)
             if self.device.type == "cuda":
                 hk, hv = hk.pin_memory(), hv.pin_memory()
+            if getattr(kc, "page_scale", None) is not None:      # E4M3 pages travel with scales
+                hk.page_scale = torch.zeros(slots, dtype=torch.float32)
+                hv.page_scale = torch.zeros(slots, dtype=torch.float32)
             self.host_kv.append((hk, hv))
 
     def apply_kv_moves(self, offloads: list, fetches: list) -> None:
@@ -336,6 +339,9 @@ class CausalLmRunner:
                     continue
                 hk[slots] = kc.index_select(0, pages).to("cpu")
                 hv[slots] = vc.index_select(0, pages).to("cpu")
+                if getattr(kc, "page_scale", None) is not None:
+                    hk.page_scale[slots] = kc.page_scale.index_select(0, pages).to("cpu")
+                    hv.page_scale[slots] = vc.page_scale.index_select(0, pages).to("cpu")
             self.d2h_bytes += sum(2 * len(offloads) * kc[0].numel() * kc.element_size()
                                   for kc, _ in self.kv_caches if kc is not None)
         if fetches:
@@ -346,6 +352,9 @@ class CausalLmRunner:
                     continue
                 kc.index_copy_(0, pages, hk[slots].to(dev, non_blocking=True))
                 vc.index_copy_(0, pages, hv[slots].to(dev, non_blocking=True))
+                if getattr(kc, "page_scale", None) is not None:
+                    kc.page_scale.index_copy_(0, pages, hk.page_scale[slots].to(dev))
+                    vc.page_scale.index_copy_(0, pages, hv.page_scale[slots].to(dev))
             self.h2d_bytes += sum(2 * len(fetches) * kc[0].numel() * kc.element_size()
                                   for kc, _ in self.kv_caches if kc is not None)
 
@@ -555,6 +564,10 @@ class CausalLmRunner:
         meta = AttnMeta(kind="prefill", slots=d[2 * T:3 * T], cu_q=d[3 * T:3 * T + nq],
                         cu_k=d[3 * T + nq:3 * T + 2 * nq], max_q=max_q, max_k=max_k,
                         context_lens=ctx, page_table=page_table, live=live, rows_real=T_real)
+        if page_table is not None and dev.type == "cuda":
+            from ..ops.attention import context_tables
+            meta.ctx_tables = context_tables(ctx, cu_q, cu_k, dev)
+            self.h2d_bytes += 4 * len(cu_q) + 8 * T_real
         self.announce("eager", T)
         hidden = self.model.forward(d[:T], d[T:2 * T], meta, self.kv_caches)
         tap = getattr(self, "hidden_tap", None)
@@ -608,6 +621,10 @@ class CausalLmRunner:
         meta = AttnMeta(kind="prefill", slots=d[2 * T:3 * T], cu_q=d[3 * T:3 * T + nq],
                         cu_k=d[3 * T + nq:3 * T + 2 * nq], max_q=max_q, max_k=max_k,
                         context_lens=ctx, page_table=page_table.to(dev))
+        if dev.type == "cuda":
+            from ..ops.attention import context_tables
+            meta.ctx_tables = context_tables(ctx, cu_q, cu_k, dev)
+            self.h2d_bytes += 4 * len(cu_q) + 8 * T
         self.announce("eager", T)
         hidden = self.model.forward(d[:T], d[T:2 * T], meta, self.kv_caches)
         toks = F.argmax(self.model.logits(hidden))

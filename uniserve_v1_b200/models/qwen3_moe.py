@@ -148,6 +148,8 @@ class AttnMeta:
     logits_rows: Optional[torch.Tensor] = None  # rows whose logits are needed (int32)
     live: Optional[torch.Tensor] = None         # device word: rows that are real (padding after)
     rows_real: Optional[int] = None             # prefill padded to a capacity: rows before the padding
+    ctx_tables: Optional[tuple] = None          # ops.attention.context_tables(...) when sequences
+                                                # have cached context (GPU: no host sync in prefill)
 
 
 class Qwen3MoeModel:
@@ -158,6 +160,8 @@ class Qwen3MoeModel:
         self.dtype = dtype
         assert expert_quant in (None, "fp8_block")
         self.expert_quant = expert_quant
+        self.kv_dtype = None            # "fp8": E4M3 pages with per-page scales (set before the
+                                        # engine allocates the cache)
         self.ctx = ctx or ParallelContext.single()
         tp = self.ctx.tp_size
         self.Hq = cfg.num_attention_heads // tp
@@ -398,14 +402,25 @@ class Qwen3MoeModel:
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         T = x.shape[0]
         qkv = F.linear(x, lw.qkv)
-        F.qk_norm_rope_kv_(qkv, lw.q_norm, lw.k_norm, positions, self.inv_freq, meta.slots,
-                           kcache, vcache, Hq, Hkv, D, eps=self.cfg.rms_norm_eps)
+        k_scale = getattr(kcache, "page_scale", None)      # E4M3 pages: one scale per page
+        v_scale = getattr(vcache, "page_scale", None)
+        if k_scale is None:
+            F.qk_norm_rope_kv_(qkv, lw.q_norm, lw.k_norm, positions, self.inv_freq, meta.slots,
+                               kcache, vcache, Hq, Hkv, D, eps=self.cfg.rms_norm_eps)
+        else:
+            # norm + rotary in place, then the scaled page write derives the pages' scales
+            F.qk_norm_rope_kv_(qkv, lw.q_norm, lw.k_norm, positions, self.inv_freq, None,
+                               None, None, Hq, Hkv, D, eps=self.cfg.rms_norm_eps)
+            v3 = qkv.view(T, Hq + 2 * Hkv, D)
+            F.kv_write_scaled(v3[:, Hq:Hq + Hkv], v3[:, Hq + Hkv:], meta.slots, kcache, vcache,
+                              k_scale, v_scale)
         if meta.kind == "decode":
             q = qkv[:, :Hq * D] if qkv.is_cuda else qkv[:, :Hq * D].reshape(T, Hq, D)
             att = F.paged_decode_attention(q, kcache, vcache, meta.page_table, meta.seq_lens,
                                            self.scale, meta.splits, self.cfg.sliding_window,
                                            scratch=meta.scratch, Hq=Hq, D=D,
-                                           counters=meta.counters)
+                                           counters=meta.counters, k_scale=k_scale,
+                                           v_scale=v_scale)
         else:
             from ..ops.attention import prefill_attention
             att = prefill_attention(qkv, Hq, Hkv, D, meta, kcache, vcache, self.scale)
@@ -605,14 +620,23 @@ class Qwen3MoeModel:
 
     # ------------------------------------------------------------- caches --
     def new_kv_caches(self, num_pages: int, page_size: int = 16):
+        """One (key, value) plane pair per layer this rank owns.  ``kv_dtype == "fp8"``: the
+        planes hold E4M3 bytes and carry their per-page FP32 scales as ``page_scale``."""
         shape = (num_pages, page_size, self.Hkv, self.D)
-        return [(torch.zeros(shape, dtype=self.dtype, device=self.device),
-                 torch.zeros(shape, dtype=self.dtype, device=self.device))
-                if self.layer_lo <= i < self.layer_hi else (None, None)
+        fp8 = self.kv_dtype == "fp8"
+
+        def plane():
+            t = torch.zeros(shape, dtype=torch.uint8 if fp8 else self.dtype, device=self.device)
+            if fp8:
+                t.page_scale = torch.zeros(num_pages, dtype=torch.float32, device=self.device)
+            return t
+        return [(plane(), plane()) if self.layer_lo <= i < self.layer_hi else (None, None)
                 for i in range(self.cfg.num_hidden_layers)]
 
     def kv_bytes_per_page(self, page_size: int = 16) -> int:
-        return 2 * page_size * self.Hkv * self.D * 2 * (self.layer_hi - self.layer_lo)
+        elem = 1 if self.kv_dtype == "fp8" else 2
+        per_layer = 2 * (page_size * self.Hkv * self.D * elem + (4 if elem == 1 else 0))
+        return per_layer * (self.layer_hi - self.layer_lo)
 
     def weight_bytes(self) -> int:
         n = self.embed.numel() + self.final_norm.numel()

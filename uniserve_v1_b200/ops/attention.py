@@ -52,18 +52,55 @@ def prefill_attention(qkv, Hq, Hkv, D, meta, kcache, vcache, scale):
     v3 = qkv.view(T, Hq + 2 * Hkv, D)
     q, k, v = v3[:, :Hq], v3[:, Hq:Hq + Hkv], v3[:, Hq + Hkv:]
     ctx_lens = meta.context_lens
+    k_scale = getattr(kcache, "page_scale", None)
+    v_scale = getattr(vcache, "page_scale", None)
     if ctx_lens is not None and any(c > 0 for c in ctx_lens):
-        # Keys already cached sit in front of this call's keys of each sequence.
-        page = kcache.shape[1]
-        ks, vs = [], []
-        cu_q = meta.cu_q.tolist()
-        for i, c in enumerate(ctx_lens):
-            if c > 0:
-                npg = (c + page - 1) // page
-                idx = meta.page_table[i, :npg].long()
-                ks.append(kcache[idx].reshape(-1, Hkv, D)[:c])
-                vs.append(vcache[idx].reshape(-1, Hkv, D)[:c])
-            ks.append(k[cu_q[i]:cu_q[i + 1]])
-            vs.append(v[cu_q[i]:cu_q[i + 1]])
-        k, v = torch.cat(ks, 0), torch.cat(vs, 0)
+        tables = getattr(meta, "ctx_tables", None)
+        if qkv.is_cuda and tables is not None:
+            # Keys already cached sit in front of this call's keys of each sequence: one
+            # gather launch through the page table (bf16 or E4M3 pages) and one row scatter
+            # of the new keys; nothing returns to the host.
+            from . import functional as F
+            ctx_cu, new_dst, ctx_total = tables
+            total = ctx_total + new_dst.shape[0]
+            kb = torch.empty(total, Hkv, D, dtype=qkv.dtype, device=qkv.device)
+            vb = torch.empty(total, Hkv, D, dtype=qkv.dtype, device=qkv.device)
+            F.kv_gather(kcache, vcache, meta.page_table, ctx_cu, ctx_total, k_scale, v_scale,
+                        out=(kb, vb), out_cu=meta.cu_k)
+            kb.index_copy_(0, new_dst, k[:new_dst.shape[0]])
+            vb.index_copy_(0, new_dst, v[:new_dst.shape[0]])
+            k, v = kb, vb
+        else:
+            page = kcache.shape[1]
+            kc, vc = kcache, vcache
+            if k_scale is not None:
+                kc, vc = R.kv_dequant(kcache, k_scale).to(qkv.dtype), \
+                    R.kv_dequant(vcache, v_scale).to(qkv.dtype)
+            ks, vs = [], []
+            cu_q = meta.cu_q.tolist()
+            for i, c in enumerate(ctx_lens):
+                if c > 0:
+                    npg = (c + page - 1) // page
+                    idx = meta.page_table[i, :npg].long()
+                    ks.append(kc[idx].reshape(-1, Hkv, D)[:c])
+                    vs.append(vc[idx].reshape(-1, Hkv, D)[:c])
+                ks.append(k[cu_q[i]:cu_q[i + 1]])
+                vs.append(v[cu_q[i]:cu_q[i + 1]])
+            k, v = torch.cat(ks, 0), torch.cat(vs, 0)
     return varlen_attention(q, k, v, meta.cu_q, meta.cu_k, meta.max_q, meta.max_k, scale, True)
+
+
+def context_tables(ctx: list, cu_q: list, cu_k: list, device):
+    """Device tables for a prefill whose sequences have cached context (all built from the
+    scheduler's host-side plan): cumulative context lengths [B + 1] (int32), the row of every
+    new key in the combined per-sequence [cached; new] buffer [T] (int64), and the total
+    number of cached rows."""
+    ctx_cu, new_dst = [0], []
+    for i, c in enumerate(ctx):
+        ctx_cu.append(ctx_cu[-1] + c)
+        n = cu_q[i + 1] - cu_q[i]
+        new_dst.extend(range(cu_k[i] + c, cu_k[i] + c + n))
+    pin = torch.device(device).type == "cuda"
+    a = torch.tensor(ctx_cu, dtype=torch.int32, pin_memory=pin).to(device, non_blocking=True)
+    b = torch.tensor(new_dst, dtype=torch.int64, pin_memory=pin).to(device, non_blocking=True)
+    return a, b, ctx_cu[-1]

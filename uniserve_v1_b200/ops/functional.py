@@ -166,13 +166,50 @@ def decode_scratch(B: int, Hq: int, Hkv: int, D: int, splits: int, device):
             torch.zeros(B * Hkv, dtype=torch.int32, device=device))
 
 
+def kv_write_scaled(k, v, slots, kcache, vcache, k_scale, v_scale):
+    """Rows k, v [T, Hkv, D] (bf16, row-strided views allowed) into E4M3 pages (uint8
+    [pages, page, Hkv, D]) with one FP32 scale per page and plane, derived by the write."""
+    if not _cuda(k):
+        return R.kv_write_scaled(kcache, vcache, k_scale, v_scale, k, v, slots)
+    T, Hkv, D = k.shape
+    assert k.dtype == BF16 and k.stride(2) == 1 and k.stride(1) == D and v.stride(1) == D
+    assert kcache.dtype == torch.uint8 and k_scale.dtype == torch.float32
+    N.call("us_kv_write_scaled", N.ptr(k), N.ptr(v), k.stride(0), v.stride(0), N.ptr(slots),
+           N.ptr(kcache), N.ptr(vcache), N.ptr(k_scale), N.ptr(v_scale), T, kcache.shape[1], Hkv, D,
+           N.stream())
+
+
+def kv_gather(kcache, vcache, page_table, cu, total_rows, k_scale=None, v_scale=None, out=None,
+              out_cu=None):
+    """Cached rows of a batch as packed bf16: sequence s contributes its first
+    cu[s + 1] - cu[s] cached positions (through ``page_table`` [B, max_pages]) to rows
+    [cu[s], cu[s + 1]) of the result ([total_rows, Hkv, D] for K and for V), or to rows
+    starting at ``out_cu[s]`` of a larger ``out``.  Pages are bf16, or E4M3 with scales.
+    Nothing is read back to the host."""
+    pages, page, Hkv, D = kcache.shape
+    B = page_table.shape[0]
+    if out is None:
+        out = (torch.empty(total_rows, Hkv, D, dtype=BF16, device=kcache.device),
+               torch.empty(total_rows, Hkv, D, dtype=BF16, device=kcache.device))
+    ko, vo = out
+    fp8 = k_scale is not None
+    N.call("us_kv_gather", N.ptr(kcache), N.ptr(vcache), N.ptr(k_scale) if fp8 else None,
+           N.ptr(v_scale) if fp8 else None, N.ptr(page_table), page_table.shape[1], N.ptr(cu),
+           N.ptr(out_cu) if out_cu is not None else None, B, total_rows, page, Hkv, D, N.ptr(ko), N.ptr(vo), ko.stride(0), int(fp8), N.stream(),
+           launches=1)
+    return ko, vo
+
+
 def paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, splits=1, window=0,
-                           out=None, scratch=None, Hq=None, D=None, counters=None):
+                           out=None, scratch=None, Hq=None, D=None, counters=None, k_scale=None,
+                           v_scale=None):
     """q: [B, Hq, D] (or a [B, >=Hq*D] row-strided view with Hq, D given);
     caches [pages, page_size, Hkv, D]; returns [B, Hq, D] bf16.  With ``counters`` (from
-    ``decode_scratch``) the split merge happens inside the attention kernel."""
+    ``decode_scratch``) the split merge happens inside the attention kernel.  With
+    ``k_scale`` / ``v_scale`` [pages] the caches hold E4M3 bytes."""
     if not _cuda(q):
-        return R.paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, window)
+        return R.paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, window,
+                                        k_scale, v_scale)
     if q.dim() == 3:
         B, Hq, D = q.shape
         ldq = q.stride(0)
@@ -186,6 +223,16 @@ def paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, split
     if splits > 1 and scratch is None:
         nbytes = N.kernels().us_paged_decode_scratch_bytes(B, Hq, D, splits)
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    if k_scale is not None:
+        if not (D == 128 and 128 % page_size == 0 and Hq // Hkv <= 16):
+            raise ValueError("FP8 pages are served for head width 128, pages dividing 128 and "
+                             "at most 16 query heads per key head")
+        N.call("us_paged_decode_attention_fp8", N.ptr(q), N.ptr(kcache), N.ptr(vcache),
+               N.ptr(k_scale), N.ptr(v_scale), N.ptr(page_table), N.ptr(seq_lens), N.ptr(out),
+               N.ptr(scratch), N.ptr(counters) if counters is not None else None, B, Hq, Hkv, D,
+               pages, page_table.shape[1], page_size, splits, window, scale, ldq, ldo, N.stream(),
+               launches=1 if (counters is not None or splits == 1) else 2)
+        return out
     if D == 128 and 128 % page_size == 0 and Hq // Hkv <= 16 and not DECODE_SIMT:
         # keys-on-M tcgen05 kernel
         if counters is not None:

@@ -40,6 +40,10 @@ _SIGNATURES = {
     "us_gemm_wx": (I, [P, P, P, I, I, I, I, I, L, L, L, I, I, I, I, P, I, P, P, P, P, P, P, I, I, P]),
     "us_gemm_wx_hint": (I, [I]),
     "us_linear_decode": (I, [P, P, P, P, I, I, I, L, L, L, I, I, P]),
+    "us_kv_write_scaled": (I, [P, P, L, L, P, P, P, P, P, I, I, I, I, P]),
+    "us_kv_gather": (I, [P, P, P, P, P, I, P, P, I, I, I, I, I, P, P, L, I, P]),
+    "us_paged_decode_attention_fp8": (I, [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I,
+                                          F, L, L, P]),
     "us_causal_conv1d": (I, [P, L, P, P, P, L, P, P, I, I, I, I, I, I, P]),
     "us_gated_delta_rule": (I, [P, P, P, L, L, L, I, I, I, I, P, P, P, P, L, P, P, P, P, P, P,
                                 I, I, I, I, I, F, P]),

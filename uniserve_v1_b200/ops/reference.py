@@ -107,8 +107,50 @@ def kv_write(kcache, vcache, k, v, slots):
     vc[slots[ok].long()] = v[ok]
 
 
-def paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, window=0):
-    """q [B,Hq,D]; caches [pages,page,Hkv,D] -> [B,Hq,D]."""
+E4M3_MAX = 448.0
+
+
+def _to_e4m3(x):
+    return x.clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+
+
+def kv_write_scaled(kcache, vcache, k_scale, v_scale, k, v, slots):
+    """The scaled FP8 page write, one page at a time: caches uint8 [pages, page, Hkv, D] holding
+    E4M3 bytes, scales FP32 [pages].  A page's scale grows to max|values| / 448 of what a call
+    brings; rows the page already holds (offsets below the call's first) are re-encoded when
+    it grows; a row at offset 0 starts the page afresh."""
+    page = kcache.shape[1]
+    for cache, scale, src in ((kcache, k_scale, k), (vcache, v_scale, v)):
+        c8 = cache.view(torch.float8_e4m3fn)
+        done = set()
+        sl = slots.tolist()
+        for t, s in enumerate(sl):
+            if s < 0 or s // page in done:
+                continue
+            p = s // page
+            done.add(p)
+            rows = [i for i in range(t, len(sl)) if sl[i] >= 0 and sl[i] // page == p]
+            off0 = s - p * page
+            amax = float(src[rows].float().abs().max())
+            old = float(scale[p]) if off0 > 0 else 0.0
+            now = max(old, max(amax, 1e-12) / E4M3_MAX)
+            if now > old and off0 > 0:
+                c8[p, :off0] = _to_e4m3(c8[p, :off0].float() * (old / now))
+            for i in rows:
+                c8[p, sl[i] - p * page] = _to_e4m3(src[i].float() * (1.0 / now))
+            scale[p] = now
+
+
+def kv_dequant(cache, scale):
+    """E4M3 pages [pages, page, Hkv, D] (uint8) and their scales -> FP32 values."""
+    return cache.view(torch.float8_e4m3fn).float() * scale.float()[:, None, None, None]
+
+
+def paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, window=0,
+                           k_scale=None, v_scale=None):
+    """q [B,Hq,D]; caches [pages,page,Hkv,D] -> [B,Hq,D].  With scales the caches are E4M3."""
+    if k_scale is not None:
+        kcache, vcache = kv_dequant(kcache, k_scale), kv_dequant(vcache, v_scale)
     B, Hq, D = q.shape
     pages, page, Hkv, _ = kcache.shape
     G = Hq // Hkv
