@@ -832,3 +832,28 @@ def test_kv_gather_and_cached_context_prefill():
     agree = lambda a, b: sum(x == y for p, q_ in zip(a, b) for x, y in zip(p, q_)) / 24.0
     assert agree(outs["whole"], outs["chunked"]) >= 0.9, outs
     assert agree(outs["whole"], outs["fp8"]) >= 0.6, outs
+
+
+def test_engine_sleep_levels_free_memory_and_wake_restores_tokens():
+    """Level 1 frees the KV cache and graphs, level 2 parks the weights in pinned host memory;
+    after wake the engine gives the tokens it gave before."""
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    cfg = Qwen3MoeConfig.tiny()
+    model = Qwen3MoeModel(cfg, DEV, BF).init_random(seed=0)
+    eng = LLMEngine(model, num_pages=256, max_num_seqs=4, max_model_len=256)
+    prompts = [[(3 * i + j) % cfg.vocab_size for i in range(n)] for j, n in enumerate((17, 40))]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    want = eng.generate(prompts, sp)
+    for level in (1, 2):
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated()
+        out = eng.sleep(level)
+        after = torch.cuda.memory_allocated()
+        assert out["freed_bytes"] > 0 and before - after >= 0.9 * out["freed_bytes"]
+        if level == 2:
+            assert model.embed is None and model.layers[0].qkv is None
+        assert eng.step() == [] and not eng.has_work()
+        eng.wake()
+        assert eng.generate(prompts, sp) == want

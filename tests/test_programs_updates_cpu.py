@@ -208,3 +208,106 @@ def test_epoch_update_switches_drains_commits_and_rolls_back():
         events = c.get("/admin/query", params={"q": "select fields from events where kind = 'update'"}
                        ).json()["rows"]
         assert len(events) >= 6
+
+
+def test_sleep_and_wake_keep_the_queue_and_give_the_same_tokens():
+    """POST /admin/sleep frees the KV cache (level 1) and the weights (level 2) while the
+    process and its queue stay; a request sent while asleep is answered after /admin/wake with
+    the tokens an engine that never slept gives."""
+    import threading
+    from fastapi.testclient import TestClient
+    from uniserve_v1_b200.server.app import create_app
+    from uniserve_v1_b200.server.tokenizer import ByteTokenizer
+    eng = _engine()
+    app = create_app(package=Package.parse('model = "random:tiny"\nserved_model_name = "tiny"\n'),
+                     engine=eng, tokenizer=ByteTokenizer(1024, 1023), served_model_name="tiny")
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}],
+            "max_tokens": 12, "temperature": 0, "ignore_eos": True}
+    with TestClient(app) as c:
+        want = c.post("/v1/chat/completions", json=body).json()["choices"][0]["message"]["content"]
+        for level in (1, 2):
+            r = c.post("/admin/sleep", params={"level": level})
+            assert r.status_code == 200 and r.json()["freed_bytes"] > 0
+            assert eng.runner.kv_caches is None and c.get("/health").json()["asleep"] == level
+            if level == 2 and eng.device.type == "cuda":      # host copies only of GPU weights
+                assert eng.model.embed is None
+            got = {}
+            t = threading.Thread(target=lambda: got.update(
+                r=c.post("/v1/chat/completions", json=body).json()))
+            t.start()
+            time.sleep(0.3)
+            assert not got                                    # queued, not refused
+            assert c.post("/admin/wake").json()["was"] == level
+            t.join(timeout=60)
+            assert got["r"]["choices"][0]["message"]["content"] == want
+        assert c.post("/admin/sleep", params={"level": 3}).status_code == 400
+
+
+def test_otlp_push_resends_what_a_refused_push_carried():
+    from uniserve_v1_b200.server.export import OtlpPusher
+    from uniserve_v1_b200.server.observation import ObservationStore
+    obs = ObservationStore()
+    sent, refuse = [], [True]
+
+    def post(url, body, timeout):
+        if refuse[0]:
+            return 503
+        sent.append((url, body))
+        return 200
+    p = OtlpPusher(obs, "http://collector:4318/", deployment="d", post=post)
+    obs.inc("uniserve_requests_total", {"outcome": "ok"})
+    obs.set("uniserve_running_requests", 3)
+    obs.observe("uniserve_ttft_seconds", 0.25, {"replica": "r0"})
+    obs.snapshot()
+    obs.event("update", phase="committed")
+    assert p.push_once() is False and p.failures == 1 and not sent
+    obs.observe("uniserve_ttft_seconds", 0.5, {"replica": "r0"})
+    refuse[0] = False
+    assert p.push_once() is True
+    urls = [u for u, _ in sent]
+    assert urls == ["http://collector:4318/v1/metrics", "http://collector:4318/v1/logs"]
+    metrics = {m["name"]: m for m in
+               sent[0][1]["resourceMetrics"][0]["scopeMetrics"][0]["metrics"]}
+    assert metrics["uniserve_requests_total"]["sum"]["isMonotonic"] is True
+    assert len(metrics["uniserve_ttft_seconds"]["gauge"]["dataPoints"]) == 2     # both observations
+    rec = sent[1][1]["resourceLogs"][0]["scopeLogs"][0]["logRecords"][0]
+    assert rec["body"]["stringValue"] == "update"
+    sent.clear()
+    assert p.push_once() is True and not sent                                  # nothing new
+
+
+def test_kv_events_follow_commits_reuse_and_flush():
+    """An engine with a publisher: the pages a prompt fills are announced as BlockStored with
+    SGLang's chained hashes, a second request with the same prefix stores only its new pages,
+    pages handed out again are BlockRemoved, a flush clears."""
+    import msgpack
+    import struct
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.server.export import KvEventPublisher, block_digest, block_hash
+    eng = _engine()
+    frames = []
+    eng.blocks.kv_events = KvEventPublisher(None, rank=2, block_size=16, send=frames.append)
+    prompt = [(11 * i) % 1000 for i in range(50)]
+    sp = SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)
+    eng.generate([prompt], sp)
+    batches = [msgpack.unpackb(f[2]) for f in frames]
+    assert [struct.unpack(">Q", f[1])[0] for f in frames] == list(range(len(frames)))
+    assert frames[0][0] == b"kv-events" and batches[0][2] == 2
+    events = [e for b in batches for e in b[1]]
+    assert events[0]["type"] == "AllBlocksCleared"
+    stored = [e for e in events if e["type"] == "BlockStored"]
+    d0 = block_digest(None, prompt[:16])
+    d1 = block_digest(d0, prompt[16:32])
+    d2 = block_digest(d1, prompt[32:48])
+    hashes = [h for e in stored for h in e["block_hashes"]]
+    assert hashes[:3] == [block_hash(d0), block_hash(d1), block_hash(d2)]
+    assert stored[0]["parent_block_hash"] is None and stored[0]["block_size"] == 16
+    assert stored[0]["token_ids"][:16] == prompt[:16] and stored[0]["medium"] == "GPU"
+    n0 = len(stored)
+    eng.generate([prompt[:32] + [7] * 20], sp)        # shares two pages, fills one new
+    events = [e for f in frames for e in msgpack.unpackb(f[2])[1]]
+    new = [e for e in events if e["type"] == "BlockStored"][n0:]
+    assert new and new[0]["parent_block_hash"] == block_hash(d1)
+    eng.blocks.flush()
+    eng.blocks.kv_events.flush()
+    assert msgpack.unpackb(frames[-1][2])[1][-1]["type"] == "AllBlocksCleared"

@@ -50,6 +50,7 @@ class BlockManager:
                  enable_prefix_cache: bool = True):
         self.lib = _lib()
         self.num_pages = num_pages
+        self.kv_events = None        # server.export.KvEventPublisher of this scheduler
         self.page_size = page_size
         self.enable_prefix_cache = enable_prefix_cache
         self.identity = weights_identity
@@ -153,7 +154,12 @@ class BlockManager:
             return []
         out = np.empty(n, dtype=np.int32)
         rc = self.lib.us_bm_alloc(self.h, n, out.ctypes.data)
-        return None if rc != 0 else out.tolist()
+        if rc != 0:
+            return None
+        pages = out.tolist()
+        if self.kv_events is not None:      # whatever these pages cached is gone
+            self.kv_events.reused(pages)
+        return pages
 
     def release(self, pages: Sequence[int]) -> None:
         if not pages:
@@ -203,6 +209,8 @@ class BlockManager:
         return self.lib.us_bm_refcount(self.h, page)
 
     def flush(self) -> int:
+        if self.kv_events is not None:
+            self.kv_events.cleared()
         return self.lib.us_bm_flush(self.h)
 
     def stats(self) -> dict:

@@ -47,6 +47,30 @@ class Watchdog:
         return None
 
 
+def _weight_tensors(model):
+    """(holder, attribute or key, tensor) of every weight tensor a model object owns: its own
+    tensor attributes and those of its per-layer weight records."""
+    def walk(holder):
+        items = holder.items() if isinstance(holder, dict) else vars(holder).items()
+        for name, v in list(items):
+            if torch.is_tensor(v) and v.dim() > 0:
+                yield holder, name, v
+    yield from walk(model)
+    for lw in getattr(model, "layers", None) or []:
+        if lw is not None:
+            yield from walk(lw)
+            fp8 = getattr(lw, "fp8", None)
+            if fp8 is not None:
+                yield from walk(fp8)
+
+
+def _set_tensor(holder, name, value) -> None:
+    if isinstance(holder, dict):
+        holder[name] = value
+    else:
+        setattr(holder, name, value)
+
+
 class LLMEngine:
     def __init__(self, model: Qwen3MoeModel, num_pages: Optional[int] = None, page_size: int = 16,
                  max_num_seqs: int = 128, max_model_len: int = 4096,
@@ -91,6 +115,9 @@ class LLMEngine:
         self._ids = itertools.count()
         self.failed: Optional[str] = None
         self.health = None        # parallel.health.Heartbeat of a multi-rank deployment
+        self.asleep = 0           # sleep level (0 = awake)
+        self._parked: list = []   # weights held in host memory while asleep at level 2
+        self._parked_hosts: dict = {}
         self.profiler = None      # engine.profiling.StepProfiler when profiling is on
         self.spec_stats = {"steps": 0, "proposed": 0, "accepted": 0}
 
@@ -128,14 +155,77 @@ class LLMEngine:
         return self.scheduler.abort(request_id) is not None
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return not self.asleep and self.scheduler.has_work()
+
+    # ---------------------------------------------------------- sleep / wake --
+    def sleep(self, level: int = 1) -> dict:
+        """Gives the GPU back while the process, its scheduler and its queue stay.
+        Level 1 frees the KV cache and the captured graphs (the prefix cache is dropped);
+        level 2 also moves the weights to pinned host memory.  Requests in flight are
+        preempted (they recompute after ``wake``); new ones queue.  Returns the bytes freed.
+        Reference behaviour: crates/engine/src/process (sleep / wake of a deployment)."""
+        if self.asleep:
+            return {"level": self.asleep, "freed_bytes": 0}
+        sch = self.scheduler
+        while sch.running:                      # recompute-style preemption of everything
+            if not sch._preempt_one():
+                break
+        self.blocks.flush()
+        freed = 0
+        self.runner.release_graphs()
+        for pair in self.runner.kv_caches:
+            for t in pair:
+                if t is not None:
+                    freed += t.numel() * t.element_size()
+        self.runner.kv_caches = None
+        self._parked = []
+        if level >= 2:
+            hosts = {}                          # one host copy per tensor (tied weights alias)
+            for holder, name, t in _weight_tensors(self.model):
+                if t.is_cuda:
+                    if id(t) not in hosts:
+                        host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                        host.copy_(t)
+                        hosts[id(t)] = (host, t)        # keeps t alive until every alias is cut
+                        freed += t.numel() * t.element_size()
+                    self._parked.append((holder, name, id(t), t.device))
+                    _set_tensor(holder, name, None)
+            self._parked_hosts = {k: h for k, (h, _) in hosts.items()}
+            del hosts
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+            torch.cuda.empty_cache()
+        self.asleep = level
+        return {"level": level, "freed_bytes": freed}
+
+    def wake(self) -> dict:
+        """Undoes ``sleep``: weights back on the device, a fresh (empty) KV cache of the same
+        size; graphs are captured again on first use."""
+        if not self.asleep:
+            return {"level": 0}
+        back = {}
+        for holder, name, key, dev in self._parked:
+            if key not in back:
+                back[key] = self._parked_hosts[key].to(dev, non_blocking=True)
+            _set_tensor(holder, name, back[key])
+        self._parked, self._parked_hosts = [], {}
+        self.runner.kv_caches = self.model.new_kv_caches(self.blocks.num_pages, self.config.page_size)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        level, self.asleep = self.asleep, 0
+        return {"level": 0, "was": level}
 
     # ------------------------------------------------------------------ step --
     def step(self) -> list:
+        if self.asleep:
+            return []
         batch = self.scheduler.schedule()
         if batch is None:
             return []
-        return self.run_batch(batch)
+        outs = self.run_batch(batch)
+        if self.blocks.kv_events is not None:
+            self.blocks.kv_events.flush()       # a step's KV events are one batch
+        return outs
 
     def run_batch(self, batch, capacity: Optional[int] = None) -> list:
         """Executes a scheduled batch and applies its results.  ``capacity``: the row count

@@ -13,6 +13,8 @@ object rather than a wasm program.
 """
 from __future__ import annotations
 
+import hashlib
+
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -276,6 +278,19 @@ class Scheduler:
             keys.append(k)
         for i in range(req.committed_pages, full):
             self.blocks.commit(req.pages[i], keys[i])
+        ev = self.blocks.kv_events
+        if ev is not None:                  # the same pages as KV events for outside routers
+            from ..server.export import block_digest
+            dig = getattr(req, "_ev_digests", None)
+            if dig is None:
+                salt = req.cache_salt.encode() if req.cache_salt else None
+                dig = req._ev_digests = [hashlib.sha256(salt).digest() if salt else None]
+            while len(dig) - 1 < full:
+                i = len(dig) - 1
+                dig.append(block_digest(dig[-1], req.token_slice(i * ps, (i + 1) * ps)))
+            lo = req.committed_pages
+            ev.stored(req.pages[lo:full], dig[lo + 1:full + 1], dig[lo],
+                      req.token_slice(lo * ps, full * ps))
         req.committed_pages = full
 
     def _finish(self, req: Request, reason: FinishReason, error: Optional[str] = None) -> None:

@@ -260,15 +260,8 @@ class Qwen35MoeModel:
             q, k = self._norm_mrope(q, L["q_norm"], pos3), self._norm_mrope(k, L["k_norm"], pos3)
         st.k = k if st.k is None else torch.cat([st.k, k], 0)
         st.v = v if st.v is None else torch.cat([st.v, v], 0)
-        rep = Hq // Hkv
-        K = st.k.float().repeat_interleave(rep, 1)
-        V = st.v.float().repeat_interleave(rep, 1)
-        s = torch.einsum("thd,nhd->htn", q.float(), K) / math.sqrt(D)
-        n_ctx = K.shape[0]
-        seq = torch.arange(n_ctx - T, n_ctx, device=n.device)         # sequence index of each row
-        mask = torch.arange(n_ctx, device=n.device)[None, :] > (seq[:, None])
-        s = s.masked_fill(mask[None], float("-inf"))
-        att = torch.einsum("htn,nhd->thd", s.softmax(-1), V).reshape(T, Hq * D)
+        from ..ops.attention import cached_causal_attention
+        att = cached_causal_attention(q, st.k, st.v, 1.0 / math.sqrt(D)).reshape(T, Hq * D)
         att = (att * torch.sigmoid(gate.float())).to(n.dtype)
         return F.linear(att, L["o"])
 
@@ -362,16 +355,14 @@ class Qwen35MoeModel:
                 v = F.linear(n, L["v"]).view(B, Hkv, D)
                 q = self._norm_mrope(q, L["q_norm"], pos3)
                 k = self._norm_mrope(k, L["k_norm"], pos3)
+                from ..ops.attention import cached_causal_attention
                 att = torch.empty(B, Hq * D, dtype=torch.float32, device=x.device)
-                rep = Hq // Hkv
                 for b in range(B):
                     st = states[b][i]
                     st.k = k[b:b + 1] if st.k is None else torch.cat([st.k, k[b:b + 1]], 0)
                     st.v = v[b:b + 1] if st.v is None else torch.cat([st.v, v[b:b + 1]], 0)
-                    K = st.k.float().repeat_interleave(rep, 1)
-                    V = st.v.float().repeat_interleave(rep, 1)
-                    p = (torch.einsum("hd,nhd->hn", q[b].float(), K) / math.sqrt(D)).softmax(-1)
-                    att[b] = torch.einsum("hn,nhd->hd", p, V).reshape(Hq * D)
+                    att[b] = cached_causal_attention(q[b:b + 1], st.k, st.v,
+                                                     1.0 / math.sqrt(D)).reshape(Hq * D)
                 mix = F.linear((att * torch.sigmoid(gate.float())).to(n.dtype), L["o"])
             else:
                 proj = F.linear(n, L["qkvz"])

@@ -144,15 +144,9 @@ class MtpHead:
                               w["layers.0.self_attn.k_norm.weight"], pos, t.inv_freq, D, False, eps)
         kv[0] = k if kv[0] is None else torch.cat([kv[0], k], 0)
         kv[1] = v if kv[1] is None else torch.cat([kv[1], v], 0)
-        rep = Hq // Hkv
-        K = kv[0].float().repeat_interleave(rep, 1)                     # [n, Hq, D]
-        V = kv[1].float().repeat_interleave(rep, 1)
-        s = torch.einsum("thd,nhd->htn", q.float(), K) / math.sqrt(D)
-        n_ctx = K.shape[0]
-        seq = torch.arange(n_ctx - T, n_ctx, device=self.device)
-        s = s.masked_fill((torch.arange(n_ctx, device=self.device)[None, :] > seq[:, None])[None],
-                          float("-inf"))
-        att = torch.einsum("htn,nhd->thd", s.softmax(-1), V).reshape(T, Hq * D).to(self.dtype)
+        from ..ops.attention import cached_causal_attention
+        att = cached_causal_attention(q, kv[0], kv[1], 1.0 / math.sqrt(D)) \
+            .reshape(T, Hq * D).to(self.dtype)
         x = x + R.linear(att, w["layers.0.self_attn.o_proj.weight"])
         n = R.rmsnorm(x, w["layers.0.post_attention_layernorm.weight"], eps)
         if c.num_experts:

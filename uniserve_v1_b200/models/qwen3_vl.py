@@ -124,14 +124,9 @@ class Qwen3VLDenseModel:
         v = qkv[:, Hq + Hkv:]
         st.k = k if st.k is None else torch.cat([st.k, k], 0)
         st.v = v if st.v is None else torch.cat([st.v, v], 0)
-        rep = Hq // Hkv
-        K, V = st.k.float().repeat_interleave(rep, 1), st.v.float().repeat_interleave(rep, 1)
-        s = torch.einsum("thd,nhd->htn", q.float(), K) / math.sqrt(D)
-        n_ctx = K.shape[0]
-        seq = torch.arange(n_ctx - T, n_ctx, device=n.device)
-        s = s.masked_fill((torch.arange(n_ctx, device=n.device)[None, :] > seq[:, None])[None],
-                          float("-inf"))
-        att = torch.einsum("htn,nhd->thd", s.softmax(-1), V).reshape(T, Hq * D).to(n.dtype)
+        from ..ops.attention import cached_causal_attention
+        att = cached_causal_attention(q, st.k, st.v, 1.0 / math.sqrt(D)) \
+            .reshape(T, Hq * D).to(n.dtype)
         return F.linear(att, L["o"])
 
     def forward(self, ids: torch.Tensor, state: list, pos0: int = 0, embeds=None,

@@ -104,3 +104,27 @@ def context_tables(ctx: list, cu_q: list, cu_k: list, device):
     a = torch.tensor(ctx_cu, dtype=torch.int32, pin_memory=pin).to(device, non_blocking=True)
     b = torch.tensor(new_dst, dtype=torch.int64, pin_memory=pin).to(device, non_blocking=True)
     return a, b, ctx_cu[-1]
+
+
+def cached_causal_attention(q, k_all, v_all, scale):
+    """One sequence whose T newest rows ``q`` [T, Hq, D] attend causally to all of its keys
+    ``k_all`` / ``v_all`` [N, Hkv, D] (the T newest included, aligned to the end).  bf16 on a
+    GPU with a head width the flash kernel serves: the varlen flash kernel; otherwise the
+    FP32 restatement.  Returns [T, Hq, D] FP32 (restatement) or bf16 (kernel)."""
+    T, Hq, D = q.shape
+    N_, Hkv = k_all.shape[0], k_all.shape[1]
+    if q.is_cuda and q.dtype == BF16 and D % 8 == 0 and D <= 128:
+        dev = q.device
+        cu_q = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        cu_k = torch.tensor([0, N_], dtype=torch.int32, device=dev)
+        q, k_all, v_all = (t if (t.stride(2) == 1 and t.stride(1) == D) else t.contiguous()
+                           for t in (q, k_all, v_all))
+        return varlen_attention(q, k_all.to(BF16), v_all.to(BF16), cu_q, cu_k, T, N_, scale, True)
+    rep = Hq // Hkv
+    K = k_all.float().repeat_interleave(rep, 1)
+    V = v_all.float().repeat_interleave(rep, 1)
+    s_ = torch.einsum("thd,nhd->htn", q.float(), K) * scale
+    seq = torch.arange(N_ - T, N_, device=q.device)
+    s_ = s_.masked_fill((torch.arange(N_, device=q.device)[None, :] > seq[:, None])[None],
+                        float("-inf"))
+    return torch.einsum("htn,nhd->thd", s_.softmax(-1), V)

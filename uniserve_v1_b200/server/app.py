@@ -263,6 +263,16 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
             s.service.start()
         if s.video:
             s.video.start()
+        oc = s.package.observation_config
+        if oc.otlp_endpoint:                   # the store is pushed to an OTLP collector
+            from .export import OtlpPusher
+            s.otlp = OtlpPusher(s.obs, oc.otlp_endpoint, deployment=s.served,
+                                period=max(1.0, float(oc.fine_bucket) * 10))
+            s.otlp.start()
+        blocks = getattr(s.engine, "blocks", None)
+        if oc.kv_events and blocks is not None and blocks.kv_events is None:
+            from .export import KvEventPublisher
+            blocks.kv_events = KvEventPublisher(oc.kv_events, block_size=blocks.page_size)
 
     @app.on_event("shutdown")
     async def _stop():
@@ -270,6 +280,11 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
             s.service.stop(float(s.package.server_config.shutdown_timeout))
         if s.video:
             s.video.stop()
+        if getattr(s, "otlp", None) is not None:
+            s.otlp.stop()
+        blocks = getattr(s.engine, "blocks", None)
+        if blocks is not None and getattr(blocks, "kv_events", None) is not None:
+            blocks.kv_events.close()
 
     # ------------------------------------------------------------ middleware --
     @app.middleware("http")
@@ -324,6 +339,7 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
     async def health():
         ok = (s.service is None or (s.service.thread.is_alive() and not s.engine.failed))
         body = {"status": "ok" if ok else "failed", "uptime_seconds": time.time() - s.started,
+                "asleep": int(getattr(s.engine, "asleep", 0) or 0),
                 "routes": sorted(r.path for r in app.routes if hasattr(r, "path"))}
         return JSONResponse(body, status_code=200 if ok else 503)
 
@@ -703,6 +719,27 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
             return _err(400, str(e), param=e.path)
         status, body = apply_package(new)
         return JSONResponse(body, status_code=status)
+
+    @app.post("/admin/sleep")
+    async def admin_sleep(level: int = 1):
+        """Frees the KV cache and graphs (level 1) and the weights too (level 2); requests in
+        flight recompute after ``/admin/wake``, new ones queue meanwhile."""
+        if s.service is None or not hasattr(s.engine, "sleep"):
+            return _err(409, "this deployment has no engine that can sleep")
+        if level not in (1, 2):
+            return _err(400, "level is 1 or 2", param="level")
+        out = await asyncio.to_thread(s.service.call, lambda e: e.sleep(level))
+        s.obs.event("sleep", **out)
+        return out
+
+    @app.post("/admin/wake")
+    async def admin_wake():
+        if s.service is None or not hasattr(s.engine, "wake"):
+            return _err(409, "this deployment has no engine that can sleep")
+        out = await asyncio.to_thread(s.service.call, lambda e: e.wake())
+        s.service.wake.set()
+        s.obs.event("wake", **out)
+        return out
 
     @app.get("/admin/update")
     async def get_update():

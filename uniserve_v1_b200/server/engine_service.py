@@ -50,6 +50,20 @@ class EngineService:
         self.update = None                        # server.updates.EpochUpdate in progress
         self.draining = None                      # the previous engine while it drains
 
+    def call(self, fn, timeout: float = 300.0):
+        """Runs ``fn(engine)`` on the engine's own thread, between two steps, and returns its
+        value (sleep, wake and other actions that must not race a step)."""
+        if not self.started or not self.thread.is_alive():
+            return fn(self.engine)
+        box, done = {}, threading.Event()
+        self.inbox.put(("call", fn, box, done))
+        self.wake.set()
+        if not done.wait(timeout):
+            raise TimeoutError("the engine loop did not take the action in time")
+        if "error" in box:
+            raise box["error"]
+        return box.get("value")
+
     def start(self):
         if not self.started:
             self.started = True
@@ -212,6 +226,13 @@ class EngineService:
                         except Exception as e:
                             self._deliver(StepOutput(msg[1], [], True, FinishReason.ERROR,
                                                      error=f"hand-off refused: {e}"))
+                    elif msg[0] == "call":          # an operator action on the engine's thread
+                        _, fn, box, done = msg
+                        try:
+                            box["value"] = fn(self.engine)
+                        except Exception as e:
+                            box["error"] = e
+                        done.set()
                     elif msg[0] == "abort":
                         if self.engine.abort(msg[1]) or \
                                 (self.draining is not None and self.draining.abort(msg[1])):
