@@ -110,6 +110,8 @@ _LAYOUTS = {
     "tp2": "tensor_parallel_size = 2\n",
     # data-parallel attention + expert parallelism: two members, each with half the experts
     "dp_ep2": "data_parallel_size = 2\n[moe_config]\nexpert_parallel = true\n",
+    # distributed weight data parallelism: two members that read each other's expert shards
+    "dwdp2": 'data_parallel_size = 2\n[moe_config]\nexpert_parallel = true\nexchange = "weights"\n',
     # attention / expert disaggregation: two attention members, one experts-only rank
     "afd": '[moe_config]\nexpert_parallel = true\n[[worker_groups]]\nid = "attention"\n'
            'ranks = ["cuda:0-1"]\n[[worker_groups]]\nid = "experts"\nrole = "experts"\n'
@@ -117,7 +119,7 @@ _LAYOUTS = {
 }
 
 
-@pytest.mark.parametrize("layout", ["tp2", "dp_ep2", "afd"])
+@pytest.mark.parametrize("layout", ["tp2", "dp_ep2", "dwdp2", "afd"])
 def test_serve_command_runs_a_two_rank_deployment(tmp_path, layout):
     """`serve` starts the other ranks of the package's layout itself (gloo ranks on CPU
     here) - a tensor-parallel pair, an expert union of two members, or two attention members

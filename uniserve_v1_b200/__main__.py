@@ -184,8 +184,14 @@ def serve(args) -> int:
         n_src = union["sources"]
         sources = tuple(range(n_src))
         experts = sources if union["shared"] else tuple(range(n_src, world))
-        ctx = ParallelContext(world_rank=rank, world_size=world)
-        ctx.source_ranks, ctx.expert_ranks = sources, experts
+        # `moe_config.exchange = "weights"`: distributed weight data parallelism - the members
+        # keep their tokens and read the expert shards they miss from their peers
+        dwdp = union["shared"] and (pkg.moe_config.exchange or "") == "weights"
+        if dwdp:
+            ctx = ParallelContext.from_world(expert=world)
+        else:
+            ctx = ParallelContext(world_rank=rank, world_size=world)
+            ctx.source_ranks, ctx.expert_ranks = sources, experts
         if directory:
             from .checkpoint.quantized import open_checkpoint
             ld = open_checkpoint(directory, dtype)
@@ -196,7 +202,12 @@ def serve(args) -> int:
                 else Qwen3MoeConfig.qwen3_30b_a3b()
             model = Qwen3MoeModel(cfg, device, dtype, ctx).init_random(0)
         limit = min(int(pkg.max_num_batched_tokens or 8192), 8192)
-        if device.type == "cuda":
+        if dwdp:
+            import torch.distributed as dist
+            from .parallel.dwdp import attach_weight_peers
+            attach_weight_peers(model, dist.group.WORLD if device.type == "cuda" else control,
+                                rank, world)
+        elif device.type == "cuda":
             import torch.distributed as dist
             from .parallel.expert_exchange import ExpertExchange
             model.exchange = ExpertExchange(dist.group.WORLD, rank, world, device, limit,
@@ -219,9 +230,11 @@ def serve(args) -> int:
                             mem_fraction_static=pkg.mem_fraction_static,
                             enable_prefix_cache=pkg.kv_cache_config.prefix_caching,
                             watchdog_timeout=float(pkg.profiling_config.watchdog_timeout),
-                            **({"num_pages": 512, "use_graphs": False} if device.type == "cpu" else {}))
+                            **({"num_pages": 512, "use_graphs": False} if device.type == "cpu"
+                               else ({"use_graphs": False} if dwdp else {})))
         member = UnionMember(control, rank, world, sources, experts, engine=eng, model=model,
-                             capacity_limit=limit)
+                             capacity_limit=limit,
+                             exchange_free=dwdp and device.type == "cuda")
         if rank > 0:
             member_loop(member, 0)
             return 0

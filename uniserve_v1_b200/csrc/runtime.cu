@@ -192,3 +192,12 @@ US_API int us_device_info(int* sm_count, int* cc_major, int* cc_minor, size_t* s
   if (smem_optin) *smem_optin = p.sharedMemPerBlockOptin;
   return US_OK;
 }
+
+// Plain device-to-device copy of raw addresses on a stream (either side may be a peer's
+// memory mapped into this process: the copy engines move it over NVLink).
+US_API int us_copy_async(void* dst, const void* src, long long bytes, void* stream) {
+  US_REQUIRE(dst && src && bytes >= 0);
+  if (bytes == 0) return US_OK;
+  US_CUDA_CHECK(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, (cudaStream_t)stream));
+  return US_OK;
+}

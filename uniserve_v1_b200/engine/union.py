@@ -58,13 +58,17 @@ class UnionMember:
     members) or None (expert members, which only need ``model``)."""
 
     def __init__(self, control_group, rank: int, world: int, source_ranks, expert_ranks,
-                 engine=None, model=None, capacity_limit: int = 8192):
+                 engine=None, model=None, capacity_limit: int = 8192,
+                 exchange_free: bool = False):
         self.group, self.rank, self.world = control_group, rank, world
         self.sources, self.experts = tuple(source_ranks), tuple(expert_ranks)
         self.engine = engine
         self.model = model if model is not None else engine.model
         self.is_source = rank in self.sources
         self.limit = capacity_limit
+        # members that move no tokens between them (weights are read one-sidedly from the
+        # peers): an idle member has nothing to join
+        self.exchange_free = exchange_free
         self.stats = {"ticks": 0, "steps": 0, "joins": 0, "idle_ticks": 0, "capacities": {}}
         if engine is not None:
             # a member's prefill chunk must fit the agreed capacity
@@ -101,8 +105,9 @@ class UnionMember:
             self.stats["joins"] += 1
             return [], gathered
         if batch is None:
-            self.engine.runner.join(cap)
-            self.stats["joins"] += 1
+            if not self.exchange_free:
+                self.engine.runner.join(cap)
+                self.stats["joins"] += 1
             return [], gathered
         self.stats["steps"] += 1
         try:

@@ -177,6 +177,8 @@ class Qwen3MoeModel:
         self.expert_ranks = getattr(self.ctx, "expert_ranks", None)
         self.source_ranks = getattr(self.ctx, "source_ranks", None)
         self.exchange = None
+        self.weight_peers = None        # parallel.dwdp: experts read from the peers' shards
+        self.moe_layer_order: list = []
         if self.expert_ranks is not None:
             r = self.ctx.world_rank
             n = len(self.expert_ranks)
@@ -470,7 +472,15 @@ class Qwen3MoeModel:
                                            cfg.hidden_size, cfg.moe_intermediate_size, x.device,
                                            E_total=cfg.num_experts)
                 self._moe_ws[key] = ws
-        reduce = self.ctx.ep_size > 1
+        # distributed weight data parallelism: every expert runs here, on weights read from the
+        # peers' resident shards; tokens stay, so nothing is reduced across ranks
+        peers = self.weight_peers
+        w13, w2 = lw.w13, lw.w2
+        if peers is not None:
+            order = self.moe_layer_order
+            nxt = order[(order.index(lw.index) + 1) % len(order)]
+            w13, w2 = peers.layer_weights(lw.index, nxt if len(order) > 1 else None)
+        reduce = self.ctx.ep_size > 1 and peers is None
         small = x.is_cuda and T <= 512 and lw.fp8 is None
         # decode-size batches: route, sort and gather in one launch; the un-permute rides on
         # the norm (or the fused all-reduce) that follows
@@ -494,9 +504,11 @@ class Qwen3MoeModel:
             out = moe_experts_fp8(x, ids, weights, lw.fp8, e_lo=self.e_lo, ws=ws)
         else:
             later = defer and small and FUSED_UNPERMUTE and (fc is not None or not reduce)
-            out = F.moe_experts(x, ids, weights, lw.w13, lw.w2, e_lo=self.e_lo, ws=ws,
+            out = F.moe_experts(x, ids, weights, w13, w2, e_lo=self.e_lo, ws=ws,
                                 presorted=presorted, pregathered=fused_route,
                                 defer_unpermute=later)
+            if peers is not None:
+                peers.release(lw.index)
             if later:
                 y_perm, perm = out
                 return y_perm, ("routed", y_perm, perm, weights, reduce and fc is not None)
