@@ -482,3 +482,46 @@ def test_fp8_kv_pages_write_rule_and_engine_tokens():
     same = sum(a == b for x, y in zip(outs[None], outs["fp8"]) for a, b in zip(x, y))
     total = sum(len(x) for x in outs[None])
     assert same >= 0.7 * total, (outs[None], outs["fp8"])
+
+
+def test_decode_steps_in_flight_give_the_same_tokens():
+    """Two-turn decode (the next step is issued before the last one is read) against plain
+    stepping: requests that stop at different lengths, one aborted while steps are in
+    flight, one that arrives in the middle; every call returns one step's tokens."""
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    cfg = Qwen3MoeConfig.tiny()
+    prompts = [[(7 * i + j) % cfg.vocab_size for i in range(n)] for j, n in enumerate((12, 30, 19, 8))]
+    lens = (5, 40, 17, 26)
+
+    def run(pipeline):
+        model = Qwen3MoeModel(cfg, "cpu", torch.float32).init_random(seed=0)
+        eng = LLMEngine(model, num_pages=128, max_num_seqs=8, max_model_len=128, use_graphs=False,
+                        pipeline_decode=pipeline)
+        eng.stream_steps = 7                      # several uploads of the step state per request
+        ids = [eng.add_request(p, SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True))
+               for p, n in zip(prompts[:3], lens[:3])]
+        got, calls, late = {i: [] for i in ids}, 0, None
+        while eng.has_work():
+            outs = eng.step()
+            calls += 1
+            for o in outs:
+                got.setdefault(o.request_id, []).extend(o.new_token_ids)
+            per_call = {}
+            for o in outs:
+                per_call[o.request_id] = per_call.get(o.request_id, 0) + len(o.new_token_ids)
+            assert all(v <= 1 for v in per_call.values())          # one step per call
+            if calls == 9:
+                eng.abort(ids[2])
+            if calls == 12:
+                late = eng.add_request(prompts[3], SamplingParams(temperature=0.0, max_tokens=lens[3],
+                                                                  ignore_eos=True))
+        return [got[i] for i in ids] + [got[late]], calls, eng
+    plain, calls_plain, eng0 = run(False)
+    piped, calls_piped, eng = run(True)
+    assert plain[0] == piped[0] and plain[1] == piped[1] and plain[3] == piped[3]
+    assert len(plain[0]) == 5 and len(plain[1]) == 40 and len(plain[3]) == 26
+    n = min(len(plain[2]), len(piped[2]))
+    assert n >= 5 and plain[2][:n] == piped[2][:n]                  # the aborted one, up to the abort
+    assert eng._stream is None and eng.blocks.num_free == eng0.blocks.num_free   # no page leaked

@@ -12,6 +12,8 @@ crates/engine/src/worker.rs:1587 (worker loop), docs/architecture.md:128
 """
 from __future__ import annotations
 
+import os
+
 import itertools
 import time
 from typing import Optional
@@ -79,7 +81,7 @@ class LLMEngine:
                  policy: Optional[Policy] = None, weights_identity: str = "random-init",
                  watchdog_timeout: float = 150.0, host_kv_pages: int = 0,
                  host_kv_ratio: float = 0.0, host_kv_gib: Optional[float] = None,
-                 kv_dtype: Optional[str] = None):
+                 kv_dtype: Optional[str] = None, pipeline_decode: Optional[bool] = None):
         self.model = model
         self.device = model.device
         if kv_dtype in ("fp8", "fp8_e4m3", "e4m3"):
@@ -115,6 +117,12 @@ class LLMEngine:
         self._ids = itertools.count()
         self.failed: Optional[str] = None
         self.health = None        # parallel.health.Heartbeat of a multi-rank deployment
+        # decode steps in flight (two turns): US_PIPELINE_DECODE=0 reads every step before the
+        # next is issued
+        self.pipeline_decode = pipeline_decode if pipeline_decode is not None else \
+            (self.device.type == "cuda" and os.environ.get("US_PIPELINE_DECODE", "1") == "1")
+        self.stream_steps = 32    # steps per upload of the step state
+        self._stream = None
         self.asleep = 0           # sleep level (0 = awake)
         self._parked: list = []   # weights held in host memory while asleep at level 2
         self._parked_hosts: dict = {}
@@ -172,6 +180,9 @@ class LLMEngine:
                 break
         self.blocks.flush()
         freed = 0
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self._stream = None                     # steps in flight have completed
         self.runner.release_graphs()
         for pair in self.runner.kv_caches:
             for t in pair:
@@ -216,9 +227,84 @@ class LLMEngine:
         return {"level": 0, "was": level}
 
     # ------------------------------------------------------------------ step --
+    # ------------------------------------------------- decode steps in flight --
+    def _stream_start(self):
+        """Starts a stream of decode steps when every running request is decoding and
+        nothing waits: pages for the next steps are taken now, the step state is uploaded
+        once, and two steps are issued before the first is read."""
+        sch = self.scheduler
+        rows = [r for r in sch.running if r.output_ids and r.num_computed == r.num_tokens - 1]
+        if not rows or len(rows) != len(sch.running) or sch.waiting or self.profiler is not None:
+            return None
+        if self.runner.variant_for(rows) == "logits":
+            return None
+        limit = min(self.runner.history_steps, self.stream_steps,
+                    min(self.config.max_model_len - r.num_tokens for r in rows),
+                    max(r.params.max_tokens - len(r.output_ids) for r in rows))
+        if limit < 2:
+            return None
+        for r in rows:
+            pages = self.blocks.allocate(sch._pages_needed(r, r.num_tokens + limit))
+            if pages is None:
+                return None
+            r.pages.extend(pages)
+        if getattr(self.blocks, "host_slots", 0):
+            self.runner.apply_kv_moves(*self.blocks.take_moves())
+        st = self.runner.decode_begin(rows)
+        st.limit = limit
+        return st
+
+    def _stream_step(self) -> list:
+        """One call = one step's tokens.  The next step is already on the device when this
+        one is read (two turns in flight), so the host's share of a step - reading, stop
+        rules, page commits, streaming - overlaps the device's."""
+        from .scheduler import Batch, Chunk
+        st, sch = self._stream, self.scheduler
+        self.watchdog.begin(f"decode stream step {st.collected}")
+        try:
+            while not st.draining and st.launched < st.limit and st.launched - st.collected < 2:
+                self.runner.decode_launch(st)
+            toks = self.runner.decode_collect(st, st.collected)
+        except Exception as e:
+            self._stream = None
+            self.failed = f"{ErrorClass.FATAL_WORKER_FAILURE.value}: {e}"
+            if self.health is not None:
+                self.health.report_failure(self.failed)
+            raise
+        finally:
+            self.watchdog.end()
+        st.collected += 1
+        live = [(i, r) for i, r in enumerate(st.rows)
+                if not r.finished and r.request_id in sch.requests]
+        outs = []
+        if live:
+            V = self.model.cfg.vocab_size
+            errors = {r.request_id: f"{ErrorClass.NUMERICAL_FAULT.value}: sampled token {toks[i]}"
+                      for i, r in live if toks[i] < 0 or toks[i] >= V}
+            batch = Batch("decode", [Chunk(r, r.num_tokens - 1, 1, True) for _, r in live])
+            sch.stats["decode_tokens"] += len(live)
+            outs = sch.update(batch, {r.request_id: int(toks[i]) for i, r in live}, None, errors)
+        # the set of rows changed, or somebody waits: read what is in flight, then re-plan
+        if len(sch.running) != len(st.rows) or sch.waiting or \
+                any(r.finished for r in st.rows):
+            st.draining = True
+        if st.collected >= st.launched and (st.draining or st.launched >= st.limit):
+            self._stream = None
+        elif st.draining and not any(not r.finished and r.request_id in sch.requests
+                                     for r in st.rows):
+            self._stream = None             # nobody is left to read the steps in flight for
+        return outs
+
     def step(self) -> list:
         if self.asleep:
             return []
+        if self._stream is None and self.pipeline_decode:
+            self._stream = self._stream_start()
+        if self._stream is not None:
+            outs = self._stream_step()
+            if self.blocks.kv_events is not None:
+                self.blocks.kv_events.flush()
+            return outs
         batch = self.scheduler.schedule()
         if batch is None:
             return []

@@ -15,7 +15,7 @@ project paths.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Optional
 
 import torch
@@ -79,6 +79,23 @@ class DecodeGraph:
     logits: Optional[torch.Tensor]
     sampled: torch.Tensor
     launches: int = 0
+
+
+@dataclass
+class DecodeStream:
+    """Decode steps of one fixed set of rows, issued one at a time and read back one at a
+    time (see ``CausalLmRunner.decode_begin``)."""
+    rows: list
+    n: int
+    B: int
+    blk: object
+    graph: object
+    variant: str
+    launched: int = 0
+    collected: int = 0
+    limit: int = 0              # steps the rows have cache pages for
+    draining: bool = False      # no further step is issued; the ones in flight are read
+    events: list = field(default_factory=list)
 
 
 class CausalLmRunner:
@@ -411,6 +428,49 @@ class CausalLmRunner:
         else:
             out = blk.history[:steps, :n].clone()
         return out, info
+
+    # ------------------------------------------------ decode steps in flight --
+    def decode_begin(self, rows: list) -> "DecodeStream":
+        """Uploads the step state of ``rows`` once; ``decode_launch`` then issues one decode
+        step at a time (the device advances positions, slots and input tokens itself) and
+        ``decode_collect`` reads a step's tokens once its own copy has landed - so the host
+        can issue step k + 1 before it has read step k."""
+        n = len(rows)
+        B = self.bucket_for(n)
+        blk = self._decode_block(B)
+        variant = self.variant_for(rows)
+        assert variant != "logits"
+        self._fill_decode(blk, rows, B)
+        g = self._graph(B, variant) if B <= self.buckets[-1] or B in self._graphs else None
+        self.h2d_bytes += blk.upload()
+        return DecodeStream(rows=list(rows), n=n, B=B, blk=blk, graph=g, variant=variant)
+
+    def decode_launch(self, st: "DecodeStream") -> None:
+        k = st.launched
+        assert k < self.history_steps
+        self.announce("replay" if st.graph is not None else "eager", st.B, 1)
+        if st.graph is not None:
+            st.graph.graph.replay()
+            N.launch_count += st.graph.launches
+        else:
+            self._decode_body(st.blk, st.B, st.variant)
+        if self.device.type == "cuda":
+            st.blk.readback[k:k + 1].copy_(st.blk.history[k:k + 1], non_blocking=True)
+            self._queue_status_copy()
+            ev = torch.cuda.Event()
+            ev.record()
+            st.events.append(ev)
+        st.launched += 1
+
+    def decode_collect(self, st: "DecodeStream", k: int) -> list:
+        """Tokens of step ``k`` (one per row of the stream), on the host."""
+        assert k < st.launched
+        if self.device.type == "cuda":
+            st.events[k].synchronize()
+            self.check_device_status()
+            self.d2h_bytes += st.n * 4 + 4
+            return st.blk.readback[k, :st.n].tolist()
+        return st.blk.history[k, :st.n].tolist()
 
     def _to_host(self, t: torch.Tensor) -> torch.Tensor:
         host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
