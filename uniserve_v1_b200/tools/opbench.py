@@ -72,6 +72,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="decode: page type")
     a = ap.parse_args()
     tbs, tfl, tag = peaks()
     dev, bf = "cuda", torch.bfloat16
@@ -301,10 +302,20 @@ def main():
         sl = torch.full((B,), a.ctx, dtype=torch.int32, device=dev)
         splits = a.splits or F.decode_splits(B, Hkv, a.ctx)
         scratch, counters = F.decode_scratch(B, Hq, Hkv, D, splits, dev)
+        ks = vs = None
+        esz = 2.0
+        if a.kv == "fp8":            # E4M3 pages with one scale per page and plane
+            kc = torch.randint(0, 120, kc.shape, dtype=torch.uint8, device=dev)
+            vc = torch.randint(0, 120, vc.shape, dtype=torch.uint8, device=dev)
+            ks = torch.rand(pages, device=dev) * 0.01 + 0.001
+            vs = torch.rand(pages, device=dev) * 0.01 + 0.001
+            esz = 1.0
         ms = timeit(lambda: F.paged_decode_attention(q, kc, vc, pt, sl, 1 / math.sqrt(D), splits,
-                                                     scratch=scratch, counters=counters),
+                                                     scratch=scratch, counters=counters,
+                                                     k_scale=ks, v_scale=vs),
                     a.iters)
-        byts = 2.0 * B * a.ctx * Hkv * D * 2
+        byts = 2.0 * B * a.ctx * Hkv * D * esz
+        out["kv"] = a.kv
         out.update(batch=B, ctx=a.ctx, splits=splits, ms=ms, tbs=byts / ms / 1e9,
                    frac_memory=byts / ms / 1e9 / tbs)
     out["roofline"] = tag
