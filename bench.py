@@ -423,6 +423,9 @@ def qwen3_record(job: Job) -> dict:
     model = Qwen3MoeModel(cfg, dev, torch.bfloat16, ctx,
                           expert_quant=args.expert_quant).init_random(seed=0)
     model.exchange = exchange
+    if world > 1 and layout == "tp-ep" and os.environ.get("US_NO_FUSED", "0") != "1":
+        from uniserve_v1_b200.parallel.tp_fused import attach_fused_tp
+        attach_fused_tp(model, 8192)          # prefill chunks: fused reduce-scatter / all-gather
     mark("weights ready")
 
     if not is_attention:

@@ -144,9 +144,22 @@ def _worker(rank, world, port, q):
     torch.cuda.synchronize()
     result["status"] = N.read_status()
     result["tokens"] = out
+    # 4. prefill chunks above the one-shot limit: reduce-scatter in the GEMM epilogue, all-gather
+    #    from the norm kernel, no library collective in the layer loop
+    from uniserve_v1_b200.parallel.tp_fused import attach_fused_tp
+    ft = attach_fused_tp(model, 1024)
+    long_prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (300, 700, 41)]
+    eng2 = LLMEngine(model, num_pages=256, max_num_seqs=4, max_model_len=1024, use_graphs=True,
+                     max_num_batched_tokens=1024)
+    result["long_tokens"] = eng2.generate(long_prompts, SamplingParams(temperature=0.0, max_tokens=6,
+                                                                       ignore_eos=True))
+    torch.cuda.synchronize()
+    result["fused_prefills"] = ft.calls
+    result["status2"] = N.read_status()
     if rank == 0:
         q.put(result)
     dist.barrier()
+    ft.close()
     fc.close()
     dist.destroy_process_group()
 
@@ -183,6 +196,15 @@ def test_fused_collectives_and_sharded_engine(world):
     need_first, need_all = (len(single), 0.7) if world == 2 else (len(single) - 1, 0.5)
     assert firsts >= need_first, (single, res["tokens"])
     assert agree >= need_all * total, (single, res["tokens"])
+    # the fused tensor-parallel prefill served those long prompts, and gives the single GPU's tokens
+    assert res["fused_prefills"] >= 1 and res["status2"] == 0, res
+    long_prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (300, 700, 41)]
+    single_long = LLMEngine(model, num_pages=256, max_num_seqs=4, max_model_len=1024,
+                            max_num_batched_tokens=1024).generate(
+        long_prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    firsts = sum(s_[0] == t[0] for s_, t in zip(single_long, res["long_tokens"]))
+    agree = sum(a == b for s_, t in zip(single_long, res["long_tokens"]) for a, b in zip(s_, t))
+    assert firsts >= len(single_long) - 1 and agree >= 0.5 * 18, (single_long, res["long_tokens"])
 
 
 def _h3_worker(rank, world, port, q):

@@ -263,6 +263,8 @@ def serve(args) -> int:
         if ctx is not None and ctx.tp_size > 1 and device.type == "cuda":
             from .parallel.symm import attach_fused
             attach_fused(ctx, device, hidden=cfg.hidden_size)
+            from .parallel.tp_fused import attach_fused_tp      # prefill chunks: fused RS / AG
+            attach_fused_tp(model, int(pkg.max_num_batched_tokens or 8192))
 
         def make_engine(pkg=pkg):
             policy = None

@@ -245,7 +245,38 @@ reduce_slots_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ slots, int n_s
   }
 }
 
+// Partial rows -> the slot of the rank that owns them (a reduce-scatter by peer stores for a
+// partial sum that no GEMM epilogue produced, e.g. the un-permuted expert output): row r goes
+// to peers[r / peer_rows] at row slot * peer_rows + r % peer_rows.  One CTA per row, 16-byte
+// stores: a row leaves as one contiguous run of whole lines.
+__global__ void __launch_bounds__(kThreads)
+push_rows_to_slots_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const PeerRows dst,
+                          int rows, int H, int peer_rows, int slot) {
+  US_PDL_PROLOGUE();
+  const int r = blockIdx.x;
+  const int p = r / peer_rows;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ldx);
+  uint4* out = reinterpret_cast<uint4*>(dst.y[p] +
+                                        ((long long)slot * peer_rows + (r - p * peer_rows)) * H);
+  for (int v = threadIdx.x; v < (H >> 3); v += kThreads) out[v] = src[v];
+}
+
 }  // namespace
+
+US_API int us_push_rows_to_slots(const void* x, long long ldx, void* const* peers, int n_peers,
+                                 int rows, int H, int peer_rows, int slot, void* stream) {
+  US_REQUIRE(x && peers && n_peers >= 1 && n_peers <= 8 && rows >= 0 && H > 0 && (H % 8) == 0 &&
+             (ldx % 8) == 0 && peer_rows > 0 && peer_rows * n_peers >= rows && slot >= 0);
+  if (rows == 0) return US_OK;
+  PeerRows dst;
+  dst.n = n_peers;
+  for (int p = 0; p < 8; ++p) dst.y[p] = p < n_peers ? (__nv_bfloat16*)peers[p] : nullptr;
+  for (int p = 0; p < n_peers; ++p) US_REQUIRE(dst.y[p] && ((uintptr_t)dst.y[p] % 16) == 0);
+  us::launch_pdl(push_rows_to_slots_kernel, dim3(rows), dim3(kThreads), 0, (cudaStream_t)stream,
+                 (const __nv_bfloat16*)x, ldx, dst, rows, H, peer_rows, slot);
+  US_LAUNCH_CHECK();
+  return US_OK;
+}
 
 US_API int us_rmsnorm(const void* x, const void* w, void* y, int T, int H, long long ldx,
                       long long ldy, float eps, void* stream) {

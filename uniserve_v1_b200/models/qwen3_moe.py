@@ -113,6 +113,9 @@ FUSED_ROUTE_SORT = _os.environ.get("US_ROUTE_SORT", "0") == "1"
 # experts; US_UNPERMUTE_FUSED=0 is the A/B switch.
 FUSED_ROUTE_GATHER = _os.environ.get("US_ROUTE_FUSED", "0") == "1"
 FUSED_UNPERMUTE = _os.environ.get("US_UNPERMUTE_FUSED", "1") == "1"
+# Tensor-parallel prefill above this many rows takes the fused reduce-scatter / all-gather path
+# when a FusedTP heap is attached (US_TP_FUSED=0: library all-reduce instead).
+TP_FUSED_MIN_ROWS = 256 if _os.environ.get("US_TP_FUSED", "1") == "1" else 1 << 30
 
 
 @dataclass
@@ -177,6 +180,7 @@ class Qwen3MoeModel:
         self.expert_ranks = getattr(self.ctx, "expert_ranks", None)
         self.source_ranks = getattr(self.ctx, "source_ranks", None)
         self.exchange = None
+        self.tp_fused = None            # parallel.tp_fused.FusedTP: prefill with fused collectives
         self.weight_peers = None        # parallel.dwdp: experts read from the peers' shards
         self.moe_layer_order: list = []
         if self.expert_ranks is not None:
@@ -400,7 +404,10 @@ class Qwen3MoeModel:
             return F.unpermute_add_rmsnorm(y_perm, perm, weights, residual, w, eps)
         return fc.allreduce_add_rmsnorm(h, residual, w, eps)
 
-    def _attention(self, fc, lw: LayerWeights, x, positions, meta: AttnMeta, kcache, vcache):
+    def _attention(self, fc, lw: LayerWeights, x, positions, meta: AttnMeta, kcache, vcache,
+                   project: bool = True):
+        """``project=False`` returns the heads' output [T, Hq_l * D] before the output
+        projection (the caller runs it as a GEMM whose epilogue reduce-scatters)."""
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         T = x.shape[0]
         qkv = F.linear(x, lw.qkv)
@@ -426,6 +433,8 @@ class Qwen3MoeModel:
         else:
             from ..ops.attention import prefill_attention
             att = prefill_attention(qkv, Hq, Hkv, D, meta, kcache, vcache, self.scale)
+        if not project:
+            return att.reshape(T, Hq * D), None
         out = F.linear(att.reshape(T, Hq * D), lw.o_proj)
         if fc is not None:
             return out, ("sum",)
@@ -440,13 +449,16 @@ class Qwen3MoeModel:
         lw.fp8 = Fp8Experts.from_bf16(lw.w13, lw.w2)
         lw.w13 = lw.w2 = None
 
-    def _mlp(self, fc, lw: LayerWeights, x, defer: bool = True):
+    def _mlp(self, fc, lw: LayerWeights, x, defer: bool = True, reduce_out: bool = True):
         """Returns (hidden, pending); see ``_reduce_norm``.  ``defer=False`` returns finished
-        rows (no pending un-permute) for callers that use them without a norm."""
+        rows (no pending un-permute) for callers that use them without a norm;
+        ``reduce_out=False`` returns this rank's partial sum (the caller reduce-scatters it)."""
         cfg = self.cfg
         T = x.shape[0]
         if lw.dense:
             h = F.linear_gated(x, lw.w13[0])
+            if not reduce_out:
+                return h, ("down", lw.w2[0])       # the caller's GEMM reduce-scatters
             out = F.linear(h, lw.w2[0])
             if fc is not None:
                 return out, ("sum",)
@@ -480,7 +492,7 @@ class Qwen3MoeModel:
             order = self.moe_layer_order
             nxt = order[(order.index(lw.index) + 1) % len(order)]
             w13, w2 = peers.layer_weights(lw.index, nxt if len(order) > 1 else None)
-        reduce = self.ctx.ep_size > 1 and peers is None
+        reduce = self.ctx.ep_size > 1 and peers is None and reduce_out
         small = x.is_cuda and T <= 512 and lw.fp8 is None
         # decode-size batches: route, sort and gather in one launch; the un-permute rides on
         # the norm (or the fused all-reduce) that follows
@@ -523,6 +535,11 @@ class Qwen3MoeModel:
         ``kv_caches[layer] = (k, v)`` each [pages, page_size, Hkv_local, D]."""
         self._live = meta.live
         T = input_ids.shape[0]
+        ft = self.tp_fused
+        if ft is not None and meta.kind == "prefill" and input_ids.is_cuda and self.pp == 1 \
+                and self.exchange is None and self.weight_peers is None and meta.rows_real is None \
+                and T > TP_FUSED_MIN_ROWS and ft.padded(T, ft.P) <= ft.rows_max:
+            return self._forward_tp_fused(ft, input_ids, positions, meta, kv_caches)
         fc = self._fused(T, input_ids.is_cuda)
         if fc is not None:
             fc.begin_forward()
@@ -550,6 +567,58 @@ class Qwen3MoeModel:
             x, _ = self._reduce_norm(fc, hidden, site, residual, self.final_norm)
         # every stage samples the same tokens from the last stage's rows
         return self.ctx.broadcast(x.contiguous(), last, "layer")
+
+    def _forward_tp_fused(self, ft, input_ids, positions, meta: AttnMeta, kv_caches):
+        """Tensor-parallel prefill with the collectives inside the kernels: the residual stream
+        is row-sharded (rank r owns rows [r * ro, (r + 1) * ro) in FP32), every row-parallel
+        product leaves as a reduce-scatter (the output projection's GEMM epilogue, or a row
+        push for the un-permuted expert output), and the slot sum + residual add + RMSNorm
+        kernel stores the normalised rows into every rank's gathered buffer, so the next
+        column-parallel GEMM is local.  No library collective runs in the layer loop."""
+        from ..parallel.tp_fused import SITE_NORM_A, SITE_NORM_B
+        cfg, eps = self.cfg, self.cfg.rms_norm_eps
+        T, H = input_ids.shape[0], cfg.hidden_size
+        P, r = ft.P, ft.rank
+        ft.set_rows(ft.padded(T, P))
+        Tp, ro = ft.rows, ft.ro
+
+        def padded(t):                       # [T, n] -> [Tp, n], zero rows behind
+            if t.shape[0] == Tp:
+                return t
+            out = torch.zeros(Tp, t.shape[1], dtype=t.dtype, device=t.device)
+            out[:T] = t
+            return out
+        hidden = F.embedding(input_ids, self.embed)
+        lo, hi = r * ro, min((r + 1) * ro, T)
+        residual = torch.zeros(ro, H, dtype=torch.float32, device=self.device)
+        if hi > lo:
+            residual[:hi - lo] = hidden[lo:hi].float()
+        site_in, site_out = SITE_NORM_A, SITE_NORM_B
+        ft.barrier()                         # every rank has left its previous use of the sites
+        xa = ft.gathered(site_in)
+        xa[:T] = F.rmsnorm(hidden, self.layers[self.layer_lo].input_norm, eps)
+        if Tp > T:
+            xa[T:].zero_()
+        for i in range(self.layer_lo, self.layer_hi):
+            lw = self.layers[i]
+            kc, vc = kv_caches[i]
+            att, _ = self._attention(None, lw, ft.gathered(site_in)[:T], positions, meta, kc, vc,
+                                     project=False)
+            ft.reduce_scatter_linear(lw.o_proj, padded(att))
+            ft.barrier()                     # every partial row has landed in its owner's slots
+            ft.reduce_add_rmsnorm(residual, lw.post_norm, site_out, eps)
+            ft.barrier()                     # every normalised row has landed everywhere
+            out, pending = self._mlp(None, lw, ft.gathered(site_out)[:T], defer=False,
+                                     reduce_out=False)
+            if pending is not None and pending[0] == "down":
+                ft.reduce_scatter_linear(pending[1], padded(out))
+            else:
+                ft.push_rows(padded(out))
+            ft.barrier()
+            nxt = self.layers[i + 1].input_norm if i + 1 < self.layer_hi else self.final_norm
+            ft.reduce_add_rmsnorm(residual, nxt, site_in, eps)
+            ft.barrier()
+        return ft.gathered(site_in)[:T].clone()
 
     def encode(self, input_ids, num_layers: Optional[int] = None) -> torch.Tensor:
         """Encoder use of the decoder (text conditioning of the video family): one causal

@@ -37,6 +37,7 @@ N.register_signatures({
                                         N.I, N.I, N.P]),
     "us_reduce_slots_add_rmsnorm": (N.I, [N.P, N.I, N.P, N.P, N.P, N.I, N.I, N.I, N.L, N.F, N.I,
                                           N.P]),
+    "us_push_rows_to_slots": (N.I, [N.P, N.L, N.P, N.I, N.I, N.I, N.I, N.I, N.P]),
 })
 
 SITE_NORM_A, SITE_NORM_B, SITE_SLOTS, SITE_B0, SITE_B1 = 0, 1, 2, 3, 4
@@ -53,11 +54,40 @@ class FusedTP:
     def __init__(self, group, rank: int, world: int, device, rows_all: int, hidden: int):
         assert rows_all % world == 0
         self.P, self.rank, self.H = world, rank, hidden
-        self.rows, self.ro = rows_all, rows_all // world
-        self.bn = _row_block(self.ro)
+        self.rows_max = rows_all
         self.fc = FusedComm(group, rank, world, device, hidden=0, sites=7,
-                            site_bytes=world * self.ro * hidden * 2)
+                            site_bytes=rows_all * hidden * 2)
         self._ptrs = {}
+        self.set_rows(rows_all)
+        self._flip = 0
+
+    def set_rows(self, rows: int) -> None:
+        """The row count of the calls that follow (a multiple of 16 x world, at most the count
+        the heap was sized for).  Rank r owns rows [r * rows / P, (r + 1) * rows / P)."""
+        assert rows % (16 * self.P) == 0 and rows <= self.rows_max, (rows, self.rows_max)
+        self.rows, self.ro = rows, rows // self.P
+        self.bn = _row_block(self.ro)
+        self.calls += 1
+
+    calls = 0
+
+    @staticmethod
+    def padded(rows: int, world: int) -> int:
+        unit = 16 * world
+        return (rows + unit - 1) // unit * unit
+
+    def barrier(self) -> None:
+        """The next of the two barrier sites in turn (a site's flags may be reused only after
+        another site's barrier was crossed)."""
+        self.fc.barrier(SITE_B0 if self._flip == 0 else SITE_B1)
+        self._flip ^= 1
+
+    def push_rows(self, x: torch.Tensor) -> None:
+        """Partial rows [rows, hidden] (bf16, any row stride) into the owners' slot of this
+        rank: the reduce-scatter of a partial sum that did not come out of a GEMM."""
+        assert x.shape[0] == self.rows and x.shape[1] == self.H and x.stride(1) == 1
+        N.call("us_push_rows_to_slots", N.ptr(x), x.stride(0), self.ptrs(SITE_SLOTS), self.P,
+               self.rows, self.H, self.ro, self.rank, N.stream())
 
     def close(self):
         self.fc.close()
@@ -79,7 +109,7 @@ class FusedTP:
 
     def _own_row_ptrs(self, site: int):
         """Address of this rank's row interval inside every rank's gathered buffer."""
-        key = ("rows", site)
+        key = ("rows", site, self.ro)
         arr = self._ptrs.get(key)
         if arr is None:
             off = self.rank * self.ro * self.H * 2
@@ -127,3 +157,15 @@ class FusedTP:
         self.reduce_scatter_linear(w2, hidden)
         self.fc.barrier(SITE_B1)                      # every partial has landed
         return self.reduce_add_rmsnorm(residual, next_norm_w, out_site, eps)
+
+
+def attach_fused_tp(model, rows_max: int = 8192):
+    """Gives a tensor-parallel model the heap of its fused prefill path (collective: every rank
+    of the tensor group calls it).  ``rows_max``: the largest prefill chunk."""
+    ctx = model.ctx
+    if ctx.tp_size <= 1 or model.device.type != "cuda" or model.pp != 1:
+        return None
+    ax = ctx.axis("tensor")
+    model.tp_fused = FusedTP(ax.group, ax.rank, ax.size, model.device,
+                             FusedTP.padded(rows_max, ax.size), model.cfg.hidden_size)
+    return model.tp_fused

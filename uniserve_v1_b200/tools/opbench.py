@@ -52,7 +52,7 @@ def timeit(fn, iters=10, warmup=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["flash", "gemm", "gated", "decode", "moe", "fused-norm",
+    ap.add_argument("op", choices=["delta", "flash", "gemm", "gated", "decode", "moe", "fused-norm",
                                    "ulysses", "tp", "moe-fp8", "gemm-fp8", "gemm-fp8t", "ep",
                                    "rank-decode"])
     ap.add_argument("--tp", type=int, default=8, help="rank-decode: ranks of the emulated layout")
@@ -271,9 +271,48 @@ def main():
         ms2 = timeit(lambda: N_.call("us_gemm_wx_pull", N_.ptr(wout), ptr_a, 1, hl * D, N_.ptr(o),
                                      H, hl * D, rows, hl * D, hl * D, H, 0, bn, N_.stream()),
                      a.iters)
+        # the Ulysses return: attention over the scattered heads, rows pushed to their owner
+        full = fc.site_tensor(0, rows, W)
+        full.copy_(rnd(rows, W))
+        qh, kh, vh = full[:, :hl * D], full[:, hl * D:2 * hl * D], full[:, 2 * hl * D:]
+        cu = torch.tensor([0, rows], dtype=torch.int32, device=dev)
+        ms3 = timeit(lambda: N_.call("us_flash_attn_push", N_.ptr(qh), N_.ptr(kh), N_.ptr(vh),
+                                     N_.ptr(cu), N_.ptr(cu), rows, rows, hl, hl, W, W, W,
+                                     1.0 / math.sqrt(D), ptr_a, 1, rows, 0, hl * D, N_.stream()),
+                     max(2, a.iters // 3))
+        out.update(push_ms=ms3, push_tflops=4.0 * rows * rows * hl * D / ms3 / 1e9)
         out.update(rows=rows, hidden=H, heads_local=hl, scatter_ms=ms1,
                    scatter_tflops=2.0 * rows * W * H / ms1 / 1e9, pull_ms=ms2,
                    pull_tflops=2.0 * rows * H * hl * D / ms2 / 1e9)
+    elif a.op == "delta":
+        # recurrent layer kernels at the Qwen3.5 shape: a decode step of `batch` sequences
+        # (state traffic bound) and a prefill of `rows` tokens of one sequence (latency bound)
+        from ..ops import gated_delta as GD
+        Hk, Hv, Dk, Dv = 16, 32, 128, 128
+        B = a.batch
+        pool = torch.zeros(B, Hv, Dk, Dv, dtype=torch.float32, device=dev)
+        A = -(torch.rand(Hv, device=dev) * 2 + 0.2)
+        dtb = torch.rand(Hv, device=dev)
+
+        def run(T, cu, slots):
+            q, k, v = rnd(T, Hk, Dk), rnd(T, Hk, Dk), rnd(T, Hv, Dv)
+            ar, br = rnd(T, Hv), rnd(T, Hv)
+            return timeit(lambda: GD.gated_delta_rule_packed(q, k, v, pool, cu, slots,
+                                                             raw=(ar, br, A, dtb)), a.iters)
+        cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        ms_dec = run(B, cu, cu[:B])
+        T = min(a.rows, 4096)
+        cu1 = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        ms_pre = run(T, cu1, cu[:1])
+        state_bytes = 2.0 * B * Hv * Dk * Dv * 4
+        C = 2 * Hk * Dk + Hv * Dv
+        x, w = rnd(T, C), rnd(C, 4)
+        st = torch.zeros(1, 3, C, dtype=bf, device=dev)
+        ms_conv = timeit(lambda: GD.causal_conv1d(x, w, st, cu=cu1, slots=cu[:1]), a.iters)
+        out.update(batch=B, decode_ms=ms_dec, decode_tbs=state_bytes / ms_dec / 1e9,
+                   frac_memory=state_bytes / ms_dec / 1e9 / tbs, prefill_tokens=T,
+                   prefill_ms=ms_pre, us_per_token=ms_pre * 1e3 / T, conv_ms=ms_conv,
+                   conv_tbs=2.0 * T * C * 2 / ms_conv / 1e9)
     elif a.op == "tp":
         # the fused tensor-parallel MLP with this rank as its own (only) peer: gated
         # up-projection gathering its rows by TMA from the heap, down-projection
