@@ -275,7 +275,9 @@ def test_reference_afd_package_resolves_to_an_expert_union():
     import pytest
     from uniserve_v1_b200.config.policy import Package
     from uniserve_v1_b200.server import multirank as MR
-    root = "/root/reference/configs"
+    from pathlib import Path
+    root = os.environ.get("UNISERVE_REFERENCE_CONFIGS",
+                          str(Path(__file__).resolve().parents[2] / "reference" / "configs"))
     if not os.path.isdir(root):
         pytest.skip("reference configs not present")
     afd = Package.load(os.path.join(root, "afd/qwen3_moe"))

@@ -451,5 +451,7 @@ class LLMEngine:
         s = dict(self.scheduler.stats)
         s.update({"kv": self.blocks.stats(), "running": len(self.scheduler.running),
                   "waiting": len(self.scheduler.waiting), "h2d_bytes": self.runner.h2d_bytes,
-                  "d2h_bytes": self.runner.d2h_bytes})
+                  "d2h_bytes": self.runner.d2h_bytes,
+                  "blocking_calls": dict(self.runner.blocking),
+                  "blocking_seconds": self.runner.blocking_s})
         return s

@@ -113,6 +113,10 @@ class CausalLmRunner:
         self.use_graphs = use_graphs and self.device.type == "cuda"
         self.buckets = [b for b in DECODE_BUCKETS if b < max_num_seqs] + [max_num_seqs]
         self.history_steps = history_steps
+        # always-on counters of the places where the host waits for the device, by site
+        # (reference: the blocking-call counters of the engine's profiling layer)
+        self.blocking = {"decode_readback": 0, "stream_readback": 0, "to_host": 0}
+        self.blocking_s = 0.0
         self._blocks: dict = {}
         self._graphs: dict = {}
         self._pool = None
@@ -421,7 +425,7 @@ class CausalLmRunner:
             host = blk.readback[:steps]
             host.copy_(blk.history[:steps], non_blocking=True)
             self._queue_status_copy()          # read with the tokens, no extra synchronisation
-            torch.cuda.current_stream().synchronize()
+            self._wait(torch.cuda.current_stream().synchronize, "decode_readback")
             self.check_device_status()
             self.d2h_bytes += steps * n * 4 + 4
             out = host[:, :n]
@@ -466,7 +470,7 @@ class CausalLmRunner:
         """Tokens of step ``k`` (one per row of the stream), on the host."""
         assert k < st.launched
         if self.device.type == "cuda":
-            st.events[k].synchronize()
+            self._wait(st.events[k].synchronize, "stream_readback")
             self.check_device_status()
             self.d2h_bytes += st.n * 4 + 4
             return st.blk.readback[k, :st.n].tolist()
@@ -476,10 +480,18 @@ class CausalLmRunner:
         host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
         host.copy_(t, non_blocking=True)
         self._queue_status_copy()
-        torch.cuda.current_stream().synchronize()
+        self._wait(torch.cuda.current_stream().synchronize, "to_host")
         self.check_device_status()
         self.d2h_bytes += host.numel() * host.element_size()
         return host
+
+    def _wait(self, fn, site: str) -> None:
+        """A host wait on the device, counted by site with the time it took."""
+        import time as _time
+        t0 = _time.perf_counter()
+        fn()
+        self.blocking[site] += 1
+        self.blocking_s += _time.perf_counter() - t0
 
     # ------------------------------------------------ shaping outside graphs --
     def _shape_and_sample(self, logits: torch.Tensor, rows: list):

@@ -283,4 +283,7 @@ class EngineService:
                 self.obs.set("uniserve_running_requests", st["running"])
                 self.obs.set("uniserve_waiting_requests", st["waiting"])
                 self.obs.set("uniserve_preemptions_total", st["preemptions"])
+                for site, n in (st.get("blocking_calls") or {}).items():
+                    self.obs.set("uniserve_blocking_calls_total", n, {"site": site})
+                self.obs.set("uniserve_blocking_seconds_total", st.get("blocking_seconds", 0.0))
                 self.obs.snapshot()

@@ -217,8 +217,9 @@ def op_tp(b: Bench, a):
     b.row("down GEMM -> reduce-scatter (peer stores)", ms2, flops=2.0 * rows * I * H,
           link_bytes=(P - 1) * (rows // P) * H * 2.0, rows=rows)
     ms3 = b.time(lambda: tp.reduce_add_rmsnorm(res, nw, TP.SITE_NORM_B, 1e-6), a.iters)
-    b.row("slot sum + residual + RMSNorm", ms3, hbm_bytes=(rows // P) * H * (2.0 * P + 4 + 4 + 2),
-          rows_own=rows // P)
+    b.row("slot sum + residual + RMSNorm + all-gather stores", ms3,
+          hbm_bytes=(rows // P) * H * (2.0 * P + 4 + 4 + 2),
+          link_bytes=(P - 1) * (rows // P) * H * 2.0, rows_own=rows // P)
 
     def nccl():
         full = torch.empty(rows, H, dtype=torch.bfloat16, device=b.dev)
