@@ -83,7 +83,8 @@ def test_linear_bf16(rows, M, K):
 
 
 @pytest.mark.parametrize("rows,M,K", [(64, 768, 2048), (64, 2048, 512), (33, 128, 2048),
-                                       (7, 1000, 256), (16, 5120, 4096), (1, 24, 768)])
+                                       (7, 1000, 256), (16, 5120, 4096), (1, 24, 768),
+                                       (64, 128, 4096), (20, 512, 1536)])
 def test_linear_decode_kernel(rows, M, K, monkeypatch):
     """The weight-streaming kernel of decode-size projections (at most 64 rows, K a multiple
     of 256): bf16 and fp32 outputs, bias, a strided activation view, and the same result as

@@ -15,7 +15,14 @@
 // CTA = 8 warps = 2 groups of 8 output features x 4 slices of K; grid = M / 16.
 // K order inside an instruction is free (both operands use the same order), so a lane's
 // one 16-byte weight load (8 consecutive k of its feature) feeds two instructions.
+//
+// Few output features (a router's 128, one rank's share of a QKV projection) would leave
+// most SMs idle with one CTA per 16 features: such launches split K over the S CTAs of a
+// thread-block cluster (grid = M / 16 x S).  CTA s takes the K iterations s, s + S, ...;
+// the partial sums meet in the first CTA through distributed shared memory, in a fixed
+// order (the result does not depend on timing).
 #include "include/us_common.cuh"
+#include "include/us_tc05.cuh"
 
 namespace {
 
@@ -50,7 +57,8 @@ template <int MT>
 __global__ void __launch_bounds__(256)
 linear_decode_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                      void* __restrict__ out, const void* __restrict__ bias, int rows, int M, int K,
-                     long long ldw, long long ldx, long long ldo, int out_f32, int bias_f32) {
+                     long long ldw, long long ldx, long long ldo, int out_f32, int bias_f32,
+                     int ksplit) {
   // Weights are never written by a kernel: the first loads go out before the wait on the
   // kernels that produce the activation.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -66,14 +74,18 @@ linear_decode_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
   const int feat = blockIdx.x * kFeat + ng * 8 + n;
   const bool feat_ok = feat < M;
   const __nv_bfloat16* wrow = W + (long long)(feat_ok ? feat : 0) * ldw;
-  const int iters = K / kIterK;
+  // this CTA's K iterations: every ksplit-th one starting at its cluster rank
+  const int kr = ksplit > 1 ? (int)tc::cluster_ctarank() : 0;
+  const int all_iters = K / kIterK;
+  const int iters = all_iters > kr ? (all_iters - kr + ksplit - 1) / ksplit : 0;
+  auto k_of = [&](int it) { return (it * ksplit + kr) * kIterK; };
   constexpr int kAhead = 4;                             // iterations of weights in registers
   uint4 wreg[kAhead][2];
   // lane's weights of iteration it: k = it*256 + ks*64 + b*32 + kq*8 .. +7, b = 0, 1
   auto load_w = [&](int it, uint4 (&dst)[2]) {
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
-      const int k = it * kIterK + ks * kChunk + b * 32 + kq * 8;
+      const int k = k_of(it) + ks * kChunk + b * 32 + kq * 8;
       dst[b] = (feat_ok && it < iters)
                    ? __ldg(reinterpret_cast<const uint4*>(wrow + k))
                    : make_uint4(0, 0, 0, 0);
@@ -89,7 +101,7 @@ linear_decode_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     for (int p = threadIdx.x; p < kPieces; p += 256) {
       const int r = p / (kIterK / 8), c = p - r * (kIterK / 8);
       cp_async16(&xs[buf][r][swz(c, r)],
-                 X + (long long)(r < rows ? r : 0) * ldx + it * kIterK + c * 8, r < rows);
+                 X + (long long)(r < rows ? r : 0) * ldx + k_of(it) + c * 8, r < rows);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -147,6 +159,37 @@ linear_decode_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     red[ks][ng][m * 16 + n + 8][2 * kq + 1] = acc[m][3];
   }
   __syncthreads();
+  if (ksplit > 1) {
+    // every CTA folds its K slices into slice 0, then the first CTA of the cluster adds the
+    // others' sums in rank order
+    for (int e = threadIdx.x; e < 16 * MT * kFeat; e += 256) {
+      const int r = e / kFeat, f = e - r * kFeat;
+      float v = 0.f;
+#pragma unroll
+      for (int s = 0; s < kSlices; ++s) v += red[s][f >> 3][r][f & 7];
+      red[0][f >> 3][r][f & 7] = v;
+    }
+    tc::cluster_sync();
+    if (kr == 0) {
+      for (int e = threadIdx.x; e < 16 * MT * kFeat; e += 256) {
+        const int r = e / kFeat, f = e - r * kFeat;
+        const int col = blockIdx.x * kFeat + f;
+        if (r >= rows || col >= M) continue;
+        const uint32_t local = (uint32_t)__cvta_generic_to_shared(&red[0][f >> 3][r][f & 7]);
+        float v = red[0][f >> 3][r][f & 7];
+        for (int p = 1; p < ksplit; ++p) v += tc::ld_dsmem_f32(tc::map_to_cta(local, (uint32_t)p));
+        if (bias)
+          v += bias_f32 ? reinterpret_cast<const float*>(bias)[col]
+                        : us::bf2f(reinterpret_cast<const __nv_bfloat16*>(bias)[col]);
+        if (out_f32)
+          reinterpret_cast<float*>(out)[(long long)r * ldo + col] = v;
+        else
+          reinterpret_cast<__nv_bfloat16*>(out)[(long long)r * ldo + col] = us::f2bf(v);
+      }
+    }
+    tc::cluster_sync();           // nobody leaves while its sums may still be read
+    return;
+  }
   for (int e = threadIdx.x; e < 16 * MT * kFeat; e += 256) {
     const int r = e / kFeat, f = e - r * kFeat;
     const int col = blockIdx.x * kFeat + f;
@@ -189,15 +232,47 @@ US_API int us_linear_decode(const void* W, const void* X, void* out, const void*
                                        2 * kStages * 8192));
     configured = true;
   }
+  // K split over a cluster when one CTA per 16 features would leave most SMs idle
+  static int sms = 0;
+  static int max_split = -1;
+  if (sms == 0) {
+    int dev = 0;
+    US_CUDA_CHECK(cudaGetDevice(&dev));
+    US_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const char* e = getenv("US_LINEAR_KSPLIT");      // 1 switches the split off
+    max_split = e ? atoi(e) : 8;
+    if (max_split < 1) max_split = 1;
+    if (max_split > 8) max_split = 8;
+  }
+  int ksplit = 1;
+  const int iters = K / kIterK;
+  // double while the CTAs still fit one wave and every CTA keeps at least one K iteration
+  while (ksplit * 2 <= max_split && (int)grid.x * ksplit * 2 <= sms && iters >= ksplit * 2)
+    ksplit *= 2;
+  auto launch = [&](auto kernel, size_t smem) -> cudaError_t {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid.x, ksplit);
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = us::pdl_enabled() ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = ksplit;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ksplit > 1 ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, w, x, out, bias, rows, M, K, ldw, ldx, ldo, out_f32,
+                              bias_f32, ksplit);
+  };
   // kStages buffers x (16 MT) rows x 512 bytes
   if (rows <= 16)
-    US_CUDA_CHECK(us::launch_pdl(linear_decode_kernel<1>, grid, block, kStages * 8192, stream, w,
-                                 x, out, bias, rows, M, K, ldw, ldx, ldo, out_f32, bias_f32));
+    US_CUDA_CHECK(launch(linear_decode_kernel<1>, kStages * 8192));
   else if (rows <= 32)
-    US_CUDA_CHECK(us::launch_pdl(linear_decode_kernel<2>, grid, block, 2 * kStages * 8192, stream,
-                                 w, x, out, bias, rows, M, K, ldw, ldx, ldo, out_f32, bias_f32));
+    US_CUDA_CHECK(launch(linear_decode_kernel<2>, 2 * kStages * 8192));
   else
-    US_CUDA_CHECK(us::launch_pdl(linear_decode_kernel<4>, grid, block, 4 * kStages * 8192, stream,
-                                 w, x, out, bias, rows, M, K, ldw, ldx, ldo, out_f32, bias_f32));
+    US_CUDA_CHECK(launch(linear_decode_kernel<4>, 4 * kStages * 8192));
   return US_OK;
 }
