@@ -464,3 +464,69 @@ def test_eval_check_change_against_control(live_server):
     r = late["records"][0]
     r["submit_s"], r["ttft_s"] = late["timeline"][0]["issued_s"] + 0.001, w1 + 30.0
     assert any("inside the change window" in f for f in E.check_change(late, control))
+
+
+def test_hot_restart_hands_the_listener_to_a_successor(tmp_path):
+    """`POST /admin/restart`: a successor process takes the listening socket over, the first
+    process finishes and exits, requests before, during and after are answered alike."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import urllib.request
+    port = _free_port()
+    pkg = tmp_path / "pkg"
+    pkg.mkdir()
+    (pkg / "config.toml").write_text('model = "random:tiny"\nserved_model_name = "tiny"\n'
+                                     f'[admin_config]\nhost = "127.0.0.1"\nport = {port}\n')
+    env = dict(os.environ, UNISERVE_CPU_RANKS="1")
+    env.pop("RANK", None)
+    proc = subprocess.Popen([sys.executable, "-m", "uniserve_v1_b200", "serve", str(pkg)], env=env,
+                            cwd=os.path.dirname(os.path.dirname(__file__)))
+    base = f"http://127.0.0.1:{port}"
+    body = json.dumps({"model": "tiny", "messages": [{"role": "user", "content": "hello there"}],
+                       "max_tokens": 8, "temperature": 0, "ignore_eos": True}).encode()
+
+    def get(path):
+        with urllib.request.urlopen(base + path, timeout=5) as r:
+            return json.loads(r.read())
+
+    def chat():
+        req = urllib.request.Request(base + "/v1/chat/completions", data=body,
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return json.loads(r.read())["choices"][0]["message"]["content"]
+    successor = None
+    try:
+        for _ in range(240):
+            try:
+                first = get("/health")["pid"]
+                break
+            except Exception:
+                assert proc.poll() is None, "server ended"
+                time.sleep(0.5)
+        assert first == proc.pid
+        want = chat()
+        req = urllib.request.Request(base + "/admin/restart", data=b"", method="POST")
+        with urllib.request.urlopen(req, timeout=30) as r:
+            out = json.loads(r.read())
+        assert r.status == 202 and out["state"] == "starting" and out["successor_pid"]
+        successor = out["successor_pid"]
+        assert chat() == want                         # whoever accepts it answers
+        for _ in range(240):
+            try:
+                if get("/health")["pid"] == successor and proc.poll() is not None:
+                    break
+            except Exception:
+                pass
+            time.sleep(0.5)
+        assert proc.poll() is not None, "the first process did not leave"
+        assert get("/health")["pid"] == successor and chat() == want
+    finally:
+        if proc.poll() is None:
+            proc.terminate()
+        if successor:
+            try:
+                os.kill(successor, 15)
+            except ProcessLookupError:
+                pass

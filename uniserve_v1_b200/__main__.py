@@ -310,12 +310,34 @@ def serve(args) -> int:
                          # cache over the same weights) beside the serving one
                          engine_builder=make_engine if bus is None else None,
                          state_dir=getattr(args, "state_dir", None))
+    # The listening socket is this process's own object (not uvicorn's), so that a successor
+    # started by `POST /admin/restart` can inherit it: no connection is refused while the
+    # deployment changes hands.
+    import socket as _socket
+    listener = None
+    if getattr(args, "listen_fd", None) is not None:
+        listener = _socket.socket(fileno=args.listen_fd)          # handed over by a predecessor
+    elif not pkg.admin_config.uds:
+        listener = _socket.socket(_socket.AF_INET, _socket.SOCK_STREAM)
+        listener.setsockopt(_socket.SOL_SOCKET, _socket.SO_REUSEADDR, 1)
+        listener.bind((pkg.admin_config.host, pkg.admin_config.port or 8000))
+        listener.listen(2048)
+    if listener is not None:
+        listener.set_inheritable(True)
+    config = uvicorn.Config(app, host=pkg.admin_config.host, port=pkg.admin_config.port or 8000,
+                            uds=pkg.admin_config.uds if listener is None else None,
+                            fd=listener.fileno() if listener is not None else None,
+                            log_level=(args.log_level_http or "warning"))
+    server = uvicorn.Server(config)
+    if world == 1 and listener is not None:
+        from .server.restart import HotRestart
+        app.state.restart = HotRestart(server, listener, sys.argv[1:])
     if args.ready_fd is not None:
         os.write(args.ready_fd, json.dumps({"state": "listening", "host": pkg.admin_config.host,
-                                            "port": pkg.admin_config.port}).encode() + b"\n")
+                                            "port": pkg.admin_config.port,
+                                            "pid": os.getpid()}).encode() + b"\n")
     try:
-        uvicorn.run(app, host=pkg.admin_config.host, port=pkg.admin_config.port or 8000,
-                    uds=pkg.admin_config.uds, log_level=(args.log_level_http or "warning"))
+        server.run()
     finally:
         if shutdown is not None:
             shutdown()
@@ -360,6 +382,8 @@ def main(argv=None) -> int:
     s = sub.add_parser("serve", help="serve a policy package")
     s.add_argument("package")
     s.add_argument("--ready-fd", type=int, default=None)
+    s.add_argument("--listen-fd", type=int, default=None,
+                   help="an already listening socket handed over by the process this one replaces")
     s.add_argument("--log-level", default=None)
     s.add_argument("--log-level-http", default=None)
     s.add_argument("--state-dir", default=None,

@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import asyncio
 import json
+import os
 import time
 import uuid
 from typing import Optional
@@ -339,6 +340,7 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
     async def health():
         ok = (s.service is None or (s.service.thread.is_alive() and not s.engine.failed))
         body = {"status": "ok" if ok else "failed", "uptime_seconds": time.time() - s.started,
+                "pid": os.getpid(),
                 "asleep": int(getattr(s.engine, "asleep", 0) or 0),
                 "routes": sorted(r.path for r in app.routes if hasattr(r, "path"))}
         return JSONResponse(body, status_code=200 if ok else 503)
@@ -719,6 +721,23 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
             return _err(400, str(e), param=e.path)
         status, body = apply_package(new)
         return JSONResponse(body, status_code=status)
+
+    @app.post("/admin/restart")
+    async def admin_restart():
+        """Hot restart: a successor process takes the listening socket over; this one finishes
+        the requests it took and exits (single-process deployments started by `serve`)."""
+        hr = getattr(app.state, "restart", None)
+        if hr is None:
+            return _err(409, "this deployment cannot hand its listener over (several ranks, a "
+                             "unix socket, or not started by `serve`)")
+        out = await asyncio.to_thread(hr.begin)
+        s.obs.event("restart", **{k: v for k, v in out.items() if v is not None})
+        return JSONResponse(out, status_code=202)
+
+    @app.get("/admin/restart")
+    async def admin_restart_status():
+        hr = getattr(app.state, "restart", None)
+        return hr.status() if hr is not None else {"state": None}
 
     @app.post("/admin/sleep")
     async def admin_sleep(level: int = 1):

@@ -1,0 +1,110 @@
+"""Hot restart of a single-process deployment: a successor process of the same command takes
+the listening socket over while the process it replaces finishes the requests it took.
+
+``POST /admin/restart`` starts ``python -m uniserve_v1_b200 serve ... --listen-fd N --ready-fd M``
+with the listening socket and one end of a pipe inherited.  The successor loads the model,
+starts serving on the SAME socket (both processes accept from one kernel queue for a moment)
+and writes a line to the pipe; this process then stops accepting and exits once its
+connections have ended.  No connection is refused: one that arrives meanwhile waits in the
+listener's queue until one of the two accepts it.  If the successor exits before it reports,
+this process keeps serving as before.  The successor needs its own share of the GPU's memory
+while both live (weights and a KV cache): a deployment sized to the whole GPU sleeps first
+(``POST /admin/sleep``) or restarts cold.
+
+Reference behaviour: crates/daemon/src/restart.rs:1-40 (reference project path; there the
+engines are separate processes that the successor adopts, here the engine lives in the serving
+process, so the successor builds its own).
+"""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from typing import Optional
+
+
+class HotRestart:
+    def __init__(self, server, listener, argv: list):
+        self.server, self.listener = server, listener
+        # the successor repeats this process's command line without hand-over arguments
+        self.argv = self._strip(argv, ("--listen-fd", "--ready-fd"))
+        self.state = "serving"          # serving | starting | handed_over | failed
+        self.successor: Optional[int] = None
+        self.error: Optional[str] = None
+        self._lock = threading.Lock()
+
+    @staticmethod
+    def _strip(argv: list, flags: tuple) -> list:
+        out, skip = [], False
+        for a in argv:
+            if skip:
+                skip = False
+                continue
+            if a in flags:
+                skip = True
+                continue
+            if any(a.startswith(f + "=") for f in flags):
+                continue
+            out.append(a)
+        return out
+
+    def begin(self, timeout: float = 600.0) -> dict:
+        with self._lock:
+            if self.state == "starting":
+                return self.status()
+            self.state, self.error = "starting", None
+        r, w = os.pipe()
+        os.set_inheritable(w, True)
+        fd = self.listener.fileno()
+        cmd = [sys.executable, "-m", "uniserve_v1_b200"] + self.argv + \
+            ["--listen-fd", str(fd), "--ready-fd", str(w)]
+        env = dict(os.environ)
+        for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+            env.pop(k, None)
+        proc = subprocess.Popen(cmd, pass_fds=(fd, w), env=env)
+        os.close(w)
+        self.successor = proc.pid
+        threading.Thread(target=self._wait, args=(proc, r, timeout), daemon=True,
+                         name="hot-restart").start()
+        return self.status()
+
+    def _wait(self, proc, r: int, timeout: float) -> None:
+        deadline = time.monotonic() + timeout
+        buf = b""
+        os.set_blocking(r, False)
+        try:
+            while time.monotonic() < deadline and b"\n" not in buf:
+                if proc.poll() is not None:
+                    break
+                try:
+                    chunk = os.read(r, 4096)
+                    if chunk:
+                        buf += chunk
+                        continue
+                except BlockingIOError:
+                    pass
+                time.sleep(0.05)
+        finally:
+            os.close(r)
+        ok = False
+        if b"\n" in buf:
+            try:
+                ok = json.loads(buf.split(b"\n")[0]).get("state") == "listening"
+            except ValueError:
+                ok = False
+        if ok:
+            self.state = "handed_over"
+            self.server.should_exit = True        # stop accepting, finish what was taken
+        else:
+            self.state = "failed"
+            self.error = "the successor ended before it served" if proc.poll() is not None \
+                else "the successor did not report in time"
+            if proc.poll() is None:
+                proc.terminate()
+
+    def status(self) -> dict:
+        return {"state": self.state, "pid": os.getpid(), "successor_pid": self.successor,
+                "error": self.error}
