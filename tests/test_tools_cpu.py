@@ -530,3 +530,87 @@ def test_hot_restart_hands_the_listener_to_a_successor(tmp_path):
                 os.kill(successor, 15)
             except ProcessLookupError:
                 pass
+
+
+def test_standby_is_promoted_when_the_serving_process_dies(tmp_path):
+    """`profiling_config.standby`: a parked second process with the model loaded takes the
+    listening socket when the serving process is killed, serves as generation 1 and parks a
+    standby of its own."""
+    import json
+    import os
+    import signal
+    import subprocess
+    import sys
+    import urllib.request
+    port = _free_port()
+    pkg = tmp_path / "pkg"
+    pkg.mkdir()
+    (pkg / "config.toml").write_text('model = "random:tiny"\nserved_model_name = "tiny"\n'
+                                     f'[admin_config]\nhost = "127.0.0.1"\nport = {port}\n'
+                                     '[profiling_config]\nstandby = true\n')
+    env = dict(os.environ, UNISERVE_CPU_RANKS="1")
+    env.pop("RANK", None)
+    proc = subprocess.Popen([sys.executable, "-m", "uniserve_v1_b200", "serve", str(pkg)], env=env,
+                            cwd=os.path.dirname(os.path.dirname(__file__)))
+    base = f"http://127.0.0.1:{port}"
+    body = json.dumps({"model": "tiny", "messages": [{"role": "user", "content": "hello there"}],
+                       "max_tokens": 8, "temperature": 0, "ignore_eos": True}).encode()
+
+    def get(path):
+        with urllib.request.urlopen(base + path, timeout=5) as r:
+            return json.loads(r.read())
+
+    def chat():
+        req = urllib.request.Request(base + "/v1/chat/completions", data=body,
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return json.loads(r.read())["choices"][0]["message"]["content"]
+    pids = []
+    try:
+        sb = {"state": "none"}
+        for _ in range(360):
+            try:
+                sb = get("/admin/standby")
+                if sb["state"] == "parked":
+                    break
+            except Exception:
+                assert proc.poll() is None, "server ended"
+            time.sleep(0.5)
+        assert sb["state"] == "parked" and sb["pid"] != proc.pid
+        pids.append(sb["pid"])
+        assert get("/health")["generation"] == 0
+        want = chat()
+        os.kill(proc.pid, signal.SIGKILL)               # the serving process dies
+        proc.wait(timeout=30)
+        h = None
+        for _ in range(120):
+            try:
+                h = get("/health")
+                if h["pid"] == sb["pid"]:
+                    break
+            except Exception:
+                pass
+            time.sleep(0.25)
+        assert h and h["pid"] == sb["pid"] and h["generation"] == 1
+        assert chat() == want
+        for _ in range(360):                            # and it parks its own standby
+            nxt = get("/admin/standby")
+            if nxt["state"] == "parked":
+                break
+            time.sleep(0.5)
+        assert nxt["state"] == "parked" and nxt["generation"] == 1
+        pids.append(nxt["pid"])
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+        for p in pids:                                  # the promoted one first: its standby leaves
+            try:
+                os.kill(p, signal.SIGTERM)
+            except ProcessLookupError:
+                pass
+        time.sleep(1.0)
+        for p in pids:
+            try:
+                os.kill(p, signal.SIGKILL)
+            except ProcessLookupError:
+                pass

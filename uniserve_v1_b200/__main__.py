@@ -329,9 +329,22 @@ def serve(args) -> int:
                             fd=listener.fileno() if listener is not None else None,
                             log_level=(args.log_level_http or "warning"))
     server = uvicorn.Server(config)
+    standby = None
     if world == 1 and listener is not None:
-        from .server.restart import HotRestart
+        from .server.restart import HotRestart, Standby, park
         app.state.restart = HotRestart(server, listener, sys.argv[1:])
+        app.state.generation = int(getattr(args, "generation", 0) or 0)
+        if getattr(args, "standby_fd", None) is not None:
+            # this process is a standby: park until the serving process ends
+            eng = getattr(app.state.s, "engine", None)
+            if not park(args.standby_fd, args.ready_fd, eng,
+                        pkg.profiling_config.standby_storage):
+                return 0
+            args.ready_fd = None
+        if pkg.profiling_config.standby:
+            standby = Standby(listener, sys.argv[1:], app.state.generation)
+            standby.start()
+            app.state.standby = standby
     if args.ready_fd is not None:
         os.write(args.ready_fd, json.dumps({"state": "listening", "host": pkg.admin_config.host,
                                             "port": pkg.admin_config.port,
@@ -339,6 +352,8 @@ def serve(args) -> int:
     try:
         server.run()
     finally:
+        if standby is not None and not getattr(app.state.restart, "state", "") == "failed":
+            standby.stop()
         if shutdown is not None:
             shutdown()
         for c in children:
@@ -382,6 +397,9 @@ def main(argv=None) -> int:
     s = sub.add_parser("serve", help="serve a policy package")
     s.add_argument("package")
     s.add_argument("--ready-fd", type=int, default=None)
+    s.add_argument("--standby-fd", type=int, default=None,
+                   help="park as a standby until this pipe closes (the serving process ended)")
+    s.add_argument("--generation", type=int, default=0, help="launch generation (standbys count up)")
     s.add_argument("--listen-fd", type=int, default=None,
                    help="an already listening socket handed over by the process this one replaces")
     s.add_argument("--log-level", default=None)

@@ -207,6 +207,8 @@ class ProfilingConfig:
     expert_load: bool = opt(True, "generation")
     pc_sampling: bool = opt(False, "epoch")
     watchdog_timeout: Duration = opt(Duration(150.0), "step")
+    standby: bool = opt(False, "daemon", "keep a parked standby process beside the serving one")
+    standby_storage: str = opt("auto", "daemon", "resident | suspended | auto")
     session: ProfilingSession = optf(ProfilingSession, "step")
 
 

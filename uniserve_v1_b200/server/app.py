@@ -340,7 +340,7 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
     async def health():
         ok = (s.service is None or (s.service.thread.is_alive() and not s.engine.failed))
         body = {"status": "ok" if ok else "failed", "uptime_seconds": time.time() - s.started,
-                "pid": os.getpid(),
+                "pid": os.getpid(), "generation": int(getattr(app.state, "generation", 0)),
                 "asleep": int(getattr(s.engine, "asleep", 0) or 0),
                 "routes": sorted(r.path for r in app.routes if hasattr(r, "path"))}
         return JSONResponse(body, status_code=200 if ok else 503)
@@ -733,6 +733,11 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         out = await asyncio.to_thread(hr.begin)
         s.obs.event("restart", **{k: v for k, v in out.items() if v is not None})
         return JSONResponse(out, status_code=202)
+
+    @app.get("/admin/standby")
+    async def admin_standby():
+        sb = getattr(app.state, "standby", None)
+        return sb.status() if sb is not None else {"state": "none"}
 
     @app.get("/admin/restart")
     async def admin_restart_status():

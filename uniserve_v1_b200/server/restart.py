@@ -108,3 +108,98 @@ class HotRestart:
     def status(self) -> dict:
         return {"state": self.state, "pid": os.getpid(), "successor_pid": self.successor,
                 "error": self.error}
+
+
+class Standby:
+    """A parked second process beside the serving one (``profiling_config.standby``).
+
+    The serving process starts it with the listening socket and the read end of a pipe
+    inherited.  The standby loads the model, builds its engine, optionally releases its KV
+    cache again (``standby_storage``: ``suspended`` or ``auto``), reports ``parked`` and blocks
+    on the pipe.  When the serving process ends for ANY reason the kernel closes the pipe's
+    write end: the standby wakes, restores what it released, and serves on the same socket -
+    connections that arrived meanwhile waited in the listener's queue - then starts a standby of
+    its own (the next generation).  A clean shutdown writes ``stop`` first and the standby
+    leaves too.  Requests that were in flight on the failed process are lost with it; their
+    clients (or the replica router's migration) send them again.
+
+    Reference behaviour: crates/daemon/src/standby/mod.rs:1-30, docs/configuration.md:534-535
+    (reference project paths; there a standby repeats a rank of an engine group under a
+    daemon, here the whole single-process deployment).
+    """
+
+    def __init__(self, listener, argv: list, generation: int = 0):
+        self.listener = listener
+        self.argv = HotRestart._strip(argv, ("--listen-fd", "--ready-fd", "--standby-fd",
+                                             "--generation"))
+        self.generation = generation
+        self.state = "none"             # none | starting | parked | failed
+        self.pid: Optional[int] = None
+        self._w: Optional[int] = None
+
+    def start(self) -> None:
+        r, w = os.pipe()                # the standby blocks on r; this process keeps w
+        pr, pw = os.pipe()              # the standby reports "parked" on pw
+        os.set_inheritable(r, True)
+        os.set_inheritable(pw, True)
+        fd = self.listener.fileno()
+        cmd = [sys.executable, "-m", "uniserve_v1_b200"] + self.argv + \
+            ["--listen-fd", str(fd), "--standby-fd", str(r), "--ready-fd", str(pw),
+             "--generation", str(self.generation + 1)]
+        env = dict(os.environ)
+        for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+            env.pop(k, None)
+        proc = subprocess.Popen(cmd, pass_fds=(fd, r, pw), env=env)
+        os.close(r)
+        os.close(pw)
+        self._w, self.pid, self.state = w, proc.pid, "starting"
+
+        def watch():
+            buf = b""
+            try:
+                while b"\n" not in buf:
+                    chunk = os.read(pr, 4096)
+                    if not chunk:
+                        break
+                    buf += chunk
+            finally:
+                os.close(pr)
+            self.state = "parked" if b"parked" in buf else "failed"
+        threading.Thread(target=watch, daemon=True, name="standby-watch").start()
+
+    def stop(self) -> None:
+        """Clean shutdown of the serving process: the standby leaves too."""
+        if self._w is not None:
+            try:
+                os.write(self._w, b"stop\n")
+                os.close(self._w)
+            except OSError:
+                pass
+            self._w = None
+
+    def status(self) -> dict:
+        return {"state": self.state, "pid": self.pid, "generation": self.generation}
+
+
+def park(standby_fd: int, ready_fd: Optional[int], engine, storage: str) -> bool:
+    """The standby's side: release what ``storage`` says, report, block until the serving
+    process ends.  Returns True when this process is to serve now, False when it was told to
+    leave."""
+    suspended = storage in ("suspended", "auto") and engine is not None and hasattr(engine, "sleep")
+    if suspended:
+        engine.sleep(1)
+    if ready_fd is not None:
+        os.write(ready_fd, json.dumps({"state": "parked", "pid": os.getpid()}).encode() + b"\n")
+        os.close(ready_fd)
+    buf = b""
+    while True:
+        chunk = os.read(standby_fd, 64)
+        if not chunk:
+            break                       # the writer is gone: the serving process ended
+        buf += chunk
+        if b"stop" in buf:
+            return False
+    os.close(standby_fd)
+    if suspended:
+        engine.wake()
+    return True
