@@ -115,3 +115,49 @@ def test_frame_is_explicit_and_validated():
     import_request(b, g)                         # the honest state still imports
     while b.has_work():
         b.step()
+
+
+def test_copy_manifests_cover_every_layout_pair_and_route_a_handoff():
+    """Resharding plans between tensor-parallel degrees (with replicated heads above the head
+    count): every destination head written once from a holder; replicated sources are spread;
+    routed through a real hand-off, an importer gets exactly the shards it needs."""
+    from uniserve_v1_b200.engine.manifest import CopyManifest, head_range
+    for heads in (1, 2, 4, 8):
+        for src in (1, 2, 4, 8, 16):
+            for dst in (1, 2, 4, 8, 16):
+                m = CopyManifest.plan(heads, src, dst)
+                m.check()
+    m = CopyManifest.plan(4, 2, 4)              # each source rank feeds two destination ranks
+    assert [m.sources_of(d) for d in range(4)] == [[0], [0], [1], [1]]
+    m = CopyManifest.plan(4, 4, 1)
+    assert m.sources_of(0) == [0, 1, 2, 3] and sum(c.heads for c in m.copies) == 4
+    m = CopyManifest.plan(2, 8, 2)              # the source replicates each head four times
+    assert len(m.copies) == 2 and {c.src_rank for c in m.copies} == {0, 7} or \
+        {c.src_rank // 4 for c in m.copies} == {0, 1}
+    assert head_range(2, 8, 5) == (1, 1) and head_range(8, 2, 1) == (4, 4)
+    assert CopyManifest.plan(8, 2, 4).bytes_moved(pages=3, page_size=16, head_dim=128, layers=2) \
+        == 8 * 2 * 3 * 16 * 128 * 2 * 2
+    # a TP1 export cut into the two shards a TP2 exporter would send, routed to a TP1 importer
+    pre, dec = _engines(2)
+    rid = pre.add_request(list(range(5, 45)), SamplingParams(temperature=0.0, max_tokens=4,
+                                                            ignore_eos=True))
+    while not pre.scheduler.requests[rid].output_ids:
+        pre.step()
+    h = export_request(pre, rid, release=False)
+    H = h.heads_total
+    shards = {}
+    for r in range(2):
+        lo, n = head_range(H, 2, r)
+        shards[r] = Handoff(**{**h.__dict__, "head_lo": lo,
+                               "kv": [None if p is None else (p[0][:, :, lo:lo + n], p[1][:, :, lo:lo + n])
+                                      for p in h.kv]})
+    routed = CopyManifest.plan(H, 2, 1).route(shards)
+    assert list(routed) == [0] and len(routed[0]) == 2
+    new = import_request(dec, routed[0])
+    ref = pre.generate([list(range(5, 45))], SamplingParams(temperature=0.0, max_tokens=4,
+                                                            ignore_eos=True))[0]
+    out = list(dec.scheduler.requests[new].output_ids)
+    while dec.has_work():
+        for o in dec.step():
+            out.extend(o.new_token_ids)
+    assert out == ref
