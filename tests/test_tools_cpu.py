@@ -614,3 +614,70 @@ def test_standby_is_promoted_when_the_serving_process_dies(tmp_path):
                 os.kill(p, signal.SIGKILL)
             except ProcessLookupError:
                 pass
+
+
+def test_a_dead_rank_takes_the_deployment_through_a_relaunch(tmp_path):
+    """The leader of a two-rank deployment watches the rank it started: when that process is
+    killed, the leader replaces itself with a fresh `serve` of the next generation on the same
+    listening socket, which starts the ranks again and answers as before."""
+    import json
+    import os
+    import signal
+    import subprocess
+    import sys
+    import urllib.request
+    port = _free_port()
+    pkg = tmp_path / "pkg"
+    pkg.mkdir()
+    (pkg / "config.toml").write_text('model = "random:tiny"\nserved_model_name = "tiny"\n'
+                                     'tensor_parallel_size = 2\n'
+                                     f'[admin_config]\nhost = "127.0.0.1"\nport = {port}\n')
+    env = dict(os.environ, UNISERVE_CPU_RANKS="1")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    proc = subprocess.Popen([sys.executable, "-m", "uniserve_v1_b200", "serve", str(pkg)], env=env,
+                            cwd=os.path.dirname(os.path.dirname(__file__)))
+    base = f"http://127.0.0.1:{port}"
+    body = json.dumps({"model": "tiny", "messages": [{"role": "user", "content": "hello there"}],
+                       "max_tokens": 8, "temperature": 0, "ignore_eos": True}).encode()
+
+    def get(path):
+        with urllib.request.urlopen(base + path, timeout=5) as r:
+            return json.loads(r.read())
+
+    def chat():
+        req = urllib.request.Request(base + "/v1/chat/completions", data=body,
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return json.loads(r.read())["choices"][0]["message"]["content"]
+    try:
+        for _ in range(360):
+            try:
+                ranks = get("/admin/ranks")
+                break
+            except Exception:
+                assert proc.poll() is None, "server ended"
+                time.sleep(0.5)
+        assert len(ranks["ranks"]) == 1 and ranks["ranks"][0]["alive"] and ranks["generation"] == 0
+        want = chat()
+        os.kill(ranks["ranks"][0]["pid"], signal.SIGKILL)
+        h = None
+        for _ in range(480):
+            try:
+                h = get("/health")
+                if h.get("generation") == 1 and h["status"] == "ok":
+                    break
+            except Exception:
+                pass
+            assert proc.poll() is None, "the leader ended instead of relaunching"
+            time.sleep(0.5)
+        assert h and h["generation"] == 1 and h["pid"] == proc.pid      # the same process, new image
+        assert get("/admin/ranks")["ranks"][0]["pid"] != ranks["ranks"][0]["pid"]
+        assert chat() == want
+    finally:
+        if proc.poll() is None:
+            proc.terminate()
+            try:
+                proc.wait(timeout=30)
+            except Exception:
+                proc.kill()

@@ -345,6 +345,25 @@ def serve(args) -> int:
             standby = Standby(listener, sys.argv[1:], app.state.generation)
             standby.start()
             app.state.standby = standby
+    supervision = None
+    if children and listener is not None:
+        # the leader watches the ranks it started; a rank that ends takes the deployment
+        # through a relaunch on the same socket
+        from .server.restart import Supervision
+        app.state.generation = int(getattr(args, "generation", 0) or 0)
+
+        def rank_failed(why):
+            eng = getattr(app.state.s, "engine", None)
+            if eng is not None:
+                try:
+                    eng.failed = f"fatal_worker_failure: {why}"
+                except Exception:
+                    pass
+        supervision = Supervision(children, listener, sys.argv[1:], app.state.generation,
+                                  on_failure=rank_failed,
+                                  relaunch=os.environ.get("UNISERVE_RELAUNCH", "1") == "1")
+        supervision.start()
+        app.state.supervision = supervision
     if args.ready_fd is not None:
         os.write(args.ready_fd, json.dumps({"state": "listening", "host": pkg.admin_config.host,
                                             "port": pkg.admin_config.port,
@@ -352,6 +371,8 @@ def serve(args) -> int:
     try:
         server.run()
     finally:
+        if supervision is not None:
+            supervision.stop()
         if standby is not None and not getattr(app.state.restart, "state", "") == "failed":
             standby.stop()
         if shutdown is not None:

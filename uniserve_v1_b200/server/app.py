@@ -734,6 +734,11 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         s.obs.event("restart", **{k: v for k, v in out.items() if v is not None})
         return JSONResponse(out, status_code=202)
 
+    @app.get("/admin/ranks")
+    async def admin_ranks():
+        sup = getattr(app.state, "supervision", None)
+        return sup.status() if sup is not None else {"ranks": [], "failed": None}
+
     @app.get("/admin/standby")
     async def admin_standby():
         sb = getattr(app.state, "standby", None)

@@ -203,3 +203,74 @@ def park(standby_fd: int, ready_fd: Optional[int], engine, storage: str) -> bool
     if suspended:
         engine.wake()
     return True
+
+
+class Supervision:
+    """The leader of a multi-rank deployment watches the rank processes it started.  When one
+    ends while the deployment serves, the deployment cannot go on (its collectives would wait
+    for the missing rank): the leader marks the engine failed (``/health`` answers 503, so a
+    router moves the requests), stops the other ranks, and - unless ``relaunch`` is off - replaces
+    its own image with a fresh ``serve`` of the next generation that inherits the listening
+    socket, which starts the ranks again.  Connections that arrive meanwhile wait in the
+    listener's queue.
+
+    Reference behaviour: crates/daemon/src/supervision (child supervision and relaunch of a
+    failure domain; reference project path).
+    """
+
+    def __init__(self, children: list, listener, argv: list, generation: int, on_failure=None,
+                 relaunch: bool = True, period: float = 0.5):
+        self.children, self.listener = children, listener
+        self.argv = HotRestart._strip(argv, ("--listen-fd", "--ready-fd", "--standby-fd",
+                                             "--generation"))
+        self.generation, self.on_failure, self.relaunch = generation, on_failure, relaunch
+        self.period = period
+        self.failed: Optional[str] = None
+        self._stop = threading.Event()
+        self.thread = threading.Thread(target=self._run, daemon=True, name="supervision")
+
+    def start(self) -> None:
+        self.thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+
+    def status(self) -> dict:
+        return {"ranks": [{"rank": i + 1, "pid": c.pid, "alive": c.poll() is None}
+                          for i, c in enumerate(self.children)],
+                "failed": self.failed, "generation": self.generation}
+
+    def _run(self) -> None:
+        while not self._stop.wait(self.period):
+            for i, c in enumerate(self.children):
+                code = c.poll()
+                if code is None:
+                    continue
+                self.failed = f"rank {i + 1} (pid {c.pid}) ended with code {code}"
+                if self.on_failure is not None:
+                    try:
+                        self.on_failure(self.failed)
+                    except Exception:
+                        pass
+                for other in self.children:
+                    if other.poll() is None:
+                        other.terminate()
+                for other in self.children:
+                    try:
+                        other.wait(timeout=10)
+                    except Exception:
+                        other.kill()
+                if self.relaunch and self.listener is not None:
+                    self._exec()
+                return
+
+    def _exec(self) -> None:
+        fd = self.listener.fileno()
+        os.set_inheritable(fd, True)
+        env = {k: v for k, v in os.environ.items()
+               if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT")}
+        cmd = [sys.executable, "-m", "uniserve_v1_b200"] + self.argv + \
+            ["--listen-fd", str(fd), "--generation", str(self.generation + 1)]
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os.execve(sys.executable, cmd, env)
