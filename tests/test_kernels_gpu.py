@@ -893,3 +893,32 @@ def test_prefill_decode_handoff_between_gpu_engines(kv):
     else:       # pages are re-quantised on import: near-ties of the random model may flip
         same = sum(a == b for x, y in zip(ref, got) for a, b in zip(x, y))
         assert [x[0] for x in got] == [x[0] for x in ref] and same >= 0.7 * 27, (ref, got)
+
+
+def test_two_expert_exchanges_live_side_by_side():
+    """Exchanges are handles, not a process-wide singleton: two of them (different sizes) are
+    alive at once, used alternately, and each gives the MoE layer its local form gives."""
+    from uniserve_v1_b200.parallel.expert_exchange import ExpertExchange
+    k, H, E, I = 4, 512, 16, 256
+    exs = [ExpertExchange(None, 0, 1, DEV, T, k, H, E, I) for T in (24, 40)]
+    assert exs[0].h.value != exs[1].h.value
+    w13, w2 = rnd(E, 2 * I, H, scale=0.03, seed=1), rnd(E, H, I, scale=0.03, seed=2)
+    nw = torch.ones(H, dtype=BF, device=DEV)
+    for it in range(3):
+        for n, ex in enumerate(exs):
+            T = ex.T
+            x = rnd(T, H, scale=0.5, seed=10 * it + n)
+            logits = rnd(T, E, dtype=torch.float32, seed=100 + 10 * it + n)
+            res = rnd(T, H, dtype=torch.float32, seed=200 + 10 * it + n)
+            ids, wts = F.topk_softmax(logits, k, True)
+            live = torch.full((1,), T, dtype=torch.int32, device=DEV)
+            ex.dispatch(x, ids, wts, live)
+            ex.experts(w13, w2, T)
+            res_ex = res.clone()
+            y = ex.combine_add_rmsnorm(ids, live, res_ex, nw, 1e-6)
+            y = y[0] if isinstance(y, tuple) else y
+            local = F.moe_experts(x, ids, wts, w13, w2)
+            y_ref, _ = F.add_rmsnorm(local, res.clone(), nw, 1e-6)
+            close(y, y_ref, 4e-2, 4e-2)
+    for ex in exs:
+        ex.close()

@@ -49,11 +49,11 @@ struct Ep {
   unsigned int* state = nullptr;   // [0] dispatch epoch, [1] combine epoch, [2] done counter,
                                    // [3] dispatch epochs seen by sort, [4] combine epochs seen
 };
-Ep g_ep;
-
-peer::Table table() {
+// One exchange per handle: a process may hold several (one per expert union it belongs to,
+// or one per micro-batch window).
+peer::Table table(const Ep& e) {
   peer::Table t;
-  for (int i = 0; i < peer::kMaxRanks; ++i) t.base[i] = g_ep.peers[i];
+  for (int i = 0; i < peer::kMaxRanks; ++i) t.base[i] = e.peers[i];
   return t;
 }
 
@@ -215,10 +215,13 @@ combine_add_rmsnorm_kernel(peer::Table pt, int rank, int lo, int hi, size_t off_
 
 // Allocates this rank's exchange heap (windows for T tokens per source rank, top-k k,
 // hidden H) and writes its IPC handle.
-US_API int us_ep_create(int world, int rank, int T, int k, int H, unsigned char* handle_out) {
+US_API int us_ep_create(int world, int rank, int T, int k, int H, unsigned char* handle_out,
+                        void** ep_out) {
   US_REQUIRE(world >= 1 && world <= peer::kMaxRanks && rank >= 0 && rank < world);
-  US_REQUIRE(T >= 1 && k >= 1 && k <= 32 && (H % 8) == 0 && g_ep.local == nullptr);
-  Ep& e = g_ep;
+  US_REQUIRE(T >= 1 && k >= 1 && k <= 32 && (H % 8) == 0 && handle_out && ep_out);
+  Ep* ep = new Ep();
+  *ep_out = ep;
+  Ep& e = *ep;
   e.world = world; e.rank = rank; e.T = T; e.k = k; e.H = H;
   auto align = [](size_t v) { return (v + 255) & ~(size_t)255; };
   e.off_flags = 0;
@@ -240,9 +243,10 @@ US_API int us_ep_create(int world, int rank, int T, int k, int H, unsigned char*
   return US_OK;
 }
 
-US_API int us_ep_attach(const unsigned char* handles) {
-  Ep& e = g_ep;
-  US_REQUIRE(e.local && handles);
+US_API int us_ep_attach(void* ep, const unsigned char* handles) {
+  US_REQUIRE(ep && handles);
+  Ep& e = *(Ep*)ep;
+  US_REQUIRE(e.local);
   for (int r = 0; r < e.world; ++r) {
     if (r == e.rank) continue;
     cudaIpcMemHandle_t h;
@@ -255,66 +259,73 @@ US_API int us_ep_attach(const unsigned char* handles) {
   return US_OK;
 }
 
-US_API int us_ep_destroy() {
-  Ep& e = g_ep;
+US_API int us_ep_destroy(void* ep) {
+  if (!ep) return US_OK;
+  Ep& e = *(Ep*)ep;
   for (int r = 0; r < peer::kMaxRanks; ++r)
     if (e.opened[r]) cudaIpcCloseMemHandle(e.peers[r]);
   if (e.local) cudaFree(e.local);
   if (e.state) cudaFree(e.state);
-  e = Ep();
+  delete (Ep*)ep;
   return US_OK;
 }
 
 // Pointers the expert side of the layer needs: this rank's windows and, for the FC2
 // epilogue, every source rank's combine buffer.
-US_API void* us_ep_window(int which) {   // 0 rows, 1 ids, 2 weights, 3 recv
-  Ep& e = g_ep;
+US_API void* us_ep_window(void* ep, int which) {   // 0 rows, 1 ids, 2 weights, 3 recv
+  if (!ep) return nullptr;
+  Ep& e = *(Ep*)ep;
   if (!e.local) return nullptr;
   const size_t off[4] = {e.off_x, e.off_ids, e.off_w, e.off_recv};
   return which >= 0 && which < 4 ? e.local + off[which] : nullptr;
 }
-US_API void* us_ep_peer_recv(int rank) {
-  Ep& e = g_ep;
+US_API void* us_ep_peer_recv(void* ep, int rank) {
+  if (!ep) return nullptr;
+  Ep& e = *(Ep*)ep;
   return (e.local && rank >= 0 && rank < e.world) ? e.peers[rank] + e.off_recv : nullptr;
 }
 
-US_API int us_ep_route_dispatch(const void* x, const int* ids, const float* weights,
+US_API int us_ep_route_dispatch(void* ep, const void* x, const int* ids, const float* weights,
                                 const int* live, int T, int experts_per_rank,
                                 int first_expert_rank, void* stream) {
-  Ep& e = g_ep;
+  US_REQUIRE(ep);
+  Ep& e = *(Ep*)ep;
   US_REQUIRE(e.local && x && ids && weights && T >= 1 && T <= e.T && experts_per_rank >= 1);
-  us::launch_pdl(route_dispatch_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, table(), e.world, e.rank, (const __nv_bfloat16*)x, ids, weights, live, T, e.k, e.H,
+  us::launch_pdl(route_dispatch_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, table(e), e.world, e.rank, (const __nv_bfloat16*)x, ids, weights, live, T, e.k, e.H,
       experts_per_rank, first_expert_rank, e.off_x, e.off_ids, e.off_w, e.off_flags, e.state);
   US_LAUNCH_CHECK();
   return US_OK;
 }
 
 // which: 0 = wait for the source ranks' dispatch, 1 = wait for the expert ranks' combine.
-US_API int us_ep_wait(int which, int lo, int hi, void* stream) {
-  Ep& e = g_ep;
+US_API int us_ep_wait(void* ep, int which, int lo, int hi, void* stream) {
+  US_REQUIRE(ep);
+  Ep& e = *(Ep*)ep;
   US_REQUIRE(e.local && (which == 0 || which == 1) && lo >= 0 && hi <= e.world && lo < hi);
-  us::launch_pdl(ep_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, table(), e.rank, lo, hi, which, e.off_flags,
+  us::launch_pdl(ep_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, table(e), e.rank, lo, hi, which, e.off_flags,
                                                      e.state, us_status_ptr());
   US_LAUNCH_CHECK();
   return US_OK;
 }
 
 // Expert rank: "my pushes of this layer are complete" to the source ranks [lo, hi).
-US_API int us_ep_signal_combined(int lo, int hi, void* stream) {
-  Ep& e = g_ep;
+US_API int us_ep_signal_combined(void* ep, int lo, int hi, void* stream) {
+  US_REQUIRE(ep);
+  Ep& e = *(Ep*)ep;
   US_REQUIRE(e.local && lo >= 0 && hi <= e.world && lo < hi);
-  us::launch_pdl(ep_signal_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, table(), e.rank, lo, hi, 1, e.off_flags,
+  us::launch_pdl(ep_signal_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, table(e), e.rank, lo, hi, 1, e.off_flags,
                                                        e.state);
   US_LAUNCH_CHECK();
   return US_OK;
 }
 
-US_API int us_ep_combine_add_rmsnorm(const int* ids, const int* live, void* residual,
+US_API int us_ep_combine_add_rmsnorm(void* ep, const int* ids, const int* live, void* residual,
                                      const void* w, void* y, int T, float eps, int expert_lo,
                                      int expert_hi, void* stream) {
-  Ep& e = g_ep;
+  US_REQUIRE(ep);
+  Ep& e = *(Ep*)ep;
   US_REQUIRE(e.local && ids && residual && w && y && T >= 1 && T <= e.T);
-  us::launch_pdl(combine_add_rmsnorm_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, table(), e.rank, expert_lo, expert_hi, e.off_recv, e.off_flags, ids, live, (float*)residual,
+  us::launch_pdl(combine_add_rmsnorm_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, table(e), e.rank, expert_lo, expert_hi, e.off_recv, e.off_flags, ids, live, (float*)residual,
       (const __nv_bfloat16*)w, (__nv_bfloat16*)y, e.k, e.H, eps, e.state, us_status_ptr());
   US_LAUNCH_CHECK();
   return US_OK;

@@ -24,15 +24,15 @@ from ..ops import functional as F
 from ..ops import native as N
 
 N.register_signatures({
-    "us_ep_create": (N.I, [N.I, N.I, N.I, N.I, N.I, N.P]),
-    "us_ep_attach": (N.I, [N.P]),
-    "us_ep_destroy": (N.I, []),
-    "us_ep_window": (N.P, [N.I]),
-    "us_ep_peer_recv": (N.P, [N.I]),
-    "us_ep_route_dispatch": (N.I, [N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.P]),
-    "us_ep_wait": (N.I, [N.I, N.I, N.I, N.P]),
-    "us_ep_signal_combined": (N.I, [N.I, N.I, N.P]),
-    "us_ep_combine_add_rmsnorm": (N.I, [N.P, N.P, N.P, N.P, N.P, N.I, N.F, N.I, N.I, N.P]),
+    "us_ep_create": (N.I, [N.I, N.I, N.I, N.I, N.I, N.P, N.P]),
+    "us_ep_attach": (N.I, [N.P, N.P]),
+    "us_ep_destroy": (N.I, [N.P]),
+    "us_ep_window": (N.P, [N.P, N.I]),
+    "us_ep_peer_recv": (N.P, [N.P, N.I]),
+    "us_ep_route_dispatch": (N.I, [N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.P]),
+    "us_ep_wait": (N.I, [N.P, N.I, N.I, N.I, N.P]),
+    "us_ep_signal_combined": (N.I, [N.P, N.I, N.I, N.P]),
+    "us_ep_combine_add_rmsnorm": (N.I, [N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.F, N.I, N.I, N.P]),
     "us_gemm_fp8_block_route_push": (N.I, [N.P, N.P, N.P, N.P, N.L, N.I, N.I, N.I, N.I, N.L, N.L,
                                            N.L, N.P, N.I, N.P, N.P, N.I, N.P, N.P, N.P, N.P, N.I,
                                            N.I, N.P]),
@@ -65,24 +65,26 @@ class ExpertExchange:
         self.e_lo = (rank - self.expert_ranks[0]) * self.experts_per_rank if self.is_expert else 0
         lib = N.kernels()
         handle = (ctypes.c_ubyte * 64)()
-        N.check(lib.us_ep_create(world, rank, t_max, top_k, hidden, handle), "us_ep_create")
+        self.h = ctypes.c_void_p()      # this exchange's handle (a process may hold several)
+        N.check(lib.us_ep_create(world, rank, t_max, top_k, hidden, handle, ctypes.byref(self.h)),
+                "us_ep_create")
         if world > 1:
             gathered = [None] * world
             dist.all_gather_object(gathered, bytes(handle), group=group)
             blob = b"".join(gathered)
             buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
-            N.check(lib.us_ep_attach(buf), "us_ep_attach")
+            N.check(lib.us_ep_attach(self.h, buf), "us_ep_attach")
             dist.barrier(group=group)
         R = world * t_max * top_k
 
         def view(which, nbytes, dtype, shape):
-            raw = torch.as_tensor(_DevBuf(lib.us_ep_window(which), nbytes), device=self.device)
+            raw = torch.as_tensor(_DevBuf(lib.us_ep_window(self.h, which), nbytes), device=self.device)
             return raw.view(dtype).view(*shape)
 
         self.win_x = view(0, world * t_max * hidden * 2, torch.bfloat16, (world * t_max, hidden))
         self.win_ids = view(1, R * 4, torch.int32, (world * t_max, top_k))
         self.win_w = view(2, R * 4, torch.float32, (R,))
-        self.recv_ptrs = (ctypes.c_void_p * world)(*[lib.us_ep_peer_recv(r) for r in range(world)])
+        self.recv_ptrs = (ctypes.c_void_p * world)(*[lib.us_ep_peer_recv(self.h, r) for r in range(world)])
         self._ws = {}
 
     def workspace(self, t_step: int):
@@ -96,20 +98,22 @@ class ExpertExchange:
         return ws
 
     def close(self):
-        N.kernels().us_ep_destroy()
+        if self.h:
+            N.kernels().us_ep_destroy(self.h)
+            self.h = ctypes.c_void_p()
 
     # ------------------------------------------------------------- source side --
     def dispatch(self, x, ids, weights, live=None) -> None:
         """Pushes the rows of this rank's tokens to the ranks that own their experts."""
         T = x.shape[0]
         assert T <= self.T, f"step of {T} rows exceeds the exchange capacity {self.T}"
-        N.call("us_ep_route_dispatch", N.ptr(x), N.ptr(ids), N.ptr(weights), N.ptr(live), T,
+        N.call("us_ep_route_dispatch", self.h, N.ptr(x), N.ptr(ids), N.ptr(weights), N.ptr(live), T,
                self.experts_per_rank, self.expert_ranks[0], N.stream())
 
     def combine_add_rmsnorm(self, ids, live, residual, w, eps: float):
         T = ids.shape[0]
         y = torch.empty(T, self.H, dtype=torch.bfloat16, device=self.device)
-        N.call("us_ep_combine_add_rmsnorm", N.ptr(ids), N.ptr(live), N.ptr(residual), N.ptr(w),
+        N.call("us_ep_combine_add_rmsnorm", self.h, N.ptr(ids), N.ptr(live), N.ptr(residual), N.ptr(w),
                N.ptr(y), T, eps, self.expert_ranks[0], self.expert_ranks[-1] + 1, N.stream())
         return y, residual
 
@@ -122,7 +126,7 @@ class ExpertExchange:
         E, I2, H = w13.shape
         I_ = I2 // 2
         R = self.world * t_step * self.k
-        N.call("us_ep_wait", 0, self.source_ranks[0], self.source_ranks[-1] + 1, st)
+        N.call("us_ep_wait", self.h, 0, self.source_ranks[0], self.source_ranks[-1] + 1, st)
         N.call("us_moe_sort", N.ptr(self.win_ids), R, self.e_lo, E, ws.block_n, ws.max_tiles,
                N.ptr(ws.sorted_route), N.ptr(ws.perm_of_route), N.ptr(ws.expert_offsets),
                N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
@@ -137,7 +141,7 @@ class ExpertExchange:
                self.recv_ptrs, self.world, N.ptr(ws.sorted_route), N.ptr(self.win_w),
                t_step * self.k, N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
                N.ptr(ws.num_tiles), ws.max_tiles, ws.block_n, st)
-        N.call("us_ep_signal_combined", self.source_ranks[0], self.source_ranks[-1] + 1, st)
+        N.call("us_ep_signal_combined", self.h, self.source_ranks[0], self.source_ranks[-1] + 1, st)
 
     def experts_fp8(self, ex, t_step: int, act: str = "silu") -> None:
         """``experts`` with block-scaled FP8 weights (``ops.fp8.Fp8Experts``): the rows
@@ -159,7 +163,7 @@ class ExpertExchange:
             o = lambda kb, r: torch.ones(kb, r + Q.PAD_ROWS, dtype=torch.float32,
                                          device=self.device)
             q8 = ws._fp8 = dict(xq=z(R, H), xs=o(H // 128, R), hq=z(R, I_), hs=o(I_ // 128, R))
-        N.call("us_ep_wait", 0, self.source_ranks[0], self.source_ranks[-1] + 1, st)
+        N.call("us_ep_wait", self.h, 0, self.source_ranks[0], self.source_ranks[-1] + 1, st)
         N.call("us_moe_sort", N.ptr(self.win_ids), R, self.e_lo, E, ws.block_n, ws.max_tiles,
                N.ptr(ws.sorted_route), N.ptr(ws.perm_of_route), N.ptr(ws.expert_offsets),
                N.ptr(ws.tile_group), N.ptr(ws.tile_row0), N.ptr(ws.tile_rows),
@@ -177,7 +181,7 @@ class ExpertExchange:
         N.call("us_gemm_fp8_block_route_push", N.ptr(ex.w2), N.ptr(ex.w2_scale), N.ptr(q8["hq"]),
                N.ptr(q8["hs"]), q8["hs"].stride(0), E, H, I_, R, I_, I_, H, self.recv_ptrs,
                self.world, N.ptr(ws.sorted_route), N.ptr(self.win_w), t_step * self.k, *tiles, st)
-        N.call("us_ep_signal_combined", self.source_ranks[0], self.source_ranks[-1] + 1, st)
+        N.call("us_ep_signal_combined", self.h, self.source_ranks[0], self.source_ranks[-1] + 1, st)
 
 
 class HostExpertExchange:
