@@ -922,3 +922,51 @@ def test_two_expert_exchanges_live_side_by_side():
             close(y, y_ref, 4e-2, 4e-2)
     for ex in exs:
         ex.close()
+
+
+def test_weights_keeper_maps_device_weights_into_another_process(tmp_path):
+    """A `keep` process holds the weights in ITS device memory; this process opens the CUDA IPC
+    handles, so its model's tensors are the keeper's memory, and generates the tokens of a model
+    with its own weights."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from uniserve_v1_b200.__main__ import _qwen3_model
+    from uniserve_v1_b200.config.policy import Package
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.server.weights_keeper import stop_keeper
+    pkg_dir = tmp_path / "pkg"
+    pkg_dir.mkdir()
+    (pkg_dir / "config.toml").write_text('model = "random:tiny"\nserved_model_name = "tiny"\n')
+    sock = str(tmp_path / "w.sock")
+    r, w = os.pipe()
+    os.set_inheritable(w, True)
+    proc = subprocess.Popen([sys.executable, "-m", "uniserve_v1_b200", "keep", str(pkg_dir),
+                             "--socket", sock, "--ready-fd", str(w)], pass_fds=(w,),
+                            cwd=os.path.dirname(os.path.dirname(__file__)))
+    os.close(w)
+    try:
+        info = json.loads(os.read(r, 4096).split(b"\n")[0])
+        assert info["state"] == "keeping"
+        pkg = Package.load(str(pkg_dir))
+        dev = torch.device("cuda", 0)
+        prompts = [[(3 * i + j) % 1000 for i in range(n)] for j, n in enumerate((9, 30))]
+        sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+        _, own, _ = _qwen3_model(pkg, None, dev, BF, None)
+        want = LLMEngine(own, num_pages=64, max_num_seqs=4, max_model_len=128).generate(prompts, sp)
+        before = torch.cuda.memory_allocated()
+        _, mapped, _ = _qwen3_model(pkg, None, dev, BF, None, sock)
+        assert mapped.weights_from["keeper_pid"] == proc.pid
+        assert torch.cuda.memory_allocated() - before < own.weight_bytes() // 4   # mapped, not copied
+        assert torch.equal(mapped.embed, own.embed)
+        got = LLMEngine(mapped, num_pages=64, max_num_seqs=4, max_model_len=128).generate(prompts, sp)
+        assert got == want
+        del mapped
+        assert stop_keeper(sock)
+        proc.wait(timeout=60)
+    finally:
+        os.close(r)
+        if proc.poll() is None:
+            proc.terminate()

@@ -681,3 +681,62 @@ def test_a_dead_rank_takes_the_deployment_through_a_relaunch(tmp_path):
                 proc.wait(timeout=30)
             except Exception:
                 proc.kill()
+
+
+def test_weights_keeper_serves_weights_to_restarting_engines(tmp_path):
+    """`keep` holds a model's weights in shared memory; engines built by `serve`'s own model
+    constructor map them (no second copy, tied tensors stay tied), give the tokens of a model
+    that loaded its own weights, and a keeper of another model is refused."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from uniserve_v1_b200.__main__ import _qwen3_model
+    from uniserve_v1_b200.config.policy import Package
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.server.weights_keeper import attach, stop_keeper
+    pkg_dir = tmp_path / "pkg"
+    pkg_dir.mkdir()
+    (pkg_dir / "config.toml").write_text('model = "random:tiny"\nserved_model_name = "tiny"\n')
+    sock = str(tmp_path / "w.sock")
+    r, w = os.pipe()
+    os.set_inheritable(w, True)
+    env = dict(os.environ, UNISERVE_CPU_RANKS="1")
+    proc = subprocess.Popen([sys.executable, "-m", "uniserve_v1_b200", "keep", str(pkg_dir),
+                             "--socket", sock, "--ready-fd", str(w)], env=env, pass_fds=(w,),
+                            cwd=os.path.dirname(os.path.dirname(__file__)))
+    os.close(w)
+    try:
+        line = os.read(r, 4096)
+        info = json.loads(line.split(b"\n")[0])
+        assert info["state"] == "keeping" and info["tensors"] > 10
+        pkg = Package.load(str(pkg_dir))
+        prompts = [[(3 * i + j) % 1000 for i in range(n)] for j, n in enumerate((9, 30))]
+        sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+        _, own, _ = _qwen3_model(pkg, None, torch.device("cpu"), torch.float32, None)
+        want = LLMEngine(own, num_pages=64, max_num_seqs=4, max_model_len=128,
+                         use_graphs=False).generate(prompts, sp)
+        for _ in range(2):                                   # an engine, then its restart
+            _, mapped, _ = _qwen3_model(pkg, None, torch.device("cpu"), torch.float32, None, sock)
+            assert mapped.weights_from["keeper_pid"] == proc.pid
+            assert torch.equal(mapped.embed, own.embed) and mapped.embed.data_ptr() != own.embed.data_ptr()
+            assert (mapped.lm_head is mapped.embed) == (own.lm_head is own.embed)
+            got = LLMEngine(mapped, num_pages=64, max_num_seqs=4, max_model_len=128,
+                            use_graphs=False).generate(prompts, sp)
+            assert got == want
+        # another model's keeper is refused: the caller loads the weights itself
+        from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+        import dataclasses
+        other = Qwen3MoeModel(dataclasses.replace(Qwen3MoeConfig.tiny(), num_hidden_layers=1), "cpu",
+                              torch.float32)
+        assert attach(other, sock) is False
+        assert attach(Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32),
+                      str(tmp_path / "nobody.sock")) is False
+        assert stop_keeper(sock)
+        proc.wait(timeout=30)
+        assert not os.path.exists(sock)
+    finally:
+        os.close(r)
+        if proc.poll() is None:
+            proc.terminate()

@@ -251,15 +251,8 @@ def serve(args) -> int:
             pp = axes.get("layer", 1) if world % axes.get("layer", 1) == 0 else 1
             ctx = ParallelContext.from_world(tensor=world // pp, layer=pp,
                                              expert_over_tensor=world // pp > 1)
-        if directory:
-            from .checkpoint.quantized import open_checkpoint
-            ld = open_checkpoint(directory, dtype)       # NVFP4 / FP8 exports expand on read
-            cfg = Qwen3MoeConfig.from_hf(ld.config)
-            model = Qwen3MoeModel(cfg, device, dtype, ctx).load_state(ld)
-        else:
-            cfg = Qwen3MoeConfig.tiny() if (pkg.model or "").endswith(":tiny") \
-                else Qwen3MoeConfig.qwen3_30b_a3b()
-            model = Qwen3MoeModel(cfg, device, dtype, ctx).init_random(0)
+        cfg, model, ld = _qwen3_model(pkg, directory, device, dtype, ctx,
+                                      getattr(args, "weights_socket", None))
         if ctx is not None and ctx.tp_size > 1 and device.type == "cuda":
             from .parallel.symm import attach_fused
             attach_fused(ctx, device, hidden=cfg.hidden_size)
@@ -385,6 +378,57 @@ def serve(args) -> int:
     return 0
 
 
+def _qwen3_model(pkg, directory, device, dtype, ctx, weights_socket=None):
+    """The package's Qwen3 model: mapped from a weights keeper when one answers on
+    ``weights_socket`` with this model's identity, else read from the checkpoint (or drawn
+    at random for ``random:`` models).  Returns (config, model, checkpoint loader or None)."""
+    from .models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    ld = None
+    if directory:
+        from .checkpoint.quantized import open_checkpoint
+        ld = open_checkpoint(directory, dtype)       # NVFP4 / FP8 exports expand on read
+        cfg = Qwen3MoeConfig.from_hf(ld.config)
+    else:
+        cfg = Qwen3MoeConfig.tiny() if (pkg.model or "").endswith(":tiny") \
+            else Qwen3MoeConfig.qwen3_30b_a3b()
+    model = Qwen3MoeModel(cfg, device, dtype, ctx)
+    if weights_socket:
+        from .server.weights_keeper import attach
+        if attach(model, weights_socket):
+            logging.info("weights mapped from the keeper at %s (%s)", weights_socket,
+                         model.weights_from)
+            return cfg, model, ld
+        logging.warning("no weights keeper with this model at %s: loading", weights_socket)
+    model = model.load_state(ld) if directory else model.init_random(0)
+    return cfg, model, ld
+
+
+def keep(args) -> int:
+    """``keep PACKAGE --socket PATH``: hold the package's weights for serving processes."""
+    import torch
+    from .checkpoint.safetensors_io import resolve_hub
+    from .config.policy import Package
+    from .server.weights_keeper import WeightsKeeper
+    pkg = Package.load(args.package)
+    logging.basicConfig(level=logging.INFO)
+    cpu = os.environ.get("UNISERVE_CPU_RANKS", "0") == "1" or not torch.cuda.is_available()
+    device = torch.device("cpu") if cpu else torch.device("cuda", 0)
+    dtype = torch.float32 if cpu else {"bfloat16": torch.bfloat16, "float16": torch.float16,
+                                       "float32": torch.float32}[pkg.dtype]
+    directory = pkg.model_dir or None
+    if directory is None and pkg.model and not pkg.model.startswith("random:"):
+        directory = str(resolve_hub(pkg.model))
+    _cfg, model, _ld = _qwen3_model(pkg, directory, device, dtype, None)
+    keeper = WeightsKeeper(model, args.socket)
+
+    def ready():
+        if args.ready_fd is not None:
+            os.write(args.ready_fd, json.dumps({"state": "keeping", "pid": os.getpid(),
+                                                "tensors": len(keeper.records)}).encode() + b"\n")
+    keeper.serve_forever(ready)
+    return 0
+
+
 def admin(args) -> int:
     """Admin client over plain HTTP (crates/manager/src/main.rs:1-25, reference project
     path): prints the server's JSON answer; exit status 1 on an HTTP error."""
@@ -418,6 +462,8 @@ def main(argv=None) -> int:
     s = sub.add_parser("serve", help="serve a policy package")
     s.add_argument("package")
     s.add_argument("--ready-fd", type=int, default=None)
+    s.add_argument("--weights-socket", default=None,
+                   help="map the weights from a `keep` process on this unix socket when it answers")
     s.add_argument("--standby-fd", type=int, default=None,
                    help="park as a standby until this pipe closes (the serving process ended)")
     s.add_argument("--generation", type=int, default=0, help="launch generation (standbys count up)")
@@ -431,6 +477,10 @@ def main(argv=None) -> int:
                    help="disaggregation role of this replica (default: the package's "
                         "replicas.<id>.role for --replica-id, else mixed)")
     s.add_argument("--replica-id", default=None, help="key of this replica in [replicas]")
+    k = sub.add_parser("keep", help="hold a package's weights for serving processes to map")
+    k.add_argument("package")
+    k.add_argument("--socket", required=True, help="unix socket the keeper answers on")
+    k.add_argument("--ready-fd", type=int, default=None)
     b = sub.add_parser("build", help="compile the native libraries for sm_100a")
     b.add_argument("--force", action="store_true")
     l = sub.add_parser("layout", help="print the resolved device layout of a package")
@@ -451,6 +501,8 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     if a.cmd == "serve":
         return serve(a)
+    if a.cmd == "keep":
+        return keep(a)
     if a.cmd == "admin":
         return admin(a)
     if a.cmd == "route":
