@@ -444,3 +444,23 @@ def test_chat_with_a_video_on_the_hybrid_family(tmp_path):
     with TestClient(bare) as c:
         r = c.post("/v1/chat/completions", json=body)
         assert r.status_code == 400 and "media_config.directory" in r.text
+
+
+def test_mp4_built_in_memory_is_the_file_form_byte_for_byte(tmp_path):
+    """`write_mp4` without a path builds the file in memory (pictures encoded in parallel,
+    copied into a bytes object of the exact size); with a path it writes the file: the same
+    bytes, edge macroblocks and the audio track included."""
+    from uniserve_v1_b200.ops import media as M
+    g = torch.Generator().manual_seed(0)
+    F_, H, W = 5, 48, 70                      # not multiples of 16
+    y = torch.randint(0, 256, (F_, H, W), dtype=torch.uint8, generator=g)
+    u = torch.randint(0, 256, (F_, H // 2, W // 2), dtype=torch.uint8, generator=g)
+    v = torch.randint(0, 256, (F_, H // 2, W // 2), dtype=torch.uint8, generator=g)
+    y[1, :3] = 0                              # runs of zero bytes: emulation prevention bytes
+    pcm = torch.randint(-1000, 1000, (3200, 2), dtype=torch.int16, generator=g)
+    mem = M.write_mp4(y, u, v, 24, pcm, 32000)
+    path = tmp_path / "clip.mp4"
+    assert M.write_mp4(y, u, v, 24, pcm, 32000, path=str(path)) == b""
+    assert isinstance(mem, bytes) and mem == path.read_bytes()
+    assert mem[4:8] == b"ftyp" and b"moov" in mem[-4096:] and b"avcC" in mem
+    assert M.write_mp4(y, u, v, 24) == M.write_mp4(y, u, v, 24, None)     # video only

@@ -143,20 +143,30 @@ std::vector<uint8_t> make_idr(const uint8_t* y, const uint8_t* u, const uint8_t*
     for (int mx = 0; mx < mbw; ++mx) {
       b.ue(25);        // mb_type I_PCM
       b.align_zero();  // pcm_alignment_zero_bit
-      for (int r = 0; r < 16; ++r) {
-        const int yy = my * 16 + r < height ? my * 16 + r : height - 1;
-        for (int c = 0; c < 16; ++c) {
-          const int xx = mx * 16 + c < width ? mx * 16 + c : width - 1;
-          mb[r * 16 + c] = y[(size_t)yy * width + xx];
-        }
-      }
       const int cw = width / 2, ch = height / 2;
-      for (int r = 0; r < 8; ++r) {
-        const int yy = my * 8 + r < ch ? my * 8 + r : ch - 1;
-        for (int c = 0; c < 8; ++c) {
-          const int xx = mx * 8 + c < cw ? mx * 8 + c : cw - 1;
-          mb[256 + r * 8 + c] = u[(size_t)yy * cw + xx];
-          mb[320 + r * 8 + c] = v[(size_t)yy * cw + xx];
+      if (mx * 16 + 16 <= width && my * 16 + 16 <= height) {
+        // a macroblock inside the picture: whole rows at a time
+        for (int r = 0; r < 16; ++r)
+          memcpy(mb + r * 16, y + (size_t)(my * 16 + r) * width + mx * 16, 16);
+        for (int r = 0; r < 8; ++r) {
+          memcpy(mb + 256 + r * 8, u + (size_t)(my * 8 + r) * cw + mx * 8, 8);
+          memcpy(mb + 320 + r * 8, v + (size_t)(my * 8 + r) * cw + mx * 8, 8);
+        }
+      } else {                                   // the picture's edge is repeated
+        for (int r = 0; r < 16; ++r) {
+          const int yy = my * 16 + r < height ? my * 16 + r : height - 1;
+          for (int c = 0; c < 16; ++c) {
+            const int xx = mx * 16 + c < width ? mx * 16 + c : width - 1;
+            mb[r * 16 + c] = y[(size_t)yy * width + xx];
+          }
+        }
+        for (int r = 0; r < 8; ++r) {
+          const int yy = my * 8 + r < ch ? my * 8 + r : ch - 1;
+          for (int c = 0; c < 8; ++c) {
+            const int xx = mx * 8 + c < cw ? mx * 8 + c : cw - 1;
+            mb[256 + r * 8 + c] = u[(size_t)yy * cw + xx];
+            mb[320 + r * 8 + c] = v[(size_t)yy * cw + xx];
+          }
         }
       }
       b.bytes(mb, 384);
@@ -397,6 +407,129 @@ US_API long long us_mp4_write(const char* path, int width, int height, int fps, 
   fwrite(sz, 1, 8, f);
   fclose(f);
   return (long long)pos;
+}
+
+// The same MP4 built in memory, in two calls so that the caller can allocate the exact size:
+// us_mp4_build encodes every picture (one thread slot each) and lays the file out, returning a
+// handle and the size; us_mp4_take copies the file into the caller's buffer (pictures in
+// parallel) and frees the handle.  No file round trip, no oversized scratch buffer.
+struct Mp4Built {
+  std::vector<uint8_t> head;                    // ftyp + mdat header
+  std::vector<std::vector<uint8_t>> pics;
+  std::vector<uint64_t> at_pos;
+  const int16_t* pcm = nullptr;
+  uint64_t audio_at = 0, audio_bytes = 0, moov_at = 0, total = 0;
+  std::vector<uint8_t> moov;
+  int workers = 1;
+};
+
+US_API void* us_mp4_build(int width, int height, int fps, int n_frames, const uint8_t* y,
+                          const uint8_t* u, const uint8_t* v, const int16_t* pcm,
+                          long long audio_frames, int channels, int sample_rate,
+                          long long* size_out) {
+  if (width < 16 || height < 16 || (width & 1) || (height & 1) || fps < 1 || n_frames < 1 ||
+      !y || !u || !v || !size_out)
+    return nullptr;
+  Mp4Built* b = new Mp4Built();
+  Box ft;
+  ft.str("isom", 4); ft.u32(0x200); ft.str("isomiso2avc1mp41", 16);
+  Box ftyp = box("ftyp", ft);
+  const size_t ys = (size_t)width * height, cs = ys / 4;
+  b->workers = std::max(1, std::min({(int)std::thread::hardware_concurrency(), 32, n_frames}));
+  b->pics.resize(n_frames);
+  {
+    std::vector<std::thread> pool;
+    for (int t = 0; t < b->workers; ++t)
+      pool.emplace_back([&, t] {
+        for (int fi = t; fi < n_frames; fi += b->workers)
+          b->pics[fi] = make_idr(y + fi * ys, u + fi * cs, v + fi * cs, width, height, fi);
+      });
+    for (auto& th : pool) th.join();
+  }
+  Track vt;
+  vt.video = true; vt.id = 1; vt.timescale = (uint32_t)fps * 512; vt.sample_delta = 512;
+  vt.width = width; vt.height = height;
+  vt.sps = nal(3, 7, make_sps(width, height));
+  vt.pps = nal(3, 8, make_pps());
+  uint64_t pos = ftyp.d.size();
+  const uint64_t mdat_at = pos;
+  pos += 16;
+  b->at_pos.resize(n_frames);
+  for (int i = 0; i < n_frames; ++i) {
+    b->at_pos[i] = pos;
+    vt.chunk_offsets.push_back(pos);
+    vt.sample_sizes.push_back((uint32_t)b->pics[i].size() + 4);
+    pos += b->pics[i].size() + 4;
+  }
+  vt.sample_count = (uint32_t)n_frames;
+  vt.duration = (uint64_t)n_frames * 512;
+  Track at;
+  const bool audio = pcm != nullptr && audio_frames > 0 && channels >= 1;
+  b->audio_at = pos;
+  if (audio) {
+    at.video = false; at.id = 2; at.timescale = (uint32_t)sample_rate; at.sample_delta = 1;
+    at.channels = channels; at.sample_rate = sample_rate;
+    at.uniform_size = (uint32_t)(2 * channels);
+    at.sample_count = (uint32_t)audio_frames;
+    at.samples_per_chunk = (uint32_t)audio_frames;
+    at.chunk_offsets.push_back(pos);
+    at.duration = (uint64_t)audio_frames;
+    b->pcm = pcm;
+    b->audio_bytes = 2ull * channels * audio_frames;
+    pos += b->audio_bytes;
+  }
+  const uint64_t mdat_size = pos - mdat_at;
+  const uint32_t movie_ts = 1000;
+  Box mvhd = full(0, 0);
+  mvhd.u32(0); mvhd.u32(0); mvhd.u32(movie_ts);
+  mvhd.u32((uint32_t)((uint64_t)n_frames * movie_ts / fps));
+  mvhd.u32(0x10000); mvhd.u16(0x0100); mvhd.zeros(10);
+  matrix(mvhd);
+  mvhd.zeros(24);
+  mvhd.u32(audio ? 3 : 2);
+  Box moov;
+  moov.add(box("mvhd", mvhd));
+  moov.add(trak(vt, movie_ts));
+  if (audio) moov.add(trak(at, movie_ts));
+  Box mv = box("moov", moov);
+  b->moov = mv.d;
+  b->moov_at = pos;
+  b->total = pos + mv.d.size();
+  b->head = ftyp.d;
+  uint8_t hdr[16] = {0, 0, 0, 1, 'm', 'd', 'a', 't'};
+  for (int i = 0; i < 8; ++i) hdr[8 + i] = (uint8_t)(mdat_size >> (56 - 8 * i));
+  b->head.insert(b->head.end(), hdr, hdr + 16);
+  *size_out = (long long)b->total;
+  return b;
+}
+
+// Copies the built file into `out` (at least the size us_mp4_build reported; the audio samples
+// passed to us_mp4_build must still be alive) and frees the handle.  `out` may be null to
+// discard the handle.
+US_API long long us_mp4_take(void* handle, uint8_t* out) {
+  if (!handle) return -1;
+  Mp4Built* b = (Mp4Built*)handle;
+  const long long total = (long long)b->total;
+  if (out) {
+    memcpy(out, b->head.data(), b->head.size());
+    const int n_frames = (int)b->pics.size();
+    std::vector<std::thread> pool;
+    for (int t = 0; t < b->workers; ++t)
+      pool.emplace_back([&, t] {
+        for (int fi = t; fi < n_frames; fi += b->workers) {
+          const uint32_t len = (uint32_t)b->pics[fi].size();
+          uint8_t* d = out + b->at_pos[fi];
+          d[0] = (uint8_t)(len >> 24); d[1] = (uint8_t)(len >> 16);
+          d[2] = (uint8_t)(len >> 8); d[3] = (uint8_t)len;
+          memcpy(d + 4, b->pics[fi].data(), len);
+        }
+      });
+    for (auto& th : pool) th.join();
+    if (b->audio_bytes) memcpy(out + b->audio_at, b->pcm, b->audio_bytes);
+    memcpy(out + b->moov_at, b->moov.data(), b->moov.size());
+  }
+  delete b;
+  return total;
 }
 
 US_API long long us_wav_write(const char* path, const int16_t* pcm, long long frames, int channels,

@@ -206,6 +206,11 @@ def _host():
         vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
         lib.us_mp4_write.restype = ll
         lib.us_mp4_write.argtypes = [ctypes.c_char_p, ci, ci, ci, ci, vp, vp, vp, vp, ll, ci, ci]
+        lib.us_mp4_build.restype = vp
+        lib.us_mp4_build.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp, ll, ci, ci,
+                                     ctypes.POINTER(ll)]
+        lib.us_mp4_take.restype = ll
+        lib.us_mp4_take.argtypes = [vp, vp]
         lib.us_h264_encode_annexb.restype = ll
         lib.us_h264_encode_annexb.argtypes = [ctypes.c_char_p, ci, ci, ci, vp, vp, vp]
         lib.us_wav_write.restype = ll
@@ -226,16 +231,27 @@ def write_mp4(y, u, v, fps: int, pcm=None, sample_rate: int = 32000, path=None) 
     if pcm is not None and pcm.numel():
         pn = np.ascontiguousarray(pcm.cpu().numpy())
         frames, ch = pn.shape
-    tmp = path or tempfile.mktemp(suffix=".mp4")
-    n = lib.us_mp4_write(str(tmp).encode(), W, H, fps, Fn, yn.ctypes.data, un.ctypes.data,
+    if path is None:
+        # built in memory: the pictures are encoded in parallel, then copied straight into a
+        # bytes object of the exact size (created uninitialised through the C API, filled
+        # before anything else can see it) - no file round trip, no zeroed scratch, no copy
+        size = ctypes.c_longlong(0)
+        handle = lib.us_mp4_build(W, H, fps, Fn, yn.ctypes.data, un.ctypes.data, vn.ctypes.data,
+                                  pn.ctypes.data if pn is not None else None, frames, ch,
+                                  sample_rate, ctypes.byref(size))
+        if not handle:
+            raise RuntimeError("MP4 writer failed")
+        api = ctypes.pythonapi
+        api.PyBytes_FromStringAndSize.restype = ctypes.py_object
+        api.PyBytes_FromStringAndSize.argtypes = [ctypes.c_char_p, ctypes.c_ssize_t]
+        api.PyBytes_AsString.restype = ctypes.c_void_p
+        api.PyBytes_AsString.argtypes = [ctypes.py_object]
+        out = api.PyBytes_FromStringAndSize(None, size.value)
+        lib.us_mp4_take(handle, api.PyBytes_AsString(out))
+        return out
+    n = lib.us_mp4_write(str(path).encode(), W, H, fps, Fn, yn.ctypes.data, un.ctypes.data,
                          vn.ctypes.data, pn.ctypes.data if pn is not None else None, frames, ch,
                          sample_rate)
     if n < 0:
         raise RuntimeError("MP4 writer failed")
-    if path:
-        return b""
-    try:
-        with open(tmp, "rb") as f:
-            return f.read()
-    finally:
-        os.unlink(tmp)
+    return b""
