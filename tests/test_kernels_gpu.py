@@ -227,6 +227,34 @@ def test_moe_experts(T, E, k, H, I):
     close(out2, ref2, 3e-2, 3e-2)
 
 
+@pytest.mark.parametrize("T,E,k,H,I", [(2048, 8, 2, 512, 256), (1500, 4, 2, 1024, 384)])
+def test_moe_experts_prefill_size_on_cta_pairs(T, E, k, H, I, monkeypatch):
+    """A few hundred rows per expert: 256-row tiles of the sort kernel's list on the swapped
+    CTA-pair kernel (gated FC1 and FC2), with uneven loads - one expert almost empty, ragged
+    last tiles - against the FP32 restatement and against the single-CTA kernel."""
+    x = rnd(T, H)
+    w13, w2 = rnd(E, 2 * I, H, scale=0.03), rnd(E, H, I, scale=0.03, seed=4)
+    logits = rnd(T, E, dtype=torch.float32, seed=6)
+    logits[:, 1] -= 6.0                                  # expert 1 gets very few rows
+    logits[:, 0] += 1.0
+    ids, w = F.topk_softmax(logits, k, True)
+    ws = F.MoeWorkspace.create(T, k, E, H, I, DEV)
+    assert ws.block_n == 256
+    out = F.moe_experts(x, ids, w, w13, w2, ws=ws)
+    ref = R.moe_experts(x, ids, w, w13, w2)
+    close(out, ref, 3e-2, 3e-2)
+    monkeypatch.setattr(F, "MOE_PAIR_MIN_ROWS", 1 << 30)
+    ws1 = F.MoeWorkspace.create(T, k, E, H, I, DEV)
+    assert ws1.block_n == 128
+    out1 = F.moe_experts(x, ids, w, w13, w2, ws=ws1)
+    close(out, out1, 2e-2, 2e-2)
+    # expert-parallel window
+    ws2 = F.MoeWorkspace.create(T, k, E // 2, H, I, DEV, block_n=256)
+    out2 = F.moe_experts(x, ids, w, w13[E // 2:].contiguous(), w2[E // 2:].contiguous(),
+                         e_lo=E // 2, ws=ws2)
+    close(out2, R.moe_experts(x, ids, w, w13[E // 2:], w2[E // 2:], e_lo=E // 2), 3e-2, 3e-2)
+
+
 def test_argmax_and_logprob_stats():
     logits = rnd(9, 151936, dtype=torch.float32)
     am = F.argmax(logits)

@@ -505,7 +505,16 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   static_assert(!SWAP || (BN == 256 && !DUAL), "the swapped form is one 256-column accumulator");
   // m: tiles of the 256-row (A) side, n: tiles of the other side
   const int m_tiles = SWAP ? (args.rows + kBlockM - 1) / kBlockM : (args.M + kBlockM - 1) / kBlockM;
-  const int m_pairs = (m_tiles + 1) / 2;
+  // Grouped (swapped forms only): the row tiles come from the sort kernel's list - tile i is
+  // up to 256 rows of ONE group starting at tile_row0[i] (the even CTA takes the first 128,
+  // the odd CTA the rest), and the group's weights are rows [group * group_rows, ...) of the
+  // stacked weight map.  The list's length is on the device (the launch before wrote it).
+  const bool grouped = SWAP != 0 && args.num_tiles != nullptr;
+  const int m_pairs = grouped ? *args.num_tiles : (m_tiles + 1) / 2;
+  auto a_row_of = [&](int mp) -> int {
+    return grouped ? args.tile_row0[mp] + (int)rank * kBlockM : (2 * mp + (int)rank) * kBlockM;
+  };
+  auto b_off_of = [&](int mp) -> int { return grouped ? args.tile_group[mp] * args.group_rows : 0; };
   constexpr int kFeat = SWAP == 2 ? 2 * kBlockM : kBlockM;   // features per swapped tile
   const int n_tiles = SWAP ? (args.M + kFeat - 1) / kFeat : (args.rows + BN - 1) / BN;
   const int total = m_pairs * n_tiles;
@@ -567,6 +576,8 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         const int row0 = SWAP == 1   ? nt * kBlockM + (rank ? args.dual_offset : 0)
                          : SWAP == 2 ? nt * kFeat + (int)rank * kBlockM
                                      : nt * BN + (int)rank * (BN / 2);
+        const int a_row = SWAP ? a_row_of(mp) : 0;
+        const int b_off = SWAP ? b_off_of(mp) : 0;
         for (int kb = 0; kb < num_k; ++kb) {
           if (!tc::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
             us_dev_fail(args.status, US_DEV_TIMEOUT_EMPTY);
@@ -577,11 +588,12 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           uint8_t* st = smem + (size_t)s * kStageBytes;
           tc::mbar_expect_tx(&full_bar[s], kStageBytes);
           // weight rows past the last tile and chunks past K read as zeros
-          tc::tma_load_3d(st, &tmA, &full_bar[s], 0, m_tile * kBlockM, kb * kKC);
+          tc::tma_load_3d(st, &tmA, &full_bar[s], 0, SWAP ? a_row : m_tile * kBlockM, kb * kKC);
           if (DUAL)
             tc::tma_load_3d(st + kKC * kATile, &tmA, &full_bar[s], 0,
                             args.dual_offset + m_tile * kBlockM, kb * kKC);
-          tc::tma_load_3d(st + kKC * kATiles, &tmBs.m[0], &full_bar[s], 0, row0, kb * kKC);
+          tc::tma_load_3d(st + kKC * kATiles, &tmBs.m[0], &full_bar[s], 0, row0 + b_off,
+                          kb * kKC);
           if (++s == stages) {
             s = 0;
             ph ^= 1u;
@@ -704,7 +716,9 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       const uint32_t taddr = tmem_base + (uint32_t)buf * kAccCols + ((uint32_t)(q * 32) << 16);
       if (SWAP) {
         // this thread's activation row; its features leave as 32-byte pieces
-        const int xrow = m_tile * kBlockM + ml;
+        const int xrow = a_row_of(mp) + ml;
+        const bool row_ok = grouped ? ((int)rank * kBlockM + ml) < args.tile_rows[mp]
+                                    : xrow < args.rows;
         const int f0 = nt * kFeat;
         const int act = args.act;
         const int esz = args.out_dtype == 0 ? 2 : 4;
@@ -715,7 +729,7 @@ gemm_wx_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         const int peer_cols = args.peer_cols;
         float pre = 1.f, post = 1.f;          // scale before the activation / of the result
         char* dst = nullptr;                  // element (xrow, feature 0); null: row dropped
-        if (xrow < args.rows) {
+        if (row_ok) {
           if (args.row_scale != nullptr) (args.scale_first ? pre : post) = args.row_scale[xrow];
           if (args.route_map != nullptr) {
             const int i = args.route_map[xrow];
@@ -1103,9 +1117,14 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
                     (dual ? block_n == 128 : block_n == 256) &&
                     (long long)((M + kBlockM - 1) / kBlockM) * ((x_rows + block_n - 1) / block_n) >
                         148;
+  // Grouped problems with 256-row tiles (prefill-size expert batches) run the swapped CTA-pair
+  // kernel over the sort kernel's tile list.
+  const bool gpair = pair_enabled() && pair_mode() == 1 && num_tiles != nullptr && block_n == 256 &&
+                     !ps.x_peers && !ps.out_peers && (K % kBlockK) == 0 && bias == nullptr &&
+                     ldw == K;
   const uint32_t box_n = (uint32_t)(pair ? block_n / 2 : block_n);
   // operands swapped: one activation row per epilogue thread
-  const bool swap = pair && pair_mode() == 1;
+  const bool swap = (pair && pair_mode() == 1) || gpair;
 
   CUtensorMap tmA;
   BMaps tmB;
@@ -1113,7 +1132,8 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
   if (swap) {
     rc = pair_tmap(&tmA, X, US_TMAP_BF16, x_rows, K, ldx, kBlockM);
     if (rc) return rc;
-    rc = pair_tmap(&tmB.m[0], W, US_TMAP_BF16, w_rows, K, ldw, kBlockM);
+    // grouped: the groups' weight rows are one stacked [G * w_rows, K] matrix
+    rc = pair_tmap(&tmB.m[0], W, US_TMAP_BF16, gpair ? G * w_rows : w_rows, K, ldw, kBlockM);
     if (rc) return rc;
     for (int p = 1; p < 8; ++p) tmB.m[p] = tmB.m[0];
   } else if (pair) {
@@ -1128,7 +1148,7 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
                     US_SWZ_128);
     if (rc) return rc;
   }
-  if (pair) {
+  if (pair || gpair) {
     // maps built above
   } else if (ps.x_peers && ps.rows_per_peer > 0) {
     US_REQUIRE(ps.n_peers >= 1 && ps.n_peers <= 8 && (ps.rows_per_peer % block_n) == 0 &&
@@ -1176,6 +1196,7 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
   a.tile_row0 = tile_row0;
   a.tile_rows = tile_rows;
   a.num_tiles = num_tiles;
+  a.group_rows = w_rows;
   a.status = us_status_ptr();
   a.splits = 1;
   a.kb_per_split = 0;
@@ -1243,7 +1264,8 @@ int gemm_impl(const void* W, const void* X, void* out, int G, int w_rows, int M,
     return e && e[0] == '1';
   }();
   if (swap) {
-    const int x_pairs = ((x_rows + kBlockM - 1) / kBlockM + 1) / 2;
+    if (gpair) g_cta_hint = 0;      // the hint sizes the single-CTA kernel's pipeline only
+    const int x_pairs = gpair ? max_tiles : ((x_rows + kBlockM - 1) / kBlockM + 1) / 2;
     if (dual)
       return launch_pair<256, false, false, 1>(tmA, tmB, a, x_pairs * ((M + 127) / 128), stream);
     return launch_pair<256, false, false, 2>(tmA, tmB, a, x_pairs * ((M + 255) / 256), stream);

@@ -62,6 +62,9 @@ struct GemmArgs {
   const int* route_map;
   const float* route_w;
   int route_per;
+  // Grouped launches of the CTA-pair kernel: weight rows per group (the weight map stacks the
+  // groups' rows; a tile's group comes from tile_group).
+  int group_rows;
   // 1: the swapped epilogue writes rows bound for another GPU as whole 128-byte lines
   // (collected per warp in the staging area) instead of 32-byte pieces per thread.
   int remote_lines;

@@ -345,6 +345,11 @@ def topk_softmax(logits, top_k, renorm=True, live=None, expert_map=None, load=No
     return ids, weights
 
 
+# rows per local expert from which the grouped expert GEMMs take 256-row tiles on the CTA-pair
+# kernel (US_MOE_PAIR_ROWS; a huge value keeps the single-CTA kernel)
+MOE_PAIR_MIN_ROWS = int(_os.environ.get("US_MOE_PAIR_ROWS", "192"))
+
+
 @dataclass
 class MoeWorkspace:
     """Static buffers of one MoE layer invocation (shared by all layers)."""
@@ -371,6 +376,9 @@ class MoeWorkspace:
         if block_n is None:
             avg = max(1, R_ // max(1, E_local))
             block_n = 16 if avg <= 16 else 32 if avg <= 32 else 64 if avg <= 64 else 128
+            # prefill-size batches (a few hundred rows per expert): 256-row tiles on CTA pairs
+            if R_ // max(1, E_total or E_local) >= MOE_PAIR_MIN_ROWS:
+                block_n = 256
         max_tiles = min(R_, E_local) + R_ // block_n + 1
         i32 = dict(dtype=torch.int32, device=device)
         return MoeWorkspace(
