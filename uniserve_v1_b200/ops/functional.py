@@ -347,7 +347,7 @@ def topk_softmax(logits, top_k, renorm=True, live=None, expert_map=None, load=No
 
 # rows per local expert from which the grouped expert GEMMs take 256-row tiles on the CTA-pair
 # kernel (US_MOE_PAIR_ROWS; a huge value keeps the single-CTA kernel)
-MOE_PAIR_MIN_ROWS = int(_os.environ.get("US_MOE_PAIR_ROWS", "192"))
+MOE_PAIR_MIN_ROWS = int(_os.environ.get("US_MOE_PAIR_ROWS", "64"))
 
 
 @dataclass
