@@ -94,6 +94,11 @@ class ExpertExchange:
         if ws is None:
             ws = F.MoeWorkspace.create(self.world * t_step, self.k, self.experts_per_rank, self.H,
                                        self.I, self.device)
+            if ws.block_n > 128:
+                # FC2 pushes its rows to the token owners from the single-CTA grouped kernel's
+                # epilogue: 128-row tiles (the 256-row tiles belong to the CTA-pair kernel)
+                ws = F.MoeWorkspace.create(self.world * t_step, self.k, self.experts_per_rank,
+                                           self.H, self.I, self.device, block_n=128)
             self._ws[t_step] = ws
         return ws
 
