@@ -374,6 +374,7 @@ def qwen3_record(job: Job) -> dict:
     ctx = ParallelContext.single()
     sync_group, n_attn, is_attention = None, world, True
     exchange, control, announcer = None, None, None
+    micro = []
     if world > 1:
         sync_group = dist.group.WORLD
         if layout == "tp-ep":
@@ -400,6 +401,11 @@ def qwen3_record(job: Job) -> dict:
                                       cfg.num_experts_per_tok, cfg.hidden_size, cfg.num_experts,
                                       cfg.moe_intermediate_size, ctx.source_ranks,
                                       ctx.expert_ranks)
+            if args.microbatches >= 2:
+                micro = [ExpertExchange(dist.group.WORLD, rank, world, dev, 256,
+                                        cfg.num_experts_per_tok, cfg.hidden_size, cfg.num_experts,
+                                        cfg.moe_intermediate_size, ctx.source_ranks,
+                                        ctx.expert_ranks) for _ in (0, 1)]
         mark("heap attached")
 
     if args.concurrency:
@@ -423,6 +429,9 @@ def qwen3_record(job: Job) -> dict:
     model = Qwen3MoeModel(cfg, dev, torch.bfloat16, ctx,
                           expert_quant=args.expert_quant).init_random(seed=0)
     model.exchange = exchange
+    if micro:
+        model.micro_exchanges = micro
+        model.microbatch_now = True        # every decode step of this run is micro-batched
     if world > 1 and layout == "tp-ep" and os.environ.get("US_NO_FUSED", "0") != "1":
         from uniserve_v1_b200.parallel.tp_fused import attach_fused_tp
         attach_fused_tp(model, 8192)          # prefill chunks: fused reduce-scatter / all-gather
@@ -592,7 +601,7 @@ def qwen3_record(job: Job) -> dict:
                    "global_batch": total_c, "seq_len": prompt_len,
                    "context_during_timing": [ctx_lo, ctx_lo + K + W],
                    "page_size": 16, "step": "one decode step of all concurrent requests",
-                   "parallelism": par, "layout": layout,
+                   "parallelism": par, "layout": layout, "microbatches": args.microbatches,
                    "l2": "inputs larger than L2 (weights read per step >> 126 MB)",
                    "baseline": "64 concurrent, 20.5 ms/step on 1xGB200 (reference docs)"},
         "clocks": clocks, "e2e": e2e, "workload": workload, "gpu_launches": launches,
@@ -644,6 +653,8 @@ def main() -> int:
     ap.add_argument("--expert-quant", default=None, choices=["fp8_block"],
                     help="block-scaled FP8 expert weights (128 x 128 blocks); the value is then "
                          "reported with dtype fp8 experts + bf16 attention")
+    ap.add_argument("--microbatches", type=int, default=1,
+                    help="dp-ep / afd layouts: 2 = decode steps as two interleaved half-batches")
     ap.add_argument("--layout", default="tp-ep", choices=["tp-ep", "dp-ep", "afd"],
                     help="qwen3-moe: tp-ep: attention heads split over all ranks, whole experts "
                          "per rank, all-reduce fused into the norms (strong scaling, the default); "

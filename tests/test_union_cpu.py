@@ -26,7 +26,7 @@ def _prompts():
     return [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (9, 41, 20, 5, 33)]
 
 
-def _worker(rank, world, port, q, afd):
+def _worker(rank, world, port, q, afd, micro=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -50,8 +50,12 @@ def _worker(rank, world, port, q, afd):
     if rank in sources:
         eng = LLMEngine(model, num_pages=96, max_num_seqs=4, max_model_len=128, use_graphs=False,
                         max_num_batched_tokens=32)
+    if micro:       # decode steps as two interleaved half-batches, an exchange each
+        model.micro_exchanges = [
+            HostExpertExchange(dist.group.WORLD, rank, world, 32, cfg.num_experts_per_tok,
+                               cfg.hidden_size, cfg.num_experts, sources, experts) for _ in (0, 1)]
     member = UnionMember(dist.group.WORLD, rank, world, sources, experts, engine=eng, model=model,
-                         capacity_limit=64)
+                         capacity_limit=64, microbatches=2 if micro else 1)
     if rank != 0:
         ticks = member_loop(member, 0)
         q.put((rank, member.stats, ticks))
@@ -86,8 +90,8 @@ def _worker(rank, world, port, q, afd):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("afd", [False, True])
-def test_union_serving_matches_one_engine(afd):
+@pytest.mark.parametrize("afd,micro", [(False, False), (True, False), (False, True), (True, True)])
+def test_union_serving_matches_one_engine(afd, micro):
     from uniserve_v1_b200.engine.engine import LLMEngine
     from uniserve_v1_b200.engine.types import SamplingParams
     from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
@@ -99,7 +103,7 @@ def test_union_serving_matches_one_engine(afd):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, afd)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, afd, micro)) for r in range(world)]
     for p in procs:
         p.start()
     res = {}
@@ -121,3 +125,5 @@ def test_union_serving_matches_one_engine(afd):
         busy = res[1][0]
         assert busy["steps"] > 0
     assert len(lead["stats"]["capacities"]) >= 2          # prefill and decode classes met
+    # steps in which every member decodes (or idles) ran as two half-batches
+    assert (lead["stats"].get("micro_steps", 0) > 0) == micro

@@ -219,6 +219,24 @@ def serve(args) -> int:
             model.exchange = HostExpertExchange(control, rank, world, limit,
                                                 cfg.num_experts_per_tok, cfg.hidden_size,
                                                 cfg.num_experts, sources, experts)
+        mb = int(pkg.moe_config.microbatches or 1)
+        if mb >= 2 and not dwdp:
+            # two more exchanges of half the window each: decode steps run as two interleaved
+            # half-batches (attention of one under the experts of the other)
+            half = max(1, limit // 2)
+            if device.type == "cuda":
+                import torch.distributed as dist
+                from .parallel.expert_exchange import ExpertExchange
+                model.micro_exchanges = [
+                    ExpertExchange(dist.group.WORLD, rank, world, device, half,
+                                   cfg.num_experts_per_tok, cfg.hidden_size, cfg.num_experts,
+                                   cfg.moe_intermediate_size, sources, experts) for _ in (0, 1)]
+            else:
+                from .parallel.expert_exchange import HostExpertExchange
+                model.micro_exchanges = [
+                    HostExpertExchange(control, rank, world, half, cfg.num_experts_per_tok,
+                                       cfg.hidden_size, cfg.num_experts, sources, experts)
+                    for _ in (0, 1)]
         eng = None
         if rank in sources:
             eng = LLMEngine(model,
@@ -234,7 +252,7 @@ def serve(args) -> int:
                                else ({"use_graphs": False} if dwdp else {})))
         member = UnionMember(control, rank, world, sources, experts, engine=eng, model=model,
                              capacity_limit=limit,
-                             exchange_free=dwdp and device.type == "cuda")
+                             exchange_free=dwdp and device.type == "cuda", microbatches=mb)
         if rank > 0:
             member_loop(member, 0)
             return 0

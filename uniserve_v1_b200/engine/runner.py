@@ -220,6 +220,13 @@ class CausalLmRunner:
             N.kernels().us_status_clear_async(N.stream())
             raise DeviceStepError(code)
 
+    def _decode_kind(self, kind: str, B: int) -> str:
+        """Announcement kind of a decode-step forward: expert ranks must know when the step runs
+        as two half-batches (they then serve two windows per layer)."""
+        micro = bool(getattr(self.model, "microbatch_now", False)) and \
+            bool(getattr(self.model, "micro_exchanges", None)) and B >= 2 and B % 2 == 0
+        return kind + "+micro" if micro else kind
+
     def _queue_status_copy(self) -> None:
         if self._status_host is not None:
             N.kernels().us_status_copy_async(N.ptr(self._status_host), N.stream())
@@ -227,7 +234,8 @@ class CausalLmRunner:
     def _graph(self, B: int, variant: str) -> Optional[DecodeGraph]:
         if not self.use_graphs:
             return None
-        key = (B, variant)
+        # a union's micro-batched steps issue other kernels than its plain steps of the same size
+        key = (B, variant, bool(getattr(self.model, "microbatch_now", False)))
         g = self._graphs.get(key)
         if g is not None:
             return g
@@ -240,7 +248,7 @@ class CausalLmRunner:
         blk.dev.zero_()
         blk.d["slots"].fill_(-1)
         torch.cuda.synchronize()
-        self.announce("eager", B)
+        self.announce(self._decode_kind("eager", B), B)
         with torch.cuda.stream(s):
             self._decode_body(blk, B, variant)
         torch.cuda.current_stream().wait_stream(s)
@@ -250,7 +258,7 @@ class CausalLmRunner:
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
         before = N.launch_count
-        self.announce("capture", B)
+        self.announce(self._decode_kind("capture", B), B)
         with torch.cuda.graph(graph, pool=self._pool):
             logits, sampled = self._decode_body(blk, B, variant)
         launches = N.launch_count - before
@@ -408,7 +416,7 @@ class CausalLmRunner:
         g = self._graph(B, variant) if B <= self.buckets[-1] or B in self._graphs else None
         self.h2d_bytes += blk.upload()
         logits = sampled = None
-        self.announce("replay" if g is not None else "eager", B, steps)
+        self.announce(self._decode_kind("replay" if g is not None else "eager", B), B, steps)
         for _ in range(steps):
             if g is not None:
                 g.graph.replay()
@@ -452,7 +460,7 @@ class CausalLmRunner:
     def decode_launch(self, st: "DecodeStream") -> None:
         k = st.launched
         assert k < self.history_steps
-        self.announce("replay" if st.graph is not None else "eager", st.B, 1)
+        self.announce(self._decode_kind("replay" if st.graph is not None else "eager", st.B), st.B, 1)
         if st.graph is not None:
             st.graph.graph.replay()
             N.launch_count += st.graph.launches

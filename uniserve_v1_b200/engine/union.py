@@ -59,7 +59,7 @@ class UnionMember:
 
     def __init__(self, control_group, rank: int, world: int, source_ranks, expert_ranks,
                  engine=None, model=None, capacity_limit: int = 8192,
-                 exchange_free: bool = False):
+                 exchange_free: bool = False, microbatches: int = 1):
         self.group, self.rank, self.world = control_group, rank, world
         self.sources, self.experts = tuple(source_ranks), tuple(expert_ranks)
         self.engine = engine
@@ -69,6 +69,10 @@ class UnionMember:
         # members that move no tokens between them (weights are read one-sidedly from the
         # peers): an idle member has nothing to join
         self.exchange_free = exchange_free
+        # `moe_config.microbatches` >= 2: a step in which every member decodes (or idles) runs
+        # as two interleaved half-batches, each through its own exchange, so that attention of
+        # one half overlaps the experts of the other
+        self.microbatches = microbatches if getattr(self.model, "micro_exchanges", None) else 1
         self.stats = {"ticks": 0, "steps": 0, "joins": 0, "idle_ticks": 0, "capacities": {}}
         if engine is not None:
             # a member's prefill chunk must fit the agreed capacity
@@ -100,8 +104,14 @@ class UnionMember:
             self.stats["idle_ticks"] += 1
             return [], gathered
         self.stats["capacities"][cap] = self.stats["capacities"].get(cap, 0) + 1
+        # every member sees the same kinds, so every member takes the same decision
+        micro = self.microbatches >= 2 and cap >= 2 and cap % 2 == 0 and \
+            all(g[0] in (None, "decode") for g in gathered)
+        self.model.microbatch_now = micro
+        if micro:
+            self.stats["micro_steps"] = self.stats.get("micro_steps", 0) + 1
         if not self.is_source:
-            self.model.forward_experts_only(cap)
+            self.model.forward_experts_only(cap, micro=micro)
             self.stats["joins"] += 1
             return [], gathered
         if batch is None:

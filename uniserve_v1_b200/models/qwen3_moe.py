@@ -180,6 +180,8 @@ class Qwen3MoeModel:
         self.expert_ranks = getattr(self.ctx, "expert_ranks", None)
         self.source_ranks = getattr(self.ctx, "source_ranks", None)
         self.exchange = None
+        self.micro_exchanges: list = []  # two exchanges: decode steps as interleaved half-batches
+        self.microbatch_now = False      # set per agreed step (every member decides alike)
         self.tp_fused = None            # parallel.tp_fused.FusedTP: prefill with fused collectives
         self.weight_peers = None        # parallel.dwdp: experts read from the peers' shards
         self.moe_layer_order: list = []
@@ -540,6 +542,9 @@ class Qwen3MoeModel:
                 and self.exchange is None and self.weight_peers is None and meta.rows_real is None \
                 and T > TP_FUSED_MIN_ROWS and ft.padded(T, ft.P) <= ft.rows_max:
             return self._forward_tp_fused(ft, input_ids, positions, meta, kv_caches)
+        if self.micro_exchanges and self.microbatch_now and meta.kind == "decode" \
+                and T >= 2 and T % 2 == 0 and self.pp == 1:
+            return self._forward_microbatched(input_ids, positions, meta, kv_caches)
         fc = self._fused(T, input_ids.is_cuda)
         if fc is not None:
             fc.begin_forward()
@@ -567,6 +572,51 @@ class Qwen3MoeModel:
             x, _ = self._reduce_norm(fc, hidden, site, residual, self.final_norm)
         # every stage samples the same tokens from the last stage's rows
         return self.ctx.broadcast(x.contiguous(), last, "layer")
+
+    def _forward_microbatched(self, input_ids, positions, meta: AttnMeta, kv_caches):
+        """A decode step of an expert union as two half-batches, each with an exchange of its
+        own, interleaved layer by layer: while the experts (this rank's share, or the expert
+        ranks of the disaggregated layout) work on half A of layer l, this rank runs the
+        attention of half B; A's combine is waited for only when A's next layer starts.
+        Expert ranks serve the two windows of a layer in the same order
+        (``forward_experts_only``)."""
+        import copy
+        T = input_ids.shape[0]
+        h = T // 2
+        live = meta.live
+        halves = []
+        for j, (lo, hi) in enumerate(((0, h), (h, T))):
+            m = copy.copy(meta)
+            m.slots = meta.slots[lo:hi]
+            m.page_table = meta.page_table[lo:hi] if meta.page_table is not None else None
+            m.seq_lens = meta.seq_lens[lo:hi] if meta.seq_lens is not None else None
+            m.live = None if live is None else (live - lo).clamp(0, hi - lo).to(torch.int32)
+            halves.append({"meta": m, "ids": input_ids[lo:hi], "pos": positions[lo:hi],
+                           "hidden": None, "residual": None, "site": None})
+        saved, saved_live = self.exchange, getattr(self, "_live", None)
+        try:
+            for st in halves:
+                st["hidden"] = F.embedding(st["ids"], self.embed)
+            for i in range(self.layer_lo, self.layer_hi):
+                lw = self.layers[i]
+                kc, vc = kv_caches[i]
+                for j, st in enumerate(halves):
+                    self.exchange, self._live = self.micro_exchanges[j], st["meta"].live
+                    x, st["residual"] = self._reduce_norm(None, st["hidden"], st["site"],
+                                                          st["residual"], lw.input_norm)
+                    mixed, _ = self._attention(None, lw, x, st["pos"], st["meta"], kc, vc)
+                    x, st["residual"] = self._reduce_norm(None, mixed, None, st["residual"],
+                                                          lw.post_norm)
+                    st["hidden"], st["site"] = self._mlp(None, lw, x)
+            outs = []
+            for j, st in enumerate(halves):
+                self.exchange, self._live = self.micro_exchanges[j], st["meta"].live
+                x, _ = self._reduce_norm(None, st["hidden"], st["site"], st["residual"],
+                                         self.final_norm)
+                outs.append(x)
+        finally:
+            self.exchange, self._live = saved, saved_live
+        return torch.cat(outs, 0)
 
     def _forward_tp_fused(self, ft, input_ids, positions, meta: AttnMeta, kv_caches):
         """Tensor-parallel prefill with the collectives inside the kernels: the residual stream
@@ -669,16 +719,24 @@ class Qwen3MoeModel:
             r.wait()
         return hidden, residual
 
-    def forward_experts_only(self, t_step: int) -> None:
+    def forward_experts_only(self, t_step: int, micro: bool = False) -> None:
         """An expert rank of the disaggregated layout: every forward is the join - per
-        layer it waits for the attention ranks' rows, runs its experts and pushes back."""
+        layer it waits for the attention ranks' rows, runs its experts and pushes back.
+        ``micro``: the step runs as two half-batches, each through its own exchange."""
+        windows = [(self.exchange, t_step)]
+        if micro and self.micro_exchanges and t_step >= 2 and t_step % 2 == 0:
+            windows = [(ex, t_step // 2) for ex in self.micro_exchanges]
         for lw in self.layers:
             if lw is None or lw.dense:
                 continue
-            if lw.fp8 is not None:
-                self.exchange.experts_fp8(lw.fp8, t_step)
-            else:
-                self.exchange.experts(lw.w13, lw.w2, t_step)
+            for ex, t in windows:
+                if lw.fp8 is not None:
+                    ex.experts_fp8(lw.fp8, t)
+                else:
+                    ex.experts(lw.w13, lw.w2, t)
+        for ex, _ in windows:               # host exchanges hold a layer's last collective back
+            if hasattr(ex, "flush"):
+                ex.flush()
 
     def greedy_tokens(self, hidden_rows: torch.Tensor) -> torch.Tensor:
         """arg-max token of every row, int32 [rows], the same on every rank.  With a

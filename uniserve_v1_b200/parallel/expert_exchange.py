@@ -249,13 +249,25 @@ class HostExpertExchange:
 
     def experts(self, w13, w2, t_step: int, act: str = "silu") -> None:
         from ..ops import reference as R
+        # An expert-only rank joins the all-reduce of a layer's output when the source ranks
+        # do: at THEIR next use of this exchange (their combine runs at the start of the next
+        # layer, after the other micro-batch's collectives), so it is held back until this
+        # exchange's next call, or ``flush`` at the end of the forward.
+        self.flush()
         x, ids, w = self._gather(t_step)
         out = R.moe_experts(x, ids, w, w13.float(), w2.float(), e_lo=self.e_lo, act=act).float()
         self.layers += 1
         if self.is_source:
             self._partial = out
         else:
-            dist.all_reduce(out, group=self.group)      # expert-only: nothing to keep
+            self._held = out
+
+    def flush(self) -> None:
+        """Expert-only ranks: joins the all-reduce of the output held back by ``experts``."""
+        held = getattr(self, "_held", None)
+        if held is not None:
+            self._held = None
+            dist.all_reduce(held, group=self.group)     # nothing to keep
 
     def combine_add_rmsnorm(self, ids, live, residual, w, eps: float):
         from ..ops import reference as R

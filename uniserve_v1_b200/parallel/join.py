@@ -48,9 +48,12 @@ class ExpertJoinLoop:
             kind, rows, count = box[0]
             if kind == "stop":
                 return self.joins
+            micro = kind.endswith("+micro")      # the step runs as two half-batches
+            if micro:
+                kind = kind[:-len("+micro")]
             if kind == "eager":
                 for _ in range(count):
-                    self.model.forward_experts_only(rows)
+                    self.model.forward_experts_only(rows, micro=micro)
                     self.joins += 1
             elif kind == "capture":
                 g = torch.cuda.CUDAGraph()
@@ -58,10 +61,10 @@ class ExpertJoinLoop:
                     self.pool = torch.cuda.graph_pool_handle()
                 torch.cuda.synchronize()
                 with torch.cuda.graph(g, pool=self.pool):
-                    self.model.forward_experts_only(rows)
-                self.graphs[rows] = g
+                    self.model.forward_experts_only(rows, micro=micro)
+                self.graphs[(rows, micro)] = g
             elif kind == "replay":
-                g = self.graphs[rows]
+                g = self.graphs[(rows, micro)]
                 for _ in range(count):
                     g.replay()
                     self.joins += 1
