@@ -498,7 +498,7 @@ def qwen3_record(job: Job) -> dict:
     runner._fill_decode(blk, rows, B)
     graph = runner._graph(B, "greedy")
     blk.upload()
-    runner.announce("replay", B, W)
+    runner.announce(runner._decode_kind("replay", B), B, W)
     for _ in range(W):
         graph.graph.replay()
     sampler = ClockSampler(job.local, period_ms=50)
@@ -506,7 +506,7 @@ def qwen3_record(job: Job) -> dict:
         sampler.start()
         time.sleep(0.3)
     launches0 = native.launch_count
-    runner.announce("replay", B, K)
+    runner.announce(runner._decode_kind("replay", B), B, K)
 
     def replays():
         for _ in range(K):
