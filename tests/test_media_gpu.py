@@ -108,3 +108,37 @@ def test_vae_decoders_gpu_close_to_cpu():
                  for s in ag.stages]
     z = torch.randn(2, 8, 30)
     torch.testing.assert_close(ag.decode(z.to(DEV)).cpu(), ac.decode(z), atol=1e-4, rtol=1e-3)
+
+
+def test_video_request_on_the_gpu_returns_a_decodable_clip(tmp_path):
+    """A whole `VideoService.generate` request on the GPU (tiny transformer and decoders):
+    the planes reach pinned host memory on a copy stream while the audio decoder runs, the MP4
+    is built in memory, and a second request (buffers reused) gives the same bytes."""
+    cv2 = pytest.importorskip("cv2")
+    from uniserve_v1_b200.models.h3_vae import (AudioVaeConfig, AudioVaeDecoder, VideoVaeConfig,
+                                                VideoVaeDecoder)
+    from uniserve_v1_b200.models.minimax_h3 import H3Config, H3Transformer
+    from uniserve_v1_b200.server.video_rules import VideoPlan
+    from uniserve_v1_b200.server.video_service import VideoJob, VideoService
+    cfg = H3Config.tiny()
+    cfg.vae_spatial = 64
+    tr = H3Transformer(cfg, "cuda", torch.bfloat16).init_random(0)
+    vc = VideoVaeConfig.tiny()
+    vc.latent_channels, vc.spatial = cfg.latent_channels, 64
+    vv = VideoVaeDecoder(vc, "cuda", torch.bfloat16).init_random(1)
+    av = AudioVaeDecoder(AudioVaeConfig(latent_channels=cfg.audio_channels, decoder_dim=128,
+                                        rates=(5, 5, 2, 2, 2, 2, 2), kernels=(9, 9, 4, 4, 4, 4, 4),
+                                        res_kernels=(3,), res_dilations=(1,)), "cuda").init_random(2)
+    svc = VideoService(tr, vv, av, sizes=["256x256"], max_seconds=5)
+    plan = VideoPlan("t2va", 256, 256, 39, 24, 1000, 8)
+    one = svc.generate(VideoJob("a stream in a forest", plan))
+    two = svc.generate(VideoJob("a stream in a forest", plan))
+    assert one[4:8] == b"ftyp" and one == two
+    path = tmp_path / "clip.mp4"
+    path.write_bytes(one)
+    cap = cv2.VideoCapture(str(path))
+    n = 0
+    while cap.read()[0]:
+        n += 1
+    assert n == 39
+    assert svc.d2h_bytes >= 2 * 39 * 256 * 256 * 3 // 2
