@@ -52,7 +52,7 @@ def timeit(fn, iters=10, warmup=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["delta", "flash", "gemm", "gated", "decode", "moe", "fused-norm",
+    ap.add_argument("op", choices=["prefill", "delta", "flash", "gemm", "gated", "decode", "moe", "fused-norm",
                                    "ulysses", "tp", "moe-fp8", "gemm-fp8", "gemm-fp8t", "ep",
                                    "rank-decode"])
     ap.add_argument("--tp", type=int, default=8, help="rank-decode: ranks of the emulated layout")
@@ -88,6 +88,40 @@ def main():
                                               out=o), a.iters)
         flops = 4.0 * T * T * D * H * (0.5 if a.causal else 1.0)
         out.update(rows=T, heads=H, ms=ms, tflops=flops / ms / 1e9, frac=flops / ms / 1e9 / tfl)
+    elif a.op == "prefill":
+        # One prefill chunk through the engine at the real widths: `--batch` prompts of `--ctx`
+        # tokens (one chunk of batch x ctx rows), `--layers` layers.  ms_per_layer is what a
+        # 48-layer model pays per chunk; a launch list of this command shows the shares.
+        from ..engine.engine import LLMEngine
+        from ..engine.types import SamplingParams
+        from ..models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+        cfg = Qwen3MoeConfig.qwen3_30b_a3b()
+        cfg.num_hidden_layers = a.layers
+        model = Qwen3MoeModel(cfg, dev, bf).init_random(seed=0)
+        rows = a.batch * a.ctx
+        eng = LLMEngine(model, max_num_seqs=a.batch, max_model_len=a.ctx + 64,
+                        max_num_batched_tokens=rows, enable_prefix_cache=False)
+        gp = torch.Generator().manual_seed(1)
+        sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
+        times = []
+        for it in range(a.iters + 2):
+            for _ in range(a.batch):
+                eng.add_request(torch.randint(0, cfg.vocab_size, (a.ctx,), generator=gp).tolist(), sp)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            while eng.has_work():
+                eng.step()
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= 2:
+                times.append(e0.elapsed_time(e1))
+        times.sort()
+        ms = times[len(times) // 2]
+        out.update(rows=rows, layers=a.layers, ms=ms, ms_per_layer=ms / a.layers,
+                   tokens_per_s=rows / ms * 1e3 * a.layers / 48,
+                   note="tokens_per_s is scaled to 48 layers; embedding, head and sampling "
+                        "of the last rows are in ms once")
     elif a.op == "rank-decode":
         # One rank's share of a tensor-parallel + whole-experts decode step, alone on one GPU:
         # the model is built as rank 0 of `--tp` ranks over a detached context whose
