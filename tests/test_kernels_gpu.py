@@ -136,15 +136,19 @@ def test_linear_gated(rows):
     close(F.linear_gated(x, w, stepwise=True), R.linear_gated(x, w, stepwise=True), 3e-2, 3e-2)
 
 
-def test_qk_norm_rope_kv():
-    T, Hq, Hkv, D, page = 37, 8, 2, 128, 16
+@pytest.mark.parametrize("T,D", [(37, 128), (700, 128), (37, 64)])
+def test_qk_norm_rope_kv(T, D):
+    """128-wide heads take the one-token-per-CTA kernel (heads split over CTAs for few tokens,
+    whole tokens for many); other widths the one-warp-per-row kernel."""
+    Hq, Hkv, page = 8, 2, 16
     qkv = rnd(T, (Hq + 2 * Hkv) * D)
     qw, kw = rnd(D), rnd(D, seed=9)
     pos = torch.randint(0, 5000, (T,), device=DEV, dtype=torch.int32)
     inv = R.rope_inv_freq(D, 1e6, DEV)
-    slots = torch.randperm(8 * page, device=DEV)[:T].to(torch.int32)
+    pages = (T + page - 1) // page + 5
+    slots = torch.randperm(pages * page, device=DEV)[:T].to(torch.int32)
     slots[3] = -1
-    kc = torch.zeros(8, page, Hkv, D, dtype=BF, device=DEV)
+    kc = torch.zeros(pages, page, Hkv, D, dtype=BF, device=DEV)
     vc = torch.zeros_like(kc)
     ref = qkv.clone().cpu()
     kc_r, vc_r = kc.clone().cpu(), vc.clone().cpu()
@@ -227,11 +231,13 @@ def test_moe_experts(T, E, k, H, I):
     close(out2, ref2, 3e-2, 3e-2)
 
 
-@pytest.mark.parametrize("T,E,k,H,I", [(2048, 8, 2, 512, 256), (1500, 4, 2, 1024, 384)])
+@pytest.mark.parametrize("T,E,k,H,I", [(2048, 8, 2, 512, 256), (1500, 4, 2, 1024, 384),
+                                        (5001, 8, 2, 512, 256)])
 def test_moe_experts_prefill_size_on_cta_pairs(T, E, k, H, I, monkeypatch):
     """A few hundred rows per expert: 256-row tiles of the sort kernel's list on the swapped
     CTA-pair kernel (gated FC1 and FC2), with uneven loads - one expert almost empty, ragged
-    last tiles - against the FP32 restatement and against the single-CTA kernel."""
+    last tiles - against the FP32 restatement and against the single-CTA kernel.  The largest
+    case has more than 8192 routes: the sort runs as a cluster of CTAs."""
     x = rnd(T, H)
     w13, w2 = rnd(E, 2 * I, H, scale=0.03), rnd(E, H, I, scale=0.03, seed=4)
     logits = rnd(T, E, dtype=torch.float32, seed=6)

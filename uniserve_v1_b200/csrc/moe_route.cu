@@ -22,6 +22,7 @@
 #include <float.h>
 
 #include "include/us_common.cuh"
+#include "include/us_tc05.cuh"
 
 namespace {
 
@@ -216,6 +217,120 @@ moe_sort_kernel(const int* __restrict__ ids, int R, int e_lo, int E, int block_n
               tile_group, tile_row0, tile_rows, num_tiles, status);
 }
 
+// The same sort by a cluster of kSortCtas CTAs for prefill-sized route lists: CTA c counts
+// and scatters the routes [c * chunk, (c + 1) * chunk).  After the local histograms every
+// CTA reads its peers' counts through distributed shared memory: their sum gives the expert
+// offsets (scanned redundantly in every CTA), the sum over lower ranks gives where this
+// CTA's routes of an expert start inside the expert's run.  CTA 0 writes the offsets and the
+// tile list.
+constexpr int kSortCtas = 8;
+constexpr int kSortClusterMinRoutes = 8192;   // below this one CTA is as fast
+__global__ void __launch_bounds__(1024)
+moe_sort_cluster_kernel(const int* __restrict__ ids, int R, int e_lo, int E, int block_n,
+                        int max_tiles, int* __restrict__ sorted_route,
+                        int* __restrict__ perm_of_route, int* __restrict__ expert_offsets,
+                        int* __restrict__ tile_group, int* __restrict__ tile_row0,
+                        int* __restrict__ tile_rows, int* __restrict__ num_tiles,
+                        unsigned int* status) {
+  US_PDL_PROLOGUE();
+  __shared__ int mine[kMaxExperts];      // this CTA's counts (read by the peers)
+  __shared__ int cnt[kMaxExperts];       // counts of the whole cluster
+  __shared__ int base[kMaxExperts];      // routes of lower-ranked CTAs, per expert
+  __shared__ int off[kMaxExperts + 1];
+  __shared__ int toff[kMaxExperts + 1];
+  __shared__ int cursor[kMaxExperts];
+  const int tid = threadIdx.x;
+  const int c = (int)tc::cluster_ctarank();
+  const int chunk = (R + kSortCtas - 1) / kSortCtas;
+  const int r_lo = min(R, c * chunk), r_hi = min(R, r_lo + chunk);
+  for (int e = tid; e < E; e += blockDim.x) {
+    mine[e] = 0;
+    cursor[e] = 0;
+  }
+  __syncthreads();
+  for (int i = r_lo + tid; i < r_hi; i += blockDim.x) {
+    const int e = ids[i] - e_lo;
+    if (e >= 0 && e < E) atomicAdd(&mine[e], 1);
+  }
+  tc::cluster_sync();
+  for (int e = tid; e < E; e += blockDim.x) {
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(&mine[e]);
+    int all = 0, below = 0;
+    for (int p = 0; p < kSortCtas; ++p) {
+      const int v = __float_as_int(tc::ld_dsmem_f32(tc::map_to_cta(local, (uint32_t)p)));
+      all += v;
+      if (p < c) below += v;
+    }
+    cnt[e] = all;
+    base[e] = below;
+  }
+  tc::cluster_sync();     // nobody's counts are read after this point
+  if (tid < 32) {
+    const int per = (E + 31) / 32;
+    const int lo = tid * per, hi = min(E, lo + per);
+    int s = 0, ts = 0;
+    for (int e = lo; e < hi; ++e) {
+      s += cnt[e];
+      ts += (cnt[e] + block_n - 1) / block_n;
+    }
+    int ps = s, pts = ts;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, ps, o);
+      const int b = __shfl_up_sync(0xffffffffu, pts, o);
+      if (tid >= o) {
+        ps += a;
+        pts += b;
+      }
+    }
+    int run = ps - s, trun = pts - ts;
+    for (int e = lo; e < hi; ++e) {
+      off[e] = run;
+      toff[e] = trun;
+      run += cnt[e];
+      trun += (cnt[e] + block_n - 1) / block_n;
+    }
+    if (tid == 31) {
+      off[E] = ps;
+      toff[E] = pts;
+    }
+  }
+  __syncthreads();
+  if (c == 0) {
+    for (int e = tid; e <= E; e += blockDim.x) expert_offsets[e] = off[e];
+    if (tid == 0) {
+      int n = toff[E];
+      if (n > max_tiles) {
+        us_dev_fail(status, US_DEV_BOUNDS);
+        n = max_tiles;
+      }
+      *num_tiles = n;
+    }
+    for (int e = tid; e < E; e += blockDim.x) {
+      const int k = cnt[e];
+      const int nt = (k + block_n - 1) / block_n;
+      for (int j = 0; j < nt; ++j) {
+        const int ti = toff[e] + j;
+        if (ti < max_tiles) {
+          tile_group[ti] = e;
+          tile_row0[ti] = off[e] + j * block_n;
+          tile_rows[ti] = min(block_n, k - j * block_n);
+        }
+      }
+    }
+  }
+  for (int i = r_lo + tid; i < r_hi; i += blockDim.x) {
+    const int e = ids[i] - e_lo;
+    if (e >= 0 && e < E) {
+      const int pos = off[e] + base[e] + atomicAdd(&cursor[e], 1);
+      sorted_route[pos] = i;
+      perm_of_route[i] = pos;
+    } else {
+      perm_of_route[i] = -1;
+    }
+  }
+}
+
 // Routing and sorting in one launch (decode-size batches): the CTA's 32 warps take the
 // tokens in turn, then the whole CTA sorts the routes they wrote.
 template <int PER_LANE>
@@ -235,17 +350,32 @@ route_sort_kernel(const float* __restrict__ logits, int* __restrict__ ids,
               expert_offsets, tile_group, tile_row0, tile_rows, num_tiles, status);
 }
 
+// Four permuted rows per CTA: a thread issues its four 16-byte loads before the stores.
+constexpr int kGatherRows = 4;
 __global__ void __launch_bounds__(256)
 moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_route,
                   const int* __restrict__ total, int top_k, int H,
                   __nv_bfloat16* __restrict__ xp) {
   US_PDL_PROLOGUE();
-  const int p = blockIdx.x;
-  if (p >= *total) return;
-  const int t = sorted_route[p] / top_k;
-  const uint4* src = reinterpret_cast<const uint4*>(x + (long long)t * H);
-  uint4* dst = reinterpret_cast<uint4*>(xp + (long long)p * H);
-  for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x) dst[v] = src[v];
+  const int p0 = blockIdx.x * kGatherRows;
+  const int n = min(kGatherRows, *total - p0);
+  if (n <= 0) return;
+  const uint4* src[kGatherRows];
+#pragma unroll
+  for (int j = 0; j < kGatherRows; ++j) {
+    const int t = sorted_route[p0 + (j < n ? j : 0)] / top_k;
+    src[j] = reinterpret_cast<const uint4*>(x + (long long)t * H);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(xp + (long long)p0 * H);
+  const int nvec = H >> 3;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    uint4 r[kGatherRows];
+#pragma unroll
+    for (int j = 0; j < kGatherRows; ++j) r[j] = src[j][v];
+#pragma unroll
+    for (int j = 0; j < kGatherRows; ++j)
+      if (j < n) dst[(long long)j * nvec + v] = r[j];
+  }
 }
 
 __global__ void __launch_bounds__(256)
@@ -441,6 +571,26 @@ US_API int us_moe_sort(const int* ids, int R, int e_lo, int E, int block_n, int 
   US_REQUIRE(ids && R >= 0 && E >= 1 && E <= kMaxExperts && block_n >= 1 && max_tiles >= 1);
   US_REQUIRE(sorted_route && perm_of_route && expert_offsets && tile_group && tile_row0 &&
              tile_rows && num_tiles);
+  if (R >= kSortClusterMinRoutes) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kSortCtas);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = (cudaStream_t)stream_;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = us::pdl_enabled() ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = kSortCtas;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaLaunchKernelEx(&cfg, moe_sort_cluster_kernel, ids, R, e_lo, E, block_n, max_tiles,
+                       sorted_route, perm_of_route, expert_offsets, tile_group, tile_row0,
+                       tile_rows, num_tiles, us_status_ptr());
+    US_LAUNCH_CHECK();
+    return US_OK;
+  }
   us::launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream_, ids, R, e_lo, E, block_n, max_tiles, sorted_route, perm_of_route, expert_offsets, tile_group,
       tile_row0, tile_rows, num_tiles, us_status_ptr());
   US_LAUNCH_CHECK();
@@ -451,7 +601,7 @@ US_API int us_moe_gather(const void* x, const int* sorted_route, const int* tota
                          int top_k, int H, void* xp, void* stream_) {
   US_REQUIRE(x && sorted_route && total && xp && R >= 0 && (H % 8) == 0 && top_k >= 1);
   if (R == 0) return US_OK;
-  us::launch_pdl(moe_gather_kernel, dim3(R), dim3(256), 0, (cudaStream_t)stream_, (const __nv_bfloat16*)x, sorted_route, total, top_k, H, (__nv_bfloat16*)xp);
+  us::launch_pdl(moe_gather_kernel, dim3((R + kGatherRows - 1) / kGatherRows), dim3(256), 0, (cudaStream_t)stream_, (const __nv_bfloat16*)x, sorted_route, total, top_k, H, (__nv_bfloat16*)xp);
   US_LAUNCH_CHECK();
   return US_OK;
 }

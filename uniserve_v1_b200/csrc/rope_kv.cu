@@ -103,6 +103,75 @@ __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope_kv_kernel(const Rope
   }
 }
 
+// Fast path for 128-wide heads rotated over all channels with half-split (NeoX) pairing:
+// a CTA owns one token (and a slice of its heads), computes the token's 64 (cos, sin)
+// factors once into shared memory, then every warp takes whole heads: a lane owns four
+// adjacent channels (one 8-byte access each way), its rotation partner is lane ^ 16.
+// The arithmetic and its rounding points are those of the general kernel above.
+constexpr int kFastWarps = 8;
+__global__ void __launch_bounds__(kFastWarps * 32) qk_norm_rope_kv_fast_kernel(const RopeArgs a,
+                                                                             const int heads_per_cta) {
+  US_PDL_PROLOGUE();
+  __shared__ float2 tab[64];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = a.Hq + 2 * a.Hkv;
+  const int t = blockIdx.x;
+  if (threadIdx.x < 64) {
+    float sn, cs;
+    sincosf((float)a.positions[t] * a.inv_freq[threadIdx.x], &sn, &cs);
+    tab[threadIdx.x] = make_float2(cs, sn);
+  }
+  __syncthreads();
+  const int slot = a.slots ? a.slots[t] : -1;
+  const int h_lo = blockIdx.y * heads_per_cta;
+  const int h_hi = min(heads, h_lo + heads_per_cta);
+  const float sign = lane < 16 ? -1.f : 1.f;
+  float2 f[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) f[e] = tab[((lane & 15) << 2) + e];
+  for (int h = h_lo + warp; h < h_hi; h += kFastWarps) {
+    __nv_bfloat16* row = a.qkv + ((long long)t * heads + h) * 128 + lane * 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(row);
+    const bool is_q = h < a.Hq;
+    const bool is_k = !is_q && h < a.Hq + a.Hkv;
+    if (!is_q && !is_k) {
+      if (a.vcache && slot >= 0)
+        *reinterpret_cast<uint2*>(a.vcache + ((long long)slot * a.Hkv + (h - a.Hq - a.Hkv)) * 128 +
+                                  lane * 4) = raw;
+      continue;
+    }
+    const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    float x[4] = {__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1)};
+    const __nv_bfloat16* w = is_q ? a.qw : a.kw;
+    if (w) {
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+      ss = us::warp_sum(ss);
+      const float inv = rsqrtf(ss / 128.f + a.eps);
+      const uint2 wr = *reinterpret_cast<const uint2*>(w + lane * 4);
+      const __nv_bfloat162 w0 = *reinterpret_cast<const __nv_bfloat162*>(&wr.x);
+      const __nv_bfloat162 w1 = *reinterpret_cast<const __nv_bfloat162*>(&wr.y);
+      x[0] = x[0] * inv * __low2float(w0);
+      x[1] = x[1] * inv * __high2float(w0);
+      x[2] = x[2] * inv * __low2float(w1);
+      x[3] = x[3] * inv * __high2float(w1);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float y = __shfl_xor_sync(0xffffffffu, x[e], 16);
+      x[e] = x[e] * f[e].x + sign * y * f[e].y;
+    }
+    const __nv_bfloat162 o0 = __floats2bfloat162_rn(x[0], x[1]);
+    const __nv_bfloat162 o1 = __floats2bfloat162_rn(x[2], x[3]);
+    uint2 out;
+    out.x = *reinterpret_cast<const uint32_t*>(&o0);
+    out.y = *reinterpret_cast<const uint32_t*>(&o1);
+    *reinterpret_cast<uint2*>(row) = out;
+    if (is_k && a.kcache && slot >= 0)
+      *reinterpret_cast<uint2*>(a.kcache + ((long long)slot * a.Hkv + (h - a.Hq)) * 128 + lane * 4) = out;
+  }
+}
+
 struct Rope3Args {
   __nv_bfloat16* q;        // [T, Hq * D] rows with leading dimension ldq
   __nv_bfloat16* k;        // [T, Hk * D] rows with leading dimension ldk
@@ -243,6 +312,23 @@ US_API int us_qk_norm_rope_kv(void* qkv, const void* qw, const void* kw, const i
   a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.rot = rot; a.interleaved = interleaved;
   a.eps = eps;
   const long long units = (long long)T * (Hq + 2 * Hkv);
+  const bool aligned = ((uintptr_t)qkv % 8) == 0 && (!qw || (uintptr_t)qw % 8 == 0) &&
+                       (!kw || (uintptr_t)kw % 8 == 0) && (!kcache || (uintptr_t)kcache % 8 == 0) &&
+                       (!vcache || (uintptr_t)vcache % 8 == 0);
+  if (D == 128 && rot == 128 && !interleaved && aligned) {
+    // few tokens (decode): split a token's heads over several CTAs so that the grid fills the GPU
+    const int heads = Hq + 2 * Hkv;
+    int split = (int)((2 * 148 + T - 1) / T);
+    split = split < 1 ? 1 : split;
+    const int max_split = (heads + kFastWarps - 1) / kFastWarps;
+    if (split > max_split) split = max_split;
+    const int per = (heads + split - 1) / split;
+    split = (heads + per - 1) / per;
+    us::launch_pdl(qk_norm_rope_kv_fast_kernel, dim3((unsigned)T, (unsigned)split), dim3(kFastWarps * 32),
+                   0, (cudaStream_t)stream, a, per);
+    US_LAUNCH_CHECK();
+    return US_OK;
+  }
   const int blocks = (int)((units + kWarps - 1) / kWarps);
   us::launch_pdl(qk_norm_rope_kv_kernel, dim3(blocks), dim3(kWarps * 32), 0, (cudaStream_t)stream, a);
   US_LAUNCH_CHECK();
