@@ -81,14 +81,50 @@ __device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigne
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+__device__ __forceinline__ unsigned long long add2_rm(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// 2^t for a pair of arguments in [-126, 128) on the FMA pipe, for the share of the softmax
+// that the special-function unit cannot take: with 128-wide heads a key block costs the
+// tensor pipe as many cycles as its 2 x 128 x 128 exponentials cost that unit, so the unit
+// is the limit unless part of the work leaves it.  t = n + f with n = floor(t) taken from
+// the low mantissa bits of t + 1.5 * 2^23 (rounded down), 2^f by a cubic with 2^0 exact
+// (relative error 8.6e-5, far under the bf16 rounding of P), and n added into the exponent
+// field.  Arguments below -126 are raised to it (2^-126 rounds to nothing in P and in the
+// row sum); the caller keeps -inf (masked keys) on the exact path.
+__device__ __forceinline__ void ex2_poly2(float t0, float t1, float& p0, float& p1) {
+  const float kMagic = 12582912.f;
+  const unsigned long long x = pack2(fmaxf(t0, -126.f), fmaxf(t1, -126.f));
+  const unsigned long long tt = add2_rm(x, pack2(kMagic, kMagic));
+  const unsigned long long fi = add2(tt, pack2(-kMagic, -kMagic));
+  const unsigned long long fr = fma2(fi, pack2(-1.f, -1.f), x);
+  unsigned long long p = fma2(fr, pack2(0.07706704f, 0.07706704f), pack2(0.22764499f, 0.22764499f));
+  p = fma2(p, fr, pack2(0.69511676f, 0.69511676f));
+  p = fma2(p, fr, pack2(1.f, 1.f));
+  float q0, q1, u0, u1;
+  unpack2(p, q0, q1);
+  unpack2(tt, u0, u1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(u0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(u1) << 23));
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
 
-template <int kD>
-__global__ void __launch_bounds__(320, 1)
+// kEmu: which of every eight exponential pairs go to the polynomial (bit = pair slot).
+// kSplit: threads per query row.  1: a warpgroup per tile, a thread owns a whole row of S
+// (128 columns).  2: two warpgroups per tile, a thread owns half a row (64 columns); the two
+// threads of a row are in warps with the same number modulo 4 (the same tensor-memory lanes),
+// exchange their half-row maxima through shared memory under a 64-thread named barrier and
+// keep partial row sums that meet in the epilogue.  Four softmax warps per scheduler instead
+// of two hide the latency of the dependent chains (exponential, pack, store) that bound the
+// one-thread-per-row form.
+template <int kD, uint32_t kEmu, int kSplit>
+__global__ void __launch_bounds__((8 * kSplit + 2) * 32, 1)
 flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const Flash2Args a) {
   US_PDL_PROLOGUE();
@@ -96,6 +132,9 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   constexpr int kTile = kHalves * kHalf;    // 32 KiB (head 128) or 16 KiB (head 64)
   const int q_pair = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  constexpr int kTmaWarp = 8 * kSplit, kMmaWarp = 8 * kSplit + 1;
+  constexpr int kCols = kBN / kSplit;       // columns of S a softmax thread owns
+  constexpr int kChunks = kCols / 32;
   const int q_start = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_start;
   const int k_start = a.cu_k[seq], kv_len = a.cu_k[seq + 1] - k_start;
   const int q0 = q_pair * 2 * kBM;
@@ -146,6 +185,9 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* o_full = bars + 13;  // [2] per tile
   uint32_t* tmem_slot = (uint32_t*)(bars + 15);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  // kSplit == 2: half-row maxima [slot j & 1][tile][half][row], then partial sums [tile][half][row]
+  float* xch_max = (float*)(bars + 18);
+  float* xch_sum = xch_max + 2 * 2 * 2 * kBM;
 
   if (tid == 0) {
     tc::mbar_init(q_full, 1);
@@ -155,13 +197,13 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc::mbar_init(&v_full[i], 1);
       tc::mbar_init(&v_empty[i], 1);
       tc::mbar_init(&s_full[i], 1);
-      tc::mbar_init(&p_full[i], 128);
+      tc::mbar_init(&p_full[i], 128 * kSplit);
       tc::mbar_init(&o_full[i], 1);
     }
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tc::tmem_alloc(tmem_slot, 512);
     tc::tmem_relinquish();
   }
@@ -170,7 +212,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     if (lane == 0) {
       tc::tma_prefetch_desc(&tmQ);
       tc::tma_prefetch_desc(&tmK);
@@ -207,7 +249,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           tc::tma_load_2d(sV + st * kTile + hf * kHalf, &tmV, &v_full[st], hk * kD + 64 * hf, row);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t kIdescQK = tc::make_idesc(kBM, kBN, tc::kFmtBF16, tc::kFmtBF16, 0, 0);
       constexpr uint32_t kIdescPV = tc::make_idesc(kBM, kD, tc::kFmtBF16, tc::kFmtBF16, 0, 1);
@@ -233,7 +275,9 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           // A = P: 16 keys = 8 packed columns per instruction.  B = V: d on N (two
           // 64-wide chunks, 16 KiB apart), 16 keys = two groups of eight rows (1 KiB apart).
           const uint64_t bd = tc::smem_desc_mnmajor_sw128(v_addr + kk * 2048, kHalf, 1024);
-          tc::umma_f16_ts(o_tmem, p_tmem + kk * 8, bd, kIdescPV, (j | kk) != 0);
+          // kSplit == 2 keeps the P of every 32 keys in the first 16 columns of their own S
+          const uint32_t p_col = kSplit == 2 ? (kk >> 1) * 32 + (kk & 1) * 8 : kk * 8;
+          tc::umma_f16_ts(o_tmem, p_tmem + p_col, bd, kIdescPV, (j | kk) != 0);
         }
         tc::umma_commit(&o_full[x]);
       };
@@ -281,106 +325,242 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
     }
   } else {
-    // ---- softmax: warpgroup = tile, thread = query row ----
-    const int x = warp >> 2;
-    const int r = tid & 127;
+    // ---- softmax: tile = warp / (4 kSplit), thread = query row (or half of one) ----
+    const int x = warp / (4 * kSplit);
+    const int hx = kSplit == 2 ? (warp >> 2) & 1 : 0;   // which half of the row's columns
+    const int r = (warp & 3) * 32 + lane;
     const int nbx = nb_t[x];
+    const int col0 = hx * kCols;
     const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t s_tmem = tmem_base + (uint32_t)x * kBN + lane_addr;
     const uint32_t o_tmem = tmem_base + 256 + (uint32_t)x * kD + lane_addr;
     const int q_idx = q0 + x * kBM + r;
+    const uint32_t pair_bar = 1u + (uint32_t)x * 4u + (uint32_t)(warp & 3);   // the row's two warps
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < nbx; ++j) {
-      if (!tc::mbar_wait(&s_full[x], (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
+      // A warp that gave up keeps meeting its partner at the pair barrier (once per block and
+      // once after the loop), so that the other warp of the row is never left waiting there.
+      if (ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(&s_full[x], (uint32_t)j & 1u, abort_flag));
+      if (!ok) {
+        if (kSplit == 2) pair_sync();
+        continue;
+      }
       tc::tc_fence_after_sync();
-      const int kbase = j * kBN;
-      int lim = kv_len - kbase;   // keys of this block this row may see: [0, lim)
+      const int kbase = j * kBN + col0;
+      int lim = kv_len - kbase;   // keys of this thread's columns this row may see: [0, lim)
       if (a.causal) lim = min(lim, q_idx + shift - kbase + 1);
-      const bool need_mask = lim < kBN;
-      // The whole row of S goes to registers in one round trip; four independent
-      // chains keep the maximum and the sum from serialising on instruction latency.
-      uint32_t v0[32], v1[32], v2[32], v3[32];
-      tc::tmem_ld32(s_tmem, v0);
-      tc::tmem_ld32(s_tmem + 32, v1);
-      tc::tmem_ld32(s_tmem + 64, v2);
-      tc::tmem_ld32(s_tmem + 96, v3);
-      tc::tmem_ld_wait();
-      if (need_mask) {   // last key block of the sequence or the causal diagonal
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (i >= lim) v0[i] = 0xff800000u;
-          if (32 + i >= lim) v1[i] = 0xff800000u;
-          if (64 + i >= lim) v2[i] = 0xff800000u;
-          if (96 + i >= lim) v3[i] = 0xff800000u;
-        }
-      }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        mx0 = max3(mx0, __uint_as_float(v0[i]), __uint_as_float(v0[i + 1]));
-        mx1 = max3(mx1, __uint_as_float(v1[i]), __uint_as_float(v1[i + 1]));
-        mx2 = max3(mx2, __uint_as_float(v2[i]), __uint_as_float(v2[i + 1]));
-        mx3 = max3(mx3, __uint_as_float(v3[i]), __uint_as_float(v3[i + 1]));
-      }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      const float m_new = fmaxf(m_used, mx * a.scale_log2);
-      const bool grow = m_new - m_used > kRescaleThreshold;
-      const bool any_grow =
-          __any_sync(0xffffffffu, grow || (m_used == -INFINITY && m_new > -INFINITY));
-      if (any_grow) {
-        const float alpha = (m_used == -INFINITY) ? 0.f : ex2f(m_used - m_new);
-        if (j > 0) {
-          // O_X is stable once the previous block's second product is done.
-          if (!tc::mbar_wait(&o_full[x], (uint32_t)(j - 1) & 1u, abort_flag)) { ok = false; break; }
-          tc::tc_fence_after_sync();
-#pragma unroll 1
-          for (int c = 0; c < kD; c += 32) {
-            uint32_t v[32];
-            tc::tmem_ld32(o_tmem + c, v);
-            tc::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tc::tmem_st32(o_tmem + c, v);
-          }
-        }
-        l_sum *= alpha;
-        m_used = m_new;
-      }
-      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-      const float neg_m = -m_eff;
+      const bool need_mask = lim < kCols;
       const unsigned long long sc2 = pack2(a.scale_log2, a.scale_log2);
-      const unsigned long long nm2 = pack2(neg_m, neg_m);
-      unsigned long long l0 = pack2(0.f, 0.f), l1 = l0, l2 = l0, l3 = l0;
-      uint32_t pk0[32], pk1[32];
-      auto exp_pair = [&](uint32_t x0, uint32_t x1, unsigned long long& l) -> uint32_t {
-        float t0, t1;
+      auto exp_pair = [&](uint32_t x0, uint32_t x1, unsigned long long nm2, unsigned long long& l,
+                          bool poly) -> uint32_t {
+        float t0, t1, p0, p1;
         unpack2(fma2(pack2(__uint_as_float(x0), __uint_as_float(x1)), sc2, nm2), t0, t1);
-        const float p0 = ex2f(t0), p1 = ex2f(t1);
+        if (poly) {
+          ex2_poly2(t0, t1, p0, p1);
+        } else {
+          p0 = ex2f(t0);
+          p1 = ex2f(t1);
+        }
         l = add2(l, pack2(p0, p1));
         __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
         return *reinterpret_cast<uint32_t*>(&t);
       };
+      if constexpr (kSplit == 2) {
+        // Half a row in two chunks of 32 columns.  Pass 1 takes the maximum of both chunks and
+        // keeps the second in registers; after the exchange with the other half of the row,
+        // pass 2 turns the second chunk into P, reads the first again from tensor memory and
+        // does the same.  At most one chunk of S and one of P are live: the thread fits the
+        // 96 registers that 18 warps leave it.  The P of a chunk goes over the first 16
+        // columns of that chunk's own S, so no thread writes where another still reads.
+        uint32_t v[32];
+        auto chunk_max = [&](int c) -> float {
+          if (need_mask) {
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        pk0[i >> 1] = exp_pair(v0[i], v0[i + 1], l0);
-        pk0[16 + (i >> 1)] = exp_pair(v1[i], v1[i + 1], l1);
-        pk1[i >> 1] = exp_pair(v2[i], v2[i + 1], l2);
-        pk1[16 + (i >> 1)] = exp_pair(v3[i], v3[i + 1], l3);
+            for (int i = 0; i < 32; ++i)
+              if (32 * c + i >= lim) v[i] = 0xff800000u;
+          }
+          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+            m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+            m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+            m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+          }
+          return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        };
+        tc::tmem_ld32(s_tmem + col0, v);
+        tc::tmem_ld_wait();
+        float mx = chunk_max(0);
+        tc::tmem_ld32(s_tmem + col0 + 32, v);
+        tc::tmem_ld_wait();
+        mx = fmaxf(mx, chunk_max(1));
+        {
+          // the other half's maximum; slot j & 1 is rewritten at j + 2, after the barrier of
+          // j + 1 that both threads pass once they have read slot j
+          float* slot = xch_max + ((j & 1) * 4 + x * 2) * kBM;
+          slot[hx * kBM + r] = mx;
+          pair_sync();
+          mx = fmaxf(mx, slot[(hx ^ 1) * kBM + r]);
+        }
+        const float m_new = fmaxf(m_used, mx * a.scale_log2);
+        const bool grow = m_new - m_used > kRescaleThreshold;
+        const bool any_grow =
+            __any_sync(0xffffffffu, grow || (m_used == -INFINITY && m_new > -INFINITY));
+        if (any_grow) {
+          const float alpha = (m_used == -INFINITY) ? 0.f : ex2f(m_used - m_new);
+          if (j > 0) {
+            // O_X is stable once the previous block's second product is done.
+            ok = __all_sync(0xffffffffu,
+                            tc::mbar_wait(&o_full[x], (uint32_t)(j - 1) & 1u, abort_flag));
+            if (!ok) continue;   // this block's pair barrier is behind us
+            tc::tc_fence_after_sync();
+#pragma unroll 1
+            for (int c = hx * (kD / 2); c < (hx + 1) * (kD / 2); c += 16) {
+              uint32_t w[16];
+              tc::tmem_ld16(o_tmem + c, w);
+              tc::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) * alpha);
+              tc::tmem_st16(o_tmem + c, w);
+            }
+          }
+          l_sum *= alpha;
+          m_used = m_new;
+        }
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        const unsigned long long nm2 = pack2(neg_m, neg_m);
+        const bool poly_ok = kEmu != 0 && !__any_sync(0xffffffffu, need_mask);
+        unsigned long long la = pack2(0.f, 0.f), lb = la;
+        auto chunk_exp = [&](int c) {
+          uint32_t pk[16];
+          if (poly_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              pk[i >> 1] = exp_pair(v[i], v[i + 1], nm2, la, (kEmu >> ((i >> 1) & 7)) & 1u);
+              pk[(i >> 1) + 1] = exp_pair(v[i + 2], v[i + 3], nm2, lb, (kEmu >> (((i >> 1) + 1) & 7)) & 1u);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              pk[i >> 1] = exp_pair(v[i], v[i + 1], nm2, la, false);
+              pk[(i >> 1) + 1] = exp_pair(v[i + 2], v[i + 3], nm2, lb, false);
+            }
+          }
+          tc::tmem_st16(s_tmem + col0 + 32 * c, pk);
+        };
+        chunk_exp(1);
+        tc::tmem_ld32(s_tmem + col0, v);
+        tc::tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i >= lim) v[i] = 0xff800000u;
+        }
+        chunk_exp(0);
+        {
+          float s0, s1;
+          unpack2(add2(la, lb), s0, s1);
+          l_sum += s0 + s1;
+        }
+      } else {
+        // The thread's columns of S go to registers in one round trip; four independent
+        // chains keep the maximum and the sum from serialising on instruction latency.
+        uint32_t v[kCols];
+  #pragma unroll
+        for (int c = 0; c < kChunks; ++c) tc::tmem_ld32(s_tmem + col0 + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(v + 32 * c));
+        tc::tmem_ld_wait();
+        if (need_mask) {   // last key block of the sequence or the causal diagonal
+  #pragma unroll
+          for (int i = 0; i < kCols; ++i)
+            if (i >= lim) v[i] = 0xff800000u;
+        }
+        float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  #pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+  #pragma unroll
+          for (int c = 0; c < kChunks; ++c) {
+            const int ch = kChunks == 4 ? c : c * 2 + ((i >> 1) & 1);
+            mxs[ch] = max3(mxs[ch], __uint_as_float(v[32 * c + i]), __uint_as_float(v[32 * c + i + 1]));
+          }
+        }
+        float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+        const float m_new = fmaxf(m_used, mx * a.scale_log2);
+        const bool grow = m_new - m_used > kRescaleThreshold;
+        const bool any_grow =
+            __any_sync(0xffffffffu, grow || (m_used == -INFINITY && m_new > -INFINITY));
+        if (any_grow) {
+          const float alpha = (m_used == -INFINITY) ? 0.f : ex2f(m_used - m_new);
+          if (j > 0) {
+            // O_X is stable once the previous block's second product is done.
+            ok = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[x], (uint32_t)(j - 1) & 1u, abort_flag));
+            if (!ok) continue;   // this block's pair barrier is behind us
+            tc::tc_fence_after_sync();
+  #pragma unroll 1
+            for (int c = hx * (kD / kSplit); c < (hx + 1) * (kD / kSplit); c += 32) {
+              uint32_t w[32];
+              tc::tmem_ld32(o_tmem + c, w);
+              tc::tmem_ld_wait();
+  #pragma unroll
+              for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) * alpha);
+              tc::tmem_st32(o_tmem + c, w);
+            }
+          }
+          l_sum *= alpha;
+          m_used = m_new;
+        }
+        const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+        const float neg_m = -m_eff;
+        const unsigned long long nm2 = pack2(neg_m, neg_m);
+        unsigned long long ls[4];
+  #pragma unroll
+        for (int c = 0; c < 4; ++c) ls[c] = pack2(0.f, 0.f);
+        uint32_t pk[kCols / 2];
+        // Blocks with masked keys (-inf scores) stay on the exact path, whole warps at a time.
+        if (kEmu != 0 && !__any_sync(0xffffffffu, need_mask)) {
+  #pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+  #pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+              const int ch = kChunks == 4 ? c : c * 2 + ((i >> 1) & 1);
+              const int slot8 = kChunks == 4 ? ((i >> 1) & 1) * 4 + c : ((i >> 1) & 3) * 2 + c;
+              pk[16 * c + (i >> 1)] =
+                  exp_pair(v[32 * c + i], v[32 * c + i + 1], nm2, ls[ch], (kEmu >> slot8) & 1u);
+            }
+          }
+        } else {
+  #pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+  #pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+              const int ch = kChunks == 4 ? c : c * 2 + ((i >> 1) & 1);
+              pk[16 * c + (i >> 1)] = exp_pair(v[32 * c + i], v[32 * c + i + 1], nm2, ls[ch], false);
+            }
+          }
+        }
+        {
+          float s0, s1;
+          unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), s0, s1);
+          l_sum += s0 + s1;
+        }
+        // P (packed pairs) replaces the first half of S, which is in registers by now.
+  #pragma unroll
+        for (int c = 0; c < kChunks / 2; ++c)
+          tc::tmem_st32(s_tmem + col0 / 2 + 32 * c, *reinterpret_cast<const uint32_t(*)[32]>(pk + 32 * c));
       }
-      {
-        float s0, s1;
-        unpack2(add2(add2(l0, l1), add2(l2, l3)), s0, s1);
-        l_sum += s0 + s1;
-      }
-      // P (64 packed columns) replaces the first half of S, which is in registers now.
-      tc::tmem_st32(s_tmem, pk0);
-      tc::tmem_st32(s_tmem + 32, pk1);
       tc::tmem_st_wait();
       tc::tc_fence_before_sync();
       tc::mbar_arrive(&p_full[x]);
     }
     if (nbx > 0) {
+      if (kSplit == 2) {   // the row's sum: both halves
+        float* sums = xch_sum + x * 2 * kBM;
+        sums[hx * kBM + r] = l_sum;
+        pair_sync();
+        l_sum += sums[(hx ^ 1) * kBM + r];
+      }
       if (ok && tc::mbar_wait(&o_full[x], (uint32_t)(nbx - 1) & 1u, abort_flag)) {
         tc::tc_fence_after_sync();
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
@@ -393,16 +573,16 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                  a.peer_col0 + (long long)h * kD;
         }
 #pragma unroll 1
-        for (int c = 0; c < kD; c += 32) {
-          uint32_t v[32];
-          tc::tmem_ld32(o_tmem + c, v);
+        for (int c = hx * (kD / kSplit); c < (hx + 1) * (kD / kSplit); c += 32) {
+          uint32_t w[32];
+          tc::tmem_ld32(o_tmem + c, w);
           tc::tmem_ld_wait();
           if (row_ok) {
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
               us::Pack16 o;
 #pragma unroll
-              for (int i = 0; i < 8; ++i) o.b[i] = us::f2bf(__uint_as_float(v[q4 * 8 + i]) * inv);
+              for (int i = 0; i < 8; ++i) o.b[i] = us::f2bf(__uint_as_float(w[q4 * 8 + i]) * inv);
               *reinterpret_cast<uint4*>(orow + c + q4 * 8) = o.u;
             }
           }
@@ -414,7 +594,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   }
   tc::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     __syncwarp();
     tc::tmem_dealloc(tmem_base, 512);
   }
@@ -470,24 +650,50 @@ int flash2_impl(const void* q, const void* k, const void* v, void* out, const in
     a.peer_col0 = peer_col0;
     a.peer_ld = peer_ld;
   }
-  const size_t smem = 6 * (size_t)(D / 64) * kHalf + 16 * 8 + 16 + 1024;
-  static bool configured = false;
-  if (!configured) {
-    US_CUDA_CHECK(cudaFuncSetAttribute(flash2_fwd_kernel<128>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(12 * (size_t)kHalf + 16 * 8 + 16 + 1024)));
-    US_CUDA_CHECK(cudaFuncSetAttribute(flash2_fwd_kernel<64>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(6 * (size_t)kHalf + 16 * 8 + 16 + 1024)));
-    configured = true;
-  }
+  // barriers and flags (18 words), half-row maxima (2 x 2 x 2 x 128 floats) and sums (2 x 2 x 128)
+  constexpr size_t kTail = 18 * 8 + (8 + 4) * kBM * sizeof(float) + 1024;
+  const size_t smem = 6 * (size_t)(D / 64) * kHalf + kTail;
+  // Share of the exponentials computed by the polynomial (US_FLASH_EMU = 0, 2, 3 or 4 of
+  // every 8 pairs) and threads per query row (US_FLASH_SPLIT = 1 or 2).
+  static const int emu = [] {
+    const char* e = getenv("US_FLASH_EMU");
+    const int v = e ? atoi(e) : 0;
+    return (v == 0 || v == 2 || v == 3 || v == 4) ? v : 0;
+  }();
+  static const int split = [] {
+    const char* e = getenv("US_FLASH_SPLIT");
+    return (e && atoi(e) == 1) ? 1 : 2;
+  }();
+  const int smem128 = (int)(12 * (size_t)kHalf + kTail);
+  const int smem64 = (int)(6 * (size_t)kHalf + kTail);
   dim3 grid((max_q + 2 * kBM - 1) / (2 * kBM), Hq, n_seqs);
-  if (D == 128)
-    US_CUDA_CHECK(us::launch_pdl(flash2_fwd_kernel<128>, grid, dim3(320), smem, stream, tmQ, tmK,
-                                 tmV, a));
-  else
-    US_CUDA_CHECK(us::launch_pdl(flash2_fwd_kernel<64>, grid, dim3(320), smem, stream, tmQ, tmK,
-                                 tmV, a));
+#define US_FLASH2_LAUNCH(DD, MASK, SP)                                                          \
+  do {                                                                                          \
+    static bool configured = false;                                                             \
+    if (!configured) {                                                                          \
+      US_CUDA_CHECK(cudaFuncSetAttribute(flash2_fwd_kernel<DD, MASK, SP>,                       \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                                         DD == 128 ? smem128 : smem64));                        \
+      configured = true;                                                                        \
+    }                                                                                           \
+    US_CUDA_CHECK(us::launch_pdl(flash2_fwd_kernel<DD, MASK, SP>, grid,                         \
+                                 dim3((8 * SP + 2) * 32), smem, stream, tmQ, tmK, tmV, a));     \
+  } while (0)
+  if (D == 128 && split == 2) {
+    if (emu == 0) US_FLASH2_LAUNCH(128, 0x00u, 2);
+    else if (emu == 2) US_FLASH2_LAUNCH(128, 0x21u, 2);
+    else if (emu == 3) US_FLASH2_LAUNCH(128, 0x29u, 2);
+    else US_FLASH2_LAUNCH(128, 0xA5u, 2);
+  } else if (D == 128) {
+    if (emu == 0) US_FLASH2_LAUNCH(128, 0x00u, 1);
+    else US_FLASH2_LAUNCH(128, 0x21u, 1);
+  } else if (split == 2) {
+    if (emu == 0) US_FLASH2_LAUNCH(64, 0x00u, 2);
+    else US_FLASH2_LAUNCH(64, 0xA5u, 2);
+  } else {
+    US_FLASH2_LAUNCH(64, 0x00u, 1);
+  }
+#undef US_FLASH2_LAUNCH
   return US_OK;
 }
 
