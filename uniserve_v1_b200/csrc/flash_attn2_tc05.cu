@@ -109,6 +109,41 @@ __device__ __forceinline__ void ex2_poly2(float t0, float t1, float& p0, float& 
   p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(u0) << 23));
   p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(u1) << 23));
 }
+// tcgen05.mma with the shared-memory descriptors given as (low, high) words.  The thread that
+// issues the products is a single instruction stream: with 64 cycles of tensor work per
+// 128 x 128 x 16 product, a dozen dependent instructions of 64-bit descriptor arithmetic per
+// product make the issue the limit.  The high words are constants of the layout and the low
+// words (start address in 16-byte units) advance by compile-time offsets, so a product costs
+// one 32-bit add per operand.
+__device__ __forceinline__ void umma_f16_words(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi,
+                                               uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_ts_words(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo,
+                                                  uint32_t b_hi, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -253,31 +288,36 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (lane == 0) {
       constexpr uint32_t kIdescQK = tc::make_idesc(kBM, kBN, tc::kFmtBF16, tc::kFmtBF16, 0, 0);
       constexpr uint32_t kIdescPV = tc::make_idesc(kBM, kD, tc::kFmtBF16, tc::kFmtBF16, 0, 1);
+      // descriptor words of the operands: Q tiles and K stages K-major, V stages MN-major
+      const uint64_t dq = tc::smem_desc_kmajor_sw128(tc::smem_u32(sQ));
+      const uint64_t dk = tc::smem_desc_kmajor_sw128(tc::smem_u32(sK));
+      const uint64_t dv = tc::smem_desc_mnmajor_sw128(tc::smem_u32(sV), kHalf, 1024);
+      const uint32_t q_lo = (uint32_t)dq, k_lo = (uint32_t)dk, v_lo = (uint32_t)dv;
+      const uint32_t km_hi = (uint32_t)(dq >> 32), mn_hi = (uint32_t)(dv >> 32);
       auto issue_qk = [&](int x, int j) {
-        const uint32_t q_addr = tc::smem_u32(sQ + x * kTile);
-        const uint32_t k_addr = tc::smem_u32(sK + (j & 1) * kTile);
+        const uint32_t qa = q_lo + (uint32_t)x * (kTile >> 4);
+        const uint32_t kb = k_lo + (uint32_t)(j & 1) * (kTile >> 4);
         const uint32_t s_tmem = tmem_base + (uint32_t)x * kBN;
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
-          const uint32_t half = kk >> 2, sub = kk & 3;
-          const uint64_t ad = tc::smem_desc_kmajor_sw128(q_addr + half * kHalf) + 2 * sub;
-          const uint64_t bd = tc::smem_desc_kmajor_sw128(k_addr + half * kHalf) + 2 * sub;
-          tc::umma_f16(s_tmem, ad, bd, kIdescQK, kk != 0);
+          const uint32_t off = (uint32_t)(kk >> 2) * (kHalf >> 4) + 2u * (uint32_t)(kk & 3);
+          umma_f16_words(s_tmem, qa + off, km_hi, kb + off, km_hi, kIdescQK, kk != 0);
         }
         tc::umma_commit(&s_full[x]);
       };
       auto issue_pv = [&](int x, int j) {
-        const uint32_t v_addr = tc::smem_u32(sV + (j & 1) * kTile);
+        const uint32_t vb = v_lo + (uint32_t)(j & 1) * (kTile >> 4);
         const uint32_t p_tmem = tmem_base + (uint32_t)x * kBN;
         const uint32_t o_tmem = tmem_base + 256 + (uint32_t)x * kD;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           // A = P: 16 keys = 8 packed columns per instruction.  B = V: d on N (two
-          // 64-wide chunks, 16 KiB apart), 16 keys = two groups of eight rows (1 KiB apart).
-          const uint64_t bd = tc::smem_desc_mnmajor_sw128(v_addr + kk * 2048, kHalf, 1024);
+          // 64-wide chunks, 16 KiB apart), 16 keys = two groups of eight rows (1 KiB apart),
+          // 2 KiB further per instruction.
           // kSplit == 2 keeps the P of every 32 keys in the first 16 columns of their own S
           const uint32_t p_col = kSplit == 2 ? (kk >> 1) * 32 + (kk & 1) * 8 : kk * 8;
-          tc::umma_f16_ts(o_tmem, p_tmem + p_col, bd, kIdescPV, (j | kk) != 0);
+          umma_f16_ts_words(o_tmem, p_tmem + p_col, vb + (uint32_t)kk * (2048 >> 4), mn_hi,
+                            kIdescPV, (j | kk) != 0);
         }
         tc::umma_commit(&o_full[x]);
       };
