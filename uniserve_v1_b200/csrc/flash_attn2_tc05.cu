@@ -210,11 +210,16 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint8_t* sK = smem + 2 * kTile;      // two stages
   uint8_t* sV = smem + 4 * kTile;      // two stages
   uint64_t* bars = (uint64_t*)(smem + 6 * kTile);
+  // One "full" and one "empty" barrier per key block j (slot j & 1) instead of one per
+  // operand: kv_full[j & 1] counts the bytes of V(j) and K(j + 1), which the producer loads
+  // back to back and the issuing thread needs back to back (O += P V(j), then S = Q K(j+1)^T);
+  // kv_empty[j & 1], committed once after the block's four products, frees V stage j & 1
+  // and K stage (j + 1) & 1 together.  K(0) arrives with Q.  The issuing thread is a single
+  // instruction stream that the tensor pipe waits for: every wait and commit it does not
+  // execute is tensor time.
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;   // [2]
-  uint64_t* k_empty = bars + 3;  // [2]
-  uint64_t* v_full = bars + 5;   // [2]
-  uint64_t* v_empty = bars + 7;  // [2]
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
   uint64_t* s_full = bars + 9;   // [2] per tile
   uint64_t* p_full = bars + 11;  // [2] per tile
   uint64_t* o_full = bars + 13;  // [2] per tile
@@ -227,10 +232,8 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (tid == 0) {
     tc::mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      tc::mbar_init(&k_full[i], 1);
-      tc::mbar_init(&k_empty[i], 1);
-      tc::mbar_init(&v_full[i], 1);
-      tc::mbar_init(&v_empty[i], 1);
+      tc::mbar_init(&kv_full[i], 1);
+      tc::mbar_init(&kv_empty[i], 1);
       tc::mbar_init(&s_full[i], 1);
       tc::mbar_init(&p_full[i], 128 * kSplit);
       tc::mbar_init(&o_full[i], 1);
@@ -252,7 +255,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc::tma_prefetch_desc(&tmQ);
       tc::tma_prefetch_desc(&tmK);
       tc::tma_prefetch_desc(&tmV);
-      tc::mbar_expect_tx(q_full, 2 * kTile);
+      tc::mbar_expect_tx(q_full, 3 * kTile);
 #pragma unroll
       for (int x = 0; x < 2; ++x) {
         const int row = q_start + q0 + x * kBM;   // rows past the tensor read as zeros
@@ -260,28 +263,31 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int hf = 0; hf < kHalves; ++hf)
           tc::tma_load_2d(sQ + x * kTile + hf * kHalf, &tmQ, q_full, h * kD + 64 * hf, row);
       }
+#pragma unroll
+      for (int hf = 0; hf < kHalves; ++hf)
+        tc::tma_load_2d(sK + hf * kHalf, &tmK, q_full, hk * kD + 64 * hf, k_start);
       for (int j = 0; j < nb; ++j) {
         const int st = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        const int row = k_start + j * kBN;
-        if (!tc::mbar_wait(&k_empty[st], ph ^ 1u, abort_flag)) {
+        const bool more = j + 1 < nb;
+        // kv_empty[0] completes after blocks 0, 2, 4 ..., kv_empty[1] after the first S
+        // products (which read K stage 0, the stage K(2) goes to) and after blocks 1, 3, ...:
+        // block j waits for completion number (j + 1) / 2 of its slot, none for block 0
+        if (!tc::mbar_wait(&kv_empty[st], ((uint32_t)((j + 1) >> 1) & 1u) ^ 1u, abort_flag)) {
           us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
           *abort_flag = 1;
           break;
         }
-        tc::mbar_expect_tx(&k_full[st], kTile);
+        tc::mbar_expect_tx(&kv_full[st], more ? 2 * kTile : kTile);
 #pragma unroll
         for (int hf = 0; hf < kHalves; ++hf)
-          tc::tma_load_2d(sK + st * kTile + hf * kHalf, &tmK, &k_full[st], hk * kD + 64 * hf, row);
-        if (!tc::mbar_wait(&v_empty[st], ph ^ 1u, abort_flag)) {
-          us_dev_fail(a.status, US_DEV_TIMEOUT_EMPTY);
-          *abort_flag = 1;
-          break;
+          tc::tma_load_2d(sV + st * kTile + hf * kHalf, &tmV, &kv_full[st], hk * kD + 64 * hf,
+                          k_start + j * kBN);
+        if (more) {
+#pragma unroll
+          for (int hf = 0; hf < kHalves; ++hf)
+            tc::tma_load_2d(sK + (st ^ 1) * kTile + hf * kHalf, &tmK, &kv_full[st],
+                            hk * kD + 64 * hf, k_start + (j + 1) * kBN);
         }
-        tc::mbar_expect_tx(&v_full[st], kTile);
-#pragma unroll
-        for (int hf = 0; hf < kHalves; ++hf)
-          tc::tma_load_2d(sV + st * kTile + hf * kHalf, &tmV, &v_full[st], hk * kD + 64 * hf, row);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -319,32 +325,26 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           umma_f16_ts_words(o_tmem, p_tmem + p_col, vb + (uint32_t)kk * (2048 >> 4), mn_hi,
                             kIdescPV, (j | kk) != 0);
         }
-        tc::umma_commit(&o_full[x]);
+        // a tile's accumulator is waited for only after its last block: before that, the next
+        // S of the tile (issued after this product, committed to s_full) says the same
+        if (j == nb_t[x] - 1) tc::umma_commit(&o_full[x]);
       };
-      bool ok = tc::mbar_wait(q_full, 0, abort_flag) && tc::mbar_wait(&k_full[0], 0, abort_flag);
+      bool ok = tc::mbar_wait(q_full, 0, abort_flag);
       if (ok) {
         tc::tc_fence_after_sync();
         if (nb_t[0] > 0) issue_qk(0, 0);
         if (nb_t[1] > 0) issue_qk(1, 0);
-        tc::umma_commit(&k_empty[0]);
+        tc::umma_commit(&kv_empty[1]);   // K stage 0 may be refilled (with K(2), by block 1's loads)
       }
       for (int j = 0; ok && j < nb; ++j) {
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         const uint32_t pj = (uint32_t)j & 1u;
-        const bool more = j + 1 < nb;
-        if (!tc::mbar_wait(&v_full[j & 1], ph, abort_flag)) { ok = false; break; }
+        // V(j) and K(j + 1) are there
+        if (!tc::mbar_wait(&kv_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
         // tile A: O_A += P_A V_j, then S_A of the next block
         if (j < nb_t[0]) {
           if (!tc::mbar_wait(&p_full[0], pj, abort_flag)) { ok = false; break; }
           tc::tc_fence_after_sync();
           issue_pv(0, j);
-        }
-        if (more) {
-          if (!tc::mbar_wait(&k_full[(j + 1) & 1], (uint32_t)((j + 1) >> 1) & 1u, abort_flag)) {
-            ok = false;
-            break;
-          }
-          tc::tc_fence_after_sync();
           if (j + 1 < nb_t[0]) issue_qk(0, j + 1);
         }
         // tile B
@@ -352,12 +352,9 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           if (!tc::mbar_wait(&p_full[1], pj, abort_flag)) { ok = false; break; }
           tc::tc_fence_after_sync();
           issue_pv(1, j);
-        }
-        tc::umma_commit(&v_empty[j & 1]);
-        if (more) {
           if (j + 1 < nb_t[1]) issue_qk(1, j + 1);
-          tc::umma_commit(&k_empty[(j + 1) & 1]);
         }
+        tc::umma_commit(&kv_empty[j & 1]);
       }
       if (!ok) {
         us_dev_fail(a.status, US_DEV_TIMEOUT_FULL);
@@ -452,11 +449,8 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (any_grow) {
           const float alpha = (m_used == -INFINITY) ? 0.f : ex2f(m_used - m_new);
           if (j > 0) {
-            // O_X is stable once the previous block's second product is done.
-            ok = __all_sync(0xffffffffu,
-                            tc::mbar_wait(&o_full[x], (uint32_t)(j - 1) & 1u, abort_flag));
-            if (!ok) continue;   // this block's pair barrier is behind us
-            tc::tc_fence_after_sync();
+            // O_X is stable: this block's S was issued after the previous block's second
+            // product by the same thread, and the commit that filled s_full covers both.
 #pragma unroll 1
             for (int c = hx * (kD / 2); c < (hx + 1) * (kD / 2); c += 16) {
               uint32_t w[16];
@@ -534,10 +528,8 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (any_grow) {
           const float alpha = (m_used == -INFINITY) ? 0.f : ex2f(m_used - m_new);
           if (j > 0) {
-            // O_X is stable once the previous block's second product is done.
-            ok = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[x], (uint32_t)(j - 1) & 1u, abort_flag));
-            if (!ok) continue;   // this block's pair barrier is behind us
-            tc::tc_fence_after_sync();
+            // O_X is stable: this block's S was issued after the previous block's second
+            // product by the same thread, and the commit that filled s_full covers both.
   #pragma unroll 1
             for (int c = hx * (kD / kSplit); c < (hx + 1) * (kD / kSplit); c += 32) {
               uint32_t w[32];
@@ -601,7 +593,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         pair_sync();
         l_sum += sums[(hx ^ 1) * kBM + r];
       }
-      if (ok && tc::mbar_wait(&o_full[x], (uint32_t)(nbx - 1) & 1u, abort_flag)) {
+      if (ok && tc::mbar_wait(&o_full[x], 0, abort_flag)) {
         tc::tc_fence_after_sync();
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
         const bool row_ok = q_idx < q_len;
