@@ -479,6 +479,45 @@ def test_flash_attn_long_sequence():
     close(out, ref, 2e-2, 2e-2)
 
 
+def test_flash_attn_last_partial_wave_split_over_the_keys():
+    """12 query pairs x 13 heads are 156 (pair, head) items: one wave of 148 CTAs and 8 more,
+    which the launch splits over the keys (6 parts of 4 key blocks), leaves unnormalised with
+    their maxima and sums, and merges; K and V lengths differ from Q and are ragged."""
+    from uniserve_v1_b200.ops.flash import flash_attn_varlen
+    D, H, Tq, Tk = 128, 13, 3072 - 5, 3072 - 37
+    q, k, v = rnd(Tq, H, D, seed=1), rnd(Tk, H, D, seed=2), rnd(Tk, H, D, seed=3)
+    cu_q = torch.tensor([0, Tq], dtype=torch.int32, device=DEV)
+    cu_k = torch.tensor([0, Tk], dtype=torch.int32, device=DEV)
+    out = flash_attn_varlen(q, k, v, cu_q, cu_k, Tq, Tk, 1 / math.sqrt(D), False)
+    ref = R.varlen_attention(q, k, v, cu_q.cpu(), cu_k.cpu(), 1 / math.sqrt(D), False)
+    close(out, ref, 2e-2, 2e-2)
+    assert N.read_status() == 0
+
+
+def test_flash_attn_push_with_a_split_last_wave_equals_the_plain_kernel():
+    """The sequence-parallel return (rows stored into their owners' buffers from the epilogue,
+    here two buffers of this GPU) on a shape whose last wave is split over the keys: the merge
+    kernel does the owner mapping for those rows."""
+    import ctypes
+    from uniserve_v1_b200.ops.flash import flash_attn_varlen
+    from uniserve_v1_b200.parallel import ulysses  # registers the entry point's signature
+    D, H, T, P = 128, 13, 3072, 2
+    q, k, v = rnd(T, H, D, seed=4), rnd(T, H, D, seed=5), rnd(T, H, D, seed=6)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    ref = flash_attn_varlen(q, k, v, cu, cu, T, T, 1 / math.sqrt(D), False)
+    ro, inner = T // P, 2 * H * D                      # this rank's heads are columns [H*D, 2*H*D)
+    bufs = [torch.zeros(ro, inner, dtype=BF, device=DEV) for _ in range(P)]
+    ptrs = (ctypes.c_void_p * P)(*[b.data_ptr() for b in bufs])
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    N.call("us_flash_attn_push", N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(cu), N.ptr(cu), T, T, H, H,
+           q.stride(0), k.stride(0), v.stride(0), 1 / math.sqrt(D), ptrs, P, ro, H * D, inner, st)
+    torch.cuda.synchronize()
+    got = torch.cat([b[:, H * D:] for b in bufs], 0).view(T, H, D)
+    assert torch.equal(got, ref)
+    assert all(float(b[:, :H * D].abs().max()) == 0.0 for b in bufs)
+    assert N.read_status() == 0
+
+
 @pytest.mark.parametrize("single", [True, False])
 @pytest.mark.parametrize("causal", [False, True])
 def test_flash_attn_both_kernels(single, causal, monkeypatch):

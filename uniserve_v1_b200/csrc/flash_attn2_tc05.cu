@@ -52,6 +52,16 @@ struct Flash2Args {
   int peer_rows;
   int peer_col0;
   long long peer_ld;
+  // Linear launches (one sequence, no mask): CTA i of a launch with kv_parts >= 1 takes work
+  // item item0 + i / kv_parts = (query pair, head) with the pair running fastest, and key
+  // blocks [part * per, (part + 1) * per) of it.  With kv_parts > 1 the CTA leaves its rows
+  // unnormalised in part_o with their maxima and sums in part_ml; flash2_merge_kernel folds
+  // the parts.  kv_parts == 0: the (pair, head, sequence) grid.
+  int kv_parts, item0, items_x, blocks_per_part;
+  float* part_o;    // [CTA][256 rows][kD]
+  float* part_ml;   // [CTA][256 rows][2]: running maximum (log2 domain), sum
+  int no_wait;      // the launch reads only what the launch before it has waited for
+  int tail_follows; // the next launch is this one's tail and has no_wait set
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -162,10 +172,27 @@ template <int kD, uint32_t kEmu, int kSplit>
 __global__ void __launch_bounds__((8 * kSplit + 2) * 32, 1)
 flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const Flash2Args a) {
-  US_PDL_PROLOGUE();
+  // A launch that is followed by its own tail launch lets that one start only once every
+  // CTA here is past its wait: the tail launch does not wait itself.
+  if (a.no_wait) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  } else if (a.tail_follows) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  } else {
+    US_PDL_PROLOGUE();
+  }
   constexpr int kHalves = kD / 64;          // 64-column (128-byte) slabs per tile
   constexpr int kTile = kHalves * kHalf;    // 32 KiB (head 128) or 16 KiB (head 64)
-  const int q_pair = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
+  int q_pair = blockIdx.x, h = blockIdx.y, part = 0;
+  const int seq = blockIdx.z;
+  if (a.kv_parts > 0) {
+    const int item = a.item0 + (int)blockIdx.x / a.kv_parts;
+    part = (int)blockIdx.x % a.kv_parts;
+    q_pair = item % a.items_x;
+    h = item / a.items_x;
+  }
+  const bool partial = a.kv_parts > 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   constexpr int kTmaWarp = 8 * kSplit, kMmaWarp = 8 * kSplit + 1;
   constexpr int kCols = kBN / kSplit;       // columns of S a softmax thread owns
@@ -185,9 +212,15 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (a.causal) lim = min(kv_len, q0x + kBM + shift);
     nb_t[x] = (q0x < q_len && lim > 0) ? (lim + kBN - 1) / kBN : 0;
   }
+  // this CTA's key blocks are jb, jb + 1, ... (all of them unless the launch splits the keys)
+  const int jb = partial ? part * a.blocks_per_part : 0;
+  if (partial) {
+#pragma unroll
+    for (int x = 0; x < 2; ++x) nb_t[x] = max(0, min(nb_t[x] - jb, a.blocks_per_part));
+  }
   const int nb = max(nb_t[0], nb_t[1]);
 
-  if (tid < 2 * kBM) {  // tiles without a visible key: zeros
+  if (!partial && tid < 2 * kBM) {  // tiles without a visible key: zeros
     const int x = tid >> 7;
     const int qi = q0 + tid;
     if (nb_t[x] == 0 && qi < q_len) {
@@ -202,7 +235,14 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       for (int i = 0; i < kD / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
     }
   }
-  if (nb == 0) return;
+  if (nb == 0) {
+    if (partial && tid < 2 * kBM) {   // a part without keys: weight zero in the merge
+      const long long prow = (long long)blockIdx.x * (2 * kBM) + tid;
+      a.part_ml[prow * 2] = -INFINITY;
+      a.part_ml[prow * 2 + 1] = 0.f;
+    }
+    return;
+  }
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -265,7 +305,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
 #pragma unroll
       for (int hf = 0; hf < kHalves; ++hf)
-        tc::tma_load_2d(sK + hf * kHalf, &tmK, q_full, hk * kD + 64 * hf, k_start);
+        tc::tma_load_2d(sK + hf * kHalf, &tmK, q_full, hk * kD + 64 * hf, k_start + jb * kBN);
       for (int j = 0; j < nb; ++j) {
         const int st = j & 1;
         const bool more = j + 1 < nb;
@@ -281,12 +321,12 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
         for (int hf = 0; hf < kHalves; ++hf)
           tc::tma_load_2d(sV + st * kTile + hf * kHalf, &tmV, &kv_full[st], hk * kD + 64 * hf,
-                          k_start + j * kBN);
+                          k_start + (jb + j) * kBN);
         if (more) {
 #pragma unroll
           for (int hf = 0; hf < kHalves; ++hf)
             tc::tma_load_2d(sK + (st ^ 1) * kTile + hf * kHalf, &tmK, &kv_full[st],
-                            hk * kD + 64 * hf, k_start + (j + 1) * kBN);
+                            hk * kD + 64 * hf, k_start + (jb + j + 1) * kBN);
         }
       }
     }
@@ -385,7 +425,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         continue;
       }
       tc::tc_fence_after_sync();
-      const int kbase = j * kBN + col0;
+      const int kbase = (jb + j) * kBN + col0;
       int lim = kv_len - kbase;   // keys of this thread's columns this row may see: [0, lim)
       if (a.causal) lim = min(lim, q_idx + shift - kbase + 1);
       const bool need_mask = lim < kCols;
@@ -595,8 +635,29 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       if (ok && tc::mbar_wait(&o_full[x], 0, abort_flag)) {
         tc::tc_fence_after_sync();
+        bool continue_epilogue = true;
+        if (partial) {
+          // unnormalised rows of this part of the keys, with the row's maximum and sum
+          const long long prow = (long long)blockIdx.x * (2 * kBM) + x * kBM + r;
+          float* po = a.part_o + prow * kD;
+          if (hx == 0) {
+            a.part_ml[prow * 2] = m_used;
+            a.part_ml[prow * 2 + 1] = l_sum;
+          }
+#pragma unroll 1
+          for (int c = hx * (kD / kSplit); c < (hx + 1) * (kD / kSplit); c += 32) {
+            uint32_t w[32];
+            tc::tmem_ld32(o_tmem + c, w);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4)
+              *reinterpret_cast<uint4*>(po + c + q4 * 4) =
+                  make_uint4(w[q4 * 4], w[q4 * 4 + 1], w[q4 * 4 + 2], w[q4 * 4 + 3]);
+          }
+          continue_epilogue = false;
+        }
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-        const bool row_ok = q_idx < q_len;
+        const bool row_ok = q_idx < q_len && continue_epilogue;
         __nv_bfloat16* orow = a.out + (long long)(q_start + q_idx) * a.ldo + (long long)h * kD;
         if (a.peer_rows > 0) {
           const int row = q_start + q_idx;
@@ -605,7 +666,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                  a.peer_col0 + (long long)h * kD;
         }
 #pragma unroll 1
-        for (int c = hx * (kD / kSplit); c < (hx + 1) * (kD / kSplit); c += 32) {
+        for (int c = hx * (kD / kSplit); continue_epilogue && c < (hx + 1) * (kD / kSplit); c += 32) {
           uint32_t w[32];
           tc::tmem_ld32(o_tmem + c, w);
           tc::tmem_ld_wait();
@@ -632,9 +693,86 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   }
 }
 
+// Folds the parts of a key-split tail launch: row r of work item i has `parts` unnormalised
+// partial rows (CTA i * parts + p of the tail launch) with maxima m_p and sums l_p;
+// out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p.  A thread owns eight channels of a row.
+__global__ void __launch_bounds__(128)
+flash2_merge_kernel(const Flash2Args a, int parts, int kD) {
+  const int item_local = blockIdx.x;
+  const int item = a.item0 + item_local;
+  const int q_pair = item % a.items_x, h = item / a.items_x;
+  const int chunks = kD / 8;                       // threads per row
+  const int rows_per_cta = 128 / chunks;
+  const int r = blockIdx.y * rows_per_cta + (int)threadIdx.x / chunks;   // row of the pair
+  const int c = ((int)threadIdx.x % chunks) * 8;
+  const int q_len = a.cu_q[1] - a.cu_q[0];
+  const int q_idx = q_pair * 2 * kBM + r;
+  if (r >= 2 * kBM || q_idx >= q_len) return;
+  float M = -INFINITY;
+  for (int p = 0; p < parts; ++p)
+    M = fmaxf(M, a.part_ml[((long long)(item_local * parts + p) * (2 * kBM) + r) * 2]);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, den = 0.f;
+  for (int p = 0; p < parts; ++p) {
+    const long long prow = (long long)(item_local * parts + p) * (2 * kBM) + r;
+    const float m = a.part_ml[prow * 2], l = a.part_ml[prow * 2 + 1];
+    const float wgt = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    den += wgt * l;
+    const float4 v0 = *reinterpret_cast<const float4*>(a.part_o + prow * kD + c);
+    const float4 v1 = *reinterpret_cast<const float4*>(a.part_o + prow * kD + c + 4);
+    acc[0] += wgt * v0.x; acc[1] += wgt * v0.y; acc[2] += wgt * v0.z; acc[3] += wgt * v0.w;
+    acc[4] += wgt * v1.x; acc[5] += wgt * v1.y; acc[6] += wgt * v1.z; acc[7] += wgt * v1.w;
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  const int row = a.cu_q[0] + q_idx;
+  __nv_bfloat16* orow = a.out + (long long)row * a.ldo + (long long)h * kD;
+  if (a.peer_rows > 0) {
+    const int p = row / a.peer_rows;
+    orow = (__nv_bfloat16*)a.peer_out[p] + (long long)(row - p * a.peer_rows) * a.peer_ld +
+           a.peer_col0 + (long long)h * kD;
+  }
+  us::Pack16 o;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o.b[i] = us::f2bf(acc[i] * inv);
+  *reinterpret_cast<uint4*>(orow + c) = o.u;
+}
+
 }  // namespace
 
 namespace {
+
+// Scratch of the key-split tail launch (at most one wave of CTAs), one per stream that used it.
+struct TailScratch {
+  cudaStream_t stream;
+  float* part_o;
+  float* part_ml;
+};
+constexpr int kTailStreams = 8;
+constexpr int kTailCtas = 160;
+
+bool tail_scratch(cudaStream_t stream, float** part_o, float** part_ml) {
+  static TailScratch table[kTailStreams] = {};
+  static int used = 0;
+  for (int i = 0; i < used; ++i)
+    if (table[i].stream == stream) {
+      *part_o = table[i].part_o;
+      *part_ml = table[i].part_ml;
+      return true;
+    }
+  if (used == kTailStreams) return false;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)
+    return false;                       // no allocation inside a graph capture
+  float *po = nullptr, *pm = nullptr;
+  if (cudaMalloc(&po, (size_t)kTailCtas * 2 * kBM * kDMax * sizeof(float)) != cudaSuccess) return false;
+  if (cudaMalloc(&pm, (size_t)kTailCtas * 2 * kBM * 2 * sizeof(float)) != cudaSuccess) {
+    cudaFree(po);
+    return false;
+  }
+  table[used++] = {stream, po, pm};
+  *part_o = po;
+  *part_ml = pm;
+  return true;
+}
 
 int flash2_impl(const void* q, const void* k, const void* v, void* out, const int* cu_q,
                 const int* cu_k, int n_seqs, int Tq, int Tk, int Hq, int Hkv, int D, int max_q,
@@ -694,11 +832,10 @@ int flash2_impl(const void* q, const void* k, const void* v, void* out, const in
   }();
   static const int split = [] {
     const char* e = getenv("US_FLASH_SPLIT");
-    return (e && atoi(e) == 1) ? 1 : 2;
+    return (e && atoi(e) == 2) ? 2 : 1;
   }();
   const int smem128 = (int)(12 * (size_t)kHalf + kTail);
   const int smem64 = (int)(6 * (size_t)kHalf + kTail);
-  dim3 grid((max_q + 2 * kBM - 1) / (2 * kBM), Hq, n_seqs);
 #define US_FLASH2_LAUNCH(DD, MASK, SP)                                                          \
   do {                                                                                          \
     static bool configured = false;                                                             \
@@ -709,22 +846,85 @@ int flash2_impl(const void* q, const void* k, const void* v, void* out, const in
       configured = true;                                                                        \
     }                                                                                           \
     US_CUDA_CHECK(us::launch_pdl(flash2_fwd_kernel<DD, MASK, SP>, grid,                         \
-                                 dim3((8 * SP + 2) * 32), smem, stream, tmQ, tmK, tmV, a));     \
+                                 dim3((8 * SP + 2) * 32), smem, stream, tmQ, tmK, tmV, aa));    \
   } while (0)
-  if (D == 128 && split == 2) {
-    if (emu == 0) US_FLASH2_LAUNCH(128, 0x00u, 2);
-    else if (emu == 2) US_FLASH2_LAUNCH(128, 0x21u, 2);
-    else if (emu == 3) US_FLASH2_LAUNCH(128, 0x29u, 2);
-    else US_FLASH2_LAUNCH(128, 0xA5u, 2);
-  } else if (D == 128) {
-    if (emu == 0) US_FLASH2_LAUNCH(128, 0x00u, 1);
-    else US_FLASH2_LAUNCH(128, 0x21u, 1);
-  } else if (split == 2) {
-    if (emu == 0) US_FLASH2_LAUNCH(64, 0x00u, 2);
-    else US_FLASH2_LAUNCH(64, 0xA5u, 2);
-  } else {
-    US_FLASH2_LAUNCH(64, 0x00u, 1);
+  auto launch = [&](dim3 grid, const Flash2Args& aa) -> int {
+    if (D == 128 && split == 2) {
+      if (emu == 0) US_FLASH2_LAUNCH(128, 0x00u, 2);
+      else if (emu == 2) US_FLASH2_LAUNCH(128, 0x21u, 2);
+      else if (emu == 3) US_FLASH2_LAUNCH(128, 0x29u, 2);
+      else US_FLASH2_LAUNCH(128, 0xA5u, 2);
+    } else if (D == 128) {
+      if (emu == 0) US_FLASH2_LAUNCH(128, 0x00u, 1);
+      else US_FLASH2_LAUNCH(128, 0x21u, 1);
+    } else if (split == 2) {
+      if (emu == 0) US_FLASH2_LAUNCH(64, 0x00u, 2);
+      else US_FLASH2_LAUNCH(64, 0xA5u, 2);
+    } else {
+      US_FLASH2_LAUNCH(64, 0x00u, 1);
+    }
+    return US_OK;
+  };
+  a.kv_parts = 0;
+  a.item0 = 0;
+  a.items_x = 0;
+  a.blocks_per_part = 0;
+  a.part_o = nullptr;
+  a.part_ml = nullptr;
+  a.no_wait = 0;
+  a.tail_follows = 0;
+  const int q_pairs = (max_q + 2 * kBM - 1) / (2 * kBM);
+  // One sequence without a mask whose (pair, head) items leave a last wave at most half
+  // full: that wave's items are split over the keys so that they fill the GPU, and merged.
+  // (A rank of an 8-way Ulysses group has 152 pairs x 7 heads = 7.2 waves of 148 CTAs.)
+  static const bool tail_on = [] {
+    const char* e = getenv("US_FLASH_TAIL");
+    return !(e && e[0] == '0');
+  }();
+  static const int sms = [] {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+  }();
+  if (tail_on && n_seqs == 1 && !causal && max_q == Tq) {
+    const int total = q_pairs * Hq;
+    const int full = (total / sms) * sms, tail = total - full;
+    const int nb = (Tk + kBN - 1) / kBN;
+    if (full > 0 && tail > 0 && 2 * tail <= sms && nb >= 8) {
+      int parts = sms / tail;
+      if (parts > 8) parts = 8;
+      if (parts > nb / 4) parts = nb / 4;
+      const int per = (nb + parts - 1) / parts;
+      parts = (nb + per - 1) / per;
+      float *po = nullptr, *pm = nullptr;
+      if (parts >= 2 && tail * parts <= kTailCtas && tail_scratch(stream, &po, &pm)) {
+        Flash2Args a1 = a;
+        a1.kv_parts = 1;
+        a1.items_x = q_pairs;
+        a1.tail_follows = 1;
+        int rc1 = launch(dim3(full), a1);
+        if (rc1) return rc1;
+        Flash2Args a2 = a;
+        a2.kv_parts = parts;
+        a2.item0 = full;
+        a2.items_x = q_pairs;
+        a2.blocks_per_part = per;
+        a2.part_o = po;
+        a2.part_ml = pm;
+        a2.no_wait = 1;
+        rc1 = launch(dim3(tail * parts), a2);
+        if (rc1) return rc1;
+        // plain stream order: everything before it in the stream is complete and visible
+        const int rows_per_cta = 128 / (D / 8);
+        flash2_merge_kernel<<<dim3(tail, 2 * kBM / rows_per_cta), 128, 0, stream>>>(a2, parts, D);
+        US_LAUNCH_CHECK();
+        return US_OK;
+      }
+    }
   }
+  const int rc0 = launch(dim3(q_pairs, Hq, n_seqs), a);
+  if (rc0) return rc0;
 #undef US_FLASH2_LAUNCH
   return US_OK;
 }
