@@ -168,7 +168,9 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // keep partial row sums that meet in the epilogue.  Four softmax warps per scheduler instead
 // of two hide the latency of the dependent chains (exponential, pack, store) that bound the
 // one-thread-per-row form.
-template <int kD, uint32_t kEmu, int kSplit>
+// kHalfP (with kSplit == 1): P is handed to the issuing thread in two halves of 64 keys, so
+// that O += P V starts on the first half while the second half's exponentials run.
+template <int kD, uint32_t kEmu, int kSplit, bool kHalfP>
 __global__ void __launch_bounds__((8 * kSplit + 2) * 32, 1)
 flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const Flash2Args a) {
@@ -262,6 +264,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* kv_empty = bars + 3;  // [2]
   uint64_t* s_full = bars + 9;   // [2] per tile
   uint64_t* p_full = bars + 11;  // [2] per tile
+  uint64_t* p_second = bars + 5; // [2] per tile: the second half of P (kHalfP)
   uint64_t* o_full = bars + 13;  // [2] per tile
   uint32_t* tmem_slot = (uint32_t*)(bars + 15);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -276,6 +279,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc::mbar_init(&kv_empty[i], 1);
       tc::mbar_init(&s_full[i], 1);
       tc::mbar_init(&p_full[i], 128 * kSplit);
+      tc::mbar_init(&p_second[i], 128 * kSplit);
       tc::mbar_init(&o_full[i], 1);
     }
     *abort_flag = 0;
@@ -351,12 +355,16 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         tc::umma_commit(&s_full[x]);
       };
-      auto issue_pv = [&](int x, int j) {
+      auto issue_pv = [&](int x, int j) -> bool {
         const uint32_t vb = v_lo + (uint32_t)(j & 1) * (kTile >> 4);
         const uint32_t p_tmem = tmem_base + (uint32_t)x * kBN;
         const uint32_t o_tmem = tmem_base + 256 + (uint32_t)x * kD;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
+          if (kHalfP && kk == 4) {   // the second half of P
+            if (!tc::mbar_wait(&p_second[x], (uint32_t)j & 1u, abort_flag)) return false;
+            tc::tc_fence_after_sync();
+          }
           // A = P: 16 keys = 8 packed columns per instruction.  B = V: d on N (two
           // 64-wide chunks, 16 KiB apart), 16 keys = two groups of eight rows (1 KiB apart),
           // 2 KiB further per instruction.
@@ -368,6 +376,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // a tile's accumulator is waited for only after its last block: before that, the next
         // S of the tile (issued after this product, committed to s_full) says the same
         if (j == nb_t[x] - 1) tc::umma_commit(&o_full[x]);
+        return true;
       };
       bool ok = tc::mbar_wait(q_full, 0, abort_flag);
       if (ok) {
@@ -384,14 +393,14 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (j < nb_t[0]) {
           if (!tc::mbar_wait(&p_full[0], pj, abort_flag)) { ok = false; break; }
           tc::tc_fence_after_sync();
-          issue_pv(0, j);
+          if (!issue_pv(0, j)) { ok = false; break; }
           if (j + 1 < nb_t[0]) issue_qk(0, j + 1);
         }
         // tile B
         if (j < nb_t[1]) {
           if (!tc::mbar_wait(&p_full[1], pj, abort_flag)) { ok = false; break; }
           tc::tc_fence_after_sync();
-          issue_pv(1, j);
+          if (!issue_pv(1, j)) { ok = false; break; }
           if (j + 1 < nb_t[1]) issue_qk(1, j + 1);
         }
         tc::umma_commit(&kv_empty[j & 1]);
@@ -590,6 +599,27 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   #pragma unroll
         for (int c = 0; c < 4; ++c) ls[c] = pack2(0.f, 0.f);
         uint32_t pk[kCols / 2];
+        if constexpr (kHalfP && kSplit == 1) {
+          // keys 0 - 63 first: their P is stored and announced, then keys 64 - 127
+  #pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+  #pragma unroll
+            for (int c = 0; c < 2; ++c)
+              pk[16 * c + (i >> 1)] = exp_pair(v[32 * c + i], v[32 * c + i + 1], nm2,
+                                               ls[c * 2 + ((i >> 1) & 1)], false);
+          }
+          tc::tmem_st32(s_tmem, *reinterpret_cast<const uint32_t(*)[32]>(pk));
+          tc::tmem_st_wait();
+          tc::tc_fence_before_sync();
+          tc::mbar_arrive(&p_full[x]);
+  #pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+  #pragma unroll
+            for (int c = 2; c < 4; ++c)
+              pk[16 * c + (i >> 1)] = exp_pair(v[32 * c + i], v[32 * c + i + 1], nm2,
+                                               ls[(c - 2) * 2 + ((i >> 1) & 1)], false);
+          }
+        } else
         // Blocks with masked keys (-inf scores) stay on the exact path, whole warps at a time.
         if (kEmu != 0 && !__any_sync(0xffffffffu, need_mask)) {
   #pragma unroll
@@ -619,12 +649,17 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         // P (packed pairs) replaces the first half of S, which is in registers by now.
   #pragma unroll
-        for (int c = 0; c < kChunks / 2; ++c)
+        for (int c = (kHalfP && kSplit == 1) ? 1 : 0; c < kChunks / 2; ++c)
           tc::tmem_st32(s_tmem + col0 / 2 + 32 * c, *reinterpret_cast<const uint32_t(*)[32]>(pk + 32 * c));
       }
       tc::tmem_st_wait();
       tc::tc_fence_before_sync();
-      tc::mbar_arrive(&p_full[x]);
+      if (kHalfP) {
+        if (kSplit != 1) tc::mbar_arrive(&p_full[x]);
+        tc::mbar_arrive(&p_second[x]);
+      } else {
+        tc::mbar_arrive(&p_full[x]);
+      }
     }
     if (nbx > 0) {
       if (kSplit == 2) {   // the row's sum: both halves
@@ -836,20 +871,27 @@ int flash2_impl(const void* q, const void* k, const void* v, void* out, const in
   }();
   const int smem128 = (int)(12 * (size_t)kHalf + kTail);
   const int smem64 = (int)(6 * (size_t)kHalf + kTail);
-#define US_FLASH2_LAUNCH(DD, MASK, SP)                                                          \
+#define US_FLASH2_LAUNCH4(DD, MASK, SP, HP)                                                        \
   do {                                                                                          \
     static bool configured = false;                                                             \
     if (!configured) {                                                                          \
-      US_CUDA_CHECK(cudaFuncSetAttribute(flash2_fwd_kernel<DD, MASK, SP>,                       \
+      US_CUDA_CHECK(cudaFuncSetAttribute(flash2_fwd_kernel<DD, MASK, SP, HP>,                   \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,           \
                                          DD == 128 ? smem128 : smem64));                        \
       configured = true;                                                                        \
     }                                                                                           \
-    US_CUDA_CHECK(us::launch_pdl(flash2_fwd_kernel<DD, MASK, SP>, grid,                         \
+    US_CUDA_CHECK(us::launch_pdl(flash2_fwd_kernel<DD, MASK, SP, HP>, grid,                     \
                                  dim3((8 * SP + 2) * 32), smem, stream, tmQ, tmK, tmV, aa));    \
   } while (0)
+#define US_FLASH2_LAUNCH(DD, MASK, SP) US_FLASH2_LAUNCH4(DD, MASK, SP, false)
+  static const bool half_p = [] {
+    const char* e = getenv("US_FLASH_PHALF");
+    return e && e[0] == '1';
+  }();
   auto launch = [&](dim3 grid, const Flash2Args& aa) -> int {
-    if (D == 128 && split == 2) {
+    if (D == 128 && split == 1 && emu == 0 && half_p) {
+      US_FLASH2_LAUNCH4(128, 0x00u, 1, true);
+    } else if (D == 128 && split == 2) {
       if (emu == 0) US_FLASH2_LAUNCH(128, 0x00u, 2);
       else if (emu == 2) US_FLASH2_LAUNCH(128, 0x21u, 2);
       else if (emu == 3) US_FLASH2_LAUNCH(128, 0x29u, 2);
@@ -926,6 +968,7 @@ int flash2_impl(const void* q, const void* k, const void* v, void* out, const in
   const int rc0 = launch(dim3(q_pairs, Hq, n_seqs), a);
   if (rc0) return rc0;
 #undef US_FLASH2_LAUNCH
+#undef US_FLASH2_LAUNCH4
   return US_OK;
 }
 
