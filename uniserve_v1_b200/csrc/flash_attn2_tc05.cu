@@ -125,17 +125,24 @@ __device__ __forceinline__ void ex2_poly2(float t0, float t1, float& p0, float& 
 // product make the issue the limit.  The high words are constants of the layout and the low
 // words (start address in 16-byte units) advance by compile-time offsets, so a product costs
 // one 32-bit add per operand.
+//
+// The whole issuing warp runs the loop and one elected lane executes each tcgen05 instruction:
+// addresses, descriptors and loop control are then the same in all lanes, which lets the
+// compiler keep them in the uniform datapath where the instruction takes its operands from
+// (a single lane inside a divergent branch computes them in vector registers and moves every
+// operand of every product across).
 __device__ __forceinline__ void umma_f16_words(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi,
                                                uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
                                                uint32_t accumulate) {
   asm volatile(
       "{\n"
-      ".reg .pred p;\n"
+      ".reg .pred p, q;\n"
       ".reg .b64 da, db;\n"
       "mov.b64 da, {%1, %2};\n"
       "mov.b64 db, {%3, %4};\n"
       "setp.ne.b32 p, %6, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n"
+      "elect.sync _|q, 0xffffffff;\n"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n"
       "}\n" ::"r"(tmem_d),
       "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
@@ -145,13 +152,24 @@ __device__ __forceinline__ void umma_f16_ts_words(uint32_t tmem_d, uint32_t tmem
                                                   uint32_t accumulate) {
   asm volatile(
       "{\n"
-      ".reg .pred p;\n"
+      ".reg .pred p, q;\n"
       ".reg .b64 db;\n"
       "mov.b64 db, {%2, %3};\n"
       "setp.ne.b32 p, %5, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "elect.sync _|q, 0xffffffff;\n"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
       "}\n" ::"r"(tmem_d),
       "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// tcgen05.commit by one elected lane of a converged warp.
+__device__ __forceinline__ void umma_commit_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n"
+      ".reg .pred q;\n"
+      "elect.sync _|q, 0xffffffff;\n"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "}\n" ::"r"(tc::smem_u32(bar))
       : "memory");
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -335,7 +353,11 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
     }
   } else if (warp == kMmaWarp) {
-    if (lane == 0) {
+    {   // all 32 lanes, converged; single lanes are elected per instruction
+      // every lane waits; the vote makes the outcome (and the control flow) the same in all
+      auto warp_wait = [&](uint64_t* bar, uint32_t parity, volatile uint32_t* abort) -> bool {
+        return __all_sync(0xffffffffu, tc::mbar_wait(bar, parity, abort));
+      };
       constexpr uint32_t kIdescQK = tc::make_idesc(kBM, kBN, tc::kFmtBF16, tc::kFmtBF16, 0, 0);
       constexpr uint32_t kIdescPV = tc::make_idesc(kBM, kD, tc::kFmtBF16, tc::kFmtBF16, 0, 1);
       // descriptor words of the operands: Q tiles and K stages K-major, V stages MN-major
@@ -353,7 +375,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           const uint32_t off = (uint32_t)(kk >> 2) * (kHalf >> 4) + 2u * (uint32_t)(kk & 3);
           umma_f16_words(s_tmem, qa + off, km_hi, kb + off, km_hi, kIdescQK, kk != 0);
         }
-        tc::umma_commit(&s_full[x]);
+        umma_commit_elect(&s_full[x]);
       };
       auto issue_pv = [&](int x, int j) -> bool {
         const uint32_t vb = v_lo + (uint32_t)(j & 1) * (kTile >> 4);
@@ -362,7 +384,7 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           if (kHalfP && kk == 4) {   // the second half of P
-            if (!tc::mbar_wait(&p_second[x], (uint32_t)j & 1u, abort_flag)) return false;
+            if (!warp_wait(&p_second[x], (uint32_t)j & 1u, abort_flag)) return false;
             tc::tc_fence_after_sync();
           }
           // A = P: 16 keys = 8 packed columns per instruction.  B = V: d on N (two
@@ -375,37 +397,37 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         // a tile's accumulator is waited for only after its last block: before that, the next
         // S of the tile (issued after this product, committed to s_full) says the same
-        if (j == nb_t[x] - 1) tc::umma_commit(&o_full[x]);
+        if (j == nb_t[x] - 1) umma_commit_elect(&o_full[x]);
         return true;
       };
-      bool ok = tc::mbar_wait(q_full, 0, abort_flag);
+      bool ok = warp_wait(q_full, 0, abort_flag);
       if (ok) {
         tc::tc_fence_after_sync();
         if (nb_t[0] > 0) issue_qk(0, 0);
         if (nb_t[1] > 0) issue_qk(1, 0);
-        tc::umma_commit(&kv_empty[1]);   // K stage 0 may be refilled (with K(2), by block 1's loads)
+        umma_commit_elect(&kv_empty[1]);   // K stage 0 may be refilled (with K(2), by block 1's loads)
       }
       for (int j = 0; ok && j < nb; ++j) {
         const uint32_t pj = (uint32_t)j & 1u;
         // V(j) and K(j + 1) are there
-        if (!tc::mbar_wait(&kv_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (!warp_wait(&kv_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
         // tile A: O_A += P_A V_j, then S_A of the next block
         if (j < nb_t[0]) {
-          if (!tc::mbar_wait(&p_full[0], pj, abort_flag)) { ok = false; break; }
+          if (!warp_wait(&p_full[0], pj, abort_flag)) { ok = false; break; }
           tc::tc_fence_after_sync();
           if (!issue_pv(0, j)) { ok = false; break; }
           if (j + 1 < nb_t[0]) issue_qk(0, j + 1);
         }
         // tile B
         if (j < nb_t[1]) {
-          if (!tc::mbar_wait(&p_full[1], pj, abort_flag)) { ok = false; break; }
+          if (!warp_wait(&p_full[1], pj, abort_flag)) { ok = false; break; }
           tc::tc_fence_after_sync();
           if (!issue_pv(1, j)) { ok = false; break; }
           if (j + 1 < nb_t[1]) issue_qk(1, j + 1);
         }
-        tc::umma_commit(&kv_empty[j & 1]);
+        umma_commit_elect(&kv_empty[j & 1]);
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         us_dev_fail(a.status, US_DEV_TIMEOUT_FULL);
         *abort_flag = 1;
       }
