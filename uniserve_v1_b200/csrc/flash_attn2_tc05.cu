@@ -24,6 +24,7 @@
 // The reference runs FlashAttention-4 here (crates/ops/kernels/dense_attention/fa4,
 // reference project path); the two-tile ping-pong and P in tensor memory follow the
 // same idea, the code is independent.
+#include <mutex>
 #include "include/us_common.cuh"
 #include "include/us_tc05.cuh"
 #include "include/us_tmap.h"
@@ -809,6 +810,8 @@ constexpr int kTailCtas = 160;
 bool tail_scratch(cudaStream_t stream, float** part_o, float** part_ml) {
   static TailScratch table[kTailStreams] = {};
   static int used = 0;
+  static std::mutex lock;                  // launches may come from several host threads
+  std::lock_guard<std::mutex> guard(lock);
   for (int i = 0; i < used; ++i)
     if (table[i].stream == stream) {
       *part_o = table[i].part_o;
