@@ -428,6 +428,35 @@ def test_route_sort_gather_and_unpermute_norm_equal_the_separate_kernels(T, E, k
     assert (ids2[int(live):] == -1).all() and torch.equal(ids2[:int(live)], ids0[:int(live)])
 
 
+@pytest.mark.parametrize("Hq,Hkv,lens", [
+    (32, 4, [1, 17, 300, 64, 511]),                 # 20 pairs of 1 - 4 tiles: fewer tiles than CTAs
+    (16, 16, [1100] * 24 + [0, 5]),                 # 9 tiles per pair, a sequence without keys
+    (16, 1, [4000, 3, 129, 2050]),                  # pairs cut into many ranges
+    (8, 8, [130] * 200),                            # 1600 pairs of 2 tiles: several pairs per range
+])
+def test_paged_decode_attention_persistent_kernel(Hq, Hkv, lens):
+    """One CTA per SM over the tile list of the whole launch: pairs inside a range are written
+    directly, pairs cut by a range boundary meet through their arrival counter.  Run twice on
+    the same scratch (the counters put themselves back)."""
+    B, page, D = len(lens), 16, 128
+    per = (max(lens) + page - 1) // page + 1
+    pages = B * per + 1
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    q = rnd(B, Hq, D)
+    kc, vc = rnd(pages, page, Hkv, D, seed=1), rnd(pages, page, Hkv, D, seed=2)
+    pt = (torch.randperm(pages - 1, device=DEV)[:B * per].view(B, per) + 1).to(torch.int32)
+    ref = R.paged_decode_attention(q, kc, vc, pt, sl, 1 / math.sqrt(D))
+    scratch, counters = F.decode_persist_scratch(B, Hkv, DEV)
+    for _ in range(2):
+        out = F.paged_decode_attention(q, kc, vc, pt, sl, 1 / math.sqrt(D), F.PERSIST_SPLITS,
+                                       scratch=scratch, counters=counters)
+        live = sl > 0
+        close(out[live], ref[live], 2e-2, 2e-2)
+        assert float(out[~live].float().abs().max()) == 0.0 if bool((~live).any()) else True
+        assert int(counters.abs().sum()) == 0
+    assert N.read_status() == 0
+
+
 @pytest.mark.parametrize("Hq,Hkv,splits", [(32, 4, 4), (16, 1, 3), (8, 1, 8)])
 def test_paged_decode_attention_merges_its_splits_in_the_kernel(Hq, Hkv, splits):
     B, page, pages, D = 5, 16, 200, 128

@@ -164,6 +164,8 @@ class CausalLmRunner:
         d = blk.d
         max_len = self.max_model_len
         splits = F.decode_splits(B, self.model.Hkv, max_len) if self.device.type == "cuda" else 1
+        if self._persist_attention(B):
+            splits = F.PERSIST_SPLITS
         scratch, counters = self._attn_scratch(B, splits)
         meta = AttnMeta(kind="decode", slots=d["slots"], page_table=d["page_table"],
                         seq_lens=d["seq_lens"], splits=splits, live=d["live"], scratch=scratch,
@@ -195,10 +197,33 @@ class CausalLmRunner:
         d["sample_pos"].add_(1)
         return logits, sampled
 
+    def _persist_attention(self, B: int) -> bool:
+        """Whether this runner's decode steps use the persistent attention kernel."""
+        m = self.model
+        if self.device.type != "cuda":
+            return False
+        kc = next((k for k, _ in (self.kv_caches or []) if k is not None), None)
+        if kc is None or kc.dtype != torch.bfloat16:
+            return False
+        # with fewer (sequence, kv head) pairs than SMs a CTA would stream only a few tiles and
+        # the kernel's fixed cost (tile list, merge of the cut pairs) outweighs its ring: the
+        # split kernel stays (measured at 64 pairs: 24.6 us split four ways, 28.7 us persistent)
+        if B * m.Hkv < F.PERSIST_MIN_PAIRS:
+            return False
+        return F.decode_persist_ok(B, m.Hq, m.Hkv, m.D, kc.shape[1],
+                                   int(getattr(m.cfg, "sliding_window", 0) or 0))
+
     def _attn_scratch(self, B: int, splits: int):
         """Split-KV partials and arrival counters of the decode attention, one pair per
         (bucket, splits), shared by every layer (allocated outside any capture)."""
         m = self.model
+        if self.device.type == "cuda" and splits == F.PERSIST_SPLITS:
+            key = (B, splits)
+            got = self._scratch.get(key)
+            if got is None:
+                got = F.decode_persist_scratch(B, m.Hkv, self.device)
+                self._scratch[key] = got
+            return got
         if self.device.type != "cuda" or splits <= 1 or m.D != 128:
             return None, None
         key = (B, splits)

@@ -166,6 +166,29 @@ def decode_scratch(B: int, Hq: int, Hkv: int, D: int, splits: int, device):
             torch.zeros(B * Hkv, dtype=torch.int32, device=device))
 
 
+# US_DECODE_PERSIST=0: bf16 pages go to the per-(sequence, kv head) kernel again (A/B switch)
+DECODE_PERSIST = _os.environ.get("US_DECODE_PERSIST", "1") == "1"
+PERSIST_SPLITS = 0      # ``splits`` value that selects the persistent kernel
+PERSIST_MIN_PAIRS = int(_os.environ.get("US_DECODE_PERSIST_PAIRS", "148"))   # runner's threshold
+
+
+def decode_persist_ok(B: int, Hq: int, Hkv: int, D: int, page_size: int, window: int,
+                      fp8: bool = False) -> bool:
+    """Whether the persistent decode-attention kernel serves this case (bf16 pages, head width
+    128, pages dividing 128, no sliding window, at most 1024 sequences)."""
+    return (DECODE_PERSIST and not DECODE_SIMT and not fp8 and D == 128 and 128 % page_size == 0
+            and page_size >= 8 and Hq // Hkv <= 16 and not window and B <= 1024)
+
+
+def decode_persist_scratch(B: int, Hkv: int, device):
+    """(partial-output scratch, arrival counters) of the persistent decode-attention kernel:
+    two slots per CTA, one counter per (sequence, kv head).  The counters start at zero and
+    every call leaves them zero; calls that share the pair must be ordered on the device."""
+    nbytes = N.kernels().us_paged_decode_persist_scratch_bytes()
+    return (torch.empty(nbytes, dtype=torch.uint8, device=device),
+            torch.zeros(B * Hkv, dtype=torch.int32, device=device))
+
+
 def kv_write_scaled(k, v, slots, kcache, vcache, k_scale, v_scale):
     """Rows k, v [T, Hkv, D] (bf16, row-strided views allowed) into E4M3 pages (uint8
     [pages, page, Hkv, D]) with one FP32 scale per page and plane, derived by the write."""
@@ -224,6 +247,7 @@ def paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, split
         nbytes = N.kernels().us_paged_decode_scratch_bytes(B, Hq, D, splits)
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     if k_scale is not None:
+        splits = max(1, splits)
         if not (D == 128 and 128 % page_size == 0 and Hq // Hkv <= 16):
             raise ValueError("FP8 pages are served for head width 128, pages dividing 128 and "
                              "at most 16 query heads per key head")
@@ -232,6 +256,16 @@ def paged_decode_attention(q, kcache, vcache, page_table, seq_lens, scale, split
                N.ptr(scratch), N.ptr(counters) if counters is not None else None, B, Hq, Hkv, D,
                pages, page_table.shape[1], page_size, splits, window, scale, ldq, ldo, N.stream(),
                launches=1 if (counters is not None or splits == 1) else 2)
+        return out
+    if splits == PERSIST_SPLITS:
+        # one CTA per SM over the launch's tile list (scratch / counters of decode_persist_scratch)
+        if not decode_persist_ok(B, Hq, Hkv, D, page_size, window):
+            raise ValueError("the persistent decode-attention kernel does not serve this case")
+        if scratch is None or counters is None:
+            scratch, counters = decode_persist_scratch(B, Hkv, q.device)
+        N.call("us_paged_decode_attention_persist", N.ptr(q), N.ptr(kcache), N.ptr(vcache),
+               N.ptr(page_table), N.ptr(seq_lens), N.ptr(out), N.ptr(scratch), N.ptr(counters),
+               B, Hq, Hkv, D, pages, page_table.shape[1], page_size, scale, ldq, ldo, N.stream())
         return out
     if D == 128 and 128 % page_size == 0 and Hq // Hkv <= 16 and not DECODE_SIMT:
         # keys-on-M tcgen05 kernel

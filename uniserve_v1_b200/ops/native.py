@@ -57,6 +57,8 @@ _SIGNATURES = {
     "us_qk_norm_rope3": (I, [P, P, P, P, P, P, I, I, I, I, I, L, L, F, P]),
     "us_qk_norm_rope3_table": (I, [P, P, P, P, P, I, I, I, I, I, L, L, F, P]),
     "us_paged_decode_scratch_bytes": (L, [I, I, I, I]),
+    "us_paged_decode_persist_scratch_bytes": (L, []),
+    "us_paged_decode_attention_persist": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, L, L, P]),
     "us_paged_decode_attention": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, L, L, P]),
     "us_paged_decode_attention_tc": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, L, L, P]),
     "us_paged_decode_attention_tc_merged": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F,

@@ -73,6 +73,8 @@ def main():
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="decode: page type")
+    ap.add_argument("--persist", action="store_true",
+                    help="decode: the persistent kernel (bf16 pages)")
     a = ap.parse_args()
     tbs, tfl, tag = peaks()
     dev, bf = "cuda", torch.bfloat16
@@ -375,6 +377,9 @@ def main():
         sl = torch.full((B,), a.ctx, dtype=torch.int32, device=dev)
         splits = a.splits or F.decode_splits(B, Hkv, a.ctx)
         scratch, counters = F.decode_scratch(B, Hq, Hkv, D, splits, dev)
+        if a.persist and a.kv == "bf16":      # one CTA per SM over the launch's tile list
+            splits = F.PERSIST_SPLITS
+            scratch, counters = F.decode_persist_scratch(B, Hkv, dev)
         ks = vs = None
         esz = 2.0
         if a.kv == "fp8":            # E4M3 pages with one scale per page and plane
@@ -389,7 +394,7 @@ def main():
                     a.iters)
         byts = 2.0 * B * a.ctx * Hkv * D * esz
         out["kv"] = a.kv
-        out.update(batch=B, ctx=a.ctx, splits=splits, ms=ms, tbs=byts / ms / 1e9,
+        out.update(batch=B, ctx=a.ctx, splits=splits, persistent=bool(a.persist and a.kv == "bf16"), ms=ms, tbs=byts / ms / 1e9,
                    frac_memory=byts / ms / 1e9 / tbs)
     out["roofline"] = tag
     print(json.dumps(out))
