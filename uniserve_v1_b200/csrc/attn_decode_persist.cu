@@ -21,7 +21,8 @@
 // output and its log-sum-exp in the CTA's slot (0: the CTA's first segment, 1: a later
 // one, which then is its last) and adds one arrival to the pair's counter; the CTA that
 // brings the count to the number of CTAs the pair spans merges the slots (their indices
-// follow from the partition) and puts the counter back to zero.  Pairs inside one range
+// follow from the partition) and puts the counter back to zero; a CTA looks at the counts
+// its arrivals returned, and merges, after its last tile.  Pairs inside one range
 // are written directly.  The Q operand of the next segment is staged while the current one
 // runs (two buffers).  Every wait is bounded.
 //
@@ -368,6 +369,8 @@ paged_decode_persist_kernel(const __grid_constant__ CUtensorMap tmK,
       stage_q(nb, nhk, 1);
     }
     bool ok = true;
+    // pairs cut by this range (slot 0: its first segment, slot 1: its last) whose merge is due
+    int pb0 = -1, ph0 = 0, pt0 = 0, old0 = 0, pb1 = -1, ph1 = 0, pt1 = 0, old1 = 0;
     while (ok && g < g1) {
       const int n_seg = min(tiles - t0, g1 - g);
       if (seg >= 1 && g + n_seg < g1) {   // the segment after this one: its buffer is free now
@@ -483,51 +486,18 @@ paged_decode_persist_kernel(const __grid_constant__ CUtensorMap tmK,
         }
       }
       if (!whole) {
-        // arrival at the pair's counter; the last of the CTAs the pair spans merges
-        const int pair_begin = Hkv * pre[b] + hk * tiles, pair_last = pair_begin + tiles - 1;
-        const int c_first = cta_of(pair_begin, total, n_cta), c_last = cta_of(pair_last, total, n_cta);
+        // arrival at the pair's counter.  The count it returns is looked at only after the
+        // CTA's last tile (an atomic does not stall its thread until the value is used), so
+        // the softmax threads go on with the next segment at once.
         __threadfence();
         asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (tid == 0) {
-          int* cnt = a.counters + b * Hkv + hk;
-          const int old = atomicAdd(cnt, 1);
-          const int last = old == c_last - c_first;
-          if (last) *cnt = 0;
-          *last_s = last;
+        if (which == 0) {       // scalars, not an indexed array: the count stays in a register
+          if (tid == 0) old0 = atomicAdd(a.counters + b * Hkv + hk, 1);
+          pb0 = b; ph0 = hk; pt0 = tiles;
+        } else {
+          if (tid == 0) old1 = atomicAdd(a.counters + b * Hkv + hk, 1);
+          pb1 = b; ph1 = hk; pt1 = tiles;
         }
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (*last_s) {
-          __threadfence();
-          float mx[G], acc[G], den[G];
-#pragma unroll
-          for (int gi = 0; gi < G; ++gi) {
-            mx[gi] = -INFINITY;
-            acc[gi] = 0.f;
-            den[gi] = 0.f;
-          }
-          for (int c = c_first; c <= c_last; ++c) {
-            const int wc = range_start(c, total, n_cta) >= pair_begin ? 0 : 1;
-            const long long sl = ((long long)c * 2 + wc) * kNPad;
-#pragma unroll
-            for (int gi = 0; gi < G; ++gi) mx[gi] = fmaxf(mx[gi], __ldcg(a.part_lse + sl + gi));
-          }
-          for (int c = c_first; c <= c_last; ++c) {
-            const int wc = range_start(c, total, n_cta) >= pair_begin ? 0 : 1;
-            const long long sl = ((long long)c * 2 + wc) * kNPad;
-#pragma unroll
-            for (int gi = 0; gi < G; ++gi) {
-              const float l = __ldcg(a.part_lse + sl + gi);
-              const float wgt = (l == -INFINITY) ? 0.f : __expf(l - mx[gi]);
-              den[gi] += wgt;
-              acc[gi] += wgt * __ldcg(a.part_o + (sl + gi) * kD + tid);
-            }
-          }
-#pragma unroll
-          for (int gi = 0; gi < G; ++gi)
-            a.out[(long long)b * a.ldo + (long long)(hk * G + gi) * kD + tid] =
-                us::f2bf(den[gi] > 0.f ? acc[gi] / den[gi] : 0.f);
-        }
-        asm volatile("bar.sync 2, 128;" ::: "memory");   // last_s may be rewritten
       }
       g += n_seg;
       ++seg;
@@ -535,6 +505,53 @@ paged_decode_persist_kernel(const __grid_constant__ CUtensorMap tmK,
       if (g < g1) next_pair(pre, B, Hkv, b, hk, tiles);
     }
     if (!ok) us_dev_fail(a.status, US_DEV_TIMEOUT_ACC);
+    // the CTA that arrived last at a pair's counter merges the slots of the CTAs the pair spans
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int pb_ = k == 0 ? pb0 : pb1, phk = k == 0 ? ph0 : ph1, ptiles = k == 0 ? pt0 : pt1;
+      const int pold = k == 0 ? old0 : old1;
+      if (pb_ < 0) continue;
+      const int pair_begin = Hkv * pre[pb_] + phk * ptiles, pair_last = pair_begin + ptiles - 1;
+      const int c_first = cta_of(pair_begin, total, n_cta), c_last = cta_of(pair_last, total, n_cta);
+      if (tid == 0) {
+        const int last = pold == c_last - c_first;
+        if (last) a.counters[pb_ * Hkv + phk] = 0;
+        *last_s = last;
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (*last_s) {
+        __threadfence();
+        float mx[G], acc[G], den[G];
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+          mx[gi] = -INFINITY;
+          acc[gi] = 0.f;
+          den[gi] = 0.f;
+        }
+        for (int c = c_first; c <= c_last; ++c) {
+          const int wc = range_start(c, total, n_cta) >= pair_begin ? 0 : 1;
+          const long long sl = ((long long)c * 2 + wc) * kNPad;
+#pragma unroll
+          for (int gi = 0; gi < G; ++gi) mx[gi] = fmaxf(mx[gi], __ldcg(a.part_lse + sl + gi));
+        }
+        for (int c = c_first; c <= c_last; ++c) {
+          const int wc = range_start(c, total, n_cta) >= pair_begin ? 0 : 1;
+          const long long sl = ((long long)c * 2 + wc) * kNPad;
+#pragma unroll
+          for (int gi = 0; gi < G; ++gi) {
+            const float l = __ldcg(a.part_lse + sl + gi);
+            const float wgt = (l == -INFINITY) ? 0.f : __expf(l - mx[gi]);
+            den[gi] += wgt;
+            acc[gi] += wgt * __ldcg(a.part_o + (sl + gi) * kD + tid);
+          }
+        }
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi)
+          a.out[(long long)pb_ * a.ldo + (long long)(phk * G + gi) * kD + tid] =
+              us::f2bf(den[gi] > 0.f ? acc[gi] / den[gi] : 0.f);
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");   // last_s is rewritten for the next pair
+    }
   }
   tc::tc_fence_before_sync();
   __syncthreads();
