@@ -205,9 +205,10 @@ class CausalLmRunner:
         kc = next((k for k, _ in (self.kv_caches or []) if k is not None), None)
         if kc is None or kc.dtype != torch.bfloat16:
             return False
-        # with fewer (sequence, kv head) pairs than SMs a CTA would stream only a few tiles and
-        # the kernel's fixed cost (tile list, merge of the cut pairs) outweighs its ring: the
-        # split kernel stays (measured at 64 pairs: 24.6 us split four ways, 28.7 us persistent)
+        # with few (sequence, kv head) pairs a CTA would stream only a few tiles and the
+        # kernel's fixed cost (tile list, merge of the cut pairs) outweighs its ring: the split
+        # kernel stays (measured at 1100 keys: 64 pairs 24.6 us split four ways against 27.6 us
+        # persistent, 128 pairs 35.8 us either way, 512 pairs 84.9 against 80.0 us)
         if B * m.Hkv < F.PERSIST_MIN_PAIRS:
             return False
         return F.decode_persist_ok(B, m.Hq, m.Hkv, m.D, kc.shape[1],
