@@ -208,7 +208,8 @@ class CausalLmRunner:
         # with few (sequence, kv head) pairs a CTA would stream only a few tiles and the
         # kernel's fixed cost (tile list, merge of the cut pairs) outweighs its ring: the split
         # kernel stays (measured at 1100 keys: 64 pairs 24.6 us split four ways against 27.6 us
-        # persistent, 128 pairs 35.8 us either way, 512 pairs 84.9 against 80.0 us)
+        # persistent, 128 pairs 35.8 us either way alone but a 2-GPU decode step 10.56 against
+        # 10.85 ms, 256 pairs a 1-GPU step 14.65 against 14.29 ms, 512 pairs 84.9 against 80.0 us)
         if B * m.Hkv < F.PERSIST_MIN_PAIRS:
             return False
         return F.decode_persist_ok(B, m.Hq, m.Hkv, m.D, kc.shape[1],

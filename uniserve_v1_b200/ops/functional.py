@@ -169,7 +169,7 @@ def decode_scratch(B: int, Hq: int, Hkv: int, D: int, splits: int, device):
 # US_DECODE_PERSIST=0: bf16 pages go to the per-(sequence, kv head) kernel again (A/B switch)
 DECODE_PERSIST = _os.environ.get("US_DECODE_PERSIST", "1") == "1"
 PERSIST_SPLITS = 0      # ``splits`` value that selects the persistent kernel
-PERSIST_MIN_PAIRS = int(_os.environ.get("US_DECODE_PERSIST_PAIRS", "128"))   # runner's threshold
+PERSIST_MIN_PAIRS = int(_os.environ.get("US_DECODE_PERSIST_PAIRS", "148"))   # runner's threshold
 
 
 def decode_persist_ok(B: int, Hq: int, Hkv: int, D: int, page_size: int, window: int,
