@@ -281,6 +281,72 @@ def test_h3_fused_ulysses_matches_all_to_all_and_single_gpu():
     torch.testing.assert_close(vb, st.video.cpu(), atol=3e-2, rtol=3e-2)
 
 
+def _push_tail_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import ctypes
+    import math
+    from uniserve_v1_b200.ops import native as N
+    from uniserve_v1_b200.ops.flash import flash_attn_varlen
+    from uniserve_v1_b200.parallel.context import ParallelContext
+    from uniserve_v1_b200.parallel import ulysses as U
+    ctx = ParallelContext.from_world(ulysses=world)
+    T, hl, D = 3072, 13, 128          # 12 query pairs x 13 heads = 156 items: one wave and 8 more
+    fu = U.FusedUlysses(ctx, dev, T, hl, D)
+    ro, inner = T // world, world * hl * D
+
+    def qkv_of(r):
+        g = torch.Generator(device="cpu").manual_seed(50 + r)
+        return [(torch.randn(T, hl, D, generator=g) * 0.5).to(torch.bfloat16).to(dev) for _ in range(3)]
+
+    qr, kr, vr = qkv_of(rank)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    scale = 1 / math.sqrt(D)
+    ok = True
+    for it in range(2):
+        fu.fc.barrier(U.SITE_B1)       # nobody still reads the buffers of the round before
+        N.call("us_flash_attn_push", N.ptr(qr), N.ptr(kr), N.ptr(vr), N.ptr(cu), N.ptr(cu), T, T,
+               hl, hl, qr.stride(0), kr.stride(0), vr.stride(0), scale, fu._ptrs(U.SITE_ATT), world,
+               ro, rank * hl * D, inner, N.stream())
+        fu.fc.barrier(U.SITE_B2)
+        got = fu.fc.site_tensor(U.SITE_ATT, ro, inner).clone()
+        torch.cuda.synchronize()
+        for r in range(world):          # every rank's heads arrived in its column block
+            q2, k2, v2 = qkv_of(r)
+            ref = flash_attn_varlen(q2, k2, v2, cu, cu, T, T, scale, False)
+            mine = ref[rank * ro:(rank + 1) * ro].reshape(ro, hl * D)
+            ok &= bool(torch.equal(got[:, r * hl * D:(r + 1) * hl * D], mine))
+    torch.cuda.synchronize()
+    q.put((rank, ok, N.read_status()))
+    dist.barrier()
+    fu.close()
+    dist.destroy_process_group()
+
+
+def test_flash_push_with_split_last_wave_between_real_peers():
+    """The sequence-parallel return from the attention epilogue on a shape whose last partial
+    wave of (pair, head) items is split over the keys: those rows reach their owners from the
+    merge kernel.  Every rank checks the column block of every rank bit for bit against the
+    plain kernel."""
+    _need(2)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_push_tail_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=600) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, ok, status in res:
+        assert ok and status == 0, (rank, ok, status)
+
+
 def _ep_worker(rank, world, port, q, afd):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
