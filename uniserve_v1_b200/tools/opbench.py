@@ -71,6 +71,7 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--head-dim", type=int, default=128, help="flash: 128 or 64")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="decode: page type")
     ap.add_argument("--persist", action="store_true",
@@ -82,14 +83,14 @@ def main():
     rnd = lambda *s: (torch.randn(*s, generator=g, device=dev) * 0.5).to(bf)
     out = {"op": a.op}
     if a.op == "flash":
-        T, H, D = a.rows, a.heads, 128
+        T, H, D = a.rows, a.heads, a.head_dim
         q, k, v = rnd(T, H, D), rnd(T, H, D), rnd(T, H, D)
         cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
         o = torch.empty_like(q)
         ms = timeit(lambda: flash_attn_varlen(q, k, v, cu, cu, T, T, 1 / math.sqrt(D), a.causal,
                                               out=o), a.iters)
         flops = 4.0 * T * T * D * H * (0.5 if a.causal else 1.0)
-        out.update(rows=T, heads=H, ms=ms, tflops=flops / ms / 1e9, frac=flops / ms / 1e9 / tfl)
+        out.update(rows=T, heads=H, head_dim=D, ms=ms, tflops=flops / ms / 1e9, frac=flops / ms / 1e9 / tfl)
     elif a.op == "prefill":
         # One prefill chunk through the engine at the real widths: `--batch` prompts of `--ctx`
         # tokens (one chunk of batch x ctx rows), `--layers` layers.  ms_per_layer is what a
