@@ -205,7 +205,9 @@ flash2_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   }
   constexpr int kHalves = kD / 64;          // 64-column (128-byte) slabs per tile
   constexpr int kTile = kHalves * kHalf;    // 32 KiB (head 128) or 16 KiB (head 64)
-  int q_pair = blockIdx.x, h = blockIdx.y, part = 0;
+  // causal: the last query pairs walk the most key blocks; they start first
+  int q_pair = a.causal ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+  int h = blockIdx.y, part = 0;
   const int seq = blockIdx.z;
   if (a.kv_parts > 0) {
     const int item = a.item0 + (int)blockIdx.x / a.kv_parts;
