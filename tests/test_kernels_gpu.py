@@ -1072,3 +1072,30 @@ def test_weights_keeper_maps_device_weights_into_another_process(tmp_path):
         os.close(r)
         if proc.poll() is None:
             proc.terminate()
+
+
+def test_profile_timeline_collector_sees_the_library_kernels(tmp_path):
+    """A session with the ``timeline`` collector holds one record per kernel the process ran
+    while it was open - also the kernels this package launches through its own library, which
+    never pass through PyTorch - beside the fence probes of the step."""
+    from uniserve_v1_b200.engine.profiling import StepProfiler
+    from uniserve_v1_b200.tools import profile as P
+    x, w = rnd(64, 1024), rnd(512, 1024, scale=0.05)
+    F.linear(x, w)                                   # library loaded, kernels configured
+    torch.cuda.synchronize()
+    prof = StepProfiler(DEV)
+    path = str(tmp_path / "timeline.sqlite")
+    prof.open(path, {"case": "gpu"}, collectors=["fence_timeline", "timeline"])
+    with prof.step("decode", 0):
+        y = F.linear(x, w)
+        big = F.linear(rnd(512, 1024), w)
+    torch.cuda.synchronize()
+    prof.close()
+    s = P.load(path)
+    kernels = [k for k in s["kernels"] if k[2] == "kernel"]
+    names = " ".join(k[1] for k in kernels)
+    assert "gemm_wx" in names or "linear_decode" in names, names[:400]
+    assert all(k[5] > 0 for k in kernels)
+    assert len(P.device_ranges(s["probes"])) == 1
+    assert P.summary([s])["kernels"]
+    assert y.shape == (64, 512) and big.shape == (512, 512)

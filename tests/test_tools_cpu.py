@@ -740,3 +740,52 @@ def test_weights_keeper_serves_weights_to_restarting_engines(tmp_path):
         os.close(r)
         if proc.poll() is None:
             proc.terminate()
+
+
+def test_profile_session_collectors_and_admin_route(tmp_path):
+    """A session with the ``timeline`` collector records the activity of the process beside
+    the fence probes (on CPU ranks: host operator records), closes itself after the asked
+    number of steps, and is driven over HTTP by ``/admin/profile``; sampling collectors are
+    refused by name."""
+    import pytest
+    from fastapi.testclient import TestClient
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.profiling import StepProfiler, start_session
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.server.app import create_app
+    from uniserve_v1_b200.tools import profile as P
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    eng = LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128, use_graphs=False)
+    path = str(tmp_path / "tl.sqlite")
+    st = start_session(eng, ["fence_timeline", "timeline"], path, steps=3)
+    assert st["open"] and st["collectors"] == ["fence_timeline", "timeline"]
+    eng.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    assert eng.profiler.session is None                  # closed itself after three steps
+    s = P.load(path)
+    assert len(s["spans"]) == 3 and len(s["kernels"]) > 0
+    assert s["meta"]["collectors"] == "fence_timeline,timeline"
+    summ = P.summary([s])
+    assert summ["kernels"] and all(v["count"] >= 1 for v in summ["kernels"].values())
+    tr = P.to_trace([s])
+    assert any(e["tid"].startswith("host_ops:") for e in tr["traceEvents"])
+    with pytest.raises(ValueError, match="sampling"):
+        StepProfiler("cpu").open(str(tmp_path / "x.sqlite"), collectors=["pc_sampling"])
+    with pytest.raises(ValueError, match="unknown collector"):
+        StepProfiler("cpu").open(str(tmp_path / "y.sqlite"), collectors=["everything"])
+
+    from uniserve_v1_b200.server.tokenizer import ByteTokenizer
+    app = create_app(engine=eng, tokenizer=ByteTokenizer(256), served_model_name="tiny")
+    with TestClient(app) as c:
+        assert c.get("/admin/profile").json()["open"] is False
+        out = c.post("/admin/profile", json={"collectors": ["fence_timeline"], "steps": 100,
+                                             "output": str(tmp_path)}).json()
+        assert out["open"] and out["path"].endswith("rank0.sqlite")
+        r = c.post("/v1/chat/completions", json={"model": "tiny", "max_tokens": 3,
+                                                 "messages": [{"role": "user", "content": "hi"}]})
+        assert r.status_code == 200
+        assert c.get("/admin/profile").json()["steps_left"] < 100
+        assert c.post("/admin/profile", json={"close": True}).json()["open"] is False
+        bad = c.post("/admin/profile", json={"collectors": ["pm_sampling"]})
+        assert bad.status_code == 400
+    assert len(P.load(str(tmp_path / "rank0.sqlite"))["spans"]) >= 1

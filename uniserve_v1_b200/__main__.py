@@ -307,6 +307,13 @@ def serve(args) -> int:
         engine = make_engine()
         if bus is not None:
             shutdown = engine.shutdown
+        sess = pkg.profiling_config.session
+        if sess.collectors and bus is None:
+            # a package that names session collectors starts profiling with the deployment
+            from .engine.profiling import start_session
+            st = start_session(engine, list(sess.collectors), sess.output,
+                               seconds=float(sess.duration) if sess.duration else None, rank=rank)
+            print(f"profile session: {st['path']} ({', '.join(st['collectors'])})", file=sys.stderr)
         # a replicated engine cannot be rebuilt on one rank alone: no in-place restart
         drafter = None
         k_draft = int(pkg.speculative_config.num_draft_tokens)

@@ -6,13 +6,18 @@
   a host monotonic timestamp, so the same code paths run in CPU tests.
 * **Host spans** record (name, start, end) on the calling thread.
 * A **session** collects both into one SQLite file per rank (tables ``spans``,
-  ``probes``, ``counters``, ``meta``) which ``tools/profile.py`` turns into a
-  Perfetto / Chrome trace.
+  ``probes``, ``kernels``, ``counters``, ``meta``) which ``tools/profile.py`` turns
+  into a Perfetto / Chrome trace.  A session names its collectors:
+  ``fence_timeline`` (the probes) and ``timeline``, the activity records of every
+  kernel and copy the process launches while the session is open (``KernelTimeline``:
+  the CUPTI activity interface through ``torch.profiler``, which also sees the
+  launches this package makes through its own library).  A session ends by
+  ``close``, after a number of steps or after a duration.
 
 Reference: crates/engine/src/profiling/{markers,session,artifact,collectors}.rs,
-docs/profiling.md (reference project paths).  The reference also wraps CUPTI
-(activity records, PM/PC sampling, range profiler); those need the profiling
-libraries' own interfaces and are not part of this package.
+docs/profiling.md (reference project paths).  The reference's sampling collectors
+(PM / PC sampling, range metrics) need the profiling library's own interfaces and are
+not part of this package; asking a session for them is refused by name.
 """
 from __future__ import annotations
 
@@ -83,6 +88,8 @@ class Session:
             " end_ns INT, step INT);"
             "CREATE TABLE IF NOT EXISTS probes(rank INT, name TEXT, timer_ns INT, sm_clock INT,"
             " tag INT);"
+            "CREATE TABLE IF NOT EXISTS kernels(rank INT, name TEXT, kind TEXT, stream INT,"
+            " start_ns INT, dur_ns INT);"
             "CREATE TABLE IF NOT EXISTS counters(rank INT, name TEXT, step INT, value REAL);"
             "CREATE TABLE IF NOT EXISTS meta(key TEXT, value TEXT);")
         for k, v in (meta or {}).items():
@@ -103,6 +110,12 @@ class Session:
             self.db.executemany("INSERT INTO probes VALUES (?,?,?,?,?)",
                                 [(self.rank, n, t, c, g) for n, t, c, g in rows])
 
+    def kernels(self, rows):
+        """rows of (name, kind, stream, start_ns, dur_ns)."""
+        with self.lock:
+            self.db.executemany("INSERT INTO kernels VALUES (?,?,?,?,?,?)",
+                                [(self.rank,) + tuple(r) for r in rows])
+
     def counter(self, name: str, step: int, value: float):
         with self.lock:
             self.db.execute("INSERT INTO counters VALUES (?,?,?,?)", (self.rank, name, step, value))
@@ -111,6 +124,63 @@ class Session:
         with self.lock:
             self.db.commit()
             self.db.close()
+
+
+COLLECTORS = ("fence_timeline", "timeline")
+SAMPLING_COLLECTORS = ("pm_sampling", "pc_sampling", "range_metrics")
+
+
+class KernelTimeline:
+    """The ``timeline`` collector: one record per kernel, copy and memset the process runs
+    between ``start`` and ``stop`` (name, kind, stream, start, duration).  On a CUDA device
+    the records come from the CUPTI activity interface behind ``torch.profiler``; on CPU
+    ranks the operator records of the host stand in, so sessions are testable without a GPU.
+    Tracing costs launch latency while it runs: sessions are for windows of steps."""
+
+    def __init__(self, device="cpu"):
+        self.cuda = torch.device(device).type == "cuda"
+        self.prof = None
+
+    def start(self) -> None:
+        from torch.profiler import ProfilerActivity, profile
+        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if self.cuda else [])
+        self.prof = profile(activities=acts, record_shapes=False, with_stack=False)
+        self.prof.__enter__()
+
+    def stop(self) -> list:
+        if self.prof is None:
+            return []
+        if self.cuda:
+            torch.cuda.synchronize()
+        self.prof.__exit__(None, None, None)
+        from torch.autograd import DeviceType
+        want = DeviceType.CUDA if self.cuda else DeviceType.CPU
+        rows = []
+        if self.cuda:
+            try:    # the activity records themselves carry the stream
+                for ev in self.prof.profiler.kineto_results.events():
+                    if ev.device_type() != want:
+                        continue
+                    name = ev.name()
+                    kind = ("copy" if name.startswith("Memcpy") else
+                            "memset" if name.startswith("Memset") else "kernel")
+                    rows.append((name, kind, int(ev.device_resource_id()), int(ev.start_ns()),
+                                 int(ev.duration_ns())))
+                self.prof = None
+                return rows
+            except AttributeError:
+                rows = []
+        for e in self.prof.events():
+            if e.device_type != want:
+                continue
+            t0, t1 = e.time_range.start, e.time_range.end          # microseconds
+            name = e.name
+            kind = ("copy" if name.startswith("Memcpy") else "memset" if name.startswith("Memset")
+                    else "kernel") if self.cuda else "host_op"
+            rows.append((name, kind, int(getattr(e, "device_index", 0) or 0),
+                         int(t0 * 1000), int(max(0.0, t1 - t0) * 1000)))
+        self.prof = None
+        return rows
 
 
 class StepProfiler:
@@ -127,15 +197,47 @@ class StepProfiler:
         self.host_ns = 0
         self.probes_per_step = probes_per_step
 
-    def open(self, path: str, meta: Optional[dict] = None) -> Session:
+    def open(self, path: str, meta: Optional[dict] = None, collectors=("fence_timeline",),
+             max_steps: Optional[int] = None, max_seconds: Optional[float] = None) -> Session:
+        """Starts a session with the named collectors; it closes itself after ``max_steps``
+        engine steps or ``max_seconds`` (checked at step ends), whichever comes first."""
+        collectors = tuple(collectors or ("fence_timeline",))
+        for c in collectors:
+            if c in SAMPLING_COLLECTORS:
+                raise ValueError(f"collector {c!r} needs the profiling library's sampling "
+                                 "interfaces, which this package does not wrap")
+            if c not in COLLECTORS:
+                raise ValueError(f"unknown collector {c!r}; known: {', '.join(COLLECTORS)}")
+        if self.session:
+            self.close()
+        meta = dict(meta or {}, collectors=",".join(collectors))
         self.session = Session(path, self.rank, meta)
+        self.collectors = collectors
+        self._left = max_steps
+        self._deadline = time.monotonic() + max_seconds if max_seconds else None
+        self.timeline = None
+        if "timeline" in collectors:
+            self.timeline = KernelTimeline(self.ring.device)
+            self.timeline.start()
         return self.session
 
     def close(self):
         if self.session:
             self.flush()
+            tl = getattr(self, "timeline", None)
+            if tl is not None:
+                self.session.kernels(tl.stop())
+                self.timeline = None
             self.session.close()
             self.session = None
+            self.last_closed = time.time()
+
+    def state(self) -> dict:
+        return {"open": self.session is not None,
+                "path": self.session.path if self.session else None,
+                "collectors": list(getattr(self, "collectors", ())) if self.session else [],
+                "steps_left": getattr(self, "_left", None) if self.session else None,
+                **self.counters()}
 
     @contextmanager
     def step(self, kind: str, step_id: int):
@@ -154,6 +256,14 @@ class StepProfiler:
                 self.session.span(f"{kind} step", t0, t1, step_id)
             if len(self.ring.pending) >= 64:
                 self.flush(wait=False)
+            if self.session:
+                if getattr(self, "_left", None) is not None:
+                    self._left -= 1
+                done = (getattr(self, "_left", None) is not None and self._left <= 0) or \
+                       (getattr(self, "_deadline", None) is not None
+                        and time.monotonic() >= self._deadline)
+                if done:
+                    self.close()
 
     @contextmanager
     def span(self, name: str, step_id: int = -1):
@@ -178,3 +288,26 @@ class StepProfiler:
     def counters(self) -> dict:
         return {"steps": self.steps, "device_seconds": self.device_ns / 1e9,
                 "host_seconds": self.host_ns / 1e9}
+
+
+def start_session(engine, collectors, output: Optional[str] = None, steps: Optional[int] = None,
+                  seconds: Optional[float] = None, rank: int = 0) -> dict:
+    """Opens a session on ``engine`` (attaching a ``StepProfiler`` when it has none): the
+    form behind ``[profiling_config.session]`` of a package and ``POST /admin/profile``.
+    Without ``output`` the artifact goes to the temporary directory."""
+    import os
+    import tempfile
+    prof = getattr(engine, "profiler", None)
+    if prof is None:
+        device = getattr(getattr(engine, "model", None), "device", "cpu")
+        prof = StepProfiler(device, rank=rank)
+        engine.profiler = prof
+    if output is None:
+        output = os.path.join(tempfile.gettempdir(),
+                              f"uniserve-profile-{os.getpid()}-{int(time.time())}-rank{rank}.sqlite")
+    elif os.path.isdir(output):
+        output = os.path.join(output, f"rank{rank}.sqlite")
+    prof.open(output, {"pid": os.getpid()}, collectors=collectors,
+              max_steps=int(steps) if steps else None,
+              max_seconds=float(seconds) if seconds else None)
+    return prof.state()

@@ -749,6 +749,44 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         hr = getattr(app.state, "restart", None)
         return hr.status() if hr is not None else {"state": None}
 
+    @app.get("/admin/profile")
+    async def get_profile():
+        """State of the engine's profile session and its always-on counters."""
+        if s.service is None:
+            return _err(409, "this deployment has no engine")
+        prof = getattr(s.engine, "profiler", None)
+        return prof.state() if prof is not None else {"open": False}
+
+    @app.post("/admin/profile")
+    async def post_profile(request: Request):
+        """Opens a profile session: ``{"collectors": ["fence_timeline", "timeline"], "steps": n,
+        "seconds": t, "output": path}``; it closes itself after ``steps`` engine steps or
+        ``seconds``.  ``{"close": true}`` ends the open session."""
+        if s.service is None:
+            return _err(409, "this deployment has no engine")
+        try:
+            body = await request.json()
+        except Exception:
+            body = {}
+        from ..engine.profiling import start_session
+
+        def act(e):
+            if body.get("close"):
+                if getattr(e, "profiler", None) is not None:
+                    e.profiler.close()
+                    return e.profiler.state()
+                return {"open": False}
+            return start_session(e, body.get("collectors") or ["fence_timeline"],
+                                 body.get("output"), steps=body.get("steps"),
+                                 seconds=body.get("seconds"),
+                                 rank=getattr(getattr(e.model, "ctx", None), "rank", 0))
+        try:
+            out = await asyncio.to_thread(s.service.call, act)
+        except ValueError as ex:
+            return _err(400, str(ex), param="collectors")
+        s.obs.event("profile", **{k: v for k, v in out.items() if k in ("open", "path")})
+        return out
+
     @app.post("/admin/sleep")
     async def admin_sleep(level: int = 1):
         """Frees the KV cache and graphs (level 1) and the weights too (level 2); requests in

@@ -27,6 +27,11 @@ def load(path: str) -> dict:
                                 "ORDER BY timer_ns").fetchall(),
            "counters": db.execute("SELECT rank, name, step, value FROM counters").fetchall(),
            "meta": dict(db.execute("SELECT key, value FROM meta").fetchall())}
+    try:        # sessions with the ``timeline`` collector
+        out["kernels"] = db.execute("SELECT rank, name, kind, stream, start_ns, dur_ns FROM kernels "
+                                    "ORDER BY start_ns").fetchall()
+    except sqlite3.OperationalError:
+        out["kernels"] = []
     db.close()
     return out
 
@@ -57,6 +62,9 @@ def to_trace(sessions: list) -> dict:
         for rank, name, step, value in s["counters"]:
             events.append({"name": name, "ph": "C", "ts": float(step), "pid": rank,
                            "args": {name: value}})
+        for rank, name, kind, stream, t0, dur in s.get("kernels", []):
+            events.append({"name": name, "ph": "X", "ts": t0 / 1e3, "dur": dur / 1e3, "pid": rank,
+                           "tid": f"{kind}s:stream {stream}", "args": {}})
     return {"traceEvents": events, "displayTimeUnit": "ns"}
 
 
@@ -69,9 +77,16 @@ def summary(sessions: list) -> dict:
         for _, base, _, t0, t1, _ in device_ranges(s["probes"]):
             dev[base][0] += 1
             dev[base][1] += (t1 - t0) / 1e6
+    kern = defaultdict(lambda: [0, 0.0])
+    for s in sessions:
+        for _, name, kind, _, _, dur in s.get("kernels", []):
+            key = name if kind != "host_op" else "host:" + name
+            kern[key][0] += 1
+            kern[key][1] += dur / 1e6
     fmt = lambda d: {k: {"count": c, "total_ms": round(ms, 3), "mean_ms": round(ms / c, 4)}
                      for k, (c, ms) in sorted(d.items())}
-    return {"host_spans": fmt(host), "device_ranges": fmt(dev)}
+    top = dict(sorted(fmt(kern).items(), key=lambda kv: -kv[1]["total_ms"])[:40])
+    return {"host_spans": fmt(host), "device_ranges": fmt(dev), "kernels": top}
 
 
 def main(argv=None) -> int:
@@ -87,7 +102,7 @@ def main(argv=None) -> int:
     if args.cmd == "trace":
         with open(args.out, "w") as f:
             json.dump(to_trace(sessions), f)
-        print(f"{args.out}: {sum(len(x['spans']) + len(x['probes']) for x in sessions)} records")
+        print(f"{args.out}: {sum(len(x['spans']) + len(x['probes']) + len(x.get('kernels', [])) for x in sessions)} records")
     else:
         print(json.dumps(summary(sessions), indent=1))
     return 0
