@@ -1,5 +1,6 @@
 """Prefill / decode disaggregation on CPU engines: a request that moves after its first
 token produces what one engine produces."""
+import pytest
 import torch
 
 from uniserve_v1_b200.engine.engine import LLMEngine
@@ -161,3 +162,136 @@ def test_copy_manifests_cover_every_layout_pair_and_route_a_handoff():
         for o in dec.step():
             out.extend(o.new_token_ids)
     assert out == ref
+
+
+# ------------------------------------------------- between tensor-parallel degrees --
+def _tp_rank(rank, world, port, q, mode, body):
+    """One rank of a 2-way tensor-parallel replicated engine.  mode "lend": compute the
+    prompt and the first token, lend the request (every rank its KV heads).  mode "take":
+    continue a request that a single-rank engine lent."""
+    import os
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world))
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.parallel.context import ParallelContext
+    from uniserve_v1_b200.server import multirank as MR
+    r, w, dev, control = MR.init_rank()
+    ctx = ParallelContext.from_world(tensor=world, expert_over_tensor=True)
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32, ctx).init_random(seed=0)
+    eng = LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128, use_graphs=False)
+    bus = MR.CommandBus(control, r)
+    import torch.distributed as dist
+
+    def leave():            # an orderly end: no rank closes its sockets under the other
+        dist.barrier()
+        dist.destroy_process_group()
+
+    if r != 0:
+        MR.follower_loop(eng, bus)
+        leave()
+        return
+    rep = MR.ReplicatedEngine(eng, bus)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    if mode == "lend":
+        rid = rep.add_request(_PROMPT, sp)
+        first = []
+        while not first:
+            for o in rep.step():
+                first.extend(o.new_token_ids)
+        blob = rep.export_request(rid)
+        assert rid not in eng.scheduler.requests           # lent: gone on this side
+        rep.shutdown()
+        q.put((first, blob))
+        leave()
+        return
+    rid = rep.import_request("moved-1", body)
+    toks = []
+    while rep.has_work():
+        for o in rep.step():
+            toks.extend(o.new_token_ids)
+    try:
+        rep.import_request("moved-2", body[:-7])              # a cut body: every rank refuses it
+        refused = False
+    except Exception:
+        refused = True
+    rep.shutdown()
+    q.put((toks, refused))
+    leave()
+
+
+_PROMPT = [3, 17, 91, 250, 8, 8, 41, 700, 12, 5, 66, 301, 2, 19, 77, 123, 9, 4, 1000, 55]
+
+
+def _spawn_tp(mode, body=None):
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_tp_rank, args=(r, 2, port, q, mode, body)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return out
+
+
+def test_handoff_between_tensor_parallel_degrees_over_bytes():
+    """A request moves, as bytes, from a 2-rank tensor-parallel deployment to a single-rank
+    one and the other way round: the lender's ranks each frame the KV heads they hold, the
+    frames travel as one body, the taker's ranks re-cut the heads for themselves.  Either way
+    the tokens are those of one engine that did everything."""
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.handoff import (HandoffError, export_request, handoffs_from_bytes,
+                                                 import_request, pack_frames, unpack_frames)
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+
+    def single():
+        model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+        return LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128, use_graphs=False)
+
+    whole = single().generate([_PROMPT], sp)[0]
+
+    # two ranks lend, one rank takes
+    first, blob = _spawn_tp("lend")
+    frames = unpack_frames(blob)
+    assert len(frames) == 2 and first == whole[:len(first)]
+    hs = handoffs_from_bytes(blob)
+    assert sorted(h.head_lo for h in hs) == [0, 1] and all(h.heads_total == 2 for h in hs)
+    eng = single()
+    for h in hs:
+        h.validate_for(eng)
+    import_request(eng, hs)
+    rest = []
+    while eng.has_work():
+        for o in eng.step():
+            rest.extend(o.new_token_ids)
+    assert first + rest == whole
+
+    # one rank lends, two ranks take
+    eng = single()
+    rid = eng.add_request(_PROMPT, sp)
+    first = []
+    while not first:
+        for o in eng.step():
+            first.extend(o.new_token_ids)
+    body = export_request(eng, rid).to_bytes()
+    toks, refused = _spawn_tp("take", body)
+    assert first + toks == whole and refused
+
+    # frames that do not cover the heads, or describe different requests, are refused
+    with pytest.raises(HandoffError, match="in no frame"):
+        handoffs_from_bytes(pack_frames([frames[0], frames[0]]))
+    other = hs[1]
+    other.request_id = "someone-else"
+    with pytest.raises(HandoffError, match="different requests"):
+        handoffs_from_bytes(pack_frames([frames[0], other.to_bytes()]))

@@ -231,6 +231,69 @@ def test_replica_router_spreads_and_sticks(live_server):
         t.join(timeout=10)
 
 
+def test_router_sends_requests_where_their_prefix_is_cached():
+    """Two replicas behind a prefix-aware router.  A conversation whose first turn ran on one
+    replica continues there (the router asks both replicas how much of the prompt each holds),
+    also when that replica is the busier one by index order; a prompt nobody holds goes by
+    load; the probe allocates nothing."""
+    import json
+    import urllib.request
+    import uvicorn
+    from uniserve_v1_b200.server.router import create_router_app
+    a_url, a_srv, a_th, a_eng = _start_chat_server()
+    b_url, b_srv, b_th, b_eng = _start_chat_server()
+    port = _free_port()
+    app = create_router_app([a_url, b_url], prefix_aware=True)
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+    t = threading.Thread(target=server.run, daemon=True)
+    t.start()
+    for _ in range(200):
+        if server.started:
+            break
+        time.sleep(0.05)
+    base = f"http://127.0.0.1:{port}"
+
+    def post(url, body, path="/v1/chat/completions"):
+        req = urllib.request.Request(url + path, data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return json.loads(r.read())
+    story = "once upon a time there was a very long prompt about routing requests " * 3
+    turn1 = {"model": "tiny", "max_tokens": 4, "temperature": 0, "ignore_eos": True,
+             "messages": [{"role": "user", "content": story}]}
+    try:
+        # the first turn runs on replica B directly (the router would have picked A)
+        first = post(b_url, turn1)
+        free_b = b_eng.blocks.num_free
+        probe_a = post(a_url, turn1, "/internal/probe")
+        probe_b = post(b_url, turn1, "/internal/probe")
+        assert probe_a["cached_tokens"] == 0 and probe_b["cached_tokens"] >= 64
+        assert probe_b["prompt_tokens"] == probe_a["prompt_tokens"] > 64
+        assert b_eng.blocks.num_free == free_b                        # a probe keeps no page
+        # the second turn extends the first: it is sent to B, where the prefix is
+        turn2 = dict(turn1, messages=turn1["messages"] + [
+            {"role": "assistant", "content": first["choices"][0]["message"]["content"] or ""},
+            {"role": "user", "content": "and then?"}])
+        served_b = b_eng.scheduler.stats["prefill_tokens"]
+        out = post(base, turn2)
+        assert out["usage"]["completion_tokens"] == 4
+        with urllib.request.urlopen(base + "/router/stats", timeout=10) as r:
+            st = json.loads(r.read())
+        assert st["prefix_hits"] == 1 and st["probes"] == 1
+        assert [x["served"] for x in st["replicas"]] == [0, 1]
+        # B computed only what the first turn had not cached
+        assert b_eng.scheduler.stats["prefill_tokens"] - served_b < probe_b["prompt_tokens"]
+        # nobody holds this prompt: by load, lowest index first
+        post(base, dict(turn1, messages=[{"role": "user", "content": "something else entirely"}]))
+        with urllib.request.urlopen(base + "/router/stats", timeout=10) as r:
+            st = json.loads(r.read())
+        assert st["prefix_hits"] == 1 and [x["served"] for x in st["replicas"]] == [1, 1]
+    finally:
+        for srv, th_ in ((server, t), (a_srv, a_th), (b_srv, b_th)):
+            srv.should_exit = True
+            th_.join(timeout=10)
+
+
 def test_admin_client(live_server, capsys):
     import json
     from uniserve_v1_b200.__main__ import main
@@ -379,6 +442,31 @@ def test_router_disaggregates_prefill_and_decode(live_server):
         code, text = status(dec_url + "/internal/decode", {"request": chat, "handoff": evil}, "k3y")
         assert code == 400 and "hand-off" in text
         assert not os.path.exists("/tmp/us_handoff_pwned")
+
+        # a lender of another tensor-parallel degree: the state arrives as one frame per rank
+        # (here the prefill replica's frame cut into its two KV heads) and is re-cut on import
+        import dataclasses
+        from uniserve_v1_b200.engine.handoff import Handoff, pack_frames
+        chat9 = {"model": "tiny", "messages": [{"role": "user", "content": "tell me"}],
+                 "max_tokens": 9, "ignore_eos": True, "temperature": 0}
+        rq = urllib.request.Request(pre_url + "/internal/prefill", data=json.dumps(chat9).encode(),
+                                    headers={"Content-Type": "application/json",
+                                             "x-uniserve-internal-key": "k3y"})
+        with urllib.request.urlopen(rq, timeout=60) as r:
+            frame = r.read()
+        h = Handoff.from_bytes(frame)
+        halves = [dataclasses.replace(h, head_lo=lo, kv=[(k[:, :, lo:lo + 1].contiguous(),
+                                                          v[:, :, lo:lo + 1].contiguous())
+                                                         for k, v in h.kv]) for lo in (1, 0)]
+        two = base64.b64encode(pack_frames([x.to_bytes() for x in halves])).decode()
+        code, text = status(dec_url + "/internal/decode", {"request": chat9, "handoff": two}, "k3y")
+        assert code == 200, text
+        want9 = json.loads(post(live_server, chat9))
+        assert json.loads(text)["choices"][0]["message"] == want9["choices"][0]["message"]
+        only_one = base64.b64encode(halves[0].to_bytes()).decode()
+        code, text = status(dec_url + "/internal/decode", {"request": chat9, "handoff": only_one},
+                            "k3y")
+        assert code == 400 and "in no frame" in text
     finally:
         for srv, th_ in ((server, t), (pre_srv, pre_th), (dec_srv, dec_th)):
             srv.should_exit = True

@@ -525,6 +525,9 @@ def main(argv=None) -> int:
     r.add_argument("--program", help="routing program: a file that defines route(request, replicas)")
     r.add_argument("--internal-key", default=os.environ.get("UNISERVE_INTERNAL_KEY"),
                    help="key presented to prefill / decode replicas on their internal routes")
+    r.add_argument("--prefix-aware", action="store_true",
+                   help="ask the replicas which of them holds a request's prompt prefix and "
+                        "send it there (requests without prompt_cache_key)")
     a = ap.parse_args(argv)
     if a.cmd == "serve":
         return serve(a)
@@ -544,7 +547,8 @@ def main(argv=None) -> int:
             program = ProgramHost(open(a.program).read(), "routing", call_fuel=1_000_000)
         uvicorn.run(create_router_app(a.replica, prefill_urls=a.prefill or None,
                                       decode_urls=a.decode or None, program=program,
-                                      internal_key=a.internal_key),
+                                      internal_key=a.internal_key,
+                                      prefix_aware=a.prefix_aware),
                     host=host or "127.0.0.1", port=int(port), log_level="warning")
         return 0
     if a.cmd == "build":

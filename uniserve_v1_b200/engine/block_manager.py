@@ -200,6 +200,13 @@ class BlockManager:
         m = self.lib.us_bm_match_prefix(self.h, keys.ctypes.data, len(keys), out.ctypes.data)
         return out[:m].tolist()
 
+    def peek_prefix(self, keys: np.ndarray) -> int:
+        """Pages of the longest cached leading run, without keeping them (a routing probe)."""
+        pages = self.match_prefix(keys)
+        if pages:
+            self.release(pages)
+        return len(pages)
+
     def commit(self, page: int, key) -> int:
         if not self.enable_prefix_cache:
             return page

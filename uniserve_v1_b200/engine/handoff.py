@@ -11,7 +11,11 @@ would have produced: the decode side samples with the request's own lineage seed
 
 ``Handoff.to_bytes`` / ``from_bytes`` frame the state for any byte transport;
 ``send`` / ``recv`` move it over a ``torch.distributed`` group (gloo on the host, NCCL
-between GPUs).  ``PrefillDecodePair`` drives one prefill and one decode engine in the
+between GPUs).  A tensor-parallel deployment lends one frame per rank, packed into one
+body (``pack_frames`` / ``handoffs_from_bytes``: the frames must describe one request and
+cover the model's KV heads); the taker's ranks each re-cut the heads they hold, so the two
+deployments need not share a tensor-parallel degree (``server/multirank.py``:
+``ReplicatedEngine.export_request`` / ``import_request``).  ``PrefillDecodePair`` drives one prefill and one decode engine in the
 roles of the configuration (``role = prefill | decode | mixed``).
 
 Reference behaviour: docs/configuration.md:683-709, crates/storage-server/src/handoff.rs,
@@ -243,6 +247,68 @@ def export_request(engine, request_id: str, release: bool = True) -> Handoff:
     return h
 
 
+# ------------------------------------------------------------- several ranks --
+# A tensor-parallel exporter lends one frame per rank (each holds a range of the KV heads).
+# They travel as one body: ``SET_MAGIC | u32 count | count x u64 length | frames``; a body
+# that starts with MAGIC is a set of one.  The importer re-cuts the head ranges for its own
+# ranks, so the two sides need not share a tensor-parallel degree.
+SET_MAGIC = b"USHS"
+MAX_FRAMES = 64
+
+
+def pack_frames(frames: list) -> bytes:
+    frames = [bytes(f) for f in frames]
+    if len(frames) == 1:
+        return frames[0]
+    return b"".join([SET_MAGIC, struct.pack("<I", len(frames)),
+                     *[struct.pack("<Q", len(f)) for f in frames], *frames])
+
+
+def unpack_frames(blob: bytes) -> list:
+    blob = bytes(blob)
+    if blob[:len(MAGIC)] == MAGIC:
+        return [blob]
+    if len(blob) < len(SET_MAGIC) + 4 or blob[:len(SET_MAGIC)] != SET_MAGIC:
+        raise HandoffError("not a hand-off frame")
+    (n,) = struct.unpack_from("<I", blob, len(SET_MAGIC))
+    if not 1 <= n <= MAX_FRAMES or len(blob) < len(SET_MAGIC) + 4 + 8 * n:
+        raise HandoffError("frame count outside the body")
+    sizes = struct.unpack_from(f"<{n}Q", blob, len(SET_MAGIC) + 4)
+    off = len(SET_MAGIC) + 4 + 8 * n
+    if off + sum(sizes) != len(blob):
+        raise HandoffError("frame lengths do not add up to the body")
+    out = []
+    for sz in sizes:
+        out.append(blob[off:off + sz])
+        off += sz
+    return out
+
+
+def handoffs_from_bytes(blob: bytes) -> list:
+    """The hand-offs of every exporting rank, checked to describe one request and to cover
+    the model's KV heads exactly once."""
+    hs = [Handoff.from_bytes(f) for f in unpack_frames(blob)]
+    first = hs[0]
+    cover = []
+    for h in hs:
+        if (h.request_id, h.prompt_ids, h.output_ids, h.num_computed, h.page_size,
+                h.heads_total) != (first.request_id, first.prompt_ids, first.output_ids,
+                                   first.num_computed, first.page_size, first.heads_total):
+            raise HandoffError("the frames describe different requests")
+        pair = next((p for p in h.kv if p is not None), None)
+        if pair is not None:
+            cover.append((h.head_lo, h.head_lo + pair[0].shape[2]))
+    cover.sort()
+    at = 0
+    for lo, hi in cover:
+        if lo > at:
+            raise HandoffError(f"KV heads [{at}, {lo}) are in no frame")
+        at = max(at, hi)
+    if cover and at != first.heads_total:
+        raise HandoffError(f"KV heads [{at}, {first.heads_total}) are in no frame")
+    return hs
+
+
 def _params_of(d: dict) -> SamplingParams:
     """Sampling parameters back from their JSON form (token-id keys and tuples restored)."""
     d = dict(d)
@@ -256,11 +322,14 @@ def _params_of(d: dict) -> SamplingParams:
 def reshard_heads(shards: list, want_lo: int, want_n: int) -> torch.Tensor:
     """``shards``: (head_lo, tensor [pages, page, heads, D]) from the exporting ranks;
     returns heads [want_lo, want_lo + want_n) in order."""
-    parts = []
+    parts, at = [], want_lo
     for lo, t in sorted(shards, key=lambda s: s[0]):
-        a, b = max(lo, want_lo), min(lo + t.shape[2], want_lo + want_n)
+        # heads already taken from an earlier shard are skipped (ranks that replicate a KV
+        # head all export it)
+        a, b = max(lo, at), min(lo + t.shape[2], want_lo + want_n)
         if a < b:
             parts.append(t[:, :, a - lo:b - lo])
+            at = b
     got = sum(p.shape[2] for p in parts)
     assert got == want_n, f"head range [{want_lo}, {want_lo + want_n}) not covered ({got})"
     return parts[0] if len(parts) == 1 else torch.cat(parts, 2)

@@ -385,17 +385,46 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
                 tensor bytes); every field is checked against this engine before a page is
                 written."""
                 import base64
-                from ..engine.handoff import Handoff
+                from ..engine.handoff import handoffs_from_bytes
                 if not _internal_ok(request):
                     return _err(401, "invalid or missing internal key", "authentication_error")
                 try:
                     body = await request.json()
-                    h = Handoff.from_bytes(base64.b64decode(body["handoff"], validate=True))
-                    h.validate_for(s.engine)
+                    raw = base64.b64decode(body["handoff"], validate=True)
+                    # one frame per rank of the lending deployment; this side re-cuts the KV
+                    # heads for its own ranks
+                    hs = handoffs_from_bytes(raw)
+                    for h in hs:
+                        h.validate_for(s.engine)
                     chat_body = body["request"]
                 except Exception as e:
                     return _err(400, f"hand-off body: {e}")
-                return await _chat(request, body=chat_body, handoff=h)
+                return await _chat(request, body=chat_body, handoff=(hs, raw))
+
+        @app.post("/internal/probe")
+        async def prefix_probe(request: Request):
+            """How much of a chat request's prompt this replica already holds: the router of a
+            replicated deployment asks every replica and sends the request where its prefix
+            pages are (the cluster directory, asked instead of published).  Text requests
+            only; nothing is allocated.  With an internal key configured the route needs it."""
+            if internal_key and not _internal_ok(request):
+                return _err(401, "invalid or missing internal key", "authentication_error")
+            try:
+                req = ChatCompletionRequest.model_validate(await request.json())
+                msgs = [m.model_dump(exclude_none=True) for m in req.messages]
+                tools = [t.model_dump(exclude_none=True) for t in req.tools] if req.tools else None
+                prompt = s.template.render(msgs, tools, True, **(req.chat_template_kwargs or {}))
+                ids = s.tokenizer.encode(prompt)
+            except Exception as e:
+                return _err(400, f"probe: {e}")
+            salt = req.cache_salt or req.prompt_cache_key
+
+            def look(e):
+                blocks = e.blocks
+                return blocks.peek_prefix(blocks.page_keys(ids, salt)) * blocks.page_size
+            cached = await asyncio.to_thread(s.service.call, look)
+            return {"cached_tokens": int(cached), "prompt_tokens": len(ids),
+                    "in_flight": s.inflight}
 
         @app.post("/v1/chat/completions")
         async def chat(request: Request):
@@ -497,7 +526,7 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
                             return _err(500, out.error, "server_error")
                         return JSONResponse(run.response(), headers={"x-uniserve-finished": "1"})
             # tokens the lending engine already produced open the answer
-            seeded = list(handoff.output_ids) if handoff is not None else []
+            seeded = list(handoff[0][0].output_ids) if handoff is not None else []
             first = StepOutput(rid, seeded, False) if seeded else None
 
             if not req.stream:

@@ -95,9 +95,12 @@ class EngineService:
                               "migrations": 0, "priority": priority, "salt": cache_salt,
                               "lend": lend, "media": media}
         if handoff is not None:
-            handoff.request_id = rid
-            self.meta[rid]["outputs"] = list(handoff.output_ids)
-            self.inbox.put(("import", rid, handoff))
+            # one hand-off, or (the frames of every exporting rank, the body they came in)
+            hs, body = handoff if isinstance(handoff, tuple) else ([handoff], None)
+            for h in hs:
+                h.request_id = rid
+            self.meta[rid]["outputs"] = list(hs[0].output_ids)
+            self.inbox.put(("import", rid, hs, body))
         else:
             self.inbox.put(("add", rid, list(prompt_ids), params, priority, cache_salt, None,
                             media))
@@ -221,8 +224,14 @@ class EngineService:
                             self._deliver(StepOutput(rid, [], True, FinishReason.ERROR, error=str(e)))
                     elif msg[0] == "import":
                         try:
-                            from ..engine.handoff import import_request
-                            import_request(self.engine, msg[2])
+                            from ..engine.handoff import import_request, pack_frames
+                            whole = getattr(self.engine, "import_request", None)
+                            if whole is not None:     # every rank of a replicated engine
+                                body = msg[3] if len(msg) > 3 and msg[3] is not None else \
+                                    pack_frames([h.to_bytes() for h in msg[2]])
+                                whole(msg[1], body)
+                            else:
+                                import_request(self.engine, msg[2])
                         except Exception as e:
                             self._deliver(StepOutput(msg[1], [], True, FinishReason.ERROR,
                                                      error=f"hand-off refused: {e}"))
@@ -270,9 +279,11 @@ class EngineService:
                 meta = self.meta.get(o.request_id)
                 if meta and meta.get("lend") and o.new_token_ids and not o.finished:
                     from ..engine.handoff import export_request
+                    whole = getattr(self.engine, "export_request", None)
+                    blob = whole(o.request_id) if whole is not None else \
+                        export_request(self.engine, o.request_id).to_bytes()
                     o = StepOutput(o.request_id, o.new_token_ids, True, None,
-                                   num_cached_tokens=o.num_cached_tokens,
-                                   handoff=export_request(self.engine, o.request_id).to_bytes())
+                                   num_cached_tokens=o.num_cached_tokens, handoff=blob)
                 self._deliver(o)
             now = time.monotonic()
             if self.obs and now - self.last_snapshot > 1.0:

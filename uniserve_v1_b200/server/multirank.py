@@ -54,14 +54,24 @@ class CommandBus:
         dist.broadcast_object_list(blob, src=0, group=self.group)
         return pickle.loads(blob[0])
 
+    def gather(self, payload: bytes) -> Optional[list]:
+        """Every rank's ``payload`` in rank order on the leader (None elsewhere); called by
+        all ranks at the same point of the command stream."""
+        world = dist.get_world_size(self.group)
+        box = [None] * world if self.leader else None
+        dist.gather_object(payload, box, dst=0, group=self.group)
+        return box
+
 
 def _plain(params):
     return asdict(params) if is_dataclass(params) else params
 
 
-def apply_commands(engine, commands: list):
+def apply_commands(engine, commands: list, bus: Optional["CommandBus"] = None):
     """Applies one published batch of commands to a local engine.  Returns the
-    outputs of the step it contained (or None) and whether to keep running."""
+    outputs of the step it contained (or None) and whether to keep running.  ``export`` /
+    ``import`` move a request's state between deployments: every rank lends (or takes) the
+    KV heads it holds; the leader collects the frames over ``bus``."""
     from ..engine.types import SamplingParams
     outs, alive = None, True
     for c in commands:
@@ -80,6 +90,20 @@ def apply_commands(engine, commands: list):
             outs = engine.step()
         elif op == "burst":
             outs = engine.decode_burst(c[1])
+        elif op == "export":
+            from ..engine.handoff import export_request
+            frame = export_request(engine, c[1]).to_bytes()
+            engine.exported_frames = bus.gather(frame) if bus is not None else [frame]
+        elif op == "import":
+            from ..engine.handoff import handoffs_from_bytes, import_request
+            try:
+                hs = handoffs_from_bytes(c[2])
+                for h in hs:
+                    h.request_id = c[1]
+                import_request(engine, hs)
+                engine.import_error = None
+            except Exception as e:      # every rank refuses the same body the same way
+                engine.import_error = e
         elif op == "shutdown":
             alive = False
     return outs, alive
@@ -120,8 +144,23 @@ class ReplicatedEngine:
     def _run(self, last) -> list:
         cmds, self.pending = self.pending + [last], []
         self.bus.publish(cmds)
-        outs, _ = apply_commands(self.engine, cmds)
+        outs, _ = apply_commands(self.engine, cmds, self.bus)
         return outs or []
+
+    def export_request(self, request_id: str) -> bytes:
+        """Lends the request on every rank (between two steps) and returns the ranks' frames
+        as one body (``engine.handoff.pack_frames``)."""
+        from ..engine.handoff import pack_frames
+        self._run(("export", request_id))
+        return pack_frames(self.engine.exported_frames)
+
+    def import_request(self, request_id: str, body: bytes) -> str:
+        """Continues a lent request on every rank: each takes the KV heads it holds out of
+        the exporter's frames, whatever the exporter's tensor-parallel degree was."""
+        self._run(("import", request_id, bytes(body)))
+        if self.engine.import_error is not None:
+            raise self.engine.import_error
+        return request_id
 
     def step(self) -> list:
         return self._run(("step",))
@@ -138,7 +177,7 @@ def follower_loop(engine, bus: CommandBus) -> int:
     steps = 0
     while True:
         cmds = bus.receive()
-        _, alive = apply_commands(engine, cmds)
+        _, alive = apply_commands(engine, cmds, bus)
         steps += sum(1 for c in cmds if c[0] in ("step", "burst"))
         if not alive:
             return steps

@@ -13,6 +13,13 @@ yet.
     python -m uniserve_v1_b200 route --listen 127.0.0.1:8000 \
         --replica http://127.0.0.1:8001 --replica http://127.0.0.1:8002
 
+``--prefix-aware``: requests without a cache key are sent where their prompt prefix is
+cached.  The router asks every reachable replica (``POST /internal/probe``: the replica
+renders and tokenizes the request and looks its page keys up without allocating) and takes
+the one that holds the most tokens, unless it holds fewer than 32 or is more than four
+requests busier than the idlest replica; the reference keeps a published cluster directory
+for this, here the directory is asked per request.
+
 Roles (``replicas.<id>.role = prefill | decode | mixed``): with ``--prefill URL`` and
 ``--decode URL`` replicas a chat request is computed up to its first token on a prefill
 replica and handed, with the contents of its KV pages, to a decode replica that
@@ -55,12 +62,17 @@ class ReplicaRouter:
         self.retry_after_s = retry_after_s
         self.program = program
         self.program_faults = 0
+        self.probes = 0            # prefix-aware routing: requests probed / sent to a holder
+        self.prefix_hits = 0
 
-    def pick(self, affinity: Optional[str] = None, exclude=(), size: int = 0) -> Optional[Replica]:
+    def pick(self, affinity: Optional[str] = None, exclude=(), size: int = 0,
+             prefer: Optional[Replica] = None) -> Optional[Replica]:
         live = [r for r in self.replicas if r.up and r not in exclude] or \
             [r for r in self.replicas if r not in exclude]
         if not live:
             return None
+        if prefer is not None and prefer in live:
+            return prefer
         if self.program is not None and self.program.has("route"):
             try:
                 i = self.program.call("route", {"bytes": size, "cache_key": affinity},
@@ -88,7 +100,9 @@ class ReplicaRouter:
 def create_router_app(urls: list, api_key: Optional[str] = None,
                       prefill_urls: Optional[list] = None,
                       decode_urls: Optional[list] = None, program=None,
-                      internal_key: Optional[str] = None) -> FastAPI:
+                      internal_key: Optional[str] = None, prefix_aware: bool = False,
+                      probe_timeout_s: float = 0.25, prefix_min_tokens: int = 32,
+                      prefix_slack: int = 4) -> FastAPI:
     """``urls``: replicas of role ``mixed``.  With ``prefill_urls`` and ``decode_urls`` chat
     requests are disaggregated: a prefill replica computes the prompt and the first token
     (``/internal/prefill``), its answer - the request's framed state - goes to a decode
@@ -121,6 +135,37 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
     def _internal(req: Request) -> dict:
         return dict(_headers(req), **{"x-uniserve-internal-key": internal_key or ""})
 
+    async def where_cached(body: bytes) -> Optional[Replica]:
+        """``prefix_aware``: every reachable replica says how many tokens of the request's
+        prompt it holds (``/internal/probe``); the request goes to the best one when it holds
+        at least ``prefix_min_tokens`` and is not ``prefix_slack`` requests busier than the
+        idlest replica.  Replicas that do not answer in ``probe_timeout_s`` do not count."""
+        import asyncio
+        s = await session()
+        live = [r for r in router.replicas if r.up]
+        if len(live) < 2:
+            return None
+
+        async def ask(r):
+            try:
+                async with s.post(r.url + "/internal/probe", data=body,
+                                  headers={"content-type": "application/json",
+                                           "x-uniserve-internal-key": internal_key or ""},
+                                  timeout=aiohttp.ClientTimeout(total=probe_timeout_s)) as up:
+                    if up.status != 200:
+                        return r, -1
+                    return r, int((await up.json()).get("cached_tokens", 0))
+            except Exception:
+                return r, -1
+        got = await asyncio.gather(*[ask(r) for r in live])
+        router.probes += 1
+        best, tokens = max(got, key=lambda g: (g[1], -g[0].in_flight))
+        idlest = min(r.in_flight for r in live)
+        if tokens >= prefix_min_tokens and best.in_flight - idlest <= prefix_slack:
+            router.prefix_hits += 1
+            return best
+        return None
+
     async def forward(req: Request, path: str):
         body = await req.body()
         affinity = None
@@ -129,10 +174,14 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
                 affinity = json.loads(body).get("prompt_cache_key")
             except Exception:
                 affinity = None
+        prefer = None
+        if prefix_aware and not affinity and body and path == "/v1/chat/completions":
+            prefer = await where_cached(body)
         tried = []
         s = await session()
         while True:
-            r = router.pick(affinity, exclude=tried, size=len(body or b""))
+            r = router.pick(affinity, exclude=tried, size=len(body or b""),
+                            prefer=prefer if not tried else None)
             if r is None:
                 return JSONResponse({"error": {"message": "no replica is reachable",
                                                "type": "service_unavailable"}}, status_code=503)
@@ -227,6 +276,12 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
     @app.get("/router/replicas")
     async def replicas():
         return router.stats()
+
+    @app.get("/router/stats")
+    async def router_stats():
+        return {"replicas": router.stats(), "prefix_aware": prefix_aware,
+                "probes": router.probes, "prefix_hits": router.prefix_hits,
+                "program_faults": router.program_faults}
 
     @app.api_route("/{path:path}", methods=["GET", "POST", "PUT", "DELETE"])
     async def any_route(path: str, req: Request):
