@@ -143,3 +143,35 @@ def test_host_kv_tier_on_gpu_restores_evicted_prefix():
     torch.cuda.synchronize()
     N.raise_on_device_error()
     assert a0 == a1 == b0 == b1 and c0 == 0 and c1 == 64
+
+
+@pytest.mark.parametrize("kv_dtype", ["auto", "fp8_e4m3"])
+def test_prefix_cache_file_between_two_gpu_engines(tmp_path, kv_dtype):
+    """The cached pages of one engine, written to a file and read by another engine on the
+    GPU (bf16 pages, and E4M3 pages with their scales): the prompt is found cached and the
+    tokens are those of the first engine's own cached run."""
+    from uniserve_v1_b200.engine.prefix_store import load_prefix_cache, save_prefix_cache
+    model = Qwen3MoeModel(_cfg(), "cuda", torch.bfloat16).init_random(seed=0)
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, 2048, (100,), generator=g).tolist()
+    extra = {} if kv_dtype == "auto" else {"kv_dtype": kv_dtype}
+
+    def engine():
+        return LLMEngine(model, num_pages=32, page_size=16, max_num_seqs=2, max_model_len=256,
+                         use_graphs=False, **extra)
+    a = engine()
+    a.generate([prompt], sp)
+    want = a.generate([prompt], sp)[0]                    # through its cached pages
+    path = str(tmp_path / "gpu.kv")
+    saved = save_prefix_cache(a, path)
+    assert saved["pages"] >= 6
+    b = engine()
+    assert load_prefix_cache(b, path)["pages"] == saved["pages"]
+    rid = b.add_request(prompt, sp)
+    req = b.scheduler.requests[rid]
+    while b.has_work():
+        b.step()
+    torch.cuda.synchronize()
+    N.raise_on_device_error()
+    assert req.num_cached >= 96 and req.output_ids == want

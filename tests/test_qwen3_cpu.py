@@ -1,5 +1,7 @@
 """Tiny Qwen3-MoE on CPU: the engine (paged cache, scheduler, fused-op CPU
 formulas) must reproduce an independent FP32 reference decode."""
+import os
+
 import pytest
 import torch
 
@@ -525,3 +527,58 @@ def test_decode_steps_in_flight_give_the_same_tokens():
     n = min(len(plain[2]), len(piped[2]))
     assert n >= 5 and plain[2][:n] == piped[2][:n]                  # the aborted one, up to the abort
     assert eng._stream is None and eng.blocks.num_free == eng0.blocks.num_free   # no page leaked
+
+
+@pytest.mark.parametrize("kv_dtype", ["auto", "fp8_e4m3"])
+def test_prefix_cache_outlives_the_engine_through_a_file(tmp_path, kv_dtype):
+    """An engine writes its content-keyed pages to a file, a second engine of the same model
+    reads them: prompts the first one computed are cache hits on the second and produce the
+    same tokens; a file of another page size or model is refused; pages beyond the reader's
+    free pool are dropped oldest first."""
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.prefix_store import load_prefix_cache, save_prefix_cache
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    import dataclasses
+    cfg = Qwen3MoeConfig.tiny()
+    if kv_dtype != "auto":
+        cfg = dataclasses.replace(cfg, head_dim=128)
+    model = Qwen3MoeModel(cfg, "cpu", torch.float32).init_random(seed=0)
+    extra = {} if kv_dtype == "auto" else {"kv_dtype": kv_dtype}
+
+    def engine(pages=64, page_size=16):
+        return LLMEngine(model, num_pages=pages, page_size=page_size, max_num_seqs=4,
+                         max_model_len=256, use_graphs=False, **extra)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (70, 40)]
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    a = engine()
+    first = a.generate(prompts, sp)
+    want = a.generate(prompts, sp)       # through the cached pages (E4M3 pages round the keys)
+    if kv_dtype == "auto":
+        assert want == first
+    path = str(tmp_path / "prefix.kv")
+    saved = save_prefix_cache(a, path)
+    assert saved["pages"] >= 6 and os.path.getsize(path) == saved["bytes"]
+
+    b = engine()
+    got = load_prefix_cache(b, path, remove=False)
+    assert got["pages"] == saved["pages"] and got["dropped"] == 0
+    hits0 = b.blocks.stats()["hits"]
+    assert b.generate(prompts, sp) == want
+    assert b.blocks.stats()["hits"] - hits0 >= 6          # the prompts' full pages were found
+    assert b.scheduler.stats["prefill_tokens"] < sum(len(p) for p in prompts) // 2
+
+    assert "page_size" in load_prefix_cache(engine(page_size=8), path, remove=False)["refused"]
+    other = Qwen3MoeModel(cfg, "cpu", torch.float32).init_random(seed=1)
+    if a.blocks.identity != LLMEngine(other, num_pages=16, use_graphs=False).blocks.identity:
+        e2 = LLMEngine(other, num_pages=64, max_num_seqs=4, max_model_len=256, use_graphs=False,
+                       **extra)
+        assert "identity" in load_prefix_cache(e2, path, remove=False)["refused"]
+    small = engine(pages=5)                                # room for three pages
+    few = load_prefix_cache(small, path, remove=True)
+    assert 0 < few["pages"] <= 4 and few["dropped"] == saved["pages"] - few["pages"]
+    assert not os.path.exists(path)
+    with open(path, "wb") as f:
+        f.write(b"not a cache file")
+    assert load_prefix_cache(engine(), path)["refused"] == "not a prefix-cache file"

@@ -572,8 +572,9 @@ def test_hot_restart_hands_the_listener_to_a_successor(tmp_path):
     proc = subprocess.Popen([sys.executable, "-m", "uniserve_v1_b200", "serve", str(pkg)], env=env,
                             cwd=os.path.dirname(os.path.dirname(__file__)))
     base = f"http://127.0.0.1:{port}"
-    body = json.dumps({"model": "tiny", "messages": [{"role": "user", "content": "hello there"}],
-                       "max_tokens": 8, "temperature": 0, "ignore_eos": True}).encode()
+    body = json.dumps({"model": "tiny", "max_tokens": 8, "temperature": 0, "ignore_eos": True,
+                       "messages": [{"role": "user", "content": "hello there, " * 16}]}).encode()
+    cached = []
 
     def get(path):
         with urllib.request.urlopen(base + path, timeout=5) as r:
@@ -583,7 +584,9 @@ def test_hot_restart_hands_the_listener_to_a_successor(tmp_path):
         req = urllib.request.Request(base + "/v1/chat/completions", data=body,
                                      headers={"Content-Type": "application/json"})
         with urllib.request.urlopen(req, timeout=120) as r:
-            return json.loads(r.read())["choices"][0]["message"]["content"]
+            out = json.loads(r.read())
+        cached.append(out["usage"]["prompt_tokens_details"]["cached_tokens"])
+        return out["choices"][0]["message"]["content"]
     successor = None
     try:
         for _ in range(240):
@@ -610,6 +613,10 @@ def test_hot_restart_hands_the_listener_to_a_successor(tmp_path):
             time.sleep(0.5)
         assert proc.poll() is not None, "the first process did not leave"
         assert get("/health")["pid"] == successor and chat() == want
+        # the successor read the first process's cached pages before it served: whichever
+        # process answered after the first request found the prompt's pages cached - also the
+        # successor on the first request it ever saw
+        assert cached[0] == 0 and len(cached) >= 3 and all(c >= 64 for c in cached[1:]), cached
     finally:
         if proc.poll() is None:
             proc.terminate()
@@ -877,3 +884,36 @@ def test_profile_session_collectors_and_admin_route(tmp_path):
         bad = c.post("/admin/profile", json={"collectors": ["pm_sampling"]})
         assert bad.status_code == 400
     assert len(P.load(str(tmp_path / "rank0.sqlite"))["spans"]) >= 1
+
+
+def test_admin_prefix_cache_saves_and_loads_over_http(tmp_path):
+    """`POST /admin/prefix_cache`: one deployment writes its cached pages, another reads them
+    and answers the same prompt from the cache."""
+    from fastapi.testclient import TestClient
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    from uniserve_v1_b200.server.app import create_app
+    from uniserve_v1_b200.server.tokenizer import ByteTokenizer
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    path = str(tmp_path / "pages.kv")
+    chat = {"model": "tiny", "max_tokens": 3, "temperature": 0, "ignore_eos": True,
+            "messages": [{"role": "user", "content": "the same long question, " * 8}]}
+
+    def deployment():
+        eng = LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=512, use_graphs=False)
+        return TestClient(create_app(engine=eng, tokenizer=ByteTokenizer(1024, 1023),
+                                     served_model_name="tiny"))
+    with deployment() as a:
+        first = a.post("/v1/chat/completions", json=chat).json()
+        assert first["usage"]["prompt_tokens_details"]["cached_tokens"] == 0
+        saved = a.post("/admin/prefix_cache", json={"action": "save", "path": path}).json()
+        assert saved["pages"] >= 4
+        assert a.post("/admin/prefix_cache", json={"action": "erase", "path": path}).status_code == 400
+    with deployment() as b:
+        got = b.post("/admin/prefix_cache", json={"action": "load", "path": path}).json()
+        assert got["pages"] == saved["pages"]
+        again = b.post("/v1/chat/completions", json=chat).json()
+        assert again["choices"][0]["message"] == first["choices"][0]["message"]
+        assert again["usage"]["prompt_tokens_details"]["cached_tokens"] >= 64
+        missing = b.post("/admin/prefix_cache", json={"action": "load", "path": path + ".no"}).json()
+        assert missing["pages"] == 0 and "refused" in missing

@@ -307,6 +307,10 @@ def serve(args) -> int:
         engine = make_engine()
         if bus is not None:
             shutdown = engine.shutdown
+        if getattr(args, "prefix_cache", None) and bus is None:
+            from .engine.prefix_store import load_prefix_cache
+            got = load_prefix_cache(engine, args.prefix_cache)
+            print(f"prefix cache: {got}", file=sys.stderr)
         sess = pkg.profiling_config.session
         if sess.collectors and bus is None:
             # a package that names session collectors starts profiling with the deployment
@@ -352,8 +356,17 @@ def serve(args) -> int:
     standby = None
     if world == 1 and listener is not None:
         from .server.restart import HotRestart, Standby, park
-        app.state.restart = HotRestart(server, listener, sys.argv[1:])
         app.state.generation = int(getattr(args, "generation", 0) or 0)
+        snapshot = None
+        svc = getattr(app.state.s, "service", None)
+        if svc is not None and hasattr(getattr(app.state.s, "engine", None), "blocks"):
+            from .engine.prefix_store import default_path, save_prefix_cache
+
+            def snapshot():
+                # the successor starts with this process's cached prefixes
+                path = default_path(getattr(args, "state_dir", None), app.state.generation)
+                return svc.call(lambda e: save_prefix_cache(e, path))["path"]
+        app.state.restart = HotRestart(server, listener, sys.argv[1:], snapshot=snapshot)
         if getattr(args, "standby_fd", None) is not None:
             # this process is a standby: park until the serving process ends
             eng = getattr(app.state.s, "engine", None)
@@ -498,6 +511,9 @@ def main(argv=None) -> int:
                    help="an already listening socket handed over by the process this one replaces")
     s.add_argument("--log-level", default=None)
     s.add_argument("--log-level-http", default=None)
+    s.add_argument("--prefix-cache", default=None,
+                   help="file of a predecessor's cached KV pages to read before serving "
+                        "(written at a hot restart; removed once read)")
     s.add_argument("--state-dir", default=None,
                    help="directory where control programs keep their state across restarts")
     s.add_argument("--role", choices=["mixed", "prefill", "decode"], default=None,

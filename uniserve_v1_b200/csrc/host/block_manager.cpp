@@ -292,6 +292,30 @@ US_API int us_bm_commit(void* h, int page, uint64_t ka, uint64_t kb) {
   return page;
 }
 
+// Committed (content-keyed) device pages, most recently released last: keys_out [cap][2],
+// pages_out [cap].  Pages in use come first (they have no place in the LRU order).  Returns
+// the number written (at most cap).
+US_API int us_bm_enumerate(void* h, uint64_t* keys_out, int* pages_out, int cap) {
+  Pool* p = (Pool*)h;
+  std::lock_guard<std::mutex> g(p->mu);
+  int n = 0;
+  for (int page = 1; page < p->num_pages && n < cap; ++page) {
+    if (p->has_key[page] && !p->in_lru[page]) {
+      keys_out[2 * n] = p->key[page].a;
+      keys_out[2 * n + 1] = p->key[page].b;
+      pages_out[n++] = page;
+    }
+  }
+  for (int page : p->lru) {
+    if (n >= cap) break;
+    if (!p->has_key[page]) continue;
+    keys_out[2 * n] = p->key[page].a;
+    keys_out[2 * n + 1] = p->key[page].b;
+    pages_out[n++] = page;
+  }
+  return n;
+}
+
 US_API void us_bm_stats(void* h, uint64_t* hits, uint64_t* lookups, uint64_t* evictions) {
   Pool* p = (Pool*)h;
   std::lock_guard<std::mutex> g(p->mu);

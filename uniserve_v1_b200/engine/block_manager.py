@@ -33,6 +33,7 @@ def _lib():
         lib.us_bm_hash_chain.argtypes = [vp, vp, ctypes.c_int, ctypes.c_int, vp]
         lib.us_bm_match_prefix.argtypes = [vp, vp, ctypes.c_int, vp]
         lib.us_bm_commit.argtypes = [vp, ctypes.c_int, ctypes.c_uint64, ctypes.c_uint64]
+        lib.us_bm_enumerate.argtypes = [vp, vp, vp, ctypes.c_int]
         lib.us_bm_stats.argtypes = [vp, vp, vp, vp]
         lib.us_bm_refcount.argtypes = [vp, ctypes.c_int]
         lib.us_bm_flush.argtypes = [vp]
@@ -206,6 +207,15 @@ class BlockManager:
         if pages:
             self.release(pages)
         return len(pages)
+
+    def committed(self):
+        """(keys uint64 [n, 2], pages int32 [n]) of every content-keyed device page, the most
+        recently released last."""
+        cap = self.num_pages
+        keys = np.zeros((cap, 2), dtype=np.uint64)
+        pages = np.zeros(cap, dtype=np.int32)
+        n = self.lib.us_bm_enumerate(self.h, keys.ctypes.data, pages.ctypes.data, cap)
+        return keys[:n], pages[:n]
 
     def commit(self, page: int, key) -> int:
         if not self.enable_prefix_cache:

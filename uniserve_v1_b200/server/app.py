@@ -816,6 +816,31 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         s.obs.event("profile", **{k: v for k, v in out.items() if k in ("open", "path")})
         return out
 
+    @app.post("/admin/prefix_cache")
+    async def admin_prefix_cache(request: Request):
+        """``{"action": "save" | "load", "path": FILE}``: writes the cached KV pages to a file
+        or reads such a file into the cache (a restart by hand keeps its prefixes)."""
+        if s.service is None or not hasattr(s.engine, "blocks"):
+            return _err(409, "this deployment has no paged engine")
+        try:
+            body = await request.json()
+            action, path = body["action"], str(body["path"])
+        except Exception:
+            return _err(400, 'body: {"action": "save" | "load", "path": FILE}')
+        from ..engine.prefix_store import load_prefix_cache, save_prefix_cache
+        if action == "save":
+            fn = lambda e: save_prefix_cache(e, path, int(body.get("max_bytes", 1 << 30)))
+        elif action == "load":
+            fn = lambda e: load_prefix_cache(e, path, remove=bool(body.get("remove", False)))
+        else:
+            return _err(400, "action is save or load", param="action")
+        try:
+            out = await asyncio.to_thread(s.service.call, fn)
+        except OSError as e:
+            return _err(400, str(e), param="path")
+        s.obs.event("prefix_cache", action=action, pages=out.get("pages", 0))
+        return out
+
     @app.post("/admin/sleep")
     async def admin_sleep(level: int = 1):
         """Frees the KV cache and graphs (level 1) and the weights too (level 2); requests in

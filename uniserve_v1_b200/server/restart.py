@@ -4,7 +4,8 @@ the listening socket over while the process it replaces finishes the requests it
 ``POST /admin/restart`` starts ``python -m uniserve_v1_b200 serve ... --listen-fd N --ready-fd M``
 with the listening socket and one end of a pipe inherited.  The successor loads the model,
 starts serving on the SAME socket (both processes accept from one kernel queue for a moment)
-and writes a line to the pipe; this process then stops accepting and exits once its
+and writes a line to the pipe (before that it reads the file of cached KV pages this process
+wrote for it, ``--prefix-cache``: what was cached stays cached); this process then stops accepting and exits once its
 connections have ended.  No connection is refused: one that arrives meanwhile waits in the
 listener's queue until one of the two accepts it.  If the successor exits before it reports,
 this process keeps serving as before.  The successor needs its own share of the GPU's memory
@@ -27,10 +28,13 @@ from typing import Optional
 
 
 class HotRestart:
-    def __init__(self, server, listener, argv: list):
+    def __init__(self, server, listener, argv: list, snapshot=None):
+        """``snapshot()``: writes this process's cached KV pages to a file and returns its
+        path (``engine/prefix_store.py``); the successor reads it before it serves."""
         self.server, self.listener = server, listener
+        self.snapshot = snapshot
         # the successor repeats this process's command line without hand-over arguments
-        self.argv = self._strip(argv, ("--listen-fd", "--ready-fd"))
+        self.argv = self._strip(argv, ("--listen-fd", "--ready-fd", "--prefix-cache"))
         self.state = "serving"          # serving | starting | handed_over | failed
         self.successor: Optional[int] = None
         self.error: Optional[str] = None
@@ -61,6 +65,11 @@ class HotRestart:
         fd = self.listener.fileno()
         cmd = [sys.executable, "-m", "uniserve_v1_b200"] + self.argv + \
             ["--listen-fd", str(fd), "--ready-fd", str(w)]
+        if self.snapshot is not None:
+            try:
+                cmd += ["--prefix-cache", self.snapshot()]
+            except Exception as e:       # the restart goes on with a cold cache
+                self.error = f"prefix cache not saved: {e}"
         env = dict(os.environ)
         for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
             env.pop(k, None)
