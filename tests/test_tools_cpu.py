@@ -306,6 +306,50 @@ def test_admin_client(live_server, capsys):
     assert main(["admin", "--url", live_server, "query", "drop table events"]) == 1
 
 
+def test_admin_client_status_watch_and_apply_over_several_nodes(live_server, tmp_path, capsys):
+    """The manager's verbs: `status` tables every node (an unreachable one fails the exit
+    status), `watch` prints a line per change, `apply` puts a policy on every node and puts
+    the nodes already changed back when one refuses."""
+    import json
+    from uniserve_v1_b200.__main__ import main
+    other, other_srv, other_th, _eng = _start_chat_server()
+    dead = f"http://127.0.0.1:{_free_port()}"
+    try:
+        assert main(["admin", "--url", live_server, "--url", other, "status"]) == 0
+        rows = json.loads(capsys.readouterr().out)
+        assert [r["status"] for r in rows] == ["ok", "ok"] and rows[0]["model"] == "tiny"
+        assert main(["admin", "--url", live_server, "--url", dead, "status"]) == 1
+        assert json.loads(capsys.readouterr().out)[1]["status"] == "unreachable"
+        assert main(["admin", "--url", live_server, "--url", other, "--interval", "0.05",
+                     "--count", "3", "watch"]) == 0
+        lines = [json.loads(x) for x in capsys.readouterr().out.strip().splitlines()]
+        assert len(lines) == 2 and {x["url"] for x in lines} == {live_server, other}
+
+        good = tmp_path / "good.toml"
+        good.write_text('model = "random:tiny"\nserved_model_name = "tiny"\n'
+                        '[scheduler_config]\nmax_batch = 3\n')
+        assert main(["admin", "--url", live_server, "--url", other, "apply", str(good)]) == 0
+        capsys.readouterr()
+        for u in (live_server, other):
+            assert main(["admin", "--url", u, "get-policy"]) == 0
+            assert json.loads(capsys.readouterr().out)["config"]["scheduler_config"]["max_batch"] == 3
+        # the second node is gone: the first one returns to what it served
+        other_srv.should_exit = True
+        other_th.join(timeout=10)
+        back = tmp_path / "back.toml"
+        back.write_text('model = "random:tiny"\nserved_model_name = "tiny"\n'
+                        '[scheduler_config]\nmax_batch = 5\n')
+        bad = tmp_path / "bad.toml"
+        bad.write_text('model = "random:tiny"\nserved_model_name = "tiny"\nno_such_option = 1\n')
+        assert main(["admin", "--url", live_server, "apply", str(bad)]) == 1
+        capsys.readouterr()
+        assert main(["admin", "--url", live_server, "get-policy"]) == 0
+        assert json.loads(capsys.readouterr().out)["config"]["scheduler_config"]["max_batch"] == 3
+    finally:
+        other_srv.should_exit = True
+        other_th.join(timeout=10)
+
+
 def test_block_manager_bounded_exhaustive_check_and_mutants():
     """Every operation sequence up to depth 4 on a 5-page pool keeps the invariants of the
     native block manager; each deliberately broken variant is flagged."""

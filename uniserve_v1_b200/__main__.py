@@ -12,6 +12,7 @@ import json
 import logging
 import os
 import sys
+import time
 
 
 def serve(args) -> int:
@@ -471,25 +472,100 @@ def keep(args) -> int:
 
 def admin(args) -> int:
     """Admin client over plain HTTP (crates/manager/src/main.rs:1-25, reference project
-    path): prints the server's JSON answer; exit status 1 on an HTTP error."""
+    path): prints the server's JSON answer; exit status 1 on an HTTP error.  ``status``,
+    ``watch`` and ``apply`` take several ``--url`` and treat them as one deployment: the state
+    of every node in one table, a line per change, and a policy put on every node with the
+    nodes already changed put back when one refuses."""
     import urllib.error
     import urllib.request
     head = {"Authorization": f"Bearer {args.api_key}"} if args.api_key else {}
-    if args.verb == "get-policy":
-        req = urllib.request.Request(args.url + "/admin/policy", headers=head)
-    elif args.verb == "health":
-        req = urllib.request.Request(args.url + "/health", headers=head)
-    elif args.verb == "put-policy":
+    urls = args.url or ["http://127.0.0.1:8000"]
+
+    def call(url, path, data=None, method=None, ctype=None, timeout=60):
+        h = dict(head, **({"Content-Type": ctype} if ctype else {}))
+        req = urllib.request.Request(url + path, data=data, method=method, headers=h)
+        with urllib.request.urlopen(req, timeout=timeout) as r:
+            return r.read().decode()
+
+    def node_state(url) -> dict:
+        row = {"url": url}
+        try:
+            h = json.loads(call(url, "/health", timeout=10))
+            row.update(status=h.get("status"), pid=h.get("pid"), generation=h.get("generation"),
+                       asleep=h.get("asleep"), uptime_s=round(h.get("uptime_seconds", 0.0), 1))
+        except urllib.error.HTTPError as e:
+            row.update(status=f"http {e.code}")
+            return row
+        except Exception as e:
+            row.update(status="unreachable", error=type(e).__name__)
+            return row
+        try:
+            pol = json.loads(call(url, "/admin/policy", timeout=10))
+            row.update(revision=pol.get("revision"), model=pol.get("config", {}).get("served_model_name"),
+                       paused=pol.get("config", {}).get("paused"))
+        except Exception:
+            pass
+        return row
+
+    if args.verb == "status":
+        rows = [node_state(u) for u in urls]
+        print(json.dumps(rows, indent=1))
+        return 0 if all(r.get("status") == "ok" for r in rows) else 1
+    if args.verb == "watch":
+        # one line per node whose state changed; --count polls (0 = until interrupted)
+        last, n = {}, 0
+        try:
+            while True:
+                for u in urls:
+                    row = node_state(u)
+                    key = {k: v for k, v in row.items() if k != "uptime_s"}
+                    if last.get(u) != key:
+                        last[u] = key
+                        print(json.dumps(dict(row, at=round(time.time(), 1))), flush=True)
+                n += 1
+                if args.count and n >= args.count:
+                    return 0
+                time.sleep(args.interval)
+        except KeyboardInterrupt:
+            return 0
+    if args.verb == "apply":
         body = open(args.arg, "rb").read()
-        req = urllib.request.Request(args.url + "/admin/policy", data=body, method="PUT",
-                                     headers=dict(head, **{"Content-Type": "application/toml"}))
-    else:
-        req = urllib.request.Request(args.url + "/admin/query", data=(args.arg or "").encode(),
-                                     method="POST",
-                                     headers=dict(head, **{"Content-Type": "text/plain"}))
+        before, done = {}, []
+        for u in urls:              # what to put back if a later node refuses
+            try:
+                before[u] = json.loads(call(u, "/admin/policy", timeout=10)).get("toml")
+            except Exception:
+                before[u] = None
+        for u in urls:
+            try:
+                out = call(u, "/admin/policy", data=body, method="PUT", ctype="application/toml")
+                done.append(u)
+                print(json.dumps({"url": u, "applied": json.loads(out).get("revision")}))
+            except urllib.error.HTTPError as e:
+                print(json.dumps({"url": u, "refused": e.read().decode()[:400]}), file=sys.stderr)
+                for d in done:      # the nodes already changed return to what they served
+                    if before.get(d):
+                        try:
+                            call(d, "/admin/policy", data=before[d].encode(), method="PUT",
+                                 ctype="application/toml")
+                            print(json.dumps({"url": d, "restored": True}))
+                        except Exception as e2:
+                            print(json.dumps({"url": d, "restored": False, "error": str(e2)}),
+                                  file=sys.stderr)
+                return 1
+        return 0
+    url = urls[0]
     try:
-        with urllib.request.urlopen(req, timeout=60) as r:
-            print(r.read().decode())
+        if args.verb == "get-policy":
+            print(call(url, "/admin/policy"))
+        elif args.verb == "health":
+            print(call(url, "/health"))
+        elif args.verb == "put-policy":
+            print(call(url, "/admin/policy", data=open(args.arg, "rb").read(), method="PUT",
+                       ctype="application/toml"))
+        else:
+            print(call(url, "/admin/query", data=(args.arg or "").encode(), method="POST",
+                       ctype="text/plain"))
         return 0
     except urllib.error.HTTPError as e:
         print(e.read().decode(), file=sys.stderr)
@@ -529,10 +605,14 @@ def main(argv=None) -> int:
     l = sub.add_parser("layout", help="print the resolved device layout of a package")
     l.add_argument("package")
     ad = sub.add_parser("admin", help="admin client: policy get / put, SQL query")
-    ad.add_argument("--url", default="http://127.0.0.1:8000")
+    ad.add_argument("--url", action="append", default=None,
+                    help="node address (repeat for status / watch / apply over several nodes)")
     ad.add_argument("--api-key", default=None)
-    ad.add_argument("verb", choices=["get-policy", "put-policy", "query", "health"])
-    ad.add_argument("arg", nargs="?", help="config.toml to put, or the SQL text")
+    ad.add_argument("--interval", type=float, default=2.0, help="watch: seconds between polls")
+    ad.add_argument("--count", type=int, default=0, help="watch: polls before it ends (0: none)")
+    ad.add_argument("verb", choices=["get-policy", "put-policy", "query", "health", "status",
+                                     "watch", "apply"])
+    ad.add_argument("arg", nargs="?", help="config.toml to put / apply, or the SQL text")
     r = sub.add_parser("route", help="one address in front of data-parallel replicas")
     r.add_argument("--listen", default="127.0.0.1:8000")
     r.add_argument("--replica", action="append", default=[], help="base URL of a mixed replica")

@@ -684,8 +684,9 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
     # ------------------------------------------------------------------ admin --
     @app.get("/admin/policy")
     async def get_policy():
+        from ..config.policy import dump_toml
         return {"config": s.package.raw, "layout": s.package.layout(),
-                "revision": s.obs.revision}
+                "revision": s.obs.revision, "toml": dump_toml(s.package.raw)}
 
     def apply_package(new: Package, writer: str = "admin"):
         """Applies a parsed package: in place for step / order effects, as an epoch update
