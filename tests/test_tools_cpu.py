@@ -908,6 +908,7 @@ def test_profile_session_collectors_and_admin_route(tmp_path):
     assert summ["kernels"] and all(v["count"] >= 1 for v in summ["kernels"].values())
     tr = P.to_trace([s])
     assert any(e["tid"].startswith("host_ops:") for e in tr["traceEvents"])
+    assert P.main(["timeline", path, "--limit", "5"]) == 0
     with pytest.raises(ValueError, match="sampling"):
         StepProfiler("cpu").open(str(tmp_path / "x.sqlite"), collectors=["pc_sampling"])
     with pytest.raises(ValueError, match="unknown collector"):

@@ -2,11 +2,14 @@
 
     python -m uniserve_v1_b200.tools.profile trace session_rank0.sqlite [more ...] -o trace.json
     python -m uniserve_v1_b200.tools.profile summary session_rank0.sqlite
+    python -m uniserve_v1_b200.tools.profile timeline session_rank0.sqlite --limit 100
 
 ``trace`` merges the per-rank session files: host spans become complete events
 on one track per (rank, thread), fence-probe pairs (``X.begin`` / ``X.end`` with
 the same tag) become complete events on a "device" track per rank, counters
-become counter events.  ``summary`` prints per-name totals.
+become counter events, kernel and copy records of the ``timeline`` collector events on a
+track per stream.  ``summary`` prints per-name totals (host spans, device ranges, the heaviest
+kernels), ``timeline`` the records of every track in time order as text.
 
 Reference: tools/profile/src/{perfetto,session,timeline}.rs (reference project paths).
 """
@@ -97,8 +100,28 @@ def main(argv=None) -> int:
     t.add_argument("-o", "--out", required=True)
     s = sub.add_parser("summary")
     s.add_argument("sessions", nargs="+")
+    tl = sub.add_parser("timeline", help="records in time order, as text")
+    tl.add_argument("sessions", nargs="+")
+    tl.add_argument("--limit", type=int, default=200)
     args = ap.parse_args(argv)
     sessions = [load(p) for p in args.sessions]
+    if args.cmd == "timeline":
+        rows = []
+        for ses in sessions:
+            for rank, thread, name, t0, t1, step in ses["spans"]:
+                rows.append((t0, rank, f"host:{thread}", name, (t1 - t0) / 1e3))
+            for rank, base, tag, t0, t1, _ in device_ranges(ses["probes"]):
+                rows.append((t0, rank, "device", f"{base} [{tag}]", (t1 - t0) / 1e3))
+            for rank, name, kind, stream, t0, dur in ses.get("kernels", []):
+                rows.append((t0, rank, f"{kind}:{stream}", name, dur / 1e3))
+        # host spans and probes use the host's monotonic / the device's timer, kernel records
+        # the profiler's clock: each track is ordered in itself
+        rows.sort(key=lambda r: (r[2].split(":")[0], r[0]))
+        for t0, rank, track, name, us in rows[:args.limit]:
+            print(f"{t0 / 1e6:14.3f} ms  rank {rank}  {track:<18} {us:10.1f} us  {name[:90]}")
+        if len(rows) > args.limit:
+            print(f"... {len(rows) - args.limit} more")
+        return 0
     if args.cmd == "trace":
         with open(args.out, "w") as f:
             json.dump(to_trace(sessions), f)
