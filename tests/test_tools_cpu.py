@@ -60,6 +60,24 @@ def test_eval_run_and_checks(live_server):
     assert b2["summary"]["succeeded"] == 2
 
 
+def test_eval_plan_and_list(capsys):
+    """`plan` prints what `run` would send (the same prompts for the same seed), `list` the
+    verbs with what each checks."""
+    import json
+    from uniserve_v1_b200.tools import eval as E
+    assert E.main(["plan", "--requests", "3", "--prompt-tokens", "16", "--seed", "4",
+                   "--stop", "END", "--change", "1.5:policy.toml"]) == 0
+    plan = json.loads(capsys.readouterr().out)
+    assert plan["requests"] == 3 and [i["seed"] for i in plan["items"]] == [4, 5, 6]
+    assert plan["body"]["stop"] == ["END"] and plan["changes"] == [{"at_s": 1.5, "file": "policy.toml"}]
+    assert E.main(["plan", "--requests", "3", "--prompt-tokens", "16", "--seed", "4"]) == 0
+    again = json.loads(capsys.readouterr().out)
+    assert [i["prompt_sha256"] for i in again["items"]] == [i["prompt_sha256"] for i in plan["items"]]
+    assert E.main(["list"]) == 0
+    assert {"run", "plan", "compare", "check-change", "check-stop", "check-faults"} <= \
+        set(json.loads(capsys.readouterr().out))
+
+
 def test_eval_check_rules():
     from uniserve_v1_b200.tools import eval as E
     rec = dict(index=0, ok=True, status=200, error=None, latency_s=1.0, ttft_s=0.1,

@@ -321,6 +321,16 @@ def main(argv=None) -> int:
     r.add_argument("--out")
     r.add_argument("--change", action="append", default=[], metavar="SECONDS:FILE",
                    help="PUT the policy text of FILE to /admin/policy SECONDS into the load")
+    pl = sub.add_parser("plan", help="what `run` would send, without sending it")
+    for flag, kw in (("--concurrency", dict(type=int, default=8)), ("--requests", dict(type=int, default=32)),
+                     ("--prompt-tokens", dict(type=int, default=128)),
+                     ("--max-tokens", dict(type=int, default=128)), ("--seed", dict(type=int, default=0)),
+                     ("--model", dict(default="default")), ("--temperature", dict(type=float, default=0.0))):
+        pl.add_argument(flag, **kw)
+    pl.add_argument("--stop", action="append")
+    pl.add_argument("--no-stream", action="store_true")
+    pl.add_argument("--change", action="append", default=[], metavar="SECONDS:FILE")
+    sub.add_parser("list", help="the verbs and what each checks")
     cc = sub.add_parser("check-change")
     cc.add_argument("run")
     cc.add_argument("control")
@@ -336,6 +346,33 @@ def main(argv=None) -> int:
         s = sub.add_parser(name)
         s.add_argument("bundle")
     args = ap.parse_args(argv)
+    if args.cmd == "list":
+        print(json.dumps({
+            "run": "concurrent chat requests with synthetic prompts; a bundle of per-request "
+                   "records (tokens, latencies, finish reasons, usage) and a summary",
+            "plan": "the requests `run` would send (prompt digests, seeds, bodies) and its policy changes",
+            "compare": "two bundles: same outputs per request index, throughput and latency within a tolerance",
+            "compare-accuracy": "two accuracies on n items: difference against the binomial noise",
+            "check-change": "a run with policy changes against its control: no request lost or altered by a change",
+            "check-stop": "stop strings end the text where they first occur and are not part of it",
+            "check-faults": "every request finished or failed with an error body; none hung"}, indent=1))
+        return 0
+    if args.cmd == "plan":
+        import hashlib
+        prompts = [synth_prompt(random.Random(args.seed * 1000003 + i), args.prompt_tokens)
+                   for i in range(args.requests)]
+        plan = {"requests": args.requests, "concurrency": args.concurrency,
+                "stream": not args.no_stream,
+                "body": {"model": args.model, "max_tokens": args.max_tokens,
+                         "temperature": args.temperature, "ignore_eos": True,
+                         **({"stop": args.stop} if args.stop else {})},
+                "items": [{"index": i, "seed": args.seed + i, "prompt_chars": len(p),
+                           "prompt_sha256": hashlib.sha256(p.encode()).hexdigest()[:16]}
+                          for i, p in enumerate(prompts)],
+                "changes": [{"at_s": float(c.split(":", 1)[0]), "file": c.split(":", 1)[1]}
+                            for c in args.change]}
+        print(json.dumps(plan, indent=1))
+        return 0
     if args.cmd == "run":
         b = asyncio.run(run_load(args.url, args.concurrency, args.requests, args.prompt_tokens,
                                  args.max_tokens, not args.no_stream, args.api_key, args.model,
