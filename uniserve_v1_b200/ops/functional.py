@@ -177,7 +177,8 @@ def decode_persist_ok(B: int, Hq: int, Hkv: int, D: int, page_size: int, window:
     """Whether the persistent decode-attention kernel serves this case (bf16 pages, head width
     128, pages dividing 128, no sliding window, at most 1024 sequences)."""
     return (DECODE_PERSIST and not DECODE_SIMT and not fp8 and D == 128 and 128 % page_size == 0
-            and page_size >= 8 and Hq // Hkv <= 16 and not window and B <= 1024)
+            and page_size >= 8 and Hq % Hkv == 0 and Hq // Hkv in (1, 2, 4, 8, 16)
+            and not window and B <= 1024)
 
 
 def decode_persist_scratch(B: int, Hkv: int, device):
