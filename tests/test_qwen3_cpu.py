@@ -582,3 +582,36 @@ def test_prefix_cache_outlives_the_engine_through_a_file(tmp_path, kv_dtype):
     with open(path, "wb") as f:
         f.write(b"not a cache file")
     assert load_prefix_cache(engine(), path)["refused"] == "not a prefix-cache file"
+
+
+def test_persistent_decode_partition_covers_every_tile_and_names_its_partials():
+    """The work partition of the persistent decode-attention kernel, restated on the host and
+    enumerated over random batches: every tile of every (sequence, kv head) pair is in exactly
+    one segment, a range has at most two partial segments (its first and its last), and the
+    slots a merging CTA derives from the partition alone are the slots the partial segments
+    were written to, one arrival per range the pair spans."""
+    import random
+    from uniserve_v1_b200.ops import reference as R
+    rng = random.Random(7)
+    for _ in range(400):
+        B, Hkv = rng.randint(1, 40), rng.choice([1, 2, 4, 8])
+        lens = [rng.choice([0, 1, 100, 128, 129, 500, 1100, 4000, rng.randint(0, 3000)])
+                for _ in range(B)]
+        n = rng.choice([1, 2, 7, 148])
+        ranges = R.persist_segments(lens, Hkv, n)
+        tiles = [(l + 127) // 128 for l in lens]
+        seen, partial = {}, {}
+        for c, segs in enumerate(ranges):
+            assert segs, "no range is empty"
+            assert sum(1 for s in segs if not s[4]) <= 2
+            for k, (b, hk, t0, count, whole, slot) in enumerate(segs):
+                for t in range(t0, t0 + count):
+                    assert (b, hk, t) not in seen
+                    seen[(b, hk, t)] = c
+                if not whole:
+                    assert k in (0, len(segs) - 1) and slot == (0 if k == 0 else 1)
+                    partial.setdefault((b, hk), []).append((c, slot))
+        assert len(seen) == Hkv * sum(tiles)
+        for (b, hk), written in partial.items():
+            assert R.persist_merge_slots(lens, Hkv, n, b, hk) == sorted(written)
+            assert len(written) >= 2

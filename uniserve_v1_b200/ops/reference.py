@@ -343,3 +343,62 @@ def embedding(ids, table, vocab_lo=0, vocab_hi=None):
     local = (ids - vocab_lo).clamp(0, table.shape[0] - 1).long()
     out = table[local]
     return out * ok[:, None].to(out.dtype)
+
+
+def persist_segments(seq_lens, Hkv: int, n_cta: int, tile: int = 128):
+    """The work partition of the persistent decode-attention kernel
+    (``csrc/attn_decode_persist.cu``), restated on the host: the tiles of all (sequence, kv
+    head) pairs form one list ordered by (sequence, kv head, tile); range c of ``n`` =
+    min(n_cta, tiles) takes tiles [c T // n, (c + 1) T // n).  Returns, per range, its
+    segments ``(b, hk, first_tile, count, whole, slot)``: ``whole`` segments cover their pair
+    and are written directly, the others leave a partial result in ``slot`` (0: the range's
+    first segment, 1: a later one, which is then its last) and arrive at the pair's counter."""
+    tiles = [(int(l) + tile - 1) // tile for l in seq_lens]
+    pre = [0]
+    for t in tiles:
+        pre.append(pre[-1] + t)
+    total = Hkv * pre[-1]
+    if total == 0:
+        return []
+    n = min(n_cta, total)
+    pairs = [(b, hk) for b in range(len(tiles)) if tiles[b] for hk in range(Hkv)]
+    where = []                                   # tile index -> (pair index, tile of the pair)
+    for i, (b, _) in enumerate(pairs):
+        where.extend((i, t) for t in range(tiles[b]))
+    out = []
+    for c in range(n):
+        g, g1 = (c * total) // n, ((c + 1) * total) // n
+        segs = []
+        while g < g1:
+            i, t0 = where[g]
+            b, hk = pairs[i]
+            count = min(tiles[b] - t0, g1 - g)
+            whole = t0 == 0 and count == tiles[b]
+            segs.append((b, hk, t0, count, whole, 0 if not segs else 1))
+            g += count
+        out.append(segs)
+    return out
+
+
+def persist_merge_slots(seq_lens, Hkv: int, n_cta: int, b: int, hk: int, tile: int = 128):
+    """(range, slot) of every partial result of pair (b, hk), as the merging CTA derives them
+    from the partition alone: the ranges from the one that holds the pair's first tile to the
+    one that holds its last; slot 0 where the range starts inside the pair, else 1."""
+    tiles = [(int(l) + tile - 1) // tile for l in seq_lens]
+    pre = [0]
+    for t in tiles:
+        pre.append(pre[-1] + t)
+    total = Hkv * pre[-1]
+    n = min(n_cta, total)
+    start = lambda c: (c * total) // n
+
+    def cta_of(g):
+        c = (g * n) // total
+        while c + 1 < n and start(c + 1) <= g:
+            c += 1
+        while c > 0 and start(c) > g:
+            c -= 1
+        return c
+    begin = Hkv * pre[b] + hk * tiles[b]
+    last = begin + tiles[b] - 1
+    return [(c, 0 if start(c) >= begin else 1) for c in range(cta_of(begin), cta_of(last) + 1)]
