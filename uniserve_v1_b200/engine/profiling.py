@@ -307,6 +307,8 @@ def start_session(engine, collectors, output: Optional[str] = None, steps: Optio
                               f"uniserve-profile-{os.getpid()}-{int(time.time())}-rank{rank}.sqlite")
     elif os.path.isdir(output):
         output = os.path.join(output, f"rank{rank}.sqlite")
+    if "timeline" in collectors and not steps and not seconds:
+        seconds = 30.0         # activity records accumulate in memory: a timeline is a window
     prof.open(output, {"pid": os.getpid()}, collectors=collectors,
               max_steps=int(steps) if steps else None,
               max_seconds=float(seconds) if seconds else None)
