@@ -133,7 +133,8 @@ class VideoService:
         self.world, self.rank, self.group = ax.size, ax.rank, ax.group
         self.h2d_bytes = self.d2h_bytes = 0
         self.time_phases = False
-        self._copy_stream = None          # device -> host copies that overlap the audio decoder
+        self._copy_stream = None          # device -> host copies of the planes
+        self._audio_stream = None         # the audio decoder beside the video decoder
         self._pinned = None               # pinned host buffer of the encoded planes, reused
         self.denoiser = Denoiser(transformer)
         self.steps = self.denoiser.steps
@@ -327,6 +328,18 @@ class VideoService:
             job.step = st.step
             job.progress = 0.8 * st.step / self.denoiser.steps
             self._save_trajectory(job, st)
+        # the audio decoder (rank 0 only needs the samples) starts on a stream of its own and
+        # runs beside the video decoder instead of after it
+        wav, wav_done = None, None
+        if self.rank == 0 and st.audio.is_cuda:
+            if self._audio_stream is None:
+                self._audio_stream = torch.cuda.Stream(device=st.audio.device)
+            self._audio_stream.wait_stream(torch.cuda.current_stream(st.audio.device))
+            with torch.cuda.stream(self._audio_stream):
+                wav = self._decode_audio(st, cfg, p)
+                wav_done = torch.cuda.Event()
+                wav_done.record(self._audio_stream)
+            st.audio.record_stream(self._audio_stream)
         self._enter(job, "VideoDecode")
         units = self.video_vae.decode(st.video, self.rank, self.world)
         planes = []
@@ -352,15 +365,14 @@ class VideoService:
                 landed.record(self._copy_stream)
             packed.record_stream(self._copy_stream)
         self._enter(job, "AudioDecode")
-        # audio rows are [time x 2 channels, latent_channels]: split channels into the batch
-        a = st.audio.view(-1, 2, cfg.audio_channels).permute(1, 2, 0).contiguous()
-        wav = self.audio_vae.decode(a)
-        want = int(round(p.num_frames / p.fps * self.audio_vae.cfg.sample_rate))
-        wav = wav[:, :want] if wav.shape[1] >= want else torch.nn.functional.pad(
-            wav, (0, want - wav.shape[1]))
-        self._enter(job, "VideoEncode")
         if self.rank != 0:
             return b""
+        if wav_done is not None:
+            torch.cuda.current_stream(wav.device).wait_event(wav_done)
+            wav.record_stream(torch.cuda.current_stream(wav.device))
+        else:
+            wav = self._decode_audio(st, cfg, p)
+        self._enter(job, "VideoEncode")
         hw = p.height * p.width
         if landed is not None:
             landed.synchronize()
@@ -377,6 +389,15 @@ class VideoService:
         mp4 = M.write_mp4(y, u, v, p.fps, pcm, self.audio_vae.cfg.sample_rate)
         self._enter(job, "Done")
         return mp4
+
+    def _decode_audio(self, st, cfg, p) -> torch.Tensor:
+        """The clip's samples [2, n] from the audio latents (rows are [time x 2 channels,
+        latent_channels]: the channels go into the batch), cut or padded to the clip's length."""
+        a = st.audio.view(-1, 2, cfg.audio_channels).permute(1, 2, 0).contiguous()
+        wav = self.audio_vae.decode(a)
+        want = int(round(p.num_frames / p.fps * self.audio_vae.cfg.sample_rate))
+        return wav[:, :want] if wav.shape[1] >= want else torch.nn.functional.pad(
+            wav, (0, want - wav.shape[1]))
 
     def _pinned_planes(self, shape) -> torch.Tensor:
         """A pinned host buffer for the packed planes of a clip (kept across requests: pinning
