@@ -691,8 +691,9 @@ def test_hot_restart_hands_the_listener_to_a_successor(tmp_path):
 
 def test_standby_is_promoted_when_the_serving_process_dies(tmp_path):
     """`profiling_config.standby`: a parked second process with the model loaded takes the
-    listening socket when the serving process is killed, serves as generation 1 and parks a
-    standby of its own."""
+    listening socket when the serving process is killed, serves as generation 1 - starting
+    from the serving process's last snapshot of its cached KV pages - and parks a standby of
+    its own."""
     import json
     import os
     import signal
@@ -704,14 +705,15 @@ def test_standby_is_promoted_when_the_serving_process_dies(tmp_path):
     pkg.mkdir()
     (pkg / "config.toml").write_text('model = "random:tiny"\nserved_model_name = "tiny"\n'
                                      f'[admin_config]\nhost = "127.0.0.1"\nport = {port}\n'
-                                     '[profiling_config]\nstandby = true\n')
+                                     '[profiling_config]\nstandby = true\nstandby_snapshot = 0.3\n')
     env = dict(os.environ, UNISERVE_CPU_RANKS="1")
     env.pop("RANK", None)
     proc = subprocess.Popen([sys.executable, "-m", "uniserve_v1_b200", "serve", str(pkg)], env=env,
                             cwd=os.path.dirname(os.path.dirname(__file__)))
     base = f"http://127.0.0.1:{port}"
-    body = json.dumps({"model": "tiny", "messages": [{"role": "user", "content": "hello there"}],
-                       "max_tokens": 8, "temperature": 0, "ignore_eos": True}).encode()
+    body = json.dumps({"model": "tiny", "max_tokens": 8, "temperature": 0, "ignore_eos": True,
+                       "messages": [{"role": "user", "content": "hello there, " * 16}]}).encode()
+    cached = []
 
     def get(path):
         with urllib.request.urlopen(base + path, timeout=5) as r:
@@ -721,7 +723,9 @@ def test_standby_is_promoted_when_the_serving_process_dies(tmp_path):
         req = urllib.request.Request(base + "/v1/chat/completions", data=body,
                                      headers={"Content-Type": "application/json"})
         with urllib.request.urlopen(req, timeout=120) as r:
-            return json.loads(r.read())["choices"][0]["message"]["content"]
+            out = json.loads(r.read())
+        cached.append(out["usage"]["prompt_tokens_details"]["cached_tokens"])
+        return out["choices"][0]["message"]["content"]
     pids = []
     try:
         sb = {"state": "none"}
@@ -737,6 +741,7 @@ def test_standby_is_promoted_when_the_serving_process_dies(tmp_path):
         pids.append(sb["pid"])
         assert get("/health")["generation"] == 0
         want = chat()
+        time.sleep(1.5)                                 # a snapshot of the cached pages is taken
         os.kill(proc.pid, signal.SIGKILL)               # the serving process dies
         proc.wait(timeout=30)
         h = None
@@ -750,6 +755,8 @@ def test_standby_is_promoted_when_the_serving_process_dies(tmp_path):
             time.sleep(0.25)
         assert h and h["pid"] == sb["pid"] and h["generation"] == 1
         assert chat() == want
+        # the promoted standby read the last snapshot: its first request finds the prompt cached
+        assert cached[0] == 0 and cached[1] >= 64, cached
         for _ in range(360):                            # and it parks its own standby
             nxt = get("/admin/standby")
             if nxt["state"] == "parked":

@@ -371,14 +371,24 @@ def serve(args) -> int:
         if getattr(args, "standby_fd", None) is not None:
             # this process is a standby: park until the serving process ends
             eng = getattr(app.state.s, "engine", None)
+            from .server.restart import PrefixSnapshots
             if not park(args.standby_fd, args.ready_fd, eng,
-                        pkg.profiling_config.standby_storage):
+                        pkg.profiling_config.standby_storage,
+                        PrefixSnapshots.path_for(listener, getattr(args, "state_dir", None))):
                 return 0
             args.ready_fd = None
         if pkg.profiling_config.standby:
             standby = Standby(listener, sys.argv[1:], app.state.generation)
             standby.start()
             app.state.standby = standby
+            period = float(pkg.profiling_config.standby_snapshot)
+            if period > 0 and svc is not None and hasattr(getattr(app.state.s, "engine", None),
+                                                          "blocks"):
+                from .server.restart import PrefixSnapshots
+                snaps = PrefixSnapshots(svc, PrefixSnapshots.path_for(
+                    listener, getattr(args, "state_dir", None)), period)
+                snaps.start()
+                app.state.prefix_snapshots = snaps
     supervision = None
     if children and listener is not None:
         # the leader watches the ranks it started; a rank that ends takes the deployment

@@ -209,6 +209,8 @@ class ProfilingConfig:
     watchdog_timeout: Duration = opt(Duration(150.0), "step")
     standby: bool = opt(False, "daemon", "keep a parked standby process beside the serving one")
     standby_storage: str = opt("auto", "daemon", "resident | suspended | auto")
+    standby_snapshot: Duration = opt(Duration(0.0), "daemon",
+                                     "period of the prefix-cache snapshots a standby starts from (0: none)")
     session: ProfilingSession = optf(ProfilingSession, "step")
 
 

@@ -190,10 +190,46 @@ class Standby:
         return {"state": self.state, "pid": self.pid, "generation": self.generation}
 
 
-def park(standby_fd: int, ready_fd: Optional[int], engine, storage: str) -> bool:
+class PrefixSnapshots:
+    """The serving process of a deployment with a standby writes its cached KV pages to a
+    file every ``period_s`` seconds (``engine/prefix_store.py``, at most ``max_bytes``), so
+    that a standby promoted after the process died starts with the prefixes of the last
+    snapshot instead of an empty cache.  The file is named after the listening port, which
+    the two processes share."""
+
+    def __init__(self, service, path: str, period_s: float, max_bytes: int = 256 << 20):
+        self.service, self.path, self.period_s, self.max_bytes = service, path, period_s, max_bytes
+        self.written = 0
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True, name="prefix-snapshots")
+
+    @staticmethod
+    def path_for(listener, state_dir: Optional[str]) -> str:
+        base = state_dir or ("/dev/shm" if os.path.isdir("/dev/shm") else "/tmp")
+        return os.path.join(base, f"uniserve-prefix-port{listener.getsockname()[1]}.kv")
+
+    def start(self) -> None:
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+
+    def _run(self) -> None:
+        from ..engine.prefix_store import save_prefix_cache
+        while not self._stop.wait(self.period_s):
+            try:
+                self.service.call(lambda e: save_prefix_cache(e, self.path, self.max_bytes))
+                self.written += 1
+            except Exception:       # an engine that sleeps or restarts: try again next period
+                pass
+
+
+def park(standby_fd: int, ready_fd: Optional[int], engine, storage: str,
+         prefix_path: Optional[str] = None) -> bool:
     """The standby's side: release what ``storage`` says, report, block until the serving
     process ends.  Returns True when this process is to serve now, False when it was told to
-    leave."""
+    leave.  With ``prefix_path`` the promoted standby reads the serving process's last
+    snapshot of cached KV pages before it serves."""
     suspended = storage in ("suspended", "auto") and engine is not None and hasattr(engine, "sleep")
     if suspended:
         engine.sleep(1)
@@ -211,6 +247,11 @@ def park(standby_fd: int, ready_fd: Optional[int], engine, storage: str) -> bool
     os.close(standby_fd)
     if suspended:
         engine.wake()
+    if prefix_path and engine is not None and hasattr(engine, "blocks") and \
+            os.path.exists(prefix_path):
+        from ..engine.prefix_store import load_prefix_cache
+        got = load_prefix_cache(engine, prefix_path, remove=False)
+        print(f"standby: prefix cache {got}", file=sys.stderr)
     return True
 
 
