@@ -420,7 +420,9 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
             salt = req.cache_salt or req.prompt_cache_key
 
             def look(e):
-                blocks = e.blocks
+                blocks = getattr(e, "blocks", None)       # engines without a paged cache hold nothing
+                if blocks is None or not hasattr(blocks, "peek_prefix"):
+                    return 0
                 return blocks.peek_prefix(blocks.page_keys(ids, salt)) * blocks.page_size
             cached = await asyncio.to_thread(s.service.call, look)
             return {"cached_tokens": int(cached), "prompt_tokens": len(ids),
