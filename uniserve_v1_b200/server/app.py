@@ -421,7 +421,9 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
 
             def look(e):
                 blocks = getattr(e, "blocks", None)       # engines without a paged cache hold nothing
-                if blocks is None or not hasattr(blocks, "peek_prefix"):
+                # a look-up touches the cache's recency order: on a replicated (multi-rank)
+                # engine only commands that every rank applies may do that
+                if blocks is None or not hasattr(blocks, "peek_prefix") or hasattr(e, "bus"):
                     return 0
                 return blocks.peek_prefix(blocks.page_keys(ids, salt)) * blocks.page_size
             cached = await asyncio.to_thread(s.service.call, look)
