@@ -827,6 +827,9 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         or reads such a file into the cache (a restart by hand keeps its prefixes)."""
         if s.service is None or not hasattr(s.engine, "blocks"):
             return _err(409, "this deployment has no paged engine")
+        if hasattr(s.engine, "bus"):
+            return _err(409, "a multi-rank deployment keeps its ranks' caches in step: its "
+                             "prefix cache is not written or read from outside")
         try:
             body = await request.json()
             action, path = body["action"], str(body["path"])
