@@ -798,6 +798,9 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         ``seconds``.  ``{"close": true}`` ends the open session."""
         if s.service is None:
             return _err(409, "this deployment has no engine")
+        if hasattr(s.engine, "bus"):
+            return _err(409, "a multi-rank deployment runs its ranks in lock step: a session on "
+                             "the leader alone would change its step sequence")
         try:
             body = await request.json()
         except Exception:
