@@ -847,6 +847,26 @@ def test_a_dead_rank_takes_the_deployment_through_a_relaunch(tmp_path):
                 proc.kill()
 
 
+def test_weights_keeper_handle_records_are_plain_data():
+    """A device-memory record carries its IPC handle as JSON of integers, booleans and
+    base64 byte strings: it round-trips with its kinds intact, and anything else (a pickle
+    stream, a nested object, a string) is refused rather than constructed."""
+    import base64
+    import pickle
+    import pytest
+    from uniserve_v1_b200.server.weights_keeper import _handle_from_json, _handle_to_json
+    handle = (0, b"\x00\x01\xfehandle" * 4, 1 << 20, 256, b"refcount", 7, b"event" * 13, True)
+    text = _handle_to_json(handle)
+    back = _handle_from_json(text)
+    assert back == handle and [type(x) for x in back] == [type(x) for x in handle]
+    with pytest.raises(TypeError):
+        _handle_to_json((0, 1.5))
+    for bad in (base64.b64encode(pickle.dumps(handle)).decode(), '{"b":"AA=="}', '["text"]',
+                '[{"b":"AA==","c":1}]', '[[1]]', '[{"b":"not base64!"}]', "[" + "1," * 16 + "1]"):
+        with pytest.raises(ValueError):
+            _handle_from_json(bad)
+
+
 def test_weights_keeper_serves_weights_to_restarting_engines(tmp_path):
     """`keep` holds a model's weights in shared memory; engines built by `serve`'s own model
     constructor map them (no second copy, tied tensors stay tied), give the tokens of a model

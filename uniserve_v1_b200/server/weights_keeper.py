@@ -18,15 +18,14 @@ A keeper is tied to one weights identity (model, dtype, parallel layout, rank): 
 that asks with another identity is refused and loads the checkpoint itself.
 
 Reference behaviour: crates/storage-server (weights retained by the Storage Server across
-engine generations; reference project path).  Here the keeper retains weights only; KV pages
-are not retained across processes.
+engine generations; reference project path).  The keeper retains weights only; the content-keyed
+KV pages travel between generations as a file (``engine/prefix_store.py``).
 """
 from __future__ import annotations
 
 import base64
 import json
 import os
-import pickle
 import socket
 import struct
 import threading
@@ -67,6 +66,36 @@ def _plain_fields(record) -> dict:
     """The non-tensor fields of a per-layer weight record (flags such as ``dense``)."""
     return {f.name: getattr(record, f.name) for f in fields(record)
             if isinstance(getattr(record, f.name), (bool, int, float, str))}
+
+
+def _handle_to_json(handle) -> str:
+    """A CUDA IPC storage handle (a flat tuple of integers, booleans and byte strings) as
+    text: byte strings become ``{"b": base64}``.  Nothing but those three kinds is accepted,
+    so reading a record never constructs an object of the sender's choosing."""
+    out = []
+    for x in handle:
+        if isinstance(x, (bytes, bytearray)):
+            out.append({"b": base64.b64encode(bytes(x)).decode()})
+        elif isinstance(x, (bool, int)):
+            out.append(x)
+        else:
+            raise TypeError(f"unexpected field of kind {type(x).__name__} in an IPC handle")
+    return json.dumps(out, separators=(",", ":"))
+
+
+def _handle_from_json(text: str) -> tuple:
+    fields_ = json.loads(text)
+    if not isinstance(fields_, list) or len(fields_) > 16:
+        raise ValueError("not an IPC handle record")
+    out = []
+    for x in fields_:
+        if isinstance(x, dict) and set(x) == {"b"} and isinstance(x["b"], str):
+            out.append(base64.b64decode(x["b"], validate=True))
+        elif isinstance(x, (bool, int)):
+            out.append(x)
+        else:
+            raise ValueError("not an IPC handle record")
+    return tuple(out)
 
 
 def _send(sock, obj) -> None:
@@ -110,7 +139,7 @@ class WeightsKeeper:
             if t.is_cuda:
                 st = t.untyped_storage()
                 handle = st._share_cuda_()
-                rec["cuda"] = base64.b64encode(pickle.dumps(handle)).decode()
+                rec["cuda"] = _handle_to_json(handle)
                 rec["offset"] = t.storage_offset()
                 self._alive.append(t)
             else:
@@ -184,7 +213,7 @@ class WeightsKeeper:
 def _open(rec: dict, device) -> torch.Tensor:
     dtype = _DTYPES[rec["dtype"]]
     if "cuda" in rec:
-        handle = pickle.loads(base64.b64decode(rec["cuda"]))
+        handle = _handle_from_json(rec["cuda"])
         storage = torch.UntypedStorage._new_shared_cuda(*handle)
         t = torch.empty(0, dtype=dtype, device=storage.device)
         return t.set_(storage, rec["offset"], rec["shape"], rec["stride"])
