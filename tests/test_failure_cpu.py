@@ -23,7 +23,7 @@ def _rank(rank, world, port, mode, q):
     from uniserve_v1_b200.parallel.health import Heartbeat, PeerFailure
     store = dist.TCPStore("127.0.0.1", port, world, rank == 0, timeout=__import__("datetime").timedelta(seconds=30))
     dist.init_process_group("gloo", store=store, rank=rank, world_size=world)
-    hb = Heartbeat(store, rank, world, interval_s=0.05, timeout_s=0.6)
+    hb = Heartbeat(store, rank, world, interval_s=0.05, timeout_s=2.0)   # a loaded box may stall a beat
     x = torch.ones(4)
     steps = 0
     try:

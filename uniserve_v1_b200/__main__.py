@@ -281,6 +281,7 @@ def serve(args) -> int:
             attach_fused_tp(model, int(pkg.max_num_batched_tokens or 8192))
 
         def make_engine(pkg=pkg):
+            from .engine.quota import quota_of
             policy = None
             if "scheduling" in pkg.programs:        # the package's own scheduling program
                 from .engine.program import ProgramHost, ProgramPolicy
@@ -298,6 +299,9 @@ def serve(args) -> int:
                             host_kv_gib=pkg.kv_cache_config.host_gib,
                             watchdog_timeout=float(pkg.profiling_config.watchdog_timeout),
                             kv_dtype=pkg.kv_cache_config.dtype,
+                            # an engine built beside one that serves (the target of an epoch
+                            # update) must fit what is left of the device's quota
+                            quota_strict=quota_of(device).usage() > 0,
                             **({"num_pages": 512, "use_graphs": False} if device.type == "cpu" else {}))
             return MR.ReplicatedEngine(eng, bus) if bus is not None and rank == 0 else eng
 

@@ -16,15 +16,21 @@ import os
 
 import itertools
 import time
+import weakref
 from typing import Optional
 
 import torch
 
 from ..models.qwen3_moe import Qwen3MoeModel
 from .block_manager import BlockManager
+from .quota import QuotaExceeded, quota_of
 from .runner import CausalLmRunner
 from .scheduler import Policy, Scheduler, SchedulerConfig
 from .types import ErrorClass, FinishReason, Request, SamplingParams, StepOutput
+
+
+GRAPH_POOL_BYTES = 2 << 30      # captured graphs and their workspaces, per engine on a GPU
+_HOLDERS = itertools.count()
 
 
 class Watchdog:
@@ -66,6 +72,19 @@ def _weight_tensors(model):
                 yield from walk(fp8)
 
 
+def _weights_on(model, device) -> int:
+    """Bytes of a model's weight tensors that live on ``device``'s kind of memory (tied
+    tensors once)."""
+    seen, total = set(), 0
+    for _, name, t in _weight_tensors(model):
+        if str(name).startswith("_"):               # step scratch kept on the model object
+            continue
+        if t.device.type == device.type and id(t) not in seen:
+            seen.add(id(t))
+            total += t.numel() * t.element_size()
+    return total
+
+
 def _set_tensor(holder, name, value) -> None:
     if isinstance(holder, dict):
         holder[name] = value
@@ -81,7 +100,8 @@ class LLMEngine:
                  policy: Optional[Policy] = None, weights_identity: str = "random-init",
                  watchdog_timeout: float = 150.0, host_kv_pages: int = 0,
                  host_kv_ratio: float = 0.0, host_kv_gib: Optional[float] = None,
-                 kv_dtype: Optional[str] = None, pipeline_decode: Optional[bool] = None):
+                 kv_dtype: Optional[str] = None, pipeline_decode: Optional[bool] = None,
+                 quota=None, quota_strict: bool = False):
         self.model = model
         self.device = model.device
         if kv_dtype in ("fp8", "fp8_e4m3", "e4m3"):
@@ -92,6 +112,19 @@ class LLMEngine:
         if num_pages is None:
             num_pages = self._divide_memory(mem_fraction_static, page_size, max_num_seqs,
                                             max_model_len)
+        # the device's ledger: this engine's weights, graph pool and KV cache against the
+        # fraction of the device its deployment may use (engine/quota.py)
+        self.quota = quota if quota is not None else quota_of(self.device)
+        self.quota_holder = f"engine-{os.getpid()}-{next(_HOLDERS)}"
+        self.quota_strict = bool(quota_strict)
+        self.quota_over: Optional[str] = None
+        self._quota_items = {
+            "weights": _weights_on(model, self.device),
+            "graph_pool": GRAPH_POOL_BYTES if (self.device.type == "cuda" and use_graphs) else 0,
+            "cache_segment": int(num_pages) * int(model.kv_bytes_per_page(page_size))}
+        self.quota.state_fraction(self.quota_holder, min(1.0, max(1e-6, mem_fraction_static)))
+        weakref.finalize(self, self.quota.release, self.quota_holder)
+        self._reserve_quota(("weights", "graph_pool", "cache_segment"))
         self.blocks = BlockManager(num_pages, page_size, weights_identity, enable_prefix_cache)
         self.config = SchedulerConfig(max_num_seqs=max_num_seqs,
                                       max_num_batched_tokens=max_num_batched_tokens,
@@ -129,6 +162,32 @@ class LLMEngine:
         self.profiler = None      # engine.profiling.StepProfiler when profiling is on
         self.spec_stats = {"steps": 0, "proposed": 0, "accepted": 0}
 
+    def _reserve_quota(self, items) -> None:
+        """Reserves ``items`` of this engine against the device's ledger.  A strict engine is
+        refused past the limit (``QuotaExceeded``; what it reserved in this call is given
+        back); otherwise the reservation is recorded all the same and ``quota_over`` says
+        what did not fit."""
+        done = []
+        for item in items:
+            n = self._quota_items.get(item, 0)
+            key = f"weights-{id(self.model)}" if item == "weights" else None
+            try:
+                self.quota.reserve(self.quota_holder, item, n, key=key)
+            except QuotaExceeded as e:
+                if self.quota_strict:
+                    for it in done:
+                        self.quota.release(self.quota_holder, it)
+                    raise
+                self.quota.reserve(self.quota_holder, item, n, key=key, force=True)
+                self.quota_over = str(e)
+            done.append(item)
+
+    def retire(self) -> int:
+        """Ends this engine's reservations on the device's ledger (an engine that an update
+        committed away from, a rolled-back target, an engine replaced after a failure).
+        Returns the bytes released."""
+        return self.quota.release(self.quota_holder)
+
     def _divide_memory(self, fraction, page_size, max_num_seqs, max_model_len) -> int:
         """Quota division: what is left of ``fraction`` of the device after the
         weights goes to KV pages (crates/engine/src/memory/division.rs, reference)."""
@@ -138,7 +197,7 @@ class LLMEngine:
             return min(want, 4096)
         free, total = torch.cuda.mem_get_info(self.device)
         used_by_us = total - free
-        budget = int(total * fraction) - used_by_us - (2 << 30)   # graphs + workspaces
+        budget = int(total * fraction) - used_by_us - GRAPH_POOL_BYTES   # graphs + workspaces
         pages = max(64, budget // per_page)
         return int(min(pages, want))
 
@@ -207,6 +266,8 @@ class LLMEngine:
             torch.cuda.synchronize(self.device)
             torch.cuda.empty_cache()
         self.asleep = level
+        for item in ("cache_segment", "graph_pool") + (("weights",) if level >= 2 else ()):
+            self.quota.release(self.quota_holder, item)
         return {"level": level, "freed_bytes": freed}
 
     def wake(self) -> dict:
@@ -214,6 +275,9 @@ class LLMEngine:
         size; graphs are captured again on first use."""
         if not self.asleep:
             return {"level": 0}
+        # the quota first: a strict engine that no longer fits stays asleep, untouched
+        self._reserve_quota(("cache_segment", "graph_pool") +
+                            (("weights",) if self.asleep >= 2 else ()))
         back = {}
         for holder, name, key, dev in self._parked:
             if key not in back:
@@ -453,5 +517,8 @@ class LLMEngine:
                   "waiting": len(self.scheduler.waiting), "h2d_bytes": self.runner.h2d_bytes,
                   "d2h_bytes": self.runner.d2h_bytes,
                   "blocking_calls": dict(self.runner.blocking),
-                  "blocking_seconds": self.runner.blocking_s})
+                  "blocking_seconds": self.runner.blocking_s,
+                  "quota": {"holder": self.quota_holder, "device": self.quota.name,
+                            "bytes": self.quota.usage(self.quota_holder),
+                            "limit": self.quota.limit(), "over": self.quota_over}})
         return s

@@ -773,6 +773,13 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         sup = getattr(app.state, "supervision", None)
         return sup.status() if sup is not None else {"ranks": [], "failed": None}
 
+    @app.get("/admin/quota")
+    async def admin_quota():
+        """The devices' quota ledgers: limit, usage and every engine's reservations by item
+        (weights, cache segment, graph pool), with refusals counted."""
+        from ..engine.quota import all_reports
+        return {"devices": all_reports()}
+
     @app.get("/admin/standby")
     async def admin_standby():
         sb = getattr(app.state, "standby", None)

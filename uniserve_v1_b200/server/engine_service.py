@@ -151,6 +151,9 @@ class EngineService:
             for rid in live:
                 self._deliver(StepOutput(rid, [], True, FinishReason.ERROR, error=str(error)))
             return
+        retire = getattr(self.engine, "retire", None)
+        if retire is not None:                # the failed engine's quota goes to its successor
+            retire()
         self.engine = self.engine_factory()
         with self.lock:
             live = list(self.meta.items())

@@ -29,6 +29,18 @@ from collections import deque
 from typing import Callable, Optional
 
 
+def _retire(engine) -> None:
+    """Ends an engine's reservations on its device's quota ledger (engine/quota.py)."""
+    for e in (engine, getattr(engine, "engine", None)):
+        retire = getattr(e, "retire", None) if e is not None else None
+        if callable(retire):
+            try:
+                retire()
+            except Exception:
+                pass
+            return
+
+
 class StepClock:
     """Moving record of an engine's step times and output tokens (for the trial)."""
 
@@ -125,6 +137,7 @@ class EpochUpdate:
                 release = getattr(getattr(prev, "runner", None), "release_graphs", None)
                 if release:
                     release()
+                _retire(prev)                            # its quota ends with it
 
     def _threshold(self) -> Optional[str]:
         t, b = self.trial_clock, self.baseline
@@ -154,4 +167,5 @@ class EpochUpdate:
         except Exception:
             pass
         self.previous = None
+        _retire(target)
         self._enter("rolled_back", why)
