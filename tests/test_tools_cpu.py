@@ -419,6 +419,77 @@ def _start_chat_server(role="mixed", key=None):
     return f"http://127.0.0.1:{port}", server, th, eng
 
 
+def test_router_hand_off_legs_have_a_transfer_deadline():
+    """A prefill replica that does not answer within the transfer deadline, and a decode
+    replica that does not take the frames within it, are answered 504 and counted; the
+    router keeps serving."""
+    import json
+    import urllib.error
+    import urllib.request
+    import uvicorn
+    from fastapi import FastAPI
+    from fastapi.responses import Response
+    from uniserve_v1_b200.server.router import create_router_app
+    import asyncio
+    delays = {"prefill": 1.5, "decode": 0.0}
+    fake = FastAPI()
+
+    @fake.post("/internal/prefill")
+    async def prefill():
+        await asyncio.sleep(delays["prefill"])
+        return Response(content=b"frames", media_type="application/octet-stream")
+
+    @fake.post("/internal/decode")
+    async def decode():
+        await asyncio.sleep(delays["decode"])
+        return {"choices": [{"message": {"role": "assistant", "content": "ok"}}]}
+    servers = []
+    ports = [_free_port(), _free_port()]
+    apps = [fake, create_router_app([], prefill_urls=[f"http://127.0.0.1:{ports[0]}"],
+                                    decode_urls=[f"http://127.0.0.1:{ports[0]}"],
+                                    transfer_deadline_s=0.4)]
+    for app, port in zip(apps, ports):
+        srv = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+        th = threading.Thread(target=srv.run, daemon=True)
+        th.start()
+        servers.append((srv, th))
+    for srv, _ in servers:
+        for _ in range(200):
+            if srv.started:
+                break
+            time.sleep(0.05)
+    base = f"http://127.0.0.1:{ports[1]}"
+
+    def post():
+        req = urllib.request.Request(
+            base + "/v1/chat/completions", headers={"Content-Type": "application/json"},
+            data=json.dumps({"model": "m", "messages": [{"role": "user", "content": "x"}]}).encode())
+        try:
+            with urllib.request.urlopen(req, timeout=30) as r:
+                return r.status, json.loads(r.read())
+        except urllib.error.HTTPError as e:
+            return e.code, json.loads(e.read())
+    try:
+        t0 = time.monotonic()
+        code, ans = post()
+        assert code == 504 and "prefill" in ans["error"]["message"] and time.monotonic() - t0 < 1.4
+        delays.update(prefill=0.0, decode=1.5)
+        code, ans = post()
+        assert code == 504 and "decode" in ans["error"]["message"]
+        delays.update(decode=0.0)
+        code, ans = post()
+        assert code == 200 and ans["choices"][0]["message"]["content"] == "ok"
+        with urllib.request.urlopen(base + "/router/stats", timeout=10) as r:
+            st = json.loads(r.read())
+        assert st["deadline_misses"] == 2 and st["transfer_deadline_s"] == 0.4
+        assert all(x.in_flight == 0 for x in apps[1].state.prefill.replicas + apps[1].state.decode.replicas)
+    finally:
+        for srv, th in servers:
+            srv.should_exit = True
+        for srv, th in servers:
+            th.join(timeout=10)
+
+
 def test_router_disaggregates_prefill_and_decode(live_server):
     """A prefill replica and a decode replica behind the router: the answers (plain and
     streamed, greedy and seeded sampling) are those of one replica; the decode replica

@@ -638,6 +638,8 @@ def main(argv=None) -> int:
     r.add_argument("--prefix-aware", action="store_true",
                    help="ask the replicas which of them holds a request's prompt prefix and "
                         "send it there (requests without prompt_cache_key)")
+    r.add_argument("--transfer-deadline", type=float, default=60.0, metavar="SECONDS",
+                   help="time each leg of a prefill -> decode hand-off may take (504 after it)")
     a = ap.parse_args(argv)
     if a.cmd == "serve":
         return serve(a)
@@ -658,7 +660,8 @@ def main(argv=None) -> int:
         uvicorn.run(create_router_app(a.replica, prefill_urls=a.prefill or None,
                                       decode_urls=a.decode or None, program=program,
                                       internal_key=a.internal_key,
-                                      prefix_aware=a.prefix_aware),
+                                      prefix_aware=a.prefix_aware,
+                                      transfer_deadline_s=a.transfer_deadline),
                     host=host or "127.0.0.1", port=int(port), log_level="warning")
         return 0
     if a.cmd == "build":

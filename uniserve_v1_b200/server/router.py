@@ -30,6 +30,7 @@ configs), :1834 (submit_routed); reference project paths.
 """
 from __future__ import annotations
 
+import asyncio
 import hashlib
 import json
 import time
@@ -102,12 +103,16 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
                       decode_urls: Optional[list] = None, program=None,
                       internal_key: Optional[str] = None, prefix_aware: bool = False,
                       probe_timeout_s: float = 0.25, prefix_min_tokens: int = 32,
-                      prefix_slack: int = 4) -> FastAPI:
+                      prefix_slack: int = 4, transfer_deadline_s: float = 60.0) -> FastAPI:
     """``urls``: replicas of role ``mixed``.  With ``prefill_urls`` and ``decode_urls`` chat
     requests are disaggregated: a prefill replica computes the prompt and the first token
     (``/internal/prefill``), its answer - the request's framed state - goes to a decode
     replica (``/internal/decode``), whose stream is relayed to the client.  ``internal_key``
-    is presented on both internal routes; the replicas refuse them without it."""
+    is presented on both internal routes; the replicas refuse them without it.  Both legs of
+    a hand-off have ``transfer_deadline_s`` to complete - the prefill replica to answer with the
+    frames, the decode replica to take them and start its answer; a leg that misses it is
+    answered 504 and counted (``storage_config.transfer_deadline_s`` of the reference's
+    policy package, 60 s by default)."""
     import aiohttp
     router = ReplicaRouter(urls or (list(prefill_urls or []) + list(decode_urls or [])),
                            program=program)
@@ -115,7 +120,15 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
     dec = ReplicaRouter(decode_urls) if decode_urls else None
     app = FastAPI(title="uniserve_v1_b200 replica router")
     app.state.router, app.state.prefill, app.state.decode = router, pre, dec
-    state = {"session": None}
+    state = {"session": None, "deadline_misses": 0}
+    leg = aiohttp.ClientTimeout(total=max(0.001, float(transfer_deadline_s)))
+
+    def _missed(which: str):
+        state["deadline_misses"] += 1
+        return JSONResponse({"error": {
+            "message": f"the {which} replica did not complete its leg of the hand-off within "
+                       f"the transfer deadline ({transfer_deadline_s:g} s)",
+            "type": "timeout"}}, status_code=504)
 
     async def session():
         if state["session"] is None:
@@ -222,9 +235,12 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
         p = pre.pick()
         p.in_flight += 1
         try:
-            async with s.post(p.url + "/internal/prefill", data=body, headers=_internal(req)) as up:
+            async with s.post(p.url + "/internal/prefill", data=body, headers=_internal(req),
+                              timeout=leg) as up:
                 blob, status = await up.read(), up.status
                 ctype = up.headers.get("content-type", "")
+        except asyncio.TimeoutError:
+            return _missed("prefill")
         except aiohttp.ClientConnectionError:
             pre.mark_down(p)
             return JSONResponse({"error": {"message": "no prefill replica is reachable",
@@ -241,7 +257,14 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
                               "handoff": base64.b64encode(blob).decode()})
         hdr = dict(_internal(req), **{"content-type": "application/json"})
         try:
-            up = await s.post(d.url + "/internal/decode", data=payload, headers=hdr)
+            # the deadline covers the delivery and the first byte of the answer; the stream
+            # that follows is the request's own
+            up = await asyncio.wait_for(
+                s.post(d.url + "/internal/decode", data=payload, headers=hdr),
+                timeout=max(0.001, float(transfer_deadline_s)))
+        except asyncio.TimeoutError:
+            d.in_flight -= 1
+            return _missed("decode")
         except aiohttp.ClientConnectionError:
             d.in_flight -= 1
             dec.mark_down(d)
@@ -281,7 +304,9 @@ def create_router_app(urls: list, api_key: Optional[str] = None,
     async def router_stats():
         return {"replicas": router.stats(), "prefix_aware": prefix_aware,
                 "probes": router.probes, "prefix_hits": router.prefix_hits,
-                "program_faults": router.program_faults}
+                "program_faults": router.program_faults,
+                "transfer_deadline_s": transfer_deadline_s,
+                "deadline_misses": state["deadline_misses"]}
 
     @app.api_route("/{path:path}", methods=["GET", "POST", "PUT", "DELETE"])
     async def any_route(path: str, req: Request):
