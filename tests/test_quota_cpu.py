@@ -177,3 +177,23 @@ def test_update_whose_target_does_not_fit_the_quota_is_abandoned():
         assert c.post("/v1/chat/completions", json=body).json()["choices"][0]["message"]["content"] == want
         devices = c.get("/admin/quota").json()["devices"]
         assert isinstance(devices, list)
+
+
+def test_host_tier_leaves_the_nodes_reserve_free(monkeypatch):
+    """The host KV tier is sized as a multiple of the device pool within its own budget and
+    within what the node has beyond the reserve that stays free of KV pages."""
+    from uniserve_v1_b200.engine import engine as E
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    model = Qwen3MoeModel(Qwen3MoeConfig.tiny(), "cpu", torch.float32).init_random(seed=0)
+    per_page = model.kv_bytes_per_page(16)
+    monkeypatch.setattr(E, "_host_available", lambda: float((10 << 30) + 40 * per_page))
+
+    def tier(**kw):
+        eng = E.LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=128,
+                          use_graphs=False, host_kv_ratio=2.0, quota=DeviceQuota(1 << 40, "fake:6"),
+                          **kw)
+        return int(getattr(eng.blocks, "host_slots", 0))
+    assert tier() == 128                                   # no reserve stated: ratio x pool
+    assert tier(host_reserve_gib=1.0) == 128               # plenty beyond the reserve
+    assert tier(host_reserve_gib=10.0) == 40               # what the node has beyond it
+    assert tier(host_reserve_gib=11.0) == 0                # nothing: no host tier

@@ -297,6 +297,7 @@ def serve(args) -> int:
                             host_kv_ratio=(pkg.kv_cache_config.host_ratio
                                            if pkg.kv_cache_config.host_tier else 0.0),
                             host_kv_gib=pkg.kv_cache_config.host_gib,
+                            host_reserve_gib=float(pkg.storage_config.host_reserve_gib),
                             watchdog_timeout=float(pkg.profiling_config.watchdog_timeout),
                             kv_dtype=pkg.kv_cache_config.dtype,
                             # an engine built beside one that serves (the target of an epoch

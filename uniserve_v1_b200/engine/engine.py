@@ -85,6 +85,15 @@ def _weights_on(model, device) -> int:
     return total
 
 
+def _host_available() -> float:
+    """Bytes of host memory that can still be taken without swapping."""
+    try:
+        import psutil
+        return float(psutil.virtual_memory().available)
+    except Exception:                                   # pragma: no cover - psutil is present
+        return float("inf")
+
+
 def _set_tensor(holder, name, value) -> None:
     if isinstance(holder, dict):
         holder[name] = value
@@ -101,7 +110,8 @@ class LLMEngine:
                  watchdog_timeout: float = 150.0, host_kv_pages: int = 0,
                  host_kv_ratio: float = 0.0, host_kv_gib: Optional[float] = None,
                  kv_dtype: Optional[str] = None, pipeline_decode: Optional[bool] = None,
-                 quota=None, quota_strict: bool = False):
+                 quota=None, quota_strict: bool = False,
+                 host_reserve_gib: Optional[float] = None):
         self.model = model
         self.device = model.device
         if kv_dtype in ("fp8", "fp8_e4m3", "e4m3"):
@@ -138,6 +148,10 @@ class LLMEngine:
         if host_kv_pages == 0 and host_kv_ratio > 0:
             # sized as a multiple of the device pool, within a host-memory budget
             budget = (host_kv_gib if host_kv_gib is not None else 16.0) * (1 << 30)
+            if host_reserve_gib is not None:
+                # the node keeps this much host memory free of KV pages
+                # (storage_config.host_reserve_gib of the reference's policy package)
+                budget = min(budget, max(0.0, _host_available() - host_reserve_gib * (1 << 30)))
             per_page = max(1, model.kv_bytes_per_page(page_size))
             host_kv_pages = int(min(host_kv_ratio * num_pages, budget // per_page))
         if host_kv_pages > 0 and enable_prefix_cache:
