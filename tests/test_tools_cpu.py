@@ -918,6 +918,69 @@ def test_a_dead_rank_takes_the_deployment_through_a_relaunch(tmp_path):
                 proc.kill()
 
 
+def test_supervision_backs_off_relaunches_in_a_row(monkeypatch):
+    """The first relaunch after a rank's death is immediate; relaunches that follow one
+    another wait `restart_s`, doubling up to `restart_max_s`; an image that served longer
+    than that starts the count again; `stop` ends a wait."""
+    from uniserve_v1_b200.server import restart as R
+    assert [R.restart_delay(n, 5.0, 300.0) for n in (0, 1, 2, 3, 7, 50)] == \
+        [0.0, 5.0, 10.0, 20.0, 300.0, 300.0]
+
+    class Child:
+        pid = 4242
+
+        def __init__(self):
+            self.code = None
+
+        def poll(self):
+            return self.code
+
+        def terminate(self):
+            self.code = -15
+
+        def wait(self, timeout=None):
+            return self.code
+
+    class Listener:
+        def fileno(self):
+            return 0
+
+    class Sup(R.Supervision):
+        def _exec(self):
+            self.launched = (time.monotonic(), f"{self.relaunches + 1}")
+
+    def run(env, restart_s=0.3, stop_after=None):
+        if env is None:
+            monkeypatch.delenv(R.RESTARTS_ENV, raising=False)
+        else:
+            monkeypatch.setenv(R.RESTARTS_ENV, env)
+        dead, alive, said = Child(), Child(), []
+        sup = Sup([dead, alive], Listener(), ["serve", "pkg"], 0, on_failure=said.append,
+                  period=0.02, restart_s=restart_s, restart_max_s=60.0)
+        sup.launched = None
+        sup.start()
+        t0 = time.monotonic()
+        dead.code = 9
+        if stop_after is not None:
+            time.sleep(stop_after)
+            sup.stop()
+        sup.thread.join(timeout=10)
+        assert said and "rank 1" in said[0] and alive.code == -15
+        return sup, (sup.launched[0] - t0 if sup.launched else None)
+    sup, after = run(None)
+    assert after is not None and after < 0.25 and sup.status()["relaunches"] == 0
+    sup, after = run(f"1:{time.time():.3f}")
+    assert 0.3 <= after < 0.6 and sup.status()["waiting_s"] == 0.3
+    sup, after = run(f"2:{time.time():.3f}")
+    assert 0.6 <= after < 1.0
+    sup, after = run(f"6:{time.time() - 120:.3f}")           # served for two minutes since
+    assert after < 0.25 and sup.relaunches == 0
+    sup, after = run("garbage")
+    assert after < 0.25
+    sup, after = run(f"3:{time.time():.3f}", restart_s=5.0, stop_after=0.2)
+    assert after is None and sup.status()["waiting_s"] == 20.0
+
+
 def test_weights_keeper_handle_records_are_plain_data():
     """A device-memory record carries its IPC handle as JSON of integers, booleans and
     base64 byte strings: it round-trips with its kinds intact, and anything else (a pickle

@@ -410,7 +410,9 @@ def serve(args) -> int:
                     pass
         supervision = Supervision(children, listener, sys.argv[1:], app.state.generation,
                                   on_failure=rank_failed,
-                                  relaunch=os.environ.get("UNISERVE_RELAUNCH", "1") == "1")
+                                  relaunch=os.environ.get("UNISERVE_RELAUNCH", "1") == "1",
+                                  restart_s=float(pkg.storage_config.child_restart_s),
+                                  restart_max_s=float(pkg.storage_config.child_restart_max_s))
         supervision.start()
         app.state.supervision = supervision
     if args.ready_fd is not None:

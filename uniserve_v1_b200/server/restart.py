@@ -255,6 +255,19 @@ def park(standby_fd: int, ready_fd: Optional[int], engine, storage: str,
     return True
 
 
+RESTARTS_ENV = "UNISERVE_RESTARTS"        # "consecutive relaunches:time of the last one"
+
+
+def restart_delay(relaunches: int, restart_s: float, max_s: float) -> float:
+    """Seconds a leader waits before it relaunches its ranks: nothing the first time, then
+    ``restart_s`` doubling with every further relaunch in a row, up to ``max_s``
+    (``storage_config.child_restart_s`` / ``child_restart_max_s`` of the reference's policy
+    package: a deployment whose ranks die at once does not spin)."""
+    if relaunches <= 0:
+        return 0.0
+    return float(min(max_s, restart_s * (2 ** min(relaunches - 1, 30))))
+
+
 class Supervision:
     """The leader of a multi-rank deployment watches the rank processes it started.  When one
     ends while the deployment serves, the deployment cannot go on (its collectives would wait
@@ -262,14 +275,24 @@ class Supervision:
     router moves the requests), stops the other ranks, and - unless ``relaunch`` is off - replaces
     its own image with a fresh ``serve`` of the next generation that inherits the listening
     socket, which starts the ranks again.  Connections that arrive meanwhile wait in the
-    listener's queue.
+    listener's queue.  Relaunches that follow one another within ``restart_max_s`` back off
+    (``restart_delay``); an image that served longer than that starts the count again.
 
     Reference behaviour: crates/daemon/src/supervision (child supervision and relaunch of a
     failure domain; reference project path).
     """
 
     def __init__(self, children: list, listener, argv: list, generation: int, on_failure=None,
-                 relaunch: bool = True, period: float = 0.5):
+                 relaunch: bool = True, period: float = 0.5, restart_s: float = 5.0,
+                 restart_max_s: float = 300.0, clock=time.time):
+        self.restart_s, self.restart_max_s, self.clock = float(restart_s), float(restart_max_s), clock
+        self.relaunches, self.waiting_s = 0, 0.0
+        try:
+            n, _, ts = os.environ.get(RESTARTS_ENV, "").partition(":")
+            if n and clock() - float(ts) < self.restart_max_s:
+                self.relaunches = max(0, int(n))
+        except ValueError:
+            pass
         self.children, self.listener = children, listener
         self.argv = HotRestart._strip(argv, ("--listen-fd", "--ready-fd", "--standby-fd",
                                              "--generation"))
@@ -288,7 +311,8 @@ class Supervision:
     def status(self) -> dict:
         return {"ranks": [{"rank": i + 1, "pid": c.pid, "alive": c.poll() is None}
                           for i, c in enumerate(self.children)],
-                "failed": self.failed, "generation": self.generation}
+                "failed": self.failed, "generation": self.generation,
+                "relaunches": self.relaunches, "waiting_s": self.waiting_s}
 
     def _run(self) -> None:
         while not self._stop.wait(self.period):
@@ -311,6 +335,10 @@ class Supervision:
                     except Exception:
                         other.kill()
                 if self.relaunch and self.listener is not None:
+                    self.waiting_s = restart_delay(self.relaunches, self.restart_s,
+                                                   self.restart_max_s)
+                    if self.waiting_s and self._stop.wait(self.waiting_s):
+                        return                           # stopped while backing off
                     self._exec()
                 return
 
@@ -319,6 +347,7 @@ class Supervision:
         os.set_inheritable(fd, True)
         env = {k: v for k, v in os.environ.items()
                if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT")}
+        env[RESTARTS_ENV] = f"{self.relaunches + 1}:{self.clock():.3f}"
         cmd = [sys.executable, "-m", "uniserve_v1_b200"] + self.argv + \
             ["--listen-fd", str(fd), "--generation", str(self.generation + 1)]
         sys.stdout.flush()
