@@ -464,3 +464,35 @@ def test_mp4_built_in_memory_is_the_file_form_byte_for_byte(tmp_path):
     assert isinstance(mem, bytes) and mem == path.read_bytes()
     assert mem[4:8] == b"ftyp" and b"moov" in mem[-4096:] and b"avcC" in mem
     assert M.write_mp4(y, u, v, 24) == M.write_mp4(y, u, v, 24, None)     # video only
+
+
+def test_media_larger_than_the_deployments_bound_are_refused(tmp_path):
+    """`media_config.max_request_bytes` bounds every medium: a `data:` URL is refused before
+    it is decoded, a `file://` medium by its size; media within the bound load as before."""
+    import base64
+    import io
+    import numpy as np
+    import pytest
+    from PIL import Image
+    from uniserve_v1_b200.server import images
+    buf = io.BytesIO()
+    Image.fromarray((np.arange(64 * 64 * 3) % 251).astype(np.uint8).reshape(64, 64, 3)).save(buf, "PNG")
+    raw = buf.getvalue()
+    url = "data:image/png;base64," + base64.b64encode(raw).decode()
+    (tmp_path / "a.png").write_bytes(raw)
+    images.set_media_directory(str(tmp_path))
+    try:
+        images.set_media_limit(len(raw))
+        assert images.load_image(url).shape == (64, 64, 3)
+        assert images.load_image(f"file://{tmp_path}/a.png").shape == (64, 64, 3)
+        images.set_media_limit(len(raw) - 8)
+        for u in (url, f"file://{tmp_path}/a.png"):
+            with pytest.raises(ValueError, match="larger than the deployment accepts"):
+                images.load_image(u)
+        with pytest.raises(ValueError, match="larger than the deployment accepts"):
+            images.load_video("data:video/mp4;base64," + base64.b64encode(raw).decode())
+        with pytest.raises(ValueError, match="larger than the deployment accepts"):
+            images.load_video(f"file://{tmp_path}/a.png")
+    finally:
+        images.set_media_limit(None)
+        images.set_media_directory(None)

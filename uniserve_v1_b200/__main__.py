@@ -357,7 +357,9 @@ def serve(args) -> int:
     config = uvicorn.Config(app, host=pkg.admin_config.host, port=pkg.admin_config.port or 8000,
                             uds=pkg.admin_config.uds if listener is None else None,
                             fd=listener.fileno() if listener is not None else None,
-                            log_level=(args.log_level_http or "warning"))
+                            log_level=(args.log_level_http or pkg.logging_config.http_level
+                                       or "warning"),
+                            h11_max_incomplete_event_size=int(pkg.server_config.max_request_head))
     server = uvicorn.Server(config)
     standby = None
     if world == 1 and listener is not None:

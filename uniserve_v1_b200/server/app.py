@@ -233,6 +233,7 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
     s.package = package or Package.parse(f'model = "local/{served_model_name}"\n')
     from . import images as _images
     _images.set_media_directory(s.package.media_config.directory)
+    _images.set_media_limit(int(s.package.media_config.max_request_bytes))
     s.served = s.package.served_model_name or served_model_name
     s.tokenizer = tokenizer
     s.template = ChatTemplate(getattr(tokenizer, "chat_template", None)) if tokenizer else None
@@ -305,6 +306,9 @@ def create_app(*, package: Optional[Package] = None, engine=None, tokenizer=None
         cl = request.headers.get("content-length")
         if cl and cl.isdigit() and int(cl) > cfg.max_request_body and not path.startswith("/v1/videos"):
             return _err(413, "request body too large")
+        if cl and cl.isdigit() and path.startswith("/v1/videos") and \
+                int(cl) > int(s.package.media_config.max_request_bytes):
+            return _err(413, "request body too large")       # media routes: their own bound
         generating = path in ("/v1/chat/completions", "/v1/videos/sync")
         if generating and cfg.max_concurrent_requests is not None \
                 and s.inflight >= cfg.max_concurrent_requests:

@@ -25,6 +25,7 @@ import base64
 import io
 import math
 import os
+from typing import Optional
 
 import numpy as np
 import torch
@@ -41,6 +42,22 @@ def set_media_directory(path) -> None:
 
 def media_directory():
     return _MEDIA_DIRECTORY
+
+
+_MEDIA_LIMIT = 256 << 20         # bytes one medium of a request may have
+
+
+def set_media_limit(nbytes) -> None:
+    """The size one medium (an image, a video: a file or a decoded ``data:`` URL) may have
+    (``media_config.max_request_bytes``)."""
+    global _MEDIA_LIMIT
+    _MEDIA_LIMIT = max(1, int(nbytes)) if nbytes else 256 << 20
+
+
+def _decode_data_url(payload: str) -> bytes:
+    if (len(payload) // 4) * 3 > _MEDIA_LIMIT + 3:              # before anything is decoded
+        raise ValueError("the medium is larger than the deployment accepts")
+    return base64.b64decode(payload, validate=True)
 
 
 def resolve_file_url(url: str) -> str:
@@ -63,12 +80,12 @@ def resolve_file_url(url: str) -> str:
     return real
 
 
-def read_file_url(url: str, limit: int = 256 << 20) -> bytes:
+def read_file_url(url: str, limit: Optional[int] = None) -> bytes:
     """Bytes of a ``file://`` medium (``resolve_file_url`` rules; I/O errors become
     ValueError so that a request naming a missing file is an input error)."""
     real = resolve_file_url(url)
     try:
-        if os.path.getsize(real) > limit:
+        if os.path.getsize(real) > (limit if limit is not None else _MEDIA_LIMIT):
             raise ValueError("the file is larger than the deployment accepts")
         with open(real, "rb") as f:
             return f.read()
@@ -83,7 +100,7 @@ def load_image(url: str) -> np.ndarray:
         head, _, payload = url.partition(",")
         if not head.endswith(";base64"):
             raise ValueError("data URLs must be base64-encoded")
-        raw = base64.b64decode(payload, validate=True)
+        raw = _decode_data_url(payload)
     elif url.startswith("file://"):
         raw = read_file_url(url)
     else:
@@ -181,12 +198,14 @@ def load_video(url: str, fps: float = 2.0, max_frames: int = 64):
             raise ValueError("data URLs must be base64-encoded")
         fd, tmp = tempfile.mkstemp(suffix=".mp4")
         with os.fdopen(fd, "wb") as f:
-            f.write(base64.b64decode(payload, validate=True))
+            f.write(_decode_data_url(payload))
         path = tmp
     elif url.startswith("file://"):
         path = resolve_file_url(url)
         if not os.path.isfile(path):
             raise ValueError("cannot read the file: no such file")
+        if os.path.getsize(path) > _MEDIA_LIMIT:
+            raise ValueError("the file is larger than the deployment accepts")
     else:
         raise ValueError("video URLs must be data: or file:// URLs; remote URLs are not fetched")
     try:
