@@ -295,3 +295,31 @@ def test_first_and_last_frame_requests_over_http(tmp_path):
         body["input_references"][0]["url"] = "data:image/png;base64,AAAA"
         bad = c.post("/v1/videos/sync", json=body)
         assert bad.status_code == 400 and bad.json()["error"]["param"] == "input_references"
+
+
+def test_finished_jobs_leave_the_store_by_age_and_by_size():
+    """The job store keeps finished videos for `media_config.job_retention` and within
+    `media_config.job_store_bytes`: older ones go first; jobs that still run stay."""
+    import time
+    import types
+    from uniserve_v1_b200.server.video_service import VideoJob, VideoService
+    cfg, tr, vv, av, enc = _tiny_pipeline()
+    svc = VideoService(tr, vv, av, sizes=["256x256"], max_seconds=5, retention_s=100.0,
+                       store_bytes=2500)
+    plan = types.SimpleNamespace(width=256, height=256, num_frames=8, fps=24, seconds=1.0, seed=0,
+                                 task="t2va")
+    now = time.time()
+
+    def job(age, nbytes, done=True):
+        j = VideoJob("p", plan)
+        if done:
+            j.state, j.completed_at, j.content = "completed", now - age, b"x" * nbytes
+        svc._jobs[j.id] = j
+        return j
+    old = job(500, 10)                    # past the retention
+    a, b, c = job(50, 1000), job(40, 1000), job(30, 1000)
+    running = job(0, 0, done=False)
+    assert svc.get(old.id) is None
+    assert svc.get(a.id) is None          # 3000 bytes > 2500: the oldest content goes
+    assert svc.get(b.id) is b and svc.get(c.id) is c and svc.get(running.id) is running
+    assert [j.id for j in svc.jobs()] == [b.id, c.id, running.id]

@@ -103,6 +103,8 @@ def serve(args) -> int:
         ac = AudioEncoderConfig.tiny(cfg.audio_channels) if tiny \
             else AudioEncoderConfig(latent_channels=cfg.audio_channels)
         service = VideoService(tr, vv, av, max_seconds=15,
+                               retention_s=float(pkg.media_config.job_retention),
+                               store_bytes=int(pkg.media_config.job_store_bytes),
                                video_encoder=VideoVaeEncoder(ec, device).init_random(3),
                                audio_encoder=AudioVaeEncoder(ac, device).init_random(4))
         if rank > 0:
