@@ -615,3 +615,32 @@ def test_persistent_decode_partition_covers_every_tile_and_names_its_partials():
         for (b, hk), written in partial.items():
             assert R.persist_merge_slots(lens, Hkv, n, b, hk) == sorted(written)
             assert len(written) >= 2
+
+
+def test_expert_load_counts_every_live_route():
+    """While the expert load is lent, every forward adds each token's routes to its layer's
+    counters: prompt tokens and generated tokens, k routes each; nothing is counted before it
+    is lent or after it is taken back, and the tokens are the same either way."""
+    from uniserve_v1_b200.engine.engine import LLMEngine
+    from uniserve_v1_b200.engine.types import SamplingParams
+    from uniserve_v1_b200.models.qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+    cfg = Qwen3MoeConfig.tiny()
+    model = Qwen3MoeModel(cfg, "cpu", torch.float32).init_random(seed=0)
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    prompts = [[1, 2, 3, 4, 5, 6, 7], [9, 8, 7]]
+
+    def run():
+        return LLMEngine(model, num_pages=64, max_num_seqs=4, max_model_len=64,
+                         use_graphs=False, enable_prefix_cache=False).generate(prompts, sp)
+    want = run()
+    assert model.expert_load_snapshot() == {}
+    model.enable_expert_load()
+    assert run() == want
+    snap = model.expert_load_snapshot()
+    forwards = sum(len(p) for p in prompts) + len(prompts) * (sp.max_tokens - 1)
+    routed = [i for i, lw in enumerate(model.layers) if not lw.dense]
+    assert sorted(snap) == routed and routed
+    for row in snap.values():
+        assert len(row) == cfg.num_experts and sum(row) == forwards * cfg.num_experts_per_tok
+    model.enable_expert_load(False)
+    assert run() == want and model.expert_load_snapshot() == {}

@@ -276,6 +276,12 @@ def serve(args) -> int:
                                              expert_over_tensor=world // pp > 1)
         cfg, model, ld = _qwen3_model(pkg, directory, device, dtype, ctx,
                                       getattr(args, "weights_socket", None))
+        if pkg.profiling_config.expert_load and hasattr(model, "enable_expert_load") and \
+                (device.type == "cpu" or "expert_order" in pkg.programs
+                 or os.environ.get("US_EXPERT_LOAD") == "1"):
+            # tokens per expert and routed layer (uniserve_expert_tokens_total): on a GPU the
+            # counting costs launches, so it runs while the package's program reads it
+            model.enable_expert_load()
         if ctx is not None and ctx.tp_size > 1 and device.type == "cuda":
             from .parallel.symm import attach_fused
             attach_fused(ctx, device, hidden=cfg.hidden_size)

@@ -208,6 +208,9 @@ class Qwen3MoeModel:
         self.vocab_lo = 0
         self.vocab_hi = cfg.vocab_size
         self._moe_ws: dict = {}
+        # expert load: per routed layer an [experts] int64 counter of the tokens each expert
+        # took, added to by every forward while it is lent (None: nothing is counted)
+        self.expert_load: Optional[dict] = None
 
     # ------------------------------------------------------------- weights --
     def init_random(self, seed: int = 0, std: float = 0.02) -> "Qwen3MoeModel":
@@ -470,6 +473,7 @@ class Qwen3MoeModel:
             live = getattr(self, "_live", None)
             ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob,
                                           live=live)
+            self._count_experts(lw, ids, live)
             self.exchange.dispatch(x, ids, weights, live)
             if self.exchange.is_expert:
                 if lw.fp8 is not None:
@@ -509,6 +513,7 @@ class Qwen3MoeModel:
                                             ws, self.e_lo, self.E_local)
         else:
             ids, weights = F.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
+        self._count_experts(lw, ids, getattr(self, "_live", None) if fused_route else None)
         if lw.fp8 is not None:
             from ..ops.fp8 import moe_experts_fp8
             if ws is not None and ws.block_n > 64:
@@ -771,6 +776,45 @@ class Qwen3MoeModel:
             return t
         return [(plane(), plane()) if self.layer_lo <= i < self.layer_hi else (None, None)
                 for i in range(self.cfg.num_hidden_layers)]
+
+    # ------------------------------------------------------------ expert load --
+    def enable_expert_load(self, on: bool = True) -> None:
+        """Lends (or takes back) the expert load counters: one ``[experts]`` int64 tensor per
+        routed layer, indexed by the model's own expert id, to which every forward adds each
+        live token's routes.  On a GPU this is a few small launches per routed layer and
+        forward, so a deployment counts only while something reads the counters.
+        Reference behaviour: crates/ops/src/moe/load.rs (reference project path)."""
+        self._load_of: dict = {}
+        if not on:
+            self.expert_load = None
+            return
+        self.expert_load = {
+            i: torch.zeros(self.cfg.num_experts, dtype=torch.int64, device=self.device)
+            for i, lw in enumerate(self.layers) if lw is not None and not getattr(lw, "dense", False)}
+        self._load_of = {id(self.layers[i]): t for i, t in self.expert_load.items()}
+
+    def _count_experts(self, lw, ids, live=None) -> None:
+        load = self.expert_load
+        if load is None or ids is None:
+            return
+        counter = self._load_of.get(id(lw))
+        if counter is None:
+            return
+        flat = ids.reshape(-1).to(torch.int64)
+        if live is not None:                       # rows past the live count are padding
+            k = ids.shape[-1]
+            rows = torch.arange(ids.shape[0], device=ids.device).repeat_interleave(k)
+            ones = (rows < live.to(torch.int64)).to(torch.int64)
+        else:
+            ones = torch.ones_like(flat)
+        counter.index_add_(0, flat.clamp_(0, counter.numel() - 1), ones)
+
+    def expert_load_snapshot(self) -> dict:
+        """{layer index: tokens per expert} read back from the device (empty when nothing is
+        counted)."""
+        if not self.expert_load:
+            return {}
+        return {i: t.tolist() for i, t in sorted(self.expert_load.items())}
 
     def kv_bytes_per_page(self, page_size: int = 16) -> int:
         elem = 1 if self.kv_dtype == "fp8" else 2

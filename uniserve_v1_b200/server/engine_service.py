@@ -300,4 +300,11 @@ class EngineService:
                 for site, n in (st.get("blocking_calls") or {}).items():
                     self.obs.set("uniserve_blocking_calls_total", n, {"site": site})
                 self.obs.set("uniserve_blocking_seconds_total", st.get("blocking_seconds", 0.0))
+                snap = getattr(getattr(self.engine, "model", None), "expert_load_snapshot", None)
+                if snap is not None and now - getattr(self, "_last_load", 0.0) > 5.0:
+                    self._last_load = now          # what the expert-order program balances
+                    for layer, row in snap().items():
+                        for e, n in enumerate(row):
+                            self.obs.set("uniserve_expert_tokens_total", n,
+                                         {"layer": str(layer), "expert": str(e)})
                 self.obs.snapshot()
